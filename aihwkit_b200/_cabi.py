@@ -1,0 +1,216 @@
+"""ctypes view of the C ABI declared in ``include/aihwkit_b200.h``.
+
+The shared library ``aihwkit_b200/csrc/libaihwkit_b200.so`` is built in-tree by
+``aihwkit_b200.build`` (nvcc, sm_100a).  There is no CPU compute path and no
+fallback: if the library is missing, :func:`lib` raises and every tile call fails.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libaihwkit_b200.so")
+
+
+class IOParams(C.Structure):
+    """``ab200_io_params`` (IOMetaParameter, src/rpucuda/rpu_pulsed_meta_parameter.h:180-226)."""
+
+    _fields_ = [
+        ("is_perfect", C.c_int32),
+        ("noise_management", C.c_int32),
+        ("bound_management", C.c_int32),
+        ("w_noise_type", C.c_int32),
+        ("bm_test_negative_bound", C.c_int32),
+        ("max_bm_factor", C.c_int32),
+        ("inp_sto_round", C.c_int32),
+        ("out_sto_round", C.c_int32),
+        ("inp_bound", C.c_float),
+        ("inp_res", C.c_float),
+        ("inp_noise", C.c_float),
+        ("out_bound", C.c_float),
+        ("out_res", C.c_float),
+        ("out_noise", C.c_float),
+        ("out_scale", C.c_float),
+        ("w_noise", C.c_float),
+        ("nm_thres", C.c_float),
+        ("max_bm_res", C.c_float),
+        ("inp_asymmetry", C.c_float),
+        ("out_asymmetry", C.c_float),
+    ]
+
+
+class UpdateParams(C.Structure):
+    """``ab200_update_params`` (PulsedUpdateMetaParameter, rpu_pulsed_meta_parameter.h:248-279)."""
+
+    _fields_ = [
+        ("pulse_type", C.c_int32),
+        ("desired_bl", C.c_int32),
+        ("fixed_bl", C.c_int32),
+        ("update_management", C.c_int32),
+        ("update_bl_management", C.c_int32),
+        ("sto_round", C.c_int32),
+        ("um_grad_scale", C.c_float),
+        ("res", C.c_float),
+        ("x_res_implicit", C.c_float),
+        ("d_res_implicit", C.c_float),
+    ]
+
+
+class DeviceParams(C.Structure):
+    """``ab200_device_params`` (PulsedRPUDeviceMetaParameter, rpu_pulsed_device.h:60-110)."""
+
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("construction_seed", C.c_uint32),
+        ("enforce_consistency", C.c_int32),
+        ("dw_min_dtod_log_normal", C.c_int32),
+        ("perfect_bias", C.c_int32),
+        ("dw_min", C.c_float),
+        ("dw_min_dtod", C.c_float),
+        ("dw_min_std", C.c_float),
+        ("w_min", C.c_float),
+        ("w_min_dtod", C.c_float),
+        ("w_max", C.c_float),
+        ("w_max_dtod", C.c_float),
+        ("up_down", C.c_float),
+        ("up_down_dtod", C.c_float),
+        ("ls_mult_noise", C.c_int32),
+        ("ls_allow_increasing_slope", C.c_int32),
+        ("ls_mean_bound_reference", C.c_int32),
+        ("ls_decrease_up", C.c_float),
+        ("ls_decrease_down", C.c_float),
+        ("ls_decrease_up_dtod", C.c_float),
+        ("ls_decrease_down_dtod", C.c_float),
+        ("mult_noise", C.c_int32),
+        ("subtract_symmetry_point", C.c_int32),
+        ("slope_up_dtod", C.c_float),
+        ("slope_down_dtod", C.c_float),
+        ("reference_mean", C.c_float),
+        ("reference_std", C.c_float),
+    ]
+
+
+class TransferParams(C.Structure):
+    """``ab200_transfer_params`` (TransferRPUDeviceMetaParameter, rpu_transfer_device.h:52-75)."""
+
+    _fields_ = [
+        ("gamma", C.c_float),
+        ("transfer_every", C.c_float),
+        ("units_in_mbatch", C.c_int32),
+        ("n_reads_per_transfer", C.c_int32),
+        ("fast_lr", C.c_float),
+        ("transfer_lr", C.c_float),
+        ("scale_transfer_lr", C.c_int32),
+        ("scale_fast_lr", C.c_int32),
+        ("transfer_columns", C.c_int32),
+        ("transfer_io", IOParams),
+        ("transfer_up", UpdateParams),
+    ]
+
+
+class TileConfig(C.Structure):
+    """``ab200_tile_config``."""
+
+    _fields_ = [
+        ("x_size", C.c_int32),
+        ("d_size", C.c_int32),
+        ("forward_io", IOParams),
+        ("backward_io", IOParams),
+        ("update", UpdateParams),
+        ("device_kind", C.c_int32),
+        ("device", DeviceParams * 2),
+        ("transfer", TransferParams),
+        ("seed", C.c_uint64),
+    ]
+
+
+_lib: Optional[C.CDLL] = None
+
+_VP = C.c_void_p
+_FP = C.c_void_p  # float pointers are passed as raw addresses (host or device)
+_I = C.c_int
+
+
+def _declare(lib: C.CDLL) -> None:
+    cfgp = C.POINTER(TileConfig)
+    sig = {
+        "ab200_last_error": (C.c_char_p, []),
+        "ab200_version": (C.c_char_p, []),
+        "ab200_default_io_params": (None, [C.POINTER(IOParams)]),
+        "ab200_default_update_params": (None, [C.POINTER(UpdateParams)]),
+        "ab200_default_device_params": (None, [C.POINTER(DeviceParams), C.c_int32]),
+        "ab200_default_transfer_params": (None, [C.POINTER(TransferParams)]),
+        "ab200_tile_create": (_I, [cfgp, _I, C.POINTER(_VP)]),
+        "ab200_tile_destroy": (_I, [_VP]),
+        "ab200_tile_get_x_size": (_I, [_VP]),
+        "ab200_tile_get_d_size": (_I, [_VP]),
+        "ab200_tile_set_learning_rate": (_I, [_VP, C.c_float]),
+        "ab200_tile_get_learning_rate": (_I, [_VP, C.POINTER(C.c_float)]),
+        "ab200_tile_set_weights": (_I, [_VP, _FP]),
+        "ab200_tile_get_weights": (_I, [_VP, _FP]),
+        "ab200_tile_set_weights_device": (_I, [_VP, _FP, _VP]),
+        "ab200_tile_get_weights_device": (_I, [_VP, _FP, _VP]),
+        "ab200_tile_set_shared_weights": (_I, [_VP, _FP, C.c_uint64]),
+        "ab200_tile_hidden_parameter_count": (_I, [_VP]),
+        "ab200_tile_hidden_parameter_name": (C.c_char_p, [_VP, _I]),
+        "ab200_tile_get_hidden_parameters": (_I, [_VP, _FP]),
+        "ab200_tile_set_hidden_parameters": (_I, [_VP, _FP]),
+        "ab200_tile_forward": (_I, [_VP, _FP, _FP, _I, _I, _I, _I, _I, _VP]),
+        "ab200_tile_backward": (_I, [_VP, _FP, _FP, _I, _I, _I, _I, _VP]),
+        "ab200_tile_update": (_I, [_VP, _FP, _FP, _I, _I, _I, _I, _VP]),
+        "ab200_tile_forward_host": (_I, [_VP, _FP, _FP, _I, _I, _I, _I, _I, _VP]),
+        "ab200_tile_backward_host": (_I, [_VP, _FP, _FP, _I, _I, _I, _I, _VP]),
+        "ab200_tile_update_host": (_I, [_VP, _FP, _FP, _I, _I, _I, _I, _VP]),
+        "ab200_tile_coincidences": (_I, [_VP, _FP, _FP, _FP, _VP]),
+        "ab200_tile_last_bm_stats": (_I, [_VP, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
+        "ab200_tile_set_seed": (_I, [_VP, C.c_uint64]),
+        "ab200_array_create": (_I, [cfgp, _I, _I, _I, _I, _I, _I, _I, C.POINTER(_VP)]),
+        "ab200_array_destroy": (_I, [_VP]),
+        "ab200_array_num_in_splits": (_I, [_VP]),
+        "ab200_array_num_out_splits": (_I, [_VP]),
+        "ab200_array_set_weights": (_I, [_VP, _FP]),
+        "ab200_array_get_weights": (_I, [_VP, _FP]),
+        "ab200_array_forward": (_I, [_VP, _FP, _FP, _I, _I, _VP]),
+        "ab200_array_forward_host": (_I, [_VP, _FP, _FP, _I, _I, _VP]),
+        "ab200_array_set_seed": (_I, [_VP, C.c_uint64]),
+        "ab200_kernel_launch_count": (C.c_uint64, []),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+
+
+#: every symbol ``include/aihwkit_b200.h`` declares (checked by the CPU test-suite)
+def declared_symbols() -> list:
+    import re
+
+    header = os.path.join(os.path.dirname(_HERE), "include", "aihwkit_b200.h")
+    with open(header, "r", encoding="utf-8") as f:
+        text = f.read()
+    return sorted(set(re.findall(r"\b(ab200_[a-z0-9_]+)\s*\(", text)))
+
+
+def lib() -> C.CDLL:
+    """Load the CUDA library; raise loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: run `python -m aihwkit_b200.build` "
+                "(nvcc, sm_100a). There is no CPU fallback for the analog tile."
+            )
+        loaded = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+        _declare(loaded)
+        _lib = loaded
+    return _lib
+
+
+def check(code: int) -> None:
+    """Turn a non-zero return code into the RuntimeError the reference binding raises."""
+    if code != 0:
+        msg = lib().ab200_last_error()
+        raise RuntimeError(msg.decode("utf-8", "replace") if msg else f"ab200 error {code}")

@@ -1,0 +1,464 @@
+"""Mirror of ``aihwkit.simulator.rpu_base.devices`` for the analog-tile hot path.
+
+Class and attribute names are the ones bound in
+``src/aihwkit/simulator/rpu_base_src/rpu_base_devices.cpp:436-960`` and the enums of
+``rpu_base_utils.cpp:55-91``; default values are the C++ member initialisers of the
+reference's meta-parameter structs (``src/rpucuda/rpu_pulsed_meta_parameter.h:180-279``,
+``rpu_pulsed_device.h:60-110``, ``rpu_linearstep_device.h``, ``rpu_softbounds_reference_device.h``,
+``rpu_transfer_device.h:52-75``).  ``AnalogTileParameter.create_array`` is the factory the
+reference exposes at ``rpu_base_devices.cpp:453-467``.
+
+Devices outside the path (ExpStep, PowStep, MixedPrec, OneSided, Buffered/Chopped/Dynamic
+transfer, ...) are not provided; asking for one raises ``RuntimeError``.
+"""
+
+from __future__ import annotations
+
+import enum
+from typing import List
+
+from .. import _cabi
+
+
+class NoiseManagementType(enum.IntEnum):
+    """rpu_pulsed_meta_parameter.h:146-156 (``None`` spelt ``None_``)."""
+
+    None_ = 0
+    AbsMax = 1
+    AbsMaxNPSum = 2
+    Max = 3
+    Constant = 4
+    AverageAbsMax = 5
+
+
+class BoundManagementType(enum.IntEnum):
+    None_ = 0
+    Iterative = 1
+    IterativeWorstCase = 2
+
+
+class WeightNoiseType(enum.IntEnum):
+    None_ = 0
+    AdditiveConstant = 1
+    PCMRead = 2
+
+
+class PulseType(enum.IntEnum):
+    None_ = 0
+    StochasticCompressed = 1
+    Stochastic = 2
+    NoneWithDevice = 3
+    MeanCount = 4
+    DeterministicImplicit = 5
+
+
+class AnalogMVType(enum.IntEnum):
+    Ideal = 0
+    OnePass = 1
+    PosNegSeparate = 2
+    PosNegSeparateDigitalSum = 3
+
+
+for _e in (NoiseManagementType, BoundManagementType, WeightNoiseType, PulseType):
+    # the binding spells the first member "None"; keep that name reachable via getattr
+    _e._member_map_["None"] = _e(0)  # type: ignore[attr-defined]
+
+
+DEVICE_IDEAL = 0
+DEVICE_CONSTANT_STEP = 1
+DEVICE_LINEAR_STEP = 2
+DEVICE_SOFT_BOUNDS = 3
+DEVICE_SOFT_BOUNDS_REFERENCE = 4
+DEVICE_TRANSFER = 5
+
+
+class AnalogTileInputOutputParameter:
+    """IOMetaParameter (rpu_base_devices.cpp:485-519)."""
+
+    _unsupported = {
+        "inp_noise": 0.0,
+        "out_noise_std": 0.0,
+        "ir_drop": 0.0,
+        "out_nonlinearity": 0.0,
+        "out_nonlinearity_std": 0.0,
+        "r_series": 0.0,
+        "v_offset_std": 0.0,
+        "w_read_asymmetry_dtod": 0.0,
+    }
+
+    def __init__(self) -> None:
+        self.is_perfect = False
+        self.mv_type = AnalogMVType.OnePass
+        self.noise_management = NoiseManagementType.AbsMax
+        self.bound_management = BoundManagementType.None_
+        self.w_noise_type = WeightNoiseType.None_
+        self.bm_test_negative_bound = True
+        self.max_bm_factor = 1000
+        self.max_bm_res = 0.25
+        self.inp_sto_round = False
+        self.out_sto_round = False
+        self.inp_bound = 1.0
+        self.inp_res = 1.0 / (2.0**7 - 2.0)
+        self.inp_noise = 0.0
+        self.out_bound = 12.0
+        self.out_res = 1.0 / (2.0**9 - 2.0)
+        self.out_noise = 0.06
+        self.out_noise_std = 0.0
+        self.out_scale = 1.0
+        self.w_noise = 0.0
+        self.nm_thres = 0.0
+        self.nm_assumed_wmax = 0.6
+        self.nm_decay = 1e-3
+        self.inp_asymmetry = 0.0
+        self.out_asymmetry = 0.0
+        self.ir_drop = 0.0
+        self.ir_drop_g_ratio = 5.7143e5
+        self.out_nonlinearity = 0.0
+        self.out_nonlinearity_std = 0.0
+        self.slope_calibration = 0.5
+        self.r_series = 0.0
+        self.v_offset_std = 0.0
+        self.v_offset_w_min = 0.0
+        self.w_read_asymmetry_dtod = 0.0
+
+    def _to_c(self) -> _cabi.IOParams:
+        for name, off in self._unsupported.items():
+            if getattr(self, name) != off:
+                raise RuntimeError(
+                    f"IO parameter '{name}' is not implemented by the B200 analog tile"
+                )
+        mv = int(self.mv_type)
+        if mv not in (int(AnalogMVType.Ideal), int(AnalogMVType.OnePass)):
+            raise RuntimeError("MV type not implemented.")
+        nm = int(self.noise_management)
+        if nm not in (0, 1, 4):
+            raise RuntimeError("Noise Management type not implemented!")
+        if int(self.w_noise_type) == int(WeightNoiseType.PCMRead) and self.w_noise > 0:
+            raise RuntimeError("w_noise_type PCMRead is not implemented by the B200 analog tile")
+        if int(self.bound_management) == int(BoundManagementType.IterativeWorstCase):
+            raise RuntimeError("IterativeWorstCase bound management is not implemented")
+        c = _cabi.IOParams()
+        c.is_perfect = int(bool(self.is_perfect) or mv == int(AnalogMVType.Ideal))
+        c.noise_management = nm
+        c.bound_management = int(self.bound_management)
+        c.w_noise_type = int(self.w_noise_type)
+        c.bm_test_negative_bound = int(bool(self.bm_test_negative_bound))
+        c.max_bm_factor = int(self.max_bm_factor)
+        c.inp_sto_round = int(bool(self.inp_sto_round))
+        c.out_sto_round = int(bool(self.out_sto_round))
+        for name in (
+            "inp_bound", "inp_res", "inp_noise", "out_bound", "out_res", "out_noise", "out_scale",
+            "w_noise", "nm_thres", "max_bm_res", "inp_asymmetry", "out_asymmetry",
+        ):
+            setattr(c, name, float(getattr(self, name)))
+        return c
+
+
+class AnalogTileUpdateParameter:
+    """PulsedUpdateMetaParameter (rpu_base_devices.cpp:469-483)."""
+
+    def __init__(self) -> None:
+        self.fixed_bl = True
+        self.desired_bl = 31
+        self.pulse_type = PulseType.StochasticCompressed
+        self.res = 0.0
+        self.x_res_implicit = 0.0
+        self.d_res_implicit = 0.0
+        self.sto_round = False
+        self.um_reg_scale = 1.0
+        self.um_grad_scale = 1.0
+        self.d_sparsity = False
+        self.update_management = True
+        self.update_bl_management = True
+
+    def _to_c(self) -> _cabi.UpdateParams:
+        pt = int(self.pulse_type)
+        if pt in (int(PulseType.Stochastic), int(PulseType.MeanCount)):
+            raise RuntimeError("PulseType not supported")
+        c = _cabi.UpdateParams()
+        c.pulse_type = pt
+        c.desired_bl = int(self.desired_bl)
+        c.fixed_bl = int(bool(self.fixed_bl))
+        c.update_management = int(bool(self.update_management))
+        c.update_bl_management = int(bool(self.update_bl_management))
+        c.sto_round = int(bool(self.sto_round))
+        c.um_grad_scale = float(self.um_grad_scale)
+        c.res = float(self.res)
+        c.x_res_implicit = float(self.x_res_implicit)
+        c.d_res_implicit = float(self.d_res_implicit)
+        return c
+
+
+class AbstractResistiveDeviceParameter:
+    """AbstractRPUDeviceMetaParameter (rpu_base_devices.cpp:536-539)."""
+
+    _kind = -1
+
+    def __init__(self) -> None:
+        self.construction_seed = 0
+        self.diffusion = 0.0
+        self.lifetime = 0.0
+
+    def calc_weight_granularity(self) -> float:
+        raise RuntimeError("Needs implementation.")
+
+
+class IdealResistiveDeviceParameter(AbstractResistiveDeviceParameter):
+    """SimpleRPUDeviceMetaParameter: floating-point update (rpu_base_devices.cpp:545-552)."""
+
+    _kind = DEVICE_IDEAL
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.reset_std = 0.0
+
+
+class PulsedResistiveDeviceParameter(AbstractResistiveDeviceParameter):
+    """PulsedRPUDeviceMetaParameter (rpu_base_devices.cpp:554-581)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.dw_min = 0.001
+        self.dw_min_dtod = 0.3
+        self.dw_min_std = 0.3
+        self.dw_min_dtod_log_normal = False
+        self.w_min = -0.6
+        self.w_min_dtod = 0.3
+        self.w_max = 0.6
+        self.w_max_dtod = 0.3
+        self.up_down = 0.0
+        self.up_down_dtod = 0.01
+        self.lifetime_dtod = 0.0
+        self.diffusion_dtod = 0.0
+        self.enforce_consistency = False
+        self.perfect_bias = False
+        self.corrupt_devices_prob = 0.0
+        self.corrupt_devices_range = 3.4028234663852886e38
+        self.reset = 0.0
+        self.reset_std = 0.0
+        self.reset_dtod = 0.0
+        self.count_pulses = False
+
+    def calc_weight_granularity(self) -> float:
+        return float(self.dw_min)
+
+    def _fill_base(self, c: _cabi.DeviceParams) -> None:
+        for name, off in (
+            ("lifetime", 0.0), ("diffusion", 0.0), ("corrupt_devices_prob", 0.0), ("reset", 0.0),
+            ("reset_dtod", 0.0),
+        ):
+            if getattr(self, name) != off:
+                raise RuntimeError(
+                    f"device parameter '{name}' is not implemented by the B200 analog tile"
+                )
+        if self.count_pulses:
+            raise RuntimeError("count_pulses is not implemented by the B200 analog tile")
+        c.kind = self._kind
+        c.construction_seed = int(self.construction_seed) & 0xFFFFFFFF
+        c.enforce_consistency = int(bool(self.enforce_consistency))
+        c.dw_min_dtod_log_normal = int(bool(self.dw_min_dtod_log_normal))
+        c.perfect_bias = int(bool(self.perfect_bias))
+        for name in (
+            "dw_min", "dw_min_dtod", "dw_min_std", "w_min", "w_min_dtod", "w_max", "w_max_dtod",
+            "up_down", "up_down_dtod",
+        ):
+            setattr(c, name, float(getattr(self, name)))
+
+    def _to_c(self) -> _cabi.DeviceParams:
+        c = _cabi.DeviceParams()
+        self._fill_base(c)
+        return c
+
+
+class ConstantStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):
+    """rpu_base_devices.cpp:583-600."""
+
+    _kind = DEVICE_CONSTANT_STEP
+
+
+class LinearStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):
+    """rpu_base_devices.cpp:602-631 (``gamma_*`` are the ``ls_decrease_*`` fields)."""
+
+    _kind = DEVICE_LINEAR_STEP
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.gamma_up = 0.0
+        self.gamma_down = 0.0
+        self.gamma_up_dtod = 0.05
+        self.gamma_down_dtod = 0.05
+        self.allow_increasing = False
+        self.mean_bound_reference = True
+        self.mult_noise = True
+        self.write_noise_std = 0.0
+        self.apply_write_noise_on_set = True
+        self.reverse_up = False
+        self.reverse_down = False
+        self.reverse_offset = 0.01
+
+    def _to_c(self) -> _cabi.DeviceParams:
+        if self.write_noise_std != 0.0 or self.reverse_up or self.reverse_down:
+            raise RuntimeError("write noise / reversed slopes are not implemented")
+        c = _cabi.DeviceParams()
+        self._fill_base(c)
+        c.ls_mult_noise = int(bool(self.mult_noise))
+        c.ls_allow_increasing_slope = int(bool(self.allow_increasing))
+        c.ls_mean_bound_reference = int(bool(self.mean_bound_reference))
+        c.ls_decrease_up = float(self.gamma_up)
+        c.ls_decrease_down = float(self.gamma_down)
+        c.ls_decrease_up_dtod = float(self.gamma_up_dtod)
+        c.ls_decrease_down_dtod = float(self.gamma_down_dtod)
+        return c
+
+
+class SoftBoundsResistiveDeviceParameter(LinearStepResistiveDeviceParameter):
+    """SoftBounds = LinearStep with slopes tied to the bounds (rpu_linearstep_device.h:70-83)."""
+
+    _kind = DEVICE_SOFT_BOUNDS
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.gamma_up = 1.0
+        self.gamma_down = 1.0
+        self.gamma_up_dtod = 0.0
+        self.gamma_down_dtod = 0.0
+        self.allow_increasing = False
+        self.mean_bound_reference = False
+
+
+class SoftBoundsReferenceResistiveDeviceParameter(PulsedResistiveDeviceParameter):
+    """rpu_base_devices.cpp:926-950."""
+
+    _kind = DEVICE_SOFT_BOUNDS_REFERENCE
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.slope_up_dtod = 0.0
+        self.slope_down_dtod = 0.0
+        self.reference_mean = 0.0
+        self.reference_std = 0.0
+        self.subtract_symmetry_point = False
+        self.mult_noise = False
+        self.write_noise_std = 0.0
+        self.apply_write_noise_on_set = True
+
+    def _to_c(self) -> _cabi.DeviceParams:
+        if self.write_noise_std != 0.0:
+            raise RuntimeError("write noise is not implemented")
+        c = _cabi.DeviceParams()
+        self._fill_base(c)
+        c.mult_noise = int(bool(self.mult_noise))
+        c.subtract_symmetry_point = int(bool(self.subtract_symmetry_point))
+        c.slope_up_dtod = float(self.slope_up_dtod)
+        c.slope_down_dtod = float(self.slope_down_dtod)
+        c.reference_mean = float(self.reference_mean)
+        c.reference_std = float(self.reference_std)
+        return c
+
+
+class VectorResistiveDeviceParameter(AbstractResistiveDeviceParameter):
+    """VectorRPUDeviceMetaParameter (rpu_base_devices.cpp:686-714); container only."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.gamma_vec: List[float] = []
+        self._vec_par: List[PulsedResistiveDeviceParameter] = []
+
+    def append_parameter(self, parameter: PulsedResistiveDeviceParameter) -> bool:
+        if not isinstance(parameter, PulsedResistiveDeviceParameter):
+            raise RuntimeError("Only pulsed devices can be appended")
+        self._vec_par.append(parameter)
+        return True
+
+    def calc_weight_granularity(self) -> float:
+        return self._vec_par[0].calc_weight_granularity() if self._vec_par else 0.0
+
+
+class TransferResistiveDeviceParameter(VectorResistiveDeviceParameter):
+    """TransferRPUDeviceMetaParameter (rpu_base_devices.cpp:742-776)."""
+
+    _kind = DEVICE_TRANSFER
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.gamma = 0.0
+        self.transfer_every = 1.0
+        self.no_self_transfer = True
+        self.transfer_every_vec: List[float] = []
+        self.units_in_mbatch = False
+        self.n_reads_per_transfer = 1
+        self.with_reset_prob = 0.0
+        self.random_selection = False
+        self.transfer_columns = True
+        self.transfer_lr = 1.0
+        self.fast_lr = 0.0
+        self.transfer_lr_vec: List[float] = []
+        self.scale_transfer_lr = True
+        self.scale_fast_lr = True
+        self.transfer_forward = AnalogTileInputOutputParameter()
+        self.transfer_update = AnalogTileUpdateParameter()
+
+    def _to_c(self) -> _cabi.TransferParams:
+        if len(self._vec_par) != 2:
+            raise RuntimeError("The B200 analog tile implements Transfer with exactly 2 devices")
+        if self.gamma != 0.0 or self.gamma_vec:
+            raise RuntimeError("Only gamma = 0 (fully hidden fast tile) is implemented")
+        if self.with_reset_prob != 0.0 or self.random_selection or not self.transfer_columns:
+            raise RuntimeError("reset / random selection / row transfer are not implemented")
+        if self.transfer_every_vec or self.transfer_lr_vec:
+            raise RuntimeError("per-device transfer vectors are not implemented")
+        c = _cabi.TransferParams()
+        c.gamma = float(self.gamma)
+        c.transfer_every = float(self.transfer_every)
+        c.units_in_mbatch = int(bool(self.units_in_mbatch))
+        c.n_reads_per_transfer = int(self.n_reads_per_transfer)
+        c.fast_lr = float(self.fast_lr)
+        c.transfer_lr = float(self.transfer_lr)
+        c.scale_transfer_lr = int(bool(self.scale_transfer_lr))
+        c.scale_fast_lr = int(bool(self.scale_fast_lr))
+        c.transfer_columns = 1
+        c.transfer_io = self.transfer_forward._to_c()
+        c.transfer_up = self.transfer_update._to_c()
+        return c
+
+
+class AnalogTileParameter:
+    """PulsedMetaParameter (rpu_base_devices.cpp:453-467)."""
+
+    def __init__(self) -> None:
+        self.forward_io = AnalogTileInputOutputParameter()
+        self.backward_io = AnalogTileInputOutputParameter()
+        self.update = AnalogTileUpdateParameter()
+
+    def _config(self, x_size: int, d_size: int, device_par, seed: int = 0) -> _cabi.TileConfig:
+        cfg = _cabi.TileConfig()
+        cfg.x_size = int(x_size)
+        cfg.d_size = int(d_size)
+        cfg.forward_io = self.forward_io._to_c()
+        cfg.backward_io = self.backward_io._to_c()
+        cfg.update = self.update._to_c()
+        cfg.seed = int(seed)
+        kind = getattr(device_par, "_kind", -1)
+        if kind < 0:
+            raise RuntimeError(
+                f"{type(device_par).__name__} is not implemented by the B200 analog tile"
+            )
+        cfg.device_kind = kind
+        if kind == DEVICE_TRANSFER:
+            cfg.transfer = device_par._to_c()
+            cfg.device[0] = device_par._vec_par[0]._to_c()
+            cfg.device[1] = device_par._vec_par[1]._to_c()
+            if device_par.construction_seed:
+                cfg.device[0].construction_seed = int(device_par.construction_seed)
+        elif kind == DEVICE_IDEAL:
+            cfg.device[0].kind = DEVICE_IDEAL
+            cfg.device[0].construction_seed = int(device_par.construction_seed)
+        else:
+            cfg.device[0] = device_par._to_c()
+        return cfg
+
+    def create_array(self, x_size: int, d_size: int, device_par):
+        """Factory for an analog tile (``createRPUArray``, src/rpucuda/rpu_pulsed.cpp:49-56)."""
+        from .tiles import AnalogTile
+
+        return AnalogTile(self._config(x_size, d_size, device_par))

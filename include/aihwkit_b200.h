@@ -1,0 +1,306 @@
+/*
+ * aihwkit_b200 — C ABI of the B200-native analog-tile hot path.
+ *
+ * Every entry point is plain C: opaque handles, raw pointers, sizes and a
+ * CUDA stream passed as `void *` (a `cudaStream_t`; NULL = legacy default
+ * stream). No torch / pybind types cross this boundary.  The functions are the
+ * ones the reference's Python binding (`aihwkit.simulator.rpu_base`) would
+ * bind for the analog tile; each declaration cites the reference interface it
+ * replaces as `file:line` relative to the aihwkit source tree.
+ *
+ * Conventions
+ *  - x_size = tile inputs (columns), d_size = tile outputs (rows), m_batch =
+ *    number of input vectors per call.
+ *  - Host weight matrices at this API are row-major [d_size][x_size]
+ *    (src/rpucuda/rpu.cpp:227-236). On the device the tile keeps fp32 master
+ *    weights as [x_size][d_size] like the reference GPU tile
+ *    (src/rpucuda/cuda/rpucuda.cu:285-299).
+ *  - Activations: "batch first iff *_trans" (src/rpucuda/rpu.h:415-417):
+ *    x_trans == 0 -> X is [m_batch][x_size]; x_trans != 0 -> X is
+ *    [x_size][m_batch]; likewise for D.
+ *  - All entry points return 0 on success. On failure they return a non-zero
+ *    code and ab200_last_error() gives the message the reference would have
+ *    thrown as std::runtime_error (src/rpucuda/utility_functions.h:63-69).
+ *  - There is no CPU compute path: every compute call needs a CUDA device.
+ */
+#ifndef AIHWKIT_B200_H_
+#define AIHWKIT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums: numeric values follow src/rpucuda/rpu_pulsed_meta_parameter.h:146-178 ---- */
+enum ab200_noise_management {
+  AB200_NM_NONE = 0,
+  AB200_NM_ABS_MAX = 1,
+  AB200_NM_ABS_MAX_NP_SUM = 2,
+  AB200_NM_MAX = 3,
+  AB200_NM_CONSTANT = 4,
+  AB200_NM_AVERAGE_ABS_MAX = 5,
+  AB200_NM_AVERAGE_ABS_MAX_SINGLE_VALUE = 6,
+  AB200_NM_ABS_MAX_SINGLE_VALUE = 7
+};
+enum ab200_bound_management {
+  AB200_BM_NONE = 0,
+  AB200_BM_ITERATIVE = 1,
+  AB200_BM_ITERATIVE_WORST_CASE = 2
+};
+enum ab200_w_noise_type {
+  AB200_WNOISE_NONE = 0,
+  AB200_WNOISE_ADDITIVE_CONSTANT = 1,
+  AB200_WNOISE_PCM_READ = 2
+};
+enum ab200_pulse_type {
+  AB200_PULSE_NONE = 0,
+  AB200_PULSE_STOCHASTIC_COMPRESSED = 1,
+  AB200_PULSE_STOCHASTIC = 2,
+  AB200_PULSE_NONE_WITH_DEVICE = 3,
+  AB200_PULSE_MEAN_COUNT = 4,
+  AB200_PULSE_DETERMINISTIC_IMPLICIT = 5
+};
+enum ab200_device_kind {
+  AB200_DEVICE_IDEAL = 0,                 /* SimpleRPUDevice: floating-point update */
+  AB200_DEVICE_CONSTANT_STEP = 1,         /* rpu_constantstep_device.h */
+  AB200_DEVICE_LINEAR_STEP = 2,           /* rpu_linearstep_device.h */
+  AB200_DEVICE_SOFT_BOUNDS = 3,           /* rpu_linearstep_device.h:70-83 */
+  AB200_DEVICE_SOFT_BOUNDS_REFERENCE = 4, /* rpu_softbounds_reference_device.h */
+  AB200_DEVICE_TRANSFER = 5               /* rpu_transfer_device.h (Tiki-Taka) */
+};
+
+/* IOMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:180-226); attribute names as
+ * bound in src/aihwkit/simulator/rpu_base_src/rpu_base_devices.cpp:485-519.
+ * inp_res / out_res are the user-facing values (e.g. 1/126); the library applies
+ * res <- checkRes(res) * 2 * bound exactly once, like initializeForForward
+ * (src/rpucuda/rpu_pulsed_meta_parameter.cpp:26-37,56-57). */
+typedef struct ab200_io_params {
+  int32_t is_perfect;
+  int32_t noise_management; /* enum ab200_noise_management */
+  int32_t bound_management; /* enum ab200_bound_management */
+  int32_t w_noise_type;     /* enum ab200_w_noise_type */
+  int32_t bm_test_negative_bound;
+  int32_t max_bm_factor;
+  int32_t inp_sto_round;
+  int32_t out_sto_round;
+  float inp_bound;
+  float inp_res;
+  float inp_noise;
+  float out_bound;
+  float out_res;
+  float out_noise;
+  float out_scale;
+  float w_noise;
+  float nm_thres;
+  float max_bm_res;
+  float inp_asymmetry;
+  float out_asymmetry;
+} ab200_io_params;
+
+/* PulsedUpdateMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:248-279;
+ * rpu_base_devices.cpp:469-483). */
+typedef struct ab200_update_params {
+  int32_t pulse_type; /* enum ab200_pulse_type */
+  int32_t desired_bl;
+  int32_t fixed_bl;
+  int32_t update_management;
+  int32_t update_bl_management;
+  int32_t sto_round;
+  float um_grad_scale;
+  float res;
+  float x_res_implicit;
+  float d_res_implicit;
+} ab200_update_params;
+
+/* One pulsed device (PulsedRPUDeviceMetaParameter, src/rpucuda/rpu_pulsed_device.h:60-110,
+ * plus the LinearStep / SoftBoundsReference extras: rpu_linearstep_device.h:24-58,
+ * rpu_softbounds_reference_device.h:17-42). */
+typedef struct ab200_device_params {
+  int32_t kind; /* enum ab200_device_kind, one of the single-device kinds */
+  uint32_t construction_seed;
+  int32_t enforce_consistency;
+  int32_t dw_min_dtod_log_normal;
+  int32_t perfect_bias;
+  float dw_min;
+  float dw_min_dtod;
+  float dw_min_std;
+  float w_min;
+  float w_min_dtod;
+  float w_max;
+  float w_max_dtod;
+  float up_down;
+  float up_down_dtod;
+  /* LinearStep / SoftBounds */
+  int32_t ls_mult_noise;
+  int32_t ls_allow_increasing_slope;
+  int32_t ls_mean_bound_reference;
+  float ls_decrease_up;
+  float ls_decrease_down;
+  float ls_decrease_up_dtod;
+  float ls_decrease_down_dtod;
+  /* SoftBoundsReference */
+  int32_t mult_noise;
+  int32_t subtract_symmetry_point;
+  float slope_up_dtod;
+  float slope_down_dtod;
+  float reference_mean;
+  float reference_std;
+} ab200_device_params;
+
+/* TransferRPUDeviceMetaParameter (src/rpucuda/rpu_transfer_device.h:52-75). */
+typedef struct ab200_transfer_params {
+  float gamma;
+  float transfer_every;
+  int32_t units_in_mbatch;
+  int32_t n_reads_per_transfer;
+  float fast_lr;
+  float transfer_lr;
+  int32_t scale_transfer_lr;
+  int32_t scale_fast_lr;
+  int32_t transfer_columns;
+  ab200_io_params transfer_io;
+  ab200_update_params transfer_up;
+} ab200_transfer_params;
+
+/* Everything PulsedMetaParameter::createRPUArray needs
+ * (src/rpucuda/rpu_pulsed.cpp:49-56; rpu_base_devices.cpp:453-467). */
+typedef struct ab200_tile_config {
+  int32_t x_size;
+  int32_t d_size;
+  ab200_io_params forward_io;
+  ab200_io_params backward_io;
+  ab200_update_params update;
+  int32_t device_kind;          /* enum ab200_device_kind */
+  ab200_device_params device[2]; /* [0] only, or fast/slow pair for TRANSFER */
+  ab200_transfer_params transfer;
+  uint64_t seed;                /* Philox key for all run-time noise of this tile */
+} ab200_tile_config;
+
+typedef struct ab200_tile ab200_tile;
+typedef struct ab200_array ab200_array;
+
+/* Message of the last failed call on this thread (never NULL). */
+const char *ab200_last_error(void);
+/* Library version string. */
+const char *ab200_version(void);
+
+/* Fill the structs with the reference's defaults (IOMetaParameter / PulsedUpdateMetaParameter /
+ * PulsedRPUDeviceMetaParameter default member initialisers). */
+void ab200_default_io_params(ab200_io_params *io);
+void ab200_default_update_params(ab200_update_params *up);
+void ab200_default_device_params(ab200_device_params *dp, int32_t kind);
+void ab200_default_transfer_params(ab200_transfer_params *tp);
+
+/* ---- tile life cycle ------------------------------------------------------------------- */
+
+/* Replaces PulsedMetaParameter::createRPUArray + RPUCudaPulsed construction
+ * (src/rpucuda/rpu_pulsed.cpp:49-56, src/rpucuda/cuda/rpucuda_pulsed.cu:69-88): draws the
+ * per-element device parameters on the host, uploads them to `cuda_device`, weights start at 0. */
+int ab200_tile_create(const ab200_tile_config *cfg, int cuda_device, ab200_tile **out);
+int ab200_tile_destroy(ab200_tile *tile);
+
+int ab200_tile_get_x_size(const ab200_tile *tile); /* rpu.h getXSize */
+int ab200_tile_get_d_size(const ab200_tile *tile); /* rpu.h getDSize */
+
+/* RPUSimple::setLearningRate / getLearningRate (src/rpucuda/rpu.h:246-249). */
+int ab200_tile_set_learning_rate(ab200_tile *tile, float lr);
+int ab200_tile_get_learning_rate(const ab200_tile *tile, float *lr);
+
+/* RPUPulsed::setWeights (src/rpucuda/rpu_pulsed.cpp:288-292): host [d][x]; clipped to the
+ * per-element bounds of the device.  RPUSimple::getWeights (src/rpucuda/rpu.cpp:1308-1314). */
+int ab200_tile_set_weights(ab200_tile *tile, const float *w_host);
+int ab200_tile_get_weights(ab200_tile *tile, float *w_host);
+/* Device-resident [x_size][d_size] variants (get_weights_cuda / set_weights_cuda probed by
+ * src/aihwkit/simulator/tiles/base.py:452-453). */
+int ab200_tile_set_weights_device(ab200_tile *tile, const float *w_dev_xd, void *stream);
+int ab200_tile_get_weights_device(ab200_tile *tile, float *w_dev_xd, void *stream);
+/* RPUCudaSimple::setSharedWeights (src/rpucuda/cuda/rpucuda.cu:322-334): alias caller-owned
+ * fp32 [x_size][d_size] device memory as the master weights. `version` is any counter that
+ * changes when the caller modified the buffer (operand caches are rebuilt when (ptr, version)
+ * changes). */
+int ab200_tile_set_shared_weights(ab200_tile *tile, float *w_dev_xd, uint64_t version);
+
+/* Hidden (per-element device) parameters: RPUPulsed::getDeviceParameterNames / getDeviceParameter /
+ * setDeviceParameter (src/rpucuda/rpu_pulsed.cpp:330-380; rpu_base_tiles.cpp:764-825).
+ * Arrays are host [n][d][x]. */
+int ab200_tile_hidden_parameter_count(const ab200_tile *tile);
+const char *ab200_tile_hidden_parameter_name(const ab200_tile *tile, int index);
+int ab200_tile_get_hidden_parameters(ab200_tile *tile, float *out_host);
+int ab200_tile_set_hidden_parameters(ab200_tile *tile, const float *in_host);
+
+/* ---- the hot path ---------------------------------------------------------------------- */
+
+/* RPUSimple::forward (src/rpucuda/rpu.h:418-425; rpu.cpp:509-533) with the IO-managed MVM of
+ * ForwardBackwardPassIOManaged::forwardVector (rpu_forward_backward_pass.cpp:901-988).
+ * x_dev, d_dev: device pointers. bias != 0 appends a constant-1 input (rpu.cpp:636-648). */
+int ab200_tile_forward(ab200_tile *tile, const float *x_dev, float *d_dev, int bias, int m_batch,
+                       int x_trans, int d_trans, int is_test, void *stream);
+/* RPUSimple::backward (rpu.h:426-432; rpu_forward_backward_pass.cpp:991-1027). */
+int ab200_tile_backward(ab200_tile *tile, const float *d_dev, float *x_dev, int bias, int m_batch,
+                        int d_trans, int x_trans, void *stream);
+/* RPUSimple::update (rpu.h:433-439) -> PulsedRPUWeightUpdater::updateVectorWithDevice
+ * (rpu_weight_updater.cpp:198-294) for every sample of the batch, in batch order. */
+int ab200_tile_update(ab200_tile *tile, const float *x_dev, const float *d_dev, int bias,
+                      int m_batch, int x_trans, int d_trans, void *stream);
+
+/* Same three calls with HOST buffers: the library stages them through its own pinned/device
+ * buffers (H2D + kernel + D2H on `stream`, synchronised before returning). These are what a
+ * CPU-tensor caller of the binding reaches (rpu_base_tiles.cpp:405-445, 541-598). */
+int ab200_tile_forward_host(ab200_tile *tile, const float *x_host, float *d_host, int bias,
+                            int m_batch, int x_trans, int d_trans, int is_test, void *stream);
+int ab200_tile_backward_host(ab200_tile *tile, const float *d_host, float *x_host, int bias,
+                             int m_batch, int d_trans, int x_trans, void *stream);
+int ab200_tile_update_host(ab200_tile *tile, const float *x_host, const float *d_host, int bias,
+                           int m_batch, int x_trans, int d_trans, void *stream);
+
+/* Signed coincidence counts of ONE sample for the deterministic pulse types
+ * (DenseBitLineMaker::makeCoincidences, src/rpucuda/dense_bit_line_maker.cpp:266-331):
+ * counts_dev is int32 [d_size][x_size]; positive count = weight decreases. Uses the tile's
+ * update parameters, learning rate and weight granularity; weights are not touched. */
+int ab200_tile_coincidences(ab200_tile *tile, const float *x_dev, const float *d_dev,
+                            int32_t *counts_dev, void *stream);
+
+/* Bound-management statistics of the last forward: number of samples that were re-run at least
+ * once and the largest reduction factor used (rpu_forward_backward_pass.cpp:935-983). */
+int ab200_tile_last_bm_stats(ab200_tile *tile, int32_t *n_rerun_samples, float *max_reduction);
+
+/* Re-key the noise generator (RPUSimple::setRandomSeed, src/rpucuda/rpu.cpp:1516-1520). */
+int ab200_tile_set_seed(ab200_tile *tile, uint64_t seed);
+
+/* ---- mapped-tile layer ----------------------------------------------------------------- */
+
+/* A logical [out_size][in_size] layer split into physical tiles of at most
+ * max_output_size x max_input_size (TileModuleArray, src/aihwkit/simulator/tiles/array.py:43-198;
+ * split rule get_split_sizes :82-97). All tiles share `cfg` (x_size/d_size in cfg are ignored).
+ * Only the in-splits [in_split_begin, in_split_end) are materialised on this GPU, which is how a
+ * rank of a sharded layer owns its share; pass 0 and the total number of in-splits (or -1) for
+ * the whole layer. */
+int ab200_array_create(const ab200_tile_config *cfg, int out_size, int in_size,
+                       int max_output_size, int max_input_size, int in_split_begin,
+                       int in_split_end, int cuda_device, ab200_array **out);
+int ab200_array_destroy(ab200_array *arr);
+int ab200_array_num_in_splits(const ab200_array *arr);
+int ab200_array_num_out_splits(const ab200_array *arr);
+/* Host [out_size][in_size] logical weights (TileModuleArray.set_weights, array.py:112-135);
+ * only the locally owned in-splits are read / written. */
+int ab200_array_set_weights(ab200_array *arr, const float *w_host);
+int ab200_array_get_weights(ab200_array *arr, float *w_host);
+/* TileModuleArray.forward (array.py:155-182): every tile does its own noise management, DAC,
+ * MVM and ADC; results of the in-splits are added after the ADC, out-splits are concatenated.
+ * x_dev is the full [m_batch][in_size] input; y_dev is [m_batch][out_size] and receives the sum
+ * over the locally owned in-splits (the partial sum a sharded rank contributes). */
+int ab200_array_forward(ab200_array *arr, const float *x_dev, float *y_dev, int m_batch,
+                        int is_test, void *stream);
+int ab200_array_forward_host(ab200_array *arr, const float *x_host, float *y_host, int m_batch,
+                             int is_test, void *stream);
+int ab200_array_set_seed(ab200_array *arr, uint64_t seed);
+
+/* Number of kernels this library has launched since it was loaded (all tiles, this process). */
+uint64_t ab200_kernel_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AIHWKIT_B200_H_ */

@@ -1,0 +1,521 @@
+"""TEST INFRASTRUCTURE — numpy restatement of the reference's analog-tile hot path.
+
+This module restates, in fp32 numpy, what the reference CPU tile computes for
+  * the IO-managed forward / backward MVM
+    (src/rpucuda/rpu_forward_backward_pass.cpp:113-178, 571-719, 901-1027),
+  * the pulsed update: update management, pulse generation, coincidences
+    (src/rpucuda/rpu_pulsed_meta_parameter.cpp:153-236,
+     src/rpucuda/sparse_bit_line_maker.cpp:200-353,
+     src/rpucuda/dense_bit_line_maker.cpp:210-331,
+     src/rpucuda/rpu_weight_updater.cpp:198-294),
+  * the device rules ConstantStep / LinearStep(SoftBounds) / SoftBoundsReference
+    (src/rpucuda/rpu_constantstep_device.cpp:28-78, rpu_linearstep_device.cpp:113-164,
+     rpu_softbounds_reference_device.cpp:107-175),
+  * the Tiki-Taka sequencing of TransferRPUDevice (src/rpucuda/rpu_transfer_device.cpp:366-557).
+
+Parity pin: tests/test_oracle_vs_reference.py checks every function here against the compiled
+reference (oracle/_ref, built from the reference's own sources) where that library is present,
+and against the golden vectors in tests/golden/ (generated from the compiled reference by
+tests/golden/make_golden.py) everywhere else.
+
+It is a checker only.  The product (aihwkit_b200) never imports it.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Tuple
+
+import numpy as np
+
+f32 = np.float32
+
+# enum values: src/rpucuda/rpu_pulsed_meta_parameter.h:146-178
+NM_NONE, NM_ABS_MAX, NM_CONSTANT = 0, 1, 4
+BM_NONE, BM_ITERATIVE = 0, 1
+WN_NONE, WN_ADDITIVE_CONSTANT = 0, 1
+PULSE_NONE, PULSE_STOCHASTIC_COMPRESSED, PULSE_DETERMINISTIC_IMPLICIT = 0, 1, 5
+DEV_IDEAL, DEV_CONSTANT_STEP, DEV_LINEAR_STEP, DEV_SOFT_BOUNDS, DEV_SOFT_BOUNDS_REFERENCE = range(5)
+DEV_TRANSFER = 5
+
+
+def _check_res(res: float) -> np.float32:
+    """detail::checkRes (rpu_pulsed_meta_parameter.cpp:26-29)."""
+    r = f32(0.0) if res < 0 else f32(res)
+    return f32(1.0) / r if r > f32(1.0) else r
+
+
+@dataclass
+class IO:
+    """Effective IO parameters after initializeForForward/Backward
+    (rpu_pulsed_meta_parameter.cpp:40-128)."""
+
+    is_perfect: bool = False
+    noise_management: int = NM_ABS_MAX
+    bound_management: int = BM_NONE
+    w_noise_type: int = WN_NONE
+    bm_test_negative_bound: bool = True
+    max_bm_factor: int = 1000
+    max_bm_res: float = 0.25
+    inp_bound: float = 1.0
+    inp_res: float = 1.0 / 126.0
+    out_bound: float = 12.0
+    out_res: float = 1.0 / 510.0
+    out_noise: float = 0.06
+    out_scale: float = 1.0
+    w_noise: float = 0.0
+    nm_thres: float = 0.0
+    res_in: np.float32 = field(default=f32(0), init=False)
+    res_out: np.float32 = field(default=f32(0), init=False)
+
+    def __post_init__(self) -> None:
+        self.finalize()
+
+    def finalize(self, backward: bool = False) -> "IO":
+        self.res_out = f32(_check_res(self.out_res) * f32(2.0) * f32(self.out_bound))
+        self.res_in = f32(_check_res(self.inp_res) * f32(2.0) * f32(self.inp_bound))
+        if self.noise_management == NM_NONE:
+            self.nm_thres = 0.0
+        if self.out_bound <= 0:
+            self.out_bound = math.inf
+        if self.inp_bound <= 0:
+            self.inp_bound = math.inf
+        if backward:
+            self.bound_management = BM_NONE
+        return self
+
+    @staticmethod
+    def from_c(c, backward: bool = False) -> "IO":
+        """Build from an ``ab200_io_params`` ctypes struct."""
+        io = IO(
+            is_perfect=bool(c.is_perfect),
+            noise_management=int(c.noise_management),
+            bound_management=int(c.bound_management),
+            w_noise_type=int(c.w_noise_type),
+            bm_test_negative_bound=bool(c.bm_test_negative_bound),
+            max_bm_factor=int(c.max_bm_factor),
+            max_bm_res=float(c.max_bm_res),
+            inp_bound=float(c.inp_bound),
+            inp_res=float(c.inp_res),
+            out_bound=float(c.out_bound),
+            out_res=float(c.out_res),
+            out_noise=float(c.out_noise),
+            out_scale=float(c.out_scale),
+            w_noise=float(c.w_noise),
+            nm_thres=float(c.nm_thres),
+        )
+        return io.finalize(backward)
+
+
+def quantize(v: np.ndarray, res: np.float32) -> np.ndarray:
+    """getDiscretizedValueSR<false> (utility_functions.h:204-210); rint = ties-to-even."""
+    if res <= 0:
+        return v
+    return (np.rint((v / f32(res)).astype(f32)).astype(f32) * f32(res)).astype(f32)
+
+
+def _nm_scale(v: np.ndarray, io: IO) -> np.ndarray:
+    """computeNoiseManagement, per sample (rpu_forward_backward_pass.cpp:113-178)."""
+    m = v.shape[0]
+    if io.noise_management == NM_NONE:
+        return np.ones(m, f32)
+    if io.noise_management == NM_ABS_MAX:
+        s = np.abs(v).max(axis=1).astype(f32)
+        return np.minimum(s, f32(io.nm_thres)) if io.nm_thres > 0 else s
+    if io.noise_management == NM_CONSTANT:
+        return np.full(m, io.nm_thres if io.nm_thres > 0 else 1.0, f32)
+    raise NotImplementedError("noise management type")
+
+
+def _analog_mv(
+    w_op: np.ndarray, v_in: np.ndarray, scale: np.ndarray, scaling: np.ndarray, io: IO, bm: bool,
+    rng: Optional[np.random.Generator],
+) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """computeAnalogMV, OnePass (rpu_forward_backward_pass.cpp:795-829) for a batch of rows.
+
+    ``w_op`` is [out, in]. Returns (output, bound_test_passed per row, pre-ADC value).
+    """
+    # prepareInput (:571-604)
+    v = np.where(scaling[:, None], (v_in * scale[:, None]).astype(f32), v_in).astype(f32)
+    v = quantize(v, io.res_in)
+    bound = f32(io.inp_bound) if io.inp_bound > 0 else f32(np.inf)
+    v = np.clip(v, -bound, bound).astype(f32)
+    # gemv
+    y = (v @ w_op.T).astype(f32)
+    # applyOutputWeightNoise (:326-352)
+    if io.w_noise_type == WN_ADDITIVE_CONSTANT and io.w_noise > 0 and rng is not None:
+        nrm = np.sqrt((v.astype(np.float64) ** 2).sum(axis=1)).astype(f32)
+        y = (y + (f32(io.w_noise) * nrm)[:, None] * rng.standard_normal(y.shape).astype(f32)).astype(f32)
+    # finalizeOutput (:673-719)
+    if io.out_noise > 0 and rng is not None:
+        y = (y + f32(io.out_noise) * rng.standard_normal(y.shape).astype(f32)).astype(f32)
+    pre_adc = y.copy()
+    y = quantize(y, io.res_out)
+    ob = f32(io.out_bound) if io.out_bound > 0 else f32(np.inf)
+    passed = np.ones(y.shape[0], bool)
+    if bm:
+        hi = y > ob
+        lo = y < -ob
+        passed &= ~hi.any(axis=1)
+        if io.bm_test_negative_bound:
+            passed &= ~lo.any(axis=1)
+    y = np.clip(y, -ob, ob).astype(f32)
+    return y, passed, pre_adc
+
+
+def forward(
+    w: np.ndarray, x: np.ndarray, io: IO, rng: Optional[np.random.Generator] = None,
+    alpha: float = 1.0, return_pre_adc: bool = False,
+):
+    """ForwardBackwardPassIOManaged::forwardVector for every row of ``x``
+    (rpu_forward_backward_pass.cpp:901-988).  ``w`` is [d, x]; ``x`` is [m, x_size].
+    ``rng`` None = all noise off (deterministic regime)."""
+    w = np.asarray(w, f32)
+    x = np.asarray(x, f32)
+    m = x.shape[0]
+    if io.is_perfect:
+        return ((x @ w.T) * f32(io.out_scale * alpha)).astype(f32)
+    s = _nm_scale(x, io)
+    nm = io.noise_management != NM_NONE
+    bm = io.bound_management != BM_NONE
+    out = np.zeros((m, w.shape[0]), f32)
+    pre = np.zeros((m, w.shape[0]), f32)
+    reductions = np.ones(m, f32)
+    zero_rows = nm & (s <= 0)
+    todo = ~zero_rows
+    red = f32(0.5)
+    out_scale = f32(io.out_scale) * f32(alpha)
+    final_scale = np.ones(m, f32)
+    scaling_any = np.zeros(m, bool)
+    while todo.any():
+        red = f32(red * f32(2.0))
+        idx = np.nonzero(todo)[0]
+        scale = np.ones(len(idx), f32)
+        scaling = np.zeros(len(idx), bool)
+        if nm:
+            pos = s[idx] > 0
+            scale = np.where(pos, (f32(1.0) / s[idx]).astype(f32), scale).astype(f32)
+            scaling |= pos
+        if bm:
+            scale = (scale / red).astype(f32)
+            scaling[:] = True
+        y, passed, pre_adc = _analog_mv(w, x[idx], scale, scaling, io, bm, rng)
+        out[idx] = y
+        pre[idx] = pre_adc
+        final_scale[idx] = scale
+        scaling_any[idx] = scaling
+        reductions[idx] = red
+        if bm:
+            stop = (int(red) > io.max_bm_factor) or (io.res_in > 0 and red > f32(io.max_bm_res) / io.res_in)
+            passed = passed | stop
+        else:
+            passed[:] = True
+        todo[idx[passed]] = False
+    apply = scaling_any | (out_scale != f32(1.0))
+    fac = (out_scale / final_scale).astype(f32)
+    out = np.where(apply[:, None], (out * fac[:, None]).astype(f32), out).astype(f32)
+    out[zero_rows] = 0
+    if return_pre_adc:
+        return out, pre, final_scale, reductions
+    return out
+
+
+def backward(
+    w: np.ndarray, d: np.ndarray, io: IO, rng: Optional[np.random.Generator] = None,
+    alpha: float = 1.0, return_pre_adc: bool = False,
+):
+    """ForwardBackwardPassIOManaged::backwardVector (rpu_forward_backward_pass.cpp:991-1027).
+    ``d`` is [m, d_size]; result [m, x_size]."""
+    w = np.asarray(w, f32)
+    d = np.asarray(d, f32)
+    if io.is_perfect:
+        return ((d @ w) * f32(io.out_scale * alpha)).astype(f32)
+    s = _nm_scale(d, io)
+    nm = io.noise_management != NM_NONE
+    scaling = np.full(d.shape[0], nm) & (s > 0)
+    zero_rows = nm & (s <= 0)
+    safe = np.where(s > 0, s, f32(1.0)).astype(f32)
+    scale = (f32(1.0) / safe).astype(f32)
+    y, _, pre = _analog_mv(w.T, d, scale, scaling, io, False, rng)
+    out_scale = f32(io.out_scale) * f32(alpha)
+    apply = scaling | (out_scale != f32(1.0))
+    fac = (out_scale * s).astype(f32)
+    y = np.where(apply[:, None], (y * fac[:, None]).astype(f32), y).astype(f32)
+    y[zero_rows] = 0
+    if return_pre_adc:
+        return y, pre, scale
+    return y
+
+
+# ------------------------------------------------------------------------------------------
+# update
+# ------------------------------------------------------------------------------------------
+
+
+@dataclass
+class Up:
+    """PulsedUpdateMetaParameter after initialize() (rpu_pulsed_meta_parameter.cpp:134-151)."""
+
+    pulse_type: int = PULSE_STOCHASTIC_COMPRESSED
+    desired_bl: int = 31
+    fixed_bl: bool = True
+    update_management: bool = True
+    update_bl_management: bool = True
+    um_grad_scale: float = 1.0
+    res: float = 0.0
+    x_res_implicit: float = 0.0
+    d_res_implicit: float = 0.0
+
+    def __post_init__(self) -> None:
+        self.update_management = self.update_management or self.update_bl_management
+
+    @staticmethod
+    def from_c(c) -> "Up":
+        return Up(
+            int(c.pulse_type), int(c.desired_bl), bool(c.fixed_bl), bool(c.update_management),
+            bool(c.update_bl_management), float(c.um_grad_scale), float(c.res),
+            float(c.x_res_implicit), float(c.d_res_implicit),
+        )
+
+
+def bl_a_b(up: Up, lr: float, dw_min: float, xm: float, dm: float) -> Tuple[int, np.float32, np.float32]:
+    """calculateBlAB + performUpdateManagement in fp32
+    (rpu_pulsed_meta_parameter.cpp:153-236). Returns (BL, A, B); BL == 0 means no update."""
+    lr, dw_min = f32(lr), f32(dw_min)
+    if lr == 0:
+        return 0, f32(0), f32(0)
+    if up.fixed_bl or up.update_bl_management:
+        bl = up.desired_bl
+        a = f32(np.sqrt(f32(lr / f32(dw_min * f32(bl)))))
+        b = a
+    else:
+        if f32(dw_min * f32(up.desired_bl)) < lr:
+            a = b = f32(1.0)
+            bl = max(int(math.ceil(f32(lr / dw_min))), 1)
+        else:
+            bl = up.desired_bl
+            a = f32(np.sqrt(f32(lr / f32(dw_min * f32(bl)))))
+            b = a
+    if up.update_bl_management or up.update_management:
+        xm, dm = f32(xm), f32(dm)
+        if xm == 0 or dm == 0:
+            return 0, f32(1), f32(1)
+        x_val = xm
+        d_val = f32(f32(up.um_grad_scale) * dm)
+        k_val = f32(f32(f32(lr * x_val) * d_val) / dw_min)
+        if up.update_bl_management:
+            bl = int(np.ceil(k_val))
+            bl = min(bl, up.desired_bl)
+            a = f32(np.sqrt(f32(lr / f32(dw_min * f32(bl))))) if bl > 0 else f32(np.inf)
+            b = a
+        if up.update_management:
+            if k_val > f32(up.desired_bl):
+                d_val = f32(d_val * f32(f32(up.desired_bl) / k_val))
+            a = f32(a * f32(np.sqrt(f32(x_val / d_val))))
+            b = f32(b * f32(np.sqrt(f32(d_val / x_val))))
+    return bl, a, b
+
+
+def coincidences_det_implicit(x: np.ndarray, d: np.ndarray, lr: float, dw_min: float, up: Up) -> np.ndarray:
+    """DenseBitLineMaker::makeCoincidences, DeterministicImplicit, one sample
+    (dense_bit_line_maker.cpp:210-264, 266-331). Signed int32 [d, x]; positive = weight decreases."""
+    x = np.asarray(x, f32)
+    d = np.asarray(d, f32)
+    alr = abs(lr)
+    bl, a, b = bl_a_b(up, alr, dw_min, np.abs(x).max(initial=0), np.abs(d).max(initial=0))
+
+    def implicit(v, p, res):
+        vv = -v if lr < 0 else v
+        pp = quantize((np.abs(vv) * f32(p)).astype(f32), f32(res))
+        pp = np.clip(pp, f32(0), f32(1)).astype(f32)
+        return np.where(vv >= 0, pp, -pp).astype(f32)
+
+    xv = implicit(x, b, up.x_res_implicit)
+    dv = implicit(d, a, up.d_res_implicit)
+    dc = (dv * f32(bl)).astype(f32)
+    n = np.rint((dc[:, None] * xv[None, :]).astype(f32)).astype(np.int32)
+    n[dv == 0, :] = 0
+    return n
+
+
+def coincidences_stochastic_compressed(
+    x: np.ndarray, d: np.ndarray, lr: float, dw_min: float, up: Up, rng: np.random.Generator
+) -> np.ndarray:
+    """SparseBitLineMaker::makeCounts (StochasticCompressed) + the coincidence loop of
+    updateVectorWithDevice (sparse_bit_line_maker.cpp:200-238, 288-353;
+    rpu_weight_updater.cpp:236-283), one sample. Signed int32 [d, x]; positive = decrease."""
+    x = np.asarray(x, f32)
+    d = np.asarray(d, f32)
+    alr = abs(lr)
+    lr_sign = -1 if lr < 0 else 1
+    bl, a, b = bl_a_b(up, alr, dw_min, np.abs(x).max(initial=0), np.abs(d).max(initial=0))
+    if bl <= 0:
+        return np.zeros((d.size, x.size), np.int32)
+    px = quantize((np.abs(x) * b).astype(f32), f32(up.res))
+    pd = quantize((np.abs(d) * a).astype(f32), f32(up.res))
+    xb = px[None, :] > rng.random((bl, x.size), dtype=np.float32)
+    db = pd[None, :] > rng.random((bl, d.size), dtype=np.float32)
+    n = db.T.astype(np.int32) @ xb.astype(np.int32)
+    sx = np.where(x > 0, 1, -1)
+    sd = np.where(d > 0, 1, -1) * lr_sign
+    return (n * (sd[:, None] * sx[None, :])).astype(np.int32)
+
+
+@dataclass
+class DeviceArrays:
+    """Per-element device parameters, all [d, x] fp32 (PulsedRPUDevice members,
+    rpu_pulsed_device.cpp:594-733; names as in getDPNames :235-253)."""
+
+    kind: int
+    max_bound: np.ndarray
+    min_bound: np.ndarray
+    dwmin_up: np.ndarray
+    dwmin_down: np.ndarray
+    slope_up: Optional[np.ndarray] = None
+    slope_down: Optional[np.ndarray] = None
+    reference: Optional[np.ndarray] = None
+    dw_min_std: float = 0.0
+    mult_noise: bool = True
+
+    @staticmethod
+    def from_hidden(kind: int, names, hp: np.ndarray, dw_min_std: float, mult_noise: bool, suffix=""):
+        g = {n: hp[i] for i, n in enumerate(names)}
+        kw = dict(
+            kind=kind,
+            max_bound=g["max_bound" + suffix],
+            min_bound=g["min_bound" + suffix],
+            dwmin_up=g["dwmin_up" + suffix],
+            dwmin_down=g["dwmin_down" + suffix],
+            dw_min_std=dw_min_std,
+            mult_noise=mult_noise,
+        )
+        if "slope_up" + suffix in g:
+            kw["slope_up"] = g["slope_up" + suffix]
+            kw["slope_down"] = g["slope_down" + suffix]
+        if "reference" + suffix in g:
+            kw["reference"] = g["reference" + suffix]
+        return DeviceArrays(**kw)
+
+
+def apply_pulses(w: np.ndarray, n_signed: np.ndarray, dev: DeviceArrays,
+                 rng: Optional[np.random.Generator] = None) -> np.ndarray:
+    """Apply |n| pulses of direction sign(n) to every element, one pulse at a time with the clip
+    after each pulse (PULSED_UPDATE_W_LOOP[_DENSE], rpu_pulsed_device.h:450-474).  In place."""
+    n_abs = np.abs(n_signed)
+    down = n_signed > 0
+    std = f32(dev.dw_min_std)
+    for it in range(int(n_abs.max(initial=0))):
+        act = n_abs > it
+        if not act.any():
+            break
+        if std > 0 and rng is not None:
+            xi = (std * rng.standard_normal(w.shape).astype(f32)).astype(f32)
+        else:
+            xi = np.zeros_like(w)
+        if dev.kind == DEV_CONSTANT_STEP:
+            # rpu_constantstep_device.cpp:28-78
+            dw_down = ((f32(1.0) + xi) * dev.dwmin_down).astype(f32)
+            dw_up = ((f32(1.0) + xi) * dev.dwmin_up).astype(f32)
+            wn = np.where(down, w - dw_down, w + dw_up).astype(f32)
+            wn = np.maximum(np.minimum(wn, dev.max_bound), dev.min_bound)
+        elif dev.kind in (DEV_LINEAR_STEP, DEV_SOFT_BOUNDS):
+            # rpu_linearstep_device.cpp:113-164
+            if dev.mult_noise:
+                dn = ((dev.slope_down * w + dev.dwmin_down).astype(f32) * (f32(1.0) + xi)).astype(f32)
+                up_ = ((dev.slope_up * w + dev.dwmin_up).astype(f32) * (f32(1.0) + xi)).astype(f32)
+            else:
+                dn = (dev.slope_down * w + dev.dwmin_down * (f32(1.0) + xi)).astype(f32)
+                up_ = (dev.slope_up * w + dev.dwmin_up * (f32(1.0) + xi)).astype(f32)
+            wn = np.where(down, w - dn, w + up_).astype(f32)
+            wn = np.minimum(np.maximum(wn, dev.min_bound), dev.max_bound)
+        elif dev.kind == DEV_SOFT_BOUNDS_REFERENCE:
+            # rpu_softbounds_reference_device.cpp:107-175
+            wr = (w + dev.reference).astype(f32)
+            with np.errstate(divide="ignore", invalid="ignore"):
+                a_dn = np.where(dev.min_bound < 0, wr / dev.min_bound, f32(0)).astype(f32)
+                a_up = np.where(dev.max_bound > 0, wr / dev.max_bound, f32(0)).astype(f32)
+            if dev.mult_noise:
+                dn = (dev.dwmin_down * (f32(1.0) - a_dn) * (f32(1.0) + xi)).astype(f32)
+                up_ = (dev.dwmin_up * (f32(1.0) - a_up) * (f32(1.0) + xi)).astype(f32)
+            else:
+                dn = (dev.dwmin_down * (f32(1.0) - a_dn + xi)).astype(f32)
+                up_ = (dev.dwmin_up * (f32(1.0) - a_up + xi)).astype(f32)
+            wn = np.where(down, wr - dn, wr + up_).astype(f32)
+            wn = np.minimum(np.maximum(wn, dev.min_bound), dev.max_bound)
+            wn = (wn - dev.reference).astype(f32)
+        else:
+            raise NotImplementedError("device kind")
+        w[act] = wn[act]
+    return w
+
+
+def update(
+    w: np.ndarray, x: np.ndarray, d: np.ndarray, lr: float, dw_min: float, up: Up,
+    dev: DeviceArrays, rng: Optional[np.random.Generator] = None,
+) -> np.ndarray:
+    """RPUPulsed::updateMatrix -> updateVectorWithDevice per sample, in batch order
+    (rpu_pulsed.cpp:559-585; rpu_weight_updater.cpp:198-294).  ``w`` [d, x] is modified in
+    place.  Returns the summed signed coincidence counts (diagnostics)."""
+    total = np.zeros(w.shape, np.int64)
+    if lr == 0:
+        return total
+    for s in range(x.shape[0]):
+        if up.pulse_type == PULSE_DETERMINISTIC_IMPLICIT:
+            n = coincidences_det_implicit(x[s], d[s], lr, dw_min, up)
+        elif up.pulse_type == PULSE_STOCHASTIC_COMPRESSED:
+            assert rng is not None
+            n = coincidences_stochastic_compressed(x[s], d[s], lr, dw_min, up, rng)
+        else:
+            raise NotImplementedError("pulse type")
+        apply_pulses(w, n, dev, rng)
+        total += n
+    return total
+
+
+class TransferOracle:
+    """TransferRPUDevice with two devices and gamma = 0 (fully hidden fast tile):
+    rpu_transfer_device.cpp:366-383 (fast LR), :396-516 (transfer), :522-557 (update hooks)."""
+
+    def __init__(self, w_visible, dev_fast: DeviceArrays, dev_slow: DeviceArrays, tp, up: Up,
+                 dw_min_fast: float, dw_min_slow: float, x_size: int, d_size: int):
+        self.c = w_visible  # slow device == visible weights
+        self.a = np.zeros_like(w_visible)
+        self.dev_fast, self.dev_slow = dev_fast, dev_slow
+        self.tp, self.up = tp, up
+        self.t_io = IO.from_c(tp.transfer_io)
+        self.t_io.noise_management = NM_NONE
+        self.t_io.bound_management = BM_NONE
+        self.t_io.finalize()
+        self.t_up = Up.from_c(tp.transfer_up)
+        self.dw_min_fast, self.dw_min_slow = dw_min_fast, dw_min_slow
+        self.x_size, self.d_size = x_size, d_size
+        self.update_idx = 0
+        self.slice_idx = 0
+
+    def update(self, x, d, lr, rng=None):
+        m = x.shape[0]
+        tp = self.tp
+        pc_lr = (f32(tp.fast_lr) * f32(lr) if tp.scale_fast_lr else f32(tp.fast_lr)) if tp.fast_lr > 0 else f32(lr)
+        if tp.units_in_mbatch:
+            every = max(int(math.ceil(f32(tp.transfer_every) * f32(m))), 0)
+        else:
+            every = max(int(round(tp.transfer_every)), 0)
+        for s in range(m):
+            update(self.a, x[s : s + 1], d[s : s + 1], float(pc_lr), self.dw_min_fast, self.up,
+                   self.dev_fast, rng)
+            self.update_idx += 1
+            if every > 0 and self.update_idx % every == 0:
+                self.transfer(lr, rng)
+
+    def transfer(self, lr, rng=None):
+        tp = self.tp
+        t_lr = f32(tp.transfer_lr) * f32(lr) if tp.scale_transfer_lr else f32(tp.transfer_lr)
+        n = min(tp.n_reads_per_transfer, self.x_size)
+        for k in range(n):
+            col = (self.slice_idx + k) % self.x_size
+            e = np.zeros((1, self.x_size), f32)
+            e[0, col] = 1
+            r = forward(self.a, e, self.t_io, rng, alpha=-1.0)
+            update(self.c, e, r, float(t_lr), self.dw_min_slow, self.t_up, self.dev_slow, rng)
+        self.slice_idx = (self.slice_idx + n) % self.x_size

@@ -1,0 +1,184 @@
+"""TEST INFRASTRUCTURE — ctypes access to the compiled reference CPU tile.
+
+``oracle/_ref/librpu_ref.so`` is the UNMODIFIED reference (``RPU::RPUPulsed<float>``,
+src/rpucuda/rpu_pulsed.h:23-125) behind the thin C wrapper ``oracle/ref_capi.cpp``; it is
+built by ``make -C oracle``.  Only tests, ``smoke()`` and bench.py's CPU-baseline legs may
+import this module; the product never does.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import glob
+import os
+import sys
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(_HERE))
+from aihwkit_b200 import _cabi  # noqa: E402  (struct layouts of include/aihwkit_b200.h)
+
+REF_LIB = os.path.join(_HERE, "_ref", "librpu_ref.so")
+_lib = None
+
+
+def blas_name() -> str:
+    """Which BLAS the reference was linked against when ``_ref`` was built."""
+    path = os.path.join(_HERE, "_ref", "blas.txt")
+    if os.path.exists(path):
+        with open(path, "r", encoding="utf-8") as f:
+            return f.read().strip()
+    return "unknown"
+
+
+def available() -> bool:
+    try:
+        load()
+        return True
+    except OSError:
+        return False
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(REF_LIB):
+        raise OSError(f"{REF_LIB} not built (run `make -C oracle` where the reference is present)")
+    # the bundled OpenBLAS needs its sibling libgfortran / libquadmath, which carry hashed names
+    try:
+        import sysconfig
+
+        libs = os.path.join(sysconfig.get_paths()["purelib"], "opencv_python_headless.libs")
+        for pat in ("libquadmath*.so*", "libgfortran*.so*"):
+            for p in sorted(glob.glob(os.path.join(libs, pat))):
+                C.CDLL(p, mode=C.RTLD_GLOBAL)
+    except OSError:
+        pass
+    lib = C.CDLL(REF_LIB)
+    vp, fp, i = C.c_void_p, C.c_void_p, C.c_int
+    sig = {
+        "ref_last_error": (C.c_char_p, []),
+        "ref_tile_create": (i, [C.POINTER(_cabi.TileConfig), C.POINTER(vp)]),
+        "ref_tile_destroy": (i, [vp]),
+        "ref_tile_set_seed": (i, [vp, C.c_uint64]),
+        "ref_tile_set_learning_rate": (i, [vp, C.c_float]),
+        "ref_tile_set_weights": (i, [vp, fp]),
+        "ref_tile_get_weights": (i, [vp, fp]),
+        "ref_tile_hidden_parameter_count": (i, [vp]),
+        "ref_tile_hidden_parameter_name": (C.c_char_p, [vp, i]),
+        "ref_tile_get_hidden_parameters": (i, [vp, fp]),
+        "ref_tile_set_hidden_parameters": (i, [vp, fp]),
+        "ref_tile_forward": (i, [vp, fp, fp, i, i, i, i, i]),
+        "ref_tile_backward": (i, [vp, fp, fp, i, i, i, i]),
+        "ref_tile_update": (i, [vp, fp, fp, i, i, i, i]),
+        "ref_tile_coincidences": (i, [vp, fp, fp, C.c_float, C.c_float, fp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class RefTile:
+    """The reference CPU analog tile, driven through plain numpy arrays."""
+
+    def __init__(self, cfg: _cabi.TileConfig):
+        self._lib = load()
+        self.x_size, self.d_size = int(cfg.x_size), int(cfg.d_size)
+        h = C.c_void_p()
+        self._ck(self._lib.ref_tile_create(C.byref(cfg), C.byref(h)))
+        self._h = h
+
+    def _ck(self, code: int) -> None:
+        if code:
+            raise RuntimeError(self._lib.ref_last_error().decode())
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.ref_tile_destroy(self._h)
+            self._h = None
+
+    def set_seed(self, seed: int) -> None:
+        self._ck(self._lib.ref_tile_set_seed(self._h, seed))
+
+    def set_learning_rate(self, lr: float) -> None:
+        self._ck(self._lib.ref_tile_set_learning_rate(self._h, lr))
+
+    def set_weights(self, w) -> None:
+        w = _f32(w)
+        assert w.shape == (self.d_size, self.x_size)
+        self._ck(self._lib.ref_tile_set_weights(self._h, w.ctypes.data))
+
+    def get_weights(self) -> np.ndarray:
+        w = np.empty((self.d_size, self.x_size), np.float32)
+        self._ck(self._lib.ref_tile_get_weights(self._h, w.ctypes.data))
+        return w
+
+    def hidden_parameter_names(self) -> list:
+        n = self._lib.ref_tile_hidden_parameter_count(self._h)
+        return [self._lib.ref_tile_hidden_parameter_name(self._h, k).decode() for k in range(n)]
+
+    def get_hidden_parameters(self) -> np.ndarray:
+        n = self._lib.ref_tile_hidden_parameter_count(self._h)
+        out = np.empty((n, self.d_size, self.x_size), np.float32)
+        if n:
+            self._ck(self._lib.ref_tile_get_hidden_parameters(self._h, out.ctypes.data))
+        return out
+
+    def set_hidden_parameters(self, hp) -> None:
+        hp = _f32(hp)
+        self._ck(self._lib.ref_tile_set_hidden_parameters(self._h, hp.ctypes.data))
+
+    def forward(self, x, bias=False, x_trans=False, d_trans=False, is_test=False) -> np.ndarray:
+        x = _f32(x)
+        in_size = x.shape[0] if x_trans else x.shape[-1]
+        m = x.size // in_size
+        out = np.empty((self.d_size, m) if d_trans else (m, self.d_size), np.float32)
+        self._ck(
+            self._lib.ref_tile_forward(
+                self._h, x.ctypes.data, out.ctypes.data, int(bias), m, int(x_trans), int(d_trans),
+                int(is_test),
+            )
+        )
+        return out
+
+    def backward(self, d, bias=False, d_trans=False, x_trans=False) -> np.ndarray:
+        d = _f32(d)
+        dsz = d.shape[0] if d_trans else d.shape[-1]
+        m = d.size // dsz
+        xs = self.x_size - (1 if bias else 0)
+        out = np.empty((xs, m) if x_trans else (m, xs), np.float32)
+        self._ck(
+            self._lib.ref_tile_backward(
+                self._h, d.ctypes.data, out.ctypes.data, int(bias), m, int(d_trans), int(x_trans)
+            )
+        )
+        return out
+
+    def update(self, x, d, bias=False, x_trans=False, d_trans=False) -> None:
+        x, d = _f32(x), _f32(d)
+        in_size = x.shape[0] if x_trans else x.shape[-1]
+        m = x.size // in_size
+        self._ck(
+            self._lib.ref_tile_update(
+                self._h, x.ctypes.data, d.ctypes.data, int(bias), m, int(x_trans), int(d_trans)
+            )
+        )
+
+    def coincidences(self, x, d, lr: float, dw_min: float) -> np.ndarray:
+        """Signed coincidence counts [d, x] of one sample (deterministic pulse types)."""
+        x, d = _f32(x), _f32(d)
+        out = np.empty((self.d_size, self.x_size), np.int32)
+        self._ck(
+            self._lib.ref_tile_coincidences(
+                self._h, x.ctypes.data, d.ctypes.data, lr, dw_min, out.ctypes.data
+            )
+        )
+        return out

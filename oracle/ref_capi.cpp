@@ -1,0 +1,301 @@
+/*
+ * TEST INFRASTRUCTURE — not part of the product.
+ *
+ * C wrapper around the UNMODIFIED reference CPU tile (RPU::RPUPulsed<float>,
+ * src/rpucuda/rpu_pulsed.h:23-125).  It is compiled together with the reference's own
+ * sources, from where they lie, by oracle/Makefile into oracle/_ref/librpu_ref.so.  The
+ * wrapper only translates the flat config structs of include/aihwkit_b200.h into the
+ * reference's meta-parameter classes and forwards calls; all arithmetic is the reference's.
+ *
+ * Used by: tests/ (parity checks, golden-vector generation), bench.py's CPU-baseline legs.
+ */
+#include "aihwkit_b200.h"
+
+#include "dense_bit_line_maker.h"
+#include "rpu_constantstep_device.h"
+#include "rpu_linearstep_device.h"
+#include "rpu_pulsed.h"
+#include "rpu_softbounds_reference_device.h"
+#include "rpu_transfer_device.h"
+
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+using namespace RPU;
+
+namespace {
+thread_local std::string g_err;
+
+void toIO(const ab200_io_params &s, IOMetaParameter<float> &io) {
+  io.is_perfect = s.is_perfect != 0;
+  io.noise_management = (NoiseManagementType)s.noise_management;
+  io.bound_management = (BoundManagementType)s.bound_management;
+  io.w_noise_type = (OutputWeightNoiseType)s.w_noise_type;
+  io.bm_test_negative_bound = s.bm_test_negative_bound != 0;
+  io.max_bm_factor = s.max_bm_factor;
+  io.inp_sto_round = s.inp_sto_round != 0;
+  io.out_sto_round = s.out_sto_round != 0;
+  io.inp_bound = s.inp_bound;
+  io.inp_res = s.inp_res;
+  io.inp_noise = s.inp_noise;
+  io.out_bound = s.out_bound;
+  io.out_res = s.out_res;
+  io.out_noise = s.out_noise;
+  io.out_scale = s.out_scale;
+  io.w_noise = s.w_noise;
+  io.nm_thres = s.nm_thres;
+  io.max_bm_res = s.max_bm_res;
+  io.inp_asymmetry = s.inp_asymmetry;
+  io.out_asymmetry = s.out_asymmetry;
+}
+
+void toUp(const ab200_update_params &s, PulsedUpdateMetaParameter<float> &up) {
+  up.pulse_type = (PulseType)s.pulse_type;
+  up.desired_BL = s.desired_bl;
+  up.fixed_BL = s.fixed_bl != 0;
+  up.update_management = s.update_management != 0;
+  up.update_bl_management = s.update_bl_management != 0;
+  up.sto_round = s.sto_round != 0;
+  up.um_grad_scale = s.um_grad_scale;
+  up.res = s.res;
+  up.x_res_implicit = s.x_res_implicit;
+  up.d_res_implicit = s.d_res_implicit;
+}
+
+void toPulsedBase(const ab200_device_params &s, PulsedRPUDeviceMetaParameter<float> &p) {
+  p.construction_seed = s.construction_seed;
+  p.enforce_consistency = s.enforce_consistency != 0;
+  p.dw_min_dtod_log_normal = s.dw_min_dtod_log_normal != 0;
+  p.perfect_bias = s.perfect_bias != 0;
+  p.dw_min = s.dw_min;
+  p.dw_min_dtod = s.dw_min_dtod;
+  p.dw_min_std = s.dw_min_std;
+  p.w_min = s.w_min;
+  p.w_min_dtod = s.w_min_dtod;
+  p.w_max = s.w_max;
+  p.w_max_dtod = s.w_max_dtod;
+  p.up_down = s.up_down;
+  p.up_down_dtod = s.up_down_dtod;
+}
+
+std::unique_ptr<PulsedRPUDeviceMetaParameter<float>> makeSingle(const ab200_device_params &s) {
+  switch (s.kind) {
+  case AB200_DEVICE_CONSTANT_STEP: {
+    auto p = std::make_unique<ConstantStepRPUDeviceMetaParameter<float>>();
+    toPulsedBase(s, *p);
+    return p;
+  }
+  case AB200_DEVICE_LINEAR_STEP:
+  case AB200_DEVICE_SOFT_BOUNDS: {
+    std::unique_ptr<LinearStepRPUDeviceMetaParameter<float>> p;
+    if (s.kind == AB200_DEVICE_SOFT_BOUNDS) {
+      p = std::make_unique<SoftBoundsRPUDeviceMetaParameter<float>>();
+    } else {
+      p = std::make_unique<LinearStepRPUDeviceMetaParameter<float>>();
+      p->ls_decrease_up = s.ls_decrease_up;
+      p->ls_decrease_down = s.ls_decrease_down;
+      p->ls_decrease_up_dtod = s.ls_decrease_up_dtod;
+      p->ls_decrease_down_dtod = s.ls_decrease_down_dtod;
+      p->ls_allow_increasing_slope = s.ls_allow_increasing_slope != 0;
+      p->ls_mean_bound_reference = s.ls_mean_bound_reference != 0;
+    }
+    p->ls_mult_noise = s.ls_mult_noise != 0;
+    toPulsedBase(s, *p);
+    return p;
+  }
+  case AB200_DEVICE_SOFT_BOUNDS_REFERENCE: {
+    auto p = std::make_unique<SoftBoundsReferenceRPUDeviceMetaParameter<float>>();
+    toPulsedBase(s, *p);
+    p->mult_noise = s.mult_noise != 0;
+    p->subtract_symmetry_point = s.subtract_symmetry_point != 0;
+    p->slope_up_dtod = s.slope_up_dtod;
+    p->slope_down_dtod = s.slope_down_dtod;
+    p->reference_mean = s.reference_mean;
+    p->reference_std = s.reference_std;
+    return p;
+  }
+  default:
+    throw std::runtime_error("ref_capi: unsupported device kind");
+  }
+}
+
+struct RefTile {
+  std::unique_ptr<RPUPulsed<float>> rpu;
+  std::vector<std::string> names;
+  PulsedUpdateMetaParameter<float> up;
+  std::unique_ptr<DenseBitLineMaker<float>> dblm;
+  std::unique_ptr<RNG<float>> rng;
+};
+} // namespace
+
+#define REF_TRY try {
+#define REF_CATCH                                                                                  \
+  }                                                                                                \
+  catch (const std::exception &e) {                                                                \
+    g_err = e.what();                                                                              \
+    return 1;                                                                                      \
+  }                                                                                                \
+  return 0;
+
+extern "C" {
+
+const char *ref_last_error(void) { return g_err.c_str(); }
+
+int ref_tile_create(const ab200_tile_config *cfg, void **out) {
+  REF_TRY
+  PulsedMetaParameter<float> p;
+  toIO(cfg->forward_io, p.f_io);
+  toIO(cfg->backward_io, p.b_io);
+  toUp(cfg->update, p.up);
+
+  std::unique_ptr<AbstractRPUDeviceMetaParameter<float>> dp;
+  if (cfg->device_kind == AB200_DEVICE_TRANSFER) {
+    auto tp = std::make_unique<TransferRPUDeviceMetaParameter<float>>();
+    auto fast = makeSingle(cfg->device[0]);
+    auto slow = makeSingle(cfg->device[1]);
+    tp->appendVecPar(*fast);
+    tp->appendVecPar(*slow);
+    const ab200_transfer_params &t = cfg->transfer;
+    tp->gamma = t.gamma;
+    tp->transfer_every = t.transfer_every;
+    tp->units_in_mbatch = t.units_in_mbatch != 0;
+    tp->n_reads_per_transfer = t.n_reads_per_transfer;
+    tp->fast_lr = t.fast_lr;
+    tp->transfer_lr = t.transfer_lr;
+    tp->scale_transfer_lr = t.scale_transfer_lr != 0;
+    tp->scale_fast_lr = t.scale_fast_lr != 0;
+    tp->transfer_columns = t.transfer_columns != 0;
+    toIO(t.transfer_io, tp->transfer_io);
+    toUp(t.transfer_up, tp->transfer_up);
+    tp->construction_seed = cfg->device[0].construction_seed;
+    dp = std::move(tp);
+  } else if (cfg->device_kind == AB200_DEVICE_IDEAL) {
+    auto sp = std::make_unique<SimpleRPUDeviceMetaParameter<float>>();
+    sp->construction_seed = cfg->device[0].construction_seed;
+    dp = std::move(sp);
+  } else {
+    ab200_device_params d = cfg->device[0];
+    d.kind = cfg->device_kind;
+    dp = makeSingle(d);
+  }
+
+  auto t = new RefTile();
+  t->rpu.reset(p.createRPUArray(cfg->x_size, cfg->d_size, dp.get()));
+  std::vector<float> zeros((size_t)cfg->x_size * cfg->d_size, 0.0f);
+  t->rpu->setWeights(zeros.data());
+  t->rpu->getDeviceParameterNames(t->names);
+  t->up = p.up;
+  t->up.initialize();
+  if (cfg->seed) {
+    t->rpu->setRandomSeed((unsigned int)cfg->seed);
+  }
+  *out = t;
+  REF_CATCH
+}
+
+int ref_tile_destroy(void *h) {
+  delete static_cast<RefTile *>(h);
+  return 0;
+}
+
+int ref_tile_set_seed(void *h, uint64_t seed) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->setRandomSeed((unsigned int)seed);
+  REF_CATCH
+}
+
+int ref_tile_set_learning_rate(void *h, float lr) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->setLearningRate(lr);
+  REF_CATCH
+}
+
+int ref_tile_set_weights(void *h, const float *w) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->setWeights(w);
+  REF_CATCH
+}
+
+int ref_tile_get_weights(void *h, float *w) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->getWeights(w);
+  REF_CATCH
+}
+
+int ref_tile_hidden_parameter_count(void *h) {
+  return (int)static_cast<RefTile *>(h)->names.size();
+}
+
+const char *ref_tile_hidden_parameter_name(void *h, int i) {
+  auto *t = static_cast<RefTile *>(h);
+  if (i < 0 || i >= (int)t->names.size()) {
+    return "";
+  }
+  return t->names[i].c_str();
+}
+
+int ref_tile_get_hidden_parameters(void *h, float *out) {
+  REF_TRY
+  auto *t = static_cast<RefTile *>(h);
+  size_t sz = (size_t)t->rpu->getXSize() * t->rpu->getDSize();
+  std::vector<float *> ptrs(t->names.size());
+  for (size_t i = 0; i < ptrs.size(); i++) {
+    ptrs[i] = out + i * sz;
+  }
+  t->rpu->getDeviceParameter(ptrs);
+  REF_CATCH
+}
+
+int ref_tile_set_hidden_parameters(void *h, const float *in) {
+  REF_TRY
+  auto *t = static_cast<RefTile *>(h);
+  size_t sz = (size_t)t->rpu->getXSize() * t->rpu->getDSize();
+  std::vector<float *> ptrs(t->names.size());
+  for (size_t i = 0; i < ptrs.size(); i++) {
+    ptrs[i] = const_cast<float *>(in) + i * sz;
+  }
+  t->rpu->setDeviceParameter(ptrs);
+  REF_CATCH
+}
+
+int ref_tile_forward(
+    void *h, const float *x, float *d, int bias, int m, int x_trans, int d_trans, int is_test) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->forward(x, d, bias != 0, m, x_trans != 0, d_trans != 0,
+                                           is_test != 0);
+  REF_CATCH
+}
+
+int ref_tile_backward(void *h, const float *d, float *x, int bias, int m, int d_trans, int x_trans) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->backward(d, x, bias != 0, m, d_trans != 0, x_trans != 0);
+  REF_CATCH
+}
+
+int ref_tile_update(
+    void *h, const float *x, const float *d, int bias, int m, int x_trans, int d_trans) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->update(x, d, bias != 0, m, x_trans != 0, d_trans != 0);
+  REF_CATCH
+}
+
+/* DenseBitLineMaker<float>::makeCoincidences (src/rpucuda/dense_bit_line_maker.cpp:266-331):
+   signed counts [d][x] of one sample for MeanCount / DeterministicImplicit. */
+int ref_tile_coincidences(void *h, const float *x, const float *d, float lr, float dw_min,
+                          int32_t *counts) {
+  REF_TRY
+  auto *t = static_cast<RefTile *>(h);
+  int xs = t->rpu->getXSize(), ds = t->rpu->getDSize();
+  if (!t->dblm) {
+    t->dblm = std::make_unique<DenseBitLineMaker<float>>(xs, ds);
+    t->rng = std::make_unique<RNG<float>>(1);
+  }
+  int xnoz = 0, dnoz = 0;
+  int *c = t->dblm->makeCoincidences(x, 1, xnoz, d, 1, dnoz, t->rng.get(), lr, dw_min, t->up);
+  std::memcpy(counts, c, sizeof(int) * (size_t)xs * ds);
+  REF_CATCH
+}
+
+} // extern "C"
