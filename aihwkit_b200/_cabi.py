@@ -145,6 +145,7 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_default_transfer_params": (None, [C.POINTER(TransferParams)]),
         "ab200_tile_create": (_I, [cfgp, _I, C.POINTER(_VP)]),
         "ab200_tile_destroy": (_I, [_VP]),
+        "ab200_tile_to_device": (_I, [_VP, _I]),
         "ab200_tile_get_x_size": (_I, [_VP]),
         "ab200_tile_get_d_size": (_I, [_VP]),
         "ab200_tile_set_learning_rate": (_I, [_VP, C.c_float]),

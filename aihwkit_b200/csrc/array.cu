@@ -1,0 +1,156 @@
+#include "array.h"
+
+#include <cstring>
+
+namespace ab200 {
+
+// TileModuleArray.get_split_sizes (src/aihwkit/simulator/tiles/array.py:82-97)
+std::vector<int> splitSizes(int size, int split_max) {
+  if (split_max <= 0) {
+    return {size};
+  }
+  int n = (size + split_max - 1) / split_max;
+  int base = size / n, extra = size % n;
+  std::vector<int> out(n);
+  for (int i = 0; i < n; i++) {
+    out[i] = base + (i < extra ? 1 : 0);
+  }
+  return out;
+}
+
+static uint64_t tileSeed(uint64_t seed, int in_idx, int out_idx) {
+  // the key depends on the GLOBAL tile coordinates only, so a sharded layer draws the same noise
+  // no matter how many ranks it is spread over
+  uint64_t z = seed + 0x9E3779B97F4A7C15ull * (uint64_t)(1 + in_idx * 4099 + out_idx);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return z ? z : 1;
+}
+
+TileArray::TileArray(const ab200_tile_config &cfg, int out_size, int in_size, int max_out,
+                     int max_in, int in_begin, int in_end, int cuda_device)
+    : out_size_(out_size), in_size_(in_size), device_(cuda_device) {
+  if (out_size <= 0 || in_size <= 0) {
+    AB200_FATAL("array sizes must be positive");
+  }
+  in_sizes_ = splitSizes(in_size, max_in);
+  out_sizes_ = splitSizes(out_size, max_out);
+  int off = 0;
+  for (int v : in_sizes_) {
+    in_off_.push_back(off);
+    off += v;
+  }
+  off = 0;
+  for (int v : out_sizes_) {
+    out_off_.push_back(off);
+    off += v;
+  }
+  if (in_end < 0) {
+    in_end = (int)in_sizes_.size();
+  }
+  if (in_begin < 0 || in_begin > in_end || in_end > (int)in_sizes_.size()) {
+    AB200_FATAL("array: invalid in-split range [" << in_begin << ", " << in_end << ")");
+  }
+  in_begin_ = in_begin;
+  in_end_ = in_end;
+  uint64_t seed = cfg.seed ? cfg.seed : 0x1234567ull;
+  for (int ii = in_begin_; ii < in_end_; ii++) {
+    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
+      ab200_tile_config c = cfg;
+      c.x_size = in_sizes_[ii];
+      c.d_size = out_sizes_[oi];
+      c.seed = tileSeed(seed, ii, oi);
+      if (c.device[0].construction_seed) {
+        c.device[0].construction_seed += (uint32_t)(ii * 4099 + oi);
+      }
+      tiles_.emplace_back(new Tile(c, cuda_device));
+    }
+  }
+}
+
+TileArray::~TileArray() {
+  cudaFree(stage_dev_);
+  cudaFreeHost(stage_pinned_);
+}
+
+void TileArray::setSeed(uint64_t seed) {
+  for (int ii = in_begin_; ii < in_end_; ii++) {
+    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
+      tile(ii - in_begin_, oi).setSeed(tileSeed(seed, ii, oi));
+    }
+  }
+}
+
+void TileArray::setWeights(const float *w_host) {
+  std::vector<float> buf;
+  for (int ii = in_begin_; ii < in_end_; ii++) {
+    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
+      int xs = in_sizes_[ii], ds = out_sizes_[oi];
+      buf.resize((size_t)xs * ds);
+      for (int r = 0; r < ds; r++) {
+        std::memcpy(&buf[(size_t)r * xs],
+                    w_host + (size_t)(out_off_[oi] + r) * in_size_ + in_off_[ii],
+                    (size_t)xs * sizeof(float));
+      }
+      tile(ii - in_begin_, oi).setWeights(buf.data());
+    }
+  }
+}
+
+void TileArray::getWeights(float *w_host) {
+  std::vector<float> buf;
+  for (int ii = in_begin_; ii < in_end_; ii++) {
+    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
+      int xs = in_sizes_[ii], ds = out_sizes_[oi];
+      buf.resize((size_t)xs * ds);
+      tile(ii - in_begin_, oi).getWeights(buf.data());
+      for (int r = 0; r < ds; r++) {
+        std::memcpy(w_host + (size_t)(out_off_[oi] + r) * in_size_ + in_off_[ii],
+                    &buf[(size_t)r * xs], (size_t)xs * sizeof(float));
+      }
+    }
+  }
+}
+
+// TileModuleArray.forward (array.py:155-182): per-tile analog MVM, sum over in-splits after each
+// tile's ADC, concatenation over out-splits.
+void TileArray::forward(const float *x, float *y, int m, bool is_test, cudaStream_t s) {
+  (void)is_test;
+  if (m <= 0) {
+    return;
+  }
+  if (in_begin_ == in_end_) {
+    AB200_CUDA(cudaMemsetAsync(y, 0, (size_t)m * out_size_ * sizeof(float), s));
+    return;
+  }
+  for (int ii = in_begin_; ii < in_end_; ii++) {
+    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
+      tile(ii - in_begin_, oi)
+          .forwardStrided(x + in_off_[ii], in_size_, y + out_off_[oi], out_size_, m,
+                          /*accumulate=*/ii != in_begin_, 0, s);
+    }
+  }
+}
+
+void TileArray::forwardHost(const float *x, float *y, int m, bool is_test, cudaStream_t s) {
+  AB200_CUDA(cudaSetDevice(device_));
+  const size_t nx = (size_t)m * in_size_, ny = (size_t)m * out_size_;
+  if (nx + ny > stage_floats_) {
+    AB200_CUDA(cudaDeviceSynchronize());
+    cudaFree(stage_dev_);
+    cudaFreeHost(stage_pinned_);
+    AB200_CUDA(cudaMalloc(&stage_dev_, (nx + ny) * sizeof(float)));
+    AB200_CUDA(cudaMallocHost(&stage_pinned_, (nx + ny) * sizeof(float)));
+    stage_floats_ = nx + ny;
+  }
+  std::memcpy(stage_pinned_, x, nx * sizeof(float));
+  AB200_CUDA(cudaMemcpyAsync(stage_dev_, stage_pinned_, nx * sizeof(float), cudaMemcpyHostToDevice, s));
+  forward(stage_dev_, stage_dev_ + nx, m, is_test, s);
+  AB200_CUDA(cudaMemcpyAsync(stage_pinned_ + nx, stage_dev_ + nx, ny * sizeof(float),
+                             cudaMemcpyDeviceToHost, s));
+  AB200_CUDA(cudaStreamSynchronize(s));
+  std::memcpy(y, stage_pinned_ + nx, ny * sizeof(float));
+}
+
+} // namespace ab200

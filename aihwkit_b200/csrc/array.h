@@ -1,0 +1,37 @@
+// Mapped-tile layer: a logical [out_size][in_size] weight split into physical tiles
+// (TileModuleArray, src/aihwkit/simulator/tiles/array.py:30-198).
+#pragma once
+
+#include "tile.h"
+
+#include <memory>
+#include <vector>
+
+namespace ab200 {
+
+std::vector<int> splitSizes(int size, int split_max);
+
+class TileArray {
+public:
+  TileArray(const ab200_tile_config &cfg, int out_size, int in_size, int max_out, int max_in,
+            int in_begin, int in_end, int cuda_device);
+  ~TileArray();
+  int numInSplits() const { return (int)in_sizes_.size(); }
+  int numOutSplits() const { return (int)out_sizes_.size(); }
+  void setWeights(const float *w_host);
+  void getWeights(float *w_host);
+  void forward(const float *x, float *y, int m, bool is_test, cudaStream_t s);
+  void forwardHost(const float *x, float *y, int m, bool is_test, cudaStream_t s);
+  void setSeed(uint64_t seed);
+
+private:
+  Tile &tile(int in_local, int out_idx) { return *tiles_[(size_t)in_local * out_sizes_.size() + out_idx]; }
+  int out_size_, in_size_, device_;
+  std::vector<int> in_sizes_, out_sizes_, in_off_, out_off_;
+  int in_begin_, in_end_;
+  std::vector<std::unique_ptr<Tile>> tiles_;
+  float *stage_dev_ = nullptr, *stage_pinned_ = nullptr;
+  size_t stage_floats_ = 0;
+};
+
+} // namespace ab200

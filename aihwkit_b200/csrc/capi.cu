@@ -1,0 +1,328 @@
+// extern "C" boundary of the library (declared in include/aihwkit_b200.h): translates C++
+// exceptions into return codes + ab200_last_error(), like the reference's binding turns
+// std::runtime_error into Python RuntimeError.
+#include "array.h"
+#include "tile.h"
+
+#include <cstring>
+
+namespace ab200 {
+uint64_t launchCount();
+}
+
+using ab200::Tile;
+using ab200::TileArray;
+
+static thread_local std::string g_error;
+
+#define AB200_TRY try {
+#define AB200_CATCH                                                                                \
+  }                                                                                                \
+  catch (const std::exception &e) {                                                                \
+    g_error = e.what();                                                                            \
+    return 1;                                                                                      \
+  }                                                                                                \
+  catch (...) {                                                                                    \
+    g_error = "unknown error";                                                                     \
+    return 1;                                                                                      \
+  }                                                                                                \
+  return 0;
+
+static Tile *T(ab200_tile *t) {
+  if (!t) {
+    AB200_FATAL("null tile handle");
+  }
+  return reinterpret_cast<Tile *>(t);
+}
+static const Tile *T(const ab200_tile *t) {
+  if (!t) {
+    AB200_FATAL("null tile handle");
+  }
+  return reinterpret_cast<const Tile *>(t);
+}
+static TileArray *A(ab200_array *a) {
+  if (!a) {
+    AB200_FATAL("null array handle");
+  }
+  return reinterpret_cast<TileArray *>(a);
+}
+
+extern "C" {
+
+const char *ab200_last_error(void) { return g_error.c_str(); }
+const char *ab200_version(void) { return "aihwkit_b200 0.1.0 (sm_100a)"; }
+
+void ab200_default_io_params(ab200_io_params *io) {
+  std::memset(io, 0, sizeof(*io));
+  io->noise_management = AB200_NM_ABS_MAX;
+  io->bound_management = AB200_BM_NONE;
+  io->w_noise_type = AB200_WNOISE_NONE;
+  io->bm_test_negative_bound = 1;
+  io->max_bm_factor = 1000;
+  io->inp_bound = 1.0f;
+  io->inp_res = 1.0f / 126.0f;
+  io->out_bound = 12.0f;
+  io->out_res = 1.0f / 510.0f;
+  io->out_noise = 0.06f;
+  io->out_scale = 1.0f;
+  io->max_bm_res = 0.25f;
+}
+
+void ab200_default_update_params(ab200_update_params *up) {
+  std::memset(up, 0, sizeof(*up));
+  up->pulse_type = AB200_PULSE_STOCHASTIC_COMPRESSED;
+  up->desired_bl = 31;
+  up->fixed_bl = 1;
+  up->update_management = 1;
+  up->update_bl_management = 1;
+  up->um_grad_scale = 1.0f;
+}
+
+void ab200_default_device_params(ab200_device_params *dp, int32_t kind) {
+  std::memset(dp, 0, sizeof(*dp));
+  dp->kind = kind;
+  dp->dw_min = 0.001f;
+  dp->dw_min_dtod = 0.3f;
+  dp->dw_min_std = 0.3f;
+  dp->w_min = -0.6f;
+  dp->w_min_dtod = 0.3f;
+  dp->w_max = 0.6f;
+  dp->w_max_dtod = 0.3f;
+  dp->up_down_dtod = 0.01f;
+  dp->ls_mult_noise = 1;
+  dp->ls_mean_bound_reference = 1;
+  dp->ls_decrease_up_dtod = 0.05f;
+  dp->ls_decrease_down_dtod = 0.05f;
+  if (kind == AB200_DEVICE_SOFT_BOUNDS) {
+    dp->ls_decrease_up = dp->ls_decrease_down = 1.0f;
+    dp->ls_decrease_up_dtod = dp->ls_decrease_down_dtod = 0.0f;
+    dp->ls_mean_bound_reference = 0;
+  }
+}
+
+void ab200_default_transfer_params(ab200_transfer_params *tp) {
+  std::memset(tp, 0, sizeof(*tp));
+  tp->transfer_every = 1.0f;
+  tp->n_reads_per_transfer = 1;
+  tp->transfer_lr = 1.0f;
+  tp->scale_transfer_lr = 1;
+  tp->scale_fast_lr = 1;
+  tp->transfer_columns = 1;
+  ab200_default_io_params(&tp->transfer_io);
+  ab200_default_update_params(&tp->transfer_up);
+}
+
+int ab200_tile_create(const ab200_tile_config *cfg, int cuda_device, ab200_tile **out) {
+  AB200_TRY
+  if (!cfg || !out) {
+    AB200_FATAL("null argument");
+  }
+  *out = reinterpret_cast<ab200_tile *>(new Tile(*cfg, cuda_device));
+  AB200_CATCH
+}
+
+int ab200_tile_destroy(ab200_tile *tile) {
+  AB200_TRY
+  delete reinterpret_cast<Tile *>(tile);
+  AB200_CATCH
+}
+
+int ab200_tile_to_device(ab200_tile *tile, int cuda_device) {
+  AB200_TRY
+  T(tile)->toDevice(cuda_device);
+  AB200_CATCH
+}
+
+int ab200_tile_get_x_size(const ab200_tile *tile) { return tile ? T(tile)->xSize() : -1; }
+int ab200_tile_get_d_size(const ab200_tile *tile) { return tile ? T(tile)->dSize() : -1; }
+
+int ab200_tile_set_learning_rate(ab200_tile *tile, float lr) {
+  AB200_TRY
+  T(tile)->setLearningRate(lr);
+  AB200_CATCH
+}
+int ab200_tile_get_learning_rate(const ab200_tile *tile, float *lr) {
+  AB200_TRY
+  *lr = T(tile)->learningRate();
+  AB200_CATCH
+}
+
+int ab200_tile_set_weights(ab200_tile *tile, const float *w_host) {
+  AB200_TRY
+  T(tile)->setWeights(w_host);
+  AB200_CATCH
+}
+int ab200_tile_get_weights(ab200_tile *tile, float *w_host) {
+  AB200_TRY
+  T(tile)->getWeights(w_host);
+  AB200_CATCH
+}
+int ab200_tile_set_weights_device(ab200_tile *tile, const float *w_dev_xd, void *stream) {
+  AB200_TRY
+  if (!w_dev_xd) {
+    AB200_FATAL("null weight pointer");
+  }
+  T(tile)->setWeightsDevice(w_dev_xd, (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_tile_get_weights_device(ab200_tile *tile, float *w_dev_xd, void *stream) {
+  AB200_TRY
+  T(tile)->getWeightsDevice(w_dev_xd, (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_tile_set_shared_weights(ab200_tile *tile, float *w_dev_xd, uint64_t version) {
+  AB200_TRY
+  T(tile)->setSharedWeights(w_dev_xd, version);
+  AB200_CATCH
+}
+
+int ab200_tile_hidden_parameter_count(const ab200_tile *tile) {
+  return tile ? T(tile)->hiddenCount() : 0;
+}
+const char *ab200_tile_hidden_parameter_name(const ab200_tile *tile, int index) {
+  return tile ? T(tile)->hiddenName(index) : "";
+}
+int ab200_tile_get_hidden_parameters(ab200_tile *tile, float *out_host) {
+  AB200_TRY
+  T(tile)->getHidden(out_host);
+  AB200_CATCH
+}
+int ab200_tile_set_hidden_parameters(ab200_tile *tile, const float *in_host) {
+  AB200_TRY
+  T(tile)->setHidden(in_host);
+  AB200_CATCH
+}
+
+static void checkBatch(int m) {
+  if (m < 0) {
+    AB200_FATAL("m_batch must be >= 0");
+  }
+}
+
+int ab200_tile_forward(ab200_tile *tile, const float *x_dev, float *d_dev, int bias, int m_batch,
+                       int x_trans, int d_trans, int is_test, void *stream) {
+  AB200_TRY
+  checkBatch(m_batch);
+  T(tile)->forward(x_dev, d_dev, bias != 0, m_batch, x_trans != 0, d_trans != 0, is_test != 0,
+                   (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_tile_backward(ab200_tile *tile, const float *d_dev, float *x_dev, int bias, int m_batch,
+                        int d_trans, int x_trans, void *stream) {
+  AB200_TRY
+  checkBatch(m_batch);
+  T(tile)->backward(d_dev, x_dev, bias != 0, m_batch, d_trans != 0, x_trans != 0,
+                    (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_tile_update(ab200_tile *tile, const float *x_dev, const float *d_dev, int bias,
+                      int m_batch, int x_trans, int d_trans, void *stream) {
+  AB200_TRY
+  checkBatch(m_batch);
+  T(tile)->update(x_dev, d_dev, bias != 0, m_batch, x_trans != 0, d_trans != 0,
+                  (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_tile_forward_host(ab200_tile *tile, const float *x_host, float *d_host, int bias,
+                            int m_batch, int x_trans, int d_trans, int is_test, void *stream) {
+  AB200_TRY
+  checkBatch(m_batch);
+  T(tile)->forwardHost(x_host, d_host, bias != 0, m_batch, x_trans != 0, d_trans != 0,
+                       is_test != 0, (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_tile_backward_host(ab200_tile *tile, const float *d_host, float *x_host, int bias,
+                             int m_batch, int d_trans, int x_trans, void *stream) {
+  AB200_TRY
+  checkBatch(m_batch);
+  T(tile)->backwardHost(d_host, x_host, bias != 0, m_batch, d_trans != 0, x_trans != 0,
+                        (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_tile_update_host(ab200_tile *tile, const float *x_host, const float *d_host, int bias,
+                           int m_batch, int x_trans, int d_trans, void *stream) {
+  AB200_TRY
+  checkBatch(m_batch);
+  T(tile)->updateHost(x_host, d_host, bias != 0, m_batch, x_trans != 0, d_trans != 0,
+                      (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+int ab200_tile_coincidences(ab200_tile *tile, const float *x_dev, const float *d_dev,
+                            int32_t *counts_dev, void *stream) {
+  AB200_TRY
+  T(tile)->coincidences(x_dev, d_dev, counts_dev, (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+int ab200_tile_last_bm_stats(ab200_tile *tile, int32_t *n_rerun_samples, float *max_reduction) {
+  AB200_TRY
+  T(tile)->lastBmStats(n_rerun_samples, max_reduction);
+  AB200_CATCH
+}
+
+int ab200_tile_set_seed(ab200_tile *tile, uint64_t seed) {
+  AB200_TRY
+  T(tile)->setSeed(seed);
+  AB200_CATCH
+}
+
+int ab200_array_create(const ab200_tile_config *cfg, int out_size, int in_size,
+                       int max_output_size, int max_input_size, int in_split_begin,
+                       int in_split_end, int cuda_device, ab200_array **out) {
+  AB200_TRY
+  if (!cfg || !out) {
+    AB200_FATAL("null argument");
+  }
+  if (cuda_device < 0) {
+    AB200_FATAL("the mapped-tile array needs a CUDA device");
+  }
+  *out = reinterpret_cast<ab200_array *>(new TileArray(*cfg, out_size, in_size, max_output_size,
+                                                       max_input_size, in_split_begin,
+                                                       in_split_end, cuda_device));
+  AB200_CATCH
+}
+int ab200_array_destroy(ab200_array *arr) {
+  AB200_TRY
+  delete reinterpret_cast<TileArray *>(arr);
+  AB200_CATCH
+}
+int ab200_array_num_in_splits(const ab200_array *arr) {
+  return arr ? reinterpret_cast<const TileArray *>(arr)->numInSplits() : -1;
+}
+int ab200_array_num_out_splits(const ab200_array *arr) {
+  return arr ? reinterpret_cast<const TileArray *>(arr)->numOutSplits() : -1;
+}
+int ab200_array_set_weights(ab200_array *arr, const float *w_host) {
+  AB200_TRY
+  A(arr)->setWeights(w_host);
+  AB200_CATCH
+}
+int ab200_array_get_weights(ab200_array *arr, float *w_host) {
+  AB200_TRY
+  A(arr)->getWeights(w_host);
+  AB200_CATCH
+}
+int ab200_array_forward(ab200_array *arr, const float *x_dev, float *y_dev, int m_batch,
+                        int is_test, void *stream) {
+  AB200_TRY
+  checkBatch(m_batch);
+  A(arr)->forward(x_dev, y_dev, m_batch, is_test != 0, (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_array_forward_host(ab200_array *arr, const float *x_host, float *y_host, int m_batch,
+                             int is_test, void *stream) {
+  AB200_TRY
+  checkBatch(m_batch);
+  A(arr)->forwardHost(x_host, y_host, m_batch, is_test != 0, (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_array_set_seed(ab200_array *arr, uint64_t seed) {
+  AB200_TRY
+  A(arr)->setSeed(seed);
+  AB200_CATCH
+}
+
+uint64_t ab200_kernel_launch_count(void) { return ab200::launchCount(); }
+
+} // extern "C"

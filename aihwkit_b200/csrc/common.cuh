@@ -1,0 +1,118 @@
+// Shared device/host helpers of the B200 analog-tile library: error handling, the
+// counter-based noise generator, and the fp32 discretisation steps of the IO chain.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <sstream>
+#include <stdexcept>
+#include <string>
+
+namespace ab200 {
+
+// Errors follow the reference's convention (RPU_FATAL -> std::runtime_error,
+// src/rpucuda/utility_functions.h:63-69); the C ABI turns them into return codes.
+#define AB200_FATAL(msg)                                                                           \
+  do {                                                                                             \
+    std::ostringstream ss_;                                                                        \
+    ss_ << msg;                                                                                    \
+    throw std::runtime_error(ss_.str());                                                           \
+  } while (0)
+
+#define AB200_CUDA(call)                                                                           \
+  do {                                                                                             \
+    cudaError_t e_ = (call);                                                                       \
+    if (e_ != cudaSuccess) {                                                                       \
+      AB200_FATAL("CUDA error " << cudaGetErrorName(e_) << " (" << cudaGetErrorString(e_)          \
+                                << ") at " << __FILE__ << ":" << __LINE__);                        \
+    }                                                                                              \
+  } while (0)
+
+void countLaunch(int n = 1);
+#define AB200_LAUNCH_CHECK()                                                                       \
+  do {                                                                                             \
+    ab200::countLaunch();                                                                          \
+    AB200_CUDA(cudaGetLastError());                                                                \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11).
+// The reference keeps one XORWOW state per thread in global memory
+// (src/rpucuda/cuda/cuda_util.cu:163-211); here every noise sample is a pure function of
+// (seed, call counter, element index, purpose tag), so no generator state is ever loaded or
+// stored and the result does not depend on how the work is tiled over threads.
+// ---------------------------------------------------------------------------------------------
+struct PhiloxKey {
+  uint32_t k0, k1;
+};
+
+__host__ __device__ __forceinline__ void
+philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, PhiloxKey key, uint32_t out[4]) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+  uint32_t k0 = key.k0, k1 = key.k1;
+#pragma unroll
+  for (int r = 0; r < 10; r++) {
+#ifdef __CUDA_ARCH__
+    uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
+    uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
+#else
+    uint64_t p0 = (uint64_t)M0 * c0, p1 = (uint64_t)M1 * c2;
+    uint32_t hi0 = (uint32_t)(p0 >> 32), lo0 = (uint32_t)p0;
+    uint32_t hi1 = (uint32_t)(p1 >> 32), lo1 = (uint32_t)p1;
+#endif
+    uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0;
+    c1 = lo1;
+    c2 = n2;
+    c3 = lo0;
+    k0 += W0;
+    k1 += W1;
+  }
+  out[0] = c0;
+  out[1] = c1;
+  out[2] = c2;
+  out[3] = c3;
+}
+
+// purpose tags (4th counter word) so that streams never overlap
+enum : uint32_t {
+  TAG_FWD_OUT = 0x10000000u,   // + bound-management round
+  TAG_BWD_OUT = 0x20000000u,
+  TAG_PULSE_X = 0x30000000u,
+  TAG_PULSE_D = 0x40000000u,
+  TAG_DEVICE = 0x50000000u,    // + refill ordinal
+  TAG_TRANSFER_READ = 0x60000000u,
+};
+
+#ifdef __CUDACC__
+// uniform in (0,1) with 24 random bits
+__device__ __forceinline__ float u01(uint32_t x) { return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f); }
+
+// two standard normals from two 32-bit words (Box-Muller)
+__device__ __forceinline__ void boxMuller(uint32_t a, uint32_t b, float &z0, float &z1) {
+  float u1 = u01(a);
+  float r = sqrtf(-2.0f * __logf(u1));
+  float s, c;
+  __sincosf(6.283185307179586f * u01(b), &s, &c);
+  z0 = r * c;
+  z1 = r * s;
+}
+
+// four standard normals for noise block `blk` of call `call`
+__device__ __forceinline__ void
+gauss4(PhiloxKey key, uint64_t blk, uint32_t call, uint32_t tag, float z[4]) {
+  uint32_t r[4];
+  philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), call, tag, key, r);
+  boxMuller(r[0], r[1], z[0], z[1]);
+  boxMuller(r[2], r[3], z[2], z[3]);
+}
+
+// getDiscretizedValueSR<false> (src/rpucuda/utility_functions.h:204-210): rint(v / res) * res with
+// round-half-to-even, as separate correctly-rounded fp32 operations (no FMA contraction).
+__device__ __forceinline__ float discretize(float v, float res) {
+  return res > 0.0f ? __fmul_rn(rintf(__fdiv_rn(v, res)), res) : v;
+}
+#endif
+
+} // namespace ab200

@@ -1,0 +1,365 @@
+// IO-managed matrix-vector batch, generic CUDA-core path.
+//
+// Handles any tile shape, any activation layout (strided) and every IO setting of the path. The
+// tensor-core kernel (mvm_tc.cu) takes over for large aligned problems; both use the same
+// per-element helpers below so their results agree element by element, noise included.
+//
+// Reference semantics restated here:
+//   noise management      src/rpucuda/rpu_forward_backward_pass.cpp:113-178
+//   prepareInput (DAC)    src/rpucuda/rpu_forward_backward_pass.cpp:571-604
+//   weight noise          src/rpucuda/rpu_forward_backward_pass.cpp:326-352
+//   finalizeOutput (ADC)  src/rpucuda/rpu_forward_backward_pass.cpp:673-719
+//   bound management      src/rpucuda/rpu_forward_backward_pass.cpp:935-988
+//   backward              src/rpucuda/rpu_forward_backward_pass.cpp:991-1027
+#include "mvm_common.cuh"
+#include "tile.h"
+
+namespace ab200 {
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 1: per-sample noise management. One warp per sample (sample-contiguous layouts) or one
+// thread per sample (feature-major layouts), so that loads stay coalesced either way.
+// ---------------------------------------------------------------------------------------------
+template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKernel(MvmProblem p) {
+  const IOEff &io = p.io;
+  int lane = threadIdx.x & 31;
+  int s = WARP_PER_SAMPLE ? (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5)
+                          : (int)(blockIdx.x * (long long)blockDim.x + threadIdx.x);
+  if (s >= p.m) {
+    return;
+  }
+  const float *row = p.in + (long long)s * p.in_ss;
+  float amax = 0.0f;
+  if (!io.is_perfect && io.nm == AB200_NM_ABS_MAX) {
+    if (WARP_PER_SAMPLE) {
+      for (int k = lane; k < p.in_size; k += 32) {
+        float v = k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f;
+        amax = fmaxf(amax, fabsf(v));
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      }
+    } else {
+      for (int k = 0; k < p.in_size; k++) {
+        float v = k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f;
+        amax = fmaxf(amax, fabsf(v));
+      }
+    }
+  }
+  float sval = nmValue(io, amax);
+  float scale = inputScale(io, sval, /*reduction=*/1.0f, !p.backward);
+  float vn = 0.0f;
+  if (!io.is_perfect && io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f &&
+      scale != 0.0f) {
+    float acc = 0.0f;
+    if (WARP_PER_SAMPLE) {
+      for (int k = lane; k < p.in_size; k += 32) {
+        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale);
+        acc = fmaf(v, v, acc);
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      }
+    } else {
+      for (int k = 0; k < p.in_size; k++) {
+        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale);
+        acc = fmaf(v, v, acc);
+      }
+    }
+    vn = sqrtf(acc);
+  }
+  if (!WARP_PER_SAMPLE || lane == 0) {
+    p.scale[s] = scale;
+    p.sval[s] = sval;
+    p.factor[s] = outputFactor(io, p.alpha, sval, scale, p.backward);
+    p.vnorm[s] = vn;
+    p.flags[s] = 0;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 2: tiled fp32 product with the DAC fused into the operand load and noise / ADC / clip /
+// bound flag / rescale fused into the epilogue.
+// ---------------------------------------------------------------------------------------------
+constexpr int BM = 64, BN = 64, BK = 16;
+
+template <bool A_K_FAST, bool B_N_FAST>
+__global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  __shared__ float s_scale[BM];
+  const IOEff &io = p.io;
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+  const int K = p.in_size, N = p.out_size;
+
+  if (tid < BM) {
+    int r = row0 + tid;
+    s_scale[tid] = r < p.m ? p.scale[r] : 0.0f;
+  }
+  __syncthreads();
+
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      acc[i][j] = 0.0f;
+    }
+  }
+
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int l = 0; l < 4; l++) {
+      int e = tid + l * 256;
+      int r, kk;
+      if (A_K_FAST) {
+        kk = e % BK;
+        r = e / BK;
+      } else {
+        r = e % BM;
+        kk = e / BM;
+      }
+      int gr = row0 + r, gk = k0 + kk;
+      float v = 0.0f;
+      if (gr < p.m && gk < K) {
+        float sc = s_scale[r];
+        if (sc != 0.0f) {
+          float xin = gk < p.in_real ? p.in[(long long)gr * p.in_ss + (long long)gk * p.in_fs] : 1.0f;
+          v = prepareInput(io, xin, sc);
+        }
+      }
+      As[kk][r] = v;
+    }
+#pragma unroll
+    for (int l = 0; l < 4; l++) {
+      int e = tid + l * 256;
+      int n, kk;
+      if (B_N_FAST) {
+        n = e % BN;
+        kk = e / BN;
+      } else {
+        kk = e % BK;
+        n = e / BK;
+      }
+      int gk = k0 + kk, gn = col0 + n;
+      Bs[kk][n] = (gk < K && gn < N) ? p.w[(long long)gk * p.wk + (long long)gn * p.wn] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        a[i] = As[kk][ty * 4 + i];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        b[j] = Bs[kk][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  const uint64_t n4 = (uint64_t)((N + 3) >> 2);
+  const uint32_t tag = (p.backward ? TAG_BWD_OUT : TAG_FWD_OUT) + p.noise_id;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    int r = row0 + ty * 4 + i;
+    if (r >= p.m) {
+      continue;
+    }
+    int c = col0 + tx * 4;
+    if (c >= N) {
+      continue;
+    }
+    float sc = s_scale[ty * 4 + i];
+    float fac = p.factor[r];
+    float y[4] = {acc[i][0], acc[i][1], acc[i][2], acc[i][3]};
+    bool exceeded = false;
+    if (sc == 0.0f) {
+      y[0] = y[1] = y[2] = y[3] = 0.0f;
+    } else if (io.is_perfect) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        y[j] *= fac;
+      }
+    } else {
+      float sigma = outputSigma(io, p.vnorm[r]);
+      float z[4] = {0.f, 0.f, 0.f, 0.f};
+      if (sigma > 0.0f) {
+        gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag, z);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        y[j] = finalizeOutput(io, y[j], sigma, z[j], exceeded) * fac;
+      }
+    }
+    if (exceeded && io.bm != AB200_BM_NONE) {
+      atomicOr(&p.flags[r], 1);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      if (c + j < p.out_store) {
+        float *o = p.out + (long long)r * p.out_ss + (long long)(c + j) * p.out_fs;
+        *o = p.accumulate ? *o + y[j] : y[j];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 3: iterative bound management. Only samples whose first round clipped are re-run; each
+// is an independent mat-vec with a halved input scale per round, exactly the per-sample loop of
+// the reference CPU tile. Nothing is copied to the host.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
+  extern __shared__ float v_sh[]; // K prepared inputs
+  __shared__ float red_sh[8];
+  const IOEff &io = p.io;
+  const int K = p.in_size, N = p.out_size;
+  const uint64_t n4 = (uint64_t)((N + 3) >> 2);
+  for (int r = blockIdx.x; r < p.m; r += gridDim.x) {
+    if (p.flags[r] == 0) {
+      continue;
+    }
+    const float sval = p.sval[r];
+    const float *row = p.in + (long long)r * p.in_ss;
+    float reduction = 1.0f;
+    float scale = 1.0f;
+    int round = 0;
+    bool done = false;
+    while (!done) {
+      reduction *= 2.0f;
+      round++;
+      scale = inputScale(io, sval, reduction, true);
+      float nacc = 0.0f;
+      for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale);
+        v_sh[k] = v;
+        nacc = fmaf(v, v, nacc);
+      }
+      float vn = 0.0f;
+      if (io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f) {
+        for (int o = 16; o > 0; o >>= 1) {
+          nacc += __shfl_xor_sync(0xffffffffu, nacc, o);
+        }
+        if ((threadIdx.x & 31) == 0) {
+          red_sh[threadIdx.x >> 5] = nacc;
+        }
+        __syncthreads();
+        float t = 0.0f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); i++) {
+          t += red_sh[i];
+        }
+        vn = sqrtf(t);
+      }
+      __syncthreads();
+      float sigma = outputSigma(io, vn);
+      int fail = 0;
+      for (int n = threadIdx.x; n < N; n += blockDim.x) {
+        float acc = 0.0f;
+        const float *wp = p.w + (long long)n * p.wn;
+        for (int k = 0; k < K; k++) {
+          acc = fmaf(v_sh[k], wp[(long long)k * p.wk], acc);
+        }
+        float z[4] = {0.f, 0.f, 0.f, 0.f};
+        if (sigma > 0.0f) {
+          gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(n >> 2), p.call,
+                 TAG_FWD_OUT + p.noise_id + (uint32_t)round * 0x10000u, z);
+        }
+        bool ex = false;
+        float y = finalizeOutput(io, acc, sigma, z[n & 3], ex);
+        fail |= ex ? 1 : 0;
+        if (n < p.out_store) {
+          p.out[(long long)r * p.out_ss + (long long)n * p.out_fs] = y;
+        }
+      }
+      int any_fail = __syncthreads_or(fail);
+      done = !any_fail || ((int)reduction > io.max_bm_factor) ||
+             (io.res_in > 0.0f && reduction > __fdiv_rn(io.max_bm_res, io.res_in));
+    }
+    float fac = outputFactor(io, p.alpha, sval, scale, false);
+    for (int n = threadIdx.x; n < N && n < p.out_store; n += blockDim.x) {
+      p.out[(long long)r * p.out_ss + (long long)n * p.out_fs] *= fac;
+    }
+    if (threadIdx.x == 0) {
+      atomicAdd(&p.bm_stats[0], 1);
+      atomicMax(&p.bm_stats[1], __float_as_int(reduction));
+    }
+    __syncthreads();
+  }
+}
+
+void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
+  // noise management
+  bool sample_contig = p.in_fs == 1;
+  if (sample_contig) {
+    int blocks = (int)(((long long)p.m * 32 + 255) / 256);
+    nmScaleKernel<true><<<blocks, 256, 0, stream>>>(p);
+  } else {
+    nmScaleKernel<false><<<(p.m + 255) / 256, 256, 0, stream>>>(p);
+  }
+  AB200_LAUNCH_CHECK();
+
+  dim3 grid((p.out_size + BN - 1) / BN, (p.m + BM - 1) / BM);
+  bool a_k_fast = p.in_fs == 1;
+  bool b_n_fast = p.wn == 1;
+  if (a_k_fast && b_n_fast) {
+    mvmSimtKernel<true, true><<<grid, 256, 0, stream>>>(p);
+  } else if (a_k_fast) {
+    mvmSimtKernel<true, false><<<grid, 256, 0, stream>>>(p);
+  } else if (b_n_fast) {
+    mvmSimtKernel<false, true><<<grid, 256, 0, stream>>>(p);
+  } else {
+    mvmSimtKernel<false, false><<<grid, 256, 0, stream>>>(p);
+  }
+  AB200_LAUNCH_CHECK();
+}
+
+void launchBmRerun(const MvmProblem &p, cudaStream_t stream) {
+  if (p.backward || p.io.is_perfect || p.io.bm == AB200_BM_NONE) {
+    return;
+  }
+  if (p.accumulate) {
+    AB200_FATAL("bound management cannot be combined with accumulating outputs");
+  }
+  size_t smem = (size_t)p.in_size * sizeof(float);
+  if (smem > 200 * 1024) {
+    AB200_FATAL("bound management: x_size too large for the re-run kernel");
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    AB200_CUDA(cudaFuncSetAttribute(bmRerunKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    200 * 1024));
+    attr_set = true;
+  }
+  int blocks = p.m < 592 ? p.m : 592;
+  bmRerunKernel<<<blocks, 256, smem, stream>>>(p);
+  AB200_LAUNCH_CHECK();
+}
+
+bool tcMvmSupported(const MvmProblem &p);
+void launchMvmTc(const MvmProblem &p, cudaStream_t stream);
+
+void launchMvm(const MvmProblem &p, cudaStream_t stream) {
+  if (p.m <= 0) {
+    return;
+  }
+  if (tcMvmSupported(p)) {
+    launchMvmTc(p, stream);
+  } else {
+    launchMvmSimt(p, stream);
+  }
+  launchBmRerun(p, stream);
+}
+
+} // namespace ab200

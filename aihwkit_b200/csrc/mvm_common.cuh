@@ -1,0 +1,102 @@
+// Per-element steps of the IO-managed MVM, shared by the CUDA-core and tensor-core kernels.
+// Every step is written with explicit round-to-nearest fp32 intrinsics so that the compiler
+// cannot contract them into FMAs: the reference CPU build has no fused multiply-adds
+// (CMakeLists.txt:52-53) and a 1-ulp difference in front of rint() can move a DAC/ADC code.
+#pragma once
+
+#include "common.cuh"
+#include "tile.h"
+
+namespace ab200 {
+
+// computeNoiseManagement (src/rpucuda/rpu_forward_backward_pass.cpp:113-131)
+__device__ __forceinline__ float nmValue(const IOEff &io, float amax) {
+  if (io.is_perfect) {
+    return 1.0f;
+  }
+  switch (io.nm) {
+  case AB200_NM_ABS_MAX:
+    return io.nm_thres > 0.0f ? fminf(amax, io.nm_thres) : amax;
+  case AB200_NM_CONSTANT:
+    return io.nm_thres > 0.0f ? io.nm_thres : 1.0f;
+  default:
+    return 1.0f;
+  }
+}
+
+// Input scale of one sample; 0 marks "output is identically zero"
+// (forward: rpu_forward_backward_pass.cpp:924-969; backward: :1003-1022).
+__device__ __forceinline__ float
+inputScale(const IOEff &io, float sval, float reduction, bool forward) {
+  if (io.is_perfect) {
+    return 1.0f;
+  }
+  bool nm = io.nm != AB200_NM_NONE;
+  if (nm && sval <= 0.0f) {
+    return 0.0f;
+  }
+  float scale = 1.0f;
+  if (nm) {
+    scale = __fdiv_rn(1.0f, sval);
+  }
+  if (forward && io.bm != AB200_BM_NONE) {
+    scale = __fdiv_rn(scale, reduction);
+  }
+  return scale;
+}
+
+// prepareInputImplStage4 (rpu_forward_backward_pass.cpp:571-604): scale, DAC, clip.
+__device__ __forceinline__ float prepareInput(const IOEff &io, float x, float scale) {
+  if (io.is_perfect) {
+    return x;
+  }
+  float v = __fmul_rn(x, scale);
+  v = discretize(v, io.res_in);
+  v = v > io.inp_bound ? io.inp_bound : v;
+  v = v < -io.inp_bound ? -io.inp_bound : v;
+  return v;
+}
+
+// Std-dev of the Gaussian added before the ADC: output noise (:695-698) and the additive-constant
+// weight noise w_noise * ||v|| (:341-352) are independent zero-mean Gaussians on the same value,
+// so one draw with the combined variance is statistically identical to two draws.
+__device__ __forceinline__ float outputSigma(const IOEff &io, float vnorm) {
+  float s = io.out_noise;
+  if (io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f) {
+    float ws = io.w_noise * vnorm;
+    s = sqrtf(s * s + ws * ws);
+  }
+  return s;
+}
+
+// finalizeOutputImplStage5 (rpu_forward_backward_pass.cpp:673-719): noise, ADC, clip / bound test.
+__device__ __forceinline__ float
+finalizeOutput(const IOEff &io, float y, float sigma, float z, bool &exceeded) {
+  if (sigma > 0.0f) {
+    y = __fadd_rn(y, __fmul_rn(sigma, z));
+  }
+  y = discretize(y, io.res_out);
+  if (y > io.out_bound) {
+    y = io.out_bound;
+    exceeded = true;
+  } else if (y < -io.out_bound) {
+    y = -io.out_bound;
+    exceeded = exceeded || (io.bm_test_negative_bound != 0);
+  }
+  return y;
+}
+
+// Final rescale: forward out_scale*alpha/scale (:985-987), backward out_scale*alpha*s (:1024-1026).
+__device__ __forceinline__ float
+outputFactor(const IOEff &io, float alpha, float sval, float scale, bool backward) {
+  float os = __fmul_rn(io.out_scale, alpha);
+  if (io.is_perfect) {
+    return os;
+  }
+  if (scale == 0.0f) {
+    return 0.0f;
+  }
+  return backward ? __fmul_rn(os, sval) : __fdiv_rn(os, scale);
+}
+
+} // namespace ab200

@@ -1,0 +1,975 @@
+// Host side of the analog tile: configuration, per-element device parameters, weight access and
+// the sequencing of forward / backward / update (including Tiki-Taka transfers).
+#include "tile.h"
+
+#include <atomic>
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <random>
+
+namespace ab200 {
+
+static std::atomic<uint64_t> g_launches{0};
+void countLaunch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+uint64_t launchCount() { return g_launches.load(std::memory_order_relaxed); }
+
+// detail::checkRes (src/rpucuda/rpu_pulsed_meta_parameter.cpp:26-29)
+static float checkRes(float res) {
+  float r = res < 0.0f ? 0.0f : res;
+  return r > 1.0f ? 1.0f / r : r;
+}
+
+IOEff resolveIO(const ab200_io_params &io, bool backward) {
+  // IOMetaParameter::initializeForForward / Backward (rpu_pulsed_meta_parameter.cpp:40-128)
+  IOEff e;
+  e.is_perfect = io.is_perfect;
+  e.nm = io.noise_management;
+  e.bm = backward ? AB200_BM_NONE : io.bound_management;
+  e.w_noise_type = io.w_noise_type;
+  e.bm_test_negative_bound = io.bm_test_negative_bound;
+  e.max_bm_factor = io.max_bm_factor;
+  e.max_bm_res = io.max_bm_res;
+  e.res_out = checkRes(io.out_res) * (2.0f * io.out_bound);
+  e.res_in = checkRes(io.inp_res) * (2.0f * io.inp_bound);
+  e.nm_thres = io.noise_management == AB200_NM_NONE ? 0.0f : io.nm_thres;
+  e.out_bound = io.out_bound <= 0.0f ? std::numeric_limits<float>::infinity() : io.out_bound;
+  e.inp_bound = io.inp_bound <= 0.0f ? std::numeric_limits<float>::infinity() : io.inp_bound;
+  e.out_noise = io.out_noise;
+  e.out_scale = io.out_scale;
+  e.w_noise = io.w_noise;
+  if (!io.is_perfect) {
+    if (io.noise_management != AB200_NM_NONE && io.inp_bound != 1.0f) {
+      AB200_FATAL((backward ? "Backward noise managment expects input bound==1"
+                            : "Forward noise managment expects bound==1"));
+    }
+    if (io.noise_management != AB200_NM_NONE && io.noise_management != AB200_NM_ABS_MAX &&
+        io.noise_management != AB200_NM_CONSTANT) {
+      AB200_FATAL("Noise Management type not implemented!");
+    }
+    if (io.bound_management == AB200_BM_ITERATIVE_WORST_CASE && !backward) {
+      AB200_FATAL("IterativeWorstCase bound management is not implemented");
+    }
+    if (io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) {
+      AB200_FATAL("PCMRead weight noise is not implemented");
+    }
+    if (io.inp_noise != 0.0f || io.inp_sto_round || io.out_sto_round || io.inp_asymmetry != 0.0f ||
+        io.out_asymmetry != 0.0f) {
+      AB200_FATAL("inp_noise / stochastic rounding / asymmetry are not implemented");
+    }
+  }
+  return e;
+}
+
+UpEff resolveUp(const ab200_update_params &up) {
+  UpEff e;
+  e.pulse_type = up.pulse_type;
+  e.desired_bl = up.desired_bl;
+  e.fixed_bl = up.fixed_bl;
+  e.update_bl_management = up.update_bl_management;
+  // "always turn on UM for UBL management" (rpu_pulsed_meta_parameter.cpp:139-141)
+  e.update_management = up.update_management || up.update_bl_management;
+  e.um_grad_scale = up.um_grad_scale;
+  e.res = checkRes(up.res);
+  e.x_res_implicit = checkRes(up.x_res_implicit);
+  e.d_res_implicit = checkRes(up.d_res_implicit);
+  if (up.pulse_type == AB200_PULSE_STOCHASTIC || up.pulse_type == AB200_PULSE_MEAN_COUNT) {
+    AB200_FATAL("PulseType not supported");
+  }
+  if (up.sto_round) {
+    AB200_FATAL("stochastic rounding of pulse probabilities is not implemented");
+  }
+  return e;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-element device parameters, drawn on the host in the reference's order of draws
+// (RealWorldRNG = std::default_random_engine + std::normal_distribution<float>,
+//  src/rpucuda/rng.h:45-61; PulsedRPUDevice::populate, rpu_pulsed_device.cpp:594-733;
+//  LinearStepRPUDevice::populate, rpu_linearstep_device.cpp:21-74;
+//  SoftBoundsReferenceRPUDevice::populate, rpu_softbounds_reference_device.cpp:21-68).
+// ---------------------------------------------------------------------------------------------
+namespace {
+struct HostRNG {
+  explicit HostRNG(unsigned int seed) {
+    if (!seed) {
+      seed = (unsigned int)std::chrono::high_resolution_clock::now().time_since_epoch().count();
+    }
+    gen = std::default_random_engine(seed);
+  }
+  float gauss() { return nd(gen); }
+  float uniform() { return ud(gen); }
+  std::default_random_engine gen;
+  std::uniform_real_distribution<float> ud{0.0f, 1.0f};
+  std::normal_distribution<float> nd{0.0f, 1.0f};
+};
+
+std::vector<std::string> deviceNames(int kind) {
+  std::vector<std::string> n = {"max_bound",    "min_bound",       "dwmin_up",   "dwmin_down",
+                                "decay_scales", "diffusion_rates", "reset_bias", "drift_nu"};
+  if (kind == AB200_DEVICE_LINEAR_STEP || kind == AB200_DEVICE_SOFT_BOUNDS) {
+    n.push_back("slope_up");
+    n.push_back("slope_down");
+  } else if (kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE) {
+    n.push_back("reference");
+  }
+  return n;
+}
+
+void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_size, HostRNG &rng,
+                    DeviceStore &ds) {
+  ds.kind = kind;
+  ds.dw_min = par.dw_min;
+  ds.dw_min_std = par.dw_min_std;
+  ds.mult_noise = kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE ? par.mult_noise : par.ls_mult_noise;
+  ds.names = deviceNames(kind);
+  const size_t size = (size_t)x_size * d_size;
+  ds.host.assign(ds.names.size() * size, 0.0f);
+  float *wmax = &ds.host[0 * size], *wmin = &ds.host[1 * size], *sup = &ds.host[2 * size],
+        *sdown = &ds.host[3 * size], *decay = &ds.host[4 * size];
+
+  if (par.w_min > 0.0f || par.w_max < 0.0f) {
+    AB200_FATAL("The closed interval [w_min,w_max] needs to contain 0.");
+  }
+  const float up_bias = par.up_down > 0.0f ? 0.0f : par.up_down;
+  const float down_bias = par.up_down > 0.0f ? -par.up_down : 0.0f;
+
+  for (int j = 0; j < x_size; ++j) {
+    for (int i = 0; i < d_size; ++i) {
+      const size_t k = (size_t)i * x_size + j;
+      wmax[k] = par.w_max * (1.0f + par.w_max_dtod * rng.gauss());
+      wmin[k] = par.w_min * (1.0f + par.w_min_dtod * rng.gauss());
+      float gain = par.dw_min_dtod_log_normal ? expf(par.dw_min_dtod * rng.gauss())
+                                              : (1.0f + par.dw_min_dtod * rng.gauss());
+      float r = par.up_down_dtod * rng.gauss();
+      sup[k] = (up_bias + gain + r) * par.dw_min;
+      sdown[k] = (down_bias + gain - r) * par.dw_min;
+      if (par.enforce_consistency) {
+        sup[k] = fabsf(sup[k]);
+        sdown[k] = fabsf(sdown[k]);
+        if (wmin[k] > wmax[k]) {
+          std::swap(wmin[k], wmax[k]);
+        }
+        wmax[k] = fabsf(wmax[k]);
+        wmin[k] = -fabsf(wmin[k]);
+      } else if (wmin[k] > wmax[k]) {
+        float m = wmax[k] + (wmin[k] - wmax[k]) / 2.0f;
+        wmax[k] = m;
+        wmin[k] = m;
+      }
+      // corrupt-device draw (probability 0 here, but the draw is part of the sequence)
+      (void)rng.uniform();
+      if (par.perfect_bias && j == x_size - 1) {
+        sup[k] = par.dw_min;
+        sdown[k] = par.dw_min;
+        wmin[k] = 100.0f * par.w_min;
+        wmax[k] = 100.0f * par.w_max;
+      }
+      (void)rng.gauss(); // diffusion rate draw (diffusion = 0)
+      (void)rng.gauss(); // reset bias draw (reset = 0, reset_dtod = 0)
+      decay[k] = 1.0f;   // lifetime = 0: no decay, no draw
+    }
+  }
+
+  if (kind == AB200_DEVICE_LINEAR_STEP || kind == AB200_DEVICE_SOFT_BOUNDS) {
+    float *slope_up = &ds.host[8 * size], *slope_down = &ds.host[9 * size];
+    for (int i = 0; i < d_size; ++i) {
+      for (int j = 0; j < x_size; ++j) {
+        const size_t k = (size_t)i * x_size + j;
+        float du = par.ls_decrease_up + par.ls_decrease_up_dtod * rng.gauss();
+        float dd = par.ls_decrease_down + par.ls_decrease_down_dtod * rng.gauss();
+        if (!par.ls_allow_increasing_slope) {
+          du = fabsf(du);
+          dd = fabsf(dd);
+        }
+        float ref_up = par.ls_mean_bound_reference ? par.w_max : wmax[k];
+        float ref_down = par.ls_mean_bound_reference ? par.w_min : wmin[k];
+        slope_up[k] = ref_up != 0.0f ? -du * sup[k] / ref_up : 0.0f;
+        slope_down[k] = ref_down != 0.0f ? -dd * sdown[k] / ref_down : 0.0f;
+      }
+    }
+  } else if (kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE) {
+    float *reference = &ds.host[8 * size], *reset_bias = &ds.host[6 * size];
+    for (int i = 0; i < d_size; ++i) {
+      for (int j = 0; j < x_size; ++j) {
+        const size_t k = (size_t)i * x_size + j;
+        float w_min = wmin[k], w_max = wmax[k];
+        if (w_max > 0.0f && w_min < 0.0f) {
+          float slope_down = -sdown[k] / w_min;
+          slope_down *= fabsf(1.0f + par.slope_down_dtod * rng.gauss());
+          float slope_up = sup[k] / w_max;
+          slope_up *= fabsf(1.0f + par.slope_up_dtod * rng.gauss());
+          w_max = sup[k] / slope_up;
+          w_min = -sdown[k] / slope_down;
+          wmax[k] = w_max;
+          wmin[k] = w_min;
+        }
+        reference[k] = par.reference_mean + par.reference_std * rng.gauss();
+        if (par.subtract_symmetry_point && w_max > 0.0f && w_min < 0.0f) {
+          float sp = (sup[k] - sdown[k]) / (sup[k] / w_max - sdown[k] / w_min);
+          reference[k] += sp;
+          reset_bias[k] += sp;
+        }
+      }
+    }
+  }
+}
+} // namespace
+
+void Tile::populateHost() {
+  if (cfg_.device_kind == AB200_DEVICE_IDEAL) {
+    n_dev_ = 1;
+    dev_[0].kind = AB200_DEVICE_IDEAL;
+    return;
+  }
+  HostRNG rng(cfg_.device[0].construction_seed);
+  if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+    n_dev_ = 2;
+    for (int k = 0; k < 2; k++) {
+      int kind = cfg_.device[k].kind;
+      if (kind < AB200_DEVICE_CONSTANT_STEP || kind > AB200_DEVICE_SOFT_BOUNDS_REFERENCE) {
+        AB200_FATAL("Transfer: unit cell device kind not implemented");
+      }
+      populateDevice(cfg_.device[k], kind, x_size_, d_size_, rng, dev_[k]);
+    }
+  } else {
+    n_dev_ = 1;
+    populateDevice(cfg_.device[0], cfg_.device_kind, x_size_, d_size_, rng, dev_[0]);
+  }
+}
+
+Tile::Tile(const ab200_tile_config &cfg, int cuda_device) : cfg_(cfg) {
+  x_size_ = cfg.x_size;
+  d_size_ = cfg.d_size;
+  if (x_size_ <= 0 || d_size_ <= 0) {
+    AB200_FATAL("tile sizes must be positive");
+  }
+  f_io_ = resolveIO(cfg.forward_io, false);
+  b_io_ = resolveIO(cfg.backward_io, true);
+  up_ = resolveUp(cfg.update);
+  if (cfg.device_kind < AB200_DEVICE_IDEAL || cfg.device_kind > AB200_DEVICE_TRANSFER) {
+    AB200_FATAL("device kind not implemented");
+  }
+  if (cfg.device_kind == AB200_DEVICE_TRANSFER) {
+    const ab200_transfer_params &t = cfg.transfer;
+    if (t.gamma != 0.0f) {
+      AB200_FATAL("Transfer: only gamma = 0 (fully hidden fast tile) is implemented");
+    }
+    if (!t.transfer_columns) {
+      AB200_FATAL("Transfer: row transfer is not implemented");
+    }
+    if (t.n_reads_per_transfer < 0) {
+      AB200_FATAL("Transfer: n_reads_per_transfer must be >= 0");
+    }
+    // transfer IO: noise and bound management are turned off (rpu_transfer_device.cpp:208-217)
+    ab200_io_params tio = t.transfer_io;
+    tio.noise_management = AB200_NM_NONE;
+    tio.bound_management = AB200_BM_NONE;
+    t_io_ = resolveIO(tio, false);
+    t_up_ = resolveUp(t.transfer_up);
+  }
+  setSeed(cfg.seed);
+  populateHost();
+  host_w_dx_.assign((size_t)x_size_ * d_size_, 0.0f);
+  if (cuda_device >= 0) {
+    toDevice(cuda_device);
+  }
+}
+
+void Tile::setSeed(uint64_t seed) {
+  if (seed == 0) {
+    seed = (uint64_t)std::chrono::high_resolution_clock::now().time_since_epoch().count();
+  }
+  key_.k0 = (uint32_t)seed;
+  key_.k1 = (uint32_t)(seed >> 32) ^ 0x5bd1e995u;
+  fwd_calls_ = bwd_calls_ = upd_calls_ = transfer_calls_ = 0;
+}
+
+Tile::~Tile() {
+  if (device_ >= 0) {
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(device_);
+    cudaFree(w_owned_);
+    cudaFree(w_fast_);
+    for (int k = 0; k < 2; k++) {
+      cudaFree(dev_[k].par4);
+      cudaFree(dev_[k].par2);
+    }
+    cudaFree(scale_);
+    cudaFree(factor_);
+    cudaFree(vnorm_);
+    cudaFree(sval_);
+    cudaFree(flags_);
+    cudaFree(bm_stats_);
+    cudaFree(xw_);
+    cudaFree(dw_);
+    cudaFree(onehot_);
+    cudaFree(tread_);
+    cudaFree(stage_dev_);
+    cudaFreeHost(stage_pinned_);
+    if (prev >= 0) {
+      cudaSetDevice(prev);
+    }
+  }
+}
+
+void Tile::requireDevice(const char *what) const {
+  if (device_ < 0) {
+    AB200_FATAL(what << ": the analog tile has no CPU compute path; move it to a CUDA device first");
+  }
+  AB200_CUDA(cudaSetDevice(device_));
+}
+
+void Tile::uploadDeviceStore(DeviceStore &ds) {
+  if (ds.kind == AB200_DEVICE_IDEAL) {
+    return;
+  }
+  const size_t size = (size_t)x_size_ * d_size_;
+  std::vector<float4> p4(size);
+  std::vector<float2> p2(size);
+  const float *wmax = &ds.host[0 * size], *wmin = &ds.host[1 * size], *sup = &ds.host[2 * size],
+              *sdown = &ds.host[3 * size];
+  const float *e0 = nullptr, *e1 = nullptr;
+  if (ds.kind == AB200_DEVICE_LINEAR_STEP || ds.kind == AB200_DEVICE_SOFT_BOUNDS) {
+    e0 = &ds.host[8 * size];
+    e1 = &ds.host[9 * size];
+  } else if (ds.kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE) {
+    e0 = &ds.host[8 * size];
+  }
+  for (int i = 0; i < d_size_; i++) {
+    for (int j = 0; j < x_size_; j++) {
+      size_t src = (size_t)i * x_size_ + j, dst = (size_t)j * d_size_ + i;
+      p4[dst] = make_float4(sup[src], sdown[src], wmax[src], wmin[src]);
+      p2[dst] = make_float2(e0 ? e0[src] : 0.0f, e1 ? e1[src] : 0.0f);
+    }
+  }
+  if (!ds.par4) {
+    AB200_CUDA(cudaMalloc(&ds.par4, size * sizeof(float4)));
+    AB200_CUDA(cudaMalloc(&ds.par2, size * sizeof(float2)));
+  }
+  AB200_CUDA(cudaMemcpy(ds.par4, p4.data(), size * sizeof(float4), cudaMemcpyHostToDevice));
+  AB200_CUDA(cudaMemcpy(ds.par2, p2.data(), size * sizeof(float2), cudaMemcpyHostToDevice));
+}
+
+void Tile::toDevice(int cuda_device) {
+  if (device_ >= 0) {
+    if (device_ == cuda_device) {
+      return;
+    }
+    AB200_FATAL("tile already lives on CUDA device " << device_);
+  }
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || cuda_device >= count) {
+    AB200_FATAL("CUDA device " << cuda_device << " is not available ("
+                               << (e != cudaSuccess ? cudaGetErrorString(e) : "index out of range")
+                               << "); the analog tile has no CPU fallback");
+  }
+  AB200_CUDA(cudaSetDevice(cuda_device));
+  device_ = cuda_device;
+  const size_t size = (size_t)x_size_ * d_size_;
+  AB200_CUDA(cudaMalloc(&w_owned_, size * sizeof(float)));
+  w_ = w_owned_;
+  if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+    AB200_CUDA(cudaMalloc(&w_fast_, size * sizeof(float)));
+    AB200_CUDA(cudaMemset(w_fast_, 0, size * sizeof(float)));
+    AB200_CUDA(cudaMalloc(&onehot_, (size_t)x_size_ * sizeof(float)));
+    AB200_CUDA(cudaMalloc(&tread_, (size_t)d_size_ * sizeof(float)));
+  }
+  AB200_CUDA(cudaMalloc(&bm_stats_, 2 * sizeof(int)));
+  AB200_CUDA(cudaMemset(bm_stats_, 0, 2 * sizeof(int)));
+  for (int k = 0; k < n_dev_; k++) {
+    uploadDeviceStore(dev_[k]);
+  }
+  std::vector<float> w = host_w_dx_;
+  setWeights(w.data());
+  host_w_dx_.clear();
+  host_w_dx_.shrink_to_fit();
+}
+
+void Tile::ensureScratch(int m) {
+  if (m <= scratch_m_) {
+    return;
+  }
+  AB200_CUDA(cudaDeviceSynchronize());
+  cudaFree(scale_);
+  cudaFree(factor_);
+  cudaFree(vnorm_);
+  cudaFree(sval_);
+  cudaFree(flags_);
+  cudaFree(xw_);
+  cudaFree(dw_);
+  int cap = m + m / 4 + 16;
+  AB200_CUDA(cudaMalloc(&scale_, (size_t)cap * sizeof(float)));
+  AB200_CUDA(cudaMalloc(&factor_, (size_t)cap * sizeof(float)));
+  AB200_CUDA(cudaMalloc(&vnorm_, (size_t)cap * sizeof(float)));
+  AB200_CUDA(cudaMalloc(&sval_, (size_t)cap * sizeof(float)));
+  AB200_CUDA(cudaMalloc(&flags_, (size_t)cap * sizeof(int)));
+  xw_ = dw_ = nullptr;
+  if (cfg_.device_kind != AB200_DEVICE_IDEAL && up_.pulse_type != AB200_PULSE_NONE) {
+    AB200_CUDA(cudaMalloc(&xw_, (size_t)cap * x_size_ * sizeof(uint32_t)));
+    AB200_CUDA(cudaMalloc(&dw_, (size_t)cap * d_size_ * sizeof(uint32_t)));
+  }
+  scratch_m_ = cap;
+}
+
+void Tile::ensureStage(size_t n_floats) {
+  if (n_floats <= stage_floats_) {
+    return;
+  }
+  AB200_CUDA(cudaDeviceSynchronize());
+  cudaFree(stage_dev_);
+  cudaFreeHost(stage_pinned_);
+  AB200_CUDA(cudaMalloc(&stage_dev_, n_floats * sizeof(float)));
+  AB200_CUDA(cudaMallocHost(&stage_pinned_, n_floats * sizeof(float)));
+  stage_floats_ = n_floats;
+}
+
+// ---------------------------------------------------------------------------------------------
+// weights
+// ---------------------------------------------------------------------------------------------
+void Tile::setWeights(const float *w_host_dx) {
+  const size_t size = (size_t)x_size_ * d_size_;
+  if (device_ < 0) {
+    // host carrier: clip to the (slow / only) device's bounds like onSetWeights
+    host_w_dx_.assign(w_host_dx, w_host_dx + size);
+    const DeviceStore &ds = dev_[n_dev_ - 1];
+    if (ds.kind != AB200_DEVICE_IDEAL) {
+      for (size_t k = 0; k < size; k++) {
+        host_w_dx_[k] = std::max(std::min(host_w_dx_[k], ds.host[k]), ds.host[size + k]);
+      }
+    }
+    return;
+  }
+  requireDevice("set_weights");
+  std::vector<float> t(size);
+  for (int i = 0; i < d_size_; i++) {
+    for (int j = 0; j < x_size_; j++) {
+      t[(size_t)j * d_size_ + i] = w_host_dx[(size_t)i * x_size_ + j];
+    }
+  }
+  AB200_CUDA(cudaMemcpy(w_, t.data(), size * sizeof(float), cudaMemcpyHostToDevice));
+  setWeightsDevice(nullptr, nullptr);
+}
+
+void Tile::setWeightsDevice(const float *w_dev_xd, cudaStream_t s) {
+  requireDevice("set_weights");
+  const size_t size = (size_t)x_size_ * d_size_;
+  if (w_dev_xd && w_dev_xd != w_) {
+    AB200_CUDA(cudaMemcpyAsync(w_, w_dev_xd, size * sizeof(float), cudaMemcpyDeviceToDevice, s));
+  }
+  // RPUPulsed::setWeights -> onSetWeights (rpu_pulsed.cpp:288-292): clip to device bounds;
+  // Transfer additionally zeroes the fast tile and resets its counters
+  // (rpu_transfer_device.cpp:559-602).
+  DeviceStore &ds = dev_[n_dev_ - 1];
+  if (ds.kind != AB200_DEVICE_IDEAL) {
+    launchClipToBounds(w_, ds.par4, (long long)size, s);
+  }
+  if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+    AB200_CUDA(cudaMemsetAsync(w_fast_, 0, size * sizeof(float), s));
+    update_idx_ = 0;
+    slice_idx_ = 0;
+  }
+  AB200_CUDA(cudaStreamSynchronize(s));
+}
+
+void Tile::getWeights(float *w_host_dx) {
+  const size_t size = (size_t)x_size_ * d_size_;
+  if (device_ < 0) {
+    std::memcpy(w_host_dx, host_w_dx_.data(), size * sizeof(float));
+    return;
+  }
+  requireDevice("get_weights");
+  std::vector<float> t(size);
+  AB200_CUDA(cudaDeviceSynchronize());
+  AB200_CUDA(cudaMemcpy(t.data(), w_, size * sizeof(float), cudaMemcpyDeviceToHost));
+  for (int i = 0; i < d_size_; i++) {
+    for (int j = 0; j < x_size_; j++) {
+      w_host_dx[(size_t)i * x_size_ + j] = t[(size_t)j * d_size_ + i];
+    }
+  }
+}
+
+void Tile::getWeightsDevice(float *w_dev_xd, cudaStream_t s) {
+  requireDevice("get_weights");
+  AB200_CUDA(cudaMemcpyAsync(w_dev_xd, w_, (size_t)x_size_ * d_size_ * sizeof(float),
+                             cudaMemcpyDeviceToDevice, s));
+}
+
+void Tile::setSharedWeights(float *w_dev_xd, uint64_t version) {
+  requireDevice("set_shared_weights");
+  if (!w_dev_xd) {
+    AB200_FATAL("set_shared_weights: null pointer");
+  }
+  w_ = w_dev_xd;
+  shared_version_ = version;
+}
+
+// ---------------------------------------------------------------------------------------------
+// hidden parameters: [name][d][x], names as the reference reports them
+// (PulsedRPUDevice::getDPNames rpu_pulsed_device.cpp:235-253; VectorRPUDevice :188-203)
+// ---------------------------------------------------------------------------------------------
+int Tile::hiddenCount() const {
+  if (cfg_.device_kind == AB200_DEVICE_IDEAL) {
+    return 0;
+  }
+  if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+    return (int)dev_[0].names.size() + (int)dev_[1].names.size() + 2;
+  }
+  return (int)dev_[0].names.size();
+}
+
+const char *Tile::hiddenName(int i) const {
+  static thread_local std::string buf;
+  if (i < 0 || i >= hiddenCount()) {
+    return "";
+  }
+  if (cfg_.device_kind != AB200_DEVICE_TRANSFER) {
+    return dev_[0].names[i].c_str();
+  }
+  int n0 = (int)dev_[0].names.size();
+  int k = i <= n0 ? 0 : 1;
+  int local = k == 0 ? i : i - n0 - 1;
+  int nk = (int)dev_[k].names.size();
+  buf = local < nk ? dev_[k].names[local] + "_" + std::to_string(k)
+                   : "hidden_weights_" + std::to_string(k);
+  return buf.c_str();
+}
+
+void Tile::getHidden(float *out) {
+  const size_t size = (size_t)x_size_ * d_size_;
+  if (cfg_.device_kind == AB200_DEVICE_IDEAL) {
+    return;
+  }
+  if (cfg_.device_kind != AB200_DEVICE_TRANSFER) {
+    std::memcpy(out, dev_[0].host.data(), dev_[0].host.size() * sizeof(float));
+    return;
+  }
+  float *o = out;
+  for (int k = 0; k < 2; k++) {
+    std::memcpy(o, dev_[k].host.data(), dev_[k].host.size() * sizeof(float));
+    o += dev_[k].host.size();
+    // hidden weights of device k: fast tile A for k = 0, the visible weights for k = 1
+    if (device_ >= 0) {
+      requireDevice("get_hidden_parameters");
+      std::vector<float> t(size);
+      AB200_CUDA(cudaDeviceSynchronize());
+      AB200_CUDA(cudaMemcpy(t.data(), k == 0 ? w_fast_ : w_, size * sizeof(float),
+                            cudaMemcpyDeviceToHost));
+      for (int i = 0; i < d_size_; i++) {
+        for (int j = 0; j < x_size_; j++) {
+          o[(size_t)i * x_size_ + j] = t[(size_t)j * d_size_ + i];
+        }
+      }
+    } else if (k == 1) {
+      std::memcpy(o, host_w_dx_.data(), size * sizeof(float));
+    } else {
+      std::memset(o, 0, size * sizeof(float));
+    }
+    o += size;
+  }
+}
+
+void Tile::setHidden(const float *in) {
+  const size_t size = (size_t)x_size_ * d_size_;
+  if (cfg_.device_kind == AB200_DEVICE_IDEAL) {
+    return;
+  }
+  const float *p = in;
+  for (int k = 0; k < n_dev_; k++) {
+    std::memcpy(dev_[k].host.data(), p, dev_[k].host.size() * sizeof(float));
+    p += dev_[k].host.size();
+    // PulsedRPUDevice::setDeviceParameter re-estimates dw_min from the given step sizes when it
+    // moved by more than 2 * dw_min_dtod (rpu_pulsed_device.cpp:319-334)
+    const float *sup = &dev_[k].host[2 * size], *sdown = &dev_[k].host[3 * size];
+    double acc = 0.0;
+    for (size_t e = 0; e < size; e++) {
+      acc += (fabsf(sup[e]) + fabsf(sdown[e])) / 2.0f;
+    }
+    float est = (float)(acc / (double)size);
+    if (fabsf(est - dev_[k].dw_min) / dev_[k].dw_min > 2.0f * cfg_.device[k].dw_min_dtod) {
+      dev_[k].dw_min = est;
+    }
+    if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+      if (device_ >= 0 && k == 0) {
+        requireDevice("set_hidden_parameters");
+        std::vector<float> t(size);
+        for (int i = 0; i < d_size_; i++) {
+          for (int j = 0; j < x_size_; j++) {
+            t[(size_t)j * d_size_ + i] = p[(size_t)i * x_size_ + j];
+          }
+        }
+        AB200_CUDA(cudaMemcpy(w_fast_, t.data(), size * sizeof(float), cudaMemcpyHostToDevice));
+      }
+      p += size;
+    }
+    if (device_ >= 0) {
+      requireDevice("set_hidden_parameters");
+      uploadDeviceStore(dev_[k]);
+    }
+  }
+  // weights are re-clipped to the new bounds (onSetWeights at the end of setDeviceParameter)
+  if (device_ >= 0) {
+    launchClipToBounds(w_, dev_[n_dev_ - 1].par4, (long long)size, nullptr);
+    if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+      launchClipToBounds(w_fast_, dev_[0].par4, (long long)size, nullptr);
+    }
+    AB200_CUDA(cudaDeviceSynchronize());
+  } else {
+    std::vector<float> w = host_w_dx_;
+    setWeights(w.data());
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward / backward
+// ---------------------------------------------------------------------------------------------
+void Tile::fillMvmScratch(MvmProblem &p) {
+  ensureScratch(p.m);
+  p.scale = scale_;
+  p.factor = factor_;
+  p.vnorm = vnorm_;
+  p.sval = sval_;
+  p.flags = flags_;
+  p.bm_stats = bm_stats_;
+  p.key = key_;
+}
+
+void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, bool d_trans,
+                   bool is_test, cudaStream_t s) {
+  (void)is_test; // "Noise will be always present" (rpu_forward_backward_pass.cpp:808-810)
+  requireDevice("forward");
+  if (m <= 0) {
+    return;
+  }
+  MvmProblem p{};
+  p.in = x;
+  const int x_in = x_size_ - (bias ? 1 : 0);
+  p.in_ss = x_trans ? 1 : x_in;
+  p.in_fs = x_trans ? m : 1;
+  p.in_size = x_size_;
+  p.in_real = x_in;
+  p.out = d;
+  p.out_ss = d_trans ? 1 : d_size_;
+  p.out_fs = d_trans ? m : 1;
+  p.out_size = d_size_;
+  p.out_store = d_size_;
+  p.accumulate = 0;
+  p.w = w_;
+  p.wk = d_size_;
+  p.wn = 1;
+  p.m = m;
+  p.backward = 0;
+  p.io = f_io_;
+  p.alpha = 1.0f;
+  p.call = fwd_calls_++;
+  p.noise_id = 0;
+  fillMvmScratch(p);
+  AB200_CUDA(cudaMemsetAsync(bm_stats_, 0, 2 * sizeof(int), s));
+  launchMvm(p, s);
+}
+
+void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_ss, int m,
+                          bool accumulate, uint32_t noise_id, cudaStream_t s) {
+  requireDevice("forward");
+  MvmProblem p{};
+  p.in = x;
+  p.in_ss = x_ss;
+  p.in_fs = 1;
+  p.in_size = x_size_;
+  p.in_real = x_size_;
+  p.out = y;
+  p.out_ss = y_ss;
+  p.out_fs = 1;
+  p.out_size = d_size_;
+  p.out_store = d_size_;
+  p.accumulate = accumulate ? 1 : 0;
+  p.w = w_;
+  p.wk = d_size_;
+  p.wn = 1;
+  p.m = m;
+  p.backward = 0;
+  p.io = f_io_;
+  p.alpha = 1.0f;
+  p.call = fwd_calls_++;
+  p.noise_id = noise_id;
+  fillMvmScratch(p);
+  launchMvm(p, s);
+}
+
+void Tile::backward(const float *d, float *x, bool bias, int m, bool d_trans, bool x_trans,
+                    cudaStream_t s) {
+  requireDevice("backward");
+  if (m <= 0) {
+    return;
+  }
+  MvmProblem p{};
+  const int x_out = x_size_ - (bias ? 1 : 0);
+  p.in = d;
+  p.in_ss = d_trans ? 1 : d_size_;
+  p.in_fs = d_trans ? m : 1;
+  p.in_size = d_size_;
+  p.in_real = d_size_;
+  p.out = x;
+  p.out_ss = x_trans ? 1 : x_out;
+  p.out_fs = x_trans ? m : 1;
+  p.out_size = x_size_;
+  p.out_store = x_out; // the bias column is computed but not returned (rpu.cpp:670-690)
+  p.accumulate = 0;
+  p.w = w_;
+  p.wk = 1; // W(k = d, n = x) = w[x * d_size + d]
+  p.wn = d_size_;
+  p.m = m;
+  p.backward = 1;
+  p.io = b_io_;
+  p.alpha = 1.0f;
+  p.call = bwd_calls_++;
+  p.noise_id = 0;
+  fillMvmScratch(p);
+  launchMvm(p, s);
+}
+
+void Tile::lastBmStats(int32_t *n_rerun, float *max_red) {
+  requireDevice("last_bm_stats");
+  int h[2] = {0, 0};
+  AB200_CUDA(cudaDeviceSynchronize());
+  AB200_CUDA(cudaMemcpy(h, bm_stats_, sizeof(h), cudaMemcpyDeviceToHost));
+  *n_rerun = h[0];
+  float f;
+  std::memcpy(&f, &h[1], sizeof(float));
+  *max_red = h[0] > 0 ? f : 1.0f;
+}
+
+// ---------------------------------------------------------------------------------------------
+// update
+// ---------------------------------------------------------------------------------------------
+float Tile::pulseCountLR() const {
+  // TransferRPUDevice::getPulseCountLearningRate (rpu_transfer_device.cpp:366-383)
+  if (cfg_.device_kind == AB200_DEVICE_TRANSFER && cfg_.transfer.fast_lr > 0.0f) {
+    return cfg_.transfer.scale_fast_lr ? cfg_.transfer.fast_lr * lr_ : cfg_.transfer.fast_lr;
+  }
+  return lr_;
+}
+
+void Tile::doTransfer(cudaStream_t s) {
+  // TransferRPUDevice::transfer / readAndUpdate (rpu_transfer_device.cpp:410-516): read the next
+  // n_reads columns of the fast tile with one-hot inputs, write each to the slow tile by a pulsed
+  // update with x = one-hot, d = read-out.
+  const ab200_transfer_params &t = cfg_.transfer;
+  float t_lr = t.scale_transfer_lr ? t.transfer_lr * lr_ : t.transfer_lr;
+  int n = std::min(t.n_reads_per_transfer, x_size_);
+  for (int k = 0; k < n; k++) {
+    int col = (slice_idx_ + k) % x_size_;
+    if (t_lr == 0.0f) {
+      continue;
+    }
+    uint32_t call = transfer_calls_++;
+    launchTransferRead(w_fast_, col, d_size_, t_io_, key_, call, onehot_, x_size_, tread_, s);
+    UpdateProblem u{};
+    u.x = onehot_;
+    u.x_ss = x_size_;
+    u.x_fs = 1;
+    u.x_real = x_size_;
+    u.d = tread_;
+    u.d_ss = d_size_;
+    u.d_fs = 1;
+    u.x_size = x_size_;
+    u.d_size = d_size_;
+    u.m = 1;
+    u.lr = fabsf(t_lr);
+    u.lr_neg = t_lr < 0.0f;
+    u.dw_min = dev_[1].dw_min;
+    u.up = t_up_;
+    u.key = key_;
+    u.call = 0x40000000u + call;
+    u.xw = xw_;
+    u.dw = dw_;
+    u.w = w_;
+    u.par4 = dev_[1].par4;
+    u.par2 = dev_[1].par2;
+    u.kind = dev_[1].kind;
+    u.dw_min_std = dev_[1].dw_min_std;
+    u.mult_noise = dev_[1].mult_noise;
+    u.s_begin = 0;
+    u.s_end = 1;
+    if (t_up_.pulse_type == AB200_PULSE_NONE) {
+      launchFPUpdate(u, t_lr, s);
+    } else {
+      launchPulsePrepare(u, s);
+      launchPulsedUpdate(u, s);
+    }
+  }
+  slice_idx_ = (slice_idx_ + n) % x_size_;
+}
+
+void Tile::update(const float *x, const float *d, bool bias, int m, bool x_trans, bool d_trans,
+                  cudaStream_t s) {
+  requireDevice("update");
+  if (m <= 0 || lr_ == 0.0f) {
+    return; // "if (!learning_rate) return" (rpu_weight_updater.cpp:206-208)
+  }
+  ensureScratch(m);
+  UpdateProblem u{};
+  const int x_in = x_size_ - (bias ? 1 : 0);
+  u.x = x;
+  u.x_ss = x_trans ? 1 : x_in;
+  u.x_fs = x_trans ? m : 1;
+  u.x_real = x_in;
+  u.d = d;
+  u.d_ss = d_trans ? 1 : d_size_;
+  u.d_fs = d_trans ? m : 1;
+  u.x_size = x_size_;
+  u.d_size = d_size_;
+  u.m = m;
+  u.key = key_;
+  u.call = upd_calls_++;
+  u.xw = xw_;
+  u.dw = dw_;
+  u.s_begin = 0;
+  u.s_end = m;
+
+  const bool fp_update = cfg_.device_kind == AB200_DEVICE_IDEAL || up_.pulse_type == AB200_PULSE_NONE;
+  if (fp_update) {
+    if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+      AB200_FATAL("Transfer with PulseType::None is not implemented");
+    }
+    u.w = w_;
+    launchFPUpdate(u, lr_, s);
+    if (up_.pulse_type == AB200_PULSE_NONE_WITH_DEVICE && dev_[0].kind != AB200_DEVICE_IDEAL) {
+      launchClipToBounds(w_, dev_[0].par4, (long long)x_size_ * d_size_, s);
+    }
+    return;
+  }
+  if (up_.pulse_type == AB200_PULSE_NONE_WITH_DEVICE) {
+    u.w = w_;
+    launchFPUpdate(u, lr_, s);
+    launchClipToBounds(w_, dev_[0].par4, (long long)x_size_ * d_size_, s);
+    return;
+  }
+
+  const float pc_lr = pulseCountLR();
+  u.lr = fabsf(pc_lr);
+  u.lr_neg = pc_lr < 0.0f;
+  u.up = up_;
+  u.dw_min = dev_[0].dw_min;
+  u.par4 = dev_[0].par4;
+  u.par2 = dev_[0].par2;
+  u.kind = dev_[0].kind;
+  u.dw_min_std = dev_[0].dw_min_std;
+  u.mult_noise = dev_[0].mult_noise;
+  launchPulsePrepare(u, s);
+
+  if (cfg_.device_kind != AB200_DEVICE_TRANSFER) {
+    u.w = w_;
+    launchPulsedUpdate(u, s);
+    return;
+  }
+
+  // Tiki-Taka: gradient pulses go to the fast tile; the batch is cut where the vector-update
+  // counter reaches a multiple of the transfer period (TransferRPUDevice::finishUpdateCycle,
+  // rpu_transfer_device.cpp:539-557; getTransferEvery :400-408).
+  u.w = w_fast_;
+  const ab200_transfer_params &t = cfg_.transfer;
+  long long every = t.units_in_mbatch ? (long long)std::ceil(t.transfer_every * (float)m)
+                                      : (long long)std::lround(t.transfer_every);
+  if (every < 0) {
+    every = 0;
+  }
+  int s0 = 0;
+  while (s0 < m) {
+    int s1 = m;
+    if (every > 0) {
+      long long to_next = every - (update_idx_ % every);
+      if (to_next < (long long)(m - s0)) {
+        s1 = s0 + (int)to_next;
+      }
+    }
+    u.s_begin = s0;
+    u.s_end = s1;
+    launchPulsedUpdate(u, s);
+    update_idx_ += s1 - s0;
+    if (every > 0 && update_idx_ % every == 0) {
+      doTransfer(s);
+    }
+    s0 = s1;
+  }
+}
+
+void Tile::coincidences(const float *x, const float *d, int32_t *counts, cudaStream_t s) {
+  requireDevice("coincidences");
+  if (cfg_.device_kind == AB200_DEVICE_IDEAL || up_.pulse_type == AB200_PULSE_NONE ||
+      up_.pulse_type == AB200_PULSE_NONE_WITH_DEVICE) {
+    AB200_FATAL("coincidences need a pulsed update");
+  }
+  ensureScratch(1);
+  UpdateProblem u{};
+  u.x = x;
+  u.x_ss = x_size_;
+  u.x_fs = 1;
+  u.x_real = x_size_;
+  u.d = d;
+  u.d_ss = d_size_;
+  u.d_fs = 1;
+  u.x_size = x_size_;
+  u.d_size = d_size_;
+  u.m = 1;
+  const float pc_lr = pulseCountLR();
+  u.lr = fabsf(pc_lr);
+  u.lr_neg = pc_lr < 0.0f;
+  u.up = up_;
+  u.dw_min = dev_[0].dw_min;
+  u.key = key_;
+  u.call = 0x7fffffffu;
+  u.xw = xw_;
+  u.dw = dw_;
+  launchPulsePrepare(u, s);
+  launchCoincidences(u, counts, s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host-buffer entry points: pinned staging + H2D, kernels, D2H, all on the caller's stream
+// ---------------------------------------------------------------------------------------------
+void Tile::forwardHost(const float *x, float *d, bool bias, int m, bool x_trans, bool d_trans,
+                       bool is_test, cudaStream_t s) {
+  requireDevice("forward");
+  const size_t nx = (size_t)m * (x_size_ - (bias ? 1 : 0)), nd = (size_t)m * d_size_;
+  ensureStage(nx + nd);
+  std::memcpy(stage_pinned_, x, nx * sizeof(float));
+  AB200_CUDA(cudaMemcpyAsync(stage_dev_, stage_pinned_, nx * sizeof(float), cudaMemcpyHostToDevice, s));
+  forward(stage_dev_, stage_dev_ + nx, bias, m, x_trans, d_trans, is_test, s);
+  AB200_CUDA(cudaMemcpyAsync(stage_pinned_ + nx, stage_dev_ + nx, nd * sizeof(float),
+                             cudaMemcpyDeviceToHost, s));
+  AB200_CUDA(cudaStreamSynchronize(s));
+  std::memcpy(d, stage_pinned_ + nx, nd * sizeof(float));
+}
+
+void Tile::backwardHost(const float *d, float *x, bool bias, int m, bool d_trans, bool x_trans,
+                        cudaStream_t s) {
+  requireDevice("backward");
+  const size_t nx = (size_t)m * (x_size_ - (bias ? 1 : 0)), nd = (size_t)m * d_size_;
+  ensureStage(nx + nd);
+  std::memcpy(stage_pinned_, d, nd * sizeof(float));
+  AB200_CUDA(cudaMemcpyAsync(stage_dev_, stage_pinned_, nd * sizeof(float), cudaMemcpyHostToDevice, s));
+  backward(stage_dev_, stage_dev_ + nd, bias, m, d_trans, x_trans, s);
+  AB200_CUDA(cudaMemcpyAsync(stage_pinned_ + nd, stage_dev_ + nd, nx * sizeof(float),
+                             cudaMemcpyDeviceToHost, s));
+  AB200_CUDA(cudaStreamSynchronize(s));
+  std::memcpy(x, stage_pinned_ + nd, nx * sizeof(float));
+}
+
+void Tile::updateHost(const float *x, const float *d, bool bias, int m, bool x_trans, bool d_trans,
+                      cudaStream_t s) {
+  requireDevice("update");
+  const size_t nx = (size_t)m * (x_size_ - (bias ? 1 : 0)), nd = (size_t)m * d_size_;
+  ensureStage(nx + nd);
+  std::memcpy(stage_pinned_, x, nx * sizeof(float));
+  std::memcpy(stage_pinned_ + nx, d, nd * sizeof(float));
+  AB200_CUDA(cudaMemcpyAsync(stage_dev_, stage_pinned_, (nx + nd) * sizeof(float),
+                             cudaMemcpyHostToDevice, s));
+  update(stage_dev_, stage_dev_ + nx, bias, m, x_trans, d_trans, s);
+  AB200_CUDA(cudaStreamSynchronize(s));
+}
+
+} // namespace ab200

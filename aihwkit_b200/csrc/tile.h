@@ -1,0 +1,226 @@
+// Host-side analog tile: the B200 counterpart of RPUSimple / RPUPulsed
+// (src/rpucuda/rpu.h:194-706, src/rpucuda/rpu_pulsed.h:23-125) for the hot path.
+#pragma once
+
+#include "../../include/aihwkit_b200.h"
+#include "common.cuh"
+
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace ab200 {
+
+// IOMetaParameter after initializeForForward / initializeForBackward
+// (src/rpucuda/rpu_pulsed_meta_parameter.cpp:40-128): resolutions already multiplied by
+// 2 * bound, infinite bounds resolved.
+struct IOEff {
+  int is_perfect;
+  int nm; // ab200_noise_management
+  int bm; // ab200_bound_management
+  int w_noise_type;
+  int bm_test_negative_bound;
+  int max_bm_factor;
+  float max_bm_res;
+  float inp_bound;
+  float res_in;
+  float out_bound;
+  float res_out;
+  float out_noise;
+  float out_scale;
+  float w_noise;
+  float nm_thres;
+};
+
+IOEff resolveIO(const ab200_io_params &io, bool backward);
+
+// PulsedUpdateMetaParameter after initialize() (rpu_pulsed_meta_parameter.cpp:134-151).
+struct UpEff {
+  int pulse_type;
+  int desired_bl;
+  int fixed_bl;
+  int update_management;
+  int update_bl_management;
+  float um_grad_scale;
+  float res;
+  float x_res_implicit;
+  float d_res_implicit;
+};
+
+UpEff resolveUp(const ab200_update_params &up);
+
+// One IO-managed matrix-vector batch: out[s][n] = IO( sum_k in[s][k] * W(k, n) ).
+struct MvmProblem {
+  const float *in;
+  long long in_ss, in_fs; // strides of sample / feature
+  int in_size;            // K (including an appended bias feature)
+  int in_real;            // features k >= in_real read as 1.0 (bias column)
+  float *out;
+  long long out_ss, out_fs;
+  int out_size;  // N
+  int out_store; // only n < out_store is written
+  int accumulate; // add to `out` instead of overwriting it
+  const float *w;
+  long long wk, wn; // W(k, n) = w[k * wk + n * wn]
+  int m;
+  int backward;
+  IOEff io;
+  float alpha; // fwd / bwd alpha scale of the tile (1 unless set)
+  PhiloxKey key;
+  uint32_t call;
+  uint32_t noise_id; // distinguishes tiles of a mapped array in the noise counter
+  // per-sample scratch (m entries each)
+  float *scale;  // input scale; 0 marks a row whose output is identically zero
+  float *factor; // output factor
+  float *vnorm;  // || prepared input ||_2 (only when weight noise is on)
+  float *sval;   // noise-management value s
+  int *flags;    // bound management: sample clipped in round 1
+  int *bm_stats; // [0] re-run samples, [1] max reduction (float bits)
+};
+
+void launchMvm(const MvmProblem &p, cudaStream_t stream);
+
+// Per-element device parameters in the update kernel's layout, index = x * d_size + d.
+struct DeviceStore {
+  int kind = AB200_DEVICE_IDEAL;
+  float dw_min = 0.001f;
+  float dw_min_std = 0.0f;
+  int mult_noise = 1;
+  float4 *par4 = nullptr; // {scale_up, scale_down, max_bound, min_bound}
+  float2 *par2 = nullptr; // {slope_up, slope_down} or {reference, 0}
+  // host copies, [name][d][x] in the reference's naming / order
+  std::vector<std::string> names;
+  std::vector<float> host;
+};
+
+struct UpdateProblem {
+  const float *x;
+  long long x_ss, x_fs;
+  int x_real; // features >= x_real read as 1.0 (bias)
+  const float *d;
+  long long d_ss, d_fs;
+  int x_size, d_size, m;
+  float lr;     // |pulse-count learning rate|
+  int lr_neg;   // learning rate negative
+  float dw_min; // weight granularity
+  UpEff up;
+  PhiloxKey key;
+  uint32_t call;
+  // scratch
+  uint32_t *xw; // [m][x_size] pulse words (or float bit patterns for implicit pulses)
+  uint32_t *dw; // [m][d_size]
+  // target
+  float *w;
+  const float4 *par4;
+  const float2 *par2;
+  int kind;
+  float dw_min_std;
+  int mult_noise;
+  int s_begin, s_end; // sample range applied by the update kernel
+};
+
+void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream);
+void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream);
+void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream);
+void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream);
+void launchTransferRead(const float *w_fast, int col, int d_size, const IOEff &io, PhiloxKey key,
+                        uint32_t call, float *x_onehot, int x_size, float *r_out,
+                        cudaStream_t stream);
+void launchTransposeDX(const float *src, float *dst, int rows, int cols, cudaStream_t stream);
+void launchClipToBounds(float *w, const float4 *par4, long long n, cudaStream_t stream);
+
+class Tile {
+public:
+  Tile(const ab200_tile_config &cfg, int cuda_device);
+  ~Tile();
+  Tile(const Tile &) = delete;
+  Tile &operator=(const Tile &) = delete;
+
+  int xSize() const { return x_size_; }
+  int dSize() const { return d_size_; }
+  int device() const { return device_; }
+  void toDevice(int cuda_device);
+
+  void setLearningRate(float lr) { lr_ = lr; }
+  float learningRate() const { return lr_; }
+  void setSeed(uint64_t seed);
+
+  void setWeights(const float *w_host_dx);
+  void getWeights(float *w_host_dx);
+  void setWeightsDevice(const float *w_dev_xd, cudaStream_t s);
+  void getWeightsDevice(float *w_dev_xd, cudaStream_t s);
+  void setSharedWeights(float *w_dev_xd, uint64_t version);
+
+  int hiddenCount() const;
+  const char *hiddenName(int i) const;
+  void getHidden(float *out);
+  void setHidden(const float *in);
+
+  void forward(const float *x, float *d, bool bias, int m, bool x_trans, bool d_trans,
+               bool is_test, cudaStream_t s);
+  void backward(const float *d, float *x, bool bias, int m, bool d_trans, bool x_trans,
+                cudaStream_t s);
+  void update(const float *x, const float *d, bool bias, int m, bool x_trans, bool d_trans,
+              cudaStream_t s);
+  void forwardHost(const float *x, float *d, bool bias, int m, bool x_trans, bool d_trans,
+                   bool is_test, cudaStream_t s);
+  void backwardHost(const float *d, float *x, bool bias, int m, bool d_trans, bool x_trans,
+                    cudaStream_t s);
+  void updateHost(const float *x, const float *d, bool bias, int m, bool x_trans, bool d_trans,
+                  cudaStream_t s);
+  void coincidences(const float *x, const float *d, int32_t *counts, cudaStream_t s);
+  void lastBmStats(int32_t *n_rerun, float *max_red);
+
+  // used by the mapped array: forward on a sub-block of a wider activation matrix
+  void forwardStrided(const float *x, long long x_ss, float *y, long long y_ss, int m,
+                      bool accumulate, uint32_t noise_id, cudaStream_t s);
+
+  const IOEff &fio() const { return f_io_; }
+  float *weightsXD() { return w_; }
+
+private:
+  void requireDevice(const char *what) const;
+  void ensureScratch(int m);
+  void ensureStage(size_t n_floats);
+  void uploadDeviceStore(DeviceStore &ds);
+  void populateHost();
+  void fillMvmScratch(MvmProblem &p);
+  void pulsedUpdateRange(UpdateProblem &p, cudaStream_t s);
+  void doTransfer(cudaStream_t s);
+  float pulseCountLR() const;
+
+  ab200_tile_config cfg_;
+  int x_size_, d_size_;
+  int device_ = -1;
+  float lr_ = 0.1f; // createRPUArray sets 0.1 (rpu_pulsed.cpp:54)
+  IOEff f_io_, b_io_, t_io_;
+  UpEff up_, t_up_;
+  PhiloxKey key_;
+  uint32_t fwd_calls_ = 0, bwd_calls_ = 0, upd_calls_ = 0, transfer_calls_ = 0;
+
+  std::vector<float> host_w_dx_; // only while the tile has no device
+  float *w_ = nullptr;           // device [x][d]
+  float *w_owned_ = nullptr;
+  uint64_t shared_version_ = 0;
+  float *w_fast_ = nullptr; // Transfer: fast (hidden) tile A, [x][d]
+  DeviceStore dev_[2];
+  int n_dev_ = 1;
+  // Transfer counters (rpu_transfer_device.cpp:396-516, rpu_vector_device.cpp:513-526)
+  long long update_idx_ = 0;
+  int slice_idx_ = 0;
+
+  // scratch
+  int scratch_m_ = 0;
+  float *scale_ = nullptr, *factor_ = nullptr, *vnorm_ = nullptr, *sval_ = nullptr;
+  int *flags_ = nullptr, *bm_stats_ = nullptr;
+  uint32_t *xw_ = nullptr, *dw_ = nullptr;
+  float *onehot_ = nullptr, *tread_ = nullptr;
+  // staging for the *_host entry points
+  float *stage_dev_ = nullptr;
+  float *stage_pinned_ = nullptr;
+  size_t stage_floats_ = 0;
+};
+
+} // namespace ab200

@@ -1,0 +1,538 @@
+// Pulsed weight update.
+//
+//   pulsePrepareKernel   per sample: |x|max, |d|max -> BL, A, B (update management), then the pulse
+//                        train of every x- and d-line packed into one 32-bit word (bit 0 = sign,
+//                        bits 1..BL = pulses), or the implicit pulse values for the deterministic
+//                        pulse type.
+//   pulsedUpdateKernel   per weight element: coincidences by AND + popc over the batch, device
+//                        rule applied pulse by pulse in place; weights and per-element parameters
+//                        are read with coalesced 128-bit loads, once per call.
+//
+// Reference semantics restated here:
+//   update management      src/rpucuda/rpu_pulsed_meta_parameter.cpp:153-236
+//   stochastic trains      src/rpucuda/sparse_bit_line_maker.cpp:200-238, 288-353
+//   implicit pulses        src/rpucuda/dense_bit_line_maker.cpp:210-264
+//   coincidence loop       src/rpucuda/rpu_weight_updater.cpp:236-291
+//   ConstantStep           src/rpucuda/rpu_constantstep_device.cpp:28-78
+//   LinearStep/SoftBounds  src/rpucuda/rpu_linearstep_device.cpp:113-164
+//   SoftBoundsReference    src/rpucuda/rpu_softbounds_reference_device.cpp:107-175
+#include "mvm_common.cuh"
+#include "tile.h"
+
+namespace ab200 {
+
+__device__ __forceinline__ float blockMax(float v, float *sh) {
+  for (int o = 16; o > 0; o >>= 1) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  }
+  int w = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) {
+    sh[w] = v;
+  }
+  __syncthreads();
+  float r = 0.0f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); i++) {
+    r = fmaxf(r, sh[i]);
+  }
+  __syncthreads();
+  return r;
+}
+
+// calculateBlAB + performUpdateManagement, fp32 with the reference's association
+// (rpu_pulsed_meta_parameter.cpp:153-236). BL == 0 means "no update for this sample".
+__device__ __forceinline__ void
+blAB(const UpEff &up, float lr, float dw_min, float xm, float dm, int &BL, float &A, float &B) {
+  if (lr == 0.0f) {
+    BL = 0;
+    A = B = 0.0f;
+    return;
+  }
+  if (up.fixed_bl || up.update_bl_management) {
+    BL = up.desired_bl;
+    A = __fsqrt_rn(__fdiv_rn(lr, __fmul_rn(dw_min, (float)BL)));
+    B = A;
+  } else {
+    if (__fmul_rn(dw_min, (float)up.desired_bl) < lr) {
+      A = B = 1.0f;
+      BL = max((int)ceilf(__fdiv_rn(lr, dw_min)), 1);
+    } else {
+      BL = up.desired_bl;
+      A = __fsqrt_rn(__fdiv_rn(lr, __fmul_rn(dw_min, (float)BL)));
+      B = A;
+    }
+  }
+  if (up.update_bl_management || up.update_management) {
+    if (xm == 0.0f || dm == 0.0f) {
+      BL = 0;
+      A = B = 1.0f;
+      return;
+    }
+    float x_val = xm;
+    float d_val = __fmul_rn(up.um_grad_scale, dm);
+    float k_val = __fdiv_rn(__fmul_rn(__fmul_rn(lr, x_val), d_val), dw_min);
+    if (up.update_bl_management) {
+      BL = (int)ceilf(k_val);
+      if (BL > up.desired_bl) {
+        BL = up.desired_bl;
+      }
+      A = __fsqrt_rn(__fdiv_rn(lr, __fmul_rn(dw_min, (float)BL)));
+      B = A;
+    }
+    if (up.update_management) {
+      if (k_val > (float)up.desired_bl) {
+        d_val = __fmul_rn(d_val, __fdiv_rn((float)up.desired_bl, k_val));
+      }
+      A = __fmul_rn(A, __fsqrt_rn(__fdiv_rn(x_val, d_val)));
+      B = __fmul_rn(B, __fsqrt_rn(__fdiv_rn(d_val, x_val)));
+    }
+  }
+}
+
+// One stochastic pulse train (generateCounts, sparse_bit_line_maker.cpp:200-238): BL Bernoulli
+// draws with probability pp; each draw compares pp against a 16-bit uniform, 8 draws per
+// Philox word pair.
+__device__ __forceinline__ uint32_t
+pulseTrain(float pp, int BL, PhiloxKey key, uint32_t line, uint32_t sample, uint32_t call,
+           uint32_t tag) {
+  float thr = pp * 65536.0f;
+  uint32_t bits = 0;
+  int k = 0;
+  for (int q = 0; q * 8 < BL; q++) {
+    uint32_t r[4];
+    philox4x32_10(line, sample, call, tag + (uint32_t)q, key, r);
+#pragma unroll
+    for (int h = 0; h < 8; h++) {
+      uint32_t u16 = (r[h >> 1] >> ((h & 1) * 16)) & 0xFFFFu;
+      if (k < BL && ((float)u16 + 0.5f) < thr) {
+        bits |= 1u << (k + 1);
+      }
+      k++;
+    }
+  }
+  return bits;
+}
+
+__global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
+  __shared__ float sh[8];
+  __shared__ float s_A, s_B;
+  __shared__ int s_BL;
+  const int s = blockIdx.x;
+  const float *xr = p.x + (long long)s * p.x_ss;
+  const float *dr = p.d + (long long)s * p.d_ss;
+  const bool need_max = p.up.update_management || p.up.update_bl_management;
+  float xm = 0.0f, dm = 0.0f;
+  if (need_max) {
+    for (int j = threadIdx.x; j < p.x_size; j += blockDim.x) {
+      xm = fmaxf(xm, fabsf(j < p.x_real ? xr[(long long)j * p.x_fs] : 1.0f));
+    }
+    for (int i = threadIdx.x; i < p.d_size; i += blockDim.x) {
+      dm = fmaxf(dm, fabsf(dr[(long long)i * p.d_fs]));
+    }
+    xm = blockMax(xm, sh);
+    dm = blockMax(dm, sh);
+  }
+  if (threadIdx.x == 0) {
+    int BL;
+    float A, B;
+    blAB(p.up, p.lr, p.dw_min, xm, dm, BL, A, B);
+    s_BL = BL;
+    s_A = A;
+    s_B = B;
+  }
+  __syncthreads();
+  const int BL = s_BL;
+  const float A = s_A, B = s_B;
+  uint32_t *xw = p.xw + (long long)s * p.x_size;
+  uint32_t *dw = p.dw + (long long)s * p.d_size;
+  const bool implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT;
+
+  for (int l = threadIdx.x; l < p.x_size + p.d_size; l += blockDim.x) {
+    const bool is_x = l < p.x_size;
+    const int idx = is_x ? l : l - p.x_size;
+    float v = is_x ? (idx < p.x_real ? xr[(long long)idx * p.x_fs] : 1.0f)
+                   : dr[(long long)idx * p.d_fs];
+    const float P = is_x ? B : A;
+    uint32_t word;
+    if (implicit) {
+      // generateDetImplicit (dense_bit_line_maker.cpp:210-238); d-values carry the factor BL
+      // (generateCoincidencesDetI :240-264)
+      float vv = p.lr_neg ? -v : v;
+      float pp = discretize(__fmul_rn(fabsf(vv), P), is_x ? p.up.x_res_implicit : p.up.d_res_implicit);
+      pp = fmaxf(fminf(pp, 1.0f), 0.0f);
+      float sv = vv >= 0.0f ? pp : -pp;
+      if (BL == 0) {
+        sv = 0.0f;
+      }
+      if (!is_x) {
+        sv = __fmul_rn(sv, (float)BL);
+      }
+      word = __float_as_uint(sv);
+    } else {
+      word = 0;
+      if (BL > 0) {
+        float pp = discretize(__fmul_rn(fabsf(v), P), p.up.res);
+        if (pp != 0.0f) {
+          uint32_t neg = v > 0.0f ? 0u : 1u;
+          if (!is_x && p.lr_neg) {
+            neg ^= 1u;
+          }
+          word = pulseTrain(pp, BL, p.key, (uint32_t)idx, (uint32_t)s, p.call,
+                            is_x ? TAG_PULSE_X : TAG_PULSE_D);
+          word = word ? (word | neg) : 0u;
+        }
+      }
+    }
+    (is_x ? xw : dw)[idx] = word;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// device rules: one pulse, clipped immediately. `down` = weight decreases.
+// par4 = {scale_up, scale_down, max_bound, min_bound}
+// ---------------------------------------------------------------------------------------------
+template <int KIND>
+__device__ __forceinline__ float
+pulseOnce(float w, bool down, const float4 &q, const float2 &e, float xi, int mult_noise) {
+  if (KIND == AB200_DEVICE_CONSTANT_STEP) {
+    float dw = __fmul_rn(__fadd_rn(1.0f, xi), down ? q.y : q.x);
+    w = down ? __fsub_rn(w, dw) : __fadd_rn(w, dw);
+    w = fminf(w, q.z);
+    w = fmaxf(w, q.w);
+    return w;
+  } else if (KIND == AB200_DEVICE_LINEAR_STEP) {
+    float slope = down ? e.y : e.x;
+    float sc = down ? q.y : q.x;
+    float dw;
+    if (mult_noise) {
+      dw = __fmul_rn(__fadd_rn(__fmul_rn(slope, w), sc), __fadd_rn(1.0f, xi));
+    } else {
+      dw = __fadd_rn(__fmul_rn(slope, w), __fmul_rn(sc, __fadd_rn(1.0f, xi)));
+    }
+    w = down ? __fsub_rn(w, dw) : __fadd_rn(w, dw);
+    w = fmaxf(w, q.w);
+    w = fminf(w, q.z);
+    return w;
+  } else { // SOFT_BOUNDS_REFERENCE
+    float ref = e.x;
+    w = __fadd_rn(w, ref);
+    float bound = down ? q.w : q.z;
+    bool ok = down ? (bound < 0.0f) : (bound > 0.0f);
+    float a = ok ? __fdiv_rn(w, bound) : 0.0f;
+    float sc = down ? q.y : q.x;
+    float dw;
+    if (mult_noise) {
+      dw = __fmul_rn(__fmul_rn(sc, __fsub_rn(1.0f, a)), __fadd_rn(1.0f, xi));
+    } else {
+      dw = __fmul_rn(sc, __fadd_rn(__fsub_rn(1.0f, a), xi));
+    }
+    w = down ? __fsub_rn(w, dw) : __fadd_rn(w, dw);
+    w = fmaxf(w, q.w);
+    w = fminf(w, q.z);
+    return __fsub_rn(w, ref);
+  }
+}
+
+constexpr int UT_I = 64;  // d-lines per CTA (contiguous in memory)
+constexpr int UT_J = 16;  // x-lines per CTA
+constexpr int UE_J = 4;   // x-lines per thread
+constexpr int UCHUNK = 64; // samples staged in shared memory at a time
+
+template <int KIND, bool IMPLICIT>
+__global__ void __launch_bounds__(256) pulsedUpdateKernel(UpdateProblem p) {
+  __shared__ uint32_t sx[UCHUNK][UT_J];
+  __shared__ uint32_t sd[UCHUNK][UT_I];
+  const int ti = threadIdx.x & (UT_I - 1);
+  const int tj = threadIdx.x / UT_I; // 0..3
+  const int i = blockIdx.x * UT_I + ti;
+  const int j0 = blockIdx.y * UT_J + tj * UE_J;
+  const bool i_ok = i < p.d_size;
+
+  float w[UE_J];
+  float4 q[UE_J];
+  float2 e[UE_J];
+  bool loaded[UE_J], dirty[UE_J];
+#pragma unroll
+  for (int t = 0; t < UE_J; t++) {
+    loaded[t] = false;
+    dirty[t] = false;
+    w[t] = 0.0f;
+    q[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+    e[t] = make_float2(0.f, 0.f);
+  }
+  const float std = p.dw_min_std;
+
+  for (int s0 = p.s_begin; s0 < p.s_end; s0 += UCHUNK) {
+    const int ns = min(UCHUNK, p.s_end - s0);
+    for (int t = threadIdx.x; t < ns * UT_J; t += blockDim.x) {
+      int ss = t / UT_J, jj = t % UT_J;
+      int gj = blockIdx.y * UT_J + jj;
+      sx[ss][jj] = gj < p.x_size ? p.xw[(long long)(s0 + ss) * p.x_size + gj] : 0u;
+    }
+    for (int t = threadIdx.x; t < ns * UT_I; t += blockDim.x) {
+      int ss = t / UT_I, ii = t % UT_I;
+      int gi = blockIdx.x * UT_I + ii;
+      sd[ss][ii] = gi < p.d_size ? p.dw[(long long)(s0 + ss) * p.d_size + gi] : 0u;
+    }
+    __syncthreads();
+    if (i_ok) {
+      for (int ss = 0; ss < ns; ss++) {
+        const uint32_t dwv = sd[ss][ti];
+        if (dwv == 0u) {
+          continue;
+        }
+#pragma unroll
+        for (int t = 0; t < UE_J; t++) {
+          const uint32_t xwv = sx[ss][tj * UE_J + t];
+          int n;
+          bool down;
+          if (IMPLICIT) {
+            // n = rint(d * BL * x), positive = decrease (dense_bit_line_maker.cpp:240-264)
+            float c = rintf(__fmul_rn(__uint_as_float(dwv), __uint_as_float(xwv)));
+            n = (int)fabsf(c);
+            down = c > 0.0f;
+          } else {
+            // coincidences of the two trains; equal line signs = decrease
+            // (rpu_weight_updater.cpp:246-268)
+            n = __popc((xwv & dwv) >> 1);
+            down = ((xwv ^ dwv) & 1u) == 0u;
+          }
+          if (n == 0) {
+            continue;
+          }
+          const int j = j0 + t;
+          if (j >= p.x_size) {
+            continue;
+          }
+          const long long idx = (long long)j * p.d_size + i;
+          if (!loaded[t]) {
+            w[t] = p.w[idx];
+            q[t] = p.par4[idx];
+            if (KIND != AB200_DEVICE_CONSTANT_STEP) {
+              e[t] = p.par2[idx];
+            }
+            loaded[t] = true;
+          }
+          dirty[t] = true;
+          float z[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int k = 0; k < n; k++) {
+            if (std > 0.0f && (k & 3) == 0) {
+              gauss4(p.key, (uint64_t)idx | ((uint64_t)(uint32_t)(s0 + ss) << 32), p.call,
+                     TAG_DEVICE + (uint32_t)(k >> 2), z);
+            }
+            w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], std * z[k & 3], p.mult_noise);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (i_ok) {
+#pragma unroll
+    for (int t = 0; t < UE_J; t++) {
+      if (dirty[t]) {
+        p.w[(long long)(j0 + t) * p.d_size + i] = w[t];
+      }
+    }
+  }
+}
+
+void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream) {
+  if (p.m <= 0) {
+    return;
+  }
+  if (p.up.pulse_type != AB200_PULSE_DETERMINISTIC_IMPLICIT && p.up.desired_bl > 31) {
+    AB200_FATAL("desired_BL > 31 is not implemented for stochastic pulse trains");
+  }
+  pulsePrepareKernel<<<p.m, 256, 0, stream>>>(p);
+  AB200_LAUNCH_CHECK();
+}
+
+void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream) {
+  if (p.s_end <= p.s_begin) {
+    return;
+  }
+  dim3 grid((p.d_size + UT_I - 1) / UT_I, (p.x_size + UT_J - 1) / UT_J);
+  const bool implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT;
+#define AB200_UPD(KIND)                                                                            \
+  if (implicit) {                                                                                  \
+    pulsedUpdateKernel<KIND, true><<<grid, 256, 0, stream>>>(p);                                   \
+  } else {                                                                                         \
+    pulsedUpdateKernel<KIND, false><<<grid, 256, 0, stream>>>(p);                                  \
+  }
+  switch (p.kind) {
+  case AB200_DEVICE_CONSTANT_STEP:
+    AB200_UPD(AB200_DEVICE_CONSTANT_STEP);
+    break;
+  case AB200_DEVICE_LINEAR_STEP:
+  case AB200_DEVICE_SOFT_BOUNDS:
+    AB200_UPD(AB200_DEVICE_LINEAR_STEP);
+    break;
+  case AB200_DEVICE_SOFT_BOUNDS_REFERENCE:
+    AB200_UPD(AB200_DEVICE_SOFT_BOUNDS_REFERENCE);
+    break;
+  default:
+    AB200_FATAL("pulsed update: device kind not implemented");
+  }
+#undef AB200_UPD
+  AB200_LAUNCH_CHECK();
+}
+
+// Signed coincidence counts of sample 0 as int32 [d][x] (DenseBitLineMaker::makeCoincidences).
+__global__ void coincidenceKernel(UpdateProblem p, int32_t *counts) {
+  long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= (long long)p.x_size * p.d_size) {
+    return;
+  }
+  int i = (int)(t / p.x_size), j = (int)(t % p.x_size);
+  uint32_t xwv = p.xw[j], dwv = p.dw[i];
+  int n;
+  if (p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT) {
+    n = dwv == 0u ? 0 : (int)rintf(__fmul_rn(__uint_as_float(dwv), __uint_as_float(xwv)));
+  } else {
+    n = __popc((xwv & dwv) >> 1);
+    if (((xwv ^ dwv) & 1u) != 0u) {
+      n = -n;
+    }
+  }
+  counts[t] = n;
+}
+
+void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream) {
+  long long n = (long long)p.x_size * p.d_size;
+  coincidenceKernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p, counts_dx);
+  AB200_LAUNCH_CHECK();
+}
+
+// Floating-point update W[x][d] -= lr * sum_s x[s][x] d[s][d] (RPUSimple::updateMatrix,
+// src/rpucuda/rpu.cpp:700-745), used by ideal devices / PulseType::None.
+__global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_signed) {
+  __shared__ float xs[16][16 + 1];
+  __shared__ float ds[16][64 + 1];
+  const int ti = threadIdx.x & 63, tj = threadIdx.x >> 6; // 64 d-lines x 4 groups of 4 x-lines
+  const int i = blockIdx.x * 64 + ti;
+  const int jb = blockIdx.y * 16;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s0 = 0; s0 < p.m; s0 += 16) {
+    {
+      int ss = threadIdx.x >> 4, jj = threadIdx.x & 15;
+      int gs = s0 + ss, gj = jb + jj;
+      float v = 0.0f;
+      if (gs < p.m && gj < p.x_size) {
+        v = gj < p.x_real ? p.x[(long long)gs * p.x_ss + (long long)gj * p.x_fs] : 1.0f;
+      }
+      xs[ss][jj] = v;
+    }
+    for (int t = threadIdx.x; t < 16 * 64; t += 256) {
+      int ss = t >> 6, ii = t & 63;
+      int gs = s0 + ss, gi = blockIdx.x * 64 + ii;
+      ds[ss][ii] = (gs < p.m && gi < p.d_size) ? p.d[(long long)gs * p.d_ss + (long long)gi * p.d_fs] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ss = 0; ss < 16; ss++) {
+      float dv = ds[ss][ti];
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        acc[t] = fmaf(xs[ss][tj * 4 + t], dv, acc[t]);
+      }
+    }
+    __syncthreads();
+  }
+  if (i < p.d_size) {
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      int j = jb + tj * 4 + t;
+      if (j < p.x_size) {
+        long long idx = (long long)j * p.d_size + i;
+        p.w[idx] = p.w[idx] - lr_signed * acc[t];
+      }
+    }
+  }
+}
+
+void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream) {
+  dim3 grid((p.d_size + 63) / 64, (p.x_size + 15) / 16);
+  fpUpdateKernel<<<grid, 256, 0, stream>>>(p, lr_signed);
+  AB200_LAUNCH_CHECK();
+}
+
+// Tiki-Taka read of one column of the fast tile: forward of a one-hot vector through the transfer
+// IO (noise and bound management off) with alpha = -1
+// (TransferRPUDevice::readVector / readAndUpdate, rpu_transfer_device.cpp:410-470). Also writes
+// the one-hot vector that the following pulsed write uses as its x input.
+__global__ void transferReadKernel(const float *w_fast, int col, int d_size, IOEff io,
+                                   PhiloxKey key, uint32_t call, float *x_onehot, int x_size,
+                                   float *r_out) {
+  int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < x_size) {
+    x_onehot[t] = t == col ? 1.0f : 0.0f;
+  }
+  if (t >= d_size) {
+    return;
+  }
+  float y;
+  if (io.is_perfect) {
+    y = w_fast[(long long)col * d_size + t] * (-io.out_scale);
+  } else {
+    float v = prepareInput(io, 1.0f, 1.0f);
+    float acc = __fmul_rn(w_fast[(long long)col * d_size + t], v);
+    float sigma = outputSigma(io, fabsf(v));
+    float z[4] = {0.f, 0.f, 0.f, 0.f};
+    if (sigma > 0.0f) {
+      gauss4(key, (uint64_t)(t >> 2), call, TAG_TRANSFER_READ, z);
+    }
+    bool ex = false;
+    y = finalizeOutput(io, acc, sigma, z[t & 3], ex);
+    y = __fmul_rn(y, __fmul_rn(io.out_scale, -1.0f));
+  }
+  r_out[t] = y;
+}
+
+void launchTransferRead(const float *w_fast, int col, int d_size, const IOEff &io, PhiloxKey key,
+                        uint32_t call, float *x_onehot, int x_size, float *r_out,
+                        cudaStream_t stream) {
+  int n = d_size > x_size ? d_size : x_size;
+  transferReadKernel<<<(n + 255) / 256, 256, 0, stream>>>(w_fast, col, d_size, io, key, call,
+                                                        x_onehot, x_size, r_out);
+  AB200_LAUNCH_CHECK();
+}
+
+// dst[c][r] = src[r][c]  (host [d][x] <-> device [x][d] conversions)
+__global__ void transposeKernel(const float *src, float *dst, int rows, int cols) {
+  __shared__ float tile[32][33];
+  int c = blockIdx.x * 32 + threadIdx.x, r = blockIdx.y * 32 + threadIdx.y;
+  for (int k = 0; k < 32; k += 8) {
+    if (c < cols && r + k < rows) {
+      tile[threadIdx.y + k][threadIdx.x] = src[(long long)(r + k) * cols + c];
+    }
+  }
+  __syncthreads();
+  int oc = blockIdx.y * 32 + threadIdx.x, orow = blockIdx.x * 32 + threadIdx.y;
+  for (int k = 0; k < 32; k += 8) {
+    if (oc < rows && orow + k < cols) {
+      dst[(long long)(orow + k) * rows + oc] = tile[threadIdx.x][threadIdx.y + k];
+    }
+  }
+}
+
+void launchTransposeDX(const float *src, float *dst, int rows, int cols, cudaStream_t stream) {
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  transposeKernel<<<grid, block, 0, stream>>>(src, dst, rows, cols);
+  AB200_LAUNCH_CHECK();
+}
+
+// PulsedRPUDevice::onSetWeights: clip to the per-element bounds (rpu_pulsed_device.cpp:545-571).
+__global__ void clipKernel(float *w, const float4 *par4, long long n) {
+  long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < n) {
+    float4 q = par4[t];
+    w[t] = fmaxf(fminf(w[t], q.z), q.w);
+  }
+}
+
+void launchClipToBounds(float *w, const float4 *par4, long long n, cudaStream_t stream) {
+  clipKernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w, par4, n);
+  AB200_LAUNCH_CHECK();
+}
+
+} // namespace ab200

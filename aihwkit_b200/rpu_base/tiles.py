@@ -1,0 +1,382 @@
+"""Mirror of ``aihwkit.simulator.rpu_base.tiles`` for the analog-tile hot path.
+
+Method names, argument order and error behaviour follow the reference's binding
+(``src/aihwkit/simulator/rpu_base_src/rpu_base_tiles.cpp:53-886`` and the CUDA overrides in
+``rpu_base_tiles_cuda.cpp:45-543``).  Every compute call goes through the C ABI of
+``include/aihwkit_b200.h`` into the sm_100a kernels; there is no CPU compute path.  torch is
+used only for device memory and streams.
+
+Differences from the reference binding, all forced by "GPU only":
+  * a tile created by ``AnalogTileParameter.create_array`` carries configuration, weights and the
+    host-drawn device parameters but cannot compute until ``.cuda()`` (or ``CudaAnalogTile(tile)``)
+    has moved it to a device;
+  * CUDA tensors are processed in place on the current torch stream; CPU tensors are accepted
+    too and are staged through pinned memory by the library (host -> device -> host per call).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from .. import _cabi
+from .._cabi import check
+
+
+def _stream_ptr(t: torch.Tensor) -> int:
+    return int(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _check_input(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"{name} must be a float32 tensor")
+    return t.contiguous()
+
+
+class AnalogTile:
+    """``tiles.AnalogTile`` / ``tiles.CudaAnalogTile`` (RPUPulsed / RPUCudaPulsed)."""
+
+    def __init__(self, config: _cabi.TileConfig, cuda_device: int = -1):
+        self._lib = _cabi.lib()
+        self._cfg = config
+        handle = C.c_void_p()
+        check(self._lib.ab200_tile_create(C.byref(config), int(cuda_device), C.byref(handle)))
+        self._h = handle
+        self._device_index = int(cuda_device)
+        self._shared: Optional[torch.Tensor] = None
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.ab200_tile_destroy(h)
+
+    # -- placement -------------------------------------------------------------------------
+    def cuda(self, device=None) -> "AnalogTile":
+        """Move the tile to a CUDA device (``CudaAnalogTile(cpu_tile)``,
+        rpu_base_tiles_cuda.cpp:532-538)."""
+        if device is None:
+            index = torch.cuda.current_device() if torch.cuda.is_available() else 0
+        else:
+            index = torch.device(device).index if not isinstance(device, int) else device
+            index = 0 if index is None else index
+        check(self._lib.ab200_tile_to_device(self._h, int(index)))
+        self._device_index = int(index)
+        return self
+
+    @property
+    def is_cuda(self) -> bool:
+        return self._device_index >= 0
+
+    # -- sizes / learning rate ---------------------------------------------------------------
+    def get_x_size(self) -> int:
+        return int(self._lib.ab200_tile_get_x_size(self._h))
+
+    def get_d_size(self) -> int:
+        return int(self._lib.ab200_tile_get_d_size(self._h))
+
+    def set_learning_rate(self, learning_rate: float) -> None:
+        check(self._lib.ab200_tile_set_learning_rate(self._h, float(learning_rate)))
+
+    def get_learning_rate(self) -> float:
+        out = C.c_float()
+        check(self._lib.ab200_tile_get_learning_rate(self._h, C.byref(out)))
+        return float(out.value)
+
+    def set_seed(self, seed: int) -> None:
+        check(self._lib.ab200_tile_set_seed(self._h, int(seed)))
+
+    # -- weights ---------------------------------------------------------------------------
+    def set_weights(self, weights: torch.Tensor) -> None:
+        """``[d_size, x_size]`` (rpu_base_tiles.cpp:150-178)."""
+        w = weights.detach().to(torch.float32).cpu().contiguous()
+        if tuple(w.shape) != (self.get_d_size(), self.get_x_size()):
+            raise RuntimeError(
+                f"Invalid weights dimensions: expected [{self.get_d_size()},{self.get_x_size()}] array"
+            )
+        check(self._lib.ab200_tile_set_weights(self._h, w.data_ptr()))
+
+    def get_weights(self) -> torch.Tensor:
+        """CPU tensor ``[d_size, x_size]`` (rpu_base_tiles.cpp:130-148)."""
+        w = torch.empty(self.get_d_size(), self.get_x_size(), dtype=torch.float32)
+        check(self._lib.ab200_tile_get_weights(self._h, w.data_ptr()))
+        return w
+
+    def set_weights_cuda(self, weights_xd: torch.Tensor) -> None:
+        """Device tensor ``[x_size, d_size]`` (probed by tiles/base.py:452-453)."""
+        w = _check_input(weights_xd, "weights")
+        if not w.is_cuda or tuple(w.shape) != (self.get_x_size(), self.get_d_size()):
+            raise RuntimeError("set_weights_cuda expects a CUDA [x_size, d_size] tensor")
+        check(self._lib.ab200_tile_set_weights_device(self._h, w.data_ptr(), _stream_ptr(w)))
+
+    def get_weights_cuda(self) -> torch.Tensor:
+        dev = torch.device("cuda", self._device_index)
+        w = torch.empty(self.get_x_size(), self.get_d_size(), dtype=torch.float32, device=dev)
+        check(self._lib.ab200_tile_get_weights_device(self._h, w.data_ptr(), _stream_ptr(w)))
+        return w
+
+    def set_shared_weights(self, weights_xd: torch.Tensor) -> None:
+        """Alias caller-owned ``[x_size, d_size]`` CUDA memory as the tile's weights
+        (rpu_base_tiles_cuda.cpp:96-124; src/rpucuda/cuda/rpucuda.cu:322-334)."""
+        if not weights_xd.is_cuda or weights_xd.dtype != torch.float32:
+            raise RuntimeError("set_shared_weights expects a float32 CUDA tensor")
+        if not weights_xd.is_contiguous() or weights_xd.numel() != self.get_x_size() * self.get_d_size():
+            raise RuntimeError("Shared weights need to be contiguous [x_size, d_size]")
+        self._shared = weights_xd
+        check(
+            self._lib.ab200_tile_set_shared_weights(
+                self._h, weights_xd.data_ptr(), int(weights_xd._version)
+            )
+        )
+
+    # -- hidden parameters ---------------------------------------------------------------------
+    def get_hidden_parameter_names(self) -> List[str]:
+        n = self._lib.ab200_tile_hidden_parameter_count(self._h)
+        return [self._lib.ab200_tile_hidden_parameter_name(self._h, i).decode() for i in range(n)]
+
+    def get_hidden_parameters(self) -> torch.Tensor:
+        """``[n, d_size, x_size]`` CPU tensor (rpu_base_tiles.cpp:764-789)."""
+        n = self._lib.ab200_tile_hidden_parameter_count(self._h)
+        if n == 0:
+            return torch.empty(0, dtype=torch.float32)
+        out = torch.empty(n, self.get_d_size(), self.get_x_size(), dtype=torch.float32)
+        check(self._lib.ab200_tile_get_hidden_parameters(self._h, out.data_ptr()))
+        return out
+
+    def set_hidden_parameters(self, hidden_parameters: torch.Tensor) -> None:
+        n = self._lib.ab200_tile_hidden_parameter_count(self._h)
+        if n == 0:
+            return
+        hp = hidden_parameters.detach().to(torch.float32).cpu().contiguous()
+        if tuple(hp.shape) != (n, self.get_d_size(), self.get_x_size()):
+            raise RuntimeError("Hidden parameter shape mismatch!")
+        check(self._lib.ab200_tile_set_hidden_parameters(self._h, hp.data_ptr()))
+
+    # -- the hot path ------------------------------------------------------------------------
+    def forward(
+        self, x_input: torch.Tensor, bias: bool = False, x_trans: bool = False,
+        d_trans: bool = False, is_test: bool = False, non_blocking: bool = False,
+    ) -> torch.Tensor:
+        """rpu_base_tiles.cpp:405-445 / rpu_base_tiles_cuda.cpp:160-205."""
+        x = _check_input(x_input, "x_input")
+        if x.dim() < 1:
+            raise RuntimeError("Invalid x_input dimensions: expected at least 1 dimensional tensor")
+        in_size = x.size(0) if x_trans else x.size(-1)
+        expected = self.get_x_size() - (1 if bias else 0)
+        if in_size != expected:
+            shape = f"[*, {expected}]" if x_trans else f"[{expected},*]"
+            raise RuntimeError(f"Invalid x_input dimensions: expected {shape} tensor")
+        m = x.numel() // in_size if in_size else 0
+        dims = list(x.shape)
+        if x_trans != d_trans:
+            # mixed layouts: the reference binding keeps the input's leading dims, which only
+            # fits when both flags agree; give the batch its own dimension instead
+            dims = [self.get_d_size(), m] if d_trans else [m, self.get_d_size()]
+        elif d_trans:
+            dims[0] = self.get_d_size()
+        else:
+            dims[-1] = self.get_d_size()
+        out = torch.empty(dims, dtype=torch.float32, device=x.device)
+        if x.is_cuda:
+            check(
+                self._lib.ab200_tile_forward(
+                    self._h, x.data_ptr(), out.data_ptr(), int(bias), m, int(x_trans), int(d_trans),
+                    int(is_test), _stream_ptr(x),
+                )
+            )
+            if not non_blocking:
+                torch.cuda.current_stream(x.device).synchronize()
+        else:
+            check(
+                self._lib.ab200_tile_forward_host(
+                    self._h, x.data_ptr(), out.data_ptr(), int(bias), m, int(x_trans), int(d_trans),
+                    int(is_test), None,
+                )
+            )
+        return out
+
+    def backward(
+        self, d_input: torch.Tensor, bias: bool = False, d_trans: bool = False,
+        x_trans: bool = False, non_blocking: bool = False,
+    ) -> torch.Tensor:
+        """rpu_base_tiles.cpp:473-512."""
+        d = _check_input(d_input, "d_input")
+        if d.dim() < 1:
+            raise RuntimeError("Invalid d_input dimensions: expected at least 1 dimensional tensor")
+        dsz = d.size(0) if d_trans else d.size(-1)
+        if dsz != self.get_d_size():
+            shape = f"[*, {self.get_d_size()}]" if d_trans else f"[{self.get_d_size()},*]"
+            raise RuntimeError(f"Invalid d_input dimensions: expected {shape} tensor")
+        m = d.numel() // dsz if dsz else 0
+        x_out = self.get_x_size() - (1 if bias else 0)
+        dims = list(d.shape)
+        if x_trans != d_trans:
+            dims = [x_out, m] if x_trans else [m, x_out]
+        elif x_trans:
+            dims[0] = x_out
+        else:
+            dims[-1] = x_out
+        out = torch.empty(dims, dtype=torch.float32, device=d.device)
+        if d.is_cuda:
+            check(
+                self._lib.ab200_tile_backward(
+                    self._h, d.data_ptr(), out.data_ptr(), int(bias), m, int(d_trans), int(x_trans),
+                    _stream_ptr(d),
+                )
+            )
+            if not non_blocking:
+                torch.cuda.current_stream(d.device).synchronize()
+        else:
+            check(
+                self._lib.ab200_tile_backward_host(
+                    self._h, d.data_ptr(), out.data_ptr(), int(bias), m, int(d_trans), int(x_trans), None
+                )
+            )
+        return out
+
+    def update(
+        self, x_input: torch.Tensor, d_input: torch.Tensor, bias: bool = False,
+        x_trans: bool = False, d_trans: bool = False, non_blocking: bool = False,
+    ) -> None:
+        """rpu_base_tiles.cpp:541-598 (4th / 5th positional arguments are x_trans, d_trans)."""
+        x = _check_input(x_input, "x_input")
+        d = _check_input(d_input, "d_input")
+        in_size = x.size(0) if x_trans else x.size(-1)
+        expected = self.get_x_size() - (1 if bias else 0)
+        dsz = d.size(0) if d_trans else d.size(-1)
+        if in_size != expected or dsz != self.get_d_size():
+            raise RuntimeError("Invalid x_input / d_input dimensions for update")
+        m = x.numel() // in_size if in_size else 0
+        if m != (d.numel() // dsz if dsz else 0):
+            raise RuntimeError("x_input and d_input need the same batch size")
+        if x.is_cuda != d.is_cuda:
+            raise RuntimeError("x_input and d_input need to live on the same device")
+        if x.is_cuda:
+            check(
+                self._lib.ab200_tile_update(
+                    self._h, x.data_ptr(), d.data_ptr(), int(bias), m, int(x_trans), int(d_trans),
+                    _stream_ptr(x),
+                )
+            )
+            if not non_blocking:
+                torch.cuda.current_stream(x.device).synchronize()
+        else:
+            check(
+                self._lib.ab200_tile_update_host(
+                    self._h, x.data_ptr(), d.data_ptr(), int(bias), m, int(x_trans), int(d_trans), None
+                )
+            )
+
+    # -- diagnostics -------------------------------------------------------------------------
+    def coincidences(self, x: torch.Tensor, d: torch.Tensor) -> torch.Tensor:
+        """Signed coincidence counts ``[d_size, x_size]`` (int32) of one sample."""
+        x = _check_input(x, "x").reshape(-1)
+        d = _check_input(d, "d").reshape(-1)
+        if x.numel() != self.get_x_size() or d.numel() != self.get_d_size() or not x.is_cuda:
+            raise RuntimeError("coincidences expects CUDA vectors of size x_size and d_size")
+        out = torch.empty(self.get_d_size(), self.get_x_size(), dtype=torch.int32, device=x.device)
+        check(
+            self._lib.ab200_tile_coincidences(
+                self._h, x.data_ptr(), d.data_ptr(), out.data_ptr(), _stream_ptr(x)
+            )
+        )
+        torch.cuda.current_stream(x.device).synchronize()
+        return out
+
+    def last_bm_stats(self):
+        n = C.c_int32()
+        r = C.c_float()
+        check(self._lib.ab200_tile_last_bm_stats(self._h, C.byref(n), C.byref(r)))
+        return int(n.value), float(r.value)
+
+    def get_brief_info(self) -> str:
+        return f"AnalogTile(B200, {self.get_d_size()}x{self.get_x_size()})"
+
+    __str__ = get_brief_info
+
+
+class FloatingPointTile(AnalogTile):
+    """``tiles.FloatingPointTile`` (RPUSimple): perfect IO and floating-point update."""
+
+    def __init__(self, x_size: int, d_size: int, cuda_device: int = -1):
+        from . import devices
+
+        par = devices.AnalogTileParameter()
+        par.forward_io.is_perfect = True
+        par.backward_io.is_perfect = True
+        par.update.pulse_type = devices.PulseType.None_
+        cfg = par._config(x_size, d_size, devices.IdealResistiveDeviceParameter())
+        super().__init__(cfg, cuda_device)
+
+
+def CudaAnalogTile(tile: AnalogTile, device=None) -> AnalogTile:
+    """``tiles.CudaAnalogTile(cpu_tile)`` (rpu_base_tiles_cuda.cpp:524-543)."""
+    return tile.cuda(device)
+
+
+def CudaFloatingPointTile(tile: FloatingPointTile, device=None) -> AnalogTile:
+    """``tiles.CudaFloatingPointTile(cpu_tile)`` (rpu_base_tiles_cuda.cpp:45-58)."""
+    return tile.cuda(device)
+
+
+class TileArray:
+    """Native mapped-tile layer (``TileModuleArray``, src/aihwkit/simulator/tiles/array.py:30-198).
+
+    ``in_split_range`` selects the in-splits this process materialises (sharded layer)."""
+
+    def __init__(self, config: _cabi.TileConfig, out_size: int, in_size: int,
+                 max_output_size: int, max_input_size: int, cuda_device: int = 0,
+                 in_split_range=None):
+        self._lib = _cabi.lib()
+        self.out_size, self.in_size = int(out_size), int(in_size)
+        begin, end = (0, -1) if in_split_range is None else in_split_range
+        h = C.c_void_p()
+        check(
+            self._lib.ab200_array_create(
+                C.byref(config), self.out_size, self.in_size, int(max_output_size),
+                int(max_input_size), int(begin), int(end), int(cuda_device), C.byref(h),
+            )
+        )
+        self._h = h
+        self.device = torch.device("cuda", int(cuda_device))
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.ab200_array_destroy(h)
+
+    @property
+    def num_in_splits(self) -> int:
+        return int(self._lib.ab200_array_num_in_splits(self._h))
+
+    @property
+    def num_out_splits(self) -> int:
+        return int(self._lib.ab200_array_num_out_splits(self._h))
+
+    def set_seed(self, seed: int) -> None:
+        check(self._lib.ab200_array_set_seed(self._h, int(seed)))
+
+    def set_weights(self, weight: torch.Tensor) -> None:
+        w = weight.detach().to(torch.float32).cpu().reshape(self.out_size, self.in_size).contiguous()
+        check(self._lib.ab200_array_set_weights(self._h, w.data_ptr()))
+
+    def get_weights(self) -> torch.Tensor:
+        w = torch.zeros(self.out_size, self.in_size, dtype=torch.float32)
+        check(self._lib.ab200_array_get_weights(self._h, w.data_ptr()))
+        return w
+
+    def forward(self, x_input: torch.Tensor, is_test: bool = True, non_blocking: bool = False) -> torch.Tensor:
+        x = _check_input(x_input, "x_input")
+        if x.size(-1) != self.in_size:
+            raise RuntimeError(f"Invalid x_input dimensions: expected [{self.in_size},*] tensor")
+        m = x.numel() // self.in_size
+        out = torch.empty(list(x.shape[:-1]) + [self.out_size], dtype=torch.float32, device=x.device)
+        if x.is_cuda:
+            check(self._lib.ab200_array_forward(self._h, x.data_ptr(), out.data_ptr(), m, int(is_test), _stream_ptr(x)))
+            if not non_blocking:
+                torch.cuda.current_stream(x.device).synchronize()
+        else:
+            check(self._lib.ab200_array_forward_host(self._h, x.data_ptr(), out.data_ptr(), m, int(is_test), None))
+        return out

@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the analog-tile hot path.
+
+Workload (N GPUs): "analog inference MVM" — a logical 4096 x 4096 weight (~N(0, 1/64)) mapped onto
+64 physical 512 x 512 tiles, batch of 8192 rows ~N(0, 1), forward only, 8-bit DAC / ADC,
+out_noise 0.04, additive-constant weight noise 0.0175, out_bound 10, ABS_MAX noise management,
+no bound management.  A step is one forward pass of the whole batch through all tiles; with N > 1
+the in-splits are sharded over the ranks and the partial outputs are summed to rank 0 with one
+NCCL reduce (strong scaling: the total work is fixed).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+`--impl reference` times the reference's own CPU tile (oracle/_ref, built from the reference's
+sources) on a bounded sample of the same workload on the host cores.
+
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(out_size=4096, in_size=4096, max_tile=512, batch=8192)
+METRIC = "analog_inference_rows_per_s"
+UNIT = "rows/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path, "r", encoding="utf-8") as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained"), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def inference_config(seed: int):
+    from aihwkit_b200.rpu_base import devices as D
+
+    p = D.AnalogTileParameter()
+    io = p.forward_io
+    io.inp_res = 1.0 / 254.0
+    io.out_res = 1.0 / 254.0
+    io.out_noise = 0.04
+    io.w_noise = 0.0175
+    io.w_noise_type = D.WeightNoiseType.AdditiveConstant
+    io.out_bound = 10.0
+    io.inp_bound = 1.0
+    io.noise_management = D.NoiseManagementType.AbsMax
+    io.bound_management = D.BoundManagementType.None_
+    p.update.pulse_type = D.PulseType.None_
+    return p._config(512, 512, D.IdealResistiveDeviceParameter(), seed=seed)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None,
+                    sm_max_mhz=max(smax) if smax else None, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's own CPU tile on a bounded sample
+# --------------------------------------------------------------------------------------------
+def _ref_worker(args):
+    """Runs `rows` input rows through the tiles `tile_ids` of the mapped layer with the reference
+    CPU tile (one C++ forward call per tile, as TileModuleArray does)."""
+    tile_ids, rows, seed, reps = args
+    from oracle import ref
+
+    cfg = inference_config(seed)
+    rng = np.random.default_rng(seed)
+    tiles = []
+    for tid in tile_ids:
+        t = ref.RefTile(cfg)
+        t.set_weights(rng.normal(0, 1.0 / 64.0, (512, 512)).astype(np.float32))
+        tiles.append(t)
+    x = rng.normal(0, 1, (rows, 512)).astype(np.float32)
+    for t in tiles[:1]:
+        t.forward(x[: max(1, rows // 8)], is_test=True)  # warm-up
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        for t in tiles:
+            t.forward(x, is_test=True)
+    return time.perf_counter() - t0
+
+
+def cpu_reference_rate(rows: int, reps: int = 1, workers=None):
+    """rows/s of the reference CPU tile for the full 64-tile layer, all host cores: the 64 tiles
+    are independent, so they are spread over `workers` processes (the analog CPU path itself is a
+    serial per-sample loop, src/rpucuda/rpu_pulsed.h:107)."""
+    from concurrent.futures import ProcessPoolExecutor
+    from oracle import ref
+
+    if not ref.available():
+        return None
+    n_tiles = (WORKLOAD["out_size"] // WORKLOAD["max_tile"]) * (WORKLOAD["in_size"] // WORKLOAD["max_tile"])
+    workers = workers or min(os.cpu_count() or 1, n_tiles)
+    os.environ.setdefault("OPENBLAS_NUM_THREADS", "1")
+    os.environ.setdefault("OMP_NUM_THREADS", "1")
+    chunks = [list(range(n_tiles))[i::workers] for i in range(workers)]
+    t0 = time.perf_counter()
+    with ProcessPoolExecutor(max_workers=workers) as ex:
+        times = list(ex.map(_ref_worker, [(c, rows, 17 + i, reps) for i, c in enumerate(chunks)]))
+    wall = time.perf_counter() - t0
+    busy = max(times)
+    return dict(value=rows * reps / busy, unit=UNIT, cores=workers, kind="reference",
+                sample=f"{rows} of {WORKLOAD['batch']} rows through all {n_tiles} tiles x {reps} "
+                       f"(reference CPU RPUPulsed, BLAS {ref.blas_name()}, 1 BLAS thread per "
+                       f"process, tiles spread over {workers} processes; wall {wall:.1f} s)",
+                seconds=busy)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = cpu_reference_rate(rows=args.ref_rows, reps=1)
+    if base is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/librpu_ref.so is not built or does not load on this box"}))
+        return
+    # K timed steps of the bounded sample (W warm-up steps are the worker's own warm-up call)
+    vals = [base["value"]]
+    for _ in range(max(0, min(args.steps, 3) - 1)):
+        vals.append(cpu_reference_rate(rows=args.ref_rows, reps=1)["value"])
+    v = statistics.median(vals)
+    base["value"] = v
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": len(vals), "warmup": args.warmup, "ms_per_step": 1e3 * WORKLOAD["batch"] / v,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "cfg1: 4096x4096 analog inference MVM, 64 tiles of 512x512, batch 8192",
+                   "timed": f"bounded sample of {args.ref_rows} rows per step, extrapolated linearly"},
+        "cpu_baseline": base,
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import tiles as T
+    from aihwkit_b200.sharded import ShardedTileArray, column_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the analog tile has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _cabi.lib()
+
+    W = WORKLOAD
+    m = W["batch"]
+    cfg = inference_config(seed=1234)
+    arr = ShardedTileArray(
+        W["out_size"], W["in_size"], W["max_tile"], W["max_tile"],
+        lambda b, e: T.TileArray(cfg, W["out_size"], W["in_size"], W["max_tile"], W["max_tile"],
+                                 cuda_device=local_rank, in_split_range=(b, e)))
+    g = torch.Generator().manual_seed(1)
+    weight = torch.randn(W["out_size"], W["in_size"], generator=g) / 64.0
+    arr.local.set_weights(weight)
+    x_host = torch.randn(m, W["in_size"], generator=g).pin_memory()
+    x = x_host.to(dev)
+
+    def step():
+        y = arr.forward_partial(x, is_test=True, non_blocking=True)
+        return arr.reduce(y, dst=0)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = lib.ab200_kernel_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = lib.ab200_kernel_launch_count() - launches0
+    clocks = sampler.stop()
+
+    # kernel-only time of the local MVM work (no reduce), for the roofline
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(args.steps):
+        arr.forward_partial(x, is_test=True, non_blocking=True)
+    k1.record()
+    torch.cuda.synchronize()
+    kernel_ms = k0.elapsed_time(k1) / args.steps
+
+    # end to end through the public API with host buffers: this rank's input columns come from
+    # pinned host memory every step, the result goes back to the host on rank 0
+    c0, c1 = column_range(W["in_size"], W["max_tile"], rank, world)
+    y_host = torch.empty(m, W["out_size"]).pin_memory() if rank == 0 else None
+    x_stage = torch.empty(m, W["in_size"], device=dev)
+
+    def e2e_step():
+        if c1 > c0:
+            x_stage[:, c0:c1].copy_(x_host[:, c0:c1], non_blocking=True)
+        y = arr.forward_partial(x_stage, is_test=True, non_blocking=True)
+        y = arr.reduce(y, dst=0)
+        if rank == 0:
+            y_host.copy_(y, non_blocking=True)
+
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms, kernel_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms, kernel_ms = (float(v) for v in t.tolist())
+        tl = torch.tensor([launches], device=dev, dtype=torch.int64)
+        dist.all_reduce(tl)
+        launches = int(tl.item())
+
+    if rank == 0:
+        peaks = measured_peaks()
+        n_local = arr.n_local_tiles
+        flops = 2.0 * m * 512 * 512 * n_local  # algorithmic: one multiply-add per weight per row
+        achieved = flops / (kernel_ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"]
+        value = m * args.steps / (ms * 1e-3)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {
+                "workload": "cfg1: 4096x4096 analog inference MVM, 64 tiles of 512x512, batch 8192",
+                "sharding": f"in-splits over {world} rank(s), NCCL reduce to rank 0",
+                "l2": "input (134 MB) and output (134 MB) per step exceed the 126 MB L2",
+            },
+            "clocks": clocks,
+            "e2e": {"value": m * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": int(m * W["in_size"] * 4),
+                    "d2h_bytes_per_step": int(m * W["out_size"] * 4)},
+            "gpu_launches": int(launches),
+            "roofline": {
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None,
+                "peak_source": f"bf16_tflops (burst), {peaks['source']}",
+                "kernel": "IO-managed MVM of this rank's tiles",
+                "kernel_ms_per_step": kernel_ms, "tiles_per_launch_group": n_local,
+            },
+        }
+        if world == 1:
+            base = cpu_reference_rate(rows=args.ref_rows)
+            if base is not None:
+                line["cpu_baseline"] = base
+            else:
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference",
+                                        "sample": "oracle/_ref not available on this box"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ref-rows", type=int, default=4096,
+                    help="rows of the bounded CPU sample (reference arm / cpu_baseline)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -200,6 +200,10 @@ void ab200_default_transfer_params(ab200_transfer_params *tp);
  * per-element device parameters on the host, uploads them to `cuda_device`, weights start at 0. */
 int ab200_tile_create(const ab200_tile_config *cfg, int cuda_device, ab200_tile **out);
 int ab200_tile_destroy(ab200_tile *tile);
+/* CudaAnalogTile(cpu_tile) (src/aihwkit/simulator/rpu_base_src/rpu_base_tiles_cuda.cpp:532-538):
+ * a tile created with cuda_device = -1 only carries configuration, weights and the host-drawn
+ * device parameters; this uploads it. Compute calls on a tile without a device fail. */
+int ab200_tile_to_device(ab200_tile *tile, int cuda_device);
 
 int ab200_tile_get_x_size(const ab200_tile *tile); /* rpu.h getXSize */
 int ab200_tile_get_d_size(const ab200_tile *tile); /* rpu.h getDSize */

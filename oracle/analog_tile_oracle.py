@@ -69,10 +69,19 @@ class IO:
     res_in: np.float32 = field(default=f32(0), init=False)
     res_out: np.float32 = field(default=f32(0), init=False)
 
+    _finalized: bool = field(default=False, init=False)
+
     def __post_init__(self) -> None:
         self.finalize()
 
     def finalize(self, backward: bool = False) -> "IO":
+        if backward:
+            self.bound_management = BM_NONE
+        if self.noise_management == NM_NONE:
+            self.nm_thres = 0.0
+        if self._finalized:
+            return self
+        self._finalized = True
         self.res_out = f32(_check_res(self.out_res) * f32(2.0) * f32(self.out_bound))
         self.res_in = f32(_check_res(self.inp_res) * f32(2.0) * f32(self.inp_bound))
         if self.noise_management == NM_NONE:

@@ -1,0 +1,99 @@
+"""Shared builders for the parity tests: tile configurations (the five benchmark configurations
+at reduced and full size), seeded inputs and comparison utilities."""
+
+from __future__ import annotations
+
+import numpy as np
+
+from aihwkit_b200.rpu_base import devices as D
+
+KINDS = {
+    "cs": D.ConstantStepResistiveDeviceParameter,
+    "ls": D.LinearStepResistiveDeviceParameter,
+    "sb": D.SoftBoundsResistiveDeviceParameter,
+    "sbr": D.SoftBoundsReferenceResistiveDeviceParameter,
+}
+
+
+def training_params(noise: bool, pulse_det: bool, bm: bool = True, out_bound: float = 12.0,
+                    adc: bool = True) -> D.AnalogTileParameter:
+    """IO of benchmark configuration 0: 7-bit DAC, 9-bit ADC, out_noise 0.06, ABS_MAX noise
+    management, ITERATIVE bound management; StochasticCompressed BL=31 with UM + UBLM."""
+    p = D.AnalogTileParameter()
+    for io in (p.forward_io, p.backward_io):
+        io.inp_res = 1.0 / 126.0
+        io.out_res = 1.0 / 510.0 if adc else -1.0
+        io.out_noise = 0.06 if noise else 0.0
+        io.out_bound = out_bound
+        io.inp_bound = 1.0
+        io.noise_management = D.NoiseManagementType.AbsMax
+    p.forward_io.bound_management = (
+        D.BoundManagementType.Iterative if bm else D.BoundManagementType.None_
+    )
+    p.update.pulse_type = (
+        D.PulseType.DeterministicImplicit if pulse_det else D.PulseType.StochasticCompressed
+    )
+    p.update.desired_bl = 31
+    p.update.update_management = True
+    p.update.update_bl_management = True
+    return p
+
+
+def inference_params(noise: bool) -> D.AnalogTileParameter:
+    """IO of benchmark configuration 1: 8-bit DAC / ADC, out_noise 0.04, additive-constant weight
+    noise 0.0175, out_bound 10, ABS_MAX, no bound management."""
+    p = D.AnalogTileParameter()
+    io = p.forward_io
+    io.inp_res = 1.0 / 254.0
+    io.out_res = 1.0 / 254.0
+    io.out_noise = 0.04 if noise else 0.0
+    io.w_noise = 0.0175 if noise else 0.0
+    io.w_noise_type = D.WeightNoiseType.AdditiveConstant
+    io.out_bound = 10.0
+    io.noise_management = D.NoiseManagementType.AbsMax
+    io.bound_management = D.BoundManagementType.None_
+    p.update.pulse_type = D.PulseType.None_
+    return p
+
+
+def device(kind: str, noise: bool, seed: int = 11, **kw):
+    dp = KINDS[kind]()
+    dp.construction_seed = seed
+    dp.enforce_consistency = True  # Python-side default of the reference (configs/devices.py:188)
+    if not noise:
+        dp.dw_min_std = 0.0
+    if kind == "sbr":
+        dp.reference_std = 0.05
+    for k, v in kw.items():
+        setattr(dp, k, v)
+    return dp
+
+
+def transfer_device(noise: bool, seed: int = 21, transfer_every: float = 2.0,
+                    units_in_mbatch: bool = True, n_reads: int = 1, transfer_lr: float = 0.01,
+                    det: bool = False):
+    """Benchmark configuration 2: TransferCompound of two SoftBoundsReference devices."""
+    dp = D.TransferResistiveDeviceParameter()
+    for _ in range(2):
+        dp.append_parameter(device("sbr", noise, dw_min=0.002, w_max=1.0, w_min=-1.0))
+    dp.construction_seed = seed
+    dp.gamma = 0.0
+    dp.transfer_every = transfer_every
+    dp.units_in_mbatch = units_in_mbatch
+    dp.n_reads_per_transfer = n_reads
+    dp.transfer_lr = transfer_lr
+    dp.fast_lr = 1.0
+    # Python defaults of TransferCompound: IOParameters() / UpdateParameters()
+    tf = dp.transfer_forward
+    tf.bound_management = D.BoundManagementType.Iterative
+    tf.out_noise = 0.06 if noise else 0.0
+    if det:
+        dp.transfer_update.pulse_type = D.PulseType.DeterministicImplicit
+    return dp
+
+
+def lsb_report(a: np.ndarray, b: np.ndarray, lsb: np.ndarray):
+    """Fraction of elements that differ and the largest difference in units of `lsb`."""
+    diff = np.abs(a.astype(np.float64) - b.astype(np.float64))
+    rel = diff / np.maximum(lsb, 1e-30)
+    return float((rel > 1e-3).mean()), float(rel.max(initial=0.0))

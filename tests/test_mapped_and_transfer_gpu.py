@@ -1,0 +1,184 @@
+"""GPU parity of the mapped-tile layer and of the Tiki-Taka (TransferCompound) tile."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import analog_tile_oracle as O
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def _array_oracle(W, X, cfg, max_out, max_in, rng=None):
+    """TileModuleArray.forward restated with the single-tile oracle
+    (src/aihwkit/simulator/tiles/array.py:155-182)."""
+    from aihwkit_b200.sharded import split_sizes
+
+    io = O.IO.from_c(cfg.forward_io)
+    out_sizes, in_sizes = split_sizes(W.shape[0], max_out), split_sizes(W.shape[1], max_in)
+    y = np.zeros((X.shape[0], W.shape[0]), np.float32)
+    lsb = np.zeros_like(y)
+    c0 = 0
+    for isz in in_sizes:
+        r0 = 0
+        for osz in out_sizes:
+            yt, _, scale, _ = O.forward(W[r0 : r0 + osz, c0 : c0 + isz], X[:, c0 : c0 + isz], io, rng,
+                                        return_pre_adc=True)
+            y[:, r0 : r0 + osz] += yt
+            lsb[:, r0 : r0 + osz] = np.maximum(lsb[:, r0 : r0 + osz], (io.res_out / scale)[:, None])
+            r0 += osz
+        c0 += isz
+    return y, lsb, len(in_sizes)
+
+
+@pytest.mark.parametrize("out_size,in_size,max_tile,m", [(256, 384, 128, 40), (768, 2304, 512, 24),
+                                                         (100, 1030, 512, 7)])
+def test_mapped_forward_noise_off(out_size, in_size, max_tile, m):
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    rng = np.random.default_rng(out_size)
+    p = H.inference_params(noise=False)
+    cfg = p._config(1, 1, D.IdealResistiveDeviceParameter(), seed=3)
+    arr = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+    W = rng.normal(0, 1 / np.sqrt(in_size), (out_size, in_size)).astype(np.float32)
+    arr.set_weights(torch.from_numpy(W))
+    assert np.array_equal(arr.get_weights().numpy(), W)
+    X = rng.normal(0, 1, (m, in_size)).astype(np.float32)
+    y = arr.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    y_or, lsb, n_in = _array_oracle(W, X, cfg, max_tile, max_tile)
+    diff = np.abs(y - y_or)
+    # each in-split contributes its own ADC step; allow one step per in-split at most
+    assert (diff > 1e-3 * lsb).mean() <= 1e-3 * n_in
+    assert (diff <= 1.001 * lsb * n_in).all()
+    # host-buffer entry point gives the same numbers
+    y_h = arr.forward(torch.from_numpy(X))
+    assert np.array_equal(y_h.numpy(), y)
+
+
+def test_mapped_forward_sharded_partials_add_up():
+    """The partial sums of disjoint in-split ranges add up to the full layer (noise off), which
+    is what the multi-GPU reduce relies on; with noise on, the full layer and the sum of the
+    shards are bit-identical because noise keys depend on global tile coordinates only."""
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    rng = np.random.default_rng(4)
+    out_size, in_size, max_tile, m = 384, 1024, 256, 33
+    for noise in (False, True):
+        p = H.inference_params(noise=noise)
+        cfg = p._config(1, 1, D.IdealResistiveDeviceParameter(), seed=77)
+        W = rng.normal(0, 1 / 32.0, (out_size, in_size)).astype(np.float32)
+        X = torch.from_numpy(rng.normal(0, 1, (m, in_size)).astype(np.float32)).cuda()
+        full = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+        full.set_weights(torch.from_numpy(W))
+        y_full = full.forward(X)
+        parts = []
+        for b, e in ((0, 1), (1, 3), (3, 4)):
+            a = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0,
+                            in_split_range=(b, e))
+            a.set_weights(torch.from_numpy(W))
+            parts.append(a.forward(X))
+        y_sum = parts[0] + parts[1] + parts[2]
+        assert torch.allclose(y_full, y_sum, atol=1e-5, rtol=1e-6)
+
+
+def test_mapped_forward_noise_statistics():
+    from scipy import stats
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    rng = np.random.default_rng(9)
+    out_size, in_size, max_tile, m, reps = 128, 512, 256, 16, 100
+    p = H.inference_params(noise=True)
+    cfg = p._config(1, 1, D.IdealResistiveDeviceParameter(), seed=5)
+    arr = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+    W = rng.normal(0, 1 / np.sqrt(in_size), (out_size, in_size)).astype(np.float32)
+    arr.set_weights(torch.from_numpy(W))
+    X = rng.normal(0, 1, (m, in_size)).astype(np.float32)
+    xg = torch.from_numpy(X).cuda()
+    ys = np.stack([arr.forward(xg).cpu().numpy() for _ in range(reps)])
+    org = np.random.default_rng(1)
+    yo = np.stack([_array_oracle(W, X, cfg, max_tile, max_tile, org)[0] for _ in range(reps)])
+    se = yo.std(axis=0).mean() / np.sqrt(reps)
+    assert np.abs(ys.mean(axis=0) - yo.mean(axis=0)).max() < 6 * se
+    assert abs(ys.std(axis=0).mean() / yo.std(axis=0).mean() - 1) < 0.05
+    ks = stats.ks_2samp((ys - yo.mean(axis=0)).ravel(), (yo - yo.mean(axis=0)).ravel())
+    assert ks.pvalue > 0.01, ks
+
+
+def _transfer_setup(x_size, d_size, noise, det, **kw):
+    from aihwkit_b200.rpu_base import tiles as T
+
+    p = H.training_params(noise=noise, pulse_det=det)
+    dp = H.transfer_device(noise=noise, det=det, **kw)
+    cfg = p._config(x_size, d_size, dp, seed=9)
+    return T.AnalogTile(cfg, cuda_device=0), cfg, dp
+
+
+def _transfer_oracle(t, cfg, dp, x_size, d_size):
+    names = t.get_hidden_parameter_names()
+    hp = t.get_hidden_parameters().numpy()
+    fast = O.DeviceArrays.from_hidden(O.DEV_SOFT_BOUNDS_REFERENCE, names, hp,
+                                      dp._vec_par[0].dw_min_std, False, suffix="_0")
+    slow = O.DeviceArrays.from_hidden(O.DEV_SOFT_BOUNDS_REFERENCE, names, hp,
+                                      dp._vec_par[1].dw_min_std, False, suffix="_1")
+    w = t.get_weights().numpy().copy()
+    return O.TransferOracle(w, fast, slow, cfg.transfer, O.Up.from_c(cfg.update),
+                            dp._vec_par[0].dw_min, dp._vec_par[1].dw_min, x_size, d_size)
+
+
+@pytest.mark.parametrize("every,units,m", [(2.0, True, 12), (5.0, False, 12), (1.0, False, 7)])
+def test_transfer_deterministic(every, units, m):
+    """Noise off, deterministic pulses: fast tile A and visible weights C follow the oracle's
+    sample-by-sample Tiki-Taka sequencing, including transfers in the middle of a batch."""
+    x_size, d_size = 40, 24
+    t, cfg, dp = _transfer_setup(x_size, d_size, noise=False, det=True, transfer_every=every,
+                                 units_in_mbatch=units, n_reads=2, transfer_lr=1.0)
+    rng = np.random.default_rng(3)
+    orc = _transfer_oracle(t, cfg, dp, x_size, d_size)
+    lr = 0.1
+    t.set_learning_rate(lr)
+    names = t.get_hidden_parameter_names()
+    ia = names.index("hidden_weights_0")
+    for _ in range(6):
+        X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        Dm = rng.normal(0, 0.5, (m, d_size)).astype(np.float32)
+        t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+        orc.update(X, Dm, lr)
+    A = t.get_hidden_parameters().numpy()[ia]
+    C = t.get_weights().numpy()
+    assert np.abs(orc.a).max() > 0 and np.abs(orc.c).max() > 0
+    assert np.abs(A - orc.a).max() <= 1e-6
+    assert np.abs(C - orc.c).max() <= 1e-6
+
+
+def test_transfer_noisy_statistics():
+    """Noise on, stochastic pulses: moments of A and C over repeats agree with the oracle."""
+    x_size, d_size, m, reps = 16, 12, 8, 60
+    rng = np.random.default_rng(5)
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.5, (m, d_size)).astype(np.float32)
+    t, cfg, dp = _transfer_setup(x_size, d_size, noise=True, det=False, transfer_every=1.0,
+                                 units_in_mbatch=True, n_reads=4, transfer_lr=1.0)
+    names = t.get_hidden_parameter_names()
+    ia = names.index("hidden_weights_0")
+    lr = 0.1
+    t.set_learning_rate(lr)
+    org = np.random.default_rng(11)
+    As, Cs, Ao, Co = [], [], [], []
+    xg, dg = torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda()
+    for _ in range(reps):
+        t.set_weights(torch.zeros(d_size, x_size))
+        orc = _transfer_oracle(t, cfg, dp, x_size, d_size)
+        for _ in range(4):
+            t.update(xg, dg)
+            orc.update(X, Dm, lr, org)
+        As.append(t.get_hidden_parameters().numpy()[ia])
+        Cs.append(t.get_weights().numpy())
+        Ao.append(orc.a.copy())
+        Co.append(orc.c.copy())
+    As, Cs, Ao, Co = (np.stack(v) for v in (As, Cs, Ao, Co))
+    for mine, ref in ((As, Ao), (Cs, Co)):
+        sd = ref.std(axis=0).mean()
+        assert sd > 0
+        assert np.abs(mine.mean(axis=0) - ref.mean(axis=0)).max() < 7 * sd / np.sqrt(reps) * np.sqrt(2)
+        assert abs(mine.std(axis=0).mean() / sd - 1) < 0.15

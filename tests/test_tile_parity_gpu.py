@@ -1,0 +1,275 @@
+"""GPU parity of the single analog tile against the oracle, through the C ABI.
+
+Deterministic regime (noise off, DeterministicImplicit pulses): coincidence counts bit-exact;
+forward / backward within 1e-5 (relative to the output range) before the ADC and at most 0.1 %
+of the elements off by one ADC step after it; weights after an update within 1e-6.
+Noisy regime: first two moments within 4 sigma of their sampling error and a two-sample
+Kolmogorov-Smirnov test with p > 0.01."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import analog_tile_oracle as O
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL_PRE_ADC = 1e-5
+MAX_LSB_FLIP_FRACTION = 1e-3
+KS_P = 0.01
+
+
+def _tile(p, dp, x, d, seed=5):
+    from aihwkit_b200.rpu_base import tiles as T
+
+    cfg = p._config(x, d, dp, seed=seed)
+    return T.AnalogTile(cfg, cuda_device=0), cfg
+
+
+def _inputs(rng, m, x, d):
+    X = rng.uniform(-1, 1, (m, x)).astype(np.float32)
+    Dm = rng.normal(0, 0.1, (m, d)).astype(np.float32)
+    return X, Dm
+
+
+SHAPES = [(64, 48, 17), (256, 256, 64), (100, 36, 33), (512, 512, 96)]
+
+
+@pytest.mark.parametrize("x_size,d_size,m", SHAPES)
+def test_forward_backward_pre_adc(x_size, d_size, m):
+    """ADC off, noise off: only the MVM arithmetic differs from the oracle's fp32 product."""
+    rng = np.random.default_rng(x_size + m)
+    p = H.training_params(noise=False, pulse_det=True, bm=False, adc=False, out_bound=0.0)
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().numpy()
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    X[1] = 0.0  # all-zero row: output is identically zero
+    y = t.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    y_or = O.forward(W, X, O.IO.from_c(cfg.forward_io))
+    assert np.abs(y - y_or).max() <= REL_TOL_PRE_ADC * np.abs(y_or).max()
+    assert np.all(y[1] == 0)
+    g = t.backward(torch.from_numpy(Dm).cuda()).cpu().numpy()
+    g_or = O.backward(W, Dm, O.IO.from_c(cfg.backward_io, backward=True))
+    assert np.abs(g - g_or).max() <= REL_TOL_PRE_ADC * np.abs(g_or).max()
+
+
+@pytest.mark.parametrize("x_size,d_size,m", SHAPES)
+@pytest.mark.parametrize("out_bound", [12.0, 2.0])
+def test_forward_backward_post_adc(x_size, d_size, m, out_bound):
+    """Full IO chain, noise off; out_bound = 2 forces iterative bound management to re-run."""
+    rng = np.random.default_rng(7 * x_size + m)
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=out_bound)
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().numpy()
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    fio = O.IO.from_c(cfg.forward_io)
+    y = t.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    y_or, _, scale, red = O.forward(W, X, fio, return_pre_adc=True)
+    lsb = (fio.res_out / scale)[:, None]
+    frac, worst = H.lsb_report(y, y_or, lsb)
+    assert frac <= MAX_LSB_FLIP_FRACTION and worst <= 1.001, (frac, worst)
+    n_rerun, max_red = t.last_bm_stats()
+    assert n_rerun == int((red > 1).sum())
+    assert max_red == float(red.max())
+    if out_bound == 2.0:
+        assert n_rerun > 0
+    bio = O.IO.from_c(cfg.backward_io, backward=True)
+    g = t.backward(torch.from_numpy(Dm).cuda()).cpu().numpy()
+    g_or = O.backward(W, Dm, bio)
+    s = np.abs(Dm).max(axis=1)
+    frac, worst = H.lsb_report(g, g_or, (bio.res_out * s)[:, None])
+    assert frac <= MAX_LSB_FLIP_FRACTION and worst <= 1.001, (frac, worst)
+
+
+@pytest.mark.parametrize("trans", [(True, False), (False, True), (True, True)])
+def test_transposed_layouts_and_bias(trans):
+    """`batch first iff *_trans` layouts and the appended bias column give the same numbers."""
+    x_trans, d_trans = trans
+    rng = np.random.default_rng(3)
+    x_size, d_size, m = 65, 40, 24
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=3.0)
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().numpy()
+    X = rng.uniform(-1, 1, (m, x_size - 1)).astype(np.float32)  # bias=True: one feature less
+    Xb = np.concatenate([X, np.ones((m, 1), np.float32)], axis=1)
+    fio = O.IO.from_c(cfg.forward_io)
+    y_or, _, scale, _ = O.forward(W, Xb, fio, return_pre_adc=True)
+    xin = torch.from_numpy(np.ascontiguousarray(X.T if x_trans else X)).cuda()
+    y = t.forward(xin, bias=True, x_trans=x_trans, d_trans=d_trans).cpu().numpy()
+    y = y.T if d_trans else y
+    frac, worst = H.lsb_report(y, y_or, (fio.res_out / scale)[:, None])
+    assert frac <= 2e-3 and worst <= 1.001
+    Dm = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+    bio = O.IO.from_c(cfg.backward_io, backward=True)
+    g_or = O.backward(W, Dm, bio)[:, : x_size - 1]
+    din = torch.from_numpy(np.ascontiguousarray(Dm.T if d_trans else Dm)).cuda()
+    g = t.backward(din, bias=True, d_trans=d_trans, x_trans=x_trans).cpu().numpy()
+    g = g.T if x_trans else g
+    assert g.shape == g_or.shape
+    frac, worst = H.lsb_report(g, g_or, (bio.res_out * np.abs(Dm).max(axis=1))[:, None])
+    assert frac <= 2e-3 and worst <= 1.001
+
+
+@pytest.mark.parametrize("kind", ["cs", "ls", "sb", "sbr"])
+@pytest.mark.parametrize("x_size,d_size,m", [(64, 48, 17), (256, 256, 64), (70, 130, 9)])
+def test_deterministic_update_bit_exact_counts(kind, x_size, d_size, m):
+    rng = np.random.default_rng(11 + x_size)
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.device(kind, False)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().numpy()
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    X[2] = 0.0  # no update for this sample
+    up = O.Up.from_c(cfg.update)
+    lr = 0.01
+    t.set_learning_rate(lr)
+    # pulse counts per element, sample by sample: bit-exact
+    for s in (0, 2, m - 1):
+        c = t.coincidences(torch.from_numpy(X[s]).cuda(), torch.from_numpy(Dm[s]).cuda()).cpu().numpy()
+        c_or = O.coincidences_det_implicit(X[s], Dm[s], lr, dp.dw_min, up)
+        assert np.array_equal(c, c_or)
+    names = t.get_hidden_parameter_names()
+    hp = t.get_hidden_parameters().numpy()
+    dev = O.DeviceArrays.from_hidden(
+        {"cs": O.DEV_CONSTANT_STEP, "ls": O.DEV_LINEAR_STEP, "sb": O.DEV_SOFT_BOUNDS,
+         "sbr": O.DEV_SOFT_BOUNDS_REFERENCE}[kind], names, hp, 0.0, getattr(dp, "mult_noise", True))
+    W_or = W.copy()
+    O.update(W_or, X, Dm, lr, dp.dw_min, up, dev)
+    t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    W_new = t.get_weights().numpy()
+    assert np.abs(W_new - W).max() > 0
+    assert np.abs(W_new - W_or).max() <= 1e-6
+
+
+def test_forward_noise_statistics():
+    """Noise on: per-element mean / std of the output over repeats, and a KS test of the
+    standardised residuals against the oracle's."""
+    from scipy import stats
+
+    rng = np.random.default_rng(5)
+    x_size, d_size, m, reps = 128, 64, 8, 200
+    p = H.training_params(noise=True, pulse_det=False, bm=True)
+    t, cfg = _tile(p, H.device("cs", True), x_size, d_size)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().numpy()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    xg = torch.from_numpy(X).cuda()
+    ys = np.stack([t.forward(xg).cpu().numpy() for _ in range(reps)])
+    fio = O.IO.from_c(cfg.forward_io)
+    org = np.random.default_rng(99)
+    yo = np.stack([O.forward(W, X, fio, org) for _ in range(reps)])
+    se = yo.std(axis=0).mean() / np.sqrt(reps)
+    assert np.abs(ys.mean(axis=0) - yo.mean(axis=0)).max() < 6 * se
+    assert abs(ys.std(axis=0).mean() / yo.std(axis=0).mean() - 1) < 0.05
+    # successive calls must not repeat the noise
+    assert not np.array_equal(ys[0], ys[1])
+    ks = stats.ks_2samp((ys - yo.mean(axis=0)).ravel(), (yo - yo.mean(axis=0)).ravel())
+    assert ks.pvalue > KS_P, ks
+
+
+@pytest.mark.parametrize("kind", ["cs", "sb", "sbr"])
+def test_stochastic_update_statistics(kind):
+    """Noise on, StochasticCompressed pulses: mean and std of the weight change per element over
+    repeats agree with the oracle (the reference's own test criterion, 2/sqrt(nloop) scaled)."""
+    from scipy import stats
+
+    rng = np.random.default_rng(17)
+    x_size, d_size, m, reps = 32, 24, 10, 150
+    p = H.training_params(noise=True, pulse_det=False)
+    dp = H.device(kind, True)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    W0 = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    up = O.Up.from_c(cfg.update)
+    names = t.get_hidden_parameter_names()
+    hp = t.get_hidden_parameters().numpy()
+    dev = O.DeviceArrays.from_hidden(
+        {"cs": O.DEV_CONSTANT_STEP, "sb": O.DEV_SOFT_BOUNDS, "sbr": O.DEV_SOFT_BOUNDS_REFERENCE}[kind],
+        names, hp, dp.dw_min_std, getattr(dp, "mult_noise", True))
+    lr = 0.05
+    t.set_learning_rate(lr)
+    xg, dg = torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda()
+    dws, dwo = [], []
+    org = np.random.default_rng(123)
+    for _ in range(reps):
+        t.set_weights(torch.from_numpy(W0))
+        Wc = t.get_weights().numpy()
+        t.update(xg, dg)
+        dws.append(t.get_weights().numpy() - Wc)
+        Wo = Wc.copy()
+        O.update(Wo, X, Dm, lr, dp.dw_min, up, dev, org)
+        dwo.append(Wo - Wc)
+    dws, dwo = np.stack(dws), np.stack(dwo)
+    sd = dwo.std(axis=0).mean()
+    assert sd > 0
+    # element-wise means within sampling error; global std ratio within 10 %
+    assert np.abs(dws.mean(axis=0) - dwo.mean(axis=0)).max() < 6 * sd / np.sqrt(reps) * np.sqrt(2)
+    assert abs(dws.std(axis=0).mean() / sd - 1) < 0.1
+    # gradient direction: expected change follows -lr * d^T x
+    grad = -(Dm.T @ X).ravel()
+    corr = np.corrcoef(dws.mean(axis=0).ravel(), grad)[0, 1]
+    corr_or = np.corrcoef(dwo.mean(axis=0).ravel(), grad)[0, 1]
+    assert corr > 0.5 and abs(corr - corr_or) < 0.1
+    ks = stats.ks_2samp(dws.sum(axis=(1, 2)), dwo.sum(axis=(1, 2)))
+    assert ks.pvalue > KS_P, ks
+
+
+def test_floating_point_tile_mimics_mac():
+    """Perfect IO + floating-point update equal numpy (tests/test_bindings_tiles.py:138-177)."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(1)
+    x_size, d_size, m = 30, 20, 12
+    t = T.FloatingPointTile(x_size, d_size).cuda(0)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    y = t.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    np.testing.assert_allclose(y, X @ W.T, atol=1e-5)
+    g = t.backward(torch.from_numpy(Dm).cuda()).cpu().numpy()
+    np.testing.assert_allclose(g, Dm @ W, atol=1e-5)
+    t.set_learning_rate(0.1)
+    t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    np.testing.assert_allclose(t.get_weights().numpy(), W - 0.1 * Dm.T @ X, atol=1e-5)
+
+
+def test_host_buffer_entry_points_match_device_path():
+    """CPU tensors go through the *_host entry points (pinned staging inside the library)."""
+    rng = np.random.default_rng(2)
+    x_size, d_size, m = 96, 80, 20
+    p = H.training_params(noise=False, pulse_det=True)
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    y_dev = t.forward(torch.from_numpy(X).cuda()).cpu()
+    y_host = t.forward(torch.from_numpy(X))
+    assert not y_host.is_cuda and torch.equal(y_dev, y_host)
+    g_dev = t.backward(torch.from_numpy(Dm).cuda()).cpu()
+    g_host = t.backward(torch.from_numpy(Dm))
+    assert torch.equal(g_dev, g_host)
+
+
+def test_empty_batch_and_errors():
+    p = H.training_params(noise=False, pulse_det=True)
+    t, _ = _tile(p, H.device("cs", False), 16, 8)
+    y = t.forward(torch.empty(0, 16).cuda())
+    assert tuple(y.shape) == (0, 8)
+    with pytest.raises(RuntimeError):
+        t.forward(torch.zeros(4, 15).cuda())
+    with pytest.raises(RuntimeError):
+        t.set_weights(torch.zeros(3, 3))
+    t.set_learning_rate(0.0)  # lr == 0: update is a no-op (rpu_weight_updater.cpp:206-208)
+    w0 = t.get_weights()
+    t.update(torch.ones(4, 16).cuda(), torch.ones(4, 8).cuda())
+    assert torch.equal(w0, t.get_weights())
