@@ -15,6 +15,10 @@ using ab200::TileArray;
 
 static thread_local std::string g_error;
 
+namespace ab200 {
+void setLastError(const char *msg) { g_error = msg ? msg : ""; }
+} // namespace ab200
+
 #define AB200_TRY try {
 #define AB200_CATCH                                                                                \
   }                                                                                                \

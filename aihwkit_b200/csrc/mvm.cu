@@ -362,4 +362,125 @@ void launchMvm(const MvmProblem &p, cudaStream_t stream) {
   launchBmRerun(p, stream);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Forward pass for callers that must not allocate.
+//
+// Some hosts hand the whole GPU to their own memory pool at start-up and forbid every later
+// device allocation (an inference server's execute callback, a real-time control loop, a plugin
+// whose contract says "no allocation after initialisation"); for them a cudaMalloc in the middle
+// of a request either fails outright or stalls every stream of the device while the driver
+// serialises it. The tile entry points grow their per-sample scratch with cudaMalloc on demand,
+// so those callers get this variant: the same kernels, with the per-sample scratch (input scale,
+// output factor, input norm, noise-management value, bound-management flag, two counters) living
+// in a fixed array inside the library image. Every GPU that loads the library carries that array
+// (about 320 KB) until the process exits.
+//
+// The array below is named from host code only as a *symbol*: its device address is looked up
+// once per device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+// ---------------------------------------------------------------------------------------------
+constexpr int kNoAllocMaxBatch = AB200_NOALLOC_MAX_BATCH;
+constexpr size_t kNoAllocBytes = (size_t)kNoAllocMaxBatch * 5 * sizeof(float) + 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kMaxDevices = 64;
+static unsigned char *g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+static unsigned char *noAllocScratchForCurrentDevice() {
+  int dev = -1;
+  AB200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    AB200_FATAL("no-alloc forward: unsupported device index " << dev);
+  }
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // first call on this device: resolve the symbol to this device's address
+    void *ptr = nullptr;
+    AB200_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    if (ptr == nullptr) {
+      AB200_FATAL("no-alloc forward: scratch symbol has no device address");
+    }
+    g_noalloc_ptr[dev] = static_cast<unsigned char *>(ptr);
+  }
+  return g_noalloc_ptr[dev];
+}
+
+void forwardNoAlloc(const ab200_io_params &io_user, const float *w_dev_xd, int x_size, int d_size,
+                    const float *x_dev, float *d_dev, int m_batch, uint64_t seed, uint32_t call,
+                    cudaStream_t stream) {
+  if (x_size <= 0 || d_size <= 0) {
+    AB200_FATAL("no-alloc forward: tile sizes must be positive");
+  }
+  if (m_batch < 0) {
+    AB200_FATAL("m_batch must be >= 0");
+  }
+  if (m_batch > kNoAllocMaxBatch) {
+    AB200_FATAL("no-alloc forward: m_batch " << m_batch << " exceeds the built-in scratch ("
+                                             << kNoAllocMaxBatch
+                                             << " rows); split the batch or use ab200_tile_forward");
+  }
+  if (!w_dev_xd || (m_batch > 0 && (!x_dev || !d_dev))) {
+    AB200_FATAL("no-alloc forward: null pointer");
+  }
+  if (m_batch == 0) {
+    return;
+  }
+  unsigned char *base = noAllocScratchForCurrentDevice();
+  MvmProblem p{};
+  p.in = x_dev;
+  p.in_ss = x_size;
+  p.in_fs = 1;
+  p.in_size = x_size;
+  p.in_real = x_size;
+  p.out = d_dev;
+  p.out_ss = d_size;
+  p.out_fs = 1;
+  p.out_size = d_size;
+  p.out_store = d_size;
+  p.accumulate = 0;
+  p.w = w_dev_xd;
+  p.wk = d_size;
+  p.wn = 1;
+  p.m = m_batch;
+  p.backward = 0;
+  p.io = resolveIO(io_user, false);
+  p.alpha = 1.0f;
+  p.key.k0 = (uint32_t)seed;
+  p.key.k1 = (uint32_t)(seed >> 32) ^ 0x5bd1e995u;
+  p.call = call;
+  p.noise_id = 0;
+  float *f = reinterpret_cast<float *>(base);
+  p.scale = f;
+  p.factor = f + kNoAllocMaxBatch;
+  p.vnorm = f + 2 * (size_t)kNoAllocMaxBatch;
+  p.sval = f + 3 * (size_t)kNoAllocMaxBatch;
+  p.flags = reinterpret_cast<int *>(f + 4 * (size_t)kNoAllocMaxBatch);
+  p.bm_stats = reinterpret_cast<int *>(base + (size_t)kNoAllocMaxBatch * 5 * sizeof(float));
+  // the array keeps what the previous call left: the two counters must start at zero (the
+  // per-sample entries are rewritten by the first kernel before anything reads them)
+  AB200_CUDA(cudaMemsetAsync(p.bm_stats, 0, 2 * sizeof(int), stream));
+  launchMvm(p, stream);
+}
+
+} // namespace ab200
+
+namespace ab200 {
+void setLastError(const char *msg);
+}
+
+extern "C" int ab200_mvm_forward_noalloc(const ab200_io_params *forward_io, const float *w_dev_xd,
+                                         int x_size, int d_size, const float *x_dev, float *d_dev,
+                                         int m_batch, uint64_t seed, uint32_t call, void *stream) {
+  try {
+    if (!forward_io) {
+      AB200_FATAL("no-alloc forward: null IO parameters");
+    }
+    ab200::forwardNoAlloc(*forward_io, w_dev_xd, x_size, d_size, x_dev, d_dev, m_batch, seed, call,
+                          (cudaStream_t)stream);
+  } catch (const std::exception &e) {
+    ab200::setLastError(e.what());
+    return 1;
+  }
+  return 0;
+}
+
+namespace ab200 {
 } // namespace ab200

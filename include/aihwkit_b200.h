@@ -301,6 +301,30 @@ int ab200_array_forward_host(ab200_array *arr, const float *x_host, float *y_hos
                              int is_test, void *stream);
 int ab200_array_set_seed(ab200_array *arr, uint64_t seed);
 
+/* ---- forward pass without any allocation ------------------------------------------------- */
+
+/* No counterpart in the reference (its GPU tile allocates buffers on demand).
+ *
+ * For hosts that pre-reserve the GPU's memory and forbid allocation afterwards - an inference
+ * server's execute callback, a real-time loop, a plugin with a "no allocation after init"
+ * contract - where a cudaMalloc mid-request would fail or stall every stream of the device.
+ * Computes the same IO-managed forward pass as ab200_tile_forward (non-transposed layouts, no
+ * bias) from caller-owned memory only: w_dev_xd is the fp32 [x_size][d_size] weight, x_dev is
+ * [m_batch][x_size], d_dev is [m_batch][d_size]. The per-sample scratch lives in a fixed array
+ * inside the library image (about 320 KB per GPU, held until the process exits), so m_batch is
+ * limited to AB200_NOALLOC_MAX_BATCH; larger batches are rejected with an error - split them.
+ * The call performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ *  - The first call on each device looks up the array's device address; make that first call
+ *    during start-up, outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's contents (the
+ *    library clears what has to start at zero): calls that overlap on the GPU - different
+ *    streams, or several host threads - race on it. Run them one after the other.
+ *  - (seed, call) key the noise: the same pair reproduces the same noise; vary `call`. */
+#define AB200_NOALLOC_MAX_BATCH 16384
+int ab200_mvm_forward_noalloc(const ab200_io_params *forward_io, const float *w_dev_xd,
+                              int x_size, int d_size, const float *x_dev, float *d_dev,
+                              int m_batch, uint64_t seed, uint32_t call, void *stream);
+
 /* Number of kernels this library has launched since it was loaded (all tiles, this process). */
 uint64_t ab200_kernel_launch_count(void);
 
