@@ -1,0 +1,143 @@
+"""Generate the golden vectors of tests/golden/*.npz from the COMPILED REFERENCE (oracle/_ref).
+
+    make -C oracle && python tests/golden/make_golden.py
+
+Every array is an input or an output of the unmodified reference CPU tile
+(RPU::RPUPulsed<float>) for the configurations built by tests/helpers.py; nothing here comes from
+the numpy restatement or from the CUDA code.  The noisy cases store the reference's output samples
+so that distributions can be compared where the reference itself cannot run.
+"""
+
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from oracle import ref  # noqa: E402
+from tests import helpers as H  # noqa: E402
+
+
+def deterministic_case(kind, x_size, d_size, m, out_bound, seed):
+    rng = np.random.default_rng(seed)
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=out_bound)
+    dp = H.device(kind, False)
+    cfg = p._config(x_size, d_size, dp, seed=seed)
+    t = ref.RefTile(cfg)
+    w = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(w)
+    w0 = t.get_weights()
+    x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    d = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+    x[1] = 0
+    y = t.forward(x)
+    g = t.backward(d)
+    lr = 0.01
+    t.set_learning_rate(lr)
+    counts = np.stack([t.coincidences(x[s], d[s], lr, dp.dw_min) for s in range(min(m, 4))])
+    hp = t.get_hidden_parameters()
+    t.update(x, d)
+    w1 = t.get_weights()
+    return dict(w0=w0, x=x, d=d, y=y, g=g, counts=counts, hidden=hp, w1=w1,
+                lr=np.float32(lr), out_bound=np.float32(out_bound))
+
+
+def noisy_forward_case(seed, reps=300):
+    rng = np.random.default_rng(seed)
+    x_size, d_size, m = 64, 32, 4
+    p = H.training_params(noise=True, pulse_det=False, bm=True)
+    cfg = p._config(x_size, d_size, H.device("cs", True), seed=seed)
+    t = ref.RefTile(cfg)
+    t.set_seed(seed)
+    w = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(w)
+    w0 = t.get_weights()
+    x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    ys = np.stack([t.forward(x) for _ in range(reps)])
+    return dict(w0=w0, x=x, ys=ys)
+
+
+def noisy_inference_case(seed, reps=300):
+    rng = np.random.default_rng(seed)
+    x_size, d_size, m = 128, 24, 4
+    p = H.inference_params(noise=True)
+    from aihwkit_b200.rpu_base import devices as D
+
+    cfg = p._config(x_size, d_size, D.IdealResistiveDeviceParameter(), seed=seed)
+    t = ref.RefTile(cfg)
+    t.set_seed(seed)
+    w = rng.normal(0, 1 / np.sqrt(x_size), (d_size, x_size)).astype(np.float32)
+    t.set_weights(w)
+    x = rng.normal(0, 1, (m, x_size)).astype(np.float32)
+    ys = np.stack([t.forward(x, is_test=True) for _ in range(reps)])
+    return dict(w0=w, x=x, ys=ys)
+
+
+def noisy_update_case(kind, seed, reps=150):
+    rng = np.random.default_rng(seed)
+    x_size, d_size, m = 16, 12, 8
+    p = H.training_params(noise=True, pulse_det=False)
+    dp = H.device(kind, True)
+    cfg = p._config(x_size, d_size, dp, seed=seed)
+    t = ref.RefTile(cfg)
+    t.set_seed(seed)
+    w = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    d = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+    lr = 0.05
+    t.set_learning_rate(lr)
+    hp = t.get_hidden_parameters()
+    dws = []
+    for _ in range(reps):
+        t.set_weights(w)
+        w0 = t.get_weights()
+        t.update(x, d)
+        dws.append(t.get_weights() - w0)
+    return dict(w=w, w0=w0, x=x, d=d, hidden=hp, dws=np.stack(dws).astype(np.float32),
+                lr=np.float32(lr))
+
+
+def transfer_case(seed):
+    rng = np.random.default_rng(seed)
+    x_size, d_size, m = 20, 12, 6
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.transfer_device(noise=False, det=True, transfer_every=2.0, units_in_mbatch=True,
+                           n_reads=2, transfer_lr=1.0)
+    cfg = p._config(x_size, d_size, dp, seed=seed)
+    t = ref.RefTile(cfg)
+    lr = 0.1
+    t.set_learning_rate(lr)
+    hp0 = t.get_hidden_parameters()
+    xs, ds, ws, hs = [], [], [], []
+    for _ in range(6):
+        x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        d = rng.normal(0, 0.5, (m, d_size)).astype(np.float32)
+        t.update(x, d)
+        xs.append(x)
+        ds.append(d)
+        ws.append(t.get_weights())
+        names = t.hidden_parameter_names()
+        hs.append(t.get_hidden_parameters()[names.index("hidden_weights_0")])
+    return dict(hidden0=hp0, xs=np.stack(xs), ds=np.stack(ds), ws=np.stack(ws), a=np.stack(hs),
+                lr=np.float32(lr))
+
+
+def main():
+    out = {}
+    for kind in ("cs", "ls", "sb", "sbr"):
+        for (x, d, m, ob) in ((40, 24, 9, 12.0), (70, 33, 6, 2.0)):
+            out[f"det_{kind}_{x}x{d}_ob{int(ob)}"] = deterministic_case(kind, x, d, m, ob, 100 + x)
+    for name, case in out.items():
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **case)
+    np.savez_compressed(os.path.join(HERE, "noisy_forward.npz"), **noisy_forward_case(5))
+    np.savez_compressed(os.path.join(HERE, "noisy_inference.npz"), **noisy_inference_case(6))
+    for kind in ("cs", "sbr"):
+        np.savez_compressed(os.path.join(HERE, f"noisy_update_{kind}.npz"), **noisy_update_case(kind, 7))
+    np.savez_compressed(os.path.join(HERE, "transfer_det.npz"), **transfer_case(8))
+    print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
+
+
+if __name__ == "__main__":
+    main()

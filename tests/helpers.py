@@ -97,3 +97,17 @@ def lsb_report(a: np.ndarray, b: np.ndarray, lsb: np.ndarray):
     diff = np.abs(a.astype(np.float64) - b.astype(np.float64))
     rel = diff / np.maximum(lsb, 1e-30)
     return float((rel > 1e-3).mean()), float(rel.max(initial=0.0))
+
+
+def assert_moments_agree(a: np.ndarray, b: np.ndarray, z_max: float = 5.0, std_tol: float = 0.1):
+    """Two sets of repeats `[reps, ...]` agree in their first two moments: every element's mean
+    difference is within `z_max` standard errors (the reference's own tests use 2/sqrt(nloop) on
+    unit-scale data, src/rpucuda/cuda/rpucuda_pulsed_test.cpp:1050-1131) and the average
+    per-element standard deviations agree within `std_tol`."""
+    ra, rb = a.shape[0], b.shape[0]
+    se = np.sqrt(a.var(axis=0) / ra + b.var(axis=0) / rb)
+    floor = 1e-3 * max(float(a.std()), float(b.std()), 1e-30) / np.sqrt(min(ra, rb))
+    z = np.abs(a.mean(axis=0) - b.mean(axis=0)) / np.maximum(se, floor)
+    assert float(z.max()) < z_max, f"max z-score {float(z.max()):.2f}"
+    sa, sb = float(a.std(axis=0).mean()), float(b.std(axis=0).mean())
+    assert sb > 0 and abs(sa / sb - 1.0) < std_tol, f"std ratio {sa / sb:.3f}"

@@ -1,0 +1,154 @@
+"""CPU checks of the boundary: the library loads and exports every symbol the header declares,
+the host-side tile logic (configuration, parameter draw, weights, hidden parameters, errors)
+behaves like the reference's.  No compute call is made: there is no CPU compute path."""
+
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from aihwkit_b200 import _cabi
+from aihwkit_b200.rpu_base import devices as D, tiles as T, cuda as rpu_cuda
+from tests import helpers as H
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _cabi.lib()
+    names = _cabi.declared_symbols()
+    assert len(names) >= 40
+    for name in names:
+        assert hasattr(lib, name), name
+    assert rpu_cuda.is_compiled()
+    assert b"sm_100a" in lib.ab200_version()
+
+
+def test_struct_sizes_match_header():
+    # layouts are plain int32 / float / uint64 fields; sizes are what a C compiler produces
+    assert C.sizeof(_cabi.IOParams) == 20 * 4
+    assert C.sizeof(_cabi.UpdateParams) == 10 * 4
+    assert C.sizeof(_cabi.DeviceParams) == 27 * 4
+    assert C.sizeof(_cabi.TransferParams) == 9 * 4 + 20 * 4 + 10 * 4
+    assert C.sizeof(_cabi.TileConfig) % 8 == 0
+
+
+def test_defaults_follow_reference_member_initialisers():
+    lib = _cabi.lib()
+    io = _cabi.IOParams()
+    lib.ab200_default_io_params(C.byref(io))
+    ref = D.AnalogTileInputOutputParameter()._to_c()
+    for name, _ in _cabi.IOParams._fields_:
+        assert getattr(io, name) == pytest.approx(getattr(ref, name)), name
+    up = _cabi.UpdateParams()
+    lib.ab200_default_update_params(C.byref(up))
+    refu = D.AnalogTileUpdateParameter()._to_c()
+    for name, _ in _cabi.UpdateParams._fields_:
+        assert getattr(up, name) == pytest.approx(getattr(refu, name)), name
+    for kind, cls in ((D.DEVICE_CONSTANT_STEP, D.ConstantStepResistiveDeviceParameter),
+                      (D.DEVICE_SOFT_BOUNDS, D.SoftBoundsResistiveDeviceParameter),
+                      (D.DEVICE_LINEAR_STEP, D.LinearStepResistiveDeviceParameter)):
+        dp = _cabi.DeviceParams()
+        lib.ab200_default_device_params(C.byref(dp), kind)
+        refd = cls()._to_c()
+        for name, _ in _cabi.DeviceParams._fields_:
+            if kind == D.DEVICE_CONSTANT_STEP and name.startswith("ls_"):
+                continue  # LinearStep-only fields are not read for ConstantStep
+            assert getattr(dp, name) == pytest.approx(getattr(refd, name)), (kind, name)
+
+
+@pytest.mark.parametrize("kind", ["cs", "ls", "sb", "sbr"])
+def test_host_parameter_draw_equals_reference_golden(kind):
+    """For a given construction_seed the host-side draw reproduces the reference's per-element
+    parameters bit for bit (golden `hidden` arrays come from the compiled reference)."""
+    g = np.load(os.path.join(GOLD, f"det_{kind}_40x24_ob12.npz"))
+    p = H.training_params(noise=False, pulse_det=True)
+    t = T.AnalogTile(p._config(40, 24, H.device(kind, False), seed=1))
+    assert np.array_equal(t.get_hidden_parameters().numpy(), g["hidden"])
+    t.set_weights(torch.from_numpy(np.full((24, 40), 10.0, np.float32)))
+    assert np.array_equal(t.get_weights().numpy(), g["hidden"][0])  # clipped to max_bound
+
+
+def test_transfer_hidden_parameters_equal_reference_golden():
+    g = np.load(os.path.join(GOLD, "transfer_det.npz"))
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.transfer_device(noise=False, det=True, transfer_every=2.0, units_in_mbatch=True,
+                           n_reads=2, transfer_lr=1.0)
+    t = T.AnalogTile(p._config(20, 12, dp, seed=1))
+    names = t.get_hidden_parameter_names()
+    assert len(names) == 20 and names[9] == "hidden_weights_0" and names[-1] == "hidden_weights_1"
+    assert np.array_equal(t.get_hidden_parameters().numpy(), g["hidden0"])
+
+
+def test_hidden_parameter_round_trip_and_weight_reclip():
+    p = H.training_params(noise=False, pulse_det=True)
+    t = T.AnalogTile(p._config(12, 8, H.device("sb", False), seed=1))
+    hp = t.get_hidden_parameters()
+    assert tuple(hp.shape) == (10, 8, 12)
+    t.set_weights(torch.full((8, 12), 0.2))
+    hp2 = hp.clone()
+    hp2[0] = 0.05  # max_bound
+    t.set_hidden_parameters(hp2)
+    assert torch.equal(t.get_hidden_parameters(), hp2)
+    assert float(t.get_weights().max()) <= 0.05 + 1e-7
+    with pytest.raises(RuntimeError):
+        t.set_hidden_parameters(hp[:3])
+
+
+def test_compute_without_device_fails_loudly():
+    p = H.training_params(noise=False, pulse_det=True)
+    t = T.AnalogTile(p._config(8, 4, H.device("cs", False), seed=1))
+    for call in (lambda: t.forward(torch.zeros(2, 8)), lambda: t.backward(torch.zeros(2, 4)),
+                 lambda: t.update(torch.zeros(2, 8), torch.zeros(2, 4))):
+        with pytest.raises(RuntimeError, match="no CPU compute path"):
+            call()
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="no CPU fallback|not available"):
+            t.cuda(0)
+
+
+def test_unsupported_settings_raise():
+    p = D.AnalogTileParameter()
+    p.forward_io.inp_noise = 0.1
+    with pytest.raises(RuntimeError):
+        p._config(4, 4, D.ConstantStepResistiveDeviceParameter())
+    p = D.AnalogTileParameter()
+    p.update.pulse_type = D.PulseType.Stochastic
+    with pytest.raises(RuntimeError, match="PulseType not supported"):
+        p._config(4, 4, D.ConstantStepResistiveDeviceParameter())
+    p = D.AnalogTileParameter()
+    p.forward_io.inp_bound = 2.0  # noise management expects bound == 1
+    with pytest.raises(RuntimeError, match="expects bound==1"):
+        T.AnalogTile(p._config(4, 4, D.ConstantStepResistiveDeviceParameter()))
+    dp = D.ConstantStepResistiveDeviceParameter()
+    dp.w_min = 0.1
+    with pytest.raises(RuntimeError, match="needs to contain 0"):
+        T.AnalogTile(D.AnalogTileParameter()._config(4, 4, dp))
+    with pytest.raises(RuntimeError):
+        T.AnalogTile(D.AnalogTileParameter()._config(0, 4, D.ConstantStepResistiveDeviceParameter()))
+
+
+def test_learning_rate_and_sizes():
+    t = T.AnalogTile(D.AnalogTileParameter()._config(7, 5, D.ConstantStepResistiveDeviceParameter()))
+    assert (t.get_x_size(), t.get_d_size()) == (7, 5)
+    assert t.get_learning_rate() == pytest.approx(0.1)  # createRPUArray default
+    t.set_learning_rate(0.02)
+    assert t.get_learning_rate() == pytest.approx(0.02)
+    with pytest.raises(RuntimeError, match="Invalid weights dimensions"):
+        t.set_weights(torch.zeros(7, 5))
+
+
+def test_split_sizes_follow_reference_rule():
+    from aihwkit_b200.sharded import split_sizes, in_split_range, column_range
+
+    assert split_sizes(4096, 512) == [512] * 8
+    assert split_sizes(768, 512) == [384, 384]
+    assert split_sizes(2304, 512) == [461, 461, 461, 461, 460]
+    assert split_sizes(100, 0) == [100]
+    for world in (1, 2, 3, 4, 8, 16):
+        ranges = [in_split_range(8, r, world) for r in range(world)]
+        assert ranges[0][0] == 0 and ranges[-1][1] == 8
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+    assert column_range(2304, 512, 1, 2) == (461 * 3, 2304)

@@ -1,0 +1,120 @@
+"""The CUDA path against the golden vectors recorded from the compiled reference CPU tile
+(tests/golden/*.npz), through the C ABI."""
+
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+DET = sorted(glob.glob(os.path.join(GOLD, "det_*.npz")))
+
+
+def _gpu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("path", DET, ids=[os.path.basename(p)[:-4] for p in DET])
+def test_deterministic_case(path):
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import analog_tile_oracle as O
+
+    g = np.load(path)
+    kind = os.path.basename(path).split("_")[1]
+    d_size, x_size = g["w0"].shape
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=float(g["out_bound"]))
+    dp = H.device(kind, False)
+    cfg = p._config(x_size, d_size, dp, seed=1)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    t.set_hidden_parameters(torch.from_numpy(g["hidden"]))
+    t.set_weights(torch.from_numpy(g["w0"]))
+    assert np.array_equal(t.get_weights().numpy(), g["w0"])
+    fio, bio = O.IO.from_c(cfg.forward_io), O.IO.from_c(cfg.backward_io, backward=True)
+    # ADC step in output units: res_out / input scale (per row; bound management may halve it)
+    _, _, scale, _ = O.forward(g["w0"], g["x"], fio, return_pre_adc=True)
+    y = t.forward(_gpu(g["x"])).cpu().numpy()
+    frac, worst = H.lsb_report(y, g["y"], (fio.res_out / scale)[:, None])
+    assert frac <= 2e-3 and worst <= 1.001, (frac, worst)
+    gb = t.backward(_gpu(g["d"])).cpu().numpy()
+    frac, worst = H.lsb_report(gb, g["g"], (bio.res_out * np.abs(g["d"]).max(axis=1))[:, None])
+    assert frac <= 2e-3 and worst <= 1.001, (frac, worst)
+    t.set_learning_rate(float(g["lr"]))
+    for s in range(g["counts"].shape[0]):
+        c = t.coincidences(_gpu(g["x"][s]), _gpu(g["d"][s])).cpu().numpy()
+        assert np.array_equal(c, g["counts"][s])  # pulse counts: bit-exact
+    t.update(_gpu(g["x"]), _gpu(g["d"]))
+    assert np.abs(t.get_weights().numpy() - g["w1"]).max() <= 1e-6
+
+
+def test_noisy_forward_against_reference_samples():
+    from scipy import stats
+    from aihwkit_b200.rpu_base import tiles as T
+
+    g = np.load(os.path.join(GOLD, "noisy_forward.npz"))
+    p = H.training_params(noise=True, pulse_det=False, bm=True)
+    t = T.AnalogTile(p._config(64, 32, H.device("cs", True), seed=11), cuda_device=0)
+    t.set_weights(torch.from_numpy(g["w0"]))
+    xg = _gpu(g["x"])
+    ys = np.stack([t.forward(xg).cpu().numpy() for _ in range(g["ys"].shape[0])])
+    H.assert_moments_agree(ys, g["ys"], std_tol=0.05)
+    mu = g["ys"].mean(axis=0)
+    assert stats.ks_2samp((ys - mu).ravel(), (g["ys"] - mu).ravel()).pvalue > 0.01
+
+
+def test_noisy_inference_against_reference_samples():
+    from scipy import stats
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    g = np.load(os.path.join(GOLD, "noisy_inference.npz"))
+    p = H.inference_params(noise=True)
+    t = T.AnalogTile(p._config(128, 24, D.IdealResistiveDeviceParameter(), seed=12), cuda_device=0)
+    t.set_weights(torch.from_numpy(g["w0"]))
+    xg = _gpu(g["x"])
+    ys = np.stack([t.forward(xg, is_test=True).cpu().numpy() for _ in range(g["ys"].shape[0])])
+    H.assert_moments_agree(ys, g["ys"], std_tol=0.05)
+    mu = g["ys"].mean(axis=0)
+    assert stats.ks_2samp((ys - mu).ravel(), (g["ys"] - mu).ravel()).pvalue > 0.01
+
+
+@pytest.mark.parametrize("kind", ["cs", "sbr"])
+def test_noisy_update_against_reference_samples(kind):
+    from scipy import stats
+    from aihwkit_b200.rpu_base import tiles as T
+
+    g = np.load(os.path.join(GOLD, f"noisy_update_{kind}.npz"))
+    p = H.training_params(noise=True, pulse_det=False)
+    t = T.AnalogTile(p._config(16, 12, H.device(kind, True), seed=13), cuda_device=0)
+    t.set_hidden_parameters(torch.from_numpy(g["hidden"]))
+    t.set_learning_rate(float(g["lr"]))
+    xg, dg = _gpu(g["x"]), _gpu(g["d"])
+    dws = []
+    for _ in range(g["dws"].shape[0]):
+        t.set_weights(torch.from_numpy(g["w"]))
+        w0 = t.get_weights().numpy()
+        t.update(xg, dg)
+        dws.append(t.get_weights().numpy() - w0)
+    dws = np.stack(dws)
+    H.assert_moments_agree(dws, g["dws"])
+    assert stats.ks_2samp(dws.sum(axis=(1, 2)), g["dws"].sum(axis=(1, 2))).pvalue > 0.01
+
+
+def test_transfer_sequence_against_reference():
+    from aihwkit_b200.rpu_base import tiles as T
+
+    g = np.load(os.path.join(GOLD, "transfer_det.npz"))
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.transfer_device(noise=False, det=True, transfer_every=2.0, units_in_mbatch=True,
+                           n_reads=2, transfer_lr=1.0)
+    t = T.AnalogTile(p._config(20, 12, dp, seed=1), cuda_device=0)
+    assert np.array_equal(t.get_hidden_parameters().numpy(), g["hidden0"])
+    t.set_learning_rate(float(g["lr"]))
+    ia = t.get_hidden_parameter_names().index("hidden_weights_0")
+    for k in range(g["xs"].shape[0]):
+        t.update(_gpu(g["xs"][k]), _gpu(g["ds"][k]))
+        assert np.abs(t.get_hidden_parameters().numpy()[ia] - g["a"][k]).max() <= 1e-6, k
+        assert np.abs(t.get_weights().numpy() - g["ws"][k]).max() <= 1e-6, k

@@ -98,9 +98,7 @@ def test_mapped_forward_noise_statistics():
     ys = np.stack([arr.forward(xg).cpu().numpy() for _ in range(reps)])
     org = np.random.default_rng(1)
     yo = np.stack([_array_oracle(W, X, cfg, max_tile, max_tile, org)[0] for _ in range(reps)])
-    se = yo.std(axis=0).mean() / np.sqrt(reps)
-    assert np.abs(ys.mean(axis=0) - yo.mean(axis=0)).max() < 6 * se
-    assert abs(ys.std(axis=0).mean() / yo.std(axis=0).mean() - 1) < 0.05
+    H.assert_moments_agree(ys, yo, std_tol=0.05)
     ks = stats.ks_2samp((ys - yo.mean(axis=0)).ravel(), (yo - yo.mean(axis=0)).ravel())
     assert ks.pvalue > 0.01, ks
 
@@ -178,7 +176,4 @@ def test_transfer_noisy_statistics():
         Co.append(orc.c.copy())
     As, Cs, Ao, Co = (np.stack(v) for v in (As, Cs, Ao, Co))
     for mine, ref in ((As, Ao), (Cs, Co)):
-        sd = ref.std(axis=0).mean()
-        assert sd > 0
-        assert np.abs(mine.mean(axis=0) - ref.mean(axis=0)).max() < 7 * sd / np.sqrt(reps) * np.sqrt(2)
-        assert abs(mine.std(axis=0).mean() / sd - 1) < 0.15
+        H.assert_moments_agree(mine, ref, std_tol=0.15)
