@@ -180,6 +180,7 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_mvm_forward_noalloc": (
             _I, [C.POINTER(IOParams), _FP, _I, _I, _FP, _FP, _I, C.c_uint64, C.c_uint32, _VP]
         ),
+        "ab200_set_mvm_path": (_I, [_I]),
         "ab200_kernel_launch_count": (C.c_uint64, []),
     }
     for name, (res, args) in sig.items():

@@ -124,6 +124,10 @@ void TileArray::forward(const float *x, float *y, int m, bool is_test, cudaStrea
     AB200_CUDA(cudaMemsetAsync(y, 0, (size_t)m * out_size_ * sizeof(float), s));
     return;
   }
+  if (tcEligible(m)) {
+    forwardTc(x, y, m, s);
+    return;
+  }
   for (int ii = in_begin_; ii < in_end_; ii++) {
     for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
       tile(ii - in_begin_, oi)
@@ -131,6 +135,52 @@ void TileArray::forward(const float *x, float *y, int m, bool is_test, cudaStrea
                           /*accumulate=*/ii != in_begin_, 0, s);
     }
   }
+}
+
+bool TileArray::tcEligible(int m) {
+  const int mode = mvmPath();
+  if (mode == 1 || tiles_.empty()) {
+    return false;
+  }
+  const IOEff &io = tiles_[0]->fio();
+  if (!TcEngine::ioSupported(io) || io.bm != AB200_BM_NONE) {
+    return false;
+  }
+  return mode == 2 || m >= 128;
+}
+
+// All local tiles in one launch: the DAC kernel quantises every (row, in-split) once, the MMA
+// kernel walks the in-splits per 128 x 128 output block and sums them after each tile's ADC.
+void TileArray::forwardTc(const float *x, float *y, int m, cudaStream_t s) {
+  const int n_in = in_end_ - in_begin_, n_out = (int)out_sizes_.size();
+  if (!tc_) {
+    tc_.reset(new TcEngine(device_));
+    tc_->configure(std::vector<int>(in_sizes_.begin() + in_begin_, in_sizes_.begin() + in_end_),
+                   out_sizes_);
+    tc_versions_.assign((size_t)n_in * n_out, 0);
+  }
+  TcEngine::Run r;
+  r.meta.resize((size_t)n_in * n_out);
+  for (int il = 0; il < n_in; il++) {
+    for (int oi = 0; oi < n_out; oi++) {
+      Tile &t = tile(il, oi);
+      const size_t idx = (size_t)il * n_out + oi;
+      if (tc_versions_[idx] != t.weightsVersion()) {
+        // forward operand: B[n = d][k = x] = w[k * d_size + n]
+        tc_->loadOperand(il, oi, t.weightsXD(), t.dSize(), 1, s);
+        tc_versions_[idx] = t.weightsVersion();
+      }
+      r.meta[idx].key = t.noiseKey();
+      r.meta[idx].call = t.nextForwardCall();
+    }
+  }
+  r.in = x + in_off_[in_begin_];
+  r.in_ss = in_size_;
+  r.m = m;
+  r.out = y;
+  r.out_ss = out_size_;
+  r.io = tiles_[0]->fio();
+  tc_->run(r, s);
 }
 
 void TileArray::forwardHost(const float *x, float *y, int m, bool is_test, cudaStream_t s) {

@@ -2,6 +2,7 @@
 // (TileModuleArray, src/aihwkit/simulator/tiles/array.py:30-198).
 #pragma once
 
+#include "tc_engine.h"
 #include "tile.h"
 
 #include <memory>
@@ -30,6 +31,12 @@ private:
   std::vector<int> in_sizes_, out_sizes_, in_off_, out_off_;
   int in_begin_, in_end_;
   std::vector<std::unique_ptr<Tile>> tiles_;
+  // one tensor-core engine for all locally owned tiles; operands are refreshed per tile when
+  // that tile's weights changed
+  std::unique_ptr<TcEngine> tc_;
+  std::vector<uint64_t> tc_versions_;
+  bool tcEligible(int m);
+  void forwardTc(const float *x, float *y, int m, cudaStream_t s);
   float *stage_dev_ = nullptr, *stage_pinned_ = nullptr;
   size_t stage_floats_ = 0;
 };

@@ -327,6 +327,15 @@ int ab200_array_set_seed(ab200_array *arr, uint64_t seed) {
   AB200_CATCH
 }
 
+int ab200_set_mvm_path(int mode) {
+  AB200_TRY
+  if (mode < 0 || mode > 2) {
+    AB200_FATAL("mvm path mode must be 0, 1 or 2");
+  }
+  ab200::setMvmPath(mode);
+  AB200_CATCH
+}
+
 uint64_t ab200_kernel_launch_count(void) { return ab200::launchCount(); }
 
 } // extern "C"

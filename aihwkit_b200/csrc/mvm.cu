@@ -336,29 +336,20 @@ void launchBmRerun(const MvmProblem &p, cudaStream_t stream) {
   if (smem > 200 * 1024) {
     AB200_FATAL("bound management: x_size too large for the re-run kernel");
   }
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (smem > 48 * 1024) {
     AB200_CUDA(cudaFuncSetAttribute(bmRerunKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     200 * 1024));
-    attr_set = true;
   }
   int blocks = p.m < 592 ? p.m : 592;
   bmRerunKernel<<<blocks, 256, smem, stream>>>(p);
   AB200_LAUNCH_CHECK();
 }
 
-bool tcMvmSupported(const MvmProblem &p);
-void launchMvmTc(const MvmProblem &p, cudaStream_t stream);
-
 void launchMvm(const MvmProblem &p, cudaStream_t stream) {
   if (p.m <= 0) {
     return;
   }
-  if (tcMvmSupported(p)) {
-    launchMvmTc(p, stream);
-  } else {
-    launchMvmSimt(p, stream);
-  }
+  launchMvmSimt(p, stream);
   launchBmRerun(p, stream);
 }
 

@@ -1,8 +1,758 @@
-// Tensor-core (tcgen05 / TMEM / TMA) IO-managed MVM. Placeholder selection logic until the
-// kernel lands: every problem goes to the CUDA-core path.
-#include "tile.h"
+// Tensor-core IO-managed MVM for sm_100a.
+//
+//   dacQuantizeKernel   noise management + DAC per (row, in-split): abs-max, scale, integer code
+//                       (exact in bf16), per-row scale / factor / ||v||.
+//   splitWeightsKernel  fp32 weight -> bf16 hi + bf16 lo (hi + lo keeps 16 mantissa bits), laid
+//                       out K-major for the MMA B operand.
+//   mvmTcKernel         warp-specialised: one TMA producer thread, one tcgen05.mma issuer thread,
+//                       eight epilogue warps. Accumulators live in TMEM (two 128-column buffers), so
+//                       the epilogue of in-split i (TMEM -> registers, Philox noise, ADC, clip,
+//                       bound flag, rescale, sum over in-splits in registers) overlaps the MMAs
+//                       of in-split i + 1. Every wait is bounded; on a time-out the kernel
+//                       records a status code, lets its copies land, frees TMEM and returns.
+//
+// Element-wise semantics are the helpers of mvm_common.cuh, shared with the CUDA-core path, and
+// the noise counters are the same, so both paths produce the same noise for the same call.
+#include "mvm_common.cuh"
+#include "tc_engine.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstring>
+#include <mutex>
 
 namespace ab200 {
-bool tcMvmSupported(const MvmProblem &) { return false; }
-void launchMvmTc(const MvmProblem &, cudaStream_t) { AB200_FATAL("tensor-core MVM not built"); }
+
+constexpr int TC_M = 128;      // rows per CTA
+constexpr int TC_N = 128;      // output columns per CTA (one chunk)
+constexpr int TC_K = 64;       // K elements per pipeline stage (128 B of bf16: one swizzle row)
+constexpr int TC_STAGES = 4;
+constexpr int TC_STAGE_A = TC_M * TC_K * 2;
+constexpr int TC_STAGE_B = TC_N * TC_K * 2;
+constexpr int TC_STAGE_BYTES = TC_STAGE_A + 2 * TC_STAGE_B; // A, B hi, B lo
+constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 2048;
+constexpr int TC_EPI_WARPS = 8;  // two per TMEM lane quarter, 64 columns each
+constexpr int TC_EPI_COLS = TC_N / (TC_EPI_WARPS / 4);
+// warp 0 TMA, warp 1 MMA + TMEM owner, warps 2..3 idle (keeps warp id % 4 == lane quarter for
+// the epilogue warps 4..11)
+constexpr int TC_THREADS = (4 + TC_EPI_WARPS) * 32;
+constexpr unsigned long long TC_WAIT_CYCLES = 4000000000ull; // about 2 s at 2 GHz
+
+enum : int { TC_ERR_FULL = 1, TC_ERR_EMPTY = 2, TC_ERR_TMEM_FULL = 3, TC_ERR_TMEM_EMPTY = 4 };
+
+struct TcKernelParams {
+  int m, I, O, n_chunks, nrows_pad, kpad;
+  const int4 *chunk;   // {o, n_local0, n_global0, valid}
+  const int4 *insplit; // {k0 (code column), n_k_stages, K_i, in_off}
+  const int *outn;     // N_o
+  const TcTileMeta *meta;
+  const float *scale, *factor, *vnorm;
+  int *flags;
+  float *out;
+  long long out_ss;
+  int accumulate, backward;
+  IOEff io;
+  int *status;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smemAddr(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbarInit(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbarArrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbarExpectTx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemAddr(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbarTry(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(smemAddr(bar)), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+// bounded wait: false after TC_WAIT_CYCLES or when another role already gave up
+__device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbarTry(bar, parity)) {
+    return true;
+  }
+  const long long t0 = clock64();
+  unsigned spins = 0;
+  while (!mbarTry(bar, parity)) {
+    if ((++spins & 255u) == 0u) {
+      if (*abort_flag != 0 || (unsigned long long)(clock64() - t0) > TC_WAIT_CYCLES) {
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tmaLoad2d(void *dst, const CUtensorMap *map, uint64_t *bar, int x,
+                                          int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes"
+               " [%0], [%1, {%3, %4}], [%2];" ::"r"(smemAddr(dst)),
+               "l"((uint64_t)map), "r"(smemAddr(bar)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tcFenceBefore() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcFenceAfter() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcCommit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smemAddr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tcMma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                      uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void tcLd32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
+               "[%32];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                 "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),
+                 "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                 "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                 "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+                 "=r"(v[31])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tcWaitLd() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major, 128-byte-swizzled tile whose rows are 64 bf16:
+// 8-row groups are 1024 B apart (stride byte offset), layout type 2 = SWIZZLE_128B, descriptor
+// version 1. Advancing by one 16-element K step adds 32 bytes to the start address.
+__device__ __forceinline__ uint64_t smemDesc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);      // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                      // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                      // descriptor version
+  d |= (uint64_t)2 << 61;                      // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: D = F32, A = B = BF16, both K-major, N = 128, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_N >> 3) << 17) |
+                            ((uint32_t)(TC_M >> 4) << 24);
+
+// ---------------------------------------------------------------------------------------------
+// the MVM kernel
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    mvmTcKernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_bhi,
+                const __grid_constant__ CUtensorMap tm_blo, const TcKernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the swizzled tiles
+  uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = (uint64_t *)(smem + TC_STAGES * TC_STAGE_BYTES);
+  uint64_t *full = bars;                       // [TC_STAGES]
+  uint64_t *empty = bars + TC_STAGES;          // [TC_STAGES]
+  uint64_t *tmem_full = bars + 2 * TC_STAGES;  // [2]
+  uint64_t *tmem_empty = tmem_full + 2;        // [2]
+  uint32_t *tmem_slot = (uint32_t *)(tmem_empty + 2);
+  volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk_idx = blockIdx.x;
+  const int r0 = blockIdx.y * TC_M;
+  const int4 ch = p.chunk[chunk_idx];
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; s++) {
+      mbarInit(&full[s], 1);
+      mbarInit(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbarInit(&tmem_full[b], 1);
+      mbarInit(&tmem_empty[b], TC_EPI_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    // TMEM: 256 columns = two fp32 accumulator buffers of 128 lanes x 128 columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smemAddr(tmem_slot)),
+                 "r"(256)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcFenceBefore();
+  __syncthreads();
+  tcFenceAfter();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int i = 0; i < p.I && ok; i++) {
+        const int4 is = p.insplit[i];
+        const int brow = i * p.nrows_pad + chunk_idx * TC_N;
+        for (int kc = 0; kc < is.y; kc++, it++) {
+          const int s = it % TC_STAGES;
+          if (!mbarWait(&empty[s], ((it / TC_STAGES) & 1) ^ 1, abort_flag)) {
+            atomicCAS(p.status, 0, TC_ERR_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t *st = smem + s * TC_STAGE_BYTES;
+          mbarExpectTx(&full[s], TC_STAGE_BYTES);
+          tmaLoad2d(st, &tm_a, &full[s], is.x + kc * TC_K, r0);
+          tmaLoad2d(st + TC_STAGE_A, &tm_bhi, &full[s], kc * TC_K, brow);
+          tmaLoad2d(st + TC_STAGE_A + TC_STAGE_B, &tm_blo, &full[s], kc * TC_K, brow);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int i = 0; i < p.I && ok; i++) {
+        const int nk = p.insplit[i].y;
+        const int b = i & 1;
+        if (!mbarWait(&tmem_empty[b], ((i >> 1) & 1) ^ 1, abort_flag)) {
+          atomicCAS(p.status, 0, TC_ERR_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tcFenceAfter();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * TC_N);
+        for (int kc = 0; kc < nk; kc++, it++) {
+          const int s = it % TC_STAGES;
+          if (!mbarWait(&full[s], (it / TC_STAGES) & 1, abort_flag)) {
+            atomicCAS(p.status, 0, TC_ERR_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tcFenceAfter();
+          const uint32_t a0 = smemAddr(smem + s * TC_STAGE_BYTES);
+          const uint64_t da = smemDesc(a0), dh = smemDesc(a0 + TC_STAGE_A),
+                         dl = smemDesc(a0 + TC_STAGE_A + TC_STAGE_B);
+#pragma unroll
+          for (int k = 0; k < TC_K / 16; k++) {
+            // +2 in the 16-byte-unit address field = 32 bytes = 16 bf16 along K
+            tcMma(d_tmem, da + 2 * k, dh + 2 * k, kIdesc, (kc > 0 || k > 0) ? 1u : 0u);
+            tcMma(d_tmem, da + 2 * k, dl + 2 * k, kIdesc, 1u);
+          }
+          tcCommit(&empty[s]); // frees the stage when these MMAs have read it
+        }
+        if (ok) {
+          tcCommit(&tmem_full[b]); // accumulator of in-split i is complete
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue warps ------------------------------
+    const int q = warp & 3;              // TMEM lane quarter this warp may access
+    const int cbase = ((warp - 4) >> 2) * TC_EPI_COLS; // first of this warp's columns
+    const int row = r0 + q * 32 + lane;
+    const bool row_ok = row < p.m;
+    const IOEff &io = p.io;
+    const int n_tile = p.outn[ch.x];
+    const uint64_t n4 = (uint64_t)((n_tile + 3) >> 2);
+    const uint32_t tag = p.backward ? TAG_BWD_OUT : TAG_FWD_OUT;
+    const float inv_res_out = io.res_out > 0.0f ? 1.0f / io.res_out : 0.0f;
+    float sum[TC_EPI_COLS];
+#pragma unroll
+    for (int c = 0; c < TC_EPI_COLS; c++) {
+      sum[c] = 0.0f;
+    }
+    bool exceeded = false;
+    bool ok = true;
+    for (int i = 0; i < p.I; i++) {
+      const int b = i & 1;
+      if (!mbarWait(&tmem_full[b], (i >> 1) & 1, abort_flag)) {
+        atomicCAS(p.status, 0, TC_ERR_TMEM_FULL);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tcFenceAfter();
+      const TcTileMeta meta = p.meta[i * p.O + ch.x];
+      float sc = 0.0f, fac = 0.0f, sigma = 0.0f;
+      if (row_ok) {
+        const long long si = (long long)i * p.m + row;
+        sc = p.scale[si];
+        fac = p.factor[si];
+        sigma = outputSigma(io, p.vnorm[si]);
+      }
+      const uint32_t taddr =
+          tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_N + cbase);
+#pragma unroll
+      for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 32) {
+        uint32_t v[32];
+        tcLd32(taddr + (uint32_t)c0, v);
+        tcWaitLd();
+        if (row_ok && sc != 0.0f) {
+          if (sigma > 0.0f) {
+            // noisy regime: the Gaussian decides the ADC code, so the divisions of the exact
+            // chain are replaced by multiplications with the reciprocal step
+#pragma unroll
+            for (int g = 0; g < 8; g++) {
+              const int cl = cbase + c0 + 4 * g; // column inside this 128-column chunk
+              if (cl < ch.w) {
+                float z[4];
+                gauss4(meta.key, (uint64_t)row * n4 + (uint64_t)((ch.y + cl) >> 2), meta.call, tag, z);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  float y = fmaf(__uint_as_float(v[4 * g + j]), io.res_in, sigma * z[j]);
+                  if (io.res_out > 0.0f) {
+                    y = rintf(y * inv_res_out) * io.res_out;
+                  }
+                  exceeded = exceeded || (y > io.out_bound) ||
+                             (io.bm_test_negative_bound && y < -io.out_bound);
+                  y = fminf(fmaxf(y, -io.out_bound), io.out_bound);
+                  sum[c0 + 4 * g + j] = fmaf(y, fac, sum[c0 + 4 * g + j]);
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 8; g++) {
+              const int cl = cbase + c0 + 4 * g;
+              if (cl < ch.w) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  // the MMA summed integer codes; one multiply by the DAC step gives sum(v * w)
+                  float y = __fmul_rn(__uint_as_float(v[4 * g + j]), io.res_in);
+                  y = finalizeOutput(io, y, 0.0f, 0.0f, exceeded);
+                  sum[c0 + 4 * g + j] += y * fac;
+                }
+              }
+            }
+          }
+        }
+      }
+      tcFenceBefore();
+      __syncwarp();
+      if (lane == 0) {
+        mbarArrive(&tmem_empty[b]);
+      }
+    }
+    if (ok && row_ok) {
+      if (exceeded && io.bm != AB200_BM_NONE && p.flags != nullptr) {
+        atomicOr(&p.flags[row], 1);
+      }
+      float *orow = p.out + (long long)row * p.out_ss + ch.z + cbase;
+      const bool vec = ((p.out_ss & 3) == 0) && ((ch.z & 3) == 0) &&
+                       ((((uintptr_t)p.out) & 15) == 0) && !p.accumulate;
+#pragma unroll
+      for (int c = 0; c < TC_EPI_COLS; c += 4) {
+        if (vec && cbase + c + 3 < ch.w) {
+          *reinterpret_cast<float4 *>(orow + c) =
+              make_float4(sum[c], sum[c + 1], sum[c + 2], sum[c + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            if (cbase + c + j < ch.w) {
+              orow[c + j] = p.accumulate ? orow[c + j] + sum[c + j] : sum[c + j];
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // teardown: everyone meets here, also after a time-out
+  tcFenceBefore();
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    // give copies that are still in flight time to land before the shared memory is released
+    const long long t0 = clock64();
+    while ((unsigned long long)(clock64() - t0) < 2000000ull) {
+      __nanosleep(1000);
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tcFenceAfter();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// DAC: one warp per (row, in-split)
+// ---------------------------------------------------------------------------------------------
+struct DacParams {
+  const float *in;
+  long long in_ss;
+  int m, I, kpad;
+  const int4 *insplit; // {k0, n_k_stages, K_i, in_off}
+  __nv_bfloat16 *codes;
+  long long codes_ld;
+  float *scale, *factor, *vnorm, *sval;
+  int *flags;
+  IOEff io;
+  float alpha;
+  int backward;
+  float code_bound; // largest |code| = inp_bound / res_in
+};
+
+__global__ void __launch_bounds__(256) dacQuantizeKernel(DacParams p) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long long)p.m * p.I) {
+    return;
+  }
+  const int i = (int)(w / p.m), row = (int)(w % p.m);
+  const int4 is = p.insplit[i];
+  const int K = is.z;
+  const float *x = p.in + (long long)row * p.in_ss + is.w;
+  const IOEff &io = p.io;
+  float amax = 0.0f;
+  if (io.nm == AB200_NM_ABS_MAX) {
+    for (int k = lane; k < K; k += 32) {
+      amax = fmaxf(amax, fabsf(x[k]));
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    }
+  }
+  const float sval = nmValue(io, amax);
+  const float scale = inputScale(io, sval, 1.0f, !p.backward);
+  __nv_bfloat16 *c = p.codes + (long long)row * p.codes_ld + is.x;
+  float acc = 0.0f;
+  for (int k = lane; k < p.kpad; k += 32) {
+    float code = 0.0f;
+    if (k < K && scale != 0.0f) {
+      code = rintf(__fdiv_rn(__fmul_rn(x[k], scale), io.res_in));
+      code = fminf(fmaxf(code, -p.code_bound), p.code_bound);
+    }
+    c[k] = __float2bfloat16_rn(code);
+    acc = fmaf(code, code, acc);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  }
+  if (lane == 0) {
+    const long long si = (long long)i * p.m + row;
+    p.scale[si] = scale;
+    p.factor[si] = outputFactor(io, p.alpha, sval, scale, p.backward);
+    p.vnorm[si] = sqrtf(acc) * io.res_in;
+    if (p.sval) {
+      p.sval[si] = sval;
+    }
+    if (p.flags) {
+      p.flags[si] = 0;
+    }
+  }
+}
+
+// B[n][k] = w[k * wk + n * wn]  ->  bf16 hi, lo at row (row0 + n) of the padded operand
+__global__ void __launch_bounds__(256)
+    splitWeightsKernel(const float *w, long long wk, long long wn, int N, int K, __nv_bfloat16 *hi,
+                       __nv_bfloat16 *lo, long long row0, int kpad) {
+  __shared__ float t[32][33];
+  const int bx = blockIdx.x * 32, by = blockIdx.y * 32; // bx along k, by along n
+  const bool k_fast = wk == 1;                          // which index is contiguous in memory
+  for (int r = threadIdx.y; r < 32; r += 8) {
+    // read with the contiguous index across threadIdx.x
+    int k = k_fast ? bx + threadIdx.x : bx + r;
+    int n = k_fast ? by + r : by + threadIdx.x;
+    float v = (k < K && n < N) ? w[(long long)k * wk + (long long)n * wn] : 0.0f;
+    if (k_fast) {
+      t[r][threadIdx.x] = v; // t[n][k]
+    } else {
+      t[threadIdx.x][r] = v; // t[n][k]
+    }
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += 8) {
+    int n = by + r, k = bx + threadIdx.x;
+    if (n < N && k < K) {
+      float v = t[r][threadIdx.x];
+      __nv_bfloat16 h = __float2bfloat16_rn(v);
+      float rem = v - __bfloat162float(h);
+      long long o = (row0 + n) * (long long)kpad + k;
+      hi[o] = h;
+      lo[o] = __float2bfloat16_rn(rem);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encodeTiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res);
+    if (e == cudaSuccess && res == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  if (!fn) {
+    AB200_FATAL("cuTensorMapEncodeTiled is not available from the CUDA driver");
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor [rows][cols] with row pitch `ld` elements; box = 64 columns x 128 rows,
+// 128-byte swizzle, out-of-range elements read as zero.
+static CUtensorMap makeMap(void *base, uint64_t rows, uint64_t cols, uint64_t ld) {
+  CUtensorMap map;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TC_K, (cuuint32_t)TC_M};
+  cuuint32_t estr[2] = {1, 1};
+  if (((uintptr_t)base & 15) != 0 || (strides[0] & 15) != 0) {
+    AB200_FATAL("tensor map: base and row pitch must be 16-byte aligned");
+  }
+  CUresult r = encodeTiled()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box,
+                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    AB200_FATAL("cuTensorMapEncodeTiled failed with code " << (int)r);
+  }
+  return map;
+}
+
+bool TcEngine::ioSupported(const IOEff &io) {
+  if (io.is_perfect || !(io.res_in > 0.0f) || !(io.inp_bound < 1e30f)) {
+    return false;
+  }
+  float cb = io.inp_bound / io.res_in;
+  float r = rintf(cb);
+  return r >= 1.0f && r <= 256.0f && fabsf(cb - r) < 1e-3f;
+}
+
+TcEngine::TcEngine(int device) : device_(device) {
+  AB200_CUDA(cudaSetDevice(device_));
+  AB200_CUDA(cudaHostAlloc(&status_host_, sizeof(int), cudaHostAllocMapped));
+  *status_host_ = 0;
+  AB200_CUDA(cudaHostGetDevicePointer(&status_dev_, status_host_, 0));
+}
+
+TcEngine::~TcEngine() {
+  int prev = -1;
+  cudaGetDevice(&prev);
+  cudaSetDevice(device_);
+  cudaFree(op_hi_);
+  cudaFree(op_lo_);
+  cudaFree(codes_);
+  cudaFree(scale_);
+  cudaFree(factor_);
+  cudaFree(vnorm_);
+  cudaFree(sval_);
+  cudaFree(flags_);
+  cudaFree(chunk_tab_);
+  cudaFree(insplit_tab_);
+  cudaFree(outn_tab_);
+  cudaFree(meta_dev_);
+  cudaFreeHost(status_host_);
+  if (prev >= 0) {
+    cudaSetDevice(prev);
+  }
+}
+
+void TcEngine::checkStatus() {
+  if (status_host_ && *status_host_ != 0) {
+    int code = *status_host_;
+    *status_host_ = 0;
+    AB200_FATAL("tensor-core MVM kernel gave up on a bounded wait (status " << code << ")");
+  }
+}
+
+void TcEngine::configure(const std::vector<int> &in_sizes, const std::vector<int> &out_sizes) {
+  AB200_CUDA(cudaSetDevice(device_));
+  in_sizes_ = in_sizes;
+  out_sizes_ = out_sizes;
+  int kmax = 0;
+  for (int k : in_sizes) {
+    kmax = std::max(kmax, k);
+  }
+  kpad_ = (kmax + TC_K - 1) / TC_K * TC_K;
+  std::vector<int4> chunks;
+  out_off_.clear();
+  int off = 0;
+  for (int o = 0; o < (int)out_sizes.size(); o++) {
+    out_off_.push_back(off);
+    for (int c = 0; c < out_sizes[o]; c += TC_N) {
+      chunks.push_back(make_int4(o, c, off + c, std::min(TC_N, out_sizes[o] - c)));
+    }
+    off += out_sizes[o];
+  }
+  n_chunks_ = (int)chunks.size();
+  nrows_pad_ = n_chunks_ * TC_N;
+  in_off_.clear();
+  std::vector<int4> ins;
+  off = 0;
+  for (int i = 0; i < (int)in_sizes.size(); i++) {
+    in_off_.push_back(off);
+    ins.push_back(make_int4(i * kpad_, (in_sizes[i] + TC_K - 1) / TC_K, in_sizes[i], off));
+    off += in_sizes[i];
+  }
+  const size_t op_elems = (size_t)in_sizes.size() * nrows_pad_ * kpad_;
+  cudaFree(op_hi_);
+  cudaFree(op_lo_);
+  cudaFree(chunk_tab_);
+  cudaFree(insplit_tab_);
+  cudaFree(outn_tab_);
+  cudaFree(meta_dev_);
+  AB200_CUDA(cudaMalloc(&op_hi_, op_elems * 2));
+  AB200_CUDA(cudaMalloc(&op_lo_, op_elems * 2));
+  AB200_CUDA(cudaMemset(op_hi_, 0, op_elems * 2));
+  AB200_CUDA(cudaMemset(op_lo_, 0, op_elems * 2));
+  AB200_CUDA(cudaMalloc(&chunk_tab_, chunks.size() * sizeof(int4)));
+  AB200_CUDA(cudaMemcpy(chunk_tab_, chunks.data(), chunks.size() * sizeof(int4), cudaMemcpyHostToDevice));
+  AB200_CUDA(cudaMalloc(&insplit_tab_, ins.size() * sizeof(int4)));
+  AB200_CUDA(cudaMemcpy(insplit_tab_, ins.data(), ins.size() * sizeof(int4), cudaMemcpyHostToDevice));
+  AB200_CUDA(cudaMalloc(&outn_tab_, out_sizes.size() * sizeof(int)));
+  AB200_CUDA(cudaMemcpy(outn_tab_, out_sizes.data(), out_sizes.size() * sizeof(int), cudaMemcpyHostToDevice));
+  AB200_CUDA(cudaMalloc(&meta_dev_, in_sizes.size() * out_sizes.size() * sizeof(TcTileMeta)));
+  m_cap_ = 0;
+}
+
+void TcEngine::loadOperand(int i, int o, const float *w, long long wk, long long wn,
+                           cudaStream_t s) {
+  AB200_CUDA(cudaSetDevice(device_));
+  const int N = out_sizes_[o], K = in_sizes_[i];
+  // row of the padded operand where out-split o starts: its first chunk * 128
+  long long chunk0 = 0;
+  for (int oo = 0; oo < o; oo++) {
+    chunk0 += (out_sizes_[oo] + TC_N - 1) / TC_N;
+  }
+  const long long row0 = (long long)i * nrows_pad_ + chunk0 * TC_N;
+  dim3 grid((K + 31) / 32, (N + 31) / 32), block(32, 8);
+  splitWeightsKernel<<<grid, block, 0, s>>>(w, wk, wn, N, K, (__nv_bfloat16 *)op_hi_,
+                                            (__nv_bfloat16 *)op_lo_, row0, kpad_);
+  AB200_LAUNCH_CHECK();
+}
+
+void TcEngine::ensureBatch(int m) {
+  if (m <= m_cap_) {
+    return;
+  }
+  AB200_CUDA(cudaDeviceSynchronize());
+  cudaFree(codes_);
+  cudaFree(scale_);
+  cudaFree(factor_);
+  cudaFree(vnorm_);
+  cudaFree(sval_);
+  cudaFree(flags_);
+  const int cap = m + m / 4 + 128;
+  const size_t I = in_sizes_.size();
+  AB200_CUDA(cudaMalloc(&codes_, (size_t)cap * I * kpad_ * 2));
+  AB200_CUDA(cudaMalloc(&scale_, (size_t)cap * I * sizeof(float)));
+  AB200_CUDA(cudaMalloc(&factor_, (size_t)cap * I * sizeof(float)));
+  AB200_CUDA(cudaMalloc(&vnorm_, (size_t)cap * I * sizeof(float)));
+  AB200_CUDA(cudaMalloc(&sval_, (size_t)cap * I * sizeof(float)));
+  AB200_CUDA(cudaMalloc(&flags_, (size_t)cap * I * sizeof(int)));
+  m_cap_ = cap;
+}
+
+void TcEngine::run(const Run &r, cudaStream_t s) {
+  AB200_CUDA(cudaSetDevice(device_));
+  checkStatus();
+  if (r.m <= 0) {
+    return;
+  }
+  const int I = (int)in_sizes_.size(), O = (int)out_sizes_.size();
+  if ((int)r.meta.size() != I * O) {
+    AB200_FATAL("tensor-core MVM: tile meta size mismatch");
+  }
+  if (!ioSupported(r.io)) {
+    AB200_FATAL("tensor-core MVM: IO settings not expressible as integer DAC codes");
+  }
+  ensureBatch(r.m);
+  const bool ext = r.scale != nullptr;
+  if (ext && I != 1) {
+    AB200_FATAL("tensor-core MVM: caller-owned scratch needs a single in-split");
+  }
+  AB200_CUDA(cudaMemcpyAsync(meta_dev_, r.meta.data(), r.meta.size() * sizeof(TcTileMeta),
+                             cudaMemcpyHostToDevice, s));
+
+  DacParams d{};
+  d.in = r.in;
+  d.in_ss = r.in_ss;
+  d.m = r.m;
+  d.I = I;
+  d.kpad = kpad_;
+  d.insplit = (const int4 *)insplit_tab_;
+  d.codes = (__nv_bfloat16 *)codes_;
+  d.codes_ld = (long long)I * kpad_;
+  d.scale = ext ? r.scale : scale_;
+  d.factor = ext ? r.factor : factor_;
+  d.vnorm = ext ? r.vnorm : vnorm_;
+  d.sval = ext ? r.sval : sval_;
+  d.flags = ext ? r.flags : flags_;
+  d.io = r.io;
+  d.alpha = r.alpha;
+  d.backward = r.backward ? 1 : 0;
+  d.code_bound = rintf(r.io.inp_bound / r.io.res_in);
+  const long long warps = (long long)r.m * I;
+  dacQuantizeKernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(d);
+  AB200_LAUNCH_CHECK();
+
+  CUtensorMap tm_a = makeMap(codes_, (uint64_t)r.m, (uint64_t)I * kpad_, (uint64_t)I * kpad_);
+  CUtensorMap tm_bhi = makeMap(op_hi_, (uint64_t)I * nrows_pad_, (uint64_t)kpad_, (uint64_t)kpad_);
+  CUtensorMap tm_blo = makeMap(op_lo_, (uint64_t)I * nrows_pad_, (uint64_t)kpad_, (uint64_t)kpad_);
+
+  TcKernelParams p{};
+  p.m = r.m;
+  p.I = I;
+  p.O = O;
+  p.n_chunks = n_chunks_;
+  p.nrows_pad = nrows_pad_;
+  p.kpad = kpad_;
+  p.chunk = (const int4 *)chunk_tab_;
+  p.insplit = (const int4 *)insplit_tab_;
+  p.outn = outn_tab_;
+  p.meta = meta_dev_;
+  p.scale = d.scale;
+  p.factor = d.factor;
+  p.vnorm = d.vnorm;
+  p.flags = r.io.bm != AB200_BM_NONE ? d.flags : nullptr;
+  p.out = r.out;
+  p.out_ss = r.out_ss;
+  p.accumulate = r.accumulate ? 1 : 0;
+  p.backward = r.backward ? 1 : 0;
+  p.io = r.io;
+  p.status = status_dev_;
+  AB200_CUDA(cudaFuncSetAttribute(mvmTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  TC_SMEM_BYTES));
+  dim3 grid(n_chunks_, (r.m + TC_M - 1) / TC_M);
+  mvmTcKernel<<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
+  AB200_LAUNCH_CHECK();
+}
+
 } // namespace ab200

@@ -1,0 +1,83 @@
+// Tensor-core engine of the IO-managed MVM: tcgen05 MMAs with TMEM accumulators, operands staged
+// in shared memory by TMA, DAC codes x split-bf16 weights.
+//
+// One engine serves a group of physical tiles that form a logical layer:
+//     out[m][N_total] = sum over in-splits i of  IO_i( codes_i[m][K_i] * W_i[K_i][N_total] )
+// where IO_i is the per-tile noise / ADC / clip / rescale of the reference
+// (src/rpucuda/rpu_forward_backward_pass.cpp:673-719, 985-987) applied to each in-split's product
+// before the sum (TileModuleArray.forward, src/aihwkit/simulator/tiles/array.py:155-182).
+// A single tile is the group I = O = 1; backward uses the transposed operand.
+#pragma once
+
+#include "tile.h"
+
+#include <vector>
+
+namespace ab200 {
+
+struct TcTileMeta {
+  PhiloxKey key;
+  uint32_t call;
+  uint32_t pad;
+};
+
+class TcEngine {
+public:
+  explicit TcEngine(int device);
+  ~TcEngine();
+  TcEngine(const TcEngine &) = delete;
+  TcEngine &operator=(const TcEngine &) = delete;
+
+  // in_sizes[i] = K_i, out_sizes[o] = N_o
+  void configure(const std::vector<int> &in_sizes, const std::vector<int> &out_sizes);
+  // operand of tile (i, o):  B[n][k] = w[k * wk + n * wn],  stored as bf16 hi + lo
+  void loadOperand(int i, int o, const float *w, long long wk, long long wn, cudaStream_t s);
+
+  struct Run {
+    const float *in = nullptr; // [m][*], row stride in_ss, in-split i starts at column in_off[i]
+    long long in_ss = 0;
+    int m = 0;
+    float *out = nullptr; // [m][N_total], row stride out_ss
+    long long out_ss = 0;
+    bool accumulate = false;
+    bool backward = false;
+    IOEff io;
+    float alpha = 1.0f;
+    std::vector<TcTileMeta> meta; // [I * O], index i * O + o
+    // optional caller-owned per-row scratch (only valid for I == 1): lets the bound-management
+    // re-run kernel see the same noise-management values and flags
+    float *scale = nullptr, *factor = nullptr, *vnorm = nullptr, *sval = nullptr;
+    int *flags = nullptr;
+  };
+  void run(const Run &r, cudaStream_t s);
+
+  // whether the IO settings can be expressed as integer DAC codes in bf16
+  static bool ioSupported(const IOEff &io);
+  // throws if an earlier launch reported a device-side failure (timeout of a bounded wait)
+  void checkStatus();
+
+  int numIn() const { return (int)in_sizes_.size(); }
+  int numOut() const { return (int)out_sizes_.size(); }
+
+private:
+  void ensureBatch(int m);
+
+  int device_;
+  std::vector<int> in_sizes_, out_sizes_, in_off_, out_off_;
+  int kpad_ = 0;      // padded K of every in-split (multiple of 64)
+  int n_chunks_ = 0;  // 128-column chunks over all out-splits
+  int nrows_pad_ = 0; // n_chunks_ * 128
+  void *op_hi_ = nullptr, *op_lo_ = nullptr; // bf16 [I * nrows_pad][kpad]
+  void *codes_ = nullptr;                    // bf16 [m_cap][I * kpad]
+  int m_cap_ = 0;
+  float *scale_ = nullptr, *factor_ = nullptr, *vnorm_ = nullptr, *sval_ = nullptr;
+  int *flags_ = nullptr;
+  int *chunk_tab_ = nullptr;   // int4 per chunk
+  int *insplit_tab_ = nullptr; // int4 per in-split
+  int *outn_tab_ = nullptr;    // N_o per out-split
+  TcTileMeta *meta_dev_ = nullptr;
+  int *status_host_ = nullptr; // mapped pinned word written by the kernel on failure
+  int *status_dev_ = nullptr;
+};
+
+} // namespace ab200

@@ -1,6 +1,7 @@
 // Host side of the analog tile: configuration, per-element device parameters, weight access and
 // the sequencing of forward / backward / update (including Tiki-Taka transfers).
 #include "tile.h"
+#include "tc_engine.h"
 
 #include <atomic>
 #include <chrono>
@@ -14,6 +15,10 @@ namespace ab200 {
 static std::atomic<uint64_t> g_launches{0};
 void countLaunch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 uint64_t launchCount() { return g_launches.load(std::memory_order_relaxed); }
+
+static std::atomic<int> g_mvm_path{0};
+void setMvmPath(int mode) { g_mvm_path.store(mode); }
+int mvmPath() { return g_mvm_path.load(); }
 
 // detail::checkRes (src/rpucuda/rpu_pulsed_meta_parameter.cpp:26-29)
 static float checkRes(float res) {
@@ -472,6 +477,7 @@ void Tile::setWeightsDevice(const float *w_dev_xd, cudaStream_t s) {
     update_idx_ = 0;
     slice_idx_ = 0;
   }
+  w_version_++;
   AB200_CUDA(cudaStreamSynchronize(s));
 }
 
@@ -502,6 +508,9 @@ void Tile::setSharedWeights(float *w_dev_xd, uint64_t version) {
   requireDevice("set_shared_weights");
   if (!w_dev_xd) {
     AB200_FATAL("set_shared_weights: null pointer");
+  }
+  if (w_ != w_dev_xd || shared_version_ != version) {
+    w_version_++;
   }
   w_ = w_dev_xd;
   shared_version_ = version;
@@ -611,6 +620,7 @@ void Tile::setHidden(const float *in) {
     }
   }
   // weights are re-clipped to the new bounds (onSetWeights at the end of setDeviceParameter)
+  w_version_++;
   if (device_ >= 0) {
     launchClipToBounds(w_, dev_[n_dev_ - 1].par4, (long long)size, nullptr);
     if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
@@ -668,7 +678,12 @@ void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, boo
   p.noise_id = 0;
   fillMvmScratch(p);
   AB200_CUDA(cudaMemsetAsync(bm_stats_, 0, 2 * sizeof(int), s));
-  launchMvm(p, s);
+  if (tcEligible(p)) {
+    runTc(p, s);
+    launchBmRerun(p, s);
+  } else {
+    launchMvm(p, s);
+  }
 }
 
 void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_ss, int m,
@@ -696,7 +711,11 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
   p.call = fwd_calls_++;
   p.noise_id = noise_id;
   fillMvmScratch(p);
-  launchMvm(p, s);
+  if (!accumulate && tcEligible(p)) {
+    runTc(p, s);
+  } else {
+    launchMvm(p, s);
+  }
 }
 
 void Tile::backward(const float *d, float *x, bool bias, int m, bool d_trans, bool x_trans,
@@ -728,7 +747,62 @@ void Tile::backward(const float *d, float *x, bool bias, int m, bool d_trans, bo
   p.call = bwd_calls_++;
   p.noise_id = 0;
   fillMvmScratch(p);
-  launchMvm(p, s);
+  if (tcEligible(p)) {
+    runTc(p, s);
+  } else {
+    launchMvm(p, s);
+  }
+}
+
+// Tensor-core path: rows contiguous, no bias column, DAC codes representable, and either forced
+// or large enough that the extra kernels (operand split, DAC) pay off.
+bool Tile::tcEligible(const MvmProblem &p) const {
+  const int mode = mvmPath();
+  if (mode == 1) {
+    return false;
+  }
+  if (p.in_fs != 1 || p.out_fs != 1 || p.in_real != p.in_size || p.out_store != p.out_size ||
+      p.noise_id != 0 || !TcEngine::ioSupported(p.io)) {
+    return false;
+  }
+  if (mode == 2) {
+    return true;
+  }
+  return p.m >= 128 && (double)p.m * p.in_size * p.out_size >= 16777216.0;
+}
+
+void Tile::runTc(const MvmProblem &p, cudaStream_t s) {
+  std::unique_ptr<TcEngine> &eng = p.backward ? tc_bwd_ : tc_fwd_;
+  uint64_t &ver = p.backward ? tc_bwd_version_ : tc_fwd_version_;
+  if (!eng) {
+    eng.reset(new TcEngine(device_));
+    eng->configure({p.in_size}, {p.out_size});
+    ver = 0;
+  }
+  if (ver != w_version_) {
+    eng->loadOperand(0, 0, p.w, p.wk, p.wn, s);
+    ver = w_version_;
+  }
+  TcEngine::Run r;
+  r.in = p.in;
+  r.in_ss = p.in_ss;
+  r.m = p.m;
+  r.out = p.out;
+  r.out_ss = p.out_ss;
+  r.accumulate = p.accumulate != 0;
+  r.backward = p.backward != 0;
+  r.io = p.io;
+  r.alpha = p.alpha;
+  TcTileMeta meta{};
+  meta.key = p.key;
+  meta.call = p.call;
+  r.meta.push_back(meta);
+  r.scale = p.scale;
+  r.factor = p.factor;
+  r.vnorm = p.vnorm;
+  r.sval = p.sval;
+  r.flags = p.flags;
+  eng->run(r, s);
 }
 
 void Tile::lastBmStats(int32_t *n_rerun, float *max_red) {
@@ -811,6 +885,7 @@ void Tile::update(const float *x, const float *d, bool bias, int m, bool x_trans
     return; // "if (!learning_rate) return" (rpu_weight_updater.cpp:206-208)
   }
   ensureScratch(m);
+  w_version_++;
   UpdateProblem u{};
   const int x_in = x_size_ - (bias ? 1 : 0);
   u.x = x;

@@ -80,7 +80,15 @@ struct MvmProblem {
   int *bm_stats; // [0] re-run samples, [1] max reduction (float bits)
 };
 
+// CUDA-core path: noise management, fused MVM, bound-management re-run
 void launchMvm(const MvmProblem &p, cudaStream_t stream);
+// bound-management re-run of the rows whose first round clipped (forward only; no-op otherwise)
+void launchBmRerun(const MvmProblem &p, cudaStream_t stream);
+
+// Kernel selection for the MVM: 0 = automatic, 1 = always CUDA cores, 2 = tensor cores whenever
+// the problem can be expressed on them.
+void setMvmPath(int mode);
+int mvmPath();
 
 // Per-element device parameters in the update kernel's layout, index = x * d_size + d.
 struct DeviceStore {
@@ -131,6 +139,8 @@ void launchTransferRead(const float *w_fast, int col, int d_size, const IOEff &i
 void launchTransposeDX(const float *src, float *dst, int rows, int cols, cudaStream_t stream);
 void launchClipToBounds(float *w, const float4 *par4, long long n, cudaStream_t stream);
 
+class TcEngine;
+
 class Tile {
 public:
   Tile(const ab200_tile_config &cfg, int cuda_device);
@@ -179,6 +189,9 @@ public:
 
   const IOEff &fio() const { return f_io_; }
   float *weightsXD() { return w_; }
+  uint64_t weightsVersion() const { return w_version_; }
+  PhiloxKey noiseKey() const { return key_; }
+  uint32_t nextForwardCall() { return fwd_calls_++; }
 
 private:
   void requireDevice(const char *what) const;
@@ -187,6 +200,8 @@ private:
   void uploadDeviceStore(DeviceStore &ds);
   void populateHost();
   void fillMvmScratch(MvmProblem &p);
+  bool tcEligible(const MvmProblem &p) const;
+  void runTc(const MvmProblem &p, cudaStream_t s);
   void pulsedUpdateRange(UpdateProblem &p, cudaStream_t s);
   void doTransfer(cudaStream_t s);
   float pulseCountLR() const;
@@ -217,6 +232,9 @@ private:
   int *flags_ = nullptr, *bm_stats_ = nullptr;
   uint32_t *xw_ = nullptr, *dw_ = nullptr;
   float *onehot_ = nullptr, *tread_ = nullptr;
+  // tensor-core engines (forward / backward operand caches), rebuilt when the weights change
+  std::unique_ptr<TcEngine> tc_fwd_, tc_bwd_;
+  uint64_t w_version_ = 1, tc_fwd_version_ = 0, tc_bwd_version_ = 0;
   // staging for the *_host entry points
   float *stage_dev_ = nullptr;
   float *stage_pinned_ = nullptr;

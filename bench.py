@@ -68,7 +68,7 @@ def inference_config(seed: int):
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -81,7 +81,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -90,9 +90,12 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
+    def stop(self, window=None):
+        """`window` = (t0, t1) wall-clock bounds of the timed region: samples inside it are used;
+        if the region was shorter than the sampling period, all samples taken under load (from
+        the warm-up on) are used instead and the result says so."""
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         self.proc.terminate()
@@ -102,7 +105,13 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        lines = self.lines
+        scope = "warm-up + timed region"
+        if window is not None:
+            inside = [l for l in lines if window[0] <= l[0] <= window[1] + 0.02]
+            if inside:
+                lines, scope = inside, "timed region"
+        for _, line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -116,7 +125,7 @@ class ClockSampler:
                     reasons.add(name)
         return dict(sm_mhz=statistics.median(sm) if sm else None,
                     sm_max_mhz=max(smax) if smax else None, reasons=sorted(reasons),
-                    samples=len(sm))
+                    samples=len(sm), scope=scope)
 
 
 # --------------------------------------------------------------------------------------------
@@ -244,11 +253,12 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    t_wall0 = time.time()
     launches0 = lib.ab200_kernel_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
@@ -258,7 +268,7 @@ def run_ours(args):
     barrier()
     ms = ev0.elapsed_time(ev1)
     launches = lib.ab200_kernel_launch_count() - launches0
-    clocks = sampler.stop()
+    clocks = sampler.stop((t_wall0, time.time()))
 
     # kernel-only time of the local MVM work (no reduce), for the roofline
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -332,7 +342,7 @@ def run_ours(args):
                 "kernel_ms_per_step": kernel_ms, "tiles_per_launch_group": n_local,
             },
         }
-        if world == 1:
+        if world == 1 and not args.no_cpu_baseline:
             base = cpu_reference_rate(rows=args.ref_rows)
             if base is not None:
                 line["cpu_baseline"] = base
@@ -347,11 +357,13 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ref-rows", type=int, default=4096,
                     help="rows of the bounded CPU sample (reference arm / cpu_baseline)")
+    ap.add_argument("--no-cpu-baseline", action="store_true",
+                    help="skip the CPU baseline leg (used for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -325,6 +325,11 @@ int ab200_mvm_forward_noalloc(const ab200_io_params *forward_io, const float *w_
                               int x_size, int d_size, const float *x_dev, float *d_dev,
                               int m_batch, uint64_t seed, uint32_t call, void *stream);
 
+/* Kernel selection for the MVM (no counterpart in the reference, which always calls cuBLAS):
+ * 0 = automatic (tensor cores for large aligned problems), 1 = CUDA cores only, 2 = tensor
+ * cores whenever the IO settings allow. Process-wide; used by tests and benchmarks. */
+int ab200_set_mvm_path(int mode);
+
 /* Number of kernels this library has launched since it was loaded (all tiles, this process). */
 uint64_t ab200_kernel_launch_count(void);
 

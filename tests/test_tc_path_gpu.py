@@ -1,0 +1,155 @@
+"""The tensor-core (tcgen05 / TMEM / TMA) MVM kernel against the oracle and against the
+CUDA-core kernels, forced on with ab200_set_mvm_path(2) so that small and ragged shapes are
+covered too."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import analog_tile_oracle as O
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def path():
+    from aihwkit_b200 import _cabi
+
+    lib = _cabi.lib()
+
+    def set_path(mode):
+        assert lib.ab200_set_mvm_path(mode) == 0
+
+    yield set_path
+    lib.ab200_set_mvm_path(0)
+
+
+def _tile(p, dp, x, d, seed=5):
+    from aihwkit_b200.rpu_base import tiles as T
+
+    cfg = p._config(x, d, dp, seed=seed)
+    return T.AnalogTile(cfg, cuda_device=0), cfg
+
+
+SHAPES = [(64, 128, 128), (512, 512, 256), (100, 36, 33), (461, 300, 130), (1024, 1024, 256)]
+
+
+@pytest.mark.parametrize("x_size,d_size,m", SHAPES)
+def test_tc_forward_backward_pre_adc(path, x_size, d_size, m):
+    """ADC off, noise off: integer DAC codes x (bf16 hi + lo) weights with fp32 accumulation
+    stay within 1e-5 of the output range of the fp32 oracle."""
+    path(2)
+    rng = np.random.default_rng(x_size + m)
+    p = H.training_params(noise=False, pulse_det=True, bm=False, adc=False, out_bound=0.0)
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+    X[1] = 0.0
+    y = t.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    y_or = O.forward(W, X, O.IO.from_c(cfg.forward_io))
+    assert np.abs(y - y_or).max() <= 1e-5 * np.abs(y_or).max()
+    assert np.all(y[1] == 0)
+    g = t.backward(torch.from_numpy(Dm).cuda()).cpu().numpy()
+    g_or = O.backward(W, Dm, O.IO.from_c(cfg.backward_io, backward=True))
+    assert np.abs(g - g_or).max() <= 1e-5 * np.abs(g_or).max()
+
+
+@pytest.mark.parametrize("x_size,d_size,m", SHAPES)
+@pytest.mark.parametrize("out_bound", [12.0, 2.0])
+def test_tc_forward_backward_post_adc(path, x_size, d_size, m, out_bound):
+    path(2)
+    rng = np.random.default_rng(7 * x_size + m)
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=out_bound)
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+    fio = O.IO.from_c(cfg.forward_io)
+    y = t.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    y_or, _, scale, red = O.forward(W, X, fio, return_pre_adc=True)
+    frac, worst = H.lsb_report(y, y_or, (fio.res_out / scale)[:, None])
+    assert frac <= 1e-3 and worst <= 1.001, (frac, worst)
+    n_rerun, max_red = t.last_bm_stats()
+    assert n_rerun == int((red > 1).sum()) and max_red == float(red.max())
+    bio = O.IO.from_c(cfg.backward_io, backward=True)
+    g = t.backward(torch.from_numpy(Dm).cuda()).cpu().numpy()
+    g_or = O.backward(W, Dm, bio)
+    frac, worst = H.lsb_report(g, g_or, (bio.res_out * np.abs(Dm).max(axis=1))[:, None])
+    assert frac <= 1e-3 and worst <= 1.001, (frac, worst)
+
+
+def test_tc_and_cuda_core_paths_draw_the_same_noise(path):
+    """Noise on: both kernels key the noise by (seed, call, element), so the same call gives the
+    same output up to rare ADC flips caused by the different product rounding."""
+    rng = np.random.default_rng(3)
+    x_size, d_size, m = 256, 192, 160
+    p = H.training_params(noise=True, pulse_det=False, bm=True)
+    outs = []
+    for mode in (1, 2):
+        path(mode)
+        t, cfg = _tile(p, H.device("cs", True), x_size, d_size, seed=99)
+        t.set_weights(torch.from_numpy(np.random.default_rng(1).uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+        X = torch.from_numpy(np.random.default_rng(2).uniform(-1, 1, (m, x_size)).astype(np.float32)).cuda()
+        outs.append(t.forward(X).cpu().numpy())
+    lsb = O.IO.from_c(cfg.forward_io).res_out * 1.0  # scale <= 1 since |x| <= 1
+    diff = np.abs(outs[0] - outs[1])
+    assert (diff > 1e-4).mean() <= 1e-3
+    assert diff.max() <= 1.01 * lsb * np.abs(X.cpu().numpy()).max()
+
+
+@pytest.mark.parametrize("out_size,in_size,max_tile,m", [(256, 384, 128, 140), (768, 2304, 512, 130),
+                                                         (100, 1030, 512, 7), (1024, 1024, 512, 512)])
+def test_tc_mapped_forward(path, out_size, in_size, max_tile, m):
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+    from tests.test_mapped_and_transfer_gpu import _array_oracle
+
+    rng = np.random.default_rng(out_size)
+    W = rng.normal(0, 1 / np.sqrt(in_size), (out_size, in_size)).astype(np.float32)
+    X = rng.normal(0, 1, (m, in_size)).astype(np.float32)
+    # noise off against the oracle
+    path(2)
+    cfg = H.inference_params(noise=False)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=3)
+    arr = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+    arr.set_weights(torch.from_numpy(W))
+    y = arr.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    y_or, lsb, n_in = _array_oracle(W, X, cfg, max_tile, max_tile)
+    diff = np.abs(y - y_or)
+    assert (diff > 1e-3 * lsb).mean() <= 1e-3 * n_in
+    assert (diff <= 1.001 * lsb * n_in).all()
+    # noise on: tensor-core and CUDA-core paths agree call by call
+    cfgn = H.inference_params(noise=True)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=8)
+    outs = []
+    for mode in (1, 2):
+        path(mode)
+        a = T.TileArray(cfgn, out_size, in_size, max_tile, max_tile, cuda_device=0)
+        a.set_weights(torch.from_numpy(W))
+        outs.append(a.forward(torch.from_numpy(X).cuda()).cpu().numpy())
+    d2 = np.abs(outs[0] - outs[1])
+    assert (d2 > 1e-3 * lsb).mean() <= 2e-3 * n_in
+    assert (d2 <= 1.001 * lsb * n_in).all()
+
+
+def test_tc_operand_cache_follows_weight_changes(path):
+    path(2)
+    rng = np.random.default_rng(5)
+    x_size, d_size, m = 128, 128, 128
+    p = H.training_params(noise=False, pulse_det=True, bm=False)
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    X = torch.from_numpy(rng.uniform(-1, 1, (m, x_size)).astype(np.float32)).cuda()
+    Dm = torch.from_numpy(rng.normal(0, 0.1, (m, d_size)).astype(np.float32)).cuda()
+    fio = O.IO.from_c(cfg.forward_io)
+    for step in range(3):
+        if step == 0:
+            t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+        else:
+            t.set_learning_rate(0.05)
+            t.update(X, Dm)  # weights move; the bf16 operand must be rebuilt
+        W = t.get_weights().numpy()
+        y = t.forward(X).cpu().numpy()
+        y_or, _, scale, _ = O.forward(W, X.cpu().numpy(), fio, return_pre_adc=True)
+        frac, worst = H.lsb_report(y, y_or, (fio.res_out / scale)[:, None])
+        assert frac <= 1e-3 and worst <= 1.001, (step, frac, worst)
