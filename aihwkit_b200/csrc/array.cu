@@ -18,15 +18,9 @@ std::vector<int> splitSizes(int size, int split_max) {
   return out;
 }
 
-static uint64_t tileSeed(uint64_t seed, int in_idx, int out_idx) {
-  // the key depends on the GLOBAL tile coordinates only, so a sharded layer draws the same noise
-  // no matter how many ranks it is spread over
-  uint64_t z = seed + 0x9E3779B97F4A7C15ull * (uint64_t)(1 + in_idx * 4099 + out_idx);
-  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-  z ^= z >> 31;
-  return z ? z : 1;
-}
+// All tiles of a layer share one noise key; tile (i, o) draws from its own counter stream,
+// selected by its GLOBAL index i * n_out + o, so a sharded layer draws the same noise no matter
+// how many ranks it is spread over.
 
 TileArray::TileArray(const ab200_tile_config &cfg, int out_size, int in_size, int max_out,
                      int max_in, int in_begin, int in_end, int cuda_device)
@@ -60,7 +54,7 @@ TileArray::TileArray(const ab200_tile_config &cfg, int out_size, int in_size, in
       ab200_tile_config c = cfg;
       c.x_size = in_sizes_[ii];
       c.d_size = out_sizes_[oi];
-      c.seed = tileSeed(seed, ii, oi);
+      c.seed = seed;
       if (c.device[0].construction_seed) {
         c.device[0].construction_seed += (uint32_t)(ii * 4099 + oi);
       }
@@ -77,7 +71,7 @@ TileArray::~TileArray() {
 void TileArray::setSeed(uint64_t seed) {
   for (int ii = in_begin_; ii < in_end_; ii++) {
     for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
-      tile(ii - in_begin_, oi).setSeed(tileSeed(seed, ii, oi));
+      tile(ii - in_begin_, oi).setSeed(seed ? seed : 0x1234567ull);
     }
   }
 }
@@ -132,7 +126,8 @@ void TileArray::forward(const float *x, float *y, int m, bool is_test, cudaStrea
     for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
       tile(ii - in_begin_, oi)
           .forwardStrided(x + in_off_[ii], in_size_, y + out_off_[oi], out_size_, m,
-                          /*accumulate=*/ii != in_begin_, 0, s);
+                          /*accumulate=*/ii != in_begin_,
+                          (uint32_t)(ii * (int)out_sizes_.size() + oi), s);
     }
   }
 }
@@ -160,7 +155,8 @@ void TileArray::forwardTc(const float *x, float *y, int m, cudaStream_t s) {
     tc_versions_.assign((size_t)n_in * n_out, 0);
   }
   TcEngine::Run r;
-  r.meta.resize((size_t)n_in * n_out);
+  r.key = tile(0, 0).noiseKey();
+  r.noise_id0 = (uint32_t)(in_begin_ * n_out);
   for (int il = 0; il < n_in; il++) {
     for (int oi = 0; oi < n_out; oi++) {
       Tile &t = tile(il, oi);
@@ -170,8 +166,11 @@ void TileArray::forwardTc(const float *x, float *y, int m, cudaStream_t s) {
         tc_->loadOperand(il, oi, t.weightsXD(), t.dSize(), 1, s);
         tc_versions_[idx] = t.weightsVersion();
       }
-      r.meta[idx].key = t.noiseKey();
-      r.meta[idx].call = t.nextForwardCall();
+      // every tile's call counter advances together; the group uses one value
+      const uint32_t call = t.nextForwardCall();
+      if (idx == 0) {
+        r.call = call;
+      }
     }
   }
   r.in = x + in_off_[in_begin_];

@@ -47,12 +47,13 @@ struct PhiloxKey {
   uint32_t k0, k1;
 };
 
+template <int ROUNDS>
 __host__ __device__ __forceinline__ void
-philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, PhiloxKey key, uint32_t out[4]) {
+philox4x32(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, PhiloxKey key, uint32_t out[4]) {
   const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
   uint32_t k0 = key.k0, k1 = key.k1;
 #pragma unroll
-  for (int r = 0; r < 10; r++) {
+  for (int r = 0; r < ROUNDS; r++) {
 #ifdef __CUDA_ARCH__
     uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
     uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
@@ -75,6 +76,15 @@ philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, PhiloxKey key,
   out[3] = c3;
 }
 
+// Ten rounds is the standard strength, used wherever individual bits are consumed (pulse
+// trains). The Gaussian output noise of the MVM uses seven rounds, the smallest count the
+// authors report as passing BigCrush; it is generated once per output element and is the
+// largest arithmetic cost of the tensor-core epilogue.
+__host__ __device__ __forceinline__ void
+philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, PhiloxKey key, uint32_t out[4]) {
+  philox4x32<10>(c0, c1, c2, c3, key, out);
+}
+
 // purpose tags (4th counter word) so that streams never overlap
 enum : uint32_t {
   TAG_FWD_OUT = 0x10000000u,   // + bound-management round
@@ -89,21 +99,25 @@ enum : uint32_t {
 // uniform in (0,1) with 24 random bits
 __device__ __forceinline__ float u01(uint32_t x) { return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f); }
 
-// two standard normals from two 32-bit words (Box-Muller)
+// Two standard normals from two 32-bit words (Box-Muller). The uniforms are built from the top
+// 23 bits by setting the exponent, which keeps the integer-to-float conversions off the
+// quarter-rate conversion pipe; u1 lies in [2^-23, 1], so the radius is finite (<= 5.65).
 __device__ __forceinline__ void boxMuller(uint32_t a, uint32_t b, float &z0, float &z1) {
-  float u1 = u01(a);
-  float r = sqrtf(-2.0f * __logf(u1));
-  float s, c;
-  __sincosf(6.283185307179586f * u01(b), &s, &c);
-  z0 = r * c;
-  z1 = r * s;
+  float u1 = 2.0f - __uint_as_float(0x3f800000u | (a >> 9));
+  float u2 = __uint_as_float(0x3f800000u | (b >> 9)) - 1.0f;
+  float r2 = -1.3862943611198906f * __log2f(u1); // -2 ln(u1)
+  float r;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(r2));
+  float ang = 6.283185307179586f * u2;
+  z0 = r * __cosf(ang);
+  z1 = r * __sinf(ang);
 }
 
 // four standard normals for noise block `blk` of call `call`
 __device__ __forceinline__ void
 gauss4(PhiloxKey key, uint64_t blk, uint32_t call, uint32_t tag, float z[4]) {
   uint32_t r[4];
-  philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), call, tag, key, r);
+  philox4x32<7>((uint32_t)blk, (uint32_t)(blk >> 32), call, tag, key, r);
   boxMuller(r[0], r[1], z[0], z[1]);
   boxMuller(r[2], r[3], z[2], z[3]);
 }

@@ -5,7 +5,7 @@
 //   splitWeightsKernel  fp32 weight -> bf16 hi + bf16 lo (hi + lo keeps 16 mantissa bits), laid
 //                       out K-major for the MMA B operand.
 //   mvmTcKernel         warp-specialised: one TMA producer thread, one tcgen05.mma issuer thread,
-//                       eight epilogue warps. Accumulators live in TMEM (two 128-column buffers), so
+//                       sixteen epilogue warps. Accumulators live in TMEM (two 128-column buffers), so
 //                       the epilogue of in-split i (TMEM -> registers, Philox noise, ADC, clip,
 //                       bound flag, rescale, sum over in-splits in registers) overlaps the MMAs
 //                       of in-split i + 1. Every wait is bounded; on a time-out the kernel
@@ -32,11 +32,12 @@ constexpr int TC_STAGE_A = TC_M * TC_K * 2;
 constexpr int TC_STAGE_B = TC_N * TC_K * 2;
 constexpr int TC_STAGE_BYTES = TC_STAGE_A + 2 * TC_STAGE_B; // A, B hi, B lo
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 2048;
-constexpr int TC_EPI_WARPS = 8;  // two per TMEM lane quarter, 64 columns each
+constexpr int TC_EPI_WARPS = 16; // four per TMEM lane quarter, 32 columns each
 constexpr int TC_EPI_COLS = TC_N / (TC_EPI_WARPS / 4);
-// warp 0 TMA, warp 1 MMA + TMEM owner, warps 2..3 idle (keeps warp id % 4 == lane quarter for
-// the epilogue warps 4..11)
-constexpr int TC_THREADS = (4 + TC_EPI_WARPS) * 32;
+// warps 0..15 epilogue (warp id % 4 = TMEM lane quarter), warp 16 TMA, warp 17 MMA + TMEM owner
+constexpr int TC_WARP_TMA = TC_EPI_WARPS;
+constexpr int TC_WARP_MMA = TC_EPI_WARPS + 1;
+constexpr int TC_THREADS = (TC_EPI_WARPS + 2) * 32;
 constexpr unsigned long long TC_WAIT_CYCLES = 4000000000ull; // about 2 s at 2 GHz
 
 enum : int { TC_ERR_FULL = 1, TC_ERR_EMPTY = 2, TC_ERR_TMEM_FULL = 3, TC_ERR_TMEM_EMPTY = 4 };
@@ -46,7 +47,8 @@ struct TcKernelParams {
   const int4 *chunk;   // {o, n_local0, n_global0, valid}
   const int4 *insplit; // {k0 (code column), n_k_stages, K_i, in_off}
   const int *outn;     // N_o
-  const TcTileMeta *meta;
+  PhiloxKey key;
+  uint32_t call, noise_id0;
   const float *scale, *factor, *vnorm;
   int *flags;
   float *out;
@@ -139,6 +141,15 @@ __device__ __forceinline__ void tcLd32(uint32_t taddr, uint32_t (&v)[32]) {
                : "r"(taddr)
                : "memory");
 }
+__device__ __forceinline__ void tcLd16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                 "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),
+                 "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+               : "r"(taddr)
+               : "memory");
+}
 __device__ __forceinline__ void tcWaitLd() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -163,6 +174,7 @@ constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_
 // ---------------------------------------------------------------------------------------------
 // the MVM kernel
 // ---------------------------------------------------------------------------------------------
+template <bool BM>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     mvmTcKernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_bhi,
                 const __grid_constant__ CUtensorMap tm_blo, const TcKernelParams p) {
@@ -194,7 +206,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == TC_WARP_MMA) {
     // TMEM: 256 columns = two fp32 accumulator buffers of 128 lanes x 128 columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smemAddr(tmem_slot)),
@@ -207,7 +219,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   tcFenceAfter();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == TC_WARP_TMA) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int it = 0;
@@ -231,7 +243,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == TC_WARP_MMA) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       int it = 0;
@@ -271,17 +283,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
       }
     }
-  } else if (warp >= 4) {
+  } else {
     // ------------------------------ epilogue warps ------------------------------
-    const int q = warp & 3;              // TMEM lane quarter this warp may access
-    const int cbase = ((warp - 4) >> 2) * TC_EPI_COLS; // first of this warp's columns
+    const int q = warp & 3;                      // TMEM lane quarter this warp may access
+    const int cbase = (warp >> 2) * TC_EPI_COLS; // first of this warp's columns
     const int row = r0 + q * 32 + lane;
     const bool row_ok = row < p.m;
     const IOEff &io = p.io;
     const int n_tile = p.outn[ch.x];
     const uint64_t n4 = (uint64_t)((n_tile + 3) >> 2);
     const uint32_t tag = p.backward ? TAG_BWD_OUT : TAG_FWD_OUT;
-    const float inv_res_out = io.res_out > 0.0f ? 1.0f / io.res_out : 0.0f;
+    const bool adc = io.res_out > 0.0f;
+    const float inv_res_out = adc ? 1.0f / io.res_out : 0.0f;
+    const float kMagic = 12582912.0f; // 1.5 * 2^23: adding and subtracting rounds to nearest even
     float sum[TC_EPI_COLS];
 #pragma unroll
     for (int c = 0; c < TC_EPI_COLS; c++) {
@@ -289,8 +303,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
     bool exceeded = false;
     bool ok = true;
+    // per-row scalars of the next in-split are fetched one iteration ahead
+    float sc_n = 0.0f, fac_n = 0.0f, vn_n = 0.0f;
+    if (row_ok) {
+      sc_n = p.scale[row];
+      fac_n = p.factor[row];
+      vn_n = p.vnorm[row];
+    }
     for (int i = 0; i < p.I; i++) {
       const int b = i & 1;
+      const float sc = sc_n, fac = fac_n;
+      const float sigma = outputSigma(io, vn_n);
+      if (row_ok && i + 1 < p.I) {
+        const long long si = (long long)(i + 1) * p.m + row;
+        sc_n = p.scale[si];
+        fac_n = p.factor[si];
+        vn_n = p.vnorm[si];
+      }
+      const uint32_t tile_tag = tag + p.noise_id0 + (uint32_t)(i * p.O + ch.x);
       if (!mbarWait(&tmem_full[b], (i >> 1) & 1, abort_flag)) {
         atomicCAS(p.status, 0, TC_ERR_TMEM_FULL);
         *abort_flag = 1;
@@ -298,39 +328,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         break;
       }
       tcFenceAfter();
-      const TcTileMeta meta = p.meta[i * p.O + ch.x];
-      float sc = 0.0f, fac = 0.0f, sigma = 0.0f;
-      if (row_ok) {
-        const long long si = (long long)i * p.m + row;
-        sc = p.scale[si];
-        fac = p.factor[si];
-        sigma = outputSigma(io, p.vnorm[si]);
-      }
       const uint32_t taddr =
           tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_N + cbase);
 #pragma unroll
-      for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 32) {
-        uint32_t v[32];
-        tcLd32(taddr + (uint32_t)c0, v);
+      for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 16) {
+        uint32_t v[16];
+        tcLd16(taddr + (uint32_t)c0, v);
         tcWaitLd();
         if (row_ok && sc != 0.0f) {
           if (sigma > 0.0f) {
             // noisy regime: the Gaussian decides the ADC code, so the divisions of the exact
             // chain are replaced by multiplications with the reciprocal step
 #pragma unroll
-            for (int g = 0; g < 8; g++) {
+            for (int g = 0; g < 4; g++) {
               const int cl = cbase + c0 + 4 * g; // column inside this 128-column chunk
               if (cl < ch.w) {
                 float z[4];
-                gauss4(meta.key, (uint64_t)row * n4 + (uint64_t)((ch.y + cl) >> 2), meta.call, tag, z);
+                gauss4(p.key, (uint64_t)row * n4 + (uint64_t)((ch.y + cl) >> 2), p.call, tile_tag, z);
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                   float y = fmaf(__uint_as_float(v[4 * g + j]), io.res_in, sigma * z[j]);
-                  if (io.res_out > 0.0f) {
-                    y = rintf(y * inv_res_out) * io.res_out;
+                  if (adc) {
+                    y = (fmaf(y, inv_res_out, kMagic) - kMagic) * io.res_out;
                   }
-                  exceeded = exceeded || (y > io.out_bound) ||
-                             (io.bm_test_negative_bound && y < -io.out_bound);
+                  if (BM) {
+                    exceeded = exceeded || (y > io.out_bound) ||
+                               (io.bm_test_negative_bound && y < -io.out_bound);
+                  }
                   y = fminf(fmaxf(y, -io.out_bound), io.out_bound);
                   sum[c0 + 4 * g + j] = fmaf(y, fac, sum[c0 + 4 * g + j]);
                 }
@@ -338,7 +362,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
           } else {
 #pragma unroll
-            for (int g = 0; g < 8; g++) {
+            for (int g = 0; g < 4; g++) {
               const int cl = cbase + c0 + 4 * g;
               if (cl < ch.w) {
 #pragma unroll
@@ -394,7 +418,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
   }
   __syncthreads();
-  if (warp == 1) {
+  if (warp == TC_WARP_MMA) {
     tcFenceAfter();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256)
                  : "memory");
@@ -577,7 +601,6 @@ TcEngine::~TcEngine() {
   cudaFree(chunk_tab_);
   cudaFree(insplit_tab_);
   cudaFree(outn_tab_);
-  cudaFree(meta_dev_);
   cudaFreeHost(status_host_);
   if (prev >= 0) {
     cudaSetDevice(prev);
@@ -627,7 +650,6 @@ void TcEngine::configure(const std::vector<int> &in_sizes, const std::vector<int
   cudaFree(chunk_tab_);
   cudaFree(insplit_tab_);
   cudaFree(outn_tab_);
-  cudaFree(meta_dev_);
   AB200_CUDA(cudaMalloc(&op_hi_, op_elems * 2));
   AB200_CUDA(cudaMalloc(&op_lo_, op_elems * 2));
   AB200_CUDA(cudaMemset(op_hi_, 0, op_elems * 2));
@@ -638,7 +660,6 @@ void TcEngine::configure(const std::vector<int> &in_sizes, const std::vector<int
   AB200_CUDA(cudaMemcpy(insplit_tab_, ins.data(), ins.size() * sizeof(int4), cudaMemcpyHostToDevice));
   AB200_CUDA(cudaMalloc(&outn_tab_, out_sizes.size() * sizeof(int)));
   AB200_CUDA(cudaMemcpy(outn_tab_, out_sizes.data(), out_sizes.size() * sizeof(int), cudaMemcpyHostToDevice));
-  AB200_CUDA(cudaMalloc(&meta_dev_, in_sizes.size() * out_sizes.size() * sizeof(TcTileMeta)));
   m_cap_ = 0;
 }
 
@@ -687,9 +708,6 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
     return;
   }
   const int I = (int)in_sizes_.size(), O = (int)out_sizes_.size();
-  if ((int)r.meta.size() != I * O) {
-    AB200_FATAL("tensor-core MVM: tile meta size mismatch");
-  }
   if (!ioSupported(r.io)) {
     AB200_FATAL("tensor-core MVM: IO settings not expressible as integer DAC codes");
   }
@@ -698,9 +716,6 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   if (ext && I != 1) {
     AB200_FATAL("tensor-core MVM: caller-owned scratch needs a single in-split");
   }
-  AB200_CUDA(cudaMemcpyAsync(meta_dev_, r.meta.data(), r.meta.size() * sizeof(TcTileMeta),
-                             cudaMemcpyHostToDevice, s));
-
   DacParams d{};
   d.in = r.in;
   d.in_ss = r.in_ss;
@@ -737,7 +752,9 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   p.chunk = (const int4 *)chunk_tab_;
   p.insplit = (const int4 *)insplit_tab_;
   p.outn = outn_tab_;
-  p.meta = meta_dev_;
+  p.key = r.key;
+  p.call = r.call;
+  p.noise_id0 = r.noise_id0;
   p.scale = d.scale;
   p.factor = d.factor;
   p.vnorm = d.vnorm;
@@ -748,10 +765,16 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   p.backward = r.backward ? 1 : 0;
   p.io = r.io;
   p.status = status_dev_;
-  AB200_CUDA(cudaFuncSetAttribute(mvmTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  TC_SMEM_BYTES));
   dim3 grid(n_chunks_, (r.m + TC_M - 1) / TC_M);
-  mvmTcKernel<<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
+  if (r.io.bm != AB200_BM_NONE) {
+    AB200_CUDA(cudaFuncSetAttribute(mvmTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    TC_SMEM_BYTES));
+    mvmTcKernel<true><<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
+  } else {
+    AB200_CUDA(cudaFuncSetAttribute(mvmTcKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    TC_SMEM_BYTES));
+    mvmTcKernel<false><<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
+  }
   AB200_LAUNCH_CHECK();
 }
 

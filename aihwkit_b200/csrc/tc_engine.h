@@ -15,12 +15,6 @@
 
 namespace ab200 {
 
-struct TcTileMeta {
-  PhiloxKey key;
-  uint32_t call;
-  uint32_t pad;
-};
-
 class TcEngine {
 public:
   explicit TcEngine(int device);
@@ -43,7 +37,12 @@ public:
     bool backward = false;
     IOEff io;
     float alpha = 1.0f;
-    std::vector<TcTileMeta> meta; // [I * O], index i * O + o
+    // noise: one key and call counter for the whole group; tile (i, o) draws from the stream
+    // with purpose tag + noise_id0 + i * O + o, so tiles are independent and the result does
+    // not depend on how a layer is split over engines
+    PhiloxKey key{0, 0};
+    uint32_t call = 0;
+    uint32_t noise_id0 = 0;
     // optional caller-owned per-row scratch (only valid for I == 1): lets the bound-management
     // re-run kernel see the same noise-management values and flags
     float *scale = nullptr, *factor = nullptr, *vnorm = nullptr, *sval = nullptr;
@@ -75,7 +74,6 @@ private:
   int *chunk_tab_ = nullptr;   // int4 per chunk
   int *insplit_tab_ = nullptr; // int4 per in-split
   int *outn_tab_ = nullptr;    // N_o per out-split
-  TcTileMeta *meta_dev_ = nullptr;
   int *status_host_ = nullptr; // mapped pinned word written by the kernel on failure
   int *status_dev_ = nullptr;
 };

@@ -762,7 +762,7 @@ bool Tile::tcEligible(const MvmProblem &p) const {
     return false;
   }
   if (p.in_fs != 1 || p.out_fs != 1 || p.in_real != p.in_size || p.out_store != p.out_size ||
-      p.noise_id != 0 || !TcEngine::ioSupported(p.io)) {
+      !TcEngine::ioSupported(p.io)) {
     return false;
   }
   if (mode == 2) {
@@ -793,10 +793,9 @@ void Tile::runTc(const MvmProblem &p, cudaStream_t s) {
   r.backward = p.backward != 0;
   r.io = p.io;
   r.alpha = p.alpha;
-  TcTileMeta meta{};
-  meta.key = p.key;
-  meta.call = p.call;
-  r.meta.push_back(meta);
+  r.key = p.key;
+  r.call = p.call;
+  r.noise_id0 = p.noise_id;
   r.scale = p.scale;
   r.factor = p.factor;
   r.vnorm = p.vnorm;
