@@ -4,12 +4,17 @@
 //                       (exact in bf16), per-row scale / factor / ||v||.
 //   splitWeightsKernel  fp32 weight -> bf16 hi + bf16 lo (hi + lo keeps 16 mantissa bits), laid
 //                       out K-major for the MMA B operand.
-//   mvmTcKernel         warp-specialised: one TMA producer thread, one tcgen05.mma issuer thread,
-//                       sixteen epilogue warps. Accumulators live in TMEM (two 128-column buffers), so
-//                       the epilogue of in-split i (TMEM -> registers, Philox noise, ADC, clip,
-//                       bound flag, rescale, sum over in-splits in registers) overlaps the MMAs
-//                       of in-split i + 1. Every wait is bounded; on a time-out the kernel
-//                       records a status code, lets its copies land, frees TMEM and returns.
+//   mvmTcKernel         persistent, warp-specialised: one TMA producer thread stages the codes and
+//                       the weight operand in shared memory, hi and lo stacked as one 256-row B
+//                       tile, so a single tcgen05.mma (M 128, N 256, K 16) per K step yields the
+//                       hi product in accumulator columns 0..127 and the lo product in columns
+//                       128..255 while reading the codes once; one thread issues the MMAs;
+//                       sixteen epilogue warps. TMEM holds two such 256-column accumulators, so
+//                       the epilogue of in-split i (TMEM -> registers, hi + lo, Philox noise, ADC,
+//                       clip, bound flag, rescale, running sum over the in-splits in registers)
+//                       overlaps the MMAs of in-split i + 1. Every wait is bounded; on a time-out
+//                       the kernel records a status code, lets its copies land, frees TMEM and
+//                       returns.
 //
 // Element-wise semantics are the helpers of mvm_common.cuh, shared with the CUDA-core path, and
 // the noise counters are the same, so both paths produce the same noise for the same call.
@@ -19,8 +24,11 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace ab200 {
 
@@ -30,17 +38,24 @@ constexpr int TC_K = 64;       // K elements per pipeline stage (128 B of bf16: 
 constexpr int TC_STAGES = 4;
 constexpr int TC_STAGE_A = TC_M * TC_K * 2;
 constexpr int TC_STAGE_B = TC_N * TC_K * 2;
-constexpr int TC_STAGE_BYTES = TC_STAGE_A + 2 * TC_STAGE_B; // A, B hi, B lo
+constexpr int TC_STAGE_BYTES = TC_STAGE_A + 2 * TC_STAGE_B; // A, then B hi and B lo back to back
+constexpr int TC_ACC_COLS = 2 * TC_N;                       // hi and lo halves of one accumulator
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 2048;
 constexpr int TC_EPI_WARPS = 16; // four per TMEM lane quarter, 32 columns each
 constexpr int TC_EPI_COLS = TC_N / (TC_EPI_WARPS / 4);
-// warps 0..15 epilogue (warp id % 4 = TMEM lane quarter), warp 16 TMA, warp 17 MMA + TMEM owner
+// warps 0..15 epilogue (warp id % 4 = TMEM lane quarter), warp 16 TMA, warp 17 MMA issuer + TMEM
+// owner
 constexpr int TC_WARP_TMA = TC_EPI_WARPS;
 constexpr int TC_WARP_MMA = TC_EPI_WARPS + 1;
 constexpr int TC_THREADS = (TC_EPI_WARPS + 2) * 32;
 constexpr unsigned long long TC_WAIT_CYCLES = 4000000000ull; // about 2 s at 2 GHz
 
-enum : int { TC_ERR_FULL = 1, TC_ERR_EMPTY = 2, TC_ERR_TMEM_FULL = 3, TC_ERR_TMEM_EMPTY = 4 };
+enum : int {
+  TC_ERR_FULL = 1,
+  TC_ERR_EMPTY = 2,
+  TC_ERR_TMEM_FULL = 3,
+  TC_ERR_TMEM_EMPTY = 4
+};
 
 struct TcKernelParams {
   int m, I, O, n_chunks, nrows_pad, kpad;
@@ -56,6 +71,10 @@ struct TcKernelParams {
   int accumulate, backward;
   IOEff io;
   int *status;
+  // optional per-CTA cycle counters of time spent waiting, by role (diagnostics; null = off):
+  // [0] MMA on operands, [2] MMA on a free accumulator, [3] MMA total, [4] TMA producer on a
+  // free stage, [6] epilogue on a complete accumulator, [7] epilogue total
+  long long *prof;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -119,12 +138,20 @@ __device__ __forceinline__ void tcCommit(uint64_t *bar) {
                    smemAddr(bar))
                : "memory");
 }
+// D[tmem] (+)= A[smem descriptor] * B[smem descriptor]
 __device__ __forceinline__ void tcMma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                       uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\t"
                "setp.ne.b32 p, %4, 0;\n\t"
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
                "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void tcLd8(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                 "=r"(v[7])
+               : "r"(taddr)
                : "memory");
 }
 __device__ __forceinline__ void tcLd32(uint32_t taddr, uint32_t (&v)[32]) {
@@ -150,6 +177,17 @@ __device__ __forceinline__ void tcLd16(uint32_t taddr, uint32_t (&v)[16]) {
                : "r"(taddr)
                : "memory");
 }
+__device__ __forceinline__ void tcSt16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+               "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+               "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),
+               "r"(v[15])
+               : "memory");
+}
+__device__ __forceinline__ void tcWaitSt() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tcWaitLd() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -167,9 +205,18 @@ __device__ __forceinline__ uint64_t smemDesc(uint32_t saddr) {
   return d;
 }
 
-// kind::f16 instruction descriptor: D = F32, A = B = BF16, both K-major, N = 128, M = 128.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_N >> 3) << 17) |
-                            ((uint32_t)(TC_M >> 4) << 24);
+// kind::f16 instruction descriptor: D = F32, A = B = BF16, both K-major, M = 128, N = 256 (the
+// stacked hi and lo rows of the weight tile).
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                            ((uint32_t)(TC_ACC_COLS >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+
+#define TC_TIMED_WAIT(acc, expr)                                                                   \
+  ([&]() {                                                                                         \
+    const long long t_ = clock64();                                                                \
+    const bool r_ = (expr);                                                                        \
+    (acc) += clock64() - t_;                                                                       \
+    return r_;                                                                                     \
+  }())
 
 // ---------------------------------------------------------------------------------------------
 // the MVM kernel
@@ -182,17 +229,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   // 1024-byte alignment for the swizzled tiles
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = (uint64_t *)(smem + TC_STAGES * TC_STAGE_BYTES);
-  uint64_t *full = bars;                       // [TC_STAGES]
-  uint64_t *empty = bars + TC_STAGES;          // [TC_STAGES]
-  uint64_t *tmem_full = bars + 2 * TC_STAGES;  // [2]
-  uint64_t *tmem_empty = tmem_full + 2;        // [2]
+  uint64_t *full = bars;                       // [TC_STAGES] operands landed in shared memory
+  uint64_t *empty = bars + TC_STAGES;          // [TC_STAGES] MMAs have read the stage
+  uint64_t *tmem_full = bars + 2 * TC_STAGES;  // [2]         accumulator complete
+  uint64_t *tmem_empty = tmem_full + 2;        // [2]         accumulator drained
   uint32_t *tmem_slot = (uint32_t *)(tmem_empty + 2);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int chunk_idx = blockIdx.x;
-  const int r0 = blockIdx.y * TC_M;
-  const int4 ch = p.chunk[chunk_idx];
+  // persistent CTA: work item w = (row block, 128-column chunk); consecutive items share the
+  // row block, so the codes stay in L2 while all chunks of that row block are produced
+  const int n_items = p.n_chunks * ((p.m + TC_M - 1) / TC_M);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; s++) {
@@ -207,10 +254,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == TC_WARP_MMA) {
-    // TMEM: 256 columns = two fp32 accumulator buffers of 128 lanes x 128 columns
+    // TMEM: all 512 columns = two accumulators of 128 lanes x (128 hi + 128 lo) fp32 columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smemAddr(tmem_slot)),
-                 "r"(256)
+                 "r"(512)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -224,12 +271,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     if (lane == 0) {
       int it = 0;
       bool ok = true;
+      long long w_empty = 0;
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+      const int chunk_idx = w % p.n_chunks;
+      const int r0 = (w / p.n_chunks) * TC_M;
       for (int i = 0; i < p.I && ok; i++) {
         const int4 is = p.insplit[i];
         const int brow = i * p.nrows_pad + chunk_idx * TC_N;
         for (int kc = 0; kc < is.y; kc++, it++) {
           const int s = it % TC_STAGES;
-          if (!mbarWait(&empty[s], ((it / TC_STAGES) & 1) ^ 1, abort_flag)) {
+          if (!TC_TIMED_WAIT(w_empty, mbarWait(&empty[s], ((it / TC_STAGES) & 1) ^ 1, abort_flag))) {
             atomicCAS(p.status, 0, TC_ERR_EMPTY);
             *abort_flag = 1;
             ok = false;
@@ -242,25 +293,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           tmaLoad2d(st + TC_STAGE_A + TC_STAGE_B, &tm_blo, &full[s], kc * TC_K, brow);
         }
       }
+      }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 4] = w_empty;
+      }
     }
   } else if (warp == TC_WARP_MMA) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      int it = 0;
+      int it = 0, ai = 0; // pipeline stage counter, accumulator-buffer use counter
       bool ok = true;
-      for (int i = 0; i < p.I && ok; i++) {
+      long long w_full = 0, w_tmem = 0;
+      const long long t_start = clock64();
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+      for (int i = 0; i < p.I && ok; i++, ai++) {
         const int nk = p.insplit[i].y;
-        const int b = i & 1;
-        if (!mbarWait(&tmem_empty[b], ((i >> 1) & 1) ^ 1, abort_flag)) {
+        const int b = ai & 1;
+        if (!TC_TIMED_WAIT(w_tmem, mbarWait(&tmem_empty[b], ((ai >> 1) & 1) ^ 1, abort_flag))) {
           atomicCAS(p.status, 0, TC_ERR_TMEM_EMPTY);
           *abort_flag = 1;
+          ok = false;
           break;
         }
         tcFenceAfter();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(b * TC_N);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * TC_ACC_COLS);
         for (int kc = 0; kc < nk; kc++, it++) {
           const int s = it % TC_STAGES;
-          if (!mbarWait(&full[s], (it / TC_STAGES) & 1, abort_flag)) {
+          if (!TC_TIMED_WAIT(w_full, mbarWait(&full[s], (it / TC_STAGES) & 1, abort_flag))) {
             atomicCAS(p.status, 0, TC_ERR_FULL);
             *abort_flag = 1;
             ok = false;
@@ -268,13 +327,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           }
           tcFenceAfter();
           const uint32_t a0 = smemAddr(smem + s * TC_STAGE_BYTES);
-          const uint64_t da = smemDesc(a0), dh = smemDesc(a0 + TC_STAGE_A),
-                         dl = smemDesc(a0 + TC_STAGE_A + TC_STAGE_B);
+          // the B descriptor starts at the hi tile; its 256 rows run on into the lo tile
+          const uint64_t da = smemDesc(a0), db = smemDesc(a0 + TC_STAGE_A);
 #pragma unroll
           for (int k = 0; k < TC_K / 16; k++) {
             // +2 in the 16-byte-unit address field = 32 bytes = 16 bf16 along K
-            tcMma(d_tmem, da + 2 * k, dh + 2 * k, kIdesc, (kc > 0 || k > 0) ? 1u : 0u);
-            tcMma(d_tmem, da + 2 * k, dl + 2 * k, kIdesc, 1u);
+            tcMma(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kc > 0 || k > 0) ? 1u : 0u);
           }
           tcCommit(&empty[s]); // frees the stage when these MMAs have read it
         }
@@ -282,27 +340,40 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           tcCommit(&tmem_full[b]); // accumulator of in-split i is complete
         }
       }
+      }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = w_full;
+        p.prof[blockIdx.x * 8 + 2] = w_tmem;
+        p.prof[blockIdx.x * 8 + 3] = clock64() - t_start;
+      }
     }
   } else {
     // ------------------------------ epilogue warps ------------------------------
     const int q = warp & 3;                      // TMEM lane quarter this warp may access
     const int cbase = (warp >> 2) * TC_EPI_COLS; // first of this warp's columns
-    const int row = r0 + q * 32 + lane;
-    const bool row_ok = row < p.m;
     const IOEff &io = p.io;
-    const int n_tile = p.outn[ch.x];
-    const uint64_t n4 = (uint64_t)((n_tile + 3) >> 2);
     const uint32_t tag = p.backward ? TAG_BWD_OUT : TAG_FWD_OUT;
     const bool adc = io.res_out > 0.0f;
     const float inv_res_out = adc ? 1.0f / io.res_out : 0.0f;
     const float kMagic = 12582912.0f; // 1.5 * 2^23: adding and subtracting rounds to nearest even
-    float sum[TC_EPI_COLS];
+    bool ok = true;
+    int ai = 0; // accumulator-buffer use counter, in step with the MMA issuer
+    long long w_tfull = 0;
+    const long long t_epi = clock64();
+    for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+    const int4 ch = p.chunk[w % p.n_chunks];
+    const int row = (w / p.n_chunks) * TC_M + q * 32 + lane;
+    const bool row_ok = row < p.m;
+    const uint64_t n4 = (uint64_t)((p.outn[ch.x] + 3) >> 2);
+    const bool vec = ((p.out_ss & 3) == 0) && ((ch.z & 3) == 0) &&
+                     ((((uintptr_t)p.out) & 15) == 0) && !p.accumulate;
+    float *orow = p.out + (long long)row * p.out_ss + ch.z + cbase;
+    bool exceeded = false;
+    float sum[TC_EPI_COLS]; // running sums over the in-splits
 #pragma unroll
     for (int c = 0; c < TC_EPI_COLS; c++) {
       sum[c] = 0.0f;
     }
-    bool exceeded = false;
-    bool ok = true;
     // per-row scalars of the next in-split are fetched one iteration ahead
     float sc_n = 0.0f, fac_n = 0.0f, vn_n = 0.0f;
     if (row_ok) {
@@ -310,18 +381,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       fac_n = p.factor[row];
       vn_n = p.vnorm[row];
     }
-    for (int i = 0; i < p.I; i++) {
-      const int b = i & 1;
+    for (int i = 0; i < p.I; i++, ai++) {
+      const int b = ai & 1;
+      const bool last = i + 1 == p.I;
       const float sc = sc_n, fac = fac_n;
       const float sigma = outputSigma(io, vn_n);
-      if (row_ok && i + 1 < p.I) {
+      if (row_ok && !last) {
         const long long si = (long long)(i + 1) * p.m + row;
         sc_n = p.scale[si];
         fac_n = p.factor[si];
         vn_n = p.vnorm[si];
       }
       const uint32_t tile_tag = tag + p.noise_id0 + (uint32_t)(i * p.O + ch.x);
-      if (!mbarWait(&tmem_full[b], (i >> 1) & 1, abort_flag)) {
+      if (!TC_TIMED_WAIT(w_tfull, mbarWait(&tmem_full[b], (ai >> 1) & 1, abort_flag))) {
         atomicCAS(p.status, 0, TC_ERR_TMEM_FULL);
         *abort_flag = 1;
         ok = false;
@@ -329,25 +401,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       }
       tcFenceAfter();
       const uint32_t taddr =
-          tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_N + cbase);
+          tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_ACC_COLS + cbase);
+      const bool live = row_ok && sc != 0.0f;
 #pragma unroll
-      for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 16) {
-        uint32_t v[16];
-        tcLd16(taddr + (uint32_t)c0, v);
+      for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 8) {
+        uint32_t vh[8], vl[8];
+        tcLd8(taddr + (uint32_t)c0, vh);          // codes x hi
+        tcLd8(taddr + (uint32_t)(TC_N + c0), vl); // codes x lo
         tcWaitLd();
-        if (row_ok && sc != 0.0f) {
+        if (live) {
           if (sigma > 0.0f) {
             // noisy regime: the Gaussian decides the ADC code, so the divisions of the exact
             // chain are replaced by multiplications with the reciprocal step
 #pragma unroll
-            for (int g = 0; g < 4; g++) {
+            for (int g = 0; g < 2; g++) {
               const int cl = cbase + c0 + 4 * g; // column inside this 128-column chunk
               if (cl < ch.w) {
                 float z[4];
                 gauss4(p.key, (uint64_t)row * n4 + (uint64_t)((ch.y + cl) >> 2), p.call, tile_tag, z);
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                  float y = fmaf(__uint_as_float(v[4 * g + j]), io.res_in, sigma * z[j]);
+                  const float acc = __uint_as_float(vh[4 * g + j]) + __uint_as_float(vl[4 * g + j]);
+                  float y = fmaf(acc, io.res_in, sigma * z[j]);
                   if (adc) {
                     y = (fmaf(y, inv_res_out, kMagic) - kMagic) * io.res_out;
                   }
@@ -362,13 +437,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
           } else {
 #pragma unroll
-            for (int g = 0; g < 4; g++) {
+            for (int g = 0; g < 2; g++) {
               const int cl = cbase + c0 + 4 * g;
               if (cl < ch.w) {
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                  // the MMA summed integer codes; one multiply by the DAC step gives sum(v * w)
-                  float y = __fmul_rn(__uint_as_float(v[4 * g + j]), io.res_in);
+                  // the MMA summed integer codes times weights; one multiply by the DAC step
+                  // gives sum(v * w)
+                  const float acc = __fadd_rn(__uint_as_float(vh[4 * g + j]), __uint_as_float(vl[4 * g + j]));
+                  float y = __fmul_rn(acc, io.res_in);
                   y = finalizeOutput(io, y, 0.0f, 0.0f, exceeded);
                   sum[c0 + 4 * g + j] += y * fac;
                 }
@@ -387,23 +464,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       if (exceeded && io.bm != AB200_BM_NONE && p.flags != nullptr) {
         atomicOr(&p.flags[row], 1);
       }
-      float *orow = p.out + (long long)row * p.out_ss + ch.z + cbase;
-      const bool vec = ((p.out_ss & 3) == 0) && ((ch.z & 3) == 0) &&
-                       ((((uintptr_t)p.out) & 15) == 0) && !p.accumulate;
 #pragma unroll
       for (int c = 0; c < TC_EPI_COLS; c += 4) {
-        if (vec && cbase + c + 3 < ch.w) {
+        const int cl = cbase + c;
+        if (vec && cl + 3 < ch.w) {
           *reinterpret_cast<float4 *>(orow + c) =
               make_float4(sum[c], sum[c + 1], sum[c + 2], sum[c + 3]);
         } else {
 #pragma unroll
           for (int j = 0; j < 4; j++) {
-            if (cbase + c + j < ch.w) {
-              orow[c + j] = p.accumulate ? orow[c + j] + sum[c + j] : sum[c + j];
+            if (cl + j < ch.w) {
+              float *o = orow + c + j;
+              *o = p.accumulate ? *o + sum[c + j] : sum[c + j];
             }
           }
         }
       }
+    }
+    }
+    if (p.prof && threadIdx.x == 0) {
+      p.prof[blockIdx.x * 8 + 6] = w_tfull;
+      p.prof[blockIdx.x * 8 + 7] = clock64() - t_epi;
     }
   }
 
@@ -420,7 +501,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   __syncthreads();
   if (warp == TC_WARP_MMA) {
     tcFenceAfter();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
                  : "memory");
   }
 }
@@ -765,7 +846,17 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   p.backward = r.backward ? 1 : 0;
   p.io = r.io;
   p.status = status_dev_;
-  dim3 grid(n_chunks_, (r.m + TC_M - 1) / TC_M);
+  static const bool prof_on = getenv("AB200_TC_PROFILE") != nullptr;
+  long long *prof_dev = nullptr;
+  if (prof_on) {
+    AB200_CUDA(cudaMalloc(&prof_dev, 148 * 8 * sizeof(long long) * 2));
+    AB200_CUDA(cudaMemsetAsync(prof_dev, 0, 148 * 8 * sizeof(long long) * 2, s));
+  }
+  p.prof = prof_dev;
+  const int n_items = n_chunks_ * ((r.m + TC_M - 1) / TC_M);
+  int n_sm = 0;
+  AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device_));
+  dim3 grid(n_items < n_sm ? n_items : n_sm); // one persistent CTA per SM
   if (r.io.bm != AB200_BM_NONE) {
     AB200_CUDA(cudaFuncSetAttribute(mvmTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     TC_SMEM_BYTES));
@@ -776,6 +867,24 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
     mvmTcKernel<false><<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
   }
   AB200_LAUNCH_CHECK();
+  if (prof_on) {
+    // diagnostics only: average wait cycles per role over the CTAs (synchronises)
+    const int n = (int)grid.x < 296 ? (int)grid.x : 296;
+    std::vector<long long> h((size_t)n * 8);
+    AB200_CUDA(cudaStreamSynchronize(s));
+    AB200_CUDA(cudaMemcpy(h.data(), prof_dev, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+    cudaFree(prof_dev);
+    double avg[8] = {0};
+    for (int c = 0; c < n; c++) {
+      for (int k = 0; k < 8; k++) {
+        avg[k] += (double)h[(size_t)c * 8 + k] / n;
+      }
+    }
+    fprintf(stderr,
+            "[ab200 tc] cycles/CTA: mma total %.0f (wait operands %.0f, accumulator %.0f) | "
+            "tma wait stage %.0f | epilogue total %.0f (wait accumulator %.0f)\n",
+            avg[3], avg[0], avg[2], avg[4], avg[7], avg[6]);
+  }
 }
 
 } // namespace ab200
