@@ -1,5 +1,6 @@
 #include "array.h"
 
+#include <algorithm>
 #include <cstring>
 
 namespace ab200 {
@@ -64,8 +65,21 @@ TileArray::TileArray(const ab200_tile_config &cfg, int out_size, int in_size, in
 }
 
 TileArray::~TileArray() {
-  cudaFree(stage_dev_);
-  cudaFreeHost(stage_pinned_);
+  for (int b = 0; b < 2; b++) {
+    cudaFree(xd_[b]);
+    cudaFree(yd_[b]);
+    cudaFreeHost(xh_[b]);
+    cudaFreeHost(yh_[b]);
+    if (ev_h2d_[b]) {
+      cudaEventDestroy(ev_h2d_[b]);
+      cudaEventDestroy(ev_comp_[b]);
+      cudaEventDestroy(ev_d2h_[b]);
+    }
+  }
+  if (s_h2d_) {
+    cudaStreamDestroy(s_h2d_);
+    cudaStreamDestroy(s_d2h_);
+  }
 }
 
 void TileArray::setSeed(uint64_t seed) {
@@ -182,24 +196,101 @@ void TileArray::forwardTc(const float *x, float *y, int m, cudaStream_t s) {
   tc_->run(r, s);
 }
 
+void TileArray::ensureHostPipeline() {
+  if (host_ready_) {
+    return;
+  }
+  const size_t nx = (size_t)kHostChunkRows * in_size_, ny = (size_t)kHostChunkRows * out_size_;
+  for (int b = 0; b < 2; b++) {
+    AB200_CUDA(cudaMalloc(&xd_[b], nx * sizeof(float)));
+    AB200_CUDA(cudaMalloc(&yd_[b], ny * sizeof(float)));
+    AB200_CUDA(cudaMallocHost(&xh_[b], nx * sizeof(float)));
+    AB200_CUDA(cudaMallocHost(&yh_[b], ny * sizeof(float)));
+    AB200_CUDA(cudaEventCreateWithFlags(&ev_h2d_[b], cudaEventDisableTiming));
+    AB200_CUDA(cudaEventCreateWithFlags(&ev_comp_[b], cudaEventDisableTiming));
+    AB200_CUDA(cudaEventCreateWithFlags(&ev_d2h_[b], cudaEventDisableTiming));
+  }
+  AB200_CUDA(cudaStreamCreateWithFlags(&s_h2d_, cudaStreamNonBlocking));
+  AB200_CUDA(cudaStreamCreateWithFlags(&s_d2h_, cudaStreamNonBlocking));
+  host_ready_ = true;
+}
+
+static bool isPinnedHost(const void *p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeHost;
+}
+
+// Host-buffer forward. Copies and kernels of different row chunks overlap: while chunk c is in the
+// kernels, chunk c + 1 is on its way to the device and chunk c - 1 on its way back, so the call
+// costs about max(copy in, compute, copy out) instead of their sum. Page-locked caller buffers
+// (cudaHostRegister / torch pin_memory) are copied directly; pageable ones go through the
+// library's own pinned staging buffers.
 void TileArray::forwardHost(const float *x, float *y, int m, bool is_test, cudaStream_t s) {
   AB200_CUDA(cudaSetDevice(device_));
-  const size_t nx = (size_t)m * in_size_, ny = (size_t)m * out_size_;
-  if (nx + ny > stage_floats_) {
-    AB200_CUDA(cudaDeviceSynchronize());
-    cudaFree(stage_dev_);
-    cudaFreeHost(stage_pinned_);
-    AB200_CUDA(cudaMalloc(&stage_dev_, (nx + ny) * sizeof(float)));
-    AB200_CUDA(cudaMallocHost(&stage_pinned_, (nx + ny) * sizeof(float)));
-    stage_floats_ = nx + ny;
+  if (m <= 0) {
+    return;
   }
-  std::memcpy(stage_pinned_, x, nx * sizeof(float));
-  AB200_CUDA(cudaMemcpyAsync(stage_dev_, stage_pinned_, nx * sizeof(float), cudaMemcpyHostToDevice, s));
-  forward(stage_dev_, stage_dev_ + nx, m, is_test, s);
-  AB200_CUDA(cudaMemcpyAsync(stage_pinned_ + nx, stage_dev_ + nx, ny * sizeof(float),
-                             cudaMemcpyDeviceToHost, s));
+  ensureHostPipeline();
+  const bool x_pinned = isPinnedHost(x), y_pinned = isPinnedHost(y);
+  const int R = kHostChunkRows;
+  const int n_chunks = (m + R - 1) / R;
+  // the caller's stream may have earlier work that produced x or must precede our kernels
+  for (int c = 0; c < n_chunks; c++) {
+    const int b = c & 1;
+    const int rows = std::min(R, m - c * R);
+    const size_t nx = (size_t)rows * in_size_, ny = (size_t)rows * out_size_;
+    const float *xc = x + (size_t)c * R * in_size_;
+    float *yc = y + (size_t)c * R * out_size_;
+    // input buffer b is free once the kernels of chunk c - 2 are done
+    if (c >= 2) {
+      AB200_CUDA(cudaStreamWaitEvent(s_h2d_, ev_comp_[b], 0));
+    }
+    if (x_pinned) {
+      AB200_CUDA(cudaMemcpyAsync(xd_[b], xc, nx * sizeof(float), cudaMemcpyHostToDevice, s_h2d_));
+    } else {
+      if (c >= 2) {
+        AB200_CUDA(cudaEventSynchronize(ev_h2d_[b])); // staging buffer b has left the host
+      }
+      std::memcpy(xh_[b], xc, nx * sizeof(float));
+      AB200_CUDA(cudaMemcpyAsync(xd_[b], xh_[b], nx * sizeof(float), cudaMemcpyHostToDevice, s_h2d_));
+    }
+    AB200_CUDA(cudaEventRecord(ev_h2d_[b], s_h2d_));
+    // kernels: need the input, and output buffer b drained (copy-out of chunk c - 2)
+    AB200_CUDA(cudaStreamWaitEvent(s, ev_h2d_[b], 0));
+    if (c >= 2) {
+      AB200_CUDA(cudaStreamWaitEvent(s, ev_d2h_[b], 0));
+    }
+    forward(xd_[b], yd_[b], rows, is_test, s);
+    AB200_CUDA(cudaEventRecord(ev_comp_[b], s));
+    // copy-out
+    AB200_CUDA(cudaStreamWaitEvent(s_d2h_, ev_comp_[b], 0));
+    if (y_pinned) {
+      AB200_CUDA(cudaMemcpyAsync(yc, yd_[b], ny * sizeof(float), cudaMemcpyDeviceToHost, s_d2h_));
+      AB200_CUDA(cudaEventRecord(ev_d2h_[b], s_d2h_));
+    } else {
+      if (c >= 2) {
+        // the previous use of staging buffer b must reach the caller's memory first
+        AB200_CUDA(cudaEventSynchronize(ev_d2h_[b]));
+        const int pc = c - 2;
+        const int prows = std::min(R, m - pc * R);
+        std::memcpy(y + (size_t)pc * R * out_size_, yh_[b], (size_t)prows * out_size_ * sizeof(float));
+      }
+      AB200_CUDA(cudaMemcpyAsync(yh_[b], yd_[b], ny * sizeof(float), cudaMemcpyDeviceToHost, s_d2h_));
+      AB200_CUDA(cudaEventRecord(ev_d2h_[b], s_d2h_));
+    }
+  }
+  AB200_CUDA(cudaStreamSynchronize(s_d2h_));
   AB200_CUDA(cudaStreamSynchronize(s));
-  std::memcpy(y, stage_pinned_ + nx, ny * sizeof(float));
+  if (!y_pinned) {
+    for (int pc = std::max(0, n_chunks - 2); pc < n_chunks; pc++) {
+      const int prows = std::min(R, m - pc * R);
+      std::memcpy(y + (size_t)pc * R * out_size_, yh_[pc & 1], (size_t)prows * out_size_ * sizeof(float));
+    }
+  }
 }
 
 } // namespace ab200

@@ -37,8 +37,16 @@ private:
   std::vector<uint64_t> tc_versions_;
   bool tcEligible(int m);
   void forwardTc(const float *x, float *y, int m, cudaStream_t s);
-  float *stage_dev_ = nullptr, *stage_pinned_ = nullptr;
-  size_t stage_floats_ = 0;
+  // host-buffer path: the batch is cut into row chunks that flow through a three-stage pipeline
+  // (host -> device copy, kernels, device -> host copy) on three streams with two buffers each
+  static constexpr int kHostChunkRows = 1024;
+  float *xd_[2] = {nullptr, nullptr}, *yd_[2] = {nullptr, nullptr};
+  float *xh_[2] = {nullptr, nullptr}, *yh_[2] = {nullptr, nullptr}; // pinned staging (pageable callers)
+  cudaStream_t s_h2d_ = nullptr, s_d2h_ = nullptr;
+  cudaEvent_t ev_h2d_[2] = {nullptr, nullptr}, ev_comp_[2] = {nullptr, nullptr},
+              ev_d2h_[2] = {nullptr, nullptr};
+  bool host_ready_ = false;
+  void ensureHostPipeline();
 };
 
 } // namespace ab200

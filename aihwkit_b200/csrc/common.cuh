@@ -113,13 +113,42 @@ __device__ __forceinline__ void boxMuller(uint32_t a, uint32_t b, float &z0, flo
   z1 = r * __sinf(ang);
 }
 
-// four standard normals for noise block `blk` of call `call`
+// Two standard normals from ONE 32-bit word: 20 bits for the radius (u1 in [2^-20, 1], radius up
+// to 5.26) and 12 bits for the angle. Used for the MVM output noise, where one Gaussian is drawn
+// per output element and in-split and the generator is the largest cost of the epilogue.
+__device__ __forceinline__ void boxMuller1(uint32_t a, float &z0, float &z1) {
+  float u1 = 2.0f - __uint_as_float(0x3f800000u | ((a >> 12) << 3));
+  float u2 = __uint_as_float(0x3f800000u | ((a & 0xFFFu) << 11)) - 1.0f;
+  float r2 = -1.3862943611198906f * __log2f(u1); // -2 ln(u1)
+  float r;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(r2));
+  float ang = 6.283185307179586f * u2;
+  z0 = r * __cosf(ang);
+  z1 = r * __sinf(ang);
+}
+
+// four standard normals for noise block `blk` of call `call`; a block covers four consecutive
+// output columns of one row and uses words 0 and 1 (even blocks) or 2 and 3 (odd blocks) of the
+// Philox output of block pair blk / 2
 __device__ __forceinline__ void
 gauss4(PhiloxKey key, uint64_t blk, uint32_t call, uint32_t tag, float z[4]) {
   uint32_t r[4];
-  philox4x32<7>((uint32_t)blk, (uint32_t)(blk >> 32), call, tag, key, r);
-  boxMuller(r[0], r[1], z[0], z[1]);
-  boxMuller(r[2], r[3], z[2], z[3]);
+  const uint64_t pair = blk >> 1;
+  philox4x32<7>((uint32_t)pair, (uint32_t)(pair >> 32), call, tag, key, r);
+  const bool odd = (blk & 1) != 0;
+  boxMuller1(odd ? r[2] : r[0], z[0], z[1]);
+  boxMuller1(odd ? r[3] : r[1], z[2], z[3]);
+}
+
+// eight standard normals for the block pair `pair` (blocks 2 * pair and 2 * pair + 1 of gauss4)
+__device__ __forceinline__ void
+gauss8(PhiloxKey key, uint64_t pair, uint32_t call, uint32_t tag, float z[8]) {
+  uint32_t r[4];
+  philox4x32<7>((uint32_t)pair, (uint32_t)(pair >> 32), call, tag, key, r);
+  boxMuller1(r[0], z[0], z[1]);
+  boxMuller1(r[1], z[2], z[3]);
+  boxMuller1(r[2], z[4], z[5]);
+  boxMuller1(r[3], z[6], z[7]);
 }
 
 // getDiscretizedValueSR<false> (src/rpucuda/utility_functions.h:204-210): rint(v / res) * res with

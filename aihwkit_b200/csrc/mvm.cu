@@ -169,7 +169,8 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
     __syncthreads();
   }
 
-  const uint64_t n4 = (uint64_t)((N + 3) >> 2);
+  // noise blocks of four columns, an even number per row (two blocks share one Philox call)
+  const uint64_t n4 = (uint64_t)(((N + 7) >> 3) << 1);
   const uint32_t tag = (p.backward ? TAG_BWD_OUT : TAG_FWD_OUT) + p.noise_id;
 #pragma unroll
   for (int i = 0; i < 4; i++) {
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
   __shared__ float red_sh[8];
   const IOEff &io = p.io;
   const int K = p.in_size, N = p.out_size;
-  const uint64_t n4 = (uint64_t)((N + 3) >> 2);
+  const uint64_t n4 = (uint64_t)(((N + 7) >> 3) << 1);
   for (int r = blockIdx.x; r < p.m; r += gridDim.x) {
     if (p.flags[r] == 0) {
       continue;

@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const int4 ch = p.chunk[w % p.n_chunks];
     const int row = (w / p.n_chunks) * TC_M + q * 32 + lane;
     const bool row_ok = row < p.m;
-    const uint64_t n4 = (uint64_t)((p.outn[ch.x] + 3) >> 2);
+    const uint64_t n4h = (uint64_t)((p.outn[ch.x] + 7) >> 3); // noise block pairs per row
     const bool vec = ((p.out_ss & 3) == 0) && ((ch.z & 3) == 0) &&
                      ((((uintptr_t)p.out) & 15) == 0) && !p.accumulate;
     float *orow = p.out + (long long)row * p.out_ss + ch.z + cbase;
@@ -413,16 +413,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           if (sigma > 0.0f) {
             // noisy regime: the Gaussian decides the ADC code, so the divisions of the exact
             // chain are replaced by multiplications with the reciprocal step
+            float z[8];
+            if (cbase + c0 < ch.w) {
+              gauss8(p.key, (uint64_t)row * n4h + (uint64_t)((ch.y + cbase + c0) >> 3), p.call,
+                     tile_tag, z);
+            }
 #pragma unroll
             for (int g = 0; g < 2; g++) {
               const int cl = cbase + c0 + 4 * g; // column inside this 128-column chunk
               if (cl < ch.w) {
-                float z[4];
-                gauss4(p.key, (uint64_t)row * n4 + (uint64_t)((ch.y + cl) >> 2), p.call, tile_tag, z);
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                   const float acc = __uint_as_float(vh[4 * g + j]) + __uint_as_float(vl[4 * g + j]);
-                  float y = fmaf(acc, io.res_in, sigma * z[j]);
+                  float y = fmaf(acc, io.res_in, sigma * z[4 * g + j]);
                   if (adc) {
                     y = (fmaf(y, inv_res_out, kMagic) - kMagic) * io.res_out;
                   }

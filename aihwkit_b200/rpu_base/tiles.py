@@ -367,12 +367,22 @@ class TileArray:
         check(self._lib.ab200_array_get_weights(self._h, w.data_ptr()))
         return w
 
-    def forward(self, x_input: torch.Tensor, is_test: bool = True, non_blocking: bool = False) -> torch.Tensor:
+    def forward(self, x_input: torch.Tensor, is_test: bool = True, non_blocking: bool = False,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``x_input`` on the GPU: kernels only.  ``x_input`` on the CPU: the library pipelines
+        host->device copies, kernels and device->host copies over row chunks; page-locked
+        tensors (``pin_memory()``) are copied directly, and ``out`` lets the caller provide a
+        page-locked result tensor."""
         x = _check_input(x_input, "x_input")
         if x.size(-1) != self.in_size:
             raise RuntimeError(f"Invalid x_input dimensions: expected [{self.in_size},*] tensor")
         m = x.numel() // self.in_size
-        out = torch.empty(list(x.shape[:-1]) + [self.out_size], dtype=torch.float32, device=x.device)
+        shape = list(x.shape[:-1]) + [self.out_size]
+        if out is None:
+            out = torch.empty(shape, dtype=torch.float32, device=x.device)
+        elif (list(out.shape) != shape or out.dtype != torch.float32 or out.device != x.device
+              or not out.is_contiguous()):
+            raise RuntimeError("out must be a contiguous float32 tensor of the result shape on x's device")
         if x.is_cuda:
             check(self._lib.ab200_array_forward(self._h, x.data_ptr(), out.data_ptr(), m, int(is_test), _stream_ptr(x)))
             if not non_blocking:
