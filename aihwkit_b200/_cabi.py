@@ -176,6 +176,8 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_array_get_weights": (_I, [_VP, _FP]),
         "ab200_array_forward": (_I, [_VP, _FP, _FP, _I, _I, _VP]),
         "ab200_array_forward_host": (_I, [_VP, _FP, _FP, _I, _I, _VP]),
+        "ab200_array_forward_local": (_I, [_VP, _FP, _FP, _I, _I, _VP]),
+        "ab200_array_local_in_size": (_I, [_VP]),
         "ab200_array_set_seed": (_I, [_VP, C.c_uint64]),
         "ab200_mvm_forward_noalloc": (
             _I, [C.POINTER(IOParams), _FP, _I, _I, _FP, _FP, _I, C.c_uint64, C.c_uint32, _VP]

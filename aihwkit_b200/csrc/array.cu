@@ -123,8 +123,25 @@ void TileArray::getWeights(float *w_host) {
 
 // TileModuleArray.forward (array.py:155-182): per-tile analog MVM, sum over in-splits after each
 // tile's ADC, concatenation over out-splits.
+int TileArray::localInSize() const {
+  int n = 0;
+  for (int ii = in_begin_; ii < in_end_; ii++) {
+    n += in_sizes_[ii];
+  }
+  return n;
+}
+
 void TileArray::forward(const float *x, float *y, int m, bool is_test, cudaStream_t s) {
   (void)is_test;
+  forwardImpl(in_begin_ < in_end_ ? x + in_off_[in_begin_] : x, in_size_, y, m, s);
+}
+
+void TileArray::forwardLocal(const float *x_local, float *y, int m, bool is_test, cudaStream_t s) {
+  (void)is_test;
+  forwardImpl(x_local, localInSize(), y, m, s);
+}
+
+void TileArray::forwardImpl(const float *x0, long long x_ss, float *y, int m, cudaStream_t s) {
   if (m <= 0) {
     return;
   }
@@ -133,13 +150,14 @@ void TileArray::forward(const float *x, float *y, int m, bool is_test, cudaStrea
     return;
   }
   if (tcEligible(m)) {
-    forwardTc(x, y, m, s);
+    forwardTc(x0, x_ss, y, m, s);
     return;
   }
   for (int ii = in_begin_; ii < in_end_; ii++) {
     for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
       tile(ii - in_begin_, oi)
-          .forwardStrided(x + in_off_[ii], in_size_, y + out_off_[oi], out_size_, m,
+          .forwardStrided(x0 + (in_off_[ii] - in_off_[in_begin_]), x_ss, y + out_off_[oi],
+                          out_size_, m,
                           /*accumulate=*/ii != in_begin_,
                           (uint32_t)(ii * (int)out_sizes_.size() + oi), s);
     }
@@ -160,7 +178,7 @@ bool TileArray::tcEligible(int m) {
 
 // All local tiles in one launch: the DAC kernel quantises every (row, in-split) once, the MMA
 // kernel walks the in-splits per 128 x 128 output block and sums them after each tile's ADC.
-void TileArray::forwardTc(const float *x, float *y, int m, cudaStream_t s) {
+void TileArray::forwardTc(const float *x0, long long x_ss, float *y, int m, cudaStream_t s) {
   const int n_in = in_end_ - in_begin_, n_out = (int)out_sizes_.size();
   if (!tc_) {
     tc_.reset(new TcEngine(device_));
@@ -187,8 +205,8 @@ void TileArray::forwardTc(const float *x, float *y, int m, cudaStream_t s) {
       }
     }
   }
-  r.in = x + in_off_[in_begin_];
-  r.in_ss = in_size_;
+  r.in = x0;
+  r.in_ss = x_ss;
   r.m = m;
   r.out = y;
   r.out_ss = out_size_;

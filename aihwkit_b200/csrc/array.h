@@ -22,6 +22,9 @@ public:
   void setWeights(const float *w_host);
   void getWeights(float *w_host);
   void forward(const float *x, float *y, int m, bool is_test, cudaStream_t s);
+  // input that holds only the locally owned columns: [m][localInSize()]
+  void forwardLocal(const float *x_local, float *y, int m, bool is_test, cudaStream_t s);
+  int localInSize() const;
   void forwardHost(const float *x, float *y, int m, bool is_test, cudaStream_t s);
   void setSeed(uint64_t seed);
 
@@ -36,7 +39,9 @@ private:
   std::unique_ptr<TcEngine> tc_;
   std::vector<uint64_t> tc_versions_;
   bool tcEligible(int m);
-  void forwardTc(const float *x, float *y, int m, cudaStream_t s);
+  // x0 points at the first locally owned column of row 0, x_ss is the row pitch
+  void forwardImpl(const float *x0, long long x_ss, float *y, int m, cudaStream_t s);
+  void forwardTc(const float *x0, long long x_ss, float *y, int m, cudaStream_t s);
   // host-buffer path: the batch is cut into row chunks that flow through a three-stage pipeline
   // (host -> device copy, kernels, device -> host copy) on three streams with two buffers each
   static constexpr int kHostChunkRows = 1024;

@@ -314,6 +314,16 @@ int ab200_array_forward(ab200_array *arr, const float *x_dev, float *y_dev, int 
   A(arr)->forward(x_dev, y_dev, m_batch, is_test != 0, (cudaStream_t)stream);
   AB200_CATCH
 }
+int ab200_array_forward_local(ab200_array *arr, const float *x_local_dev, float *y_dev,
+                              int m_batch, int is_test, void *stream) {
+  AB200_TRY
+  checkBatch(m_batch);
+  A(arr)->forwardLocal(x_local_dev, y_dev, m_batch, is_test != 0, (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_array_local_in_size(const ab200_array *arr) {
+  return arr ? reinterpret_cast<const TileArray *>(arr)->localInSize() : -1;
+}
 int ab200_array_forward_host(ab200_array *arr, const float *x_host, float *y_host, int m_batch,
                              int is_test, void *stream) {
   AB200_TRY

@@ -367,6 +367,24 @@ class TileArray:
         check(self._lib.ab200_array_get_weights(self._h, w.data_ptr()))
         return w
 
+    @property
+    def local_in_size(self) -> int:
+        """Number of input columns covered by the in-splits this object owns."""
+        return int(self._lib.ab200_array_local_in_size(self._h))
+
+    def forward_local(self, x_local: torch.Tensor, out: Optional[torch.Tensor] = None,
+                      is_test: bool = True) -> torch.Tensor:
+        """Forward on a CUDA input that holds only this object's own input columns
+        ``[m, local_in_size]``; asynchronous on the current stream."""
+        x = _check_input(x_local, "x_local")
+        if not x.is_cuda or x.dim() != 2 or x.size(1) != self.local_in_size:
+            raise RuntimeError(f"expected a CUDA [m, {self.local_in_size}] tensor")
+        if out is None:
+            out = torch.empty(x.size(0), self.out_size, dtype=torch.float32, device=x.device)
+        check(self._lib.ab200_array_forward_local(self._h, x.data_ptr(), out.data_ptr(), x.size(0),
+                                                  int(is_test), _stream_ptr(x)))
+        return out
+
     def forward(self, x_input: torch.Tensor, is_test: bool = True, non_blocking: bool = False,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``x_input`` on the GPU: kernels only.  ``x_input`` on the CPU: the library pipelines

@@ -79,3 +79,46 @@ class ShardedTileArray:
 
     def forward(self, x: torch.Tensor, dst: Optional[int] = 0, **kw) -> torch.Tensor:
         return self.reduce(self.forward_partial(x, **kw), dst)
+
+    def forward_host(self, x_local_host: torch.Tensor, out_host: Optional[torch.Tensor] = None,
+                     dst: int = 0, chunk_rows: int = 1024) -> Optional[torch.Tensor]:
+        """End-to-end forward from host memory on every rank.
+
+        ``x_local_host`` is this rank's own input columns ``[m, local_in_size]`` in page-locked
+        host memory (inputs are scattered over the ranks, not broadcast).  Row chunks are copied
+        to the device on a side stream while earlier chunks are in the kernels; the partial
+        outputs are summed to ``dst`` with one collective and copied to ``out_host`` there.
+        With a single rank the library's own pipelined host entry point does all of it."""
+        if self.world == 1:
+            return self.local.forward(x_local_host, out=out_host)
+        dev = self.local.device
+        m = x_local_host.size(0)
+        if not hasattr(self, "_copy_stream"):
+            self._copy_stream = torch.cuda.Stream(device=dev)
+            self._stage = None
+        if self._stage is None or self._stage[0].size(0) < chunk_rows or self._partial.size(0) != m:
+            self._stage = [torch.empty(chunk_rows, max(self.local.local_in_size, 1), device=dev)
+                           for _ in range(2)]
+            self._partial = torch.empty(m, self.out_size, device=dev)
+            self._events = [[torch.cuda.Event(), torch.cuda.Event()] for _ in range(2)]
+        main = torch.cuda.current_stream(dev)
+        if self.local.local_in_size == 0:
+            self._partial.zero_()
+        else:
+            for c, r0 in enumerate(range(0, m, chunk_rows)):
+                b = c & 1
+                rows = min(chunk_rows, m - r0)
+                h2d_done, comp_done = self._events[b]
+                with torch.cuda.stream(self._copy_stream):
+                    if c >= 2:
+                        self._copy_stream.wait_event(comp_done)  # staging buffer b is free again
+                    self._stage[b][:rows].copy_(x_local_host[r0 : r0 + rows], non_blocking=True)
+                    h2d_done.record(self._copy_stream)
+                main.wait_event(h2d_done)
+                self.local.forward_local(self._stage[b][:rows], out=self._partial[r0 : r0 + rows])
+                comp_done.record(main)
+        self.reduce(self._partial, dst)
+        if self.rank == dst and out_host is not None:
+            out_host.copy_(self._partial, non_blocking=True)
+            return out_host
+        return None

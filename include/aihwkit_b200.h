@@ -299,6 +299,12 @@ int ab200_array_forward(ab200_array *arr, const float *x_dev, float *y_dev, int 
                         int is_test, void *stream);
 int ab200_array_forward_host(ab200_array *arr, const float *x_host, float *y_host, int m_batch,
                              int is_test, void *stream);
+/* Same as ab200_array_forward for a rank of a sharded layer whose input holds only the columns
+ * of its own in-splits: x_local_dev is [m_batch][ab200_array_local_in_size()] (the reference
+ * passes each in-split its slice of the input, array.py:165-167). */
+int ab200_array_forward_local(ab200_array *arr, const float *x_local_dev, float *y_dev,
+                              int m_batch, int is_test, void *stream);
+int ab200_array_local_in_size(const ab200_array *arr);
 int ab200_array_set_seed(ab200_array *arr, uint64_t seed);
 
 /* ---- forward pass without any allocation ------------------------------------------------- */

@@ -209,3 +209,33 @@ def test_mapped_forward_host_pipeline(pinned):
     assert close(y, y_dev)
     # twice in a row: buffers and events are reused
     assert close(arr.forward(x), y_dev)
+
+
+def test_mapped_forward_local_input_equals_full_width_input():
+    """A shard fed only its own input columns gives the same partial sum as the same shard fed
+    the full-width input (same noise: keys depend on global tile coordinates)."""
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+    from aihwkit_b200.sharded import column_range
+
+    rng = np.random.default_rng(21)
+    out_size, in_size, max_tile, m = 256, 1000, 256, 150
+    cfg = H.inference_params(noise=True)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=31)
+    W = torch.from_numpy(rng.normal(0, 0.05, (out_size, in_size)).astype(np.float32))
+    X = torch.from_numpy(rng.normal(0, 1, (m, in_size)).astype(np.float32)).cuda()
+    for rank in range(2):
+        c0, c1 = column_range(in_size, max_tile, rank, 2)
+        from aihwkit_b200.sharded import in_split_range
+
+        b, e = in_split_range(4, rank, 2)
+        outs = []
+        for local in (False, True):
+            a = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0,
+                            in_split_range=(b, e))
+            a.set_weights(W)
+            assert a.local_in_size == c1 - c0
+            if local:
+                outs.append(a.forward_local(X[:, c0:c1].contiguous()))
+            else:
+                outs.append(a.forward(X))
+            torch.cuda.synchronize()
+        assert torch.equal(outs[0], outs[1])
