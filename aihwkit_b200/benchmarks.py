@@ -1,0 +1,181 @@
+"""Training-step timings of the analog tile on one GPU: forward + backward + pulsed update.
+
+    python -m aihwkit_b200.benchmarks --config 0|2|3 [--steps K] [--warmup W] [--cpu-baseline]
+
+Configurations (seeded synthetic inputs with the stated shapes and distributions):
+  0  single tile 256 x 256, batch 64, ConstantStep device, 7-bit DAC / 9-bit ADC, out_noise 0.06,
+     ABS_MAX noise management, ITERATIVE bound management, StochasticCompressed BL 31, UM + UBLM
+  2  Tiki-Taka: 1024 x 1024 TransferCompound of two SoftBoundsReference devices, batch 256,
+     transfer every 2 batches, one column per transfer
+  3  convolution-shaped tile 256 x 2304 (3x3x256), 131072 input columns per step, SoftBounds device
+     (the activations are fed as an already unfolded [columns, 2304] matrix)
+
+Prints one JSON line: columns/s for the whole step and per phase, and for the update kernel the
+achieved HBM bandwidth on its algorithmic bytes `x*d*(8+P) + 4*m*(x+d)` against the measured copy
+bandwidth (P = per-element parameter bytes: 16 ConstantStep, 24 SoftBounds / SoftBoundsReference).
+For large batches the update is bound by the coincidence arithmetic (x*d*m AND+popc), not by HBM;
+the line then also reports coincidence pairs per second.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path, "r", encoding="utf-8") as f:
+            p = json.load(f)
+        return p["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+def build(config: int):
+    from .rpu_base import devices as D
+
+    p = D.AnalogTileParameter()
+    for io in (p.forward_io, p.backward_io):
+        io.inp_res, io.out_res = 1.0 / 126.0, 1.0 / 510.0
+        io.out_noise, io.out_bound, io.inp_bound = 0.06, 12.0, 1.0
+        io.noise_management = D.NoiseManagementType.AbsMax
+    p.forward_io.bound_management = D.BoundManagementType.Iterative
+    p.update.pulse_type = D.PulseType.StochasticCompressed
+    p.update.desired_bl = 31
+    if config == 0:
+        dp = D.ConstantStepResistiveDeviceParameter()
+        dp.dw_min, dp.dw_min_dtod, dp.dw_min_std = 0.001, 0.3, 0.3
+        dp.up_down, dp.up_down_dtod, dp.w_max, dp.w_min = 0.0, 0.01, 0.6, -0.6
+        dp.enforce_consistency = True
+        dp.construction_seed = 1
+        return p, dp, dict(x=256, d=256, m=64, lr=0.01, par_bytes=16, xdist="uniform", dstd=0.1,
+                           winit="uniform")
+    if config == 2:
+        dp = D.TransferResistiveDeviceParameter()
+        for _ in range(2):
+            u = D.SoftBoundsReferenceResistiveDeviceParameter()
+            u.dw_min, u.w_max, u.w_min, u.reference_std = 0.002, 1.0, -1.0, 0.05
+            u.enforce_consistency = True
+            dp.append_parameter(u)
+        dp.construction_seed = 2
+        dp.gamma, dp.transfer_every, dp.units_in_mbatch = 0.0, 2.0, True
+        dp.n_reads_per_transfer, dp.transfer_lr, dp.fast_lr = 1, 0.01, 1.0
+        dp.transfer_forward.bound_management = D.BoundManagementType.Iterative
+        return p, dp, dict(x=1024, d=1024, m=256, lr=0.01, par_bytes=24, xdist="uniform",
+                           dstd=0.05, winit="zero")
+    if config == 3:
+        dp = D.SoftBoundsResistiveDeviceParameter()
+        dp.dw_min, dp.w_max, dp.w_min, dp.dw_min_dtod = 0.001, 0.6, -0.6, 0.3
+        dp.enforce_consistency = True
+        dp.construction_seed = 3
+        return p, dp, dict(x=2304, d=256, m=131072, lr=0.01, par_bytes=24, xdist="relu",
+                           dstd=0.01, winit="uniform")
+    raise SystemExit("config must be 0, 2 or 3")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", type=int, default=0)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=0, help="override the batch size")
+    ap.add_argument("--cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    import torch
+
+    from .rpu_base import tiles as T
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("needs a CUDA device: the analog tile has no CPU path")
+    p, dp, w = build(args.config)
+    x_size, d_size = w["x"], w["d"]
+    m = args.batch or w["m"]
+    cfg = p._config(x_size, d_size, dp, seed=100 + args.config)
+    tile = T.AnalogTile(cfg, cuda_device=0)
+    g = torch.Generator().manual_seed(args.config)
+    if w["winit"] == "uniform":
+        tile.set_weights(torch.rand(d_size, x_size, generator=g) - 0.5)
+    tile.set_learning_rate(w["lr"])
+    if w["xdist"] == "uniform":
+        x = torch.rand(m, x_size, generator=g) * 2 - 1
+    else:
+        x = torch.relu(torch.randn(m, x_size, generator=g))
+    d = torch.randn(m, d_size, generator=g) * w["dstd"]
+    x, d = x.cuda(), d.cuda()
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    for _ in range(args.warmup):
+        tile.forward(x, non_blocking=True)
+        tile.backward(d, non_blocking=True)
+        tile.update(x, d, non_blocking=True)
+    torch.cuda.synchronize()
+    t_f = t_b = t_u = 0.0
+    e = [ev() for _ in range(4)]
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e[0].record()
+        tile.forward(x, non_blocking=True)
+        e[1].record()
+        tile.backward(d, non_blocking=True)
+        e[2].record()
+        tile.update(x, d, non_blocking=True)
+        e[3].record()
+        torch.cuda.synchronize()
+        t_f += e[0].elapsed_time(e[1])
+        t_b += e[1].elapsed_time(e[2])
+        t_u += e[2].elapsed_time(e[3])
+    wall = time.perf_counter() - t0
+    k = args.steps
+    t_f, t_b, t_u = t_f / k, t_b / k, t_u / k
+    step_ms = t_f + t_b + t_u
+    hbm, src = _peaks()
+    upd_bytes = x_size * d_size * (8 + w["par_bytes"]) + 4 * m * (x_size + d_size)
+    flops = 2.0 * m * x_size * d_size
+    line = {
+        "metric": "analog_tile_fwd_bwd_update_columns_per_s",
+        "config": args.config, "x_size": x_size, "d_size": d_size, "batch": m,
+        "value": m / (step_ms * 1e-3), "unit": "columns/s",
+        "ms": {"forward": t_f, "backward": t_b, "update": t_u, "step": step_ms,
+               "wall_per_step": 1e3 * wall / k},
+        "forward_tflops": flops / (t_f * 1e-3) / 1e12,
+        "backward_tflops": flops / (t_b * 1e-3) / 1e12,
+        "update_roofline": {
+            "bound": "hbm", "algorithmic_bytes": upd_bytes,
+            "achieved": upd_bytes / (t_u * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+            "frac": upd_bytes / (t_u * 1e-3) / 1e9 / hbm, "peak_source": src,
+            "coincidence_pairs_per_s": float(x_size) * d_size * m / (t_u * 1e-3),
+        },
+    }
+    if args.cpu_baseline:
+        sys.path.insert(0, ROOT)
+        from oracle import ref
+
+        if ref.available():
+            rt = ref.RefTile(cfg)
+            mc = min(m, 512)
+            xc, dc = x[:mc].cpu().numpy(), d[:mc].cpu().numpy()
+            rt.set_learning_rate(w["lr"])
+            rt.forward(xc[:8])
+            t0 = time.perf_counter()
+            rt.forward(xc)
+            rt.backward(dc)
+            rt.update(xc, dc)
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": mc / dt, "unit": "columns/s", "cores": 1,
+                                    "kind": "reference", "sample": f"{mc} of {m} columns, 1 thread"}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -59,6 +59,7 @@ enum : int {
 
 struct TcKernelParams {
   int m, I, O, n_chunks, nrows_pad, kpad;
+  int group; // chunks per group of the work-item order
   const int4 *chunk;   // {o, n_local0, n_global0, valid}
   const int4 *insplit; // {k0 (code column), n_k_stages, K_i, in_off}
   const int *outn;     // N_o
@@ -237,9 +238,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // persistent CTA: work item w = (row block, 128-column chunk); consecutive items share the
-  // row block, so the codes stay in L2 while all chunks of that row block are produced
-  const int n_items = p.n_chunks * ((p.m + TC_M - 1) / TC_M);
+  // persistent CTA: work item w = (row block, 128-column chunk). Items are ordered so that a
+  // group of `p.group` chunks is finished for every row block before the next group starts: the
+  // group's weight operand (p.group * I * 256 KB) stays in L2 while the codes stream past once
+  // per group.
+  const int n_rb = (p.m + TC_M - 1) / TC_M;
+  const int n_items = p.n_chunks * n_rb;
+  auto item = [&](int w, int &chunk_idx, int &rb) {
+    const int per_group = p.group * n_rb;
+    const int g = w / per_group, rem = w - g * per_group;
+    const int gsize = min(p.group, p.n_chunks - g * p.group); // last group may be smaller
+    rb = rem / gsize;
+    chunk_idx = g * p.group + (rem - rb * gsize);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; s++) {
@@ -273,8 +284,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       bool ok = true;
       long long w_empty = 0;
       for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-      const int chunk_idx = w % p.n_chunks;
-      const int r0 = (w / p.n_chunks) * TC_M;
+      int chunk_idx, rb;
+      item(w, chunk_idx, rb);
+      const int r0 = rb * TC_M;
       for (int i = 0; i < p.I && ok; i++) {
         const int4 is = p.insplit[i];
         const int brow = i * p.nrows_pad + chunk_idx * TC_N;
@@ -361,8 +373,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     long long w_tfull = 0;
     const long long t_epi = clock64();
     for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-    const int4 ch = p.chunk[w % p.n_chunks];
-    const int row = (w / p.n_chunks) * TC_M + q * 32 + lane;
+    int chunk_idx, rb;
+    item(w, chunk_idx, rb);
+    const int4 ch = p.chunk[chunk_idx];
+    const int row = rb * TC_M + q * 32 + lane;
     const bool row_ok = row < p.m;
     const uint64_t n4h = (uint64_t)((p.outn[ch.x] + 7) >> 3); // noise block pairs per row
     const bool vec = ((p.out_ss & 3) == 0) && ((ch.z & 3) == 0) &&
@@ -833,6 +847,12 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   p.n_chunks = n_chunks_;
   p.nrows_pad = nrows_pad_;
   p.kpad = kpad_;
+  {
+    // chunks per group: weight operand of a group (hi + lo, all in-splits) about 32 MB
+    const double per_chunk = (double)I * kpad_ * TC_N * 4.0;
+    int g = (int)(32.0 * 1024 * 1024 / per_chunk);
+    p.group = g < 1 ? 1 : (g > n_chunks_ ? n_chunks_ : g);
+  }
   p.chunk = (const int4 *)chunk_tab_;
   p.insplit = (const int4 *)insplit_tab_;
   p.outn = outn_tab_;

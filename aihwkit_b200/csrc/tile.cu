@@ -310,8 +310,11 @@ Tile::~Tile() {
     cudaFree(bm_stats_);
     cudaFree(xw_);
     cudaFree(dw_);
+    cudaFree(xnz_);
+    cudaFree(dnz_);
     cudaFree(onehot_);
     cudaFree(tread_);
+    cudaFree(t_words_);
     cudaFree(stage_dev_);
     cudaFreeHost(stage_pinned_);
     if (prev >= 0) {
@@ -382,6 +385,7 @@ void Tile::toDevice(int cuda_device) {
     AB200_CUDA(cudaMemset(w_fast_, 0, size * sizeof(float)));
     AB200_CUDA(cudaMalloc(&onehot_, (size_t)x_size_ * sizeof(float)));
     AB200_CUDA(cudaMalloc(&tread_, (size_t)d_size_ * sizeof(float)));
+    AB200_CUDA(cudaMalloc(&t_words_, 2 * (size_t)(x_size_ + d_size_) * sizeof(uint32_t)));
   }
   AB200_CUDA(cudaMalloc(&bm_stats_, 2 * sizeof(int)));
   AB200_CUDA(cudaMemset(bm_stats_, 0, 2 * sizeof(int)));
@@ -406,16 +410,21 @@ void Tile::ensureScratch(int m) {
   cudaFree(flags_);
   cudaFree(xw_);
   cudaFree(dw_);
+  cudaFree(xnz_);
+  cudaFree(dnz_);
   int cap = m + m / 4 + 16;
   AB200_CUDA(cudaMalloc(&scale_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&factor_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&vnorm_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&sval_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&flags_, (size_t)cap * sizeof(int)));
-  xw_ = dw_ = nullptr;
+  xw_ = dw_ = xnz_ = dnz_ = nullptr;
   if (cfg_.device_kind != AB200_DEVICE_IDEAL && up_.pulse_type != AB200_PULSE_NONE) {
     AB200_CUDA(cudaMalloc(&xw_, (size_t)cap * x_size_ * sizeof(uint32_t)));
     AB200_CUDA(cudaMalloc(&dw_, (size_t)cap * d_size_ * sizeof(uint32_t)));
+    const size_t nblk = (size_t)(cap + 31) / 32;
+    AB200_CUDA(cudaMalloc(&xnz_, nblk * x_size_ * sizeof(uint32_t)));
+    AB200_CUDA(cudaMalloc(&dnz_, nblk * d_size_ * sizeof(uint32_t)));
   }
   scratch_m_ = cap;
 }
@@ -857,8 +866,12 @@ void Tile::doTransfer(cudaStream_t s) {
     u.up = t_up_;
     u.key = key_;
     u.call = 0x40000000u + call;
-    u.xw = xw_;
-    u.dw = dw_;
+    // own scratch: the gradient batch's pulse words are still in use when a transfer falls in
+    // the middle of a batch
+    u.xw = t_words_;
+    u.dw = t_words_ + x_size_;
+    u.xnz = t_words_ + x_size_ + d_size_;
+    u.dnz = t_words_ + 2 * x_size_ + d_size_;
     u.w = w_;
     u.par4 = dev_[1].par4;
     u.par2 = dev_[1].par2;
@@ -901,6 +914,8 @@ void Tile::update(const float *x, const float *d, bool bias, int m, bool x_trans
   u.call = upd_calls_++;
   u.xw = xw_;
   u.dw = dw_;
+  u.xnz = xnz_;
+  u.dnz = dnz_;
   u.s_begin = 0;
   u.s_end = m;
 
@@ -998,6 +1013,8 @@ void Tile::coincidences(const float *x, const float *d, int32_t *counts, cudaStr
   u.call = 0x7fffffffu;
   u.xw = xw_;
   u.dw = dw_;
+  u.xnz = xnz_;
+  u.dnz = dnz_;
   launchPulsePrepare(u, s);
   launchCoincidences(u, counts, s);
 }

@@ -232,15 +232,51 @@ pulseOnce(float w, bool down, const float4 &q, const float2 &e, float xi, int mu
   }
 }
 
-constexpr int UT_I = 64;  // d-lines per CTA (contiguous in memory)
-constexpr int UT_J = 16;  // x-lines per CTA
-constexpr int UE_J = 4;   // x-lines per thread
-constexpr int UCHUNK = 64; // samples staged in shared memory at a time
+constexpr int UT_I = 64; // d-lines per CTA (contiguous in memory)
+constexpr int UT_J = 16; // x-lines per CTA
+constexpr int UE_J = 4;  // x-lines per thread
+constexpr int UBLK = 32; // samples per block = bits of one non-zero bitmap word
+constexpr int UT_JP = UT_J + 1; // padded row length of the staged x words (bank spread)
 
+// Bitmaps of the non-empty pulse words: bit s of nz[blk][line] is set when the word of sample
+// blk * 32 + s on that line carries at least one pulse (or a non-zero implicit value). The update
+// kernel intersects the bitmaps of a d-line and an x-line and only looks at the samples that
+// survive - the GPU form of the index lists the reference CPU builds per pulse slot
+// (src/rpucuda/sparse_bit_line_maker.cpp:200-238).
+__global__ void __launch_bounds__(256)
+    pulseNzKernel(const uint32_t *words, int n_lines, int m, uint32_t *nz, int implicit) {
+  const int line = blockIdx.x * blockDim.x + threadIdx.x;
+  const int blk = blockIdx.y;
+  if (line >= n_lines) {
+    return;
+  }
+  uint32_t bits = 0;
+  const int s0 = blk * UBLK;
+#pragma unroll 4
+  for (int s = 0; s < UBLK; s++) {
+    if (s0 + s < m) {
+      uint32_t w = words[(long long)(s0 + s) * n_lines + line];
+      if (implicit) {
+        w &= 0x7fffffffu;
+      }
+      bits |= (w != 0u ? 1u : 0u) << s;
+    }
+  }
+  nz[(long long)blk * n_lines + line] = bits;
+}
+
+// Every thread owns four weights (one d-line, four x-lines). Per block of 32 samples it walks, for
+// each of its weights, the samples where both lines pulsed; the walk is decoupled from the
+// (expensive, rare) pulse application: each lane first advances to ITS next coincidence, then
+// the whole warp applies one event per lane together, so lanes whose events fall on different
+// samples do not serialise each other. Weights are independent, so the per-weight sample order -
+// the only order the reference defines (rpu_weight_updater.cpp:243-291) - is preserved.
 template <int KIND, bool IMPLICIT>
 __global__ void __launch_bounds__(256) pulsedUpdateKernel(UpdateProblem p) {
-  __shared__ uint32_t sx[UCHUNK][UT_J];
-  __shared__ uint32_t sd[UCHUNK][UT_I];
+  __shared__ uint32_t sx[UBLK][UT_JP];
+  __shared__ uint32_t sd[UBLK][UT_I];
+  __shared__ uint32_t sxnz[UT_J];
+  __shared__ uint32_t sdnz[UT_I];
   const int ti = threadIdx.x & (UT_I - 1);
   const int tj = threadIdx.x / UT_I; // 0..3
   const int i = blockIdx.x * UT_I + ti;
@@ -261,30 +297,49 @@ __global__ void __launch_bounds__(256) pulsedUpdateKernel(UpdateProblem p) {
   }
   const float std = p.dw_min_std;
 
-  for (int s0 = p.s_begin; s0 < p.s_end; s0 += UCHUNK) {
-    const int ns = min(UCHUNK, p.s_end - s0);
-    for (int t = threadIdx.x; t < ns * UT_J; t += blockDim.x) {
+  const int b_first = p.s_begin / UBLK, b_last = (p.s_end - 1) / UBLK;
+  for (int blk = b_first; blk <= b_last; blk++) {
+    const int s0 = blk * UBLK;
+    // samples of this block that belong to [s_begin, s_end)
+    uint32_t range = 0xffffffffu;
+    if (s0 < p.s_begin) {
+      range &= 0xffffffffu << (p.s_begin - s0);
+    }
+    if (s0 + UBLK > p.s_end) {
+      range &= 0xffffffffu >> (s0 + UBLK - p.s_end);
+    }
+    for (int t = threadIdx.x; t < UBLK * UT_J; t += blockDim.x) {
       int ss = t / UT_J, jj = t % UT_J;
       int gj = blockIdx.y * UT_J + jj;
-      sx[ss][jj] = gj < p.x_size ? p.xw[(long long)(s0 + ss) * p.x_size + gj] : 0u;
+      sx[ss][jj] = (gj < p.x_size && s0 + ss < p.m) ? p.xw[(long long)(s0 + ss) * p.x_size + gj] : 0u;
     }
-    for (int t = threadIdx.x; t < ns * UT_I; t += blockDim.x) {
+    for (int t = threadIdx.x; t < UBLK * UT_I; t += blockDim.x) {
       int ss = t / UT_I, ii = t % UT_I;
       int gi = blockIdx.x * UT_I + ii;
-      sd[ss][ii] = gi < p.d_size ? p.dw[(long long)(s0 + ss) * p.d_size + gi] : 0u;
+      sd[ss][ii] = (gi < p.d_size && s0 + ss < p.m) ? p.dw[(long long)(s0 + ss) * p.d_size + gi] : 0u;
+    }
+    if (threadIdx.x < UT_J) {
+      int gj = blockIdx.y * UT_J + threadIdx.x;
+      sxnz[threadIdx.x] = gj < p.x_size ? p.xnz[(long long)blk * p.x_size + gj] : 0u;
+    } else if (threadIdx.x >= 64 && threadIdx.x < 64 + UT_I) {
+      int gi = blockIdx.x * UT_I + (threadIdx.x - 64);
+      sdnz[threadIdx.x - 64] = gi < p.d_size ? p.dnz[(long long)blk * p.d_size + gi] : 0u;
     }
     __syncthreads();
-    if (i_ok) {
-      for (int ss = 0; ss < ns; ss++) {
-        const uint32_t dwv = sd[ss][ti];
-        if (dwv == 0u) {
-          continue;
-        }
+    const uint32_t dmask = i_ok ? (sdnz[ti] & range) : 0u;
 #pragma unroll
-        for (int t = 0; t < UE_J; t++) {
-          const uint32_t xwv = sx[ss][tj * UE_J + t];
-          int n;
-          bool down;
+    for (int t = 0; t < UE_J; t++) {
+      const int j = j0 + t;
+      uint32_t cand = (j < p.x_size) ? (dmask & sxnz[tj * UE_J + t]) : 0u;
+      const long long idx = (long long)j * p.d_size + i;
+      while (true) {
+        // advance to this lane's next coincidence
+        int n = 0, ss = 0;
+        bool down = false;
+        while (cand != 0u) {
+          ss = __ffs(cand) - 1;
+          cand &= cand - 1u;
+          const uint32_t dwv = sd[ss][ti], xwv = sx[ss][tj * UE_J + t];
           if (IMPLICIT) {
             // n = rint(d * BL * x), positive = decrease (dense_bit_line_maker.cpp:240-264)
             float c = rintf(__fmul_rn(__uint_as_float(dwv), __uint_as_float(xwv)));
@@ -296,14 +351,14 @@ __global__ void __launch_bounds__(256) pulsedUpdateKernel(UpdateProblem p) {
             n = __popc((xwv & dwv) >> 1);
             down = ((xwv ^ dwv) & 1u) == 0u;
           }
-          if (n == 0) {
-            continue;
+          if (n != 0) {
+            break;
           }
-          const int j = j0 + t;
-          if (j >= p.x_size) {
-            continue;
-          }
-          const long long idx = (long long)j * p.d_size + i;
+        }
+        if (!__any_sync(0xffffffffu, n != 0)) {
+          break;
+        }
+        if (n != 0) {
           if (!loaded[t]) {
             w[t] = p.w[idx];
             q[t] = p.par4[idx];
@@ -344,6 +399,14 @@ void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream) {
     AB200_FATAL("desired_BL > 31 is not implemented for stochastic pulse trains");
   }
   pulsePrepareKernel<<<p.m, 256, 0, stream>>>(p);
+  AB200_LAUNCH_CHECK();
+  const int implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT ? 1 : 0;
+  const int n_blk = (p.m + UBLK - 1) / UBLK;
+  pulseNzKernel<<<dim3((p.x_size + 255) / 256, n_blk), 256, 0, stream>>>(p.xw, p.x_size, p.m, p.xnz,
+                                                                       implicit);
+  AB200_LAUNCH_CHECK();
+  pulseNzKernel<<<dim3((p.d_size + 255) / 256, n_blk), 256, 0, stream>>>(p.dw, p.d_size, p.m, p.dnz,
+                                                                       implicit);
   AB200_LAUNCH_CHECK();
 }
 
