@@ -265,18 +265,30 @@ __global__ void __launch_bounds__(256)
   nz[(long long)blk * n_lines + line] = bits;
 }
 
-// Every thread owns four weights (one d-line, four x-lines). Per block of 32 samples it walks, for
-// each of its weights, the samples where both lines pulsed; the walk is decoupled from the
-// (expensive, rare) pulse application: each lane first advances to ITS next coincidence, then
+// Every thread owns four weights (one d-line, four x-lines). Per super-block of 128 samples it
+// walks, for each of its weights, the samples where both lines pulsed; the walk is decoupled from
+// the (expensive, rare) pulse application: each lane first advances to ITS next coincidence, then
 // the whole warp applies one event per lane together, so lanes whose events fall on different
-// samples do not serialise each other. Weights are independent, so the per-weight sample order -
-// the only order the reference defines (rpu_weight_updater.cpp:243-291) - is preserved.
-template <int KIND, bool IMPLICIT>
-__global__ void __launch_bounds__(256) pulsedUpdateKernel(UpdateProblem p) {
-  __shared__ uint32_t sx[UBLK][UT_JP];
-  __shared__ uint32_t sd[UBLK][UT_I];
-  __shared__ uint32_t sxnz[UT_J];
-  __shared__ uint32_t sdnz[UT_I];
+// samples do not serialise each other. The super-block is long so that the number of events per
+// lane has a small relative spread (the warp runs as many rounds as its busiest lane). Weights
+// are independent, so the per-weight sample order - the only order the reference defines
+// (rpu_weight_updater.cpp:243-291) - is preserved.
+constexpr int USUP = 4;              // bitmap words per super-block
+constexpr int USAMP = USUP * UBLK;   // samples per super-block
+constexpr int URES = 8;              // Gaussians per thread in the reservoir
+
+struct UpdateSmem {
+  uint32_t sd[USAMP][UT_I];
+  uint32_t sx[USAMP][UT_JP];
+  uint32_t sdnz[USUP][UT_I];
+  uint32_t sxnz[USUP][UT_J];
+  float sz[URES][256];
+};
+
+template <int KIND, bool IMPLICIT, bool NOISY>
+__global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  UpdateSmem &sm = *reinterpret_cast<UpdateSmem *>(smem_raw);
   const int ti = threadIdx.x & (UT_I - 1);
   const int tj = threadIdx.x / UT_I; // 0..3
   const int i = blockIdx.x * UT_I + ti;
@@ -296,50 +308,80 @@ __global__ void __launch_bounds__(256) pulsedUpdateKernel(UpdateProblem p) {
     e[t] = make_float2(0.f, 0.f);
   }
   const float std = p.dw_min_std;
+  const uint32_t gid = (blockIdx.y * gridDim.x + blockIdx.x) * 256u + threadIdx.x;
+  uint32_t refills = 0;
+  int rc = 0;
 
-  const int b_first = p.s_begin / UBLK, b_last = (p.s_end - 1) / UBLK;
+  const int b_first = p.s_begin / USAMP, b_last = (p.s_end - 1) / USAMP;
+  const int n_words = (p.m + UBLK - 1) / UBLK;
   for (int blk = b_first; blk <= b_last; blk++) {
-    const int s0 = blk * UBLK;
-    // samples of this block that belong to [s_begin, s_end)
-    uint32_t range = 0xffffffffu;
-    if (s0 < p.s_begin) {
-      range &= 0xffffffffu << (p.s_begin - s0);
+    const int s0 = blk * USAMP;
+    {
+      // every thread stages one fixed column of the x words and one of the d words, so the
+      // loop only advances a pointer by a row
+      const int jj = threadIdx.x % UT_J, sj = threadIdx.x / UT_J;
+      const int gj = blockIdx.y * UT_J + jj;
+      const uint32_t *src = p.xw + (long long)(s0 + sj) * p.x_size + gj;
+      const long long step = (long long)(256 / UT_J) * p.x_size;
+#pragma unroll 4
+      for (int ss = sj; ss < USAMP; ss += 256 / UT_J, src += step) {
+        sm.sx[ss][jj] = (gj < p.x_size && s0 + ss < p.m) ? *src : 0u;
+      }
     }
-    if (s0 + UBLK > p.s_end) {
-      range &= 0xffffffffu >> (s0 + UBLK - p.s_end);
+    {
+      const int ii = threadIdx.x % UT_I, si = threadIdx.x / UT_I;
+      const int gi = blockIdx.x * UT_I + ii;
+      const uint32_t *src = p.dw + (long long)(s0 + si) * p.d_size + gi;
+      const long long step = (long long)(256 / UT_I) * p.d_size;
+#pragma unroll 8
+      for (int ss = si; ss < USAMP; ss += 256 / UT_I, src += step) {
+        sm.sd[ss][ii] = (gi < p.d_size && s0 + ss < p.m) ? *src : 0u;
+      }
     }
-    for (int t = threadIdx.x; t < UBLK * UT_J; t += blockDim.x) {
-      int ss = t / UT_J, jj = t % UT_J;
-      int gj = blockIdx.y * UT_J + jj;
-      sx[ss][jj] = (gj < p.x_size && s0 + ss < p.m) ? p.xw[(long long)(s0 + ss) * p.x_size + gj] : 0u;
-    }
-    for (int t = threadIdx.x; t < UBLK * UT_I; t += blockDim.x) {
-      int ss = t / UT_I, ii = t % UT_I;
-      int gi = blockIdx.x * UT_I + ii;
-      sd[ss][ii] = (gi < p.d_size && s0 + ss < p.m) ? p.dw[(long long)(s0 + ss) * p.d_size + gi] : 0u;
-    }
-    if (threadIdx.x < UT_J) {
-      int gj = blockIdx.y * UT_J + threadIdx.x;
-      sxnz[threadIdx.x] = gj < p.x_size ? p.xnz[(long long)blk * p.x_size + gj] : 0u;
-    } else if (threadIdx.x >= 64 && threadIdx.x < 64 + UT_I) {
-      int gi = blockIdx.x * UT_I + (threadIdx.x - 64);
-      sdnz[threadIdx.x - 64] = gi < p.d_size ? p.dnz[(long long)blk * p.d_size + gi] : 0u;
+    for (int t = threadIdx.x; t < USUP * (UT_I + UT_J); t += blockDim.x) {
+      const int wi = t / (UT_I + UT_J), c = t % (UT_I + UT_J);
+      const int word = blk * USUP + wi;
+      if (c < UT_I) {
+        int gi = blockIdx.x * UT_I + c;
+        // samples of this word that belong to [s_begin, s_end)
+        uint32_t range = 0xffffffffu;
+        const int sb = word * UBLK;
+        if (sb < p.s_begin) {
+          range = p.s_begin - sb >= UBLK ? 0u : range << (p.s_begin - sb);
+        }
+        if (sb + UBLK > p.s_end) {
+          range = sb >= p.s_end ? 0u : range & (0xffffffffu >> (sb + UBLK - p.s_end));
+        }
+        sm.sdnz[wi][c] =
+            (gi < p.d_size && word < n_words) ? (p.dnz[(long long)word * p.d_size + gi] & range) : 0u;
+      } else {
+        int gj = blockIdx.y * UT_J + (c - UT_I);
+        sm.sxnz[wi][c - UT_I] =
+            (gj < p.x_size && word < n_words) ? p.xnz[(long long)word * p.x_size + gj] : 0u;
+      }
     }
     __syncthreads();
-    const uint32_t dmask = i_ok ? (sdnz[ti] & range) : 0u;
 #pragma unroll
     for (int t = 0; t < UE_J; t++) {
-      const int j = j0 + t;
-      uint32_t cand = (j < p.x_size) ? (dmask & sxnz[tj * UE_J + t]) : 0u;
-      const long long idx = (long long)j * p.d_size + i;
+      const int jl = tj * UE_J + t;
+      const long long idx = (long long)(j0 + t) * p.d_size + i;
+      int wi = 0;
+      uint32_t cand = sm.sdnz[0][ti] & sm.sxnz[0][jl];
       while (true) {
         // advance to this lane's next coincidence
-        int n = 0, ss = 0;
+        int n = 0;
         bool down = false;
-        while (cand != 0u) {
-          ss = __ffs(cand) - 1;
+        while (true) {
+          if (cand == 0u) {
+            if (++wi >= USUP) {
+              break;
+            }
+            cand = sm.sdnz[wi][ti] & sm.sxnz[wi][jl];
+            continue;
+          }
+          const int ss = wi * UBLK + __ffs(cand) - 1;
           cand &= cand - 1u;
-          const uint32_t dwv = sd[ss][ti], xwv = sx[ss][tj * UE_J + t];
+          const uint32_t dwv = sm.sd[ss][ti], xwv = sm.sx[ss][jl];
           if (IMPLICIT) {
             // n = rint(d * BL * x), positive = decrease (dense_bit_line_maker.cpp:240-264)
             float c = rintf(__fmul_rn(__uint_as_float(dwv), __uint_as_float(xwv)));
@@ -368,13 +410,37 @@ __global__ void __launch_bounds__(256) pulsedUpdateKernel(UpdateProblem p) {
             loaded[t] = true;
           }
           dirty[t] = true;
-          float z[4] = {0.f, 0.f, 0.f, 0.f};
+        }
+        if (!NOISY) {
           for (int k = 0; k < n; k++) {
-            if (std > 0.0f && (k & 3) == 0) {
-              gauss4(p.key, (uint64_t)idx | ((uint64_t)(uint32_t)(s0 + ss) << 32), p.call,
-                     TAG_DEVICE + (uint32_t)(k >> 2), z);
+            w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], 0.0f, p.mult_noise);
+          }
+        } else if (!__any_sync(0xffffffffu, n > rc)) {
+          // One Gaussian per pulse, taken from a per-thread reservoir in shared memory: the
+          // generator - by far the most expensive part of a pulse - runs once per several
+          // events instead of per event.
+          for (int k = 0; k < n; k++) {
+            rc--;
+            w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], std * sm.sz[rc][threadIdx.x], p.mult_noise);
+          }
+        } else {
+          // Some lane needs more Gaussians than it has left: refill the whole warp whenever a
+          // lane with a pulse to apply runs dry (leftovers are discarded).
+          for (int k = 0; __any_sync(0xffffffffu, k < n); k++) {
+            if (__any_sync(0xffffffffu, k < n && rc == 0)) {
+              float z[8];
+              gauss8(p.key, (uint64_t)gid | ((uint64_t)refills << 32), p.call, TAG_DEVICE, z);
+#pragma unroll
+              for (int r = 0; r < URES; r++) {
+                sm.sz[r][threadIdx.x] = z[r];
+              }
+              rc = URES;
+              refills++;
             }
-            w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], std * z[k & 3], p.mult_noise);
+            if (k < n) {
+              rc--;
+              w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], std * sm.sz[rc][threadIdx.x], p.mult_noise);
+            }
           }
         }
       }
@@ -389,6 +455,20 @@ __global__ void __launch_bounds__(256) pulsedUpdateKernel(UpdateProblem p) {
       }
     }
   }
+}
+
+template <int KIND, bool IMPLICIT, bool NOISY>
+static void launchUpdateInstance(const UpdateProblem &p, dim3 grid, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  AB200_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    AB200_CUDA(cudaFuncSetAttribute(pulsedUpdateKernel<KIND, IMPLICIT, NOISY>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)sizeof(UpdateSmem)));
+    configured[dev] = true;
+  }
+  pulsedUpdateKernel<KIND, IMPLICIT, NOISY><<<grid, 256, sizeof(UpdateSmem), stream>>>(p);
 }
 
 void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream) {
@@ -416,11 +496,18 @@ void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream) {
   }
   dim3 grid((p.d_size + UT_I - 1) / UT_I, (p.x_size + UT_J - 1) / UT_J);
   const bool implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT;
+  const bool noisy = p.dw_min_std > 0.0f;
+#define AB200_UPD2(KIND, IMPL)                                                                     \
+  if (noisy) {                                                                                     \
+    launchUpdateInstance<KIND, IMPL, true>(p, grid, stream);                                       \
+  } else {                                                                                         \
+    launchUpdateInstance<KIND, IMPL, false>(p, grid, stream);                                      \
+  }
 #define AB200_UPD(KIND)                                                                            \
   if (implicit) {                                                                                  \
-    pulsedUpdateKernel<KIND, true><<<grid, 256, 0, stream>>>(p);                                   \
+    AB200_UPD2(KIND, true)                                                                         \
   } else {                                                                                         \
-    pulsedUpdateKernel<KIND, false><<<grid, 256, 0, stream>>>(p);                                  \
+    AB200_UPD2(KIND, false)                                                                        \
   }
   switch (p.kind) {
   case AB200_DEVICE_CONSTANT_STEP:
@@ -437,6 +524,7 @@ void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream) {
     AB200_FATAL("pulsed update: device kind not implemented");
   }
 #undef AB200_UPD
+#undef AB200_UPD2
   AB200_LAUNCH_CHECK();
 }
 
