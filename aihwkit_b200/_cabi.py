@@ -166,6 +166,11 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_backward_host": (_I, [_VP, _FP, _FP, _I, _I, _I, _I, _VP]),
         "ab200_tile_update_host": (_I, [_VP, _FP, _FP, _I, _I, _I, _I, _VP]),
         "ab200_tile_coincidences": (_I, [_VP, _FP, _FP, _FP, _VP]),
+        "ab200_tile_set_matrix_indices": (_I, [_VP, _FP, C.c_longlong, _VP]),
+        "ab200_tile_has_matrix_indices": (_I, [_VP]),
+        "ab200_tile_forward_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _I, _VP]),
+        "ab200_tile_backward_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _VP]),
+        "ab200_tile_update_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _VP]),
         "ab200_tile_last_bm_stats": (_I, [_VP, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
         "ab200_tile_set_seed": (_I, [_VP, C.c_uint64]),
         "ab200_array_create": (_I, [cfgp, _I, _I, _I, _I, _I, _I, _I, C.POINTER(_VP)]),

@@ -259,6 +259,44 @@ int ab200_tile_coincidences(ab200_tile *tile, const float *x_dev, const float *d
   AB200_CATCH
 }
 
+int ab200_tile_set_matrix_indices(ab200_tile *tile, const int32_t *indices, long long count,
+                                  void *stream) {
+  AB200_TRY
+  T(tile)->setMatrixIndices(indices, count, (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+int ab200_tile_has_matrix_indices(ab200_tile *tile) {
+  return tile != nullptr && T(tile)->hasMatrixIndices() ? 1 : 0;
+}
+
+int ab200_tile_forward_indexed(ab200_tile *tile, const float *x_dev, float *d_dev,
+                               long long total_input_size, int m_batch, int dim3, int trans,
+                               int is_test, void *stream) {
+  AB200_TRY
+  T(tile)->forwardIndexed(x_dev, d_dev, total_input_size, m_batch, dim3, trans != 0, is_test != 0,
+                          (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+int ab200_tile_backward_indexed(ab200_tile *tile, const float *d_dev, float *x_dev,
+                                long long total_output_size, int m_batch, int dim3, int trans,
+                                void *stream) {
+  AB200_TRY
+  T(tile)->backwardIndexed(d_dev, x_dev, total_output_size, m_batch, dim3, trans != 0,
+                           (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+int ab200_tile_update_indexed(ab200_tile *tile, const float *x_dev, const float *d_dev,
+                              long long total_input_size, int m_batch, int dim3, int trans,
+                              void *stream) {
+  AB200_TRY
+  T(tile)->updateIndexed(x_dev, d_dev, total_input_size, m_batch, dim3, trans != 0,
+                         (cudaStream_t)stream);
+  AB200_CATCH
+}
+
 int ab200_tile_last_bm_stats(ab200_tile *tile, int32_t *n_rerun_samples, float *max_reduction) {
   AB200_TRY
   T(tile)->lastBmStats(n_rerun_samples, max_reduction);

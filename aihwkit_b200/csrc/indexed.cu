@@ -1,0 +1,271 @@
+// Indexed (im2col-free) convolution interface of the analog tile: the caller hands over whole
+// images and an index array that says, for every tile input and every output position, which
+// image element feeds it (0 = padding, 1 = the constant of an analog bias, j >= 2 = element j - 2).
+// Reference: RPUSimple<T>::copyIndexedInput / copyIndexedOutput / forwardIndexed / backwardIndexed /
+// updateIndexed (src/rpucuda/rpu.cpp:846-1013, 1117-1239); the reference GPU reads through
+// iterators instead (src/rpucuda/cuda/io_iterator.h:194-303).
+//
+// Here the gather writes the sample-major matrix [dim3 * m_batch][x_size] that the MVM and
+// update kernels read (row = one output position of one image), so the tensor-core path with
+// its TMA-tiled operands applies unchanged; the image-major output layout [dim3][d_size][m_batch]
+// is produced by a batched transpose.
+#include "tile.h"
+
+namespace ab200 {
+
+namespace {
+
+// cols[(n * m_batch + l) * size + r] = src(n, idx[r][l]);  idx is [size][m_batch]
+// Tile of 32 positions x 32 inputs through shared memory: the index array and the image are read
+// along l (neighbouring output positions read neighbouring pixels), the matrix is written along r.
+__global__ void __launch_bounds__(256)
+    gatherTransKernel(const float *x, const int *idx, float *cols, int size, int m_batch,
+                      long long in_mat) {
+  __shared__ float tile[32][33];
+  const int n = blockIdx.z;
+  const int l0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const float *img = x + (long long)n * in_mat;
+  for (int k = threadIdx.y; k < 32; k += 8) {
+    const int r = r0 + k, l = l0 + threadIdx.x;
+    float v = 0.0f;
+    if (r < size && l < m_batch) {
+      const int j = idx[(long long)r * m_batch + l];
+      v = j <= 1 ? (float)j : img[j - 2];
+    }
+    tile[k][threadIdx.x] = v;
+  }
+  __syncthreads();
+  for (int k = threadIdx.y; k < 32; k += 8) {
+    const int l = l0 + k, r = r0 + threadIdx.x;
+    if (r < size && l < m_batch) {
+      cols[((long long)n * m_batch + l) * size + r] = tile[threadIdx.x][k];
+    }
+  }
+}
+
+// idx is [m_batch][size]: the matrix and the index array have the same order
+__global__ void __launch_bounds__(256)
+    gatherPlainKernel(const float *x, const int *idx, float *cols, long long per_image,
+                      long long in_mat) {
+  const int n = blockIdx.y;
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < per_image) {
+    const int j = idx[t];
+    cols[n * per_image + t] = j <= 1 ? (float)j : x[n * in_mat + j - 2];
+  }
+}
+
+// out(n, idx[r][l]) += cols[(n * m_batch + l) * size + r]
+__global__ void __launch_bounds__(256)
+    scatterTransKernel(const float *cols, const int *idx, float *out, int size, int m_batch,
+                       long long out_mat) {
+  __shared__ float tile[32][33];
+  const int n = blockIdx.z;
+  const int l0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int k = threadIdx.y; k < 32; k += 8) {
+    const int l = l0 + k, r = r0 + threadIdx.x;
+    tile[k][threadIdx.x] =
+        (r < size && l < m_batch) ? cols[((long long)n * m_batch + l) * size + r] : 0.0f;
+  }
+  __syncthreads();
+  float *img = out + (long long)n * out_mat;
+  for (int k = threadIdx.y; k < 32; k += 8) {
+    const int r = r0 + k, l = l0 + threadIdx.x;
+    if (r < size && l < m_batch) {
+      const int j = idx[(long long)r * m_batch + l];
+      if (j > 1) {
+        atomicAdd(img + (j - 2), tile[threadIdx.x][k]);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    scatterPlainKernel(const float *cols, const int *idx, float *out, long long per_image,
+                       long long out_mat) {
+  const int n = blockIdx.y;
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < per_image) {
+    const int j = idx[t];
+    if (j > 1) {
+      atomicAdd(out + n * out_mat + (j - 2), cols[n * per_image + t]);
+    }
+  }
+}
+
+// dst[b][c][r] = src[b][r][c]
+__global__ void __launch_bounds__(256)
+    batchedTransposeKernel(const float *src, float *dst, int rows, int cols) {
+  __shared__ float tile[32][33];
+  const long long base = (long long)blockIdx.z * rows * cols;
+  const int c = blockIdx.x * 32 + threadIdx.x, r = blockIdx.y * 32 + threadIdx.y;
+  for (int k = 0; k < 32; k += 8) {
+    if (c < cols && r + k < rows) {
+      tile[threadIdx.y + k][threadIdx.x] = src[base + (long long)(r + k) * cols + c];
+    }
+  }
+  __syncthreads();
+  const int oc = blockIdx.y * 32 + threadIdx.x, orow = blockIdx.x * 32 + threadIdx.y;
+  for (int k = 0; k < 32; k += 8) {
+    if (oc < rows && orow + k < cols) {
+      dst[base + (long long)(orow + k) * rows + oc] = tile[threadIdx.x][threadIdx.y + k];
+    }
+  }
+}
+
+void launchBatchedTranspose(const float *src, float *dst, int rows, int cols, int batch,
+                            cudaStream_t s) {
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch), block(32, 8);
+  batchedTransposeKernel<<<grid, block, 0, s>>>(src, dst, rows, cols);
+  AB200_LAUNCH_CHECK();
+}
+
+} // namespace
+
+void Tile::setMatrixIndices(const int32_t *indices, long long n, cudaStream_t s) {
+  requireDevice("set_matrix_indices");
+  if (n <= 0 || indices == nullptr) {
+    AB200_FATAL("set_matrix_indices: empty index array");
+  }
+  AB200_CUDA(cudaSetDevice(device_));
+  if (n > idx_cap_) {
+    if (idx_) {
+      AB200_CUDA(cudaFree(idx_));
+      idx_ = nullptr;
+    }
+    AB200_CUDA(cudaMalloc(&idx_, (size_t)n * sizeof(int32_t)));
+    idx_cap_ = n;
+  }
+  // the array may live on the host or on a device; keep an own copy and learn its value range
+  // once, so that every later call can reject images that are too small for it on the host
+  std::vector<int32_t> host((size_t)n);
+  AB200_CUDA(cudaMemcpyAsync(idx_, indices, (size_t)n * sizeof(int32_t), cudaMemcpyDefault, s));
+  AB200_CUDA(cudaMemcpyAsync(host.data(), idx_, (size_t)n * sizeof(int32_t),
+                             cudaMemcpyDeviceToHost, s));
+  AB200_CUDA(cudaStreamSynchronize(s));
+  int32_t lo = host[0], hi = host[0];
+  for (long long k = 1; k < n; k++) {
+    lo = host[k] < lo ? host[k] : lo;
+    hi = host[k] > hi ? host[k] : hi;
+  }
+  if (lo < 0) {
+    idx_count_ = 0;
+    AB200_FATAL("set_matrix_indices: negative index " << lo);
+  }
+  idx_count_ = n;
+  idx_max_ = hi;
+}
+
+void Tile::requireIndices(const char *what, long long image_size, int m_batch, int n_img) const {
+  if (idx_count_ == 0) {
+    AB200_FATAL("Matrix indices not set yet!"); // rpu.h:457-463
+  }
+  if (m_batch <= 0 || n_img <= 0) {
+    AB200_FATAL(what << ": m_batch and dim3 must be positive");
+  }
+  if (idx_count_ != (long long)x_size_ * m_batch) {
+    AB200_FATAL(what << ": the index array has " << idx_count_ << " entries, expected x_size * m_batch = "
+                     << (long long)x_size_ * m_batch);
+  }
+  if ((long long)idx_max_ - 2 >= image_size) {
+    AB200_FATAL(what << ": index " << idx_max_ << " points outside an image of " << image_size
+                     << " elements");
+  }
+  if (n_img > 65535) {
+    AB200_FATAL(what << ": more than 65535 images per call are not supported");
+  }
+}
+
+void Tile::ensureIndexedScratch(long long b) {
+  if (b > cols_cap_) {
+    if (cols_x_) {
+      AB200_CUDA(cudaFree(cols_x_));
+      AB200_CUDA(cudaFree(cols_d_));
+      cols_x_ = cols_d_ = nullptr;
+    }
+    AB200_CUDA(cudaMalloc(&cols_x_, (size_t)b * x_size_ * sizeof(float)));
+    AB200_CUDA(cudaMalloc(&cols_d_, (size_t)b * d_size_ * sizeof(float)));
+    cols_cap_ = b;
+  }
+}
+
+void Tile::gatherIndexed(const float *x, long long in_mat, int m_batch, int n_img, bool trans,
+                         cudaStream_t s) {
+  if (trans) {
+    dim3 grid((m_batch + 31) / 32, (x_size_ + 31) / 32, n_img), block(32, 8);
+    gatherTransKernel<<<grid, block, 0, s>>>(x, idx_, cols_x_, x_size_, m_batch, in_mat);
+  } else {
+    const long long per_image = (long long)m_batch * x_size_;
+    dim3 grid((unsigned)((per_image + 255) / 256), n_img);
+    gatherPlainKernel<<<grid, 256, 0, s>>>(x, idx_, cols_x_, per_image, in_mat);
+  }
+  AB200_LAUNCH_CHECK();
+}
+
+void Tile::forwardIndexed(const float *x, float *d, long long total_input_size, int m_batch,
+                          int n_img, bool trans, bool is_test, cudaStream_t s) {
+  requireDevice("forward_indexed");
+  const long long in_mat = n_img > 0 ? total_input_size / n_img : 0;
+  requireIndices("forward_indexed", in_mat, m_batch, n_img);
+  const long long b = (long long)m_batch * n_img;
+  if (b > 0x7fffffffLL) {
+    AB200_FATAL("forward_indexed: m_batch * dim3 does not fit an int");
+  }
+  ensureIndexedScratch(b);
+  gatherIndexed(x, in_mat, m_batch, n_img, trans, s);
+  if (trans) {
+    forward(cols_x_, cols_d_, false, (int)b, false, false, is_test, s);
+    launchBatchedTranspose(cols_d_, d, m_batch, d_size_, n_img, s); // -> [dim3][d_size][m_batch]
+  } else {
+    forward(cols_x_, d, false, (int)b, false, false, is_test, s);
+  }
+}
+
+void Tile::backwardIndexed(const float *d, float *x, long long total_output_size, int m_batch,
+                           int n_img, bool trans, cudaStream_t s) {
+  requireDevice("backward_indexed");
+  const long long out_mat = n_img > 0 ? total_output_size / n_img : 0;
+  requireIndices("backward_indexed", out_mat, m_batch, n_img);
+  const long long b = (long long)m_batch * n_img;
+  if (b > 0x7fffffffLL) {
+    AB200_FATAL("backward_indexed: m_batch * dim3 does not fit an int");
+  }
+  ensureIndexedScratch(b);
+  const float *src = d;
+  if (trans) {
+    launchBatchedTranspose(d, cols_d_, d_size_, m_batch, n_img, s); // -> [dim3][m_batch][d_size]
+    src = cols_d_;
+  }
+  backward(src, cols_x_, false, (int)b, false, false, s);
+  AB200_CUDA(cudaMemsetAsync(x, 0, (size_t)total_output_size * sizeof(float), s));
+  if (trans) {
+    dim3 grid((m_batch + 31) / 32, (x_size_ + 31) / 32, n_img), block(32, 8);
+    scatterTransKernel<<<grid, block, 0, s>>>(cols_x_, idx_, x, x_size_, m_batch, out_mat);
+  } else {
+    const long long per_image = (long long)m_batch * x_size_;
+    dim3 grid((unsigned)((per_image + 255) / 256), n_img);
+    scatterPlainKernel<<<grid, 256, 0, s>>>(cols_x_, idx_, x, per_image, out_mat);
+  }
+  AB200_LAUNCH_CHECK();
+}
+
+void Tile::updateIndexed(const float *x, const float *d, long long total_input_size, int m_batch,
+                         int n_img, bool trans, cudaStream_t s) {
+  requireDevice("update_indexed");
+  const long long in_mat = n_img > 0 ? total_input_size / n_img : 0;
+  requireIndices("update_indexed", in_mat, m_batch, n_img);
+  const long long b = (long long)m_batch * n_img;
+  if (b > 0x7fffffffLL) {
+    AB200_FATAL("update_indexed: m_batch * dim3 does not fit an int");
+  }
+  ensureIndexedScratch(b);
+  gatherIndexed(x, in_mat, m_batch, n_img, trans, s);
+  const float *src = d;
+  if (trans) {
+    launchBatchedTranspose(d, cols_d_, d_size_, m_batch, n_img, s);
+    src = cols_d_;
+  }
+  update(cols_x_, src, false, (int)b, false, false, s);
+}
+
+} // namespace ab200

@@ -315,6 +315,9 @@ Tile::~Tile() {
     cudaFree(onehot_);
     cudaFree(tread_);
     cudaFree(t_words_);
+    cudaFree(idx_);
+    cudaFree(cols_x_);
+    cudaFree(cols_d_);
     cudaFree(stage_dev_);
     cudaFreeHost(stage_pinned_);
     if (prev >= 0) {

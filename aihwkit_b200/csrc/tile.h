@@ -183,6 +183,17 @@ public:
   void updateHost(const float *x, const float *d, bool bias, int m, bool x_trans, bool d_trans,
                   cudaStream_t s);
   void coincidences(const float *x, const float *d, int32_t *counts, cudaStream_t s);
+
+  // indexed convolution interface (RPUSimple::setMatrixIndices / forwardIndexed / backwardIndexed /
+  // updateIndexed, src/rpucuda/rpu.h:452-478); `indices` may be host or device memory and is copied
+  void setMatrixIndices(const int32_t *indices, long long n, cudaStream_t s);
+  bool hasMatrixIndices() const { return idx_count_ != 0; }
+  void forwardIndexed(const float *x, float *d, long long total_input_size, int m_batch, int n_img,
+                      bool trans, bool is_test, cudaStream_t s);
+  void backwardIndexed(const float *d, float *x, long long total_output_size, int m_batch,
+                       int n_img, bool trans, cudaStream_t s);
+  void updateIndexed(const float *x, const float *d, long long total_input_size, int m_batch,
+                     int n_img, bool trans, cudaStream_t s);
   void lastBmStats(int32_t *n_rerun, float *max_red);
 
   // used by the mapped array: forward on a sub-block of a wider activation matrix
@@ -207,6 +218,10 @@ private:
   void pulsedUpdateRange(UpdateProblem &p, cudaStream_t s);
   void doTransfer(cudaStream_t s);
   float pulseCountLR() const;
+  void requireIndices(const char *what, long long image_size, int m_batch, int n_img) const;
+  void ensureIndexedScratch(long long b);
+  void gatherIndexed(const float *x, long long in_mat, int m_batch, int n_img, bool trans,
+                     cudaStream_t s);
 
   ab200_tile_config cfg_;
   int x_size_, d_size_;
@@ -238,6 +253,13 @@ private:
   // tensor-core engines (forward / backward operand caches), rebuilt when the weights change
   std::unique_ptr<TcEngine> tc_fwd_, tc_bwd_;
   uint64_t w_version_ = 1, tc_fwd_version_ = 0, tc_bwd_version_ = 0;
+  // indexed interface: own copy of the index array, its largest entry, and the sample-major
+  // matrices [n_img * m_batch][x_size] and [n_img * m_batch][d_size]
+  int32_t *idx_ = nullptr;
+  long long idx_cap_ = 0, idx_count_ = 0;
+  int32_t idx_max_ = 0;
+  float *cols_x_ = nullptr, *cols_d_ = nullptr;
+  long long cols_cap_ = 0;
   // staging for the *_host entry points
   float *stage_dev_ = nullptr;
   float *stage_pinned_ = nullptr;

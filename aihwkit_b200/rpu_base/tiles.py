@@ -269,6 +269,73 @@ class AnalogTile:
                 )
             )
 
+    # -- indexed convolution interface ---------------------------------------------------------
+    def set_matrix_indices(self, indices: torch.Tensor) -> None:
+        """rpu_base_tiles.cpp ``set_matrix_indices``: int32 index tensor of a convolution
+        (``AnalogConv2d._calculate_indexes``, nn/modules/conv.py:534-571).  The tile keeps its
+        own copy."""
+        if indices.dtype != torch.int32:
+            raise RuntimeError("indices must be an int32 tensor")
+        idx = indices.contiguous()
+        stream = _stream_ptr(idx) if idx.is_cuda else None
+        check(self._lib.ab200_tile_set_matrix_indices(self._h, idx.data_ptr(), idx.numel(), stream))
+
+    def has_matrix_indices(self) -> bool:
+        return bool(self._lib.ab200_tile_has_matrix_indices(self._h))
+
+    def _indexed_dims(self, d: torch.Tensor):
+        n = d.size(0)
+        return n, d.numel() // (d.size(0) * d.size(1))
+
+    def forward_indexed(self, x_input: torch.Tensor, d_tensor: torch.Tensor, is_test: bool = False,
+                        non_blocking: bool = False) -> torch.Tensor:
+        """rpu_base_tiles_cuda.cpp:399-432: ``x_input`` is ``[N, C, H, W]``, ``d_tensor`` the
+        preallocated ``[N, d_size, H_out, W_out]`` result, which is filled and returned."""
+        x = _check_input(x_input, "x_input")
+        if not (x.is_cuda and d_tensor.is_cuda and d_tensor.is_contiguous()):
+            raise RuntimeError("forward_indexed expects contiguous CUDA tensors")
+        if d_tensor.size(1) != self.get_d_size() or d_tensor.size(0) != x.size(0):
+            raise RuntimeError("d_tensor must be [N, d_size, ...]")
+        n, d_image = self._indexed_dims(d_tensor)
+        check(self._lib.ab200_tile_forward_indexed(
+            self._h, x.data_ptr(), d_tensor.data_ptr(), x.numel(), d_image, n, 1, int(is_test),
+            _stream_ptr(x)))
+        if not non_blocking:
+            torch.cuda.current_stream(x.device).synchronize()
+        return d_tensor
+
+    def backward_indexed(self, d_input: torch.Tensor, x_tensor: torch.Tensor,
+                         non_blocking: bool = False) -> torch.Tensor:
+        """rpu_base_tiles_cuda.cpp:444-477: ``d_input`` is ``[N, d_size, H_out, W_out]``,
+        ``x_tensor`` the preallocated ``[N, C, H, W]`` result."""
+        d = _check_input(d_input, "d_input")
+        if not (d.is_cuda and x_tensor.is_cuda and x_tensor.is_contiguous()):
+            raise RuntimeError("backward_indexed expects contiguous CUDA tensors")
+        if d.size(1) != self.get_d_size() or d.size(0) != x_tensor.size(0):
+            raise RuntimeError("d_input must be [N, d_size, ...]")
+        n, d_image = self._indexed_dims(d)
+        check(self._lib.ab200_tile_backward_indexed(
+            self._h, d.data_ptr(), x_tensor.data_ptr(), x_tensor.numel(), d_image, n, 1,
+            _stream_ptr(d)))
+        if not non_blocking:
+            torch.cuda.current_stream(d.device).synchronize()
+        return x_tensor
+
+    def update_indexed(self, x_input: torch.Tensor, d_input: torch.Tensor,
+                       non_blocking: bool = False) -> None:
+        """rpu_base_tiles_cuda.cpp:489-516."""
+        x = _check_input(x_input, "x_input")
+        d = _check_input(d_input, "d_input")
+        if not (x.is_cuda and d.is_cuda):
+            raise RuntimeError("update_indexed expects CUDA tensors")
+        if d.size(1) != self.get_d_size() or d.size(0) != x.size(0):
+            raise RuntimeError("d_input must be [N, d_size, ...]")
+        n, d_image = self._indexed_dims(d)
+        check(self._lib.ab200_tile_update_indexed(
+            self._h, x.data_ptr(), d.data_ptr(), x.numel(), d_image, n, 1, _stream_ptr(x)))
+        if not non_blocking:
+            torch.cuda.current_stream(x.device).synchronize()
+
     # -- diagnostics -------------------------------------------------------------------------
     def coincidences(self, x: torch.Tensor, d: torch.Tensor) -> torch.Tensor:
         """Signed coincidence counts ``[d_size, x_size]`` (int32) of one sample."""

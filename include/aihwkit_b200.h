@@ -266,6 +266,35 @@ int ab200_tile_update_host(ab200_tile *tile, const float *x_host, const float *d
 int ab200_tile_coincidences(ab200_tile *tile, const float *x_dev, const float *d_dev,
                             int32_t *counts_dev, void *stream);
 
+/* ---- indexed (im2col-free) convolution interface -------------------------------------------
+ * Replaces RPUSimple<T>::setMatrixIndices / hasMatrixIndices / forwardIndexed / backwardIndexed /
+ * updateIndexed (src/rpucuda/rpu.h:452-478, src/rpucuda/rpu.cpp:846-1013, 1117-1239) as bound by
+ * set_matrix_indices / forward_indexed / backward_indexed / update_indexed
+ * (src/aihwkit/simulator/rpu_base_src/rpu_base_tiles_cuda.cpp:399-522, rpu_base_tiles.cpp:700-760).
+ *
+ * `indices` holds x_size * m_batch int32 entries, [x_size][m_batch] when `trans` is non-zero (the
+ * layout AnalogConv2d builds, src/aihwkit/nn/modules/conv.py:534-571) or [m_batch][x_size]
+ * otherwise: 0 = zero padding, 1 = the constant 1.0 (analog bias), j >= 2 = element j - 2 of an
+ * image. It may be host or device memory and is copied (the reference borrows the pointer).
+ * Images: x is [dim3][total_size / dim3]; d is [dim3][d_size][m_batch] when `trans`, else
+ * [dim3][m_batch][d_size]. m_batch = output positions per image, dim3 = images per call (the
+ * binding passes the batch size N and trans = 1). backward_indexed overwrites x_dev with the
+ * scatter-added result (sums of at most kernel-size terms are accumulated with float atomics, so
+ * the last bit may depend on the execution order). Negative indices are rejected when the array is
+ * set; an index beyond the image size is rejected by every call. */
+int ab200_tile_set_matrix_indices(ab200_tile *tile, const int32_t *indices, long long count,
+                                  void *stream);
+int ab200_tile_has_matrix_indices(ab200_tile *tile);
+int ab200_tile_forward_indexed(ab200_tile *tile, const float *x_dev, float *d_dev,
+                               long long total_input_size, int m_batch, int dim3, int trans,
+                               int is_test, void *stream);
+int ab200_tile_backward_indexed(ab200_tile *tile, const float *d_dev, float *x_dev,
+                                long long total_output_size, int m_batch, int dim3, int trans,
+                                void *stream);
+int ab200_tile_update_indexed(ab200_tile *tile, const float *x_dev, const float *d_dev,
+                              long long total_input_size, int m_batch, int dim3, int trans,
+                              void *stream);
+
 /* Bound-management statistics of the last forward: number of samples that were re-run at least
  * once and the largest reduction factor used (rpu_forward_backward_pass.cpp:935-983). */
 int ab200_tile_last_bm_stats(ab200_tile *tile, int32_t *n_rerun_samples, float *max_reduction);

@@ -528,3 +528,81 @@ class TransferOracle:
             r = forward(self.a, e, self.t_io, rng, alpha=-1.0)
             update(self.c, e, r, float(t_lr), self.dw_min_slow, self.t_up, self.dev_slow, rng)
         self.slice_idx = (self.slice_idx + n) % self.x_size
+
+
+# ---------------------------------------------------------------------------------------------
+# Indexed (im2col-free) convolution interface
+# ---------------------------------------------------------------------------------------------
+def conv_indices(in_shape, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
+                 analog_bias: bool = False) -> np.ndarray:
+    """Index array of a 2-D convolution, as ``AnalogConv2d._calculate_indexes`` builds it
+    (src/aihwkit/nn/modules/conv.py:534-571): the unfold of ``arange(2, C*H*W + 2)`` with zero
+    padding, flattened ``[C*kh*kw][H_out*W_out]``; 0 marks padding, 1 (appended row) the constant
+    input of an analog bias.  ``in_shape`` = (C, H, W)."""
+    c, h, w = in_shape
+    kh, kw = kernel
+    ho = (h + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+    wo = (w + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+    idx = np.zeros((c * kh * kw, ho * wo), np.int32)
+    for ci in range(c):
+        for ki in range(kh):
+            for kj in range(kw):
+                r = (ci * kh + ki) * kw + kj
+                for oy in range(ho):
+                    y = oy * stride[0] - padding[0] + ki * dilation[0]
+                    if y < 0 or y >= h:
+                        continue
+                    xs = np.arange(wo) * stride[1] - padding[1] + kj * dilation[1]
+                    ok = (xs >= 0) & (xs < w)
+                    row = np.where(ok, 2 + ci * h * w + y * w + xs, 0)
+                    idx[r, oy * wo:(oy + 1) * wo] = row
+    flat = idx.reshape(-1)
+    if analog_bias:
+        flat = np.concatenate([flat, np.ones(ho * wo, np.int32)])
+    return flat
+
+
+def indexed_input(x: np.ndarray, indices: np.ndarray, size: int, m_batch: int, dim3: int,
+                  trans: bool) -> np.ndarray:
+    """``RPUSimple::copyIndexedInput`` (src/rpucuda/rpu.cpp:846-941, no batch slice), returned as
+    the sample-major matrix ``[dim3 * m_batch][size]``: sample ``n * m_batch + l`` is position
+    ``l`` of image ``n``.  The index array is ``[size][m_batch]`` if ``trans`` else
+    ``[m_batch][size]``; entries 0 and 1 give the constants 0.0 and 1.0, ``j >= 2`` reads element
+    ``j - 2`` of the image."""
+    x = np.asarray(x, np.float32).reshape(dim3, -1)
+    idx = np.asarray(indices, np.int64).reshape((size, m_batch) if trans else (m_batch, size))
+    if trans:
+        idx = idx.T  # [m_batch][size]
+    src = np.concatenate([np.zeros((dim3, 1), np.float32), np.ones((dim3, 1), np.float32), x], 1)
+    return src[:, idx].reshape(dim3 * m_batch, size)
+
+
+def indexed_output(x_cols: np.ndarray, indices: np.ndarray, size: int, m_batch: int, dim3: int,
+                   trans: bool, total_output_size: int) -> np.ndarray:
+    """``RPUSimple::copyIndexedOutput`` (src/rpucuda/rpu.cpp:943-1013): scatter-add of the
+    sample-major matrix ``[dim3 * m_batch][size]`` into zeroed images ``[dim3][total / dim3]``."""
+    idx = np.asarray(indices, np.int64).reshape((size, m_batch) if trans else (m_batch, size))
+    if trans:
+        idx = idx.T
+    out = np.zeros((dim3, total_output_size // dim3), np.float32)
+    cols = np.asarray(x_cols, np.float32).reshape(dim3, m_batch, size)
+    sel = idx > 1
+    for n in range(dim3):
+        np.add.at(out[n], idx[sel] - 2, cols[n][sel])
+    return out
+
+
+def to_sample_major(t: np.ndarray, size: int, m_batch: int, dim3: int, trans: bool) -> np.ndarray:
+    """Output-side tensor ``[dim3][size][m_batch]`` (``trans``) or ``[dim3][m_batch][size]`` as the
+    sample-major matrix ``[dim3 * m_batch][size]`` (the ``permute132`` of rpu.cpp:1136-1139)."""
+    t = np.asarray(t, np.float32)
+    if trans:
+        return t.reshape(dim3, size, m_batch).transpose(0, 2, 1).reshape(dim3 * m_batch, size)
+    return t.reshape(dim3 * m_batch, size)
+
+
+def from_sample_major(a: np.ndarray, size: int, m_batch: int, dim3: int, trans: bool) -> np.ndarray:
+    a = np.asarray(a, np.float32)
+    if trans:
+        return np.ascontiguousarray(a.reshape(dim3, m_batch, size).transpose(0, 2, 1))
+    return a.reshape(dim3, m_batch, size)

@@ -74,6 +74,10 @@ def load() -> C.CDLL:
         "ref_tile_backward": (i, [vp, fp, fp, i, i, i, i]),
         "ref_tile_update": (i, [vp, fp, fp, i, i, i, i]),
         "ref_tile_coincidences": (i, [vp, fp, fp, C.c_float, C.c_float, fp]),
+        "ref_tile_set_matrix_indices": (i, [vp, fp, C.c_longlong]),
+        "ref_tile_forward_indexed": (i, [vp, fp, fp, C.c_longlong, i, i, i, i]),
+        "ref_tile_backward_indexed": (i, [vp, fp, fp, C.c_longlong, i, i, i]),
+        "ref_tile_update_indexed": (i, [vp, fp, fp, C.c_longlong, i, i, i]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -182,3 +186,43 @@ class RefTile:
             )
         )
         return out
+
+    # indexed convolution interface (src/rpucuda/rpu.cpp:1117-1239); images are [N, C, H, W]
+    # (`trans=True`, the layout the Python binding always uses) or [N, H*W, C] (`trans=False`)
+    def set_matrix_indices(self, indices) -> None:
+        idx = np.ascontiguousarray(indices, dtype=np.int32)
+        self._ck(self._lib.ref_tile_set_matrix_indices(self._h, idx.ctypes.data, idx.size))
+
+    def forward_indexed(self, x, d_shape, trans=True, is_test=False) -> np.ndarray:
+        x = _f32(x)
+        out = np.zeros(d_shape, np.float32)
+        n = x.shape[0]
+        m_batch = out.size // (n * self.d_size)
+        self._ck(
+            self._lib.ref_tile_forward_indexed(
+                self._h, x.ctypes.data, out.ctypes.data, x.size, m_batch, n, int(trans), int(is_test)
+            )
+        )
+        return out
+
+    def backward_indexed(self, d, x_shape, trans=True) -> np.ndarray:
+        d = _f32(d)
+        out = np.zeros(x_shape, np.float32)
+        n = d.shape[0]
+        m_batch = d.size // (n * self.d_size)
+        self._ck(
+            self._lib.ref_tile_backward_indexed(
+                self._h, d.ctypes.data, out.ctypes.data, out.size, m_batch, n, int(trans)
+            )
+        )
+        return out
+
+    def update_indexed(self, x, d, trans=True) -> None:
+        x, d = _f32(x), _f32(d)
+        n = d.shape[0]
+        m_batch = d.size // (n * self.d_size)
+        self._ck(
+            self._lib.ref_tile_update_indexed(
+                self._h, x.ctypes.data, d.ctypes.data, x.size, m_batch, n, int(trans)
+            )
+        )

@@ -127,6 +127,7 @@ struct RefTile {
   PulsedUpdateMetaParameter<float> up;
   std::unique_ptr<DenseBitLineMaker<float>> dblm;
   std::unique_ptr<RNG<float>> rng;
+  std::vector<int> indices; // the reference borrows the index array; the wrapper keeps it alive
 };
 } // namespace
 
@@ -295,6 +296,40 @@ int ref_tile_coincidences(void *h, const float *x, const float *d, float lr, flo
   int xnoz = 0, dnoz = 0;
   int *c = t->dblm->makeCoincidences(x, 1, xnoz, d, 1, dnoz, t->rng.get(), lr, dw_min, t->up);
   std::memcpy(counts, c, sizeof(int) * (size_t)xs * ds);
+  REF_CATCH
+}
+
+/* Indexed (im2col-free) convolution interface, RPUSimple<T>::setMatrixIndices / forwardIndexed /
+   backwardIndexed / updateIndexed (src/rpucuda/rpu.h:452-478, src/rpucuda/rpu.cpp:1117-1239). */
+int ref_tile_set_matrix_indices(void *h, const int *indices, long long n) {
+  REF_TRY
+  auto *t = static_cast<RefTile *>(h);
+  t->indices.assign(indices, indices + n);
+  t->rpu->setMatrixIndices(t->indices.data());
+  REF_CATCH
+}
+
+int ref_tile_forward_indexed(void *h, const float *x, float *d, long long total_input_size,
+                             int m_batch, int dim3, int trans, int is_test) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->forwardIndexed(x, d, (int)total_input_size, m_batch, dim3,
+                                                 trans != 0, is_test != 0);
+  REF_CATCH
+}
+
+int ref_tile_backward_indexed(void *h, const float *d, float *x, long long total_output_size,
+                              int m_batch, int dim3, int trans) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->backwardIndexed(d, x, (int)total_output_size, m_batch, dim3,
+                                                  trans != 0);
+  REF_CATCH
+}
+
+int ref_tile_update_indexed(void *h, const float *x, const float *d, long long total_input_size,
+                            int m_batch, int dim3, int trans) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->updateIndexed(x, d, (int)total_input_size, m_batch, dim3,
+                                                trans != 0);
   REF_CATCH
 }
 

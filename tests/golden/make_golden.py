@@ -1,6 +1,7 @@
 """Generate the golden vectors of tests/golden/*.npz from the COMPILED REFERENCE (oracle/_ref).
 
-    make -C oracle && python tests/golden/make_golden.py
+    make -C oracle && python tests/golden/make_golden.py            # everything
+    make -C oracle && python tests/golden/make_golden.py indexed    # only indexed_conv.npz
 
 Every array is an input or an output of the unmodified reference CPU tile
 (RPU::RPUPulsed<float>) for the configurations built by tests/helpers.py; nothing here comes from
@@ -124,7 +125,51 @@ def transfer_case(seed):
                 lr=np.float32(lr))
 
 
+def indexed_conv_case(seed):
+    """Indexed convolution interface in the layout the Python binding uses (trans): a padded,
+    strided 3x3 convolution with an analog bias row.  The index array is built here with plain
+    loops (0 = padding, 1 = bias constant, j >= 2 = element j - 2 of the image)."""
+    rng = np.random.default_rng(seed)
+    n, c, h, w, c_out = 4, 5, 9, 8, 12
+    kh = kw = 3
+    stride, pad = (2, 1), (1, 1)
+    ho = (h + 2 * pad[0] - kh) // stride[0] + 1
+    wo = (w + 2 * pad[1] - kw) // stride[1] + 1
+    x_size = c * kh * kw + 1
+    idx = np.zeros((x_size, ho * wo), np.int32)
+    for ci in range(c):
+        for ki in range(kh):
+            for kj in range(kw):
+                for oy in range(ho):
+                    for ox in range(wo):
+                        y, xx = oy * stride[0] - pad[0] + ki, ox * stride[1] - pad[1] + kj
+                        if 0 <= y < h and 0 <= xx < w:
+                            idx[(ci * kh + ki) * kw + kj, oy * wo + ox] = 2 + (ci * h + y) * w + xx
+    idx[-1] = 1
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+    dp = H.device("sb", False)
+    cfg = p._config(x_size, c_out, dp, seed=seed)
+    t = ref.RefTile(cfg)
+    t.set_weights(rng.uniform(-0.5, 0.5, (c_out, x_size)).astype(np.float32))
+    t.set_matrix_indices(idx)
+    w0 = t.get_weights()
+    x = rng.uniform(-1, 1, (n, c, h, w)).astype(np.float32)
+    d = rng.normal(0, 0.1, (n, c_out, ho, wo)).astype(np.float32)
+    y = t.forward_indexed(x, d.shape)
+    g = t.backward_indexed(d, x.shape)
+    lr = 0.01
+    t.set_learning_rate(lr)
+    hp = t.get_hidden_parameters()
+    t.update_indexed(x, d)
+    return dict(w0=w0, indices=idx.reshape(-1), x=x, d=d, y=y, g=g, hidden=hp, w1=t.get_weights(),
+                lr=np.float32(lr), out_bound=np.float32(2.0))
+
+
 def main():
+    if sys.argv[1:] == ["indexed"]:
+        np.savez_compressed(os.path.join(HERE, "indexed_conv.npz"), **indexed_conv_case(9))
+        print("wrote indexed_conv.npz")
+        return
     out = {}
     for kind in ("cs", "ls", "sb", "sbr"):
         for (x, d, m, ob) in ((40, 24, 9, 12.0), (70, 33, 6, 2.0)):
@@ -136,6 +181,7 @@ def main():
     for kind in ("cs", "sbr"):
         np.savez_compressed(os.path.join(HERE, f"noisy_update_{kind}.npz"), **noisy_update_case(kind, 7))
     np.savez_compressed(os.path.join(HERE, "transfer_det.npz"), **transfer_case(8))
+    np.savez_compressed(os.path.join(HERE, "indexed_conv.npz"), **indexed_conv_case(9))
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 

@@ -135,3 +135,27 @@ def test_transfer_sequence():
         assert np.abs(orc.a - g["a"][k]).max() <= 1e-7, k
         assert np.abs(orc.c - g["ws"][k]).max() <= 1e-7, k
     assert np.abs(g["ws"][-1]).max() > 0
+
+
+def test_indexed_conv_fixture():
+    """The numpy restatement of the indexed interface against the vectors of the compiled
+    reference (tests/golden/indexed_conv.npz)."""
+    g = np.load(os.path.join(GOLD, "indexed_conv.npz"))
+    n, c, h, w = g["x"].shape
+    c_out, x_size = g["w0"].shape
+    m_batch = g["indices"].size // x_size
+    assert np.array_equal(g["indices"], O.conv_indices((c, h, w), (3, 3), (2, 1), (1, 1), (1, 1), True))
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=float(g["out_bound"]))
+    dp = H.device("sb", False)
+    cfg = p._config(x_size, c_out, dp, seed=1)
+    cols = O.indexed_input(g["x"], g["indices"], x_size, m_batch, n, True)
+    y = O.forward(g["w0"], cols, O.IO.from_c(cfg.forward_io))
+    assert np.array_equal(O.from_sample_major(y, c_out, m_batch, n, True).reshape(g["y"].shape), g["y"])
+    d_cols = O.to_sample_major(g["d"], c_out, m_batch, n, True)
+    xg = O.backward(g["w0"], d_cols, O.IO.from_c(cfg.backward_io, backward=True))
+    xo = O.indexed_output(xg, g["indices"], x_size, m_batch, n, True, g["x"].size)
+    assert np.abs(xo.reshape(g["g"].shape) - g["g"]).max() <= 1e-5
+    w1 = g["w0"].copy()
+    dev = O.DeviceArrays.from_hidden(O.DEV_SOFT_BOUNDS, names_for("sb"), g["hidden"], 0.0, True)
+    O.update(w1, cols, d_cols, float(g["lr"]), dp.dw_min, O.Up.from_c(cfg.update), dev)
+    assert np.abs(w1 - g["w1"]).max() <= 1e-7

@@ -85,3 +85,46 @@ def test_noisy_stochastic_update_moments():
         do.append(wo - w0)
     dr, do = np.stack(dr), np.stack(do)
     H.assert_moments_agree(do, dr)
+
+
+@pytest.mark.parametrize("trans", [True, False])
+@pytest.mark.parametrize("analog_bias", [False, True])
+def test_indexed_interface(trans, analog_bias):
+    """forward/backward/update through the index array of a padded, strided 3x3 convolution."""
+    rng = np.random.default_rng(4)
+    n, c, h, w, c_out = 3, 4, 7, 6, 5
+    idx_t = O.conv_indices((c, h, w), (3, 3), (2, 1), (1, 1), (1, 1), analog_bias)
+    x_size = c * 9 + (1 if analog_bias else 0)
+    m_batch = idx_t.size // x_size
+    idx = idx_t if trans else np.ascontiguousarray(idx_t.reshape(x_size, m_batch).T).reshape(-1)
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+    dp = H.device("sb", False)
+    cfg = p._config(x_size, c_out, dp, seed=3)
+    t = ref.RefTile(cfg)
+    t.set_weights(rng.uniform(-0.5, 0.5, (c_out, x_size)).astype(np.float32))
+    t.set_matrix_indices(idx)
+    W = t.get_weights()
+    # image layout: [N][C*H*W]; the gather only sees flat images
+    X = rng.uniform(-1, 1, (n, c, h, w)).astype(np.float32)
+    d_shape = (n, c_out, m_batch) if trans else (n, m_batch, c_out)
+    Dm = rng.normal(0, 0.1, d_shape).astype(np.float32)
+
+    cols = O.indexed_input(X, idx, x_size, m_batch, n, trans)
+    y = O.forward(W, cols, O.IO.from_c(cfg.forward_io))
+    assert np.array_equal(t.forward_indexed(X, d_shape, trans),
+                          O.from_sample_major(y, c_out, m_batch, n, trans).reshape(d_shape))
+
+    d_cols = O.to_sample_major(Dm, c_out, m_batch, n, trans)
+    xg = O.backward(W, d_cols, O.IO.from_c(cfg.backward_io, backward=True))
+    xo = O.indexed_output(xg, idx, x_size, m_batch, n, trans, X.size)
+    got = t.backward_indexed(Dm, X.shape, trans).reshape(n, -1)
+    assert np.abs(got - xo).max() <= 1e-5 * max(1.0, np.abs(xo).max())
+
+    lr = 0.01
+    t.set_learning_rate(lr)
+    dev = O.DeviceArrays.from_hidden(KIND["sb"], t.hidden_parameter_names(),
+                                     t.get_hidden_parameters(), 0.0, True)
+    t.update_indexed(X, Dm, trans)
+    Wo = W.copy()
+    O.update(Wo, cols, d_cols, lr, dp.dw_min, O.Up.from_c(cfg.update), dev)
+    assert np.abs(t.get_weights() - Wo).max() <= 1e-7
