@@ -8,7 +8,10 @@ Configurations (seeded synthetic inputs with the stated shapes and distributions
   2  Tiki-Taka: 1024 x 1024 TransferCompound of two SoftBoundsReference devices, batch 256,
      transfer every 2 batches, one column per transfer
   3  convolution-shaped tile 256 x 2304 (3x3x256), 131072 input columns per step, SoftBounds device
-     (the activations are fed as an already unfolded [columns, 2304] matrix)
+     (default: the activations are fed as an already unfolded [columns, 2304] matrix; with
+     --indexed the step goes through forward_indexed / backward_indexed / update_indexed on
+     [128, 256, 32, 32] images and the index array of a padded 3x3 convolution, as a convolution
+     layer calls the tile)
 
 Prints one JSON line: columns/s for the whole step and per phase, and for the update kernel the
 achieved HBM bandwidth on its algorithmic bytes `x*d*(8+P) + 4*m*(x+d)` against the measured copy
@@ -88,6 +91,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=0, help="override the batch size")
     ap.add_argument("--cpu-baseline", action="store_true")
+    ap.add_argument("--indexed", action="store_true", help="config 3 through the indexed interface")
     args = ap.parse_args()
 
     import torch
@@ -111,25 +115,44 @@ def main():
         x = torch.relu(torch.randn(m, x_size, generator=g))
     d = torch.randn(m, d_size, generator=g) * w["dstd"]
     x, d = x.cuda(), d.cuda()
+    fwd = lambda: tile.forward(x, non_blocking=True)  # noqa: E731
+    bwd = lambda: tile.backward(d, non_blocking=True)  # noqa: E731
+    upd = lambda: tile.update(x, d, non_blocking=True)  # noqa: E731
+    if args.indexed:
+        if args.config != 3:
+            raise SystemExit("--indexed applies to config 3")
+        c, hw = 256, 32
+        n_img = m // (hw * hw)
+        m = n_img * hw * hw
+        img = torch.relu(torch.randn(n_img, c, hw, hw, generator=g)).cuda()
+        err = (torch.randn(n_img, d_size, hw, hw, generator=g) * w["dstd"]).cuda()
+        idx = torch.nn.functional.unfold(
+            torch.arange(2, c * hw * hw + 2, dtype=torch.float64).reshape(1, c, hw, hw),
+            kernel_size=3, padding=1).flatten().round().to(torch.int32).cuda()
+        tile.set_matrix_indices(idx)
+        y_img, g_img = torch.empty_like(err), torch.empty_like(img)
+        fwd = lambda: tile.forward_indexed(img, y_img, non_blocking=True)  # noqa: E731
+        bwd = lambda: tile.backward_indexed(err, g_img, non_blocking=True)  # noqa: E731
+        upd = lambda: tile.update_indexed(img, err, non_blocking=True)  # noqa: E731
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
 
     for _ in range(args.warmup):
-        tile.forward(x, non_blocking=True)
-        tile.backward(d, non_blocking=True)
-        tile.update(x, d, non_blocking=True)
+        fwd()
+        bwd()
+        upd()
     torch.cuda.synchronize()
     t_f = t_b = t_u = 0.0
     e = [ev() for _ in range(4)]
     t0 = time.perf_counter()
     for _ in range(args.steps):
         e[0].record()
-        tile.forward(x, non_blocking=True)
+        fwd()
         e[1].record()
-        tile.backward(d, non_blocking=True)
+        bwd()
         e[2].record()
-        tile.update(x, d, non_blocking=True)
+        upd()
         e[3].record()
         torch.cuda.synchronize()
         t_f += e[0].elapsed_time(e[1])
@@ -144,7 +167,7 @@ def main():
     flops = 2.0 * m * x_size * d_size
     line = {
         "metric": "analog_tile_fwd_bwd_update_columns_per_s",
-        "config": args.config, "x_size": x_size, "d_size": d_size, "batch": m,
+        "config": args.config, "indexed": bool(args.indexed), "x_size": x_size, "d_size": d_size, "batch": m,
         "value": m / (step_ms * 1e-3), "unit": "columns/s",
         "ms": {"forward": t_f, "backward": t_b, "update": t_u, "step": step_ms,
                "wall_per_step": 1e3 * wall / k},
