@@ -173,7 +173,7 @@ bool TileArray::tcEligible(int m) {
   if (!TcEngine::ioSupported(io) || io.bm != AB200_BM_NONE) {
     return false;
   }
-  return mode == 2 || m >= 128;
+  return mode >= 2 || m >= 128;
 }
 
 // All local tiles in one launch: the DAC kernel quantises every (row, in-split) once, the MMA

@@ -377,8 +377,8 @@ int ab200_array_set_seed(ab200_array *arr, uint64_t seed) {
 
 int ab200_set_mvm_path(int mode) {
   AB200_TRY
-  if (mode < 0 || mode > 2) {
-    AB200_FATAL("mvm path mode must be 0, 1 or 2");
+  if (mode < 0 || mode > 3) {
+    AB200_FATAL("mvm path mode must be 0, 1, 2 or 3");
   }
   ab200::setMvmPath(mode);
   AB200_CATCH

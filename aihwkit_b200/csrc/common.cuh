@@ -54,14 +54,10 @@ philox4x32(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, PhiloxKey key, ui
   uint32_t k0 = key.k0, k1 = key.k1;
 #pragma unroll
   for (int r = 0; r < ROUNDS; r++) {
-#ifdef __CUDA_ARCH__
-    uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
-    uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
-#else
+    // one widening multiply per S-box gives both halves of the product
     uint64_t p0 = (uint64_t)M0 * c0, p1 = (uint64_t)M1 * c2;
     uint32_t hi0 = (uint32_t)(p0 >> 32), lo0 = (uint32_t)p0;
     uint32_t hi1 = (uint32_t)(p1 >> 32), lo1 = (uint32_t)p1;
-#endif
     uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
     c0 = n0;
     c1 = lo1;
@@ -118,11 +114,11 @@ __device__ __forceinline__ void boxMuller(uint32_t a, uint32_t b, float &z0, flo
 // per output element and in-split and the generator is the largest cost of the epilogue.
 __device__ __forceinline__ void boxMuller1(uint32_t a, float &z0, float &z1) {
   float u1 = 2.0f - __uint_as_float(0x3f800000u | ((a >> 12) << 3));
-  float u2 = __uint_as_float(0x3f800000u | ((a & 0xFFFu) << 11)) - 1.0f;
+  float f2 = __uint_as_float(0x3f800000u | ((a & 0xFFFu) << 11)); // 1 + u2
   float r2 = -1.3862943611198906f * __log2f(u1); // -2 ln(u1)
   float r;
   asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(r2));
-  float ang = 6.283185307179586f * u2;
+  float ang = fmaf(6.283185307179586f, f2, -6.283185307179586f); // 2 pi u2
   z0 = r * __cosf(ang);
   z1 = r * __sinf(ang);
 }

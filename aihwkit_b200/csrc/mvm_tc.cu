@@ -49,6 +49,11 @@ constexpr int TC_WARP_TMA = TC_EPI_WARPS;
 constexpr int TC_WARP_MMA = TC_EPI_WARPS + 1;
 constexpr int TC_THREADS = (TC_EPI_WARPS + 2) * 32;
 constexpr unsigned long long TC_WAIT_CYCLES = 4000000000ull; // about 2 s at 2 GHz
+// CTA-pair variant (cta_group::2): every CTA of a pair stages its own 128 rows of codes and ONE
+// half of the stacked weight tile (rank 0 the hi rows, rank 1 the lo rows), so a stage is 32 KB
+constexpr int TC2_STAGES = 6;
+constexpr int TC2_STAGE_BYTES = TC_STAGE_A + TC_STAGE_B;
+constexpr int TC2_SMEM_BYTES = TC2_STAGES * TC2_STAGE_BYTES + 2048;
 
 enum : int {
   TC_ERR_FULL = 1,
@@ -126,6 +131,52 @@ __device__ __forceinline__ void tmaLoad2d(void *dst, const CUtensorMap *map, uin
   asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes"
                " [%0], [%1, {%3, %4}], [%2];" ::"r"(smemAddr(dst)),
                "l"((uint64_t)map), "r"(smemAddr(bar)), "r"(x), "r"(y)
+               : "memory");
+}
+// ---- CTA pairs ----
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapaShared(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void clusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\t"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbarArriveCluster(uint32_t cluster_addr) {
+  // default semantics (release at CTA scope): the TMEM reads this arrive publishes were completed
+  // by tcgen05.wait::ld and fenced; a cluster-scope release would also wait for the warp's
+  // outstanding global stores
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// the copy lands in this CTA's shared memory; its bytes are counted on the barrier of the pair's
+// leader (cluster address), which the MMA-issuing thread waits on for both CTAs' tiles
+__device__ __forceinline__ void tmaLoad2dPair(void *dst, const CUtensorMap *map,
+                                              uint32_t leader_bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+               " [%0], [%1, {%3, %4}], [%2];" ::"r"(smemAddr(dst)),
+               "l"((uint64_t)map), "r"(leader_bar), "r"(x), "r"(y)
+               : "memory");
+}
+// arrive on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void tcCommitPair(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+               " [%0], %1;" ::"r"(smemAddr(bar)),
+               "h"((uint16_t)3)
+               : "memory");
+}
+__device__ __forceinline__ void tcMmaPair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
                : "memory");
 }
 __device__ __forceinline__ void tcFenceBefore() {
@@ -210,6 +261,10 @@ __device__ __forceinline__ uint64_t smemDesc(uint32_t saddr) {
 // stacked hi and lo rows of the weight tile).
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) |
                             ((uint32_t)(TC_ACC_COLS >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+// the same for a CTA pair: M = 256, 128 rows in each CTA
+constexpr uint32_t kIdescPair = (1u << 4) | (1u << 7) | (1u << 10) |
+                                ((uint32_t)(TC_ACC_COLS >> 3) << 17) |
+                                ((uint32_t)((2 * TC_M) >> 4) << 24);
 
 #define TC_TIMED_WAIT(acc, expr)                                                                   \
   ([&]() {                                                                                         \
@@ -222,28 +277,40 @@ constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) |
 // ---------------------------------------------------------------------------------------------
 // the MVM kernel
 // ---------------------------------------------------------------------------------------------
-template <bool BM>
+// PAIR = false: one CTA per work item (128 rows x one 128-column chunk).
+// PAIR = true:  a cluster of two CTAs per work item of 256 rows; the MMAs are issued by the thread
+//               of rank 0 for both CTAs (cta_group::2, M 256): each CTA's tensor core reads its own
+//               128 rows of codes and half of the stacked weight tile from its own shared memory,
+//               so the shared-memory traffic per SM and per FLOP drops by a third. Each CTA keeps
+//               the accumulator rows of its own 128 rows in its own TMEM and runs its own epilogue.
+template <bool BM, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     mvmTcKernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_bhi,
                 const __grid_constant__ CUtensorMap tm_blo, const TcKernelParams p) {
+  constexpr int STAGES = PAIR ? TC2_STAGES : TC_STAGES;
+  constexpr int STAGE_BYTES = PAIR ? TC2_STAGE_BYTES : TC_STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t *bars = (uint64_t *)(smem + TC_STAGES * TC_STAGE_BYTES);
-  uint64_t *full = bars;                       // [TC_STAGES] operands landed in shared memory
-  uint64_t *empty = bars + TC_STAGES;          // [TC_STAGES] MMAs have read the stage
-  uint64_t *tmem_full = bars + 2 * TC_STAGES;  // [2]         accumulator complete
-  uint64_t *tmem_empty = tmem_full + 2;        // [2]         accumulator drained
+  uint64_t *bars = (uint64_t *)(smem + STAGES * STAGE_BYTES);
+  uint64_t *full = bars;                    // [STAGES] operands landed in shared memory
+  uint64_t *empty = bars + STAGES;          // [STAGES] MMAs have read the stage
+  uint64_t *tmem_full = bars + 2 * STAGES;  // [2]      accumulator complete
+  uint64_t *tmem_empty = tmem_full + 2;     // [2]      accumulator drained
   uint32_t *tmem_slot = (uint32_t *)(tmem_empty + 2);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // persistent CTA: work item w = (row block, 128-column chunk). Items are ordered so that a
-  // group of `p.group` chunks is finished for every row block before the next group starts: the
+  const int rank = PAIR ? (int)clusterCtaRank() : 0; // rank 0 of a pair issues the MMAs
+  // persistent CTA (pair): work item w = (row block, 128-column chunk). Items are ordered so that
+  // a group of `p.group` chunks is finished for every row block before the next group starts: the
   // group's weight operand (p.group * I * 256 KB) stays in L2 while the codes stream past once
   // per group.
-  const int n_rb = (p.m + TC_M - 1) / TC_M;
+  constexpr int ROWS = PAIR ? 2 * TC_M : TC_M; // rows per work item
+  const int n_rb = (p.m + ROWS - 1) / ROWS;
   const int n_items = p.n_chunks * n_rb;
+  const int worker = PAIR ? (int)blockIdx.x / 2 : (int)blockIdx.x;
+  const int n_workers = PAIR ? (int)gridDim.x / 2 : (int)gridDim.x;
   auto item = [&](int w, int &chunk_idx, int &rb) {
     const int per_group = p.group * n_rb;
     const int g = w / per_group, rem = w - g * per_group;
@@ -253,27 +320,41 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   };
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < TC_STAGES; s++) {
+    for (int s = 0; s < STAGES; s++) {
       mbarInit(&full[s], 1);
       mbarInit(&empty[s], 1);
     }
     for (int b = 0; b < 2; b++) {
       mbarInit(&tmem_full[b], 1);
-      mbarInit(&tmem_empty[b], TC_EPI_WARPS);
+      // the issuer waits for the epilogue warps of every CTA it computes for
+      mbarInit(&tmem_empty[b], PAIR ? 2 * TC_EPI_WARPS : TC_EPI_WARPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == TC_WARP_MMA) {
-    // TMEM: all 512 columns = two accumulators of 128 lanes x (128 hi + 128 lo) fp32 columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smemAddr(tmem_slot)),
-                 "r"(512)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    // TMEM: all 512 columns = two accumulators of 128 lanes x (128 hi + 128 lo) fp32 columns.
+    // For a pair the same warp of both CTAs allocates together, at the same shared-memory slot.
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smemAddr(tmem_slot)),
+                   "r"(512)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smemAddr(tmem_slot)),
+                   "r"(512)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tcFenceBefore();
   __syncthreads();
+  if (PAIR) {
+    __syncwarp();
+    clusterSync(); // the peer's barriers are initialised before anything arrives on them
+  }
   tcFenceAfter();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -283,28 +364,47 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       int it = 0;
       bool ok = true;
       long long w_empty = 0;
-      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+      for (int w = worker; w < n_items && ok; w += n_workers) {
       int chunk_idx, rb;
       item(w, chunk_idx, rb);
-      const int r0 = rb * TC_M;
+      const int r0 = rb * ROWS + rank * TC_M;
       for (int i = 0; i < p.I && ok; i++) {
         const int4 is = p.insplit[i];
         const int brow = i * p.nrows_pad + chunk_idx * TC_N;
         for (int kc = 0; kc < is.y; kc++, it++) {
-          const int s = it % TC_STAGES;
-          if (!TC_TIMED_WAIT(w_empty, mbarWait(&empty[s], ((it / TC_STAGES) & 1) ^ 1, abort_flag))) {
+          const int s = it % STAGES;
+          if (!TC_TIMED_WAIT(w_empty, mbarWait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag))) {
             atomicCAS(p.status, 0, TC_ERR_EMPTY);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          uint8_t *st = smem + s * TC_STAGE_BYTES;
-          mbarExpectTx(&full[s], TC_STAGE_BYTES);
-          tmaLoad2d(st, &tm_a, &full[s], is.x + kc * TC_K, r0);
-          tmaLoad2d(st + TC_STAGE_A, &tm_bhi, &full[s], kc * TC_K, brow);
-          tmaLoad2d(st + TC_STAGE_A + TC_STAGE_B, &tm_blo, &full[s], kc * TC_K, brow);
+          uint8_t *st = smem + s * STAGE_BYTES;
+          if (PAIR) {
+            // rank 0 announces the bytes of both CTAs on its barrier; both CTAs' copies count there
+            const uint32_t leader_bar = mapaShared(smemAddr(&full[s]), 0);
+            if (rank == 0) {
+              mbarExpectTx(&full[s], 2 * STAGE_BYTES);
+            }
+            tmaLoad2dPair(st, &tm_a, leader_bar, is.x + kc * TC_K, r0);
+            tmaLoad2dPair(st + TC_STAGE_A, rank == 0 ? &tm_bhi : &tm_blo, leader_bar, kc * TC_K, brow);
+          } else {
+            mbarExpectTx(&full[s], STAGE_BYTES);
+            tmaLoad2d(st, &tm_a, &full[s], is.x + kc * TC_K, r0);
+            tmaLoad2d(st + TC_STAGE_A, &tm_bhi, &full[s], kc * TC_K, brow);
+            tmaLoad2d(st + TC_STAGE_A + TC_STAGE_B, &tm_blo, &full[s], kc * TC_K, brow);
+          }
         }
       }
+      }
+      if (PAIR && ok) {
+        // drain: the completions of the last MMAs arrive on this CTA's barriers from the thread
+        // of rank 0 and must not find the CTA gone
+        for (int k = it; k < it + STAGES; k++) {
+          if (k >= STAGES && !mbarWait(&empty[k % STAGES], ((k / STAGES) & 1) ^ 1, abort_flag)) {
+            break;
+          }
+        }
       }
       if (p.prof) {
         p.prof[blockIdx.x * 8 + 4] = w_empty;
@@ -312,12 +412,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
   } else if (warp == TC_WARP_MMA) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       int it = 0, ai = 0; // pipeline stage counter, accumulator-buffer use counter
       bool ok = true;
       long long w_full = 0, w_tmem = 0;
       const long long t_start = clock64();
-      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+      for (int w = worker; w < n_items && ok; w += n_workers) {
       for (int i = 0; i < p.I && ok; i++, ai++) {
         const int nk = p.insplit[i].y;
         const int b = ai & 1;
@@ -330,26 +430,41 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         tcFenceAfter();
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * TC_ACC_COLS);
         for (int kc = 0; kc < nk; kc++, it++) {
-          const int s = it % TC_STAGES;
-          if (!TC_TIMED_WAIT(w_full, mbarWait(&full[s], (it / TC_STAGES) & 1, abort_flag))) {
+          const int s = it % STAGES;
+          if (!TC_TIMED_WAIT(w_full, mbarWait(&full[s], (it / STAGES) & 1, abort_flag))) {
             atomicCAS(p.status, 0, TC_ERR_FULL);
             *abort_flag = 1;
             ok = false;
             break;
           }
           tcFenceAfter();
-          const uint32_t a0 = smemAddr(smem + s * TC_STAGE_BYTES);
-          // the B descriptor starts at the hi tile; its 256 rows run on into the lo tile
+          const uint32_t a0 = smemAddr(smem + s * STAGE_BYTES);
+          // single CTA: the B descriptor starts at the hi tile and its 256 rows run on into the
+          // lo tile. Pair: each CTA supplies 128 of the 256 B rows from the same offset.
           const uint64_t da = smemDesc(a0), db = smemDesc(a0 + TC_STAGE_A);
 #pragma unroll
           for (int k = 0; k < TC_K / 16; k++) {
             // +2 in the 16-byte-unit address field = 32 bytes = 16 bf16 along K
-            tcMma(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kc > 0 || k > 0) ? 1u : 0u);
+            if (PAIR) {
+              tcMmaPair(d_tmem, da + 2 * k, db + 2 * k, kIdescPair, (kc > 0 || k > 0) ? 1u : 0u);
+            } else {
+              tcMma(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kc > 0 || k > 0) ? 1u : 0u);
+            }
           }
-          tcCommit(&empty[s]); // frees the stage when these MMAs have read it
+          // frees the stage (in both CTAs of a pair) when these MMAs have read it
+          if (PAIR) {
+            tcCommitPair(&empty[s]);
+          } else {
+            tcCommit(&empty[s]);
+          }
         }
         if (ok) {
-          tcCommit(&tmem_full[b]); // accumulator of in-split i is complete
+          // accumulator of in-split i is complete
+          if (PAIR) {
+            tcCommitPair(&tmem_full[b]);
+          } else {
+            tcCommit(&tmem_full[b]);
+          }
         }
       }
       }
@@ -368,20 +483,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const bool adc = io.res_out > 0.0f;
     const float inv_res_out = adc ? 1.0f / io.res_out : 0.0f;
     const float kMagic = 12582912.0f; // 1.5 * 2^23: adding and subtracting rounds to nearest even
+    const float in_codes = io.res_in * inv_res_out, bound_codes = io.out_bound * inv_res_out;
     bool ok = true;
     int ai = 0; // accumulator-buffer use counter, in step with the MMA issuer
     long long w_tfull = 0;
     const long long t_epi = clock64();
-    for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+    for (int w = worker; w < n_items && ok; w += n_workers) {
     int chunk_idx, rb;
     item(w, chunk_idx, rb);
     const int4 ch = p.chunk[chunk_idx];
-    const int row = rb * TC_M + q * 32 + lane;
+    const int row = rb * ROWS + rank * TC_M + q * 32 + lane;
     const bool row_ok = row < p.m;
-    const uint64_t n4h = (uint64_t)((p.outn[ch.x] + 7) >> 3); // noise block pairs per row
-    const bool vec = ((p.out_ss & 3) == 0) && ((ch.z & 3) == 0) &&
-                     ((((uintptr_t)p.out) & 15) == 0) && !p.accumulate;
-    float *orow = p.out + (long long)row * p.out_ss + ch.z + cbase;
+    const uint32_t n4h = (uint32_t)((p.outn[ch.x] + 7) >> 3); // noise block pairs per row
     bool exceeded = false;
     float sum[TC_EPI_COLS]; // running sums over the in-splits
 #pragma unroll
@@ -417,12 +530,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       const uint32_t taddr =
           tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_ACC_COLS + cbase);
       const bool live = row_ok && sc != 0.0f;
+      const float sig_codes = sigma * inv_res_out, fac_codes = fac * io.res_out;
 #pragma unroll
       for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 8) {
         uint32_t vh[8], vl[8];
         tcLd8(taddr + (uint32_t)c0, vh);          // codes x hi
         tcLd8(taddr + (uint32_t)(TC_N + c0), vl); // codes x lo
         tcWaitLd();
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          acc[j] = __fadd_rn(__uint_as_float(vh[j]), __uint_as_float(vl[j]));
+        }
         if (live) {
           if (sigma > 0.0f) {
             // noisy regime: the Gaussian decides the ADC code, so the divisions of the exact
@@ -438,17 +557,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
               if (cl < ch.w) {
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                  const float acc = __uint_as_float(vh[4 * g + j]) + __uint_as_float(vl[4 * g + j]);
-                  float y = fmaf(acc, io.res_in, sigma * z[4 * g + j]);
                   if (adc) {
-                    y = (fmaf(y, inv_res_out, kMagic) - kMagic) * io.res_out;
+                    // in units of the ADC step: round, clip and rescale with one multiply each
+                    float r = fmaf(z[4 * g + j], sig_codes, acc[4 * g + j] * in_codes);
+                    r = (r + kMagic) - kMagic;
+                    if (BM) {
+                      exceeded = exceeded || (r > bound_codes) ||
+                                 (io.bm_test_negative_bound && r < -bound_codes);
+                    }
+                    r = fminf(fmaxf(r, -bound_codes), bound_codes);
+                    sum[c0 + 4 * g + j] = fmaf(r, fac_codes, sum[c0 + 4 * g + j]);
+                  } else {
+                    float y = fmaf(acc[4 * g + j], io.res_in, sigma * z[4 * g + j]);
+                    if (BM) {
+                      exceeded = exceeded || (y > io.out_bound) ||
+                                 (io.bm_test_negative_bound && y < -io.out_bound);
+                    }
+                    y = fminf(fmaxf(y, -io.out_bound), io.out_bound);
+                    sum[c0 + 4 * g + j] = fmaf(y, fac, sum[c0 + 4 * g + j]);
                   }
-                  if (BM) {
-                    exceeded = exceeded || (y > io.out_bound) ||
-                               (io.bm_test_negative_bound && y < -io.out_bound);
-                  }
-                  y = fminf(fmaxf(y, -io.out_bound), io.out_bound);
-                  sum[c0 + 4 * g + j] = fmaf(y, fac, sum[c0 + 4 * g + j]);
                 }
               }
             }
@@ -461,8 +588,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 for (int j = 0; j < 4; j++) {
                   // the MMA summed integer codes times weights; one multiply by the DAC step
                   // gives sum(v * w)
-                  const float acc = __fadd_rn(__uint_as_float(vh[4 * g + j]), __uint_as_float(vl[4 * g + j]));
-                  float y = __fmul_rn(acc, io.res_in);
+                  float y = __fmul_rn(acc[4 * g + j], io.res_in);
                   y = finalizeOutput(io, y, 0.0f, 0.0f, exceeded);
                   sum[c0 + 4 * g + j] += y * fac;
                 }
@@ -474,13 +600,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) {
-        mbarArrive(&tmem_empty[b]);
+        if (PAIR) {
+          // the issuer's "accumulator drained" barriers live in rank 0 of the pair
+          mbarArriveCluster(mapaShared(smemAddr(&tmem_empty[b]), 0));
+        } else {
+          mbarArrive(&tmem_empty[b]);
+        }
       }
     }
     if (ok && row_ok) {
       if (exceeded && io.bm != AB200_BM_NONE && p.flags != nullptr) {
         atomicOr(&p.flags[row], 1);
       }
+      const bool vec = ((p.out_ss & 3) == 0) && ((ch.z & 3) == 0) &&
+                       ((((uintptr_t)p.out) & 15) == 0) && !p.accumulate;
+      float *orow = p.out + (long long)row * p.out_ss + ch.z + cbase;
 #pragma unroll
       for (int c = 0; c < TC_EPI_COLS; c += 4) {
         const int cl = cbase + c;
@@ -516,10 +650,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
   }
   __syncthreads();
+  if (PAIR) {
+    // neither CTA leaves while its peer may still arrive on its barriers or feed its tensor core
+    __syncwarp();
+    clusterSync();
+  }
   if (warp == TC_WARP_MMA) {
     tcFenceAfter();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
-                 : "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
+                   : "memory");
+    } else {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
+                   : "memory");
+    }
   }
 }
 
@@ -876,23 +1020,43 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
     AB200_CUDA(cudaMemsetAsync(prof_dev, 0, 148 * 8 * sizeof(long long) * 2, s));
   }
   p.prof = prof_dev;
-  const int n_items = n_chunks_ * ((r.m + TC_M - 1) / TC_M);
+  int grid_x = 0;
   int n_sm = 0;
   AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device_));
-  dim3 grid(n_items < n_sm ? n_items : n_sm); // one persistent CTA per SM
-  if (r.io.bm != AB200_BM_NONE) {
-    AB200_CUDA(cudaFuncSetAttribute(mvmTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    TC_SMEM_BYTES));
-    mvmTcKernel<true><<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
+  // CTA pairs whenever there are at least two 128-row blocks (and the mode allows it)
+  const bool pair = mvmPath() != 3 && r.m > TC_M;
+  const bool bm = r.io.bm != AB200_BM_NONE;
+  if (pair) {
+    const int n_items = n_chunks_ * ((r.m + 2 * TC_M - 1) / (2 * TC_M));
+    const int n_pairs = n_items < n_sm / 2 ? n_items : n_sm / 2;
+    auto kernel = bm ? mvmTcKernel<true, true> : mvmTcKernel<false, true>;
+    AB200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC2_SMEM_BYTES));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * n_pairs);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = TC2_SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    AB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_bhi, tm_blo, p));
+    grid_x = 2 * n_pairs;
   } else {
-    AB200_CUDA(cudaFuncSetAttribute(mvmTcKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    TC_SMEM_BYTES));
-    mvmTcKernel<false><<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
+    const int n_items = n_chunks_ * ((r.m + TC_M - 1) / TC_M);
+    dim3 grid(n_items < n_sm ? n_items : n_sm); // one persistent CTA per SM
+    auto kernel = bm ? mvmTcKernel<true, false> : mvmTcKernel<false, false>;
+    AB200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
+    kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
+    grid_x = (int)grid.x;
   }
   AB200_LAUNCH_CHECK();
   if (prof_on) {
     // diagnostics only: average wait cycles per role over the CTAs (synchronises)
-    const int n = (int)grid.x < 296 ? (int)grid.x : 296;
+    const int n = grid_x < 296 ? grid_x : 296;
     std::vector<long long> h((size_t)n * 8);
     AB200_CUDA(cudaStreamSynchronize(s));
     AB200_CUDA(cudaMemcpy(h.data(), prof_dev, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));

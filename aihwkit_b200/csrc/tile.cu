@@ -777,7 +777,7 @@ bool Tile::tcEligible(const MvmProblem &p) const {
       !TcEngine::ioSupported(p.io)) {
     return false;
   }
-  if (mode == 2) {
+  if (mode >= 2) {
     return true;
   }
   return p.m >= 128 && (double)p.m * p.in_size * p.out_size >= 16777216.0;

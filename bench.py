@@ -224,6 +224,8 @@ def run_ours(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the analog tile has no CPU path")
+    if args.mvm_path:
+        _cabi.check(_cabi.lib().ab200_set_mvm_path(args.mvm_path))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -360,6 +362,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ref-rows", type=int, default=4096,
                     help="rows of the bounded CPU sample (reference arm / cpu_baseline)")
+    ap.add_argument("--mvm-path", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="kernel selection of the library (ab200_set_mvm_path); 0 = automatic")
     ap.add_argument("--no-cpu-baseline", action="store_true",
                     help="skip the CPU baseline leg (used for profiler captures)")
     args = ap.parse_args()

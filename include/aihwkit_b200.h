@@ -362,7 +362,8 @@ int ab200_mvm_forward_noalloc(const ab200_io_params *forward_io, const float *w_
 
 /* Kernel selection for the MVM (no counterpart in the reference, which always calls cuBLAS):
  * 0 = automatic (tensor cores for large aligned problems), 1 = CUDA cores only, 2 = tensor
- * cores whenever the IO settings allow. Process-wide; used by tests and benchmarks. */
+ * cores whenever the IO settings allow, 3 = as 2 but never the kernel variant that pairs two
+ * CTAs on one 256-row tile. Process-wide; used by tests and benchmarks. */
 int ab200_set_mvm_path(int mode);
 
 /* Number of kernels this library has launched since it was loaded (all tiles, this process). */

@@ -153,3 +153,38 @@ def test_tc_operand_cache_follows_weight_changes(path):
         y_or, _, scale, _ = O.forward(W, X.cpu().numpy(), fio, return_pre_adc=True)
         frac, worst = H.lsb_report(y, y_or, (fio.res_out / scale)[:, None])
         assert frac <= 1e-3 and worst <= 1.001, (step, frac, worst)
+
+
+@pytest.mark.parametrize("out_size,in_size,max_tile,m", [(768, 2304, 512, 300), (1024, 1024, 512, 1024),
+                                                         (256, 384, 128, 129)])
+def test_cta_pair_and_single_cta_kernels_agree(path, out_size, in_size, max_tile, m):
+    """The kernel variant that pairs two CTAs on a 256-row tile (mode 2, used whenever there are
+    more than 128 rows) and the single-CTA variant (mode 3) compute the same products and draw
+    the same noise: results are equal bit for bit, ragged last row block included."""
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    rng = np.random.default_rng(m)
+    W = rng.normal(0, 1 / np.sqrt(in_size), (out_size, in_size)).astype(np.float32)
+    X = torch.from_numpy(rng.normal(0, 1, (m, in_size)).astype(np.float32)).cuda()
+    cfg = H.inference_params(noise=True)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=8)
+    outs = []
+    for mode in (2, 3):
+        path(mode)
+        a = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+        a.set_weights(torch.from_numpy(W))
+        outs.append([a.forward(X).cpu().numpy() for _ in range(2)])
+    assert np.array_equal(outs[0][0], outs[1][0])
+    assert np.array_equal(outs[0][1], outs[1][1])
+    assert not np.array_equal(outs[0][0], outs[0][1])  # a new call draws new noise
+    # single tile with bound management, forward and backward
+    p = H.training_params(noise=True, pulse_det=True, bm=True, out_bound=2.0)
+    res = []
+    for mode in (2, 3):
+        path(mode)
+        t, _ = _tile(p, H.device("cs", False), 384, 200, seed=6)
+        t.set_weights(torch.from_numpy(W[:200, :384] * 5))
+        y = t.forward(X[:, :384].contiguous()).cpu().numpy()
+        g = t.backward(X[:, :200].contiguous()).cpu().numpy()
+        res.append((y, g))
+    assert np.array_equal(res[0][0], res[1][0])
+    assert np.array_equal(res[0][1], res[1][1])
