@@ -92,6 +92,24 @@ enum : uint32_t {
 };
 
 #ifdef __CUDACC__
+// MUFU approximations in their flush-to-zero form: the arguments here are never subnormal, and
+// the plain forms carry extra instructions that rescale subnormal inputs
+__device__ __forceinline__ float lg2Ftz(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float cosFtz(float x) {
+  float y;
+  asm("cos.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sinFtz(float x) {
+  float y;
+  asm("sin.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // uniform in (0,1) with 24 random bits
 __device__ __forceinline__ float u01(uint32_t x) { return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f); }
 
@@ -115,12 +133,12 @@ __device__ __forceinline__ void boxMuller(uint32_t a, uint32_t b, float &z0, flo
 __device__ __forceinline__ void boxMuller1(uint32_t a, float &z0, float &z1) {
   float u1 = 2.0f - __uint_as_float(0x3f800000u | ((a >> 12) << 3));
   float f2 = __uint_as_float(0x3f800000u | ((a & 0xFFFu) << 11)); // 1 + u2
-  float r2 = -1.3862943611198906f * __log2f(u1); // -2 ln(u1)
+  float r2 = -1.3862943611198906f * lg2Ftz(u1); // -2 ln(u1)
   float r;
   asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(r2));
   float ang = fmaf(6.283185307179586f, f2, -6.283185307179586f); // 2 pi u2
-  z0 = r * __cosf(ang);
-  z1 = r * __sinf(ang);
+  z0 = r * cosFtz(ang);
+  z1 = r * sinFtz(ang);
 }
 
 // four standard normals for noise block `blk` of call `call`; a block covers four consecutive

@@ -285,6 +285,19 @@ struct UpdateSmem {
   float sz[URES][256];
 };
 
+// Eight fresh Gaussians for one thread's column of the reservoir. Kept out of line: the refill is
+// rare, and inlining it into each of the four per-weight loop bodies makes the kernel spill out of
+// the instruction cache.
+__device__ __noinline__ void refillReservoir(PhiloxKey key, uint32_t gid, uint32_t refills,
+                                             uint32_t call, float *column) {
+  float z[8];
+  gauss8(key, (uint64_t)gid | ((uint64_t)refills << 32), call, TAG_DEVICE, z);
+#pragma unroll
+  for (int r = 0; r < URES; r++) {
+    column[r * 256] = z[r];
+  }
+}
+
 template <int KIND, bool IMPLICIT, bool NOISY>
 __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -428,12 +441,7 @@ __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
           // lane with a pulse to apply runs dry (leftovers are discarded).
           for (int k = 0; __any_sync(0xffffffffu, k < n); k++) {
             if (__any_sync(0xffffffffu, k < n && rc == 0)) {
-              float z[8];
-              gauss8(p.key, (uint64_t)gid | ((uint64_t)refills << 32), p.call, TAG_DEVICE, z);
-#pragma unroll
-              for (int r = 0; r < URES; r++) {
-                sm.sz[r][threadIdx.x] = z[r];
-              }
+              refillReservoir(p.key, gid, refills, p.call, &sm.sz[0][threadIdx.x]);
               rc = URES;
               refills++;
             }
