@@ -428,27 +428,25 @@ __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
           for (int k = 0; k < n; k++) {
             w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], 0.0f, p.mult_noise);
           }
-        } else if (!__any_sync(0xffffffffu, n > rc)) {
+        } else {
           // One Gaussian per pulse, taken from a per-thread reservoir in shared memory: the
           // generator - by far the most expensive part of a pulse - runs once per several
-          // events instead of per event.
-          for (int k = 0; k < n; k++) {
-            rc--;
-            w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], std * sm.sz[rc][threadIdx.x], p.mult_noise);
+          // events instead of per event. The whole warp refills together as soon as one lane
+          // cannot serve its event (leftovers are discarded), so the refill is never divergent;
+          // only an event with more pulses than the reservoir holds refills on its own.
+          if (__any_sync(0xffffffffu, n > rc)) {
+            refillReservoir(p.key, gid, refills, p.call, &sm.sz[0][threadIdx.x]);
+            rc = URES;
+            refills++;
           }
-        } else {
-          // Some lane needs more Gaussians than it has left: refill the whole warp whenever a
-          // lane with a pulse to apply runs dry (leftovers are discarded).
-          for (int k = 0; __any_sync(0xffffffffu, k < n); k++) {
-            if (__any_sync(0xffffffffu, k < n && rc == 0)) {
+          for (int k = 0; k < n; k++) {
+            if (rc == 0) {
               refillReservoir(p.key, gid, refills, p.call, &sm.sz[0][threadIdx.x]);
               rc = URES;
               refills++;
             }
-            if (k < n) {
-              rc--;
-              w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], std * sm.sz[rc][threadIdx.x], p.mult_noise);
-            }
+            rc--;
+            w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], std * sm.sz[rc][threadIdx.x], p.mult_noise);
           }
         }
       }
