@@ -234,7 +234,6 @@ pulseOnce(float w, bool down, const float4 &q, const float2 &e, float xi, int mu
 
 constexpr int UT_I = 64; // d-lines per CTA (contiguous in memory)
 constexpr int UT_J = 16; // x-lines per CTA
-constexpr int UE_J = 4;  // x-lines per thread
 constexpr int UBLK = 32; // samples per block = bits of one non-zero bitmap word
 constexpr int UT_JP = UT_J + 1; // padded row length of the staged x words (bank spread)
 
@@ -265,7 +264,11 @@ __global__ void __launch_bounds__(256)
   nz[(long long)blk * n_lines + line] = bits;
 }
 
-// Every thread owns four weights (one d-line, four x-lines). Per super-block of 128 samples it
+// Every thread owns EJ weights (one d-line, EJ x-lines; EJ = 4 with 256 threads per CTA for large
+// problems, EJ = 1 with 1024 threads when the grid would otherwise not fill the GPU). The loop
+// over a thread's weights is NOT unrolled: its body always works on slot 0 of the register arrays,
+// which are rotated by one after every weight, so the (large) body exists once and stays in the
+// instruction cache. Per super-block of 128 samples the thread
 // walks, for each of its weights, the samples where both lines pulsed; the walk is decoupled from
 // the (expensive, rare) pulse application: each lane first advances to ITS next coincidence, then
 // the whole warp applies one event per lane together, so lanes whose events fall on different
@@ -277,33 +280,36 @@ constexpr int USUP = 4;              // bitmap words per super-block
 constexpr int USAMP = USUP * UBLK;   // samples per super-block
 constexpr int URES = 8;              // Gaussians per thread in the reservoir
 
-struct UpdateSmem {
+template <int NT> struct UpdateSmem {
   uint32_t sd[USAMP][UT_I];
   uint32_t sx[USAMP][UT_JP];
   uint32_t sdnz[USUP][UT_I];
   uint32_t sxnz[USUP][UT_J];
-  float sz[URES][256];
+  float sz[URES][NT];
 };
 
 // Eight fresh Gaussians for one thread's column of the reservoir. Kept out of line: the refill is
 // rare, and inlining it into each of the four per-weight loop bodies makes the kernel spill out of
 // the instruction cache.
 __device__ __noinline__ void refillReservoir(PhiloxKey key, uint32_t gid, uint32_t refills,
-                                             uint32_t call, float *column) {
+                                             uint32_t call, float *column, int stride) {
   float z[8];
   gauss8(key, (uint64_t)gid | ((uint64_t)refills << 32), call, TAG_DEVICE, z);
 #pragma unroll
   for (int r = 0; r < URES; r++) {
-    column[r * 256] = z[r];
+    column[r * stride] = z[r];
   }
 }
 
-template <int KIND, bool IMPLICIT, bool NOISY>
-__global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
+template <int KIND, bool IMPLICIT, bool NOISY, int EJ>
+__global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
+    pulsedUpdateKernel(UpdateProblem p) {
+  constexpr int UE_J = EJ;
+  constexpr int UNT = UT_I * UT_J / EJ; // threads per CTA
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  UpdateSmem &sm = *reinterpret_cast<UpdateSmem *>(smem_raw);
+  UpdateSmem<UNT> &sm = *reinterpret_cast<UpdateSmem<UNT> *>(smem_raw);
   const int ti = threadIdx.x & (UT_I - 1);
-  const int tj = threadIdx.x / UT_I; // 0..3
+  const int tj = threadIdx.x / UT_I;
   const int i = blockIdx.x * UT_I + ti;
   const int j0 = blockIdx.y * UT_J + tj * UE_J;
   const bool i_ok = i < p.d_size;
@@ -321,7 +327,7 @@ __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
     e[t] = make_float2(0.f, 0.f);
   }
   const float std = p.dw_min_std;
-  const uint32_t gid = (blockIdx.y * gridDim.x + blockIdx.x) * 256u + threadIdx.x;
+  const uint32_t gid = (blockIdx.y * gridDim.x + blockIdx.x) * (uint32_t)UNT + threadIdx.x;
   uint32_t refills = 0;
   int rc = 0;
 
@@ -335,9 +341,9 @@ __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
       const int jj = threadIdx.x % UT_J, sj = threadIdx.x / UT_J;
       const int gj = blockIdx.y * UT_J + jj;
       const uint32_t *src = p.xw + (long long)(s0 + sj) * p.x_size + gj;
-      const long long step = (long long)(256 / UT_J) * p.x_size;
+      const long long step = (long long)(UNT / UT_J) * p.x_size;
 #pragma unroll 4
-      for (int ss = sj; ss < USAMP; ss += 256 / UT_J, src += step) {
+      for (int ss = sj; ss < USAMP; ss += UNT / UT_J, src += step) {
         sm.sx[ss][jj] = (gj < p.x_size && s0 + ss < p.m) ? *src : 0u;
       }
     }
@@ -345,9 +351,9 @@ __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
       const int ii = threadIdx.x % UT_I, si = threadIdx.x / UT_I;
       const int gi = blockIdx.x * UT_I + ii;
       const uint32_t *src = p.dw + (long long)(s0 + si) * p.d_size + gi;
-      const long long step = (long long)(256 / UT_I) * p.d_size;
+      const long long step = (long long)(UNT / UT_I) * p.d_size;
 #pragma unroll 8
-      for (int ss = si; ss < USAMP; ss += 256 / UT_I, src += step) {
+      for (int ss = si; ss < USAMP; ss += UNT / UT_I, src += step) {
         sm.sd[ss][ii] = (gi < p.d_size && s0 + ss < p.m) ? *src : 0u;
       }
     }
@@ -374,7 +380,7 @@ __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
       }
     }
     __syncthreads();
-#pragma unroll
+#pragma unroll 1
     for (int t = 0; t < UE_J; t++) {
       const int jl = tj * UE_J + t;
       const long long idx = (long long)(j0 + t) * p.d_size + i;
@@ -414,19 +420,19 @@ __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
           break;
         }
         if (n != 0) {
-          if (!loaded[t]) {
-            w[t] = p.w[idx];
-            q[t] = p.par4[idx];
+          if (!loaded[0]) {
+            w[0] = p.w[idx];
+            q[0] = p.par4[idx];
             if (KIND != AB200_DEVICE_CONSTANT_STEP) {
-              e[t] = p.par2[idx];
+              e[0] = p.par2[idx];
             }
-            loaded[t] = true;
+            loaded[0] = true;
           }
-          dirty[t] = true;
+          dirty[0] = true;
         }
         if (!NOISY) {
           for (int k = 0; k < n; k++) {
-            w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], 0.0f, p.mult_noise);
+            w[0] = pulseOnce<KIND>(w[0], down, q[0], e[0], 0.0f, p.mult_noise);
           }
         } else {
           // One Gaussian per pulse, taken from a per-thread reservoir in shared memory: the
@@ -435,20 +441,40 @@ __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
           // cannot serve its event (leftovers are discarded), so the refill is never divergent;
           // only an event with more pulses than the reservoir holds refills on its own.
           if (__any_sync(0xffffffffu, n > rc)) {
-            refillReservoir(p.key, gid, refills, p.call, &sm.sz[0][threadIdx.x]);
+            refillReservoir(p.key, gid, refills, p.call, &sm.sz[0][threadIdx.x], UNT);
             rc = URES;
             refills++;
           }
           for (int k = 0; k < n; k++) {
             if (rc == 0) {
-              refillReservoir(p.key, gid, refills, p.call, &sm.sz[0][threadIdx.x]);
+              refillReservoir(p.key, gid, refills, p.call, &sm.sz[0][threadIdx.x], UNT);
               rc = URES;
               refills++;
             }
             rc--;
-            w[t] = pulseOnce<KIND>(w[t], down, q[t], e[t], std * sm.sz[rc][threadIdx.x], p.mult_noise);
+            w[0] = pulseOnce<KIND>(w[0], down, q[0], e[0], std * sm.sz[rc][threadIdx.x], p.mult_noise);
           }
         }
+      }
+      if (UE_J > 1) {
+        // rotate the register arrays by one: the next weight moves into slot 0
+        const float w0 = w[0];
+        const float4 q0 = q[0];
+        const float2 e0 = e[0];
+        const bool l0 = loaded[0], d0 = dirty[0];
+#pragma unroll
+        for (int k = 0; k + 1 < UE_J; k++) {
+          w[k] = w[k + 1];
+          q[k] = q[k + 1];
+          e[k] = e[k + 1];
+          loaded[k] = loaded[k + 1];
+          dirty[k] = dirty[k + 1];
+        }
+        w[UE_J - 1] = w0;
+        q[UE_J - 1] = q0;
+        e[UE_J - 1] = e0;
+        loaded[UE_J - 1] = l0;
+        dirty[UE_J - 1] = d0;
       }
     }
     __syncthreads();
@@ -463,18 +489,37 @@ __global__ void __launch_bounds__(256, 4) pulsedUpdateKernel(UpdateProblem p) {
   }
 }
 
-template <int KIND, bool IMPLICIT, bool NOISY>
-static void launchUpdateInstance(const UpdateProblem &p, dim3 grid, cudaStream_t stream) {
+template <int KIND, bool IMPLICIT, bool NOISY, int EJ>
+static void launchUpdateVariant(const UpdateProblem &p, cudaStream_t stream) {
+  constexpr int NT = UT_I * UT_J / EJ;
   static bool configured[64] = {};
   int dev = 0;
   AB200_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    AB200_CUDA(cudaFuncSetAttribute(pulsedUpdateKernel<KIND, IMPLICIT, NOISY>,
+    AB200_CUDA(cudaFuncSetAttribute(pulsedUpdateKernel<KIND, IMPLICIT, NOISY, EJ>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)sizeof(UpdateSmem)));
+                                    (int)sizeof(UpdateSmem<NT>)));
     configured[dev] = true;
   }
-  pulsedUpdateKernel<KIND, IMPLICIT, NOISY><<<grid, 256, sizeof(UpdateSmem), stream>>>(p);
+  dim3 grid((p.d_size + UT_I - 1) / UT_I, (p.x_size + UT_J - 1) / UT_J);
+  pulsedUpdateKernel<KIND, IMPLICIT, NOISY, EJ><<<grid, NT, sizeof(UpdateSmem<NT>), stream>>>(p);
+}
+
+template <int KIND, bool IMPLICIT, bool NOISY>
+static void launchUpdateInstance(const UpdateProblem &p, dim3 grid, cudaStream_t stream) {
+  // four weights per thread (256 threads, four CTAs per SM) once the grid fills the GPU several
+  // times over; one weight per thread (1024 threads) for small tiles
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    AB200_CUDA(cudaGetDevice(&dev));
+    AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  }
+  if ((long long)grid.x * grid.y >= 3LL * n_sm) {
+    launchUpdateVariant<KIND, IMPLICIT, NOISY, 4>(p, stream);
+  } else {
+    launchUpdateVariant<KIND, IMPLICIT, NOISY, 1>(p, stream);
+  }
 }
 
 void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream) {
