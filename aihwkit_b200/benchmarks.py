@@ -1,6 +1,6 @@
 """Training-step timings of the analog tile on one GPU: forward + backward + pulsed update.
 
-    python -m aihwkit_b200.benchmarks --config 0|2|3 [--steps K] [--warmup W] [--cpu-baseline]
+    python -m aihwkit_b200.benchmarks --config 0|2|3 [--steps K] [--warmup W] [--indexed]
 
 Configurations (seeded synthetic inputs with the stated shapes and distributions):
   0  single tile 256 x 256, batch 64, ConstantStep device, 7-bit DAC / 9-bit ADC, out_noise 0.06,
@@ -25,7 +25,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import sys
 import time
 
 import numpy as np
@@ -84,15 +83,16 @@ def build(config: int):
     raise SystemExit("config must be 0, 2 or 3")
 
 
-def main():
+def main(argv=None, on_line=None):
+    """``on_line(line, cfg, x, d, lr)``, when given, may extend the JSON line before it is printed
+    (``bench.py --config N`` adds the CPU baseline of the compiled reference there)."""
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, default=0)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=0, help="override the batch size")
-    ap.add_argument("--cpu-baseline", action="store_true")
     ap.add_argument("--indexed", action="store_true", help="config 3 through the indexed interface")
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
 
     import torch
 
@@ -180,23 +180,8 @@ def main():
             "coincidence_pairs_per_s": float(x_size) * d_size * m / (t_u * 1e-3),
         },
     }
-    if args.cpu_baseline:
-        sys.path.insert(0, ROOT)
-        from oracle import ref
-
-        if ref.available():
-            rt = ref.RefTile(cfg)
-            mc = min(m, 512)
-            xc, dc = x[:mc].cpu().numpy(), d[:mc].cpu().numpy()
-            rt.set_learning_rate(w["lr"])
-            rt.forward(xc[:8])
-            t0 = time.perf_counter()
-            rt.forward(xc)
-            rt.backward(dc)
-            rt.update(xc, dc)
-            dt = time.perf_counter() - t0
-            line["cpu_baseline"] = {"value": mc / dt, "unit": "columns/s", "cores": 1,
-                                    "kind": "reference", "sample": f"{mc} of {m} columns, 1 thread"}
+    if on_line is not None:
+        on_line(line, cfg, x, d, w["lr"])
     print(json.dumps(line))
 
 

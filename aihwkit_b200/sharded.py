@@ -80,6 +80,30 @@ class ShardedTileArray:
     def forward(self, x: torch.Tensor, dst: Optional[int] = 0, **kw) -> torch.Tensor:
         return self.reduce(self.forward_partial(x, **kw), dst)
 
+    def forward_overlapped(self, x: torch.Tensor, dst: Optional[int] = 0, n_chunks: int = 4,
+                           **kw) -> torch.Tensor:
+        """Forward with the partial-sum collective overlapped with the kernels: the batch is cut
+        into ``n_chunks`` row blocks; the collective of block ``k`` runs (on the process group's
+        own stream) while the tiles compute block ``k + 1``.  Same result as :meth:`forward`."""
+        if not self.distributed or self.world == 1 or n_chunks <= 1:
+            return self.forward(x, dst, **kw)
+        m = x.size(0)
+        if getattr(self, "_ov_partial", None) is None or self._ov_partial.size(0) != m:
+            self._ov_partial = torch.empty(m, self.out_size, dtype=torch.float32, device=x.device)
+        rows = (m + n_chunks - 1) // n_chunks
+        works = []
+        for r0 in range(0, m, rows):
+            part = self._ov_partial[r0 : r0 + rows]
+            self.local.forward(x[r0 : r0 + rows], out=part, non_blocking=True, **kw)
+            if dst is None:
+                works.append(dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            else:
+                works.append(dist.reduce(part, dst=dst, op=dist.ReduceOp.SUM, group=self.group,
+                                         async_op=True))
+        for w in works:
+            w.wait()
+        return self._ov_partial
+
     def forward_host(self, x_local_host: torch.Tensor, out_host: Optional[torch.Tensor] = None,
                      dst: int = 0, chunk_rows: int = 1024) -> Optional[torch.Tensor]:
         """End-to-end forward from host memory on every rank.

@@ -247,6 +247,8 @@ def run_ours(args):
     x = x_host.to(dev)
 
     def step():
+        if world > 1 and args.reduce_chunks > 1:
+            return arr.forward_overlapped(x, dst=0, n_chunks=args.reduce_chunks, is_test=True)
         y = arr.forward_partial(x, is_test=True, non_blocking=True)
         return arr.reduce(y, dst=0)
 
@@ -354,6 +356,41 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_training_config(args):
+    """Configurations 0, 2, 3: GPU timing by the package's benchmark module; the compiled
+    reference CPU tile runs a bounded sample of the same step on one host thread."""
+    from aihwkit_b200 import benchmarks
+
+    def add_cpu_baseline(line, cfg, x, d, lr):
+        if args.no_cpu_baseline:
+            return
+        from oracle import ref
+
+        if not ref.available():
+            line["cpu_baseline"] = {"value": None, "kind": "reference", "sample": "oracle/_ref not built"}
+            return
+        rt = ref.RefTile(cfg)
+        m = x.size(0)
+        mc = min(m, 512)
+        xc, dc = x[:mc].cpu().numpy(), d[:mc].cpu().numpy()
+        rt.set_learning_rate(lr)
+        rt.forward(xc[:8])
+        t0 = time.perf_counter()
+        rt.forward(xc)
+        rt.backward(dc)
+        rt.update(xc, dc)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": mc / dt, "unit": "columns/s", "cores": 1, "kind": "reference",
+                                "sample": f"{mc} of {m} columns, 1 thread"}
+
+    argv = ["--config", str(args.config)]
+    if args.steps != 200:
+        argv += ["--steps", str(args.steps)]
+    if args.warmup != 10:
+        argv += ["--warmup", str(args.warmup)]
+    benchmarks.main(argv, on_line=add_cpu_baseline)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -364,10 +401,18 @@ def main():
                     help="rows of the bounded CPU sample (reference arm / cpu_baseline)")
     ap.add_argument("--mvm-path", type=int, default=0, choices=[0, 1, 2, 3],
                     help="kernel selection of the library (ab200_set_mvm_path); 0 = automatic")
+    ap.add_argument("--reduce-chunks", type=int, default=1,
+                    help="N > 1: row blocks whose partial-sum reduce overlaps the next block's kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true",
                     help="skip the CPU baseline leg (used for profiler captures)")
+    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3],
+                    help="1 = the mapped inference layer (the contract line); 0, 2, 3 = training "
+                         "step of a single tile (aihwkit_b200.benchmarks) with the reference CPU "
+                         "tile timed beside it")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.config != 1:
+        run_training_config(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

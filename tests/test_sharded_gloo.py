@@ -25,7 +25,14 @@ class _OracleArray:
         self.in_sizes = split_sizes(W.shape[1], max_tile)
         self.out_sizes = split_sizes(W.shape[0], max_tile)
 
-    def forward(self, x):
+    def forward(self, x, out=None, **_):
+        y = self._forward(x)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def _forward(self, x):
         from oracle import analog_tile_oracle as O
 
         io = O.IO.from_c(self.cfg.forward_io)
@@ -60,9 +67,13 @@ def _worker(rank, world, port, out_path):
     assert arr.world == world and len(arr.in_sizes) == 4
     y = arr.forward(X, dst=0)
     y_all = arr.reduce(arr.forward_partial(X), dst=None)
+    # row blocks whose collectives are issued asynchronously, ragged last block
+    y_ov = arr.forward_overlapped(X, dst=None, n_chunks=3).clone()
+    y_ov0 = arr.forward_overlapped(X, dst=0, n_chunks=4)
     if rank == 0:
         full = _OracleArray(W, cfg, max_tile, 0, 4).forward(X)
         ok = torch.allclose(y, full, atol=1e-5) and torch.allclose(y_all, full, atol=1e-5)
+        ok = ok and torch.allclose(y_ov, full, atol=1e-5) and torch.allclose(y_ov0, full, atol=1e-5)
         with open(out_path, "w") as f:
             f.write("ok" if ok else "mismatch")
     dist.barrier()
