@@ -90,6 +90,13 @@ class DeviceParams(C.Structure):
         ("slope_down_dtod", C.c_float),
         ("reference_mean", C.c_float),
         ("reference_std", C.c_float),
+        ("lifetime", C.c_float),
+        ("lifetime_dtod", C.c_float),
+        ("diffusion", C.c_float),
+        ("diffusion_dtod", C.c_float),
+        ("reset", C.c_float),
+        ("reset_dtod", C.c_float),
+        ("reset_std", C.c_float),
     ]
 
 
@@ -171,6 +178,11 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_forward_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _I, _VP]),
         "ab200_tile_backward_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _VP]),
         "ab200_tile_update_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _VP]),
+        "ab200_tile_decay_weights": (_I, [_VP, C.c_float, _I, _VP]),
+        "ab200_tile_diffuse_weights": (_I, [_VP, _VP]),
+        "ab200_tile_clip_weights": (_I, [_VP, _I, C.c_float, C.c_float, _VP]),
+        "ab200_tile_reset_columns": (_I, [_VP, _I, _I, C.c_float, _VP]),
+        "ab200_tile_set_weights_uniform_random": (_I, [_VP, C.c_float, C.c_float, _VP]),
         "ab200_tile_last_bm_stats": (_I, [_VP, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
         "ab200_tile_set_seed": (_I, [_VP, C.c_uint64]),
         "ab200_array_create": (_I, [cfgp, _I, _I, _I, _I, _I, _I, _I, C.POINTER(_VP)]),

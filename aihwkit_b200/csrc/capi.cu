@@ -297,6 +297,39 @@ int ab200_tile_update_indexed(ab200_tile *tile, const float *x_dev, const float 
   AB200_CATCH
 }
 
+int ab200_tile_decay_weights(ab200_tile *tile, float alpha, int bias_no_decay, void *stream) {
+  AB200_TRY
+  T(tile)->decayWeights(alpha, bias_no_decay != 0, (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+int ab200_tile_diffuse_weights(ab200_tile *tile, void *stream) {
+  AB200_TRY
+  T(tile)->diffuseWeights((cudaStream_t)stream);
+  AB200_CATCH
+}
+
+int ab200_tile_clip_weights(ab200_tile *tile, int clip_type, float fixed_value, float sigma,
+                            void *stream) {
+  AB200_TRY
+  T(tile)->clipWeights(clip_type, fixed_value, sigma, (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+int ab200_tile_reset_columns(ab200_tile *tile, int start_col, int n_cols, float reset_prob,
+                             void *stream) {
+  AB200_TRY
+  T(tile)->resetColumns(start_col, n_cols, reset_prob, (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+int ab200_tile_set_weights_uniform_random(ab200_tile *tile, float min_value, float max_value,
+                                          void *stream) {
+  AB200_TRY
+  T(tile)->setWeightsUniformRandom(min_value, max_value, (cudaStream_t)stream);
+  AB200_CATCH
+}
+
 int ab200_tile_last_bm_stats(ab200_tile *tile, int32_t *n_rerun_samples, float *max_reduction) {
   AB200_TRY
   T(tile)->lastBmStats(n_rerun_samples, max_reduction);

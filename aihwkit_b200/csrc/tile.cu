@@ -132,7 +132,9 @@ void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_
   const size_t size = (size_t)x_size * d_size;
   ds.host.assign(ds.names.size() * size, 0.0f);
   float *wmax = &ds.host[0 * size], *wmin = &ds.host[1 * size], *sup = &ds.host[2 * size],
-        *sdown = &ds.host[3 * size], *decay = &ds.host[4 * size];
+        *sdown = &ds.host[3 * size], *decay = &ds.host[4 * size], *diffusion = &ds.host[5 * size],
+        *reset_bias0 = &ds.host[6 * size];
+  ds.reset_std = par.reset_std;
 
   if (par.w_min > 0.0f || par.w_max < 0.0f) {
     AB200_FATAL("The closed interval [w_min,w_max] needs to contain 0.");
@@ -171,9 +173,16 @@ void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_
         wmin[k] = 100.0f * par.w_min;
         wmax[k] = 100.0f * par.w_max;
       }
-      (void)rng.gauss(); // diffusion rate draw (diffusion = 0)
-      (void)rng.gauss(); // reset bias draw (reset = 0, reset_dtod = 0)
-      decay[k] = 1.0f;   // lifetime = 0: no decay, no draw
+      // diffusion rate, reset bias, decay scale (rpu_pulsed_device.cpp:704-731): the first two
+      // always draw, the decay scale only with a lifetime
+      diffusion[k] = fabsf(par.diffusion * (1.0f + par.diffusion_dtod * rng.gauss()));
+      reset_bias0[k] = par.reset + par.reset_dtod * rng.gauss();
+      if (par.lifetime > 0.0f) {
+        float t = par.lifetime * (1.0f + par.lifetime_dtod * rng.gauss());
+        decay[k] = t > 1.0f ? 1.0f - 1.0f / t : 0.0f;
+      } else {
+        decay[k] = 1.0f;
+      }
     }
   }
 
@@ -301,6 +310,7 @@ Tile::~Tile() {
     for (int k = 0; k < 2; k++) {
       cudaFree(dev_[k].par4);
       cudaFree(dev_[k].par2);
+      cudaFree(dev_[k].par3);
     }
     cudaFree(scale_);
     cudaFree(factor_);
@@ -601,6 +611,7 @@ void Tile::setHidden(const float *in) {
   const float *p = in;
   for (int k = 0; k < n_dev_; k++) {
     std::memcpy(dev_[k].host.data(), p, dev_[k].host.size() * sizeof(float));
+    dev_[k].par3_valid = false;
     p += dev_[k].host.size();
     // PulsedRPUDevice::setDeviceParameter re-estimates dw_min from the given step sizes when it
     // moved by more than 2 * dw_min_dtod (rpu_pulsed_device.cpp:319-334)

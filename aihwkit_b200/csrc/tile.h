@@ -98,6 +98,9 @@ struct DeviceStore {
   int mult_noise = 1;
   float4 *par4 = nullptr; // {scale_up, scale_down, max_bound, min_bound}
   float2 *par2 = nullptr; // {slope_up, slope_down} or {reference, 0}
+  float4 *par3 = nullptr; // {decay_scale, diffusion_rate, reset_bias, 0}; uploaded on first use
+  bool par3_valid = false;
+  float reset_std = 0.0f;
   // host copies, [name][d][x] in the reference's naming / order
   std::vector<std::string> names;
   std::vector<float> host;
@@ -196,6 +199,14 @@ public:
                      int n_img, bool trans, cudaStream_t s);
   void lastBmStats(int32_t *n_rerun, float *max_red);
 
+  // weight operations between updates (RPUPulsed::decayWeights / diffuseWeights / clipWeights /
+  // resetCols / setWeightsUniformRandom, src/rpucuda/rpu_pulsed.cpp:189-284)
+  void decayWeights(float alpha, bool bias_no_decay, cudaStream_t s);
+  void diffuseWeights(cudaStream_t s);
+  void clipWeights(int type, float fixed_value, float sigma, cudaStream_t s);
+  void resetColumns(int start_col, int n_cols, float reset_prob, cudaStream_t s);
+  void setWeightsUniformRandom(float lo, float hi, cudaStream_t s);
+
   // used by the mapped array: forward on a sub-block of a wider activation matrix
   void forwardStrided(const float *x, long long x_ss, float *y, long long y_ss, int m,
                       bool accumulate, uint32_t noise_id, cudaStream_t s);
@@ -218,6 +229,8 @@ private:
   void pulsedUpdateRange(UpdateProblem &p, cudaStream_t s);
   void doTransfer(cudaStream_t s);
   float pulseCountLR() const;
+  void requireSingleDevice(const char *what);
+  void ensurePar3();
   void requireIndices(const char *what, long long image_size, int m_batch, int n_img) const;
   void ensureIndexedScratch(long long b);
   void gatherIndexed(const float *x, long long in_mat, int m_batch, int n_img, bool trans,
@@ -230,7 +243,7 @@ private:
   IOEff f_io_, b_io_, t_io_;
   UpEff up_, t_up_;
   PhiloxKey key_;
-  uint32_t fwd_calls_ = 0, bwd_calls_ = 0, upd_calls_ = 0, transfer_calls_ = 0;
+  uint32_t fwd_calls_ = 0, bwd_calls_ = 0, upd_calls_ = 0, transfer_calls_ = 0, op_calls_ = 0;
 
   std::vector<float> host_w_dx_; // only while the tile has no device
   float *w_ = nullptr;           // device [x][d]

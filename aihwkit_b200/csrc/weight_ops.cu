@@ -1,0 +1,337 @@
+// Weight operations between updates: decay, diffusion, clipping, column reset, uniform
+// re-initialisation. Per-element device rules of PulsedRPUDevice
+// (src/rpucuda/rpu_pulsed_device.cpp:362-490); for the floating-point (ideal) device the rules of
+// RPUSimple / SimpleRPUDevice (src/rpucuda/rpu.cpp:1556-1625, rpu_simple_device.cpp:149-169) and
+// WeightClipper::apply (src/rpucuda/weight_clipper.cpp:38-118).
+//
+// All kernels are one pass over the weights [x_size][d_size] (plus the 16-byte bounds and the
+// 16-byte decay / diffusion / reset record per element): HBM-bound, 24-40 B per weight.
+#include "tile.h"
+
+#include <cmath>
+
+namespace ab200 {
+
+enum : uint32_t {
+  TAG_DIFFUSE = 0x70000000u,
+  TAG_RESET = 0x71000000u,
+  TAG_UNIFORM_INIT = 0x72000000u,
+};
+
+namespace {
+
+// par4 = {scale_up, scale_down, max_bound, min_bound}, par3 = {decay_scale, diffusion, reset_bias, -}
+__global__ void __launch_bounds__(256)
+    decayKernel(float *w, const float4 *par4, const float4 *par3, long long n, long long first_bias,
+                float alpha, int use_alpha) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= n) {
+    return;
+  }
+  const float4 q = par4[t], r = par3[t];
+  // w = (w - b) * s + b with s = decay_scale, or 1 + alpha * (decay_scale - 1)
+  float s = use_alpha ? __fadd_rn(1.0f, __fmul_rn(alpha, __fsub_rn(r.x, 1.0f))) : r.x;
+  if (t >= first_bias) {
+    s = 1.0f; // bias column does not decay
+  }
+  float v = __fadd_rn(__fmul_rn(__fsub_rn(w[t], r.z), s), r.z);
+  v = fminf(v, q.z);
+  v = fmaxf(v, q.w);
+  w[t] = v;
+}
+
+__global__ void __launch_bounds__(256)
+    scaleKernel(float *w, long long n, long long first_bias, float scale) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < n && t < first_bias) {
+    w[t] = __fmul_rn(w[t], scale);
+  }
+}
+
+// w += rate * N(0,1), then the element's bounds (par4 null: floating-point tile, one rate, no bounds)
+__global__ void __launch_bounds__(256)
+    diffuseKernel(float *w, const float4 *par4, const float4 *par3, long long n, float rate,
+                  PhiloxKey key, uint32_t call) {
+  const long long t4 = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t4 * 4 >= n) {
+    return;
+  }
+  float z[4];
+  gauss4(key, (uint64_t)t4, call, TAG_DIFFUSE, z);
+  for (int k = 0; k < 4; k++) {
+    const long long t = t4 * 4 + k;
+    if (t < n) {
+      float v = w[t];
+      if (par4) {
+        const float4 q = par4[t];
+        v += par3[t].y * z[k];
+        v = fminf(v, q.z);
+        v = fmaxf(v, q.w);
+      } else {
+        v += rate * z[k];
+      }
+      w[t] = v;
+    }
+  }
+}
+
+// device bounds, optionally tightened to [-clip, clip] (clip < 0: bounds only)
+__global__ void __launch_bounds__(256)
+    clipBoundsKernel(float *w, const float4 *par4, long long n, float clip) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= n) {
+    return;
+  }
+  float hi = clip, lo = -clip;
+  if (par4) {
+    const float4 q = par4[t];
+    hi = clip < 0.0f ? q.z : fminf(q.z, clip);
+    lo = clip < 0.0f ? q.w : fmaxf(q.w, -clip);
+  }
+  w[t] = fmaxf(fminf(w[t], hi), lo);
+}
+
+// sums for the data-dependent clip values: acc[0] = sum w, acc[1] = sum w^2 (double), and
+// rowmax[i] = max_j |w_ij| as float bits (non-negative floats order like unsigned integers)
+__global__ void __launch_bounds__(256)
+    clipStatsKernel(const float *w, long long n, int d_size, double *acc, unsigned int *rowmax) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  double s = 0.0, s2 = 0.0;
+  if (t < n) {
+    const float v = w[t];
+    s = v;
+    s2 = (double)v * v;
+    if (rowmax) {
+      atomicMax(&rowmax[t % d_size], __float_as_uint(fabsf(v)));
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_down_sync(0xffffffffu, s, o);
+    s2 += __shfl_down_sync(0xffffffffu, s2, o);
+  }
+  if ((threadIdx.x & 31) == 0 && acc) {
+    atomicAdd(&acc[0], s);
+    atomicAdd(&acc[1], s2);
+  }
+}
+
+// columns [start, start + n_col) of the x dimension, wrapping around
+__global__ void __launch_bounds__(256)
+    resetColsKernel(float *w, const float4 *par4, const float4 *par3, int x_size, int d_size,
+                    int start_col, int n_col, float reset_prob, float reset_std, PhiloxKey key,
+                    uint32_t call) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= (long long)n_col * d_size) {
+    return;
+  }
+  const int jc = (int)(t / d_size), i = (int)(t % d_size);
+  const int j = (start_col + jc) % x_size;
+  const long long e = (long long)j * d_size + i;
+  uint32_t r[4];
+  philox4x32_10((uint32_t)e, (uint32_t)(e >> 32), call, TAG_RESET, key, r);
+  if (reset_prob < 1.0f && !(u01(r[0]) < reset_prob)) {
+    return;
+  }
+  float z0, z1;
+  boxMuller(r[1], r[2], z0, z1);
+  float v = reset_std > 0.0f ? reset_std * z0 : 0.0f;
+  if (par4) {
+    const float4 q = par4[e];
+    v += par3[e].z;
+    v = fminf(v, q.z);
+    v = fmaxf(v, q.w);
+  }
+  w[e] = v;
+}
+
+__global__ void __launch_bounds__(256)
+    uniformInitKernel(float *w, long long n, float lo, float hi, PhiloxKey key, uint32_t call) {
+  const long long t4 = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t4 * 4 >= n) {
+    return;
+  }
+  uint32_t r[4];
+  philox4x32_10((uint32_t)t4, (uint32_t)(t4 >> 32), call, TAG_UNIFORM_INIT, key, r);
+  for (int k = 0; k < 4; k++) {
+    const long long t = t4 * 4 + k;
+    if (t < n) {
+      w[t] = lo + (hi - lo) * u01(r[k]);
+    }
+  }
+}
+
+inline unsigned blocksFor(long long n) { return (unsigned)((n + 255) / 256); }
+
+} // namespace
+
+void Tile::requireSingleDevice(const char *what) {
+  requireDevice(what);
+  if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+    AB200_FATAL(what << " is not implemented for compound (Transfer) devices");
+  }
+}
+
+// decay scale, diffusion rate and reset bias per element, uploaded on first use
+void Tile::ensurePar3() {
+  DeviceStore &ds = dev_[0];
+  if (ds.kind == AB200_DEVICE_IDEAL || ds.par3_valid) {
+    return;
+  }
+  const size_t size = (size_t)x_size_ * d_size_;
+  const float *decay = &ds.host[4 * size], *diff = &ds.host[5 * size], *rb = &ds.host[6 * size];
+  std::vector<float4> p3(size);
+  for (int i = 0; i < d_size_; i++) {
+    for (int j = 0; j < x_size_; j++) {
+      const size_t src = (size_t)i * x_size_ + j, dst = (size_t)j * d_size_ + i;
+      p3[dst] = make_float4(decay[src], diff[src], rb[src], 0.0f);
+    }
+  }
+  if (!ds.par3) {
+    AB200_CUDA(cudaMalloc(&ds.par3, size * sizeof(float4)));
+  }
+  AB200_CUDA(cudaMemcpy(ds.par3, p3.data(), size * sizeof(float4), cudaMemcpyHostToDevice));
+  ds.par3_valid = true;
+}
+
+void Tile::decayWeights(float alpha, bool bias_no_decay, cudaStream_t s) {
+  requireSingleDevice("decay_weights");
+  const long long n = (long long)x_size_ * d_size_;
+  const long long first_bias = bias_no_decay ? (long long)(x_size_ - 1) * d_size_ : n;
+  if (dev_[0].kind == AB200_DEVICE_IDEAL) {
+    const float lifetime = cfg_.device[0].lifetime;
+    const float rate = lifetime > 1.0f ? 1.0f / lifetime : 0.0f;
+    const float scale = 1.0f - alpha * rate;
+    if (scale > 0.0f && scale < 1.0f) {
+      scaleKernel<<<blocksFor(n), 256, 0, s>>>(w_, n, first_bias, scale);
+      AB200_LAUNCH_CHECK();
+      w_version_++;
+    }
+    return;
+  }
+  ensurePar3();
+  decayKernel<<<blocksFor(n), 256, 0, s>>>(w_, dev_[0].par4, dev_[0].par3, n, first_bias, alpha, 1);
+  AB200_LAUNCH_CHECK();
+  w_version_++;
+}
+
+void Tile::diffuseWeights(cudaStream_t s) {
+  requireSingleDevice("diffuse_weights");
+  const long long n = (long long)x_size_ * d_size_;
+  const bool ideal = dev_[0].kind == AB200_DEVICE_IDEAL;
+  if (ideal && !(cfg_.device[0].diffusion > 0.0f)) {
+    return;
+  }
+  if (!ideal) {
+    ensurePar3();
+  }
+  diffuseKernel<<<blocksFor((n + 3) / 4), 256, 0, s>>>(w_, ideal ? nullptr : dev_[0].par4,
+                                                      ideal ? nullptr : dev_[0].par3, n,
+                                                      cfg_.device[0].diffusion, key_, op_calls_++);
+  AB200_LAUNCH_CHECK();
+  w_version_++;
+}
+
+void Tile::clipWeights(int type, float fixed_value, float sigma, cudaStream_t s) {
+  requireSingleDevice("clip_weights");
+  const long long n = (long long)x_size_ * d_size_;
+  const bool ideal = dev_[0].kind == AB200_DEVICE_IDEAL;
+  const float4 *bounds = ideal ? nullptr : dev_[0].par4;
+  float clip = -1.0f;
+  if (type == AB200_CLIP_NONE) {
+    return;
+  } else if (type == AB200_CLIP_FIXED_VALUE) {
+    clip = fixed_value;
+    if (ideal && clip < 0.0f) {
+      return; // RPUSimple::clipWeights: nothing to do without a value
+    }
+  } else if (type == AB200_CLIP_LAYER_GAUSSIAN || type == AB200_CLIP_AVERAGE_CHANNEL_MAX) {
+    if (!ideal) {
+      // rpu_pulsed.cpp:269-279
+      AB200_FATAL("Sophisticated clipping is NOT implemented for most training devices");
+    }
+    // one statistics pass, read back: the clip value is a scalar the host needs anyway
+    double *acc = nullptr;
+    unsigned int *rowmax = nullptr;
+    AB200_CUDA(cudaMalloc(&acc, 2 * sizeof(double)));
+    AB200_CUDA(cudaMemsetAsync(acc, 0, 2 * sizeof(double), s));
+    if (type == AB200_CLIP_AVERAGE_CHANNEL_MAX) {
+      AB200_CUDA(cudaMalloc(&rowmax, (size_t)d_size_ * sizeof(unsigned int)));
+      AB200_CUDA(cudaMemsetAsync(rowmax, 0, (size_t)d_size_ * sizeof(unsigned int), s));
+    }
+    clipStatsKernel<<<blocksFor(n), 256, 0, s>>>(w_, n, d_size_, acc, rowmax);
+    AB200_LAUNCH_CHECK();
+    double h[2];
+    AB200_CUDA(cudaMemcpyAsync(h, acc, sizeof(h), cudaMemcpyDeviceToHost, s));
+    std::vector<float> hmax;
+    if (rowmax) {
+      hmax.resize(d_size_);
+      AB200_CUDA(cudaMemcpyAsync(hmax.data(), rowmax, (size_t)d_size_ * sizeof(float),
+                                 cudaMemcpyDeviceToHost, s));
+    }
+    AB200_CUDA(cudaStreamSynchronize(s));
+    cudaFree(acc);
+    cudaFree(rowmax);
+    if (type == AB200_CLIP_LAYER_GAUSSIAN) {
+      const double mean = h[0] / (double)n;
+      const double var = n > 1 ? (h[1] - (double)n * mean * mean) / (double)(n - 1) : 0.0;
+      clip = (float)(std::sqrt(var > 0.0 ? var : 0.0) * (double)sigma);
+    } else {
+      double sum = 0.0;
+      for (float v : hmax) {
+        sum += v;
+      }
+      clip = (float)std::fabs(sum / (double)d_size_);
+    }
+    if (fixed_value > 0.0f) {
+      clip = clip < fixed_value ? clip : fixed_value;
+    }
+    if (!(clip > 0.0f)) {
+      return;
+    }
+  } else {
+    AB200_FATAL("Clipping type not implemented.");
+  }
+  clipBoundsKernel<<<blocksFor(n), 256, 0, s>>>(w_, bounds, n, clip);
+  AB200_LAUNCH_CHECK();
+  w_version_++;
+}
+
+void Tile::resetColumns(int start_col, int n_cols, float reset_prob, cudaStream_t s) {
+  requireSingleDevice("reset_columns");
+  if (reset_prob == 0.0f) {
+    return; // rpu_pulsed.cpp:219-224
+  }
+  int n_col = n_cols >= 0 ? n_cols : x_size_;
+  n_col = n_col > x_size_ ? x_size_ : n_col;
+  if (n_col == 0) {
+    return;
+  }
+  if (start_col < 0 || start_col >= x_size_) {
+    AB200_FATAL("reset_columns: start column " << start_col << " outside [0, " << x_size_ << ")");
+  }
+  const bool ideal = dev_[0].kind == AB200_DEVICE_IDEAL;
+  if (!ideal) {
+    ensurePar3();
+  }
+  const float reset_std = ideal ? cfg_.device[0].reset_std : dev_[0].reset_std;
+  resetColsKernel<<<blocksFor((long long)n_col * d_size_), 256, 0, s>>>(
+      w_, ideal ? nullptr : dev_[0].par4, ideal ? nullptr : dev_[0].par3, x_size_, d_size_,
+      start_col, n_col, reset_prob, reset_std, key_, op_calls_++);
+  AB200_LAUNCH_CHECK();
+  w_version_++;
+}
+
+void Tile::setWeightsUniformRandom(float lo, float hi, cudaStream_t s) {
+  requireSingleDevice("set_weights_uniform_random");
+  const long long n = (long long)x_size_ * d_size_;
+  uniformInitKernel<<<blocksFor((n + 3) / 4), 256, 0, s>>>(w_, n, lo, hi, key_, op_calls_++);
+  AB200_LAUNCH_CHECK();
+  if (dev_[0].kind != AB200_DEVICE_IDEAL) {
+    // onSetWeights: clip to the per-element bounds (rpu_pulsed.cpp:280-284)
+    clipBoundsKernel<<<blocksFor(n), 256, 0, s>>>(w_, dev_[0].par4, n, -1.0f);
+    AB200_LAUNCH_CHECK();
+  }
+  w_version_++;
+}
+
+} // namespace ab200

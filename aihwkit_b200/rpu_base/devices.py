@@ -203,6 +203,24 @@ class AbstractResistiveDeviceParameter:
         raise RuntimeError("Needs implementation.")
 
 
+class WeightClipType(enum.IntEnum):
+    """rpu_base_utils.cpp ``WeightClipType`` (src/rpucuda/weight_clipper.h:14-19)."""
+
+    None_ = 0
+    FixedValue = 1
+    LayerGaussian = 2
+    AverageChannelMax = 3
+
+
+class WeightClipParameter:
+    """``WeightClipParameter`` (src/rpucuda/weight_clipper.h:22-27)."""
+
+    def __init__(self) -> None:
+        self.type = WeightClipType.None_
+        self.fixed_value = -1.0
+        self.sigma = 2.5
+
+
 class IdealResistiveDeviceParameter(AbstractResistiveDeviceParameter):
     """SimpleRPUDeviceMetaParameter: floating-point update (rpu_base_devices.cpp:545-552)."""
 
@@ -243,14 +261,10 @@ class PulsedResistiveDeviceParameter(AbstractResistiveDeviceParameter):
         return float(self.dw_min)
 
     def _fill_base(self, c: _cabi.DeviceParams) -> None:
-        for name, off in (
-            ("lifetime", 0.0), ("diffusion", 0.0), ("corrupt_devices_prob", 0.0), ("reset", 0.0),
-            ("reset_dtod", 0.0),
-        ):
-            if getattr(self, name) != off:
-                raise RuntimeError(
-                    f"device parameter '{name}' is not implemented by the B200 analog tile"
-                )
+        if self.corrupt_devices_prob != 0.0:
+            raise RuntimeError(
+                "device parameter 'corrupt_devices_prob' is not implemented by the B200 analog tile"
+            )
         if self.count_pulses:
             raise RuntimeError("count_pulses is not implemented by the B200 analog tile")
         c.kind = self._kind
@@ -260,7 +274,8 @@ class PulsedResistiveDeviceParameter(AbstractResistiveDeviceParameter):
         c.perfect_bias = int(bool(self.perfect_bias))
         for name in (
             "dw_min", "dw_min_dtod", "dw_min_std", "w_min", "w_min_dtod", "w_max", "w_max_dtod",
-            "up_down", "up_down_dtod",
+            "up_down", "up_down_dtod", "lifetime", "lifetime_dtod", "diffusion", "diffusion_dtod",
+            "reset", "reset_dtod", "reset_std",
         ):
             setattr(c, name, float(getattr(self, name)))
 
@@ -452,6 +467,9 @@ class AnalogTileParameter:
                 cfg.device[0].construction_seed = int(device_par.construction_seed)
         elif kind == DEVICE_IDEAL:
             cfg.device[0].kind = DEVICE_IDEAL
+            cfg.device[0].lifetime = float(device_par.lifetime)
+            cfg.device[0].diffusion = float(device_par.diffusion)
+            cfg.device[0].reset_std = float(device_par.reset_std)
             cfg.device[0].construction_seed = int(device_par.construction_seed)
         else:
             cfg.device[0] = device_par._to_c()

@@ -269,6 +269,39 @@ class AnalogTile:
                 )
             )
 
+    # -- weight operations between updates -------------------------------------------------------
+    def _op_stream(self):
+        if self._device_index < 0:
+            return None  # the library raises: no CPU compute path
+        return int(torch.cuda.current_stream(torch.device("cuda", self._device_index)).cuda_stream)
+
+    def decay_weights(self, alpha: float = 1.0) -> None:
+        """rpu_base_tiles.cpp:277-292: ``W = (W - b) * (1 + alpha * (decay_scale - 1)) + b`` per
+        element, clipped to the device bounds (floating-point tile: ``W *= 1 - alpha / lifetime``)."""
+        check(self._lib.ab200_tile_decay_weights(self._h, float(alpha), 0, self._op_stream()))
+
+    def diffuse_weights(self) -> None:
+        """rpu_base_tiles.cpp:373-386: ``W += diffusion_rate * N(0, 1)`` per element, clipped."""
+        check(self._lib.ab200_tile_diffuse_weights(self._h, self._op_stream()))
+
+    def clip_weights(self, weight_clipper_params) -> None:
+        """rpu_base_tiles.cpp:316-330; ``weight_clipper_params`` is a ``WeightClipParameter``."""
+        check(self._lib.ab200_tile_clip_weights(
+            self._h, int(weight_clipper_params.type), float(weight_clipper_params.fixed_value),
+            float(weight_clipper_params.sigma), self._op_stream()))
+
+    def reset_columns(self, start_column_idx: int = 0, num_columns: int = 1,
+                      reset_prob: float = 1.0) -> None:
+        """rpu_base_tiles.cpp:388-410: ``W_ij = xi * reset_std + reset_bias_ij`` for the given
+        input columns (wrapping around), each element with probability ``reset_prob``."""
+        check(self._lib.ab200_tile_reset_columns(self._h, int(start_column_idx), int(num_columns),
+                                                 float(reset_prob), self._op_stream()))
+
+    def set_weights_uniform_random(self, min_value: float, max_value: float) -> None:
+        """rpu_base_tiles.cpp:263-275."""
+        check(self._lib.ab200_tile_set_weights_uniform_random(self._h, float(min_value),
+                                                              float(max_value), self._op_stream()))
+
     # -- indexed convolution interface ---------------------------------------------------------
     def set_matrix_indices(self, indices: torch.Tensor) -> None:
         """rpu_base_tiles.cpp ``set_matrix_indices``: int32 index tensor of a convolution

@@ -147,6 +147,16 @@ typedef struct ab200_device_params {
   float slope_down_dtod;
   float reference_mean;
   float reference_std;
+  /* decay / diffusion / reset (SimpleMetaParameter lifetime, diffusion; PulsedRPUDeviceMetaParameter
+   * lifetime_dtod, diffusion_dtod, reset, reset_dtod; reset_std; rpu_pulsed_device.h:70-85,
+   * rpu_simple_device.h:40-90) */
+  float lifetime;
+  float lifetime_dtod;
+  float diffusion;
+  float diffusion_dtod;
+  float reset;
+  float reset_dtod;
+  float reset_std;
 } ab200_device_params;
 
 /* TransferRPUDeviceMetaParameter (src/rpucuda/rpu_transfer_device.h:52-75). */
@@ -294,6 +304,30 @@ int ab200_tile_backward_indexed(ab200_tile *tile, const float *d_dev, float *x_d
 int ab200_tile_update_indexed(ab200_tile *tile, const float *x_dev, const float *d_dev,
                               long long total_input_size, int m_batch, int dim3, int trans,
                               void *stream);
+
+/* ---- weight operations between updates -------------------------------------------------------
+ * Replace RPUPulsed<T>::decayWeights(alpha, bias_no_decay) / diffuseWeights() / clipWeights(...) /
+ * resetCols(start_col, n_cols, reset_prob) / setWeightsUniformRandom (src/rpucuda/rpu_pulsed.cpp:
+ * 189-282) with the per-element device rules of PulsedRPUDevice (src/rpucuda/rpu_pulsed_device.cpp:
+ * 362-490), and for the floating-point (ideal) device the RPUSimple rules (src/rpucuda/rpu.cpp:
+ * 1556-1625) and WeightClipper::apply (src/rpucuda/weight_clipper.cpp:38-118); bound as
+ * decay_weights / diffuse_weights / clip_weights / reset_columns / set_weights_uniform_random
+ * (rpu_base_tiles.cpp:263-400). All run on `stream` on the tile's weights in place. Compound
+ * (Transfer) devices are not supported. */
+enum ab200_clip_type {
+  AB200_CLIP_NONE = 0,
+  AB200_CLIP_FIXED_VALUE = 1,
+  AB200_CLIP_LAYER_GAUSSIAN = 2,
+  AB200_CLIP_AVERAGE_CHANNEL_MAX = 3
+};
+int ab200_tile_decay_weights(ab200_tile *tile, float alpha, int bias_no_decay, void *stream);
+int ab200_tile_diffuse_weights(ab200_tile *tile, void *stream);
+int ab200_tile_clip_weights(ab200_tile *tile, int clip_type, float fixed_value, float sigma,
+                            void *stream);
+int ab200_tile_reset_columns(ab200_tile *tile, int start_col, int n_cols, float reset_prob,
+                             void *stream);
+int ab200_tile_set_weights_uniform_random(ab200_tile *tile, float min_value, float max_value,
+                                          void *stream);
 
 /* Bound-management statistics of the last forward: number of samples that were re-run at least
  * once and the largest reduction factor used (rpu_forward_backward_pass.cpp:935-983). */

@@ -606,3 +606,57 @@ def from_sample_major(a: np.ndarray, size: int, m_batch: int, dim3: int, trans: 
     if trans:
         return np.ascontiguousarray(a.reshape(dim3, m_batch, size).transpose(0, 2, 1))
     return a.reshape(dim3, m_batch, size)
+
+
+# ---------------------------------------------------------------------------------------------
+# Weight operations between updates
+# ---------------------------------------------------------------------------------------------
+def _hidden(names, hp, name):
+    return np.asarray(hp[list(names).index(name)], np.float32)
+
+
+def decay_weights(w: np.ndarray, names, hp: np.ndarray, alpha: float = 1.0,
+                  bias_no_decay: bool = False) -> np.ndarray:
+    """``PulsedRPUDevice::decayWeights(weights, alpha, bias_no_decay)``
+    (src/rpucuda/rpu_pulsed_device.cpp:391-420): ``w = (w - b) * (1 + alpha * (wd - 1)) + b``,
+    clipped to the element's bounds; weights are ``[d][x]``."""
+    f = np.float32
+    wd, b = _hidden(names, hp, "decay_scales"), _hidden(names, hp, "reset_bias")
+    s = f(1.0) + f(alpha) * (wd - f(1.0))
+    if bias_no_decay:
+        s = s.copy()
+        s[:, -1] = f(1.0)
+    out = (np.asarray(w, f) - b) * s + b
+    out = np.minimum(out, _hidden(names, hp, "max_bound"))
+    return np.maximum(out, _hidden(names, hp, "min_bound")).astype(f)
+
+
+def decay_weights_simple(w: np.ndarray, lifetime: float, alpha: float = 1.0) -> np.ndarray:
+    """``RPUSimple::decayWeights`` (src/rpucuda/rpu.cpp:1556-1575)."""
+    f = np.float32
+    rate = f(1.0) / f(lifetime) if lifetime > 1.0 else f(0.0)
+    scale = f(1.0) - f(alpha) * rate
+    return (np.asarray(w, f) * scale).astype(f) if 0.0 < scale < 1.0 else np.asarray(w, f).copy()
+
+
+def clip_to_device(w: np.ndarray, names, hp: np.ndarray, clip: float = -1.0) -> np.ndarray:
+    """``PulsedRPUDevice::clipWeights`` (src/rpucuda/rpu_pulsed_device.cpp:451-470)."""
+    hi, lo = _hidden(names, hp, "max_bound"), _hidden(names, hp, "min_bound")
+    if clip >= 0:
+        hi, lo = np.minimum(hi, np.float32(clip)), np.maximum(lo, np.float32(-clip))
+    return np.maximum(np.minimum(np.asarray(w, np.float32), hi), lo)
+
+
+def clip_value(w: np.ndarray, clip_type: int, fixed_value: float = -1.0, sigma: float = 2.5) -> float:
+    """Clip value of ``WeightClipper::apply`` (src/rpucuda/weight_clipper.cpp:38-112) for the
+    types 1 FixedValue, 2 LayerGaussian, 3 AverageChannelMax; <= 0 means no clipping."""
+    w = np.asarray(w, np.float32)
+    if clip_type == 1:
+        return float(fixed_value)
+    if clip_type == 2:
+        c = float(np.std(w.astype(np.float64), ddof=1)) * sigma
+    elif clip_type == 3:
+        c = float(np.abs(w).max(axis=1).astype(np.float64).mean())
+    else:
+        return -1.0
+    return min(c, fixed_value) if fixed_value > 0 else c

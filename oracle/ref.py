@@ -74,6 +74,10 @@ def load() -> C.CDLL:
         "ref_tile_backward": (i, [vp, fp, fp, i, i, i, i]),
         "ref_tile_update": (i, [vp, fp, fp, i, i, i, i]),
         "ref_tile_coincidences": (i, [vp, fp, fp, C.c_float, C.c_float, fp]),
+        "ref_tile_decay_weights": (i, [vp, C.c_float, i]),
+        "ref_tile_diffuse_weights": (i, [vp]),
+        "ref_tile_clip_weights": (i, [vp, i, C.c_float, C.c_float]),
+        "ref_tile_reset_columns": (i, [vp, i, i, C.c_float]),
         "ref_tile_set_matrix_indices": (i, [vp, fp, C.c_longlong]),
         "ref_tile_forward_indexed": (i, [vp, fp, fp, C.c_longlong, i, i, i, i]),
         "ref_tile_backward_indexed": (i, [vp, fp, fp, C.c_longlong, i, i, i]),
@@ -226,3 +230,16 @@ class RefTile:
                 self._h, x.ctypes.data, d.ctypes.data, x.size, m_batch, n, int(trans)
             )
         )
+
+    # weight operations between updates (src/rpucuda/rpu_pulsed.cpp:189-284)
+    def decay_weights(self, alpha: float = 1.0, bias_no_decay: bool = False) -> None:
+        self._ck(self._lib.ref_tile_decay_weights(self._h, alpha, int(bias_no_decay)))
+
+    def diffuse_weights(self) -> None:
+        self._ck(self._lib.ref_tile_diffuse_weights(self._h))
+
+    def clip_weights(self, clip_type: int, fixed_value: float = -1.0, sigma: float = 2.5) -> None:
+        self._ck(self._lib.ref_tile_clip_weights(self._h, int(clip_type), fixed_value, sigma))
+
+    def reset_columns(self, start_col: int = 0, n_cols: int = 1, reset_prob: float = 1.0) -> None:
+        self._ck(self._lib.ref_tile_reset_columns(self._h, start_col, n_cols, reset_prob))

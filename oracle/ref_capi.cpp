@@ -78,6 +78,13 @@ void toPulsedBase(const ab200_device_params &s, PulsedRPUDeviceMetaParameter<flo
   p.w_max_dtod = s.w_max_dtod;
   p.up_down = s.up_down;
   p.up_down_dtod = s.up_down_dtod;
+  p.lifetime = s.lifetime;
+  p.lifetime_dtod = s.lifetime_dtod;
+  p.diffusion = s.diffusion;
+  p.diffusion_dtod = s.diffusion_dtod;
+  p.reset = s.reset;
+  p.reset_dtod = s.reset_dtod;
+  p.reset_std = s.reset_std;
 }
 
 std::unique_ptr<PulsedRPUDeviceMetaParameter<float>> makeSingle(const ab200_device_params &s) {
@@ -175,6 +182,9 @@ int ref_tile_create(const ab200_tile_config *cfg, void **out) {
   } else if (cfg->device_kind == AB200_DEVICE_IDEAL) {
     auto sp = std::make_unique<SimpleRPUDeviceMetaParameter<float>>();
     sp->construction_seed = cfg->device[0].construction_seed;
+    sp->lifetime = cfg->device[0].lifetime;
+    sp->diffusion = cfg->device[0].diffusion;
+    sp->reset_std = cfg->device[0].reset_std;
     dp = std::move(sp);
   } else {
     ab200_device_params d = cfg->device[0];
@@ -330,6 +340,35 @@ int ref_tile_update_indexed(void *h, const float *x, const float *d, long long t
   REF_TRY
   static_cast<RefTile *>(h)->rpu->updateIndexed(x, d, (int)total_input_size, m_batch, dim3,
                                                 trans != 0);
+  REF_CATCH
+}
+
+/* Weight operations between updates (src/rpucuda/rpu_pulsed.cpp:189-284). */
+int ref_tile_decay_weights(void *h, float alpha, int bias_no_decay) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->decayWeights(alpha, bias_no_decay != 0);
+  REF_CATCH
+}
+
+int ref_tile_diffuse_weights(void *h) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->diffuseWeights();
+  REF_CATCH
+}
+
+int ref_tile_clip_weights(void *h, int clip_type, float fixed_value, float sigma) {
+  REF_TRY
+  WeightClipParameter wc;
+  wc.type = (WeightClipType)clip_type;
+  wc.fixed_value = fixed_value;
+  wc.sigma = sigma;
+  static_cast<RefTile *>(h)->rpu->clipWeights(wc);
+  REF_CATCH
+}
+
+int ref_tile_reset_columns(void *h, int start_col, int n_cols, float reset_prob) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->resetCols(start_col, n_cols, reset_prob);
   REF_CATCH
 }
 

@@ -30,7 +30,7 @@ def test_struct_sizes_match_header():
     # layouts are plain int32 / float / uint64 fields; sizes are what a C compiler produces
     assert C.sizeof(_cabi.IOParams) == 20 * 4
     assert C.sizeof(_cabi.UpdateParams) == 10 * 4
-    assert C.sizeof(_cabi.DeviceParams) == 27 * 4
+    assert C.sizeof(_cabi.DeviceParams) == 34 * 4
     assert C.sizeof(_cabi.TransferParams) == 9 * 4 + 20 * 4 + 10 * 4
     assert C.sizeof(_cabi.TileConfig) % 8 == 0
 

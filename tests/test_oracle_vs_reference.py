@@ -128,3 +128,90 @@ def test_indexed_interface(trans, analog_bias):
     Wo = W.copy()
     O.update(Wo, cols, d_cols, lr, dp.dw_min, O.Up.from_c(cfg.update), dev)
     assert np.abs(t.get_weights() - Wo).max() <= 1e-7
+
+
+def _decay_device(kind="sb"):
+    dp = H.device(kind, False)
+    dp.lifetime, dp.lifetime_dtod = 50.0, 0.2
+    dp.diffusion, dp.diffusion_dtod = 0.01, 0.3
+    dp.reset, dp.reset_dtod, dp.reset_std = 0.05, 0.1, 0.02
+    dp.w_max_dtod = dp.w_min_dtod = 0.2
+    return dp
+
+
+def test_weight_ops_deterministic():
+    """Decay and clipping against the compiled reference (exact), and the per-element decay /
+    diffusion / reset parameters the host draws."""
+    rng = np.random.default_rng(5)
+    x_size, d_size = 23, 11
+    p = H.training_params(noise=False, pulse_det=True)
+    cfg = p._config(x_size, d_size, _decay_device(), seed=3)
+    t = ref.RefTile(cfg)
+    t.set_weights(rng.uniform(-0.7, 0.7, (d_size, x_size)).astype(np.float32))
+    names, hp = t.hidden_parameter_names(), t.get_hidden_parameters()
+    assert np.ptp(hp[names.index("decay_scales")]) > 0 and np.ptp(hp[names.index("reset_bias")]) > 0
+    w = t.get_weights()
+    for alpha, bnd in ((1.0, False), (0.3, True)):
+        t.decay_weights(alpha, bnd)
+        w = O.decay_weights(w, names, hp, alpha, bnd)
+        assert np.array_equal(t.get_weights(), w)
+    t.clip_weights(1, fixed_value=0.3)
+    w = O.clip_to_device(w, names, hp, 0.3)
+    assert np.array_equal(t.get_weights(), w)
+    # floating-point tile: scalar decay and the data-dependent clip values
+    from aihwkit_b200.rpu_base import devices as D
+
+    ideal = D.IdealResistiveDeviceParameter()
+    ideal.lifetime = 20.0
+    t2 = ref.RefTile(p._config(x_size, d_size, ideal, seed=3))
+    w2 = rng.normal(0, 0.3, (d_size, x_size)).astype(np.float32)
+    t2.set_weights(w2)
+    t2.decay_weights(0.5)
+    w2 = O.decay_weights_simple(w2, 20.0, 0.5)
+    assert np.array_equal(t2.get_weights(), w2)
+    for ctype, fixed in ((2, -1.0), (3, -1.0), (3, 0.4)):
+        c = O.clip_value(w2, ctype, fixed, 1.5)
+        t2.clip_weights(ctype, fixed, 1.5)
+        w2 = np.clip(w2, -np.float32(c), np.float32(c))
+        assert np.abs(t2.get_weights() - w2).max() <= 1e-6
+
+
+def test_weight_ops_stochastic_moments():
+    """Diffusion and column reset of the reference: per-element standard deviations follow the
+    hidden diffusion rates / reset_std, means the reset bias."""
+    x_size, d_size, reps = 12, 10, 400
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = _decay_device()
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = ref.RefTile(cfg)
+    t.set_seed(7)
+    names, hp = t.hidden_parameter_names(), t.get_hidden_parameters()
+    rate, bias = hp[names.index("diffusion_rates")], hp[names.index("reset_bias")]
+    w0 = np.zeros((d_size, x_size), np.float32)
+    diffs, resets = [], []
+    for _ in range(reps):
+        t.set_weights(w0)
+        t.diffuse_weights()
+        diffs.append(t.get_weights())
+        t.reset_columns(10, 4, 1.0)  # columns 10, 11, 0, 1
+        resets.append(t.get_weights())
+    diffs, resets = np.stack(diffs), np.stack(resets)
+    assert np.abs(diffs.std(0) / rate - 1).mean() < 0.05
+    cols = [10, 11, 0, 1]
+    assert np.abs(resets[:, :, cols].mean(0) - bias[:, cols]).max() < 5 * dp.reset_std / np.sqrt(reps) + 1e-3
+    assert abs(resets[:, :, cols].std(0).mean() / dp.reset_std - 1) < 0.08
+    assert np.array_equal(resets[:, :, 2:10], diffs[:, :, 2:10])
+
+
+@pytest.mark.parametrize("kind", ["cs", "sb", "sbr"])
+def test_host_parameter_draw_with_decay_diffusion_reset(kind):
+    """The library's host-side draw of decay scales, diffusion rates and reset biases equals the
+    reference's for the same construction seed (needs no GPU: the tile stays on the host)."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    p = H.training_params(noise=False, pulse_det=True)
+    cfg = p._config(17, 9, _decay_device(kind), seed=3)
+    ours = T.AnalogTile(cfg)
+    t = ref.RefTile(cfg)
+    assert ours.get_hidden_parameter_names() == t.hidden_parameter_names()
+    assert np.array_equal(ours.get_hidden_parameters().numpy(), t.get_hidden_parameters())

@@ -1,0 +1,156 @@
+"""Weight operations between updates on the GPU (decay, diffusion, clipping, column reset,
+uniform re-initialisation) against the numpy oracle (which is pinned to the compiled reference in
+tests/test_oracle_vs_reference.py) and, where it is built, against the compiled reference."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import analog_tile_oracle as O
+from oracle import ref
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def _device(kind="sb"):
+    dp = H.device(kind, False)
+    dp.lifetime, dp.lifetime_dtod = 50.0, 0.2
+    dp.diffusion, dp.diffusion_dtod = 0.01, 0.3
+    dp.reset, dp.reset_dtod, dp.reset_std = 0.05, 0.1, 0.02
+    dp.w_max_dtod = dp.w_min_dtod = 0.2
+    return dp
+
+
+def _tile(cfg):
+    from aihwkit_b200.rpu_base import tiles as T
+
+    return T.AnalogTile(cfg, cuda_device=0)
+
+
+@pytest.mark.parametrize("kind", ["cs", "sbr"])
+def test_decay_and_clip_exact(kind):
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(5)
+    x_size, d_size = 70, 33
+    p = H.training_params(noise=False, pulse_det=True)
+    cfg = p._config(x_size, d_size, _device(kind), seed=3)
+    t = _tile(cfg)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.7, 0.7, (d_size, x_size)).astype(np.float32)))
+    names, hp = t.get_hidden_parameter_names(), t.get_hidden_parameters().numpy()
+    w = t.get_weights().numpy()
+    for alpha in (1.0, 0.3):
+        t.decay_weights(alpha)
+        w = O.decay_weights(w, names, hp, alpha)
+        assert np.array_equal(t.get_weights().numpy(), w)
+    # bias column kept (C ABI only; the binding always passes bias_no_decay = False)
+    from aihwkit_b200 import _cabi
+
+    _cabi.check(_cabi.lib().ab200_tile_decay_weights(t._h, 0.5, 1, None))
+    w = O.decay_weights(w, names, hp, 0.5, True)
+    assert np.array_equal(t.get_weights().numpy(), w)
+    wc = D.WeightClipParameter()
+    wc.type, wc.fixed_value = D.WeightClipType.FixedValue, 0.25
+    t.clip_weights(wc)
+    w = O.clip_to_device(w, names, hp, 0.25)
+    assert np.array_equal(t.get_weights().numpy(), w)
+    wc.type = D.WeightClipType.LayerGaussian
+    with pytest.raises(RuntimeError, match="Sophisticated clipping"):
+        t.clip_weights(wc)
+    if ref.available():
+        rt = ref.RefTile(cfg)
+        rt.set_weights(w)
+        rt.decay_weights(0.7)
+        t.decay_weights(0.7)
+        assert np.array_equal(t.get_weights().numpy(), rt.get_weights())
+
+
+def test_floating_point_tile_ops():
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(6)
+    x_size, d_size = 130, 40
+    ideal = D.IdealResistiveDeviceParameter()
+    ideal.lifetime, ideal.diffusion, ideal.reset_std = 20.0, 0.05, 0.1
+    p = H.training_params(noise=False, pulse_det=True)
+    t = _tile(p._config(x_size, d_size, ideal, seed=3))
+    w = rng.normal(0, 0.3, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(w))
+    t.decay_weights(0.5)
+    w = O.decay_weights_simple(w, 20.0, 0.5)
+    assert np.array_equal(t.get_weights().numpy(), w)
+    wc = D.WeightClipParameter()
+    for ctype, fixed in ((D.WeightClipType.LayerGaussian, -1.0), (D.WeightClipType.AverageChannelMax, -1.0),
+                         (D.WeightClipType.AverageChannelMax, 0.4), (D.WeightClipType.FixedValue, 0.2)):
+        wc.type, wc.fixed_value, wc.sigma = ctype, fixed, 1.5
+        c = O.clip_value(w, int(ctype), fixed, 1.5)
+        t.clip_weights(wc)
+        w = np.clip(w, -np.float32(c), np.float32(c))
+        assert np.abs(t.get_weights().numpy() - w).max() <= 2e-6
+    # diffusion: one global rate, no bounds
+    before = t.get_weights().numpy()
+    t.diffuse_weights()
+    mid = t.get_weights().numpy()
+    delta = mid - before
+    assert abs(delta.std() / 0.05 - 1) < 0.05 and abs(delta.mean()) < 4 * 0.05 / np.sqrt(delta.size)
+    # reset: N(0, reset_std) in the chosen columns only
+    t.reset_columns(128, 5, 1.0)  # 128, 129, 0, 1, 2
+    after = t.get_weights().numpy()
+    cols = [128, 129, 0, 1, 2]
+    assert abs(after[:, cols].std() / 0.1 - 1) < 0.15
+    keep = [c for c in range(x_size) if c not in cols]
+    assert np.array_equal(after[:, keep], mid[:, keep])
+    t.set_weights_uniform_random(-0.3, 0.5)
+    u = t.get_weights().numpy()
+    assert u.min() >= -0.3 and u.max() <= 0.5 and abs(u.mean() - 0.1) < 0.01
+    assert abs(u.std() - 0.8 / np.sqrt(12)) < 0.01
+
+
+def test_diffusion_and_reset_moments_against_reference():
+    """Per-element diffusion rates and reset biases: the GPU samples and the reference's samples
+    have the same element-wise means and standard deviations."""
+    x_size, d_size, reps = 12, 10, 300
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = _device()
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = _tile(cfg)
+    names, hp = t.get_hidden_parameter_names(), t.get_hidden_parameters().numpy()
+    rate, bias = hp[names.index("diffusion_rates")], hp[names.index("reset_bias")]
+    hi, lo = hp[names.index("max_bound")], hp[names.index("min_bound")]
+    w0 = torch.zeros(d_size, x_size)
+    diffs, resets, partial = [], [], []
+    for _ in range(reps):
+        t.set_weights(w0)
+        t.diffuse_weights()
+        diffs.append(t.get_weights().numpy())
+        t.reset_columns(10, 4, 1.0)
+        resets.append(t.get_weights().numpy())
+        t.set_weights(w0 + 0.3)
+        t.reset_columns(0, -1, 0.25)  # every column, a quarter of the elements
+        partial.append(t.get_weights().numpy())
+    diffs, resets, partial = np.stack(diffs), np.stack(resets), np.stack(partial)
+    assert np.abs(diffs.std(0) / rate - 1).mean() < 0.06
+    assert (diffs <= hi).all() and (diffs >= lo).all()
+    cols = [10, 11, 0, 1]
+    assert np.abs(resets[:, :, cols].mean(0) - bias[:, cols]).max() < 5 * dp.reset_std / np.sqrt(reps) + 1e-3
+    assert abs(resets[:, :, cols].std(0).mean() / dp.reset_std - 1) < 0.08
+    assert np.array_equal(resets[:, :, 2:10], diffs[:, :, 2:10])
+    untouched = np.isclose(partial, np.minimum(0.3, hi)[None])
+    assert abs((~untouched).mean() - 0.25) < 0.02
+    if ref.available():
+        rt = ref.RefTile(cfg)
+        rt.set_seed(7)
+        rd = []
+        for _ in range(reps):
+            rt.set_weights(w0.numpy())
+            rt.diffuse_weights()
+            rd.append(rt.get_weights())
+        H.assert_moments_agree(diffs, np.stack(rd))
+
+
+def test_compound_device_is_rejected():
+    p = H.training_params(noise=False, pulse_det=True)
+    t = _tile(p._config(8, 6, H.transfer_device(noise=False), seed=3))
+    with pytest.raises(RuntimeError, match="compound"):
+        t.decay_weights()
