@@ -97,6 +97,14 @@ class DeviceParams(C.Structure):
         ("reset", C.c_float),
         ("reset_dtod", C.c_float),
         ("reset_std", C.c_float),
+        ("es_A_up", C.c_float),
+        ("es_A_down", C.c_float),
+        ("es_gamma_up", C.c_float),
+        ("es_gamma_down", C.c_float),
+        ("es_a", C.c_float),
+        ("es_b", C.c_float),
+        ("dw_min_std_add", C.c_float),
+        ("dw_min_std_slope", C.c_float),
     ]
 
 

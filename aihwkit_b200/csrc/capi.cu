@@ -97,6 +97,12 @@ void ab200_default_device_params(ab200_device_params *dp, int32_t kind) {
   dp->ls_mean_bound_reference = 1;
   dp->ls_decrease_up_dtod = 0.05f;
   dp->ls_decrease_down_dtod = 0.05f;
+  dp->es_A_up = 0.00081f;
+  dp->es_A_down = 0.36833f;
+  dp->es_gamma_up = 12.44625f;
+  dp->es_gamma_down = 12.78785f;
+  dp->es_a = 0.244f;
+  dp->es_b = 0.2425f;
   if (kind == AB200_DEVICE_SOFT_BOUNDS) {
     dp->ls_decrease_up = dp->ls_decrease_down = 1.0f;
     dp->ls_decrease_up_dtod = dp->ls_decrease_down_dtod = 0.0f;

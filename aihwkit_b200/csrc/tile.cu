@@ -127,6 +127,18 @@ void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_
   ds.kind = kind;
   ds.dw_min = par.dw_min;
   ds.dw_min_std = par.dw_min_std;
+  if (kind == AB200_DEVICE_EXP_STEP) {
+    ds.es0 = make_float4(par.es_a, par.es_b, par.es_A_up, par.es_A_down);
+    ds.es1 = make_float4(par.es_gamma_up, par.es_gamma_down, par.dw_min_std_add, par.dw_min_std_slope);
+    // ExpStepRPUDeviceMetaParameter::calcWeightGranularity (rpu_expstep_device.h:43-55): the step
+    // at w = 0 (the reference averages the down step with itself)
+    const float down_bias = par.up_down > 0.0f ? -par.up_down : 0.0f;
+    const float scale_down = (down_bias + 1.0f) * par.dw_min;
+    const float z = par.es_b;
+    const float dw_down = scale_down * fmaxf(1.0f - par.es_A_down * expf(par.es_gamma_down * (-z)), 0.0f);
+    const float g = fmaxf((dw_down + dw_down) / 2.0f, 0.0f);
+    ds.dw_min = g > 0.0f ? g : par.dw_min;
+  }
   ds.mult_noise = kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE ? par.mult_noise : par.ls_mult_noise;
   ds.names = deviceNames(kind);
   const size_t size = (size_t)x_size * d_size;
@@ -242,7 +254,8 @@ void Tile::populateHost() {
     n_dev_ = 2;
     for (int k = 0; k < 2; k++) {
       int kind = cfg_.device[k].kind;
-      if (kind < AB200_DEVICE_CONSTANT_STEP || kind > AB200_DEVICE_SOFT_BOUNDS_REFERENCE) {
+      if ((kind < AB200_DEVICE_CONSTANT_STEP || kind > AB200_DEVICE_SOFT_BOUNDS_REFERENCE) &&
+          kind != AB200_DEVICE_EXP_STEP) {
         AB200_FATAL("Transfer: unit cell device kind not implemented");
       }
       populateDevice(cfg_.device[k], kind, x_size_, d_size_, rng, dev_[k]);
@@ -262,7 +275,7 @@ Tile::Tile(const ab200_tile_config &cfg, int cuda_device) : cfg_(cfg) {
   f_io_ = resolveIO(cfg.forward_io, false);
   b_io_ = resolveIO(cfg.backward_io, true);
   up_ = resolveUp(cfg.update);
-  if (cfg.device_kind < AB200_DEVICE_IDEAL || cfg.device_kind > AB200_DEVICE_TRANSFER) {
+  if (cfg.device_kind < AB200_DEVICE_IDEAL || cfg.device_kind > AB200_DEVICE_EXP_STEP) {
     AB200_FATAL("device kind not implemented");
   }
   if (cfg.device_kind == AB200_DEVICE_TRANSFER) {
@@ -891,6 +904,8 @@ void Tile::doTransfer(cudaStream_t s) {
     u.par2 = dev_[1].par2;
     u.kind = dev_[1].kind;
     u.dw_min_std = dev_[1].dw_min_std;
+    u.es0 = dev_[1].es0;
+    u.es1 = dev_[1].es1;
     u.mult_noise = dev_[1].mult_noise;
     u.s_begin = 0;
     u.s_end = 1;
@@ -961,6 +976,8 @@ void Tile::update(const float *x, const float *d, bool bias, int m, bool x_trans
   u.par2 = dev_[0].par2;
   u.kind = dev_[0].kind;
   u.dw_min_std = dev_[0].dw_min_std;
+  u.es0 = dev_[0].es0;
+  u.es1 = dev_[0].es1;
   u.mult_noise = dev_[0].mult_noise;
   launchPulsePrepare(u, s);
 

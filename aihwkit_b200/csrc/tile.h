@@ -101,6 +101,8 @@ struct DeviceStore {
   float4 *par3 = nullptr; // {decay_scale, diffusion_rate, reset_bias, 0}; uploaded on first use
   bool par3_valid = false;
   float reset_std = 0.0f;
+  // ExpStep: {a, b, A_up, A_down} and {gamma_up, gamma_down, dw_min_std_add, dw_min_std_slope}
+  float4 es0 = {0.f, 0.f, 0.f, 0.f}, es1 = {0.f, 0.f, 0.f, 0.f};
   // host copies, [name][d][x] in the reference's naming / order
   std::vector<std::string> names;
   std::vector<float> host;
@@ -131,6 +133,7 @@ struct UpdateProblem {
   int kind;
   float dw_min_std;
   int mult_noise;
+  float4 es0, es1; // ExpStep globals (DeviceStore)
   int s_begin, s_end; // sample range applied by the update kernel
 };
 

@@ -191,9 +191,33 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
 // par4 = {scale_up, scale_down, max_bound, min_bound}
 // ---------------------------------------------------------------------------------------------
 template <int KIND>
-__device__ __forceinline__ float
-pulseOnce(float w, bool down, const float4 &q, const float2 &e, float xi, int mult_noise) {
-  if (KIND == AB200_DEVICE_CONSTANT_STEP) {
+__device__ __forceinline__ float pulseOnce(float w, bool down, const float4 &q, const float2 &e,
+                                           float xi, int mult_noise, const float4 &es0,
+                                           const float4 &es1) {
+  if (KIND == AB200_DEVICE_EXP_STEP) {
+    // ExpStepRPUDevice update_once / update_once_complex_noise (rpu_expstep_device.cpp:18-100):
+    // z = 2 w / (max - min) * a + b;  step = scale * max(1 - A exp(+-gamma z), 0)
+    // es0 = {a, b, A_up, A_down}, es1 = {gamma_up, gamma_down, std_add, std_slope}; xi = std * N
+    const float b_diff = __fsub_rn(q.z, q.w);
+    if (!(b_diff > 0.0f)) {
+      return w;
+    }
+    const float z = __fadd_rn(__fmul_rn(__fdiv_rn(__fmul_rn(2.0f, w), b_diff), es0.x), es0.y);
+    const float y = down ? fmaxf(__fsub_rn(1.0f, __fmul_rn(es0.w, expf(__fmul_rn(es1.y, -z)))), 0.0f)
+                         : fmaxf(__fsub_rn(1.0f, __fmul_rn(es0.z, expf(__fmul_rn(es1.x, z)))), 0.0f);
+    if (es1.z != 0.0f || es1.w != 0.0f) {
+      const float dw = down ? -__fmul_rn(y, q.y) : __fmul_rn(y, q.x);
+      const float spread =
+          __fadd_rn(__fadd_rn(fabsf(dw), es1.z), __fmul_rn(es1.w, fabsf(w)));
+      w = __fadd_rn(w, __fadd_rn(dw, __fmul_rn(spread, xi)));
+    } else {
+      const float step = __fmul_rn(__fmul_rn(y, __fadd_rn(1.0f, xi)), down ? q.y : q.x);
+      w = down ? __fsub_rn(w, step) : __fadd_rn(w, step);
+    }
+    w = fminf(w, q.z);
+    w = fmaxf(w, q.w);
+    return w;
+  } else if (KIND == AB200_DEVICE_CONSTANT_STEP) {
     float dw = __fmul_rn(__fadd_rn(1.0f, xi), down ? q.y : q.x);
     w = down ? __fsub_rn(w, dw) : __fadd_rn(w, dw);
     w = fminf(w, q.z);
@@ -423,7 +447,7 @@ __global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
           if (!loaded[0]) {
             w[0] = p.w[idx];
             q[0] = p.par4[idx];
-            if (KIND != AB200_DEVICE_CONSTANT_STEP) {
+            if (KIND != AB200_DEVICE_CONSTANT_STEP && KIND != AB200_DEVICE_EXP_STEP) {
               e[0] = p.par2[idx];
             }
             loaded[0] = true;
@@ -432,7 +456,7 @@ __global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
         }
         if (!NOISY) {
           for (int k = 0; k < n; k++) {
-            w[0] = pulseOnce<KIND>(w[0], down, q[0], e[0], 0.0f, p.mult_noise);
+            w[0] = pulseOnce<KIND>(w[0], down, q[0], e[0], 0.0f, p.mult_noise, p.es0, p.es1);
           }
         } else {
           // One Gaussian per pulse, taken from a per-thread reservoir in shared memory: the
@@ -452,7 +476,8 @@ __global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
               refills++;
             }
             rc--;
-            w[0] = pulseOnce<KIND>(w[0], down, q[0], e[0], std * sm.sz[rc][threadIdx.x], p.mult_noise);
+            w[0] = pulseOnce<KIND>(w[0], down, q[0], e[0], std * sm.sz[rc][threadIdx.x], p.mult_noise, p.es0,
+                                    p.es1);
           }
         }
       }
@@ -570,6 +595,9 @@ void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream) {
     break;
   case AB200_DEVICE_SOFT_BOUNDS_REFERENCE:
     AB200_UPD(AB200_DEVICE_SOFT_BOUNDS_REFERENCE);
+    break;
+  case AB200_DEVICE_EXP_STEP:
+    AB200_UPD(AB200_DEVICE_EXP_STEP);
     break;
   default:
     AB200_FATAL("pulsed update: device kind not implemented");

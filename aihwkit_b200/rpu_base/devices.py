@@ -70,6 +70,7 @@ DEVICE_LINEAR_STEP = 2
 DEVICE_SOFT_BOUNDS = 3
 DEVICE_SOFT_BOUNDS_REFERENCE = 4
 DEVICE_TRANSFER = 5
+DEVICE_EXP_STEP = 6
 
 
 class AnalogTileInputOutputParameter:
@@ -289,6 +290,45 @@ class ConstantStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):
     """rpu_base_devices.cpp:583-600."""
 
     _kind = DEVICE_CONSTANT_STEP
+
+
+class ExpStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):
+    """rpu_base_devices.cpp:658-683 (ExpStepRPUDeviceMetaParameter, rpu_expstep_device.h:22-29)."""
+
+    _kind = DEVICE_EXP_STEP
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.A_up = 0.00081
+        self.A_down = 0.36833
+        self.gamma_up = 12.44625
+        self.gamma_down = 12.78785
+        self.a = 0.244
+        self.b = 0.2425
+        self.write_noise_std = 0.0
+        self.apply_write_noise_on_set = True
+        self.dw_min_std_add = 0.0
+        self.dw_min_std_slope = 0.0
+
+    def calc_weight_granularity(self) -> float:
+        """ExpStepRPUDeviceMetaParameter::calcWeightGranularity (rpu_expstep_device.h:43-55)."""
+        import math
+
+        down_bias = -self.up_down if self.up_down > 0 else 0.0
+        dw_down = (down_bias + 1.0) * self.dw_min * max(
+            1.0 - self.A_down * math.exp(self.gamma_down * (-self.b)), 0.0)
+        return dw_down if dw_down > 0 else float(self.dw_min)
+
+    def _to_c(self) -> _cabi.DeviceParams:
+        if self.write_noise_std != 0.0:
+            raise RuntimeError("write noise is not implemented by the B200 analog tile")
+        c = _cabi.DeviceParams()
+        self._fill_base(c)
+        c.es_A_up, c.es_A_down = float(self.A_up), float(self.A_down)
+        c.es_gamma_up, c.es_gamma_down = float(self.gamma_up), float(self.gamma_down)
+        c.es_a, c.es_b = float(self.a), float(self.b)
+        c.dw_min_std_add, c.dw_min_std_slope = float(self.dw_min_std_add), float(self.dw_min_std_slope)
+        return c
 
 
 class LinearStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):

@@ -68,7 +68,8 @@ enum ab200_device_kind {
   AB200_DEVICE_LINEAR_STEP = 2,           /* rpu_linearstep_device.h */
   AB200_DEVICE_SOFT_BOUNDS = 3,           /* rpu_linearstep_device.h:70-83 */
   AB200_DEVICE_SOFT_BOUNDS_REFERENCE = 4, /* rpu_softbounds_reference_device.h */
-  AB200_DEVICE_TRANSFER = 5               /* rpu_transfer_device.h (Tiki-Taka) */
+  AB200_DEVICE_TRANSFER = 5,              /* rpu_transfer_device.h (Tiki-Taka) */
+  AB200_DEVICE_EXP_STEP = 6               /* rpu_expstep_device.h */
 };
 
 /* IOMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:180-226); attribute names as
@@ -157,6 +158,16 @@ typedef struct ab200_device_params {
   float reset;
   float reset_dtod;
   float reset_std;
+  /* ExpStep (ExpStepRPUDeviceMetaParameter, rpu_expstep_device.h:22-29; bound as A_up, A_down,
+   * gamma_up, gamma_down, a, b, dw_min_std_add, dw_min_std_slope) */
+  float es_A_up;
+  float es_A_down;
+  float es_gamma_up;
+  float es_gamma_down;
+  float es_a;
+  float es_b;
+  float dw_min_std_add;
+  float dw_min_std_slope;
 } ab200_device_params;
 
 /* TransferRPUDeviceMetaParameter (src/rpucuda/rpu_transfer_device.h:52-75). */

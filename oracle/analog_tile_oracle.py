@@ -38,6 +38,7 @@ WN_NONE, WN_ADDITIVE_CONSTANT = 0, 1
 PULSE_NONE, PULSE_STOCHASTIC_COMPRESSED, PULSE_DETERMINISTIC_IMPLICIT = 0, 1, 5
 DEV_IDEAL, DEV_CONSTANT_STEP, DEV_LINEAR_STEP, DEV_SOFT_BOUNDS, DEV_SOFT_BOUNDS_REFERENCE = range(5)
 DEV_TRANSFER = 5
+DEV_EXP_STEP = 6
 
 
 def _check_res(res: float) -> np.float32:
@@ -386,6 +387,8 @@ class DeviceArrays:
     reference: Optional[np.ndarray] = None
     dw_min_std: float = 0.0
     mult_noise: bool = True
+    # ExpStep globals: (a, b, A_up, A_down, gamma_up, gamma_down, dw_min_std_add, dw_min_std_slope)
+    es: Optional[tuple] = None
 
     @staticmethod
     def from_hidden(kind: int, names, hp: np.ndarray, dw_min_std: float, mult_noise: bool, suffix=""):
@@ -453,6 +456,25 @@ def apply_pulses(w: np.ndarray, n_signed: np.ndarray, dev: DeviceArrays,
             wn = np.where(down, wr - dn, wr + up_).astype(f32)
             wn = np.minimum(np.maximum(wn, dev.min_bound), dev.max_bound)
             wn = (wn - dev.reference).astype(f32)
+        elif dev.kind == DEV_EXP_STEP:
+            # rpu_expstep_device.cpp:18-100 (expf in fp32)
+            a, b, A_up, A_dn, g_up, g_dn, s_add, s_slope = (f32(v) for v in dev.es)
+            b_diff = (dev.max_bound - dev.min_bound).astype(f32)
+            with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+                z = ((f32(2.0) * w / b_diff).astype(f32) * a + b).astype(f32)
+                y_dn = np.maximum(f32(1.0) - A_dn * np.exp((g_dn * (-z)).astype(f32)).astype(f32), f32(0))
+                y_up = np.maximum(f32(1.0) - A_up * np.exp((g_up * z).astype(f32)).astype(f32), f32(0))
+            if std > 0 and (s_add != 0 or s_slope != 0):
+                dw = np.where(down, -(y_dn * dev.dwmin_down), y_up * dev.dwmin_up).astype(f32)
+                # the oracle's xi already carries dw_min_std
+                spread = (np.abs(dw) + s_add + s_slope * np.abs(w)).astype(f32)
+                wn = (w + (dw + spread * xi)).astype(f32)
+            else:
+                dn = ((y_dn * (f32(1.0) + xi)).astype(f32) * dev.dwmin_down).astype(f32)
+                up_ = ((y_up * (f32(1.0) + xi)).astype(f32) * dev.dwmin_up).astype(f32)
+                wn = np.where(down, w - dn, w + up_).astype(f32)
+            wn = np.maximum(np.minimum(wn, dev.max_bound), dev.min_bound)
+            wn = np.where(b_diff > 0, wn, w)
         else:
             raise NotImplementedError("device kind")
         w[act] = wn[act]

@@ -13,6 +13,7 @@
 
 #include "dense_bit_line_maker.h"
 #include "rpu_constantstep_device.h"
+#include "rpu_expstep_device.h"
 #include "rpu_linearstep_device.h"
 #include "rpu_pulsed.h"
 #include "rpu_softbounds_reference_device.h"
@@ -121,6 +122,19 @@ std::unique_ptr<PulsedRPUDeviceMetaParameter<float>> makeSingle(const ab200_devi
     p->slope_down_dtod = s.slope_down_dtod;
     p->reference_mean = s.reference_mean;
     p->reference_std = s.reference_std;
+    return p;
+  }
+  case AB200_DEVICE_EXP_STEP: {
+    auto p = std::make_unique<ExpStepRPUDeviceMetaParameter<float>>();
+    toPulsedBase(s, *p);
+    p->es_A_up = s.es_A_up;
+    p->es_A_down = s.es_A_down;
+    p->es_gamma_up = s.es_gamma_up;
+    p->es_gamma_down = s.es_gamma_down;
+    p->es_a = s.es_a;
+    p->es_b = s.es_b;
+    p->dw_min_std_add = s.dw_min_std_add;
+    p->dw_min_std_slope = s.dw_min_std_slope;
     return p;
   }
   default:

@@ -12,6 +12,7 @@ KINDS = {
     "ls": D.LinearStepResistiveDeviceParameter,
     "sb": D.SoftBoundsResistiveDeviceParameter,
     "sbr": D.SoftBoundsReferenceResistiveDeviceParameter,
+    "es": D.ExpStepResistiveDeviceParameter,
 }
 
 

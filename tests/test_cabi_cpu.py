@@ -30,7 +30,7 @@ def test_struct_sizes_match_header():
     # layouts are plain int32 / float / uint64 fields; sizes are what a C compiler produces
     assert C.sizeof(_cabi.IOParams) == 20 * 4
     assert C.sizeof(_cabi.UpdateParams) == 10 * 4
-    assert C.sizeof(_cabi.DeviceParams) == 34 * 4
+    assert C.sizeof(_cabi.DeviceParams) == 42 * 4
     assert C.sizeof(_cabi.TransferParams) == 9 * 4 + 20 * 4 + 10 * 4
     assert C.sizeof(_cabi.TileConfig) % 8 == 0
 
@@ -49,13 +49,16 @@ def test_defaults_follow_reference_member_initialisers():
         assert getattr(up, name) == pytest.approx(getattr(refu, name)), name
     for kind, cls in ((D.DEVICE_CONSTANT_STEP, D.ConstantStepResistiveDeviceParameter),
                       (D.DEVICE_SOFT_BOUNDS, D.SoftBoundsResistiveDeviceParameter),
-                      (D.DEVICE_LINEAR_STEP, D.LinearStepResistiveDeviceParameter)):
+                      (D.DEVICE_LINEAR_STEP, D.LinearStepResistiveDeviceParameter),
+                      (D.DEVICE_EXP_STEP, D.ExpStepResistiveDeviceParameter)):
         dp = _cabi.DeviceParams()
         lib.ab200_default_device_params(C.byref(dp), kind)
         refd = cls()._to_c()
         for name, _ in _cabi.DeviceParams._fields_:
-            if kind == D.DEVICE_CONSTANT_STEP and name.startswith("ls_"):
-                continue  # LinearStep-only fields are not read for ConstantStep
+            if kind in (D.DEVICE_CONSTANT_STEP, D.DEVICE_EXP_STEP) and name.startswith("ls_"):
+                continue  # LinearStep-only fields are not read for other kinds
+            if kind != D.DEVICE_EXP_STEP and name.startswith("es_"):
+                continue  # ExpStep-only fields
             assert getattr(dp, name) == pytest.approx(getattr(refd, name)), (kind, name)
 
 

@@ -11,7 +11,7 @@ from tests import helpers as H
 pytestmark = pytest.mark.skipif(not ref.available(), reason="oracle/_ref not built")
 
 KIND = {"cs": O.DEV_CONSTANT_STEP, "ls": O.DEV_LINEAR_STEP, "sb": O.DEV_SOFT_BOUNDS,
-        "sbr": O.DEV_SOFT_BOUNDS_REFERENCE}
+        "sbr": O.DEV_SOFT_BOUNDS_REFERENCE, "es": O.DEV_EXP_STEP}
 
 
 @pytest.mark.parametrize("kind", ["cs", "ls", "sb", "sbr"])
@@ -215,3 +215,42 @@ def test_host_parameter_draw_with_decay_diffusion_reset(kind):
     t = ref.RefTile(cfg)
     assert ours.get_hidden_parameter_names() == t.hidden_parameter_names()
     assert np.array_equal(ours.get_hidden_parameters().numpy(), t.get_hidden_parameters())
+
+
+def _es_tuple(dp):
+    return (dp.a, dp.b, dp.A_up, dp.A_down, dp.gamma_up, dp.gamma_down, dp.dw_min_std_add,
+            dp.dw_min_std_slope)
+
+
+@pytest.mark.parametrize("shape", [(96, 64, 32), (33, 70, 5)])
+def test_exp_step_device_noise_off(shape):
+    """ExpStep device: granularity, host parameter draw and the weights after a deterministic
+    update (expf of numpy vs glibc: last-bit differences allowed)."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    x_size, d_size, m = shape
+    rng = np.random.default_rng(x_size)
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+    dp = H.device("es", False, A_up=0.1, A_down=0.3, gamma_up=3.0, gamma_down=2.5)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = ref.RefTile(cfg)
+    ours = T.AnalogTile(cfg)
+    assert np.array_equal(ours.get_hidden_parameters().numpy(), t.get_hidden_parameters())
+    t.set_weights(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32))
+    W = t.get_weights()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+    lr = 0.01
+    gran = dp.calc_weight_granularity()
+    up = O.Up.from_c(cfg.update)
+    assert np.array_equal(t.coincidences(X[0], Dm[0], lr, gran),
+                          O.coincidences_det_implicit(X[0], Dm[0], lr, gran, up))
+    dev = O.DeviceArrays.from_hidden(O.DEV_EXP_STEP, t.hidden_parameter_names(),
+                                     t.get_hidden_parameters(), 0.0, True)
+    dev.es = _es_tuple(dp)
+    t.set_learning_rate(lr)
+    t.update(X, Dm)
+    Wo = W.copy()
+    O.update(Wo, X, Dm, lr, gran, up, dev)
+    assert np.abs(t.get_weights() - Wo).max() <= 2e-6
+    assert np.abs(t.get_weights() - W).max() > 1e-3  # the update did something

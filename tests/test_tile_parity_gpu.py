@@ -267,3 +267,67 @@ def test_empty_batch_and_errors():
     w0 = t.get_weights()
     t.update(torch.ones(4, 16).cuda(), torch.ones(4, 8).cuda())
     assert torch.equal(w0, t.get_weights())
+
+
+def _exp_step_device(noise, **kw):
+    return H.device("es", noise, A_up=0.1, A_down=0.3, gamma_up=3.0, gamma_down=2.5, **kw)
+
+
+def _es_arrays(t, dp, std):
+    dev = O.DeviceArrays.from_hidden(O.DEV_EXP_STEP, t.get_hidden_parameter_names(),
+                                     t.get_hidden_parameters().numpy(), std, True)
+    dev.es = (dp.a, dp.b, dp.A_up, dp.A_down, dp.gamma_up, dp.gamma_down, dp.dw_min_std_add,
+              dp.dw_min_std_slope)
+    return dev
+
+
+@pytest.mark.parametrize("x_size,d_size,m", [(64, 48, 17), (70, 130, 9)])
+def test_exp_step_deterministic_update(x_size, d_size, m):
+    """ExpStep device (rpu_expstep_device.cpp): bit-exact pulse counts with the device's own weight
+    granularity, weights after the update within the expf rounding of the two platforms."""
+    rng = np.random.default_rng(3 + x_size)
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = _exp_step_device(False)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    up = O.Up.from_c(cfg.update)
+    lr, gran = 0.01, dp.calc_weight_granularity()
+    t.set_learning_rate(lr)
+    c = t.coincidences(torch.from_numpy(X[0]).cuda(), torch.from_numpy(Dm[0]).cuda()).cpu().numpy()
+    assert np.array_equal(c, O.coincidences_det_implicit(X[0], Dm[0], lr, gran, up))
+    W_or = W.copy()
+    O.update(W_or, X, Dm, lr, gran, up, _es_arrays(t, dp, 0.0))
+    t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    W_new = t.get_weights().numpy()
+    assert np.abs(W_new - W).max() > 1e-3
+    assert np.abs(W_new - W_or).max() <= 2e-6
+
+
+@pytest.mark.parametrize("complex_noise", [False, True])
+def test_exp_step_stochastic_update_statistics(complex_noise):
+    rng = np.random.default_rng(19)
+    x_size, d_size, m, reps = 32, 24, 10, 150
+    p = H.training_params(noise=True, pulse_det=False)
+    kw = dict(dw_min_std_add=0.5, dw_min_std_slope=0.3) if complex_noise else {}
+    dp = _exp_step_device(True, **kw)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    W0 = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    up = O.Up.from_c(cfg.update)
+    dev = _es_arrays(t, dp, dp.dw_min_std)
+    lr, gran = 0.05, dp.calc_weight_granularity()
+    t.set_learning_rate(lr)
+    xg, dg = torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda()
+    dws, dwo = [], []
+    org = np.random.default_rng(123)
+    for _ in range(reps):
+        t.set_weights(torch.from_numpy(W0))
+        Wc = t.get_weights().numpy()
+        t.update(xg, dg)
+        dws.append(t.get_weights().numpy() - Wc)
+        Wo = Wc.copy()
+        O.update(Wo, X, Dm, lr, gran, up, dev, org)
+        dwo.append(Wo - Wc)
+    H.assert_moments_agree(np.stack(dws), np.stack(dwo))
