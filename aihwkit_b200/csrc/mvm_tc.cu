@@ -78,8 +78,9 @@ struct TcKernelParams {
   IOEff io;
   int *status;
   // optional per-CTA cycle counters of time spent waiting, by role (diagnostics; null = off):
-  // [0] MMA on operands, [2] MMA on a free accumulator, [3] MMA total, [4] TMA producer on a
-  // free stage, [6] epilogue on a complete accumulator, [7] epilogue total
+  // [0] MMA on operands, [1] MMA issuing instructions, [2] MMA on a free accumulator, [3] MMA
+  // total, [4] TMA producer on a free stage, [5] TMA producer issuing copies, [6] epilogue on a
+  // complete accumulator, [7] epilogue total
   long long *prof;
 };
 
@@ -268,6 +269,9 @@ constexpr uint32_t kIdescPair = (1u << 4) | (1u << 7) | (1u << 10) |
 
 #define TC_TIMED_WAIT(acc, expr)                                                                   \
   ([&]() {                                                                                         \
+    if (!timed) {                                                                                  \
+      return (expr);                                                                               \
+    }                                                                                              \
     const long long t_ = clock64();                                                                \
     const bool r_ = (expr);                                                                        \
     (acc) += clock64() - t_;                                                                       \
@@ -301,6 +305,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool timed = p.prof != nullptr;
   const int rank = PAIR ? (int)clusterCtaRank() : 0; // rank 0 of a pair issues the MMAs
   // persistent CTA (pair): work item w = (row block, 128-column chunk). Items are ordered so that
   // a group of `p.group` chunks is finished for every row block before the next group starts: the
@@ -363,7 +368,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      long long w_empty = 0;
+      long long w_empty = 0, w_issue = 0;
       for (int w = worker; w < n_items && ok; w += n_workers) {
       int chunk_idx, rb;
       item(w, chunk_idx, rb);
@@ -380,6 +385,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             break;
           }
           uint8_t *st = smem + s * STAGE_BYTES;
+          const long long t_issue = timed ? clock64() : 0;
           if (PAIR) {
             // rank 0 announces the bytes of both CTAs on its barrier; both CTAs' copies count there
             const uint32_t leader_bar = mapaShared(smemAddr(&full[s]), 0);
@@ -393,6 +399,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             tmaLoad2d(st, &tm_a, &full[s], is.x + kc * TC_K, r0);
             tmaLoad2d(st + TC_STAGE_A, &tm_bhi, &full[s], kc * TC_K, brow);
             tmaLoad2d(st + TC_STAGE_A + TC_STAGE_B, &tm_blo, &full[s], kc * TC_K, brow);
+          }
+          if (timed) {
+            w_issue += clock64() - t_issue;
           }
         }
       }
@@ -408,6 +417,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       }
       if (p.prof) {
         p.prof[blockIdx.x * 8 + 4] = w_empty;
+        p.prof[blockIdx.x * 8 + 5] = w_issue;
       }
     }
   } else if (warp == TC_WARP_MMA) {
@@ -415,7 +425,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     if (lane == 0 && rank == 0) {
       int it = 0, ai = 0; // pipeline stage counter, accumulator-buffer use counter
       bool ok = true;
-      long long w_full = 0, w_tmem = 0;
+      long long w_full = 0, w_tmem = 0, w_mma = 0;
       const long long t_start = clock64();
       for (int w = worker; w < n_items && ok; w += n_workers) {
       for (int i = 0; i < p.I && ok; i++, ai++) {
@@ -438,6 +448,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             break;
           }
           tcFenceAfter();
+          const long long t_mma = timed ? clock64() : 0;
           const uint32_t a0 = smemAddr(smem + s * STAGE_BYTES);
           // single CTA: the B descriptor starts at the hi tile and its 256 rows run on into the
           // lo tile. Pair: each CTA supplies 128 of the 256 B rows from the same offset.
@@ -457,6 +468,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           } else {
             tcCommit(&empty[s]);
           }
+          if (timed) {
+            w_mma += clock64() - t_mma;
+          }
         }
         if (ok) {
           // accumulator of in-split i is complete
@@ -470,6 +484,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       }
       if (p.prof) {
         p.prof[blockIdx.x * 8 + 0] = w_full;
+        p.prof[blockIdx.x * 8 + 1] = w_mma;
         p.prof[blockIdx.x * 8 + 2] = w_tmem;
         p.prof[blockIdx.x * 8 + 3] = clock64() - t_start;
       }
@@ -1068,9 +1083,10 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
       }
     }
     fprintf(stderr,
-            "[ab200 tc] cycles/CTA: mma total %.0f (wait operands %.0f, accumulator %.0f) | "
-            "tma wait stage %.0f | epilogue total %.0f (wait accumulator %.0f)\n",
-            avg[3], avg[0], avg[2], avg[4], avg[7], avg[6]);
+            "[ab200 tc] cycles/CTA: mma total %.0f (wait operands %.0f, accumulator %.0f, issuing "
+            "%.0f) | tma wait stage %.0f, issuing %.0f | epilogue total %.0f (wait accumulator "
+            "%.0f)\n",
+            avg[3], avg[0], avg[2], avg[1], avg[4], avg[5], avg[7], avg[6]);
   }
 }
 
