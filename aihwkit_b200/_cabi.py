@@ -186,6 +186,10 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_forward_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _I, _VP]),
         "ab200_tile_backward_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _VP]),
         "ab200_tile_update_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _VP]),
+        "ab200_tile_extra_count": (_I, []),
+        "ab200_tile_extra_name": (C.c_char_p, [_I]),
+        "ab200_tile_dump_extra": (_I, [_VP, C.POINTER(C.c_double)]),
+        "ab200_tile_load_extra": (_I, [_VP, C.POINTER(C.c_char_p), C.POINTER(C.c_double), _I, _I]),
         "ab200_tile_decay_weights": (_I, [_VP, C.c_float, _I, _VP]),
         "ab200_tile_diffuse_weights": (_I, [_VP, _VP]),
         "ab200_tile_clip_weights": (_I, [_VP, _I, C.c_float, C.c_float, _VP]),

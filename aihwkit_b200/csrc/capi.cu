@@ -303,6 +303,30 @@ int ab200_tile_update_indexed(ab200_tile *tile, const float *x_dev, const float 
   AB200_CATCH
 }
 
+int ab200_tile_extra_count(void) { return ab200::Tile::extraCount(); }
+
+const char *ab200_tile_extra_name(int k) {
+  try {
+    return ab200::Tile::extraName(k);
+  } catch (const std::exception &e) {
+    g_error = e.what();
+    return nullptr;
+  }
+}
+
+int ab200_tile_dump_extra(ab200_tile *tile, double *values) {
+  AB200_TRY
+  T(tile)->dumpExtra(values);
+  AB200_CATCH
+}
+
+int ab200_tile_load_extra(ab200_tile *tile, const char *const *names, const double *values,
+                          int count, int strict) {
+  AB200_TRY
+  T(tile)->loadExtra(names, values, count, strict != 0);
+  AB200_CATCH
+}
+
 int ab200_tile_decay_weights(ab200_tile *tile, float alpha, int bias_no_decay, void *stream) {
   AB200_TRY
   T(tile)->decayWeights(alpha, bias_no_decay != 0, (cudaStream_t)stream);

@@ -313,6 +313,83 @@ void Tile::setSeed(uint64_t seed) {
   fwd_calls_ = bwd_calls_ = upd_calls_ = transfer_calls_ = 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// extra state
+// ---------------------------------------------------------------------------------------------
+namespace {
+const char *const kExtraNames[] = {
+    "learning_rate",                           // RPUSimple (rpu.cpp:438)
+    "rpu_device.current_update_idx",           // VectorRPUDevice
+    "rpu_device.current_slice_indices",        // TransferRPUDevice (rpu_transfer_device.cpp:679)
+    "noise.key0",  "noise.key1",               // Philox key of all run-time noise
+    "noise.forward_calls", "noise.backward_calls", "noise.update_calls", "noise.transfer_calls",
+    "noise.weight_op_calls",
+};
+constexpr int kExtraCount = (int)(sizeof(kExtraNames) / sizeof(kExtraNames[0]));
+} // namespace
+
+int Tile::extraCount() { return kExtraCount; }
+
+const char *Tile::extraName(int k) {
+  if (k < 0 || k >= kExtraCount) {
+    AB200_FATAL("extra state index out of range");
+  }
+  return kExtraNames[k];
+}
+
+void Tile::dumpExtra(double *values) const {
+  const double v[kExtraCount] = {(double)lr_,
+                                 (double)update_idx_,
+                                 (double)slice_idx_,
+                                 (double)key_.k0,
+                                 (double)key_.k1,
+                                 (double)fwd_calls_,
+                                 (double)bwd_calls_,
+                                 (double)upd_calls_,
+                                 (double)transfer_calls_,
+                                 (double)op_calls_};
+  for (int k = 0; k < kExtraCount; k++) {
+    values[k] = v[k];
+  }
+}
+
+void Tile::loadExtra(const char *const *names, const double *values, int n, bool strict) {
+  bool seen[kExtraCount] = {};
+  for (int e = 0; e < n; e++) {
+    int k = 0;
+    while (k < kExtraCount && std::strcmp(names[e], kExtraNames[k]) != 0) {
+      k++;
+    }
+    if (k == kExtraCount) {
+      if (strict) {
+        AB200_FATAL("load_extra: unexpected key '" << names[e] << "'");
+      }
+      continue;
+    }
+    seen[k] = true;
+    const double v = values[e];
+    switch (k) {
+    case 0: lr_ = (float)v; break;
+    case 1: update_idx_ = (long long)v; break;
+    case 2: slice_idx_ = (int)v; break;
+    case 3: key_.k0 = (uint32_t)v; break;
+    case 4: key_.k1 = (uint32_t)v; break;
+    case 5: fwd_calls_ = (uint32_t)v; break;
+    case 6: bwd_calls_ = (uint32_t)v; break;
+    case 7: upd_calls_ = (uint32_t)v; break;
+    case 8: transfer_calls_ = (uint32_t)v; break;
+    case 9: op_calls_ = (uint32_t)v; break;
+    }
+  }
+  if (strict) {
+    for (int k = 0; k < kExtraCount; k++) {
+      if (!seen[k]) {
+        AB200_FATAL("load_extra: key '" << kExtraNames[k] << "' is missing"); // RPU::load, strict
+      }
+    }
+  }
+}
+
 Tile::~Tile() {
   if (device_ >= 0) {
     int prev = -1;

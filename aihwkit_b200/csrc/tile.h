@@ -202,6 +202,14 @@ public:
                      int n_img, bool trans, cudaStream_t s);
   void lastBmStats(int32_t *n_rerun, float *max_red);
 
+  // state that is neither a weight nor a hidden parameter, as name -> value pairs
+  // (RPUSimple / RPUPulsed / TransferRPUDevice::dumpExtra / loadExtra, src/rpucuda/rpu.cpp:405-503,
+  // rpu_pulsed.cpp:433-456, rpu_transfer_device.cpp:674-707), plus the noise key and counters
+  static int extraCount();
+  static const char *extraName(int k);
+  void dumpExtra(double *values) const;
+  void loadExtra(const char *const *names, const double *values, int n, bool strict);
+
   // weight operations between updates (RPUPulsed::decayWeights / diffuseWeights / clipWeights /
   // resetCols / setWeightsUniformRandom, src/rpucuda/rpu_pulsed.cpp:189-284)
   void decayWeights(float alpha, bool bias_no_decay, cudaStream_t s);

@@ -269,6 +269,39 @@ class AnalogTile:
                 )
             )
 
+    # -- extra state, copies ---------------------------------------------------------------------
+    def dump_extra(self) -> dict:
+        """rpu_base_tiles.cpp ``dump_extra``: state besides weights and hidden parameters as
+        ``{name: [values]}`` (learning rate, Tiki-Taka counters, noise key and call counters)."""
+        n = self._lib.ab200_tile_extra_count()
+        values = (C.c_double * n)()
+        check(self._lib.ab200_tile_dump_extra(self._h, values))
+        return {self._lib.ab200_tile_extra_name(k).decode(): [float(values[k])] for k in range(n)}
+
+    def load_extra(self, extra: dict, strict: bool = False) -> None:
+        """rpu_base_tiles.cpp ``load_extra``; with ``strict`` unknown or missing keys raise."""
+        names = list(extra.keys())
+        n = len(names)
+        c_names = (C.c_char_p * max(n, 1))(*[k.encode() for k in names])
+        c_vals = (C.c_double * max(n, 1))(*[float(extra[k][0] if isinstance(extra[k], (list, tuple)) else extra[k])
+                                            for k in names])
+        check(self._lib.ab200_tile_load_extra(self._h, c_names, c_vals, n, int(strict)))
+
+    def __copy__(self):
+        """A new tile with the same configuration, device parameters, weights and state
+        (rpu_base_tiles.cpp ``__copy__`` / ``__deepcopy__``)."""
+        other = type(self).__new__(type(self))
+        AnalogTile.__init__(other, self._cfg, cuda_device=self._device_index)
+        # weights first: setting them resets a compound device's hidden tiles and counters
+        other.set_weights(self.get_weights())
+        if self.get_hidden_parameter_names():
+            other.set_hidden_parameters(self.get_hidden_parameters())
+        other.load_extra(self.dump_extra(), strict=True)
+        return other
+
+    def __deepcopy__(self, memo):
+        return self.__copy__()
+
     # -- weight operations between updates -------------------------------------------------------
     def _op_stream(self):
         if self._device_index < 0:

@@ -316,6 +316,21 @@ int ab200_tile_update_indexed(ab200_tile *tile, const float *x_dev, const float 
                               long long total_input_size, int m_batch, int dim3, int trans,
                               void *stream);
 
+/* ---- extra state (checkpoint / resume) ---------------------------------------------------------
+ * Replaces RPUSimple / RPUPulsed / TransferRPUDevice::dumpExtra and loadExtra (src/rpucuda/rpu.cpp:
+ * 405-503, rpu_pulsed.cpp:433-456, rpu_transfer_device.cpp:674-707) as bound by dump_extra /
+ * load_extra (rpu_base_tiles.cpp:775-800): everything a resumed tile needs besides its weights and
+ * hidden parameters, as name -> value pairs: learning rate, the Tiki-Taka update and column
+ * counters and - unlike the reference, which does not save RNG state - the noise key and call
+ * counters, so that a resumed run continues the same noise streams. `values` holds
+ * ab200_tile_extra_count() doubles in the order of ab200_tile_extra_name(k). With `strict`
+ * unknown or missing keys are errors. */
+int ab200_tile_extra_count(void);
+const char *ab200_tile_extra_name(int k);
+int ab200_tile_dump_extra(ab200_tile *tile, double *values);
+int ab200_tile_load_extra(ab200_tile *tile, const char *const *names, const double *values,
+                          int count, int strict);
+
 /* ---- weight operations between updates -------------------------------------------------------
  * Replace RPUPulsed<T>::decayWeights(alpha, bias_no_decay) / diffuseWeights() / clipWeights(...) /
  * resetCols(start_col, n_cols, reset_prob) / setWeightsUniformRandom (src/rpucuda/rpu_pulsed.cpp:

@@ -155,3 +155,29 @@ def test_split_sizes_follow_reference_rule():
         assert ranges[0][0] == 0 and ranges[-1][1] == 8
         assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
     assert column_range(2304, 512, 1, 2) == (461 * 3, 2304)
+
+
+def test_extra_state_round_trip_and_copy():
+    """dump_extra / load_extra / copy on a host-side tile (no compute involved)."""
+    import copy
+
+    p = H.training_params(noise=False, pulse_det=True)
+    t = T.AnalogTile(p._config(6, 4, H.device("sb", False), seed=9))
+    t.set_learning_rate(0.03)
+    t.set_weights(torch.full((4, 6), 0.1))
+    extra = t.dump_extra()
+    assert extra["learning_rate"][0] == pytest.approx(0.03)
+    assert set(extra) >= {"rpu_device.current_update_idx", "noise.key0", "noise.forward_calls"}
+    t2 = copy.deepcopy(t)
+    assert t2.dump_extra() == extra
+    assert torch.equal(t2.get_weights(), t.get_weights())
+    assert torch.equal(t2.get_hidden_parameters(), t.get_hidden_parameters())
+    extra["learning_rate"] = [0.5]
+    t2.load_extra(extra, strict=True)
+    assert t2.get_learning_rate() == pytest.approx(0.5)
+    with pytest.raises(RuntimeError, match="unexpected key"):
+        t2.load_extra({"bogus": [1.0]}, strict=True)
+    t2.load_extra({"bogus": [1.0], "learning_rate": [0.25]})  # not strict: ignored
+    assert t2.get_learning_rate() == pytest.approx(0.25)
+    with pytest.raises(RuntimeError, match="is missing"):
+        t2.load_extra({"learning_rate": [0.25]}, strict=True)

@@ -239,3 +239,42 @@ def test_mapped_forward_local_input_equals_full_width_input():
                 outs.append(a.forward(X))
             torch.cuda.synchronize()
         assert torch.equal(outs[0], outs[1])
+
+
+def test_resume_from_extra_state_continues_identically():
+    """Checkpoint / resume: a Tiki-Taka tile rebuilt from weights, hidden parameters and
+    dump_extra() continues exactly like the uninterrupted one (transfer counters and noise call
+    counters are part of the extra state), also through a deep copy."""
+    import copy
+
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(3)
+    x_size, d_size, m = 24, 16, 5
+    p = H.training_params(noise=True, pulse_det=False)
+    dp = H.transfer_device(noise=True, transfer_every=1.0, units_in_mbatch=False, n_reads=2)
+    cfg = p._config(x_size, d_size, dp, seed=11)
+    a = T.AnalogTile(cfg, cuda_device=0)
+    a.set_learning_rate(0.1)
+    batches = [(torch.from_numpy(rng.uniform(-1, 1, (m, x_size)).astype(np.float32)).cuda(),
+                torch.from_numpy(rng.normal(0, 0.5, (m, d_size)).astype(np.float32)).cuda())
+               for _ in range(6)]
+    for x, d in batches[:3]:
+        a.update(x, d)
+    # rebuild from the saved pieces
+    b = T.AnalogTile(cfg, cuda_device=0)
+    # order as in the reference's __setstate__ (tiles/base.py): weights first - setting them
+    # zeroes the hidden fast tile and its counters - then hidden parameters, then the extra state
+    b.set_weights(a.get_weights())
+    b.set_hidden_parameters(a.get_hidden_parameters())
+    b.load_extra(a.dump_extra(), strict=True)
+    c = copy.deepcopy(a)
+    for x, d in batches[3:]:
+        a.update(x, d)
+        b.update(x, d)
+        c.update(x, d)
+    assert torch.equal(a.get_weights(), b.get_weights())
+    assert torch.equal(a.get_hidden_parameters(), b.get_hidden_parameters())
+    assert torch.equal(a.get_weights(), c.get_weights())
+    ya = a.forward(batches[0][0])
+    assert torch.equal(ya, b.forward(batches[0][0]))  # same noise stream after the resume
