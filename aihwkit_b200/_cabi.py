@@ -202,6 +202,9 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_array_num_in_splits": (_I, [_VP]),
         "ab200_array_num_out_splits": (_I, [_VP]),
         "ab200_array_set_weights": (_I, [_VP, _FP]),
+        "ab200_array_set_weights_scaled": (_I, [_VP, _FP, C.c_float]),
+        "ab200_array_get_tile_scales": (_I, [_VP, _FP]),
+        "ab200_array_set_bias": (_I, [_VP, _FP]),
         "ab200_array_get_weights": (_I, [_VP, _FP]),
         "ab200_array_forward": (_I, [_VP, _FP, _FP, _I, _I, _VP]),
         "ab200_array_forward_host": (_I, [_VP, _FP, _FP, _I, _I, _VP]),

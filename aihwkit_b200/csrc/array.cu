@@ -80,6 +80,8 @@ TileArray::~TileArray() {
     cudaStreamDestroy(s_h2d_);
     cudaStreamDestroy(s_d2h_);
   }
+  cudaFree(tile_scale_dev_);
+  cudaFree(bias_dev_);
 }
 
 void TileArray::setSeed(uint64_t seed) {
@@ -90,20 +92,57 @@ void TileArray::setSeed(uint64_t seed) {
   }
 }
 
-void TileArray::setWeights(const float *w_host) {
+void TileArray::setWeights(const float *w_host, float omega) {
   std::vector<float> buf;
+  const int n_out = (int)out_sizes_.size();
+  tile_scale_host_.assign((size_t)(in_end_ - in_begin_) * n_out, 1.0f);
+  scaled_ = omega > 0.0f;
   for (int ii = in_begin_; ii < in_end_; ii++) {
-    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
+    for (int oi = 0; oi < n_out; oi++) {
       int xs = in_sizes_[ii], ds = out_sizes_[oi];
       buf.resize((size_t)xs * ds);
+      float amax = 0.0f;
       for (int r = 0; r < ds; r++) {
-        std::memcpy(&buf[(size_t)r * xs],
-                    w_host + (size_t)(out_off_[oi] + r) * in_size_ + in_off_[ii],
-                    (size_t)xs * sizeof(float));
+        const float *src = w_host + (size_t)(out_off_[oi] + r) * in_size_ + in_off_[ii];
+        std::memcpy(&buf[(size_t)r * xs], src, (size_t)xs * sizeof(float));
+        for (int c = 0; c < xs; c++) {
+          amax = std::max(amax, std::fabs(src[c]));
+        }
+      }
+      if (scaled_) {
+        float alpha = amax / omega;
+        if (alpha == 0.0f) {
+          alpha = 1.0f;
+        }
+        for (float &v : buf) {
+          v /= alpha;
+        }
+        tile_scale_host_[(size_t)(ii - in_begin_) * n_out + oi] = alpha;
       }
       tile(ii - in_begin_, oi).setWeights(buf.data());
     }
   }
+  if (!tile_scale_host_.empty()) {
+    AB200_CUDA(cudaSetDevice(device_));
+    if (!tile_scale_dev_) {
+      AB200_CUDA(cudaMalloc(&tile_scale_dev_, tile_scale_host_.size() * sizeof(float)));
+    }
+    AB200_CUDA(cudaMemcpy(tile_scale_dev_, tile_scale_host_.data(),
+                          tile_scale_host_.size() * sizeof(float), cudaMemcpyHostToDevice));
+  }
+}
+
+void TileArray::setBias(const float *bias_host) {
+  AB200_CUDA(cudaSetDevice(device_));
+  if (!bias_host) {
+    cudaFree(bias_dev_);
+    bias_dev_ = nullptr;
+    return;
+  }
+  if (!bias_dev_) {
+    AB200_CUDA(cudaMalloc(&bias_dev_, (size_t)out_size_ * sizeof(float)));
+  }
+  AB200_CUDA(cudaMemcpy(bias_dev_, bias_host, (size_t)out_size_ * sizeof(float), cudaMemcpyHostToDevice));
 }
 
 void TileArray::getWeights(float *w_host) {
@@ -113,11 +152,26 @@ void TileArray::getWeights(float *w_host) {
       int xs = in_sizes_[ii], ds = out_sizes_[oi];
       buf.resize((size_t)xs * ds);
       tile(ii - in_begin_, oi).getWeights(buf.data());
+      if (scaled_) {
+        const float alpha = tile_scale_host_[(size_t)(ii - in_begin_) * out_sizes_.size() + oi];
+        for (float &v : buf) {
+          v *= alpha;
+        }
+      }
       for (int r = 0; r < ds; r++) {
         std::memcpy(w_host + (size_t)(out_off_[oi] + r) * in_size_ + in_off_[ii],
                     &buf[(size_t)r * xs], (size_t)xs * sizeof(float));
       }
     }
+  }
+}
+
+// digital bias of the layer, for the path that runs the tiles one by one
+__global__ void __launch_bounds__(256)
+    addBiasKernel(float *y, const float *bias, long long n, int out_size) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < n) {
+    y[t] += bias[t % out_size];
   }
 }
 
@@ -153,14 +207,22 @@ void TileArray::forwardImpl(const float *x0, long long x_ss, float *y, int m, cu
     forwardTc(x0, x_ss, y, m, s);
     return;
   }
+  const int n_out = (int)out_sizes_.size();
   for (int ii = in_begin_; ii < in_end_; ii++) {
-    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
+    for (int oi = 0; oi < n_out; oi++) {
+      const float alpha =
+          scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_out + oi] : 1.0f;
       tile(ii - in_begin_, oi)
           .forwardStrided(x0 + (in_off_[ii] - in_off_[in_begin_]), x_ss, y + out_off_[oi],
                           out_size_, m,
                           /*accumulate=*/ii != in_begin_,
-                          (uint32_t)(ii * (int)out_sizes_.size() + oi), s);
+                          (uint32_t)(ii * n_out + oi), alpha, s);
     }
+  }
+  if (bias_dev_) {
+    const long long n = (long long)m * out_size_;
+    addBiasKernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, bias_dev_, n, out_size_);
+    AB200_LAUNCH_CHECK();
   }
 }
 
@@ -211,6 +273,8 @@ void TileArray::forwardTc(const float *x0, long long x_ss, float *y, int m, cuda
   r.out = y;
   r.out_ss = out_size_;
   r.io = tiles_[0]->fio();
+  r.tile_scale = scaled_ ? tile_scale_dev_ : nullptr;
+  r.bias = bias_dev_;
   tc_->run(r, s);
 }
 

@@ -19,8 +19,15 @@ public:
   ~TileArray();
   int numInSplits() const { return (int)in_sizes_.size(); }
   int numOutSplits() const { return (int)out_sizes_.size(); }
-  void setWeights(const float *w_host);
+  // omega > 0: every tile's weights are divided by max|w_tile| / omega and the quotient becomes
+  // the tile's digital output scale (TileWithPeriphery.apply_weight_scaling,
+  // src/aihwkit/simulator/tiles/periphery.py:437-500, layer-wise form); omega = 0: scales 1
+  void setWeights(const float *w_host, float omega = 0.0f);
+  // logical weights: tile weights times their output scales
   void getWeights(float *w_host);
+  // digital bias [out_size] added after the sum over in-splits (array.py:178-181); null removes it
+  void setBias(const float *bias_host);
+  const std::vector<float> &tileScales() const { return tile_scale_host_; }
   void forward(const float *x, float *y, int m, bool is_test, cudaStream_t s);
   // input that holds only the locally owned columns: [m][localInSize()]
   void forwardLocal(const float *x_local, float *y, int m, bool is_test, cudaStream_t s);
@@ -36,6 +43,11 @@ private:
   std::vector<std::unique_ptr<Tile>> tiles_;
   // one tensor-core engine for all locally owned tiles; operands are refreshed per tile when
   // that tile's weights changed
+  // digital periphery: output scale per local tile [in_local][out] and bias [out_size]
+  std::vector<float> tile_scale_host_;
+  float *tile_scale_dev_ = nullptr;
+  bool scaled_ = false;
+  float *bias_dev_ = nullptr;
   std::unique_ptr<TcEngine> tc_;
   std::vector<uint64_t> tc_versions_;
   bool tcEligible(int m);

@@ -4,6 +4,7 @@
 #include "array.h"
 #include "tile.h"
 
+#include <algorithm>
 #include <cstring>
 
 namespace ab200 {
@@ -401,6 +402,22 @@ int ab200_array_num_out_splits(const ab200_array *arr) {
 int ab200_array_set_weights(ab200_array *arr, const float *w_host) {
   AB200_TRY
   A(arr)->setWeights(w_host);
+  AB200_CATCH
+}
+int ab200_array_set_weights_scaled(ab200_array *arr, const float *w_host, float omega) {
+  AB200_TRY
+  A(arr)->setWeights(w_host, omega);
+  AB200_CATCH
+}
+int ab200_array_get_tile_scales(ab200_array *arr, float *scales_host) {
+  AB200_TRY
+  const std::vector<float> &sc = A(arr)->tileScales();
+  std::copy(sc.begin(), sc.end(), scales_host);
+  AB200_CATCH
+}
+int ab200_array_set_bias(ab200_array *arr, const float *bias_host) {
+  AB200_TRY
+  A(arr)->setBias(bias_host);
   AB200_CATCH
 }
 int ab200_array_get_weights(ab200_array *arr, float *w_host) {

@@ -71,6 +71,8 @@ struct TcKernelParams {
   PhiloxKey key;
   uint32_t call, noise_id0;
   const float *scale, *factor, *vnorm;
+  const float *tile_scale; // [I][O] or null
+  const float *bias;       // [N_total] or null
   int *flags;
   float *out;
   long long out_ss;
@@ -522,6 +524,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       sc_n = p.scale[row];
       fac_n = p.factor[row];
       vn_n = p.vnorm[row];
+      if (p.tile_scale) {
+        fac_n *= p.tile_scale[ch.x];
+      }
     }
     for (int i = 0; i < p.I; i++, ai++) {
       const int b = ai & 1;
@@ -533,6 +538,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         sc_n = p.scale[si];
         fac_n = p.factor[si];
         vn_n = p.vnorm[si];
+        if (p.tile_scale) {
+          fac_n *= p.tile_scale[(i + 1) * p.O + ch.x];
+        }
       }
       const uint32_t tile_tag = tag + p.noise_id0 + (uint32_t)(i * p.O + ch.x);
       if (!TC_TIMED_WAIT(w_tfull, mbarWait(&tmem_full[b], (ai >> 1) & 1, abort_flag))) {
@@ -630,6 +638,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       const bool vec = ((p.out_ss & 3) == 0) && ((ch.z & 3) == 0) &&
                        ((((uintptr_t)p.out) & 15) == 0) && !p.accumulate;
       float *orow = p.out + (long long)row * p.out_ss + ch.z + cbase;
+      if (p.bias) {
+#pragma unroll
+        for (int c = 0; c < TC_EPI_COLS; c++) {
+          if (cbase + c < ch.w) {
+            sum[c] += p.bias[ch.z + cbase + c];
+          }
+        }
+      }
 #pragma unroll
       for (int c = 0; c < TC_EPI_COLS; c += 4) {
         const int cl = cbase + c;
@@ -1021,6 +1037,8 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   p.scale = d.scale;
   p.factor = d.factor;
   p.vnorm = d.vnorm;
+  p.tile_scale = r.tile_scale;
+  p.bias = r.bias;
   p.flags = r.io.bm != AB200_BM_NONE ? d.flags : nullptr;
   p.out = r.out;
   p.out_ss = r.out_ss;

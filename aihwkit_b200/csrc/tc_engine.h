@@ -43,6 +43,11 @@ public:
     PhiloxKey key{0, 0};
     uint32_t call = 0;
     uint32_t noise_id0 = 0;
+    // optional digital periphery of a mapped layer (device pointers): one scale per tile,
+    // [I][O], applied to that tile's output before the sum over in-splits, and a bias per output
+    // column added once
+    const float *tile_scale = nullptr;
+    const float *bias = nullptr;
     // optional caller-owned per-row scratch (only valid for I == 1): lets the bound-management
     // re-run kernel see the same noise-management values and flags
     float *scale = nullptr, *factor = nullptr, *vnorm = nullptr, *sval = nullptr;

@@ -800,7 +800,7 @@ void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, boo
 }
 
 void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_ss, int m,
-                          bool accumulate, uint32_t noise_id, cudaStream_t s) {
+                          bool accumulate, uint32_t noise_id, float out_scale, cudaStream_t s) {
   requireDevice("forward");
   MvmProblem p{};
   p.in = x;
@@ -820,7 +820,7 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
   p.m = m;
   p.backward = 0;
   p.io = f_io_;
-  p.alpha = 1.0f;
+  p.alpha = out_scale; // digital scale of this tile's output (mapping scale)
   p.call = fwd_calls_++;
   p.noise_id = noise_id;
   fillMvmScratch(p);

@@ -220,7 +220,7 @@ public:
 
   // used by the mapped array: forward on a sub-block of a wider activation matrix
   void forwardStrided(const float *x, long long x_ss, float *y, long long y_ss, int m,
-                      bool accumulate, uint32_t noise_id, cudaStream_t s);
+                      bool accumulate, uint32_t noise_id, float out_scale, cudaStream_t s);
 
   const IOEff &fio() const { return f_io_; }
   float *weightsXD() { return w_; }

@@ -49,22 +49,22 @@ def inference_config(seed: int, max_tile: int = 512):
 
 
 class AnalogLinear:
-    """``y = scale * tiles(x) + bias``: the weight matrix is divided by its largest magnitude so
-    that it fills the conductance range [-1, 1] (the reference's weight-scaling omega = 1,
-    src/aihwkit/simulator/tiles/periphery.py:785-901, here one scale per layer), split over tiles,
-    and the scale and the digital bias are applied to the summed tile outputs."""
+    """``y = sum over tiles of alpha_tile * tile(x) + bias``: every tile stores its block of the
+    weight matrix divided by ``alpha_tile = max|w_tile|`` so that it fills the conductance range
+    [-1, 1] (the reference's weight-scaling omega = 1, layer-wise per tile,
+    src/aihwkit/simulator/tiles/periphery.py:437-500); the scales and the digital bias are applied
+    inside the mapped layer's kernels, so a layer is two launches (DAC, MVM)."""
 
     def __init__(self, in_features: int, out_features: int, device: int, seed: int,
                  gen: torch.Generator, max_tile: int = 512):
         from .rpu_base import tiles as T
 
         w = torch.randn(out_features, in_features, generator=gen) * 0.02
-        self.scale = float(w.abs().max())
         self.array = T.TileArray(inference_config(seed, max_tile), out_features, in_features,
                                  max_tile, max_tile, cuda_device=device)
         self.array.set_seed(seed)
-        self.array.set_weights(w / self.scale)
-        self.bias = torch.zeros(out_features, device=f"cuda:{device}")
+        self.array.set_weights(w, weight_scaling_omega=1.0)
+        self.array.set_bias(torch.zeros(out_features))
         self.in_features, self.out_features = in_features, out_features
 
     @property
@@ -73,7 +73,7 @@ class AnalogLinear:
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         y = self.array.forward(x.reshape(-1, self.in_features), is_test=True, non_blocking=True)
-        return torch.add(self.bias, y, alpha=self.scale).reshape(*x.shape[:-1], self.out_features)
+        return y.reshape(*x.shape[:-1], self.out_features)
 
 
 class Block:

@@ -473,6 +473,7 @@ class TileArray:
             )
         )
         self._h = h
+        self._n_local_in = None if in_split_range is None else max(0, int(end) - int(begin))
         self.device = torch.device("cuda", int(cuda_device))
 
     def __del__(self):
@@ -491,9 +492,29 @@ class TileArray:
     def set_seed(self, seed: int) -> None:
         check(self._lib.ab200_array_set_seed(self._h, int(seed)))
 
-    def set_weights(self, weight: torch.Tensor) -> None:
+    def set_weights(self, weight: torch.Tensor, weight_scaling_omega: float = 0.0) -> None:
+        """Logical ``[out_size, in_size]`` weights.  With ``weight_scaling_omega > 0`` every tile
+        stores ``w / alpha`` with ``alpha = max|w_tile| / omega`` and applies ``alpha`` to its
+        output in digital, inside the layer's kernels (the layer-wise weight scaling of
+        ``TileWithPeriphery.apply_weight_scaling``, tiles/periphery.py:437-500)."""
         w = weight.detach().to(torch.float32).cpu().reshape(self.out_size, self.in_size).contiguous()
-        check(self._lib.ab200_array_set_weights(self._h, w.data_ptr()))
+        check(self._lib.ab200_array_set_weights_scaled(self._h, w.data_ptr(), float(weight_scaling_omega)))
+
+    def get_tile_scales(self) -> torch.Tensor:
+        """Digital output scales of the locally owned tiles ``[in-splits, out-splits]``."""
+        n_in = self.num_in_splits if self._n_local_in is None else self._n_local_in
+        sc = torch.ones(max(n_in, 1) * self.num_out_splits, dtype=torch.float32)
+        check(self._lib.ab200_array_get_tile_scales(self._h, sc.data_ptr()))
+        return sc.reshape(-1, self.num_out_splits)[:n_in]
+
+    def set_bias(self, bias: Optional[torch.Tensor]) -> None:
+        """Digital bias ``[out_size]`` added after the sum over in-splits
+        (``TileModuleArray.forward``, tiles/array.py:178-181); ``None`` removes it."""
+        if bias is None:
+            check(self._lib.ab200_array_set_bias(self._h, None))
+            return
+        b = bias.detach().to(torch.float32).cpu().reshape(self.out_size).contiguous()
+        check(self._lib.ab200_array_set_bias(self._h, b.data_ptr()))
 
     def get_weights(self) -> torch.Tensor:
         w = torch.zeros(self.out_size, self.in_size, dtype=torch.float32)

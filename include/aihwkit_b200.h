@@ -380,6 +380,18 @@ int ab200_array_num_out_splits(const ab200_array *arr);
  * only the locally owned in-splits are read / written. */
 int ab200_array_set_weights(ab200_array *arr, const float *w_host);
 int ab200_array_get_weights(ab200_array *arr, float *w_host);
+/* Digital periphery of the mapped layer, applied inside the layer's kernels.
+ * set_weights_scaled: as set_weights, but every tile's weights are divided by
+ * alpha = max|w_tile| / omega and alpha becomes that tile's digital output scale
+ * (TileWithPeriphery.apply_weight_scaling / set_scales, layer-wise form,
+ * src/aihwkit/simulator/tiles/periphery.py:437-500, 689-728; forward: apply_out_scaling :785-805).
+ * omega <= 0 means no scaling. get_weights returns the logical (re-scaled) weights.
+ * get_tile_scales: the scales of the locally owned tiles, [local in-splits][out-splits].
+ * set_bias: digital bias [out_size] added once after the sum over in-splits (array.py:178-181);
+ * NULL removes it. On a sharded layer only one rank should hold the bias. */
+int ab200_array_set_weights_scaled(ab200_array *arr, const float *w_host, float omega);
+int ab200_array_get_tile_scales(ab200_array *arr, float *scales_host);
+int ab200_array_set_bias(ab200_array *arr, const float *bias_host);
 /* TileModuleArray.forward (array.py:155-182): every tile does its own noise management, DAC,
  * MVM and ADC; results of the in-splits are added after the ADC, out-splits are concatenated.
  * x_dev is the full [m_batch][in_size] input; y_dev is [m_batch][out_size] and receives the sum

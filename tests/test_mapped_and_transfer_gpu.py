@@ -278,3 +278,68 @@ def test_resume_from_extra_state_continues_identically():
     assert torch.equal(a.get_weights(), c.get_weights())
     ya = a.forward(batches[0][0])
     assert torch.equal(ya, b.forward(batches[0][0]))  # same noise stream after the resume
+
+
+def _scaled_array_oracle(W, X, bias, cfg, max_tile, omega):
+    """Mapped forward with the layer-wise weight scaling and the digital bias: every tile holds
+    w / alpha with alpha = max|w_tile| / omega and its ADC output is multiplied by alpha
+    (tiles/periphery.py:437-500, 785-805); the bias is added once (tiles/array.py:178-181)."""
+    from aihwkit_b200.sharded import split_sizes
+
+    io = O.IO.from_c(cfg.forward_io)
+    out_sizes, in_sizes = split_sizes(W.shape[0], max_tile), split_sizes(W.shape[1], max_tile)
+    y = np.zeros((X.shape[0], W.shape[0]), np.float32)
+    lsb = np.zeros_like(y)
+    scales = np.ones((len(in_sizes), len(out_sizes)), np.float32)
+    c0 = 0
+    for ii, isz in enumerate(in_sizes):
+        r0 = 0
+        for oi, osz in enumerate(out_sizes):
+            wt = W[r0 : r0 + osz, c0 : c0 + isz]
+            alpha = np.float32(np.abs(wt).max() / np.float32(omega)) if omega > 0 else np.float32(1)
+            alpha = np.float32(1) if alpha == 0 else alpha
+            scales[ii, oi] = alpha
+            yt, _, scale, _ = O.forward((wt / alpha).astype(np.float32), X[:, c0 : c0 + isz], io, None,
+                                        return_pre_adc=True)
+            y[:, r0 : r0 + osz] += yt * alpha
+            lsb[:, r0 : r0 + osz] = np.maximum(lsb[:, r0 : r0 + osz], (alpha * io.res_out / scale)[:, None])
+            r0 += osz
+        c0 += isz
+    return y + bias[None, :], lsb, scales
+
+
+@pytest.mark.parametrize("out_size,in_size,max_tile,m,mode", [(256, 384, 128, 40, 1), (768, 2304, 512, 300, 2),
+                                                              (100, 1030, 512, 7, 1), (300, 700, 256, 200, 3)])
+def test_mapped_forward_weight_scaling_and_bias(out_size, in_size, max_tile, m, mode):
+    """Per-tile output scales and the digital bias applied inside the layer's kernels, on the
+    CUDA-core path (mode 1) and both tensor-core kernel variants (modes 2, 3)."""
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    rng = np.random.default_rng(out_size + mode)
+    cfg = H.inference_params(noise=False)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=3)
+    W = rng.normal(0, 0.02, (out_size, in_size)).astype(np.float32)
+    bias = rng.normal(0, 0.1, out_size).astype(np.float32)
+    X = rng.normal(0, 1, (m, in_size)).astype(np.float32)
+    lib = _cabi.lib()
+    assert lib.ab200_set_mvm_path(mode) == 0
+    try:
+        arr = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+        arr.set_weights(torch.from_numpy(W), weight_scaling_omega=0.8)
+        arr.set_bias(torch.from_numpy(bias))
+        y = arr.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+        y_or, lsb, scales = _scaled_array_oracle(W, X, bias, cfg, max_tile, 0.8)
+        assert np.allclose(arr.get_tile_scales().numpy(), scales, rtol=1e-6)
+        assert np.allclose(arr.get_weights().numpy(), W, rtol=1e-6, atol=1e-9)
+        n_in = scales.shape[0]
+        diff = np.abs(y - y_or)
+        assert (diff > 1e-3 * lsb).mean() <= 2e-3 * n_in
+        assert (diff <= 1.001 * lsb * n_in + 1e-6).all()
+        # removing the bias and the scaling gives the plain layer again
+        arr.set_bias(None)
+        arr.set_weights(torch.from_numpy(W))
+        y0 = arr.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+        y0_or, lsb0, _ = _array_oracle(W, X, cfg, max_tile, max_tile)
+        assert (np.abs(y0 - y0_or) <= 1.001 * lsb0 * n_in).all()
+    finally:
+        lib.ab200_set_mvm_path(0)
