@@ -202,6 +202,9 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_array_num_in_splits": (_I, [_VP]),
         "ab200_array_num_out_splits": (_I, [_VP]),
         "ab200_array_set_weights": (_I, [_VP, _FP]),
+        "ab200_array_backward": (_I, [_VP, _FP, _FP, _I, _VP]),
+        "ab200_array_update": (_I, [_VP, _FP, _FP, _I, _VP]),
+        "ab200_array_set_learning_rate": (_I, [_VP, C.c_float]),
         "ab200_array_set_weights_scaled": (_I, [_VP, _FP, C.c_float]),
         "ab200_array_get_tile_scales": (_I, [_VP, _FP]),
         "ab200_array_set_bias": (_I, [_VP, _FP]),

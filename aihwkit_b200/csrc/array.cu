@@ -82,6 +82,7 @@ TileArray::~TileArray() {
   }
   cudaFree(tile_scale_dev_);
   cudaFree(bias_dev_);
+  cudaFree(d_scratch_);
 }
 
 void TileArray::setSeed(uint64_t seed) {
@@ -223,6 +224,80 @@ void TileArray::forwardImpl(const float *x0, long long x_ss, float *y, int m, cu
     const long long n = (long long)m * out_size_;
     addBiasKernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, bias_dev_, n, out_size_);
     AB200_LAUNCH_CHECK();
+  }
+}
+
+// dst[r][c] = src[r * src_ld + c] * factor: the gradient block of one out-split, scaled
+__global__ void __launch_bounds__(256)
+    scaleBlockKernel(const float *src, long long src_ld, float *dst, int cols, long long n,
+                     float factor) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < n) {
+    dst[t] = src[(t / cols) * src_ld + t % cols] * factor;
+  }
+}
+
+const float *TileArray::scaledGradient(const float *d, int oi, int m, float factor, long long &ld,
+                                       cudaStream_t s) {
+  if (factor == 1.0f) {
+    ld = out_size_;
+    return d + out_off_[oi];
+  }
+  const int cols = out_sizes_[oi];
+  const size_t need = (size_t)m * cols;
+  if (need > d_scratch_floats_) {
+    AB200_CUDA(cudaStreamSynchronize(s));
+    cudaFree(d_scratch_);
+    AB200_CUDA(cudaMalloc(&d_scratch_, need * sizeof(float)));
+    d_scratch_floats_ = need;
+  }
+  scaleBlockKernel<<<(unsigned)((need + 255) / 256), 256, 0, s>>>(d + out_off_[oi], out_size_,
+                                                               d_scratch_, cols, (long long)need,
+                                                               factor);
+  AB200_LAUNCH_CHECK();
+  ld = cols;
+  return d_scratch_;
+}
+
+void TileArray::backward(const float *d, float *x_grad, int m, cudaStream_t s) {
+  if (m <= 0) {
+    return;
+  }
+  AB200_CUDA(cudaSetDevice(device_));
+  const int n_out = (int)out_sizes_.size();
+  for (int ii = in_begin_; ii < in_end_; ii++) {
+    for (int oi = 0; oi < n_out; oi++) {
+      const float alpha = scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_out + oi] : 1.0f;
+      long long ld = 0;
+      // pre_backward: the gradient is multiplied by the mapping scale before the tile sees it
+      const float *dt = scaledGradient(d, oi, m, alpha, ld, s);
+      tile(ii - in_begin_, oi)
+          .backwardStrided(dt, ld, x_grad + in_off_[ii], in_size_, m, /*accumulate=*/oi != 0,
+                           (uint32_t)(ii * n_out + oi), 1.0f, s);
+    }
+  }
+}
+
+void TileArray::update(const float *x, const float *d, int m, cudaStream_t s) {
+  if (m <= 0) {
+    return;
+  }
+  AB200_CUDA(cudaSetDevice(device_));
+  const int n_out = (int)out_sizes_.size();
+  for (int ii = in_begin_; ii < in_end_; ii++) {
+    for (int oi = 0; oi < n_out; oi++) {
+      const float alpha = scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_out + oi] : 1.0f;
+      long long ld = 0;
+      // pre_update: the gradient is divided by the mapping scale
+      const float *dt = scaledGradient(d, oi, m, 1.0f / alpha, ld, s);
+      tile(ii - in_begin_, oi).updateStrided(x + in_off_[ii], in_size_, dt, ld, m, s);
+    }
+  }
+}
+
+void TileArray::setLearningRate(float lr) {
+  for (auto &t : tiles_) {
+    t->setLearningRate(lr);
   }
 }
 

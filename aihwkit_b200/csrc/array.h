@@ -32,6 +32,15 @@ public:
   // input that holds only the locally owned columns: [m][localInSize()]
   void forwardLocal(const float *x_local, float *y, int m, bool is_test, cudaStream_t s);
   int localInSize() const;
+  // Training of a mapped layer, tile by tile as autograd does in the reference
+  // (TileModuleArray modules -> TileWithPeriphery.backward / update, tiles/periphery.py:1068-1110,
+  // 1154-1230). backward: x_grad[:, in-split i] = sum over out-splits o of
+  // tile(i, o).backward(d[:, out-split o] * alpha_io); update: tile(i, o).update(x[:, in-split i],
+  // d[:, out-split o] / alpha_io). d is [m][out_size]; x / x_grad are [m][in_size] (full width;
+  // only the locally owned columns are read / written).
+  void backward(const float *d, float *x_grad, int m, cudaStream_t s);
+  void update(const float *x, const float *d, int m, cudaStream_t s);
+  void setLearningRate(float lr);
   void forwardHost(const float *x, float *y, int m, bool is_test, cudaStream_t s);
   void setSeed(uint64_t seed);
 
@@ -48,6 +57,10 @@ private:
   float *tile_scale_dev_ = nullptr;
   bool scaled_ = false;
   float *bias_dev_ = nullptr;
+  float *d_scratch_ = nullptr; // [m][largest out-split]: gradients times / over the tile scale
+  size_t d_scratch_floats_ = 0;
+  const float *scaledGradient(const float *d, int oi, int m, float factor, long long &ld,
+                              cudaStream_t s);
   std::unique_ptr<TcEngine> tc_;
   std::vector<uint64_t> tc_versions_;
   bool tcEligible(int m);

@@ -404,6 +404,23 @@ int ab200_array_set_weights(ab200_array *arr, const float *w_host) {
   A(arr)->setWeights(w_host);
   AB200_CATCH
 }
+int ab200_array_backward(ab200_array *arr, const float *d_dev, float *x_grad_dev, int m_batch,
+                         void *stream) {
+  AB200_TRY
+  A(arr)->backward(d_dev, x_grad_dev, m_batch, (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_array_update(ab200_array *arr, const float *x_dev, const float *d_dev, int m_batch,
+                       void *stream) {
+  AB200_TRY
+  A(arr)->update(x_dev, d_dev, m_batch, (cudaStream_t)stream);
+  AB200_CATCH
+}
+int ab200_array_set_learning_rate(ab200_array *arr, float lr) {
+  AB200_TRY
+  A(arr)->setLearningRate(lr);
+  AB200_CATCH
+}
 int ab200_array_set_weights_scaled(ab200_array *arr, const float *w_host, float omega) {
   AB200_TRY
   A(arr)->setWeights(w_host, omega);

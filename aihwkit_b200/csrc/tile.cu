@@ -833,34 +833,47 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
 
 void Tile::backward(const float *d, float *x, bool bias, int m, bool d_trans, bool x_trans,
                     cudaStream_t s) {
+  const int x_out = x_size_ - (bias ? 1 : 0);
+  backwardCore(d, d_trans ? 1 : d_size_, d_trans ? m : 1, x, x_trans ? 1 : x_out, x_trans ? m : 1,
+               x_out, m, false, 0, 1.0f, s);
+}
+
+// used by the mapped array: backward on sub-blocks of wider gradient matrices
+void Tile::backwardStrided(const float *d, long long d_ss, float *x, long long x_ss, int m,
+                           bool accumulate, uint32_t noise_id, float out_scale, cudaStream_t s) {
+  backwardCore(d, d_ss, 1, x, x_ss, 1, x_size_, m, accumulate, noise_id, out_scale, s);
+}
+
+void Tile::backwardCore(const float *d, long long d_ss, long long d_fs, float *x, long long x_ss,
+                        long long x_fs, int x_store, int m, bool accumulate, uint32_t noise_id,
+                        float out_scale, cudaStream_t s) {
   requireDevice("backward");
   if (m <= 0) {
     return;
   }
   MvmProblem p{};
-  const int x_out = x_size_ - (bias ? 1 : 0);
   p.in = d;
-  p.in_ss = d_trans ? 1 : d_size_;
-  p.in_fs = d_trans ? m : 1;
+  p.in_ss = d_ss;
+  p.in_fs = d_fs;
   p.in_size = d_size_;
   p.in_real = d_size_;
   p.out = x;
-  p.out_ss = x_trans ? 1 : x_out;
-  p.out_fs = x_trans ? m : 1;
+  p.out_ss = x_ss;
+  p.out_fs = x_fs;
   p.out_size = x_size_;
-  p.out_store = x_out; // the bias column is computed but not returned (rpu.cpp:670-690)
-  p.accumulate = 0;
+  p.out_store = x_store; // a bias column is computed but not returned (rpu.cpp:670-690)
+  p.accumulate = accumulate ? 1 : 0;
   p.w = w_;
   p.wk = 1; // W(k = d, n = x) = w[x * d_size + d]
   p.wn = d_size_;
   p.m = m;
   p.backward = 1;
   p.io = b_io_;
-  p.alpha = 1.0f;
+  p.alpha = out_scale;
   p.call = bwd_calls_++;
-  p.noise_id = 0;
+  p.noise_id = noise_id;
   fillMvmScratch(p);
-  if (tcEligible(p)) {
+  if (!accumulate && tcEligible(p)) {
     runTc(p, s);
   } else {
     launchMvm(p, s);
@@ -998,6 +1011,19 @@ void Tile::doTransfer(cudaStream_t s) {
 
 void Tile::update(const float *x, const float *d, bool bias, int m, bool x_trans, bool d_trans,
                   cudaStream_t s) {
+  const int x_in = x_size_ - (bias ? 1 : 0);
+  updateCore(x, x_trans ? 1 : x_in, x_trans ? m : 1, x_in, d, d_trans ? 1 : d_size_,
+             d_trans ? m : 1, m, s);
+}
+
+// used by the mapped array: update from sub-blocks of wider activation / gradient matrices
+void Tile::updateStrided(const float *x, long long x_ss, const float *d, long long d_ss, int m,
+                         cudaStream_t s) {
+  updateCore(x, x_ss, 1, x_size_, d, d_ss, 1, m, s);
+}
+
+void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, const float *d,
+                      long long d_ss, long long d_fs, int m, cudaStream_t s) {
   requireDevice("update");
   if (m <= 0 || lr_ == 0.0f) {
     return; // "if (!learning_rate) return" (rpu_weight_updater.cpp:206-208)
@@ -1005,14 +1031,13 @@ void Tile::update(const float *x, const float *d, bool bias, int m, bool x_trans
   ensureScratch(m);
   w_version_++;
   UpdateProblem u{};
-  const int x_in = x_size_ - (bias ? 1 : 0);
   u.x = x;
-  u.x_ss = x_trans ? 1 : x_in;
-  u.x_fs = x_trans ? m : 1;
+  u.x_ss = x_ss;
+  u.x_fs = x_fs;
   u.x_real = x_in;
   u.d = d;
-  u.d_ss = d_trans ? 1 : d_size_;
-  u.d_fs = d_trans ? m : 1;
+  u.d_ss = d_ss;
+  u.d_fs = d_fs;
   u.x_size = x_size_;
   u.d_size = d_size_;
   u.m = m;

@@ -222,6 +222,11 @@ public:
   void forwardStrided(const float *x, long long x_ss, float *y, long long y_ss, int m,
                       bool accumulate, uint32_t noise_id, float out_scale, cudaStream_t s);
 
+  void backwardStrided(const float *d, long long d_ss, float *x, long long x_ss, int m,
+                       bool accumulate, uint32_t noise_id, float out_scale, cudaStream_t s);
+  void updateStrided(const float *x, long long x_ss, const float *d, long long d_ss, int m,
+                     cudaStream_t s);
+
   const IOEff &fio() const { return f_io_; }
   float *weightsXD() { return w_; }
   uint64_t weightsVersion() const { return w_version_; }
@@ -240,6 +245,11 @@ private:
   void pulsedUpdateRange(UpdateProblem &p, cudaStream_t s);
   void doTransfer(cudaStream_t s);
   float pulseCountLR() const;
+  void backwardCore(const float *d, long long d_ss, long long d_fs, float *x, long long x_ss,
+                    long long x_fs, int x_store, int m, bool accumulate, uint32_t noise_id,
+                    float out_scale, cudaStream_t s);
+  void updateCore(const float *x, long long x_ss, long long x_fs, int x_in, const float *d,
+                  long long d_ss, long long d_fs, int m, cudaStream_t s);
   void requireSingleDevice(const char *what);
   void ensurePar3();
   void requireIndices(const char *what, long long image_size, int m_batch, int n_img) const;

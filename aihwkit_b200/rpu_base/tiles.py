@@ -500,6 +500,37 @@ class TileArray:
         w = weight.detach().to(torch.float32).cpu().reshape(self.out_size, self.in_size).contiguous()
         check(self._lib.ab200_array_set_weights_scaled(self._h, w.data_ptr(), float(weight_scaling_omega)))
 
+    def set_learning_rate(self, lr: float) -> None:
+        check(self._lib.ab200_array_set_learning_rate(self._h, float(lr)))
+
+    def backward(self, d_input: torch.Tensor, non_blocking: bool = False) -> torch.Tensor:
+        """Gradient with respect to the layer input, ``[m, in_size]``: every tile's IO-managed
+        backward MVM on its block of ``d_input`` (``[m, out_size]``, times the tile's mapping
+        scale), summed over the out-splits."""
+        d = _check_input(d_input, "d_input")
+        if not d.is_cuda or d.size(-1) != self.out_size:
+            raise RuntimeError(f"expected a CUDA [*, {self.out_size}] tensor")
+        m = d.numel() // self.out_size
+        out = torch.zeros(list(d.shape[:-1]) + [self.in_size], dtype=torch.float32, device=d.device)
+        check(self._lib.ab200_array_backward(self._h, d.data_ptr(), out.data_ptr(), m, _stream_ptr(d)))
+        if not non_blocking:
+            torch.cuda.current_stream(d.device).synchronize()
+        return out
+
+    def update(self, x_input: torch.Tensor, d_input: torch.Tensor, non_blocking: bool = False) -> None:
+        """Pulsed (or floating-point) update of every tile with its block of the activations and
+        of the gradients (divided by the tile's mapping scale)."""
+        x = _check_input(x_input, "x_input")
+        d = _check_input(d_input, "d_input")
+        if not (x.is_cuda and d.is_cuda) or x.size(-1) != self.in_size or d.size(-1) != self.out_size:
+            raise RuntimeError("expected CUDA tensors [*, in_size] and [*, out_size]")
+        m = x.numel() // self.in_size
+        if m != d.numel() // self.out_size:
+            raise RuntimeError("x_input and d_input need the same batch size")
+        check(self._lib.ab200_array_update(self._h, x.data_ptr(), d.data_ptr(), m, _stream_ptr(x)))
+        if not non_blocking:
+            torch.cuda.current_stream(x.device).synchronize()
+
     def get_tile_scales(self) -> torch.Tensor:
         """Digital output scales of the locally owned tiles ``[in-splits, out-splits]``."""
         n_in = self.num_in_splits if self._n_local_in is None else self._n_local_in

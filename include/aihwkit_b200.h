@@ -389,6 +389,18 @@ int ab200_array_get_weights(ab200_array *arr, float *w_host);
  * get_tile_scales: the scales of the locally owned tiles, [local in-splits][out-splits].
  * set_bias: digital bias [out_size] added once after the sum over in-splits (array.py:178-181);
  * NULL removes it. On a sharded layer only one rank should hold the bias. */
+/* Training of a mapped layer, tile by tile as autograd drives the tiles of TileModuleArray in the
+ * reference (TileWithPeriphery.pre_backward / backward / pre_update / update,
+ * src/aihwkit/simulator/tiles/periphery.py:1068-1110, 1154-1230): backward writes
+ * x_grad[:, in-split i] = sum over out-splits o of tile(i, o).backward(d[:, out-split o] *
+ * alpha_io); update runs tile(i, o).update(x[:, in-split i], d[:, out-split o] / alpha_io).
+ * d_dev is [m_batch][out_size]; x_dev / x_grad_dev are [m_batch][in_size]; only the locally owned
+ * input columns are read / written. */
+int ab200_array_backward(ab200_array *arr, const float *d_dev, float *x_grad_dev, int m_batch,
+                         void *stream);
+int ab200_array_update(ab200_array *arr, const float *x_dev, const float *d_dev, int m_batch,
+                       void *stream);
+int ab200_array_set_learning_rate(ab200_array *arr, float lr);
 int ab200_array_set_weights_scaled(ab200_array *arr, const float *w_host, float omega);
 int ab200_array_get_tile_scales(ab200_array *arr, float *scales_host);
 int ab200_array_set_bias(ab200_array *arr, const float *bias_host);

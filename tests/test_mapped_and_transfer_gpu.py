@@ -343,3 +343,60 @@ def test_mapped_forward_weight_scaling_and_bias(out_size, in_size, max_tile, m, 
         assert (np.abs(y0 - y0_or) <= 1.001 * lsb0 * n_in).all()
     finally:
         lib.ab200_set_mvm_path(0)
+
+
+@pytest.mark.parametrize("omega", [0.0, 0.5])
+def test_mapped_backward_and_update(omega):
+    """Training calls of the mapped layer: backward sums the tiles' IO-managed transposed MVMs over
+    the out-splits, update pulses every tile with its block of activations and gradients; with
+    weight scaling the gradient is multiplied (backward) / divided (update) by the tile's scale."""
+    from aihwkit_b200.rpu_base import tiles as T
+    from aihwkit_b200.sharded import split_sizes
+
+    rng = np.random.default_rng(21)
+    out_size, in_size, max_tile, m = 96, 200, 64, 12
+    p = H.training_params(noise=False, pulse_det=True, bm=False)
+    dp = H.device("sb", False)
+    cfg = p._config(1, 1, dp, seed=3)
+    arr = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+    W = rng.uniform(-0.3, 0.3, (out_size, in_size)).astype(np.float32)
+    arr.set_weights(torch.from_numpy(W), weight_scaling_omega=omega)
+    scales = arr.get_tile_scales().numpy()
+    Wl = arr.get_weights().numpy()  # logical weights after the per-element clipping
+    X = rng.uniform(-1, 1, (m, in_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.1, (m, out_size)).astype(np.float32)
+    out_sizes, in_sizes = split_sizes(out_size, max_tile), split_sizes(in_size, max_tile)
+    bio = O.IO.from_c(cfg.backward_io, backward=True)
+    up = O.Up.from_c(cfg.update)
+    lr = 0.02
+    arr.set_learning_rate(lr)
+
+    g = arr.backward(torch.from_numpy(Dm).cuda()).cpu().numpy()
+    g_or = np.zeros_like(g)
+    W_new = np.zeros_like(Wl)
+    c0 = 0
+    for ii, isz in enumerate(in_sizes):
+        r0 = 0
+        for oi, osz in enumerate(out_sizes):
+            a = scales[ii, oi]
+            wt = (Wl[r0 : r0 + osz, c0 : c0 + isz] / a).astype(np.float32)
+            g_or[:, c0 : c0 + isz] += O.backward(wt, (Dm[:, r0 : r0 + osz] * a).astype(np.float32), bio)
+            # tile (i, o) of the array draws its device parameters with construction seed
+            # base + 4099 * i + o
+            dpt = H.device("sb", False, seed=dp.construction_seed + 4099 * ii + oi)
+            ref_tile = T.AnalogTile(p._config(isz, osz, dpt, seed=3))
+            dev = O.DeviceArrays.from_hidden(O.DEV_SOFT_BOUNDS, ref_tile.get_hidden_parameter_names(),
+                                             ref_tile.get_hidden_parameters().numpy(), 0.0, True)
+            wn = wt.copy()
+            O.update(wn, X[:, c0 : c0 + isz], (Dm[:, r0 : r0 + osz] / a).astype(np.float32), lr,
+                     dp.dw_min, up, dev)
+            W_new[r0 : r0 + osz, c0 : c0 + isz] = wn * a
+            r0 += osz
+        c0 += isz
+    step = bio.res_out * np.abs(Dm).max() * scales.max() * len(out_sizes)
+    assert np.abs(g - g_or).max() <= 1.001 * step
+    assert np.mean(np.abs(g - g_or) > 1e-6) <= 5e-3
+    arr.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    W_got = arr.get_weights().numpy()
+    assert np.abs(W_got - Wl).max() > 1e-4
+    assert np.abs(W_got - W_new).max() <= 2e-6
