@@ -202,6 +202,12 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_array_num_in_splits": (_I, [_VP]),
         "ab200_array_num_out_splits": (_I, [_VP]),
         "ab200_array_set_weights": (_I, [_VP, _FP]),
+        "ab200_array_forward_scatter": (_I, [_VP, _FP, _I, _VP, _I, _I, _I, _VP]),
+        "ab200_sum_slots": (_I, [_FP, _I, C.c_longlong, _FP, _VP]),
+        "ab200_peer_alloc": (_I, [C.c_size_t, _I, C.POINTER(_VP), C.c_char_p]),
+        "ab200_peer_open": (_I, [C.c_char_p, _I, C.POINTER(_VP)]),
+        "ab200_peer_close": (_I, [_VP]),
+        "ab200_peer_free": (_I, [_VP]),
         "ab200_array_backward": (_I, [_VP, _FP, _FP, _I, _VP]),
         "ab200_array_update": (_I, [_VP, _FP, _FP, _I, _VP]),
         "ab200_array_set_learning_rate": (_I, [_VP, C.c_float]),

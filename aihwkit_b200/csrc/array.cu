@@ -259,6 +259,33 @@ const float *TileArray::scaledGradient(const float *d, int oi, int m, float fact
   return d_scratch_;
 }
 
+void TileArray::forwardScatter(const float *x_local, int m, float *const *out_table_dev,
+                               int n_owners, int rows_per_owner, int rotate_rows, cudaStream_t s) {
+  if (m <= 0) {
+    return;
+  }
+  if (in_begin_ == in_end_) {
+    AB200_FATAL("forward_scatter: this shard owns no in-split");
+  }
+  if (!tcEligible(m)) {
+    AB200_FATAL("forward_scatter needs the tensor-core path (batch >= 128, IO settings with integer "
+                "DAC codes, no bound management)");
+  }
+  if (n_owners <= 0 || rows_per_owner <= 0 || (long long)n_owners * rows_per_owner < m) {
+    AB200_FATAL("forward_scatter: the owners' row blocks do not cover the batch");
+  }
+  scatter_table_ = out_table_dev;
+  scatter_rows_ = rows_per_owner;
+  scatter_rotate_ = rotate_rows;
+  try {
+    forwardTc(x_local, localInSize(), nullptr, m, s);
+  } catch (...) {
+    scatter_table_ = nullptr;
+    throw;
+  }
+  scatter_table_ = nullptr;
+}
+
 void TileArray::backward(const float *d, float *x_grad, int m, cudaStream_t s) {
   if (m <= 0) {
     return;
@@ -350,6 +377,9 @@ void TileArray::forwardTc(const float *x0, long long x_ss, float *y, int m, cuda
   r.io = tiles_[0]->fio();
   r.tile_scale = scaled_ ? tile_scale_dev_ : nullptr;
   r.bias = bias_dev_;
+  r.out_table = scatter_table_;
+  r.rows_per_owner = scatter_rows_;
+  r.rotate_rows = scatter_rotate_;
   tc_->run(r, s);
 }
 

@@ -32,6 +32,12 @@ public:
   // input that holds only the locally owned columns: [m][localInSize()]
   void forwardLocal(const float *x_local, float *y, int m, bool is_test, cudaStream_t s);
   int localInSize() const;
+  // Forward of a sharded layer with the partial sums written straight to the owners of the row
+  // blocks (reduce-scatter by direct stores): x_local is [m][localInSize()]; owner q receives
+  // rows [q * rows_per_owner, (q + 1) * rows_per_owner) at out_table[q] (device array of n_owners
+  // pointers into local or peer memory, row pitch out_size). Needs the tensor-core path.
+  void forwardScatter(const float *x_local, int m, float *const *out_table_dev, int n_owners,
+                      int rows_per_owner, int rotate_rows, cudaStream_t s);
   // Training of a mapped layer, tile by tile as autograd does in the reference
   // (TileModuleArray modules -> TileWithPeriphery.backward / update, tiles/periphery.py:1068-1110,
   // 1154-1230). backward: x_grad[:, in-split i] = sum over out-splits o of
@@ -57,6 +63,8 @@ private:
   float *tile_scale_dev_ = nullptr;
   bool scaled_ = false;
   float *bias_dev_ = nullptr;
+  float *const *scatter_table_ = nullptr; // set only while forwardScatter runs
+  int scatter_rows_ = 0, scatter_rotate_ = 0;
   float *d_scratch_ = nullptr; // [m][largest out-split]: gradients times / over the tile scale
   size_t d_scratch_floats_ = 0;
   const float *scaledGradient(const float *d, int oi, int m, float factor, long long &ld,

@@ -5,6 +5,7 @@
 #include "tile.h"
 
 #include <algorithm>
+#include <cstdint>
 #include <cstring>
 
 namespace ab200 {
@@ -421,6 +422,90 @@ int ab200_array_set_learning_rate(ab200_array *arr, float lr) {
   A(arr)->setLearningRate(lr);
   AB200_CATCH
 }
+int ab200_array_forward_scatter(ab200_array *arr, const float *x_local_dev, int m_batch,
+                                float *const *out_table_dev, int n_owners, int rows_per_owner,
+                                int rotate_rows, void *stream) {
+  AB200_TRY
+  A(arr)->forwardScatter(x_local_dev, m_batch, out_table_dev, n_owners, rows_per_owner, rotate_rows,
+                         (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+namespace {
+__global__ void __launch_bounds__(256)
+    sumSlotsKernel(const float4 *slots, int n_slots, long long elems4, float4 *out) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= elems4) {
+    return;
+  }
+  float4 acc = slots[t];
+  for (int k = 1; k < n_slots; k++) {
+    const float4 v = slots[(long long)k * elems4 + t];
+    acc.x += v.x;
+    acc.y += v.y;
+    acc.z += v.z;
+    acc.w += v.w;
+  }
+  out[t] = acc;
+}
+} // namespace
+
+int ab200_sum_slots(const float *slots_dev, int n_slots, long long elems, float *out_dev,
+                    void *stream) {
+  AB200_TRY
+  if (n_slots <= 0 || elems <= 0) {
+    AB200_FATAL("sum_slots: nothing to add");
+  }
+  if ((elems & 3) != 0 || (((uintptr_t)slots_dev | (uintptr_t)out_dev) & 15) != 0) {
+    AB200_FATAL("sum_slots: element count must be a multiple of 4 and the buffers 16-byte aligned");
+  }
+  const long long e4 = elems / 4;
+  sumSlotsKernel<<<(unsigned)((e4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const float4 *)slots_dev, n_slots, e4, (float4 *)out_dev);
+  AB200_LAUNCH_CHECK();
+  AB200_CATCH
+}
+
+int ab200_peer_alloc(size_t bytes, int cuda_device, void **dev_ptr, unsigned char handle_out[64]) {
+  AB200_TRY
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  AB200_CUDA(cudaSetDevice(cuda_device));
+  void *p = nullptr;
+  AB200_CUDA(cudaMalloc(&p, bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    AB200_FATAL("cudaIpcGetMemHandle failed: " << cudaGetErrorString(e));
+  }
+  std::memcpy(handle_out, &h, 64);
+  *dev_ptr = p;
+  AB200_CATCH
+}
+
+int ab200_peer_open(const unsigned char handle[64], int cuda_device, void **dev_ptr) {
+  AB200_TRY
+  AB200_CUDA(cudaSetDevice(cuda_device));
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  void *p = nullptr;
+  AB200_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *dev_ptr = p;
+  AB200_CATCH
+}
+
+int ab200_peer_close(void *dev_ptr) {
+  AB200_TRY
+  AB200_CUDA(cudaIpcCloseMemHandle(dev_ptr));
+  AB200_CATCH
+}
+
+int ab200_peer_free(void *dev_ptr) {
+  AB200_TRY
+  AB200_CUDA(cudaFree(dev_ptr));
+  AB200_CATCH
+}
+
 int ab200_array_set_weights_scaled(ab200_array *arr, const float *w_host, float omega) {
   AB200_TRY
   A(arr)->setWeights(w_host, omega);

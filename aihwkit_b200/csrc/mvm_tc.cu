@@ -76,6 +76,12 @@ struct TcKernelParams {
   int *flags;
   float *out;
   long long out_ss;
+  // optional scatter of the output rows over several buffers (the row-block owners of a
+  // sharded layer, local or peer memory): row r goes to out_table[r / rows_per_owner] at row
+  // r % rows_per_owner; null = everything to `out`
+  float *const *out_table;
+  int rows_per_owner;
+  int rb_rotate; // the sweep over the row blocks starts at this block (staggers the ranks)
   int accumulate, backward;
   IOEff io;
   int *status;
@@ -324,6 +330,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const int gsize = min(p.group, p.n_chunks - g * p.group); // last group may be smaller
     rb = rem / gsize;
     chunk_idx = g * p.group + (rem - rb * gsize);
+    rb += p.rb_rotate;
+    rb -= rb >= n_rb ? n_rb : 0;
   };
 
   if (threadIdx.x == 0) {
@@ -543,7 +551,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
       }
       const uint32_t tile_tag = tag + p.noise_id0 + (uint32_t)(i * p.O + ch.x);
-      if (!TC_TIMED_WAIT(w_tfull, mbarWait(&tmem_full[b], (ai >> 1) & 1, abort_flag))) {
+      // the whole warp agrees on the outcome: what follows is warp-collective
+      if (!__all_sync(0xffffffffu,
+                      TC_TIMED_WAIT(w_tfull, mbarWait(&tmem_full[b], (ai >> 1) & 1, abort_flag)))) {
         atomicCAS(p.status, 0, TC_ERR_TMEM_FULL);
         *abort_flag = 1;
         ok = false;
@@ -631,10 +641,46 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
       }
     }
-    if (ok && row_ok) {
-      if (exceeded && io.bm != AB200_BM_NONE && p.flags != nullptr) {
-        atomicOr(&p.flags[row], 1);
+    if (ok && row_ok && exceeded && io.bm != AB200_BM_NONE && p.flags != nullptr) {
+      atomicOr(&p.flags[row], 1);
+    }
+    if (ok && p.out_table) {
+      // Scatter to the row-block owners, possibly peer memory: transpose the warp's 32 x 32
+      // block in registers (five exchange steps) so that every store instruction writes 128
+      // contiguous bytes of one row - over NVLink the 16-byte pieces of the row-per-lane layout
+      // would each travel alone.
+#pragma unroll
+      for (int st = 16; st >= 1; st >>= 1) {
+#pragma unroll
+        for (int c = 0; c < TC_EPI_COLS; c++) {
+          if ((c & st) == 0) {
+            const bool upper = (lane & st) != 0;
+            const float send = upper ? sum[c] : sum[c | st];
+            const float recv = __shfl_xor_sync(0xffffffffu, send, st);
+            if (upper) {
+              sum[c] = recv;
+            } else {
+              sum[c | st] = recv;
+            }
+          }
+        }
       }
+      // now sum[r] = element (row r of this warp's row group, column cbase + lane)
+      const int col = cbase + lane;
+      const int row0 = rb * ROWS + rank * TC_M + q * 32;
+      if (col < ch.w && row0 < p.m) {
+        const float b = p.bias ? p.bias[ch.z + col] : 0.0f;
+        const int owner = row0 / p.rows_per_owner; // 32-row groups never straddle two owners
+        float *o = p.out_table[owner] + (long long)(row0 - owner * p.rows_per_owner) * p.out_ss +
+                   ch.z + col;
+#pragma unroll
+        for (int r = 0; r < 32; r++) {
+          if (row0 + r < p.m) {
+            o[(long long)r * p.out_ss] = sum[r] + b;
+          }
+        }
+      }
+    } else if (ok && row_ok) {
       const bool vec = ((p.out_ss & 3) == 0) && ((ch.z & 3) == 0) &&
                        ((((uintptr_t)p.out) & 15) == 0) && !p.accumulate;
       float *orow = p.out + (long long)row * p.out_ss + ch.z + cbase;
@@ -974,6 +1020,10 @@ void TcEngine::ensureBatch(int m) {
   m_cap_ = cap;
 }
 
+// CTA pairs whenever there are at least two 128-row blocks (and the mode allows it)
+static bool usePairs(int m) { return mvmPath() != 3 && m > TC_M; }
+static int pair_rows(int m) { return usePairs(m) ? 2 * TC_M : TC_M; }
+
 void TcEngine::run(const Run &r, cudaStream_t s) {
   AB200_CUDA(cudaSetDevice(device_));
   checkStatus();
@@ -1042,6 +1092,13 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   p.flags = r.io.bm != AB200_BM_NONE ? d.flags : nullptr;
   p.out = r.out;
   p.out_ss = r.out_ss;
+  p.out_table = r.out_table;
+  p.rows_per_owner = r.rows_per_owner > 0 ? r.rows_per_owner : 1;
+  {
+    const int rows_item = pair_rows(r.m);
+    const int n_rb_items = (r.m + rows_item - 1) / rows_item;
+    p.rb_rotate = n_rb_items > 0 ? ((r.rotate_rows / rows_item) % n_rb_items + n_rb_items) % n_rb_items : 0;
+  }
   p.accumulate = r.accumulate ? 1 : 0;
   p.backward = r.backward ? 1 : 0;
   p.io = r.io;
@@ -1056,8 +1113,7 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   int grid_x = 0;
   int n_sm = 0;
   AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device_));
-  // CTA pairs whenever there are at least two 128-row blocks (and the mode allows it)
-  const bool pair = mvmPath() != 3 && r.m > TC_M;
+  const bool pair = usePairs(r.m);
   const bool bm = r.io.bm != AB200_BM_NONE;
   if (pair) {
     const int n_items = n_chunks_ * ((r.m + 2 * TC_M - 1) / (2 * TC_M));

@@ -48,6 +48,14 @@ public:
     // column added once
     const float *tile_scale = nullptr;
     const float *bias = nullptr;
+    // optional scatter of the output rows (sharded layer): device array of buffer pointers, one
+    // per row-block owner (local or peer memory); row r goes to out_table[r / rows_per_owner] at
+    // row r % rows_per_owner with pitch out_ss. rotate_rows (a multiple of the work-item height)
+    // is the row the sweep over the row blocks starts at: it staggers the ranks' sweeps so that no
+    // owner receives from two ranks at once.
+    float *const *out_table = nullptr;
+    int rows_per_owner = 0;
+    int rotate_rows = 0;
     // optional caller-owned per-row scratch (only valid for I == 1): lets the bound-management
     // re-run kernel see the same noise-management values and flags
     float *scale = nullptr, *factor = nullptr, *vnorm = nullptr, *sval = nullptr;

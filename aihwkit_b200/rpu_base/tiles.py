@@ -570,6 +570,21 @@ class TileArray:
                                                   int(is_test), _stream_ptr(x)))
         return out
 
+    def forward_scatter(self, x_local: torch.Tensor, out_table: torch.Tensor, rows_per_owner: int,
+                        rotate_rows: int = 0) -> None:
+        """Forward on this object's own input columns with the output rows written straight to
+        the buffers of their owners: ``out_table`` is a CUDA int64 tensor of device pointers (one
+        per owner, local or peer memory, row pitch ``out_size``); row ``r`` goes to owner
+        ``r // rows_per_owner``.  Asynchronous on the current stream."""
+        x = _check_input(x_local, "x_local")
+        if not x.is_cuda or x.dim() != 2 or x.size(1) != self.local_in_size:
+            raise RuntimeError(f"expected a CUDA [m, {self.local_in_size}] tensor")
+        if not out_table.is_cuda or out_table.dtype != torch.int64 or not out_table.is_contiguous():
+            raise RuntimeError("out_table must be a contiguous CUDA int64 tensor of device pointers")
+        check(self._lib.ab200_array_forward_scatter(
+            self._h, x.data_ptr(), x.size(0), out_table.data_ptr(), out_table.numel(),
+            int(rows_per_owner), int(rotate_rows), _stream_ptr(x)))
+
     def forward(self, x_input: torch.Tensor, is_test: bool = True, non_blocking: bool = False,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``x_input`` on the GPU: kernels only.  ``x_input`` on the CPU: the library pipelines

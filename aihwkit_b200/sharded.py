@@ -104,6 +104,90 @@ class ShardedTileArray:
             w.wait()
         return self._ov_partial
 
+    # ---- reduce-scatter by direct stores --------------------------------------------------------
+    def enable_scatter(self, m: int) -> None:
+        """Prepare :meth:`forward_reduce_scatter` for batches of ``m`` rows: every rank allocates
+        two sets of ``world`` slots of ``rows x out_size`` floats (double buffering over steps),
+        shares them with the other ranks of the node through CUDA IPC handles, and builds the
+        pointer tables the kernel scatters through."""
+        import ctypes as C
+
+        from . import _cabi
+
+        lib = _cabi.lib()
+        item = 256  # work-item height of the kernel: ownership changes on item boundaries
+        per_rank = (m + self.world - 1) // self.world
+        self._sc_rows = (per_rank + item - 1) // item * item
+        self._sc_m = m
+        dev_index = self.local.device.index
+        slot_floats = self._sc_rows * self.out_size
+        handles, self._sc_mine = [], []
+        for _ in range(2):
+            ptr, h = C.c_void_p(), C.create_string_buffer(64)
+            _cabi.check(lib.ab200_peer_alloc(4 * slot_floats * self.world, dev_index, C.byref(ptr), h))
+            self._sc_mine.append(ptr.value)
+            handles.append(h.raw)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, handles, group=self.group)
+        self._sc_peers, self._sc_tables = [], []
+        for b in range(2):
+            ptrs = []
+            for q in range(self.world):
+                if q == self.rank:
+                    base = self._sc_mine[b]
+                else:
+                    p = C.c_void_p()
+                    _cabi.check(lib.ab200_peer_open(gathered[q][b], dev_index, C.byref(p)))
+                    self._sc_peers.append(p.value)
+                    base = p.value
+                ptrs.append(base + 4 * slot_floats * self.rank)  # this rank's slot at owner q
+            self._sc_tables.append(torch.tensor(ptrs, dtype=torch.int64, device=self.local.device))
+        self._sc_flag = torch.zeros(1, device=self.local.device)
+        self._sc_step = 0
+        dist.barrier(group=self.group)
+
+    def forward_reduce_scatter(self, x_local: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Forward of the sharded layer with the sum over the ranks' in-splits done by direct
+        stores: every rank's kernel writes its partial sums into its slot at the owner of each
+        row block (peer memory over NVLink, tile by tile while it computes; the ranks sweep the
+        owners in staggered order), a barrier follows, and every owner adds its ``world`` slots.
+        Returns this rank's rows ``[rows, out_size]`` of the summed output: rank ``q`` owns rows
+        ``[q * rows, (q + 1) * rows)`` with ``rows = self.scatter_rows``; all on the GPU, no host
+        synchronisation."""
+        from . import _cabi
+
+        b = self._sc_step & 1
+        self._sc_step += 1
+        rotate = ((self.rank + 1) % self.world) * self._sc_rows
+        self.local.forward_scatter(x_local, self._sc_tables[b], self._sc_rows, rotate)
+        dist.all_reduce(self._sc_flag, group=self.group)  # every rank's stores have landed
+        if out is None:
+            out = torch.empty(self._sc_rows, self.out_size, device=self.local.device)
+        stream = int(torch.cuda.current_stream(self.local.device).cuda_stream)
+        _cabi.check(_cabi.lib().ab200_sum_slots(self._sc_mine[b], self.world,
+                                                self._sc_rows * self.out_size, out.data_ptr(), stream))
+        return out
+
+    @property
+    def scatter_rows(self) -> int:
+        return self._sc_rows
+
+    def disable_scatter(self) -> None:
+        """Close the peers' buffers and free this rank's (after a barrier: nobody writes any more)."""
+        from . import _cabi
+
+        if getattr(self, "_sc_mine", None) is None:
+            return
+        torch.cuda.synchronize(self.local.device)
+        dist.barrier(group=self.group)
+        lib = _cabi.lib()
+        for p in self._sc_peers:
+            _cabi.check(lib.ab200_peer_close(p))
+        dist.barrier(group=self.group)
+        for p in self._sc_mine:
+            _cabi.check(lib.ab200_peer_free(p))
+        self._sc_mine = None
+
     def forward_host(self, x_local_host: torch.Tensor, out_host: Optional[torch.Tensor] = None,
                      dst: int = 0, chunk_rows: int = 1024) -> Optional[torch.Tensor]:
         """End-to-end forward from host memory on every rank.

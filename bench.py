@@ -246,7 +246,17 @@ def run_ours(args):
     x_host = torch.randn(m, W["in_size"], generator=g).pin_memory()
     x = x_host.to(dev)
 
+    scatter = world > 1 and args.collective == "scatter"
+    c0, c1 = column_range(W["in_size"], W["max_tile"], rank, world)
+    if scatter:
+        # partial sums are pushed to the owners of the row blocks by the MVM kernel itself
+        # (peer stores over NVLink), the result stays sharded by rows
+        arr.enable_scatter(m)
+        x_local_dev = x[:, c0:c1].contiguous()
+
     def step():
+        if scatter:
+            return arr.forward_reduce_scatter(x_local_dev)
         if world > 1 and args.reduce_chunks > 1:
             return arr.forward_overlapped(x, dst=0, n_chunks=args.reduce_chunks, is_test=True)
         y = arr.forward_partial(x, is_test=True, non_blocking=True)
@@ -285,12 +295,20 @@ def run_ours(args):
 
     # end to end through the public API with host buffers: this rank's input columns come from
     # pinned host memory every step, the result goes back to the host on rank 0
-    c0, c1 = column_range(W["in_size"], W["max_tile"], rank, world)
     y_host = torch.empty(m, W["out_size"]).pin_memory() if rank == 0 else None
     # inputs are scattered over the ranks: each holds its own columns in page-locked host memory
     x_local_host = x_host[:, c0:c1].contiguous().pin_memory() if world > 1 else x_host
 
+    if scatter:
+        x_stage = torch.empty(m, c1 - c0, device=dev)
+        y_rows_host = torch.empty(arr.scatter_rows, W["out_size"]).pin_memory()
+
     def e2e_step():
+        if scatter:
+            # every rank copies its own input columns in and its own result rows out
+            x_stage.copy_(x_local_host, non_blocking=True)
+            y_rows_host.copy_(arr.forward_reduce_scatter(x_stage), non_blocking=True)
+            return
         # ShardedTileArray.forward_host: chunked host->device copies overlapped with the kernels
         # (inside the library for one rank), one reduce, result back to the host on rank 0
         arr.forward_host(x_local_host, y_host, dst=0)
@@ -328,7 +346,10 @@ def run_ours(args):
             "data": "synthetic",
             "config": {
                 "workload": "cfg1: 4096x4096 analog inference MVM, 64 tiles of 512x512, batch 8192",
-                "sharding": f"in-splits over {world} rank(s), NCCL reduce to rank 0",
+                "sharding": (f"in-splits over {world} rank(s), partial sums stored by the kernel "
+                             "into the row-block owners' memory over NVLink + barrier + local sum "
+                             "(reduce-scatter; the result stays sharded by rows)") if scatter
+                else f"in-splits over {world} rank(s), NCCL reduce to rank 0",
                 "l2": "input (134 MB) and output (134 MB) per step exceed the 126 MB L2",
             },
             "clocks": clocks,
@@ -405,6 +426,10 @@ def main():
                     help="rows of the bounded CPU sample (reference arm / cpu_baseline)")
     ap.add_argument("--mvm-path", type=int, default=0, choices=[0, 1, 2, 3],
                     help="kernel selection of the library (ab200_set_mvm_path); 0 = automatic")
+    ap.add_argument("--collective", default="scatter", choices=["scatter", "reduce"],
+                    help="N > 1: 'scatter' = the MVM kernel stores its partial sums into the row-block "
+                         "owners' memory (reduce-scatter fused with the compute); 'reduce' = local "
+                         "partial sums + NCCL reduce to rank 0")
     ap.add_argument("--reduce-chunks", type=int, default=1,
                     help="N > 1: row blocks whose partial-sum reduce overlaps the next block's kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true",

@@ -402,6 +402,29 @@ int ab200_array_update(ab200_array *arr, const float *x_dev, const float *d_dev,
                        void *stream);
 int ab200_array_set_learning_rate(ab200_array *arr, float lr);
 int ab200_array_set_weights_scaled(ab200_array *arr, const float *w_host, float omega);
+
+/* ---- sharded layer: partial sums pushed to the row-block owners (no counterpart in the
+ * reference, which has no multi-GPU path) ----------------------------------------------------
+ * ab200_array_forward_scatter: forward of this rank's tiles on its own input columns
+ * x_local_dev [m_batch][local_in_size]; instead of one local [m_batch][out_size] partial sum, the
+ * rows are written straight into the buffers of their owners: row r goes to
+ * out_table_dev[r / rows_per_owner] at row r % rows_per_owner, row pitch out_size. out_table_dev
+ * is a DEVICE array of n_owners pointers; the pointers may be peer memory opened with
+ * ab200_peer_open (plain stores over NVLink, no multicast). rotate_rows is the row this rank's
+ * sweep over the row blocks starts at. Needs the tensor-core path.
+ * ab200_sum_slots: out[e] = sum over k < n_slots of slots[k * elems + e]: the owner adds the
+ * partial sums the ranks wrote side by side (call it after a barrier over the ranks).
+ * ab200_peer_*: cudaMalloc'ed buffers shared between the processes of one node with CUDA IPC;
+ * handle_out / handle are 64 opaque bytes to pass to the other ranks. */
+int ab200_array_forward_scatter(ab200_array *arr, const float *x_local_dev, int m_batch,
+                                float *const *out_table_dev, int n_owners, int rows_per_owner,
+                                int rotate_rows, void *stream);
+int ab200_sum_slots(const float *slots_dev, int n_slots, long long elems, float *out_dev,
+                    void *stream);
+int ab200_peer_alloc(size_t bytes, int cuda_device, void **dev_ptr, unsigned char handle_out[64]);
+int ab200_peer_open(const unsigned char handle[64], int cuda_device, void **dev_ptr);
+int ab200_peer_close(void *dev_ptr);
+int ab200_peer_free(void *dev_ptr);
 int ab200_array_get_tile_scales(ab200_array *arr, float *scales_host);
 int ab200_array_set_bias(ab200_array *arr, const float *bias_host);
 /* TileModuleArray.forward (array.py:155-182): every tile does its own noise management, DAC,

@@ -1,0 +1,74 @@
+"""Sharded layer on two GPUs: the reduce-scatter by direct peer stores against the NCCL reduce of
+the same partial sums.  Needs two CUDA devices (skipped otherwise); every wait is a host-launched
+collective, nothing spins on the device."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, out_path):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+    from aihwkit_b200.sharded import ShardedTileArray, column_range
+    from tests import helpers as H
+
+    rng = np.random.default_rng(0)
+    out_size, in_size, max_tile, m = 1024, 2048, 512, 1000
+    W = rng.normal(0, 1 / np.sqrt(in_size), (out_size, in_size)).astype(np.float32)
+    X = rng.normal(0, 1, (m, in_size)).astype(np.float32)
+    cfg = H.inference_params(noise=True)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=8)
+    ok = True
+    for trial in range(2):
+        arr = ShardedTileArray(out_size, in_size, max_tile, max_tile,
+                               lambda b, e: T.TileArray(cfg, out_size, in_size, max_tile, max_tile,
+                                                        cuda_device=rank, in_split_range=(b, e)))
+        arr.local.set_weights(torch.from_numpy(W))
+        c0, c1 = column_range(in_size, max_tile, rank, world)
+        x_local = torch.from_numpy(np.ascontiguousarray(X[:, c0:c1])).cuda()
+        if trial == 0:
+            full = arr.reduce(arr.local.forward_local(x_local), dst=None)  # NCCL all-reduce
+            ref = full.cpu().numpy()
+        else:
+            arr.enable_scatter(m)
+            rows = arr.scatter_rows
+            for step in range(3):  # several steps: double-buffered slots
+                mine = arr.forward_reduce_scatter(x_local)
+            torch.cuda.synchronize()
+            lo, hi = rank * rows, min(m, (rank + 1) * rows)
+            # the call counter advanced: compare with a fresh NCCL result of the same call number
+            arr2 = ShardedTileArray(out_size, in_size, max_tile, max_tile,
+                                    lambda b, e: T.TileArray(cfg, out_size, in_size, max_tile, max_tile,
+                                                             cuda_device=rank, in_split_range=(b, e)))
+            arr2.local.set_weights(torch.from_numpy(W))
+            for step in range(3):
+                full2 = arr2.reduce(arr2.local.forward_local(x_local), dst=None)
+            want = full2[lo:hi].cpu().numpy()
+            got = mine[: hi - lo].cpu().numpy()
+            ok = ok and np.allclose(got, want, rtol=1e-6, atol=1e-6) and not np.array_equal(want, ref[lo:hi])
+            arr.disable_scatter()
+    with open(f"{out_path}.{rank}", "w") as f:
+        f.write("ok" if ok else "mismatch")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_reduce_scatter_by_peer_stores_matches_nccl(tmp_path):
+    import torch.multiprocessing as mp
+
+    out = str(tmp_path / "result")
+    mp.spawn(_worker, args=(2, 29650 + os.getpid() % 200, out), nprocs=2, join=True)
+    assert open(out + ".0").read() == "ok" and open(out + ".1").read() == "ok"

@@ -188,3 +188,40 @@ def test_cta_pair_and_single_cta_kernels_agree(path, out_size, in_size, max_tile
         res.append((y, g))
     assert np.array_equal(res[0][0], res[1][0])
     assert np.array_equal(res[0][1], res[1][1])
+
+
+def test_forward_scatter_to_row_block_owners(path):
+    """The scatter form of the mapped forward on one GPU: two local buffers stand in for the
+    owners of the row blocks; rows land at out_table[r // rows_per_owner], whatever row block the
+    sweep starts at, and equal the plain forward (same call counter => same noise)."""
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    rng = np.random.default_rng(2)
+    out_size, in_size, max_tile, m = 384, 1024, 512, 700
+    W = rng.normal(0, 1 / np.sqrt(in_size), (out_size, in_size)).astype(np.float32)
+    X = torch.from_numpy(rng.normal(0, 1, (m, in_size)).astype(np.float32)).cuda()
+    cfg = H.inference_params(noise=True)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=8)
+    rows = 512
+    results = []
+    for rotate in (None, 0, 512):
+        a = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+        a.set_weights(torch.from_numpy(W))
+        if rotate is None:
+            results.append(a.forward_local(X).cpu().numpy())
+            continue
+        owners = [torch.full((rows, out_size), -7.0, device="cuda") for _ in range(2)]
+        table = torch.tensor([o.data_ptr() for o in owners], dtype=torch.int64, device="cuda")
+        a.forward_scatter(X, table, rows, rotate)
+        torch.cuda.synchronize()
+        got = torch.cat(owners)[:m].cpu().numpy()
+        assert float(owners[1][m - rows:].max()) == -7.0  # rows past the batch are not written
+        results.append(got)
+    assert np.array_equal(results[0], results[1])
+    assert np.array_equal(results[0], results[2])
+    # the owners' sum of the slots
+    slots = torch.from_numpy(rng.normal(0, 1, (3, 64, 20)).astype(np.float32)).cuda()
+    out = torch.empty(64, 20, device="cuda")
+    _cabi.check(_cabi.lib().ab200_sum_slots(slots.data_ptr(), 3, 64 * 20, out.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert torch.allclose(out, slots.sum(0), atol=1e-6)
