@@ -6,6 +6,7 @@
 #include "tile.h"
 
 #include <memory>
+#include <mutex>
 #include <vector>
 
 namespace ab200 {
@@ -17,6 +18,7 @@ public:
   TileArray(const ab200_tile_config &cfg, int out_size, int in_size, int max_out, int max_in,
             int in_begin, int in_end, int cuda_device);
   ~TileArray();
+  std::mutex &mutex() const { return mu_; }
   int numInSplits() const { return (int)in_sizes_.size(); }
   int numOutSplits() const { return (int)out_sizes_.size(); }
   // omega > 0: every tile's weights are divided by max|w_tile| / omega and the quotient becomes
@@ -51,6 +53,7 @@ public:
   void setSeed(uint64_t seed);
 
 private:
+  mutable std::mutex mu_; // held by every C-ABI call on this array
   Tile &tile(int in_local, int out_idx) { return *tiles_[(size_t)in_local * out_sizes_.size() + out_idx]; }
   int out_size_, in_size_, device_;
   std::vector<int> in_sizes_, out_sizes_, in_off_, out_off_;

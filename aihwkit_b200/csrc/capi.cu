@@ -5,6 +5,7 @@
 #include "tile.h"
 
 #include <algorithm>
+#include <mutex>
 #include <cstdint>
 #include <cstring>
 
@@ -34,23 +35,34 @@ void setLastError(const char *msg) { g_error = msg ? msg : ""; }
   }                                                                                                \
   return 0;
 
-static Tile *T(ab200_tile *t) {
+// Every entry point holds the object's mutex for the duration of the call, as the reference's
+// binding does (std::lock_guard on RPUSimple::mutex_, src/rpucuda/rpu.h:669,
+// rpu_base_tiles.cpp:169,439,...): the handle is returned together with the lock.
+template <class X> struct Locked {
+  X *p;
+  std::unique_lock<std::mutex> lock;
+  X *operator->() const { return p; }
+};
+static Locked<Tile> T(ab200_tile *t) {
   if (!t) {
     AB200_FATAL("null tile handle");
   }
-  return reinterpret_cast<Tile *>(t);
+  Tile *x = reinterpret_cast<Tile *>(t);
+  return Locked<Tile>{x, std::unique_lock<std::mutex>(x->mutex())};
 }
-static const Tile *T(const ab200_tile *t) {
+static Locked<const Tile> T(const ab200_tile *t) {
   if (!t) {
     AB200_FATAL("null tile handle");
   }
-  return reinterpret_cast<const Tile *>(t);
+  const Tile *x = reinterpret_cast<const Tile *>(t);
+  return Locked<const Tile>{x, std::unique_lock<std::mutex>(x->mutex())};
 }
-static TileArray *A(ab200_array *a) {
+static Locked<TileArray> A(ab200_array *a) {
   if (!a) {
     AB200_FATAL("null array handle");
   }
-  return reinterpret_cast<TileArray *>(a);
+  TileArray *x = reinterpret_cast<TileArray *>(a);
+  return Locked<TileArray>{x, std::unique_lock<std::mutex>(x->mutex())};
 }
 
 extern "C" {

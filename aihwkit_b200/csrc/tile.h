@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -156,6 +157,7 @@ public:
   Tile(const Tile &) = delete;
   Tile &operator=(const Tile &) = delete;
 
+  std::mutex &mutex() const { return mu_; }
   int xSize() const { return x_size_; }
   int dSize() const { return d_size_; }
   int device() const { return device_; }
@@ -257,6 +259,7 @@ private:
   void gatherIndexed(const float *x, long long in_mat, int m_batch, int n_img, bool trans,
                      cudaStream_t s);
 
+  mutable std::mutex mu_; // held by every C-ABI call on this tile
   ab200_tile_config cfg_;
   int x_size_, d_size_;
   int device_ = -1;
