@@ -39,6 +39,7 @@ class IOParams(C.Structure):
         ("max_bm_res", C.c_float),
         ("inp_asymmetry", C.c_float),
         ("out_asymmetry", C.c_float),
+        ("nm_assumed_wmax", C.c_float),
     ]
 
 

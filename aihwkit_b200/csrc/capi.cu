@@ -81,6 +81,7 @@ void ab200_default_io_params(ab200_io_params *io) {
   io->inp_res = 1.0f / 126.0f;
   io->out_bound = 12.0f;
   io->out_res = 1.0f / 510.0f;
+  io->nm_assumed_wmax = 0.6f;
   io->out_noise = 0.06f;
   io->out_scale = 1.0f;
   io->max_bm_res = 0.25f;

@@ -29,24 +29,20 @@ template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKe
     return;
   }
   const float *row = p.in + (long long)s * p.in_ss;
-  float amax = 0.0f;
-  if (!io.is_perfect && io.nm == AB200_NM_ABS_MAX) {
+  NmStats st;
+  if (nmNeedsStats(io)) {
     if (WARP_PER_SAMPLE) {
       for (int k = lane; k < p.in_size; k += 32) {
-        float v = k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f;
-        amax = fmaxf(amax, fabsf(v));
+        st.add(k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f);
       }
-      for (int o = 16; o > 0; o >>= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-      }
+      st.warpReduce();
     } else {
       for (int k = 0; k < p.in_size; k++) {
-        float v = k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f;
-        amax = fmaxf(amax, fabsf(v));
+        st.add(k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f);
       }
     }
   }
-  float sval = nmValue(io, amax);
+  float sval = nmValue(io, st);
   float scale = inputScale(io, sval, /*reduction=*/1.0f, !p.backward);
   float vn = 0.0f;
   if (!io.is_perfect && io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f &&
@@ -232,7 +228,7 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
     if (p.flags[r] == 0) {
       continue;
     }
-    const float sval = p.sval[r];
+    float sval = p.sval[r];
     const float *row = p.in + (long long)r * p.in_ss;
     float reduction = 1.0f;
     float scale = 1.0f;
@@ -241,6 +237,31 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
     while (!done) {
       reduction *= 2.0f;
       round++;
+      if (round == 1 && io.bm == AB200_BM_ITERATIVE_WORST_CASE && io.nm != AB200_NM_ABS_MAX_NP_SUM) {
+        // IterativeWorstCase: the first re-run switches to the AbsMaxNPSum scale and starts the
+        // halving again from there (rpu_forward_backward_pass.cpp:945-950)
+        NmStats st;
+        for (int k = threadIdx.x; k < K; k += blockDim.x) {
+          st.add(k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f);
+        }
+        st.warpReduce();
+        __shared__ float st_sh[8][3];
+        if ((threadIdx.x & 31) == 0) {
+          st_sh[threadIdx.x >> 5][0] = st.amax;
+          st_sh[threadIdx.x >> 5][1] = st.psum;
+          st_sh[threadIdx.x >> 5][2] = st.nsum;
+        }
+        __syncthreads();
+        NmStats all;
+        for (int i = 0; i < (int)(blockDim.x >> 5); i++) {
+          all.amax = fmaxf(all.amax, st_sh[i][0]);
+          all.psum += st_sh[i][1];
+          all.nsum += st_sh[i][2];
+        }
+        __syncthreads();
+        sval = nmValueNPSum(io, all);
+        reduction = 1.0f;
+      }
       scale = inputScale(io, sval, reduction, true);
       float nacc = 0.0f;
       for (int k = threadIdx.x; k < K; k += blockDim.x) {

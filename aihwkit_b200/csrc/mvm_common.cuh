@@ -9,19 +9,67 @@
 
 namespace ab200 {
 
-// computeNoiseManagement (src/rpucuda/rpu_forward_backward_pass.cpp:113-131)
-__device__ __forceinline__ float nmValue(const IOEff &io, float amax) {
+// Per-sample statistics of the raw input that the noise-management types need.
+struct NmStats {
+  float amax = 0.0f;      // max |x|
+  float vmax = -3.4e38f;  // max x
+  float psum = 0.0f;      // sum of the positive inputs
+  float nsum = 0.0f;      // sum of the negative inputs
+  __device__ __forceinline__ void add(float x) {
+    amax = fmaxf(amax, fabsf(x));
+    vmax = fmaxf(vmax, x);
+    psum += x > 0.0f ? x : 0.0f;
+    nsum += x < 0.0f ? x : 0.0f;
+  }
+  __device__ __forceinline__ void warpReduce() {
+    for (int o = 16; o > 0; o >>= 1) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+      psum += __shfl_xor_sync(0xffffffffu, psum, o);
+      nsum += __shfl_xor_sync(0xffffffffu, nsum, o);
+    }
+  }
+};
+
+// AbsMaxNPSum (rpu_forward_backward_pass.cpp:152-173): the larger of the abs-max and a bound on
+// the output, sum of the same-sign inputs times the assumed largest weight over the output bound.
+__device__ __forceinline__ float nmValueNPSum(const IOEff &io, const NmStats &st) {
+  const float bound = isinf(io.out_bound) ? 1.0f : io.out_bound;
+  const float sum = fmaxf(st.psum, -st.nsum);
+  const float amax = io.nm_thres > 0.0f ? fminf(st.amax, io.nm_thres) : st.amax;
+  float np = __fdiv_rn(__fmul_rn(sum, io.nm_assumed_wmax), bound);
+  if (io.res_in > 0.0f) {
+    np = fminf(__fmul_rn(__fdiv_rn(amax, io.res_in), io.max_bm_res), np);
+  }
+  return fmaxf(amax, np);
+}
+
+// computeNoiseManagement (src/rpucuda/rpu_forward_backward_pass.cpp:113-178)
+__device__ __forceinline__ bool nmNeedsStats(const IOEff &io) {
+  return !io.is_perfect && (io.nm == AB200_NM_ABS_MAX || io.nm == AB200_NM_MAX ||
+                            io.nm == AB200_NM_ABS_MAX_NP_SUM);
+}
+__device__ __forceinline__ float nmValue(const IOEff &io, const NmStats &st) {
   if (io.is_perfect) {
     return 1.0f;
   }
   switch (io.nm) {
   case AB200_NM_ABS_MAX:
-    return io.nm_thres > 0.0f ? fminf(amax, io.nm_thres) : amax;
+    return io.nm_thres > 0.0f ? fminf(st.amax, io.nm_thres) : st.amax;
+  case AB200_NM_MAX:
+    return io.nm_thres > 0.0f ? fminf(st.vmax, io.nm_thres) : st.vmax;
+  case AB200_NM_ABS_MAX_NP_SUM:
+    return nmValueNPSum(io, st);
   case AB200_NM_CONSTANT:
     return io.nm_thres > 0.0f ? io.nm_thres : 1.0f;
   default:
     return 1.0f;
   }
+}
+__device__ __forceinline__ float nmValue(const IOEff &io, float amax) {
+  NmStats st;
+  st.amax = amax;
+  return nmValue(io, st);
 }
 
 // Input scale of one sample; 0 marks "output is identically zero"

@@ -893,6 +893,12 @@ bool TcEngine::ioSupported(const IOEff &io) {
   if (io.is_perfect || !(io.res_in > 0.0f) || !(io.inp_bound < 1e30f)) {
     return false;
   }
+  // the DAC kernel of this path knows the common noise-management types only, and the re-run
+  // kernel of IterativeWorstCase changes the noise-management value per row
+  if ((io.nm != AB200_NM_NONE && io.nm != AB200_NM_ABS_MAX && io.nm != AB200_NM_CONSTANT) ||
+      io.bm == AB200_BM_ITERATIVE_WORST_CASE) {
+    return false;
+  }
   float cb = io.inp_bound / io.res_in;
   float r = rintf(cb);
   return r >= 1.0f && r <= 256.0f && fabsf(cb - r) < 1e-3f;

@@ -44,17 +44,17 @@ IOEff resolveIO(const ab200_io_params &io, bool backward) {
   e.out_noise = io.out_noise;
   e.out_scale = io.out_scale;
   e.w_noise = io.w_noise;
+  e.nm_assumed_wmax = io.nm_assumed_wmax;
   if (!io.is_perfect) {
     if (io.noise_management != AB200_NM_NONE && io.inp_bound != 1.0f) {
       AB200_FATAL((backward ? "Backward noise managment expects input bound==1"
                             : "Forward noise managment expects bound==1"));
     }
     if (io.noise_management != AB200_NM_NONE && io.noise_management != AB200_NM_ABS_MAX &&
-        io.noise_management != AB200_NM_CONSTANT) {
+        io.noise_management != AB200_NM_CONSTANT && io.noise_management != AB200_NM_MAX &&
+        io.noise_management != AB200_NM_ABS_MAX_NP_SUM) {
+      // the running-average types keep state between calls (:139-150)
       AB200_FATAL("Noise Management type not implemented!");
-    }
-    if (io.bound_management == AB200_BM_ITERATIVE_WORST_CASE && !backward) {
-      AB200_FATAL("IterativeWorstCase bound management is not implemented");
     }
     if (io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) {
       AB200_FATAL("PCMRead weight noise is not implemented");

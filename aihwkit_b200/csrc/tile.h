@@ -33,6 +33,7 @@ struct IOEff {
   float out_scale;
   float w_noise;
   float nm_thres;
+  float nm_assumed_wmax;
 };
 
 IOEff resolveIO(const ab200_io_params &io, bool backward);

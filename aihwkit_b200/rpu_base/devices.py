@@ -132,12 +132,10 @@ class AnalogTileInputOutputParameter:
         if mv not in (int(AnalogMVType.Ideal), int(AnalogMVType.OnePass)):
             raise RuntimeError("MV type not implemented.")
         nm = int(self.noise_management)
-        if nm not in (0, 1, 4):
+        if nm not in (0, 1, 2, 3, 4):  # the running-average types keep state between calls
             raise RuntimeError("Noise Management type not implemented!")
         if int(self.w_noise_type) == int(WeightNoiseType.PCMRead) and self.w_noise > 0:
             raise RuntimeError("w_noise_type PCMRead is not implemented by the B200 analog tile")
-        if int(self.bound_management) == int(BoundManagementType.IterativeWorstCase):
-            raise RuntimeError("IterativeWorstCase bound management is not implemented")
         c = _cabi.IOParams()
         c.is_perfect = int(bool(self.is_perfect) or mv == int(AnalogMVType.Ideal))
         c.noise_management = nm
@@ -149,7 +147,7 @@ class AnalogTileInputOutputParameter:
         c.out_sto_round = int(bool(self.out_sto_round))
         for name in (
             "inp_bound", "inp_res", "inp_noise", "out_bound", "out_res", "out_noise", "out_scale",
-            "w_noise", "nm_thres", "max_bm_res", "inp_asymmetry", "out_asymmetry",
+            "w_noise", "nm_thres", "max_bm_res", "inp_asymmetry", "out_asymmetry", "nm_assumed_wmax",
         ):
             setattr(c, name, float(getattr(self, name)))
         return c

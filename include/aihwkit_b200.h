@@ -98,6 +98,7 @@ typedef struct ab200_io_params {
   float max_bm_res;
   float inp_asymmetry;
   float out_asymmetry;
+  float nm_assumed_wmax; /* AbsMaxNPSum noise management / IterativeWorstCase bound management */
 } ab200_io_params;
 
 /* PulsedUpdateMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:248-279;

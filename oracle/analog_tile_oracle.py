@@ -32,8 +32,8 @@ import numpy as np
 f32 = np.float32
 
 # enum values: src/rpucuda/rpu_pulsed_meta_parameter.h:146-178
-NM_NONE, NM_ABS_MAX, NM_CONSTANT = 0, 1, 4
-BM_NONE, BM_ITERATIVE = 0, 1
+NM_NONE, NM_ABS_MAX, NM_ABS_MAX_NP_SUM, NM_MAX, NM_CONSTANT = 0, 1, 2, 3, 4
+BM_NONE, BM_ITERATIVE, BM_ITERATIVE_WORST_CASE = 0, 1, 2
 WN_NONE, WN_ADDITIVE_CONSTANT = 0, 1
 PULSE_NONE, PULSE_STOCHASTIC_COMPRESSED, PULSE_DETERMINISTIC_IMPLICIT = 0, 1, 5
 DEV_IDEAL, DEV_CONSTANT_STEP, DEV_LINEAR_STEP, DEV_SOFT_BOUNDS, DEV_SOFT_BOUNDS_REFERENCE = range(5)
@@ -67,6 +67,7 @@ class IO:
     out_scale: float = 1.0
     w_noise: float = 0.0
     nm_thres: float = 0.0
+    nm_assumed_wmax: float = 0.6
     res_in: np.float32 = field(default=f32(0), init=False)
     res_out: np.float32 = field(default=f32(0), init=False)
 
@@ -114,6 +115,7 @@ class IO:
             out_scale=float(c.out_scale),
             w_noise=float(c.w_noise),
             nm_thres=float(c.nm_thres),
+            nm_assumed_wmax=float(c.nm_assumed_wmax),
         )
         return io.finalize(backward)
 
@@ -125,16 +127,37 @@ def quantize(v: np.ndarray, res: np.float32) -> np.ndarray:
     return (np.rint((v / f32(res)).astype(f32)).astype(f32) * f32(res)).astype(f32)
 
 
-def _nm_scale(v: np.ndarray, io: IO) -> np.ndarray:
+def _nm_scale(v: np.ndarray, io: IO, nm_type: Optional[int] = None) -> np.ndarray:
     """computeNoiseManagement, per sample (rpu_forward_backward_pass.cpp:113-178)."""
     m = v.shape[0]
-    if io.noise_management == NM_NONE:
+    nm_type = io.noise_management if nm_type is None else nm_type
+    if nm_type == NM_NONE:
         return np.ones(m, f32)
-    if io.noise_management == NM_ABS_MAX:
+    if nm_type == NM_ABS_MAX:
         s = np.abs(v).max(axis=1).astype(f32)
         return np.minimum(s, f32(io.nm_thres)) if io.nm_thres > 0 else s
-    if io.noise_management == NM_CONSTANT:
+    if nm_type == NM_MAX:
+        s = v.max(axis=1).astype(f32)
+        return np.minimum(s, f32(io.nm_thres)) if io.nm_thres > 0 else s
+    if nm_type == NM_CONSTANT:
         return np.full(m, io.nm_thres if io.nm_thres > 0 else 1.0, f32)
+    if nm_type == NM_ABS_MAX_NP_SUM:
+        amax = np.abs(v).max(axis=1).astype(f32)
+        bound = f32(1.0) if np.isinf(io.out_bound) else f32(io.out_bound)
+        # sequential fp32 sums like the reference's loop
+        psum = np.zeros(m, f32)
+        nsum = np.zeros(m, f32)
+        for j in range(v.shape[1]):
+            col = v[:, j]
+            psum = (psum + np.where(col > 0, col, f32(0))).astype(f32)
+            nsum = (nsum + np.where(col < 0, col, f32(0))).astype(f32)
+        tot = np.maximum(psum, -nsum)
+        if io.nm_thres > 0:
+            amax = np.minimum(amax, f32(io.nm_thres))
+        np_scale = (tot * f32(io.nm_assumed_wmax) / bound).astype(f32)
+        if io.res_in > 0:
+            np_scale = np.minimum((amax / io.res_in * f32(io.max_bm_res)).astype(f32), np_scale)
+        return np.maximum(amax, np_scale).astype(f32)
     raise NotImplementedError("noise management type")
 
 
@@ -198,9 +221,17 @@ def forward(
     out_scale = f32(io.out_scale) * f32(alpha)
     final_scale = np.ones(m, f32)
     scaling_any = np.zeros(m, bool)
+    bm_round = 0
+    s = s.copy()
     while todo.any():
         red = f32(red * f32(2.0))
         idx = np.nonzero(todo)[0]
+        if (bm_round == 1 and io.bound_management == BM_ITERATIVE_WORST_CASE
+                and io.noise_management != NM_ABS_MAX_NP_SUM):
+            # the first re-run switches to the AbsMaxNPSum scale and restarts the halving (:945-950)
+            s[idx] = _nm_scale(x[idx], io, NM_ABS_MAX_NP_SUM)
+            red = f32(1.0)
+        bm_round += 1
         scale = np.ones(len(idx), f32)
         scaling = np.zeros(len(idx), bool)
         if nm:

@@ -50,6 +50,7 @@ void toIO(const ab200_io_params &s, IOMetaParameter<float> &io) {
   io.max_bm_res = s.max_bm_res;
   io.inp_asymmetry = s.inp_asymmetry;
   io.out_asymmetry = s.out_asymmetry;
+  io.nm_assumed_wmax = s.nm_assumed_wmax;
 }
 
 void toUp(const ab200_update_params &s, PulsedUpdateMetaParameter<float> &up) {

@@ -254,3 +254,39 @@ def test_exp_step_device_noise_off(shape):
     O.update(Wo, X, Dm, lr, gran, up, dev)
     assert np.abs(t.get_weights() - Wo).max() <= 2e-6
     assert np.abs(t.get_weights() - W).max() > 1e-3  # the update did something
+
+
+@pytest.mark.parametrize("nm,bm", [("Max", "Iterative"), ("AbsMaxNPSum", "Iterative"),
+                                   ("AbsMax", "IterativeWorstCase"), ("None_", "IterativeWorstCase")])
+def test_noise_and_bound_management_variants(nm, bm):
+    """Max and AbsMaxNPSum noise management, IterativeWorstCase bound management: the oracle
+    equals the compiled reference with noise off, rows that clip and re-run included."""
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(7)
+    x_size, d_size, m = 96, 40, 24
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=1.5)
+    p.forward_io.noise_management = getattr(D.NoiseManagementType, nm)
+    p.forward_io.bound_management = getattr(D.BoundManagementType, bm)
+    p.forward_io.nm_assumed_wmax = 0.5
+    if nm == "None_":
+        p.forward_io.inp_bound = 1.0
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=3)
+    t = ref.RefTile(cfg)
+    t.set_weights(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32))
+    W = t.get_weights()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    X[3] = -np.abs(X[3])  # Max noise management: no positive input => zero output
+    X[5] *= 0.05
+    io = O.IO.from_c(cfg.forward_io)
+    y_ref = t.forward(X)
+    y, _, _, red = O.forward(W, X, io, return_pre_adc=True)
+    assert np.array_equal(y_ref, y)
+    if nm == "Max":
+        assert (red > 1).any()  # some rows re-ran with a halved input
+        assert (y[3] == 0).all()
+    if bm == "IterativeWorstCase":
+        # the re-run really happened: without bound management the clipped rows differ
+        io_plain = O.IO.from_c(cfg.forward_io)
+        io_plain.bound_management = O.BM_NONE
+        assert not np.array_equal(O.forward(W, X, io_plain), y)

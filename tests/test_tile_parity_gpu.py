@@ -331,3 +331,33 @@ def test_exp_step_stochastic_update_statistics(complex_noise):
         O.update(Wo, X, Dm, lr, gran, up, dev, org)
         dwo.append(Wo - Wc)
     H.assert_moments_agree(np.stack(dws), np.stack(dwo))
+
+
+@pytest.mark.parametrize("nm,bm", [("Max", "Iterative"), ("AbsMaxNPSum", "Iterative"),
+                                   ("AbsMax", "IterativeWorstCase"), ("AbsMaxNPSum", "None_")])
+@pytest.mark.parametrize("m", [24, 300])
+def test_noise_and_bound_management_variants(nm, bm, m):
+    """Max / AbsMaxNPSum noise management and IterativeWorstCase bound management against the
+    oracle (pinned to the compiled reference in tests/test_oracle_vs_reference.py)."""
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(7)
+    x_size, d_size = 96, 40
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=1.5)
+    p.forward_io.noise_management = getattr(D.NoiseManagementType, nm)
+    p.forward_io.bound_management = getattr(D.BoundManagementType, bm)
+    p.forward_io.nm_assumed_wmax = 0.5
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    X[3] = -np.abs(X[3])
+    X[5] *= 0.05
+    fio = O.IO.from_c(cfg.forward_io)
+    y_or, _, scale, _ = O.forward(W, X, fio, return_pre_adc=True)
+    y = t.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    lsb = (fio.res_out / np.maximum(scale, 1e-30))[:, None]
+    frac, worst = H.lsb_report(y, y_or, lsb)
+    assert frac <= 3e-3 and worst <= 1.001, (frac, worst)
+    if nm == "Max":
+        assert (y[3] == 0).all()
