@@ -187,6 +187,7 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_forward_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _I, _VP]),
         "ab200_tile_backward_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _VP]),
         "ab200_tile_update_indexed": (_I, [_VP, _FP, _FP, C.c_longlong, _I, _I, _I, _VP]),
+        "ab200_sizeof": (C.c_size_t, [_I]),
         "ab200_tile_extra_count": (_I, []),
         "ab200_tile_extra_name": (C.c_char_p, [_I]),
         "ab200_tile_dump_extra": (_I, [_VP, C.POINTER(C.c_double)]),

@@ -69,6 +69,16 @@ extern "C" {
 
 const char *ab200_last_error(void) { return g_error.c_str(); }
 const char *ab200_version(void) { return "aihwkit_b200 0.1.0 (sm_100a)"; }
+size_t ab200_sizeof(int which) {
+  switch (which) {
+  case 0: return sizeof(ab200_io_params);
+  case 1: return sizeof(ab200_update_params);
+  case 2: return sizeof(ab200_device_params);
+  case 3: return sizeof(ab200_transfer_params);
+  case 4: return sizeof(ab200_tile_config);
+  default: return 0;
+  }
+}
 
 void ab200_default_io_params(ab200_io_params *io) {
   std::memset(io, 0, sizeof(*io));

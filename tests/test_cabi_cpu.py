@@ -27,11 +27,12 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_sizes_match_header():
-    # layouts are plain int32 / float / uint64 fields; sizes are what a C compiler produces
-    assert C.sizeof(_cabi.IOParams) == 20 * 4
-    assert C.sizeof(_cabi.UpdateParams) == 10 * 4
-    assert C.sizeof(_cabi.DeviceParams) == 42 * 4
-    assert C.sizeof(_cabi.TransferParams) == 9 * 4 + 20 * 4 + 10 * 4
+    # the ctypes mirrors have the layout the library was compiled with
+    lib = _cabi.lib()
+    for which, cls in enumerate((_cabi.IOParams, _cabi.UpdateParams, _cabi.DeviceParams,
+                                 _cabi.TransferParams, _cabi.TileConfig)):
+        assert C.sizeof(cls) == lib.ab200_sizeof(which), cls.__name__
+    assert C.sizeof(_cabi.IOParams) == 21 * 4
     assert C.sizeof(_cabi.TileConfig) % 8 == 0
 
 
