@@ -124,6 +124,11 @@ class TransferParams(C.Structure):
         ("transfer_columns", C.c_int32),
         ("transfer_io", IOParams),
         ("transfer_up", UpdateParams),
+        ("buffered", C.c_int32),
+        ("forget_buffer", C.c_int32),
+        ("thres_scale", C.c_float),
+        ("step", C.c_float),
+        ("momentum", C.c_float),
     ]
 
 

@@ -139,6 +139,9 @@ void ab200_default_transfer_params(ab200_transfer_params *tp) {
   std::memset(tp, 0, sizeof(*tp));
   tp->transfer_every = 1.0f;
   tp->n_reads_per_transfer = 1;
+  tp->thres_scale = 1.0f;
+  tp->step = 1.0f;
+  tp->forget_buffer = 1;
   tp->transfer_lr = 1.0f;
   tp->scale_transfer_lr = 1;
   tp->scale_fast_lr = 1;

@@ -415,6 +415,7 @@ Tile::~Tile() {
     cudaFree(onehot_);
     cudaFree(tread_);
     cudaFree(t_words_);
+    cudaFree(t_buffer_);
     cudaFree(idx_);
     cudaFree(cols_x_);
     cudaFree(cols_d_);
@@ -489,6 +490,10 @@ void Tile::toDevice(int cuda_device) {
     AB200_CUDA(cudaMalloc(&onehot_, (size_t)x_size_ * sizeof(float)));
     AB200_CUDA(cudaMalloc(&tread_, (size_t)d_size_ * sizeof(float)));
     AB200_CUDA(cudaMalloc(&t_words_, 2 * (size_t)(x_size_ + d_size_) * sizeof(uint32_t)));
+    if (cfg_.transfer.buffered) {
+      AB200_CUDA(cudaMalloc(&t_buffer_, size * sizeof(float)));
+      AB200_CUDA(cudaMemset(t_buffer_, 0, size * sizeof(float)));
+    }
   }
   AB200_CUDA(cudaMalloc(&bm_stats_, 2 * sizeof(int)));
   AB200_CUDA(cudaMemset(bm_stats_, 0, 2 * sizeof(int)));
@@ -637,7 +642,8 @@ int Tile::hiddenCount() const {
     return 0;
   }
   if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
-    return (int)dev_[0].names.size() + (int)dev_[1].names.size() + 2;
+    return (int)dev_[0].names.size() + (int)dev_[1].names.size() + 2 +
+           (cfg_.transfer.buffered ? 1 : 0);
   }
   return (int)dev_[0].names.size();
 }
@@ -651,6 +657,10 @@ const char *Tile::hiddenName(int i) const {
     return dev_[0].names[i].c_str();
   }
   int n0 = (int)dev_[0].names.size();
+  if (cfg_.transfer.buffered && i == hiddenCount() - 1) {
+    buf = "buffered_FP_weight_0"; // rpu_buffered_transfer_device.cpp:217-227
+    return buf.c_str();
+  }
   int k = i <= n0 ? 0 : 1;
   int local = k == 0 ? i : i - n0 - 1;
   int nk = (int)dev_[k].names.size();
@@ -690,6 +700,19 @@ void Tile::getHidden(float *out) {
       std::memset(o, 0, size * sizeof(float));
     }
     o += size;
+  }
+  if (cfg_.transfer.buffered) {
+    if (device_ >= 0) {
+      std::vector<float> t(size);
+      AB200_CUDA(cudaMemcpy(t.data(), t_buffer_, size * sizeof(float), cudaMemcpyDeviceToHost));
+      for (int i = 0; i < d_size_; i++) {
+        for (int j = 0; j < x_size_; j++) {
+          o[(size_t)i * x_size_ + j] = t[(size_t)j * d_size_ + i];
+        }
+      }
+    } else {
+      std::memset(o, 0, size * sizeof(float));
+    }
   }
 }
 
@@ -731,6 +754,15 @@ void Tile::setHidden(const float *in) {
       requireDevice("set_hidden_parameters");
       uploadDeviceStore(dev_[k]);
     }
+  }
+  if (cfg_.device_kind == AB200_DEVICE_TRANSFER && cfg_.transfer.buffered && device_ >= 0) {
+    std::vector<float> t(size);
+    for (int i = 0; i < d_size_; i++) {
+      for (int j = 0; j < x_size_; j++) {
+        t[(size_t)j * d_size_ + i] = p[(size_t)i * x_size_ + j];
+      }
+    }
+    AB200_CUDA(cudaMemcpy(t_buffer_, t.data(), size * sizeof(float), cudaMemcpyHostToDevice));
   }
   // weights are re-clipped to the new bounds (onSetWeights at the end of setDeviceParameter)
   w_version_++;
@@ -965,7 +997,20 @@ void Tile::doTransfer(cudaStream_t s) {
       continue;
     }
     uint32_t call = transfer_calls_++;
-    launchTransferRead(w_fast_, col, d_size_, t_io_, key_, call, onehot_, x_size_, tread_, s);
+    float write_lr = t_lr;
+    if (t.buffered) {
+      // Tiki-Taka v2 (BufferedTransferRPUDevice::readAndUpdate,
+      // rpu_buffered_transfer_device.cpp:142-212): plain read, accumulate into the buffer column,
+      // pulse the slow tile with the whole steps only, each worth `step` granularities
+      launchTransferRead(w_fast_, col, d_size_, t_io_, key_, call, onehot_, x_size_, tread_, 1.0f, s);
+      const float gran = dev_[1].dw_min;
+      launchTransferBuffer(t_buffer_ + (size_t)col * d_size_, tread_, d_size_, fabsf(t_lr),
+                           t.thres_scale * gran, (float)t_up_.desired_bl, t.momentum,
+                           t.forget_buffer, s);
+      write_lr = t.step * gran;
+    } else {
+      launchTransferRead(w_fast_, col, d_size_, t_io_, key_, call, onehot_, x_size_, tread_, -1.0f, s);
+    }
     UpdateProblem u{};
     u.x = onehot_;
     u.x_ss = x_size_;
@@ -977,8 +1022,8 @@ void Tile::doTransfer(cudaStream_t s) {
     u.x_size = x_size_;
     u.d_size = d_size_;
     u.m = 1;
-    u.lr = fabsf(t_lr);
-    u.lr_neg = t_lr < 0.0f;
+    u.lr = fabsf(write_lr);
+    u.lr_neg = write_lr < 0.0f;
     u.dw_min = dev_[1].dw_min;
     u.up = t_up_;
     u.key = key_;
@@ -1000,7 +1045,7 @@ void Tile::doTransfer(cudaStream_t s) {
     u.s_begin = 0;
     u.s_end = 1;
     if (t_up_.pulse_type == AB200_PULSE_NONE) {
-      launchFPUpdate(u, t_lr, s);
+      launchFPUpdate(u, write_lr, s);
     } else {
       launchPulsePrepare(u, s);
       launchPulsedUpdate(u, s);

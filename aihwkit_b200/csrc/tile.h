@@ -144,8 +144,12 @@ void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream);
 void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream);
 void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream);
 void launchTransferRead(const float *w_fast, int col, int d_size, const IOEff &io, PhiloxKey key,
-                        uint32_t call, float *x_onehot, int x_size, float *r_out,
+                        uint32_t call, float *x_onehot, int x_size, float *r_out, float alpha,
                         cudaStream_t stream);
+// buffered Transfer: accumulate a read-out column into the buffer, emit the whole steps
+void launchTransferBuffer(float *buffer_col, float *read_inout, int d_size, float lr_abs,
+                          float buffer_granularity, float max_steps, float momentum,
+                          int forget_buffer, cudaStream_t stream);
 void launchTransposeDX(const float *src, float *dst, int rows, int cols, cudaStream_t stream);
 void launchClipToBounds(float *w, const float4 *par4, long long n, cudaStream_t stream);
 
@@ -275,6 +279,7 @@ private:
   float *w_owned_ = nullptr;
   uint64_t shared_version_ = 0;
   float *w_fast_ = nullptr; // Transfer: fast (hidden) tile A, [x][d]
+  float *t_buffer_ = nullptr; // buffered Transfer: digital buffer per element, [x][d]
   DeviceStore dev_[2];
   int n_dev_ = 1;
   // Transfer counters (rpu_transfer_device.cpp:396-516, rpu_vector_device.cpp:513-526)

@@ -692,7 +692,7 @@ void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream
 // the one-hot vector that the following pulsed write uses as its x input.
 __global__ void transferReadKernel(const float *w_fast, int col, int d_size, IOEff io,
                                    PhiloxKey key, uint32_t call, float *x_onehot, int x_size,
-                                   float *r_out) {
+                                   float *r_out, float alpha) {
   int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < x_size) {
     x_onehot[t] = t == col ? 1.0f : 0.0f;
@@ -702,7 +702,7 @@ __global__ void transferReadKernel(const float *w_fast, int col, int d_size, IOE
   }
   float y;
   if (io.is_perfect) {
-    y = w_fast[(long long)col * d_size + t] * (-io.out_scale);
+    y = w_fast[(long long)col * d_size + t] * (alpha * io.out_scale);
   } else {
     float v = prepareInput(io, 1.0f, 1.0f);
     float acc = __fmul_rn(w_fast[(long long)col * d_size + t], v);
@@ -713,17 +713,47 @@ __global__ void transferReadKernel(const float *w_fast, int col, int d_size, IOE
     }
     bool ex = false;
     y = finalizeOutput(io, acc, sigma, z[t & 3], ex);
-    y = __fmul_rn(y, __fmul_rn(io.out_scale, -1.0f));
+    y = __fmul_rn(y, __fmul_rn(io.out_scale, alpha));
   }
   r_out[t] = y;
 }
 
+// Buffered transfer (Tiki-Taka v2), BufferedTransferRPUDevice::readAndUpdate
+// (src/rpucuda/rpu_buffered_transfer_device.cpp:178-208): omega = H + read * |lr|;
+// n = trunc(omega / granularity) limited to +-max_steps; H keeps omega * momentum (forget) or
+// omega minus the transferred part; the slow tile is then pulsed with d = -n.
+__global__ void transferBufferKernel(float *buffer_col, float *read_inout, int d_size, float lr_abs,
+                                     float bg, float max_steps, float momentum, int forget_buffer) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= d_size) {
+    return;
+  }
+  const float omega = __fadd_rn(buffer_col[t], __fmul_rn(read_inout[t], lr_abs));
+  const float n = fmaxf(fminf(truncf(__fdiv_rn(omega, bg)), max_steps), -max_steps);
+  float h = omega;
+  if (n != 0.0f) {
+    const float sub_momentum = 1.0f - fmaxf(fminf(momentum, 1.0f), 0.0f);
+    h = forget_buffer ? __fmul_rn(omega, momentum)
+                      : __fsub_rn(omega, __fmul_rn(__fmul_rn(sub_momentum, n), bg));
+  }
+  buffer_col[t] = h;
+  read_inout[t] = -n;
+}
+
+void launchTransferBuffer(float *buffer_col, float *read_inout, int d_size, float lr_abs,
+                          float buffer_granularity, float max_steps, float momentum,
+                          int forget_buffer, cudaStream_t stream) {
+  transferBufferKernel<<<(d_size + 255) / 256, 256, 0, stream>>>(
+      buffer_col, read_inout, d_size, lr_abs, buffer_granularity, max_steps, momentum, forget_buffer);
+  AB200_LAUNCH_CHECK();
+}
+
 void launchTransferRead(const float *w_fast, int col, int d_size, const IOEff &io, PhiloxKey key,
-                        uint32_t call, float *x_onehot, int x_size, float *r_out,
+                        uint32_t call, float *x_onehot, int x_size, float *r_out, float alpha,
                         cudaStream_t stream) {
   int n = d_size > x_size ? d_size : x_size;
   transferReadKernel<<<(n + 255) / 256, 256, 0, stream>>>(w_fast, col, d_size, io, key, call,
-                                                        x_onehot, x_size, r_out);
+                                                        x_onehot, x_size, r_out, alpha);
   AB200_LAUNCH_CHECK();
 }
 

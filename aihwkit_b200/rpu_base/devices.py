@@ -472,6 +472,34 @@ class TransferResistiveDeviceParameter(VectorResistiveDeviceParameter):
         c.transfer_columns = 1
         c.transfer_io = self.transfer_forward._to_c()
         c.transfer_up = self.transfer_update._to_c()
+        c.buffered = 0
+        c.thres_scale, c.step, c.momentum, c.forget_buffer = 1.0, 1.0, 0.0, 1
+        return c
+
+
+class BufferedTransferResistiveDeviceParameter(TransferResistiveDeviceParameter):
+    """BufferedTransferRPUDeviceMetaParameter, Tiki-Taka v2 (rpu_base_devices.cpp
+    ``BufferedTransferResistiveDeviceParameter``; defaults of ``initDefaults``,
+    src/rpucuda/rpu_buffered_transfer_device.h:54-68)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.thres_scale = 1.0
+        self.step = 1.0
+        self.momentum = 0.0
+        self.forget_buffer = True
+        self.transfer_lr = 1.0
+        self.scale_transfer_lr = True
+        self.transfer_update.update_bl_management = False
+        self.transfer_update.update_management = False
+        self.transfer_update.desired_bl = 1
+        self.transfer_update.fixed_bl = True
+
+    def _to_c(self) -> _cabi.TransferParams:
+        c = super()._to_c()
+        c.buffered = 1
+        c.thres_scale, c.step = float(self.thres_scale), float(self.step)
+        c.momentum, c.forget_buffer = float(self.momentum), int(bool(self.forget_buffer))
         return c
 
 

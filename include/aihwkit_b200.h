@@ -184,6 +184,14 @@ typedef struct ab200_transfer_params {
   int32_t transfer_columns;
   ab200_io_params transfer_io;
   ab200_update_params transfer_up;
+  /* BufferedTransferRPUDeviceMetaParameter (Tiki-Taka v2, src/rpucuda/rpu_buffered_transfer_device.h:
+   * 20-37): the read-out of the fast tile is accumulated in a digital buffer per element, and
+   * the slow tile is pulsed only by the whole multiples of thres_scale * granularity in it */
+  int32_t buffered;
+  int32_t forget_buffer;
+  float thres_scale;
+  float step;
+  float momentum;
 } ab200_transfer_params;
 
 /* Everything PulsedMetaParameter::createRPUArray needs

@@ -554,6 +554,7 @@ class TransferOracle:
         self.x_size, self.d_size = x_size, d_size
         self.update_idx = 0
         self.slice_idx = 0
+        self.h = np.zeros_like(w_visible)  # digital buffer of the buffered variant (Tiki-Taka v2)
 
     def update(self, x, d, lr, rng=None):
         m = x.shape[0]
@@ -578,6 +579,24 @@ class TransferOracle:
             col = (self.slice_idx + k) % self.x_size
             e = np.zeros((1, self.x_size), f32)
             e[0, col] = 1
+            if getattr(tp, "buffered", 0):
+                # BufferedTransferRPUDevice::readAndUpdate (rpu_buffered_transfer_device.cpp:142-212)
+                r = forward(self.a, e, self.t_io, rng, alpha=1.0)[0]
+                bg = f32(tp.thres_scale) * f32(self.dw_min_slow)
+                omega = (self.h[:, col] + r * abs(t_lr)).astype(f32)
+                max_steps = f32(self.t_up.desired_bl)
+                n_steps = np.clip(np.trunc((omega / bg).astype(f32)), -max_steps, max_steps).astype(f32)
+                mom = f32(tp.momentum)
+                if tp.forget_buffer:
+                    keep = (omega * mom).astype(f32)
+                else:
+                    sub = f32(1.0) - min(max(mom, f32(0)), f32(1))
+                    keep = (omega - (sub * n_steps).astype(f32) * bg).astype(f32)
+                self.h[:, col] = np.where(n_steps != 0, keep, omega)
+                if (n_steps != 0).any():
+                    update(self.c, e, (-n_steps)[None, :], float(f32(tp.step) * f32(self.dw_min_slow)),
+                           self.dw_min_slow, self.t_up, self.dev_slow, rng)
+                continue
             r = forward(self.a, e, self.t_io, rng, alpha=-1.0)
             update(self.c, e, r, float(t_lr), self.dw_min_slow, self.t_up, self.dev_slow, rng)
         self.slice_idx = (self.slice_idx + n) % self.x_size

@@ -12,6 +12,7 @@
 #include "aihwkit_b200.h"
 
 #include "dense_bit_line_maker.h"
+#include "rpu_buffered_transfer_device.h"
 #include "rpu_constantstep_device.h"
 #include "rpu_expstep_device.h"
 #include "rpu_linearstep_device.h"
@@ -175,7 +176,17 @@ int ref_tile_create(const ab200_tile_config *cfg, void **out) {
 
   std::unique_ptr<AbstractRPUDeviceMetaParameter<float>> dp;
   if (cfg->device_kind == AB200_DEVICE_TRANSFER) {
-    auto tp = std::make_unique<TransferRPUDeviceMetaParameter<float>>();
+    std::unique_ptr<TransferRPUDeviceMetaParameter<float>> tp;
+    if (cfg->transfer.buffered) {
+      auto bp = std::make_unique<BufferedTransferRPUDeviceMetaParameter<float>>();
+      bp->thres_scale = cfg->transfer.thres_scale;
+      bp->step = cfg->transfer.step;
+      bp->momentum = cfg->transfer.momentum;
+      bp->forget_buffer = cfg->transfer.forget_buffer != 0;
+      tp = std::move(bp);
+    } else {
+      tp = std::make_unique<TransferRPUDeviceMetaParameter<float>>();
+    }
     auto fast = makeSingle(cfg->device[0]);
     auto slow = makeSingle(cfg->device[1]);
     tp->appendVecPar(*fast);

@@ -112,3 +112,25 @@ def assert_moments_agree(a: np.ndarray, b: np.ndarray, z_max: float = 5.0, std_t
     assert float(z.max()) < z_max, f"max z-score {float(z.max()):.2f}"
     sa, sb = float(a.std(axis=0).mean()), float(b.std(axis=0).mean())
     assert sb > 0 and abs(sa / sb - 1.0) < std_tol, f"std ratio {sa / sb:.3f}"
+
+
+def buffered_transfer_device(seed: int = 21, transfer_every: float = 1.0, n_reads: int = 2,
+                             thres_scale: float = 1.0, momentum: float = 0.0,
+                             forget_buffer: bool = True, transfer_lr: float = 1.0):
+    """Tiki-Taka v2: BufferedTransferCompound of two noise-free SoftBoundsReference devices; the
+    gradient update of the fast tile uses deterministic pulses, the write of the slow tile the
+    device's default of exactly one pulse per whole step in the buffer."""
+    dp = D.BufferedTransferResistiveDeviceParameter()
+    for _ in range(2):
+        dp.append_parameter(device("sbr", False, dw_min=0.002, w_max=1.0, w_min=-1.0))
+    dp.construction_seed = seed
+    dp.gamma = 0.0
+    dp.transfer_every = transfer_every
+    dp.units_in_mbatch = False
+    dp.n_reads_per_transfer = n_reads
+    dp.transfer_lr = transfer_lr
+    dp.fast_lr = 1.0
+    dp.thres_scale, dp.momentum, dp.forget_buffer = thres_scale, momentum, forget_buffer
+    dp.transfer_forward.out_noise = 0.0
+    dp.transfer_forward.bound_management = D.BoundManagementType.Iterative
+    return dp

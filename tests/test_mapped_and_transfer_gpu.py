@@ -400,3 +400,43 @@ def test_mapped_backward_and_update(omega):
     W_got = arr.get_weights().numpy()
     assert np.abs(W_got - Wl).max() > 1e-4
     assert np.abs(W_got - W_new).max() <= 2e-6
+
+
+@pytest.mark.parametrize("forget,momentum,thres", [(True, 0.0, 2.0), (False, 0.3, 2.0), (True, 0.5, 0.5)])
+def test_buffered_transfer_deterministic(forget, momentum, thres):
+    """Tiki-Taka v2 on the GPU: fast tile, digital buffer and visible weights follow the oracle
+    (pinned to the compiled reference in tests/test_oracle_vs_reference.py) update by update,
+    with transfers falling inside the batches."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(13)
+    x_size, d_size, m = 12, 10, 4
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.buffered_transfer_device(thres_scale=thres, momentum=momentum, forget_buffer=forget,
+                                    transfer_lr=4.0)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    lr = 0.1
+    t.set_learning_rate(lr)
+    names, hp = t.get_hidden_parameter_names(), t.get_hidden_parameters().numpy()
+    assert names[-1] == "buffered_FP_weight_0"
+    fast = O.DeviceArrays.from_hidden(O.DEV_SOFT_BOUNDS_REFERENCE, names, hp, 0.0, False, "_0")
+    slow = O.DeviceArrays.from_hidden(O.DEV_SOFT_BOUNDS_REFERENCE, names, hp, 0.0, False, "_1")
+    orc = O.TransferOracle(np.zeros((d_size, x_size), np.float32), fast, slow, cfg.transfer,
+                           O.Up.from_c(cfg.update), 0.002, 0.002, x_size, d_size)
+    org = np.random.default_rng(0)
+    for _ in range(10):
+        x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        d = rng.normal(0, 0.5, (m, d_size)).astype(np.float32)
+        t.update(torch.from_numpy(x).cuda(), torch.from_numpy(d).cuda())
+        orc.update(x, d, lr, org)
+        hp = t.get_hidden_parameters().numpy()
+        assert np.abs(hp[names.index("hidden_weights_0")] - orc.a).max() <= 1e-6
+        assert np.abs(hp[names.index("buffered_FP_weight_0")] - orc.h).max() <= 1e-5
+        assert np.abs(t.get_weights().numpy() - orc.c).max() <= 1e-6
+    assert np.abs(orc.c).max() > 0
+    # the buffer travels with the hidden parameters
+    t2 = T.AnalogTile(cfg, cuda_device=0)
+    t2.set_weights(t.get_weights())
+    t2.set_hidden_parameters(t.get_hidden_parameters())
+    assert torch.equal(t2.get_hidden_parameters(), t.get_hidden_parameters())

@@ -290,3 +290,41 @@ def test_noise_and_bound_management_variants(nm, bm):
         io_plain = O.IO.from_c(cfg.forward_io)
         io_plain.bound_management = O.BM_NONE
         assert not np.array_equal(O.forward(W, X, io_plain), y)
+
+
+@pytest.mark.parametrize("forget,momentum", [(True, 0.0), (False, 0.3), (True, 0.5)])
+def test_buffered_transfer_sequence(forget, momentum):
+    """Tiki-Taka v2 (BufferedTransfer): fast tile, digital buffer and slow tile of the oracle
+    follow the compiled reference update by update."""
+    rng = np.random.default_rng(13)
+    x_size, d_size, m = 12, 10, 4
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.buffered_transfer_device(thres_scale=2.0, momentum=momentum, forget_buffer=forget,
+                                    transfer_lr=4.0)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = ref.RefTile(cfg)
+    lr = 0.1
+    t.set_learning_rate(lr)
+    names, hp = t.hidden_parameter_names(), t.get_hidden_parameters()
+    assert names[-1] == "buffered_FP_weight_0"
+    fast = O.DeviceArrays.from_hidden(O.DEV_SOFT_BOUNDS_REFERENCE, names, hp, 0.0, False, "_0")
+    slow = O.DeviceArrays.from_hidden(O.DEV_SOFT_BOUNDS_REFERENCE, names, hp, 0.0, False, "_1")
+    orc = O.TransferOracle(np.zeros((d_size, x_size), np.float32), fast, slow, cfg.transfer,
+                           O.Up.from_c(cfg.update), 0.002, 0.002, x_size, d_size)
+    moved = False
+    # the write uses stochastic trains with probability exactly 1 per line (one pulse per whole
+    # step): the generator is consulted but cannot change the outcome
+    org = np.random.default_rng(0)
+    for _ in range(10):
+        x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        d = rng.normal(0, 0.5, (m, d_size)).astype(np.float32)
+        t.update(x, d)
+        orc.update(x, d, lr, org)
+        hp = t.get_hidden_parameters()
+        assert np.abs(hp[names.index("hidden_weights_0")] - orc.a).max() <= 1e-7
+        assert np.abs(hp[names.index("buffered_FP_weight_0")] - orc.h).max() <= 1e-6
+        assert np.abs(t.get_weights() - orc.c).max() <= 1e-7
+        moved = moved or np.abs(orc.c).max() > 0
+    assert moved
+    if momentum > 0 or not forget:
+        assert np.abs(orc.h).max() > 0
