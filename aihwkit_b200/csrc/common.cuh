@@ -127,16 +127,19 @@ __device__ __forceinline__ void boxMuller(uint32_t a, uint32_t b, float &z0, flo
   z1 = r * __sinf(ang);
 }
 
-// Two standard normals from ONE 32-bit word: 20 bits for the radius (u1 in [2^-20, 1], radius up
-// to 5.26) and 12 bits for the angle. Used for the MVM output noise, where one Gaussian is drawn
-// per output element and in-split and the generator is the largest cost of the epilogue.
-__device__ __forceinline__ void boxMuller1(uint32_t a, float &z0, float &z1) {
-  float u1 = 2.0f - __uint_as_float(0x3f800000u | ((a >> 12) << 3));
-  float f2 = __uint_as_float(0x3f800000u | ((a & 0xFFFu) << 11)); // 1 + u2
-  float r2 = -1.3862943611198906f * lg2Ftz(u1); // -2 ln(u1)
+// Two standard normals from ONE 32-bit word, 16 bits each for radius and angle (the MVM output
+// noise draws one Gaussian per output element and in-split; the generator is the largest
+// arithmetic cost of the epilogue). A byte permute
+// drops a half-word into the low mantissa bits of 1.0f (f = 1 + X * 2^-23), and one FMA each maps
+// that to u1 = 1 - X * 2^-16 in [2^-16, 1] (radius up to 4.71) and to the angle 2 pi X * 2^-16.
+__device__ __forceinline__ void boxMuller16(uint32_t a, float &z0, float &z1) {
+  const float fr = __uint_as_float(__byte_perm(a, 0x3f800000u, 0x7632));
+  const float fa = __uint_as_float(__byte_perm(a, 0x3f800000u, 0x7610));
+  const float u1 = fmaf(fr, -128.0f, 129.0f);
+  const float ang = fmaf(fa, 804.24771931898703f, -804.24771931898703f); // 2 pi * 128 * (f - 1)
+  const float r2 = -1.3862943611198906f * lg2Ftz(u1); // -2 ln(u1)
   float r;
   asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(r2));
-  float ang = fmaf(6.283185307179586f, f2, -6.283185307179586f); // 2 pi u2
   z0 = r * cosFtz(ang);
   z1 = r * sinFtz(ang);
 }
@@ -150,8 +153,8 @@ gauss4(PhiloxKey key, uint64_t blk, uint32_t call, uint32_t tag, float z[4]) {
   const uint64_t pair = blk >> 1;
   philox4x32<7>((uint32_t)pair, (uint32_t)(pair >> 32), call, tag, key, r);
   const bool odd = (blk & 1) != 0;
-  boxMuller1(odd ? r[2] : r[0], z[0], z[1]);
-  boxMuller1(odd ? r[3] : r[1], z[2], z[3]);
+  boxMuller16(odd ? r[2] : r[0], z[0], z[1]);
+  boxMuller16(odd ? r[3] : r[1], z[2], z[3]);
 }
 
 // eight standard normals for the block pair `pair` (blocks 2 * pair and 2 * pair + 1 of gauss4)
@@ -159,10 +162,52 @@ __device__ __forceinline__ void
 gauss8(PhiloxKey key, uint64_t pair, uint32_t call, uint32_t tag, float z[8]) {
   uint32_t r[4];
   philox4x32<7>((uint32_t)pair, (uint32_t)(pair >> 32), call, tag, key, r);
-  boxMuller1(r[0], z[0], z[1]);
-  boxMuller1(r[1], z[2], z[3]);
-  boxMuller1(r[2], z[4], z[5]);
-  boxMuller1(r[3], z[6], z[7]);
+  boxMuller16(r[0], z[0], z[1]);
+  boxMuller16(r[1], z[2], z[3]);
+  boxMuller16(r[2], z[4], z[5]);
+  boxMuller16(r[3], z[6], z[7]);
+}
+
+// ---- generator of the tensor-core epilogue: the same Philox4x32-7 stream, lean in instructions ----
+// Round keys of one launch, computed once (the key is the same for every draw of a launch).
+struct Philox7Keys {
+  uint32_t a[7], b[7];
+};
+__device__ __forceinline__ Philox7Keys philox7Keys(PhiloxKey key) {
+  Philox7Keys k;
+#pragma unroll
+  for (int r = 0; r < 7; r++) {
+    k.a[r] = key.k0 + (uint32_t)r * 0x9E3779B9u;
+    k.b[r] = key.k1 + (uint32_t)r * 0xBB67AE85u;
+  }
+  return k;
+}
+__device__ __forceinline__ void
+philox7Keyed(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, const Philox7Keys &k, uint32_t out[4]) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
+#pragma unroll
+  for (int r = 0; r < 7; r++) {
+    const uint64_t p0 = (uint64_t)M0 * c0, p1 = (uint64_t)M1 * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k.a[r], n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k.b[r];
+    c0 = n0;
+    c1 = (uint32_t)p1;
+    c2 = n2;
+    c3 = (uint32_t)p0;
+  }
+  out[0] = c0;
+  out[1] = c1;
+  out[2] = c2;
+  out[3] = c3;
+}
+// eight standard normals of noise block pair `pair` (64-bit ordinal) of call `call`
+__device__ __forceinline__ void
+gauss8Keyed(const Philox7Keys &k, uint64_t pair, uint32_t call, uint32_t tag, float z[8]) {
+  uint32_t r[4];
+  philox7Keyed((uint32_t)pair, (uint32_t)(pair >> 32), call, tag, k, r);
+  boxMuller16(r[0], z[0], z[1]);
+  boxMuller16(r[1], z[2], z[3]);
+  boxMuller16(r[2], z[4], z[5]);
+  boxMuller16(r[3], z[6], z[7]);
 }
 
 // getDiscretizedValueSR<false> (src/rpucuda/utility_functions.h:204-210): rint(v / res) * res with

@@ -34,12 +34,18 @@ namespace ab200 {
 
 constexpr int TC_M = 128;      // rows per CTA
 constexpr int TC_N = 128;      // output columns per CTA (one chunk)
-constexpr int TC_K = 64;       // K elements per pipeline stage (128 B of bf16: one swizzle row)
-constexpr int TC_STAGES = 4;
+constexpr int TC_K = 64;       // K elements per chunk (128 B of bf16: one swizzle row)
+// K chunks (of TC_K) per pipeline stage: one barrier round trip of the producer and of the MMA
+// issuer moves this many chunks. Two chunks per stage measured 5 % faster than one at the same
+// bytes in flight; the ring depth itself (4, 6 or 7 chunks) made no difference.
+constexpr int TC_KCH = 2;
+constexpr int TC_STAGES = 2;
 constexpr int TC_STAGE_A = TC_M * TC_K * 2;
 constexpr int TC_STAGE_B = TC_N * TC_K * 2;
-constexpr int TC_STAGE_BYTES = TC_STAGE_A + 2 * TC_STAGE_B; // A, then B hi and B lo back to back
-constexpr int TC_ACC_COLS = 2 * TC_N;                       // hi and lo halves of one accumulator
+constexpr int TC_CHUNK_BYTES = TC_STAGE_A + 2 * TC_STAGE_B; // A, then B hi and B lo back to back
+constexpr int TC_STAGE_BYTES = TC_KCH * TC_CHUNK_BYTES;
+constexpr int TC_ACC_COLS = 2 * TC_N; // hi and lo halves of one accumulator
+constexpr int TC_ACC_STAGES = 512 / TC_ACC_COLS;
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 2048;
 constexpr int TC_EPI_WARPS = 16; // four per TMEM lane quarter, 32 columns each
 constexpr int TC_EPI_COLS = TC_N / (TC_EPI_WARPS / 4);
@@ -50,9 +56,11 @@ constexpr int TC_WARP_MMA = TC_EPI_WARPS + 1;
 constexpr int TC_THREADS = (TC_EPI_WARPS + 2) * 32;
 constexpr unsigned long long TC_WAIT_CYCLES = 4000000000ull; // about 2 s at 2 GHz
 // CTA-pair variant (cta_group::2): every CTA of a pair stages its own 128 rows of codes and ONE
-// half of the stacked weight tile (rank 0 the hi rows, rank 1 the lo rows), so a stage is 32 KB
-constexpr int TC2_STAGES = 6;
-constexpr int TC2_STAGE_BYTES = TC_STAGE_A + TC_STAGE_B;
+// half of the stacked weight tile (rank 0 the hi rows, rank 1 the lo rows), so a chunk is 32 KB
+constexpr int TC2_KCH = 2;
+constexpr int TC2_STAGES = 3;
+constexpr int TC2_CHUNK_BYTES = TC_STAGE_A + TC_STAGE_B;
+constexpr int TC2_STAGE_BYTES = TC2_KCH * TC2_CHUNK_BYTES;
 constexpr int TC2_SMEM_BYTES = TC2_STAGES * TC2_STAGE_BYTES + 2048;
 
 enum : int {
@@ -301,15 +309,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 const __grid_constant__ CUtensorMap tm_blo, const TcKernelParams p) {
   constexpr int STAGES = PAIR ? TC2_STAGES : TC_STAGES;
   constexpr int STAGE_BYTES = PAIR ? TC2_STAGE_BYTES : TC_STAGE_BYTES;
+  constexpr int KCH = PAIR ? TC2_KCH : TC_KCH;
+  constexpr int CHUNK_BYTES = PAIR ? TC2_CHUNK_BYTES : TC_CHUNK_BYTES;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = (uint64_t *)(smem + STAGES * STAGE_BYTES);
   uint64_t *full = bars;                    // [STAGES] operands landed in shared memory
   uint64_t *empty = bars + STAGES;          // [STAGES] MMAs have read the stage
-  uint64_t *tmem_full = bars + 2 * STAGES;  // [2]      accumulator complete
-  uint64_t *tmem_empty = tmem_full + 2;     // [2]      accumulator drained
-  uint32_t *tmem_slot = (uint32_t *)(tmem_empty + 2);
+  uint64_t *tmem_full = bars + 2 * STAGES;         // [TC_ACC_STAGES] accumulator complete
+  uint64_t *tmem_empty = tmem_full + TC_ACC_STAGES; // [TC_ACC_STAGES] accumulator drained
+  uint32_t *tmem_slot = (uint32_t *)(tmem_empty + TC_ACC_STAGES);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -339,7 +349,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       mbarInit(&full[s], 1);
       mbarInit(&empty[s], 1);
     }
-    for (int b = 0; b < 2; b++) {
+    for (int b = 0; b < TC_ACC_STAGES; b++) {
       mbarInit(&tmem_full[b], 1);
       // the issuer waits for the epilogue warps of every CTA it computes for
       mbarInit(&tmem_empty[b], PAIR ? 2 * TC_EPI_WARPS : TC_EPI_WARPS);
@@ -377,6 +387,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int it = 0;
+      int ps = 0;       // ring position and its phase parity
+      uint32_t pph = 0;
       bool ok = true;
       long long w_empty = 0, w_issue = 0;
       for (int w = worker; w < n_items && ok; w += n_workers) {
@@ -386,29 +398,46 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       for (int i = 0; i < p.I && ok; i++) {
         const int4 is = p.insplit[i];
         const int brow = i * p.nrows_pad + chunk_idx * TC_N;
-        for (int kc = 0; kc < is.y; kc++, it++) {
-          const int s = it % STAGES;
-          if (!TC_TIMED_WAIT(w_empty, mbarWait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag))) {
+        for (int kc0 = 0; kc0 < is.y; kc0 += KCH, it++) {
+          const int nch = min(KCH, is.y - kc0); // chunks in this stage
+          if (!TC_TIMED_WAIT(w_empty, mbarWait(&empty[ps], pph ^ 1u, abort_flag))) {
             atomicCAS(p.status, 0, TC_ERR_EMPTY);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          uint8_t *st = smem + s * STAGE_BYTES;
           const long long t_issue = timed ? clock64() : 0;
           if (PAIR) {
             // rank 0 announces the bytes of both CTAs on its barrier; both CTAs' copies count there
-            const uint32_t leader_bar = mapaShared(smemAddr(&full[s]), 0);
+            const uint32_t leader_bar = mapaShared(smemAddr(&full[ps]), 0);
             if (rank == 0) {
-              mbarExpectTx(&full[s], 2 * STAGE_BYTES);
+              mbarExpectTx(&full[ps], 2 * nch * CHUNK_BYTES);
             }
-            tmaLoad2dPair(st, &tm_a, leader_bar, is.x + kc * TC_K, r0);
-            tmaLoad2dPair(st + TC_STAGE_A, rank == 0 ? &tm_bhi : &tm_blo, leader_bar, kc * TC_K, brow);
+#pragma unroll
+            for (int c = 0; c < KCH; c++) {
+              if (c < nch) {
+                uint8_t *st = smem + ps * STAGE_BYTES + c * CHUNK_BYTES;
+                const int kc = kc0 + c;
+                tmaLoad2dPair(st, &tm_a, leader_bar, is.x + kc * TC_K, r0);
+                tmaLoad2dPair(st + TC_STAGE_A, rank == 0 ? &tm_bhi : &tm_blo, leader_bar, kc * TC_K, brow);
+              }
+            }
           } else {
-            mbarExpectTx(&full[s], STAGE_BYTES);
-            tmaLoad2d(st, &tm_a, &full[s], is.x + kc * TC_K, r0);
-            tmaLoad2d(st + TC_STAGE_A, &tm_bhi, &full[s], kc * TC_K, brow);
-            tmaLoad2d(st + TC_STAGE_A + TC_STAGE_B, &tm_blo, &full[s], kc * TC_K, brow);
+            mbarExpectTx(&full[ps], nch * CHUNK_BYTES);
+#pragma unroll
+            for (int c = 0; c < KCH; c++) {
+              if (c < nch) {
+                uint8_t *st = smem + ps * STAGE_BYTES + c * CHUNK_BYTES;
+                const int kc = kc0 + c;
+                tmaLoad2d(st, &tm_a, &full[ps], is.x + kc * TC_K, r0);
+                tmaLoad2d(st + TC_STAGE_A, &tm_bhi, &full[ps], kc * TC_K, brow);
+                tmaLoad2d(st + TC_STAGE_A + TC_STAGE_B, &tm_blo, &full[ps], kc * TC_K, brow);
+              }
+            }
+          }
+          if (++ps == STAGES) {
+            ps = 0;
+            pph ^= 1u;
           }
           if (timed) {
             w_issue += clock64() - t_issue;
@@ -433,15 +462,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   } else if (warp == TC_WARP_MMA) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0 && rank == 0) {
-      int it = 0, ai = 0; // pipeline stage counter, accumulator-buffer use counter
+      int ai = 0;       // accumulator-buffer use counter
+      int ms = 0;       // operand ring position and its phase parity
+      uint32_t mph = 0;
       bool ok = true;
       long long w_full = 0, w_tmem = 0, w_mma = 0;
+      const uint32_t smem0 = smemAddr(smem);
+      const uint64_t desc_hi = smemDesc(0); // every field but the start address
       const long long t_start = clock64();
       for (int w = worker; w < n_items && ok; w += n_workers) {
       for (int i = 0; i < p.I && ok; i++, ai++) {
         const int nk = p.insplit[i].y;
-        const int b = ai & 1;
-        if (!TC_TIMED_WAIT(w_tmem, mbarWait(&tmem_empty[b], ((ai >> 1) & 1) ^ 1, abort_flag))) {
+        const int b = ai % TC_ACC_STAGES;
+        if (!TC_TIMED_WAIT(w_tmem, mbarWait(&tmem_empty[b], ((ai / TC_ACC_STAGES) & 1) ^ 1, abort_flag))) {
           atomicCAS(p.status, 0, TC_ERR_TMEM_EMPTY);
           *abort_flag = 1;
           ok = false;
@@ -449,9 +482,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
         tcFenceAfter();
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * TC_ACC_COLS);
-        for (int kc = 0; kc < nk; kc++, it++) {
-          const int s = it % STAGES;
-          if (!TC_TIMED_WAIT(w_full, mbarWait(&full[s], (it / STAGES) & 1, abort_flag))) {
+        for (int kc0 = 0; kc0 < nk; kc0 += KCH) {
+          if (!TC_TIMED_WAIT(w_full, mbarWait(&full[ms], mph, abort_flag))) {
             atomicCAS(p.status, 0, TC_ERR_FULL);
             *abort_flag = 1;
             ok = false;
@@ -459,24 +491,36 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           }
           tcFenceAfter();
           const long long t_mma = timed ? clock64() : 0;
-          const uint32_t a0 = smemAddr(smem + s * STAGE_BYTES);
-          // single CTA: the B descriptor starts at the hi tile and its 256 rows run on into the
-          // lo tile. Pair: each CTA supplies 128 of the 256 B rows from the same offset.
-          const uint64_t da = smemDesc(a0), db = smemDesc(a0 + TC_STAGE_A);
+          // descriptors differ between stages and chunks only in the start-address field
+          // (16-byte units); +2 there = 32 bytes = 16 bf16 along K
+          const uint32_t a0 = (smem0 + (uint32_t)(ms * STAGE_BYTES)) >> 4;
 #pragma unroll
-          for (int k = 0; k < TC_K / 16; k++) {
-            // +2 in the 16-byte-unit address field = 32 bytes = 16 bf16 along K
-            if (PAIR) {
-              tcMmaPair(d_tmem, da + 2 * k, db + 2 * k, kIdescPair, (kc > 0 || k > 0) ? 1u : 0u);
-            } else {
-              tcMma(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kc > 0 || k > 0) ? 1u : 0u);
+          for (int c = 0; c < KCH; c++) {
+            if (c < nk - kc0) {
+              // single CTA: the B descriptor starts at the hi tile and its 256 rows run on into
+              // the lo tile. Pair: each CTA supplies 128 of the 256 B rows from the same offset.
+              const uint64_t da = desc_hi | (uint64_t)(a0 + (uint32_t)(c * CHUNK_BYTES >> 4));
+              const uint64_t db = da + (uint64_t)(TC_STAGE_A >> 4);
+#pragma unroll
+              for (int k = 0; k < TC_K / 16; k++) {
+                const uint32_t accum = (kc0 > 0 || c > 0 || k > 0) ? 1u : 0u;
+                if (PAIR) {
+                  tcMmaPair(d_tmem, da + 2 * k, db + 2 * k, kIdescPair, accum);
+                } else {
+                  tcMma(d_tmem, da + 2 * k, db + 2 * k, kIdesc, accum);
+                }
+              }
             }
           }
           // frees the stage (in both CTAs of a pair) when these MMAs have read it
           if (PAIR) {
-            tcCommitPair(&empty[s]);
+            tcCommitPair(&empty[ms]);
           } else {
-            tcCommit(&empty[s]);
+            tcCommit(&empty[ms]);
+          }
+          if (++ms == STAGES) {
+            ms = 0;
+            mph ^= 1u;
           }
           if (timed) {
             w_mma += clock64() - t_mma;
@@ -509,6 +553,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const float inv_res_out = adc ? 1.0f / io.res_out : 0.0f;
     const float kMagic = 12582912.0f; // 1.5 * 2^23: adding and subtracting rounds to nearest even
     const float in_codes = io.res_in * inv_res_out, bound_codes = io.out_bound * inv_res_out;
+    // uniform over the launch: every row draws output noise and converts through the ADC
+    const bool fast = adc && (io.out_noise > 0.0f ||
+                              (io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f));
+    const Philox7Keys rkeys = philox7Keys(p.key);
+    // eight accumulator columns of this thread's row: the product with hi + lo
+    auto loadAcc8 = [](uint32_t ta, float (&acc)[8]) {
+      uint32_t vh[8], vl[8];
+      tcLd8(ta, vh);
+      tcLd8(ta + (uint32_t)TC_N, vl);
+      tcWaitLd();
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        acc[j] = __fadd_rn(__uint_as_float(vh[j]), __uint_as_float(vl[j]));
+      }
+    };
     bool ok = true;
     int ai = 0; // accumulator-buffer use counter, in step with the MMA issuer
     long long w_tfull = 0;
@@ -520,6 +579,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const int row = rb * ROWS + rank * TC_M + q * 32 + lane;
     const bool row_ok = row < p.m;
     const uint32_t n4h = (uint32_t)((p.outn[ch.x] + 7) >> 3); // noise block pairs per row
+    // first noise block pair of this warp's columns (chunks and column groups start on
+    // multiples of 8 columns)
+    const uint64_t ctr0 = (uint64_t)((ch.y + cbase) >> 3);
     bool exceeded = false;
     float sum[TC_EPI_COLS]; // running sums over the in-splits
 #pragma unroll
@@ -537,7 +599,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       }
     }
     for (int i = 0; i < p.I; i++, ai++) {
-      const int b = ai & 1;
+      const int b = ai % TC_ACC_STAGES;
       const bool last = i + 1 == p.I;
       const float sc = sc_n, fac = fac_n;
       const float sigma = outputSigma(io, vn_n);
@@ -553,7 +615,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       const uint32_t tile_tag = tag + p.noise_id0 + (uint32_t)(i * p.O + ch.x);
       // the whole warp agrees on the outcome: what follows is warp-collective
       if (!__all_sync(0xffffffffu,
-                      TC_TIMED_WAIT(w_tfull, mbarWait(&tmem_full[b], (ai >> 1) & 1, abort_flag)))) {
+                      TC_TIMED_WAIT(w_tfull, mbarWait(&tmem_full[b], (ai / TC_ACC_STAGES) & 1, abort_flag)))) {
         atomicCAS(p.status, 0, TC_ERR_TMEM_FULL);
         *abort_flag = 1;
         ok = false;
@@ -563,68 +625,58 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       const uint32_t taddr =
           tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_ACC_COLS + cbase);
       const bool live = row_ok && sc != 0.0f;
-      const float sig_codes = sigma * inv_res_out, fac_codes = fac * io.res_out;
+      if (fast) {
+        // Noisy regime with an ADC (the inference setting): the Gaussian decides the ADC code, so
+        // the divisions of the exact chain become multiplications with the reciprocal step, all
+        // in units of the ADC step. Straight-line code: rows without input (or beyond the batch)
+        // run with factor 0, columns beyond the chunk are computed and never stored.
+        const float sig_codes = live ? sigma * inv_res_out : 0.0f;
+        const float fac_codes = live ? fac * io.res_out : 0.0f;
+        const uint64_t ctr = ctr0 + (uint64_t)row * n4h;
 #pragma unroll
-      for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 8) {
-        uint32_t vh[8], vl[8];
-        tcLd8(taddr + (uint32_t)c0, vh);          // codes x hi
-        tcLd8(taddr + (uint32_t)(TC_N + c0), vl); // codes x lo
-        tcWaitLd();
-        float acc[8];
+        for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 8) {
+          float acc[8];
+          loadAcc8(taddr + (uint32_t)c0, acc);
+          float z[8];
+          gauss8Keyed(rkeys, ctr + (uint64_t)(c0 >> 3), p.call, tile_tag, z);
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          acc[j] = __fadd_rn(__uint_as_float(vh[j]), __uint_as_float(vl[j]));
+          for (int j = 0; j < 8; j++) {
+            float r = fmaf(z[j], sig_codes, acc[j] * in_codes);
+            r = (r + kMagic) - kMagic; // round to nearest even
+            if (BM && cbase + c0 + j < ch.w) {
+              exceeded = exceeded || (r > bound_codes) || (io.bm_test_negative_bound && r < -bound_codes);
+            }
+            r = fminf(fmaxf(r, -bound_codes), bound_codes);
+            sum[c0 + j] = fmaf(r, fac_codes, sum[c0 + j]);
+          }
         }
-        if (live) {
-          if (sigma > 0.0f) {
-            // noisy regime: the Gaussian decides the ADC code, so the divisions of the exact
-            // chain are replaced by multiplications with the reciprocal step
+      } else {
+#pragma unroll
+        for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 8) {
+          float acc[8];
+          loadAcc8(taddr + (uint32_t)c0, acc);
+          if (live) {
             float z[8];
-            if (cbase + c0 < ch.w) {
-              gauss8(p.key, (uint64_t)row * n4h + (uint64_t)((ch.y + cbase + c0) >> 3), p.call,
-                     tile_tag, z);
+            if (sigma > 0.0f && cbase + c0 < ch.w) {
+              gauss8Keyed(rkeys, ctr0 + (uint64_t)row * n4h + (uint64_t)(c0 >> 3), p.call, tile_tag, z);
             }
 #pragma unroll
-            for (int g = 0; g < 2; g++) {
-              const int cl = cbase + c0 + 4 * g; // column inside this 128-column chunk
-              if (cl < ch.w) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                  if (adc) {
-                    // in units of the ADC step: round, clip and rescale with one multiply each
-                    float r = fmaf(z[4 * g + j], sig_codes, acc[4 * g + j] * in_codes);
-                    r = (r + kMagic) - kMagic;
-                    if (BM) {
-                      exceeded = exceeded || (r > bound_codes) ||
-                                 (io.bm_test_negative_bound && r < -bound_codes);
-                    }
-                    r = fminf(fmaxf(r, -bound_codes), bound_codes);
-                    sum[c0 + 4 * g + j] = fmaf(r, fac_codes, sum[c0 + 4 * g + j]);
-                  } else {
-                    float y = fmaf(acc[4 * g + j], io.res_in, sigma * z[4 * g + j]);
-                    if (BM) {
-                      exceeded = exceeded || (y > io.out_bound) ||
-                                 (io.bm_test_negative_bound && y < -io.out_bound);
-                    }
-                    y = fminf(fmaxf(y, -io.out_bound), io.out_bound);
-                    sum[c0 + 4 * g + j] = fmaf(y, fac, sum[c0 + 4 * g + j]);
+            for (int j = 0; j < 8; j++) {
+              if (cbase + c0 + j < ch.w) {
+                float y;
+                if (sigma > 0.0f) { // noise without an ADC
+                  y = fmaf(acc[j], io.res_in, sigma * z[j]);
+                  if (BM) {
+                    exceeded = exceeded || (y > io.out_bound) ||
+                               (io.bm_test_negative_bound && y < -io.out_bound);
                   }
+                  y = fminf(fmaxf(y, -io.out_bound), io.out_bound);
+                } else {
+                  // exact chain: the MMA summed integer codes times weights; one multiply by
+                  // the DAC step gives sum(v * w)
+                  y = finalizeOutput(io, __fmul_rn(acc[j], io.res_in), 0.0f, 0.0f, exceeded);
                 }
-              }
-            }
-          } else {
-#pragma unroll
-            for (int g = 0; g < 2; g++) {
-              const int cl = cbase + c0 + 4 * g;
-              if (cl < ch.w) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                  // the MMA summed integer codes times weights; one multiply by the DAC step
-                  // gives sum(v * w)
-                  float y = __fmul_rn(acc[4 * g + j], io.res_in);
-                  y = finalizeOutput(io, y, 0.0f, 0.0f, exceeded);
-                  sum[c0 + 4 * g + j] += y * fac;
-                }
+                sum[c0 + j] = fmaf(y, fac, sum[c0 + j]);
               }
             }
           }

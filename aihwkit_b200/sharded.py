@@ -121,27 +121,43 @@ class ShardedTileArray:
         self._sc_m = m
         dev_index = self.local.device.index
         slot_floats = self._sc_rows * self.out_size
-        handles, self._sc_mine = [], []
-        for _ in range(2):
-            ptr, h = C.c_void_p(), C.create_string_buffer(64)
-            _cabi.check(lib.ab200_peer_alloc(4 * slot_floats * self.world, dev_index, C.byref(ptr), h))
-            self._sc_mine.append(ptr.value)
-            handles.append(h.raw)
+        # a rank whose allocation or mapping fails tells the others through the same exchange, so
+        # that every rank raises (and none waits in a collective the failed one never joins)
+        handles, self._sc_mine, self._sc_peers, failure = [], [], [], None
+        try:
+            for _ in range(2):
+                ptr, h = C.c_void_p(), C.create_string_buffer(64)
+                _cabi.check(lib.ab200_peer_alloc(4 * slot_floats * self.world, dev_index, C.byref(ptr), h))
+                self._sc_mine.append(ptr.value)
+                handles.append(h.raw)
+        except RuntimeError as exc:
+            failure = f"rank {self.rank}: {exc}"
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, handles, group=self.group)
-        self._sc_peers, self._sc_tables = [], []
-        for b in range(2):
-            ptrs = []
-            for q in range(self.world):
-                if q == self.rank:
-                    base = self._sc_mine[b]
-                else:
-                    p = C.c_void_p()
-                    _cabi.check(lib.ab200_peer_open(gathered[q][b], dev_index, C.byref(p)))
-                    self._sc_peers.append(p.value)
-                    base = p.value
-                ptrs.append(base + 4 * slot_floats * self.rank)  # this rank's slot at owner q
-            self._sc_tables.append(torch.tensor(ptrs, dtype=torch.int64, device=self.local.device))
+        dist.all_gather_object(gathered, failure or handles, group=self.group)
+        failure = next((g for g in gathered if isinstance(g, str)), None)
+        self._sc_tables = []
+        if failure is None:
+            try:
+                for b in range(2):
+                    ptrs = []
+                    for q in range(self.world):
+                        if q == self.rank:
+                            base = self._sc_mine[b]
+                        else:
+                            p = C.c_void_p()
+                            _cabi.check(lib.ab200_peer_open(gathered[q][b], dev_index, C.byref(p)))
+                            self._sc_peers.append(p.value)
+                            base = p.value
+                        ptrs.append(base + 4 * slot_floats * self.rank)  # this rank's slot at owner q
+                    self._sc_tables.append(torch.tensor(ptrs, dtype=torch.int64, device=self.local.device))
+            except RuntimeError as exc:
+                failure = f"rank {self.rank}: {exc}"
+        opened = [None] * self.world
+        dist.all_gather_object(opened, failure, group=self.group)
+        failure = next((g for g in opened if g is not None), None)
+        if failure is not None:
+            self.disable_scatter()
+            raise RuntimeError(f"peer memory for the fused reduce-scatter is not available ({failure})")
         self._sc_flag = torch.zeros(1, device=self.local.device)
         self._sc_step = 0
         dist.barrier(group=self.group)
@@ -178,6 +194,7 @@ class ShardedTileArray:
 
         if getattr(self, "_sc_mine", None) is None:
             return
+        self._sc_tables = []
         torch.cuda.synchronize(self.local.device)
         dist.barrier(group=self.group)
         lib = _cabi.lib()

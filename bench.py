@@ -251,8 +251,14 @@ def run_ours(args):
     if scatter:
         # partial sums are pushed to the owners of the row blocks by the MVM kernel itself
         # (peer stores over NVLink), the result stays sharded by rows
-        arr.enable_scatter(m)
-        x_local_dev = x[:, c0:c1].contiguous()
+        try:
+            arr.enable_scatter(m)
+            x_local_dev = x[:, c0:c1].contiguous()
+        except RuntimeError as exc:  # raised on every rank alike: fall back to the NCCL reduce
+            if rank == 0:
+                print(f"bench: {exc}; using --collective reduce", file=sys.stderr)
+            scatter = False
+            args.collective = "reduce"
 
     def step():
         if scatter:
