@@ -92,7 +92,17 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append((time.time(), line.strip()))
 
-    def stop(self, window=None):
+    def wait_first(self, timeout=8.0):
+        """Block until nvidia-smi has printed its first sample (its start-up takes a second or
+        more on a multi-GPU host), so that a short run is not over before sampling begins."""
+        t0 = time.time()
+        while self.proc is not None and not self.lines and time.time() - t0 < timeout:
+            time.sleep(0.02)
+
+    def samples_in(self, window):
+        return sum(1 for l in self.lines if window[0] <= l[0] <= window[1] + 0.02)
+
+    def stop(self, window=None, scope_if_window="timed region"):
         """`window` = (t0, t1) wall-clock bounds of the timed region: samples inside it are used;
         if the region was shorter than the sampling period, all samples taken under load (from
         the warm-up on) are used instead and the result says so."""
@@ -103,14 +113,14 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, smax, reasons = [], [], set()
+        sm, smax, reasons, power, masks = [], [], set(), [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         lines = self.lines
         scope = "warm-up + timed region"
         if window is not None:
             inside = [l for l in lines if window[0] <= l[0] <= window[1] + 0.02]
             if inside:
-                lines, scope = inside, "timed region"
+                lines, scope = inside, scope_if_window
         for _, line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
@@ -120,12 +130,18 @@ class ClockSampler:
                 smax.append(float(parts[2]))
             except ValueError:
                 continue
+            try:
+                power.append(float(parts[3]))
+            except ValueError:
+                pass
+            masks.add(parts[4])
             for name, val in zip(names, parts[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return dict(sm_mhz=statistics.median(sm) if sm else None,
                     sm_max_mhz=max(smax) if smax else None, reasons=sorted(reasons),
-                    samples=len(sm), scope=scope)
+                    samples=len(sm), scope=scope, power_w_max=max(power) if power else None,
+                    reasons_mask=sorted(masks))
 
 
 # --------------------------------------------------------------------------------------------
@@ -275,6 +291,7 @@ def run_ours(args):
 
     sampler = ClockSampler(local_rank)
     sampler.start()
+    sampler.wait_first()
     for _ in range(args.warmup):
         step()
     barrier()
@@ -288,7 +305,21 @@ def run_ours(args):
     barrier()
     ms = ev0.elapsed_time(ev1)
     launches = lib.ab200_kernel_launch_count() - launches0
-    clocks = sampler.stop((t_wall0, time.time()))
+    window, scope = (t_wall0, time.time()), "timed region"
+    n_extra = max(args.steps, int(0.15 / max(ms * 1e-3 / args.steps, 1e-6)))
+    extra = torch.tensor([1 if sampler.samples_in(window) < 3 else 0, n_extra], device=dev)
+    if world > 1:
+        dist.all_reduce(extra, op=dist.ReduceOp.MAX)  # every rank takes the same decision
+    if int(extra[0]) != 0:
+        # the timed region held fewer than three samples: keep the same load running
+        # (untimed) for a few periods and report the clocks seen under it
+        n_extra = int(extra[1])
+        t_extra0 = time.time()
+        for _ in range(n_extra):
+            step()
+        barrier()
+        window, scope = (t_extra0, time.time()), "same load continued right after the timed region"
+    clocks = sampler.stop(window, scope)
 
     # kernel-only time of the local MVM work (no reduce), for the roofline
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
