@@ -89,6 +89,10 @@ enum : uint32_t {
   TAG_PULSE_D = 0x40000000u,
   TAG_DEVICE = 0x50000000u,    // + refill ordinal
   TAG_TRANSFER_READ = 0x60000000u,
+  TAG_FWD_IN = 0x70000000u,    // input noise / stochastic DAC rounding; + bound-management round
+  TAG_BWD_IN = 0x80000000u,
+  TAG_FWD_OUT_U = 0x90000000u, // stochastic ADC rounding; + bound-management round
+  TAG_BWD_OUT_U = 0xA0000000u,
 };
 
 #ifdef __CUDACC__

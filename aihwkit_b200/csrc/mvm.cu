@@ -44,13 +44,15 @@ template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKe
   }
   float sval = nmValue(io, st);
   float scale = inputScale(io, sval, /*reduction=*/1.0f, !p.backward);
+  const ElemRng g{p.key, p.call, (p.backward ? TAG_BWD_IN : TAG_FWD_IN) + p.noise_id};
   float vn = 0.0f;
   if (!io.is_perfect && io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f &&
       scale != 0.0f) {
     float acc = 0.0f;
     if (WARP_PER_SAMPLE) {
       for (int k = lane; k < p.in_size; k += 32) {
-        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale);
+        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale, g,
+                               (uint32_t)s, (uint32_t)k);
         acc = fmaf(v, v, acc);
       }
       for (int o = 16; o > 0; o >>= 1) {
@@ -58,7 +60,8 @@ template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKe
       }
     } else {
       for (int k = 0; k < p.in_size; k++) {
-        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale);
+        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale, g,
+                               (uint32_t)s, (uint32_t)k);
         acc = fmaf(v, v, acc);
       }
     }
@@ -89,6 +92,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   const int tx = tid & 15, ty = tid >> 4;
   const int row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
   const int K = p.in_size, N = p.out_size;
+  const ElemRng g{p.key, p.call, (p.backward ? TAG_BWD_IN : TAG_FWD_IN) + p.noise_id};
 
   if (tid < BM) {
     int r = row0 + tid;
@@ -123,7 +127,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
         float sc = s_scale[r];
         if (sc != 0.0f) {
           float xin = gk < p.in_real ? p.in[(long long)gr * p.in_ss + (long long)gk * p.in_fs] : 1.0f;
-          v = prepareInput(io, xin, sc);
+          v = prepareInput(io, xin, sc, g, (uint32_t)gr, (uint32_t)gk);
         }
       }
       As[kk][r] = v;
@@ -168,6 +172,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   // noise blocks of four columns, an even number per row (two blocks share one Philox call)
   const uint64_t n4 = (uint64_t)(((N + 7) >> 3) << 1);
   const uint32_t tag = (p.backward ? TAG_BWD_OUT : TAG_FWD_OUT) + p.noise_id;
+  const uint32_t tag_u = (p.backward ? TAG_BWD_OUT_U : TAG_FWD_OUT_U) + p.noise_id;
 #pragma unroll
   for (int i = 0; i < 4; i++) {
     int r = row0 + ty * 4 + i;
@@ -195,9 +200,13 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
       if (sigma > 0.0f) {
         gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag, z);
       }
+      float u[4] = {0.5f, 0.5f, 0.5f, 0.5f};
+      if (io.out_sto_round) {
+        uniform4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag_u, u);
+      }
 #pragma unroll
       for (int j = 0; j < 4; j++) {
-        y[j] = finalizeOutput(io, y[j], sigma, z[j], exceeded) * fac;
+        y[j] = finalizeOutput(io, y[j], sigma, z[j], exceeded, u[j]) * fac;
       }
     }
     if (exceeded && io.bm != AB200_BM_NONE) {
@@ -263,9 +272,11 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
         reduction = 1.0f;
       }
       scale = inputScale(io, sval, reduction, true);
+      const ElemRng g{p.key, p.call, TAG_FWD_IN + p.noise_id + (uint32_t)round * 0x10000u};
       float nacc = 0.0f;
       for (int k = threadIdx.x; k < K; k += blockDim.x) {
-        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale);
+        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale, g,
+                               (uint32_t)r, (uint32_t)k);
         v_sh[k] = v;
         nacc = fmaf(v, v, nacc);
       }
@@ -298,8 +309,13 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
           gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(n >> 2), p.call,
                  TAG_FWD_OUT + p.noise_id + (uint32_t)round * 0x10000u, z);
         }
+        float u[4] = {0.5f, 0.5f, 0.5f, 0.5f};
+        if (io.out_sto_round) {
+          uniform4(p.key, (uint64_t)r * n4 + (uint64_t)(n >> 2), p.call,
+                   TAG_FWD_OUT_U + p.noise_id + (uint32_t)round * 0x10000u, u);
+        }
         bool ex = false;
-        float y = finalizeOutput(io, acc, sigma, z[n & 3], ex);
+        float y = finalizeOutput(io, acc, sigma, z[n & 3], ex, u[n & 3]);
         fail |= ex ? 1 : 0;
         if (n < p.out_store) {
           p.out[(long long)r * p.out_ss + (long long)n * p.out_fs] = y;

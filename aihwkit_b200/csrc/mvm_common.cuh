@@ -81,7 +81,10 @@ inputScale(const IOEff &io, float sval, float reduction, bool forward) {
   }
   bool nm = io.nm != AB200_NM_NONE;
   if (nm && sval <= 0.0f) {
-    return 0.0f;
+    if (!(forward && io.inp_noise > 0.0f)) {
+      return 0.0f;
+    }
+    nm = false; // forward with input noise goes on without the input scaling (:924, :960-963)
   }
   float scale = 1.0f;
   if (nm) {
@@ -93,13 +96,59 @@ inputScale(const IOEff &io, float sval, float reduction, bool forward) {
   return scale;
 }
 
-// prepareInputImplStage4 (rpu_forward_backward_pass.cpp:571-604): scale, DAC, clip.
-__device__ __forceinline__ float prepareInput(const IOEff &io, float x, float scale) {
+// Random numbers of one input element: a pure function of (sample, feature, call, tag), so every
+// kernel that prepares the same element (norm of the inputs, product, bound-management re-run of
+// the same round) sees the same draw.
+struct ElemRng {
+  PhiloxKey key;
+  uint32_t call;
+  uint32_t tag; // TAG_FWD_IN / TAG_BWD_IN + tile id + round
+};
+__device__ __forceinline__ bool inputIsRandom(const IOEff &io) {
+  return !io.is_perfect && (io.inp_noise > 0.0f || (io.inp_sto_round && io.res_in > 0.0f));
+}
+
+// getDiscretizedValue with sto_round (src/rpucuda/utility_functions.h:186-193):
+// rint(v / res + (u - 0.5)) * res
+__device__ __forceinline__ float discretizeSto(float v, float res, float u) {
+  return res > 0.0f ? __fmul_rn(rintf(__fadd_rn(__fdiv_rn(v, res), __fadd_rn(u, -0.5f))), res) : v;
+}
+
+// prepareInputImplStage4 (rpu_forward_backward_pass.cpp:571-604): scale, DAC (rounding to nearest
+// or stochastic), clip, input noise (after the clip, as there), asymmetry of negative values.
+__device__ __forceinline__ float
+prepareInput(const IOEff &io, float x, float scale, const ElemRng &g, uint32_t sample, uint32_t k) {
   if (io.is_perfect) {
     return x;
   }
   float v = __fmul_rn(x, scale);
-  v = discretize(v, io.res_in);
+  if (inputIsRandom(io)) {
+    uint32_t r[4];
+    philox4x32<7>(k, sample, g.call, g.tag, g.key, r);
+    v = io.inp_sto_round ? discretizeSto(v, io.res_in, u01(r[0])) : discretize(v, io.res_in);
+    v = v > io.inp_bound ? io.inp_bound : v;
+    v = v < -io.inp_bound ? -io.inp_bound : v;
+    if (io.inp_noise > 0.0f) {
+      float z0, z1;
+      boxMuller(r[1], r[2], z0, z1);
+      v = __fadd_rn(v, __fmul_rn(io.inp_noise, z0));
+    }
+  } else {
+    v = discretize(v, io.res_in);
+    v = v > io.inp_bound ? io.inp_bound : v;
+    v = v < -io.inp_bound ? -io.inp_bound : v;
+  }
+  if (io.inp_asym != 1.0f) {
+    v = v < 0.0f ? __fmul_rn(v, io.inp_asym) : v;
+  }
+  return v;
+}
+// the plain DAC (no random part, no asymmetry): read-out of a transfer
+__device__ __forceinline__ float prepareInput(const IOEff &io, float x, float scale) {
+  if (io.is_perfect) {
+    return x;
+  }
+  float v = discretize(__fmul_rn(x, scale), io.res_in);
   v = v > io.inp_bound ? io.inp_bound : v;
   v = v < -io.inp_bound ? -io.inp_bound : v;
   return v;
@@ -117,13 +166,28 @@ __device__ __forceinline__ float outputSigma(const IOEff &io, float vnorm) {
   return s;
 }
 
-// finalizeOutputImplStage5 (rpu_forward_backward_pass.cpp:673-719): noise, ADC, clip / bound test.
+// four uniforms in (0,1) for the stochastic ADC rounding of noise block `blk` (four output columns)
+__device__ __forceinline__ void
+uniform4(PhiloxKey key, uint64_t blk, uint32_t call, uint32_t tag, float u[4]) {
+  uint32_t r[4];
+  philox4x32<7>((uint32_t)blk, (uint32_t)(blk >> 32), call, tag, key, r);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    u[j] = u01(r[j]);
+  }
+}
+
+// finalizeOutputImplStage5 (rpu_forward_backward_pass.cpp:673-719): asymmetry of negative values,
+// noise, ADC (rounding to nearest, or stochastic with the uniform `u`), clip / bound test.
 __device__ __forceinline__ float
-finalizeOutput(const IOEff &io, float y, float sigma, float z, bool &exceeded) {
+finalizeOutput(const IOEff &io, float y, float sigma, float z, bool &exceeded, float u = 0.5f) {
+  if (io.out_asym != 1.0f) {
+    y = y < 0.0f ? __fmul_rn(y, io.out_asym) : y;
+  }
   if (sigma > 0.0f) {
     y = __fadd_rn(y, __fmul_rn(sigma, z));
   }
-  y = discretize(y, io.res_out);
+  y = io.out_sto_round ? discretizeSto(y, io.res_out, u) : discretize(y, io.res_out);
   if (y > io.out_bound) {
     y = io.out_bound;
     exceeded = true;

@@ -945,6 +945,12 @@ bool TcEngine::ioSupported(const IOEff &io) {
   if (io.is_perfect || !(io.res_in > 0.0f) || !(io.inp_bound < 1e30f)) {
     return false;
   }
+  // input noise takes the DAC output off the integer grid; asymmetries and stochastic rounding
+  // are left to the CUDA-core kernels too
+  if (io.inp_noise > 0.0f || io.inp_asym != 1.0f || io.out_asym != 1.0f || io.inp_sto_round ||
+      io.out_sto_round) {
+    return false;
+  }
   // the DAC kernel of this path knows the common noise-management types only, and the re-run
   // kernel of IterativeWorstCase changes the noise-management value per row
   if ((io.nm != AB200_NM_NONE && io.nm != AB200_NM_ABS_MAX && io.nm != AB200_NM_CONSTANT) ||

@@ -26,7 +26,7 @@ static float checkRes(float res) {
   return r > 1.0f ? 1.0f / r : r;
 }
 
-IOEff resolveIO(const ab200_io_params &io, bool backward) {
+IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only) {
   // IOMetaParameter::initializeForForward / Backward (rpu_pulsed_meta_parameter.cpp:40-128)
   IOEff e;
   e.is_perfect = io.is_perfect;
@@ -45,6 +45,11 @@ IOEff resolveIO(const ab200_io_params &io, bool backward) {
   e.out_scale = io.out_scale;
   e.w_noise = io.w_noise;
   e.nm_assumed_wmax = io.nm_assumed_wmax;
+  e.inp_noise = io.inp_noise;
+  e.inp_asym = 1.0f - io.inp_asymmetry;
+  e.out_asym = 1.0f - io.out_asymmetry;
+  e.inp_sto_round = io.inp_sto_round;
+  e.out_sto_round = io.out_sto_round;
   if (!io.is_perfect) {
     if (io.noise_management != AB200_NM_NONE && io.inp_bound != 1.0f) {
       AB200_FATAL((backward ? "Backward noise managment expects input bound==1"
@@ -59,9 +64,10 @@ IOEff resolveIO(const ab200_io_params &io, bool backward) {
     if (io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) {
       AB200_FATAL("PCMRead weight noise is not implemented");
     }
-    if (io.inp_noise != 0.0f || io.inp_sto_round || io.out_sto_round || io.inp_asymmetry != 0.0f ||
-        io.out_asymmetry != 0.0f) {
-      AB200_FATAL("inp_noise / stochastic rounding / asymmetry are not implemented");
+    if (plain_only && (io.inp_noise != 0.0f || io.inp_sto_round || io.out_sto_round ||
+                       io.inp_asymmetry != 0.0f || io.out_asymmetry != 0.0f)) {
+      AB200_FATAL("inp_noise / stochastic rounding / asymmetry are not implemented for the "
+                  "read-out of a transfer");
     }
   }
   return e;
@@ -293,7 +299,7 @@ Tile::Tile(const ab200_tile_config &cfg, int cuda_device) : cfg_(cfg) {
     ab200_io_params tio = t.transfer_io;
     tio.noise_management = AB200_NM_NONE;
     tio.bound_management = AB200_BM_NONE;
-    t_io_ = resolveIO(tio, false);
+    t_io_ = resolveIO(tio, false, /*plain_only=*/true);
     t_up_ = resolveUp(t.transfer_up);
   }
   setSeed(cfg.seed);

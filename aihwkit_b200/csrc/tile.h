@@ -34,9 +34,18 @@ struct IOEff {
   float w_noise;
   float nm_thres;
   float nm_assumed_wmax;
+  // Gaussian added to the DAC output, factors applied to negative DAC outputs / negative values
+  // in front of the ADC (1 - asymmetry), stochastic rounding of DAC / ADC
+  float inp_noise;
+  float inp_asym;
+  float out_asym;
+  int inp_sto_round;
+  int out_sto_round;
 };
 
-IOEff resolveIO(const ab200_io_params &io, bool backward);
+// `plain_only`: reject the settings only the forward / backward kernels implement (input noise,
+// asymmetries, stochastic rounding), as for the read-out of a transfer.
+IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only = false);
 
 // PulsedUpdateMetaParameter after initialize() (rpu_pulsed_meta_parameter.cpp:134-151).
 struct UpEff {

@@ -77,7 +77,6 @@ class AnalogTileInputOutputParameter:
     """IOMetaParameter (rpu_base_devices.cpp:485-519)."""
 
     _unsupported = {
-        "inp_noise": 0.0,
         "out_noise_std": 0.0,
         "ir_drop": 0.0,
         "out_nonlinearity": 0.0,

@@ -400,7 +400,7 @@ def run_ours(args):
                 # dram__bytes_read.sum + dram__bytes_write.sum of one full-batch launch of the
                 # MVM kernel on one GPU, from the ncu capture summarised under profiles/
                 # (283.5 MB + 121.6 MB); algorithmic bytes of the launch are 335 MB
-                "traffic": 405.1e6 if world == 1 else None,
+                "traffic": 411.0e6 if world == 1 else None,
                 "peak_source": f"bf16_tflops (burst), {peaks['source']}",
                 "kernel": "IO-managed MVM of this rank's tiles",
                 "kernel_ms_per_step": kernel_ms, "tiles_per_launch_group": n_local,

@@ -68,6 +68,11 @@ class IO:
     w_noise: float = 0.0
     nm_thres: float = 0.0
     nm_assumed_wmax: float = 0.6
+    inp_noise: float = 0.0
+    inp_asymmetry: float = 0.0
+    out_asymmetry: float = 0.0
+    inp_sto_round: bool = False
+    out_sto_round: bool = False
     res_in: np.float32 = field(default=f32(0), init=False)
     res_out: np.float32 = field(default=f32(0), init=False)
 
@@ -116,6 +121,11 @@ class IO:
             w_noise=float(c.w_noise),
             nm_thres=float(c.nm_thres),
             nm_assumed_wmax=float(c.nm_assumed_wmax),
+            inp_noise=float(c.inp_noise),
+            inp_asymmetry=float(c.inp_asymmetry),
+            out_asymmetry=float(c.out_asymmetry),
+            inp_sto_round=bool(c.inp_sto_round),
+            out_sto_round=bool(c.out_sto_round),
         )
         return io.finalize(backward)
 
@@ -125,6 +135,16 @@ def quantize(v: np.ndarray, res: np.float32) -> np.ndarray:
     if res <= 0:
         return v
     return (np.rint((v / f32(res)).astype(f32)).astype(f32) * f32(res)).astype(f32)
+
+
+def quantize_sto(v: np.ndarray, res: np.float32, rng: np.random.Generator) -> np.ndarray:
+    """getDiscretizedValue with sto_round (utility_functions.h:186-193):
+    rint(v / res + (u - 0.5)) * res with u uniform in [0, 1)."""
+    if res <= 0:
+        return v
+    u = rng.random(v.shape).astype(f32)
+    q = ((v / f32(res)).astype(f32) + (u - f32(0.5)).astype(f32)).astype(f32)
+    return (np.rint(q).astype(f32) * f32(res)).astype(f32)
 
 
 def _nm_scale(v: np.ndarray, io: IO, nm_type: Optional[int] = None) -> np.ndarray:
@@ -171,20 +191,26 @@ def _analog_mv(
     """
     # prepareInput (:571-604)
     v = np.where(scaling[:, None], (v_in * scale[:, None]).astype(f32), v_in).astype(f32)
-    v = quantize(v, io.res_in)
+    v = quantize_sto(v, io.res_in, rng) if (io.inp_sto_round and rng is not None) else quantize(v, io.res_in)
     bound = f32(io.inp_bound) if io.inp_bound > 0 else f32(np.inf)
     v = np.clip(v, -bound, bound).astype(f32)
+    if io.inp_noise > 0 and rng is not None:  # after the clip, as in the reference
+        v = (v + f32(io.inp_noise) * rng.standard_normal(v.shape).astype(f32)).astype(f32)
+    if io.inp_asymmetry != 0:
+        v = np.where(v < 0, (v * f32(f32(1.0) - f32(io.inp_asymmetry))).astype(f32), v).astype(f32)
     # gemv
     y = (v @ w_op.T).astype(f32)
     # applyOutputWeightNoise (:326-352)
     if io.w_noise_type == WN_ADDITIVE_CONSTANT and io.w_noise > 0 and rng is not None:
         nrm = np.sqrt((v.astype(np.float64) ** 2).sum(axis=1)).astype(f32)
         y = (y + (f32(io.w_noise) * nrm)[:, None] * rng.standard_normal(y.shape).astype(f32)).astype(f32)
-    # finalizeOutput (:673-719)
+    # finalizeOutput (:673-719): asymmetry, noise, ADC, clip
+    if io.out_asymmetry != 0:
+        y = np.where(y < 0, (y * f32(f32(1.0) - f32(io.out_asymmetry))).astype(f32), y).astype(f32)
     if io.out_noise > 0 and rng is not None:
         y = (y + f32(io.out_noise) * rng.standard_normal(y.shape).astype(f32)).astype(f32)
     pre_adc = y.copy()
-    y = quantize(y, io.res_out)
+    y = quantize_sto(y, io.res_out, rng) if (io.out_sto_round and rng is not None) else quantize(y, io.res_out)
     ob = f32(io.out_bound) if io.out_bound > 0 else f32(np.inf)
     passed = np.ones(y.shape[0], bool)
     if bm:
@@ -215,7 +241,8 @@ def forward(
     out = np.zeros((m, w.shape[0]), f32)
     pre = np.zeros((m, w.shape[0]), f32)
     reductions = np.ones(m, f32)
-    zero_rows = nm & (s <= 0)
+    # all-zero rows give zero, unless input noise is on (:924-933)
+    zero_rows = nm & (s <= 0) & (not (io.inp_noise > 0 and rng is not None))
     todo = ~zero_rows
     red = f32(0.5)
     out_scale = f32(io.out_scale) * f32(alpha)
@@ -236,7 +263,8 @@ def forward(
         scaling = np.zeros(len(idx), bool)
         if nm:
             pos = s[idx] > 0
-            scale = np.where(pos, (f32(1.0) / s[idx]).astype(f32), scale).astype(f32)
+            safe = np.where(pos, s[idx], f32(1.0)).astype(f32)
+            scale = np.where(pos, (f32(1.0) / safe).astype(f32), scale).astype(f32)
             scaling |= pos
         if bm:
             scale = (scale / red).astype(f32)

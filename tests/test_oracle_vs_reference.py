@@ -328,3 +328,57 @@ def test_buffered_transfer_sequence(forget, momentum):
     assert moved
     if momentum > 0 or not forget:
         assert np.abs(orc.h).max() > 0
+
+
+def test_io_asymmetries_exact():
+    """inp_asymmetry / out_asymmetry (negative DAC outputs and negative pre-ADC values scaled by
+    1 - asymmetry): deterministic, the oracle equals the compiled reference, forward and backward."""
+    rng = np.random.default_rng(17)
+    x_size, d_size, m = 70, 33, 20
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=4.0)
+    for io in (p.forward_io, p.backward_io):
+        io.inp_asymmetry, io.out_asymmetry = 0.1, 0.2
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=3)
+    t = ref.RefTile(cfg)
+    t.set_weights(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32))
+    W = t.get_weights()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+    y = O.forward(W, X, O.IO.from_c(cfg.forward_io))
+    assert np.array_equal(t.forward(X), y)
+    g = O.backward(W, Dm, O.IO.from_c(cfg.backward_io, backward=True))
+    assert np.array_equal(t.backward(Dm), g)
+    plain = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=4.0)
+    y0 = O.forward(W, X, O.IO.from_c(plain._config(x_size, d_size, H.device("cs", False), seed=3).forward_io))
+    assert np.abs(y - y0).max() > 1e-2  # the asymmetries did something
+
+
+@pytest.mark.parametrize("what", ["inp_noise", "inp_sto_round", "out_sto_round"])
+def test_io_random_input_stage_moments(what):
+    """Input noise and stochastic DAC / ADC rounding: the oracle's samples and the compiled
+    reference's samples agree in their element-wise means and standard deviations."""
+    rng = np.random.default_rng(19)
+    x_size, d_size, m, reps = 40, 12, 6, 300
+    p = H.training_params(noise=False, pulse_det=True)
+    if what == "inp_noise":
+        p.forward_io.inp_noise = 0.1
+    else:
+        p.forward_io.inp_res, p.forward_io.out_res = 1 / 14.0, 1 / 30.0  # coarse: rounding matters
+        setattr(p.forward_io, what, True)
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=3)
+    t = ref.RefTile(cfg)
+    t.set_seed(5)
+    t.set_weights(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32))
+    W = t.get_weights()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    X[2] = 0.0  # zero row: zero output without input noise, pure noise with it
+    io = O.IO.from_c(cfg.forward_io)
+    org = np.random.default_rng(1)
+    ys_ref = np.stack([t.forward(X) for _ in range(reps)])
+    ys = np.stack([O.forward(W, X, io, org) for _ in range(reps)])
+    assert ys.std(axis=0).max() > 0  # something random happened
+    if what == "inp_noise":
+        assert ys_ref[:, 2].std() > 0 and ys[:, 2].std() > 0
+    else:
+        assert (ys_ref[:, 2] == 0).all() and (ys[:, 2] == 0).all()
+    H.assert_moments_agree(ys, ys_ref)

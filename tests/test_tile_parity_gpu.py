@@ -361,3 +361,59 @@ def test_noise_and_bound_management_variants(nm, bm, m):
     assert frac <= 3e-3 and worst <= 1.001, (frac, worst)
     if nm == "Max":
         assert (y[3] == 0).all()
+
+
+def test_io_asymmetries():
+    """inp_asymmetry / out_asymmetry on the GPU against the oracle, forward and backward, a batch
+    small enough for the per-sample kernels and one large enough for the tiled ones."""
+    rng = np.random.default_rng(17)
+    x_size, d_size = 70, 33
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=4.0)
+    for io in (p.forward_io, p.backward_io):
+        io.inp_asymmetry, io.out_asymmetry = 0.1, 0.2
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    fio, bio = O.IO.from_c(cfg.forward_io), O.IO.from_c(cfg.backward_io, backward=True)
+    for m in (20, 300):
+        X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+        y_or, _, scale, _ = O.forward(W, X, fio, return_pre_adc=True)
+        y = t.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+        frac, worst = H.lsb_report(y, y_or, (fio.res_out / scale)[:, None])
+        assert frac <= 3e-3 and worst <= 1.001, (frac, worst)
+        g_or = O.backward(W, Dm, bio)
+        g = t.backward(torch.from_numpy(Dm).cuda()).cpu().numpy()
+        frac, worst = H.lsb_report(g, g_or, (bio.res_out * np.abs(Dm).max(axis=1))[:, None])
+        assert frac <= 3e-3 and worst <= 1.001, (frac, worst)
+
+
+@pytest.mark.parametrize("what", ["inp_noise", "inp_sto_round", "out_sto_round"])
+def test_io_random_input_stage_moments(what):
+    """Input noise and stochastic DAC / ADC rounding: the GPU's samples and the oracle's (pinned to
+    the compiled reference in tests/test_oracle_vs_reference.py) agree in their element-wise means
+    and standard deviations; a zero row stays zero unless input noise is on."""
+    rng = np.random.default_rng(19)
+    x_size, d_size, m, reps = 40, 12, 6, 300
+    p = H.training_params(noise=False, pulse_det=True)
+    if what == "inp_noise":
+        p.forward_io.inp_noise = 0.1
+    else:
+        p.forward_io.inp_res, p.forward_io.out_res = 1 / 14.0, 1 / 30.0
+        setattr(p.forward_io, what, True)
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    X[2] = 0.0
+    io = O.IO.from_c(cfg.forward_io)
+    org = np.random.default_rng(1)
+    xg = torch.from_numpy(X).cuda()
+    ys = np.stack([t.forward(xg).cpu().numpy() for _ in range(reps)])
+    ys_or = np.stack([O.forward(W, X, io, org) for _ in range(reps)])
+    assert ys.std(axis=0).max() > 0
+    if what == "inp_noise":
+        assert ys[:, 2].std() > 0
+    else:
+        assert (ys[:, 2] == 0).all()
+    H.assert_moments_agree(ys, ys_or)
