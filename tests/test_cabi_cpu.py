@@ -115,8 +115,8 @@ def test_compute_without_device_fails_loudly():
 
 def test_unsupported_settings_raise():
     p = D.AnalogTileParameter()
-    p.forward_io.inp_noise = 0.1
-    with pytest.raises(RuntimeError):
+    p.forward_io.ir_drop = 0.1
+    with pytest.raises(RuntimeError, match="ir_drop"):
         p._config(4, 4, D.ConstantStepResistiveDeviceParameter())
     p = D.AnalogTileParameter()
     p.update.pulse_type = D.PulseType.Stochastic
