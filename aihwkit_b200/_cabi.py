@@ -106,6 +106,10 @@ class DeviceParams(C.Structure):
         ("es_b", C.c_float),
         ("dw_min_std_add", C.c_float),
         ("dw_min_std_slope", C.c_float),
+        ("ps_gamma", C.c_float),
+        ("ps_gamma_dtod", C.c_float),
+        ("ps_gamma_up_down", C.c_float),
+        ("ps_gamma_up_down_dtod", C.c_float),
     ]
 
 

@@ -128,6 +128,10 @@ void ab200_default_device_params(ab200_device_params *dp, int32_t kind) {
   dp->es_gamma_down = 12.78785f;
   dp->es_a = 0.244f;
   dp->es_b = 0.2425f;
+  dp->ps_gamma = 1.0f; /* rpu_powstep_device.h:22-25 */
+  dp->ps_gamma_dtod = 0.1f;
+  dp->ps_gamma_up_down = 0.0f;
+  dp->ps_gamma_up_down_dtod = 0.0f;
   if (kind == AB200_DEVICE_SOFT_BOUNDS) {
     dp->ls_decrease_up = dp->ls_decrease_down = 1.0f;
     dp->ls_decrease_up_dtod = dp->ls_decrease_down_dtod = 0.0f;

@@ -124,6 +124,9 @@ std::vector<std::string> deviceNames(int kind) {
     n.push_back("slope_down");
   } else if (kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE) {
     n.push_back("reference");
+  } else if (kind == AB200_DEVICE_POW_STEP) {
+    n.push_back("gamma_up");
+    n.push_back("gamma_down");
   }
   return n;
 }
@@ -144,6 +147,10 @@ void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_
     const float dw_down = scale_down * fmaxf(1.0f - par.es_A_down * expf(par.es_gamma_down * (-z)), 0.0f);
     const float g = fmaxf((dw_down + dw_down) / 2.0f, 0.0f);
     ds.dw_min = g > 0.0f ? g : par.dw_min;
+  }
+  if (kind == AB200_DEVICE_POW_STEP) {
+    // PowStepRPUDeviceMetaParameter::calcWeightGranularity (rpu_powstep_device.h:33)
+    ds.dw_min = par.dw_min * powf(0.5f, par.ps_gamma);
   }
   ds.mult_noise = kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE ? par.mult_noise : par.ls_mult_noise;
   ds.names = deviceNames(kind);
@@ -221,6 +228,24 @@ void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_
         slope_down[k] = ref_down != 0.0f ? -dd * sdown[k] / ref_down : 0.0f;
       }
     }
+  } else if (kind == AB200_DEVICE_POW_STEP) {
+    // PowStepRPUDevice::populate (rpu_powstep_device.cpp:21-51)
+    float *gamma_up = &ds.host[8 * size], *gamma_down = &ds.host[9 * size];
+    const float g_up_bias = par.ps_gamma_up_down > 0.0f ? 0.0f : par.ps_gamma_up_down;
+    const float g_down_bias = par.ps_gamma_up_down > 0.0f ? -par.ps_gamma_up_down : 0.0f;
+    for (int i = 0; i < d_size; ++i) {
+      for (int j = 0; j < x_size; ++j) {
+        const size_t k = (size_t)i * x_size + j;
+        const float gain = 1.0f + par.ps_gamma_dtod * rng.gauss();
+        const float r = par.ps_gamma_up_down_dtod * rng.gauss();
+        gamma_up[k] = (g_up_bias + gain + r) * par.ps_gamma;
+        gamma_down[k] = (g_down_bias + gain - r) * par.ps_gamma;
+        if (par.enforce_consistency) {
+          gamma_up[k] = fabsf(gamma_up[k]);
+          gamma_down[k] = fabsf(gamma_down[k]);
+        }
+      }
+    }
   } else if (kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE) {
     float *reference = &ds.host[8 * size], *reset_bias = &ds.host[6 * size];
     for (int i = 0; i < d_size; ++i) {
@@ -261,7 +286,7 @@ void Tile::populateHost() {
     for (int k = 0; k < 2; k++) {
       int kind = cfg_.device[k].kind;
       if ((kind < AB200_DEVICE_CONSTANT_STEP || kind > AB200_DEVICE_SOFT_BOUNDS_REFERENCE) &&
-          kind != AB200_DEVICE_EXP_STEP) {
+          kind != AB200_DEVICE_EXP_STEP && kind != AB200_DEVICE_POW_STEP) {
         AB200_FATAL("Transfer: unit cell device kind not implemented");
       }
       populateDevice(cfg_.device[k], kind, x_size_, d_size_, rng, dev_[k]);
@@ -281,7 +306,7 @@ Tile::Tile(const ab200_tile_config &cfg, int cuda_device) : cfg_(cfg) {
   f_io_ = resolveIO(cfg.forward_io, false);
   b_io_ = resolveIO(cfg.backward_io, true);
   up_ = resolveUp(cfg.update);
-  if (cfg.device_kind < AB200_DEVICE_IDEAL || cfg.device_kind > AB200_DEVICE_EXP_STEP) {
+  if (cfg.device_kind < AB200_DEVICE_IDEAL || cfg.device_kind > AB200_DEVICE_POW_STEP) {
     AB200_FATAL("device kind not implemented");
   }
   if (cfg.device_kind == AB200_DEVICE_TRANSFER) {
@@ -450,7 +475,8 @@ void Tile::uploadDeviceStore(DeviceStore &ds) {
   const float *wmax = &ds.host[0 * size], *wmin = &ds.host[1 * size], *sup = &ds.host[2 * size],
               *sdown = &ds.host[3 * size];
   const float *e0 = nullptr, *e1 = nullptr;
-  if (ds.kind == AB200_DEVICE_LINEAR_STEP || ds.kind == AB200_DEVICE_SOFT_BOUNDS) {
+  if (ds.kind == AB200_DEVICE_LINEAR_STEP || ds.kind == AB200_DEVICE_SOFT_BOUNDS ||
+      ds.kind == AB200_DEVICE_POW_STEP) {
     e0 = &ds.host[8 * size];
     e1 = &ds.host[9 * size];
   } else if (ds.kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE) {

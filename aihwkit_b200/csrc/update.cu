@@ -217,6 +217,23 @@ __device__ __forceinline__ float pulseOnce(float w, bool down, const float4 &q, 
     w = fminf(w, q.z);
     w = fmaxf(w, q.w);
     return w;
+  } else if (KIND == AB200_DEVICE_POW_STEP) {
+    // PowStepRPUDevice update_once (rpu_powstep_device.cpp:91-121): the step shrinks with a power
+    // of the distance to the bound, e = {gamma_up, gamma_down}
+    const float range = __fsub_rn(q.z, q.w);
+    if (range == 0.0f) {
+      return w;
+    }
+    if (down) {
+      const float f = powf(__fdiv_rn(__fsub_rn(w, q.w), range), e.y);
+      w = __fsub_rn(w, __fmul_rn(__fmul_rn(q.y, f), __fadd_rn(1.0f, xi)));
+    } else {
+      const float f = powf(__fdiv_rn(__fsub_rn(q.z, w), range), e.x);
+      w = __fadd_rn(w, __fmul_rn(__fmul_rn(q.x, f), __fadd_rn(1.0f, xi)));
+    }
+    w = fmaxf(w, q.w);
+    w = fminf(w, q.z);
+    return w;
   } else if (KIND == AB200_DEVICE_CONSTANT_STEP) {
     float dw = __fmul_rn(__fadd_rn(1.0f, xi), down ? q.y : q.x);
     w = down ? __fsub_rn(w, dw) : __fadd_rn(w, dw);
@@ -595,6 +612,9 @@ void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream) {
     break;
   case AB200_DEVICE_SOFT_BOUNDS_REFERENCE:
     AB200_UPD(AB200_DEVICE_SOFT_BOUNDS_REFERENCE);
+    break;
+  case AB200_DEVICE_POW_STEP:
+    AB200_UPD(AB200_DEVICE_POW_STEP);
     break;
   case AB200_DEVICE_EXP_STEP:
     AB200_UPD(AB200_DEVICE_EXP_STEP);

@@ -8,8 +8,9 @@ reference's meta-parameter structs (``src/rpucuda/rpu_pulsed_meta_parameter.h:18
 ``rpu_transfer_device.h:52-75``).  ``AnalogTileParameter.create_array`` is the factory the
 reference exposes at ``rpu_base_devices.cpp:453-467``.
 
-Devices outside the path (ExpStep, PowStep, MixedPrec, OneSided, Buffered/Chopped/Dynamic
-transfer, ...) are not provided; asking for one raises ``RuntimeError``.
+Also provided: ExpStep, PowStep and the buffered transfer (Tiki-Taka v2).  Other devices
+(PiecewiseStep, MixedPrec, OneSided, Chopped / Dynamic transfer, ...) are not; there is no class
+for them here.
 """
 
 from __future__ import annotations
@@ -71,6 +72,7 @@ DEVICE_SOFT_BOUNDS = 3
 DEVICE_SOFT_BOUNDS_REFERENCE = 4
 DEVICE_TRANSFER = 5
 DEVICE_EXP_STEP = 6
+DEVICE_POW_STEP = 7
 
 
 class AnalogTileInputOutputParameter:
@@ -287,6 +289,35 @@ class ConstantStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):
     """rpu_base_devices.cpp:583-600."""
 
     _kind = DEVICE_CONSTANT_STEP
+
+
+class PowStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):
+    """rpu_base_devices.cpp:806-813 (PowStepRPUDeviceMetaParameter, rpu_powstep_device.h:22-25):
+    the step shrinks with a power of the distance to the bound."""
+
+    _kind = DEVICE_POW_STEP
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.pow_gamma = 1.0
+        self.pow_gamma_dtod = 0.1
+        self.pow_up_down = 0.0
+        self.pow_up_down_dtod = 0.0
+        self.write_noise_std = 0.0
+        self.apply_write_noise_on_set = True
+
+    def calc_weight_granularity(self) -> float:
+        """PowStepRPUDeviceMetaParameter::calcWeightGranularity (rpu_powstep_device.h:33)."""
+        return float(self.dw_min) * 0.5 ** float(self.pow_gamma)
+
+    def _to_c(self) -> _cabi.DeviceParams:
+        if self.write_noise_std != 0.0:
+            raise RuntimeError("write noise is not implemented by the B200 analog tile")
+        c = _cabi.DeviceParams()
+        self._fill_base(c)
+        c.ps_gamma, c.ps_gamma_dtod = float(self.pow_gamma), float(self.pow_gamma_dtod)
+        c.ps_gamma_up_down, c.ps_gamma_up_down_dtod = float(self.pow_up_down), float(self.pow_up_down_dtod)
+        return c
 
 
 class ExpStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):

@@ -69,7 +69,8 @@ enum ab200_device_kind {
   AB200_DEVICE_SOFT_BOUNDS = 3,           /* rpu_linearstep_device.h:70-83 */
   AB200_DEVICE_SOFT_BOUNDS_REFERENCE = 4, /* rpu_softbounds_reference_device.h */
   AB200_DEVICE_TRANSFER = 5,              /* rpu_transfer_device.h (Tiki-Taka) */
-  AB200_DEVICE_EXP_STEP = 6               /* rpu_expstep_device.h */
+  AB200_DEVICE_EXP_STEP = 6,              /* rpu_expstep_device.h */
+  AB200_DEVICE_POW_STEP = 7               /* rpu_powstep_device.h */
 };
 
 /* IOMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:180-226); attribute names as
@@ -169,6 +170,12 @@ typedef struct ab200_device_params {
   float es_b;
   float dw_min_std_add;
   float dw_min_std_slope;
+  /* PowStep (PowStepRPUDeviceMetaParameter, rpu_powstep_device.h:22-25; bound as pow_gamma,
+   * pow_gamma_dtod, pow_up_down, pow_up_down_dtod) */
+  float ps_gamma;
+  float ps_gamma_dtod;
+  float ps_gamma_up_down;
+  float ps_gamma_up_down_dtod;
 } ab200_device_params;
 
 /* TransferRPUDeviceMetaParameter (src/rpucuda/rpu_transfer_device.h:52-75). */

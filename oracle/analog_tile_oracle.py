@@ -39,6 +39,7 @@ PULSE_NONE, PULSE_STOCHASTIC_COMPRESSED, PULSE_DETERMINISTIC_IMPLICIT = 0, 1, 5
 DEV_IDEAL, DEV_CONSTANT_STEP, DEV_LINEAR_STEP, DEV_SOFT_BOUNDS, DEV_SOFT_BOUNDS_REFERENCE = range(5)
 DEV_TRANSFER = 5
 DEV_EXP_STEP = 6
+DEV_POW_STEP = 7
 
 
 def _check_res(res: float) -> np.float32:
@@ -444,6 +445,8 @@ class DeviceArrays:
     slope_up: Optional[np.ndarray] = None
     slope_down: Optional[np.ndarray] = None
     reference: Optional[np.ndarray] = None
+    gamma_up: Optional[np.ndarray] = None  # PowStep exponents
+    gamma_down: Optional[np.ndarray] = None
     dw_min_std: float = 0.0
     mult_noise: bool = True
     # ExpStep globals: (a, b, A_up, A_down, gamma_up, gamma_down, dw_min_std_add, dw_min_std_slope)
@@ -466,6 +469,9 @@ class DeviceArrays:
             kw["slope_down"] = g["slope_down" + suffix]
         if "reference" + suffix in g:
             kw["reference"] = g["reference" + suffix]
+        if "gamma_up" + suffix in g:
+            kw["gamma_up"] = g["gamma_up" + suffix]
+            kw["gamma_down"] = g["gamma_down" + suffix]
         return DeviceArrays(**kw)
 
 
@@ -534,6 +540,17 @@ def apply_pulses(w: np.ndarray, n_signed: np.ndarray, dev: DeviceArrays,
                 wn = np.where(down, w - dn, w + up_).astype(f32)
             wn = np.maximum(np.minimum(wn, dev.max_bound), dev.min_bound)
             wn = np.where(b_diff > 0, wn, w)
+        elif dev.kind == DEV_POW_STEP:
+            # rpu_powstep_device.cpp:91-121 (powf in fp32)
+            rng_w = (dev.max_bound - dev.min_bound).astype(f32)
+            with np.errstate(divide="ignore", invalid="ignore"):
+                f_dn = np.power(((w - dev.min_bound) / rng_w).astype(f32), dev.gamma_down).astype(f32)
+                f_up = np.power(((dev.max_bound - w) / rng_w).astype(f32), dev.gamma_up).astype(f32)
+            dn = ((dev.dwmin_down * f_dn).astype(f32) * (f32(1.0) + xi)).astype(f32)
+            up_ = ((dev.dwmin_up * f_up).astype(f32) * (f32(1.0) + xi)).astype(f32)
+            wn = np.where(down, w - dn, w + up_).astype(f32)
+            wn = np.minimum(np.maximum(wn, dev.min_bound), dev.max_bound)
+            wn = np.where(rng_w == 0, w, wn)
         else:
             raise NotImplementedError("device kind")
         w[act] = wn[act]

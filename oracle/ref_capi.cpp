@@ -16,6 +16,7 @@
 #include "rpu_constantstep_device.h"
 #include "rpu_expstep_device.h"
 #include "rpu_linearstep_device.h"
+#include "rpu_powstep_device.h"
 #include "rpu_pulsed.h"
 #include "rpu_softbounds_reference_device.h"
 #include "rpu_transfer_device.h"
@@ -137,6 +138,15 @@ std::unique_ptr<PulsedRPUDeviceMetaParameter<float>> makeSingle(const ab200_devi
     p->es_b = s.es_b;
     p->dw_min_std_add = s.dw_min_std_add;
     p->dw_min_std_slope = s.dw_min_std_slope;
+    return p;
+  }
+  case AB200_DEVICE_POW_STEP: {
+    auto p = std::make_unique<PowStepRPUDeviceMetaParameter<float>>();
+    toPulsedBase(s, *p);
+    p->ps_gamma = s.ps_gamma;
+    p->ps_gamma_dtod = s.ps_gamma_dtod;
+    p->ps_gamma_up_down = s.ps_gamma_up_down;
+    p->ps_gamma_up_down_dtod = s.ps_gamma_up_down_dtod;
     return p;
   }
   default:

@@ -13,6 +13,7 @@ KINDS = {
     "sb": D.SoftBoundsResistiveDeviceParameter,
     "sbr": D.SoftBoundsReferenceResistiveDeviceParameter,
     "es": D.ExpStepResistiveDeviceParameter,
+    "ps": D.PowStepResistiveDeviceParameter,
 }
 
 

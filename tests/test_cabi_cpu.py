@@ -51,15 +51,18 @@ def test_defaults_follow_reference_member_initialisers():
     for kind, cls in ((D.DEVICE_CONSTANT_STEP, D.ConstantStepResistiveDeviceParameter),
                       (D.DEVICE_SOFT_BOUNDS, D.SoftBoundsResistiveDeviceParameter),
                       (D.DEVICE_LINEAR_STEP, D.LinearStepResistiveDeviceParameter),
-                      (D.DEVICE_EXP_STEP, D.ExpStepResistiveDeviceParameter)):
+                      (D.DEVICE_EXP_STEP, D.ExpStepResistiveDeviceParameter),
+                      (D.DEVICE_POW_STEP, D.PowStepResistiveDeviceParameter)):
         dp = _cabi.DeviceParams()
         lib.ab200_default_device_params(C.byref(dp), kind)
         refd = cls()._to_c()
         for name, _ in _cabi.DeviceParams._fields_:
-            if kind in (D.DEVICE_CONSTANT_STEP, D.DEVICE_EXP_STEP) and name.startswith("ls_"):
+            if kind in (D.DEVICE_CONSTANT_STEP, D.DEVICE_EXP_STEP, D.DEVICE_POW_STEP) and name.startswith("ls_"):
                 continue  # LinearStep-only fields are not read for other kinds
             if kind != D.DEVICE_EXP_STEP and name.startswith("es_"):
                 continue  # ExpStep-only fields
+            if kind != D.DEVICE_POW_STEP and name.startswith("ps_"):
+                continue  # PowStep-only fields
             assert getattr(dp, name) == pytest.approx(getattr(refd, name)), (kind, name)
 
 

@@ -382,3 +382,37 @@ def test_io_random_input_stage_moments(what):
     else:
         assert (ys_ref[:, 2] == 0).all() and (ys[:, 2] == 0).all()
     H.assert_moments_agree(ys, ys_ref)
+
+
+@pytest.mark.parametrize("shape", [(96, 64, 32), (33, 70, 5)])
+def test_pow_step_device_noise_off(shape):
+    """PowStep device: granularity, host parameter draw (per-element exponents included) and the
+    weights after a deterministic update (powf of numpy vs glibc: last-bit differences allowed)."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    x_size, d_size, m = shape
+    rng = np.random.default_rng(x_size)
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+    dp = H.device("ps", False, pow_gamma=1.3, pow_gamma_dtod=0.2, pow_up_down=0.1, pow_up_down_dtod=0.05)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = ref.RefTile(cfg)
+    ours = T.AnalogTile(cfg)
+    names = t.hidden_parameter_names()
+    assert names == ours.get_hidden_parameter_names() and names[-2:] == ["gamma_up", "gamma_down"]
+    assert np.array_equal(ours.get_hidden_parameters().numpy(), t.get_hidden_parameters())
+    t.set_weights(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32))
+    W = t.get_weights()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+    lr = 0.01
+    gran = dp.calc_weight_granularity()
+    up = O.Up.from_c(cfg.update)
+    assert np.array_equal(t.coincidences(X[0], Dm[0], lr, gran),
+                          O.coincidences_det_implicit(X[0], Dm[0], lr, gran, up))
+    dev = O.DeviceArrays.from_hidden(O.DEV_POW_STEP, names, t.get_hidden_parameters(), 0.0, True)
+    t.set_learning_rate(lr)
+    t.update(X, Dm)
+    Wo = W.copy()
+    O.update(Wo, X, Dm, lr, gran, up, dev)
+    assert np.abs(t.get_weights() - Wo).max() <= 2e-6
+    assert np.abs(t.get_weights() - W).max() > 1e-3  # the update did something

@@ -417,3 +417,60 @@ def test_io_random_input_stage_moments(what):
     else:
         assert (ys[:, 2] == 0).all()
     H.assert_moments_agree(ys, ys_or)
+
+
+def _pow_step_device(noise):
+    return H.device("ps", noise, pow_gamma=1.3, pow_gamma_dtod=0.2, pow_up_down=0.1, pow_up_down_dtod=0.05)
+
+
+@pytest.mark.parametrize("x_size,d_size,m", [(64, 48, 17), (70, 130, 9)])
+def test_pow_step_deterministic_update(x_size, d_size, m):
+    """PowStep device (rpu_powstep_device.cpp): bit-exact pulse counts with the device's own weight
+    granularity, weights after the update within the powf rounding of the two platforms."""
+    rng = np.random.default_rng(5 + x_size)
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = _pow_step_device(False)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    up = O.Up.from_c(cfg.update)
+    lr, gran = 0.01, dp.calc_weight_granularity()
+    t.set_learning_rate(lr)
+    c = t.coincidences(torch.from_numpy(X[0]).cuda(), torch.from_numpy(Dm[0]).cuda()).cpu().numpy()
+    assert np.array_equal(c, O.coincidences_det_implicit(X[0], Dm[0], lr, gran, up))
+    dev = O.DeviceArrays.from_hidden(O.DEV_POW_STEP, t.get_hidden_parameter_names(),
+                                     t.get_hidden_parameters().numpy(), 0.0, True)
+    W_or = W.copy()
+    O.update(W_or, X, Dm, lr, gran, up, dev)
+    t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    W_new = t.get_weights().numpy()
+    assert np.abs(W_new - W).max() > 1e-3
+    assert np.abs(W_new - W_or).max() <= 3e-6
+
+
+def test_pow_step_stochastic_update_statistics():
+    rng = np.random.default_rng(23)
+    x_size, d_size, m, reps = 32, 24, 10, 150
+    p = H.training_params(noise=True, pulse_det=False)
+    dp = _pow_step_device(True)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    W0 = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    up = O.Up.from_c(cfg.update)
+    dev = O.DeviceArrays.from_hidden(O.DEV_POW_STEP, t.get_hidden_parameter_names(),
+                                     t.get_hidden_parameters().numpy(), dp.dw_min_std, True)
+    lr, gran = 0.05, dp.calc_weight_granularity()
+    t.set_learning_rate(lr)
+    xg, dg = torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda()
+    dws, dwo = [], []
+    org = np.random.default_rng(123)
+    for _ in range(reps):
+        t.set_weights(torch.from_numpy(W0))
+        Wc = t.get_weights().numpy()
+        t.update(xg, dg)
+        dws.append(t.get_weights().numpy() - Wc)
+        Wo = Wc.copy()
+        O.update(Wo, X, Dm, lr, gran, up, dev, org)
+        dwo.append(Wo - Wc)
+    H.assert_moments_agree(np.stack(dws), np.stack(dwo))
