@@ -85,7 +85,7 @@ UpEff resolveUp(const ab200_update_params &up) {
   e.res = checkRes(up.res);
   e.x_res_implicit = checkRes(up.x_res_implicit);
   e.d_res_implicit = checkRes(up.d_res_implicit);
-  if (up.pulse_type == AB200_PULSE_STOCHASTIC || up.pulse_type == AB200_PULSE_MEAN_COUNT) {
+  if (up.pulse_type == AB200_PULSE_STOCHASTIC) {
     AB200_FATAL("PulseType not supported");
   }
   if (up.sto_round) {

@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
   uint32_t *xw = p.xw + (long long)s * p.x_size;
   uint32_t *dw = p.dw + (long long)s * p.d_size;
   const bool implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT;
+  const bool mean_count = p.up.pulse_type == AB200_PULSE_MEAN_COUNT;
 
   for (int l = threadIdx.x; l < p.x_size + p.d_size; l += blockDim.x) {
     const bool is_x = l < p.x_size;
@@ -165,6 +166,21 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
       }
       if (!is_x) {
         sv = __fmul_rn(sv, (float)BL);
+      }
+      word = __float_as_uint(sv);
+    } else if (mean_count) {
+      // generateCountsMean / generateCoincidences (dense_bit_line_maker.cpp:142-204): the mean
+      // number of pulses per line, no fluctuation; the d count carries the factor 1 / BL, so the
+      // coincidences are rint(d * x) like those of the implicit type
+      const float vv = p.lr_neg ? -v : v;
+      const float pp = discretize(__fmul_rn(fabsf(vv), P), p.up.res);
+      float sv = 0.0f;
+      if (pp != 0.0f && BL > 0) {
+        const int ntimes = max(min((int)rintf(__fmul_rn((float)BL, pp)), BL), 0);
+        sv = (vv >= 0.0f || ntimes == 0) ? (float)ntimes : -(float)ntimes;
+        if (!is_x) {
+          sv = __fdiv_rn(sv, (float)BL);
+        }
       }
       word = __float_as_uint(sv);
     } else {
@@ -568,12 +584,16 @@ void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream) {
   if (p.m <= 0) {
     return;
   }
-  if (p.up.pulse_type != AB200_PULSE_DETERMINISTIC_IMPLICIT && p.up.desired_bl > 31) {
+  if (p.up.pulse_type == AB200_PULSE_STOCHASTIC_COMPRESSED && p.up.desired_bl > 31) {
     AB200_FATAL("desired_BL > 31 is not implemented for stochastic pulse trains");
   }
   pulsePrepareKernel<<<p.m, 256, 0, stream>>>(p);
   AB200_LAUNCH_CHECK();
-  const int implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT ? 1 : 0;
+  // both dense types keep a float value per line; coincidences are rint(d * x)
+  const int implicit = (p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT ||
+                        p.up.pulse_type == AB200_PULSE_MEAN_COUNT)
+                           ? 1
+                           : 0;
   const int n_blk = (p.m + UBLK - 1) / UBLK;
   pulseNzKernel<<<dim3((p.x_size + 255) / 256, n_blk), 256, 0, stream>>>(p.xw, p.x_size, p.m, p.xnz,
                                                                        implicit);
@@ -588,7 +608,8 @@ void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream) {
     return;
   }
   dim3 grid((p.d_size + UT_I - 1) / UT_I, (p.x_size + UT_J - 1) / UT_J);
-  const bool implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT;
+  const bool implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT ||
+                        p.up.pulse_type == AB200_PULSE_MEAN_COUNT;
   const bool noisy = p.dw_min_std > 0.0f;
 #define AB200_UPD2(KIND, IMPL)                                                                     \
   if (noisy) {                                                                                     \
@@ -636,7 +657,8 @@ __global__ void coincidenceKernel(UpdateProblem p, int32_t *counts) {
   int i = (int)(t / p.x_size), j = (int)(t % p.x_size);
   uint32_t xwv = p.xw[j], dwv = p.dw[i];
   int n;
-  if (p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT) {
+  if (p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT ||
+      p.up.pulse_type == AB200_PULSE_MEAN_COUNT) {
     n = dwv == 0u ? 0 : (int)rintf(__fmul_rn(__uint_as_float(dwv), __uint_as_float(xwv)));
   } else {
     n = __popc((xwv & dwv) >> 1);

@@ -173,7 +173,7 @@ class AnalogTileUpdateParameter:
 
     def _to_c(self) -> _cabi.UpdateParams:
         pt = int(self.pulse_type)
-        if pt in (int(PulseType.Stochastic), int(PulseType.MeanCount)):
+        if pt == int(PulseType.Stochastic):
             raise RuntimeError("PulseType not supported")
         c = _cabi.UpdateParams()
         c.pulse_type = pt

@@ -36,6 +36,7 @@ NM_NONE, NM_ABS_MAX, NM_ABS_MAX_NP_SUM, NM_MAX, NM_CONSTANT = 0, 1, 2, 3, 4
 BM_NONE, BM_ITERATIVE, BM_ITERATIVE_WORST_CASE = 0, 1, 2
 WN_NONE, WN_ADDITIVE_CONSTANT = 0, 1
 PULSE_NONE, PULSE_STOCHASTIC_COMPRESSED, PULSE_DETERMINISTIC_IMPLICIT = 0, 1, 5
+PULSE_MEAN_COUNT = 4
 DEV_IDEAL, DEV_CONSTANT_STEP, DEV_LINEAR_STEP, DEV_SOFT_BOUNDS, DEV_SOFT_BOUNDS_REFERENCE = range(5)
 DEV_TRANSFER = 5
 DEV_EXP_STEP = 6
@@ -409,6 +410,31 @@ def coincidences_det_implicit(x: np.ndarray, d: np.ndarray, lr: float, dw_min: f
     return n
 
 
+def coincidences_mean_count(x: np.ndarray, d: np.ndarray, lr: float, dw_min: float, up: Up) -> np.ndarray:
+    """DenseBitLineMaker::makeCoincidences, MeanCount, one sample (dense_bit_line_maker.cpp:142-204,
+    266-312): the mean number of pulses per line, coincidences rint(d_count / BL * x_count).
+    Signed int32 [d, x]; positive = weight decreases."""
+    x = np.asarray(x, f32)
+    d = np.asarray(d, f32)
+    alr = abs(lr)
+    bl, a, b = bl_a_b(up, alr, dw_min, np.abs(x).max(initial=0), np.abs(d).max(initial=0))
+    if bl <= 0:
+        return np.zeros((d.size, x.size), np.int32)
+
+    def counts(v, p):
+        vv = -v if lr < 0 else v
+        pp = quantize((np.abs(vv) * f32(p)).astype(f32), f32(up.res))
+        nt = np.clip(np.rint((f32(bl) * pp).astype(f32)), 0, bl).astype(np.int32)
+        nt = np.where(pp == 0, 0, nt)
+        return np.where(vv >= 0, nt, -nt).astype(np.int32)
+
+    xc = counts(x, b)
+    dc = (counts(d, a).astype(f32) / f32(bl)).astype(f32)
+    n = np.rint((dc[:, None] * xc[None, :].astype(f32)).astype(f32)).astype(np.int32)
+    n[dc == 0, :] = 0
+    return n
+
+
 def coincidences_stochastic_compressed(
     x: np.ndarray, d: np.ndarray, lr: float, dw_min: float, up: Up, rng: np.random.Generator
 ) -> np.ndarray:
@@ -570,6 +596,8 @@ def update(
     for s in range(x.shape[0]):
         if up.pulse_type == PULSE_DETERMINISTIC_IMPLICIT:
             n = coincidences_det_implicit(x[s], d[s], lr, dw_min, up)
+        elif up.pulse_type == PULSE_MEAN_COUNT:
+            n = coincidences_mean_count(x[s], d[s], lr, dw_min, up)
         elif up.pulse_type == PULSE_STOCHASTIC_COMPRESSED:
             assert rng is not None
             n = coincidences_stochastic_compressed(x[s], d[s], lr, dw_min, up, rng)

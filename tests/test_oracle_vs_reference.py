@@ -416,3 +416,42 @@ def test_pow_step_device_noise_off(shape):
     O.update(Wo, X, Dm, lr, gran, up, dev)
     assert np.abs(t.get_weights() - Wo).max() <= 2e-6
     assert np.abs(t.get_weights() - W).max() > 1e-3  # the update did something
+
+
+@pytest.mark.parametrize("kind,bl,ubl", [("cs", 31, True), ("sb", 100, True), ("cs", 20, False)])
+def test_mean_count_pulse_type(kind, bl, ubl):
+    """PulseType.MeanCount (the mean number of pulses per line, no fluctuation; pulse trains
+    longer than 31 allowed): coincidences and weights after an update equal the compiled
+    reference's."""
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(29)
+    x_size, d_size, m = 40, 24, 12
+    p = H.training_params(noise=False, pulse_det=True)
+    p.update.pulse_type = D.PulseType.MeanCount
+    p.update.desired_bl = bl
+    p.update.update_bl_management = ubl
+    p.update.update_management = ubl
+    dp = H.device(kind, False)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = ref.RefTile(cfg)
+    t.set_weights(rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32))
+    W = t.get_weights()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.2, (m, d_size)).astype(np.float32)
+    up = O.Up.from_c(cfg.update)
+    lr = 0.02
+    for s in range(3):
+        for sign in (1.0, -1.0):
+            c_ref = t.coincidences(X[s], Dm[s], sign * lr, dp.dw_min)
+            c = O.coincidences_mean_count(X[s], Dm[s], sign * lr, dp.dw_min, up)
+            assert np.array_equal(c_ref, c)
+            assert np.abs(c).max() > 0
+    dev = O.DeviceArrays.from_hidden(KIND[kind], t.hidden_parameter_names(), t.get_hidden_parameters(),
+                                     0.0, bool(getattr(dp, "mult_noise", True)))
+    t.set_learning_rate(lr)
+    t.update(X, Dm)
+    Wo = W.copy()
+    O.update(Wo, X, Dm, lr, dp.dw_min, up, dev)
+    assert np.abs(t.get_weights() - Wo).max() <= 1e-6
+    assert np.abs(t.get_weights() - W).max() > 1e-3

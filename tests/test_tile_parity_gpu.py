@@ -474,3 +474,38 @@ def test_pow_step_stochastic_update_statistics():
         O.update(Wo, X, Dm, lr, gran, up, dev, org)
         dwo.append(Wo - Wc)
     H.assert_moments_agree(np.stack(dws), np.stack(dwo))
+
+
+@pytest.mark.parametrize("kind,bl,ubl", [("cs", 31, True), ("sb", 100, True), ("cs", 20, False)])
+def test_mean_count_pulse_type(kind, bl, ubl):
+    """PulseType.MeanCount on the GPU: bit-exact coincidence counts (pulse trains longer than 31
+    included) and the weights after the update against the oracle."""
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(29)
+    x_size, d_size, m = 70, 40, 40
+    p = H.training_params(noise=False, pulse_det=True)
+    p.update.pulse_type = D.PulseType.MeanCount
+    p.update.desired_bl = bl
+    p.update.update_bl_management = ubl
+    p.update.update_management = ubl
+    dp = H.device(kind, False)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    up = O.Up.from_c(cfg.update)
+    lr = 0.02
+    t.set_learning_rate(lr)
+    for s in range(3):
+        c = t.coincidences(torch.from_numpy(X[s]).cuda(), torch.from_numpy(Dm[s]).cuda()).cpu().numpy()
+        assert np.array_equal(c, O.coincidences_mean_count(X[s], Dm[s], lr, dp.dw_min, up))
+    names = t.get_hidden_parameter_names()
+    kinds = {"cs": O.DEV_CONSTANT_STEP, "sb": O.DEV_SOFT_BOUNDS}
+    dev = O.DeviceArrays.from_hidden(kinds[kind], names, t.get_hidden_parameters().numpy(), 0.0, True)
+    W_or = W.copy()
+    O.update(W_or, X, Dm, lr, dp.dw_min, up, dev)
+    t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    W_new = t.get_weights().numpy()
+    assert np.abs(W_new - W).max() > 1e-3
+    assert np.abs(W_new - W_or).max() <= 1e-6
