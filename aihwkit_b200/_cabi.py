@@ -215,6 +215,10 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_array_set_weights": (_I, [_VP, _FP]),
         "ab200_array_forward_scatter": (_I, [_VP, _FP, _I, _VP, _I, _I, _I, _VP]),
         "ab200_sum_slots": (_I, [_FP, _I, C.c_longlong, _FP, _VP]),
+        "ab200_array_scatter_codes_supported": (_I, [_VP]),
+        "ab200_array_forward_scatter_codes": (_I, [_VP, _FP, _I, _VP, _VP, _I, _I, _I, _VP]),
+        "ab200_sum_code_slots": (_I, [_VP, C.c_longlong, _VP, C.c_longlong, _I, C.POINTER(_I), _I, _I, _I,
+                                      _FP, _VP]),
         "ab200_peer_alloc": (_I, [C.c_size_t, _I, C.POINTER(_VP), C.c_char_p]),
         "ab200_peer_open": (_I, [C.c_char_p, _I, C.POINTER(_VP)]),
         "ab200_peer_close": (_I, [_VP]),

@@ -286,6 +286,47 @@ void TileArray::forwardScatter(const float *x_local, int m, float *const *out_ta
   scatter_table_ = nullptr;
 }
 
+bool TileArray::scatterCodesSupported() {
+  if (in_begin_ == in_end_ || scaled_ || bias_dev_ != nullptr || (out_size_ & 31) != 0) {
+    return false;
+  }
+  for (int n : out_sizes_) {
+    if ((n % 128) != 0) {
+      return false;
+    }
+  }
+  return TcEngine::codesSupported(tiles_[0]->fio());
+}
+
+void TileArray::forwardScatterCodes(const float *x_local, int m, uint8_t *const *code_table_dev,
+                                    float *const *fac_table_dev, int n_owners, int rows_per_owner,
+                                    int rotate_rows, cudaStream_t s) {
+  if (m <= 0) {
+    return;
+  }
+  if (!scatterCodesSupported() || !tcEligible(m)) {
+    AB200_FATAL("forward_scatter_codes: this array is not eligible (see "
+                "ab200_array_scatter_codes_supported; batch >= 128)");
+  }
+  if (n_owners <= 0 || rows_per_owner <= 0 || (rows_per_owner & 31) != 0 ||
+      (long long)n_owners * rows_per_owner < m) {
+    AB200_FATAL("forward_scatter_codes: the owners' row blocks do not cover the batch");
+  }
+  scatter_codes_ = code_table_dev;
+  scatter_facs_ = fac_table_dev;
+  scatter_rows_ = rows_per_owner;
+  scatter_rotate_ = rotate_rows;
+  try {
+    forwardTc(x_local, localInSize(), nullptr, m, s);
+  } catch (...) {
+    scatter_codes_ = nullptr;
+    scatter_facs_ = nullptr;
+    throw;
+  }
+  scatter_codes_ = nullptr;
+  scatter_facs_ = nullptr;
+}
+
 void TileArray::backward(const float *d, float *x_grad, int m, cudaStream_t s) {
   if (m <= 0) {
     return;
@@ -378,6 +419,8 @@ void TileArray::forwardTc(const float *x0, long long x_ss, float *y, int m, cuda
   r.tile_scale = scaled_ ? tile_scale_dev_ : nullptr;
   r.bias = bias_dev_;
   r.out_table = scatter_table_;
+  r.code_table = scatter_codes_;
+  r.fac_table = scatter_facs_;
   r.rows_per_owner = scatter_rows_;
   r.rotate_rows = scatter_rotate_;
   tc_->run(r, s);

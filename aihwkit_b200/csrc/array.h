@@ -40,6 +40,11 @@ public:
   // pointers into local or peer memory, row pitch out_size). Needs the tensor-core path.
   void forwardScatter(const float *x_local, int m, float *const *out_table_dev, int n_owners,
                       int rows_per_owner, int rotate_rows, cudaStream_t s);
+  // the same with signed-byte ADC codes per in-split instead of fp32 sums (see the C header)
+  bool scatterCodesSupported();
+  void forwardScatterCodes(const float *x_local, int m, uint8_t *const *code_table_dev,
+                           float *const *fac_table_dev, int n_owners, int rows_per_owner,
+                           int rotate_rows, cudaStream_t s);
   // Training of a mapped layer, tile by tile as autograd does in the reference
   // (TileModuleArray modules -> TileWithPeriphery.backward / update, tiles/periphery.py:1068-1110,
   // 1154-1230). backward: x_grad[:, in-split i] = sum over out-splits o of
@@ -67,6 +72,8 @@ private:
   bool scaled_ = false;
   float *bias_dev_ = nullptr;
   float *const *scatter_table_ = nullptr; // set only while forwardScatter runs
+  uint8_t *const *scatter_codes_ = nullptr; // set only while forwardScatterCodes runs
+  float *const *scatter_facs_ = nullptr;
   int scatter_rows_ = 0, scatter_rotate_ = 0;
   float *d_scratch_ = nullptr; // [m][largest out-split]: gradients times / over the tile scale
   size_t d_scratch_floats_ = 0;

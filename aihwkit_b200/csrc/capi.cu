@@ -496,6 +496,107 @@ int ab200_sum_slots(const float *slots_dev, int n_slots, long long elems, float 
   AB200_CATCH
 }
 
+int ab200_array_scatter_codes_supported(ab200_array *arr) {
+  try {
+    auto a = A(arr);
+    return a->scatterCodesSupported() ? 1 : 0;
+  } catch (...) {
+    return 0;
+  }
+}
+int ab200_array_forward_scatter_codes(ab200_array *arr, const float *x_local_dev, int m_batch,
+                                      unsigned char *const *code_table_dev,
+                                      float *const *fac_table_dev, int n_owners,
+                                      int rows_per_owner, int rotate_rows, void *stream) {
+  AB200_TRY
+  A(arr)->forwardScatterCodes(x_local_dev, m_batch, code_table_dev, fac_table_dev, n_owners,
+                              rows_per_owner, rotate_rows, (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+namespace {
+struct CodeSlots {
+  const unsigned char *codes;
+  long long code_stride;
+  const float *facs;
+  long long fac_stride;
+  int n_slots;
+  int n_planes[16];
+  int rows_per_owner, rows_valid, out_size;
+  float *out;
+};
+// one thread per row and four columns: the word of four codes of every slot and plane, times the
+// row's factor; planes of a slot first (fused multiply-add chain from zero, as the MVM kernel sums
+// its in-splits), then the slots in order (as sumSlotsKernel adds them)
+__global__ void __launch_bounds__(256) codeSlotsKernel(CodeSlots p) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const int w4 = p.out_size >> 2;
+  if (t >= (long long)p.rows_valid * w4) {
+    return;
+  }
+  const int row = (int)(t / w4), c4 = (int)(t % w4);
+  const int col = c4 * 4;
+  const long long plane_bytes = (long long)p.rows_per_owner * p.out_size;
+  const long long off = ((long long)(row >> 5) * (p.out_size >> 5) + (col >> 5)) * 1024 +
+                        (long long)(row & 31) * 32 + (col & 31);
+  float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int q = 0; q < p.n_slots; q++) {
+    const unsigned char *cs = p.codes + (long long)q * p.code_stride;
+    const float *fs = p.facs + (long long)q * p.fac_stride;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < p.n_planes[q]; i++) {
+      const uint32_t w = *reinterpret_cast<const uint32_t *>(cs + (long long)i * plane_bytes + off);
+      const float f = fs[(long long)i * p.rows_per_owner + row];
+      acc.x = fmaf((float)(signed char)(w & 0xFF), f, acc.x);
+      acc.y = fmaf((float)(signed char)((w >> 8) & 0xFF), f, acc.y);
+      acc.z = fmaf((float)(signed char)((w >> 16) & 0xFF), f, acc.z);
+      acc.w = fmaf((float)(signed char)(w >> 24), f, acc.w);
+    }
+    if (q == 0) {
+      total = acc;
+    } else {
+      total.x += acc.x;
+      total.y += acc.y;
+      total.z += acc.z;
+      total.w += acc.w;
+    }
+  }
+  *reinterpret_cast<float4 *>(p.out + (long long)row * p.out_size + col) = total;
+}
+} // namespace
+
+int ab200_sum_code_slots(const unsigned char *code_slots_dev, long long code_slot_stride,
+                         const float *fac_slots_dev, long long fac_slot_stride, int n_slots,
+                         const int *n_planes, int rows_per_owner, int rows_valid, int out_size,
+                         float *out_dev, void *stream) {
+  AB200_TRY
+  if (n_slots <= 0 || n_slots > 16 || n_planes == nullptr || rows_valid < 0 ||
+      rows_valid > rows_per_owner || (rows_per_owner & 31) != 0 || (out_size & 31) != 0 ||
+      (((uintptr_t)out_dev) & 15) != 0 || (((uintptr_t)code_slots_dev | (uintptr_t)code_slot_stride) & 3) != 0) {
+    AB200_FATAL("sum_code_slots: 1..16 slots, rows and columns in multiples of 32, aligned buffers");
+  }
+  if (rows_valid == 0) {
+    return 0;
+  }
+  CodeSlots p{};
+  p.codes = code_slots_dev;
+  p.code_stride = code_slot_stride;
+  p.facs = fac_slots_dev;
+  p.fac_stride = fac_slot_stride;
+  p.n_slots = n_slots;
+  for (int q = 0; q < n_slots; q++) {
+    p.n_planes[q] = n_planes[q];
+  }
+  p.rows_per_owner = rows_per_owner;
+  p.rows_valid = rows_valid;
+  p.out_size = out_size;
+  p.out = out_dev;
+  const long long n = (long long)rows_valid * (out_size >> 2);
+  codeSlotsKernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p);
+  AB200_LAUNCH_CHECK();
+  AB200_CATCH
+}
+
 int ab200_peer_alloc(size_t bytes, int cuda_device, void **dev_ptr, unsigned char handle_out[64]) {
   AB200_TRY
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");

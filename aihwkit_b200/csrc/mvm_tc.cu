@@ -88,6 +88,12 @@ struct TcKernelParams {
   // sharded layer, local or peer memory): row r goes to out_table[r / rows_per_owner] at row
   // r % rows_per_owner; null = everything to `out`
   float *const *out_table;
+  // codes variant of the scatter: instead of the fp32 sum over this launch's in-splits, the ADC
+  // code (one signed byte) of every in-split goes to the owner, plane i of this rank's slot, in
+  // blocks of 32 rows x 32 columns (1 KB, row-major); the per-row factors go to fac_table[owner]
+  // as [in-split][row]. The owner multiplies and sums (codeSlotsKernel).
+  uint8_t *const *code_table;
+  float *const *fac_table;
   int rows_per_owner;
   int rb_rotate; // the sweep over the row blocks starts at this block (staggers the ranks)
   int accumulate, backward;
@@ -303,7 +309,7 @@ constexpr uint32_t kIdescPair = (1u << 4) | (1u << 7) | (1u << 10) |
 //               128 rows of codes and half of the stacked weight tile from its own shared memory,
 //               so the shared-memory traffic per SM and per FLOP drops by a third. Each CTA keeps
 //               the accumulator rows of its own 128 rows in its own TMEM and runs its own epilogue.
-template <bool BM, bool PAIR>
+template <bool BM, bool PAIR, bool CODES = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     mvmTcKernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_bhi,
                 const __grid_constant__ CUtensorMap tm_blo, const TcKernelParams p) {
@@ -633,6 +639,58 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const float sig_codes = live ? sigma * inv_res_out : 0.0f;
         const float fac_codes = live ? fac * io.res_out : 0.0f;
         const uint64_t ctr = ctr0 + (uint64_t)row * n4h;
+        if (CODES) {
+          // The rounded, clipped code stays in the low mantissa bits of (value + 1.5 * 2^23):
+          // its low byte is the two's-complement code. Four codes per word, eight words per row.
+          uint32_t cw[TC_EPI_COLS / 4];
+          const float lo_m = kMagic - bound_codes, hi_m = kMagic + bound_codes;
+#pragma unroll
+          for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 8) {
+            float acc[8];
+            loadAcc8(taddr + (uint32_t)c0, acc);
+            float z[8];
+            gauss8Keyed(rkeys, ctr + (uint64_t)(c0 >> 3), p.call, tile_tag, z);
+            uint32_t bits[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              float r = fmaf(z[j], sig_codes, acc[j] * in_codes) + kMagic;
+              r = fminf(fmaxf(r, lo_m), hi_m);
+              bits[j] = __float_as_uint(r);
+            }
+#pragma unroll
+            for (int g = 0; g < 2; g++) {
+              cw[(c0 >> 2) + g] =
+                  __byte_perm(__byte_perm(bits[4 * g], bits[4 * g + 1], 0x0040),
+                              __byte_perm(bits[4 * g + 2], bits[4 * g + 3], 0x0040), 0x5410);
+            }
+          }
+          // this warp's 32 x 32 bytes are one contiguous 1 KB block at the owner: after an
+          // exchange, every store instruction writes 512 contiguous bytes (rows 0-15, then 16-31)
+          const int row0 = rb * ROWS + rank * TC_M + q * 32;
+          if (row0 < p.m) {
+            const int owner = row0 / p.rows_per_owner;
+            const int lrow0 = row0 - owner * p.rows_per_owner;
+            const long long n_total = p.out_ss; // columns of the whole layer
+            const long long blk = (long long)(lrow0 >> 5) * (n_total >> 5) + ((ch.z + cbase) >> 5);
+            uint8_t *dst = p.code_table[owner] + (long long)i * p.rows_per_owner * n_total + blk * 1024;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+              uint32_t v[4];
+#pragma unroll
+              for (int j = 0; j < TC_EPI_COLS / 4; j++) {
+                const uint32_t t = __shfl_sync(0xffffffffu, cw[j], (lane >> 1) + 16 * h);
+                if ((j >> 2) == (lane & 1)) {
+                  v[j & 3] = t;
+                }
+              }
+              *reinterpret_cast<uint4 *>(dst + h * 512 + lane * 16) = make_uint4(v[0], v[1], v[2], v[3]);
+            }
+            if (ch.z == 0 && cbase == 0 && row_ok) {
+              p.fac_table[owner][(long long)i * p.rows_per_owner + (row - owner * p.rows_per_owner)] =
+                  fac_codes;
+            }
+          }
+        } else {
 #pragma unroll
         for (int c0 = 0; c0 < TC_EPI_COLS; c0 += 8) {
           float acc[8];
@@ -649,6 +707,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             r = fminf(fmaxf(r, -bound_codes), bound_codes);
             sum[c0 + j] = fmaf(r, fac_codes, sum[c0 + j]);
           }
+        }
         }
       } else {
 #pragma unroll
@@ -696,7 +755,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     if (ok && row_ok && exceeded && io.bm != AB200_BM_NONE && p.flags != nullptr) {
       atomicOr(&p.flags[row], 1);
     }
-    if (ok && p.out_table) {
+    if (CODES) {
+      // everything went out in-split by in-split
+    } else if (ok && p.out_table) {
       // Scatter to the row-block owners, possibly peer memory: transpose the warp's 32 x 32
       // block in registers (five exchange steps) so that every store instruction writes 128
       // contiguous bytes of one row - over NVLink the 16-byte pieces of the row-per-lane layout
@@ -941,6 +1002,18 @@ static CUtensorMap makeMap(void *base, uint64_t rows, uint64_t cols, uint64_t ld
   return map;
 }
 
+// The scatter of ADC codes needs the noisy regime with an ADC whose codes fit a signed byte, and
+// no bound management (nothing is re-run after the codes have left).
+bool TcEngine::codesSupported(const IOEff &io) {
+  if (!ioSupported(io) || io.bm != AB200_BM_NONE || !(io.res_out > 0.0f)) {
+    return false;
+  }
+  const bool noisy = io.out_noise > 0.0f ||
+                     (io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f);
+  const float bc = io.out_bound / io.res_out;
+  return noisy && bc <= 127.0f && fabsf(bc - rintf(bc)) < 1e-3f;
+}
+
 bool TcEngine::ioSupported(const IOEff &io) {
   if (io.is_perfect || !(io.res_in > 0.0f) || !(io.inp_bound < 1e30f)) {
     return false;
@@ -1157,6 +1230,21 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   p.out = r.out;
   p.out_ss = r.out_ss;
   p.out_table = r.out_table;
+  p.code_table = r.code_table;
+  p.fac_table = r.fac_table;
+  const bool codes = r.code_table != nullptr;
+  if (codes) {
+    if (!codesSupported(r.io) || r.fac_table == nullptr || r.tile_scale != nullptr ||
+        r.bias != nullptr || r.accumulate || r.backward || r.rows_per_owner <= 0 ||
+        (r.rows_per_owner & 31) != 0 || (r.out_ss & 31) != 0) {
+      AB200_FATAL("tensor-core MVM: settings not eligible for the scatter of ADC codes");
+    }
+    for (int n : out_sizes_) {
+      if ((n % TC_N) != 0) {
+        AB200_FATAL("tensor-core MVM: the scatter of ADC codes needs out-splits that are multiples of 128");
+      }
+    }
+  }
   p.rows_per_owner = r.rows_per_owner > 0 ? r.rows_per_owner : 1;
   {
     const int rows_item = pair_rows(r.m);
@@ -1182,7 +1270,8 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   if (pair) {
     const int n_items = n_chunks_ * ((r.m + 2 * TC_M - 1) / (2 * TC_M));
     const int n_pairs = n_items < n_sm / 2 ? n_items : n_sm / 2;
-    auto kernel = bm ? mvmTcKernel<true, true> : mvmTcKernel<false, true>;
+    auto kernel = codes ? mvmTcKernel<false, true, true>
+                        : (bm ? mvmTcKernel<true, true> : mvmTcKernel<false, true>);
     AB200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC2_SMEM_BYTES));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * n_pairs);
@@ -1201,7 +1290,8 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   } else {
     const int n_items = n_chunks_ * ((r.m + TC_M - 1) / TC_M);
     dim3 grid(n_items < n_sm ? n_items : n_sm); // one persistent CTA per SM
-    auto kernel = bm ? mvmTcKernel<true, false> : mvmTcKernel<false, false>;
+    auto kernel = codes ? mvmTcKernel<false, false, true>
+                        : (bm ? mvmTcKernel<true, false> : mvmTcKernel<false, false>);
     AB200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
     kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
     grid_x = (int)grid.x;

@@ -54,6 +54,12 @@ public:
     // is the row the sweep over the row blocks starts at: it staggers the ranks' sweeps so that no
     // owner receives from two ranks at once.
     float *const *out_table = nullptr;
+    // codes variant of the scatter (needs codesSupported, out-splits that are multiples of 128,
+    // no tile scales / bias): the signed-byte ADC code of every in-split goes to plane i of
+    // code_table[owner] in 32 x 32 blocks of 1 KB, the per-row factors to fac_table[owner] as
+    // [in-split][row]; `out` is not written
+    uint8_t *const *code_table = nullptr;
+    float *const *fac_table = nullptr;
     int rows_per_owner = 0;
     int rotate_rows = 0;
     // optional caller-owned per-row scratch (only valid for I == 1): lets the bound-management
@@ -65,6 +71,8 @@ public:
 
   // whether the IO settings can be expressed as integer DAC codes in bf16
   static bool ioSupported(const IOEff &io);
+  // whether, in addition, every in-split's result can leave the kernel as signed-byte ADC codes
+  static bool codesSupported(const IOEff &io);
   // throws if an earlier launch reported a device-side failure (timeout of a bounded wait)
   void checkStatus();
 

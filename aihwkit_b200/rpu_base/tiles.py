@@ -585,6 +585,32 @@ class TileArray:
             self._h, x.data_ptr(), x.size(0), out_table.data_ptr(), out_table.numel(),
             int(rows_per_owner), int(rotate_rows), _stream_ptr(x)))
 
+    def scatter_codes_supported(self) -> bool:
+        """Whether :meth:`forward_scatter_codes` can be used: noisy inference settings whose ADC
+        codes fit a signed byte, no bound management, out-splits in multiples of 128, no mapping
+        scales or bias on this object."""
+        return bool(self._lib.ab200_array_scatter_codes_supported(self._h))
+
+    def forward_scatter_codes(self, x_local: torch.Tensor, code_table: torch.Tensor,
+                              fac_table: torch.Tensor, rows_per_owner: int,
+                              rotate_rows: int = 0) -> None:
+        """Like :meth:`forward_scatter`, but every in-split's integer ADC code (one byte per
+        element) is written to the owners instead of the fp32 sum over the in-splits, together
+        with the per-row factors; the owner multiplies and sums
+        (``ab200_sum_code_slots``).  ``code_table`` / ``fac_table``: CUDA int64 tensors of device
+        pointers, one per owner."""
+        x = _check_input(x_local, "x_local")
+        if not x.is_cuda or x.dim() != 2 or x.size(1) != self.local_in_size:
+            raise RuntimeError(f"expected a CUDA [m, {self.local_in_size}] tensor")
+        for t in (code_table, fac_table):
+            if not t.is_cuda or t.dtype != torch.int64 or not t.is_contiguous():
+                raise RuntimeError("pointer tables must be contiguous CUDA int64 tensors")
+        if code_table.numel() != fac_table.numel():
+            raise RuntimeError("code_table and fac_table need one pointer per owner each")
+        check(self._lib.ab200_array_forward_scatter_codes(
+            self._h, x.data_ptr(), x.size(0), code_table.data_ptr(), fac_table.data_ptr(),
+            code_table.numel(), int(rows_per_owner), int(rotate_rows), _stream_ptr(x)))
+
     def forward(self, x_input: torch.Tensor, is_test: bool = True, non_blocking: bool = False,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``x_input`` on the GPU: kernels only.  ``x_input`` on the CPU: the library pipelines

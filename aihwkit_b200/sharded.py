@@ -105,11 +105,17 @@ class ShardedTileArray:
         return self._ov_partial
 
     # ---- reduce-scatter by direct stores --------------------------------------------------------
-    def enable_scatter(self, m: int) -> None:
+    def enable_scatter(self, m: int, codes: Optional[bool] = None) -> None:
         """Prepare :meth:`forward_reduce_scatter` for batches of ``m`` rows: every rank allocates
         two sets of ``world`` slots of ``rows x out_size`` floats (double buffering over steps),
         shares them with the other ranks of the node through CUDA IPC handles, and builds the
-        pointer tables the kernel scatters through."""
+        pointer tables the kernel scatters through.
+
+        ``codes``: send the signed-byte ADC code of every in-split (plus one factor per row and
+        in-split) instead of the fp32 sum over the rank's in-splits - a quarter of the bytes on
+        the wire per in-split, so it pays while a rank holds fewer than four in-splits.  Default:
+        used when every rank's tiles are eligible (``TileArray.scatter_codes_supported``) and no
+        rank holds more than three in-splits."""
         import ctypes as C
 
         from . import _cabi
@@ -121,13 +127,31 @@ class ShardedTileArray:
         self._sc_m = m
         dev_index = self.local.device.index
         slot_floats = self._sc_rows * self.out_size
+        # codes variant: agreed on by all ranks
+        mine = (self.end - self.begin, bool(self.local.scatter_codes_supported()) if self.end > self.begin else False)
+        infos = [None] * self.world
+        dist.all_gather_object(infos, mine, group=self.group)
+        self._sc_planes = [int(i[0]) for i in infos]
+        eligible = all(i[1] for i in infos) and (self._sc_rows % 32 == 0) and self.world <= 16
+        if codes is None:
+            codes = eligible and max(self._sc_planes) <= 3
+        elif codes and not eligible:
+            raise RuntimeError("the scatter of ADC codes is not available for this layer")
+        self._sc_codes = bool(codes)
+        max_planes = max(self._sc_planes)
+        self._sc_code_stride = max_planes * self._sc_rows * self.out_size  # bytes per sender slot
+        self._sc_fac_stride = max_planes * self._sc_rows                   # floats per sender slot
+        if self._sc_codes:
+            alloc_bytes = self.world * (self._sc_code_stride + 4 * self._sc_fac_stride)
+        else:
+            alloc_bytes = 4 * slot_floats * self.world
         # a rank whose allocation or mapping fails tells the others through the same exchange, so
         # that every rank raises (and none waits in a collective the failed one never joins)
         handles, self._sc_mine, self._sc_peers, failure = [], [], [], None
         try:
             for _ in range(2):
                 ptr, h = C.c_void_p(), C.create_string_buffer(64)
-                _cabi.check(lib.ab200_peer_alloc(4 * slot_floats * self.world, dev_index, C.byref(ptr), h))
+                _cabi.check(lib.ab200_peer_alloc(alloc_bytes, dev_index, C.byref(ptr), h))
                 self._sc_mine.append(ptr.value)
                 handles.append(h.raw)
         except RuntimeError as exc:
@@ -135,11 +159,11 @@ class ShardedTileArray:
         gathered = [None] * self.world
         dist.all_gather_object(gathered, failure or handles, group=self.group)
         failure = next((g for g in gathered if isinstance(g, str)), None)
-        self._sc_tables = []
+        self._sc_tables, self._sc_fac_tables = [], []
         if failure is None:
             try:
                 for b in range(2):
-                    ptrs = []
+                    ptrs, fptrs = [], []
                     for q in range(self.world):
                         if q == self.rank:
                             base = self._sc_mine[b]
@@ -148,8 +172,17 @@ class ShardedTileArray:
                             _cabi.check(lib.ab200_peer_open(gathered[q][b], dev_index, C.byref(p)))
                             self._sc_peers.append(p.value)
                             base = p.value
-                        ptrs.append(base + 4 * slot_floats * self.rank)  # this rank's slot at owner q
+                        if self._sc_codes:
+                            # this rank's code planes and factors at owner q
+                            ptrs.append(base + self._sc_code_stride * self.rank)
+                            fptrs.append(base + self._sc_code_stride * self.world
+                                         + 4 * self._sc_fac_stride * self.rank)
+                        else:
+                            ptrs.append(base + 4 * slot_floats * self.rank)  # this rank's slot at owner q
                     self._sc_tables.append(torch.tensor(ptrs, dtype=torch.int64, device=self.local.device))
+                    if self._sc_codes:
+                        self._sc_fac_tables.append(
+                            torch.tensor(fptrs, dtype=torch.int64, device=self.local.device))
             except RuntimeError as exc:
                 failure = f"rank {self.rank}: {exc}"
         opened = [None] * self.world
@@ -172,14 +205,28 @@ class ShardedTileArray:
         synchronisation."""
         from . import _cabi
 
+        import ctypes as C
+
         b = self._sc_step & 1
         self._sc_step += 1
         rotate = ((self.rank + 1) % self.world) * self._sc_rows
-        self.local.forward_scatter(x_local, self._sc_tables[b], self._sc_rows, rotate)
-        dist.all_reduce(self._sc_flag, group=self.group)  # every rank's stores have landed
         if out is None:
             out = torch.empty(self._sc_rows, self.out_size, device=self.local.device)
         stream = int(torch.cuda.current_stream(self.local.device).cuda_stream)
+        if self._sc_codes:
+            self.local.forward_scatter_codes(x_local, self._sc_tables[b], self._sc_fac_tables[b],
+                                             self._sc_rows, rotate)
+            dist.all_reduce(self._sc_flag, group=self.group)  # every rank's stores have landed
+            valid = max(0, min(self._sc_rows, x_local.size(0) - self.rank * self._sc_rows))
+            planes = (C.c_int * self.world)(*self._sc_planes)
+            base = self._sc_mine[b]
+            _cabi.check(_cabi.lib().ab200_sum_code_slots(
+                base, self._sc_code_stride, base + self._sc_code_stride * self.world,
+                self._sc_fac_stride, self.world, planes, self._sc_rows, valid, self.out_size,
+                out.data_ptr(), stream))
+            return out
+        self.local.forward_scatter(x_local, self._sc_tables[b], self._sc_rows, rotate)
+        dist.all_reduce(self._sc_flag, group=self.group)  # every rank's stores have landed
         _cabi.check(_cabi.lib().ab200_sum_slots(self._sc_mine[b], self.world,
                                                 self._sc_rows * self.out_size, out.data_ptr(), stream))
         return out

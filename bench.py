@@ -268,7 +268,7 @@ def run_ours(args):
         # partial sums are pushed to the owners of the row blocks by the MVM kernel itself
         # (peer stores over NVLink), the result stays sharded by rows
         try:
-            arr.enable_scatter(m)
+            arr.enable_scatter(m, codes={"auto": None, "on": True, "off": False}[args.scatter_codes])
             x_local_dev = x[:, c0:c1].contiguous()
         except RuntimeError as exc:  # raised on every rank alike: fall back to the NCCL reduce
             if rank == 0:
@@ -383,10 +383,13 @@ def run_ours(args):
             "data": "synthetic",
             "config": {
                 "workload": "cfg1: 4096x4096 analog inference MVM, 64 tiles of 512x512, batch 8192",
-                "sharding": (f"in-splits over {world} rank(s), partial sums stored by the kernel "
-                             "into the row-block owners' memory over NVLink + barrier + local sum "
-                             "(reduce-scatter; the result stays sharded by rows)") if scatter
-                else f"in-splits over {world} rank(s), NCCL reduce to rank 0",
+                "sharding": (f"in-splits over {world} rank(s), "
+                             + ("signed-byte ADC codes of every in-split"
+                                if getattr(arr, "_sc_codes", False) else "fp32 partial sums")
+                             + " stored by the kernel into the row-block owners' memory over NVLink "
+                             "+ barrier + local sum (reduce-scatter; the result stays sharded by rows)")
+                if scatter else (f"in-splits over {world} rank(s), NCCL reduce to rank 0"
+                                 if world > 1 else "one rank, all 64 tiles"),
                 "l2": "input (134 MB) and output (134 MB) per step exceed the 126 MB L2",
             },
             "clocks": clocks,
@@ -463,6 +466,10 @@ def main():
                     help="rows of the bounded CPU sample (reference arm / cpu_baseline)")
     ap.add_argument("--mvm-path", type=int, default=0, choices=[0, 1, 2, 3],
                     help="kernel selection of the library (ab200_set_mvm_path); 0 = automatic")
+    ap.add_argument("--scatter-codes", default="auto", choices=["auto", "on", "off"],
+                    help="N > 1 with --collective scatter: send the signed-byte ADC codes of every "
+                         "in-split instead of fp32 partial sums (auto: when a rank holds at most "
+                         "three in-splits)")
     ap.add_argument("--collective", default="scatter", choices=["scatter", "reduce"],
                     help="N > 1: 'scatter' = the MVM kernel stores its partial sums into the row-block "
                          "owners' memory (reduce-scatter fused with the compute); 'reduce' = local "

@@ -440,6 +440,27 @@ int ab200_array_forward_scatter(ab200_array *arr, const float *x_local_dev, int 
                                 int rotate_rows, void *stream);
 int ab200_sum_slots(const float *slots_dev, int n_slots, long long elems, float *out_dev,
                     void *stream);
+/* The same with a quarter (or less) of the bytes on the wire, for layers whose ADC codes fit a
+ * signed byte (ab200_array_scatter_codes_supported: noisy inference settings, no bound management,
+ * out-splits that are multiples of 128, no mapping scales / bias on this array): the kernel sends
+ * the integer ADC code of every in-split instead of the fp32 sum over the rank's in-splits.
+ * code_table_dev[owner] points to this rank's slot at the owner: n_in_splits planes of
+ * rows_per_owner x out_size bytes, each plane in blocks of 32 rows x 32 columns (1 KB, row-major,
+ * blocks ordered by row block, then column block); fac_table_dev[owner] to
+ * [n_in_splits][rows_per_owner] floats (the factor of each row and in-split).
+ * ab200_sum_code_slots: the owner's sum out[r][c] = sum over slots q (in order) of
+ * (sum over planes i < n_planes[q] of code * factor), the same association as the fp32 variant;
+ * slot q starts at code_slots_dev + q * code_slot_stride (bytes) and fac_slots_dev + q *
+ * fac_slot_stride (floats); rows_valid <= rows_per_owner rows are written. */
+int ab200_array_scatter_codes_supported(ab200_array *arr);
+int ab200_array_forward_scatter_codes(ab200_array *arr, const float *x_local_dev, int m_batch,
+                                      unsigned char *const *code_table_dev,
+                                      float *const *fac_table_dev, int n_owners,
+                                      int rows_per_owner, int rotate_rows, void *stream);
+int ab200_sum_code_slots(const unsigned char *code_slots_dev, long long code_slot_stride,
+                         const float *fac_slots_dev, long long fac_slot_stride, int n_slots,
+                         const int *n_planes, int rows_per_owner, int rows_valid, int out_size,
+                         float *out_dev, void *stream);
 int ab200_peer_alloc(size_t bytes, int cuda_device, void **dev_ptr, unsigned char handle_out[64]);
 int ab200_peer_open(const unsigned char handle[64], int cuda_device, void **dev_ptr);
 int ab200_peer_close(void *dev_ptr);

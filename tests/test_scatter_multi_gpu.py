@@ -1,5 +1,5 @@
-"""Sharded layer on two GPUs: the reduce-scatter by direct peer stores against the NCCL reduce of
-the same partial sums.  Needs two CUDA devices (skipped otherwise); every wait is a host-launched
+"""Sharded layer on two GPUs: the reduce-scatter by direct peer stores (fp32 partial sums, and the
+signed-byte ADC codes of every in-split) against the NCCL reduce of the same partial sums.  Needs two CUDA devices (skipped otherwise); every wait is a host-launched
 collective, nothing spins on the device."""
 
 import os
@@ -31,7 +31,7 @@ def _worker(rank, world, port, out_path):
     X = rng.normal(0, 1, (m, in_size)).astype(np.float32)
     cfg = H.inference_params(noise=True)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=8)
     ok = True
-    for trial in range(2):
+    for trial in range(3):  # NCCL reference, fp32 partial sums, signed-byte ADC codes
         arr = ShardedTileArray(out_size, in_size, max_tile, max_tile,
                                lambda b, e: T.TileArray(cfg, out_size, in_size, max_tile, max_tile,
                                                         cuda_device=rank, in_split_range=(b, e)))
@@ -42,7 +42,7 @@ def _worker(rank, world, port, out_path):
             full = arr.reduce(arr.local.forward_local(x_local), dst=None)  # NCCL all-reduce
             ref = full.cpu().numpy()
         else:
-            arr.enable_scatter(m)
+            arr.enable_scatter(m, codes=(trial == 2))
             rows = arr.scatter_rows
             for step in range(3):  # several steps: double-buffered slots
                 mine = arr.forward_reduce_scatter(x_local)
@@ -57,7 +57,8 @@ def _worker(rank, world, port, out_path):
                 full2 = arr2.reduce(arr2.local.forward_local(x_local), dst=None)
             want = full2[lo:hi].cpu().numpy()
             got = mine[: hi - lo].cpu().numpy()
-            ok = ok and np.allclose(got, want, rtol=1e-6, atol=1e-6) and not np.array_equal(want, ref[lo:hi])
+            tol = 1e-6 if trial == 1 else 1e-5  # codes: the clip bound sits a hair below the top code
+            ok = ok and np.allclose(got, want, rtol=tol, atol=tol) and not np.array_equal(want, ref[lo:hi])
             arr.disable_scatter()
     with open(f"{out_path}.{rank}", "w") as f:
         f.write("ok" if ok else "mismatch")

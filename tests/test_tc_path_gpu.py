@@ -225,3 +225,53 @@ def test_forward_scatter_to_row_block_owners(path):
     _cabi.check(_cabi.lib().ab200_sum_slots(slots.data_ptr(), 3, 64 * 20, out.data_ptr(), None))
     torch.cuda.synchronize()
     assert torch.allclose(out, slots.sum(0), atol=1e-6)
+
+
+@pytest.mark.parametrize("m", [700, 130])
+def test_forward_scatter_of_adc_codes(path, m):
+    """The codes form of the scatter on one GPU: two local slots stand in for the owners; the
+    kernel writes one signed byte per element and in-split plus the per-row factors, the owner's
+    kernel multiplies and sums. Same call counter => same noise => the plain forward, up to the
+    clip bound being a hair below the integer code at saturation."""
+    import ctypes as C
+
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    rng = np.random.default_rng(4)
+    out_size, in_size, max_tile = 384, 1536, 512  # three in-splits, one out-split of 384
+    W = rng.normal(0, 1 / np.sqrt(in_size), (out_size, in_size)).astype(np.float32)
+    X = torch.from_numpy(rng.normal(0, 1, (m, in_size)).astype(np.float32)).cuda()
+    X[5] = 0.0  # a row without input: factor 0
+    cfg = H.inference_params(noise=True)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=8)
+    rows, planes = 512, 3
+    ref_out = None
+    for rotate in (None, 0, 512):
+        a = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+        a.set_weights(torch.from_numpy(W))
+        if rotate is None:
+            assert a.scatter_codes_supported()
+            ref_out = a.forward_local(X).cpu().numpy()
+            continue
+        codes = [torch.zeros(planes * rows * out_size, dtype=torch.uint8, device="cuda") for _ in range(2)]
+        facs = [torch.zeros(planes * rows, device="cuda") for _ in range(2)]
+        ct = torch.tensor([c.data_ptr() for c in codes], dtype=torch.int64, device="cuda")
+        ft = torch.tensor([f.data_ptr() for f in facs], dtype=torch.int64, device="cuda")
+        a.forward_scatter_codes(X, ct, ft, rows, rotate)
+        outs = []
+        for o in range(2):
+            valid = max(0, min(rows, m - o * rows))
+            out = torch.full((rows, out_size), -7.0, device="cuda")
+            n_planes = (C.c_int * 1)(planes)
+            _cabi.check(_cabi.lib().ab200_sum_code_slots(
+                codes[o].data_ptr(), 0, facs[o].data_ptr(), 0, 1, n_planes, rows, valid, out_size,
+                out.data_ptr(), None))
+            outs.append(out[:valid])
+        torch.cuda.synchronize()
+        got = torch.cat(outs).cpu().numpy()
+        assert got.shape == ref_out.shape
+        assert np.abs(got - ref_out).max() <= 1e-5 * np.abs(ref_out).max()
+        assert (got[5] == 0).all() and np.abs(got).max() > 0
+    # a layer with a ragged out-split is not eligible
+    b = T.TileArray(cfg, 400, in_size, max_tile, max_tile, cuda_device=0)
+    assert not b.scatter_codes_supported()
