@@ -603,6 +603,13 @@ int ab200_peer_alloc(size_t bytes, int cuda_device, void **dev_ptr, unsigned cha
   AB200_CUDA(cudaSetDevice(cuda_device));
   void *p = nullptr;
   AB200_CUDA(cudaMalloc(&p, bytes));
+  // slots of ranks that never write (they own no in-split) and rows beyond the batch are summed
+  // like any others: they must read as zero
+  cudaError_t ez = cudaMemset(p, 0, bytes);
+  if (ez != cudaSuccess) {
+    cudaFree(p);
+    AB200_FATAL("cudaMemset of the peer buffer failed: " << cudaGetErrorString(ez));
+  }
   cudaIpcMemHandle_t h;
   cudaError_t e = cudaIpcGetMemHandle(&h, p);
   if (e != cudaSuccess) {

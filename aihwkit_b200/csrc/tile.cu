@@ -451,6 +451,7 @@ Tile::~Tile() {
     cudaFree(cols_x_);
     cudaFree(cols_d_);
     cudaFree(stage_dev_);
+    cudaFree(acc_block_);
     cudaFreeHost(stage_pinned_);
     if (prev >= 0) {
       cudaSetDevice(prev);
@@ -888,10 +889,32 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
   p.call = fwd_calls_++;
   p.noise_id = noise_id;
   fillMvmScratch(p);
-  if (!accumulate && tcEligible(p)) {
+  AB200_CUDA(cudaMemsetAsync(bm_stats_, 0, 2 * sizeof(int), s));
+  // The bound-management re-run rewrites whole output rows, so a tile that adds to the sum of
+  // the earlier in-splits computes into its own block first and is added afterwards.
+  const bool bm = !f_io_.is_perfect && f_io_.bm != AB200_BM_NONE;
+  const bool via_block = accumulate && bm;
+  if (via_block) {
+    const size_t need = (size_t)m * d_size_;
+    if (need > acc_block_floats_) {
+      AB200_CUDA(cudaStreamSynchronize(s));
+      cudaFree(acc_block_);
+      acc_block_ = nullptr;
+      AB200_CUDA(cudaMalloc(&acc_block_, need * sizeof(float)));
+      acc_block_floats_ = need;
+    }
+    p.out = acc_block_;
+    p.out_ss = d_size_;
+    p.accumulate = 0;
+  }
+  if (!p.accumulate && tcEligible(p)) {
     runTc(p, s);
+    launchBmRerun(p, s);
   } else {
     launchMvm(p, s);
+  }
+  if (via_block) {
+    launchAddBlock(acc_block_, d_size_, y, y_ss, m, d_size_, s);
   }
 }
 

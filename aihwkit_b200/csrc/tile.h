@@ -161,6 +161,9 @@ void launchTransferBuffer(float *buffer_col, float *read_inout, int d_size, floa
                           int forget_buffer, cudaStream_t stream);
 void launchTransposeDX(const float *src, float *dst, int rows, int cols, cudaStream_t stream);
 void launchClipToBounds(float *w, const float4 *par4, long long n, cudaStream_t stream);
+// dst[r * dst_ld + c] += src[r * src_ld + c]
+void launchAddBlock(const float *src, long long src_ld, float *dst, long long dst_ld, int rows,
+                    int cols, cudaStream_t stream);
 
 class TcEngine;
 
@@ -312,6 +315,9 @@ private:
   int32_t idx_max_ = 0;
   float *cols_x_ = nullptr, *cols_d_ = nullptr;
   long long cols_cap_ = 0;
+  // output block of a tile that adds to earlier in-splits under bound management
+  float *acc_block_ = nullptr;
+  size_t acc_block_floats_ = 0;
   // staging for the *_host entry points
   float *stage_dev_ = nullptr;
   float *stage_pinned_ = nullptr;

@@ -837,4 +837,24 @@ void launchClipToBounds(float *w, const float4 *par4, long long n, cudaStream_t 
   AB200_LAUNCH_CHECK();
 }
 
+__global__ void __launch_bounds__(256)
+    addBlockKernel(const float *src, long long src_ld, float *dst, long long dst_ld, int cols,
+                   long long n) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < n) {
+    const long long r = t / cols, c = t - r * cols;
+    dst[r * dst_ld + c] += src[r * src_ld + c];
+  }
+}
+
+void launchAddBlock(const float *src, long long src_ld, float *dst, long long dst_ld, int rows,
+                    int cols, cudaStream_t stream) {
+  const long long n = (long long)rows * cols;
+  if (n <= 0) {
+    return;
+  }
+  addBlockKernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(src, src_ld, dst, dst_ld, cols, n);
+  AB200_LAUNCH_CHECK();
+}
+
 } // namespace ab200

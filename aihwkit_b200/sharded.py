@@ -132,6 +132,13 @@ class ShardedTileArray:
         infos = [None] * self.world
         dist.all_gather_object(infos, mine, group=self.group)
         self._sc_planes = [int(i[0]) for i in infos]
+        if min(self._sc_planes) == 0:
+            # every rank sees the same list, so every rank raises: a rank without tiles would
+            # launch no kernel and never signal its peers, which would wait for it on the GPU
+            empty = [q for q, n in enumerate(self._sc_planes) if n == 0]
+            raise RuntimeError(
+                f"the fused reduce-scatter needs at least one in-split per rank; ranks {empty} of "
+                f"{self.world} own none ({len(self.in_sizes)} in-splits)")
         eligible = all(i[1] for i in infos) and (self._sc_rows % 32 == 0) and self.world <= 16
         if codes is None:
             codes = eligible and max(self._sc_planes) <= 3

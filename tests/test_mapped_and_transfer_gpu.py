@@ -56,6 +56,34 @@ def test_mapped_forward_noise_off(out_size, in_size, max_tile, m):
     assert np.array_equal(y_h.numpy(), y)
 
 
+@pytest.mark.parametrize("m", [40, 256])
+def test_mapped_forward_iterative_bound_management(m):
+    """A 2 x 2 mapped layer with the training IO (iterative bound management) and an output bound
+    small enough that many rows clip in the first round: every tile re-runs its clipped rows on its
+    own before its result joins the sum over the in-splits. 256 rows take the tensor-core kernel
+    per tile, 40 rows the CUDA-core one."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(m)
+    out_size, in_size, max_out, max_in = 512, 640, 256, 320
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+    cfg = p._config(1, 1, H.device("cs", False), seed=3)
+    arr = T.TileArray(cfg, out_size, in_size, max_out, max_in, cuda_device=0)
+    W = rng.uniform(-0.5, 0.5, (out_size, in_size)).astype(np.float32)
+    arr.set_weights(torch.from_numpy(W))
+    W = arr.get_weights().numpy()  # clipped to the device bounds
+    X = rng.uniform(-1, 1, (m, in_size)).astype(np.float32)
+    y = arr.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    y_or, lsb, n_in = _array_oracle(W, X, cfg, max_out, max_in)
+    # the test is only meaningful when the first round clips
+    io = O.IO.from_c(cfg.forward_io)
+    _, _, _, reductions = O.forward(W[:max_out, :max_in], X[:, :max_in], io, return_pre_adc=True)
+    assert (reductions > 1).mean() > 0.2
+    diff = np.abs(y - y_or)
+    assert (diff > 1e-3 * lsb).mean() <= 2e-3 * n_in
+    assert (diff <= 1.001 * lsb * n_in).all()
+
+
 def test_mapped_forward_sharded_partials_add_up():
     """The partial sums of disjoint in-split ranges add up to the full layer (noise off), which
     is what the multi-GPU reduce relies on; with noise on, the full layer and the sum of the

@@ -86,3 +86,40 @@ def test_sharded_partial_sums_reduce_to_full_layer(tmp_path, world):
     port = 29500 + (os.getpid() % 400) + world
     mp.spawn(_worker, args=(world, port, str(out)), nprocs=world, join=True)
     assert out.read_text() == "ok"
+
+
+def _empty_rank_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from aihwkit_b200.sharded import ShardedTileArray
+
+    class _Local:
+        device = torch.device("cpu")
+
+        def scatter_codes_supported(self):
+            return False
+
+    # two in-splits on three ranks: the last rank owns none
+    arr = ShardedTileArray(64, 100, 64, 64, lambda b, e: _Local())
+    msg = "no error"
+    try:
+        arr.enable_scatter(256)
+    except RuntimeError as exc:
+        msg = str(exc)
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write(msg)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_scatter_setup_raises_on_every_rank_when_one_owns_no_in_split(tmp_path):
+    """A rank without tiles would never signal its peers; the set-up refuses on all ranks alike
+    instead of letting the others wait for it."""
+    world = 3
+    port = 29950 + (os.getpid() % 40)
+    mp.spawn(_empty_rank_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    msgs = [(tmp_path / f"rank{r}.txt").read_text() for r in range(world)]
+    assert all("at least one in-split per rank" in m for m in msgs), msgs
+    assert len(set(msgs)) == 1
