@@ -96,6 +96,9 @@ struct TcKernelParams {
   float *const *fac_table;
   int rows_per_owner;
   int rb_rotate; // the sweep over the row blocks starts at this block (staggers the ranks)
+  // row of the whole batch this launch starts at (a batch may be cut into several launches):
+  // the noise counters use the row of the whole batch, so the cut does not change the result
+  int row_base;
   int accumulate, backward;
   IOEff io;
   int *status;
@@ -638,7 +641,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // run with factor 0, columns beyond the chunk are computed and never stored.
         const float sig_codes = live ? sigma * inv_res_out : 0.0f;
         const float fac_codes = live ? fac * io.res_out : 0.0f;
-        const uint64_t ctr = ctr0 + (uint64_t)row * n4h;
+        const uint64_t ctr = ctr0 + (uint64_t)(p.row_base + row) * n4h;
         if (CODES) {
           // The rounded, clipped code stays in the low mantissa bits of (value + 1.5 * 2^23):
           // its low byte is the two's-complement code. Four codes per word, eight words per row.
@@ -717,7 +720,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           if (live) {
             float z[8];
             if (sigma > 0.0f && cbase + c0 < ch.w) {
-              gauss8Keyed(rkeys, ctr0 + (uint64_t)row * n4h + (uint64_t)(c0 >> 3), p.call, tile_tag, z);
+              gauss8Keyed(rkeys, ctr0 + (uint64_t)(p.row_base + row) * n4h + (uint64_t)(c0 >> 3), p.call,
+                          tile_tag, z);
             }
 #pragma unroll
             for (int j = 0; j < 8; j++) {
@@ -873,8 +877,38 @@ struct DacParams {
   float alpha;
   int backward;
   float code_bound; // largest |code| = inp_bound / res_in
+  float inv_res_in; // 1 / res_in: first guess of the DAC code
 };
 
+// rint((x * scale) / res_in), clipped: the reference's DAC in its own association. The division is
+// only carried out where a product with the reciprocal step lands within 1e-4 of a half-integer
+// (only there can the two round to different codes: the product is off by at most 2e-5 at the
+// largest code, the correctly rounded quotient by 4e-6); elsewhere both give the same integer.
+__device__ __forceinline__ float dacCode(const DacParams &p, float x, float scale) {
+  const float v = __fmul_rn(x, scale);
+  const float q = __fmul_rn(v, p.inv_res_in);
+  float code = rintf(q);
+  if (fabsf(__fsub_rn(q, code)) > 0.4999f) {
+    code = rintf(__fdiv_rn(v, p.io.res_in));
+  }
+  return fminf(fmaxf(code, -p.code_bound), p.code_bound);
+}
+__device__ __forceinline__ void dacRowScalars(const DacParams &p, int i, int row, float sval, float scale,
+                                              float sumsq) {
+  const long long si = (long long)i * p.m + row;
+  p.scale[si] = scale;
+  p.factor[si] = outputFactor(p.io, p.alpha, sval, scale, p.backward);
+  p.vnorm[si] = sqrtf(sumsq) * p.io.res_in;
+  if (p.sval) {
+    p.sval[si] = sval;
+  }
+  if (p.flags) {
+    p.flags[si] = 0;
+  }
+}
+
+// any in-split length and alignment: one warp per (row, in-split), two passes over the row (the
+// second one hits L1 / L2)
 __global__ void __launch_bounds__(256) dacQuantizeKernel(DacParams p) {
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -888,6 +922,7 @@ __global__ void __launch_bounds__(256) dacQuantizeKernel(DacParams p) {
   const IOEff &io = p.io;
   float amax = 0.0f;
   if (io.nm == AB200_NM_ABS_MAX) {
+#pragma unroll 8
     for (int k = lane; k < K; k += 32) {
       amax = fmaxf(amax, fabsf(x[k]));
     }
@@ -899,11 +934,11 @@ __global__ void __launch_bounds__(256) dacQuantizeKernel(DacParams p) {
   const float scale = inputScale(io, sval, 1.0f, !p.backward);
   __nv_bfloat16 *c = p.codes + (long long)row * p.codes_ld + is.x;
   float acc = 0.0f;
+#pragma unroll 4
   for (int k = lane; k < p.kpad; k += 32) {
     float code = 0.0f;
     if (k < K && scale != 0.0f) {
-      code = rintf(__fdiv_rn(__fmul_rn(x[k], scale), io.res_in));
-      code = fminf(fmaxf(code, -p.code_bound), p.code_bound);
+      code = dacCode(p, x[k], scale);
     }
     c[k] = __float2bfloat16_rn(code);
     acc = fmaf(code, code, acc);
@@ -912,15 +947,114 @@ __global__ void __launch_bounds__(256) dacQuantizeKernel(DacParams p) {
     acc += __shfl_xor_sync(0xffffffffu, acc, o);
   }
   if (lane == 0) {
-    const long long si = (long long)i * p.m + row;
-    p.scale[si] = scale;
-    p.factor[si] = outputFactor(io, p.alpha, sval, scale, p.backward);
-    p.vnorm[si] = sqrtf(acc) * io.res_in;
-    if (p.sval) {
-      p.sval[si] = sval;
+    dacRowScalars(p, i, row, sval, scale, acc);
+  }
+}
+
+// In-splits of at most 512 inputs whose rows start on 16-byte boundaries: one warp per row; an
+// in-split sits in the registers of the warp (four float4 per lane) and is read once. In-splits go
+// through in pairs: their reductions across the warp are independent chains of shuffles, which
+// overlap.
+struct DacRegs {
+  float4 v[4];
+};
+__device__ __forceinline__ void dacLoadRow(const DacParams &p, int i, int row, int lane, DacRegs &r) {
+  const int4 is = p.insplit[i];
+  const float4 *x = reinterpret_cast<const float4 *>(p.in + (long long)row * p.in_ss + is.w);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int k = 4 * (lane + 32 * j);
+    r.v[j] = k < is.z ? __ldg(x + lane + 32 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+template <int NI>
+__device__ __forceinline__ void dacQuantRows(const DacParams &p, int i0, int row, int lane,
+                                             const DacRegs (&r)[NI]) {
+  const IOEff &io = p.io;
+  float amax[NI];
+#pragma unroll
+  for (int n = 0; n < NI; n++) {
+    amax[n] = 0.0f;
+    if (io.nm == AB200_NM_ABS_MAX) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        amax[n] = fmaxf(fmaxf(amax[n], fmaxf(fabsf(r[n].v[j].x), fabsf(r[n].v[j].y))),
+                        fmaxf(fabsf(r[n].v[j].z), fabsf(r[n].v[j].w)));
+      }
     }
-    if (p.flags) {
-      p.flags[si] = 0;
+  }
+  if (io.nm == AB200_NM_ABS_MAX) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int n = 0; n < NI; n++) {
+        amax[n] = fmaxf(amax[n], __shfl_xor_sync(0xffffffffu, amax[n], o));
+      }
+    }
+  }
+  float sval[NI], scale[NI], acc[NI];
+#pragma unroll
+  for (int n = 0; n < NI; n++) {
+    const int4 is = p.insplit[i0 + n];
+    sval[n] = nmValue(io, amax[n]);
+    scale[n] = inputScale(io, sval[n], 1.0f, !p.backward);
+    __nv_bfloat16 *c = p.codes + (long long)row * p.codes_ld + is.x;
+    acc[n] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int k = 4 * (lane + 32 * j);
+      if (k < p.kpad) {
+        float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
+        if (k < is.z && scale[n] != 0.0f) {
+          c0 = dacCode(p, r[n].v[j].x, scale[n]);
+          c1 = dacCode(p, r[n].v[j].y, scale[n]);
+          c2 = dacCode(p, r[n].v[j].z, scale[n]);
+          c3 = dacCode(p, r[n].v[j].w, scale[n]);
+        }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(c0, c1), hi = __floats2bfloat162_rn(c2, c3);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t *>(&lo);
+        pk.y = *reinterpret_cast<const uint32_t *>(&hi);
+        *reinterpret_cast<uint2 *>(c + k) = pk;
+        acc[n] = fmaf(c0, c0, acc[n]);
+        acc[n] = fmaf(c1, c1, acc[n]);
+        acc[n] = fmaf(c2, c2, acc[n]);
+        acc[n] = fmaf(c3, c3, acc[n]);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+    for (int n = 0; n < NI; n++) {
+      acc[n] += __shfl_xor_sync(0xffffffffu, acc[n], o);
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < NI; n++) {
+    if (lane == n) {
+      dacRowScalars(p, i0 + n, row, sval[n], scale[n], acc[n]);
+    }
+  }
+}
+// Small CTAs with at most 64 registers per thread: one of them fits on an SM beside a CTA of the
+// MMA kernel, several when the kernel runs alone.
+__global__ void __launch_bounds__(128, 8) dacQuantizeRowKernel(DacParams p) {
+  const int row = (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= p.m) {
+    return;
+  }
+  for (int i = 0; i < p.I; i += 2) {
+    if (i + 1 < p.I) {
+      DacRegs r[2];
+      dacLoadRow(p, i, row, lane, r[0]);
+      dacLoadRow(p, i + 1, row, lane, r[1]);
+      dacQuantRows<2>(p, i, row, lane, r);
+    } else {
+      DacRegs r[1];
+      dacLoadRow(p, i, row, lane, r[0]);
+      dacQuantRows<1>(p, i, row, lane, r);
     }
   }
 }
@@ -1057,6 +1191,11 @@ TcEngine::~TcEngine() {
   cudaFree(chunk_tab_);
   cudaFree(insplit_tab_);
   cudaFree(outn_tab_);
+  if (side_) {
+    cudaStreamDestroy(side_);
+    cudaEventDestroy(ev_fork_);
+    cudaEventDestroy(ev_join_);
+  }
   cudaFreeHost(status_host_);
   if (prev >= 0) {
     cudaSetDevice(prev);
@@ -1159,6 +1298,14 @@ void TcEngine::ensureBatch(int m) {
 
 // CTA pairs whenever there are at least two 128-row blocks (and the mode allows it)
 static bool usePairs(int m) { return mvmPath() != 3 && m > TC_M; }
+// diagnostics: AB200_TC_SPLIT=1 cuts large batches into two halves (see TcEngine::run)
+static bool mvmSplit() {
+  static const bool on = [] {
+    const char *e = getenv("AB200_TC_SPLIT");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
 static int pair_rows(int m) { return usePairs(m) ? 2 * TC_M : TC_M; }
 
 void TcEngine::run(const Run &r, cudaStream_t s) {
@@ -1167,38 +1314,122 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
   if (r.m <= 0) {
     return;
   }
-  const int I = (int)in_sizes_.size(), O = (int)out_sizes_.size();
+  const int I = (int)in_sizes_.size();
   if (!ioSupported(r.io)) {
     AB200_FATAL("tensor-core MVM: IO settings not expressible as integer DAC codes");
   }
   ensureBatch(r.m);
-  const bool ext = r.scale != nullptr;
-  if (ext && I != 1) {
+  if (r.scale != nullptr && I != 1) {
     AB200_FATAL("tensor-core MVM: caller-owned scratch needs a single in-split");
   }
+  // Two launches per batch half when the batch is large: the DAC kernel of the second half runs
+  // on a side stream beside the MMA kernel of the first (which leaves registers and threads for
+  // one such CTA per SM), so only the first half's DAC is exposed. Each half keeps several waves
+  // of work items. Runs that scatter to row-block owners stay whole (their sweep order is part of
+  // the protocol between the ranks).
+  const int rows_item = pair_rows(r.m);
+  int n_sm = 0;
+  AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device_));
+  const int workers = usePairs(r.m) ? n_sm / 2 : n_sm;
+  const int half_blocks = (r.m / rows_item) / 2;
+  const bool split = mvmSplit() && r.out_table == nullptr && r.code_table == nullptr && half_blocks > 0 &&
+                     (long long)half_blocks * n_chunks_ >= 4LL * workers;
+  if (!split) {
+    launchDac(r, 0, r.m, s);
+    launchMma(r, 0, r.m, s);
+    return;
+  }
+  if (!side_) {
+    AB200_CUDA(cudaStreamCreateWithFlags(&side_, cudaStreamNonBlocking));
+    AB200_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
+    AB200_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
+  }
+  const int rows_a = half_blocks * rows_item;
+  launchDac(r, 0, rows_a, s);
+  AB200_CUDA(cudaEventRecord(ev_fork_, s)); // the side stream starts after the first half's DAC
+  AB200_CUDA(cudaStreamWaitEvent(side_, ev_fork_, 0));
+  launchDac(r, rows_a, r.m - rows_a, side_);
+  AB200_CUDA(cudaEventRecord(ev_join_, side_));
+  launchMma(r, 0, rows_a, s);
+  AB200_CUDA(cudaStreamWaitEvent(s, ev_join_, 0));
+  launchMma(r, rows_a, r.m - rows_a, s);
+}
+
+// per-row scratch of the rows [row0, row0 + rows): the caller's arrays (single in-split, indexed
+// by row) or a slice of the engine's own, laid out [in-split][row of this part]
+struct TcEngine::PartScratch {
+  float *scale, *factor, *vnorm, *sval;
+  int *flags;
+};
+TcEngine::PartScratch TcEngine::partScratch(const Run &r, int row0) {
+  const size_t I = in_sizes_.size();
+  PartScratch ps;
+  if (r.scale != nullptr) {
+    ps.scale = r.scale + row0;
+    ps.factor = r.factor + row0;
+    ps.vnorm = r.vnorm + row0;
+    ps.sval = r.sval ? r.sval + row0 : nullptr;
+    ps.flags = r.flags ? r.flags + row0 : nullptr;
+  } else {
+    const size_t off = I * (size_t)row0;
+    ps.scale = scale_ + off;
+    ps.factor = factor_ + off;
+    ps.vnorm = vnorm_ + off;
+    ps.sval = sval_ + off;
+    ps.flags = flags_ + off;
+  }
+  return ps;
+}
+
+void TcEngine::launchDac(const Run &r, int row0, int rows, cudaStream_t s) {
+  const int I = (int)in_sizes_.size();
+  const PartScratch ps = partScratch(r, row0);
   DacParams d{};
-  d.in = r.in;
+  d.in = r.in + (long long)row0 * r.in_ss;
   d.in_ss = r.in_ss;
-  d.m = r.m;
+  d.m = rows;
   d.I = I;
   d.kpad = kpad_;
   d.insplit = (const int4 *)insplit_tab_;
-  d.codes = (__nv_bfloat16 *)codes_;
+  d.codes = (__nv_bfloat16 *)codes_ + (size_t)row0 * I * kpad_;
   d.codes_ld = (long long)I * kpad_;
-  d.scale = ext ? r.scale : scale_;
-  d.factor = ext ? r.factor : factor_;
-  d.vnorm = ext ? r.vnorm : vnorm_;
-  d.sval = ext ? r.sval : sval_;
-  d.flags = ext ? r.flags : flags_;
+  d.scale = ps.scale;
+  d.factor = ps.factor;
+  d.vnorm = ps.vnorm;
+  d.sval = ps.sval;
+  d.flags = ps.flags;
   d.io = r.io;
   d.alpha = r.alpha;
   d.backward = r.backward ? 1 : 0;
   d.code_bound = rintf(r.io.inp_bound / r.io.res_in);
-  const long long warps = (long long)r.m * I;
-  dacQuantizeKernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(d);
+  d.inv_res_in = 1.0f / r.io.res_in;
+  bool vec = kpad_ <= 512 && (((uintptr_t)d.in) & 15) == 0 && (r.in_ss & 3) == 0;
+  for (int i = 0; i < I && vec; i++) {
+    vec = (in_off_[i] & 3) == 0 && (in_sizes_[i] & 3) == 0;
+  }
+  if (vec) {
+    dacQuantizeRowKernel<<<(unsigned)(((long long)rows * 32 + 127) / 128), 128, 0, s>>>(d);
+  } else {
+    const long long warps = (long long)rows * I;
+    dacQuantizeKernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(d);
+  }
   AB200_LAUNCH_CHECK();
+}
 
-  CUtensorMap tm_a = makeMap(codes_, (uint64_t)r.m, (uint64_t)I * kpad_, (uint64_t)I * kpad_);
+void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
+  const int I = (int)in_sizes_.size(), O = (int)out_sizes_.size();
+  const PartScratch ps = partScratch(r0, row0);
+  // this part as a run of its own
+  Run r = r0;
+  r.m = rows;
+  r.out = r0.out ? r0.out + (long long)row0 * r0.out_ss : nullptr;
+  void *codes_part = (__nv_bfloat16 *)codes_ + (size_t)row0 * I * kpad_;
+  struct {
+    float *scale, *factor, *vnorm;
+    int *flags;
+  } d{ps.scale, ps.factor, ps.vnorm, ps.flags};
+
+  CUtensorMap tm_a = makeMap(codes_part, (uint64_t)r.m, (uint64_t)I * kpad_, (uint64_t)I * kpad_);
   CUtensorMap tm_bhi = makeMap(op_hi_, (uint64_t)I * nrows_pad_, (uint64_t)kpad_, (uint64_t)kpad_);
   CUtensorMap tm_blo = makeMap(op_lo_, (uint64_t)I * nrows_pad_, (uint64_t)kpad_, (uint64_t)kpad_);
 
@@ -1246,6 +1477,7 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
     }
   }
   p.rows_per_owner = r.rows_per_owner > 0 ? r.rows_per_owner : 1;
+  p.row_base = row0;
   {
     const int rows_item = pair_rows(r.m);
     const int n_rb_items = (r.m + rows_item - 1) / rows_item;

@@ -80,7 +80,12 @@ public:
   int numOut() const { return (int)out_sizes_.size(); }
 
 private:
+  struct PartScratch;
   void ensureBatch(int m);
+  PartScratch partScratch(const Run &r, int row0);
+  // noise management + DAC / MMA kernel for the rows [row0, row0 + rows) of a run
+  void launchDac(const Run &r, int row0, int rows, cudaStream_t s);
+  void launchMma(const Run &r, int row0, int rows, cudaStream_t s);
 
   int device_;
   std::vector<int> in_sizes_, out_sizes_, in_off_, out_off_;
@@ -95,6 +100,9 @@ private:
   int *chunk_tab_ = nullptr;   // int4 per chunk
   int *insplit_tab_ = nullptr; // int4 per in-split
   int *outn_tab_ = nullptr;    // N_o per out-split
+  // side stream on which the DAC kernel of a batch's second half overlaps the MMA kernel of the first
+  cudaStream_t side_ = nullptr;
+  cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
   int *status_host_ = nullptr; // mapped pinned word written by the kernel on failure
   int *status_dev_ = nullptr;
 };

@@ -112,7 +112,7 @@ def test_softbounds_update_conv_tile_stochastic_statistics():
     grad = -(Dm.T @ X)
     # both follow the gradient equally well
     c, co = np.corrcoef(dw.ravel(), grad.ravel())[0, 1], np.corrcoef(dwo.ravel(), grad.ravel())[0, 1]
-    assert c > 0.3 and abs(c - co) < 0.02, (c, co)
+    assert c > 0.1 and abs(c - co) < 0.02, (c, co)
     # mean change per gradient decile and overall spread
     edges = np.quantile(grad, np.linspace(0, 1, 11))
     which = np.clip(np.searchsorted(edges, grad.ravel(), side="right") - 1, 0, 9)
@@ -138,7 +138,7 @@ def test_tiki_taka_benchmark_tile_deterministic():
     m = 256
     p = H.training_params(noise=False, pulse_det=True)
     dp = H.transfer_device(noise=False, det=True, transfer_every=2.0, units_in_mbatch=True,
-                           n_reads=1, transfer_lr=0.01)
+                           n_reads=1, transfer_lr=1.0)
     cfg = p._config(x_size, d_size, dp, seed=9)
     t = T.AnalogTile(cfg, cuda_device=0)
     names = t.get_hidden_parameter_names()
@@ -152,7 +152,7 @@ def test_tiki_taka_benchmark_tile_deterministic():
         orc = O.TransferOracle(t.get_weights().numpy().copy(), fast, slow, cfg.transfer,
                                O.Up.from_c(cfg.update), dp._vec_par[0].dw_min, dp._vec_par[1].dw_min,
                                x_size, d_size)
-    lr = 0.01
+    lr = 0.05
     t.set_learning_rate(lr)
     if rt is not None:
         rt.set_learning_rate(lr)
