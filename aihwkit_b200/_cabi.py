@@ -152,6 +152,23 @@ class TileConfig(C.Structure):
     ]
 
 
+class ScatterPlan(C.Structure):
+    """``ab200_scatter_plan``."""
+
+    _fields_ = [
+        ("out_table_dev", C.c_void_p),
+        ("code_table_dev", C.c_void_p),
+        ("fac_table_dev", C.c_void_p),
+        ("flag_table_dev", C.c_void_p),
+        ("n_owners", C.c_int32),
+        ("rows_per_owner", C.c_int32),
+        ("rotate_rows", C.c_int32),
+        ("row_base", C.c_int32),
+        ("owner_block_rows", C.c_int32),
+        ("epoch", C.c_int32),
+    ]
+
+
 _lib: Optional[C.CDLL] = None
 
 _VP = C.c_void_p
@@ -219,6 +236,11 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_array_forward_scatter_codes": (_I, [_VP, _FP, _I, _VP, _VP, _I, _I, _I, _VP]),
         "ab200_sum_code_slots": (_I, [_VP, C.c_longlong, _VP, C.c_longlong, _I, C.POINTER(_I), _I, _I, _I,
                                       _FP, _VP]),
+        "ab200_array_forward_scatter_plan": (_I, [_VP, _FP, _I, C.POINTER(ScatterPlan), _VP]),
+        "ab200_sum_slots_wait": (_I, [_FP, _I, C.c_longlong, _I, _I, _I, _FP, _VP, _I, _I, C.c_float, _VP]),
+        "ab200_sum_code_slots_wait": (_I, [_VP, C.c_longlong, _VP, C.c_longlong, _I, C.POINTER(_I), _I, _I,
+                                           _I, _I, _FP, _VP, _I, _I, C.c_float, _VP]),
+        "ab200_wait_status": (_I, [_I, C.POINTER(_I)]),
         "ab200_peer_alloc": (_I, [C.c_size_t, _I, C.POINTER(_VP), C.c_char_p]),
         "ab200_peer_open": (_I, [C.c_char_p, _I, C.POINTER(_VP)]),
         "ab200_peer_close": (_I, [_VP]),
@@ -239,6 +261,7 @@ def _declare(lib: C.CDLL) -> None:
             _I, [C.POINTER(IOParams), _FP, _I, _I, _FP, _FP, _I, C.c_uint64, C.c_uint32, _VP]
         ),
         "ab200_set_mvm_path": (_I, [_I]),
+        "ab200_measure_popc_peak": (_I, [_I, C.POINTER(C.c_double)]),
         "ab200_kernel_launch_count": (C.c_uint64, []),
     }
     for name, (res, args) in sig.items():

@@ -83,29 +83,54 @@ def build(config: int):
     raise SystemExit("config must be 0, 2 or 3")
 
 
-def main(argv=None, on_line=None):
-    """``on_line(line, cfg, x, d, lr)``, when given, may extend the JSON line before it is printed
-    (``bench.py --config N`` adds the CPU baseline of the compiled reference there)."""
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, default=0)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--batch", type=int, default=0, help="override the batch size")
-    ap.add_argument("--indexed", action="store_true", help="config 3 through the indexed interface")
-    args = ap.parse_args(argv)
+def _bf16_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path, "r", encoding="utf-8") as f:
+            return json.load(f)["bf16_tflops"], "measured"
+    return 1590.0, "fallback"
+
+
+def launch_floor_us(lib, n: int = 300) -> float:
+    """Time per launch of a chain of dependent, near-empty kernels of the library on the current
+    stream: the floor a phase made of L launches cannot go below (L times this)."""
+    import torch
+
+    a = torch.zeros(2, 4, device="cuda")
+    o = torch.zeros(4, device="cuda")
+    for _ in range(20):
+        lib.ab200_sum_slots(a.data_ptr(), 2, 4, o.data_ptr(), None)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(n):
+        lib.ab200_sum_slots(a.data_ptr(), 2, 4, o.data_ptr(), None)
+    e1.record()
+    torch.cuda.synchronize()
+    return 1e3 * e0.elapsed_time(e1) / n
+
+
+def run(config: int, steps: int = 20, warmup: int = 3, batch: int = 0, indexed: bool = False,
+        on_line=None) -> dict:
+    """One benchmark line (a dict) for configuration 0, 2 or 3.  ``on_line(line, cfg, x, d, lr)``,
+    when given, may extend it (``bench.py --config N`` adds the CPU baseline of the compiled
+    reference there)."""
+    import ctypes as C
 
     import torch
 
+    from . import _cabi
     from .rpu_base import tiles as T
 
     if not torch.cuda.is_available():
         raise RuntimeError("needs a CUDA device: the analog tile has no CPU path")
-    p, dp, w = build(args.config)
+    lib = _cabi.lib()
+    p, dp, w = build(config)
     x_size, d_size = w["x"], w["d"]
-    m = args.batch or w["m"]
-    cfg = p._config(x_size, d_size, dp, seed=100 + args.config)
+    m = batch or w["m"]
+    cfg = p._config(x_size, d_size, dp, seed=100 + config)
     tile = T.AnalogTile(cfg, cuda_device=0)
-    g = torch.Generator().manual_seed(args.config)
+    g = torch.Generator().manual_seed(config)
     if w["winit"] == "uniform":
         tile.set_weights(torch.rand(d_size, x_size, generator=g) - 0.5)
     tile.set_learning_rate(w["lr"])
@@ -118,8 +143,8 @@ def main(argv=None, on_line=None):
     fwd = lambda: tile.forward(x, non_blocking=True)  # noqa: E731
     bwd = lambda: tile.backward(d, non_blocking=True)  # noqa: E731
     upd = lambda: tile.update(x, d, non_blocking=True)  # noqa: E731
-    if args.indexed:
-        if args.config != 3:
+    if indexed:
+        if config != 3:
             raise SystemExit("--indexed applies to config 3")
         c, hw = 256, 32
         n_img = m // (hw * hw)
@@ -138,15 +163,22 @@ def main(argv=None, on_line=None):
     def ev():
         return torch.cuda.Event(enable_timing=True)
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         fwd()
         bwd()
         upd()
     torch.cuda.synchronize()
+    # launches per phase (the library counts its own)
+    launches = []
+    for fn in (fwd, bwd, upd):
+        n0 = lib.ab200_kernel_launch_count()
+        fn()
+        launches.append(int(lib.ab200_kernel_launch_count() - n0))
+    torch.cuda.synchronize()
     t_f = t_b = t_u = 0.0
     e = [ev() for _ in range(4)]
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         e[0].record()
         fwd()
         e[1].record()
@@ -159,30 +191,77 @@ def main(argv=None, on_line=None):
         t_b += e[1].elapsed_time(e[2])
         t_u += e[2].elapsed_time(e[3])
     wall = time.perf_counter() - t0
-    k = args.steps
+    # the same step without a host synchronisation between steps: what a training loop sees
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(steps):
+        fwd()
+        bwd()
+        upd()
+    e1.record()
+    torch.cuda.synchronize()
+    stream_ms = e0.elapsed_time(e1) / steps
+    k = steps
     t_f, t_b, t_u = t_f / k, t_b / k, t_u / k
     step_ms = t_f + t_b + t_u
     hbm, src = _peaks()
+    bf16, bf16_src = _bf16_peak()
+    floor_us = launch_floor_us(lib)
     upd_bytes = x_size * d_size * (8 + w["par_bytes"]) + 4 * m * (x_size + d_size)
+    mvm_bytes = 4 * m * (x_size + d_size) + 4 * x_size * d_size
     flops = 2.0 * m * x_size * d_size
+    pairs = float(x_size) * d_size * m
+    popc = C.c_double(0.0)
+    _cabi.check(lib.ab200_measure_popc_peak(0, C.byref(popc)))
+
+    def mvm_roofline(t_ms, n_launch):
+        tf = flops / (t_ms * 1e-3) / 1e12
+        gbs = mvm_bytes / (t_ms * 1e-3) / 1e9
+        # whichever ceiling is nearer bounds the pass: the split-bf16 tensor rate or the HBM copy rate
+        t_tensor = flops / (bf16 / 2 * 1e12)
+        t_hbm = mvm_bytes / (hbm * 1e9)
+        bound = "tensor" if t_tensor >= t_hbm else "hbm"
+        return {"bound": bound, "logical_tflops": tf, "tensor_peak": bf16, "terms": 2,
+                "frac_of_split_bf16_peak": tf / (bf16 / 2), "algorithmic_gbs": gbs,
+                "frac_of_hbm": gbs / hbm, "launches": n_launch,
+                "launch_floor_ms": n_launch * floor_us * 1e-3,
+                "frac_of_time_above_launch_floor": max(0.0, 1.0 - n_launch * floor_us * 1e-3 / t_ms)}
+
     line = {
         "metric": "analog_tile_fwd_bwd_update_columns_per_s",
-        "config": args.config, "indexed": bool(args.indexed), "x_size": x_size, "d_size": d_size, "batch": m,
-        "value": m / (step_ms * 1e-3), "unit": "columns/s",
-        "ms": {"forward": t_f, "backward": t_b, "update": t_u, "step": step_ms,
-               "wall_per_step": 1e3 * wall / k},
-        "forward_tflops": flops / (t_f * 1e-3) / 1e12,
-        "backward_tflops": flops / (t_b * 1e-3) / 1e12,
+        "config": config, "indexed": bool(indexed), "x_size": x_size, "d_size": d_size, "batch": m,
+        "value": m / (stream_ms * 1e-3), "unit": "columns/s",
+        "ms": {"forward": t_f, "backward": t_b, "update": t_u, "step_sum_of_phases": step_ms,
+               "step_back_to_back": stream_ms, "wall_per_step": 1e3 * wall / k},
+        "launch_floor_us_per_launch": floor_us,
+        "forward_roofline": mvm_roofline(t_f, launches[0]),
+        "backward_roofline": mvm_roofline(t_b, launches[1]),
         "update_roofline": {
-            "bound": "hbm", "algorithmic_bytes": upd_bytes,
+            "bound": "integer" if pairs / (popc.value or 1.0) > upd_bytes / (hbm * 1e9) else "hbm",
+            "algorithmic_bytes": upd_bytes,
             "achieved": upd_bytes / (t_u * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
             "frac": upd_bytes / (t_u * 1e-3) / 1e9 / hbm, "peak_source": src,
-            "coincidence_pairs_per_s": float(x_size) * d_size * m / (t_u * 1e-3),
+            "coincidence_pairs_per_s": pairs / (t_u * 1e-3),
+            "popc_pairs_per_s_peak": popc.value,
+            "frac_of_popc_peak": pairs / (t_u * 1e-3) / (popc.value or 1.0),
+            "launches": launches[2], "launch_floor_ms": launches[2] * floor_us * 1e-3,
         },
+        "peak_sources": {"hbm": src, "bf16": bf16_src},
     }
     if on_line is not None:
         on_line(line, cfg, x, d, w["lr"])
-    print(json.dumps(line))
+    return line
+
+
+def main(argv=None, on_line=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", type=int, default=0)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=0, help="override the batch size")
+    ap.add_argument("--indexed", action="store_true", help="config 3 through the indexed interface")
+    args = ap.parse_args(argv)
+    print(json.dumps(run(args.config, args.steps, args.warmup, args.batch, args.indexed, on_line)))
 
 
 if __name__ == "__main__":

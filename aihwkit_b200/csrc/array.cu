@@ -261,29 +261,12 @@ const float *TileArray::scaledGradient(const float *d, int oi, int m, float fact
 
 void TileArray::forwardScatter(const float *x_local, int m, float *const *out_table_dev,
                                int n_owners, int rows_per_owner, int rotate_rows, cudaStream_t s) {
-  if (m <= 0) {
-    return;
-  }
-  if (in_begin_ == in_end_) {
-    AB200_FATAL("forward_scatter: this shard owns no in-split");
-  }
-  if (!tcEligible(m)) {
-    AB200_FATAL("forward_scatter needs the tensor-core path (batch >= 128, IO settings with integer "
-                "DAC codes, no bound management)");
-  }
-  if (n_owners <= 0 || rows_per_owner <= 0 || (long long)n_owners * rows_per_owner < m) {
-    AB200_FATAL("forward_scatter: the owners' row blocks do not cover the batch");
-  }
-  scatter_table_ = out_table_dev;
-  scatter_rows_ = rows_per_owner;
-  scatter_rotate_ = rotate_rows;
-  try {
-    forwardTc(x_local, localInSize(), nullptr, m, s);
-  } catch (...) {
-    scatter_table_ = nullptr;
-    throw;
-  }
-  scatter_table_ = nullptr;
+  ab200_scatter_plan plan{};
+  plan.out_table_dev = out_table_dev;
+  plan.n_owners = n_owners;
+  plan.rows_per_owner = rows_per_owner;
+  plan.rotate_rows = rotate_rows;
+  forwardScatterPlan(x_local, m, plan, s);
 }
 
 bool TileArray::scatterCodesSupported() {
@@ -301,30 +284,62 @@ bool TileArray::scatterCodesSupported() {
 void TileArray::forwardScatterCodes(const float *x_local, int m, uint8_t *const *code_table_dev,
                                     float *const *fac_table_dev, int n_owners, int rows_per_owner,
                                     int rotate_rows, cudaStream_t s) {
+  ab200_scatter_plan plan{};
+  plan.code_table_dev = code_table_dev;
+  plan.fac_table_dev = fac_table_dev;
+  plan.n_owners = n_owners;
+  plan.rows_per_owner = rows_per_owner;
+  plan.rotate_rows = rotate_rows;
+  forwardScatterPlan(x_local, m, plan, s);
+}
+
+void TileArray::forwardScatterPlan(const float *x_local, int m, const ab200_scatter_plan &plan,
+                                   cudaStream_t s) {
   if (m <= 0) {
     return;
   }
-  if (!scatterCodesSupported() || !tcEligible(m)) {
+  const bool codes = plan.code_table_dev != nullptr;
+  if (in_begin_ == in_end_) {
+    AB200_FATAL("forward_scatter: this shard owns no in-split");
+  }
+  if ((plan.out_table_dev != nullptr) == codes) {
+    AB200_FATAL("forward_scatter: give either the fp32 buffers or the code and factor buffers");
+  }
+  if (!tcEligible(m)) {
+    AB200_FATAL("forward_scatter needs the tensor-core path (batch >= 128, IO settings with integer "
+                "DAC codes, no bound management)");
+  }
+  if (codes && (!scatterCodesSupported() || plan.fac_table_dev == nullptr)) {
     AB200_FATAL("forward_scatter_codes: this array is not eligible (see "
                 "ab200_array_scatter_codes_supported; batch >= 128)");
   }
-  if (n_owners <= 0 || rows_per_owner <= 0 || (rows_per_owner & 31) != 0 ||
-      (long long)n_owners * rows_per_owner < m) {
-    AB200_FATAL("forward_scatter_codes: the owners' row blocks do not cover the batch");
+  if (plan.n_owners <= 0 || plan.rows_per_owner <= 0 || plan.row_base < 0 ||
+      (codes && (plan.rows_per_owner & 31) != 0) || plan.owner_block_rows < 0 ||
+      (plan.owner_block_rows & 31) != 0 || (plan.row_base & 31) != 0) {
+    AB200_FATAL("forward_scatter: invalid owner layout");
   }
-  scatter_codes_ = code_table_dev;
-  scatter_facs_ = fac_table_dev;
-  scatter_rows_ = rows_per_owner;
-  scatter_rotate_ = rotate_rows;
+  // the last row of the launch has to fit into its owner's buffer
+  {
+    const long long last = (long long)plan.row_base + m - 1;
+    long long lrow;
+    if (plan.owner_block_rows > 0) {
+      const long long blk = last / plan.owner_block_rows;
+      lrow = (blk / plan.n_owners) * plan.owner_block_rows + last % plan.owner_block_rows;
+    } else {
+      lrow = last - (long long)(plan.n_owners - 1) * plan.rows_per_owner;
+    }
+    if (lrow >= plan.rows_per_owner) {
+      AB200_FATAL("forward_scatter: the owners' row blocks do not cover the batch");
+    }
+  }
+  plan_ = &plan;
   try {
     forwardTc(x_local, localInSize(), nullptr, m, s);
   } catch (...) {
-    scatter_codes_ = nullptr;
-    scatter_facs_ = nullptr;
+    plan_ = nullptr;
     throw;
   }
-  scatter_codes_ = nullptr;
-  scatter_facs_ = nullptr;
+  plan_ = nullptr;
 }
 
 void TileArray::backward(const float *d, float *x_grad, int m, cudaStream_t s) {
@@ -418,11 +433,18 @@ void TileArray::forwardTc(const float *x0, long long x_ss, float *y, int m, cuda
   r.io = tiles_[0]->fio();
   r.tile_scale = scaled_ ? tile_scale_dev_ : nullptr;
   r.bias = bias_dev_;
-  r.out_table = scatter_table_;
-  r.code_table = scatter_codes_;
-  r.fac_table = scatter_facs_;
-  r.rows_per_owner = scatter_rows_;
-  r.rotate_rows = scatter_rotate_;
+  if (plan_) {
+    r.out_table = plan_->out_table_dev;
+    r.code_table = plan_->code_table_dev;
+    r.fac_table = plan_->fac_table_dev;
+    r.rows_per_owner = plan_->rows_per_owner;
+    r.rotate_rows = plan_->rotate_rows;
+    r.row_base = plan_->row_base;
+    r.n_owners = plan_->n_owners;
+    r.owner_block_rows = plan_->owner_block_rows;
+    r.flag_table = plan_->flag_table_dev;
+    r.epoch = plan_->epoch;
+  }
   tc_->run(r, s);
 }
 

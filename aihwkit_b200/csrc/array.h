@@ -45,6 +45,9 @@ public:
   void forwardScatterCodes(const float *x_local, int m, uint8_t *const *code_table_dev,
                            float *const *fac_table_dev, int n_owners, int rows_per_owner,
                            int rotate_rows, cudaStream_t s);
+  // general form of both (ab200_scatter_plan of the C header): a batch cut into several
+  // launches, rows dealt to the owners in blocks, completion flags for the owners
+  void forwardScatterPlan(const float *x_local, int m, const ab200_scatter_plan &plan, cudaStream_t s);
   // Training of a mapped layer, tile by tile as autograd does in the reference
   // (TileModuleArray modules -> TileWithPeriphery.backward / update, tiles/periphery.py:1068-1110,
   // 1154-1230). backward: x_grad[:, in-split i] = sum over out-splits o of
@@ -71,10 +74,7 @@ private:
   float *tile_scale_dev_ = nullptr;
   bool scaled_ = false;
   float *bias_dev_ = nullptr;
-  float *const *scatter_table_ = nullptr; // set only while forwardScatter runs
-  uint8_t *const *scatter_codes_ = nullptr; // set only while forwardScatterCodes runs
-  float *const *scatter_facs_ = nullptr;
-  int scatter_rows_ = 0, scatter_rotate_ = 0;
+  const ab200_scatter_plan *plan_ = nullptr; // set only while a scatter forward runs
   float *d_scratch_ = nullptr; // [m][largest out-split]: gradients times / over the tile scale
   size_t d_scratch_floats_ = 0;
   const float *scaledGradient(const float *d, int oi, int m, float factor, long long &ld,

@@ -76,6 +76,7 @@ size_t ab200_sizeof(int which) {
   case 2: return sizeof(ab200_device_params);
   case 3: return sizeof(ab200_transfer_params);
   case 4: return sizeof(ab200_tile_config);
+  case 5: return sizeof(ab200_scatter_plan);
   default: return 0;
   }
 }
@@ -462,6 +463,69 @@ int ab200_array_forward_scatter(ab200_array *arr, const float *x_local_dev, int 
 }
 
 namespace {
+// Count of waits that ran out, in page-locked host memory the kernels write through a mapped
+// pointer: one word per device, created on first use.
+constexpr int kMaxWaitDevices = 64;
+int *g_wait_host[kMaxWaitDevices] = {nullptr};
+int *g_wait_dev[kMaxWaitDevices] = {nullptr};
+std::mutex g_wait_mu;
+
+int *waitStatusWord(int dev) {
+  if (dev < 0 || dev >= kMaxWaitDevices) {
+    AB200_FATAL("unsupported device index " << dev);
+  }
+  std::lock_guard<std::mutex> lock(g_wait_mu);
+  if (!g_wait_host[dev]) {
+    AB200_CUDA(cudaHostAlloc(&g_wait_host[dev], sizeof(int), cudaHostAllocMapped));
+    *g_wait_host[dev] = 0;
+    AB200_CUDA(cudaHostGetDevicePointer(&g_wait_dev[dev], g_wait_host[dev], 0));
+  }
+  return g_wait_dev[dev];
+}
+
+// Thread 0 of every CTA waits (bounded) until all flags have reached `epoch`; false = gave up.
+__device__ __forceinline__ bool waitFlags(const int *flags, int n_flags, int epoch,
+                                          long long max_cycles, int *status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const long long t0 = clock64();
+    for (int k = 0; k < n_flags && ok; k++) {
+      unsigned pause = 32;
+      while (true) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + k) : "memory");
+        if (v - epoch >= 0) {
+          break;
+        }
+        if (clock64() - t0 > max_cycles) {
+          ok = 0;
+          break;
+        }
+        __nanosleep(pause);
+        pause = pause < 1024u ? pause * 2u : pause;
+      }
+    }
+    if (!ok && blockIdx.x == 0) {
+      atomicAdd_system(status, 1);
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+long long waitCycles(float max_wait_ms, int dev) {
+  int khz = 0;
+  AB200_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+  if (!(max_wait_ms > 0.0f)) {
+    max_wait_ms = 2000.0f;
+  }
+  return (long long)((double)max_wait_ms * (double)(khz > 0 ? khz : 1500000));
+}
+} // namespace
+
+namespace {
 __global__ void __launch_bounds__(256)
     sumSlotsKernel(const float4 *slots, int n_slots, long long elems4, float4 *out) {
   const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -524,13 +588,23 @@ struct CodeSlots {
   int n_planes[16];
   int rows_per_owner, rows_valid, out_size;
   float *out;
+  // optional: rows [row0, rows_valid) only, after the flags have reached `epoch`
+  int row0;
+  const int *flags;
+  int n_flags, epoch;
+  long long max_cycles;
+  int *status;
 };
+
 // one thread per row and four columns: the word of four codes of every slot and plane, times the
 // row's factor; planes of a slot first (fused multiply-add chain from zero, as the MVM kernel sums
 // its in-splits), then the slots in order (as sumSlotsKernel adds them)
 __global__ void __launch_bounds__(256) codeSlotsKernel(CodeSlots p) {
-  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (p.n_flags > 0 && !waitFlags(p.flags, p.n_flags, p.epoch, p.max_cycles, p.status)) {
+    return;
+  }
   const int w4 = p.out_size >> 2;
+  const long long t = (long long)p.row0 * w4 + blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (t >= (long long)p.rows_valid * w4) {
     return;
   }
@@ -594,6 +668,133 @@ int ab200_sum_code_slots(const unsigned char *code_slots_dev, long long code_slo
   const long long n = (long long)rows_valid * (out_size >> 2);
   codeSlotsKernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p);
   AB200_LAUNCH_CHECK();
+  AB200_CATCH
+}
+
+int ab200_sum_code_slots_wait(const unsigned char *code_slots_dev, long long code_slot_stride,
+                              const float *fac_slots_dev, long long fac_slot_stride, int n_slots,
+                              const int *n_planes, int rows_per_owner, int row0, int rows,
+                              int out_size, float *out_dev, const int32_t *flags_dev, int n_flags,
+                              int epoch, float max_wait_ms, void *stream) {
+  AB200_TRY
+  if (n_slots <= 0 || n_slots > 16 || n_planes == nullptr || rows < 0 || row0 < 0 ||
+      row0 + rows > rows_per_owner || (rows_per_owner & 31) != 0 || (out_size & 31) != 0 ||
+      (((uintptr_t)out_dev) & 15) != 0 || (((uintptr_t)code_slots_dev | (uintptr_t)code_slot_stride) & 3) != 0) {
+    AB200_FATAL("sum_code_slots_wait: 1..16 slots, rows and columns in multiples of 32, aligned buffers");
+  }
+  if (rows == 0) {
+    return 0;
+  }
+  int dev = 0;
+  AB200_CUDA(cudaGetDevice(&dev));
+  CodeSlots p{};
+  p.codes = code_slots_dev;
+  p.code_stride = code_slot_stride;
+  p.facs = fac_slots_dev;
+  p.fac_stride = fac_slot_stride;
+  p.n_slots = n_slots;
+  for (int q = 0; q < n_slots; q++) {
+    p.n_planes[q] = n_planes[q];
+  }
+  p.rows_per_owner = rows_per_owner;
+  p.row0 = row0;
+  p.rows_valid = row0 + rows;
+  p.out_size = out_size;
+  p.out = out_dev;
+  p.flags = flags_dev;
+  p.n_flags = flags_dev ? n_flags : 0;
+  p.epoch = epoch;
+  p.max_cycles = waitCycles(max_wait_ms, dev);
+  p.status = waitStatusWord(dev);
+  const long long n = (long long)rows * (out_size >> 2);
+  codeSlotsKernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p);
+  AB200_LAUNCH_CHECK();
+  AB200_CATCH
+}
+
+int ab200_array_forward_scatter_plan(ab200_array *arr, const float *x_local_dev, int m_batch,
+                                     const ab200_scatter_plan *plan, void *stream) {
+  AB200_TRY
+  if (!plan) {
+    AB200_FATAL("forward_scatter: null plan");
+  }
+  A(arr)->forwardScatterPlan(x_local_dev, m_batch, *plan, (cudaStream_t)stream);
+  AB200_CATCH
+}
+
+namespace {
+__global__ void __launch_bounds__(256)
+    sumSlotsWaitKernel(const float4 *slots, int n_slots, long long stride4, long long e0, long long e1,
+                       float4 *out, const int *flags, int n_flags, int epoch, long long max_cycles,
+                       int *status) {
+  if (n_flags > 0 && !waitFlags(flags, n_flags, epoch, max_cycles, status)) {
+    return;
+  }
+  const long long t = e0 + blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= e1) {
+    return;
+  }
+  float4 acc = slots[t];
+  for (int k = 1; k < n_slots; k++) {
+    const float4 v = slots[(long long)k * stride4 + t];
+    acc.x += v.x;
+    acc.y += v.y;
+    acc.z += v.z;
+    acc.w += v.w;
+  }
+  out[t] = acc;
+}
+
+} // namespace
+
+int ab200_sum_slots_wait(const float *slots_dev, int n_slots, long long slot_stride, int row0,
+                         int rows, int out_size, float *out_dev, const int32_t *flags_dev,
+                         int n_flags, int epoch, float max_wait_ms, void *stream) {
+  AB200_TRY
+  if (n_slots <= 0 || rows < 0 || row0 < 0 || out_size <= 0) {
+    AB200_FATAL("sum_slots_wait: invalid sizes");
+  }
+  if ((out_size & 3) != 0 || (slot_stride & 3) != 0 ||
+      (((uintptr_t)slots_dev | (uintptr_t)out_dev) & 15) != 0) {
+    AB200_FATAL("sum_slots_wait: sizes must be multiples of 4 floats and the buffers 16-byte aligned");
+  }
+  if (rows == 0) {
+    return 0;
+  }
+  int dev = 0;
+  AB200_CUDA(cudaGetDevice(&dev));
+  int *status = waitStatusWord(dev);
+  const long long e0 = (long long)row0 * out_size / 4, e1 = (long long)(row0 + rows) * out_size / 4;
+  sumSlotsWaitKernel<<<(unsigned)((e1 - e0 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const float4 *)slots_dev, n_slots, slot_stride / 4, e0, e1, (float4 *)out_dev, flags_dev,
+      flags_dev ? n_flags : 0, epoch, waitCycles(max_wait_ms, dev), status);
+  AB200_LAUNCH_CHECK();
+  AB200_CATCH
+}
+
+int ab200_measure_popc_peak(int cuda_device, double *pairs_per_s) {
+  AB200_TRY
+  if (!pairs_per_s) {
+    AB200_FATAL("measure_popc_peak: null pointer");
+  }
+  AB200_CUDA(cudaSetDevice(cuda_device));
+  *pairs_per_s = ab200::measurePopcPeak(nullptr);
+  AB200_CATCH
+}
+
+int ab200_wait_status(int cuda_device, int *timed_out) {
+  AB200_TRY
+  if (!timed_out) {
+    AB200_FATAL("wait_status: null pointer");
+  }
+  *timed_out = 0;
+  if (cuda_device >= 0 && cuda_device < kMaxWaitDevices) {
+    std::lock_guard<std::mutex> lock(g_wait_mu);
+    if (g_wait_host[cuda_device]) {
+      *timed_out = *(volatile int *)g_wait_host[cuda_device];
+      *(volatile int *)g_wait_host[cuda_device] = 0;
+    }
+  }
   AB200_CATCH
 }
 

@@ -97,8 +97,19 @@ struct TcKernelParams {
   int rows_per_owner;
   int rb_rotate; // the sweep over the row blocks starts at this block (staggers the ranks)
   // row of the whole batch this launch starts at (a batch may be cut into several launches):
-  // the noise counters use the row of the whole batch, so the cut does not change the result
+  // the noise counters and the owner of a scattered row use the row of the whole batch, so the
+  // cut does not change the result
   int row_base;
+  // scatter: number of owners; owner_blk > 0 deals blocks of that many rows to the owners in
+  // turn (block b of the batch is block b / n_owners of owner b % n_owners) instead of giving
+  // owner q the rows [q * rows_per_owner, (q + 1) * rows_per_owner)
+  int n_owners, owner_blk;
+  // optional completion signal of a scatter launch: the last CTA to finish writes `epoch` to
+  // flag_table[q] for every owner q (system scope, after every CTA's stores); done_ctr counts
+  // the finished CTAs of the launch and is left at zero
+  int *const *flag_table;
+  int *done_ctr;
+  int epoch;
   int accumulate, backward;
   IOEff io;
   int *status;
@@ -291,6 +302,19 @@ constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) |
 constexpr uint32_t kIdescPair = (1u << 4) | (1u << 7) | (1u << 10) |
                                 ((uint32_t)(TC_ACC_COLS >> 3) << 17) |
                                 ((uint32_t)((2 * TC_M) >> 4) << 24);
+
+// owner and row inside the owner's buffer of the 32-row group that starts at row `grow0` of the
+// whole batch (a group never straddles two owners)
+__device__ __forceinline__ void ownerOf(const TcKernelParams &p, int grow0, int &owner, int &lrow0) {
+  if (p.owner_blk > 0) {
+    const int blk = grow0 / p.owner_blk;
+    owner = blk % p.n_owners;
+    lrow0 = (blk / p.n_owners) * p.owner_blk + (grow0 - blk * p.owner_blk);
+  } else {
+    owner = grow0 / p.rows_per_owner;
+    lrow0 = grow0 - owner * p.rows_per_owner;
+  }
+}
 
 #define TC_TIMED_WAIT(acc, expr)                                                                   \
   ([&]() {                                                                                         \
@@ -671,8 +695,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           // exchange, every store instruction writes 512 contiguous bytes (rows 0-15, then 16-31)
           const int row0 = rb * ROWS + rank * TC_M + q * 32;
           if (row0 < p.m) {
-            const int owner = row0 / p.rows_per_owner;
-            const int lrow0 = row0 - owner * p.rows_per_owner;
+            int owner, lrow0;
+            ownerOf(p, p.row_base + row0, owner, lrow0);
             const long long n_total = p.out_ss; // columns of the whole layer
             const long long blk = (long long)(lrow0 >> 5) * (n_total >> 5) + ((ch.z + cbase) >> 5);
             uint8_t *dst = p.code_table[owner] + (long long)i * p.rows_per_owner * n_total + blk * 1024;
@@ -689,8 +713,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
               *reinterpret_cast<uint4 *>(dst + h * 512 + lane * 16) = make_uint4(v[0], v[1], v[2], v[3]);
             }
             if (ch.z == 0 && cbase == 0 && row_ok) {
-              p.fac_table[owner][(long long)i * p.rows_per_owner + (row - owner * p.rows_per_owner)] =
-                  fac_codes;
+              p.fac_table[owner][(long long)i * p.rows_per_owner + lrow0 + (row - row0)] = fac_codes;
             }
           }
         } else {
@@ -787,9 +810,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       const int row0 = rb * ROWS + rank * TC_M + q * 32;
       if (col < ch.w && row0 < p.m) {
         const float b = p.bias ? p.bias[ch.z + col] : 0.0f;
-        const int owner = row0 / p.rows_per_owner; // 32-row groups never straddle two owners
-        float *o = p.out_table[owner] + (long long)(row0 - owner * p.rows_per_owner) * p.out_ss +
-                   ch.z + col;
+        int owner, lrow0;
+        ownerOf(p, p.row_base + row0, owner, lrow0);
+        float *o = p.out_table[owner] + (long long)lrow0 * p.out_ss + ch.z + col;
 #pragma unroll
         for (int r = 0; r < 32; r++) {
           if (row0 + r < p.m) {
@@ -834,8 +857,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   }
 
   // teardown: everyone meets here, also after a time-out
+  if (p.flag_table != nullptr) {
+    __threadfence_system(); // this thread's stores, peer memory included, before the signal
+  }
   tcFenceBefore();
   __syncthreads();
+  if (p.flag_table != nullptr && threadIdx.x == 0 && *abort_flag == 0) {
+    __threadfence();
+    const int finished = atomicAdd(p.done_ctr, 1);
+    if (finished == (int)gridDim.x - 1) {
+      // every CTA of this launch has passed its fence: tell the owners
+      atomicExch(p.done_ctr, 0);
+      __threadfence_system();
+      for (int q = 0; q < p.n_owners; q++) {
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flag_table[q]), "r"(p.epoch) : "memory");
+      }
+    }
+  }
   if (*abort_flag != 0 && threadIdx.x == 0) {
     // give copies that are still in flight time to land before the shared memory is released
     const long long t0 = clock64();
@@ -1191,6 +1229,7 @@ TcEngine::~TcEngine() {
   cudaFree(chunk_tab_);
   cudaFree(insplit_tab_);
   cudaFree(outn_tab_);
+  cudaFree(done_ctr_);
   if (side_) {
     cudaStreamDestroy(side_);
     cudaEventDestroy(ev_fork_);
@@ -1477,7 +1516,21 @@ void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
     }
   }
   p.rows_per_owner = r.rows_per_owner > 0 ? r.rows_per_owner : 1;
-  p.row_base = row0;
+  p.row_base = row0 + r.row_base;
+  p.n_owners = r.n_owners > 0 ? r.n_owners : 1;
+  p.owner_blk = r.owner_block_rows;
+  if (r.owner_block_rows < 0 || (r.owner_block_rows & 31) != 0) {
+    AB200_FATAL("tensor-core MVM: owner blocks must be a multiple of 32 rows");
+  }
+  p.flag_table = r.flag_table;
+  p.epoch = r.epoch;
+  if (r.flag_table != nullptr) {
+    if (!done_ctr_) {
+      AB200_CUDA(cudaMalloc(&done_ctr_, sizeof(int)));
+      AB200_CUDA(cudaMemset(done_ctr_, 0, sizeof(int)));
+    }
+    p.done_ctr = done_ctr_;
+  }
   {
     const int rows_item = pair_rows(r.m);
     const int n_rb_items = (r.m + rows_item - 1) / rows_item;

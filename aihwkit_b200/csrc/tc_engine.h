@@ -62,6 +62,16 @@ public:
     float *const *fac_table = nullptr;
     int rows_per_owner = 0;
     int rotate_rows = 0;
+    // scatter of a batch that is cut into several launches, or dealt to the owners in blocks:
+    // row_base = row of the whole batch this launch starts at; owner_block_rows > 0: blocks of
+    // that many rows go to the owners in turn; flag_table (device array, one address per owner,
+    // local or peer memory) receives `epoch` when every store of the launch has been issued and
+    // fenced at system scope
+    int row_base = 0;
+    int n_owners = 0;
+    int owner_block_rows = 0;
+    int *const *flag_table = nullptr;
+    int epoch = 0;
     // optional caller-owned per-row scratch (only valid for I == 1): lets the bound-management
     // re-run kernel see the same noise-management values and flags
     float *scale = nullptr, *factor = nullptr, *vnorm = nullptr, *sval = nullptr;
@@ -97,6 +107,7 @@ private:
   int m_cap_ = 0;
   float *scale_ = nullptr, *factor_ = nullptr, *vnorm_ = nullptr, *sval_ = nullptr;
   int *flags_ = nullptr;
+  int *done_ctr_ = nullptr; // finished CTAs of a scatter launch that signals its completion
   int *chunk_tab_ = nullptr;   // int4 per chunk
   int *insplit_tab_ = nullptr; // int4 per in-split
   int *outn_tab_ = nullptr;    // N_o per out-split

@@ -161,6 +161,8 @@ void launchTransferBuffer(float *buffer_col, float *read_inout, int d_size, floa
                           int forget_buffer, cudaStream_t stream);
 void launchTransposeDX(const float *src, float *dst, int rows, int cols, cudaStream_t stream);
 void launchClipToBounds(float *w, const float4 *par4, long long n, cudaStream_t stream);
+// AND + popc + add triples per second the current device sustains from registers
+double measurePopcPeak(cudaStream_t stream);
 // dst[r * dst_ld + c] += src[r * src_ld + c]
 void launchAddBlock(const float *src, long long src_ld, float *dst, long long dst_ld, int rows,
                     int cols, cudaStream_t stream);

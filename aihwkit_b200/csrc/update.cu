@@ -837,6 +837,53 @@ void launchClipToBounds(float *w, const float4 *par4, long long n, cudaStream_t 
   AB200_LAUNCH_CHECK();
 }
 
+// Throughput of the arithmetic a coincidence costs at the least - one AND, one population count,
+// one add per pair of pulse words - with everything in registers and four independent chains per
+// thread: the integer ceiling the update kernel's pair rate is reported against.
+__global__ void __launch_bounds__(256) popcPeakKernel(uint32_t *sink, int iters) {
+  uint32_t a0 = threadIdx.x * 2654435761u + 1u, a1 = a0 ^ 0x9E3779B9u, a2 = a0 + 0x7F4A7C15u,
+           a3 = a1 * 3u;
+  const uint32_t b = blockIdx.x * 40503u + 0x5bd1e995u;
+  uint32_t c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+  for (int k = 0; k < iters; k++) {
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      c0 += __popc(a0 & (b + c3));
+      c1 += __popc(a1 & (b + c0));
+      c2 += __popc(a2 & (b + c1));
+      c3 += __popc(a3 & (b + c2));
+    }
+  }
+  if (c0 + c1 + c2 + c3 == 0xFFFFFFFFu) {
+    sink[0] = c0; // never true in practice: keeps the loop alive
+  }
+}
+
+double measurePopcPeak(cudaStream_t stream) {
+  int dev = 0, n_sm = 0;
+  AB200_CUDA(cudaGetDevice(&dev));
+  AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  uint32_t *sink = nullptr;
+  AB200_CUDA(cudaMalloc(&sink, sizeof(uint32_t)));
+  cudaEvent_t e0, e1;
+  AB200_CUDA(cudaEventCreate(&e0));
+  AB200_CUDA(cudaEventCreate(&e1));
+  const int iters = 4096, blocks = n_sm * 8;
+  popcPeakKernel<<<blocks, 256, 0, stream>>>(sink, 64); // warm-up
+  AB200_CUDA(cudaEventRecord(e0, stream));
+  popcPeakKernel<<<blocks, 256, 0, stream>>>(sink, iters);
+  AB200_CUDA(cudaEventRecord(e1, stream));
+  AB200_CUDA(cudaEventSynchronize(e1));
+  float ms = 0.0f;
+  AB200_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(sink);
+  AB200_LAUNCH_CHECK();
+  const double pairs = (double)blocks * 256.0 * (double)iters * 32.0;
+  return pairs / ((double)ms * 1e-3);
+}
+
 __global__ void __launch_bounds__(256)
     addBlockKernel(const float *src, long long src_ld, float *dst, long long dst_ld, int cols,
                    long long n) {

@@ -148,14 +148,14 @@ class AnalogGPT2:
         return sum(lin.n_tiles for blk in self.blocks for lin in blk.linears())
 
 
-def main():
+def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
 
     import torch.distributed as dist
 

@@ -585,6 +585,19 @@ class TileArray:
             self._h, x.data_ptr(), x.size(0), out_table.data_ptr(), out_table.numel(),
             int(rows_per_owner), int(rotate_rows), _stream_ptr(x)))
 
+    def forward_scatter_plan(self, x_local: torch.Tensor, plan) -> None:
+        """General scatter forward (``ab200_array_forward_scatter_plan``): ``plan`` is an
+        ``aihwkit_b200._cabi.ScatterPlan`` with the owners' buffer tables, the row of the whole
+        batch this launch starts at, the owner layout (contiguous or dealt in blocks) and the
+        completion flags.  Asynchronous on the current stream."""
+        import ctypes as C
+
+        x = _check_input(x_local, "x_local")
+        if not x.is_cuda or x.dim() != 2 or x.size(1) != self.local_in_size:
+            raise RuntimeError(f"expected a CUDA [m, {self.local_in_size}] tensor")
+        check(self._lib.ab200_array_forward_scatter_plan(self._h, x.data_ptr(), x.size(0),
+                                                         C.byref(plan), _stream_ptr(x)))
+
     def scatter_codes_supported(self) -> bool:
         """Whether :meth:`forward_scatter_codes` can be used: noisy inference settings whose ADC
         codes fit a signed byte, no bound management, out-splits in multiples of 128, no mapping

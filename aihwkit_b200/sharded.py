@@ -105,11 +105,19 @@ class ShardedTileArray:
         return self._ov_partial
 
     # ---- reduce-scatter by direct stores --------------------------------------------------------
-    def enable_scatter(self, m: int, codes: Optional[bool] = None) -> None:
+    ITEM_ROWS = 256  # work-item height of the kernel: ownership changes on item boundaries
+    FLAG_BYTES = 256
+
+    def enable_scatter(self, m: int, codes: Optional[bool] = None, cyclic: bool = False) -> None:
         """Prepare :meth:`forward_reduce_scatter` for batches of ``m`` rows: every rank allocates
-        two sets of ``world`` slots of ``rows x out_size`` floats (double buffering over steps),
-        shares them with the other ranks of the node through CUDA IPC handles, and builds the
-        pointer tables the kernel scatters through.
+        two sets of ``world`` slots of ``rows x out_size`` floats (double buffering over steps)
+        plus one arrival flag per sender, shares them with the other ranks of the node through
+        CUDA IPC handles, and builds the pointer tables the kernel scatters through.
+
+        ``cyclic``: deal the 256-row blocks of the batch to the ranks in turn (block ``b`` is
+        block ``b // world`` of rank ``b % world``) instead of giving rank ``q`` the rows
+        ``[q * rows, (q + 1) * rows)``; every part of a batch then feeds all owners alike, which
+        is what :meth:`forward_reduce_scatter_host` pipelines over.
 
         ``codes``: send the signed-byte ADC code of every in-split (plus one factor per row and
         in-split) instead of the fp32 sum over the rank's in-splits - a quarter of the bytes on
@@ -121,9 +129,14 @@ class ShardedTileArray:
         from . import _cabi
 
         lib = _cabi.lib()
-        item = 256  # work-item height of the kernel: ownership changes on item boundaries
-        per_rank = (m + self.world - 1) // self.world
-        self._sc_rows = (per_rank + item - 1) // item * item
+        item = self.ITEM_ROWS
+        if cyclic:
+            n_blocks = (m + item - 1) // item
+            self._sc_rows = (n_blocks + self.world - 1) // self.world * item
+        else:
+            per_rank = (m + self.world - 1) // self.world
+            self._sc_rows = (per_rank + item - 1) // item * item
+        self._sc_blk = item if cyclic else 0
         self._sc_m = m
         dev_index = self.local.device.index
         slot_floats = self._sc_rows * self.out_size
@@ -149,11 +162,14 @@ class ShardedTileArray:
         self._sc_code_stride = max_planes * self._sc_rows * self.out_size  # bytes per sender slot
         self._sc_fac_stride = max_planes * self._sc_rows                   # floats per sender slot
         if self._sc_codes:
-            alloc_bytes = self.world * (self._sc_code_stride + 4 * self._sc_fac_stride)
+            data_bytes = self.world * (self._sc_code_stride + 4 * self._sc_fac_stride)
         else:
-            alloc_bytes = 4 * slot_floats * self.world
+            data_bytes = 4 * slot_floats * self.world
+        # arrival flags (one int per sender) behind the slots of the first buffer
+        self._sc_flag_off = (data_bytes + 255) // 256 * 256
+        alloc_bytes = self._sc_flag_off + max(self.FLAG_BYTES, 4 * self.world)
         # a rank whose allocation or mapping fails tells the others through the same exchange, so
-        # that every rank raises (and none waits in a collective the failed one never joins)
+        # that every rank raises (and none waits for a rank that gave up)
         handles, self._sc_mine, self._sc_peers, failure = [], [], [], None
         try:
             for _ in range(2):
@@ -166,11 +182,11 @@ class ShardedTileArray:
         gathered = [None] * self.world
         dist.all_gather_object(gathered, failure or handles, group=self.group)
         failure = next((g for g in gathered if isinstance(g, str)), None)
-        self._sc_tables, self._sc_fac_tables = [], []
+        self._sc_tables, self._sc_fac_tables, self._sc_flag_table = [], [], None
         if failure is None:
             try:
                 for b in range(2):
-                    ptrs, fptrs = [], []
+                    ptrs, fptrs, flags = [], [], []
                     for q in range(self.world):
                         if q == self.rank:
                             base = self._sc_mine[b]
@@ -179,6 +195,7 @@ class ShardedTileArray:
                             _cabi.check(lib.ab200_peer_open(gathered[q][b], dev_index, C.byref(p)))
                             self._sc_peers.append(p.value)
                             base = p.value
+                        flags.append(base + self._sc_flag_off + 4 * self.rank)
                         if self._sc_codes:
                             # this rank's code planes and factors at owner q
                             ptrs.append(base + self._sc_code_stride * self.rank)
@@ -190,6 +207,10 @@ class ShardedTileArray:
                     if self._sc_codes:
                         self._sc_fac_tables.append(
                             torch.tensor(fptrs, dtype=torch.int64, device=self.local.device))
+                    if b == 0:
+                        # this rank's arrival flag at every owner (the first buffer holds them)
+                        self._sc_flag_table = torch.tensor(flags, dtype=torch.int64,
+                                                           device=self.local.device)
             except RuntimeError as exc:
                 failure = f"rank {self.rank}: {exc}"
         opened = [None] * self.world
@@ -198,45 +219,162 @@ class ShardedTileArray:
         if failure is not None:
             self.disable_scatter()
             raise RuntimeError(f"peer memory for the fused reduce-scatter is not available ({failure})")
-        self._sc_flag = torch.zeros(1, device=self.local.device)
+        self._sc_flags_local = self._sc_mine[0] + self._sc_flag_off
         self._sc_step = 0
+        self._sc_epoch = 0
+        self._sc_wait_ms = 2000.0
         dist.barrier(group=self.group)
 
-    def forward_reduce_scatter(self, x_local: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Forward of the sharded layer with the sum over the ranks' in-splits done by direct
-        stores: every rank's kernel writes its partial sums into its slot at the owner of each
-        row block (peer memory over NVLink, tile by tile while it computes; the ranks sweep the
-        owners in staggered order), a barrier follows, and every owner adds its ``world`` slots.
-        Returns this rank's rows ``[rows, out_size]`` of the summed output: rank ``q`` owns rows
-        ``[q * rows, (q + 1) * rows)`` with ``rows = self.scatter_rows``; all on the GPU, no host
-        synchronisation."""
-        from . import _cabi
+    def _owned_rows(self, r0: int, rows: int) -> Tuple[int, int]:
+        """Rows of this rank's buffer that the rows ``[r0, r0 + rows)`` of the batch fill:
+        ``(first local row, count)``.  ``r0`` must start a round of the deal when blocks are
+        dealt in turn."""
+        if self._sc_blk == 0:
+            lo = max(r0, self.rank * self._sc_rows)
+            hi = min(r0 + rows, (self.rank + 1) * self._sc_rows)
+            return (max(lo - self.rank * self._sc_rows, 0), max(hi - lo, 0))
+        blk = self._sc_blk
+        if r0 % (blk * self.world) != 0:
+            raise RuntimeError("a part of the batch must start on a multiple of 256 * world rows")
+        count = 0
+        for b in range(r0 // blk, (r0 + rows + blk - 1) // blk):
+            if b % self.world == self.rank:
+                count += min(blk, r0 + rows - b * blk)
+        return (r0 // self.world, count)
 
+    def _check_wait_status(self) -> None:
         import ctypes as C
 
+        from . import _cabi
+
+        n = C.c_int(0)
+        _cabi.check(_cabi.lib().ab200_wait_status(self.local.device.index, C.byref(n)))
+        if n.value:
+            raise RuntimeError(
+                f"reduce-scatter: {n.value} wait(s) for the other ranks' partial sums ran out "
+                f"(rank {self.rank}); a rank is missing or far behind")
+
+    def _scatter_part(self, x_part: torch.Tensor, r0: int, b: int, out: torch.Tensor,
+                      events=None) -> Tuple[int, int]:
+        """One launch of the scatter kernel on the rows ``[r0, r0 + rows)`` of the batch followed
+        by this owner's sum of what all ranks sent for them (which first waits, on the GPU and
+        bounded, for the senders' arrival flags).  Returns the owner's local row range.
+        ``events``: three CUDA events recorded before the scatter, between the two and after the
+        sum (a phase breakdown for benchmarks)."""
+        import ctypes as C
+
+        from . import _cabi
+
+        lib = _cabi.lib()
+        self._sc_epoch += 1
+        plan = _cabi.ScatterPlan()
+        if self._sc_codes:
+            plan.code_table_dev = self._sc_tables[b].data_ptr()
+            plan.fac_table_dev = self._sc_fac_tables[b].data_ptr()
+        else:
+            plan.out_table_dev = self._sc_tables[b].data_ptr()
+        plan.flag_table_dev = self._sc_flag_table.data_ptr()
+        plan.n_owners = self.world
+        plan.rows_per_owner = self._sc_rows
+        # the ranks sweep the owners in staggered order, so that no owner receives from all
+        # ranks at once
+        plan.rotate_rows = (self.rank * self._sc_blk if self._sc_blk
+                            else ((self.rank + 1) % self.world) * self._sc_rows)
+        plan.row_base = r0
+        plan.owner_block_rows = self._sc_blk
+        plan.epoch = self._sc_epoch
+        if events is not None:
+            events[0].record()
+        self.local.forward_scatter_plan(x_part, plan)
+        if events is not None:
+            events[1].record()
+        lr0, n = self._owned_rows(r0, x_part.size(0))
+        stream = int(torch.cuda.current_stream(self.local.device).cuda_stream)
+        base = self._sc_mine[b]
+        if self._sc_codes:
+            planes = (C.c_int * self.world)(*self._sc_planes)
+            _cabi.check(lib.ab200_sum_code_slots_wait(
+                base, self._sc_code_stride, base + self._sc_code_stride * self.world,
+                self._sc_fac_stride, self.world, planes, self._sc_rows, lr0, n, self.out_size,
+                out.data_ptr(), self._sc_flags_local, self.world, self._sc_epoch,
+                self._sc_wait_ms, stream))
+        else:
+            _cabi.check(lib.ab200_sum_slots_wait(
+                base, self.world, self._sc_rows * self.out_size, lr0, n, self.out_size,
+                out.data_ptr(), self._sc_flags_local, self.world, self._sc_epoch,
+                self._sc_wait_ms, stream))
+        if events is not None:
+            events[2].record()
+        return lr0, n
+
+    def forward_reduce_scatter(self, x_local: torch.Tensor, out: Optional[torch.Tensor] = None,
+                               events=None) -> torch.Tensor:
+        """Forward of the sharded layer with the sum over the ranks' in-splits done by direct
+        stores: every rank's kernel writes its partial sums into its slot at the owner of each
+        row block (peer memory over NVLink, tile by tile while it computes) and, once all its
+        stores are out, raises its arrival flag at every owner; every owner's sum kernel waits
+        for the flags of all senders (bounded: a missing rank makes the next call raise) and adds
+        its ``world`` slots.  No collective, no host synchronisation.  Returns this rank's rows
+        ``[rows, out_size]`` of the summed output: rank ``q`` owns rows ``[q * rows, (q + 1) *
+        rows)`` with ``rows = self.scatter_rows`` (or, with ``cyclic`` ownership, the 256-row
+        blocks ``q, q + world, ...`` of the batch, packed)."""
+        self._check_wait_status()
         b = self._sc_step & 1
         self._sc_step += 1
-        rotate = ((self.rank + 1) % self.world) * self._sc_rows
         if out is None:
             out = torch.empty(self._sc_rows, self.out_size, device=self.local.device)
-        stream = int(torch.cuda.current_stream(self.local.device).cuda_stream)
-        if self._sc_codes:
-            self.local.forward_scatter_codes(x_local, self._sc_tables[b], self._sc_fac_tables[b],
-                                             self._sc_rows, rotate)
-            dist.all_reduce(self._sc_flag, group=self.group)  # every rank's stores have landed
-            valid = max(0, min(self._sc_rows, x_local.size(0) - self.rank * self._sc_rows))
-            planes = (C.c_int * self.world)(*self._sc_planes)
-            base = self._sc_mine[b]
-            _cabi.check(_cabi.lib().ab200_sum_code_slots(
-                base, self._sc_code_stride, base + self._sc_code_stride * self.world,
-                self._sc_fac_stride, self.world, planes, self._sc_rows, valid, self.out_size,
-                out.data_ptr(), stream))
-            return out
-        self.local.forward_scatter(x_local, self._sc_tables[b], self._sc_rows, rotate)
-        dist.all_reduce(self._sc_flag, group=self.group)  # every rank's stores have landed
-        _cabi.check(_cabi.lib().ab200_sum_slots(self._sc_mine[b], self.world,
-                                                self._sc_rows * self.out_size, out.data_ptr(), stream))
+        _, n = self._scatter_part(x_local, 0, b, out, events)
+        if n < self._sc_rows:
+            out[n:].zero_()  # rows of the buffer beyond the batch
         return out
+
+    def forward_reduce_scatter_host(self, x_local_host: torch.Tensor, out_rows_host: torch.Tensor,
+                                    chunk_rows: int = 2048) -> torch.Tensor:
+        """The same end to end from and to page-locked host memory, pipelined over parts of the
+        batch (needs ``enable_scatter(..., cyclic=True)``): while part ``c`` is in the kernels,
+        part ``c + 1`` of this rank's input columns is on its way to the device and this rank's
+        rows of part ``c - 1`` are on their way back.  ``x_local_host``: ``[m, local_in_size]``;
+        ``out_rows_host``: ``[scatter_rows, out_size]``, filled with this rank's blocks.  Returns
+        when the result is in host memory."""
+        if not self._sc_blk:
+            raise RuntimeError("forward_reduce_scatter_host needs enable_scatter(m, cyclic=True)")
+        self._check_wait_status()
+        dev = self.local.device
+        m = x_local_host.size(0)
+        round_rows = self._sc_blk * self.world
+        chunk_rows = max(round_rows, chunk_rows // round_rows * round_rows)
+        if getattr(self, "_sh_streams", None) is None:
+            self._sh_streams = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
+            self._sh_x = None
+        if self._sh_x is None or self._sh_x[0].size(0) < chunk_rows:
+            self._sh_x = [torch.empty(chunk_rows, self.local.local_in_size, device=dev) for _ in range(2)]
+            self._sh_out = torch.empty(self._sc_rows, self.out_size, device=dev)
+            self._sh_ev = [[torch.cuda.Event(), torch.cuda.Event()] for _ in range(2)]
+        s_h2d, s_d2h = self._sh_streams
+        main = torch.cuda.current_stream(dev)
+        b = self._sc_step & 1
+        self._sc_step += 1
+        s_h2d.wait_stream(main)
+        for c, r0 in enumerate(range(0, m, chunk_rows)):
+            rows = min(chunk_rows, m - r0)
+            xb = c & 1
+            h2d_done, comp_done = self._sh_ev[xb]
+            with torch.cuda.stream(s_h2d):
+                if c >= 2:
+                    s_h2d.wait_event(comp_done)  # staging buffer xb has been read
+                self._sh_x[xb][:rows].copy_(x_local_host[r0:r0 + rows], non_blocking=True)
+                h2d_done.record(s_h2d)
+            main.wait_event(h2d_done)
+            lr0, n = self._scatter_part(self._sh_x[xb][:rows], r0, b, self._sh_out)
+            comp_done.record(main)
+            if n:
+                s_d2h.wait_event(comp_done)
+                with torch.cuda.stream(s_d2h):
+                    out_rows_host[lr0:lr0 + n].copy_(self._sh_out[lr0:lr0 + n], non_blocking=True)
+        s_d2h.synchronize()
+        main.synchronize()
+        self._check_wait_status()
+        return out_rows_host
 
     @property
     def scatter_rows(self) -> int:

@@ -227,11 +227,50 @@ def run_reference(args):
 # --------------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------------
+def owned_blocks(m: int, rank: int, world: int, blk: int = 256):
+    """(first row of the batch, first row in the owner's buffer, rows) of the 256-row blocks of a
+    batch that are dealt to ``rank``."""
+    out = []
+    for b in range(rank, (m + blk - 1) // blk, world):
+        out.append((b * blk, (b // world) * blk, min(blk, m - b * blk)))
+    return out
+
+
+def other_configurations(args):
+    """Short one-GPU runs of the other benchmark configurations (GPU part only), so that their
+    lines are measured in the same run: 0, 2, 3 = training step of a single tile, 4 = the
+    GPT-2-small-shaped forward."""
+    import io
+    import contextlib
+
+    from aihwkit_b200 import benchmarks, gpt2_inference
+
+    out = {}
+    for c, steps in ((0, 50), (2, 30), (3, 4)):
+        try:
+            line = benchmarks.run(c, steps=steps, warmup=3)
+            out[f"cfg{c}"] = {k: line[k] for k in ("value", "unit", "batch", "ms", "forward_roofline",
+                                                   "backward_roofline", "update_roofline",
+                                                   "launch_floor_us_per_launch")}
+        except Exception as exc:  # a failing side run must not lose the contract line
+            out[f"cfg{c}"] = {"error": str(exc)[:200]}
+    try:
+        buf = io.StringIO()
+        with contextlib.redirect_stdout(buf):
+            gpt2_inference.main(["--steps", "2", "--warmup", "2"])
+        g = json.loads(buf.getvalue().strip().splitlines()[-1])
+        out["cfg4"] = {k: g[k] for k in ("value", "unit", "ms_per_step", "config", "e2e", "analog_layers",
+                                         "gpu_launches")}
+    except Exception as exc:
+        out["cfg4"] = {"error": str(exc)[:200]}
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    from aihwkit_b200 import _cabi
+    from aihwkit_b200 import _cabi, hostmem
     from aihwkit_b200.rpu_base import tiles as T
     from aihwkit_b200.sharded import ShardedTileArray, column_range
 
@@ -244,6 +283,8 @@ def run_ours(args):
         _cabi.check(_cabi.lib().ab200_set_mvm_path(args.mvm_path))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # page-locked staging buffers on the CPU socket this GPU hangs off (before they are allocated)
+    numa_cpus = hostmem.bind_to_gpu_numa(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -264,12 +305,13 @@ def run_ours(args):
 
     scatter = world > 1 and args.collective == "scatter"
     c0, c1 = column_range(W["in_size"], W["max_tile"], rank, world)
+    x_local_dev = x[:, c0:c1].contiguous() if world > 1 else x
     if scatter:
         # partial sums are pushed to the owners of the row blocks by the MVM kernel itself
         # (peer stores over NVLink), the result stays sharded by rows
         try:
-            arr.enable_scatter(m, codes={"auto": None, "on": True, "off": False}[args.scatter_codes])
-            x_local_dev = x[:, c0:c1].contiguous()
+            arr.enable_scatter(m, codes={"auto": None, "on": True, "off": False}[args.scatter_codes],
+                               cyclic=True)
         except RuntimeError as exc:  # raised on every rank alike: fall back to the NCCL reduce
             if rank == 0:
                 print(f"bench: {exc}; using --collective reduce", file=sys.stderr)
@@ -289,6 +331,26 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # ---- the fused data plane against NCCL, same noise (the call counters restart with the seed)
+    check = None
+    if scatter:
+        arr.local.set_seed(4242)
+        mine = arr.forward_reduce_scatter(x_local_dev).clone()
+        arr.local.set_seed(4242)
+        full = arr.local.forward_local(x_local_dev)
+        dist.all_reduce(full)
+        diff = torch.zeros(2, device=dev)
+        for r0, l0, n in owned_blocks(m, rank, world):
+            diff[0] = torch.maximum(diff[0], (mine[l0:l0 + n] - full[r0:r0 + n]).abs().max())
+        diff[1] = full.abs().max()
+        dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+        tol = 2e-5 * float(diff[1])
+        check = {"against": "NCCL all-reduce of the ranks' partial sums, same noise draws",
+                 "max_abs_diff": float(diff[0]), "max_abs_value": float(diff[1]), "tolerance": tol,
+                 "ok": bool(float(diff[0]) <= tol)}
+        arr.local.set_seed(1234)
+        del mine, full
+
     sampler = ClockSampler(local_rank)
     sampler.start()
     sampler.wait_first()
@@ -305,66 +367,83 @@ def run_ours(args):
     barrier()
     ms = ev0.elapsed_time(ev1)
     launches = lib.ab200_kernel_launch_count() - launches0
-    window, scope = (t_wall0, time.time()), "timed region"
-    n_extra = max(args.steps, int(0.15 / max(ms * 1e-3 / args.steps, 1e-6)))
-    extra = torch.tensor([1 if sampler.samples_in(window) < 3 else 0, n_extra], device=dev)
+    window = (t_wall0, time.time())
+
+    # ---- the same load for at least a second, with the clock samples taken inside it
+    n_sus = max(args.steps, int(args.sustain_s / max(ms * 1e-3 / args.steps, 1e-6)))
+    n_sus_t = torch.tensor([n_sus], device=dev)
     if world > 1:
-        dist.all_reduce(extra, op=dist.ReduceOp.MAX)  # every rank takes the same decision
-    if int(extra[0]) != 0:
-        # the timed region held fewer than three samples: keep the same load running
-        # (untimed) for a few periods and report the clocks seen under it
-        n_extra = int(extra[1])
-        t_extra0 = time.time()
-        for _ in range(n_extra):
-            step()
-        barrier()
-        window, scope = (t_extra0, time.time()), "same load continued right after the timed region"
-    clocks = sampler.stop(window, scope)
+        dist.all_reduce(n_sus_t, op=dist.ReduceOp.MAX)  # every rank runs the same count
+    n_sus = int(n_sus_t)
+    barrier()
+    t_sus0 = time.time()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(n_sus):
+        step()
+    s1.record()
+    barrier()
+    sus_ms = s0.elapsed_time(s1)
+    sus_window = (t_sus0, time.time())
+    if sampler.samples_in(window) >= 3:
+        clocks = sampler.stop(window, "timed region")
+        sus_clocks = None
+    else:
+        # the timed region is shorter than a few sampling periods: the clocks are those of the
+        # sustained loop of the same step that followed it
+        clocks = sampler.stop(sus_window, "sustained loop of the same step right after the timed region")
+        sus_clocks = clocks
 
-    # kernel-only time of the local MVM work (no reduce), for the roofline
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k0.record()
-    for _ in range(args.steps):
-        arr.forward_partial(x, is_test=True, non_blocking=True)
-    k1.record()
-    torch.cuda.synchronize()
-    kernel_ms = k0.elapsed_time(k1) / args.steps
-
-    # end to end through the public API with host buffers: this rank's input columns come from
-    # pinned host memory every step, the result goes back to the host on rank 0
-    y_host = torch.empty(m, W["out_size"]).pin_memory() if rank == 0 else None
-    # inputs are scattered over the ranks: each holds its own columns in page-locked host memory
-    x_local_host = x_host[:, c0:c1].contiguous().pin_memory() if world > 1 else x_host
-
+    # ---- phases of the step (N > 1): kernel with its stores / owner's wait + sum
+    phases = None
+    mvm_ms = ms / args.steps
     if scatter:
-        x_stage = torch.empty(m, c1 - c0, device=dev)
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        acc = [0.0, 0.0]
+        for _ in range(args.steps):
+            arr.forward_reduce_scatter(x_local_dev, events=evs)
+            torch.cuda.synchronize()
+            acc[0] += evs[0].elapsed_time(evs[1])
+            acc[1] += evs[1].elapsed_time(evs[2])
+        t = torch.tensor(acc, device=dev) / args.steps
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        phases = {"dac_mvm_and_peer_stores_ms": float(t[0]),
+                  "wait_for_senders_and_owner_sum_ms": float(t[1]),
+                  "note": "max over ranks, one step at a time (host synchronisation between steps)"}
+        mvm_ms = float(t[0])
+
+    # ---- end to end through the public API with host buffers: this rank's input columns come
+    # from page-locked host memory every step, its rows of the result go back to the host
+    x_local_host = x_host[:, c0:c1].contiguous().pin_memory() if world > 1 else x_host
+    if scatter:
         y_rows_host = torch.empty(arr.scatter_rows, W["out_size"]).pin_memory()
 
-    def e2e_step():
-        if scatter:
-            # every rank copies its own input columns in and its own result rows out
-            x_stage.copy_(x_local_host, non_blocking=True)
-            y_rows_host.copy_(arr.forward_reduce_scatter(x_stage), non_blocking=True)
-            return
-        # ShardedTileArray.forward_host: chunked host->device copies overlapped with the kernels
-        # (inside the library for one rank), one reduce, result back to the host on rank 0
-        arr.forward_host(x_local_host, y_host, dst=0)
+        def e2e_step():
+            arr.forward_reduce_scatter_host(x_local_host, y_rows_host, chunk_rows=args.e2e_chunk_rows)
+    else:
+        y_host = torch.empty(m, W["out_size"]).pin_memory() if rank == 0 else None
+
+        def e2e_step():
+            # ShardedTileArray.forward_host: chunked host->device copies overlapped with the
+            # kernels (inside the library for one rank), result back to the host on rank 0
+            arr.forward_host(x_local_host, y_host, dst=0)
 
     for _ in range(max(1, args.warmup // 2)):
         e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = min(args.steps, 50)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(e2e_steps):
         e2e_step()
     e1.record()
     barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     if world > 1:
-        t = torch.tensor([ms, e2e_ms, kernel_ms], device=dev)
+        t = torch.tensor([ms, e2e_ms, sus_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms, kernel_ms = (float(v) for v in t.tolist())
+        ms, e2e_ms, sus_ms = (float(v) for v in t.tolist())
         tl = torch.tensor([launches], device=dev, dtype=torch.int64)
         dist.all_reduce(tl)
         launches = int(tl.item())
@@ -373,9 +452,10 @@ def run_ours(args):
         peaks = measured_peaks()
         n_local = arr.n_local_tiles
         flops = 2.0 * m * 512 * 512 * n_local  # algorithmic: one multiply-add per weight per row
-        achieved = flops / (kernel_ms * 1e-3) / 1e12
+        achieved = flops / (mvm_ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops"]
         value = m * args.steps / (ms * 1e-3)
+        pcie = 2.0 * m * W["in_size"] * 4 / world / (e2e_ms * 1e-3) / 1e9  # both directions, per rank
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -386,29 +466,43 @@ def run_ours(args):
                 "sharding": (f"in-splits over {world} rank(s), "
                              + ("signed-byte ADC codes of every in-split"
                                 if getattr(arr, "_sc_codes", False) else "fp32 partial sums")
-                             + " stored by the kernel into the row-block owners' memory over NVLink "
-                             "+ barrier + local sum (reduce-scatter; the result stays sharded by rows)")
+                             + " stored by the kernel into the row-block owners' memory over NVLink, "
+                             "arrival flags, owner's sum (reduce-scatter, no collective call; the "
+                             "256-row blocks are dealt to the ranks in turn and stay there)")
                 if scatter else (f"in-splits over {world} rank(s), NCCL reduce to rank 0"
                                  if world > 1 else "one rank, all 64 tiles"),
                 "l2": "input (134 MB) and output (134 MB) per step exceed the 126 MB L2",
+                "host_numa_cpus": numa_cpus,
             },
             "clocks": clocks,
-            "e2e": {"value": m * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+            "e2e": {"value": m / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": int(m * W["in_size"] * 4),  # summed over the ranks
-                    "d2h_bytes_per_step": int(m * W["out_size"] * 4)},
+                    "d2h_bytes_per_step": int(m * W["out_size"] * 4),
+                    "ms_per_step": e2e_ms, "pcie_gbs_per_rank_both_directions": pcie},
             "gpu_launches": int(launches),
+            "sustained": {"value": m * n_sus / (sus_ms * 1e-3), "unit": UNIT, "steps": n_sus,
+                          "seconds": sus_ms * 1e-3, "ms_per_step": sus_ms / n_sus,
+                          "clocks": sus_clocks if sus_clocks is not None else "see clocks (timed region)"},
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one full-batch launch of the
-                # MVM kernel on one GPU, from the ncu capture summarised under profiles/
-                # (283.5 MB + 121.6 MB); algorithmic bytes of the launch are 335 MB
-                "traffic": 411.0e6 if world == 1 else None,
+                "terms": 2, "frac_of_split_bf16_peak": achieved / (peak / 2),
+                # dram__bytes_read.sum + dram__bytes_write.sum of the step's two kernels on one
+                # GPU (DAC 201 MB + MVM 411 MB), from the ncu captures summarised under profiles/;
+                # algorithmic bytes of the step are 335 MB
+                "traffic": 612.0e6 if world == 1 else None,
                 "peak_source": f"bf16_tflops (burst), {peaks['source']}",
-                "kernel": "IO-managed MVM of this rank's tiles",
-                "kernel_ms_per_step": kernel_ms, "tiles_per_launch_group": n_local,
+                "kernel": ("DAC + IO-managed MVM of this rank's tiles: the timed step itself"
+                           if world == 1 else "DAC + MVM + peer stores phase of the step (max over ranks)"),
+                "kernel_ms_per_step": mvm_ms, "tiles_per_launch_group": n_local,
             },
         }
+        if check is not None:
+            line["check"] = check
+        if phases is not None:
+            line["phases"] = phases
+        if world == 1 and not args.no_other_configs:
+            line["other_configs"] = other_configurations(args)
         if world == 1 and not args.no_cpu_baseline:
             base = cpu_reference_rate(rows=args.ref_rows)
             if base is not None:
@@ -419,6 +513,8 @@ def run_ours(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    if check is not None and not check["ok"]:
+        sys.exit(3)
 
 
 def run_training_config(args):
@@ -478,6 +574,12 @@ def main():
                     help="N > 1: row blocks whose partial-sum reduce overlaps the next block's kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true",
                     help="skip the CPU baseline leg (used for profiler captures)")
+    ap.add_argument("--no-other-configs", action="store_true",
+                    help="N = 1: skip the short runs of configurations 0, 2, 3, 4")
+    ap.add_argument("--sustain-s", type=float, default=1.2,
+                    help="length of the sustained loop of the same step (clock samples inside it)")
+    ap.add_argument("--e2e-chunk-rows", type=int, default=2048,
+                    help="N > 1: rows per part of the pipelined end-to-end path")
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3],
                     help="1 = the mapped inference layer (the contract line); 0, 2, 3 = training "
                          "step of a single tile (aihwkit_b200.benchmarks) with the reference CPU "

@@ -461,6 +461,52 @@ int ab200_sum_code_slots(const unsigned char *code_slots_dev, long long code_slo
                          const float *fac_slots_dev, long long fac_slot_stride, int n_slots,
                          const int *n_planes, int rows_per_owner, int rows_valid, int out_size,
                          float *out_dev, void *stream);
+/* General form of the two scatter calls above, for a batch that is cut into several launches, for
+ * rows dealt to the owners in blocks, and for owners that learn of the arrival from a flag
+ * instead of a barrier over the ranks (no counterpart in the reference):
+ *  - row_base: row of the whole batch this launch starts at (a multiple of 32); noise draws and
+ *    owners are those of the row of the whole batch, so cutting a batch does not change where a
+ *    row goes.
+ *  - owner_block_rows = 0: owner q holds the rows [q * rows_per_owner, (q + 1) * rows_per_owner).
+ *    owner_block_rows = B > 0 (a multiple of 32): block b = row / B of the batch is block
+ *    b / n_owners of owner b % n_owners, so that every part of a batch in row order feeds all
+ *    owners alike. rows_per_owner is the number of rows an owner's buffer holds either way.
+ *  - flag_table_dev (or null): device array of n_owners addresses, local or peer memory; when
+ *    every store of the launch has been issued and fenced at system scope, the kernel writes
+ *    `epoch` to each of them. Epochs of successive launches must increase.
+ * Exactly one of out_table_dev and code_table_dev (+ fac_table_dev) is given.
+ * ab200_sum_slots_wait / ab200_sum_code_slots_wait: the owner's side. The kernel first waits until
+ * all n_flags words at flags_dev (this owner's arrival flags, one per sender) have reached
+ * `epoch` - at most max_wait_ms, then it gives up WITHOUT summing, records the failure, and the
+ * next ab200_wait_status call (after synchronising the stream) reports it - then adds the slots
+ * for the local rows [row0, row0 + rows): out[r][c] = sum over k of slots[k * slot_stride + r *
+ * out_size + c] (slot_stride in floats). The waiting kernel and the kernels that raise the flags
+ * must run on different GPUs (or the flags must already be up): kernels of one GPU do not
+ * necessarily run at the same time.
+ * ab200_wait_status: 0, or the number of waits that ran out since the last call (and clears it). */
+typedef struct ab200_scatter_plan {
+  float *const *out_table_dev;
+  unsigned char *const *code_table_dev;
+  float *const *fac_table_dev;
+  int32_t *const *flag_table_dev;
+  int32_t n_owners;
+  int32_t rows_per_owner;
+  int32_t rotate_rows;
+  int32_t row_base;
+  int32_t owner_block_rows;
+  int32_t epoch;
+} ab200_scatter_plan;
+int ab200_array_forward_scatter_plan(ab200_array *arr, const float *x_local_dev, int m_batch,
+                                     const ab200_scatter_plan *plan, void *stream);
+int ab200_sum_slots_wait(const float *slots_dev, int n_slots, long long slot_stride, int row0,
+                         int rows, int out_size, float *out_dev, const int32_t *flags_dev,
+                         int n_flags, int epoch, float max_wait_ms, void *stream);
+int ab200_sum_code_slots_wait(const unsigned char *code_slots_dev, long long code_slot_stride,
+                              const float *fac_slots_dev, long long fac_slot_stride, int n_slots,
+                              const int *n_planes, int rows_per_owner, int row0, int rows,
+                              int out_size, float *out_dev, const int32_t *flags_dev, int n_flags,
+                              int epoch, float max_wait_ms, void *stream);
+int ab200_wait_status(int cuda_device, int *timed_out);
 int ab200_peer_alloc(size_t bytes, int cuda_device, void **dev_ptr, unsigned char handle_out[64]);
 int ab200_peer_open(const unsigned char handle[64], int cuda_device, void **dev_ptr);
 int ab200_peer_close(void *dev_ptr);
@@ -512,6 +558,10 @@ int ab200_mvm_forward_noalloc(const ab200_io_params *forward_io, const float *w_
  * cores whenever the IO settings allow, 3 = as 2 but never the kernel variant that pairs two
  * CTAs on one 256-row tile. Process-wide; used by tests and benchmarks. */
 int ab200_set_mvm_path(int mode);
+/* Measurement aid (no counterpart in the reference): AND + population count + add triples per
+ * second the device sustains from registers, the integer ceiling that the pair rate of the pulsed
+ * update at large batches (x_size * d_size * m_batch word pairs per call) is compared with. */
+int ab200_measure_popc_peak(int cuda_device, double *pairs_per_s);
 
 /* Number of kernels this library has launched since it was loaded (all tiles, this process). */
 uint64_t ab200_kernel_launch_count(void);

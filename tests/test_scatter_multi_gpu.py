@@ -1,6 +1,8 @@
 """Sharded layer on two GPUs: the reduce-scatter by direct peer stores (fp32 partial sums, and the
-signed-byte ADC codes of every in-split) against the NCCL reduce of the same partial sums.  Needs two CUDA devices (skipped otherwise); every wait is a host-launched
-collective, nothing spins on the device."""
+signed-byte ADC codes of every in-split; rows owned in contiguous ranges or dealt in blocks; on the
+device and pipelined from / to host memory) against the NCCL reduce of the same partial sums.
+Needs two CUDA devices (skipped otherwise).  The owners' sum kernels wait for the senders' arrival
+flags with a bound; the kernels that raise them run on the other GPU."""
 
 import os
 import sys
@@ -59,6 +61,22 @@ def _worker(rank, world, port, out_path):
             got = mine[: hi - lo].cpu().numpy()
             tol = 1e-6 if trial == 1 else 1e-5  # codes: the clip bound sits a hair below the top code
             ok = ok and np.allclose(got, want, rtol=tol, atol=tol) and not np.array_equal(want, ref[lo:hi])
+            arr.disable_scatter()
+            # blocks dealt in turn, end to end from and to page-locked host memory, in parts
+            arr.enable_scatter(m, codes=(trial == 2), cyclic=True)
+            arr.local.set_seed(77)
+            x_host = torch.from_numpy(np.ascontiguousarray(X[:, c0:c1])).pin_memory()
+            y_host = torch.empty(arr.scatter_rows, out_size).pin_memory()
+            arr.forward_reduce_scatter_host(x_host, y_host, chunk_rows=512)
+            arr2.local.set_seed(77)
+            fulls = [arr2.reduce(arr2.local.forward_local(x_local), dst=None) for _ in range(2)]
+            blk = 256
+            for bi in range(rank, (m + blk - 1) // blk, world):
+                part = bi * blk // 512  # the part (and call counter) the block went through with
+                n = min(blk, m - bi * blk)
+                lrow = (bi // world) * blk
+                ok = ok and np.allclose(y_host[lrow:lrow + n].numpy(),
+                                        fulls[part][bi * blk:bi * blk + n].cpu().numpy(), rtol=tol, atol=tol)
             arr.disable_scatter()
     with open(f"{out_path}.{rank}", "w") as f:
         f.write("ok" if ok else "mismatch")

@@ -275,3 +275,106 @@ def test_forward_scatter_of_adc_codes(path, m):
     # a layer with a ragged out-split is not eligible
     b = T.TileArray(cfg, 400, in_size, max_tile, max_tile, cuda_device=0)
     assert not b.scatter_codes_supported()
+
+
+def test_scatter_plan_in_parts_with_blocks_dealt_in_turn_and_arrival_flags(path):
+    """General scatter on one GPU, two local buffers as owners: the batch goes through in two
+    launches (row_base), its 256-row blocks are dealt to the owners in turn, every launch raises
+    the sender's flag at both owners when its stores are out, and the owners' sum kernels look at
+    the flags first (they are up by then: the launches of one stream run one after the other).
+    Whole-batch noise counters: the result equals the plain forward of the whole batch run with
+    the call counter of each part."""
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    lib = _cabi.lib()
+    rng = np.random.default_rng(6)
+    out_size, in_size, max_tile, m = 256, 1024, 512, 1500
+    W = rng.normal(0, 1 / np.sqrt(in_size), (out_size, in_size)).astype(np.float32)
+    X = torch.from_numpy(rng.normal(0, 1, (m, in_size)).astype(np.float32)).cuda()
+    cfg = H.inference_params(noise=True)._config(1, 1, D.IdealResistiveDeviceParameter(), seed=8)
+    n_owners, blk = 2, 256
+    rows_per_owner = 3 * blk  # six blocks of the batch, three per owner
+    parts = [(0, 1024), (1024, m - 1024)]  # each part starts a round of the deal
+    # reference: the whole batch once per part (call counters 0 and 1), rows of the part taken
+    ref = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+    ref.set_weights(torch.from_numpy(W))
+    want = torch.empty(m, out_size, device="cuda")
+    for r0, rows in parts:
+        want[r0:r0 + rows] = ref.forward_local(X)[r0:r0 + rows]
+    a = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+    a.set_weights(torch.from_numpy(W))
+    slots = [torch.full((rows_per_owner, out_size), -7.0, device="cuda") for _ in range(n_owners)]
+    flags = torch.zeros(n_owners, 64, dtype=torch.int32, device="cuda")  # one sender, one line each
+    table = torch.tensor([s.data_ptr() for s in slots], dtype=torch.int64, device="cuda")
+    flag_table = torch.tensor([flags[q].data_ptr() for q in range(n_owners)], dtype=torch.int64, device="cuda")
+    outs = [torch.full((rows_per_owner, out_size), -9.0, device="cuda") for _ in range(n_owners)]
+    for epoch, (r0, rows) in enumerate(parts, start=1):
+        plan = _cabi.ScatterPlan()
+        plan.out_table_dev = table.data_ptr()
+        plan.flag_table_dev = flag_table.data_ptr()
+        plan.n_owners, plan.rows_per_owner, plan.rotate_rows = n_owners, rows_per_owner, 0
+        plan.row_base, plan.owner_block_rows, plan.epoch = r0, blk, epoch
+        a.forward_scatter_plan(X[r0:r0 + rows], plan)
+        for q in range(n_owners):
+            # the owner's rows of this part
+            lr0 = r0 // n_owners
+            n = sum(min(blk, r0 + rows - b * blk) for b in range(r0 // blk, (r0 + rows + blk - 1) // blk)
+                    if b % n_owners == q)
+            _cabi.check(lib.ab200_sum_slots_wait(slots[q].data_ptr(), 1, rows_per_owner * out_size, lr0, n,
+                                                 out_size, outs[q].data_ptr(), flags[q].data_ptr(), 1,
+                                                 epoch, 50.0, None))
+    torch.cuda.synchronize()
+    assert flags[:, 0].tolist() == [2, 2]
+    got = torch.empty(m, out_size, device="cuda")
+    for b in range((m + blk - 1) // blk):
+        n = min(blk, m - b * blk)
+        lrow = (b // n_owners) * blk
+        got[b * blk:b * blk + n] = outs[b % n_owners][lrow:lrow + n]
+    assert torch.equal(got, want)
+    timed_out = C_int()
+    _cabi.check(lib.ab200_wait_status(0, timed_out.ref()))
+    assert timed_out.value == 0
+
+
+class C_int:
+    def __init__(self):
+        import ctypes
+
+        self._c = ctypes.c_int(0)
+
+    def ref(self):
+        import ctypes
+
+        return ctypes.byref(self._c)
+
+    @property
+    def value(self):
+        return self._c.value
+
+
+def test_owner_sum_gives_up_when_a_sender_never_arrives():
+    """A flag nobody raises: the owner's kernel waits its (short) limit, returns without summing
+    and the status call reports the wait that ran out. The device stays usable."""
+    from aihwkit_b200 import _cabi
+
+    lib = _cabi.lib()
+    slots = torch.ones(2, 32, 64, device="cuda")
+    out = torch.full((32, 64), -3.0, device="cuda")
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    flags[0] = 5  # one sender arrived, the other never does
+    n = C_int()
+    _cabi.check(lib.ab200_wait_status(0, n.ref()))  # clear
+    _cabi.check(lib.ab200_sum_slots_wait(slots.data_ptr(), 2, 32 * 64, 0, 32, 64, out.data_ptr(),
+                                         flags.data_ptr(), 2, 5, 20.0, None))
+    torch.cuda.synchronize()
+    _cabi.check(lib.ab200_wait_status(0, n.ref()))
+    assert n.value == 1
+    assert float(out.max()) == -3.0  # nothing was summed
+    # with both flags up the same call goes through
+    flags[1] = 7  # a later epoch counts as arrived
+    _cabi.check(lib.ab200_sum_slots_wait(slots.data_ptr(), 2, 32 * 64, 0, 32, 64, out.data_ptr(),
+                                         flags.data_ptr(), 2, 5, 20.0, None))
+    torch.cuda.synchronize()
+    _cabi.check(lib.ab200_wait_status(0, n.ref()))
+    assert n.value == 0 and torch.equal(out, torch.full((32, 64), 2.0, device="cuda"))
