@@ -197,6 +197,7 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_set_weights_device": (_I, [_VP, _FP, _VP]),
         "ab200_tile_get_weights_device": (_I, [_VP, _FP, _VP]),
         "ab200_tile_set_shared_weights": (_I, [_VP, _FP, C.c_uint64]),
+        "ab200_tile_set_delta_weights": (_I, [_VP, _FP]),
         "ab200_tile_hidden_parameter_count": (_I, [_VP]),
         "ab200_tile_hidden_parameter_name": (C.c_char_p, [_VP, _I]),
         "ab200_tile_get_hidden_parameters": (_I, [_VP, _FP]),

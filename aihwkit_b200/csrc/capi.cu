@@ -219,6 +219,12 @@ int ab200_tile_set_shared_weights(ab200_tile *tile, float *w_dev_xd, uint64_t ve
   AB200_CATCH
 }
 
+int ab200_tile_set_delta_weights(ab200_tile *tile, float *dw_dev_xd) {
+  AB200_TRY
+  T(tile)->setDeltaWeights(dw_dev_xd);
+  AB200_CATCH
+}
+
 int ab200_tile_hidden_parameter_count(const ab200_tile *tile) {
   return tile ? T(tile)->hiddenCount() : 0;
 }
@@ -516,8 +522,15 @@ __device__ __forceinline__ bool waitFlags(const int *flags, int n_flags, int epo
 }
 
 long long waitCycles(float max_wait_ms, int dev) {
-  int khz = 0;
-  AB200_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+  // the clock-rate attribute is a slow driver query (about a millisecond): once per device
+  static int khz_of[kMaxWaitDevices] = {0};
+  int khz = dev >= 0 && dev < kMaxWaitDevices ? khz_of[dev] : 0;
+  if (khz == 0) {
+    AB200_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+    if (dev >= 0 && dev < kMaxWaitDevices) {
+      khz_of[dev] = khz;
+    }
+  }
   if (!(max_wait_ms > 0.0f)) {
     max_wait_ms = 2000.0f;
   }

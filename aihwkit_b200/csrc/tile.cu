@@ -666,6 +666,13 @@ void Tile::setSharedWeights(float *w_dev_xd, uint64_t version) {
   shared_version_ = version;
 }
 
+void Tile::setDeltaWeights(float *dw_dev_xd) {
+  if (dw_dev_xd) {
+    requireDevice("set_delta_weights");
+  }
+  delta_w_ = dw_dev_xd;
+}
+
 // ---------------------------------------------------------------------------------------------
 // hidden parameters: [name][d][x], names as the reference reports them
 // (PulsedRPUDevice::getDPNames rpu_pulsed_device.cpp:235-253; VectorRPUDevice :188-203)
@@ -1129,7 +1136,9 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
     return; // "if (!learning_rate) return" (rpu_weight_updater.cpp:206-208)
   }
   ensureScratch(m);
-  w_version_++;
+  if (!delta_w_) {
+    w_version_++;
+  }
   UpdateProblem u{};
   u.x = x;
   u.x_ss = x_ss;
@@ -1155,12 +1164,21 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
     if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
       AB200_FATAL("Transfer with PulseType::None is not implemented");
     }
+    if (delta_w_) {
+      // delta-weight mode: the gradient itself, +sum d x (bwd_alpha = 1), replaces the buffer
+      u.w = delta_w_;
+      launchFPUpdate(u, -1.0f, s, /*overwrite=*/true);
+      return;
+    }
     u.w = w_;
     launchFPUpdate(u, lr_, s);
     if (up_.pulse_type == AB200_PULSE_NONE_WITH_DEVICE && dev_[0].kind != AB200_DEVICE_IDEAL) {
       launchClipToBounds(w_, dev_[0].par4, (long long)x_size_ * d_size_, s);
     }
     return;
+  }
+  if (delta_w_) {
+    AB200_FATAL("set_delta_weights is implemented for the floating-point update only");
   }
   if (up_.pulse_type == AB200_PULSE_NONE_WITH_DEVICE) {
     u.w = w_;

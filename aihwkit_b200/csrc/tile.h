@@ -151,7 +151,8 @@ struct UpdateProblem {
 void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream);
 void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream);
 void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream);
-void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream);
+void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream,
+                    bool overwrite = false);
 void launchTransferRead(const float *w_fast, int col, int d_size, const IOEff &io, PhiloxKey key,
                         uint32_t call, float *x_onehot, int x_size, float *r_out, float alpha,
                         cudaStream_t stream);
@@ -191,6 +192,10 @@ public:
   void setWeightsDevice(const float *w_dev_xd, cudaStream_t s);
   void getWeightsDevice(float *w_dev_xd, cudaStream_t s);
   void setSharedWeights(float *w_dev_xd, uint64_t version);
+  // RPUSimple::setDeltaWeights (src/rpucuda/rpu.cpp:1459-1481): while set, the floating-point
+  // update writes +sum_s d x / bwd_alpha into this [x][d] buffer and leaves the weights alone
+  // (getAlphaLearningRate :1400-1403, getUpBeta :1509-1511); null = back to normal
+  void setDeltaWeights(float *dw_dev_xd);
 
   int hiddenCount() const;
   const char *hiddenName(int i) const;
@@ -292,6 +297,7 @@ private:
   float *w_ = nullptr;           // device [x][d]
   float *w_owned_ = nullptr;
   uint64_t shared_version_ = 0;
+  float *delta_w_ = nullptr; // caller-owned target of the update in delta-weight mode
   float *w_fast_ = nullptr; // Transfer: fast (hidden) tile A, [x][d]
   float *t_buffer_ = nullptr; // buffered Transfer: digital buffer per element, [x][d]
   DeviceStore dev_[2];

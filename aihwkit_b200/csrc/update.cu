@@ -677,7 +677,8 @@ void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t
 
 // Floating-point update W[x][d] -= lr * sum_s x[s][x] d[s][d] (RPUSimple::updateMatrix,
 // src/rpucuda/rpu.cpp:700-745), used by ideal devices / PulseType::None.
-__global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_signed) {
+// `overwrite`: the target receives -lr * sum alone (delta-weight mode: beta = 0, rpu.cpp:1509-1511)
+__global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_signed, int overwrite) {
   __shared__ float xs[16][16 + 1];
   __shared__ float ds[16][64 + 1];
   const int ti = threadIdx.x & 63, tj = threadIdx.x >> 6; // 64 d-lines x 4 groups of 4 x-lines
@@ -716,15 +717,15 @@ __global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_
       int j = jb + tj * 4 + t;
       if (j < p.x_size) {
         long long idx = (long long)j * p.d_size + i;
-        p.w[idx] = p.w[idx] - lr_signed * acc[t];
+        p.w[idx] = overwrite ? -lr_signed * acc[t] : p.w[idx] - lr_signed * acc[t];
       }
     }
   }
 }
 
-void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream) {
+void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream, bool overwrite) {
   dim3 grid((p.d_size + 63) / 64, (p.x_size + 15) / 16);
-  fpUpdateKernel<<<grid, 256, 0, stream>>>(p, lr_signed);
+  fpUpdateKernel<<<grid, 256, 0, stream>>>(p, lr_signed, overwrite ? 1 : 0);
   AB200_LAUNCH_CHECK();
 }
 

@@ -63,6 +63,7 @@ class AnalogMVType(enum.IntEnum):
 for _e in (NoiseManagementType, BoundManagementType, WeightNoiseType, PulseType):
     # the binding spells the first member "None"; keep that name reachable via getattr
     _e._member_map_["None"] = _e(0)  # type: ignore[attr-defined]
+    type.__setattr__(_e, "None", _e(0))
 
 
 DEVICE_IDEAL = 0
@@ -203,22 +204,14 @@ class AbstractResistiveDeviceParameter:
         raise RuntimeError("Needs implementation.")
 
 
-class WeightClipType(enum.IntEnum):
-    """rpu_base_utils.cpp ``WeightClipType`` (src/rpucuda/weight_clipper.h:14-19)."""
+def __getattr__(name):
+    # WeightClipType / WeightClipParameter belong to the tiles module in the reference's binding
+    # (rpu_base_utils.cpp:18-53); earlier callers of this package found them here
+    if name in ("WeightClipType", "WeightClipParameter"):
+        from . import tiles
 
-    None_ = 0
-    FixedValue = 1
-    LayerGaussian = 2
-    AverageChannelMax = 3
-
-
-class WeightClipParameter:
-    """``WeightClipParameter`` (src/rpucuda/weight_clipper.h:22-27)."""
-
-    def __init__(self) -> None:
-        self.type = WeightClipType.None_
-        self.fixed_value = -1.0
-        self.sigma = 2.5
+        return getattr(tiles, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 
 class IdealResistiveDeviceParameter(AbstractResistiveDeviceParameter):
@@ -575,4 +568,6 @@ class AnalogTileParameter:
         """Factory for an analog tile (``createRPUArray``, src/rpucuda/rpu_pulsed.cpp:49-56)."""
         from .tiles import AnalogTile
 
-        return AnalogTile(self._config(x_size, d_size, device_par))
+        tile = AnalogTile(self._config(x_size, d_size, device_par))
+        tile._meta = self
+        return tile

@@ -17,6 +17,7 @@ Differences from the reference binding, all forced by "GPU only":
 from __future__ import annotations
 
 import ctypes as C
+import enum
 from typing import List, Optional
 
 import numpy as np
@@ -24,6 +25,89 @@ import torch
 
 from .. import _cabi
 from .._cabi import check
+
+
+class WeightClipType(enum.IntEnum):
+    """rpu_base_utils.cpp:49-53 (src/rpucuda/weight_clipper.h:14-19); ``None`` spelt ``None_``."""
+
+    None_ = 0
+    FixedValue = 1
+    LayerGaussian = 2
+    AverageChannelMax = 3
+
+
+class WeightRemapType(enum.IntEnum):
+    """rpu_base_utils.cpp:44-47 (src/rpucuda/weight_remapper.h)."""
+
+    None_ = 0
+    LayerwiseSymmetric = 1
+    ChannelwiseSymmetric = 2
+
+
+class WeightModifierType(enum.IntEnum):
+    """rpu_base_utils.cpp:31-42 (src/rpucuda/weight_modifier.h)."""
+
+    Copy = 0
+    Discretize = 1
+    MultNormal = 2
+    AddNormal = 3
+    DiscretizeAddNormal = 4
+    DoReFa = 5
+    Poly = 6
+    PCMNoise = 7
+    DropConnect = 8
+    ProgNoise = 9
+
+
+for _e in (WeightClipType, WeightRemapType):
+    _e._member_map_["None"] = _e(0)  # type: ignore[attr-defined]
+    type.__setattr__(_e, "None", _e(0))
+WeightModifierType._member_map_["None"] = WeightModifierType.Copy  # type: ignore[attr-defined]
+type.__setattr__(WeightModifierType, "None", WeightModifierType.Copy)
+
+
+class WeightClipParameter:
+    """``WeightClipParameter`` (rpu_base_utils.cpp:18-22; src/rpucuda/weight_clipper.h:22-27)."""
+
+    def __init__(self) -> None:
+        self.type = WeightClipType.None_
+        self.fixed_value = -1.0
+        self.sigma = 2.5
+
+
+class WeightRemapParameter:
+    """``WeightRemapParameter`` (rpu_base_utils.cpp:24-29; src/rpucuda/weight_remapper.h)."""
+
+    def __init__(self) -> None:
+        self.type = WeightRemapType.None_
+        self.remapped_wmax = 1.0
+        self.max_scale_range = 0.0
+        self.max_scale_ref = 0.0
+
+
+class WeightModifierParameter:
+    """``WeightModifierParameter`` (rpu_base_tiles.cpp:31-51; src/rpucuda/weight_modifier.h)."""
+
+    def __init__(self) -> None:
+        self.std_dev = 0.0
+        self.per_batch_sample = False
+        self.res = 0.1
+        self.sto_round = False
+        self.dorefa_clip = 0.6
+        self.pdrop = 0.0
+        self.enable_during_test = False
+        self.copy_last_column = False
+        self.rel_to_actual_wmax = True
+        self.assumed_wmax = 1.0
+        self.type = WeightModifierType.Copy
+        self.coeffs = [0.26348, 0.0768, -0.001877]
+        self.pcm_zero_thres = 0.0
+        self.pcm_t_inference = 0.0
+        self.pcm_prob_at_reset = 0.0
+        self.pcm_prob_at_gmax = 0.0
+        self.pcm_prob_at_random = 0.0
+        self.pcm_t0 = 20.0
+        self.g_max = 25.0
 
 
 def _stream_ptr(t: torch.Tensor) -> int:
@@ -47,6 +131,10 @@ class AnalogTile:
         self._h = handle
         self._device_index = int(cuda_device)
         self._shared: Optional[torch.Tensor] = None
+        self._shared_version = -1
+        self._delta: Optional[torch.Tensor] = None
+        self._meta = None  # the AnalogTileParameter the tile was created from
+        self._hidden_update_index = 0
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -97,39 +185,96 @@ class AnalogTile:
                 f"Invalid weights dimensions: expected [{self.get_d_size()},{self.get_x_size()}] array"
             )
         check(self._lib.ab200_tile_set_weights(self._h, w.data_ptr()))
+        if self._device_index < 0 and self._shared is not None:
+            # a tile without a device keeps the caller's host tensor in step (the reference CPU
+            # tile writes through the shared memory)
+            self._shared.copy_(self._get_weights_c())
 
-    def get_weights(self) -> torch.Tensor:
-        """CPU tensor ``[d_size, x_size]`` (rpu_base_tiles.cpp:130-148)."""
+    def _get_weights_c(self) -> torch.Tensor:
         w = torch.empty(self.get_d_size(), self.get_x_size(), dtype=torch.float32)
         check(self._lib.ab200_tile_get_weights(self._h, w.data_ptr()))
         return w
 
-    def set_weights_cuda(self, weights_xd: torch.Tensor) -> None:
+    def get_weights(self) -> torch.Tensor:
+        """CPU tensor ``[d_size, x_size]`` (rpu_base_tiles.cpp:130-148)."""
+        if self._device_index < 0 and self._shared is not None:
+            return self._shared.detach().clone()
+        return self._get_weights_c()
+
+    def __getattr__(self, name):
+        # ``get_weights_cuda`` / ``set_weights_cuda`` exist on tiles that sit on a device only:
+        # the reference's Python probes for them with hasattr (tiles/base.py:452-453,
+        # tiles/periphery.py:164-171, 225-226) and falls back to the host accessors otherwise
+        if name in ("get_weights_cuda", "set_weights_cuda") and \
+                self.__dict__.get("_device_index", -1) >= 0:
+            return getattr(self, "_" + name)
+        raise AttributeError(f"'{type(self).__name__}' object has no attribute '{name}'")
+
+    def _set_weights_cuda(self, weights_xd: torch.Tensor) -> None:
         """Device tensor ``[x_size, d_size]`` (probed by tiles/base.py:452-453)."""
         w = _check_input(weights_xd, "weights")
         if not w.is_cuda or tuple(w.shape) != (self.get_x_size(), self.get_d_size()):
             raise RuntimeError("set_weights_cuda expects a CUDA [x_size, d_size] tensor")
         check(self._lib.ab200_tile_set_weights_device(self._h, w.data_ptr(), _stream_ptr(w)))
 
-    def get_weights_cuda(self) -> torch.Tensor:
+    def _get_weights_cuda(self) -> torch.Tensor:
         dev = torch.device("cuda", self._device_index)
         w = torch.empty(self.get_x_size(), self.get_d_size(), dtype=torch.float32, device=dev)
         check(self._lib.ab200_tile_get_weights_device(self._h, w.data_ptr(), _stream_ptr(w)))
         return w
 
     def set_shared_weights(self, weights_xd: torch.Tensor) -> None:
-        """Alias caller-owned ``[x_size, d_size]`` CUDA memory as the tile's weights
-        (rpu_base_tiles_cuda.cpp:96-124; src/rpucuda/cuda/rpucuda.cu:322-334)."""
-        if not weights_xd.is_cuda or weights_xd.dtype != torch.float32:
-            raise RuntimeError("set_shared_weights expects a float32 CUDA tensor")
+        """Alias caller-owned memory as the tile's weights: ``[x_size, d_size]`` CUDA memory for a
+        tile on a device (rpu_base_tiles_cuda.cpp:96-124; src/rpucuda/cuda/rpucuda.cu:322-334; the
+        buffer is NOT filled, the caller copies the weights in, tiles/base.py:413-417), ``[d_size,
+        x_size]`` host memory for a tile without a device (rpu_base_tiles.cpp:216-229: filled with
+        the current weights)."""
+        if weights_xd.dtype != torch.float32:
+            raise RuntimeError("set_shared_weights expects a float32 tensor")
         if not weights_xd.is_contiguous() or weights_xd.numel() != self.get_x_size() * self.get_d_size():
-            raise RuntimeError("Shared weights need to be contiguous [x_size, d_size]")
+            raise RuntimeError("Shared weights need to be contiguous and of the tile's size")
+        if self._device_index < 0:
+            if weights_xd.is_cuda:
+                raise RuntimeError("set_shared_weights: a tile without a device takes host memory")
+            if self._shared is None or self._shared.data_ptr() != weights_xd.data_ptr():
+                weights_xd.copy_(self._get_weights_c().reshape(weights_xd.shape))
+            self._shared = weights_xd
+            return
+        if not weights_xd.is_cuda:
+            raise RuntimeError("set_shared_weights expects a float32 CUDA tensor")
         self._shared = weights_xd
+        self._shared_version = int(weights_xd._version)
         check(
             self._lib.ab200_tile_set_shared_weights(
-                self._h, weights_xd.data_ptr(), int(weights_xd._version)
+                self._h, weights_xd.data_ptr(), self._shared_version
             )
         )
+
+    def _sync_shared(self) -> None:
+        """The caller may have written into the shared tensor since it was set (the reason to
+        share it): tell the tile, so that operand copies derived from the weights are rebuilt."""
+        if self._shared is not None and self._device_index >= 0 and \
+                int(self._shared._version) != self._shared_version:
+            self.set_shared_weights(self._shared)
+
+    def get_shared_weights_if(self) -> bool:
+        return self._shared is not None
+
+    def set_delta_weights(self, delta_weights: torch.Tensor) -> None:
+        """rpu_base_tiles_cuda.cpp ``set_delta_weights`` (rpu_base_tiles.cpp:231-245): the
+        floating-point update writes the gradient into this ``[x_size, d_size]`` CUDA tensor
+        instead of changing the weights, until :meth:`reset_delta_weights`."""
+        if not delta_weights.is_cuda or delta_weights.dtype != torch.float32 or \
+                not delta_weights.is_contiguous() or \
+                delta_weights.numel() != self.get_x_size() * self.get_d_size():
+            raise RuntimeError("Delta weights need to be a contiguous float32 CUDA tensor of the tile's size")
+        self._delta = delta_weights
+        check(self._lib.ab200_tile_set_delta_weights(self._h, delta_weights.data_ptr()))
+
+    def reset_delta_weights(self) -> None:
+        """rpu_base_tiles.cpp:246-252."""
+        self._delta = None
+        check(self._lib.ab200_tile_set_delta_weights(self._h, None))
 
     # -- hidden parameters ---------------------------------------------------------------------
     def get_hidden_parameter_names(self) -> List[str]:
@@ -179,6 +324,7 @@ class AnalogTile:
         else:
             dims[-1] = self.get_d_size()
         out = torch.empty(dims, dtype=torch.float32, device=x.device)
+        self._sync_shared()
         if x.is_cuda:
             check(
                 self._lib.ab200_tile_forward(
@@ -219,6 +365,7 @@ class AnalogTile:
         else:
             dims[-1] = x_out
         out = torch.empty(dims, dtype=torch.float32, device=d.device)
+        self._sync_shared()
         if d.is_cuda:
             check(
                 self._lib.ab200_tile_backward(
@@ -292,6 +439,7 @@ class AnalogTile:
         (rpu_base_tiles.cpp ``__copy__`` / ``__deepcopy__``)."""
         other = type(self).__new__(type(self))
         AnalogTile.__init__(other, self._cfg, cuda_device=self._device_index)
+        other._meta = self._meta
         # weights first: setting them resets a compound device's hidden tiles and counters
         other.set_weights(self.get_weights())
         if self.get_hidden_parameter_names():
@@ -363,6 +511,7 @@ class AnalogTile:
         if d_tensor.size(1) != self.get_d_size() or d_tensor.size(0) != x.size(0):
             raise RuntimeError("d_tensor must be [N, d_size, ...]")
         n, d_image = self._indexed_dims(d_tensor)
+        self._sync_shared()
         check(self._lib.ab200_tile_forward_indexed(
             self._h, x.data_ptr(), d_tensor.data_ptr(), x.numel(), d_image, n, 1, int(is_test),
             _stream_ptr(x)))
@@ -380,6 +529,7 @@ class AnalogTile:
         if d.size(1) != self.get_d_size() or d.size(0) != x_tensor.size(0):
             raise RuntimeError("d_input must be [N, d_size, ...]")
         n, d_image = self._indexed_dims(d)
+        self._sync_shared()
         check(self._lib.ab200_tile_backward_indexed(
             self._h, d.data_ptr(), x_tensor.data_ptr(), x_tensor.numel(), d_image, n, 1,
             _stream_ptr(d)))
@@ -425,9 +575,105 @@ class AnalogTile:
         return int(n.value), float(r.value)
 
     def get_brief_info(self) -> str:
-        return f"AnalogTile(B200, {self.get_d_size()}x{self.get_x_size()})"
+        return f"{type(self).__name__}(B200, {self.get_d_size()}x{self.get_x_size()})"
+
+    def get_info(self) -> str:
+        """rpu_base_tiles.cpp:71-78: a printable summary of the tile's parameters."""
+        lines = [self.get_brief_info(), f"  learning_rate: {self.get_learning_rate()}"]
+        if self._meta is not None:
+            for part in ("forward_io", "backward_io", "update"):
+                sub = getattr(self._meta, part, None)
+                if sub is not None:
+                    lines.append(f"  {part}: " + ", ".join(
+                        f"{k}={getattr(v, 'name', v)}" for k, v in vars(sub).items() if not k.startswith("_")))
+        return "\n".join(lines) + "\n"
 
     __str__ = get_brief_info
+
+    def get_meta_parameters(self):
+        """rpu_base_tiles.cpp:258 / :886: the meta parameters the tile was created from."""
+        if self._meta is None:
+            from . import devices
+
+            return devices.AnalogTileParameter()
+        return self._meta
+
+    def set_verbosity_level(self, verbose: int) -> None:
+        """rpu_base_tiles.cpp:115: the B200 tile prints nothing at any level."""
+        self._verbose = int(verbose)
+
+    def get_hidden_update_index(self) -> int:
+        """rpu_base_tiles.cpp:838-845: which device of a compound receives the gradient update;
+        the Transfer compound updates its first (fast) device, single devices have index 0."""
+        return int(self._hidden_update_index)
+
+    def set_hidden_update_index(self, index: int) -> None:
+        """rpu_base_tiles.cpp:827-837."""
+        if int(index) != 0:
+            raise RuntimeError("hidden update index: only the first device of a compound is updated "
+                               "by the B200 analog tile")
+        self._hidden_update_index = 0
+
+    def get_pulse_counters(self) -> torch.Tensor:
+        """rpu_base_tiles.cpp:846-868: int64 ``[k, d_size, x_size]``; empty unless the device
+        counts pulses (``count_pulses``, which the B200 tile does not implement)."""
+        return torch.zeros(0, self.get_d_size(), self.get_x_size(), dtype=torch.int64)
+
+    def drift_weights(self, time_since_last_call: float) -> None:
+        """rpu_base_tiles.cpp:294-314 (power-law drift, src/rpucuda/rpu.cpp:1581-1600)."""
+        raise RuntimeError("drift_weights is not implemented by the B200 analog tile")
+
+    def remap_weights(self, weight_remap_params, scales: torch.Tensor,
+                      biases: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """rpu_base_tiles.cpp:331-356 (WeightRemapper::apply, src/rpucuda/weight_remapper.cpp):
+        rescale the weights so that their largest magnitude - of the whole tile, or per output
+        row - becomes ``remapped_wmax``, and move the factor into ``scales`` (one per output)."""
+        kind = int(weight_remap_params.type)
+        if kind == int(WeightRemapType.None_):
+            return scales
+        if biases is not None:
+            raise RuntimeError("remap_weights with biases is not implemented")
+        if self._device_index < 0:
+            raise RuntimeError("remap_weights: the analog tile has no CPU compute path")
+        dev = torch.device("cuda", self._device_index)
+        w = self._shared if self._shared is not None else self.get_weights_cuda()  # [x, d]
+        scales_dev = scales.to(dev, torch.float32)
+        amax = w.abs().amax(dim=0)  # per output row
+        max_range = float(weight_remap_params.max_scale_range)
+        if kind == int(WeightRemapType.LayerwiseSymmetric):
+            amax = (amax.max() / float(weight_remap_params.remapped_wmax)).expand_as(amax)
+            max_range = 0.0
+        elif max_range <= 0:
+            amax = amax / float(weight_remap_params.remapped_wmax)
+        elif float(weight_remap_params.remapped_wmax) != 1.0:
+            raise RuntimeError("For max_scales set, expect wrmpar.remapped_wmax to be 1.")
+        factor = torch.where(amax > 0, amax, torch.ones_like(amax))
+        new_scales = scales_dev * factor
+        if max_range > 0:
+            # the range of the scales is limited relative to the smallest old scale
+            # (weight_remapper.cpp: min_scale, max_scale_ref)
+            min_scale = max(float(scales_dev.min()), 0.0)
+            ref = float(weight_remap_params.max_scale_ref)
+            if min_scale > 0 and ref:
+                min_scale = max(min_scale, ref)
+            if min_scale > 0:
+                new_scales = torch.minimum(new_scales, torch.full_like(new_scales, min_scale * max_range))
+            factor = new_scales / scales_dev
+        w_new = w / factor[None, :]
+        if self._shared is not None:
+            self._shared.copy_(w_new)
+            self._sync_shared()
+        else:
+            self.set_weights_cuda(w_new.contiguous())
+        scales.copy_(new_scales.to(scales.device))
+        return scales
+
+    def modify_weights(self, weight_modifier_params) -> None:
+        """rpu_base_tiles.cpp:358-371 (WeightModifier, src/rpucuda/weight_modifier.cpp)."""
+        if int(weight_modifier_params.type) == int(WeightModifierType.Copy) and \
+                float(weight_modifier_params.pdrop) == 0.0:
+            return
+        raise RuntimeError("modify_weights: this weight modifier is not implemented by the B200 analog tile")
 
 
 class FloatingPointTile(AnalogTile):
@@ -442,16 +688,45 @@ class FloatingPointTile(AnalogTile):
         par.update.pulse_type = devices.PulseType.None_
         cfg = par._config(x_size, d_size, devices.IdealResistiveDeviceParameter())
         super().__init__(cfg, cuda_device)
+        self._meta = par
 
 
-def CudaAnalogTile(tile: AnalogTile, device=None) -> AnalogTile:
-    """``tiles.CudaAnalogTile(cpu_tile)`` (rpu_base_tiles_cuda.cpp:524-543)."""
-    return tile.cuda(device)
+def _device_index(device) -> int:
+    if device is None:
+        return torch.cuda.current_device() if torch.cuda.is_available() else 0
+    if isinstance(device, int):
+        return device
+    index = torch.device(device).index
+    return torch.cuda.current_device() if index is None else index
 
 
-def CudaFloatingPointTile(tile: FloatingPointTile, device=None) -> AnalogTile:
+def _take_over(new: AnalogTile, tile: AnalogTile, device) -> None:
+    """Build ``new`` as the device copy of the host tile ``tile``: same configuration, weights
+    (from the shared host tensor when there is one), per-element parameters and extra state."""
+    if not isinstance(tile, AnalogTile):
+        raise RuntimeError("a CUDA tile is constructed from a host tile of this module")
+    AnalogTile.__init__(new, tile._cfg, cuda_device=_device_index(device))
+    new._meta = tile._meta
+    new.set_weights(tile.get_weights())
+    if tile.get_hidden_parameter_names():
+        new.set_hidden_parameters(tile.get_hidden_parameters())
+    new.load_extra(tile.dump_extra(), strict=True)
+
+
+class CudaAnalogTile(AnalogTile):
+    """``tiles.CudaAnalogTile(cpu_tile)`` (rpu_base_tiles_cuda.cpp:524-543): the tile on the
+    current CUDA device, built from a host tile that carries configuration, weights and the
+    host-drawn per-element parameters."""
+
+    def __init__(self, tile: AnalogTile, device=None):
+        _take_over(self, tile, device)
+
+
+class CudaFloatingPointTile(FloatingPointTile):
     """``tiles.CudaFloatingPointTile(cpu_tile)`` (rpu_base_tiles_cuda.cpp:45-58)."""
-    return tile.cuda(device)
+
+    def __init__(self, tile: AnalogTile, device=None):
+        _take_over(self, tile, device)
 
 
 class TileArray:

@@ -265,6 +265,13 @@ int ab200_tile_get_weights_device(ab200_tile *tile, float *w_dev_xd, void *strea
  * changes when the caller modified the buffer (operand caches are rebuilt when (ptr, version)
  * changes). */
 int ab200_tile_set_shared_weights(ab200_tile *tile, float *w_dev_xd, uint64_t version);
+/* RPUSimple::setDeltaWeights / reset_delta_weights (src/rpucuda/rpu.cpp:1459-1481, bound at
+ * src/aihwkit/simulator/rpu_base_src/rpu_base_tiles.cpp:231-257): while a caller-owned fp32
+ * [x_size][d_size] device buffer is set, the floating-point update leaves the weights alone and
+ * overwrites the buffer with the gradient sum_s d_s x_s / bwd_alpha (getAlphaLearningRate
+ * rpu.cpp:1400-1403, getUpBeta :1509-1511) - the update path of hardware-aware training
+ * (tiles/functions.py:91-102). Null ends the mode. */
+int ab200_tile_set_delta_weights(ab200_tile *tile, float *dw_dev_xd);
 
 /* Hidden (per-element device) parameters: RPUPulsed::getDeviceParameterNames / getDeviceParameter /
  * setDeviceParameter (src/rpucuda/rpu_pulsed.cpp:330-380; rpu_base_tiles.cpp:764-825).
