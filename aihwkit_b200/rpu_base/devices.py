@@ -190,8 +190,52 @@ class AnalogTileUpdateParameter:
         return c
 
 
+class DriftParameter:
+    """DriftParameter (rpu_base_devices.cpp:521-533): power-law drift of the weights over time.
+    Only the inactive default (``nu = 0``) is implemented by the B200 analog tile."""
+
+    def __init__(self) -> None:
+        self.nu = 0.0
+        self.nu_dtod = 0.0
+        self.nu_std = 0.0
+        self.wg_ratio = 1.0
+        self.g_offset = 0.0
+        self.w_offset = 0.0
+        self.nu_k = 0.0
+        self.log_g0 = 0.0
+        self.t_0 = 1.0
+        self.reset_tol = 1e-7
+        self.w_noise_std = 0.0
+
+    def _active(self) -> bool:
+        return self.nu != 0.0 or self.nu_dtod != 0.0 or self.nu_std != 0.0 or self.nu_k != 0.0
+
+
+class FloatingPointTileParameter:
+    """SimpleMetaParameter (rpu_base_devices.cpp:436-451): the floating-point tile's own
+    parameters and its factory."""
+
+    def __init__(self) -> None:
+        self.diffusion = 0.0
+        self.lifetime = 0.0
+        self.drift = DriftParameter()
+
+    def create_array(self, x_size: int, d_size: int):
+        """``createRPUArray`` of the floating-point tile (src/rpucuda/rpu.cpp)."""
+        from .tiles import FloatingPointTile
+
+        if self.drift._active():
+            raise RuntimeError("power-law drift is not implemented by the B200 analog tile")
+        return FloatingPointTile(x_size, d_size, lifetime=float(self.lifetime),
+                                 diffusion=float(self.diffusion))
+
+    def __str__(self) -> str:
+        return f"FloatingPointTileParameter(diffusion={self.diffusion}, lifetime={self.lifetime})"
+
+
 class AbstractResistiveDeviceParameter:
-    """AbstractRPUDeviceMetaParameter (rpu_base_devices.cpp:536-539)."""
+    """AbstractRPUDeviceMetaParameter (rpu_base_devices.cpp:536-539), derived from the
+    floating-point tile's parameters as in the reference."""
 
     _kind = -1
 
@@ -199,6 +243,7 @@ class AbstractResistiveDeviceParameter:
         self.construction_seed = 0
         self.diffusion = 0.0
         self.lifetime = 0.0
+        self.drift = DriftParameter()
 
     def calc_weight_granularity(self) -> float:
         raise RuntimeError("Needs implementation.")

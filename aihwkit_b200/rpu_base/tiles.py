@@ -679,14 +679,17 @@ class AnalogTile:
 class FloatingPointTile(AnalogTile):
     """``tiles.FloatingPointTile`` (RPUSimple): perfect IO and floating-point update."""
 
-    def __init__(self, x_size: int, d_size: int, cuda_device: int = -1):
+    def __init__(self, x_size: int, d_size: int, cuda_device: int = -1, lifetime: float = 0.0,
+                 diffusion: float = 0.0):
         from . import devices
 
         par = devices.AnalogTileParameter()
         par.forward_io.is_perfect = True
         par.backward_io.is_perfect = True
         par.update.pulse_type = devices.PulseType.None_
-        cfg = par._config(x_size, d_size, devices.IdealResistiveDeviceParameter())
+        dev = devices.IdealResistiveDeviceParameter()
+        dev.lifetime, dev.diffusion = lifetime, diffusion
+        cfg = par._config(x_size, d_size, dev)
         super().__init__(cfg, cuda_device)
         self._meta = par
 
