@@ -262,6 +262,7 @@ def _declare(lib: C.CDLL) -> None:
             _I, [C.POINTER(IOParams), _FP, _I, _I, _FP, _FP, _I, C.c_uint64, C.c_uint32, _VP]
         ),
         "ab200_set_mvm_path": (_I, [_I]),
+        "ab200_set_update_path": (_I, [_I]),
         "ab200_measure_popc_peak": (_I, [_I, C.POINTER(C.c_double)]),
         "ab200_kernel_launch_count": (C.c_uint64, []),
     }

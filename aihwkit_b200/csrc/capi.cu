@@ -918,6 +918,15 @@ int ab200_set_mvm_path(int mode) {
   AB200_CATCH
 }
 
+int ab200_set_update_path(int mode) {
+  AB200_TRY
+  if (mode < 0 || mode > 2) {
+    AB200_FATAL("set_update_path: mode must be 0, 1 or 2");
+  }
+  ab200::setUpdatePath(mode);
+  AB200_CATCH
+}
+
 uint64_t ab200_kernel_launch_count(void) { return ab200::launchCount(); }
 
 } // extern "C"

@@ -80,10 +80,14 @@ template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKe
 // Kernel 2: tiled fp32 product with the DAC fused into the operand load and noise / ADC / clip /
 // bound flag / rescale fused into the epilogue.
 // ---------------------------------------------------------------------------------------------
-constexpr int BM = 64, BN = 64, BK = 16;
+// T x T outputs per thread, 16 x 16 threads: 64 x 64 outputs per CTA for large problems, 32 x 32 or
+// 16 x 16 when the larger tile would leave most SMs without a CTA (a 256 x 256 tile with a batch of
+// 64 is four CTAs of 64 x 64, but 64 of 16 x 16).
+constexpr int BK = 16;
 
-template <bool A_K_FAST, bool B_N_FAST>
+template <bool A_K_FAST, bool B_N_FAST, int T>
 __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
+  constexpr int BM = 16 * T, BN = 16 * T;
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   __shared__ float s_scale[BM];
@@ -100,19 +104,18 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   }
   __syncthreads();
 
-  float acc[4][4];
+  float acc[T][T];
 #pragma unroll
-  for (int i = 0; i < 4; i++) {
+  for (int i = 0; i < T; i++) {
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < T; j++) {
       acc[i][j] = 0.0f;
     }
   }
 
   for (int k0 = 0; k0 < K; k0 += BK) {
 #pragma unroll
-    for (int l = 0; l < 4; l++) {
-      int e = tid + l * 256;
+    for (int e = tid; e < BM * BK; e += 256) {
       int r, kk;
       if (A_K_FAST) {
         kk = e % BK;
@@ -133,8 +136,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
       As[kk][r] = v;
     }
 #pragma unroll
-    for (int l = 0; l < 4; l++) {
-      int e = tid + l * 256;
+    for (int e = tid; e < BN * BK; e += 256) {
       int n, kk;
       if (B_N_FAST) {
         n = e % BN;
@@ -149,19 +151,19 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < BK; kk++) {
-      float a[4], b[4];
+      float a[T], b[T];
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        a[i] = As[kk][ty * 4 + i];
+      for (int i = 0; i < T; i++) {
+        a[i] = As[kk][ty * T + i];
       }
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        b[j] = Bs[kk][tx * 4 + j];
+      for (int j = 0; j < T; j++) {
+        b[j] = Bs[kk][tx * T + j];
       }
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
+      for (int i = 0; i < T; i++) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+        for (int j = 0; j < T; j++) {
           acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
       }
@@ -169,29 +171,37 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
     __syncthreads();
   }
 
-  // noise blocks of four columns, an even number per row (two blocks share one Philox call)
+  // noise blocks of four columns, an even number per row (two blocks share one Philox call); a
+  // thread with fewer than four columns draws its block and takes its columns from it
   const uint64_t n4 = (uint64_t)(((N + 7) >> 3) << 1);
   const uint32_t tag = (p.backward ? TAG_BWD_OUT : TAG_FWD_OUT) + p.noise_id;
   const uint32_t tag_u = (p.backward ? TAG_BWD_OUT_U : TAG_FWD_OUT_U) + p.noise_id;
 #pragma unroll
-  for (int i = 0; i < 4; i++) {
-    int r = row0 + ty * 4 + i;
+  for (int i = 0; i < T; i++) {
+    int r = row0 + ty * T + i;
     if (r >= p.m) {
       continue;
     }
-    int c = col0 + tx * 4;
+    int c = col0 + tx * T;
     if (c >= N) {
       continue;
     }
-    float sc = s_scale[ty * 4 + i];
+    float sc = s_scale[ty * T + i];
     float fac = p.factor[r];
-    float y[4] = {acc[i][0], acc[i][1], acc[i][2], acc[i][3]};
+    float y[T];
+#pragma unroll
+    for (int j = 0; j < T; j++) {
+      y[j] = acc[i][j];
+    }
     bool exceeded = false;
     if (sc == 0.0f) {
-      y[0] = y[1] = y[2] = y[3] = 0.0f;
+#pragma unroll
+      for (int j = 0; j < T; j++) {
+        y[j] = 0.0f;
+      }
     } else if (io.is_perfect) {
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
+      for (int j = 0; j < T; j++) {
         y[j] *= fac;
       }
     } else {
@@ -205,15 +215,16 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
         uniform4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag_u, u);
       }
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        y[j] = finalizeOutput(io, y[j], sigma, z[j], exceeded, u[j]) * fac;
+      for (int j = 0; j < T; j++) {
+        const int q = (c + j) & 3; // T divides 4 and c is a multiple of T: same block for all j
+        y[j] = finalizeOutput(io, y[j], sigma, z[q], exceeded, u[q]) * fac;
       }
     }
     if (exceeded && io.bm != AB200_BM_NONE) {
       atomicOr(&p.flags[r], 1);
     }
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < T; j++) {
       if (c + j < p.out_store) {
         float *o = p.out + (long long)r * p.out_ss + (long long)(c + j) * p.out_fs;
         *o = p.accumulate ? *o + y[j] : y[j];
@@ -348,18 +359,40 @@ void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
   }
   AB200_LAUNCH_CHECK();
 
-  dim3 grid((p.out_size + BN - 1) / BN, (p.m + BM - 1) / BM);
-  bool a_k_fast = p.in_fs == 1;
-  bool b_n_fast = p.wn == 1;
-  if (a_k_fast && b_n_fast) {
-    mvmSimtKernel<true, true><<<grid, 256, 0, stream>>>(p);
-  } else if (a_k_fast) {
-    mvmSimtKernel<true, false><<<grid, 256, 0, stream>>>(p);
-  } else if (b_n_fast) {
-    mvmSimtKernel<false, true><<<grid, 256, 0, stream>>>(p);
-  } else {
-    mvmSimtKernel<false, false><<<grid, 256, 0, stream>>>(p);
+  const bool a_k_fast = p.in_fs == 1;
+  const bool b_n_fast = p.wn == 1;
+  // the largest tile that still gives every SM a CTA
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    AB200_CUDA(cudaGetDevice(&dev));
+    AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
   }
+  auto ctas = [&](int t) {
+    return (long long)((p.out_size + 16 * t - 1) / (16 * t)) * ((p.m + 16 * t - 1) / (16 * t));
+  };
+  const int T = ctas(4) >= n_sm ? 4 : (ctas(2) >= n_sm ? 2 : 1);
+#define AB200_SIMT(TT)                                                                             \
+  {                                                                                                \
+    dim3 grid((p.out_size + 16 * TT - 1) / (16 * TT), (p.m + 16 * TT - 1) / (16 * TT));           \
+    if (a_k_fast && b_n_fast) {                                                                    \
+      mvmSimtKernel<true, true, TT><<<grid, 256, 0, stream>>>(p);                                  \
+    } else if (a_k_fast) {                                                                         \
+      mvmSimtKernel<true, false, TT><<<grid, 256, 0, stream>>>(p);                                 \
+    } else if (b_n_fast) {                                                                         \
+      mvmSimtKernel<false, true, TT><<<grid, 256, 0, stream>>>(p);                                 \
+    } else {                                                                                       \
+      mvmSimtKernel<false, false, TT><<<grid, 256, 0, stream>>>(p);                                \
+    }                                                                                              \
+  }
+  if (T == 4) {
+    AB200_SIMT(4)
+  } else if (T == 2) {
+    AB200_SIMT(2)
+  } else {
+    AB200_SIMT(1)
+  }
+#undef AB200_SIMT
   AB200_LAUNCH_CHECK();
 }
 

@@ -86,7 +86,12 @@ UpEff resolveUp(const ab200_update_params &up) {
   e.x_res_implicit = checkRes(up.x_res_implicit);
   e.d_res_implicit = checkRes(up.d_res_implicit);
   if (up.pulse_type == AB200_PULSE_STOCHASTIC) {
-    AB200_FATAL("PulseType not supported");
+    // Separate trains for positive and negative x-lines (generateCountsPN,
+    // sparse_bit_line_maker.cpp:147-197, applied one sign group after the other,
+    // rpu_weight_updater.cpp:262-286): a line has one sign per sample, so it carries exactly one
+    // Bernoulli train either way, and a weight receives a pulse in slot k iff both its lines
+    // pulse in k - the same law per weight, in the same per-weight order, as the compressed type.
+    e.pulse_type = AB200_PULSE_STOCHASTIC_COMPRESSED;
   }
   if (up.sto_round) {
     AB200_FATAL("stochastic rounding of pulse probabilities is not implemented");
@@ -443,6 +448,8 @@ Tile::~Tile() {
     cudaFree(dw_);
     cudaFree(xnz_);
     cudaFree(dnz_);
+    cudaFree(xwt_);
+    cudaFree(xnzt_);
     cudaFree(onehot_);
     cudaFree(tread_);
     cudaFree(t_words_);
@@ -522,7 +529,13 @@ void Tile::toDevice(int cuda_device) {
     AB200_CUDA(cudaMemset(w_fast_, 0, size * sizeof(float)));
     AB200_CUDA(cudaMalloc(&onehot_, (size_t)x_size_ * sizeof(float)));
     AB200_CUDA(cudaMalloc(&tread_, (size_t)d_size_ * sizeof(float)));
-    AB200_CUDA(cudaMalloc(&t_words_, 2 * (size_t)(x_size_ + d_size_) * sizeof(uint32_t)));
+    {
+      // pulse words of the single sample of a transfer write (all its segments) + their bitmaps
+      const size_t nseg_t = (size_t)std::max(1, (cfg_.transfer.transfer_up.desired_bl + kPulseSegSlots - 1) /
+                                                    kPulseSegSlots);
+      AB200_CUDA(cudaMalloc(&t_words_, (nseg_t + (nseg_t + 31) / 32) * (size_t)(x_size_ + d_size_) *
+                                           sizeof(uint32_t)));
+    }
     if (cfg_.transfer.buffered) {
       AB200_CUDA(cudaMalloc(&t_buffer_, size * sizeof(float)));
       AB200_CUDA(cudaMemset(t_buffer_, 0, size * sizeof(float)));
@@ -568,6 +581,21 @@ void Tile::ensureScratch(int m) {
     AB200_CUDA(cudaMalloc(&dnz_, nblk * d_size_ * sizeof(uint32_t)));
   }
   scratch_m_ = cap;
+}
+
+void Tile::ensureStreamScratch(int m_pad) {
+  const size_t need = (size_t)m_pad * x_size_;
+  if (need <= xwt_words_) {
+    return;
+  }
+  AB200_CUDA(cudaDeviceSynchronize());
+  cudaFree(xwt_);
+  cudaFree(xnzt_);
+  xwt_ = xnzt_ = nullptr;
+  const size_t cap = need + need / 8;
+  AB200_CUDA(cudaMalloc(&xwt_, cap * sizeof(uint32_t)));
+  AB200_CUDA(cudaMalloc(&xnzt_, (cap / 32 + x_size_) * sizeof(uint32_t)));
+  xwt_words_ = cap;
 }
 
 void Tile::ensureStage(size_t n_floats) {
@@ -1038,6 +1066,14 @@ void Tile::lastBmStats(int32_t *n_rerun, float *max_red) {
 // ---------------------------------------------------------------------------------------------
 // update
 // ---------------------------------------------------------------------------------------------
+// rows of pulse words per sample (see UpdateProblem::nseg)
+static int pulseSegments(const UpEff &up) {
+  if (up.pulse_type != AB200_PULSE_STOCHASTIC_COMPRESSED) {
+    return 1;
+  }
+  return std::max(1, (up.desired_bl + kPulseSegSlots - 1) / kPulseSegSlots);
+}
+
 float Tile::pulseCountLR() const {
   // TransferRPUDevice::getPulseCountLearningRate (rpu_transfer_device.cpp:366-383)
   if (cfg_.device_kind == AB200_DEVICE_TRANSFER && cfg_.transfer.fast_lr > 0.0f) {
@@ -1088,14 +1124,15 @@ void Tile::doTransfer(cudaStream_t s) {
     u.lr_neg = write_lr < 0.0f;
     u.dw_min = dev_[1].dw_min;
     u.up = t_up_;
+    u.nseg = pulseSegments(t_up_);
     u.key = key_;
     u.call = 0x40000000u + call;
     // own scratch: the gradient batch's pulse words are still in use when a transfer falls in
     // the middle of a batch
     u.xw = t_words_;
-    u.dw = t_words_ + x_size_;
-    u.xnz = t_words_ + x_size_ + d_size_;
-    u.dnz = t_words_ + 2 * x_size_ + d_size_;
+    u.dw = t_words_ + (size_t)u.nseg * x_size_;
+    u.xnz = t_words_ + (size_t)u.nseg * (x_size_ + d_size_);
+    u.dnz = u.xnz + (size_t)((u.nseg + 31) / 32) * x_size_;
     u.w = w_;
     u.par4 = dev_[1].par4;
     u.par2 = dev_[1].par2;
@@ -1135,7 +1172,7 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
   if (m <= 0 || lr_ == 0.0f) {
     return; // "if (!learning_rate) return" (rpu_weight_updater.cpp:206-208)
   }
-  ensureScratch(m);
+  ensureScratch(m * pulseSegments(up_));
   if (!delta_w_) {
     w_version_++;
   }
@@ -1191,6 +1228,7 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
   u.lr = fabsf(pc_lr);
   u.lr_neg = pc_lr < 0.0f;
   u.up = up_;
+  u.nseg = pulseSegments(up_);
   u.dw_min = dev_[0].dw_min;
   u.par4 = dev_[0].par4;
   u.par2 = dev_[0].par2;
@@ -1200,10 +1238,23 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
   u.es1 = dev_[0].es1;
   u.mult_noise = dev_[0].mult_noise;
   launchPulsePrepare(u, s);
+  const bool stream_upd = streamUpdateEligible(u);
+  const int m_pad = (m * u.nseg + 31) / 32 * 32;
+  if (stream_upd) {
+    ensureStreamScratch(m_pad);
+    launchPulseTranspose(u, xwt_, xnzt_, m_pad, s);
+  }
+  auto applyRange = [&](UpdateProblem &r) {
+    if (stream_upd) {
+      launchPulsedUpdateStream(r, xwt_, xnzt_, m_pad, s);
+    } else {
+      launchPulsedUpdate(r, s);
+    }
+  };
 
   if (cfg_.device_kind != AB200_DEVICE_TRANSFER) {
     u.w = w_;
-    launchPulsedUpdate(u, s);
+    applyRange(u);
     return;
   }
 
@@ -1228,7 +1279,7 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
     }
     u.s_begin = s0;
     u.s_end = s1;
-    launchPulsedUpdate(u, s);
+    applyRange(u);
     update_idx_ += s1 - s0;
     if (every > 0 && update_idx_ % every == 0) {
       doTransfer(s);
@@ -1243,7 +1294,7 @@ void Tile::coincidences(const float *x, const float *d, int32_t *counts, cudaStr
       up_.pulse_type == AB200_PULSE_NONE_WITH_DEVICE) {
     AB200_FATAL("coincidences need a pulsed update");
   }
-  ensureScratch(1);
+  ensureScratch(pulseSegments(up_));
   UpdateProblem u{};
   u.x = x;
   u.x_ss = x_size_;
@@ -1259,6 +1310,7 @@ void Tile::coincidences(const float *x, const float *d, int32_t *counts, cudaStr
   u.lr = fabsf(pc_lr);
   u.lr_neg = pc_lr < 0.0f;
   u.up = up_;
+  u.nseg = pulseSegments(up_);
   u.dw_min = dev_[0].dw_min;
   u.key = key_;
   u.call = 0x7fffffffu;

@@ -48,6 +48,8 @@ struct IOEff {
 IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only = false);
 
 // PulsedUpdateMetaParameter after initialize() (rpu_pulsed_meta_parameter.cpp:134-151).
+constexpr int kPulseSegSlots = 31; // pulse slots of one 32-bit pulse word (bit 0 is the sign)
+
 struct UpEff {
   int pulse_type;
   int desired_bl;
@@ -126,6 +128,12 @@ struct UpdateProblem {
   const float *d;
   long long d_ss, d_fs;
   int x_size, d_size, m;
+  // Stochastic pulse trains longer than 31 slots are cut into segments of at most 31: a sample
+  // then has `nseg` rows of pulse words (row = sample * nseg + segment), each with its own sign
+  // bit, and the update kernels see m * nseg rows. Coincidences of one sample commute, so the
+  // per-weight result is that of the reference's multi-word trains
+  // (nK32 words per line, src/rpucuda/cuda/bit_line_maker.cu:24-28).
+  int nseg;
   float lr;     // |pulse-count learning rate|
   int lr_neg;   // learning rate negative
   float dw_min; // weight granularity
@@ -149,6 +157,17 @@ struct UpdateProblem {
 };
 
 void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream);
+// Large batches of stochastic pulse trains: the update streams over the samples of an x-line
+// (transposed x words + their bitmaps) instead of staging blocks of samples per weight tile.
+constexpr int kStreamUpdateMinBatch = 1024;
+bool streamUpdateEligible(const UpdateProblem &p);
+// kernel selection of the pulsed update: 0 = automatic, 1 = always the staged kernel, 2 = the
+// streaming kernel whenever the pulse type allows it (any batch size)
+void setUpdatePath(int mode);
+void launchPulseTranspose(const UpdateProblem &p, uint32_t *xwT, uint32_t *xnzT, int m_pad,
+                          cudaStream_t stream);
+void launchPulsedUpdateStream(const UpdateProblem &p, const uint32_t *xwT, const uint32_t *xnzT,
+                              int m_pad, cudaStream_t stream);
 void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream);
 void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream);
 void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream,
@@ -311,6 +330,10 @@ private:
   float *scale_ = nullptr, *factor_ = nullptr, *vnorm_ = nullptr, *sval_ = nullptr;
   int *flags_ = nullptr, *bm_stats_ = nullptr;
   uint32_t *xw_ = nullptr, *dw_ = nullptr, *xnz_ = nullptr, *dnz_ = nullptr;
+  // transposed x words [x_size][m_pad] and their bitmaps, for the streaming update of large batches
+  uint32_t *xwt_ = nullptr, *xnzt_ = nullptr;
+  size_t xwt_words_ = 0;
+  void ensureStreamScratch(int m_pad);
   float *onehot_ = nullptr, *tread_ = nullptr;
   uint32_t *t_words_ = nullptr; // Tiki-Taka write: pulse words and bitmaps of its single sample
   // tensor-core engines (forward / backward operand caches), rebuilt when the weights change

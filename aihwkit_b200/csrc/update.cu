@@ -92,18 +92,21 @@ blAB(const UpEff &up, float lr, float dw_min, float xm, float dm, int &BL, float
 // draws with probability pp; each draw compares pp against a 16-bit uniform, 8 draws per
 // Philox word pair.
 __device__ __forceinline__ uint32_t
-pulseTrain(float pp, int BL, PhiloxKey key, uint32_t line, uint32_t sample, uint32_t call,
+pulseTrain(float pp, int BL, int seg, PhiloxKey key, uint32_t line, uint32_t sample, uint32_t call,
            uint32_t tag) {
+  // slots [seg * 31, min(BL, seg * 31 + 31)) of the train, as bits 1.. of one word
+  const int k0 = seg * kPulseSegSlots;
+  const int nk = min(BL - k0, kPulseSegSlots);
   float thr = pp * 65536.0f;
   uint32_t bits = 0;
   int k = 0;
-  for (int q = 0; q * 8 < BL; q++) {
+  for (int q = 0; q * 8 < nk; q++) {
     uint32_t r[4];
-    philox4x32_10(line, sample, call, tag + (uint32_t)q, key, r);
+    philox4x32_10(line, sample, call, tag + (uint32_t)(seg * 4 + q), key, r);
 #pragma unroll
     for (int h = 0; h < 8; h++) {
       uint32_t u16 = (r[h >> 1] >> ((h & 1) * 16)) & 0xFFFFu;
-      if (k < BL && ((float)u16 + 0.5f) < thr) {
+      if (k < nk && ((float)u16 + 0.5f) < thr) {
         bits |= 1u << (k + 1);
       }
       k++;
@@ -142,8 +145,9 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
   __syncthreads();
   const int BL = s_BL;
   const float A = s_A, B = s_B;
-  uint32_t *xw = p.xw + (long long)s * p.x_size;
-  uint32_t *dw = p.dw + (long long)s * p.d_size;
+  const int nseg = p.nseg > 0 ? p.nseg : 1;
+  uint32_t *xw = p.xw + (long long)s * nseg * p.x_size;
+  uint32_t *dw = p.dw + (long long)s * nseg * p.d_size;
   const bool implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT;
   const bool mean_count = p.up.pulse_type == AB200_PULSE_MEAN_COUNT;
 
@@ -184,19 +188,26 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
       }
       word = __float_as_uint(sv);
     } else {
-      word = 0;
+      float pp = 0.0f;
+      uint32_t neg = 0u;
       if (BL > 0) {
-        float pp = discretize(__fmul_rn(fabsf(v), P), p.up.res);
-        if (pp != 0.0f) {
-          uint32_t neg = v > 0.0f ? 0u : 1u;
-          if (!is_x && p.lr_neg) {
-            neg ^= 1u;
-          }
-          word = pulseTrain(pp, BL, p.key, (uint32_t)idx, (uint32_t)s, p.call,
+        pp = discretize(__fmul_rn(fabsf(v), P), p.up.res);
+        neg = v > 0.0f ? 0u : 1u;
+        if (!is_x && p.lr_neg) {
+          neg ^= 1u;
+        }
+      }
+      const int n_lines = is_x ? p.x_size : p.d_size;
+      for (int g = 0; g < nseg; g++) {
+        word = 0;
+        if (pp != 0.0f && g * kPulseSegSlots < BL) {
+          word = pulseTrain(pp, BL, g, p.key, (uint32_t)idx, (uint32_t)s, p.call,
                             is_x ? TAG_PULSE_X : TAG_PULSE_D);
           word = word ? (word | neg) : 0u;
         }
+        (is_x ? xw : dw)[(long long)g * n_lines + idx] = word;
       }
+      continue;
     }
     (is_x ? xw : dw)[idx] = word;
   }
@@ -580,12 +591,267 @@ static void launchUpdateInstance(const UpdateProblem &p, dim3 grid, cudaStream_t
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Large batches: the update as a stream over the samples of one x-line.
+//
+// A warp owns 32 consecutive d-lines of ONE x-line. The x-line's pulse words are the same for all
+// its lanes, so the walk over the samples is uniform across the warp: it visits the samples
+// where the x word is not empty (bitmap of the transposed x words), loads the 32 d words of that
+// sample with one coalesced access, and every lane counts its coincidences with AND + popc. No
+// lane waits for another lane's candidates. The rare expensive part - applying the pulses - is
+// decoupled: a lane pushes its events (count, direction) into a small queue in a register pair,
+// and the warp drains the queues together when one of them is full, so that most lanes have work
+// in every round of the drain. The Gaussians of the device noise come from a pool per warp in
+// shared memory that all lanes refill together and take from without gaps (ballot + prefix
+// count). Per-weight sample order, one pulse at a time with the clip after each, as in
+// rpu_weight_updater.cpp:243-291.
+// ---------------------------------------------------------------------------------------------
+constexpr int USQ_BITS = 6;   // bits per queued event: 5 for the count (BL <= 31), 1 direction
+constexpr int USQ_SLOTS = 10; // events per 64-bit queue
+constexpr int USP_POOL = 256; // Gaussians per warp pool (eight per lane and refill)
+
+// xwT[line][sample] = xw[sample][line] for one 32 x 32 tile, plus the line's bitmap word of the
+// non-empty samples
+__global__ void __launch_bounds__(256)
+    pulseTransposeKernel(const uint32_t *words, int n_lines, int m, int m_pad, uint32_t *wordsT,
+                         uint32_t *nzT) {
+  __shared__ uint32_t tile[32][33];
+  const int l0 = blockIdx.x * 32, s0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += 8) {
+    const int s = s0 + r, l = l0 + threadIdx.x;
+    tile[r][threadIdx.x] = (s < m && l < n_lines) ? words[(long long)s * n_lines + l] : 0u;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += 8) {
+    const int l = l0 + r, sidx = s0 + threadIdx.x;
+    const uint32_t w = tile[threadIdx.x][r];
+    const uint32_t nz = __ballot_sync(0xffffffffu, w != 0u);
+    if (l < n_lines) {
+      wordsT[(long long)l * m_pad + sidx] = w;
+      if (threadIdx.x == 0) {
+        nzT[(long long)l * (m_pad / 32) + blockIdx.y] = nz;
+      }
+    }
+  }
+}
+
+struct StreamUpdate {
+  const uint32_t *xwT; // [x_size][m_pad]
+  const uint32_t *xnzT; // [x_size][m_pad / 32]
+  int m_pad;
+};
+
+template <int KIND, bool NOISY>
+__global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p, StreamUpdate st) {
+  __shared__ float pool[8][USP_POOL];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_dblk = (p.d_size + 31) >> 5;
+  const long long task = (long long)blockIdx.x * 8 + warp;
+  if (task >= (long long)n_dblk * p.x_size) {
+    return;
+  }
+  const int j = (int)(task / n_dblk);
+  const int i = (int)(task - (long long)j * n_dblk) * 32 + lane;
+  const bool i_ok = i < p.d_size;
+  const long long idx = (long long)j * p.d_size + (i_ok ? i : 0);
+  float w = 0.0f;
+  float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+  float2 e = make_float2(0.f, 0.f);
+  if (i_ok) {
+    w = p.w[idx];
+    q = p.par4[idx];
+    if (KIND != AB200_DEVICE_CONSTANT_STEP && KIND != AB200_DEVICE_EXP_STEP) {
+      e = p.par2[idx];
+    }
+  }
+  const float w_in = w;
+  const float std = p.dw_min_std;
+  unsigned long long queue = 0ull;
+  int cnt = 0;
+  int pool_pos = USP_POOL; // empty
+  uint32_t refills = 0;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+
+  auto drain = [&]() {
+    while (__any_sync(0xffffffffu, cnt > 0)) {
+      int n = 0;
+      bool down = false;
+      if (cnt > 0) {
+        const uint32_t ev = (uint32_t)queue & ((1u << USQ_BITS) - 1u);
+        queue >>= USQ_BITS;
+        cnt--;
+        n = (int)(ev >> 1);
+        down = (ev & 1u) != 0u;
+      }
+      for (int k = 0; __any_sync(0xffffffffu, k < n); k++) {
+        const bool act = k < n;
+        float xi = 0.0f;
+        if (NOISY) {
+          const uint32_t takers = __ballot_sync(0xffffffffu, act);
+          if (pool_pos + __popc(takers) > USP_POOL) {
+            // all lanes refill together; what is left of the old pool is dropped
+            float z[8];
+            gauss8(p.key, (uint64_t)(task * 32 + lane) | ((uint64_t)refills << 40), p.call, TAG_DEVICE, z);
+            __syncwarp();
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+              pool[warp][r * 32 + lane] = z[r];
+            }
+            __syncwarp();
+            refills++;
+            pool_pos = 0;
+          }
+          if (act) {
+            xi = std * pool[warp][pool_pos + __popc(takers & lt_mask)];
+          }
+          pool_pos += __popc(takers);
+        }
+        if (act) {
+          w = pulseOnce<KIND>(w, down, q, e, xi, p.mult_noise, p.es0, p.es1);
+        }
+      }
+    }
+  };
+
+  const int nw = st.m_pad >> 5;
+  const int w_first = p.s_begin >> 5, w_last = (p.s_end - 1) >> 5;
+  const uint32_t *nz_line = st.xnzT + (long long)j * nw;
+  const uint32_t *x_line = st.xwT + (long long)j * st.m_pad;
+  uint32_t bits_next = nz_line[w_first];
+  for (int wd = w_first; wd <= w_last; wd++) {
+    uint32_t bits = bits_next;
+    if (wd < w_last) {
+      bits_next = nz_line[wd + 1];
+    }
+    // samples of this word that belong to [s_begin, s_end)
+    const int sb = wd << 5;
+    if (sb < p.s_begin) {
+      bits &= 0xffffffffu << (p.s_begin - sb);
+    }
+    if (sb + 32 > p.s_end) {
+      bits &= 0xffffffffu >> (sb + 32 - p.s_end);
+    }
+    if (bits == 0u) {
+      continue;
+    }
+    // the x words of these 32 samples: one coalesced load, handed out by shuffle
+    const uint32_t xrow = x_line[sb + lane];
+    while (bits != 0u) {
+      // up to four samples at a time, so that their d words are in flight together
+      int sidx[4];
+      uint32_t dwv[4];
+      int nb = 0;
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        sidx[t] = -1;
+        if (bits != 0u) {
+          sidx[t] = __ffs(bits) - 1;
+          bits &= bits - 1u;
+          nb = t + 1;
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        dwv[t] = (t < nb && i_ok) ? p.dw[(long long)(sb + sidx[t]) * p.d_size + i] : 0u;
+      }
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        if (t < nb) {
+          const uint32_t xwv = __shfl_sync(0xffffffffu, xrow, sidx[t]);
+          const uint32_t both = xwv & dwv[t];
+          const int n = __popc(both >> 1);
+          if (n != 0) {
+            // equal line signs = decrease (rpu_weight_updater.cpp:246-268)
+            const uint32_t down = (((xwv ^ dwv[t]) & 1u) == 0u) ? 1u : 0u;
+            queue |= (unsigned long long)(((uint32_t)n << 1) | down) << (cnt * USQ_BITS);
+            cnt++;
+          }
+          if (__any_sync(0xffffffffu, cnt >= USQ_SLOTS)) {
+            drain();
+          }
+        }
+      }
+    }
+  }
+  drain();
+  if (i_ok && w != w_in) {
+    p.w[idx] = w;
+  }
+}
+
+template <int KIND>
+static void launchStreamKind(const UpdateProblem &p, const StreamUpdate &st, cudaStream_t stream) {
+  const long long tasks = (long long)((p.d_size + 31) / 32) * p.x_size;
+  const unsigned blocks = (unsigned)((tasks + 7) / 8);
+  if (p.dw_min_std > 0.0f) {
+    pulsedUpdateStreamKernel<KIND, true><<<blocks, 256, 0, stream>>>(p, st);
+  } else {
+    pulsedUpdateStreamKernel<KIND, false><<<blocks, 256, 0, stream>>>(p, st);
+  }
+}
+
+// the same problem in rows of pulse words: a sample has nseg of them
+static UpdateProblem inRows(const UpdateProblem &p0) {
+  UpdateProblem p = p0;
+  const int nseg = p0.nseg > 0 ? p0.nseg : 1;
+  p.m = p0.m * nseg;
+  p.s_begin = p0.s_begin * nseg;
+  p.s_end = p0.s_end * nseg;
+  p.nseg = 1;
+  return p;
+}
+
+static int g_update_path = 0;
+void setUpdatePath(int mode) { g_update_path = mode; }
+
+bool streamUpdateEligible(const UpdateProblem &p) {
+  if (g_update_path == 1 || p.up.pulse_type != AB200_PULSE_STOCHASTIC_COMPRESSED) {
+    return false;
+  }
+  return g_update_path == 2 || p.m * (p.nseg > 0 ? p.nseg : 1) >= kStreamUpdateMinBatch;
+}
+
+void launchPulseTranspose(const UpdateProblem &p0, uint32_t *xwT, uint32_t *xnzT, int m_pad,
+                          cudaStream_t stream) {
+  const UpdateProblem p = inRows(p0);
+  dim3 grid((p.x_size + 31) / 32, m_pad / 32), block(32, 8);
+  pulseTransposeKernel<<<grid, block, 0, stream>>>(p.xw, p.x_size, p.m, m_pad, xwT, xnzT);
+  AB200_LAUNCH_CHECK();
+}
+
+void launchPulsedUpdateStream(const UpdateProblem &p0, const uint32_t *xwT, const uint32_t *xnzT,
+                              int m_pad, cudaStream_t stream) {
+  const UpdateProblem p = inRows(p0);
+  if (p.s_end <= p.s_begin) {
+    return;
+  }
+  StreamUpdate st{xwT, xnzT, m_pad};
+  switch (p.kind) {
+  case AB200_DEVICE_CONSTANT_STEP:
+    launchStreamKind<AB200_DEVICE_CONSTANT_STEP>(p, st, stream);
+    break;
+  case AB200_DEVICE_LINEAR_STEP:
+  case AB200_DEVICE_SOFT_BOUNDS:
+    launchStreamKind<AB200_DEVICE_LINEAR_STEP>(p, st, stream);
+    break;
+  case AB200_DEVICE_SOFT_BOUNDS_REFERENCE:
+    launchStreamKind<AB200_DEVICE_SOFT_BOUNDS_REFERENCE>(p, st, stream);
+    break;
+  case AB200_DEVICE_POW_STEP:
+    launchStreamKind<AB200_DEVICE_POW_STEP>(p, st, stream);
+    break;
+  case AB200_DEVICE_EXP_STEP:
+    launchStreamKind<AB200_DEVICE_EXP_STEP>(p, st, stream);
+    break;
+  default:
+    AB200_FATAL("pulsed update: device kind not implemented");
+  }
+  AB200_LAUNCH_CHECK();
+}
+
 void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream) {
   if (p.m <= 0) {
     return;
-  }
-  if (p.up.pulse_type == AB200_PULSE_STOCHASTIC_COMPRESSED && p.up.desired_bl > 31) {
-    AB200_FATAL("desired_BL > 31 is not implemented for stochastic pulse trains");
   }
   pulsePrepareKernel<<<p.m, 256, 0, stream>>>(p);
   AB200_LAUNCH_CHECK();
@@ -594,16 +860,18 @@ void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream) {
                         p.up.pulse_type == AB200_PULSE_MEAN_COUNT)
                            ? 1
                            : 0;
-  const int n_blk = (p.m + UBLK - 1) / UBLK;
-  pulseNzKernel<<<dim3((p.x_size + 255) / 256, n_blk), 256, 0, stream>>>(p.xw, p.x_size, p.m, p.xnz,
+  const int rows = p.m * (p.nseg > 0 ? p.nseg : 1);
+  const int n_blk = (rows + UBLK - 1) / UBLK;
+  pulseNzKernel<<<dim3((p.x_size + 255) / 256, n_blk), 256, 0, stream>>>(p.xw, p.x_size, rows, p.xnz,
                                                                        implicit);
   AB200_LAUNCH_CHECK();
-  pulseNzKernel<<<dim3((p.d_size + 255) / 256, n_blk), 256, 0, stream>>>(p.dw, p.d_size, p.m, p.dnz,
+  pulseNzKernel<<<dim3((p.d_size + 255) / 256, n_blk), 256, 0, stream>>>(p.dw, p.d_size, rows, p.dnz,
                                                                        implicit);
   AB200_LAUNCH_CHECK();
 }
 
-void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream) {
+void launchPulsedUpdate(const UpdateProblem &p0, cudaStream_t stream) {
+  const UpdateProblem p = inRows(p0);
   if (p.s_end <= p.s_begin) {
     return;
   }
@@ -661,9 +929,13 @@ __global__ void coincidenceKernel(UpdateProblem p, int32_t *counts) {
       p.up.pulse_type == AB200_PULSE_MEAN_COUNT) {
     n = dwv == 0u ? 0 : (int)rintf(__fmul_rn(__uint_as_float(dwv), __uint_as_float(xwv)));
   } else {
-    n = __popc((xwv & dwv) >> 1);
-    if (((xwv ^ dwv) & 1u) != 0u) {
-      n = -n;
+    n = 0;
+    const int nseg = p.nseg > 0 ? p.nseg : 1;
+    for (int g = 0; g < nseg; g++) {
+      xwv = p.xw[(long long)g * p.x_size + j];
+      dwv = p.dw[(long long)g * p.d_size + i];
+      const int c = __popc((xwv & dwv) >> 1);
+      n += ((xwv ^ dwv) & 1u) != 0u ? -c : c;
     }
   }
   counts[t] = n;

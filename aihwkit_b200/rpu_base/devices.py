@@ -174,8 +174,6 @@ class AnalogTileUpdateParameter:
 
     def _to_c(self) -> _cabi.UpdateParams:
         pt = int(self.pulse_type)
-        if pt == int(PulseType.Stochastic):
-            raise RuntimeError("PulseType not supported")
         c = _cabi.UpdateParams()
         c.pulse_type = pt
         c.desired_bl = int(self.desired_bl)

@@ -565,6 +565,11 @@ int ab200_mvm_forward_noalloc(const ab200_io_params *forward_io, const float *w_
  * cores whenever the IO settings allow, 3 = as 2 but never the kernel variant that pairs two
  * CTAs on one 256-row tile. Process-wide; used by tests and benchmarks. */
 int ab200_set_mvm_path(int mode);
+/* Kernel selection of the pulsed update, for tests and benchmarks: 0 = automatic (stochastic pulse
+ * trains with batches of 1024 samples or more stream over the samples of each x-line, everything
+ * else goes through the kernel that stages blocks of samples per weight tile), 1 = always the
+ * staged kernel, 2 = the streaming kernel for every batch size the pulse type allows. */
+int ab200_set_update_path(int mode);
 /* Measurement aid (no counterpart in the reference): AND + population count + add triples per
  * second the device sustains from registers, the integer ceiling that the pair rate of the pulsed
  * update at large batches (x_size * d_size * m_batch word pairs per call) is compared with. */

@@ -83,7 +83,7 @@ def test_softbounds_update_conv_tile_stochastic_statistics():
     from aihwkit_b200.rpu_base import tiles as T
 
     rng = np.random.default_rng(32)
-    x_size, d_size, m = 2304, 256, 512
+    x_size, d_size, m = 2304, 256, 1536  # large enough for the streaming update kernel
     p = H.training_params(noise=True, pulse_det=False)
     dp = H.device("sb", True, dw_min=0.001, w_max=0.6, w_min=-0.6, dw_min_dtod=0.3)
     cfg = p._config(x_size, d_size, dp, seed=5)
@@ -294,3 +294,37 @@ def test_conv_tile_indexed_on_whole_images():
     w_new = t.get_weights().numpy()
     assert np.abs(w_new - w0).max() > 0
     assert np.abs(w_new - w1).max() <= 1e-6
+
+
+@pytest.mark.parametrize("kind,x_size,d_size,m", [("sb", 2304, 256, 1536), ("cs", 300, 100, 70),
+                                                  ("sbr", 256, 256, 1100)])
+def test_streaming_update_equals_staged_update(kind, x_size, d_size, m):
+    """The two kernels of the stochastic pulsed update - blocks of samples staged per weight tile,
+    and the stream over the samples of each x-line that large batches take - see the same pulse
+    trains (same noise key and call counter) and apply the same pulses in the same per-weight
+    order: without device noise their results are identical bit for bit."""
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import tiles as T
+
+    lib = _cabi.lib()
+    rng = np.random.default_rng(x_size)
+    p = H.training_params(noise=True, pulse_det=False)
+    dp = H.device(kind, False, dw_min=0.001, dw_min_dtod=0.3)  # per-element spread, no pulse noise
+    cfg = p._config(x_size, d_size, dp, seed=5)
+    W0 = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    X = np.maximum(rng.standard_normal((m, x_size)), 0).astype(np.float32)
+    Dm = rng.normal(0, 0.05, (m, d_size)).astype(np.float32)
+    results = []
+    try:
+        for mode in (1, 2):
+            _cabi.check(lib.ab200_set_update_path(mode))
+            t = T.AnalogTile(cfg, cuda_device=0)
+            t.set_weights(torch.from_numpy(W0))
+            t.set_learning_rate(0.02)
+            for _ in range(2):
+                t.update(_gpu(X), _gpu(Dm))
+            results.append(t.get_weights().numpy())
+    finally:
+        _cabi.check(lib.ab200_set_update_path(0))
+    assert np.abs(results[0] - W0).max() > 0
+    assert np.array_equal(results[0], results[1])

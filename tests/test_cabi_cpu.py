@@ -122,9 +122,8 @@ def test_unsupported_settings_raise():
     with pytest.raises(RuntimeError, match="ir_drop"):
         p._config(4, 4, D.ConstantStepResistiveDeviceParameter())
     p = D.AnalogTileParameter()
-    p.update.pulse_type = D.PulseType.Stochastic
-    with pytest.raises(RuntimeError, match="PulseType not supported"):
-        p._config(4, 4, D.ConstantStepResistiveDeviceParameter())
+    p.update.pulse_type = D.PulseType.Stochastic  # separate +- trains: same law as the compressed type
+    T.AnalogTile(p._config(4, 4, D.ConstantStepResistiveDeviceParameter()))
     p = D.AnalogTileParameter()
     p.forward_io.inp_bound = 2.0  # noise management expects bound == 1
     with pytest.raises(RuntimeError, match="expects bound==1"):

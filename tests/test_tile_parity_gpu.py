@@ -509,3 +509,49 @@ def test_mean_count_pulse_type(kind, bl, ubl):
     W_new = t.get_weights().numpy()
     assert np.abs(W_new - W).max() > 1e-3
     assert np.abs(W_new - W_or).max() <= 1e-6
+
+
+@pytest.mark.parametrize("pulse_type", ["long_trains", "separate_sign_trains"])
+def test_stochastic_update_long_trains_and_separate_sign_trains(pulse_type):
+    """Pulse trains longer than one 32-bit word (desired_BL 80, learning rate large enough that
+    update management asks for about 50 slots) and the `Stochastic` pulse type (separate trains
+    for positive and negative lines): mean and spread of the weight change per element agree with
+    the oracle's loop over the pulse slots."""
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(23)
+    x_size, d_size, m, reps = 24, 20, 6, 150
+    p = H.training_params(noise=True, pulse_det=False)
+    if pulse_type == "long_trains":
+        p.update.desired_bl = 80
+        lr = 0.5
+    else:
+        p.update.pulse_type = D.PulseType.Stochastic
+        lr = 0.05
+    dp = H.device("cs", True)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    W0 = rng.uniform(-0.2, 0.2, (d_size, x_size)).astype(np.float32)
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    up = O.Up.from_c(cfg.update)
+    up.pulse_type = O.PULSE_STOCHASTIC_COMPRESSED  # the oracle's compressed trains: same law
+    if pulse_type == "long_trains":
+        xm, dmx = np.abs(X).max(axis=1), np.abs(Dm).max(axis=1)
+        assert (np.ceil(lr * xm * dmx / dp.dw_min) > 31).mean() > 0.5  # trains of more than one word
+    hp = t.get_hidden_parameters().numpy()
+    dev = O.DeviceArrays.from_hidden(O.DEV_CONSTANT_STEP, t.get_hidden_parameter_names(), hp,
+                                     dp.dw_min_std, True)
+    t.set_learning_rate(lr)
+    xg, dg = torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda()
+    dws, dwo = [], []
+    org = np.random.default_rng(7)
+    for _ in range(reps):
+        t.set_weights(torch.from_numpy(W0))
+        Wc = t.get_weights().numpy()
+        t.update(xg, dg)
+        dws.append(t.get_weights().numpy() - Wc)
+        Wo = Wc.copy()
+        O.update(Wo, X, Dm, lr, dp.dw_min, up, dev, org)
+        dwo.append(Wo - Wc)
+    dws, dwo = np.stack(dws), np.stack(dwo)
+    H.assert_moments_agree(dws, dwo)
+    assert np.abs(dws).max() > 0
