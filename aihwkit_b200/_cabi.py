@@ -227,6 +227,7 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_last_bm_stats": (_I, [_VP, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
         "ab200_tile_set_seed": (_I, [_VP, C.c_uint64]),
         "ab200_array_create": (_I, [cfgp, _I, _I, _I, _I, _I, _I, _I, C.POINTER(_VP)]),
+        "ab200_array_create_block": (_I, [cfgp, _I, _I, _I, _I, _I, _I, _I, _I, _I, C.POINTER(_VP)]),
         "ab200_array_destroy": (_I, [_VP]),
         "ab200_array_num_in_splits": (_I, [_VP]),
         "ab200_array_num_out_splits": (_I, [_VP]),

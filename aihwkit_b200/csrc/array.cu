@@ -24,7 +24,7 @@ std::vector<int> splitSizes(int size, int split_max) {
 // how many ranks it is spread over.
 
 TileArray::TileArray(const ab200_tile_config &cfg, int out_size, int in_size, int max_out,
-                     int max_in, int in_begin, int in_end, int cuda_device)
+                     int max_in, int in_begin, int in_end, int cuda_device, int out_begin, int out_end)
     : out_size_(out_size), in_size_(in_size), device_(cuda_device) {
   if (out_size <= 0 || in_size <= 0) {
     AB200_FATAL("array sizes must be positive");
@@ -49,9 +49,17 @@ TileArray::TileArray(const ab200_tile_config &cfg, int out_size, int in_size, in
   }
   in_begin_ = in_begin;
   in_end_ = in_end;
+  if (out_end < 0) {
+    out_end = (int)out_sizes_.size();
+  }
+  if (out_begin < 0 || out_begin > out_end || out_end > (int)out_sizes_.size()) {
+    AB200_FATAL("array: invalid out-split range [" << out_begin << ", " << out_end << ")");
+  }
+  out_begin_ = out_begin;
+  out_end_ = out_end;
   uint64_t seed = cfg.seed ? cfg.seed : 0x1234567ull;
   for (int ii = in_begin_; ii < in_end_; ii++) {
-    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
+    for (int oi = out_begin_; oi < out_end_; oi++) {
       ab200_tile_config c = cfg;
       c.x_size = in_sizes_[ii];
       c.d_size = out_sizes_[oi];
@@ -86,20 +94,18 @@ TileArray::~TileArray() {
 }
 
 void TileArray::setSeed(uint64_t seed) {
-  for (int ii = in_begin_; ii < in_end_; ii++) {
-    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
-      tile(ii - in_begin_, oi).setSeed(seed ? seed : 0x1234567ull);
-    }
+  for (auto &t : tiles_) {
+    t->setSeed(seed ? seed : 0x1234567ull);
   }
 }
 
 void TileArray::setWeights(const float *w_host, float omega) {
   std::vector<float> buf;
-  const int n_out = (int)out_sizes_.size();
+  const int n_out = nOutLocal();
   tile_scale_host_.assign((size_t)(in_end_ - in_begin_) * n_out, 1.0f);
   scaled_ = omega > 0.0f;
   for (int ii = in_begin_; ii < in_end_; ii++) {
-    for (int oi = 0; oi < n_out; oi++) {
+    for (int oi = out_begin_; oi < out_end_; oi++) {
       int xs = in_sizes_[ii], ds = out_sizes_[oi];
       buf.resize((size_t)xs * ds);
       float amax = 0.0f;
@@ -118,9 +124,9 @@ void TileArray::setWeights(const float *w_host, float omega) {
         for (float &v : buf) {
           v /= alpha;
         }
-        tile_scale_host_[(size_t)(ii - in_begin_) * n_out + oi] = alpha;
+        tile_scale_host_[(size_t)(ii - in_begin_) * n_out + (oi - out_begin_)] = alpha;
       }
-      tile(ii - in_begin_, oi).setWeights(buf.data());
+      tile(ii - in_begin_, oi - out_begin_).setWeights(buf.data());
     }
   }
   if (!tile_scale_host_.empty()) {
@@ -149,12 +155,12 @@ void TileArray::setBias(const float *bias_host) {
 void TileArray::getWeights(float *w_host) {
   std::vector<float> buf;
   for (int ii = in_begin_; ii < in_end_; ii++) {
-    for (int oi = 0; oi < (int)out_sizes_.size(); oi++) {
+    for (int oi = out_begin_; oi < out_end_; oi++) {
       int xs = in_sizes_[ii], ds = out_sizes_[oi];
       buf.resize((size_t)xs * ds);
-      tile(ii - in_begin_, oi).getWeights(buf.data());
+      tile(ii - in_begin_, oi - out_begin_).getWeights(buf.data());
       if (scaled_) {
-        const float alpha = tile_scale_host_[(size_t)(ii - in_begin_) * out_sizes_.size() + oi];
+        const float alpha = tile_scale_host_[(size_t)(ii - in_begin_) * nOutLocal() + (oi - out_begin_)];
         for (float &v : buf) {
           v *= alpha;
         }
@@ -167,12 +173,15 @@ void TileArray::getWeights(float *w_host) {
   }
 }
 
-// digital bias of the layer, for the path that runs the tiles one by one
+// digital bias of the layer, for the path that runs the tiles one by one: y[r * ld + c] += bias[c]
+// for a block of `cols` columns
 __global__ void __launch_bounds__(256)
-    addBiasKernel(float *y, const float *bias, long long n, int out_size) {
+    addBiasBlockKernel(float *y, long long ld, const float *bias, int cols, long long n) {
   const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (t < n) {
-    y[t] += bias[t % out_size];
+    const long long r = t / cols;
+    const int c = (int)(t - r * cols);
+    y[r * ld + c] += bias[c];
   }
 }
 
@@ -200,29 +209,36 @@ void TileArray::forwardImpl(const float *x0, long long x_ss, float *y, int m, cu
   if (m <= 0) {
     return;
   }
-  if (in_begin_ == in_end_) {
+  if (in_begin_ == in_end_ || out_begin_ == out_end_) {
     AB200_CUDA(cudaMemsetAsync(y, 0, (size_t)m * out_size_ * sizeof(float), s));
     return;
+  }
+  if (!ownsAllOutSplits()) {
+    // a shard's contribution to the sum over all shards: zero outside its own columns
+    AB200_CUDA(cudaMemsetAsync(y, 0, (size_t)m * out_size_ * sizeof(float), s));
   }
   if (tcEligible(m)) {
     forwardTc(x0, x_ss, y, m, s);
     return;
   }
-  const int n_out = (int)out_sizes_.size();
+  const int n_out = (int)out_sizes_.size(), n_ol = nOutLocal();
   for (int ii = in_begin_; ii < in_end_; ii++) {
-    for (int oi = 0; oi < n_out; oi++) {
+    for (int oi = out_begin_; oi < out_end_; oi++) {
       const float alpha =
-          scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_out + oi] : 1.0f;
-      tile(ii - in_begin_, oi)
+          scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_ol + (oi - out_begin_)] : 1.0f;
+      tile(ii - in_begin_, oi - out_begin_)
           .forwardStrided(x0 + (in_off_[ii] - in_off_[in_begin_]), x_ss, y + out_off_[oi],
                           out_size_, m,
                           /*accumulate=*/ii != in_begin_,
                           (uint32_t)(ii * n_out + oi), alpha, s);
     }
   }
-  if (bias_dev_) {
-    const long long n = (long long)m * out_size_;
-    addBiasKernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, bias_dev_, n, out_size_);
+  // the digital bias enters the sum over the shards once: with the shard of the first in-split
+  if (bias_dev_ && in_begin_ == 0) {
+    const int c0 = out_off_[out_begin_];
+    const int cols = (out_end_ < (int)out_sizes_.size() ? out_off_[out_end_] : out_size_) - c0;
+    addBiasBlockKernel<<<(unsigned)(((long long)m * cols + 255) / 256), 256, 0, s>>>(
+        y + c0, out_size_, bias_dev_ + c0, cols, (long long)m * cols);
     AB200_LAUNCH_CHECK();
   }
 }
@@ -270,7 +286,8 @@ void TileArray::forwardScatter(const float *x_local, int m, float *const *out_ta
 }
 
 bool TileArray::scatterCodesSupported() {
-  if (in_begin_ == in_end_ || scaled_ || bias_dev_ != nullptr || (out_size_ & 31) != 0) {
+  if (in_begin_ == in_end_ || !ownsAllOutSplits() || scaled_ || bias_dev_ != nullptr ||
+      (out_size_ & 31) != 0) {
     return false;
   }
   for (int n : out_sizes_) {
@@ -301,6 +318,9 @@ void TileArray::forwardScatterPlan(const float *x_local, int m, const ab200_scat
   const bool codes = plan.code_table_dev != nullptr;
   if (in_begin_ == in_end_) {
     AB200_FATAL("forward_scatter: this shard owns no in-split");
+  }
+  if (!ownsAllOutSplits()) {
+    AB200_FATAL("forward_scatter: the shard has to own all out-splits of its in-splits");
   }
   if ((plan.out_table_dev != nullptr) == codes) {
     AB200_FATAL("forward_scatter: give either the fp32 buffers or the code and factor buffers");
@@ -347,15 +367,16 @@ void TileArray::backward(const float *d, float *x_grad, int m, cudaStream_t s) {
     return;
   }
   AB200_CUDA(cudaSetDevice(device_));
-  const int n_out = (int)out_sizes_.size();
+  const int n_out = (int)out_sizes_.size(), n_ol = nOutLocal();
   for (int ii = in_begin_; ii < in_end_; ii++) {
-    for (int oi = 0; oi < n_out; oi++) {
-      const float alpha = scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_out + oi] : 1.0f;
+    for (int oi = out_begin_; oi < out_end_; oi++) {
+      const float alpha =
+          scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_ol + (oi - out_begin_)] : 1.0f;
       long long ld = 0;
       // pre_backward: the gradient is multiplied by the mapping scale before the tile sees it
       const float *dt = scaledGradient(d, oi, m, alpha, ld, s);
-      tile(ii - in_begin_, oi)
-          .backwardStrided(dt, ld, x_grad + in_off_[ii], in_size_, m, /*accumulate=*/oi != 0,
+      tile(ii - in_begin_, oi - out_begin_)
+          .backwardStrided(dt, ld, x_grad + in_off_[ii], in_size_, m, /*accumulate=*/oi != out_begin_,
                            (uint32_t)(ii * n_out + oi), 1.0f, s);
     }
   }
@@ -366,14 +387,15 @@ void TileArray::update(const float *x, const float *d, int m, cudaStream_t s) {
     return;
   }
   AB200_CUDA(cudaSetDevice(device_));
-  const int n_out = (int)out_sizes_.size();
+  const int n_ol = nOutLocal();
   for (int ii = in_begin_; ii < in_end_; ii++) {
-    for (int oi = 0; oi < n_out; oi++) {
-      const float alpha = scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_out + oi] : 1.0f;
+    for (int oi = out_begin_; oi < out_end_; oi++) {
+      const float alpha =
+          scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_ol + (oi - out_begin_)] : 1.0f;
       long long ld = 0;
       // pre_update: the gradient is divided by the mapping scale
       const float *dt = scaledGradient(d, oi, m, 1.0f / alpha, ld, s);
-      tile(ii - in_begin_, oi).updateStrided(x + in_off_[ii], in_size_, dt, ld, m, s);
+      tile(ii - in_begin_, oi - out_begin_).updateStrided(x + in_off_[ii], in_size_, dt, ld, m, s);
     }
   }
 }
@@ -399,16 +421,18 @@ bool TileArray::tcEligible(int m) {
 // All local tiles in one launch: the DAC kernel quantises every (row, in-split) once, the MMA
 // kernel walks the in-splits per 128 x 128 output block and sums them after each tile's ADC.
 void TileArray::forwardTc(const float *x0, long long x_ss, float *y, int m, cudaStream_t s) {
-  const int n_in = in_end_ - in_begin_, n_out = (int)out_sizes_.size();
+  const int n_in = in_end_ - in_begin_, n_out = nOutLocal(), n_out_total = (int)out_sizes_.size();
   if (!tc_) {
     tc_.reset(new TcEngine(device_));
     tc_->configure(std::vector<int>(in_sizes_.begin() + in_begin_, in_sizes_.begin() + in_end_),
-                   out_sizes_);
+                   std::vector<int>(out_sizes_.begin() + out_begin_, out_sizes_.begin() + out_end_));
     tc_versions_.assign((size_t)n_in * n_out, 0);
   }
   TcEngine::Run r;
   r.key = tile(0, 0).noiseKey();
-  r.noise_id0 = (uint32_t)(in_begin_ * n_out);
+  // tile (i, o) of the whole layer draws from stream i * n_out_total + o, whatever the shard
+  r.noise_id0 = (uint32_t)(in_begin_ * n_out_total + out_begin_);
+  r.noise_stride = n_out_total;
   for (int il = 0; il < n_in; il++) {
     for (int oi = 0; oi < n_out; oi++) {
       Tile &t = tile(il, oi);
@@ -428,11 +452,13 @@ void TileArray::forwardTc(const float *x0, long long x_ss, float *y, int m, cuda
   r.in = x0;
   r.in_ss = x_ss;
   r.m = m;
-  r.out = y;
+  const int c0 = out_off_[out_begin_];
+  r.out = y ? y + c0 : nullptr;
   r.out_ss = out_size_;
   r.io = tiles_[0]->fio();
   r.tile_scale = scaled_ ? tile_scale_dev_ : nullptr;
-  r.bias = bias_dev_;
+  // the digital bias enters the sum over the shards once: with the shard of the first in-split
+  r.bias = (bias_dev_ && in_begin_ == 0) ? bias_dev_ + c0 : nullptr;
   if (plan_) {
     r.out_table = plan_->out_table_dev;
     r.code_table = plan_->code_table_dev;

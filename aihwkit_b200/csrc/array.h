@@ -15,8 +15,10 @@ std::vector<int> splitSizes(int size, int split_max);
 
 class TileArray {
 public:
+  // [in_begin, in_end) x [out_begin, out_end): the in-splits and out-splits this object
+  // materialises (a shard of the layer); an end of -1 means "to the last one"
   TileArray(const ab200_tile_config &cfg, int out_size, int in_size, int max_out, int max_in,
-            int in_begin, int in_end, int cuda_device);
+            int in_begin, int in_end, int cuda_device, int out_begin = 0, int out_end = -1);
   ~TileArray();
   std::mutex &mutex() const { return mu_; }
   int numInSplits() const { return (int)in_sizes_.size(); }
@@ -62,10 +64,14 @@ public:
 
 private:
   mutable std::mutex mu_; // held by every C-ABI call on this array
-  Tile &tile(int in_local, int out_idx) { return *tiles_[(size_t)in_local * out_sizes_.size() + out_idx]; }
+  // in_local / out_local count from in_begin_ / out_begin_
+  Tile &tile(int in_local, int out_local) { return *tiles_[(size_t)in_local * nOutLocal() + out_local]; }
+  int nOutLocal() const { return out_end_ - out_begin_; }
+  bool ownsAllOutSplits() const { return out_begin_ == 0 && out_end_ == (int)out_sizes_.size(); }
   int out_size_, in_size_, device_;
   std::vector<int> in_sizes_, out_sizes_, in_off_, out_off_;
   int in_begin_, in_end_;
+  int out_begin_ = 0, out_end_ = 0;
   std::vector<std::unique_ptr<Tile>> tiles_;
   // one tensor-core engine for all locally owned tiles; operands are refreshed per tile when
   // that tile's weights changed

@@ -426,6 +426,23 @@ int ab200_array_create(const ab200_tile_config *cfg, int out_size, int in_size,
                                                        in_split_end, cuda_device));
   AB200_CATCH
 }
+int ab200_array_create_block(const ab200_tile_config *cfg, int out_size, int in_size,
+                             int max_output_size, int max_input_size, int in_split_begin,
+                             int in_split_end, int out_split_begin, int out_split_end,
+                             int cuda_device, ab200_array **out) {
+  AB200_TRY
+  if (!cfg || !out) {
+    AB200_FATAL("null argument");
+  }
+  if (cuda_device < 0) {
+    AB200_FATAL("the mapped-tile array needs a CUDA device");
+  }
+  *out = reinterpret_cast<ab200_array *>(new TileArray(*cfg, out_size, in_size, max_output_size,
+                                                       max_input_size, in_split_begin, in_split_end,
+                                                       cuda_device, out_split_begin, out_split_end));
+  AB200_CATCH
+}
+
 int ab200_array_destroy(ab200_array *arr) {
   AB200_TRY
   delete reinterpret_cast<TileArray *>(arr);

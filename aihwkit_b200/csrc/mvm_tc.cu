@@ -72,6 +72,7 @@ enum : int {
 
 struct TcKernelParams {
   int m, I, O, n_chunks, nrows_pad, kpad;
+  int noise_stride; // tile (i, o) draws from noise stream noise_id0 + i * noise_stride + o
   int group; // chunks per group of the work-item order
   const int4 *chunk;   // {o, n_local0, n_global0, valid}
   const int4 *insplit; // {k0 (code column), n_k_stages, K_i, in_off}
@@ -645,7 +646,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           fac_n *= p.tile_scale[(i + 1) * p.O + ch.x];
         }
       }
-      const uint32_t tile_tag = tag + p.noise_id0 + (uint32_t)(i * p.O + ch.x);
+      const uint32_t tile_tag = tag + p.noise_id0 + (uint32_t)(i * p.noise_stride + ch.x);
       // the whole warp agrees on the outcome: what follows is warp-collective
       if (!__all_sync(0xffffffffu,
                       TC_TIMED_WAIT(w_tfull, mbarWait(&tmem_full[b], (ai / TC_ACC_STAGES) & 1, abort_flag)))) {
@@ -1491,6 +1492,7 @@ void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
   p.key = r.key;
   p.call = r.call;
   p.noise_id0 = r.noise_id0;
+  p.noise_stride = r.noise_stride > 0 ? r.noise_stride : O;
   p.scale = d.scale;
   p.factor = d.factor;
   p.vnorm = d.vnorm;

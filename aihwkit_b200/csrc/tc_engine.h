@@ -43,6 +43,10 @@ public:
     PhiloxKey key{0, 0};
     uint32_t call = 0;
     uint32_t noise_id0 = 0;
+    // tile (i, o) of this engine draws from stream noise_id0 + i * noise_stride + o; 0 = the
+    // engine's own number of out-splits (an engine that holds a block of a larger layer passes
+    // the layer's)
+    int noise_stride = 0;
     // optional digital periphery of a mapped layer (device pointers): one scale per tile,
     // [I][O], applied to that tile's output before the sum over in-splits, and a bias per output
     // column added once

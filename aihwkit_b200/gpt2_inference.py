@@ -14,9 +14,16 @@ Embeddings, LayerNorm, attention, GELU, residuals and the vocabulary projection 
 as they are digital in the reference too (``AnalogLinear`` only replaces ``nn.Linear``,
 src/aihwkit/nn/conversion.py).
 
-Sequences are independent, so N ranks each take ``batch / N`` sequences and hold all tiles; there
-is no collective on the data path.  Prints one JSON line (rank 0): tokens/s of the whole forward,
-the share of the analog layers, and their logical TFLOP/s.
+Two ways to use N ranks (``--shard``):
+  ``sequences`` (default): sequences are independent, so every rank takes ``batch / N`` sequences
+      and holds all tiles; no collective on the data path.
+  ``tiles``: the tiles of every analog layer are dealt to the ranks - over the in-splits first,
+      over the out-splits where a layer has fewer in-splits than ranks (768 -> 2 in-splits) - every
+      rank computes the partial output of its block of tiles for ALL tokens, and one NCCL
+      all-reduce per layer adds the partial outputs up (``TileModuleArray``'s ``result.add_`` over
+      in-splits, tiles/array.py:173-176, across GPUs).  The digital parts run replicated.
+Prints one JSON line (rank 0): tokens/s of the whole forward, the share of the analog layers, and
+their logical TFLOP/s.
 """
 
 from __future__ import annotations
@@ -56,12 +63,25 @@ class AnalogLinear:
     inside the mapped layer's kernels, so a layer is two launches (DAC, MVM)."""
 
     def __init__(self, in_features: int, out_features: int, device: int, seed: int,
-                 gen: torch.Generator, max_tile: int = 512):
+                 gen: torch.Generator, max_tile: int = 512, shard_tiles: bool = False):
         from .rpu_base import tiles as T
+        from .sharded import ShardedTileArray
 
         w = torch.randn(out_features, in_features, generator=gen) * 0.02
-        self.array = T.TileArray(inference_config(seed, max_tile), out_features, in_features,
-                                 max_tile, max_tile, cuda_device=device)
+        cfg = inference_config(seed, max_tile)
+        self.sharded = None
+        if shard_tiles:
+            # this rank's block of the layer's tiles; the ranks' partial outputs are all-reduced
+            self.sharded = ShardedTileArray(
+                out_features, in_features, max_tile, max_tile,
+                lambda b, e, ob, oe: T.TileArray(cfg, out_features, in_features, max_tile, max_tile,
+                                                 cuda_device=device, in_split_range=(b, e),
+                                                 out_split_range=(ob, oe)),
+                two_d=True)
+            self.array = self.sharded.local
+        else:
+            self.array = T.TileArray(cfg, out_features, in_features, max_tile, max_tile,
+                                     cuda_device=device)
         self.array.set_seed(seed)
         self.array.set_weights(w, weight_scaling_omega=1.0)
         self.array.set_bias(torch.zeros(out_features))
@@ -73,19 +93,22 @@ class AnalogLinear:
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         y = self.array.forward(x.reshape(-1, self.in_features), is_test=True, non_blocking=True)
+        if self.sharded is not None:
+            y = self.sharded.reduce(y, dst=None)  # all-reduce of the shards' partial outputs
         return y.reshape(*x.shape[:-1], self.out_features)
 
 
 class Block:
-    def __init__(self, d_model: int, n_head: int, device: int, seed: int, gen: torch.Generator):
+    def __init__(self, d_model: int, n_head: int, device: int, seed: int, gen: torch.Generator,
+                 shard_tiles: bool = False):
         dev = f"cuda:{device}"
         self.n_head = n_head
         self.ln1_w, self.ln1_b = torch.ones(d_model, device=dev), torch.zeros(d_model, device=dev)
         self.ln2_w, self.ln2_b = torch.ones(d_model, device=dev), torch.zeros(d_model, device=dev)
-        self.qkv = AnalogLinear(d_model, 3 * d_model, device, seed + 1, gen)
-        self.proj = AnalogLinear(d_model, d_model, device, seed + 2, gen)
-        self.fc = AnalogLinear(d_model, 4 * d_model, device, seed + 3, gen)
-        self.fc_out = AnalogLinear(4 * d_model, d_model, device, seed + 4, gen)
+        self.qkv = AnalogLinear(d_model, 3 * d_model, device, seed + 1, gen, shard_tiles=shard_tiles)
+        self.proj = AnalogLinear(d_model, d_model, device, seed + 2, gen, shard_tiles=shard_tiles)
+        self.fc = AnalogLinear(d_model, 4 * d_model, device, seed + 3, gen, shard_tiles=shard_tiles)
+        self.fc_out = AnalogLinear(4 * d_model, d_model, device, seed + 4, gen, shard_tiles=shard_tiles)
 
     def linears(self) -> List[AnalogLinear]:
         return [self.qkv, self.proj, self.fc, self.fc_out]
@@ -116,14 +139,15 @@ def timed(timer, fn, x):
 
 class AnalogGPT2:
     def __init__(self, n_layer: int = 12, d_model: int = 768, n_head: int = 12, device: int = 0,
-                 seed: int = 4):
+                 seed: int = 4, shard_tiles: bool = False):
         gen = torch.Generator().manual_seed(seed)
         dev = f"cuda:{device}"
         self.device = dev
         self.d_model = d_model
         self.wte = (torch.randn(VOCAB, d_model, generator=gen) * 0.02).to(dev)
         self.wpe = (torch.randn(N_POS, d_model, generator=gen) * 0.01).to(dev)
-        self.blocks = [Block(d_model, n_head, device, seed * 1000 + 10 * i, gen) for i in range(n_layer)]
+        self.blocks = [Block(d_model, n_head, device, seed * 1000 + 10 * i, gen, shard_tiles)
+                       for i in range(n_layer)]
         self.lnf_w, self.lnf_b = torch.ones(d_model, device=dev), torch.zeros(d_model, device=dev)
 
     def forward(self, ids: torch.Tensor, timer=None) -> torch.Tensor:
@@ -155,6 +179,8 @@ def main(argv=None):
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--shard", default="sequences", choices=["sequences", "tiles"],
+                    help="N > 1: split the sequences over the ranks, or the tiles of every analog layer")
     args = ap.parse_args(argv)
 
     import torch.distributed as dist
@@ -169,16 +195,17 @@ def main(argv=None):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    if args.batch % world:
+    shard_tiles = world > 1 and args.shard == "tiles"
+    if args.batch % world and not shard_tiles:
         raise SystemExit("--batch must be a multiple of the number of ranks")
-    local_batch = args.batch // world
-    model = AnalogGPT2(args.layers, device=local_rank, seed=4)
+    local_batch = args.batch if shard_tiles else args.batch // world
+    model = AnalogGPT2(args.layers, device=local_rank, seed=4, shard_tiles=shard_tiles)
     k = 0
-    for blk in model.blocks:  # independent noise per layer and rank
+    for blk in model.blocks:  # independent noise per layer (and per rank when ranks hold replicas)
         for lin in blk.linears():
-            lin.array.set_seed(100003 * (rank + 1) + k)
+            lin.array.set_seed((1 if shard_tiles else 100003 * (rank + 1)) + k)
             k += 1
-    g = torch.Generator().manual_seed(4 + rank)
+    g = torch.Generator().manual_seed(4 + (0 if shard_tiles else rank))
     ids_host = torch.randint(0, VOCAB, (local_batch, args.seq), generator=g).pin_memory()
     out_host = torch.empty(local_batch, args.seq, dtype=torch.long).pin_memory()
     ids = ids_host.to(model.device)
@@ -221,16 +248,19 @@ def main(argv=None):
         analog_ms = sum(a.elapsed_time(b) for a, b in timer)
     tokens = args.batch * args.seq
     if rank == 0:
-        flops = model.analog_flops_per_token() * local_batch * args.seq
+        flops = model.analog_flops_per_token() * local_batch * args.seq / (world if shard_tiles else 1)
         print(json.dumps({
             "metric": "analog_inference_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "dtype": "f32 (analog layers: DAC codes x split-bf16 weights, f32 accumulate)",
             "data": "synthetic",
             "config": {"workload": f"GPT-2-small-shaped forward, {args.layers} blocks, batch {args.batch} x seq {args.seq}",
-                       "analog_tiles": model.n_tiles(), "parallelism": f"sequences over {world} rank(s)"},
+                       "analog_tiles": model.n_tiles(), "parallelism": (f"tiles of every analog layer over {world} rank(s), all-reduce of the "
+                                       "partial outputs, digital parts replicated" if shard_tiles
+                                       else f"sequences over {world} rank(s)")},
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": ids_host.numel() * 8 * world, "d2h_bytes_per_step": out_host.numel() * 8 * world},
+                    "h2d_bytes_per_step": ids_host.numel() * 8 * (1 if shard_tiles else world),
+                    "d2h_bytes_per_step": out_host.numel() * 8 * (1 if shard_tiles else world)},
             "analog_layers": {"ms_per_step": analog_ms, "share": analog_ms / ms,
                               "logical_tflops": flops / (analog_ms * 1e-3) / 1e12},
             "gpu_launches": int(launches),

@@ -735,19 +735,23 @@ class CudaFloatingPointTile(FloatingPointTile):
 class TileArray:
     """Native mapped-tile layer (``TileModuleArray``, src/aihwkit/simulator/tiles/array.py:30-198).
 
-    ``in_split_range`` selects the in-splits this process materialises (sharded layer)."""
+    ``in_split_range`` / ``out_split_range`` select the in-splits and out-splits this process
+    materialises (a shard of the layer: the partial sums of the shards add up to the layer's
+    output; a shard writes zeros outside its own output columns)."""
 
     def __init__(self, config: _cabi.TileConfig, out_size: int, in_size: int,
                  max_output_size: int, max_input_size: int, cuda_device: int = 0,
-                 in_split_range=None):
+                 in_split_range=None, out_split_range=None):
         self._lib = _cabi.lib()
         self.out_size, self.in_size = int(out_size), int(in_size)
         begin, end = (0, -1) if in_split_range is None else in_split_range
+        obegin, oend = (0, -1) if out_split_range is None else out_split_range
         h = C.c_void_p()
         check(
-            self._lib.ab200_array_create(
+            self._lib.ab200_array_create_block(
                 C.byref(config), self.out_size, self.in_size, int(max_output_size),
-                int(max_input_size), int(begin), int(end), int(cuda_device), C.byref(h),
+                int(max_input_size), int(begin), int(end), int(obegin), int(oend),
+                int(cuda_device), C.byref(h),
             )
         )
         self._h = h

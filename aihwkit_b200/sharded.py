@@ -42,6 +42,25 @@ def column_range(in_size: int, split_max: int, rank: int, world: int) -> Tuple[i
     return sum(sizes[:b]), sum(sizes[:e])
 
 
+def tile_grid(n_in_splits: int, n_out_splits: int, world: int) -> Tuple[int, int]:
+    """Ranks along the in-splits and along the out-splits, ``(g_in, g_out)`` with ``g_in * g_out
+    == world``: as many ranks as possible share the in-splits (their partial sums are the only
+    thing that has to be added up), the rest divide the out-splits."""
+    g_in = 1
+    for g in range(1, world + 1):
+        if world % g == 0 and g <= max(1, n_in_splits):
+            g_in = g
+    return g_in, world // g_in
+
+
+def block_of_rank(n_in_splits: int, n_out_splits: int, rank: int, world: int):
+    """The block of tiles of ``rank`` in the 2-D map: ``((in_begin, in_end), (out_begin, out_end))``;
+    ranks sit in-split-major (``rank = r_in * g_out + r_out``). A block may be empty."""
+    g_in, g_out = tile_grid(n_in_splits, n_out_splits, world)
+    r_in, r_out = divmod(rank, g_out)
+    return in_split_range(n_in_splits, r_in, g_in), in_split_range(n_out_splits, r_out, g_out)
+
+
 class ShardedTileArray:
     """One rank's share of a mapped analog layer plus the partial-sum collective.
 
@@ -49,7 +68,10 @@ class ShardedTileArray:
     (``aihwkit_b200.rpu_base.tiles.TileArray`` on a GPU; any callable stand-in in CPU tests)."""
 
     def __init__(self, out_size: int, in_size: int, max_output_size: int, max_input_size: int,
-                 local_factory, group: Optional[dist.ProcessGroup] = None):
+                 local_factory, group: Optional[dist.ProcessGroup] = None, two_d: bool = False):
+        """``two_d``: map the tiles onto a grid of ranks over in-splits AND out-splits
+        (:func:`tile_grid`) - for layers with fewer in-splits than ranks; ``local_factory`` is
+        then called as ``local_factory(in_begin, in_end, out_begin, out_end)``."""
         self.out_size, self.in_size = out_size, in_size
         self.group = group
         self.distributed = dist.is_available() and dist.is_initialized()
@@ -57,12 +79,18 @@ class ShardedTileArray:
         self.world = dist.get_world_size(group) if self.distributed else 1
         self.in_sizes = split_sizes(in_size, max_input_size)
         self.out_sizes = split_sizes(out_size, max_output_size)
-        self.begin, self.end = in_split_range(len(self.in_sizes), self.rank, self.world)
-        self.local = local_factory(self.begin, self.end)
+        if two_d:
+            (self.begin, self.end), (self.out_begin, self.out_end) = block_of_rank(
+                len(self.in_sizes), len(self.out_sizes), self.rank, self.world)
+            self.local = local_factory(self.begin, self.end, self.out_begin, self.out_end)
+        else:
+            self.begin, self.end = in_split_range(len(self.in_sizes), self.rank, self.world)
+            self.out_begin, self.out_end = 0, len(self.out_sizes)
+            self.local = local_factory(self.begin, self.end)
 
     @property
     def n_local_tiles(self) -> int:
-        return (self.end - self.begin) * len(self.out_sizes)
+        return (self.end - self.begin) * (self.out_end - self.out_begin)
 
     def forward_partial(self, x: torch.Tensor, **kw) -> torch.Tensor:
         return self.local.forward(x, **kw)

@@ -399,6 +399,15 @@ int ab200_tile_set_seed(ab200_tile *tile, uint64_t seed);
 int ab200_array_create(const ab200_tile_config *cfg, int out_size, int in_size,
                        int max_output_size, int max_input_size, int in_split_begin,
                        int in_split_end, int cuda_device, ab200_array **out);
+/* The same for a block of the layer's tiles, in-splits [in_split_begin, in_split_end) x
+ * out-splits [out_split_begin, out_split_end) (an end of -1 = to the last): the 2-D tile -> GPU
+ * map of a layer with fewer in-splits than ranks. Forward writes the block's columns of y and
+ * zeroes the others, so that the shards' results add up; the digital bias is added by the
+ * shards that hold in-split 0; noise streams are those of the tile's place in the whole layer. */
+int ab200_array_create_block(const ab200_tile_config *cfg, int out_size, int in_size,
+                             int max_output_size, int max_input_size, int in_split_begin,
+                             int in_split_end, int out_split_begin, int out_split_end,
+                             int cuda_device, ab200_array **out);
 int ab200_array_destroy(ab200_array *arr);
 int ab200_array_num_in_splits(const ab200_array *arr);
 int ab200_array_num_out_splits(const ab200_array *arr);
