@@ -110,6 +110,40 @@ def test_mapped_forward_sharded_partials_add_up():
         assert torch.allclose(y_full, y_sum, atol=1e-5, rtol=1e-6)
 
 
+@pytest.mark.parametrize("m", [33, 300])
+def test_mapped_forward_blocks_of_tiles_add_up(m):
+    """A 2-D map of the tiles (blocks over in-splits and out-splits, as a layer with two in-splits
+    is spread over more than two ranks): every block writes its own output columns and zeros
+    elsewhere, the bias enters with the blocks of in-split 0 only, the noise is that of the tile's
+    place in the whole layer - so the blocks' outputs add up to the full layer's, noise included."""
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+    from aihwkit_b200.sharded import block_of_rank, split_sizes
+
+    rng = np.random.default_rng(14)
+    out_size, in_size, max_tile = 2304, 768, 512  # in-splits [384, 384], five out-splits of 460/461
+    p = H.inference_params(noise=True)
+    cfg = p._config(1, 1, D.IdealResistiveDeviceParameter(), seed=21)
+    W = rng.normal(0, 0.02, (out_size, in_size)).astype(np.float32)
+    bias = rng.normal(0, 0.1, out_size).astype(np.float32)
+    X = torch.from_numpy(rng.normal(0, 1, (m, in_size)).astype(np.float32)).cuda()
+    full = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+    full.set_weights(torch.from_numpy(W), weight_scaling_omega=1.0)
+    full.set_bias(torch.from_numpy(bias))
+    y_full = full.forward(X)
+    n_in, n_out = len(split_sizes(in_size, max_tile)), len(split_sizes(out_size, max_tile))
+    world = 8
+    total = torch.zeros_like(y_full)
+    for rank in range(world):
+        (ib, ie), (ob, oe) = block_of_rank(n_in, n_out, rank, world)
+        blk = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0,
+                          in_split_range=(ib, ie), out_split_range=(ob, oe))
+        blk.set_weights(torch.from_numpy(W), weight_scaling_omega=1.0)
+        blk.set_bias(torch.from_numpy(bias))
+        total += blk.forward(X)
+    assert torch.allclose(total, y_full, atol=2e-5, rtol=1e-6)
+    assert float(y_full.abs().max()) > 0
+
+
 def test_mapped_forward_noise_statistics():
     from scipy import stats
     from aihwkit_b200.rpu_base import devices as D, tiles as T

@@ -123,3 +123,24 @@ def test_scatter_setup_raises_on_every_rank_when_one_owns_no_in_split(tmp_path):
     msgs = [(tmp_path / f"rank{r}.txt").read_text() for r in range(world)]
     assert all("at least one in-split per rank" in m for m in msgs), msgs
     assert len(set(msgs)) == 1
+
+
+def test_two_d_tile_map_covers_every_tile_once():
+    """Blocks over in-splits and out-splits: every tile of the layer belongs to exactly one rank,
+    for the layer shapes of the transformer benchmark on 1 to 8 ranks."""
+    sys.path.insert(0, ROOT)
+    from aihwkit_b200.sharded import block_of_rank, split_sizes, tile_grid
+
+    for in_size, out_size in ((768, 2304), (768, 768), (768, 3072), (3072, 768), (4096, 4096)):
+        n_in, n_out = len(split_sizes(in_size, 512)), len(split_sizes(out_size, 512))
+        for world in (1, 2, 3, 4, 8):
+            g_in, g_out = tile_grid(n_in, n_out, world)
+            assert g_in * g_out == world and g_in <= max(1, n_in)
+            owner = {}
+            for rank in range(world):
+                (ib, ie), (ob, oe) = block_of_rank(n_in, n_out, rank, world)
+                for i in range(ib, ie):
+                    for o in range(ob, oe):
+                        assert (i, o) not in owner
+                        owner[(i, o)] = rank
+            assert len(owner) == n_in * n_out
