@@ -446,8 +446,6 @@ Tile::~Tile() {
     cudaFree(bm_stats_);
     cudaFree(xw_);
     cudaFree(dw_);
-    cudaFree(xnz_);
-    cudaFree(dnz_);
     cudaFree(xwt_);
     cudaFree(xnzt_);
     cudaFree(onehot_);
@@ -530,11 +528,10 @@ void Tile::toDevice(int cuda_device) {
     AB200_CUDA(cudaMalloc(&onehot_, (size_t)x_size_ * sizeof(float)));
     AB200_CUDA(cudaMalloc(&tread_, (size_t)d_size_ * sizeof(float)));
     {
-      // pulse words of the single sample of a transfer write (all its segments) + their bitmaps
+      // pulse words of the single sample of a transfer write (all its segments)
       const size_t nseg_t = (size_t)std::max(1, (cfg_.transfer.transfer_up.desired_bl + kPulseSegSlots - 1) /
                                                     kPulseSegSlots);
-      AB200_CUDA(cudaMalloc(&t_words_, (nseg_t + (nseg_t + 31) / 32) * (size_t)(x_size_ + d_size_) *
-                                           sizeof(uint32_t)));
+      AB200_CUDA(cudaMalloc(&t_words_, nseg_t * (size_t)(x_size_ + d_size_) * sizeof(uint32_t)));
     }
     if (cfg_.transfer.buffered) {
       AB200_CUDA(cudaMalloc(&t_buffer_, size * sizeof(float)));
@@ -564,21 +561,16 @@ void Tile::ensureScratch(int m) {
   cudaFree(flags_);
   cudaFree(xw_);
   cudaFree(dw_);
-  cudaFree(xnz_);
-  cudaFree(dnz_);
   int cap = m + m / 4 + 16;
   AB200_CUDA(cudaMalloc(&scale_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&factor_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&vnorm_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&sval_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&flags_, (size_t)cap * sizeof(int)));
-  xw_ = dw_ = xnz_ = dnz_ = nullptr;
+  xw_ = dw_ = nullptr;
   if (cfg_.device_kind != AB200_DEVICE_IDEAL && up_.pulse_type != AB200_PULSE_NONE) {
     AB200_CUDA(cudaMalloc(&xw_, (size_t)cap * x_size_ * sizeof(uint32_t)));
     AB200_CUDA(cudaMalloc(&dw_, (size_t)cap * d_size_ * sizeof(uint32_t)));
-    const size_t nblk = (size_t)(cap + 31) / 32;
-    AB200_CUDA(cudaMalloc(&xnz_, nblk * x_size_ * sizeof(uint32_t)));
-    AB200_CUDA(cudaMalloc(&dnz_, nblk * d_size_ * sizeof(uint32_t)));
   }
   scratch_m_ = cap;
 }
@@ -1131,8 +1123,6 @@ void Tile::doTransfer(cudaStream_t s) {
     // the middle of a batch
     u.xw = t_words_;
     u.dw = t_words_ + (size_t)u.nseg * x_size_;
-    u.xnz = t_words_ + (size_t)u.nseg * (x_size_ + d_size_);
-    u.dnz = u.xnz + (size_t)((u.nseg + 31) / 32) * x_size_;
     u.w = w_;
     u.par4 = dev_[1].par4;
     u.par2 = dev_[1].par2;
@@ -1191,8 +1181,6 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
   u.call = upd_calls_++;
   u.xw = xw_;
   u.dw = dw_;
-  u.xnz = xnz_;
-  u.dnz = dnz_;
   u.s_begin = 0;
   u.s_end = m;
 
@@ -1316,8 +1304,6 @@ void Tile::coincidences(const float *x, const float *d, int32_t *counts, cudaStr
   u.call = 0x7fffffffu;
   u.xw = xw_;
   u.dw = dw_;
-  u.xnz = xnz_;
-  u.dnz = dnz_;
   launchPulsePrepare(u, s);
   launchCoincidences(u, counts, s);
 }

@@ -143,8 +143,6 @@ struct UpdateProblem {
   // scratch
   uint32_t *xw; // [m][x_size] pulse words (or float bit patterns for implicit pulses)
   uint32_t *dw; // [m][d_size]
-  uint32_t *xnz; // [ceil(m/32)][x_size] bitmaps of the samples with a non-empty word
-  uint32_t *dnz; // [ceil(m/32)][d_size]
   // target
   float *w;
   const float4 *par4;
@@ -329,13 +327,13 @@ private:
   int scratch_m_ = 0;
   float *scale_ = nullptr, *factor_ = nullptr, *vnorm_ = nullptr, *sval_ = nullptr;
   int *flags_ = nullptr, *bm_stats_ = nullptr;
-  uint32_t *xw_ = nullptr, *dw_ = nullptr, *xnz_ = nullptr, *dnz_ = nullptr;
+  uint32_t *xw_ = nullptr, *dw_ = nullptr;
   // transposed x words [x_size][m_pad] and their bitmaps, for the streaming update of large batches
   uint32_t *xwt_ = nullptr, *xnzt_ = nullptr;
   size_t xwt_words_ = 0;
   void ensureStreamScratch(int m_pad);
   float *onehot_ = nullptr, *tread_ = nullptr;
-  uint32_t *t_words_ = nullptr; // Tiki-Taka write: pulse words and bitmaps of its single sample
+  uint32_t *t_words_ = nullptr; // Tiki-Taka write: pulse words of its single sample
   // tensor-core engines (forward / backward operand caches), rebuilt when the weights change
   std::unique_ptr<TcEngine> tc_fwd_, tc_bwd_;
   uint64_t w_version_ = 1, tc_fwd_version_ = 0, tc_bwd_version_ = 0;

@@ -305,32 +305,11 @@ constexpr int UT_J = 16; // x-lines per CTA
 constexpr int UBLK = 32; // samples per block = bits of one non-zero bitmap word
 constexpr int UT_JP = UT_J + 1; // padded row length of the staged x words (bank spread)
 
-// Bitmaps of the non-empty pulse words: bit s of nz[blk][line] is set when the word of sample
-// blk * 32 + s on that line carries at least one pulse (or a non-zero implicit value). The update
-// kernel intersects the bitmaps of a d-line and an x-line and only looks at the samples that
-// survive - the GPU form of the index lists the reference CPU builds per pulse slot
-// (src/rpucuda/sparse_bit_line_maker.cpp:200-238).
-__global__ void __launch_bounds__(256)
-    pulseNzKernel(const uint32_t *words, int n_lines, int m, uint32_t *nz, int implicit) {
-  const int line = blockIdx.x * blockDim.x + threadIdx.x;
-  const int blk = blockIdx.y;
-  if (line >= n_lines) {
-    return;
-  }
-  uint32_t bits = 0;
-  const int s0 = blk * UBLK;
-#pragma unroll 4
-  for (int s = 0; s < UBLK; s++) {
-    if (s0 + s < m) {
-      uint32_t w = words[(long long)(s0 + s) * n_lines + line];
-      if (implicit) {
-        w &= 0x7fffffffu;
-      }
-      bits |= (w != 0u ? 1u : 0u) << s;
-    }
-  }
-  nz[(long long)blk * n_lines + line] = bits;
-}
+// Bitmaps of the non-empty pulse words: bit s of the word of a line is set when the pulse word of
+// sample blk * 32 + s on that line carries at least one pulse (or a non-zero implicit value). The
+// update kernel builds them in shared memory while it stages the words, intersects the bitmaps of
+// a d-line and an x-line and only looks at the samples that survive - the GPU form of the index
+// lists the reference CPU builds per pulse slot (src/rpucuda/sparse_bit_line_maker.cpp:200-238).
 
 // Every thread owns EJ weights (one d-line, EJ x-lines; EJ = 4 with 256 threads per CTA for large
 // problems, EJ = 1 with 1024 threads when the grid would otherwise not fill the GPU). The loop
@@ -400,9 +379,19 @@ __global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
   int rc = 0;
 
   const int b_first = p.s_begin / USAMP, b_last = (p.s_end - 1) / USAMP;
-  const int n_words = (p.m + UBLK - 1) / UBLK;
   for (int blk = b_first; blk <= b_last; blk++) {
     const int s0 = blk * USAMP;
+    // bitmaps of the non-empty words of this super-block, built while the words are staged
+    for (int t = threadIdx.x; t < USUP * (UT_I + UT_J); t += blockDim.x) {
+      if (t < USUP * UT_I) {
+        (&sm.sdnz[0][0])[t] = 0u;
+      } else {
+        (&sm.sxnz[0][0])[t - USUP * UT_I] = 0u;
+      }
+    }
+    __syncthreads();
+    // samples of this super-block that belong to [s_begin, s_end) (only the d bitmap needs the
+    // range: a candidate needs both lines)
     {
       // every thread stages one fixed column of the x words and one of the d words, so the
       // loop only advances a pointer by a row
@@ -412,7 +401,11 @@ __global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
       const long long step = (long long)(UNT / UT_J) * p.x_size;
 #pragma unroll 4
       for (int ss = sj; ss < USAMP; ss += UNT / UT_J, src += step) {
-        sm.sx[ss][jj] = (gj < p.x_size && s0 + ss < p.m) ? *src : 0u;
+        const uint32_t wv = (gj < p.x_size && s0 + ss < p.m) ? *src : 0u;
+        sm.sx[ss][jj] = wv;
+        if ((IMPLICIT ? (wv & 0x7fffffffu) : wv) != 0u) {
+          atomicOr(&sm.sxnz[ss >> 5][jj], 1u << (ss & 31));
+        }
       }
     }
     {
@@ -422,29 +415,12 @@ __global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
       const long long step = (long long)(UNT / UT_I) * p.d_size;
 #pragma unroll 8
       for (int ss = si; ss < USAMP; ss += UNT / UT_I, src += step) {
-        sm.sd[ss][ii] = (gi < p.d_size && s0 + ss < p.m) ? *src : 0u;
-      }
-    }
-    for (int t = threadIdx.x; t < USUP * (UT_I + UT_J); t += blockDim.x) {
-      const int wi = t / (UT_I + UT_J), c = t % (UT_I + UT_J);
-      const int word = blk * USUP + wi;
-      if (c < UT_I) {
-        int gi = blockIdx.x * UT_I + c;
-        // samples of this word that belong to [s_begin, s_end)
-        uint32_t range = 0xffffffffu;
-        const int sb = word * UBLK;
-        if (sb < p.s_begin) {
-          range = p.s_begin - sb >= UBLK ? 0u : range << (p.s_begin - sb);
+        const int sg = s0 + ss;
+        const uint32_t wv = (gi < p.d_size && sg < p.m) ? *src : 0u;
+        sm.sd[ss][ii] = wv;
+        if ((IMPLICIT ? (wv & 0x7fffffffu) : wv) != 0u && sg >= p.s_begin && sg < p.s_end) {
+          atomicOr(&sm.sdnz[ss >> 5][ii], 1u << (ss & 31));
         }
-        if (sb + UBLK > p.s_end) {
-          range = sb >= p.s_end ? 0u : range & (0xffffffffu >> (sb + UBLK - p.s_end));
-        }
-        sm.sdnz[wi][c] =
-            (gi < p.d_size && word < n_words) ? (p.dnz[(long long)word * p.d_size + gi] & range) : 0u;
-      } else {
-        int gj = blockIdx.y * UT_J + (c - UT_I);
-        sm.sxnz[wi][c - UT_I] =
-            (gj < p.x_size && word < n_words) ? p.xnz[(long long)word * p.x_size + gj] : 0u;
       }
     }
     __syncthreads();
@@ -854,19 +830,6 @@ void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream) {
     return;
   }
   pulsePrepareKernel<<<p.m, 256, 0, stream>>>(p);
-  AB200_LAUNCH_CHECK();
-  // both dense types keep a float value per line; coincidences are rint(d * x)
-  const int implicit = (p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT ||
-                        p.up.pulse_type == AB200_PULSE_MEAN_COUNT)
-                           ? 1
-                           : 0;
-  const int rows = p.m * (p.nseg > 0 ? p.nseg : 1);
-  const int n_blk = (rows + UBLK - 1) / UBLK;
-  pulseNzKernel<<<dim3((p.x_size + 255) / 256, n_blk), 256, 0, stream>>>(p.xw, p.x_size, rows, p.xnz,
-                                                                       implicit);
-  AB200_LAUNCH_CHECK();
-  pulseNzKernel<<<dim3((p.d_size + 255) / 256, n_blk), 256, 0, stream>>>(p.dw, p.d_size, rows, p.dnz,
-                                                                       implicit);
   AB200_LAUNCH_CHECK();
 }
 
