@@ -111,7 +111,7 @@ def launch_floor_us(lib, n: int = 300) -> float:
 
 
 def run(config: int, steps: int = 20, warmup: int = 3, batch: int = 0, indexed: bool = False,
-        on_line=None) -> dict:
+        on_line=None, update_path: int = 0) -> dict:
     """One benchmark line (a dict) for configuration 0, 2 or 3.  ``on_line(line, cfg, x, d, lr)``,
     when given, may extend it (``bench.py --config N`` adds the CPU baseline of the compiled
     reference there)."""
@@ -125,6 +125,7 @@ def run(config: int, steps: int = 20, warmup: int = 3, batch: int = 0, indexed: 
     if not torch.cuda.is_available():
         raise RuntimeError("needs a CUDA device: the analog tile has no CPU path")
     lib = _cabi.lib()
+    _cabi.check(lib.ab200_set_update_path(int(update_path)))
     p, dp, w = build(config)
     x_size, d_size = w["x"], w["d"]
     m = batch or w["m"]
@@ -260,8 +261,11 @@ def main(argv=None, on_line=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=0, help="override the batch size")
     ap.add_argument("--indexed", action="store_true", help="config 3 through the indexed interface")
+    ap.add_argument("--update-path", type=int, default=0, choices=[0, 1, 2],
+                    help="kernel of the pulsed update: 0 automatic, 1 staged, 2 streaming")
     args = ap.parse_args(argv)
-    print(json.dumps(run(args.config, args.steps, args.warmup, args.batch, args.indexed, on_line)))
+    print(json.dumps(run(args.config, args.steps, args.warmup, args.batch, args.indexed, on_line,
+                         args.update_path)))
 
 
 if __name__ == "__main__":

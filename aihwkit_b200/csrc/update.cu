@@ -327,11 +327,11 @@ constexpr int USUP = 4;              // bitmap words per super-block
 constexpr int USAMP = USUP * UBLK;   // samples per super-block
 constexpr int URES = 8;              // Gaussians per thread in the reservoir
 
-template <int NT> struct UpdateSmem {
+template <int NT, int UTJ> struct UpdateSmem {
   uint32_t sd[USAMP][UT_I];
-  uint32_t sx[USAMP][UT_JP];
+  uint32_t sx[USAMP][(UTJ + 1)];
   uint32_t sdnz[USUP][UT_I];
-  uint32_t sxnz[USUP][UT_J];
+  uint32_t sxnz[USUP][UTJ];
   float sz[URES][NT];
 };
 
@@ -348,17 +348,17 @@ __device__ __noinline__ void refillReservoir(PhiloxKey key, uint32_t gid, uint32
   }
 }
 
-template <int KIND, bool IMPLICIT, bool NOISY, int EJ>
-__global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
+template <int KIND, bool IMPLICIT, bool NOISY, int EJ, int UTJ>
+__global__ void __launch_bounds__(UT_I *UTJ / EJ, (UT_I * UTJ / EJ) >= 1024 ? 1 : 4)
     pulsedUpdateKernel(UpdateProblem p) {
   constexpr int UE_J = EJ;
-  constexpr int UNT = UT_I * UT_J / EJ; // threads per CTA
+  constexpr int UNT = UT_I * UTJ / EJ; // threads per CTA
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  UpdateSmem<UNT> &sm = *reinterpret_cast<UpdateSmem<UNT> *>(smem_raw);
+  UpdateSmem<UNT, UTJ> &sm = *reinterpret_cast<UpdateSmem<UNT, UTJ> *>(smem_raw);
   const int ti = threadIdx.x & (UT_I - 1);
   const int tj = threadIdx.x / UT_I;
   const int i = blockIdx.x * UT_I + ti;
-  const int j0 = blockIdx.y * UT_J + tj * UE_J;
+  const int j0 = blockIdx.y * UTJ + tj * UE_J;
   const bool i_ok = i < p.d_size;
 
   float w[UE_J];
@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
   for (int blk = b_first; blk <= b_last; blk++) {
     const int s0 = blk * USAMP;
     // bitmaps of the non-empty words of this super-block, built while the words are staged
-    for (int t = threadIdx.x; t < USUP * (UT_I + UT_J); t += blockDim.x) {
+    for (int t = threadIdx.x; t < USUP * (UT_I + UTJ); t += blockDim.x) {
       if (t < USUP * UT_I) {
         (&sm.sdnz[0][0])[t] = 0u;
       } else {
@@ -390,36 +390,71 @@ __global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
       }
     }
     __syncthreads();
-    // samples of this super-block that belong to [s_begin, s_end) (only the d bitmap needs the
-    // range: a candidate needs both lines)
     {
       // every thread stages one fixed column of the x words and one of the d words, so the
-      // loop only advances a pointer by a row
-      const int jj = threadIdx.x % UT_J, sj = threadIdx.x / UT_J;
-      const int gj = blockIdx.y * UT_J + jj;
+      // loop only advances a pointer by a row; it collects the column's bitmap bits of its
+      // samples in registers (the word a sample falls into is known at compile time, or one of
+      // a few) and adds them to the shared bitmap at the end
+      constexpr int STEP = UNT / UTJ;               // samples between two rows of a thread
+      constexpr int WPS = STEP >= 32 ? STEP / 32 : 1; // bitmap words its first row can fall into
+      const int jj = threadIdx.x % UTJ, sj = threadIdx.x / UTJ;
+      const int gj = blockIdx.y * UTJ + jj;
       const uint32_t *src = p.xw + (long long)(s0 + sj) * p.x_size + gj;
-      const long long step = (long long)(UNT / UT_J) * p.x_size;
-#pragma unroll 4
-      for (int ss = sj; ss < USAMP; ss += UNT / UT_J, src += step) {
+      const long long step = (long long)STEP * p.x_size;
+      uint32_t nzb[USUP];
+#pragma unroll
+      for (int wq = 0; wq < USUP; wq++) {
+        nzb[wq] = 0u;
+      }
+#pragma unroll
+      for (int k = 0; k < USAMP / STEP; k++, src += step) {
+        const int ss = sj + STEP * k;
         const uint32_t wv = (gj < p.x_size && s0 + ss < p.m) ? *src : 0u;
         sm.sx[ss][jj] = wv;
-        if ((IMPLICIT ? (wv & 0x7fffffffu) : wv) != 0u) {
-          atomicOr(&sm.sxnz[ss >> 5][jj], 1u << (ss & 31));
+        const bool nz = (IMPLICIT ? (wv & 0x7fffffffu) : wv) != 0u;
+        const uint32_t bit = nz ? 1u << (ss & 31) : 0u;
+        if (STEP < 32) {
+          nzb[(STEP * k) >> 5] |= bit;
+        } else {
+#pragma unroll
+          for (int c = 0; c < WPS; c++) {
+            nzb[WPS * k + c] |= (sj >> 5) == c ? bit : 0u;
+          }
+        }
+      }
+#pragma unroll
+      for (int wq = 0; wq < USUP; wq++) {
+        if (nzb[wq] != 0u) {
+          atomicOr(&sm.sxnz[wq][jj], nzb[wq]);
         }
       }
     }
     {
+      constexpr int STEP = UNT / UT_I; // 4 or 16: a thread's rows never leave the word of STEP * k
       const int ii = threadIdx.x % UT_I, si = threadIdx.x / UT_I;
       const int gi = blockIdx.x * UT_I + ii;
       const uint32_t *src = p.dw + (long long)(s0 + si) * p.d_size + gi;
-      const long long step = (long long)(UNT / UT_I) * p.d_size;
-#pragma unroll 8
-      for (int ss = si; ss < USAMP; ss += UNT / UT_I, src += step) {
+      const long long step = (long long)STEP * p.d_size;
+      uint32_t nzb[USUP];
+#pragma unroll
+      for (int wq = 0; wq < USUP; wq++) {
+        nzb[wq] = 0u;
+      }
+#pragma unroll
+      for (int k = 0; k < USAMP / STEP; k++, src += step) {
+        const int ss = si + STEP * k;
         const int sg = s0 + ss;
         const uint32_t wv = (gi < p.d_size && sg < p.m) ? *src : 0u;
         sm.sd[ss][ii] = wv;
-        if ((IMPLICIT ? (wv & 0x7fffffffu) : wv) != 0u && sg >= p.s_begin && sg < p.s_end) {
-          atomicOr(&sm.sdnz[ss >> 5][ii], 1u << (ss & 31));
+        // samples of this super-block that belong to [s_begin, s_end): only the d bitmap needs
+        // the range, a candidate needs both lines
+        const bool nz = (IMPLICIT ? (wv & 0x7fffffffu) : wv) != 0u && sg >= p.s_begin && sg < p.s_end;
+        nzb[(STEP * k) >> 5] |= nz ? 1u << (ss & 31) : 0u;
+      }
+#pragma unroll
+      for (int wq = 0; wq < USUP; wq++) {
+        if (nzb[wq] != 0u) {
+          atomicOr(&sm.sdnz[wq][ii], nzb[wq]);
         }
       }
     }
@@ -534,36 +569,42 @@ __global__ void __launch_bounds__(UT_I *UT_J / EJ, EJ == 1 ? 1 : 4)
   }
 }
 
-template <int KIND, bool IMPLICIT, bool NOISY, int EJ>
+template <int KIND, bool IMPLICIT, bool NOISY, int EJ, int UTJ>
 static void launchUpdateVariant(const UpdateProblem &p, cudaStream_t stream) {
-  constexpr int NT = UT_I * UT_J / EJ;
+  constexpr int NT = UT_I * UTJ / EJ;
   static bool configured[64] = {};
   int dev = 0;
   AB200_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    AB200_CUDA(cudaFuncSetAttribute(pulsedUpdateKernel<KIND, IMPLICIT, NOISY, EJ>,
+    AB200_CUDA(cudaFuncSetAttribute(pulsedUpdateKernel<KIND, IMPLICIT, NOISY, EJ, UTJ>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)sizeof(UpdateSmem<NT>)));
+                                    (int)sizeof(UpdateSmem<NT, UTJ>)));
     configured[dev] = true;
   }
-  dim3 grid((p.d_size + UT_I - 1) / UT_I, (p.x_size + UT_J - 1) / UT_J);
-  pulsedUpdateKernel<KIND, IMPLICIT, NOISY, EJ><<<grid, NT, sizeof(UpdateSmem<NT>), stream>>>(p);
+  dim3 grid((p.d_size + UT_I - 1) / UT_I, (p.x_size + UTJ - 1) / UTJ);
+  pulsedUpdateKernel<KIND, IMPLICIT, NOISY, EJ, UTJ>
+      <<<grid, NT, sizeof(UpdateSmem<NT, UTJ>), stream>>>(p);
 }
 
 template <int KIND, bool IMPLICIT, bool NOISY>
 static void launchUpdateInstance(const UpdateProblem &p, dim3 grid, cudaStream_t stream) {
-  // four weights per thread (256 threads, four CTAs per SM) once the grid fills the GPU several
-  // times over; one weight per thread (1024 threads) for small tiles
+  // `grid` = CTAs of 64 d-lines x 16 x-lines. Four weights per thread (256 threads, four CTAs
+  // per SM) once that grid fills the GPU several times over; one weight per thread (1024
+  // threads) for small tiles; and CTAs of 64 x 4 weights (256 threads) when even that would
+  // leave SMs without a CTA (a 256 x 256 tile is 64 CTAs of 64 x 16, but 256 of 64 x 4)
   static int n_sm = 0;
   if (n_sm == 0) {
     int dev = 0;
     AB200_CUDA(cudaGetDevice(&dev));
     AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
   }
-  if ((long long)grid.x * grid.y >= 3LL * n_sm) {
-    launchUpdateVariant<KIND, IMPLICIT, NOISY, 4>(p, stream);
+  const long long n = (long long)grid.x * grid.y;
+  if (n >= 3LL * n_sm) {
+    launchUpdateVariant<KIND, IMPLICIT, NOISY, 4, UT_J>(p, stream);
+  } else if (n >= n_sm) {
+    launchUpdateVariant<KIND, IMPLICIT, NOISY, 1, UT_J>(p, stream);
   } else {
-    launchUpdateVariant<KIND, IMPLICIT, NOISY, 1>(p, stream);
+    launchUpdateVariant<KIND, IMPLICIT, NOISY, 1, 4>(p, stream);
   }
 }
 

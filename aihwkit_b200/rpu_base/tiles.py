@@ -160,10 +160,10 @@ class AnalogTile:
 
     # -- sizes / learning rate ---------------------------------------------------------------
     def get_x_size(self) -> int:
-        return int(self._lib.ab200_tile_get_x_size(self._h))
+        return int(self._cfg.x_size)
 
     def get_d_size(self) -> int:
-        return int(self._lib.ab200_tile_get_d_size(self._h))
+        return int(self._cfg.d_size)
 
     def set_learning_rate(self, learning_rate: float) -> None:
         check(self._lib.ab200_tile_set_learning_rate(self._h, float(learning_rate)))
