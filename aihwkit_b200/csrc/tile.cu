@@ -457,6 +457,7 @@ Tile::~Tile() {
     cudaFree(cols_d_);
     cudaFree(stage_dev_);
     cudaFree(acc_block_);
+    cudaFree(clip_stats_);
     cudaFreeHost(stage_pinned_);
     if (prev >= 0) {
       cudaSetDevice(prev);

@@ -344,6 +344,7 @@ private:
   int32_t idx_max_ = 0;
   float *cols_x_ = nullptr, *cols_d_ = nullptr;
   long long cols_cap_ = 0;
+  unsigned char *clip_stats_ = nullptr; // statistics of clipWeights (sum, sum of squares, row maxima)
   // output block of a tile that adds to earlier in-splits under bound management
   float *acc_block_ = nullptr;
   size_t acc_block_floats_ = 0;

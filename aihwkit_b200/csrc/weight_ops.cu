@@ -250,12 +250,15 @@ void Tile::clipWeights(int type, float fixed_value, float sigma, cudaStream_t s)
       AB200_FATAL("Sophisticated clipping is NOT implemented for most training devices");
     }
     // one statistics pass, read back: the clip value is a scalar the host needs anyway
-    double *acc = nullptr;
+    // statistics buffer of the tile, allocated once: two doubles + one word per output row
+    if (!clip_stats_) {
+      AB200_CUDA(cudaMalloc(&clip_stats_, 2 * sizeof(double) + (size_t)d_size_ * sizeof(unsigned int)));
+    }
+    double *acc = reinterpret_cast<double *>(clip_stats_);
     unsigned int *rowmax = nullptr;
-    AB200_CUDA(cudaMalloc(&acc, 2 * sizeof(double)));
     AB200_CUDA(cudaMemsetAsync(acc, 0, 2 * sizeof(double), s));
     if (type == AB200_CLIP_AVERAGE_CHANNEL_MAX) {
-      AB200_CUDA(cudaMalloc(&rowmax, (size_t)d_size_ * sizeof(unsigned int)));
+      rowmax = reinterpret_cast<unsigned int *>(clip_stats_ + 2 * sizeof(double));
       AB200_CUDA(cudaMemsetAsync(rowmax, 0, (size_t)d_size_ * sizeof(unsigned int), s));
     }
     clipStatsKernel<<<blocksFor(n), 256, 0, s>>>(w_, n, d_size_, acc, rowmax);
@@ -269,8 +272,6 @@ void Tile::clipWeights(int type, float fixed_value, float sigma, cudaStream_t s)
                                  cudaMemcpyDeviceToHost, s));
     }
     AB200_CUDA(cudaStreamSynchronize(s));
-    cudaFree(acc);
-    cudaFree(rowmax);
     if (type == AB200_CLIP_LAYER_GAUSSIAN) {
       const double mean = h[0] / (double)n;
       const double var = n > 1 ? (h[1] - (double)n * mean * mean) / (double)(n - 1) : 0.0;

@@ -552,9 +552,14 @@ int ab200_array_set_seed(ab200_array *arr, uint64_t seed);
  * For hosts that pre-reserve the GPU's memory and forbid allocation afterwards - an inference
  * server's execute callback, a real-time loop, a plugin with a "no allocation after init"
  * contract - where a cudaMalloc mid-request would fail or stall every stream of the device.
- * Computes the same IO-managed forward pass as ab200_tile_forward (non-transposed layouts, no
- * bias) from caller-owned memory only: w_dev_xd is the fp32 [x_size][d_size] weight, x_dev is
- * [m_batch][x_size], d_dev is [m_batch][d_size]. The per-sample scratch lives in a fixed array
+ * Computes the IO-managed forward pass of ab200_tile_forward (non-transposed layouts, no bias)
+ * from caller-owned memory only: w_dev_xd is the fp32 [x_size][d_size] weight, x_dev is
+ * [m_batch][x_size], d_dev is [m_batch][d_size]. It always runs the CUDA-core kernels (the
+ * tensor-core path keeps an operand copy of the weights that it would have to allocate), so for
+ * sizes where ab200_tile_forward picks the tensor cores the two agree up to the summation order:
+ * a rare element may land on the neighbouring ADC step. All pointers belong to the CURRENT CUDA
+ * device of the calling thread, which is also the device whose scratch array is used: make the
+ * device current (cudaSetDevice) before the call. The per-sample scratch lives in a fixed array
  * inside the library image (about 320 KB per GPU, held until the process exits), so m_batch is
  * limited to AB200_NOALLOC_MAX_BATCH; larger batches are rejected with an error - split them.
  * The call performs no cudaMalloc / cudaFree and calls no allocating library routine.

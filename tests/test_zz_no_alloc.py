@@ -54,6 +54,40 @@ def test_noalloc_forward_matches_tile_forward_twice(noise):
         assert torch.allclose(y, y_tile, rtol=0.0, atol=1e-6), (y - y_tile).abs().max()
 
 
+def test_noalloc_forward_against_the_oracle_and_without_allocating():
+    """Noise off: the entry point against the numpy oracle directly; and the call leaves the
+    device's free memory as it found it (batch near the limit, bound management active)."""
+    from aihwkit_b200 import _cabi
+    from oracle import analog_tile_oracle as O
+
+    lib = _cabi.lib()
+    x_size, d_size, m = 96, 72, 16000
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=3.0)
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=7)
+    rng = np.random.default_rng(5)
+    w = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    w_xd = torch.from_numpy(np.ascontiguousarray(w.T)).cuda()
+    xg = torch.from_numpy(x).cuda()
+    y = torch.empty(m, d_size, device="cuda")
+
+    def call(k):
+        rc = lib.ab200_mvm_forward_noalloc(C.byref(cfg.forward_io), w_xd.data_ptr(), x_size, d_size,
+                                           xg.data_ptr(), y.data_ptr(), m, 7, k, _stream(xg))
+        assert rc == 0, lib.ab200_last_error()
+        torch.cuda.synchronize()
+
+    call(0)  # the first call on a device resolves the scratch array's address
+    free_before, _ = torch.cuda.mem_get_info()
+    call(1)
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    io = O.IO.from_c(cfg.forward_io)
+    y_or, _, scale, _ = O.forward(w, x, io, return_pre_adc=True)
+    frac, worst = H.lsb_report(y.cpu().numpy(), y_or, (io.res_out / scale)[:, None])
+    assert frac <= 2e-3 and worst <= 1.001, (frac, worst)
+
+
 def test_noalloc_rejects_oversized_batch():
     from aihwkit_b200 import _cabi
 
