@@ -40,6 +40,7 @@ class IOParams(C.Structure):
         ("inp_asymmetry", C.c_float),
         ("out_asymmetry", C.c_float),
         ("nm_assumed_wmax", C.c_float),
+        ("out_noise_std", C.c_float),
     ]
 
 
@@ -110,6 +111,9 @@ class DeviceParams(C.Structure):
         ("ps_gamma_dtod", C.c_float),
         ("ps_gamma_up_down", C.c_float),
         ("ps_gamma_up_down_dtod", C.c_float),
+        ("pw_n", C.c_int32),
+        ("pw_up", C.c_float * 32),
+        ("pw_down", C.c_float * 32),
     ]
 
 

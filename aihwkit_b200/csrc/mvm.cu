@@ -83,11 +83,15 @@ template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKe
 // T x T outputs per thread, 16 x 16 threads: 64 x 64 outputs per CTA for large problems, 32 x 32 or
 // 16 x 16 when the larger tile would leave most SMs without a CTA (a 256 x 256 tile with a batch of
 // 64 is four CTAs of 64 x 64, but 64 of 16 x 16).
-constexpr int BK = 16;
+// The K step of a CTA grows as its tile shrinks: the small tiles serve small problems, whose time is
+// the latency of the K loop (global load -> DAC -> shared memory -> barrier per step), not its
+// arithmetic, so they take 64 or 32 features per step with several loads in flight per thread.
 
-template <bool A_K_FAST, bool B_N_FAST, int T>
+// PCM: also accumulate sum_k |w| v^2 per output, the variance factor of the PCMRead weight noise.
+template <bool A_K_FAST, bool B_N_FAST, int T, bool PCM>
 __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   constexpr int BM = 16 * T, BN = 16 * T;
+  constexpr int BK = T == 1 ? 64 : (T == 2 ? 32 : 16);
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   __shared__ float s_scale[BM];
@@ -105,11 +109,15 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   __syncthreads();
 
   float acc[T][T];
+  float acc2[PCM ? T : 1][PCM ? T : 1];
 #pragma unroll
   for (int i = 0; i < T; i++) {
 #pragma unroll
     for (int j = 0; j < T; j++) {
       acc[i][j] = 0.0f;
+      if (PCM) {
+        acc2[PCM ? i : 0][PCM ? j : 0] = 0.0f;
+      }
     }
   }
 
@@ -165,6 +173,10 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
 #pragma unroll
         for (int j = 0; j < T; j++) {
           acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          if (PCM) {
+            acc2[PCM ? i : 0][PCM ? j : 0] =
+                fmaf(a[i] * a[i], fabsf(b[j]), acc2[PCM ? i : 0][PCM ? j : 0]);
+          }
         }
       }
     }
@@ -205,9 +217,10 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
         y[j] *= fac;
       }
     } else {
+      const bool line_sigma = PCM || p.out_noise_vals != nullptr;
       float sigma = outputSigma(io, p.vnorm[r]);
       float z[4] = {0.f, 0.f, 0.f, 0.f};
-      if (sigma > 0.0f) {
+      if (sigma > 0.0f || line_sigma) {
         gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag, z);
       }
       float u[4] = {0.5f, 0.5f, 0.5f, 0.5f};
@@ -217,6 +230,10 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
 #pragma unroll
       for (int j = 0; j < T; j++) {
         const int q = (c + j) & 3; // T divides 4 and c is a multiple of T: same block for all j
+        if (line_sigma && c + j < N) {
+          sigma = outputSigmaLine(io, p.vnorm[r], p.out_noise_vals, c + j,
+                                  PCM ? acc2[PCM ? i : 0][PCM ? j : 0] : 0.0f);
+        }
         y[j] = finalizeOutput(io, y[j], sigma, z[q], exceeded, u[q]) * fac;
       }
     }
@@ -308,12 +325,25 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
       }
       __syncthreads();
       float sigma = outputSigma(io, vn);
+      const bool pcm = io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f;
+      const bool line_sigma = pcm || p.out_noise_vals != nullptr;
       int fail = 0;
       for (int n = threadIdx.x; n < N; n += blockDim.x) {
-        float acc = 0.0f;
+        float acc = 0.0f, acc2 = 0.0f;
         const float *wp = p.w + (long long)n * p.wn;
-        for (int k = 0; k < K; k++) {
-          acc = fmaf(v_sh[k], wp[(long long)k * p.wk], acc);
+        if (pcm) {
+          for (int k = 0; k < K; k++) {
+            float wv = wp[(long long)k * p.wk];
+            acc = fmaf(v_sh[k], wv, acc);
+            acc2 = fmaf(v_sh[k] * v_sh[k], fabsf(wv), acc2);
+          }
+        } else {
+          for (int k = 0; k < K; k++) {
+            acc = fmaf(v_sh[k], wp[(long long)k * p.wk], acc);
+          }
+        }
+        if (line_sigma) {
+          sigma = outputSigmaLine(io, vn, p.out_noise_vals, n, acc2);
         }
         float z[4] = {0.f, 0.f, 0.f, 0.f};
         if (sigma > 0.0f) {
@@ -372,25 +402,33 @@ void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
     return (long long)((p.out_size + 16 * t - 1) / (16 * t)) * ((p.m + 16 * t - 1) / (16 * t));
   };
   const int T = ctas(4) >= n_sm ? 4 : (ctas(2) >= n_sm ? 2 : 1);
-#define AB200_SIMT(TT)                                                                             \
+  const bool pcm =
+      !p.io.is_perfect && p.io.w_noise_type == AB200_WNOISE_PCM_READ && p.io.w_noise > 0.0f;
+#define AB200_SIMT(TT, PCM)                                                                        \
   {                                                                                                \
     dim3 grid((p.out_size + 16 * TT - 1) / (16 * TT), (p.m + 16 * TT - 1) / (16 * TT));           \
     if (a_k_fast && b_n_fast) {                                                                    \
-      mvmSimtKernel<true, true, TT><<<grid, 256, 0, stream>>>(p);                                  \
+      mvmSimtKernel<true, true, TT, PCM><<<grid, 256, 0, stream>>>(p);                             \
     } else if (a_k_fast) {                                                                         \
-      mvmSimtKernel<true, false, TT><<<grid, 256, 0, stream>>>(p);                                 \
+      mvmSimtKernel<true, false, TT, PCM><<<grid, 256, 0, stream>>>(p);                            \
     } else if (b_n_fast) {                                                                         \
-      mvmSimtKernel<false, true, TT><<<grid, 256, 0, stream>>>(p);                                 \
+      mvmSimtKernel<false, true, TT, PCM><<<grid, 256, 0, stream>>>(p);                            \
     } else {                                                                                       \
-      mvmSimtKernel<false, false, TT><<<grid, 256, 0, stream>>>(p);                                \
+      mvmSimtKernel<false, false, TT, PCM><<<grid, 256, 0, stream>>>(p);                           \
     }                                                                                              \
   }
-  if (T == 4) {
-    AB200_SIMT(4)
+  if (pcm) { // the second accumulator doubles the registers of a thread: the 32-wide tile at most
+    if (T >= 2) {
+      AB200_SIMT(2, true)
+    } else {
+      AB200_SIMT(1, true)
+    }
+  } else if (T == 4) {
+    AB200_SIMT(4, false)
   } else if (T == 2) {
-    AB200_SIMT(2)
+    AB200_SIMT(2, false)
   } else {
-    AB200_SIMT(1)
+    AB200_SIMT(1, false)
   }
 #undef AB200_SIMT
   AB200_LAUNCH_CHECK();
@@ -484,6 +522,9 @@ void forwardNoAlloc(const ab200_io_params &io_user, const float *w_dev_xd, int x
   }
   if (m_batch == 0) {
     return;
+  }
+  if (io_user.out_noise_std > 0.0f && !io_user.is_perfect) {
+    AB200_FATAL("no-alloc forward: out_noise_std needs a tile (the per-line values belong to it)");
   }
   unsigned char *base = noAllocScratchForCurrentDevice();
   MvmProblem p{};

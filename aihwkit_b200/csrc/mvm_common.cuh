@@ -166,6 +166,26 @@ __device__ __forceinline__ float outputSigma(const IOEff &io, float vnorm) {
   return s;
 }
 
+// The same with the two extensions of the CUDA-core kernels: a std-dev of the output noise per
+// output line (`onv`, rpu_forward_backward_pass.cpp:306-313, :696) and the PCMRead weight noise
+// w_noise * sqrt(sum_j |w_ij| v_j^2) (:353-381), `pcm` being that sum for the element.
+__device__ __forceinline__ float
+outputSigmaLine(const IOEff &io, float vnorm, const float *onv, int col, float pcm) {
+  float s = onv ? onv[col] : io.out_noise;
+  if (io.w_noise > 0.0f) {
+    if (io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT) {
+      float ws = io.w_noise * vnorm;
+      s = sqrtf(s * s + ws * ws);
+    } else if (io.w_noise_type == AB200_WNOISE_PCM_READ) {
+      s = sqrtf(s * s + io.w_noise * io.w_noise * pcm);
+    }
+  }
+  return s;
+}
+__host__ __device__ __forceinline__ bool ioLineSigma(const IOEff &io) {
+  return io.out_noise_std > 0.0f || (io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f);
+}
+
 // four uniforms in (0,1) for the stochastic ADC rounding of noise block `blk` (four output columns)
 __device__ __forceinline__ void
 uniform4(PhiloxKey key, uint64_t blk, uint32_t call, uint32_t tag, float u[4]) {

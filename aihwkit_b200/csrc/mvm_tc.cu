@@ -1272,6 +1272,10 @@ bool TcEngine::ioSupported(const IOEff &io) {
       io.out_sto_round) {
     return false;
   }
+  // a noise std-dev per output line or per element (PCMRead) likewise
+  if (ioLineSigma(io)) {
+    return false;
+  }
   // the DAC kernel of this path knows the common noise-management types only, and the re-run
   // kernel of IterativeWorstCase changes the noise-management value per row
   if ((io.nm != AB200_NM_NONE && io.nm != AB200_NM_ABS_MAX && io.nm != AB200_NM_CONSTANT) ||

@@ -42,6 +42,7 @@ IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only) {
   e.out_bound = io.out_bound <= 0.0f ? std::numeric_limits<float>::infinity() : io.out_bound;
   e.inp_bound = io.inp_bound <= 0.0f ? std::numeric_limits<float>::infinity() : io.inp_bound;
   e.out_noise = io.out_noise;
+  e.out_noise_std = io.out_noise_std > 0.0f ? io.out_noise_std : 0.0f;
   e.out_scale = io.out_scale;
   e.w_noise = io.w_noise;
   e.nm_assumed_wmax = io.nm_assumed_wmax;
@@ -61,8 +62,10 @@ IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only) {
       // the running-average types keep state between calls (:139-150)
       AB200_FATAL("Noise Management type not implemented!");
     }
-    if (io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) {
-      AB200_FATAL("PCMRead weight noise is not implemented");
+    if (plain_only && ((io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) ||
+                       io.out_noise_std > 0.0f)) {
+      AB200_FATAL("PCMRead weight noise / out_noise_std are not implemented for the read-out of "
+                  "a transfer");
     }
     if (plain_only && (io.inp_noise != 0.0f || io.inp_sto_round || io.out_sto_round ||
                        io.inp_asymmetry != 0.0f || io.out_asymmetry != 0.0f)) {
@@ -152,6 +155,20 @@ void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_
     const float dw_down = scale_down * fmaxf(1.0f - par.es_A_down * expf(par.es_gamma_down * (-z)), 0.0f);
     const float g = fmaxf((dw_down + dw_down) / 2.0f, 0.0f);
     ds.dw_min = g > 0.0f ? g : par.dw_min;
+  }
+  if (kind == AB200_DEVICE_PIECEWISE_STEP) {
+    // PiecewiseStepRPUDeviceMetaParameter::initialize / calcWeightGranularity
+    // (rpu_piecewisestep_device.h:34-50)
+    if (par.pw_n <= 0) {
+      AB200_FATAL("piecewise_up_vec and piecewise_down_vec needs to have some contents.");
+    }
+    if (par.pw_n > AB200_PIECEWISE_MAX_NODES) {
+      AB200_FATAL("PiecewiseStep: at most " << AB200_PIECEWISE_MAX_NODES << " nodes per direction");
+    }
+    ds.pw_n = par.pw_n;
+    ds.pw_host.assign(par.pw_up, par.pw_up + par.pw_n);
+    ds.pw_host.insert(ds.pw_host.end(), par.pw_down, par.pw_down + par.pw_n);
+    ds.dw_min = par.dw_min * par.pw_up[par.pw_n / 2];
   }
   if (kind == AB200_DEVICE_POW_STEP) {
     // PowStepRPUDeviceMetaParameter::calcWeightGranularity (rpu_powstep_device.h:33)
@@ -291,7 +308,8 @@ void Tile::populateHost() {
     for (int k = 0; k < 2; k++) {
       int kind = cfg_.device[k].kind;
       if ((kind < AB200_DEVICE_CONSTANT_STEP || kind > AB200_DEVICE_SOFT_BOUNDS_REFERENCE) &&
-          kind != AB200_DEVICE_EXP_STEP && kind != AB200_DEVICE_POW_STEP) {
+          kind != AB200_DEVICE_EXP_STEP && kind != AB200_DEVICE_POW_STEP &&
+          kind != AB200_DEVICE_PIECEWISE_STEP) {
         AB200_FATAL("Transfer: unit cell device kind not implemented");
       }
       populateDevice(cfg_.device[k], kind, x_size_, d_size_, rng, dev_[k]);
@@ -311,7 +329,7 @@ Tile::Tile(const ab200_tile_config &cfg, int cuda_device) : cfg_(cfg) {
   f_io_ = resolveIO(cfg.forward_io, false);
   b_io_ = resolveIO(cfg.backward_io, true);
   up_ = resolveUp(cfg.update);
-  if (cfg.device_kind < AB200_DEVICE_IDEAL || cfg.device_kind > AB200_DEVICE_POW_STEP) {
+  if (cfg.device_kind < AB200_DEVICE_IDEAL || cfg.device_kind > AB200_DEVICE_PIECEWISE_STEP) {
     AB200_FATAL("device kind not implemented");
   }
   if (cfg.device_kind == AB200_DEVICE_TRANSFER) {
@@ -437,6 +455,7 @@ Tile::~Tile() {
       cudaFree(dev_[k].par4);
       cudaFree(dev_[k].par2);
       cudaFree(dev_[k].par3);
+      cudaFree(dev_[k].pw);
     }
     cudaFree(scale_);
     cudaFree(factor_);
@@ -444,6 +463,8 @@ Tile::~Tile() {
     cudaFree(sval_);
     cudaFree(flags_);
     cudaFree(bm_stats_);
+    cudaFree(f_onv_);
+    cudaFree(b_onv_);
     cudaFree(xw_);
     cudaFree(dw_);
     cudaFree(xwt_);
@@ -502,6 +523,13 @@ void Tile::uploadDeviceStore(DeviceStore &ds) {
   }
   AB200_CUDA(cudaMemcpy(ds.par4, p4.data(), size * sizeof(float4), cudaMemcpyHostToDevice));
   AB200_CUDA(cudaMemcpy(ds.par2, p2.data(), size * sizeof(float2), cudaMemcpyHostToDevice));
+  if (ds.kind == AB200_DEVICE_PIECEWISE_STEP) {
+    if (!ds.pw) {
+      AB200_CUDA(cudaMalloc(&ds.pw, ds.pw_host.size() * sizeof(float)));
+    }
+    AB200_CUDA(cudaMemcpy(ds.pw, ds.pw_host.data(), ds.pw_host.size() * sizeof(float),
+                          cudaMemcpyHostToDevice));
+  }
 }
 
 void Tile::toDevice(int cuda_device) {
@@ -541,6 +569,22 @@ void Tile::toDevice(int cuda_device) {
   }
   AB200_CUDA(cudaMalloc(&bm_stats_, 2 * sizeof(int)));
   AB200_CUDA(cudaMemset(bm_stats_, 0, 2 * sizeof(int)));
+  {
+    HostRNG rng(key_.k0 ^ (key_.k1 * 0x9e3779b9u) ^ 0x6f6e7631u);
+    auto draw = [&](const IOEff &io, int n, float **dst) {
+      if (io.is_perfect || !(io.out_noise_std > 0.0f)) {
+        return;
+      }
+      std::vector<float> v((size_t)n);
+      for (auto &e : v) {
+        e = std::fabs(io.out_noise * (1.0f + io.out_noise_std * rng.gauss()));
+      }
+      AB200_CUDA(cudaMalloc(dst, v.size() * sizeof(float)));
+      AB200_CUDA(cudaMemcpy(*dst, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice));
+    };
+    draw(f_io_, d_size_, &f_onv_);
+    draw(b_io_, x_size_, &b_onv_);
+  }
   for (int k = 0; k < n_dev_; k++) {
     uploadDeviceStore(dev_[k]);
   }
@@ -879,6 +923,7 @@ void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, boo
   p.m = m;
   p.backward = 0;
   p.io = f_io_;
+  p.out_noise_vals = f_onv_;
   p.alpha = 1.0f;
   p.call = fwd_calls_++;
   p.noise_id = 0;
@@ -913,6 +958,7 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
   p.m = m;
   p.backward = 0;
   p.io = f_io_;
+  p.out_noise_vals = f_onv_;
   p.alpha = out_scale; // digital scale of this tile's output (mapping scale)
   p.call = fwd_calls_++;
   p.noise_id = noise_id;
@@ -984,6 +1030,7 @@ void Tile::backwardCore(const float *d, long long d_ss, long long d_fs, float *x
   p.m = m;
   p.backward = 1;
   p.io = b_io_;
+  p.out_noise_vals = b_onv_;
   p.alpha = out_scale;
   p.call = bwd_calls_++;
   p.noise_id = noise_id;
@@ -1131,6 +1178,8 @@ void Tile::doTransfer(cudaStream_t s) {
     u.dw_min_std = dev_[1].dw_min_std;
     u.es0 = dev_[1].es0;
     u.es1 = dev_[1].es1;
+    u.pw = dev_[1].pw;
+    u.pw_n = dev_[1].pw_n;
     u.mult_noise = dev_[1].mult_noise;
     u.s_begin = 0;
     u.s_end = 1;
@@ -1225,6 +1274,8 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
   u.dw_min_std = dev_[0].dw_min_std;
   u.es0 = dev_[0].es0;
   u.es1 = dev_[0].es1;
+  u.pw = dev_[0].pw;
+  u.pw_n = dev_[0].pw_n;
   u.mult_noise = dev_[0].mult_noise;
   launchPulsePrepare(u, s);
   const bool stream_upd = streamUpdateEligible(u);

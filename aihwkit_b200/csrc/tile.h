@@ -30,6 +30,7 @@ struct IOEff {
   float out_bound;
   float res_out;
   float out_noise;
+  float out_noise_std; // > 0: the kernels read the std-dev of every output line from a table
   float out_scale;
   float w_noise;
   float nm_thres;
@@ -91,6 +92,8 @@ struct MvmProblem {
   float *sval;   // noise-management value s
   int *flags;    // bound management: sample clipped in round 1
   int *bm_stats; // [0] re-run samples, [1] max reduction (float bits)
+  // std-dev of the output noise of every output line (out_size entries) when io.out_noise_std > 0
+  const float *out_noise_vals = nullptr;
 };
 
 // CUDA-core path: noise management, fused MVM, bound-management re-run
@@ -116,6 +119,10 @@ struct DeviceStore {
   float reset_std = 0.0f;
   // ExpStep: {a, b, A_up, A_down} and {gamma_up, gamma_down, dw_min_std_add, dw_min_std_slope}
   float4 es0 = {0.f, 0.f, 0.f, 0.f}, es1 = {0.f, 0.f, 0.f, 0.f};
+  // PiecewiseStep: pw_n factors for the up direction followed by pw_n for the down direction
+  std::vector<float> pw_host;
+  float *pw = nullptr;
+  int pw_n = 0;
   // host copies, [name][d][x] in the reference's naming / order
   std::vector<std::string> names;
   std::vector<float> host;
@@ -151,6 +158,8 @@ struct UpdateProblem {
   float dw_min_std;
   int mult_noise;
   float4 es0, es1; // ExpStep globals (DeviceStore)
+  const float *pw;  // PiecewiseStep tables (DeviceStore), pw_n nodes per direction
+  int pw_n;
   int s_begin, s_end; // sample range applied by the update kernel
 };
 
@@ -327,6 +336,9 @@ private:
   int scratch_m_ = 0;
   float *scale_ = nullptr, *factor_ = nullptr, *vnorm_ = nullptr, *sval_ = nullptr;
   int *flags_ = nullptr, *bm_stats_ = nullptr;
+  // out_noise_std > 0: std-dev of the output noise of every output line, forward (d_size) and
+  // backward (x_size), drawn once per tile (rpu_forward_backward_pass.cpp:306-313)
+  float *f_onv_ = nullptr, *b_onv_ = nullptr;
   uint32_t *xw_ = nullptr, *dw_ = nullptr;
   // transposed x words [x_size][m_pad] and their bitmaps, for the streaming update of large batches
   uint32_t *xwt_ = nullptr, *xnzt_ = nullptr;

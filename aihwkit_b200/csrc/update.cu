@@ -220,8 +220,31 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
 template <int KIND>
 __device__ __forceinline__ float pulseOnce(float w, bool down, const float4 &q, const float2 &e,
                                            float xi, int mult_noise, const float4 &es0,
-                                           const float4 &es1) {
-  if (KIND == AB200_DEVICE_EXP_STEP) {
+                                           const float4 &es1, const float *pw = nullptr,
+                                           int pw_n = 0) {
+  if (KIND == AB200_DEVICE_PIECEWISE_STEP) {
+    // PiecewiseStepRPUDevice update_once (rpu_piecewisestep_device.cpp:30-80): the step factor is
+    // interpolated linearly between pw_n nodes spread evenly over [min_bound, max_bound];
+    // pw[0..pw_n) are the up factors, pw[pw_n..2 pw_n) the down factors
+    const float *tab = down ? pw + pw_n : pw;
+    const int n_sec = pw_n - 1;
+    float f;
+    if (n_sec <= 0 || q.z <= q.w) {
+      f = __ldg(tab);
+    } else {
+      const float ws = fmaxf(
+          __fmul_rn(__fdiv_rn(__fsub_rn(w, q.w), __fsub_rn(q.z, q.w)), (float)n_sec), 0.0f);
+      const int idx = min((int)floorf(ws), n_sec - 1);
+      const float t = fminf(__fsub_rn(ws, (float)idx), 1.0f);
+      const float t1 = __fsub_rn(1.0f, t);
+      f = __fadd_rn(__fmul_rn(t1, __ldg(tab + idx)), __fmul_rn(t, __ldg(tab + idx + 1)));
+    }
+    const float step = __fmul_rn(__fmul_rn(down ? q.y : q.x, f), __fadd_rn(1.0f, xi));
+    w = down ? __fsub_rn(w, step) : __fadd_rn(w, step);
+    w = fmaxf(w, q.w);
+    w = fminf(w, q.z);
+    return w;
+  } else if (KIND == AB200_DEVICE_EXP_STEP) {
     // ExpStepRPUDevice update_once / update_once_complex_noise (rpu_expstep_device.cpp:18-100):
     // z = 2 w / (max - min) * a + b;  step = scale * max(1 - A exp(+-gamma z), 0)
     // es0 = {a, b, A_up, A_down}, es1 = {gamma_up, gamma_down, std_add, std_slope}; xi = std * N
@@ -502,7 +525,8 @@ __global__ void __launch_bounds__(UT_I *UTJ / EJ, (UT_I * UTJ / EJ) >= 1024 ? 1 
           if (!loaded[0]) {
             w[0] = p.w[idx];
             q[0] = p.par4[idx];
-            if (KIND != AB200_DEVICE_CONSTANT_STEP && KIND != AB200_DEVICE_EXP_STEP) {
+            if (KIND != AB200_DEVICE_CONSTANT_STEP && KIND != AB200_DEVICE_EXP_STEP &&
+                KIND != AB200_DEVICE_PIECEWISE_STEP) {
               e[0] = p.par2[idx];
             }
             loaded[0] = true;
@@ -511,7 +535,7 @@ __global__ void __launch_bounds__(UT_I *UTJ / EJ, (UT_I * UTJ / EJ) >= 1024 ? 1 
         }
         if (!NOISY) {
           for (int k = 0; k < n; k++) {
-            w[0] = pulseOnce<KIND>(w[0], down, q[0], e[0], 0.0f, p.mult_noise, p.es0, p.es1);
+            w[0] = pulseOnce<KIND>(w[0], down, q[0], e[0], 0.0f, p.mult_noise, p.es0, p.es1, p.pw, p.pw_n);
           }
         } else {
           // One Gaussian per pulse, taken from a per-thread reservoir in shared memory: the
@@ -532,7 +556,7 @@ __global__ void __launch_bounds__(UT_I *UTJ / EJ, (UT_I * UTJ / EJ) >= 1024 ? 1 
             }
             rc--;
             w[0] = pulseOnce<KIND>(w[0], down, q[0], e[0], std * sm.sz[rc][threadIdx.x], p.mult_noise, p.es0,
-                                    p.es1);
+                                    p.es1, p.pw, p.pw_n);
           }
         }
       }
@@ -677,7 +701,8 @@ __global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p,
   if (i_ok) {
     w = p.w[idx];
     q = p.par4[idx];
-    if (KIND != AB200_DEVICE_CONSTANT_STEP && KIND != AB200_DEVICE_EXP_STEP) {
+    if (KIND != AB200_DEVICE_CONSTANT_STEP && KIND != AB200_DEVICE_EXP_STEP &&
+                KIND != AB200_DEVICE_PIECEWISE_STEP) {
       e = p.par2[idx];
     }
   }
@@ -694,9 +719,9 @@ __global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p,
       int n = 0;
       bool down = false;
       if (cnt > 0) {
-        const uint32_t ev = (uint32_t)queue & ((1u << USQ_BITS) - 1u);
-        queue >>= USQ_BITS;
+        // the oldest event sits on top: pushes shift the queue up
         cnt--;
+        const uint32_t ev = (uint32_t)(queue >> (cnt * USQ_BITS)) & ((1u << USQ_BITS) - 1u);
         n = (int)(ev >> 1);
         down = (ev & 1u) != 0u;
       }
@@ -724,7 +749,7 @@ __global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p,
           pool_pos += __popc(takers);
         }
         if (act) {
-          w = pulseOnce<KIND>(w, down, q, e, xi, p.mult_noise, p.es0, p.es1);
+          w = pulseOnce<KIND>(w, down, q, e, xi, p.mult_noise, p.es0, p.es1, p.pw, p.pw_n);
         }
       }
     }
@@ -751,8 +776,9 @@ __global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p,
     if (bits == 0u) {
       continue;
     }
-    // the x words of these 32 samples: one coalesced load, handed out by shuffle
-    const uint32_t xrow = x_line[sb + lane];
+    // the x words of these 32 samples: one coalesced load, handed out by shuffle; the sign bit is
+    // flipped here so that (x ^ d) & 1 is the direction bit of an event
+    const uint32_t xrow = x_line[sb + lane] ^ 1u;
     while (bits != 0u) {
       // up to four samples at a time, so that their d words are in flight together
       int sidx[4];
@@ -775,18 +801,18 @@ __global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p,
       for (int t = 0; t < 4; t++) {
         if (t < nb) {
           const uint32_t xwv = __shfl_sync(0xffffffffu, xrow, sidx[t]);
-          const uint32_t both = xwv & dwv[t];
-          const int n = __popc(both >> 1);
-          if (n != 0) {
+          const uint32_t both = xwv & dwv[t] & ~1u;
+          if (both != 0u) {
             // equal line signs = decrease (rpu_weight_updater.cpp:246-268)
-            const uint32_t down = (((xwv ^ dwv[t]) & 1u) == 0u) ? 1u : 0u;
-            queue |= (unsigned long long)(((uint32_t)n << 1) | down) << (cnt * USQ_BITS);
+            const uint32_t ev = ((uint32_t)__popc(both) << 1) | ((xwv ^ dwv[t]) & 1u);
+            queue = (queue << USQ_BITS) | ev;
             cnt++;
           }
-          if (__any_sync(0xffffffffu, cnt >= USQ_SLOTS)) {
-            drain();
-          }
         }
+      }
+      // room for the (at most four) events of the next group
+      if (__any_sync(0xffffffffu, cnt > USQ_SLOTS - 4)) {
+        drain();
       }
     }
   }
@@ -860,6 +886,9 @@ void launchPulsedUpdateStream(const UpdateProblem &p0, const uint32_t *xwT, cons
   case AB200_DEVICE_EXP_STEP:
     launchStreamKind<AB200_DEVICE_EXP_STEP>(p, st, stream);
     break;
+  case AB200_DEVICE_PIECEWISE_STEP:
+    launchStreamKind<AB200_DEVICE_PIECEWISE_STEP>(p, st, stream);
+    break;
   default:
     AB200_FATAL("pulsed update: device kind not implemented");
   }
@@ -911,6 +940,9 @@ void launchPulsedUpdate(const UpdateProblem &p0, cudaStream_t stream) {
     break;
   case AB200_DEVICE_EXP_STEP:
     AB200_UPD(AB200_DEVICE_EXP_STEP);
+    break;
+  case AB200_DEVICE_PIECEWISE_STEP:
+    AB200_UPD(AB200_DEVICE_PIECEWISE_STEP);
     break;
   default:
     AB200_FATAL("pulsed update: device kind not implemented");

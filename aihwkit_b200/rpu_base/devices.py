@@ -74,13 +74,13 @@ DEVICE_SOFT_BOUNDS_REFERENCE = 4
 DEVICE_TRANSFER = 5
 DEVICE_EXP_STEP = 6
 DEVICE_POW_STEP = 7
+DEVICE_PIECEWISE_STEP = 8
 
 
 class AnalogTileInputOutputParameter:
     """IOMetaParameter (rpu_base_devices.cpp:485-519)."""
 
     _unsupported = {
-        "out_noise_std": 0.0,
         "ir_drop": 0.0,
         "out_nonlinearity": 0.0,
         "out_nonlinearity_std": 0.0,
@@ -136,8 +136,6 @@ class AnalogTileInputOutputParameter:
         nm = int(self.noise_management)
         if nm not in (0, 1, 2, 3, 4):  # the running-average types keep state between calls
             raise RuntimeError("Noise Management type not implemented!")
-        if int(self.w_noise_type) == int(WeightNoiseType.PCMRead) and self.w_noise > 0:
-            raise RuntimeError("w_noise_type PCMRead is not implemented by the B200 analog tile")
         c = _cabi.IOParams()
         c.is_perfect = int(bool(self.is_perfect) or mv == int(AnalogMVType.Ideal))
         c.noise_management = nm
@@ -150,6 +148,7 @@ class AnalogTileInputOutputParameter:
         for name in (
             "inp_bound", "inp_res", "inp_noise", "out_bound", "out_res", "out_noise", "out_scale",
             "w_noise", "nm_thres", "max_bm_res", "inp_asymmetry", "out_asymmetry", "nm_assumed_wmax",
+            "out_noise_std",
         ):
             setattr(c, name, float(getattr(self, name)))
         return c
@@ -325,6 +324,50 @@ class ConstantStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):
     """rpu_base_devices.cpp:583-600."""
 
     _kind = DEVICE_CONSTANT_STEP
+
+
+class PiecewiseStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):
+    """rpu_base_devices.cpp:857-870 (PiecewiseStepRPUDeviceMetaParameter,
+    rpu_piecewisestep_device.h:17-50): the step is ``dw_min`` times a factor interpolated linearly
+    between equally spaced nodes over the weight range of the element, one table per direction."""
+
+    _kind = DEVICE_PIECEWISE_STEP
+    MAX_NODES = 32
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.piecewise_up = [1.0]
+        self.piecewise_down = [1.0]
+        self.write_noise_std = 0.0
+        self.apply_write_noise_on_set = True
+
+    def calc_weight_granularity(self) -> float:
+        """PiecewiseStepRPUDeviceMetaParameter::calcWeightGranularity
+        (rpu_piecewisestep_device.h:34-39)."""
+        up = list(self.piecewise_up)
+        if up and len(self.piecewise_down) > 0:
+            return float(self.dw_min) * float(up[len(up) // 2])
+        return float(self.dw_min)
+
+    def _to_c(self) -> _cabi.DeviceParams:
+        if self.write_noise_std != 0.0:
+            raise RuntimeError("write noise is not implemented by the B200 analog tile")
+        up, down = list(self.piecewise_up), list(self.piecewise_down)
+        if not up or not down:
+            raise RuntimeError("piecewise_up_vec and piecewise_down_vec needs to have some contents.")
+        if len(up) != len(down):
+            raise RuntimeError("piecewise_up_vec and piecewise_down_vec needs to have some size.")
+        if len(up) > self.MAX_NODES:
+            raise RuntimeError(
+                f"PiecewiseStep: at most {self.MAX_NODES} nodes per direction are implemented"
+            )
+        c = _cabi.DeviceParams()
+        self._fill_base(c)
+        c.pw_n = len(up)
+        for i, (u, d) in enumerate(zip(up, down)):
+            c.pw_up[i] = float(u)
+            c.pw_down[i] = float(d)
+        return c
 
 
 class PowStepResistiveDeviceParameter(PulsedResistiveDeviceParameter):

@@ -580,12 +580,24 @@ def main():
                     help="length of the sustained loop of the same step (clock samples inside it)")
     ap.add_argument("--e2e-chunk-rows", type=int, default=2048,
                     help="N > 1: rows per part of the pipelined end-to-end path")
-    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3],
+    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4],
                     help="1 = the mapped inference layer (the contract line); 0, 2, 3 = training "
                          "step of a single tile (aihwkit_b200.benchmarks) with the reference CPU "
-                         "tile timed beside it")
+                         "tile timed beside it; 4 = forward of the GPT-2-small-shaped stack "
+                         "(aihwkit_b200.gpt2_inference), under torchrun with --shard")
+    ap.add_argument("--shard", default="tiles", choices=["tiles", "sequences"],
+                    help="--config 4, N > 1: deal the tiles of every analog layer to the ranks "
+                         "(all-reduce of the activations per layer) or the sequences (no collective)")
     args = ap.parse_args()
-    if args.config != 1:
+    if args.config == 4:
+        from aihwkit_b200 import gpt2_inference
+        argv = ["--shard", args.shard]
+        if args.steps != 200:
+            argv += ["--steps", str(args.steps)]
+        if args.warmup != 10:
+            argv += ["--warmup", str(args.warmup)]
+        gpt2_inference.main(argv)
+    elif args.config != 1:
         run_training_config(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -70,8 +70,12 @@ enum ab200_device_kind {
   AB200_DEVICE_SOFT_BOUNDS_REFERENCE = 4, /* rpu_softbounds_reference_device.h */
   AB200_DEVICE_TRANSFER = 5,              /* rpu_transfer_device.h (Tiki-Taka) */
   AB200_DEVICE_EXP_STEP = 6,              /* rpu_expstep_device.h */
-  AB200_DEVICE_POW_STEP = 7               /* rpu_powstep_device.h */
+  AB200_DEVICE_POW_STEP = 7,              /* rpu_powstep_device.h */
+  AB200_DEVICE_PIECEWISE_STEP = 8         /* rpu_piecewisestep_device.h */
 };
+
+/* largest number of nodes of the PiecewiseStep interpolation tables */
+#define AB200_PIECEWISE_MAX_NODES 32
 
 /* IOMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:180-226); attribute names as
  * bound in src/aihwkit/simulator/rpu_base_src/rpu_base_devices.cpp:485-519.
@@ -100,6 +104,10 @@ typedef struct ab200_io_params {
   float inp_asymmetry;
   float out_asymmetry;
   float nm_assumed_wmax; /* AbsMaxNPSum noise management / IterativeWorstCase bound management */
+  /* relative spread of the output noise over the output lines: line i keeps
+   * |out_noise * (1 + out_noise_std * N(0,1))| for the life of the tile
+   * (rpu_forward_backward_pass.cpp:306-313, :696) */
+  float out_noise_std;
 } ab200_io_params;
 
 /* PulsedUpdateMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:248-279;
@@ -176,6 +184,12 @@ typedef struct ab200_device_params {
   float ps_gamma_dtod;
   float ps_gamma_up_down;
   float ps_gamma_up_down_dtod;
+  /* PiecewiseStep (PiecewiseStepRPUDeviceMetaParameter, rpu_piecewisestep_device.h:17-50; bound as
+   * piecewise_up, piecewise_down): the step is dw_min times a factor interpolated linearly
+   * between pw_n equally spaced nodes over [w_min, w_max] of the element */
+  int32_t pw_n;
+  float pw_up[AB200_PIECEWISE_MAX_NODES];
+  float pw_down[AB200_PIECEWISE_MAX_NODES];
 } ab200_device_params;
 
 /* TransferRPUDeviceMetaParameter (src/rpucuda/rpu_transfer_device.h:52-75). */

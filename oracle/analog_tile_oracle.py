@@ -34,13 +34,14 @@ f32 = np.float32
 # enum values: src/rpucuda/rpu_pulsed_meta_parameter.h:146-178
 NM_NONE, NM_ABS_MAX, NM_ABS_MAX_NP_SUM, NM_MAX, NM_CONSTANT = 0, 1, 2, 3, 4
 BM_NONE, BM_ITERATIVE, BM_ITERATIVE_WORST_CASE = 0, 1, 2
-WN_NONE, WN_ADDITIVE_CONSTANT = 0, 1
+WN_NONE, WN_ADDITIVE_CONSTANT, WN_PCM_READ = 0, 1, 2
 PULSE_NONE, PULSE_STOCHASTIC_COMPRESSED, PULSE_DETERMINISTIC_IMPLICIT = 0, 1, 5
 PULSE_MEAN_COUNT = 4
 DEV_IDEAL, DEV_CONSTANT_STEP, DEV_LINEAR_STEP, DEV_SOFT_BOUNDS, DEV_SOFT_BOUNDS_REFERENCE = range(5)
 DEV_TRANSFER = 5
 DEV_EXP_STEP = 6
 DEV_POW_STEP = 7
+DEV_PIECEWISE_STEP = 8
 
 
 def _check_res(res: float) -> np.float32:
@@ -206,6 +207,10 @@ def _analog_mv(
     if io.w_noise_type == WN_ADDITIVE_CONSTANT and io.w_noise > 0 and rng is not None:
         nrm = np.sqrt((v.astype(np.float64) ** 2).sum(axis=1)).astype(f32)
         y = (y + (f32(io.w_noise) * nrm)[:, None] * rng.standard_normal(y.shape).astype(f32)).astype(f32)
+    if io.w_noise_type == WN_PCM_READ and io.w_noise > 0 and rng is not None:
+        # :353-381: std-dev w_noise * sqrt(sum_j |w_ij| v_j^2) per output
+        var = ((v.astype(np.float64) ** 2) @ np.abs(w_op.astype(np.float64)).T)
+        y = (y + f32(io.w_noise) * np.sqrt(var).astype(f32) * rng.standard_normal(y.shape).astype(f32)).astype(f32)
     # finalizeOutput (:673-719): asymmetry, noise, ADC, clip
     if io.out_asymmetry != 0:
         y = np.where(y < 0, (y * f32(f32(1.0) - f32(io.out_asymmetry))).astype(f32), y).astype(f32)
@@ -477,6 +482,8 @@ class DeviceArrays:
     mult_noise: bool = True
     # ExpStep globals: (a, b, A_up, A_down, gamma_up, gamma_down, dw_min_std_add, dw_min_std_slope)
     es: Optional[tuple] = None
+    # PiecewiseStep: (up factors, down factors) at equally spaced nodes over [min_bound, max_bound]
+    pw: Optional[tuple] = None
 
     @staticmethod
     def from_hidden(kind: int, names, hp: np.ndarray, dw_min_std: float, mult_noise: bool, suffix=""):
@@ -577,6 +584,29 @@ def apply_pulses(w: np.ndarray, n_signed: np.ndarray, dev: DeviceArrays,
             wn = np.where(down, w - dn, w + up_).astype(f32)
             wn = np.minimum(np.maximum(wn, dev.min_bound), dev.max_bound)
             wn = np.where(rng_w == 0, w, wn)
+        elif dev.kind == DEV_PIECEWISE_STEP:
+            # rpu_piecewisestep_device.cpp:30-80
+            up_t, dn_t = (np.asarray(t, f32) for t in dev.pw)
+            n_sec = len(up_t) - 1
+            rng_w = (dev.max_bound - dev.min_bound).astype(f32)
+            if n_sec <= 0:
+                f_up = np.full_like(w, up_t[0])
+                f_dn = np.full_like(w, dn_t[0])
+            else:
+                with np.errstate(divide="ignore", invalid="ignore"):
+                    ws = np.maximum((((w - dev.min_bound) / rng_w).astype(f32) * f32(n_sec)).astype(f32), f32(0))
+                ws = np.where(rng_w > 0, ws, f32(0)).astype(f32)
+                idx = np.minimum(np.floor(ws).astype(np.int64), n_sec - 1)
+                t = np.minimum((ws - idx.astype(f32)).astype(f32), f32(1))
+                t1 = (f32(1) - t).astype(f32)
+                f_up = ((t1 * up_t[idx]).astype(f32) + (t * up_t[idx + 1]).astype(f32)).astype(f32)
+                f_dn = ((t1 * dn_t[idx]).astype(f32) + (t * dn_t[idx + 1]).astype(f32)).astype(f32)
+                f_up = np.where(rng_w > 0, f_up, up_t[0]).astype(f32)
+                f_dn = np.where(rng_w > 0, f_dn, dn_t[0]).astype(f32)
+            dn = ((dev.dwmin_down * f_dn).astype(f32) * (f32(1.0) + xi)).astype(f32)
+            up_ = ((dev.dwmin_up * f_up).astype(f32) * (f32(1.0) + xi)).astype(f32)
+            wn = np.where(down, w - dn, w + up_).astype(f32)
+            wn = np.minimum(np.maximum(wn, dev.min_bound), dev.max_bound)
         else:
             raise NotImplementedError("device kind")
         w[act] = wn[act]

@@ -16,6 +16,7 @@
 #include "rpu_constantstep_device.h"
 #include "rpu_expstep_device.h"
 #include "rpu_linearstep_device.h"
+#include "rpu_piecewisestep_device.h"
 #include "rpu_powstep_device.h"
 #include "rpu_pulsed.h"
 #include "rpu_softbounds_reference_device.h"
@@ -53,6 +54,7 @@ void toIO(const ab200_io_params &s, IOMetaParameter<float> &io) {
   io.inp_asymmetry = s.inp_asymmetry;
   io.out_asymmetry = s.out_asymmetry;
   io.nm_assumed_wmax = s.nm_assumed_wmax;
+  io.out_noise_std = s.out_noise_std;
 }
 
 void toUp(const ab200_update_params &s, PulsedUpdateMetaParameter<float> &up) {
@@ -147,6 +149,13 @@ std::unique_ptr<PulsedRPUDeviceMetaParameter<float>> makeSingle(const ab200_devi
     p->ps_gamma_dtod = s.ps_gamma_dtod;
     p->ps_gamma_up_down = s.ps_gamma_up_down;
     p->ps_gamma_up_down_dtod = s.ps_gamma_up_down_dtod;
+    return p;
+  }
+  case AB200_DEVICE_PIECEWISE_STEP: {
+    auto p = std::make_unique<PiecewiseStepRPUDeviceMetaParameter<float>>();
+    toPulsedBase(s, *p);
+    p->piecewise_up_vec.assign(s.pw_up, s.pw_up + s.pw_n);
+    p->piecewise_down_vec.assign(s.pw_down, s.pw_down + s.pw_n);
     return p;
   }
   default:

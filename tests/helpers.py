@@ -14,6 +14,7 @@ KINDS = {
     "sbr": D.SoftBoundsReferenceResistiveDeviceParameter,
     "es": D.ExpStepResistiveDeviceParameter,
     "ps": D.PowStepResistiveDeviceParameter,
+    "pw": D.PiecewiseStepResistiveDeviceParameter,
 }
 
 
@@ -69,6 +70,17 @@ def device(kind: str, noise: bool, seed: int = 11, **kw):
     for k, v in kw.items():
         setattr(dp, k, v)
     return dp
+
+
+PIECEWISE_UP = [1.2, 1.0, 0.8, 0.55, 0.4, 0.3]
+PIECEWISE_DOWN = [0.25, 0.5, 0.7, 0.9, 1.0, 1.3]
+
+
+def piecewise_device(noise: bool, **kw):
+    """PiecewiseStep with six nodes per direction: steps up shrink towards the upper bound, steps
+    down towards the lower one."""
+    return device("pw", noise, piecewise_up=list(PIECEWISE_UP), piecewise_down=list(PIECEWISE_DOWN),
+                  dw_min=0.002, dw_min_dtod=0.2, up_down=0.05, up_down_dtod=0.02, **kw)
 
 
 def transfer_device(noise: bool, seed: int = 21, transfer_every: float = 2.0,

@@ -1,0 +1,185 @@
+"""GPU checks of two IO settings whose noise std-dev differs from element to element:
+
+* ``w_noise_type = PCMRead``: the Gaussian added to output i has std-dev
+  ``w_noise * sqrt(sum_j |w_ij| v_j^2)``, v the DAC output
+  (src/rpucuda/rpu_forward_backward_pass.cpp:353-381);
+* ``out_noise_std``: every output line keeps ``|out_noise * (1 + out_noise_std * N(0,1))|`` for the
+  life of the tile (:306-313, :696), forward and backward lines drawn separately.
+
+Both are random, so the criteria are moments: the empirical std-dev of every output element over
+repeated calls against the closed form (PCMRead) and against the compiled reference tile run on
+the same inputs; the spread, mean and persistence of the per-line values (out_noise_std)."""
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def _params(out_noise, w_noise=0.0, pcm=False, out_noise_std=0.0):
+    from aihwkit_b200.rpu_base import devices as D
+
+    p = H.training_params(noise=False, pulse_det=True, bm=False, adc=False, out_bound=0.0)
+    for io in (p.forward_io, p.backward_io):
+        io.out_noise = out_noise
+        io.out_noise_std = out_noise_std
+        io.w_noise = w_noise
+        io.w_noise_type = D.WeightNoiseType.PCMRead if pcm else D.WeightNoiseType.None_
+    return p
+
+
+def _repeat(fn, n):
+    return np.stack([fn() for _ in range(n)])
+
+
+@pytest.mark.parametrize("x_size,d_size,m", [(128, 96, 16), (300, 70, 40)])
+def test_pcm_read_noise_std_per_element(x_size, d_size, m):
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    rng = np.random.default_rng(x_size)
+    p = _params(out_noise=0.0, w_noise=0.1, pcm=True)
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=9)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().cpu().numpy()  # clipped to the bounds of the devices
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    xg = torch.from_numpy(X).cuda()
+    reps = 400
+    ys = _repeat(lambda: t.forward(xg).cpu().numpy(), reps)
+    # closed form: v = DAC(x / amax), output rescaled by amax
+    amax = np.abs(X).max(axis=1, keepdims=True)
+    res = np.float32(2.0 / 126.0)
+    v = np.clip(np.rint(X / amax / res) * res, -1, 1)
+    sig = 0.1 * np.sqrt((v.astype(np.float64) ** 2) @ np.abs(W.astype(np.float64)).T) * amax
+    mean = (v.astype(np.float64) @ W.astype(np.float64).T) * amax
+    est = ys.std(axis=0)
+    # sampling error of a std-dev estimate from `reps` draws: 1 / sqrt(2 reps) = 3.5 %
+    ratio = est / sig
+    assert abs(ratio.mean() - 1.0) < 0.01, ratio.mean()
+    assert np.abs(ratio - 1.0).max() < 5.5 / np.sqrt(2 * reps), np.abs(ratio - 1.0).max()
+    zmean = (ys.mean(axis=0) - mean) / (sig / np.sqrt(reps))
+    assert np.abs(zmean).max() < 5.5, np.abs(zmean).max()
+    # backward: the transposed weights, std-dev per input line
+    Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+    dg = torch.from_numpy(Dm).cuda()
+    gs = _repeat(lambda: t.backward(dg).cpu().numpy(), reps)
+    dmax = np.abs(Dm).max(axis=1, keepdims=True)
+    vd = np.clip(np.rint(Dm / dmax / res) * res, -1, 1)
+    sig_b = 0.1 * np.sqrt((vd.astype(np.float64) ** 2) @ np.abs(W.astype(np.float64))) * dmax
+    rb = gs.std(axis=0) / sig_b
+    assert abs(rb.mean() - 1.0) < 0.01 and np.abs(rb - 1.0).max() < 5.5 / np.sqrt(2 * reps)
+    if ref.available():
+        rt = ref.RefTile(cfg)
+        rt.set_weights(W)
+        yr = _repeat(lambda: rt.forward(X), reps)
+        rr = est / yr.std(axis=0)
+        assert abs(rr.mean() - 1.0) < 0.015 and np.abs(rr - 1.0).max() < 0.3, (rr.mean(), rr.max())
+
+
+def test_pcm_read_with_bound_management_rerun():
+    """Rows that clip are re-run with a halved input: the re-run kernel draws with the std-dev of
+    the halved input as well."""
+    from aihwkit_b200.rpu_base import devices as D
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(3)
+    x_size, d_size, m = 64, 32, 8
+    p = H.training_params(noise=False, pulse_det=True, bm=True, adc=False, out_bound=1.0)
+    p.forward_io.w_noise = 0.05
+    p.forward_io.w_noise_type = D.WeightNoiseType.PCMRead
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=9)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    W = np.full((d_size, x_size), 0.05, np.float32)  # every output = 0.05 * sum(v): clips at 1
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().cpu().numpy()  # clipped to the bounds of the devices
+    X = rng.uniform(0.5, 1.0, (m, x_size)).astype(np.float32)
+    xg = torch.from_numpy(X).cuda()
+    ys = _repeat(lambda: t.forward(xg).cpu().numpy(), 300)
+    n_rerun, max_red = t.last_bm_stats()
+    assert n_rerun == m and max_red >= 2.0
+    exact = X @ W.T
+    # bound management recovers the unclipped value (up to the coarser DAC grid) plus noise
+    assert np.abs(ys.mean(axis=0) - exact).max() < 0.05 * np.abs(exact).max()
+    assert ys.std(axis=0).min() > 0.0
+
+
+def test_out_noise_std_per_line_values_persist():
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    rng = np.random.default_rng(17)
+    x_size, d_size, m = 96, 256, 32
+    out_noise, spread = 0.1, 0.4
+    p = _params(out_noise=out_noise, out_noise_std=spread)
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=21)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    W = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().cpu().numpy()  # clipped to the bounds of the devices
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    X /= np.abs(X).max(axis=1, keepdims=True)  # abs-max 1: the output factor is 1 for every row
+    xg = torch.from_numpy(X).cuda()
+    reps = 100
+    ys = _repeat(lambda: t.forward(xg).cpu().numpy(), reps)
+    dev = ys - ys.mean(axis=0, keepdims=True)
+    # per-line std-dev from the two halves of the repeats: the same lines are noisy in both
+    a = dev[: reps // 2].reshape(-1, d_size).std(axis=0)
+    b = dev[reps // 2:].reshape(-1, d_size).std(axis=0)
+    assert np.corrcoef(a, b)[0, 1] > 0.98
+    line = dev.reshape(-1, d_size).std(axis=0) * np.sqrt(reps / (reps - 1.0))
+    # E|1 + s z| = 1 up to the 0.6 % of the mass below zero; spread of 256 lines: +-4.4 % (1 sigma)
+    assert abs(line.mean() / out_noise - 1.0) < 0.1, line.mean()
+    assert abs(line.std() / line.mean() / spread - 1.0) < 0.2, line.std() / line.mean()
+    # the backward lines have their own values (x_size of them)
+    Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+    Dm /= np.abs(Dm).max(axis=1, keepdims=True)
+    dg = torch.from_numpy(Dm).cuda()
+    gs = _repeat(lambda: t.backward(dg).cpu().numpy(), reps)
+    gdev = (gs - gs.mean(axis=0, keepdims=True)).reshape(-1, x_size)
+    gline = gdev.std(axis=0) * np.sqrt(reps / (reps - 1.0))
+    assert abs(gline.mean() / out_noise - 1.0) < 0.15
+    assert abs(gline.std() / gline.mean() / spread - 1.0) < 0.35
+    # a second tile with another seed has other lines
+    cfg2 = p._config(x_size, d_size, H.device("cs", False), seed=22)
+    t2 = T.AnalogTile(cfg2, cuda_device=0)
+    t2.set_weights(torch.from_numpy(W))
+    y2 = _repeat(lambda: t2.forward(xg).cpu().numpy(), reps)
+    line2 = (y2 - y2.mean(axis=0, keepdims=True)).reshape(-1, d_size).std(axis=0)
+    assert np.corrcoef(line, line2)[0, 1] < 0.5
+    if ref.available():
+        rt = ref.RefTile(cfg)
+        rt.set_weights(W)
+        yr = _repeat(lambda: rt.forward(X), reps)
+        rline = (yr - yr.mean(axis=0, keepdims=True)).reshape(-1, d_size).std(axis=0)
+        assert abs(rline.mean() / line.mean() - 1.0) < 0.15
+        assert abs((rline.std() / rline.mean()) / (line.std() / line.mean()) - 1.0) < 0.3
+
+
+def test_line_noise_settings_take_the_cuda_core_kernels_at_tensor_core_sizes():
+    """A mapped-layer-sized forward with PCMRead noise is accepted (the tensor-core kernel is not
+    eligible) and its noise follows the closed form on a sample of elements."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(5)
+    x_size, d_size, m = 512, 512, 512
+    p = _params(out_noise=0.02, w_noise=0.05, pcm=True)
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=9)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().cpu().numpy()  # clipped to the bounds of the devices
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    xg = torch.from_numpy(X).cuda()
+    reps = 60
+    ys = _repeat(lambda: t.forward(xg)[:8].cpu().numpy(), reps)
+    amax = np.abs(X[:8]).max(axis=1, keepdims=True)
+    res = np.float32(2.0 / 126.0)
+    v = np.clip(np.rint(X[:8] / amax / res) * res, -1, 1).astype(np.float64)
+    sig = np.sqrt(0.02 ** 2 + 0.05 ** 2 * ((v ** 2) @ np.abs(W.astype(np.float64)).T)) * amax
+    ratio = ys.std(axis=0) / sig
+    assert abs(ratio.mean() - 1.0) < 0.02 and np.abs(ratio - 1.0).max() < 0.5

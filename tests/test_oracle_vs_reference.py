@@ -418,6 +418,45 @@ def test_pow_step_device_noise_off(shape):
     assert np.abs(t.get_weights() - W).max() > 1e-3  # the update did something
 
 
+@pytest.mark.parametrize("shape", [(96, 64, 32), (33, 70, 5)])
+@pytest.mark.parametrize("nodes", [6, 1])
+def test_piecewise_step_device_noise_off(shape, nodes):
+    """PiecewiseStep device (rpu_piecewisestep_device.cpp:30-80): granularity, host parameter draw
+    and the weights after a deterministic update; one node = the short-cut without interpolation."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    x_size, d_size, m = shape
+    rng = np.random.default_rng(x_size + nodes)
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+    dp = H.piecewise_device(False)
+    if nodes == 1:
+        dp.piecewise_up, dp.piecewise_down = [0.7], [1.1]
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = ref.RefTile(cfg)
+    ours = T.AnalogTile(cfg)
+    names = t.hidden_parameter_names()
+    assert names == ours.get_hidden_parameter_names()
+    assert np.array_equal(ours.get_hidden_parameters().numpy(), t.get_hidden_parameters())
+    t.set_weights(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32))
+    W = t.get_weights()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+    lr = 0.01
+    gran = dp.calc_weight_granularity()
+    assert gran == pytest.approx(dp.dw_min * dp.piecewise_up[len(dp.piecewise_up) // 2])
+    up = O.Up.from_c(cfg.update)
+    assert np.array_equal(t.coincidences(X[0], Dm[0], lr, gran),
+                          O.coincidences_det_implicit(X[0], Dm[0], lr, gran, up))
+    dev = O.DeviceArrays.from_hidden(O.DEV_PIECEWISE_STEP, names, t.get_hidden_parameters(), 0.0, True)
+    dev.pw = (dp.piecewise_up, dp.piecewise_down)
+    t.set_learning_rate(lr)
+    t.update(X, Dm)
+    Wo = W.copy()
+    O.update(Wo, X, Dm, lr, gran, up, dev)
+    assert np.abs(t.get_weights() - Wo).max() <= 1e-6
+    assert np.abs(t.get_weights() - W).max() > 1e-3  # the update did something
+
+
 @pytest.mark.parametrize("kind,bl,ubl", [("cs", 31, True), ("sb", 100, True), ("cs", 20, False)])
 def test_mean_count_pulse_type(kind, bl, ubl):
     """PulseType.MeanCount (the mean number of pulses per line, no fluctuation; pulse trains

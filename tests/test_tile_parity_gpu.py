@@ -476,6 +476,90 @@ def test_pow_step_stochastic_update_statistics():
     H.assert_moments_agree(np.stack(dws), np.stack(dwo))
 
 
+def _piecewise_arrays(t, dp, std):
+    dev = O.DeviceArrays.from_hidden(O.DEV_PIECEWISE_STEP, t.get_hidden_parameter_names(),
+                                     t.get_hidden_parameters().numpy(), std, True)
+    dev.pw = (dp.piecewise_up, dp.piecewise_down)
+    return dev
+
+
+@pytest.mark.parametrize("x_size,d_size,m", [(64, 48, 17), (70, 130, 9), (256, 256, 300)])
+def test_piecewise_step_deterministic_update(x_size, d_size, m):
+    """PiecewiseStep device (rpu_piecewisestep_device.cpp:30-80): bit-exact pulse counts with the
+    device's own granularity, weights after the update within 1e-6 of the oracle (which equals the
+    compiled reference for this device, tests/test_oracle_vs_reference.py)."""
+    rng = np.random.default_rng(5 + x_size)
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.piecewise_device(False)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    up = O.Up.from_c(cfg.update)
+    lr, gran = 0.01, dp.calc_weight_granularity()
+    t.set_learning_rate(lr)
+    c = t.coincidences(torch.from_numpy(X[0]).cuda(), torch.from_numpy(Dm[0]).cuda()).cpu().numpy()
+    assert np.array_equal(c, O.coincidences_det_implicit(X[0], Dm[0], lr, gran, up))
+    W_or = W.copy()
+    O.update(W_or, X, Dm, lr, gran, up, _piecewise_arrays(t, dp, 0.0))
+    t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    W_new = t.get_weights().numpy()
+    assert np.abs(W_new - W).max() > 1e-3
+    assert np.abs(W_new - W_or).max() <= 1e-6
+
+
+def test_piecewise_step_stochastic_update_statistics():
+    rng = np.random.default_rng(23)
+    x_size, d_size, m, reps = 32, 24, 10, 150
+    p = H.training_params(noise=True, pulse_det=False)
+    dp = H.piecewise_device(True)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    W0 = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    up = O.Up.from_c(cfg.update)
+    dev = _piecewise_arrays(t, dp, dp.dw_min_std)
+    lr, gran = 0.05, dp.calc_weight_granularity()
+    t.set_learning_rate(lr)
+    xg, dg = torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda()
+    dws, dwo = [], []
+    org = np.random.default_rng(123)
+    for _ in range(reps):
+        t.set_weights(torch.from_numpy(W0))
+        Wc = t.get_weights().numpy()
+        t.update(xg, dg)
+        dws.append(t.get_weights().numpy() - Wc)
+        Wo = Wc.copy()
+        O.update(Wo, X, Dm, lr, gran, up, dev, org)
+        dwo.append(Wo - Wc)
+    H.assert_moments_agree(np.stack(dws), np.stack(dwo))
+
+
+def test_piecewise_step_stream_kernel_equals_staged():
+    """Both update kernels apply the same pulses in the same per-weight order."""
+    from aihwkit_b200 import _cabi
+
+    rng = np.random.default_rng(41)
+    x_size, d_size, m = 96, 64, 1100
+    p = H.training_params(noise=True, pulse_det=False)
+    dp = H.piecewise_device(False)
+    W0 = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    res = []
+    lib = _cabi.lib()
+    try:
+        for path in (1, 2):
+            lib.ab200_set_update_path(path)
+            t, _ = _tile(p, dp, x_size, d_size)
+            t.set_weights(torch.from_numpy(W0))
+            t.set_learning_rate(0.05)
+            t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+            res.append(t.get_weights().numpy())
+    finally:
+        lib.ab200_set_update_path(0)
+    assert np.abs(res[0] - W0).max() > 1e-3
+    assert np.array_equal(res[0], res[1])
+
+
 @pytest.mark.parametrize("kind,bl,ubl", [("cs", 31, True), ("sb", 100, True), ("cs", 20, False)])
 def test_mean_count_pulse_type(kind, bl, ubl):
     """PulseType.MeanCount on the GPU: bit-exact coincidence counts (pulse trains longer than 31
