@@ -195,10 +195,12 @@ def run(config: int, steps: int = 20, warmup: int = 3, batch: int = 0, indexed: 
     # the same step without a host synchronisation between steps: what a training loop sees
     e0, e1 = ev(), ev()
     e0.record()
+    th0 = time.perf_counter()
     for _ in range(steps):
         fwd()
         bwd()
         upd()
+    host_ms = 1e3 * (time.perf_counter() - th0) / steps  # time the host needs to enqueue a step
     e1.record()
     torch.cuda.synchronize()
     stream_ms = e0.elapsed_time(e1) / steps
@@ -233,7 +235,7 @@ def run(config: int, steps: int = 20, warmup: int = 3, batch: int = 0, indexed: 
         "config": config, "indexed": bool(indexed), "x_size": x_size, "d_size": d_size, "batch": m,
         "value": m / (stream_ms * 1e-3), "unit": "columns/s",
         "ms": {"forward": t_f, "backward": t_b, "update": t_u, "step_sum_of_phases": step_ms,
-               "step_back_to_back": stream_ms, "wall_per_step": 1e3 * wall / k},
+               "step_back_to_back": stream_ms, "host_enqueue_per_step": host_ms, "wall_per_step": 1e3 * wall / k},
         "launch_floor_us_per_launch": floor_us,
         "forward_roofline": mvm_roofline(t_f, launches[0]),
         "backward_roofline": mvm_roofline(t_b, launches[1]),

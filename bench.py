@@ -488,9 +488,11 @@ def run_ours(args):
                 "frac": achieved / peak,
                 "terms": 2, "frac_of_split_bf16_peak": achieved / (peak / 2),
                 # dram__bytes_read.sum + dram__bytes_write.sum of the step's two kernels on one
-                # GPU (DAC 201 MB + MVM 411 MB), from the ncu captures summarised under profiles/;
-                # algorithmic bytes of the step are 335 MB
-                "traffic": 612.0e6 if world == 1 else None,
+                # GPU (dacQuantizeRowKernel 173 MB + mvmTcKernel 419 MB), from the two ncu captures
+                # of this command summarised in profiles/mvmTcKernel_cfg1_inference_4096x4096_b8192.md;
+                # algorithmic bytes of the step are 536 MB (input 134, codes 67 written + 67 read,
+                # bf16 hi / lo operands 134, output 134)
+                "traffic": 592.0e6 if world == 1 else None,
                 "peak_source": f"bf16_tflops (burst), {peaks['source']}",
                 "kernel": ("DAC + IO-managed MVM of this rank's tiles: the timed step itself"
                            if world == 1 else "DAC + MVM + peer stores phase of the step (max over ranks)"),
