@@ -61,6 +61,14 @@ class UpdateParams(C.Structure):
     ]
 
 
+class DriftParams(C.Structure):
+    """``ab200_drift_params`` (DriftParameter, src/rpucuda/weight_drifter.h:17-60)."""
+
+    _fields_ = [(n, C.c_float) for n in (
+        "nu", "nu_dtod", "nu_std", "wg_ratio", "g_offset", "w_offset", "nu_k", "log_g0", "t0",
+        "reset_tol", "w_read_std")]
+
+
 class DeviceParams(C.Structure):
     """``ab200_device_params`` (PulsedRPUDeviceMetaParameter, rpu_pulsed_device.h:60-110)."""
 
@@ -114,6 +122,7 @@ class DeviceParams(C.Structure):
         ("pw_n", C.c_int32),
         ("pw_up", C.c_float * 32),
         ("pw_down", C.c_float * 32),
+        ("drift", DriftParams),
     ]
 
 
@@ -224,6 +233,7 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_dump_extra": (_I, [_VP, C.POINTER(C.c_double)]),
         "ab200_tile_load_extra": (_I, [_VP, C.POINTER(C.c_char_p), C.POINTER(C.c_double), _I, _I]),
         "ab200_tile_decay_weights": (_I, [_VP, C.c_float, _I, _VP]),
+        "ab200_tile_drift_weights": (_I, [_VP, C.c_float, _VP]),
         "ab200_tile_diffuse_weights": (_I, [_VP, _VP]),
         "ab200_tile_clip_weights": (_I, [_VP, _I, C.c_float, C.c_float, _VP]),
         "ab200_tile_reset_columns": (_I, [_VP, _I, _I, C.c_float, _VP]),

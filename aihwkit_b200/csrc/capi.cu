@@ -133,6 +133,11 @@ void ab200_default_device_params(ab200_device_params *dp, int32_t kind) {
   dp->ps_gamma_dtod = 0.1f;
   dp->ps_gamma_up_down = 0.0f;
   dp->ps_gamma_up_down_dtod = 0.0f;
+  dp->pw_n = 1; /* rpu_piecewisestep_device.h:24-25 */
+  dp->pw_up[0] = dp->pw_down[0] = 1.0f;
+  dp->drift.wg_ratio = 1.0f; /* weight_drifter.h:17-45 */
+  dp->drift.t0 = 1.0f;
+  dp->drift.reset_tol = 1e-7f;
   if (kind == AB200_DEVICE_SOFT_BOUNDS) {
     dp->ls_decrease_up = dp->ls_decrease_down = 1.0f;
     dp->ls_decrease_up_dtod = dp->ls_decrease_down_dtod = 0.0f;
@@ -363,6 +368,12 @@ int ab200_tile_load_extra(ab200_tile *tile, const char *const *names, const doub
                           int count, int strict) {
   AB200_TRY
   T(tile)->loadExtra(names, values, count, strict != 0);
+  AB200_CATCH
+}
+
+int ab200_tile_drift_weights(ab200_tile *tile, float time_since_last_call, void *stream) {
+  AB200_TRY
+  T(tile)->driftWeights(time_since_last_call, (cudaStream_t)stream);
   AB200_CATCH
 }
 

@@ -8,6 +8,7 @@
 #include <sstream>
 #include <stdexcept>
 #include <string>
+#include <utility>
 
 namespace ab200 {
 
@@ -35,6 +36,38 @@ void countLaunch(int n = 1);
     ab200::countLaunch();                                                                          \
     AB200_CUDA(cudaGetLastError());                                                                \
   } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch for the chains of small kernels of a training step (noise
+// management -> MVM -> bound-management re-run -> pulse preparation -> update): a kernel launched
+// with launchChained may be scheduled while its predecessor in the stream still runs, so that its
+// launch latency hides behind it. Every such kernel starts with pdlEnter(): it waits there until
+// the predecessor grid has completed and its writes are visible, and then lets its own successor
+// start launching. Before pdlEnter() a kernel touches no global memory. Set AB200_PDL=0 to launch
+// the same kernels with plain stream order.
+// ---------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdlEnter() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+#endif
+bool pdlEnabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launchChained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdlEnabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
 
 // ---------------------------------------------------------------------------------------------
 // Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11).

@@ -21,7 +21,13 @@ namespace ab200 {
 // thread per sample (feature-major layouts), so that loads stay coalesced either way.
 // ---------------------------------------------------------------------------------------------
 template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKernel(MvmProblem p) {
+  pdlEnter();
   const IOEff &io = p.io;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && !p.backward && p.bm_stats) {
+    // counters of the bound-management re-run of this pass
+    p.bm_stats[0] = 0;
+    p.bm_stats[1] = 0;
+  }
   int lane = threadIdx.x & 31;
   int s = WARP_PER_SAMPLE ? (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5)
                           : (int)(blockIdx.x * (long long)blockDim.x + threadIdx.x);
@@ -90,6 +96,7 @@ template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKe
 // PCM: also accumulate sum_k |w| v^2 per output, the variance factor of the PCMRead weight noise.
 template <bool A_K_FAST, bool B_N_FAST, int T, bool PCM>
 __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
+  pdlEnter();
   constexpr int BM = 16 * T, BN = 16 * T;
   constexpr int BK = T == 1 ? 64 : (T == 2 ? 32 : 16);
   __shared__ float As[BK][BM + 4];
@@ -256,6 +263,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
 // the reference CPU tile. Nothing is copied to the host.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
+  pdlEnter();
   extern __shared__ float v_sh[]; // K prepared inputs
   __shared__ float red_sh[8];
   const IOEff &io = p.io;
@@ -383,9 +391,9 @@ void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
   bool sample_contig = p.in_fs == 1;
   if (sample_contig) {
     int blocks = (int)(((long long)p.m * 32 + 255) / 256);
-    nmScaleKernel<true><<<blocks, 256, 0, stream>>>(p);
+    AB200_CUDA(launchChained(nmScaleKernel<true>, dim3(blocks), dim3(256), 0, stream, p));
   } else {
-    nmScaleKernel<false><<<(p.m + 255) / 256, 256, 0, stream>>>(p);
+    AB200_CUDA(launchChained(nmScaleKernel<false>, dim3((p.m + 255) / 256), dim3(256), 0, stream, p));
   }
   AB200_LAUNCH_CHECK();
 
@@ -408,13 +416,13 @@ void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
   {                                                                                                \
     dim3 grid((p.out_size + 16 * TT - 1) / (16 * TT), (p.m + 16 * TT - 1) / (16 * TT));           \
     if (a_k_fast && b_n_fast) {                                                                    \
-      mvmSimtKernel<true, true, TT, PCM><<<grid, 256, 0, stream>>>(p);                             \
+      AB200_CUDA(launchChained(mvmSimtKernel<true, true, TT, PCM>, grid, dim3(256), 0, stream, p));                             \
     } else if (a_k_fast) {                                                                         \
-      mvmSimtKernel<true, false, TT, PCM><<<grid, 256, 0, stream>>>(p);                            \
+      AB200_CUDA(launchChained(mvmSimtKernel<true, false, TT, PCM>, grid, dim3(256), 0, stream, p));                            \
     } else if (b_n_fast) {                                                                         \
-      mvmSimtKernel<false, true, TT, PCM><<<grid, 256, 0, stream>>>(p);                            \
+      AB200_CUDA(launchChained(mvmSimtKernel<false, true, TT, PCM>, grid, dim3(256), 0, stream, p));                            \
     } else {                                                                                       \
-      mvmSimtKernel<false, false, TT, PCM><<<grid, 256, 0, stream>>>(p);                           \
+      AB200_CUDA(launchChained(mvmSimtKernel<false, false, TT, PCM>, grid, dim3(256), 0, stream, p));                           \
     }                                                                                              \
   }
   if (pcm) { // the second accumulator doubles the registers of a thread: the 32-wide tile at most
@@ -450,7 +458,7 @@ void launchBmRerun(const MvmProblem &p, cudaStream_t stream) {
                                     200 * 1024));
   }
   int blocks = p.m < 592 ? p.m : 592;
-  bmRerunKernel<<<blocks, 256, smem, stream>>>(p);
+  AB200_CUDA(launchChained(bmRerunKernel, dim3(blocks), dim3(256), smem, stream, p));
   AB200_LAUNCH_CHECK();
 }
 
@@ -557,9 +565,8 @@ void forwardNoAlloc(const ab200_io_params &io_user, const float *w_dev_xd, int x
   p.sval = f + 3 * (size_t)kNoAllocMaxBatch;
   p.flags = reinterpret_cast<int *>(f + 4 * (size_t)kNoAllocMaxBatch);
   p.bm_stats = reinterpret_cast<int *>(base + (size_t)kNoAllocMaxBatch * 5 * sizeof(float));
-  // the array keeps what the previous call left: the two counters must start at zero (the
-  // per-sample entries are rewritten by the first kernel before anything reads them)
-  AB200_CUDA(cudaMemsetAsync(p.bm_stats, 0, 2 * sizeof(int), stream));
+  // the array keeps what the previous call left: the first kernel zeroes the two counters and
+  // rewrites the per-sample entries before anything reads them
   launchMvm(p, stream);
 }
 

@@ -346,6 +346,7 @@ template <bool BM, bool PAIR, bool CODES = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     mvmTcKernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_bhi,
                 const __grid_constant__ CUtensorMap tm_blo, const TcKernelParams p) {
+  pdlEnter();
   constexpr int STAGES = PAIR ? TC2_STAGES : TC_STAGES;
   constexpr int STAGE_BYTES = PAIR ? TC2_STAGE_BYTES : TC_STAGE_BYTES;
   constexpr int KCH = PAIR ? TC2_KCH : TC_KCH;
@@ -959,6 +960,7 @@ __device__ __forceinline__ void dacRowScalars(const DacParams &p, int i, int row
 // any in-split length and alignment: one warp per (row, in-split), two passes over the row (the
 // second one hits L1 / L2)
 __global__ void __launch_bounds__(256) dacQuantizeKernel(DacParams p) {
+  pdlEnter();
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= (long long)p.m * p.I) {
@@ -1089,6 +1091,7 @@ __device__ __forceinline__ void dacQuantRows(const DacParams &p, int i0, int row
 // Small CTAs with at most 64 registers per thread: one of them fits on an SM beside a CTA of the
 // MMA kernel, several when the kernel runs alone.
 __global__ void __launch_bounds__(128, 8) dacQuantizeRowKernel(DacParams p) {
+  pdlEnter();
   const int row = (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= p.m) {
@@ -1112,6 +1115,7 @@ __global__ void __launch_bounds__(128, 8) dacQuantizeRowKernel(DacParams p) {
 // convolution over 256 channels) with 16-byte aligned rows: one warp per (row, in-split), float4
 // loads, two passes over the row - the second one finds it in L1 / L2.
 __global__ void __launch_bounds__(256) dacQuantizeLongRowKernel(DacParams p) {
+  pdlEnter();
   const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= (long long)p.m * p.I) {
@@ -1177,6 +1181,7 @@ __global__ void __launch_bounds__(256) dacQuantizeLongRowKernel(DacParams p) {
 __global__ void __launch_bounds__(256)
     splitWeightsKernel(const float *w, long long wk, long long wn, int N, int K, __nv_bfloat16 *hi,
                        __nv_bfloat16 *lo, long long row0, int kpad) {
+  pdlEnter();
   __shared__ float t[32][33];
   const int bx = blockIdx.x * 32, by = blockIdx.y * 32; // bx along k, by along n
   const bool k_fast = wk == 1;                          // which index is contiguous in memory
@@ -1388,8 +1393,8 @@ void TcEngine::loadOperand(int i, int o, const float *w, long long wk, long long
   }
   const long long row0 = (long long)i * nrows_pad_ + chunk0 * TC_N;
   dim3 grid((K + 31) / 32, (N + 31) / 32), block(32, 8);
-  splitWeightsKernel<<<grid, block, 0, s>>>(w, wk, wn, N, K, (__nv_bfloat16 *)op_hi_,
-                                            (__nv_bfloat16 *)op_lo_, row0, kpad_);
+  AB200_CUDA(launchChained(splitWeightsKernel, grid, block, 0, s, w, wk, wn, N, K, (__nv_bfloat16 *)op_hi_,
+                           (__nv_bfloat16 *)op_lo_, row0, kpad_));
   AB200_LAUNCH_CHECK();
 }
 
@@ -1527,13 +1532,15 @@ void TcEngine::launchDac(const Run &r, int row0, int rows, cudaStream_t s) {
     vec = (in_off_[i] & 3) == 0 && (in_sizes_[i] & 3) == 0;
   }
   if (vec && kpad_ <= 512) {
-    dacQuantizeRowKernel<<<(unsigned)(((long long)rows * 32 + 127) / 128), 128, 0, s>>>(d);
+    AB200_CUDA(launchChained(dacQuantizeRowKernel, dim3((unsigned)(((long long)rows * 32 + 127) / 128)),
+                             dim3(128), 0, s, d));
   } else if (vec) {
     const long long warps = (long long)rows * I;
-    dacQuantizeLongRowKernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(d);
+    AB200_CUDA(launchChained(dacQuantizeLongRowKernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256),
+                             0, s, d));
   } else {
     const long long warps = (long long)rows * I;
-    dacQuantizeKernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(d);
+    AB200_CUDA(launchChained(dacQuantizeKernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, s, d));
   }
   AB200_LAUNCH_CHECK();
 }
@@ -1642,8 +1649,19 @@ void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
   }
   p.prof = prof_dev;
   int grid_x = 0;
-  int n_sm = 0;
-  AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device_));
+  if (n_sm_ == 0) {
+    AB200_CUDA(cudaDeviceGetAttribute(&n_sm_, cudaDevAttrMultiProcessorCount, device_));
+  }
+  const int n_sm = n_sm_;
+  // the dynamic shared memory limit of a kernel variant is raised once per device
+  auto raiseSmem = [&](auto kernel, int variant, int bytes) {
+    if (!(smem_raised_ & (1u << variant))) {
+      AB200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+      smem_raised_ |= 1u << variant;
+    }
+  };
+  // chained with the kernels around it (see launchChained); not when the kernel signals peers
+  const bool chained = pdlEnabled() && p.flag_table == nullptr;
   const bool pair = usePairs(r.m);
   const bool bm = r.io.bm != AB200_BM_NONE;
   if (pair) {
@@ -1651,19 +1669,21 @@ void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
     const int n_pairs = n_items < n_sm / 2 ? n_items : n_sm / 2;
     auto kernel = codes ? mvmTcKernel<false, true, true>
                         : (bm ? mvmTcKernel<true, true> : mvmTcKernel<false, true>);
-    AB200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC2_SMEM_BYTES));
+    raiseSmem(kernel, codes ? 0 : (bm ? 1 : 2), TC2_SMEM_BYTES);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * n_pairs);
     cfg.blockDim = dim3(TC_THREADS);
     cfg.dynamicSmemBytes = TC2_SMEM_BYTES;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = chained ? 2 : 1;
     AB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_bhi, tm_blo, p));
     grid_x = 2 * n_pairs;
   } else {
@@ -1671,8 +1691,18 @@ void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
     dim3 grid(n_items < n_sm ? n_items : n_sm); // one persistent CTA per SM
     auto kernel = codes ? mvmTcKernel<false, false, true>
                         : (bm ? mvmTcKernel<true, false> : mvmTcKernel<false, false>);
-    AB200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
-    kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, s>>>(tm_a, tm_bhi, tm_blo, p);
+    raiseSmem(kernel, codes ? 3 : (bm ? 4 : 5), TC_SMEM_BYTES);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = TC_SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = chained ? 1 : 0;
+    AB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_bhi, tm_blo, p));
     grid_x = (int)grid.x;
   }
   AB200_LAUNCH_CHECK();

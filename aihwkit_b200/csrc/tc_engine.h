@@ -101,6 +101,8 @@ private:
   void launchDac(const Run &r, int row0, int rows, cudaStream_t s);
   void launchMma(const Run &r, int row0, int rows, cudaStream_t s);
 
+  int n_sm_ = 0;
+  unsigned smem_raised_ = 0; // kernel variants whose shared-memory limit is set
   int device_;
   std::vector<int> in_sizes_, out_sizes_, in_off_, out_off_;
   int kpad_ = 0;      // padded K of every in-split (multiple of 64)

@@ -6,6 +6,7 @@
 #include <atomic>
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <random>
@@ -24,6 +25,14 @@ int mvmPath() { return g_mvm_path.load(); }
 static float checkRes(float res) {
   float r = res < 0.0f ? 0.0f : res;
   return r > 1.0f ? 1.0f / r : r;
+}
+
+bool pdlEnabled() {
+  static const bool on = [] {
+    const char *e = getenv("AB200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only) {
@@ -188,6 +197,15 @@ void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_
   }
   const float up_bias = par.up_down > 0.0f ? 0.0f : par.up_down;
   const float down_bias = par.up_down > 0.0f ? -par.up_down : 0.0f;
+
+  if (par.drift.nu > 0.0f) {
+    // the exponents of the drift are the first draws (SimpleRPUDevice::populate ->
+    // WeightDrifter::populate, rpu_simple_device.cpp:172-181, weight_drifter.cpp:57-65)
+    float *nu = &ds.host[7 * size];
+    for (size_t k = 0; k < size; k++) {
+      nu[k] = par.drift.nu + par.drift.nu_dtod * par.drift.nu * rng.gauss();
+    }
+  }
 
   for (int j = 0; j < x_size; ++j) {
     for (int i = 0; i < d_size; ++i) {
@@ -463,6 +481,10 @@ Tile::~Tile() {
     cudaFree(sval_);
     cudaFree(flags_);
     cudaFree(bm_stats_);
+    cudaFree(drift_prev_);
+    cudaFree(drift_w0_);
+    cudaFree(drift_t_);
+    cudaFree(drift_nu_);
     cudaFree(f_onv_);
     cudaFree(b_onv_);
     cudaFree(xw_);
@@ -827,6 +849,15 @@ void Tile::setHidden(const float *in) {
     return;
   }
   const float *p = in;
+  if (drift_prev_ && device_ >= 0) {
+    // new drift exponents: the drift state starts again with the next drift call
+    AB200_CUDA(cudaDeviceSynchronize());
+    cudaFree(drift_prev_);
+    cudaFree(drift_w0_);
+    cudaFree(drift_t_);
+    cudaFree(drift_nu_);
+    drift_prev_ = drift_w0_ = drift_t_ = drift_nu_ = nullptr;
+  }
   for (int k = 0; k < n_dev_; k++) {
     std::memcpy(dev_[k].host.data(), p, dev_[k].host.size() * sizeof(float));
     dev_[k].par3_valid = false;
@@ -928,12 +959,12 @@ void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, boo
   p.call = fwd_calls_++;
   p.noise_id = 0;
   fillMvmScratch(p);
-  AB200_CUDA(cudaMemsetAsync(bm_stats_, 0, 2 * sizeof(int), s));
   if (tcEligible(p)) {
+    AB200_CUDA(cudaMemsetAsync(bm_stats_, 0, 2 * sizeof(int), s));
     runTc(p, s);
     launchBmRerun(p, s);
   } else {
-    launchMvm(p, s);
+    launchMvm(p, s); // its first kernel zeroes the re-run counters
   }
 }
 
@@ -963,7 +994,6 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
   p.call = fwd_calls_++;
   p.noise_id = noise_id;
   fillMvmScratch(p);
-  AB200_CUDA(cudaMemsetAsync(bm_stats_, 0, 2 * sizeof(int), s));
   // The bound-management re-run rewrites whole output rows, so a tile that adds to the sum of
   // the earlier in-splits computes into its own block first and is added afterwards.
   const bool bm = !f_io_.is_perfect && f_io_.bm != AB200_BM_NONE;
@@ -982,10 +1012,11 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
     p.accumulate = 0;
   }
   if (!p.accumulate && tcEligible(p)) {
+    AB200_CUDA(cudaMemsetAsync(bm_stats_, 0, 2 * sizeof(int), s));
     runTc(p, s);
     launchBmRerun(p, s);
   } else {
-    launchMvm(p, s);
+    launchMvm(p, s); // its first kernel zeroes the re-run counters
   }
   if (via_block) {
     launchAddBlock(acc_block_, d_size_, y, y_ss, m, d_size_, s);

@@ -264,6 +264,7 @@ public:
 
   // weight operations between updates (RPUPulsed::decayWeights / diffuseWeights / clipWeights /
   // resetCols / setWeightsUniformRandom, src/rpucuda/rpu_pulsed.cpp:189-284)
+  void driftWeights(float time_since_last_call, cudaStream_t s);
   void decayWeights(float alpha, bool bias_no_decay, cudaStream_t s);
   void diffuseWeights(cudaStream_t s);
   void clipWeights(int type, float fixed_value, float sigma, cudaStream_t s);
@@ -339,6 +340,10 @@ private:
   // out_noise_std > 0: std-dev of the output noise of every output line, forward (d_size) and
   // backward (x_size), drawn once per tile (rpu_forward_backward_pass.cpp:306-313)
   float *f_onv_ = nullptr, *b_onv_ = nullptr;
+  // power-law drift: per element the weight seen by the previous call, the weight and the time of
+  // its last write, and (pulsed devices) its exponent; time in units of t0
+  float *drift_prev_ = nullptr, *drift_w0_ = nullptr, *drift_t_ = nullptr, *drift_nu_ = nullptr;
+  float drift_now_ = 0.0f;
   uint32_t *xw_ = nullptr, *dw_ = nullptr;
   // transposed x words [x_size][m_pad] and their bitmaps, for the streaming update of large batches
   uint32_t *xwt_ = nullptr, *xnzt_ = nullptr;

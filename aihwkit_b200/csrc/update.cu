@@ -116,6 +116,7 @@ pulseTrain(float pp, int BL, int seg, PhiloxKey key, uint32_t line, uint32_t sam
 }
 
 __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
+  pdlEnter();
   __shared__ float sh[8];
   __shared__ float s_A, s_B;
   __shared__ int s_BL;
@@ -374,6 +375,7 @@ __device__ __noinline__ void refillReservoir(PhiloxKey key, uint32_t gid, uint32
 template <int KIND, bool IMPLICIT, bool NOISY, int EJ, int UTJ>
 __global__ void __launch_bounds__(UT_I *UTJ / EJ, (UT_I * UTJ / EJ) >= 1024 ? 1 : 4)
     pulsedUpdateKernel(UpdateProblem p) {
+  pdlEnter();
   constexpr int UE_J = EJ;
   constexpr int UNT = UT_I * UTJ / EJ; // threads per CTA
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -606,8 +608,8 @@ static void launchUpdateVariant(const UpdateProblem &p, cudaStream_t stream) {
     configured[dev] = true;
   }
   dim3 grid((p.d_size + UT_I - 1) / UT_I, (p.x_size + UTJ - 1) / UTJ);
-  pulsedUpdateKernel<KIND, IMPLICIT, NOISY, EJ, UTJ>
-      <<<grid, NT, sizeof(UpdateSmem<NT, UTJ>), stream>>>(p);
+  AB200_CUDA(launchChained(pulsedUpdateKernel<KIND, IMPLICIT, NOISY, EJ, UTJ>, grid, dim3(NT),
+                           sizeof(UpdateSmem<NT, UTJ>), stream, p));
 }
 
 template <int KIND, bool IMPLICIT, bool NOISY>
@@ -656,6 +658,7 @@ constexpr int USP_POOL = 256; // Gaussians per warp pool (eight per lane and ref
 __global__ void __launch_bounds__(256)
     pulseTransposeKernel(const uint32_t *words, int n_lines, int m, int m_pad, uint32_t *wordsT,
                          uint32_t *nzT) {
+  pdlEnter();
   __shared__ uint32_t tile[32][33];
   const int l0 = blockIdx.x * 32, s0 = blockIdx.y * 32;
   for (int r = threadIdx.y; r < 32; r += 8) {
@@ -684,6 +687,7 @@ struct StreamUpdate {
 
 template <int KIND, bool NOISY>
 __global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p, StreamUpdate st) {
+  pdlEnter();
   __shared__ float pool[8][USP_POOL];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_dblk = (p.d_size + 31) >> 5;
@@ -827,9 +831,9 @@ static void launchStreamKind(const UpdateProblem &p, const StreamUpdate &st, cud
   const long long tasks = (long long)((p.d_size + 31) / 32) * p.x_size;
   const unsigned blocks = (unsigned)((tasks + 7) / 8);
   if (p.dw_min_std > 0.0f) {
-    pulsedUpdateStreamKernel<KIND, true><<<blocks, 256, 0, stream>>>(p, st);
+    AB200_CUDA(launchChained(pulsedUpdateStreamKernel<KIND, true>, dim3(blocks), dim3(256), 0, stream, p, st));
   } else {
-    pulsedUpdateStreamKernel<KIND, false><<<blocks, 256, 0, stream>>>(p, st);
+    AB200_CUDA(launchChained(pulsedUpdateStreamKernel<KIND, false>, dim3(blocks), dim3(256), 0, stream, p, st));
   }
 }
 
@@ -858,7 +862,8 @@ void launchPulseTranspose(const UpdateProblem &p0, uint32_t *xwT, uint32_t *xnzT
                           cudaStream_t stream) {
   const UpdateProblem p = inRows(p0);
   dim3 grid((p.x_size + 31) / 32, m_pad / 32), block(32, 8);
-  pulseTransposeKernel<<<grid, block, 0, stream>>>(p.xw, p.x_size, p.m, m_pad, xwT, xnzT);
+  AB200_CUDA(launchChained(pulseTransposeKernel, grid, block, 0, stream, p.xw, p.x_size, p.m, m_pad, xwT,
+                           xnzT));
   AB200_LAUNCH_CHECK();
 }
 
@@ -899,7 +904,7 @@ void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream) {
   if (p.m <= 0) {
     return;
   }
-  pulsePrepareKernel<<<p.m, 256, 0, stream>>>(p);
+  AB200_CUDA(launchChained(pulsePrepareKernel, dim3(p.m), dim3(256), 0, stream, p));
   AB200_LAUNCH_CHECK();
 }
 
@@ -987,6 +992,7 @@ void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t
 // src/rpucuda/rpu.cpp:700-745), used by ideal devices / PulseType::None.
 // `overwrite`: the target receives -lr * sum alone (delta-weight mode: beta = 0, rpu.cpp:1509-1511)
 __global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_signed, int overwrite) {
+  pdlEnter();
   __shared__ float xs[16][16 + 1];
   __shared__ float ds[16][64 + 1];
   const int ti = threadIdx.x & 63, tj = threadIdx.x >> 6; // 64 d-lines x 4 groups of 4 x-lines
@@ -1033,7 +1039,7 @@ __global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_
 
 void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream, bool overwrite) {
   dim3 grid((p.d_size + 63) / 64, (p.x_size + 15) / 16);
-  fpUpdateKernel<<<grid, 256, 0, stream>>>(p, lr_signed, overwrite ? 1 : 0);
+  AB200_CUDA(launchChained(fpUpdateKernel, grid, dim3(256), 0, stream, p, lr_signed, overwrite ? 1 : 0));
   AB200_LAUNCH_CHECK();
 }
 
@@ -1044,6 +1050,7 @@ void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream
 __global__ void transferReadKernel(const float *w_fast, int col, int d_size, IOEff io,
                                    PhiloxKey key, uint32_t call, float *x_onehot, int x_size,
                                    float *r_out, float alpha) {
+  pdlEnter();
   int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < x_size) {
     x_onehot[t] = t == col ? 1.0f : 0.0f;
@@ -1075,6 +1082,7 @@ __global__ void transferReadKernel(const float *w_fast, int col, int d_size, IOE
 // omega minus the transferred part; the slow tile is then pulsed with d = -n.
 __global__ void transferBufferKernel(float *buffer_col, float *read_inout, int d_size, float lr_abs,
                                      float bg, float max_steps, float momentum, int forget_buffer) {
+  pdlEnter();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= d_size) {
     return;
@@ -1094,8 +1102,9 @@ __global__ void transferBufferKernel(float *buffer_col, float *read_inout, int d
 void launchTransferBuffer(float *buffer_col, float *read_inout, int d_size, float lr_abs,
                           float buffer_granularity, float max_steps, float momentum,
                           int forget_buffer, cudaStream_t stream) {
-  transferBufferKernel<<<(d_size + 255) / 256, 256, 0, stream>>>(
-      buffer_col, read_inout, d_size, lr_abs, buffer_granularity, max_steps, momentum, forget_buffer);
+  AB200_CUDA(launchChained(transferBufferKernel, dim3((d_size + 255) / 256), dim3(256), 0, stream,
+                           buffer_col, read_inout, d_size, lr_abs, buffer_granularity, max_steps,
+                           momentum, forget_buffer));
   AB200_LAUNCH_CHECK();
 }
 
@@ -1103,8 +1112,8 @@ void launchTransferRead(const float *w_fast, int col, int d_size, const IOEff &i
                         uint32_t call, float *x_onehot, int x_size, float *r_out, float alpha,
                         cudaStream_t stream) {
   int n = d_size > x_size ? d_size : x_size;
-  transferReadKernel<<<(n + 255) / 256, 256, 0, stream>>>(w_fast, col, d_size, io, key, call,
-                                                        x_onehot, x_size, r_out, alpha);
+  AB200_CUDA(launchChained(transferReadKernel, dim3((n + 255) / 256), dim3(256), 0, stream, w_fast, col,
+                           d_size, io, key, call, x_onehot, x_size, r_out, alpha));
   AB200_LAUNCH_CHECK();
 }
 
@@ -1134,6 +1143,7 @@ void launchTransposeDX(const float *src, float *dst, int rows, int cols, cudaStr
 
 // PulsedRPUDevice::onSetWeights: clip to the per-element bounds (rpu_pulsed_device.cpp:545-571).
 __global__ void clipKernel(float *w, const float4 *par4, long long n) {
+  pdlEnter();
   long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (t < n) {
     float4 q = par4[t];
@@ -1142,7 +1152,7 @@ __global__ void clipKernel(float *w, const float4 *par4, long long n) {
 }
 
 void launchClipToBounds(float *w, const float4 *par4, long long n, cudaStream_t stream) {
-  clipKernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w, par4, n);
+  AB200_CUDA(launchChained(clipKernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, w, par4, n));
   AB200_LAUNCH_CHECK();
 }
 

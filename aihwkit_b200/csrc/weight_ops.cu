@@ -9,6 +9,7 @@
 #include "tile.h"
 
 #include <cmath>
+#include <vector>
 
 namespace ab200 {
 
@@ -16,6 +17,7 @@ enum : uint32_t {
   TAG_DIFFUSE = 0x70000000u,
   TAG_RESET = 0x71000000u,
   TAG_UNIFORM_INIT = 0x72000000u,
+  TAG_DRIFT = 0x73000000u,
 };
 
 namespace {
@@ -37,6 +39,63 @@ __global__ void __launch_bounds__(256)
   float v = __fadd_rn(__fmul_rn(__fsub_rn(w[t], r.z), s), r.z);
   v = fminf(v, q.z);
   v = fmaxf(v, q.w);
+  w[t] = v;
+}
+
+// WeightDrifter::apply (src/rpucuda/weight_drifter.cpp:111-157) for one element, followed by
+// WeightDrifter::saturate (:101-108) when the device has bounds. `nu_el` null: one exponent for
+// all elements (simple drift).
+struct DriftArgs {
+  float nu, nu_std, wg_ratio, g_offset, w_offset, nu_k, log_g0, reset_tol, w_read_std, a;
+};
+__global__ void __launch_bounds__(256)
+    driftKernel(float *w, float *prev, float *w0, float *t_set, const float *nu_el,
+                const float4 *par4, long long n, float now, DriftArgs g, PhiloxKey key,
+                uint32_t call) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= n) {
+    return;
+  }
+  float z[4] = {0.f, 0.f, 0.f, 0.f};
+  if (g.nu_std > 0.0f || g.w_read_std > 0.0f) {
+    float zz[4];
+    gauss4(key, (uint64_t)(t >> 1), call, TAG_DRIFT, zz);
+    z[0] = zz[(t & 1) * 2];
+    z[1] = zz[(t & 1) * 2 + 1];
+  }
+  float v = w[t];
+  if (fabsf(__fsub_rn(prev[t], v)) > g.reset_tol) {
+    // written since the last call: the drift starts again from here
+    t_set[t] = now;
+    w0[t] = v;
+  } else {
+    float nu = nu_el ? nu_el[t] : g.nu;
+    if (g.nu_std > 0.0f) {
+      nu = __fadd_rn(nu, __fmul_rn(__fmul_rn(g.nu_std, nu), z[0]));
+    }
+    if (g.nu_k != 0.0f) {
+      nu = __fadd_rn(__fsub_rn(nu, __fmul_rn(g.nu_k, logf(__fadd_rn(__fdiv_rn(__fsub_rn(v, g.w_offset),
+                                                                         g.wg_ratio),
+                                                               g.g_offset)))),
+                     __fmul_rn(g.nu_k, g.log_g0));
+    }
+    const float dt = fmaxf(__fsub_rn(now, t_set[t]), 1.0f);
+    const float sc = powf(dt, -nu);
+    v = __fmul_rn(w0[t], sc);
+    if (g.a != 0.0f) {
+      v = __fadd_rn(v, __fmul_rn(g.a, __fsub_rn(sc, 1.0f)));
+    }
+  }
+  if (g.w_read_std > 0.0f) {
+    v = __fadd_rn(v, __fmul_rn(g.w_read_std, z[1]));
+  }
+  float pv = v;
+  if (par4) {
+    const float4 q = par4[t];
+    v = fminf(fmaxf(q.w, v), q.z);
+    pv = v;
+  }
+  prev[t] = pv;
   w[t] = v;
 }
 
@@ -191,6 +250,63 @@ void Tile::ensurePar3() {
   }
   AB200_CUDA(cudaMemcpy(ds.par3, p3.data(), size * sizeof(float4), cudaMemcpyHostToDevice));
   ds.par3_valid = true;
+}
+
+void Tile::driftWeights(float time_since_last_call, cudaStream_t s) {
+  requireSingleDevice("drift_weights");
+  const long long n = (long long)x_size_ * d_size_;
+  const bool ideal = dev_[0].kind == AB200_DEVICE_IDEAL;
+  const ab200_drift_params &d = cfg_.device[0].drift;
+  if (!ideal && !(d.nu > 0.0f)) {
+    return; // a pulsed device without drift has no drifter (rpu_simple_device.cpp:118-122)
+  }
+  const float t0 = d.t0 > 0.0f ? d.t0 : 1.0f;
+  if (!drift_prev_) {
+    // WeightDrifter::initialize (weight_drifter.cpp:42-55): all clocks start now
+    AB200_CUDA(cudaMalloc(&drift_prev_, n * sizeof(float)));
+    AB200_CUDA(cudaMalloc(&drift_w0_, n * sizeof(float)));
+    AB200_CUDA(cudaMalloc(&drift_t_, n * sizeof(float)));
+    AB200_CUDA(cudaMemcpyAsync(drift_prev_, w_, n * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    AB200_CUDA(cudaMemcpyAsync(drift_w0_, w_, n * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    AB200_CUDA(cudaMemsetAsync(drift_t_, 0, n * sizeof(float), s));
+    drift_now_ = 0.0f;
+    if (!ideal) {
+      // the exponents of the elements, in the weights' layout [x][d]; the ideal device drifts with
+      // one exponent for all weights
+      const size_t size = (size_t)n;
+      const float *nu = &dev_[0].host[7 * size];
+      std::vector<float> nt(size);
+      for (int i = 0; i < d_size_; i++) {
+        for (int j = 0; j < x_size_; j++) {
+          nt[(size_t)j * d_size_ + i] = nu[(size_t)i * x_size_ + j];
+        }
+      }
+      AB200_CUDA(cudaMalloc(&drift_nu_, size * sizeof(float)));
+      AB200_CUDA(cudaMemcpyAsync(drift_nu_, nt.data(), size * sizeof(float), cudaMemcpyHostToDevice, s));
+      AB200_CUDA(cudaStreamSynchronize(s)); // the staging vector goes out of scope
+    }
+  }
+  drift_now_ += time_since_last_call / t0;
+  DriftArgs g;
+  g.nu = d.nu;
+  g.nu_std = d.nu_std;
+  g.wg_ratio = d.wg_ratio != 0.0f ? d.wg_ratio : 1.0f;
+  g.g_offset = d.g_offset;
+  g.w_offset = d.w_offset;
+  g.nu_k = d.nu_k;
+  g.log_g0 = d.log_g0;
+  g.reset_tol = d.reset_tol > 0.0f ? d.reset_tol : 1e-7f;
+  g.w_read_std = d.w_read_std;
+  g.a = g.g_offset * g.wg_ratio + g.w_offset;
+  if (fabsf(g.a) < g.reset_tol) {
+    g.a = 0.0f;
+  }
+  driftKernel<<<blocksFor(n), 256, 0, s>>>(w_, drift_prev_, drift_w0_, drift_t_,
+                                          drift_nu_,
+                                          ideal ? nullptr : dev_[0].par4, n, drift_now_, g, key_,
+                                          op_calls_++);
+  AB200_LAUNCH_CHECK();
+  w_version_++;
 }
 
 void Tile::decayWeights(float alpha, bool bias_no_decay, cudaStream_t s) {

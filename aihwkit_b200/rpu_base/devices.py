@@ -188,8 +188,8 @@ class AnalogTileUpdateParameter:
 
 
 class DriftParameter:
-    """DriftParameter (rpu_base_devices.cpp:521-533): power-law drift of the weights over time.
-    Only the inactive default (``nu = 0``) is implemented by the B200 analog tile."""
+    """DriftParameter (rpu_base_devices.cpp:521-533): power-law drift of the weights over time,
+    ``w(t) = w0 (t / t_0)^(-nu)`` for weights that were not written since (weight_drifter.cpp:111-157)."""
 
     def __init__(self) -> None:
         self.nu = 0.0
@@ -207,6 +207,21 @@ class DriftParameter:
     def _active(self) -> bool:
         return self.nu != 0.0 or self.nu_dtod != 0.0 or self.nu_std != 0.0 or self.nu_k != 0.0
 
+    def _to_c(self, simple: bool = False) -> "_cabi.DriftParams":
+        c = _cabi.DriftParams()
+        c.nu = float(self.nu)
+        c.nu_dtod = 0.0 if simple else float(self.nu_dtod)  # setSimpleDrift (weight_drifter.h:51-54)
+        c.nu_std = float(self.nu_std)
+        c.wg_ratio = float(self.wg_ratio)
+        c.g_offset = float(self.g_offset)
+        c.w_offset = float(self.w_offset)
+        c.nu_k = float(self.nu_k)
+        c.log_g0 = float(self.log_g0)
+        c.t0 = float(self.t_0)
+        c.reset_tol = float(self.reset_tol)
+        c.w_read_std = float(self.w_noise_std)
+        return c
+
 
 class FloatingPointTileParameter:
     """SimpleMetaParameter (rpu_base_devices.cpp:436-451): the floating-point tile's own
@@ -221,10 +236,8 @@ class FloatingPointTileParameter:
         """``createRPUArray`` of the floating-point tile (src/rpucuda/rpu.cpp)."""
         from .tiles import FloatingPointTile
 
-        if self.drift._active():
-            raise RuntimeError("power-law drift is not implemented by the B200 analog tile")
         return FloatingPointTile(x_size, d_size, lifetime=float(self.lifetime),
-                                 diffusion=float(self.diffusion))
+                                 diffusion=float(self.diffusion), drift=self.drift)
 
     def __str__(self) -> str:
         return f"FloatingPointTileParameter(diffusion={self.diffusion}, lifetime={self.lifetime})"
@@ -313,6 +326,7 @@ class PulsedResistiveDeviceParameter(AbstractResistiveDeviceParameter):
             "reset", "reset_dtod", "reset_std",
         ):
             setattr(c, name, float(getattr(self, name)))
+        c.drift = self.drift._to_c()
 
     def _to_c(self) -> _cabi.DeviceParams:
         c = _cabi.DeviceParams()
@@ -646,6 +660,8 @@ class AnalogTileParameter:
             cfg.device[0].diffusion = float(device_par.diffusion)
             cfg.device[0].reset_std = float(device_par.reset_std)
             cfg.device[0].construction_seed = int(device_par.construction_seed)
+            # SimpleMetaParameter: one exponent for all weights (src/rpucuda/rpu.h:165)
+            cfg.device[0].drift = device_par.drift._to_c(simple=True)
         else:
             cfg.device[0] = device_par._to_c()
         return cfg

@@ -620,8 +620,10 @@ class AnalogTile:
         return torch.zeros(0, self.get_d_size(), self.get_x_size(), dtype=torch.int64)
 
     def drift_weights(self, time_since_last_call: float) -> None:
-        """rpu_base_tiles.cpp:294-314 (power-law drift, src/rpucuda/rpu.cpp:1581-1600)."""
-        raise RuntimeError("drift_weights is not implemented by the B200 analog tile")
+        """rpu_base_tiles.cpp:294-314 (power-law drift, src/rpucuda/rpu.cpp:1581-1587,
+        rpu_pulsed.cpp:226-229)."""
+        check(self._lib.ab200_tile_drift_weights(self._h, float(time_since_last_call),
+                                                 self._op_stream()))
 
     def remap_weights(self, weight_remap_params, scales: torch.Tensor,
                       biases: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -680,7 +682,7 @@ class FloatingPointTile(AnalogTile):
     """``tiles.FloatingPointTile`` (RPUSimple): perfect IO and floating-point update."""
 
     def __init__(self, x_size: int, d_size: int, cuda_device: int = -1, lifetime: float = 0.0,
-                 diffusion: float = 0.0):
+                 diffusion: float = 0.0, drift=None):
         from . import devices
 
         par = devices.AnalogTileParameter()
@@ -689,6 +691,8 @@ class FloatingPointTile(AnalogTile):
         par.update.pulse_type = devices.PulseType.None_
         dev = devices.IdealResistiveDeviceParameter()
         dev.lifetime, dev.diffusion = lifetime, diffusion
+        if drift is not None:
+            dev.drift = drift
         cfg = par._config(x_size, d_size, dev)
         super().__init__(cfg, cuda_device)
         self._meta = par

@@ -125,6 +125,24 @@ typedef struct ab200_update_params {
   float d_res_implicit;
 } ab200_update_params;
 
+/* DriftParameter (src/rpucuda/weight_drifter.h:17-60; bound in rpu_base_devices.cpp:521-533 as nu,
+ * nu_dtod, nu_std, wg_ratio, g_offset, w_offset, nu_k, log_g0, t_0, reset_tol, w_noise_std):
+ * power-law drift w(t) = w0 * (t / t0)^(-nu) of weights that were not written since. A zeroed
+ * struct means "no drift" (t0, wg_ratio and reset_tol of 0 read as 1, 1 and 1e-7). */
+typedef struct ab200_drift_params {
+  float nu;
+  float nu_dtod;
+  float nu_std;
+  float wg_ratio;
+  float g_offset;
+  float w_offset;
+  float nu_k;
+  float log_g0;
+  float t0;
+  float reset_tol;
+  float w_read_std;
+} ab200_drift_params;
+
 /* One pulsed device (PulsedRPUDeviceMetaParameter, src/rpucuda/rpu_pulsed_device.h:60-110,
  * plus the LinearStep / SoftBoundsReference extras: rpu_linearstep_device.h:24-58,
  * rpu_softbounds_reference_device.h:17-42). */
@@ -190,6 +208,9 @@ typedef struct ab200_device_params {
   int32_t pw_n;
   float pw_up[AB200_PIECEWISE_MAX_NODES];
   float pw_down[AB200_PIECEWISE_MAX_NODES];
+  /* drift of the device (SimpleRPUDeviceMetaParameter::drift, rpu_simple_device.h); for
+   * AB200_DEVICE_IDEAL the tile's own simple drift (RPUSimple::driftWeights, rpu.cpp:1581-1587) */
+  ab200_drift_params drift;
 } ab200_device_params;
 
 /* TransferRPUDeviceMetaParameter (src/rpucuda/rpu_transfer_device.h:52-75). */
@@ -370,6 +391,15 @@ const char *ab200_tile_extra_name(int k);
 int ab200_tile_dump_extra(ab200_tile *tile, double *values);
 int ab200_tile_load_extra(ab200_tile *tile, const char *const *names, const double *values,
                           int count, int strict);
+
+/* Power-law drift of the weights since they were last written (RPUPulsed::driftWeights,
+ * src/rpucuda/rpu_pulsed.cpp:226-229; RPUSimple::driftWeights, rpu.cpp:1581-1587; WeightDrifter::
+ * apply, weight_drifter.cpp:111-157; rpu_base_tiles.cpp:294-314). Elements whose weight changed by
+ * more than reset_tol since the previous call restart their clock; the others are overwritten by
+ * w0 * dt^(-nu) (plus the conductance-offset term), dt in units of t0 and at least 1. Pulsed
+ * devices then clip to their bounds. The first call starts all clocks at zero. Not available for
+ * Transfer compounds. */
+int ab200_tile_drift_weights(ab200_tile *tile, float time_since_last_call, void *stream);
 
 /* ---- weight operations between updates -------------------------------------------------------
  * Replace RPUPulsed<T>::decayWeights(alpha, bias_no_decay) / diffuseWeights() / clipWeights(...) /

@@ -70,6 +70,20 @@ void toUp(const ab200_update_params &s, PulsedUpdateMetaParameter<float> &up) {
   up.d_res_implicit = s.d_res_implicit;
 }
 
+void toDrift(const ab200_drift_params &s, DriftParameter<float> &d) {
+  d.nu = s.nu;
+  d.nu_dtod = s.nu_dtod;
+  d.nu_std = s.nu_std;
+  d.wg_ratio = s.wg_ratio != 0.0f ? s.wg_ratio : 1.0f;
+  d.g_offset = s.g_offset;
+  d.w_offset = s.w_offset;
+  d.nu_k = s.nu_k;
+  d.logG0 = s.log_g0;
+  d.t0 = s.t0 > 0.0f ? s.t0 : 1.0f;
+  d.reset_tol = s.reset_tol > 0.0f ? s.reset_tol : 1e-7f;
+  d.w_read_std = s.w_read_std;
+}
+
 void toPulsedBase(const ab200_device_params &s, PulsedRPUDeviceMetaParameter<float> &p) {
   p.construction_seed = s.construction_seed;
   p.enforce_consistency = s.enforce_consistency != 0;
@@ -91,6 +105,7 @@ void toPulsedBase(const ab200_device_params &s, PulsedRPUDeviceMetaParameter<flo
   p.reset = s.reset;
   p.reset_dtod = s.reset_dtod;
   p.reset_std = s.reset_std;
+  toDrift(s.drift, p.drift);
 }
 
 std::unique_ptr<PulsedRPUDeviceMetaParameter<float>> makeSingle(const ab200_device_params &s) {
@@ -230,6 +245,7 @@ int ref_tile_create(const ab200_tile_config *cfg, void **out) {
     sp->lifetime = cfg->device[0].lifetime;
     sp->diffusion = cfg->device[0].diffusion;
     sp->reset_std = cfg->device[0].reset_std;
+    toDrift(cfg->device[0].drift, sp->drift);
     dp = std::move(sp);
   } else {
     ab200_device_params d = cfg->device[0];
@@ -392,6 +408,12 @@ int ref_tile_update_indexed(void *h, const float *x, const float *d, long long t
 int ref_tile_decay_weights(void *h, float alpha, int bias_no_decay) {
   REF_TRY
   static_cast<RefTile *>(h)->rpu->decayWeights(alpha, bias_no_decay != 0);
+  REF_CATCH
+}
+
+int ref_tile_drift_weights(void *h, float time_since_last_call) {
+  REF_TRY
+  static_cast<RefTile *>(h)->rpu->driftWeights(time_since_last_call);
   REF_CATCH
 }
 

@@ -52,17 +52,28 @@ def test_defaults_follow_reference_member_initialisers():
                       (D.DEVICE_SOFT_BOUNDS, D.SoftBoundsResistiveDeviceParameter),
                       (D.DEVICE_LINEAR_STEP, D.LinearStepResistiveDeviceParameter),
                       (D.DEVICE_EXP_STEP, D.ExpStepResistiveDeviceParameter),
-                      (D.DEVICE_POW_STEP, D.PowStepResistiveDeviceParameter)):
+                      (D.DEVICE_POW_STEP, D.PowStepResistiveDeviceParameter),
+                      (D.DEVICE_PIECEWISE_STEP, D.PiecewiseStepResistiveDeviceParameter)):
         dp = _cabi.DeviceParams()
         lib.ab200_default_device_params(C.byref(dp), kind)
         refd = cls()._to_c()
         for name, _ in _cabi.DeviceParams._fields_:
-            if kind in (D.DEVICE_CONSTANT_STEP, D.DEVICE_EXP_STEP, D.DEVICE_POW_STEP) and name.startswith("ls_"):
+            if kind in (D.DEVICE_CONSTANT_STEP, D.DEVICE_EXP_STEP, D.DEVICE_POW_STEP,
+                        D.DEVICE_PIECEWISE_STEP) and name.startswith("ls_"):
                 continue  # LinearStep-only fields are not read for other kinds
             if kind != D.DEVICE_EXP_STEP and name.startswith("es_"):
                 continue  # ExpStep-only fields
             if kind != D.DEVICE_POW_STEP and name.startswith("ps_"):
                 continue  # PowStep-only fields
+            if name.startswith("pw_"):
+                if kind == D.DEVICE_PIECEWISE_STEP:
+                    assert dp.pw_n == refd.pw_n == 1 and dp.pw_up[0] == refd.pw_up[0] == 1.0
+                    assert dp.pw_down[0] == refd.pw_down[0] == 1.0
+                continue
+            if name == "drift":
+                for f, _ in _cabi.DriftParams._fields_:
+                    assert getattr(dp.drift, f) == pytest.approx(getattr(refd.drift, f)), (kind, f)
+                continue
             assert getattr(dp, name) == pytest.approx(getattr(refd, name)), (kind, name)
 
 

@@ -154,3 +154,91 @@ def test_compound_device_is_rejected():
     t = _tile(p._config(8, 6, H.transfer_device(noise=False), seed=3))
     with pytest.raises(RuntimeError, match="compound"):
         t.decay_weights()
+
+
+def _drift(dp, **kw):
+    dp.drift.nu, dp.drift.nu_dtod = 0.1, 0.3
+    for k, v in kw.items():
+        setattr(dp.drift, k, v)
+    return dp
+
+
+@pytest.mark.skipif(not ref.available(), reason="compiled reference not built")
+@pytest.mark.parametrize("extra", [{}, {"nu_k": 0.05, "g_offset": 0.2, "wg_ratio": 0.6, "w_offset": -0.1,
+                                        "log_g0": -0.3, "t_0": 2.0}])
+def test_power_law_drift_against_reference(extra):
+    """WeightDrifter::apply + saturate (src/rpucuda/weight_drifter.cpp:101-157) on a pulsed device:
+    per-element exponents drawn as the reference draws them, clocks restarted for the elements
+    written between two calls, conductance-offset term and weight-dependent exponent."""
+    rng = np.random.default_rng(8)
+    x_size, d_size = 70, 33
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = _drift(H.device("cs", False), **extra)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t, rt = _tile(cfg), ref.RefTile(cfg)
+    names = t.get_hidden_parameter_names()
+    hp = t.get_hidden_parameters().numpy()
+    assert np.array_equal(hp, rt.get_hidden_parameters())
+    nu = hp[names.index("drift_nu")]
+    assert abs(nu.mean() - 0.1) < 0.002 and abs(nu.std() / 0.03 - 1) < 0.1
+    W = rng.uniform(0.05, 0.5, (d_size, x_size)).astype(np.float32)  # G > 0 for the log term
+    t.set_weights(torch.from_numpy(W))
+    rt.set_weights(W)
+    for step, dt in enumerate((5.0, 20.0, 300.0)):
+        if step == 1:
+            # write a block of weights between the calls: their clocks restart
+            W2 = t.get_weights().numpy().copy()
+            W2[:10, :20] = rng.uniform(0.05, 0.5, (10, 20)).astype(np.float32)
+            t.set_weights(torch.from_numpy(W2))
+            rt.set_weights(W2)
+        t.drift_weights(dt)
+        rt.drift_weights(dt)
+        a, b = t.get_weights().numpy(), rt.get_weights()
+        assert np.abs(a - b).max() <= 2e-6 * np.abs(b).max(), (step, np.abs(a - b).max())
+    assert np.abs(a - W2).max() > 0.01  # the weights did drift
+
+
+@pytest.mark.skipif(not ref.available(), reason="compiled reference not built")
+def test_power_law_drift_floating_point_tile_and_noise():
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(9)
+    x_size, d_size = 64, 48
+    ideal = _drift(D.IdealResistiveDeviceParameter())
+    ideal.construction_seed = 13
+    p = H.training_params(noise=False, pulse_det=True)
+    cfg = p._config(x_size, d_size, ideal, seed=3)
+    t, rt = _tile(cfg), ref.RefTile(cfg)
+    W = rng.normal(0, 0.3, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    rt.set_weights(W)
+    for dt in (3.0, 40.0):
+        t.drift_weights(dt)
+        rt.drift_weights(dt)
+        a, b = t.get_weights().numpy(), rt.get_weights()
+        assert np.abs(a - b).max() <= 2e-6 * np.abs(b).max()
+    # the floating-point tile proper: one exponent for all weights (RPUSimple::driftWeights)
+    fp = D.FloatingPointTileParameter()
+    fp.drift.nu, fp.drift.nu_dtod = 0.2, 0.5
+    ft = fp.create_array(x_size, d_size)
+    from aihwkit_b200.rpu_base import tiles as T
+
+    ft = T.CudaFloatingPointTile(ft)
+    ft.set_weights(torch.from_numpy(W))
+    ft.drift_weights(10.0)
+    assert np.allclose(ft.get_weights().cpu().numpy(), W * np.float32(10.0) ** np.float32(-0.2), rtol=3e-6)
+    # read noise and exponent noise: moments against the reference
+    noisy = _drift(H.device("cs", False), nu_std=0.2, w_noise_std=0.01)
+    cfg = p._config(x_size, d_size, noisy, seed=3)
+    t, rt = _tile(cfg), ref.RefTile(cfg)
+    W = rng.uniform(-0.4, 0.4, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    rt.set_weights(W)
+    t.drift_weights(50.0)
+    rt.drift_weights(50.0)
+    da, db = t.get_weights().numpy() - W, rt.get_weights() - W
+    assert abs(da.mean() - db.mean()) < 5 * db.std() / np.sqrt(db.size)
+    assert abs(da.std() / db.std() - 1) < 0.05
+    ra = (t.get_weights().numpy() / W)[np.abs(W) > 0.1]
+    rb = (rt.get_weights() / W)[np.abs(W) > 0.1]
+    assert abs(ra.std() / rb.std() - 1) < 0.1
