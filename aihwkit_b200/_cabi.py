@@ -61,6 +61,26 @@ class UpdateParams(C.Structure):
     ]
 
 
+class WeightModifierParams(C.Structure):
+    """``ab200_weight_modifier_params`` (WeightModifierParameter, src/rpucuda/weight_modifier.h:28-50)."""
+
+    _fields_ = [
+        ("type", C.c_int32),
+        ("sto_round", C.c_int32),
+        ("enable_during_test", C.c_int32),
+        ("copy_last_column", C.c_int32),
+        ("rel_to_actual_wmax", C.c_int32),
+        ("n_coeffs", C.c_int32),
+        ("std_dev", C.c_float),
+        ("res", C.c_float),
+        ("dorefa_clip", C.c_float),
+        ("pdrop", C.c_float),
+        ("assumed_wmax", C.c_float),
+        ("g_max", C.c_float),
+        ("coeffs", C.c_float * 8),
+    ]
+
+
 class DriftParams(C.Structure):
     """``ab200_drift_params`` (DriftParameter, src/rpucuda/weight_drifter.h:17-60)."""
 
@@ -234,6 +254,7 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_load_extra": (_I, [_VP, C.POINTER(C.c_char_p), C.POINTER(C.c_double), _I, _I]),
         "ab200_tile_decay_weights": (_I, [_VP, C.c_float, _I, _VP]),
         "ab200_tile_drift_weights": (_I, [_VP, C.c_float, _VP]),
+        "ab200_tile_modify_weights": (_I, [_VP, C.POINTER(WeightModifierParams), _VP]),
         "ab200_tile_diffuse_weights": (_I, [_VP, _VP]),
         "ab200_tile_clip_weights": (_I, [_VP, _I, C.c_float, C.c_float, _VP]),
         "ab200_tile_reset_columns": (_I, [_VP, _I, _I, C.c_float, _VP]),

@@ -371,6 +371,16 @@ int ab200_tile_load_extra(ab200_tile *tile, const char *const *names, const doub
   AB200_CATCH
 }
 
+int ab200_tile_modify_weights(ab200_tile *tile, const ab200_weight_modifier_params *params,
+                              void *stream) {
+  AB200_TRY
+  if (!params) {
+    AB200_FATAL("modify_weights: null parameters");
+  }
+  T(tile)->modifyWeights(*params, (cudaStream_t)stream);
+  AB200_CATCH
+}
+
 int ab200_tile_drift_weights(ab200_tile *tile, float time_since_last_call, void *stream) {
   AB200_TRY
   T(tile)->driftWeights(time_since_last_call, (cudaStream_t)stream);

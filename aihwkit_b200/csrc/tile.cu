@@ -481,6 +481,8 @@ Tile::~Tile() {
     cudaFree(sval_);
     cudaFree(flags_);
     cudaFree(bm_stats_);
+    cudaFree(fb_w_);
+    cudaFree(fb_amax_);
     cudaFree(drift_prev_);
     cudaFree(drift_w0_);
     cudaFree(drift_t_);
@@ -930,7 +932,8 @@ void Tile::fillMvmScratch(MvmProblem &p) {
 
 void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, bool d_trans,
                    bool is_test, cudaStream_t s) {
-  (void)is_test; // "Noise will be always present" (rpu_forward_backward_pass.cpp:808-810)
+  // the IO noise is present in test mode too (rpu_forward_backward_pass.cpp:808-810); is_test only
+  // selects between the weights and their modified copy
   requireDevice("forward");
   if (m <= 0) {
     return;
@@ -948,7 +951,7 @@ void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, boo
   p.out_size = d_size_;
   p.out_store = d_size_;
   p.accumulate = 0;
-  p.w = w_;
+  p.w = fbWeights(is_test);
   p.wk = d_size_;
   p.wn = 1;
   p.m = m;
@@ -983,7 +986,7 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
   p.out_size = d_size_;
   p.out_store = d_size_;
   p.accumulate = accumulate ? 1 : 0;
-  p.w = w_;
+  p.w = fbWeights(true);
   p.wk = d_size_;
   p.wn = 1;
   p.m = m;
@@ -1055,7 +1058,7 @@ void Tile::backwardCore(const float *d, long long d_ss, long long d_fs, float *x
   p.out_size = x_size_;
   p.out_store = x_store; // a bias column is computed but not returned (rpu.cpp:670-690)
   p.accumulate = accumulate ? 1 : 0;
-  p.w = w_;
+  p.w = fbWeights(false);
   p.wk = 1; // W(k = d, n = x) = w[x * d_size + d]
   p.wn = d_size_;
   p.m = m;
@@ -1098,9 +1101,11 @@ void Tile::runTc(const MvmProblem &p, cudaStream_t s) {
     eng->configure({p.in_size}, {p.out_size});
     ver = 0;
   }
-  if (ver != w_version_) {
+  // the operands follow the matrix this pass reads: the weights or their modified copy
+  const uint64_t want = p.w == w_ ? w_version_ : (0x8000000000000000ull | fb_version_);
+  if (ver != want) {
     eng->loadOperand(0, 0, p.w, p.wk, p.wn, s);
-    ver = w_version_;
+    ver = want;
   }
   TcEngine::Run r;
   r.in = p.in;
@@ -1278,18 +1283,18 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
     }
     u.w = w_;
     launchFPUpdate(u, lr_, s);
-    if (up_.pulse_type == AB200_PULSE_NONE_WITH_DEVICE && dev_[0].kind != AB200_DEVICE_IDEAL) {
-      launchClipToBounds(w_, dev_[0].par4, (long long)x_size_ * d_size_, s);
-    }
     return;
   }
   if (delta_w_) {
     AB200_FATAL("set_delta_weights is implemented for the floating-point update only");
   }
   if (up_.pulse_type == AB200_PULSE_NONE_WITH_DEVICE) {
+    if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+      AB200_FATAL("Transfer with PulseType::NoneWithDevice is not implemented");
+    }
     u.w = w_;
-    launchFPUpdate(u, lr_, s);
-    launchClipToBounds(w_, dev_[0].par4, (long long)x_size_ * d_size_, s);
+    u.par4 = dev_[0].par4;
+    launchFPUpdate(u, lr_, s, /*overwrite=*/false, /*clip_each=*/true);
     return;
   }
 

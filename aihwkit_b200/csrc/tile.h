@@ -178,7 +178,7 @@ void launchPulsedUpdateStream(const UpdateProblem &p, const uint32_t *xwT, const
 void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream);
 void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream);
 void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream,
-                    bool overwrite = false);
+                    bool overwrite = false, bool clip_each = false);
 void launchTransferRead(const float *w_fast, int col, int d_size, const IOEff &io, PhiloxKey key,
                         uint32_t call, float *x_onehot, int x_size, float *r_out, float alpha,
                         cudaStream_t stream);
@@ -265,6 +265,7 @@ public:
   // weight operations between updates (RPUPulsed::decayWeights / diffuseWeights / clipWeights /
   // resetCols / setWeightsUniformRandom, src/rpucuda/rpu_pulsed.cpp:189-284)
   void driftWeights(float time_since_last_call, cudaStream_t s);
+  void modifyWeights(const ab200_weight_modifier_params &par, cudaStream_t s);
   void decayWeights(float alpha, bool bias_no_decay, cudaStream_t s);
   void diffuseWeights(cudaStream_t s);
   void clipWeights(int type, float fixed_value, float sigma, cudaStream_t s);
@@ -342,6 +343,14 @@ private:
   float *f_onv_ = nullptr, *b_onv_ = nullptr;
   // power-law drift: per element the weight seen by the previous call, the weight and the time of
   // its last write, and (pulsed devices) its exponent; time in units of t0
+  // modified copy of the weights that forward / backward read (modify_weights), its largest
+  // magnitude (device scalar), and whether a test-mode forward reads it too
+  float *fb_w_ = nullptr, *fb_amax_ = nullptr;
+  bool fb_active_ = false, fb_in_test_ = false;
+  uint64_t fb_version_ = 0;
+  const float *fbWeights(bool is_test) const {
+    return (fb_active_ && (!is_test || fb_in_test_)) ? fb_w_ : w_;
+  }
   float *drift_prev_ = nullptr, *drift_w0_ = nullptr, *drift_t_ = nullptr, *drift_nu_ = nullptr;
   float drift_now_ = 0.0f;
   uint32_t *xw_ = nullptr, *dw_ = nullptr;

@@ -991,6 +991,10 @@ void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t
 // Floating-point update W[x][d] -= lr * sum_s x[s][x] d[s][d] (RPUSimple::updateMatrix,
 // src/rpucuda/rpu.cpp:700-745), used by ideal devices / PulseType::None.
 // `overwrite`: the target receives -lr * sum alone (delta-weight mode: beta = 0, rpu.cpp:1509-1511)
+// CLIP_EACH: PulseType::NoneWithDevice - the rank-one update of every sample is followed by the
+// clip to the element's bounds (rpu_weight_updater.cpp:216-223), so the samples are applied to the
+// weight one after the other instead of being summed first.
+template <bool CLIP_EACH>
 __global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_signed, int overwrite) {
   pdlEnter();
   __shared__ float xs[16][16 + 1];
@@ -999,6 +1003,21 @@ __global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_
   const int i = blockIdx.x * 64 + ti;
   const int jb = blockIdx.y * 16;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float wv[4] = {0.f, 0.f, 0.f, 0.f}, hi[4], lo[4];
+  if (CLIP_EACH) {
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      const int j = jb + tj * 4 + t;
+      hi[t] = lo[t] = 0.0f;
+      if (i < p.d_size && j < p.x_size) {
+        const long long idx = (long long)j * p.d_size + i;
+        const float4 q = p.par4[idx];
+        wv[t] = p.w[idx];
+        hi[t] = q.z;
+        lo[t] = q.w;
+      }
+    }
+  }
   for (int s0 = 0; s0 < p.m; s0 += 16) {
     {
       int ss = threadIdx.x >> 4, jj = threadIdx.x & 15;
@@ -1020,7 +1039,12 @@ __global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_
       float dv = ds[ss][ti];
 #pragma unroll
       for (int t = 0; t < 4; t++) {
-        acc[t] = fmaf(xs[ss][tj * 4 + t], dv, acc[t]);
+        if (CLIP_EACH) {
+          wv[t] = __fsub_rn(wv[t], __fmul_rn(__fmul_rn(lr_signed, dv), xs[ss][tj * 4 + t]));
+          wv[t] = fmaxf(fminf(wv[t], hi[t]), lo[t]);
+        } else {
+          acc[t] = fmaf(xs[ss][tj * 4 + t], dv, acc[t]);
+        }
       }
     }
     __syncthreads();
@@ -1031,15 +1055,25 @@ __global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_
       int j = jb + tj * 4 + t;
       if (j < p.x_size) {
         long long idx = (long long)j * p.d_size + i;
-        p.w[idx] = overwrite ? -lr_signed * acc[t] : p.w[idx] - lr_signed * acc[t];
+        if (CLIP_EACH) {
+          p.w[idx] = wv[t];
+        } else {
+          p.w[idx] = overwrite ? -lr_signed * acc[t] : p.w[idx] - lr_signed * acc[t];
+        }
       }
     }
   }
 }
 
-void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream, bool overwrite) {
+void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream, bool overwrite,
+                    bool clip_each) {
   dim3 grid((p.d_size + 63) / 64, (p.x_size + 15) / 16);
-  AB200_CUDA(launchChained(fpUpdateKernel, grid, dim3(256), 0, stream, p, lr_signed, overwrite ? 1 : 0));
+  if (clip_each) {
+    AB200_CUDA(launchChained(fpUpdateKernel<true>, grid, dim3(256), 0, stream, p, lr_signed, 0));
+  } else {
+    AB200_CUDA(launchChained(fpUpdateKernel<false>, grid, dim3(256), 0, stream, p, lr_signed,
+                             overwrite ? 1 : 0));
+  }
   AB200_LAUNCH_CHECK();
 }
 

@@ -8,6 +8,7 @@
 // 16-byte decay / diffusion / reset record per element): HBM-bound, 24-40 B per weight.
 #include "tile.h"
 
+#include <algorithm>
 #include <cmath>
 #include <vector>
 
@@ -18,6 +19,7 @@ enum : uint32_t {
   TAG_RESET = 0x71000000u,
   TAG_UNIFORM_INIT = 0x72000000u,
   TAG_DRIFT = 0x73000000u,
+  TAG_MODIFY = 0x74000000u,
 };
 
 namespace {
@@ -40,6 +42,115 @@ __global__ void __launch_bounds__(256)
   v = fminf(v, q.z);
   v = fmaxf(v, q.w);
   w[t] = v;
+}
+
+// Largest |w| over the first n elements (float bits compare like unsigned integers for w >= 0).
+__global__ void __launch_bounds__(256) absMaxKernel(const float *w, long long n, unsigned int *out) {
+  float a = 0.0f;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < n;
+       t += (long long)gridDim.x * blockDim.x) {
+    a = fmaxf(a, fabsf(w[t]));
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+  }
+  if ((threadIdx.x & 31) == 0 && a > 0.0f) {
+    atomicMax(out, __float_as_uint(a));
+  }
+}
+
+// WeightModifier::apply (src/rpucuda/weight_modifier.cpp:31-215) for one element: fb = f(w).
+// Elements t >= n_mod (the last input column when copy_last_column is set) are copied.
+// `amax_dev`: largest |w| of the modified elements, or null for the assumed value in g.amax.
+struct ModifyArgs {
+  int type, sto_round, n_coeffs;
+  float std_dev, res, dorefa_clip, pdrop, amax, g_max;
+  float coeffs[AB200_WMOD_MAX_COEFFS];
+};
+__device__ __forceinline__ float modRound(float v, float res, bool sto, float u) {
+  // getDiscretizedValueRound (src/rpucuda/utility_functions.h:195-203)
+  if (!(res > 0.0f)) {
+    return v;
+  }
+  // roundf here: halves away from zero, unlike the DAC / ADC steps
+  return sto ? __fmul_rn(roundf(__fadd_rn(__fdiv_rn(v, res), __fadd_rn(u, -0.5f))), res)
+             : __fmul_rn(roundf(__fdiv_rn(v, res)), res);
+}
+__global__ void __launch_bounds__(256)
+    modifyKernel(const float *w, float *fb, long long n, long long n_mod, const unsigned int *amax_dev,
+                 ModifyArgs g, PhiloxKey key, uint32_t call) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= n) {
+    return;
+  }
+  float v = w[t];
+  if (t >= n_mod) {
+    fb[t] = v;
+    return;
+  }
+  float amax = g.amax;
+  if (amax_dev) {
+    amax = __uint_as_float(*amax_dev);
+    amax = amax > 0.0f ? amax : 1.0f;
+  }
+  uint32_t r[4];
+  philox4x32<7>((uint32_t)t, (uint32_t)(t >> 32), call, TAG_MODIFY, key, r);
+  float z, z_unused;
+  boxMuller16(r[1], z, z_unused);
+  const float u = u01(r[0]);
+  const bool sto = g.sto_round != 0;
+  switch (g.type) {
+  case AB200_WMOD_DISCRETIZE:
+    if (g.res > 0.0f) {
+      v = __fmul_rn(amax, modRound(__fdiv_rn(v, amax), g.res, sto, u));
+    }
+    break;
+  case AB200_WMOD_MULT_NORMAL:
+    if (g.std_dev > 0.0f) {
+      v = __fadd_rn(v, __fmul_rn(__fmul_rn(v, __fmul_rn(g.std_dev, amax)), z));
+    }
+    break;
+  case AB200_WMOD_ADD_NORMAL:
+    if (g.std_dev > 0.0f) {
+      v = __fadd_rn(v, __fmul_rn(__fmul_rn(g.std_dev, amax), z));
+    }
+    break;
+  case AB200_WMOD_DISCRETIZE_ADD_NORMAL: {
+    const float std = __fmul_rn(g.std_dev, amax);
+    if (g.res > 0.0f || std > 0.0f) {
+      v = __fmul_rn(amax, modRound(__fdiv_rn(v, amax), g.res, sto, u));
+      v = __fadd_rn(v, __fmul_rn(std, z));
+    }
+    break;
+  }
+  case AB200_WMOD_DOREFA:
+    if (g.res > 0.0f) {
+      const float scale = fabsf(__fdiv_rn(g.dorefa_clip, tanhf(amax)));
+      v = modRound(__fmul_rn(tanhf(v), scale), g.res, sto, u);
+    }
+    break;
+  case AB200_WMOD_POLY:
+  case AB200_WMOD_PROG_NOISE:
+    if (g.std_dev > 0.0f && g.n_coeffs > 0) {
+      const float aw = __fdiv_rn(fabsf(v), amax);
+      float paw = 1.0f, sig = g.coeffs[0];
+      for (int j = 1; j < g.n_coeffs; j++) {
+        paw = __fmul_rn(paw, aw);
+        sig = __fadd_rn(sig, __fmul_rn(g.coeffs[j], paw));
+      }
+      const float std = g.type == AB200_WMOD_POLY ? g.std_dev : __fdiv_rn(g.std_dev, g.g_max);
+      sig = __fmul_rn(sig, std);
+      const float nv = __fadd_rn(v, __fmul_rn(__fmul_rn(amax, sig), z));
+      v = g.type == AB200_WMOD_POLY ? nv : (v < 0.0f ? -fabsf(nv) : fabsf(nv));
+    }
+    break;
+  default: // Copy, DropConnect
+    break;
+  }
+  if (g.pdrop > 0.0f && u01(r[2]) < g.pdrop) {
+    v = 0.0f;
+  }
+  fb[t] = v;
 }
 
 // WeightDrifter::apply (src/rpucuda/weight_drifter.cpp:111-157) for one element, followed by
@@ -250,6 +361,52 @@ void Tile::ensurePar3() {
   }
   AB200_CUDA(cudaMemcpy(ds.par3, p3.data(), size * sizeof(float4), cudaMemcpyHostToDevice));
   ds.par3_valid = true;
+}
+
+void Tile::modifyWeights(const ab200_weight_modifier_params &par, cudaStream_t s) {
+  requireDevice("modify_weights");
+  if (par.type < AB200_WMOD_COPY || par.type > AB200_WMOD_PROG_NOISE || par.type == AB200_WMOD_PCM_NOISE) {
+    AB200_FATAL("Requested WeightModifierType not implemented");
+  }
+  if (par.n_coeffs < 0 || par.n_coeffs > AB200_WMOD_MAX_COEFFS) {
+    AB200_FATAL("modify_weights: at most " << AB200_WMOD_MAX_COEFFS << " polynomial coefficients");
+  }
+  const long long n = (long long)x_size_ * d_size_;
+  if (!fb_w_) {
+    AB200_CUDA(cudaMalloc(&fb_w_, n * sizeof(float)));
+    AB200_CUDA(cudaMalloc(&fb_amax_, sizeof(float)));
+  }
+  // the last input column is the tail of the [x_size][d_size] layout
+  const long long n_mod = par.copy_last_column ? (long long)(x_size_ - 1) * d_size_ : n;
+  const bool measured = par.rel_to_actual_wmax && par.type != AB200_WMOD_COPY;
+  if (measured) {
+    AB200_CUDA(cudaMemsetAsync(fb_amax_, 0, sizeof(float), s));
+    if (n_mod > 0) {
+      const long long blocks = std::min<long long>((n_mod + 255) / 256, 1184);
+      absMaxKernel<<<(unsigned)blocks, 256, 0, s>>>(w_, n_mod, reinterpret_cast<unsigned int *>(fb_amax_));
+      AB200_LAUNCH_CHECK();
+    }
+  }
+  ModifyArgs g;
+  g.type = par.type;
+  g.sto_round = par.sto_round;
+  g.n_coeffs = par.n_coeffs;
+  g.std_dev = par.std_dev;
+  g.res = par.res;
+  g.dorefa_clip = par.dorefa_clip;
+  g.pdrop = par.pdrop;
+  g.amax = par.assumed_wmax;
+  g.g_max = par.g_max;
+  for (int k = 0; k < AB200_WMOD_MAX_COEFFS; k++) {
+    g.coeffs[k] = k < par.n_coeffs ? par.coeffs[k] : 0.0f;
+  }
+  modifyKernel<<<blocksFor(n), 256, 0, s>>>(w_, fb_w_, n, n_mod,
+                                           measured ? reinterpret_cast<unsigned int *>(fb_amax_) : nullptr,
+                                           g, key_, op_calls_++);
+  AB200_LAUNCH_CHECK();
+  fb_active_ = true;
+  fb_in_test_ = par.enable_during_test != 0;
+  fb_version_++;
 }
 
 void Tile::driftWeights(float time_since_last_call, cudaStream_t s) {

@@ -100,7 +100,7 @@ class WeightModifierParameter:
         self.rel_to_actual_wmax = True
         self.assumed_wmax = 1.0
         self.type = WeightModifierType.Copy
-        self.coeffs = [0.26348, 0.0768, -0.001877]
+        self.coeffs = [0.26348 / 25.0, 0.0768, -0.001877 * 25.0]  # weight_modifier.h:49
         self.pcm_zero_thres = 0.0
         self.pcm_t_inference = 0.0
         self.pcm_prob_at_reset = 0.0
@@ -108,6 +108,23 @@ class WeightModifierParameter:
         self.pcm_prob_at_random = 0.0
         self.pcm_t0 = 20.0
         self.g_max = 25.0
+
+    def _to_c(self) -> "_cabi.WeightModifierParams":
+        coeffs = [float(v) for v in self.coeffs]
+        if len(coeffs) > 8:
+            raise RuntimeError("modify_weights: at most 8 polynomial coefficients are implemented")
+        c = _cabi.WeightModifierParams()
+        c.type = int(self.type)
+        c.sto_round = int(bool(self.sto_round))
+        c.enable_during_test = int(bool(self.enable_during_test))
+        c.copy_last_column = int(bool(self.copy_last_column))
+        c.rel_to_actual_wmax = int(bool(self.rel_to_actual_wmax))
+        c.n_coeffs = len(coeffs)
+        for name in ("std_dev", "res", "dorefa_clip", "pdrop", "assumed_wmax", "g_max"):
+            setattr(c, name, float(getattr(self, name)))
+        for k, v in enumerate(coeffs):
+            c.coeffs[k] = v
+        return c
 
 
 def _stream_ptr(t: torch.Tensor) -> int:
@@ -672,10 +689,11 @@ class AnalogTile:
 
     def modify_weights(self, weight_modifier_params) -> None:
         """rpu_base_tiles.cpp:358-371 (WeightModifier, src/rpucuda/weight_modifier.cpp)."""
-        if int(weight_modifier_params.type) == int(WeightModifierType.Copy) and \
-                float(weight_modifier_params.pdrop) == 0.0:
-            return
-        raise RuntimeError("modify_weights: this weight modifier is not implemented by the B200 analog tile")
+        if int(weight_modifier_params.type) != int(WeightModifierType.Copy) and \
+                bool(weight_modifier_params.per_batch_sample):
+            raise RuntimeError("Per batch sample is not implemented in RPUCuda")  # weight_modifier.cpp:36-38
+        c = weight_modifier_params._to_c()
+        check(self._lib.ab200_tile_modify_weights(self._h, C.byref(c), self._op_stream()))
 
 
 class FloatingPointTile(AnalogTile):

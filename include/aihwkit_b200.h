@@ -392,6 +392,45 @@ int ab200_tile_dump_extra(ab200_tile *tile, double *values);
 int ab200_tile_load_extra(ab200_tile *tile, const char *const *names, const double *values,
                           int count, int strict);
 
+/* WeightModifierParameter (src/rpucuda/weight_modifier.h:15-50; bound in rpu_base_tiles.cpp:31-51). */
+enum ab200_weight_modifier_type {
+  AB200_WMOD_COPY = 0,
+  AB200_WMOD_DISCRETIZE = 1,
+  AB200_WMOD_MULT_NORMAL = 2,
+  AB200_WMOD_ADD_NORMAL = 3,
+  AB200_WMOD_DISCRETIZE_ADD_NORMAL = 4,
+  AB200_WMOD_DOREFA = 5,
+  AB200_WMOD_POLY = 6,
+  AB200_WMOD_PCM_NOISE = 7, /* not implemented (nor by the reference's CPU tile) */
+  AB200_WMOD_DROP_CONNECT = 8,
+  AB200_WMOD_PROG_NOISE = 9
+};
+#define AB200_WMOD_MAX_COEFFS 8
+typedef struct ab200_weight_modifier_params {
+  int32_t type; /* enum ab200_weight_modifier_type */
+  int32_t sto_round;
+  int32_t enable_during_test;
+  int32_t copy_last_column;
+  int32_t rel_to_actual_wmax;
+  int32_t n_coeffs;
+  float std_dev;
+  float res;
+  float dorefa_clip;
+  float pdrop;
+  float assumed_wmax;
+  float g_max;
+  float coeffs[AB200_WMOD_MAX_COEFFS];
+} ab200_weight_modifier_params;
+
+/* RPUSimple::modifyFBWeights (src/rpucuda/rpu.cpp:1749-1758; WeightModifier::apply,
+ * weight_modifier.cpp:31-215; rpu_base_tiles.cpp:358-371): forward and backward read a modified
+ * copy of the weights from now on - discretised, with Gaussian noise relative to the largest
+ * weight, DoReFa-quantised, with dropped connections ... - while updates keep going to the weights
+ * themselves; the copy is refreshed by the next call. A forward with is_test != 0 reads the
+ * weights themselves unless enable_during_test is set (RPUSimple::getFBWeights, rpu.cpp:1483-1487). */
+int ab200_tile_modify_weights(ab200_tile *tile, const ab200_weight_modifier_params *params,
+                              void *stream);
+
 /* Power-law drift of the weights since they were last written (RPUPulsed::driftWeights,
  * src/rpucuda/rpu_pulsed.cpp:226-229; RPUSimple::driftWeights, rpu.cpp:1581-1587; WeightDrifter::
  * apply, weight_drifter.cpp:111-157; rpu_base_tiles.cpp:294-314). Elements whose weight changed by

@@ -77,6 +77,7 @@ def load() -> C.CDLL:
         "ref_tile_decay_weights": (i, [vp, C.c_float, i]),
         "ref_tile_diffuse_weights": (i, [vp]),
         "ref_tile_drift_weights": (i, [vp, C.c_float]),
+        "ref_tile_modify_weights": (i, [vp, vp]),
         "ref_tile_clip_weights": (i, [vp, i, C.c_float, C.c_float]),
         "ref_tile_reset_columns": (i, [vp, i, i, C.c_float]),
         "ref_tile_set_matrix_indices": (i, [vp, fp, C.c_longlong]),
@@ -235,6 +236,11 @@ class RefTile:
     # weight operations between updates (src/rpucuda/rpu_pulsed.cpp:189-284)
     def decay_weights(self, alpha: float = 1.0, bias_no_decay: bool = False) -> None:
         self._ck(self._lib.ref_tile_decay_weights(self._h, alpha, int(bias_no_decay)))
+
+    def modify_weights(self, weight_modifier_params) -> None:
+        """``weight_modifier_params``: a ``WeightModifierParameter`` of aihwkit_b200.rpu_base.tiles."""
+        c = weight_modifier_params._to_c()
+        self._ck(self._lib.ref_tile_modify_weights(self._h, C.byref(c)))
 
     def drift_weights(self, time_since_last_call: float) -> None:
         self._ck(self._lib.ref_tile_drift_weights(self._h, time_since_last_call))

@@ -21,6 +21,7 @@
 #include "rpu_pulsed.h"
 #include "rpu_softbounds_reference_device.h"
 #include "rpu_transfer_device.h"
+#include "weight_modifier.h"
 
 #include <cstring>
 #include <memory>
@@ -408,6 +409,25 @@ int ref_tile_update_indexed(void *h, const float *x, const float *d, long long t
 int ref_tile_decay_weights(void *h, float alpha, int bias_no_decay) {
   REF_TRY
   static_cast<RefTile *>(h)->rpu->decayWeights(alpha, bias_no_decay != 0);
+  REF_CATCH
+}
+
+int ref_tile_modify_weights(void *h, const ab200_weight_modifier_params *s) {
+  REF_TRY
+  WeightModifierParameter<float> wm;
+  wm.type = (WeightModifierType)s->type;
+  wm.sto_round = s->sto_round != 0;
+  wm.enable_during_test = s->enable_during_test != 0;
+  wm.copy_last_column = s->copy_last_column != 0;
+  wm.rel_to_actual_wmax = s->rel_to_actual_wmax != 0;
+  wm.std_dev = s->std_dev;
+  wm.res = s->res;
+  wm.dorefa_clip = s->dorefa_clip;
+  wm.pdrop = s->pdrop;
+  wm.assumed_wmax = s->assumed_wmax;
+  wm.g_max = s->g_max;
+  wm.coeffs.assign(s->coeffs, s->coeffs + s->n_coeffs);
+  static_cast<RefTile *>(h)->rpu->modifyFBWeights(wm);
   REF_CATCH
 }
 

@@ -639,3 +639,41 @@ def test_stochastic_update_long_trains_and_separate_sign_trains(pulse_type):
     dws, dwo = np.stack(dws), np.stack(dwo)
     H.assert_moments_agree(dws, dwo)
     assert np.abs(dws).max() > 0
+
+
+def test_none_with_device_clips_after_every_sample():
+    """PulseType::NoneWithDevice (rpu_weight_updater.cpp:216-223): the floating-point rank-one
+    update of every sample is followed by the clip to the element's bounds, so a weight that
+    reaches its bound in the middle of a batch continues from there."""
+    from aihwkit_b200.rpu_base import devices as D
+    from oracle import ref
+
+    rng = np.random.default_rng(77)
+    x_size, d_size, m = 70, 40, 24
+    p = H.training_params(noise=False, pulse_det=True)
+    p.update.pulse_type = D.PulseType.NoneWithDevice
+    dp = H.device("cs", False, w_max=0.3, w_min=-0.3)
+    t, cfg = _tile(p, dp, x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.2, 0.2, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    names, hp = t.get_hidden_parameter_names(), t.get_hidden_parameters().numpy()
+    hi, lo = hp[names.index("max_bound")], hp[names.index("min_bound")]
+    X, Dm = _inputs(rng, m, x_size, d_size)
+    Dm *= 5.0
+    lr = 0.2
+    t.set_learning_rate(lr)
+    t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    W_new = t.get_weights().numpy()
+    want, summed = W.copy(), W.copy()
+    for s in range(m):
+        want = np.clip(want - np.float32(lr) * np.outer(Dm[s], X[s]).astype(np.float32), lo, hi)
+    summed = np.clip(W - np.float32(lr) * (Dm.T @ X), lo, hi)
+    assert np.abs(W_new - want).max() <= 2e-6
+    assert np.abs(summed - want).max() > 0.01  # the order of clip and sum matters for this input
+    if ref.available():
+        rt = ref.RefTile(cfg)
+        rt.set_hidden_parameters(hp)
+        rt.set_weights(W)
+        rt.set_learning_rate(lr)
+        rt.update(X, Dm)
+        assert np.abs(W_new - rt.get_weights()).max() <= 2e-6
