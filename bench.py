@@ -440,6 +440,34 @@ def run_ours(args):
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
+    # ---- what the host link of this box gives for the same bytes: this rank's input columns in
+    # and its rows out as plain page-locked copies on two streams at once (no kernels), so that
+    # the end-to-end figure can be read as a fraction of a measured copy rate
+    out_host_probe = y_rows_host if scatter else (y_host if y_host is not None else None)
+    copy_ms = None
+    if out_host_probe is not None:
+        xd_probe = torch.empty_like(x_local_host, device=dev)
+        yd_probe = torch.empty_like(out_host_probe, device=dev)
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        torch.cuda.synchronize()
+        c0e, c1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for it in range(4):
+            if it == 1:
+                c0e.record()
+                s_in.wait_event(c0e)
+                s_out.wait_event(c0e)
+            with torch.cuda.stream(s_in):
+                xd_probe.copy_(x_local_host, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                out_host_probe.copy_(yd_probe, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(s_in)
+        torch.cuda.current_stream().wait_stream(s_out)
+        c1e.record()
+        torch.cuda.synchronize()
+        copy_ms = c0e.elapsed_time(c1e) / 3
+        del xd_probe, yd_probe
+    barrier()
+
     if world > 1:
         t = torch.tensor([ms, e2e_ms, sus_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -478,7 +506,10 @@ def run_ours(args):
             "e2e": {"value": m / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": int(m * W["in_size"] * 4),  # summed over the ranks
                     "d2h_bytes_per_step": int(m * W["out_size"] * 4),
-                    "ms_per_step": e2e_ms, "pcie_gbs_per_rank_both_directions": pcie},
+                    "ms_per_step": e2e_ms, "pcie_gbs_per_rank_both_directions": pcie,
+                    # the same bytes of rank 0 as bare copies, both directions at once
+                    "copies_only_ms": copy_ms,
+                    "frac_of_copies_only": (copy_ms / e2e_ms) if copy_ms else None},
             "gpu_launches": int(launches),
             "sustained": {"value": m * n_sus / (sus_ms * 1e-3), "unit": UNIT, "steps": n_sus,
                           "seconds": sus_ms * 1e-3, "ms_per_step": sus_ms / n_sus,
