@@ -41,6 +41,7 @@ class IOParams(C.Structure):
         ("out_asymmetry", C.c_float),
         ("nm_assumed_wmax", C.c_float),
         ("out_noise_std", C.c_float),
+        ("nm_decay", C.c_float),
     ]
 
 

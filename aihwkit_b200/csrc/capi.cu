@@ -95,6 +95,7 @@ void ab200_default_io_params(ab200_io_params *io) {
   io->nm_assumed_wmax = 0.6f;
   io->out_noise = 0.06f;
   io->out_scale = 1.0f;
+  io->nm_decay = 1e-3f;
   io->max_bm_res = 0.25f;
 }
 

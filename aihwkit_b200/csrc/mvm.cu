@@ -20,7 +20,11 @@ namespace ab200 {
 // Kernel 1: per-sample noise management. One warp per sample (sample-contiguous layouts) or one
 // thread per sample (feature-major layouts), so that loads stay coalesced either way.
 // ---------------------------------------------------------------------------------------------
-template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKernel(MvmProblem p) {
+// `mode` 0: everything in one pass; 1: only the abs-max of every sample, written to p.sval;
+// 2: the noise-management value of every sample is given in p.sval (the running-average types,
+// whose value depends on the samples before it: nmAverageKernel sits between modes 1 and 2).
+template <bool WARP_PER_SAMPLE>
+__global__ void __launch_bounds__(256) nmScaleKernel(MvmProblem p, int mode) {
   pdlEnter();
   const IOEff &io = p.io;
   if (blockIdx.x == 0 && threadIdx.x == 0 && !p.backward && p.bm_stats) {
@@ -36,7 +40,7 @@ template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKe
   }
   const float *row = p.in + (long long)s * p.in_ss;
   NmStats st;
-  if (nmNeedsStats(io)) {
+  if (mode != 2 && (nmNeedsStats(io) || mode == 1)) {
     if (WARP_PER_SAMPLE) {
       for (int k = lane; k < p.in_size; k += 32) {
         st.add(k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f);
@@ -48,7 +52,13 @@ template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKe
       }
     }
   }
-  float sval = nmValue(io, st);
+  if (mode == 1) {
+    if (!WARP_PER_SAMPLE || lane == 0) {
+      p.sval[s] = st.amax;
+    }
+    return;
+  }
+  float sval = mode == 2 ? p.sval[s] : nmValue(io, st);
   float scale = inputScale(io, sval, /*reduction=*/1.0f, !p.backward);
   const ElemRng g{p.key, p.call, (p.backward ? TAG_BWD_IN : TAG_FWD_IN) + p.noise_id};
   float vn = 0.0f;
@@ -80,6 +90,23 @@ template <bool WARP_PER_SAMPLE> __global__ void __launch_bounds__(256) nmScaleKe
     p.vnorm[s] = vn;
     p.flags[s] = 0;
   }
+}
+
+// AverageAbsMax / AverageAbsMaxSingleValue (rpu_forward_backward_pass.cpp:139-150): the value of
+// sample s is the running value after sample s, s <- s (1 - decay) + decay * amax_s, started by
+// the first sample the tile ever sees. A recurrence over the samples in their order: one thread.
+__global__ void nmAverageKernel(float *sval, int m, float decay, float *state) {
+  pdlEnter();
+  if (blockIdx.x != 0 || threadIdx.x != 0) {
+    return;
+  }
+  float a = *state;
+  for (int s = 0; s < m; s++) {
+    const float amax = sval[s];
+    a = a < 0.0f ? amax : __fadd_rn(__fmul_rn(a, __fsub_rn(1.0f, decay)), __fmul_rn(decay, amax));
+    sval[s] = a;
+  }
+  *state = a;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -389,13 +416,29 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
 void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
   // noise management
   bool sample_contig = p.in_fs == 1;
-  if (sample_contig) {
-    int blocks = (int)(((long long)p.m * 32 + 255) / 256);
-    AB200_CUDA(launchChained(nmScaleKernel<true>, dim3(blocks), dim3(256), 0, stream, p));
+  auto nmPass = [&](int mode) {
+    if (sample_contig) {
+      int blocks = (int)(((long long)p.m * 32 + 255) / 256);
+      AB200_CUDA(launchChained(nmScaleKernel<true>, dim3(blocks), dim3(256), 0, stream, p, mode));
+    } else {
+      AB200_CUDA(launchChained(nmScaleKernel<false>, dim3((p.m + 255) / 256), dim3(256), 0, stream, p, mode));
+    }
+    AB200_LAUNCH_CHECK();
+  };
+  const bool running = !p.io.is_perfect && (p.io.nm == AB200_NM_AVERAGE_ABS_MAX ||
+                                            p.io.nm == AB200_NM_AVERAGE_ABS_MAX_SINGLE_VALUE);
+  if (running) {
+    if (!p.nm_state) {
+      AB200_FATAL("running-average noise management needs a tile (its state lives there)");
+    }
+    nmPass(1);
+    AB200_CUDA(launchChained(nmAverageKernel, dim3(1), dim3(32), 0, stream, p.sval, p.m, p.io.nm_decay,
+                             p.nm_state));
+    AB200_LAUNCH_CHECK();
+    nmPass(2);
   } else {
-    AB200_CUDA(launchChained(nmScaleKernel<false>, dim3((p.m + 255) / 256), dim3(256), 0, stream, p));
+    nmPass(0);
   }
-  AB200_LAUNCH_CHECK();
 
   const bool a_k_fast = p.in_fs == 1;
   const bool b_n_fast = p.wn == 1;

@@ -55,6 +55,7 @@ IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only) {
   e.out_scale = io.out_scale;
   e.w_noise = io.w_noise;
   e.nm_assumed_wmax = io.nm_assumed_wmax;
+  e.nm_decay = io.nm_decay;
   e.inp_noise = io.inp_noise;
   e.inp_asym = 1.0f - io.inp_asymmetry;
   e.out_asym = 1.0f - io.out_asymmetry;
@@ -65,11 +66,12 @@ IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only) {
       AB200_FATAL((backward ? "Backward noise managment expects input bound==1"
                             : "Forward noise managment expects bound==1"));
     }
-    if (io.noise_management != AB200_NM_NONE && io.noise_management != AB200_NM_ABS_MAX &&
-        io.noise_management != AB200_NM_CONSTANT && io.noise_management != AB200_NM_MAX &&
-        io.noise_management != AB200_NM_ABS_MAX_NP_SUM) {
-      // the running-average types keep state between calls (:139-150)
+    if (io.noise_management < AB200_NM_NONE || io.noise_management > AB200_NM_AVERAGE_ABS_MAX_SINGLE_VALUE) {
       AB200_FATAL("Noise Management type not implemented!");
+    }
+    if (plain_only && (io.noise_management == AB200_NM_AVERAGE_ABS_MAX ||
+                       io.noise_management == AB200_NM_AVERAGE_ABS_MAX_SINGLE_VALUE)) {
+      AB200_FATAL("running-average noise management is not implemented for the read-out of a transfer");
     }
     if (plain_only && ((io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) ||
                        io.out_noise_std > 0.0f)) {
@@ -487,6 +489,7 @@ Tile::~Tile() {
     cudaFree(drift_w0_);
     cudaFree(drift_t_);
     cudaFree(drift_nu_);
+    cudaFree(nm_state_);
     cudaFree(f_onv_);
     cudaFree(b_onv_);
     cudaFree(xw_);
@@ -593,6 +596,11 @@ void Tile::toDevice(int cuda_device) {
   }
   AB200_CUDA(cudaMalloc(&bm_stats_, 2 * sizeof(int)));
   AB200_CUDA(cudaMemset(bm_stats_, 0, 2 * sizeof(int)));
+  {
+    const float not_started = -1.0f; // aux_nm_value_ (rpu_forward_backward_pass.h:241)
+    AB200_CUDA(cudaMalloc(&nm_state_, sizeof(float)));
+    AB200_CUDA(cudaMemcpy(nm_state_, &not_started, sizeof(float), cudaMemcpyHostToDevice));
+  }
   {
     HostRNG rng(key_.k0 ^ (key_.k1 * 0x9e3779b9u) ^ 0x6f6e7631u);
     auto draw = [&](const IOEff &io, int n, float **dst) {
@@ -927,6 +935,7 @@ void Tile::fillMvmScratch(MvmProblem &p) {
   p.sval = sval_;
   p.flags = flags_;
   p.bm_stats = bm_stats_;
+  p.nm_state = nm_state_;
   p.key = key_;
 }
 

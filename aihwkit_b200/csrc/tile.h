@@ -35,6 +35,7 @@ struct IOEff {
   float w_noise;
   float nm_thres;
   float nm_assumed_wmax;
+  float nm_decay; // running-average noise management
   // Gaussian added to the DAC output, factors applied to negative DAC outputs / negative values
   // in front of the ADC (1 - asymmetry), stochastic rounding of DAC / ADC
   float inp_noise;
@@ -94,6 +95,9 @@ struct MvmProblem {
   int *bm_stats; // [0] re-run samples, [1] max reduction (float bits)
   // std-dev of the output noise of every output line (out_size entries) when io.out_noise_std > 0
   const float *out_noise_vals = nullptr;
+  // running value of the AverageAbsMax noise management (one float, < 0: not started), shared by
+  // the forward and backward passes of a tile as in the reference
+  float *nm_state = nullptr;
 };
 
 // CUDA-core path: noise management, fused MVM, bound-management re-run
@@ -341,6 +345,7 @@ private:
   // out_noise_std > 0: std-dev of the output noise of every output line, forward (d_size) and
   // backward (x_size), drawn once per tile (rpu_forward_backward_pass.cpp:306-313)
   float *f_onv_ = nullptr, *b_onv_ = nullptr;
+  float *nm_state_ = nullptr;
   // power-law drift: per element the weight seen by the previous call, the weight and the time of
   // its last write, and (pulsed devices) its exponent; time in units of t0
   // modified copy of the weights that forward / backward read (modify_weights), its largest

@@ -134,7 +134,7 @@ class AnalogTileInputOutputParameter:
         if mv not in (int(AnalogMVType.Ideal), int(AnalogMVType.OnePass)):
             raise RuntimeError("MV type not implemented.")
         nm = int(self.noise_management)
-        if nm not in (0, 1, 2, 3, 4):  # the running-average types keep state between calls
+        if nm not in (0, 1, 2, 3, 4, 5, 6):
             raise RuntimeError("Noise Management type not implemented!")
         c = _cabi.IOParams()
         c.is_perfect = int(bool(self.is_perfect) or mv == int(AnalogMVType.Ideal))
@@ -148,7 +148,7 @@ class AnalogTileInputOutputParameter:
         for name in (
             "inp_bound", "inp_res", "inp_noise", "out_bound", "out_res", "out_noise", "out_scale",
             "w_noise", "nm_thres", "max_bm_res", "inp_asymmetry", "out_asymmetry", "nm_assumed_wmax",
-            "out_noise_std",
+            "out_noise_std", "nm_decay",
         ):
             setattr(c, name, float(getattr(self, name)))
         return c

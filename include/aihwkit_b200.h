@@ -108,6 +108,9 @@ typedef struct ab200_io_params {
    * |out_noise * (1 + out_noise_std * N(0,1))| for the life of the tile
    * (rpu_forward_backward_pass.cpp:306-313, :696) */
   float out_noise_std;
+  /* AverageAbsMax noise management: weight of a sample's abs-max in the running value
+   * s <- s (1 - nm_decay) + nm_decay * max|x| (rpu_forward_backward_pass.cpp:139-150) */
+  float nm_decay;
 } ab200_io_params;
 
 /* PulsedUpdateMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:248-279;

@@ -56,6 +56,7 @@ void toIO(const ab200_io_params &s, IOMetaParameter<float> &io) {
   io.out_asymmetry = s.out_asymmetry;
   io.nm_assumed_wmax = s.nm_assumed_wmax;
   io.out_noise_std = s.out_noise_std;
+  io.nm_decay = s.nm_decay;
 }
 
 void toUp(const ab200_update_params &s, PulsedUpdateMetaParameter<float> &up) {

@@ -677,3 +677,53 @@ def test_none_with_device_clips_after_every_sample():
         rt.set_learning_rate(lr)
         rt.update(X, Dm)
         assert np.abs(W_new - rt.get_weights()).max() <= 2e-6
+
+
+@pytest.mark.parametrize("nm", [5, 6])  # AverageAbsMax, AverageAbsMaxSingleValue (C ABI only)
+def test_running_average_noise_management(nm):
+    """AverageAbsMax noise management (rpu_forward_backward_pass.cpp:139-150): the input scale of a
+    sample is the running value s <- s (1 - nm_decay) + nm_decay max|x| after that sample; the
+    value carries over from call to call and is shared by forward and backward."""
+    from aihwkit_b200.rpu_base import devices as D
+    from oracle import ref
+
+    rng = np.random.default_rng(61)
+    x_size, d_size, m = 48, 40, 37
+    p = H.training_params(noise=False, pulse_det=True, bm=False)
+    for io in (p.forward_io, p.backward_io):
+        io.noise_management = nm
+        io.nm_decay = 0.1
+    t, cfg = _tile(p, H.device("cs", False), x_size, d_size)
+    t.set_weights(torch.from_numpy(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)))
+    W = t.get_weights().numpy()
+    fio = O.IO.from_c(cfg.forward_io)
+    state = -1.0
+    rt = None
+    if ref.available():
+        rt = ref.RefTile(cfg)
+        rt.set_weights(W)
+    for call in range(3):
+        X = (rng.uniform(-1, 1, (m, x_size)) * rng.uniform(0.2, 1.5)).astype(np.float32)
+        backward = call == 1
+        inp = rng.normal(0, 0.3, (m, d_size)).astype(np.float32) if backward else X
+        y = (t.backward if backward else t.forward)(torch.from_numpy(inp).cuda()).cpu().numpy()
+        # the running value after every sample, then the chain of the oracle with that scale
+        s_val = np.empty(m, np.float32)
+        for s in range(m):
+            amax = np.abs(inp[s]).max()
+            state = amax if state < 0 else np.float32(state * np.float32(0.9) + np.float32(0.1) * amax)
+            s_val[s] = state
+        io_c = O.IO.from_c(cfg.backward_io if backward else cfg.forward_io, backward=backward)
+        Wop = W.T if backward else W
+        v = np.clip(np.rint((inp / s_val[:, None]) / io_c.res_in) * io_c.res_in, -1, 1).astype(np.float32)
+        pre = (v @ Wop.T).astype(np.float32)
+        want = np.clip(np.rint(pre / io_c.res_out) * io_c.res_out, -io_c.out_bound, io_c.out_bound)
+        want = (want * s_val[:, None]).astype(np.float32)
+        lsb = (io_c.res_out * s_val)[:, None]
+        frac, worst = H.lsb_report(y, want, lsb)
+        assert frac <= 2e-3 and worst <= 1.001, (call, frac, worst)
+        if rt is not None:
+            yr = rt.backward(inp) if backward else rt.forward(inp)
+            frac, worst = H.lsb_report(y, yr, lsb)
+            assert frac <= 2e-3 and worst <= 1.001, (call, frac, worst)
+    assert fio.noise_management in (5, 6)

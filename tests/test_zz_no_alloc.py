@@ -102,3 +102,32 @@ def test_noalloc_rejects_oversized_batch():
                                        y.data_ptr(), too_many, 1, 0, _stream(x))
     assert rc != 0
     assert b"exceeds" in lib.ab200_last_error()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs a second GPU")
+def test_noalloc_forward_on_a_second_device():
+    """Every GPU has its own copy of the scratch array; its address is resolved per device on the
+    first call there."""
+    from aihwkit_b200 import _cabi
+    from oracle import analog_tile_oracle as O
+
+    lib = _cabi.lib()
+    x_size, d_size, m = 64, 48, 300
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=3.0)
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=7)
+    rng = np.random.default_rng(9)
+    w = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    io = O.IO.from_c(cfg.forward_io)
+    y_or, _, scale, _ = O.forward(w, x, io, return_pre_adc=True)
+    for dev in (1, 0, 1):
+        with torch.cuda.device(dev):
+            w_xd = torch.from_numpy(np.ascontiguousarray(w.T)).cuda()
+            xg = torch.from_numpy(x).cuda()
+            y = torch.empty(m, d_size, device="cuda")
+            rc = lib.ab200_mvm_forward_noalloc(C.byref(cfg.forward_io), w_xd.data_ptr(), x_size, d_size,
+                                               xg.data_ptr(), y.data_ptr(), m, 7, 0, _stream(xg))
+            assert rc == 0, lib.ab200_last_error()
+            torch.cuda.synchronize()
+            frac, worst = H.lsb_report(y.cpu().numpy(), y_or, (io.res_out / scale)[:, None])
+            assert frac <= 2e-3 and worst <= 1.001, (dev, frac, worst)
