@@ -42,6 +42,14 @@ class IOParams(C.Structure):
         ("nm_assumed_wmax", C.c_float),
         ("out_noise_std", C.c_float),
         ("nm_decay", C.c_float),
+        ("ir_drop", C.c_float),
+        ("ir_drop_g_ratio", C.c_float),
+        ("v_offset_std", C.c_float),
+        ("r_series", C.c_float),
+        ("r_series_max_total", C.c_float),
+        ("out_nonlinearity", C.c_float),
+        ("out_nonlinearity_std", C.c_float),
+        ("slope_calibration", C.c_float),
     ]
 
 
@@ -256,6 +264,8 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_decay_weights": (_I, [_VP, C.c_float, _I, _VP]),
         "ab200_tile_drift_weights": (_I, [_VP, C.c_float, _VP]),
         "ab200_tile_modify_weights": (_I, [_VP, C.POINTER(WeightModifierParams), _VP]),
+        "ab200_tile_get_io_vector": (_I, [_VP, _I, _I, _VP, _I]),
+        "ab200_tile_set_io_vector": (_I, [_VP, _I, _I, _VP, _I]),
         "ab200_tile_diffuse_weights": (_I, [_VP, _VP]),
         "ab200_tile_clip_weights": (_I, [_VP, _I, C.c_float, C.c_float, _VP]),
         "ab200_tile_reset_columns": (_I, [_VP, _I, _I, C.c_float, _VP]),

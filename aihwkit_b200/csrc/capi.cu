@@ -96,6 +96,8 @@ void ab200_default_io_params(ab200_io_params *io) {
   io->out_noise = 0.06f;
   io->out_scale = 1.0f;
   io->nm_decay = 1e-3f;
+  io->ir_drop_g_ratio = 5.7143e5f;
+  io->slope_calibration = 0.5f;
   io->max_bm_res = 0.25f;
 }
 
@@ -369,6 +371,19 @@ int ab200_tile_load_extra(ab200_tile *tile, const char *const *names, const doub
                           int count, int strict) {
   AB200_TRY
   T(tile)->loadExtra(names, values, count, strict != 0);
+  AB200_CATCH
+}
+
+int ab200_tile_get_io_vector(ab200_tile *tile, int backward, int which, float *values_host, int n) {
+  AB200_TRY
+  T(tile)->getIoVector(backward != 0, which, values_host, n);
+  AB200_CATCH
+}
+
+int ab200_tile_set_io_vector(ab200_tile *tile, int backward, int which, const float *values_host,
+                             int n) {
+  AB200_TRY
+  T(tile)->setIoVector(backward != 0, which, values_host, n);
   AB200_CATCH
 }
 

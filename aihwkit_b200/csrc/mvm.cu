@@ -120,7 +120,9 @@ __global__ void nmAverageKernel(float *sval, int m, float decay, float *state) {
 // the latency of the K loop (global load -> DAC -> shared memory -> barrier per step), not its
 // arithmetic, so they take 64 or 32 features per step with several loads in flight per thread.
 
-// PCM: also accumulate sum_k |w| v^2 per output, the variance factor of the PCMRead weight noise.
+// PCM ("line chain"): also accumulate per output sum_k |w| v^2 (variance factor of the PCMRead
+// weight noise), sum_k |w| |v| (line current) and sum_k w v posw(k) (position-weighted product) for
+// the IR drop, and run the long output chain (lineChain) instead of the merged noise draw.
 template <bool A_K_FAST, bool B_N_FAST, int T, bool PCM>
 __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   pdlEnter();
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   __syncthreads();
 
   float acc[T][T];
-  float acc2[PCM ? T : 1][PCM ? T : 1];
+  float acc2[PCM ? T : 1][PCM ? T : 1], acc_c[PCM ? T : 1][PCM ? T : 1], acc_i[PCM ? T : 1][PCM ? T : 1];
 #pragma unroll
   for (int i = 0; i < T; i++) {
 #pragma unroll
@@ -151,6 +153,8 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
       acc[i][j] = 0.0f;
       if (PCM) {
         acc2[PCM ? i : 0][PCM ? j : 0] = 0.0f;
+        acc_c[PCM ? i : 0][PCM ? j : 0] = 0.0f;
+        acc_i[PCM ? i : 0][PCM ? j : 0] = 0.0f;
       }
     }
   }
@@ -194,6 +198,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
 #pragma unroll
     for (int kk = 0; kk < BK; kk++) {
       float a[T], b[T];
+      const float posw = PCM ? irPosWeight(k0 + kk, K) : 0.0f;
 #pragma unroll
       for (int i = 0; i < T; i++) {
         a[i] = As[kk][ty * T + i];
@@ -208,8 +213,10 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
         for (int j = 0; j < T; j++) {
           acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
           if (PCM) {
-            acc2[PCM ? i : 0][PCM ? j : 0] =
-                fmaf(a[i] * a[i], fabsf(b[j]), acc2[PCM ? i : 0][PCM ? j : 0]);
+            const float ab = fabsf(b[j]);
+            acc2[PCM ? i : 0][PCM ? j : 0] = fmaf(a[i] * a[i], ab, acc2[PCM ? i : 0][PCM ? j : 0]);
+            acc_c[PCM ? i : 0][PCM ? j : 0] = fmaf(fabsf(a[i]), ab, acc_c[PCM ? i : 0][PCM ? j : 0]);
+            acc_i[PCM ? i : 0][PCM ? j : 0] = fmaf(a[i] * posw, b[j], acc_i[PCM ? i : 0][PCM ? j : 0]);
           }
         }
       }
@@ -251,22 +258,34 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
         y[j] *= fac;
       }
     } else {
-      const bool line_sigma = PCM || p.out_noise_vals != nullptr;
-      float sigma = outputSigma(io, p.vnorm[r]);
+      const bool line_sigma = p.out_noise_vals != nullptr;
+      const float vn = p.vnorm[r];
+      float sigma = PCM ? io.out_noise : outputSigma(io, vn);
       float z[4] = {0.f, 0.f, 0.f, 0.f};
       if (sigma > 0.0f || line_sigma) {
         gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag, z);
+      }
+      float zw[4] = {0.f, 0.f, 0.f, 0.f};
+      if (PCM && io.w_noise > 0.0f && io.w_noise_type != AB200_WNOISE_NONE) {
+        // the weight noise enters before the non-linearity: a draw of its own
+        gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag ^ 0x04000000u, zw);
       }
       float u[4] = {0.5f, 0.5f, 0.5f, 0.5f};
       if (io.out_sto_round) {
         uniform4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag_u, u);
       }
+      const LineChain lc{p.v_offset, p.out_nl, p.nl_factor, __fdiv_rn((float)K, io.ir_g_ratio)};
 #pragma unroll
       for (int j = 0; j < T; j++) {
         const int q = (c + j) & 3; // T divides 4 and c is a multiple of T: same block for all j
-        if (line_sigma && c + j < N) {
-          sigma = outputSigmaLine(io, p.vnorm[r], p.out_noise_vals, c + j,
-                                  PCM ? acc2[PCM ? i : 0][PCM ? j : 0] : 0.0f);
+        if (c + j < N) {
+          if (line_sigma) {
+            sigma = PCM ? p.out_noise_vals[c + j] : outputSigmaLine(io, vn, p.out_noise_vals, c + j, 0.0f);
+          }
+          if (PCM) {
+            y[j] = lineChain(io, lc, y[j], c + j, acc_c[PCM ? i : 0][PCM ? j : 0],
+                             acc_i[PCM ? i : 0][PCM ? j : 0], acc2[PCM ? i : 0][PCM ? j : 0], vn, zw[q]);
+          }
         }
         y[j] = finalizeOutput(io, y[j], sigma, z[q], exceeded, u[q]) * fac;
       }
@@ -359,18 +378,22 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
         vn = sqrtf(t);
       }
       __syncthreads();
-      float sigma = outputSigma(io, vn);
-      const bool pcm = io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f;
-      const bool line_sigma = pcm || p.out_noise_vals != nullptr;
+      const bool pcm = ioNeedsLineChain(io);
+      float sigma = pcm ? io.out_noise : outputSigma(io, vn);
+      const bool line_sigma = p.out_noise_vals != nullptr;
+      const LineChain lc{p.v_offset, p.out_nl, p.nl_factor, __fdiv_rn((float)K, io.ir_g_ratio)};
+      const uint32_t round_tag = TAG_FWD_OUT + p.noise_id + (uint32_t)round * 0x10000u;
       int fail = 0;
       for (int n = threadIdx.x; n < N; n += blockDim.x) {
-        float acc = 0.0f, acc2 = 0.0f;
+        float acc = 0.0f, acc2 = 0.0f, acc_c = 0.0f, acc_i = 0.0f;
         const float *wp = p.w + (long long)n * p.wn;
         if (pcm) {
           for (int k = 0; k < K; k++) {
-            float wv = wp[(long long)k * p.wk];
-            acc = fmaf(v_sh[k], wv, acc);
-            acc2 = fmaf(v_sh[k] * v_sh[k], fabsf(wv), acc2);
+            const float wv = wp[(long long)k * p.wk], v = v_sh[k];
+            acc = fmaf(v, wv, acc);
+            acc2 = fmaf(v * v, fabsf(wv), acc2);
+            acc_c = fmaf(fabsf(v), fabsf(wv), acc_c);
+            acc_i = fmaf(v * irPosWeight(k, K), wv, acc_i);
           }
         } else {
           for (int k = 0; k < K; k++) {
@@ -378,7 +401,14 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
           }
         }
         if (line_sigma) {
-          sigma = outputSigmaLine(io, vn, p.out_noise_vals, n, acc2);
+          sigma = pcm ? p.out_noise_vals[n] : outputSigmaLine(io, vn, p.out_noise_vals, n, 0.0f);
+        }
+        if (pcm) {
+          float zw[4] = {0.f, 0.f, 0.f, 0.f};
+          if (io.w_noise > 0.0f && io.w_noise_type != AB200_WNOISE_NONE) {
+            gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(n >> 2), p.call, round_tag ^ 0x04000000u, zw);
+          }
+          acc = lineChain(io, lc, acc, n, acc_c, acc_i, acc2, vn, zw[n & 3]);
         }
         float z[4] = {0.f, 0.f, 0.f, 0.f};
         if (sigma > 0.0f) {
@@ -453,8 +483,7 @@ void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
     return (long long)((p.out_size + 16 * t - 1) / (16 * t)) * ((p.m + 16 * t - 1) / (16 * t));
   };
   const int T = ctas(4) >= n_sm ? 4 : (ctas(2) >= n_sm ? 2 : 1);
-  const bool pcm =
-      !p.io.is_perfect && p.io.w_noise_type == AB200_WNOISE_PCM_READ && p.io.w_noise > 0.0f;
+  const bool pcm = ioNeedsLineChain(p.io);
 #define AB200_SIMT(TT, PCM)                                                                        \
   {                                                                                                \
     dim3 grid((p.out_size + 16 * TT - 1) / (16 * TT), (p.m + 16 * TT - 1) / (16 * TT));           \
@@ -574,8 +603,10 @@ void forwardNoAlloc(const ab200_io_params &io_user, const float *w_dev_xd, int x
   if (m_batch == 0) {
     return;
   }
-  if (io_user.out_noise_std > 0.0f && !io_user.is_perfect) {
-    AB200_FATAL("no-alloc forward: out_noise_std needs a tile (the per-line values belong to it)");
+  if (!io_user.is_perfect && (io_user.out_noise_std > 0.0f || io_user.v_offset_std > 0.0f ||
+                              io_user.r_series > 0.0f || io_user.out_nonlinearity > 0.0f)) {
+    AB200_FATAL("no-alloc forward: per-line IO values (out_noise_std, v_offset_std, r_series, "
+                "out_nonlinearity) need a tile, they belong to it");
   }
   unsigned char *base = noAllocScratchForCurrentDevice();
   MvmProblem p{};

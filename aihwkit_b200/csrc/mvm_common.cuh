@@ -185,6 +185,58 @@ outputSigmaLine(const IOEff &io, float vnorm, const float *onv, int col, float p
 __host__ __device__ __forceinline__ bool ioLineSigma(const IOEff &io) {
   return io.out_noise_std > 0.0f || (io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f);
 }
+// IO settings that need the extra accumulators and the long output chain of the CUDA-core kernels
+__host__ __device__ __forceinline__ bool ioNeedsLineChain(const IOEff &io) {
+  return !io.is_perfect &&
+         ((io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) || io.ir_drop > 0.0f ||
+          io.v_offset_std > 0.0f || io.r_series > 0.0f || io.out_nl > 0.0f);
+}
+
+// Weight of input position k in the IR-drop term: 1 - (1 - k / n)^2
+// (rpu_forward_backward_pass.cpp:418-422)
+__device__ __forceinline__ float irPosWeight(int k, int n) {
+  const float p = __fsub_rn(1.0f, __fdiv_rn((float)k, (float)n));
+  return __fsub_rn(1.0f, __fmul_rn(p, p));
+}
+
+// The analog output of one line before the ADC stage, with the non-idealities in the reference's
+// order (applyNonIdealities + finalizeOutput, rpu_forward_backward_pass.cpp:540-566, :673-719):
+// IR drop, voltage offset / series resistance, weight noise, output non-linearity. `cur` =
+// sum |w| |v|, `irsum` = sum w v posw, `pcm` = sum |w| v^2 of the line; z_w a standard normal.
+struct LineChain {
+  const float *v_offset;
+  const float *out_nl;
+  float nl_factor;
+  float a_scale; // in_size / ir_drop_g_ratio
+};
+__device__ __forceinline__ float lineChain(const IOEff &io, const LineChain &lc, float y, int col,
+                                           float cur, float irsum, float pcm, float vnorm, float z_w) {
+  if (io.ir_drop > 0.0f) {
+    const float a = __fmul_rn(lc.a_scale, cur);
+    const float c = __fmul_rn(a, __fadd_rn(__fmul_rn(a, __fsub_rn(__fmul_rn(0.05f, a), 0.2f)), 0.5f));
+    y = __fsub_rn(y, __fmul_rn(c, __fmul_rn(io.ir_drop, irsum)));
+  }
+  if (lc.v_offset) {
+    const float vo = lc.v_offset[col];
+    if (io.r_series > 0.0f) {
+      const float nom = __fadd_rn(1.0f, fminf(__fmul_rn(io.r_series, fabsf(y)), io.r_series_max));
+      y = __fdiv_rn(__fmul_rn(__fsub_rn(1.0f, vo), y), nom);
+    } else {
+      y = __fmul_rn(y, __fsub_rn(1.0f, vo));
+    }
+  }
+  if (io.w_noise > 0.0f) {
+    if (io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT) {
+      y = __fadd_rn(y, __fmul_rn(__fmul_rn(io.w_noise, vnorm), z_w));
+    } else if (io.w_noise_type == AB200_WNOISE_PCM_READ) {
+      y = __fadd_rn(y, __fmul_rn(__fmul_rn(io.w_noise, sqrtf(pcm)), z_w));
+    }
+  }
+  if (lc.out_nl) {
+    y = __fdiv_rn(__fmul_rn(lc.nl_factor, y), __fadd_rn(1.0f, fabsf(__fmul_rn(lc.out_nl[col], y))));
+  }
+  return y;
+}
 
 // four uniforms in (0,1) for the stochastic ADC rounding of noise block `blk` (four output columns)
 __device__ __forceinline__ void

@@ -1277,8 +1277,9 @@ bool TcEngine::ioSupported(const IOEff &io) {
       io.out_sto_round) {
     return false;
   }
-  // a noise std-dev per output line or per element (PCMRead) likewise
-  if (ioLineSigma(io)) {
+  // a noise std-dev per output line or per element (PCMRead) likewise, and the non-idealities
+  // of the output lines (IR drop, voltage offsets, series resistance, non-linearity)
+  if (ioLineSigma(io) || ioNeedsLineChain(io)) {
     return false;
   }
   // the DAC kernel of this path knows the common noise-management types only, and the re-run

@@ -56,6 +56,14 @@ IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only) {
   e.w_noise = io.w_noise;
   e.nm_assumed_wmax = io.nm_assumed_wmax;
   e.nm_decay = io.nm_decay;
+  e.ir_drop = io.ir_drop > 0.0f ? io.ir_drop : 0.0f;
+  e.ir_g_ratio = io.ir_drop_g_ratio;
+  e.v_offset_std = io.v_offset_std > 0.0f ? io.v_offset_std : 0.0f;
+  e.r_series = io.r_series > 0.0f ? io.r_series : 0.0f;
+  e.r_series_max = io.r_series_max_total > 0.0f ? io.r_series_max_total : std::numeric_limits<float>::max();
+  e.out_nl = io.out_nonlinearity;
+  e.out_nl_std = io.out_nonlinearity_std;
+  e.slope_calibration = io.slope_calibration;
   e.inp_noise = io.inp_noise;
   e.inp_asym = 1.0f - io.inp_asymmetry;
   e.out_asym = 1.0f - io.out_asymmetry;
@@ -72,6 +80,14 @@ IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only) {
     if (plain_only && (io.noise_management == AB200_NM_AVERAGE_ABS_MAX ||
                        io.noise_management == AB200_NM_AVERAGE_ABS_MAX_SINGLE_VALUE)) {
       AB200_FATAL("running-average noise management is not implemented for the read-out of a transfer");
+    }
+    if (e.ir_drop > 0.0f && !(io.ir_drop_g_ratio > 0.0f)) {
+      AB200_FATAL("ir_drop needs a positive ir_drop_g_ratio");
+    }
+    if (plain_only && (e.ir_drop > 0.0f || e.v_offset_std > 0.0f || e.r_series > 0.0f ||
+                       io.out_nonlinearity > 0.0f)) {
+      AB200_FATAL("IR drop / voltage offsets / output non-linearity are not implemented for the "
+                  "read-out of a transfer");
     }
     if (plain_only && ((io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) ||
                        io.out_noise_std > 0.0f)) {
@@ -490,6 +506,10 @@ Tile::~Tile() {
     cudaFree(drift_t_);
     cudaFree(drift_nu_);
     cudaFree(nm_state_);
+    cudaFree(f_lt_.voff);
+    cudaFree(f_lt_.nl);
+    cudaFree(b_lt_.voff);
+    cudaFree(b_lt_.nl);
     cudaFree(f_onv_);
     cudaFree(b_onv_);
     cudaFree(xw_);
@@ -601,22 +621,7 @@ void Tile::toDevice(int cuda_device) {
     AB200_CUDA(cudaMalloc(&nm_state_, sizeof(float)));
     AB200_CUDA(cudaMemcpy(nm_state_, &not_started, sizeof(float), cudaMemcpyHostToDevice));
   }
-  {
-    HostRNG rng(key_.k0 ^ (key_.k1 * 0x9e3779b9u) ^ 0x6f6e7631u);
-    auto draw = [&](const IOEff &io, int n, float **dst) {
-      if (io.is_perfect || !(io.out_noise_std > 0.0f)) {
-        return;
-      }
-      std::vector<float> v((size_t)n);
-      for (auto &e : v) {
-        e = std::fabs(io.out_noise * (1.0f + io.out_noise_std * rng.gauss()));
-      }
-      AB200_CUDA(cudaMalloc(dst, v.size() * sizeof(float)));
-      AB200_CUDA(cudaMemcpy(*dst, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice));
-    };
-    draw(f_io_, d_size_, &f_onv_);
-    draw(b_io_, x_size_, &b_onv_);
-  }
+  populateLineTables();
   for (int k = 0; k < n_dev_; k++) {
     uploadDeviceStore(dev_[k]);
   }
@@ -624,6 +629,126 @@ void Tile::toDevice(int cuda_device) {
   setWeights(w.data());
   host_w_dx_.clear();
   host_w_dx_.shrink_to_fit();
+}
+
+// Per-line values of the two IO directions (ForwardBackwardPassIOManaged::populateFBParameter,
+// rpu_forward_backward_pass.cpp:249-316): voltage offsets, output non-linearities with the slope
+// calibration factor, output-noise values. Drawn on the host from the tile's seed.
+static bool ioHasVOffset(const IOEff &io) {
+  return !io.is_perfect && (io.v_offset_std > 0.0f || io.r_series > 0.0f);
+}
+static bool ioHasNl(const IOEff &io) {
+  return !io.is_perfect && (io.out_nl > 0.0f || io.r_series > 0.0f);
+}
+static float nlFactor(const IOEff &io, const std::vector<float> &nl) {
+  if (!(io.slope_calibration > 0.0f)) {
+    return 1.0f;
+  }
+  const float out_bound = (io.out_bound > 0.0f && io.out_bound < std::numeric_limits<float>::infinity())
+                              ? io.out_bound
+                              : 1.0f;
+  float sum = 0.0f;
+  if (io.out_nl > 0.0f || !nl.empty()) {
+    for (float v : nl) {
+      sum += std::fabs(v);
+    }
+  }
+  const float n = nl.empty() ? 1.0f : (float)nl.size();
+  const float f = 1.0f + (sum / n + io.r_series) * io.slope_calibration * out_bound;
+  return f * f;
+}
+
+void Tile::uploadLineTables(LineTables &lt, const IOEff &io, int n, float **onv) {
+  auto up = [&](const std::vector<float> &h, float **dst) {
+    if (h.empty()) {
+      return;
+    }
+    if (!*dst) {
+      AB200_CUDA(cudaMalloc(dst, h.size() * sizeof(float)));
+    }
+    AB200_CUDA(cudaMemcpy(*dst, h.data(), h.size() * sizeof(float), cudaMemcpyHostToDevice));
+  };
+  (void)n;
+  up(lt.h_voff, &lt.voff);
+  up(lt.h_nl, &lt.nl);
+  up(lt.h_onv, onv);
+  lt.nl_factor = ioHasNl(io) ? nlFactor(io, lt.h_nl) : 1.0f;
+}
+
+void Tile::populateLineTables() {
+  HostRNG rng(key_.k0 ^ (key_.k1 * 0x9e3779b9u) ^ 0x6f6e7631u);
+  auto draw = [&](const IOEff &io, int n, LineTables &lt, float **onv) {
+    if (io.is_perfect) {
+      return;
+    }
+    if (ioHasVOffset(io)) {
+      lt.h_voff.resize((size_t)n);
+      for (auto &e : lt.h_voff) {
+        e = std::max(io.v_offset_std * rng.gauss(), 0.0f);
+      }
+    }
+    if (ioHasNl(io)) {
+      const float out_bound =
+          (io.out_bound > 0.0f && io.out_bound < std::numeric_limits<float>::infinity()) ? io.out_bound : 1.0f;
+      lt.h_nl.resize((size_t)n);
+      for (auto &e : lt.h_nl) {
+        e = std::fabs(io.out_nl / out_bound * (1.0f + std::max(io.out_nl_std, 0.0f) * rng.gauss()));
+      }
+    }
+    if (io.out_noise_std > 0.0f) {
+      lt.h_onv.resize((size_t)n);
+      for (auto &e : lt.h_onv) {
+        e = std::fabs(io.out_noise * (1.0f + io.out_noise_std * rng.gauss()));
+      }
+    }
+    uploadLineTables(lt, io, n, onv);
+  };
+  draw(f_io_, d_size_, f_lt_, &f_onv_);
+  draw(b_io_, x_size_, b_lt_, &b_onv_);
+}
+
+void Tile::setLineTables(MvmProblem &p, const LineTables &lt, const float *onv) const {
+  p.out_noise_vals = onv;
+  p.v_offset = lt.voff;
+  p.out_nl = lt.nl;
+  p.nl_factor = lt.nl_factor;
+}
+
+void Tile::getIoVector(bool backward, int which, float *values, int n) {
+  const LineTables &lt = backward ? b_lt_ : f_lt_;
+  const std::vector<float> &h = which == AB200_IOVEC_V_OFFSET
+                                    ? lt.h_voff
+                                    : (which == AB200_IOVEC_OUT_NONLINEARITY ? lt.h_nl : lt.h_onv);
+  if (which < AB200_IOVEC_V_OFFSET || which > AB200_IOVEC_OUT_NOISE_VALUES) {
+    AB200_FATAL("io vector: unknown kind");
+  }
+  if (h.empty()) {
+    AB200_FATAL("io vector: the IO setting that uses it is off for this direction");
+  }
+  if (n != (int)h.size()) {
+    AB200_FATAL("io vector: expected " << h.size() << " values");
+  }
+  std::memcpy(values, h.data(), h.size() * sizeof(float));
+}
+
+void Tile::setIoVector(bool backward, int which, const float *values, int n) {
+  requireDevice("set_io_vector");
+  LineTables &lt = backward ? b_lt_ : f_lt_;
+  if (which < AB200_IOVEC_V_OFFSET || which > AB200_IOVEC_OUT_NOISE_VALUES) {
+    AB200_FATAL("io vector: unknown kind");
+  }
+  std::vector<float> &h = which == AB200_IOVEC_V_OFFSET
+                              ? lt.h_voff
+                              : (which == AB200_IOVEC_OUT_NONLINEARITY ? lt.h_nl : lt.h_onv);
+  if (h.empty()) {
+    AB200_FATAL("io vector: the IO setting that uses it is off for this direction");
+  }
+  if (n != (int)h.size()) {
+    AB200_FATAL("io vector: expected " << h.size() << " values");
+  }
+  AB200_CUDA(cudaDeviceSynchronize());
+  h.assign(values, values + n);
+  uploadLineTables(lt, backward ? b_io_ : f_io_, n, backward ? &b_onv_ : &f_onv_);
 }
 
 void Tile::ensureScratch(int m) {
@@ -966,7 +1091,7 @@ void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, boo
   p.m = m;
   p.backward = 0;
   p.io = f_io_;
-  p.out_noise_vals = f_onv_;
+  setLineTables(p, f_lt_, f_onv_);
   p.alpha = 1.0f;
   p.call = fwd_calls_++;
   p.noise_id = 0;
@@ -1001,7 +1126,7 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
   p.m = m;
   p.backward = 0;
   p.io = f_io_;
-  p.out_noise_vals = f_onv_;
+  setLineTables(p, f_lt_, f_onv_);
   p.alpha = out_scale; // digital scale of this tile's output (mapping scale)
   p.call = fwd_calls_++;
   p.noise_id = noise_id;
@@ -1073,7 +1198,7 @@ void Tile::backwardCore(const float *d, long long d_ss, long long d_fs, float *x
   p.m = m;
   p.backward = 1;
   p.io = b_io_;
-  p.out_noise_vals = b_onv_;
+  setLineTables(p, b_lt_, b_onv_);
   p.alpha = out_scale;
   p.call = bwd_calls_++;
   p.noise_id = noise_id;

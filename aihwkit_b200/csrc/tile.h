@@ -36,6 +36,14 @@ struct IOEff {
   float nm_thres;
   float nm_assumed_wmax;
   float nm_decay; // running-average noise management
+  // non-idealities of the output lines (CUDA-core kernels): IR drop, voltage offsets / series
+  // resistance, output non-linearity; the per-line tables travel in MvmProblem
+  float ir_drop;
+  float ir_g_ratio;
+  float v_offset_std;
+  float r_series;
+  float r_series_max;
+  float out_nl, out_nl_std, slope_calibration;
   // Gaussian added to the DAC output, factors applied to negative DAC outputs / negative values
   // in front of the ADC (1 - asymmetry), stochastic rounding of DAC / ADC
   float inp_noise;
@@ -98,6 +106,11 @@ struct MvmProblem {
   // running value of the AverageAbsMax noise management (one float, < 0: not started), shared by
   // the forward and backward passes of a tile as in the reference
   float *nm_state = nullptr;
+  // per-line voltage offsets and output non-linearities (out_size entries each) and the slope
+  // calibration factor, when the IO of this direction has them
+  const float *v_offset = nullptr;
+  const float *out_nl = nullptr;
+  float nl_factor = 1.0f;
 };
 
 // CUDA-core path: noise management, fused MVM, bound-management re-run
@@ -268,6 +281,8 @@ public:
 
   // weight operations between updates (RPUPulsed::decayWeights / diffuseWeights / clipWeights /
   // resetCols / setWeightsUniformRandom, src/rpucuda/rpu_pulsed.cpp:189-284)
+  void getIoVector(bool backward, int which, float *values, int n);
+  void setIoVector(bool backward, int which, const float *values, int n);
   void driftWeights(float time_since_last_call, cudaStream_t s);
   void modifyWeights(const ab200_weight_modifier_params &par, cudaStream_t s);
   void decayWeights(float alpha, bool bias_no_decay, cudaStream_t s);
@@ -346,6 +361,16 @@ private:
   // backward (x_size), drawn once per tile (rpu_forward_backward_pass.cpp:306-313)
   float *f_onv_ = nullptr, *b_onv_ = nullptr;
   float *nm_state_ = nullptr;
+  // per-line tables of a direction (MVParameter, rpu_forward_backward_pass.h:14-22)
+  struct LineTables {
+    std::vector<float> h_voff, h_nl, h_onv;
+    float *voff = nullptr, *nl = nullptr;
+    float nl_factor = 1.0f;
+  };
+  LineTables f_lt_, b_lt_;
+  void populateLineTables();
+  void uploadLineTables(LineTables &lt, const IOEff &io, int n, float **onv);
+  void setLineTables(MvmProblem &p, const LineTables &lt, const float *onv) const;
   // power-law drift: per element the weight seen by the previous call, the weight and the time of
   // its last write, and (pulsed devices) its exponent; time in units of t0
   // modified copy of the weights that forward / backward read (modify_weights), its largest

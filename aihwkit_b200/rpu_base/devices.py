@@ -81,11 +81,6 @@ class AnalogTileInputOutputParameter:
     """IOMetaParameter (rpu_base_devices.cpp:485-519)."""
 
     _unsupported = {
-        "ir_drop": 0.0,
-        "out_nonlinearity": 0.0,
-        "out_nonlinearity_std": 0.0,
-        "r_series": 0.0,
-        "v_offset_std": 0.0,
         "w_read_asymmetry_dtod": 0.0,
     }
 
@@ -130,6 +125,13 @@ class AnalogTileInputOutputParameter:
                 raise RuntimeError(
                     f"IO parameter '{name}' is not implemented by the B200 analog tile"
                 )
+        if (self.v_offset_std > 0 or self.r_series > 0) and self.v_offset_w_min != 0.0:
+            # the reference term of the offsets, - 2 vo_i g_ref sum_j x_j
+            # (rpu_forward_backward_pass.cpp:471-503); without offsets the value is not read
+            raise RuntimeError(
+                "IO parameter 'v_offset_w_min' (with voltage offsets on) is not implemented by the "
+                "B200 analog tile"
+            )
         mv = int(self.mv_type)
         if mv not in (int(AnalogMVType.Ideal), int(AnalogMVType.OnePass)):
             raise RuntimeError("MV type not implemented.")
@@ -148,7 +150,8 @@ class AnalogTileInputOutputParameter:
         for name in (
             "inp_bound", "inp_res", "inp_noise", "out_bound", "out_res", "out_noise", "out_scale",
             "w_noise", "nm_thres", "max_bm_res", "inp_asymmetry", "out_asymmetry", "nm_assumed_wmax",
-            "out_noise_std", "nm_decay",
+            "out_noise_std", "nm_decay", "ir_drop", "ir_drop_g_ratio", "v_offset_std", "r_series",
+            "out_nonlinearity", "out_nonlinearity_std", "slope_calibration",
         ):
             setattr(c, name, float(getattr(self, name)))
         return c

@@ -687,6 +687,20 @@ class AnalogTile:
         scales.copy_(new_scales.to(scales.device))
         return scales
 
+    def get_io_vector(self, backward: bool, which: int) -> torch.Tensor:
+        """Per-line values of one IO direction: 0 voltage offsets, 1 output non-linearities,
+        2 output-noise values (part of ``dump_extra`` in the reference as ``fwd.v_offset`` ...,
+        src/rpucuda/rpu_forward_backward_pass.cpp:63-82). Device tiles only."""
+        n = self.get_x_size() if backward else self.get_d_size()
+        out = torch.empty(n, dtype=torch.float32)
+        check(self._lib.ab200_tile_get_io_vector(self._h, int(bool(backward)), int(which), out.data_ptr(), n))
+        return out
+
+    def set_io_vector(self, backward: bool, which: int, values: torch.Tensor) -> None:
+        v = values.detach().to(dtype=torch.float32, device="cpu").contiguous()
+        check(self._lib.ab200_tile_set_io_vector(self._h, int(bool(backward)), int(which), v.data_ptr(),
+                                                 v.numel()))
+
     def modify_weights(self, weight_modifier_params) -> None:
         """rpu_base_tiles.cpp:358-371 (WeightModifier, src/rpucuda/weight_modifier.cpp)."""
         if int(weight_modifier_params.type) != int(WeightModifierType.Copy) and \

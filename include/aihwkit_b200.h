@@ -111,6 +111,25 @@ typedef struct ab200_io_params {
   /* AverageAbsMax noise management: weight of a sample's abs-max in the running value
    * s <- s (1 - nm_decay) + nm_decay * max|x| (rpu_forward_backward_pass.cpp:139-150) */
   float nm_decay;
+  /* Non-idealities of the analog output lines, CUDA-core kernels only
+   * (rpu_forward_backward_pass.cpp:388-517, :673-719; bound as ir_drop, ir_drop_g_ratio,
+   * v_offset_std, r_series, out_nonlinearity, out_nonlinearity_std, slope_calibration):
+   *  - IR drop: y_i -= ir_drop * c_i * sum_j w_ij v_j (1 - (1 - j/n)^2), c_i a cubic of the line
+   *    current a_i = n / ir_drop_g_ratio * sum_j |w_ij| |v_j|;
+   *  - voltage offsets and series resistance: y_i = (1 - vo_i) y_i / (1 + min(r_series |y_i|,
+   *    r_series_max_total)), vo_i = max(v_offset_std N(0,1), 0) per line;
+   *  - output non-linearity: y_i = f y_i / (1 + |nl_i y_i|), nl_i = |out_nonlinearity / out_bound *
+   *    (1 + out_nonlinearity_std N(0,1))| per line, f the slope calibration factor.
+   * The per-line values are drawn once per tile and direction; ab200_tile_get_io_vector /
+   * ab200_tile_set_io_vector read and replace them. r_series_max_total <= 0 means no limit. */
+  float ir_drop;
+  float ir_drop_g_ratio;
+  float v_offset_std;
+  float r_series;
+  float r_series_max_total;
+  float out_nonlinearity;
+  float out_nonlinearity_std;
+  float slope_calibration;
 } ab200_io_params;
 
 /* PulsedUpdateMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:248-279;
@@ -394,6 +413,19 @@ const char *ab200_tile_extra_name(int k);
 int ab200_tile_dump_extra(ab200_tile *tile, double *values);
 int ab200_tile_load_extra(ab200_tile *tile, const char *const *names, const double *values,
                           int count, int strict);
+
+/* Per-line values of a direction's IO (MVParameter, src/rpucuda/rpu_forward_backward_pass.h:14-22;
+ * part of the reference's extra state as fwd.v_offset / fwd.out_nonlinearity / fwd.out_noise_values
+ * and bwd.*, rpu_forward_backward_pass.cpp:66-79): `n` host floats, n = d_size forward, x_size
+ * backward. Fails when the IO setting that uses the vector is off. */
+enum ab200_io_vector {
+  AB200_IOVEC_V_OFFSET = 0,
+  AB200_IOVEC_OUT_NONLINEARITY = 1,
+  AB200_IOVEC_OUT_NOISE_VALUES = 2
+};
+int ab200_tile_get_io_vector(ab200_tile *tile, int backward, int which, float *values_host, int n);
+int ab200_tile_set_io_vector(ab200_tile *tile, int backward, int which, const float *values_host,
+                             int n);
 
 /* WeightModifierParameter (src/rpucuda/weight_modifier.h:15-50; bound in rpu_base_tiles.cpp:31-51). */
 enum ab200_weight_modifier_type {

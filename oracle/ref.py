@@ -78,6 +78,7 @@ def load() -> C.CDLL:
         "ref_tile_diffuse_weights": (i, [vp]),
         "ref_tile_drift_weights": (i, [vp, C.c_float]),
         "ref_tile_modify_weights": (i, [vp, vp]),
+        "ref_tile_get_io_vector": (i, [vp, i, i, fp, i]),
         "ref_tile_clip_weights": (i, [vp, i, C.c_float, C.c_float]),
         "ref_tile_reset_columns": (i, [vp, i, i, C.c_float]),
         "ref_tile_set_matrix_indices": (i, [vp, fp, C.c_longlong]),
@@ -236,6 +237,16 @@ class RefTile:
     # weight operations between updates (src/rpucuda/rpu_pulsed.cpp:189-284)
     def decay_weights(self, alpha: float = 1.0, bias_no_decay: bool = False) -> None:
         self._ck(self._lib.ref_tile_decay_weights(self._h, alpha, int(bias_no_decay)))
+
+    def get_io_vector(self, backward: bool, which: int, n: int) -> np.ndarray:
+        """The per-line IO vector the reference drew (0 v_offset, 1 out_nonlinearity,
+        2 out_noise_values); empty when it is not in use."""
+        out = np.zeros(n, np.float32)
+        cnt = self._lib.ref_tile_get_io_vector(self._h, int(backward), int(which),
+                                               out.ctypes.data_as(C.POINTER(C.c_float)), n)
+        if cnt < 0:
+            raise RuntimeError("ref_tile_get_io_vector failed")
+        return out[:cnt]
 
     def modify_weights(self, weight_modifier_params) -> None:
         """``weight_modifier_params``: a ``WeightModifierParameter`` of aihwkit_b200.rpu_base.tiles."""

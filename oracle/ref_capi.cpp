@@ -57,6 +57,16 @@ void toIO(const ab200_io_params &s, IOMetaParameter<float> &io) {
   io.nm_assumed_wmax = s.nm_assumed_wmax;
   io.out_noise_std = s.out_noise_std;
   io.nm_decay = s.nm_decay;
+  io.ir_drop = s.ir_drop;
+  io.ir_drop_Gw_div_gmax = s.ir_drop_g_ratio;
+  io.v_offset_std = s.v_offset_std;
+  io.r_series = s.r_series;
+  if (s.r_series_max_total > 0.0f) {
+    io.r_series_max_total = s.r_series_max_total;
+  }
+  io.out_nonlinearity = s.out_nonlinearity;
+  io.out_nonlinearity_std = s.out_nonlinearity_std;
+  io.slope_calibration = s.slope_calibration;
 }
 
 void toUp(const ab200_update_params &s, PulsedUpdateMetaParameter<float> &up) {
@@ -411,6 +421,35 @@ int ref_tile_decay_weights(void *h, float alpha, int bias_no_decay) {
   REF_TRY
   static_cast<RefTile *>(h)->rpu->decayWeights(alpha, bias_no_decay != 0);
   REF_CATCH
+}
+
+/* The per-line IO vectors the reference drew at construction, out of its extra state
+ * (ForwardBackwardPass::dumpExtra, src/rpucuda/rpu_forward_backward_pass.cpp:63-82). Returns the
+ * number of values (0: the vector is not in use); at most `n` are copied. */
+int ref_tile_get_io_vector(void *h, int backward, int which, float *values, int n) {
+  try {
+    RPU::state_t st;
+    static_cast<RefTile *>(h)->rpu->dumpExtra(st, "rpu");
+    const char *names[3] = {"v_offset", "out_nonlinearity", "out_noise_values"};
+    if (which < 0 || which > 2) {
+      return -1;
+    }
+    const std::string suffix = std::string("fb_pass.") + (backward ? "bwd." : "fwd.") + names[which];
+    for (const auto &kv : st) {
+      const std::string &k = kv.first;
+      if (k.size() >= suffix.size() && k.compare(k.size() - suffix.size(), suffix.size(), suffix) == 0) {
+        const int cnt = (int)kv.second.size();
+        for (int i = 0; i < cnt && i < n; i++) {
+          values[i] = (float)kv.second[(size_t)i];
+        }
+        return cnt;
+      }
+    }
+    return 0;
+  } catch (const std::exception &e) {
+    g_err = e.what();
+    return -1;
+  }
 }
 
 int ref_tile_modify_weights(void *h, const ab200_weight_modifier_params *s) {

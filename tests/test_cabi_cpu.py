@@ -32,7 +32,7 @@ def test_struct_sizes_match_header():
     for which, cls in enumerate((_cabi.IOParams, _cabi.UpdateParams, _cabi.DeviceParams,
                                  _cabi.TransferParams, _cabi.TileConfig, _cabi.ScatterPlan)):
         assert C.sizeof(cls) == lib.ab200_sizeof(which), cls.__name__
-    assert C.sizeof(_cabi.IOParams) == 23 * 4
+    assert C.sizeof(_cabi.IOParams) == 31 * 4
     assert C.sizeof(_cabi.TileConfig) % 8 == 0
 
 
@@ -129,8 +129,10 @@ def test_compute_without_device_fails_loudly():
 
 def test_unsupported_settings_raise():
     p = D.AnalogTileParameter()
-    p.forward_io.ir_drop = 0.1
-    with pytest.raises(RuntimeError, match="ir_drop"):
+    p.forward_io.v_offset_w_min = -1.0  # only read with voltage offsets on
+    p._config(4, 4, D.ConstantStepResistiveDeviceParameter())
+    p.forward_io.v_offset_std = 0.1
+    with pytest.raises(RuntimeError, match="v_offset_w_min"):
         p._config(4, 4, D.ConstantStepResistiveDeviceParameter())
     p = D.AnalogTileParameter()
     p.update.pulse_type = D.PulseType.Stochastic  # separate +- trains: same law as the compressed type

@@ -183,3 +183,100 @@ def test_line_noise_settings_take_the_cuda_core_kernels_at_tensor_core_sizes():
     sig = np.sqrt(0.02 ** 2 + 0.05 ** 2 * ((v ** 2) @ np.abs(W.astype(np.float64)).T)) * amax
     ratio = ys.std(axis=0) / sig
     assert abs(ratio.mean() - 1.0) < 0.02 and np.abs(ratio - 1.0).max() < 0.5
+
+
+_LINE_SETTINGS = {
+    "ir_drop": dict(ir_drop=1.5, ir_drop_g_ratio=3000.0),  # a wire ratio that makes the drop visible
+    "v_offset": dict(v_offset_std=0.05),
+    "r_series": dict(v_offset_std=0.03, r_series=0.02),
+    "nonlinearity": dict(out_nonlinearity=0.15, out_nonlinearity_std=0.2),
+    "all": dict(ir_drop=1.0, ir_drop_g_ratio=3000.0, v_offset_std=0.05, r_series=0.02, out_nonlinearity=0.1,
+                out_nonlinearity_std=0.2),
+}
+
+
+@pytest.mark.parametrize("name", sorted(_LINE_SETTINGS))
+@pytest.mark.parametrize("bm", [False, True])
+def test_line_non_idealities_against_reference(name, bm):
+    """IR drop, voltage offsets, series resistance and output non-linearity
+    (src/rpucuda/rpu_forward_backward_pass.cpp:388-517, :673-719) with noise off: the GPU tile,
+    given the per-line values the compiled reference drew, returns the reference's outputs up to
+    single ADC steps; forward (with and without bound-management re-runs) and backward."""
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    if not ref.available():
+        pytest.skip("compiled reference not built")
+    rng = np.random.default_rng(len(name))
+    x_size, d_size, m = 150, 70, 48
+    p = H.training_params(noise=False, pulse_det=True, bm=bm, out_bound=2.0 if bm else 12.0)
+    for io in (p.forward_io, p.backward_io):
+        for k, v in _LINE_SETTINGS[name].items():
+            setattr(io, k, v)
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=9)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    rt = ref.RefTile(cfg)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().cpu().numpy()
+    rt.set_weights(W)
+    for backward, n in ((False, d_size), (True, x_size)):
+        for which in (0, 1):
+            v = rt.get_io_vector(backward, which, n)
+            if v.size:
+                assert t.get_io_vector(backward, which).numel() == n
+                t.set_io_vector(backward, which, torch.from_numpy(v))
+                assert np.array_equal(t.get_io_vector(backward, which).numpy(), v)
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+    y = t.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    yr = rt.forward(X)
+    res_out = 2.0 * (2.0 if bm else 12.0) / 510.0
+    # the unit of comparison: one ADC step of the row at its last bound-management round
+    lsb = res_out * np.abs(X).max(axis=1, keepdims=True) * (t.last_bm_stats()[1] if bm else 1.0)
+    frac, worst = H.lsb_report(y, yr, lsb)
+    assert frac <= 5e-3 and worst <= 1.001, (frac, worst)
+    if bm:
+        assert t.last_bm_stats()[0] > 0
+    # the setting changes the output (against the same tile without it)
+    p0 = H.training_params(noise=False, pulse_det=True, bm=bm, out_bound=2.0 if bm else 12.0)
+    t0 = T.AnalogTile(p0._config(x_size, d_size, H.device("cs", False), seed=9), cuda_device=0)
+    t0.set_weights(torch.from_numpy(W))
+    assert np.abs(t0.forward(torch.from_numpy(X).cuda()).cpu().numpy() - y).max() > 2 * res_out
+    g = t.backward(torch.from_numpy(Dm).cuda()).cpu().numpy()
+    gr = rt.backward(Dm)
+    lsb_b = (2.0 * 12.0 / 510.0) * np.abs(Dm).max(axis=1, keepdims=True)
+    frac, worst = H.lsb_report(g, gr, lsb_b)
+    assert frac <= 5e-3 and worst <= 1.001, (frac, worst)
+
+
+def test_weight_noise_enters_before_the_non_linearity():
+    """With an output non-linearity the additive weight noise is compressed by it while the output
+    noise is not: the std-dev of an output follows nlf / (1 + |nl y|)^2 * w_noise ||v|| (first
+    order) instead of the merged sqrt(w^2 + o^2)."""
+    from aihwkit_b200.rpu_base import devices as D
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(12)
+    x_size, d_size, m = 64, 32, 8
+    p = H.training_params(noise=False, pulse_det=True, bm=False, adc=False, out_bound=0.0)
+    p.forward_io.w_noise = 0.02
+    p.forward_io.w_noise_type = D.WeightNoiseType.AdditiveConstant
+    p.forward_io.out_nonlinearity = 0.5
+    p.forward_io.slope_calibration = 0.0
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=9)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().cpu().numpy()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    X /= np.abs(X).max(axis=1, keepdims=True)
+    xg = torch.from_numpy(X).cuda()
+    ys = _repeat(lambda: t.forward(xg).cpu().numpy(), 300)
+    res = np.float32(2.0 / 126.0)
+    v = np.clip(np.rint(X / res) * res, -1, 1).astype(np.float64)
+    y0 = v @ W.astype(np.float64).T
+    nl = t.get_io_vector(False, 1).numpy().astype(np.float64)[None, :]
+    sig = 0.02 * np.sqrt((v ** 2).sum(axis=1, keepdims=True)) / (1.0 + np.abs(nl * y0)) ** 2
+    ratio = ys.std(axis=0) / sig
+    assert abs(ratio.mean() - 1.0) < 0.02, ratio.mean()
