@@ -324,7 +324,8 @@ private:
   void updateCore(const float *x, long long x_ss, long long x_fs, int x_in, const float *d,
                   long long d_ss, long long d_fs, int m, cudaStream_t s);
   void requireSingleDevice(const char *what);
-  void ensurePar3();
+  void ensurePar3(DeviceStore &ds);
+  int opTargets(float *w[2], DeviceStore *ds[2]);
   void requireIndices(const char *what, long long image_size, int m_batch, int n_img) const;
   void ensureIndexedScratch(long long b);
   void gatherIndexed(const float *x, long long in_mat, int m_batch, int n_img, bool trans,

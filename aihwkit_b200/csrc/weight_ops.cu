@@ -342,8 +342,24 @@ void Tile::requireSingleDevice(const char *what) {
 }
 
 // decay scale, diffusion rate and reset bias per element, uploaded on first use
-void Tile::ensurePar3() {
-  DeviceStore &ds = dev_[0];
+// The weight matrices a weight operation acts on, each with its device: the weights of a single
+// device; for a Transfer compound the fast tile with device 0 and the visible (slow) tile with
+// device 1, one after the other (TransferRPUDevice::decayWeights ... with a fully hidden fast tile,
+// rpu_transfer_device.cpp:612-638: the last device acts on the visible weights).
+int Tile::opTargets(float *w[2], DeviceStore *ds[2]) {
+  if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
+    w[0] = w_fast_;
+    ds[0] = &dev_[0];
+    w[1] = w_;
+    ds[1] = &dev_[1];
+    return 2;
+  }
+  w[0] = w_;
+  ds[0] = &dev_[0];
+  return 1;
+}
+
+void Tile::ensurePar3(DeviceStore &ds) {
   if (ds.kind == AB200_DEVICE_IDEAL || ds.par3_valid) {
     return;
   }
@@ -467,7 +483,7 @@ void Tile::driftWeights(float time_since_last_call, cudaStream_t s) {
 }
 
 void Tile::decayWeights(float alpha, bool bias_no_decay, cudaStream_t s) {
-  requireSingleDevice("decay_weights");
+  requireDevice("decay_weights");
   const long long n = (long long)x_size_ * d_size_;
   const long long first_bias = bias_no_decay ? (long long)(x_size_ - 1) * d_size_ : n;
   if (dev_[0].kind == AB200_DEVICE_IDEAL) {
@@ -481,31 +497,41 @@ void Tile::decayWeights(float alpha, bool bias_no_decay, cudaStream_t s) {
     }
     return;
   }
-  ensurePar3();
-  decayKernel<<<blocksFor(n), 256, 0, s>>>(w_, dev_[0].par4, dev_[0].par3, n, first_bias, alpha, 1);
-  AB200_LAUNCH_CHECK();
+  float *w[2];
+  DeviceStore *ds[2];
+  const int nt = opTargets(w, ds);
+  for (int k = 0; k < nt; k++) {
+    ensurePar3(*ds[k]);
+    decayKernel<<<blocksFor(n), 256, 0, s>>>(w[k], ds[k]->par4, ds[k]->par3, n, first_bias, alpha, 1);
+    AB200_LAUNCH_CHECK();
+  }
   w_version_++;
 }
 
 void Tile::diffuseWeights(cudaStream_t s) {
-  requireSingleDevice("diffuse_weights");
+  requireDevice("diffuse_weights");
   const long long n = (long long)x_size_ * d_size_;
   const bool ideal = dev_[0].kind == AB200_DEVICE_IDEAL;
   if (ideal && !(cfg_.device[0].diffusion > 0.0f)) {
     return;
   }
-  if (!ideal) {
-    ensurePar3();
+  float *w[2];
+  DeviceStore *ds[2];
+  const int nt = opTargets(w, ds);
+  for (int k = 0; k < nt; k++) {
+    if (!ideal) {
+      ensurePar3(*ds[k]);
+    }
+    diffuseKernel<<<blocksFor((n + 3) / 4), 256, 0, s>>>(w[k], ideal ? nullptr : ds[k]->par4,
+                                                        ideal ? nullptr : ds[k]->par3, n,
+                                                        cfg_.device[0].diffusion, key_, op_calls_++);
+    AB200_LAUNCH_CHECK();
   }
-  diffuseKernel<<<blocksFor((n + 3) / 4), 256, 0, s>>>(w_, ideal ? nullptr : dev_[0].par4,
-                                                      ideal ? nullptr : dev_[0].par3, n,
-                                                      cfg_.device[0].diffusion, key_, op_calls_++);
-  AB200_LAUNCH_CHECK();
   w_version_++;
 }
 
 void Tile::clipWeights(int type, float fixed_value, float sigma, cudaStream_t s) {
-  requireSingleDevice("clip_weights");
+  requireDevice("clip_weights");
   const long long n = (long long)x_size_ * d_size_;
   const bool ideal = dev_[0].kind == AB200_DEVICE_IDEAL;
   const float4 *bounds = ideal ? nullptr : dev_[0].par4;
@@ -565,13 +591,18 @@ void Tile::clipWeights(int type, float fixed_value, float sigma, cudaStream_t s)
   } else {
     AB200_FATAL("Clipping type not implemented.");
   }
-  clipBoundsKernel<<<blocksFor(n), 256, 0, s>>>(w_, bounds, n, clip);
-  AB200_LAUNCH_CHECK();
+  float *w[2];
+  DeviceStore *ds[2];
+  const int nt = opTargets(w, ds);
+  for (int k = 0; k < nt; k++) {
+    clipBoundsKernel<<<blocksFor(n), 256, 0, s>>>(w[k], ideal ? bounds : ds[k]->par4, n, clip);
+    AB200_LAUNCH_CHECK();
+  }
   w_version_++;
 }
 
 void Tile::resetColumns(int start_col, int n_cols, float reset_prob, cudaStream_t s) {
-  requireSingleDevice("reset_columns");
+  requireDevice("reset_columns");
   if (reset_prob == 0.0f) {
     return; // rpu_pulsed.cpp:219-224
   }
@@ -584,14 +615,20 @@ void Tile::resetColumns(int start_col, int n_cols, float reset_prob, cudaStream_
     AB200_FATAL("reset_columns: start column " << start_col << " outside [0, " << x_size_ << ")");
   }
   const bool ideal = dev_[0].kind == AB200_DEVICE_IDEAL;
-  if (!ideal) {
-    ensurePar3();
+  float *w[2];
+  DeviceStore *ds[2];
+  // a Transfer compound resets its fast tile only (rpu_transfer_device.cpp:646-651)
+  const int nt = cfg_.device_kind == AB200_DEVICE_TRANSFER ? (opTargets(w, ds), 1) : opTargets(w, ds);
+  for (int k = 0; k < nt; k++) {
+    if (!ideal) {
+      ensurePar3(*ds[k]);
+    }
+    const float reset_std = ideal ? cfg_.device[0].reset_std : ds[k]->reset_std;
+    resetColsKernel<<<blocksFor((long long)n_col * d_size_), 256, 0, s>>>(
+        w[k], ideal ? nullptr : ds[k]->par4, ideal ? nullptr : ds[k]->par3, x_size_, d_size_,
+        start_col, n_col, reset_prob, reset_std, key_, op_calls_++);
+    AB200_LAUNCH_CHECK();
   }
-  const float reset_std = ideal ? cfg_.device[0].reset_std : dev_[0].reset_std;
-  resetColsKernel<<<blocksFor((long long)n_col * d_size_), 256, 0, s>>>(
-      w_, ideal ? nullptr : dev_[0].par4, ideal ? nullptr : dev_[0].par3, x_size_, d_size_,
-      start_col, n_col, reset_prob, reset_std, key_, op_calls_++);
-  AB200_LAUNCH_CHECK();
   w_version_++;
 }
 

@@ -149,11 +149,61 @@ def test_diffusion_and_reset_moments_against_reference():
         H.assert_moments_agree(diffs, np.stack(rd))
 
 
-def test_compound_device_is_rejected():
+@pytest.mark.skipif(not ref.available(), reason="compiled reference not built")
+def test_weight_ops_on_a_transfer_compound_against_reference():
+    """Decay, clip and column reset of a Tiki-Taka tile (TransferRPUDevice with a fully hidden fast
+    tile, src/rpucuda/rpu_transfer_device.cpp:612-651): decay and clip act on the fast tile with
+    device 0 and on the visible weights with device 1, the reset on the fast tile only."""
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(21)
+    x_size, d_size, m = 48, 36, 24
     p = H.training_params(noise=False, pulse_det=True)
-    t = _tile(p._config(8, 6, H.transfer_device(noise=False), seed=3))
-    with pytest.raises(RuntimeError, match="compound"):
-        t.decay_weights()
+    dp = H.transfer_device(noise=False, det=True, transfer_every=2.0, units_in_mbatch=True,
+                           n_reads=1, transfer_lr=1.0)
+    for sub in dp._vec_par:
+        sub.lifetime, sub.lifetime_dtod = 30.0, 0.2
+        sub.reset, sub.reset_dtod, sub.reset_std = 0.02, 0.1, 0.0
+    cfg = p._config(x_size, d_size, dp, seed=9)
+    t = _tile(cfg)
+    rt = ref.RefTile(cfg)
+    names = t.get_hidden_parameter_names()
+    assert np.array_equal(t.get_hidden_parameters().numpy(), rt.get_hidden_parameters())
+    ia = names.index("hidden_weights_0")
+    W0 = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W0))
+    rt.set_weights(W0)
+    t.set_learning_rate(0.05)
+    rt.set_learning_rate(0.05)
+    for _ in range(3):
+        X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        Dm = rng.normal(0, 0.05, (m, d_size)).astype(np.float32)
+        t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+        rt.update(X, Dm)
+
+    def same(what):
+        a, a_r = t.get_hidden_parameters().numpy()[ia], rt.get_hidden_parameters()[ia]
+        c, c_r = t.get_weights().numpy(), rt.get_weights()
+        assert np.abs(a - a_r).max() <= 1e-6, what
+        assert np.abs(c - c_r).max() <= 1e-6, what
+        return a, c
+
+    a0, c0 = same("after the updates")
+    assert np.abs(a0).max() > 0
+    t.decay_weights(0.7)
+    rt.decay_weights(0.7)
+    a1, c1 = same("decay")
+    assert np.abs(a1 - a0).max() > 1e-4 and np.abs(c1 - c0).max() > 1e-4
+    wc = D.WeightClipParameter()
+    wc.type, wc.fixed_value = D.WeightClipType.FixedValue, 0.1
+    t.clip_weights(wc)
+    rt.clip_weights(int(wc.type), 0.1)
+    a2, c2 = same("clip")
+    assert np.abs(c2).max() <= 0.1 + 1e-6 and np.abs(a2).max() <= 0.1 + 1e-6
+    t.reset_columns(3, 5, 1.0)
+    rt.reset_columns(3, 5, 1.0)
+    a3, c3 = same("reset of the fast tile's columns")
+    assert np.array_equal(c3, c2) and np.abs(a3[:, 3:8] - a2[:, 3:8]).max() > 0
 
 
 def _drift(dp, **kw):
