@@ -166,22 +166,36 @@ std::vector<std::string> deviceNames(int kind) {
   return n;
 }
 
-void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_size, HostRNG &rng,
-                    DeviceStore &ds) {
-  ds.kind = kind;
-  ds.dw_min = par.dw_min;
-  ds.dw_min_std = par.dw_min_std;
+// calcWeightGranularity of the device kinds: the weight change the pulse-count learning rate is
+// measured in (rpu_pulsed_device.h: dw_min; rpu_expstep_device.h:43-55; rpu_powstep_device.h:33;
+// rpu_piecewisestep_device.h:34-39)
+float weightGranularity(const ab200_device_params &par, int kind) {
   if (kind == AB200_DEVICE_EXP_STEP) {
-    ds.es0 = make_float4(par.es_a, par.es_b, par.es_A_up, par.es_A_down);
-    ds.es1 = make_float4(par.es_gamma_up, par.es_gamma_down, par.dw_min_std_add, par.dw_min_std_slope);
-    // ExpStepRPUDeviceMetaParameter::calcWeightGranularity (rpu_expstep_device.h:43-55): the step
-    // at w = 0 (the reference averages the down step with itself)
+    // the step at w = 0 (the reference averages the down step with itself)
     const float down_bias = par.up_down > 0.0f ? -par.up_down : 0.0f;
     const float scale_down = (down_bias + 1.0f) * par.dw_min;
     const float z = par.es_b;
     const float dw_down = scale_down * fmaxf(1.0f - par.es_A_down * expf(par.es_gamma_down * (-z)), 0.0f);
     const float g = fmaxf((dw_down + dw_down) / 2.0f, 0.0f);
-    ds.dw_min = g > 0.0f ? g : par.dw_min;
+    return g > 0.0f ? g : par.dw_min;
+  }
+  if (kind == AB200_DEVICE_PIECEWISE_STEP && par.pw_n > 0 && par.pw_n <= AB200_PIECEWISE_MAX_NODES) {
+    return par.dw_min * par.pw_up[par.pw_n / 2];
+  }
+  if (kind == AB200_DEVICE_POW_STEP) {
+    return par.dw_min * powf(0.5f, par.ps_gamma);
+  }
+  return par.dw_min;
+}
+
+void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_size, HostRNG &rng,
+                    DeviceStore &ds) {
+  ds.kind = kind;
+  ds.dw_min = weightGranularity(par, kind);
+  ds.dw_min_std = par.dw_min_std;
+  if (kind == AB200_DEVICE_EXP_STEP) {
+    ds.es0 = make_float4(par.es_a, par.es_b, par.es_A_up, par.es_A_down);
+    ds.es1 = make_float4(par.es_gamma_up, par.es_gamma_down, par.dw_min_std_add, par.dw_min_std_slope);
   }
   if (kind == AB200_DEVICE_PIECEWISE_STEP) {
     // PiecewiseStepRPUDeviceMetaParameter::initialize / calcWeightGranularity
@@ -195,11 +209,6 @@ void populateDevice(const ab200_device_params &par, int kind, int x_size, int d_
     ds.pw_n = par.pw_n;
     ds.pw_host.assign(par.pw_up, par.pw_up + par.pw_n);
     ds.pw_host.insert(ds.pw_host.end(), par.pw_down, par.pw_down + par.pw_n);
-    ds.dw_min = par.dw_min * par.pw_up[par.pw_n / 2];
-  }
-  if (kind == AB200_DEVICE_POW_STEP) {
-    // PowStepRPUDeviceMetaParameter::calcWeightGranularity (rpu_powstep_device.h:33)
-    ds.dw_min = par.dw_min * powf(0.5f, par.ps_gamma);
   }
   ds.mult_noise = kind == AB200_DEVICE_SOFT_BOUNDS_REFERENCE ? par.mult_noise : par.ls_mult_noise;
   ds.names = deviceNames(kind);
@@ -1005,8 +1014,9 @@ void Tile::setHidden(const float *in) {
       acc += (fabsf(sup[e]) + fabsf(sdown[e])) / 2.0f;
     }
     float est = (float)(acc / (double)size);
-    if (fabsf(est - dev_[k].dw_min) / dev_[k].dw_min > 2.0f * cfg_.device[k].dw_min_dtod) {
-      dev_[k].dw_min = est;
+    if (fabsf(est - cfg_.device[k].dw_min) / cfg_.device[k].dw_min > 2.0f * cfg_.device[k].dw_min_dtod) {
+      cfg_.device[k].dw_min = est; // the parameter itself, then the granularity derived from it
+      dev_[k].dw_min = weightGranularity(cfg_.device[k], dev_[k].kind);
     }
     if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
       if (device_ >= 0 && k == 0) {

@@ -2,6 +2,7 @@
 
     make -C oracle && python tests/golden/make_golden.py            # everything
     make -C oracle && python tests/golden/make_golden.py indexed    # only indexed_conv.npz
+    make -C oracle && python tests/golden/make_golden.py extensions # only extensions_det.npz
 
 Every array is an input or an output of the unmodified reference CPU tile
 (RPU::RPUPulsed<float>) for the configurations built by tests/helpers.py; nothing here comes from
@@ -165,7 +166,109 @@ def indexed_conv_case(seed):
                 lr=np.float32(lr), out_bound=np.float32(2.0))
 
 
+LINE_ALL = dict(ir_drop=1.0, ir_drop_g_ratio=3000.0, v_offset_std=0.05, r_series=0.02,
+                out_nonlinearity=0.1, out_nonlinearity_std=0.2)
+
+
+def extensions_case(seed):
+    """Deterministic cases of the rows beyond the first tile: PiecewiseStep device, the
+    non-idealities of the output lines (with the per-line values the reference drew), power-law
+    drift, weight modifiers (read through a perfect-IO forward of the identity), the running-average
+    noise management and the NoneWithDevice update."""
+    from aihwkit_b200.rpu_base import devices as D
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(seed)
+    out = {}
+    # PiecewiseStep
+    x_size, d_size, m = 40, 24, 9
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.piecewise_device(False)
+    t = ref.RefTile(p._config(x_size, d_size, dp, seed=seed))
+    t.set_weights(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32))
+    x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    d = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+    out.update(pw_w0=t.get_weights(), pw_x=x, pw_d=d, pw_hidden=t.get_hidden_parameters())
+    t.set_learning_rate(0.01)
+    t.update(x, d)
+    out["pw_w1"] = t.get_weights()
+    # non-idealities of the output lines
+    x_size, d_size, m = 60, 36, 12
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+    for io in (p.forward_io, p.backward_io):
+        for k, v in LINE_ALL.items():
+            setattr(io, k, v)
+    t = ref.RefTile(p._config(x_size, d_size, H.device("cs", False), seed=seed))
+    t.set_weights(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32))
+    x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    d = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+    out.update(line_w0=t.get_weights(), line_x=x, line_d=d, line_y=t.forward(x), line_g=t.backward(d),
+               line_voff_f=t.get_io_vector(False, 0, d_size), line_nl_f=t.get_io_vector(False, 1, d_size),
+               line_voff_b=t.get_io_vector(True, 0, x_size), line_nl_b=t.get_io_vector(True, 1, x_size))
+    # drift
+    x_size, d_size = 30, 20
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.device("cs", False)
+    dp.drift.nu, dp.drift.nu_dtod, dp.drift.nu_k, dp.drift.g_offset, dp.drift.wg_ratio = 0.1, 0.3, 0.05, 0.2, 0.6
+    t = ref.RefTile(p._config(x_size, d_size, dp, seed=seed))
+    w = rng.uniform(0.05, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(w)
+    out.update(drift_w0=t.get_weights(), drift_hidden=t.get_hidden_parameters())
+    t.drift_weights(5.0)
+    out["drift_w1"] = t.get_weights()
+    w2 = t.get_weights().copy()
+    w2[:5, :7] = 0.25
+    t.set_weights(w2)
+    out["drift_w2"] = t.get_weights()
+    t.drift_weights(40.0)
+    out["drift_w3"] = t.get_weights()
+    # weight modifiers on a perfect-IO tile
+    x_size, d_size = 24, 16
+    pp = D.AnalogTileParameter()
+    pp.forward_io.is_perfect = True
+    pp.backward_io.is_perfect = True
+    pp.update.pulse_type = D.PulseType.None_
+    t = ref.RefTile(pp._config(x_size, d_size, D.IdealResistiveDeviceParameter(), seed=seed))
+    w = rng.normal(0, 0.3, (d_size, x_size)).astype(np.float32)
+    t.set_weights(w)
+    eye = np.eye(x_size, dtype=np.float32)
+    out["mod_w0"] = w
+    for name, kw in (("disc", dict(type=T.WeightModifierType.Discretize, res=0.1)),
+                     ("dorefa", dict(type=T.WeightModifierType.DoReFa, res=0.08, dorefa_clip=0.6))):
+        wm = T.WeightModifierParameter()
+        for k, v in kw.items():
+            setattr(wm, k, v)
+        t.modify_weights(wm)
+        out["mod_" + name] = t.forward(eye).T.copy()
+    # running-average noise management, two calls
+    x_size, d_size, m = 32, 20, 15
+    p = H.training_params(noise=False, pulse_det=True, bm=False)
+    p.forward_io.noise_management = D.NoiseManagementType.AverageAbsMax
+    p.forward_io.nm_decay = 0.1
+    t = ref.RefTile(p._config(x_size, d_size, H.device("cs", False), seed=seed))
+    t.set_weights(rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32))
+    xs = np.stack([(rng.uniform(-1, 1, (m, x_size)) * s).astype(np.float32) for s in (1.0, 0.4)])
+    out.update(nm_w0=t.get_weights(), nm_xs=xs, nm_ys=np.stack([t.forward(xs[0]), t.forward(xs[1])]))
+    # NoneWithDevice
+    x_size, d_size, m = 30, 20, 16
+    p = H.training_params(noise=False, pulse_det=True)
+    p.update.pulse_type = D.PulseType.NoneWithDevice
+    t = ref.RefTile(p._config(x_size, d_size, H.device("cs", False, w_max=0.3, w_min=-0.3), seed=seed))
+    t.set_weights(rng.uniform(-0.2, 0.2, (d_size, x_size)).astype(np.float32))
+    x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    d = (rng.normal(0, 0.5, (m, d_size))).astype(np.float32)
+    out.update(nwd_w0=t.get_weights(), nwd_x=x, nwd_d=d, nwd_hidden=t.get_hidden_parameters())
+    t.set_learning_rate(0.2)
+    t.update(x, d)
+    out["nwd_w1"] = t.get_weights()
+    return out
+
+
 def main():
+    if sys.argv[1:] == ["extensions"]:
+        np.savez_compressed(os.path.join(HERE, "extensions_det.npz"), **extensions_case(12))
+        print("wrote extensions_det.npz")
+        return
     if sys.argv[1:] == ["indexed"]:
         np.savez_compressed(os.path.join(HERE, "indexed_conv.npz"), **indexed_conv_case(9))
         print("wrote indexed_conv.npz")
@@ -182,6 +285,7 @@ def main():
         np.savez_compressed(os.path.join(HERE, f"noisy_update_{kind}.npz"), **noisy_update_case(kind, 7))
     np.savez_compressed(os.path.join(HERE, "transfer_det.npz"), **transfer_case(8))
     np.savez_compressed(os.path.join(HERE, "indexed_conv.npz"), **indexed_conv_case(9))
+    np.savez_compressed(os.path.join(HERE, "extensions_det.npz"), **extensions_case(12))
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 

@@ -118,3 +118,102 @@ def test_transfer_sequence_against_reference():
         t.update(_gpu(g["xs"][k]), _gpu(g["ds"][k]))
         assert np.abs(t.get_hidden_parameters().numpy()[ia] - g["a"][k]).max() <= 1e-6, k
         assert np.abs(t.get_weights().numpy() - g["ws"][k]).max() <= 1e-6, k
+
+
+def test_extensions_against_reference_vectors():
+    """PiecewiseStep update, non-idealities of the output lines, power-law drift, weight modifiers,
+    running-average noise management and the NoneWithDevice update against vectors recorded from
+    the compiled reference (tests/golden/make_golden.py extensions_case)."""
+    from aihwkit_b200.rpu_base import devices as D
+    from aihwkit_b200.rpu_base import tiles as T
+    from tests.golden.make_golden import LINE_ALL  # the settings the vectors were made with
+
+    g = np.load(os.path.join(GOLD, "extensions_det.npz"))
+
+    # PiecewiseStep
+    d_size, x_size = g["pw_w0"].shape
+    p = H.training_params(noise=False, pulse_det=True)
+    t = T.AnalogTile(p._config(x_size, d_size, H.piecewise_device(False), seed=1), cuda_device=0)
+    t.set_hidden_parameters(torch.from_numpy(g["pw_hidden"]))
+    t.set_weights(torch.from_numpy(g["pw_w0"]))
+    t.set_learning_rate(0.01)
+    t.update(_gpu(g["pw_x"]), _gpu(g["pw_d"]))
+    assert np.abs(t.get_weights().numpy() - g["pw_w1"]).max() <= 1e-6
+    assert np.abs(g["pw_w1"] - g["pw_w0"]).max() > 1e-3
+
+    # output-line non-idealities, bound management with out_bound 2
+    d_size, x_size = g["line_w0"].shape
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+    for io in (p.forward_io, p.backward_io):
+        for k, v in LINE_ALL.items():
+            setattr(io, k, v)
+    t = T.AnalogTile(p._config(x_size, d_size, H.device("cs", False), seed=1), cuda_device=0)
+    t.set_weights(torch.from_numpy(g["line_w0"]))
+    for backward, which, key in ((False, 0, "line_voff_f"), (False, 1, "line_nl_f"),
+                                 (True, 0, "line_voff_b"), (True, 1, "line_nl_b")):
+        t.set_io_vector(backward, which, torch.from_numpy(g[key]))
+    y = t.forward(_gpu(g["line_x"])).cpu().numpy()
+    lsb = (2.0 * 2.0 / 510.0) * np.abs(g["line_x"]).max(axis=1, keepdims=True) * t.last_bm_stats()[1]
+    frac, worst = H.lsb_report(y, g["line_y"], lsb)
+    assert frac <= 5e-3 and worst <= 1.001, (frac, worst)
+    gb = t.backward(_gpu(g["line_d"])).cpu().numpy()
+    frac, worst = H.lsb_report(gb, g["line_g"], (2.0 * 12.0 / 510.0) * np.abs(g["line_d"]).max(axis=1, keepdims=True))
+    assert frac <= 5e-3 and worst <= 1.001, (frac, worst)
+
+    # drift
+    d_size, x_size = g["drift_w0"].shape
+    dp = H.device("cs", False)
+    dp.drift.nu, dp.drift.nu_dtod, dp.drift.nu_k, dp.drift.g_offset, dp.drift.wg_ratio = 0.1, 0.3, 0.05, 0.2, 0.6
+    p = H.training_params(noise=False, pulse_det=True)
+    t = T.AnalogTile(p._config(x_size, d_size, dp, seed=1), cuda_device=0)
+    t.set_hidden_parameters(torch.from_numpy(g["drift_hidden"]))
+    t.set_weights(torch.from_numpy(g["drift_w0"]))
+    t.drift_weights(5.0)
+    assert np.abs(t.get_weights().numpy() - g["drift_w1"]).max() <= 2e-6
+    t.set_weights(torch.from_numpy(g["drift_w2"]))
+    t.drift_weights(40.0)
+    assert np.abs(t.get_weights().numpy() - g["drift_w3"]).max() <= 2e-6
+    assert np.abs(g["drift_w3"] - g["drift_w2"]).max() > 0.01
+
+    # weight modifiers
+    d_size, x_size = g["mod_w0"].shape
+    pp = D.AnalogTileParameter()
+    pp.forward_io.is_perfect = True
+    pp.backward_io.is_perfect = True
+    pp.update.pulse_type = D.PulseType.None_
+    t = T.AnalogTile(pp._config(x_size, d_size, D.IdealResistiveDeviceParameter(), seed=1), cuda_device=0)
+    t.set_weights(torch.from_numpy(g["mod_w0"]))
+    eye = torch.eye(x_size, device="cuda")
+    for name, kw in (("disc", dict(type=T.WeightModifierType.Discretize, res=0.1)),
+                     ("dorefa", dict(type=T.WeightModifierType.DoReFa, res=0.08, dorefa_clip=0.6))):
+        wm = T.WeightModifierParameter()
+        for k, v in kw.items():
+            setattr(wm, k, v)
+        t.modify_weights(wm)
+        fb = t.forward(eye).cpu().numpy().T
+        assert (np.abs(fb - g["mod_" + name]) > 1e-6).mean() <= 0.005, name
+
+    # running-average noise management over two calls
+    d_size, x_size = g["nm_w0"].shape
+    p = H.training_params(noise=False, pulse_det=True, bm=False)
+    p.forward_io.noise_management = D.NoiseManagementType.AverageAbsMax
+    p.forward_io.nm_decay = 0.1
+    t = T.AnalogTile(p._config(x_size, d_size, H.device("cs", False), seed=1), cuda_device=0)
+    t.set_weights(torch.from_numpy(g["nm_w0"]))
+    for k in range(2):
+        y = t.forward(_gpu(g["nm_xs"][k])).cpu().numpy()
+        lsb = (2.0 * 12.0 / 510.0) * np.abs(g["nm_xs"][0]).max()
+        frac, worst = H.lsb_report(y, g["nm_ys"][k], np.full((y.shape[0], 1), lsb))
+        assert frac <= 5e-3 and worst <= 1.001, (k, frac, worst)
+
+    # NoneWithDevice
+    d_size, x_size = g["nwd_w0"].shape
+    p = H.training_params(noise=False, pulse_det=True)
+    p.update.pulse_type = D.PulseType.NoneWithDevice
+    t = T.AnalogTile(p._config(x_size, d_size, H.device("cs", False, w_max=0.3, w_min=-0.3), seed=1),
+                     cuda_device=0)
+    t.set_hidden_parameters(torch.from_numpy(g["nwd_hidden"]))
+    t.set_weights(torch.from_numpy(g["nwd_w0"]))
+    t.set_learning_rate(0.2)
+    t.update(_gpu(g["nwd_x"]), _gpu(g["nwd_d"]))
+    assert np.abs(t.get_weights().numpy() - g["nwd_w1"]).max() <= 2e-6
