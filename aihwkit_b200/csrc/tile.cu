@@ -27,6 +27,16 @@ static float checkRes(float res) {
   return r > 1.0f ? 1.0f / r : r;
 }
 
+// AB200_STREAM_LISTS=0: the streaming update walks the bitmaps of the transposed x words instead of
+// compacted lists (the earlier form, kept for comparison)
+bool streamListsEnabled() {
+  static const bool on = [] {
+    const char *e = getenv("AB200_STREAM_LISTS");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 bool pdlEnabled() {
   static const bool on = [] {
     const char *e = getenv("AB200_PDL");
@@ -514,6 +524,9 @@ Tile::~Tile() {
     cudaFree(drift_w0_);
     cudaFree(drift_t_);
     cudaFree(drift_nu_);
+    cudaFree(xls_);
+    cudaFree(xlx_);
+    cudaFree(xloff_);
     cudaFree(nm_state_);
     cudaFree(f_lt_.voff);
     cudaFree(f_lt_.nl);
@@ -794,10 +807,18 @@ void Tile::ensureStreamScratch(int m_pad) {
   AB200_CUDA(cudaDeviceSynchronize());
   cudaFree(xwt_);
   cudaFree(xnzt_);
-  xwt_ = xnzt_ = nullptr;
+  cudaFree(xls_);
+  cudaFree(xlx_);
+  cudaFree(xloff_);
+  xwt_ = xnzt_ = xls_ = xlx_ = xloff_ = nullptr;
   const size_t cap = need + need / 8;
   AB200_CUDA(cudaMalloc(&xwt_, cap * sizeof(uint32_t)));
   AB200_CUDA(cudaMalloc(&xnzt_, (cap / 32 + x_size_) * sizeof(uint32_t)));
+  if (streamListsEnabled()) {
+    AB200_CUDA(cudaMalloc(&xls_, cap * sizeof(uint32_t)));
+    AB200_CUDA(cudaMalloc(&xlx_, cap * sizeof(uint32_t)));
+    AB200_CUDA(cudaMalloc(&xloff_, (cap / 32 + 2 * (size_t)x_size_) * sizeof(uint32_t)));
+  }
   xwt_words_ = cap;
 }
 
@@ -1463,10 +1484,13 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
   if (stream_upd) {
     ensureStreamScratch(m_pad);
     launchPulseTranspose(u, xwt_, xnzt_, m_pad, s);
+    if (xls_) {
+      launchPulseCompact(u, xwt_, xnzt_, m_pad, xls_, xlx_, xloff_, s);
+    }
   }
   auto applyRange = [&](UpdateProblem &r) {
     if (stream_upd) {
-      launchPulsedUpdateStream(r, xwt_, xnzt_, m_pad, s);
+      launchPulsedUpdateStream(r, xwt_, xnzt_, m_pad, s, xls_, xlx_, xloff_);
     } else {
       launchPulsedUpdate(r, s);
     }

@@ -181,17 +181,24 @@ struct UpdateProblem {
 };
 
 void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream);
-// Large batches of stochastic pulse trains: the update streams over the samples of an x-line
-// (transposed x words + their bitmaps) instead of staging blocks of samples per weight tile.
-constexpr int kStreamUpdateMinBatch = 1024;
+// Stochastic pulse trains: the update streams over the non-empty samples of an x-line (transposed
+// x words, their bitmaps and compacted lists) instead of staging blocks of samples per weight
+// tile. Measured faster from a batch of 64 (256 x 256 tile) upwards; below one bitmap word of
+// samples the three extra launches are not worth it.
+constexpr int kStreamUpdateMinBatch = 32;
 bool streamUpdateEligible(const UpdateProblem &p);
 // kernel selection of the pulsed update: 0 = automatic, 1 = always the staged kernel, 2 = the
 // streaming kernel whenever the pulse type allows it (any batch size)
 void setUpdatePath(int mode);
 void launchPulseTranspose(const UpdateProblem &p, uint32_t *xwT, uint32_t *xnzT, int m_pad,
                           cudaStream_t stream);
+// compacted (sample, word) lists of every x-line, from the transposed words and their bitmaps
+void launchPulseCompact(const UpdateProblem &p, const uint32_t *xwT, const uint32_t *xnzT, int m_pad,
+                        uint32_t *list_s, uint32_t *list_x, uint32_t *list_off, cudaStream_t stream);
+// with the lists the kernel reads them; without (null) it walks the bitmaps
 void launchPulsedUpdateStream(const UpdateProblem &p, const uint32_t *xwT, const uint32_t *xnzT,
-                              int m_pad, cudaStream_t stream);
+                              int m_pad, cudaStream_t stream, const uint32_t *list_s = nullptr,
+                              const uint32_t *list_x = nullptr, const uint32_t *list_off = nullptr);
 void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream);
 void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream);
 void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream,
@@ -362,6 +369,7 @@ private:
   // backward (x_size), drawn once per tile (rpu_forward_backward_pass.cpp:306-313)
   float *f_onv_ = nullptr, *b_onv_ = nullptr;
   float *nm_state_ = nullptr;
+  uint32_t *xls_ = nullptr, *xlx_ = nullptr, *xloff_ = nullptr; // compacted x lists (stream update)
   // per-line tables of a direction (MVParameter, rpu_forward_backward_pass.h:14-22)
   struct LineTables {
     std::vector<float> h_voff, h_nl, h_onv;

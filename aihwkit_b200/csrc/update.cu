@@ -683,7 +683,68 @@ struct StreamUpdate {
   const uint32_t *xwT; // [x_size][m_pad]
   const uint32_t *xnzT; // [x_size][m_pad / 32]
   int m_pad;
+  // compacted form of the same: per x-line the samples whose word is not empty, in order, and
+  // their words with the sign bit flipped ([x_size][m_pad] each), and the number of entries before
+  // every bitmap word ([x_size][m_pad / 32 + 1])
+  const uint32_t *list_s, *list_x, *list_off;
 };
+
+// Compaction of the transposed x words of a line: the streaming kernel then reads (sample, word)
+// pairs instead of walking a bitmap. One warp per line; every bitmap word is handled by the whole
+// warp (lane = sample), so reads and writes are contiguous.
+__global__ void __launch_bounds__(256)
+    pulseCompactKernel(const uint32_t *wordsT, const uint32_t *nzT, int n_lines, int m_pad,
+                       uint32_t *list_s, uint32_t *list_x, uint32_t *list_off) {
+  pdlEnter();
+  const int line = (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
+  if (line >= n_lines) {
+    return;
+  }
+  const int nw = m_pad >> 5;
+  const uint32_t *nz = nzT + (long long)line * nw;
+  const uint32_t *xw = wordsT + (long long)line * m_pad;
+  uint32_t *ls = list_s + (long long)line * m_pad, *lx = list_x + (long long)line * m_pad;
+  uint32_t *off = list_off + (long long)line * (nw + 1);
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  uint32_t run = 0;
+  for (int w0 = 0; w0 < nw; w0 += 32) {
+    const int wd = w0 + lane;
+    const uint32_t bits = wd < nw ? nz[wd] : 0u;
+    const uint32_t c = (uint32_t)__popc(bits);
+    uint32_t incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) {
+        incl += v;
+      }
+    }
+    const uint32_t excl = run + incl - c;
+    if (wd < nw) {
+      off[wd] = excl;
+    }
+    const int nj = nw - w0 < 32 ? nw - w0 : 32;
+    for (int j = 0; j < nj; j++) {
+      const uint32_t bj = __shfl_sync(0xffffffffu, bits, j);
+      if (bj == 0u) {
+        continue;
+      }
+      const uint32_t basej = __shfl_sync(0xffffffffu, excl, j);
+      const int smp = (w0 + j) * 32 + lane;
+      const uint32_t xv = xw[smp];
+      if ((bj >> lane) & 1u) {
+        const uint32_t pos = basej + (uint32_t)__popc(bj & lt_mask);
+        ls[pos] = (uint32_t)smp;
+        lx[pos] = xv ^ 1u; // (x ^ d) & 1 is then the direction bit of an event
+      }
+    }
+    run += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) {
+    off[nw] = run;
+  }
+}
 
 template <int KIND, bool NOISY>
 __global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p, StreamUpdate st) {
@@ -826,10 +887,149 @@ __global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p,
   }
 }
 
+// The same update reading the compacted lists: per walked sample two shuffles (sample, x word), the
+// d word, AND, and - for the lanes with coincidences - one byte pushed into the lane's column of a
+// queue in shared memory. The queues are drained together when one is nearly full, oldest event
+// first, with the pulse application of the kernel above.
+constexpr int USL_QCAP = 24; // events per lane between two drains
+
+template <int KIND, bool NOISY>
+__global__ void __launch_bounds__(256) pulsedUpdateListKernel(UpdateProblem p, StreamUpdate st) {
+  pdlEnter();
+  __shared__ float pool[8][USP_POOL];
+  __shared__ uint8_t evq[USL_QCAP][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_dblk = (p.d_size + 31) >> 5;
+  const long long task = (long long)blockIdx.x * 8 + warp;
+  if (task >= (long long)n_dblk * p.x_size) {
+    return;
+  }
+  const int j = (int)(task / n_dblk);
+  const int i = (int)(task - (long long)j * n_dblk) * 32 + lane;
+  const bool i_ok = i < p.d_size;
+  const long long idx = (long long)j * p.d_size + (i_ok ? i : 0);
+  float w = 0.0f;
+  float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+  float2 e = make_float2(0.f, 0.f);
+  if (i_ok) {
+    w = p.w[idx];
+    q = p.par4[idx];
+    if (KIND != AB200_DEVICE_CONSTANT_STEP && KIND != AB200_DEVICE_EXP_STEP &&
+        KIND != AB200_DEVICE_PIECEWISE_STEP) {
+      e = p.par2[idx];
+    }
+  }
+  const float w_in = w;
+  const float std = p.dw_min_std;
+  int cnt = 0;
+  int pool_pos = USP_POOL; // empty
+  uint32_t refills = 0;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+
+  auto drain = [&]() {
+    const int rounds = __reduce_max_sync(0xffffffffu, cnt);
+    for (int r = 0; r < rounds; r++) {
+      int n = 0;
+      bool down = false;
+      if (r < cnt) {
+        const uint32_t ev = evq[r][threadIdx.x];
+        n = (int)(ev >> 1);
+        down = (ev & 1u) != 0u;
+      }
+      for (int k = 0; __any_sync(0xffffffffu, k < n); k++) {
+        const bool act = k < n;
+        float xi = 0.0f;
+        if (NOISY) {
+          const uint32_t takers = __ballot_sync(0xffffffffu, act);
+          if (pool_pos + __popc(takers) > USP_POOL) {
+            // all lanes refill together; what is left of the old pool is dropped
+            float z[8];
+            gauss8(p.key, (uint64_t)(task * 32 + lane) | ((uint64_t)refills << 40), p.call, TAG_DEVICE, z);
+            __syncwarp();
+#pragma unroll
+            for (int rr = 0; rr < 8; rr++) {
+              pool[warp][rr * 32 + lane] = z[rr];
+            }
+            __syncwarp();
+            refills++;
+            pool_pos = 0;
+          }
+          if (act) {
+            xi = std * pool[warp][pool_pos + __popc(takers & lt_mask)];
+          }
+          pool_pos += __popc(takers);
+        }
+        if (act) {
+          w = pulseOnce<KIND>(w, down, q, e, xi, p.mult_noise, p.es0, p.es1, p.pw, p.pw_n);
+        }
+      }
+    }
+    cnt = 0;
+  };
+
+  const int nw = st.m_pad >> 5;
+  const uint32_t *off = st.list_off + (long long)j * (nw + 1);
+  const uint32_t *nz_line = st.xnzT + (long long)j * nw;
+  const uint32_t *ls = st.list_s + (long long)j * st.m_pad;
+  const uint32_t *lx = st.list_x + (long long)j * st.m_pad;
+  // entries of the samples in [s_begin, s_end)
+  auto entriesBefore = [&](int smp) -> uint32_t {
+    const int wd = smp >> 5;
+    if (wd >= nw) {
+      return off[nw];
+    }
+    return off[wd] + (uint32_t)__popc(nz_line[wd] & ((1u << (smp & 31)) - 1u));
+  };
+  const uint32_t k_begin = entriesBefore(p.s_begin), k_end = entriesBefore(p.s_end);
+  for (uint32_t k = k_begin; k < k_end; k += 32) {
+    const uint32_t kk = k + lane;
+    const uint32_t my_s = kk < k_end ? ls[kk] : 0u;
+    const uint32_t my_x = kk < k_end ? lx[kk] : 0u;
+    const int n_in = (int)(k_end - k < 32u ? k_end - k : 32u);
+    for (int t = 0; t < n_in; t += 4) {
+      // four samples at a time, so that their d words are in flight together
+      uint32_t sv[4], xv[4], dwv[4];
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        sv[c] = __shfl_sync(0xffffffffu, my_s, (t + c) & 31);
+        xv[c] = __shfl_sync(0xffffffffu, my_x, (t + c) & 31);
+      }
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        dwv[c] = (t + c < n_in && i_ok) ? p.dw[(long long)sv[c] * p.d_size + i] : 0u;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        const uint32_t both = xv[c] & dwv[c] & ~1u;
+        if (both != 0u) {
+          // equal line signs = decrease (rpu_weight_updater.cpp:246-268); the x sign is stored flipped
+          evq[cnt][threadIdx.x] = (uint8_t)(((uint32_t)__popc(both) << 1) | ((xv[c] ^ dwv[c]) & 1u));
+          cnt++;
+        }
+      }
+      if (__any_sync(0xffffffffu, cnt > USL_QCAP - 4)) {
+        drain();
+      }
+    }
+  }
+  drain();
+  if (i_ok && w != w_in) {
+    p.w[idx] = w;
+  }
+}
+
 template <int KIND>
 static void launchStreamKind(const UpdateProblem &p, const StreamUpdate &st, cudaStream_t stream) {
   const long long tasks = (long long)((p.d_size + 31) / 32) * p.x_size;
   const unsigned blocks = (unsigned)((tasks + 7) / 8);
+  if (st.list_s != nullptr) {
+    if (p.dw_min_std > 0.0f) {
+      AB200_CUDA(launchChained(pulsedUpdateListKernel<KIND, true>, dim3(blocks), dim3(256), 0, stream, p, st));
+    } else {
+      AB200_CUDA(launchChained(pulsedUpdateListKernel<KIND, false>, dim3(blocks), dim3(256), 0, stream, p, st));
+    }
+    return;
+  }
   if (p.dw_min_std > 0.0f) {
     AB200_CUDA(launchChained(pulsedUpdateStreamKernel<KIND, true>, dim3(blocks), dim3(256), 0, stream, p, st));
   } else {
@@ -867,13 +1067,23 @@ void launchPulseTranspose(const UpdateProblem &p0, uint32_t *xwT, uint32_t *xnzT
   AB200_LAUNCH_CHECK();
 }
 
+void launchPulseCompact(const UpdateProblem &p0, const uint32_t *xwT, const uint32_t *xnzT, int m_pad,
+                        uint32_t *list_s, uint32_t *list_x, uint32_t *list_off, cudaStream_t stream) {
+  const UpdateProblem p = inRows(p0);
+  const unsigned blocks = (unsigned)(((long long)p.x_size * 32 + 255) / 256);
+  AB200_CUDA(launchChained(pulseCompactKernel, dim3(blocks), dim3(256), 0, stream, xwT, xnzT, p.x_size, m_pad,
+                           list_s, list_x, list_off));
+  AB200_LAUNCH_CHECK();
+}
+
 void launchPulsedUpdateStream(const UpdateProblem &p0, const uint32_t *xwT, const uint32_t *xnzT,
-                              int m_pad, cudaStream_t stream) {
+                              int m_pad, cudaStream_t stream, const uint32_t *list_s,
+                              const uint32_t *list_x, const uint32_t *list_off) {
   const UpdateProblem p = inRows(p0);
   if (p.s_end <= p.s_begin) {
     return;
   }
-  StreamUpdate st{xwT, xnzT, m_pad};
+  StreamUpdate st{xwT, xnzT, m_pad, list_s, list_x, list_off};
   switch (p.kind) {
   case AB200_DEVICE_CONSTANT_STEP:
     launchStreamKind<AB200_DEVICE_CONSTANT_STEP>(p, st, stream);
