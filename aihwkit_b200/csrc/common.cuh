@@ -53,7 +53,6 @@ __device__ __forceinline__ void pdlEnter() {
 }
 #endif
 bool pdlEnabled();
-bool streamListsEnabled();
 template <typename... KArgs, typename... Args>
 inline cudaError_t launchChained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                  cudaStream_t stream, Args &&...args) {

@@ -27,16 +27,6 @@ static float checkRes(float res) {
   return r > 1.0f ? 1.0f / r : r;
 }
 
-// AB200_STREAM_LISTS=0: the streaming update walks the bitmaps of the transposed x words instead of
-// compacted lists (the earlier form, kept for comparison)
-bool streamListsEnabled() {
-  static const bool on = [] {
-    const char *e = getenv("AB200_STREAM_LISTS");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
-
 bool pdlEnabled() {
   static const bool on = [] {
     const char *e = getenv("AB200_PDL");
@@ -814,11 +804,9 @@ void Tile::ensureStreamScratch(int m_pad) {
   const size_t cap = need + need / 8;
   AB200_CUDA(cudaMalloc(&xwt_, cap * sizeof(uint32_t)));
   AB200_CUDA(cudaMalloc(&xnzt_, (cap / 32 + x_size_) * sizeof(uint32_t)));
-  if (streamListsEnabled()) {
-    AB200_CUDA(cudaMalloc(&xls_, cap * sizeof(uint32_t)));
-    AB200_CUDA(cudaMalloc(&xlx_, cap * sizeof(uint32_t)));
-    AB200_CUDA(cudaMalloc(&xloff_, (cap / 32 + 2 * (size_t)x_size_) * sizeof(uint32_t)));
-  }
+  AB200_CUDA(cudaMalloc(&xls_, cap * sizeof(uint32_t)));
+  AB200_CUDA(cudaMalloc(&xlx_, cap * sizeof(uint32_t)));
+  AB200_CUDA(cudaMalloc(&xloff_, (cap / 32 + 2 * (size_t)x_size_) * sizeof(uint32_t)));
   xwt_words_ = cap;
 }
 
@@ -1484,9 +1472,7 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
   if (stream_upd) {
     ensureStreamScratch(m_pad);
     launchPulseTranspose(u, xwt_, xnzt_, m_pad, s);
-    if (xls_) {
-      launchPulseCompact(u, xwt_, xnzt_, m_pad, xls_, xlx_, xloff_, s);
-    }
+    launchPulseCompact(u, xwt_, xnzt_, m_pad, xls_, xlx_, xloff_, s);
   }
   auto applyRange = [&](UpdateProblem &r) {
     if (stream_upd) {

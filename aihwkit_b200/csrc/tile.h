@@ -195,10 +195,9 @@ void launchPulseTranspose(const UpdateProblem &p, uint32_t *xwT, uint32_t *xnzT,
 // compacted (sample, word) lists of every x-line, from the transposed words and their bitmaps
 void launchPulseCompact(const UpdateProblem &p, const uint32_t *xwT, const uint32_t *xnzT, int m_pad,
                         uint32_t *list_s, uint32_t *list_x, uint32_t *list_off, cudaStream_t stream);
-// with the lists the kernel reads them; without (null) it walks the bitmaps
 void launchPulsedUpdateStream(const UpdateProblem &p, const uint32_t *xwT, const uint32_t *xnzT,
-                              int m_pad, cudaStream_t stream, const uint32_t *list_s = nullptr,
-                              const uint32_t *list_x = nullptr, const uint32_t *list_off = nullptr);
+                              int m_pad, cudaStream_t stream, const uint32_t *list_s,
+                              const uint32_t *list_x, const uint32_t *list_off);
 void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream);
 void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream);
 void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream,

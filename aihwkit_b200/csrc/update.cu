@@ -90,7 +90,8 @@ blAB(const UpEff &up, float lr, float dw_min, float xm, float dm, int &BL, float
 
 // One stochastic pulse train (generateCounts, sparse_bit_line_maker.cpp:200-238): BL Bernoulli
 // draws with probability pp; each draw compares pp against a 16-bit uniform, 8 draws per
-// Philox word pair.
+// Philox call. (A bit-serial comparison of all slots at once - one random word per bit of pp until
+// every slot is decided - needs fewer calls per lane but as many per warp, and measured slower.)
 __device__ __forceinline__ uint32_t
 pulseTrain(float pp, int BL, int seg, PhiloxKey key, uint32_t line, uint32_t sample, uint32_t call,
            uint32_t tag) {
@@ -102,7 +103,7 @@ pulseTrain(float pp, int BL, int seg, PhiloxKey key, uint32_t line, uint32_t sam
   int k = 0;
   for (int q = 0; q * 8 < nk; q++) {
     uint32_t r[4];
-    philox4x32_10(line, sample, call, tag + (uint32_t)(seg * 4 + q), key, r);
+    philox4x32<7>(line, sample, call, tag + (uint32_t)(seg * 4 + q), key, r);
 #pragma unroll
     for (int h = 0; h < 8; h++) {
       uint32_t u16 = (r[h >> 1] >> ((h & 1) * 16)) & 0xFFFFu;
@@ -635,22 +636,17 @@ static void launchUpdateInstance(const UpdateProblem &p, dim3 grid, cudaStream_t
 }
 
 // ---------------------------------------------------------------------------------------------
-// Large batches: the update as a stream over the samples of one x-line.
+// Stochastic pulse trains: the update as a stream over the samples of one x-line.
 //
 // A warp owns 32 consecutive d-lines of ONE x-line. The x-line's pulse words are the same for all
 // its lanes, so the walk over the samples is uniform across the warp: it visits the samples
-// where the x word is not empty (bitmap of the transposed x words), loads the 32 d words of that
-// sample with one coalesced access, and every lane counts its coincidences with AND + popc. No
-// lane waits for another lane's candidates. The rare expensive part - applying the pulses - is
-// decoupled: a lane pushes its events (count, direction) into a small queue in a register pair,
-// and the warp drains the queues together when one of them is full, so that most lanes have work
-// in every round of the drain. The Gaussians of the device noise come from a pool per warp in
-// shared memory that all lanes refill together and take from without gaps (ballot + prefix
-// count). Per-weight sample order, one pulse at a time with the clip after each, as in
-// rpu_weight_updater.cpp:243-291.
+// where the x word is not empty (a compacted list per x-line, built from the transposed x words
+// and their bitmaps), loads the 32 d words of that sample with one coalesced access, and every
+// lane counts its coincidences with AND + popc. No lane waits for another lane's candidates. The
+// rare expensive part - applying the pulses - is decoupled: a lane queues its events (count,
+// direction) and the warp applies the queued events together, so that most lanes have work in
+// every round.
 // ---------------------------------------------------------------------------------------------
-constexpr int USQ_BITS = 6;   // bits per queued event: 5 for the count (BL <= 31), 1 direction
-constexpr int USQ_SLOTS = 10; // events per 64-bit queue
 constexpr int USP_POOL = 256; // Gaussians per warp pool (eight per lane and refill)
 
 // xwT[line][sample] = xw[sample][line] for one 32 x 32 tile, plus the line's bitmap word of the
@@ -690,27 +686,40 @@ struct StreamUpdate {
 };
 
 // Compaction of the transposed x words of a line: the streaming kernel then reads (sample, word)
-// pairs instead of walking a bitmap. One warp per line; every bitmap word is handled by the whole
-// warp (lane = sample), so reads and writes are contiguous.
+// pairs instead of walking a bitmap. One warp per line and segment of UCS_SEG_WORDS bitmap words;
+// the warp first counts the entries of the line's earlier segments (a sum of popcounts over the
+// bitmap, which stays in L2), then handles its bitmap words one at a time with the whole warp
+// (lane = sample), so reads and writes are contiguous.
+constexpr int UCS_SEG_WORDS = 128; // 4096 samples per warp
+
 __global__ void __launch_bounds__(256)
     pulseCompactKernel(const uint32_t *wordsT, const uint32_t *nzT, int n_lines, int m_pad,
                        uint32_t *list_s, uint32_t *list_x, uint32_t *list_off) {
   pdlEnter();
-  const int line = (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5);
+  const int nw = m_pad >> 5;
+  const int n_seg = (nw + UCS_SEG_WORDS - 1) / UCS_SEG_WORDS;
+  const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (line >= n_lines) {
+  if (wid >= (long long)n_lines * n_seg) {
     return;
   }
-  const int nw = m_pad >> 5;
+  const int line = (int)(wid / n_seg), seg = (int)(wid - (long long)line * n_seg);
   const uint32_t *nz = nzT + (long long)line * nw;
   const uint32_t *xw = wordsT + (long long)line * m_pad;
   uint32_t *ls = list_s + (long long)line * m_pad, *lx = list_x + (long long)line * m_pad;
   uint32_t *off = list_off + (long long)line * (nw + 1);
   const uint32_t lt_mask = (1u << lane) - 1u;
+  const int w_begin = seg * UCS_SEG_WORDS;
+  const int w_end = w_begin + UCS_SEG_WORDS < nw ? w_begin + UCS_SEG_WORDS : nw;
+  // entries of this line before the segment
   uint32_t run = 0;
-  for (int w0 = 0; w0 < nw; w0 += 32) {
+  for (int wd = lane; wd < w_begin; wd += 32) {
+    run += (uint32_t)__popc(nz[wd]);
+  }
+  run = __reduce_add_sync(0xffffffffu, run);
+  for (int w0 = w_begin; w0 < w_end; w0 += 32) {
     const int wd = w0 + lane;
-    const uint32_t bits = wd < nw ? nz[wd] : 0u;
+    const uint32_t bits = wd < w_end ? nz[wd] : 0u;
     const uint32_t c = (uint32_t)__popc(bits);
     uint32_t incl = c;
 #pragma unroll
@@ -721,10 +730,10 @@ __global__ void __launch_bounds__(256)
       }
     }
     const uint32_t excl = run + incl - c;
-    if (wd < nw) {
+    if (wd < w_end) {
       off[wd] = excl;
     }
-    const int nj = nw - w0 < 32 ? nw - w0 : 32;
+    const int nj = w_end - w0 < 32 ? w_end - w0 : 32;
     for (int j = 0; j < nj; j++) {
       const uint32_t bj = __shfl_sync(0xffffffffu, bits, j);
       if (bj == 0u) {
@@ -741,156 +750,17 @@ __global__ void __launch_bounds__(256)
     }
     run += __shfl_sync(0xffffffffu, incl, 31);
   }
-  if (lane == 0) {
+  if (lane == 0 && w_end == nw) {
     off[nw] = run;
   }
 }
 
-template <int KIND, bool NOISY>
-__global__ void __launch_bounds__(256) pulsedUpdateStreamKernel(UpdateProblem p, StreamUpdate st) {
-  pdlEnter();
-  __shared__ float pool[8][USP_POOL];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_dblk = (p.d_size + 31) >> 5;
-  const long long task = (long long)blockIdx.x * 8 + warp;
-  if (task >= (long long)n_dblk * p.x_size) {
-    return;
-  }
-  const int j = (int)(task / n_dblk);
-  const int i = (int)(task - (long long)j * n_dblk) * 32 + lane;
-  const bool i_ok = i < p.d_size;
-  const long long idx = (long long)j * p.d_size + (i_ok ? i : 0);
-  float w = 0.0f;
-  float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
-  float2 e = make_float2(0.f, 0.f);
-  if (i_ok) {
-    w = p.w[idx];
-    q = p.par4[idx];
-    if (KIND != AB200_DEVICE_CONSTANT_STEP && KIND != AB200_DEVICE_EXP_STEP &&
-                KIND != AB200_DEVICE_PIECEWISE_STEP) {
-      e = p.par2[idx];
-    }
-  }
-  const float w_in = w;
-  const float std = p.dw_min_std;
-  unsigned long long queue = 0ull;
-  int cnt = 0;
-  int pool_pos = USP_POOL; // empty
-  uint32_t refills = 0;
-  const uint32_t lt_mask = (1u << lane) - 1u;
-
-  auto drain = [&]() {
-    while (__any_sync(0xffffffffu, cnt > 0)) {
-      int n = 0;
-      bool down = false;
-      if (cnt > 0) {
-        // the oldest event sits on top: pushes shift the queue up
-        cnt--;
-        const uint32_t ev = (uint32_t)(queue >> (cnt * USQ_BITS)) & ((1u << USQ_BITS) - 1u);
-        n = (int)(ev >> 1);
-        down = (ev & 1u) != 0u;
-      }
-      for (int k = 0; __any_sync(0xffffffffu, k < n); k++) {
-        const bool act = k < n;
-        float xi = 0.0f;
-        if (NOISY) {
-          const uint32_t takers = __ballot_sync(0xffffffffu, act);
-          if (pool_pos + __popc(takers) > USP_POOL) {
-            // all lanes refill together; what is left of the old pool is dropped
-            float z[8];
-            gauss8(p.key, (uint64_t)(task * 32 + lane) | ((uint64_t)refills << 40), p.call, TAG_DEVICE, z);
-            __syncwarp();
-#pragma unroll
-            for (int r = 0; r < 8; r++) {
-              pool[warp][r * 32 + lane] = z[r];
-            }
-            __syncwarp();
-            refills++;
-            pool_pos = 0;
-          }
-          if (act) {
-            xi = std * pool[warp][pool_pos + __popc(takers & lt_mask)];
-          }
-          pool_pos += __popc(takers);
-        }
-        if (act) {
-          w = pulseOnce<KIND>(w, down, q, e, xi, p.mult_noise, p.es0, p.es1, p.pw, p.pw_n);
-        }
-      }
-    }
-  };
-
-  const int nw = st.m_pad >> 5;
-  const int w_first = p.s_begin >> 5, w_last = (p.s_end - 1) >> 5;
-  const uint32_t *nz_line = st.xnzT + (long long)j * nw;
-  const uint32_t *x_line = st.xwT + (long long)j * st.m_pad;
-  uint32_t bits_next = nz_line[w_first];
-  for (int wd = w_first; wd <= w_last; wd++) {
-    uint32_t bits = bits_next;
-    if (wd < w_last) {
-      bits_next = nz_line[wd + 1];
-    }
-    // samples of this word that belong to [s_begin, s_end)
-    const int sb = wd << 5;
-    if (sb < p.s_begin) {
-      bits &= 0xffffffffu << (p.s_begin - sb);
-    }
-    if (sb + 32 > p.s_end) {
-      bits &= 0xffffffffu >> (sb + 32 - p.s_end);
-    }
-    if (bits == 0u) {
-      continue;
-    }
-    // the x words of these 32 samples: one coalesced load, handed out by shuffle; the sign bit is
-    // flipped here so that (x ^ d) & 1 is the direction bit of an event
-    const uint32_t xrow = x_line[sb + lane] ^ 1u;
-    while (bits != 0u) {
-      // up to four samples at a time, so that their d words are in flight together
-      int sidx[4];
-      uint32_t dwv[4];
-      int nb = 0;
-#pragma unroll
-      for (int t = 0; t < 4; t++) {
-        sidx[t] = -1;
-        if (bits != 0u) {
-          sidx[t] = __ffs(bits) - 1;
-          bits &= bits - 1u;
-          nb = t + 1;
-        }
-      }
-#pragma unroll
-      for (int t = 0; t < 4; t++) {
-        dwv[t] = (t < nb && i_ok) ? p.dw[(long long)(sb + sidx[t]) * p.d_size + i] : 0u;
-      }
-#pragma unroll
-      for (int t = 0; t < 4; t++) {
-        if (t < nb) {
-          const uint32_t xwv = __shfl_sync(0xffffffffu, xrow, sidx[t]);
-          const uint32_t both = xwv & dwv[t] & ~1u;
-          if (both != 0u) {
-            // equal line signs = decrease (rpu_weight_updater.cpp:246-268)
-            const uint32_t ev = ((uint32_t)__popc(both) << 1) | ((xwv ^ dwv[t]) & 1u);
-            queue = (queue << USQ_BITS) | ev;
-            cnt++;
-          }
-        }
-      }
-      // room for the (at most four) events of the next group
-      if (__any_sync(0xffffffffu, cnt > USQ_SLOTS - 4)) {
-        drain();
-      }
-    }
-  }
-  drain();
-  if (i_ok && w != w_in) {
-    p.w[idx] = w;
-  }
-}
-
-// The same update reading the compacted lists: per walked sample two shuffles (sample, x word), the
-// d word, AND, and - for the lanes with coincidences - one byte pushed into the lane's column of a
+// The update itself: per walked sample two shuffles (sample, x word), the d word, AND, and - for
+// the lanes with coincidences - one byte (count, direction) pushed into the lane's column of a
 // queue in shared memory. The queues are drained together when one is nearly full, oldest event
-// first, with the pulse application of the kernel above.
+// first: one pulse at a time with the clip after each, as in rpu_weight_updater.cpp:243-291. The
+// Gaussians of the device noise come from a pool per warp in shared memory that all lanes refill
+// together and take from without gaps (ballot + prefix count).
 constexpr int USL_QCAP = 24; // events per lane between two drains
 
 template <int KIND, bool NOISY>
@@ -1022,18 +892,10 @@ template <int KIND>
 static void launchStreamKind(const UpdateProblem &p, const StreamUpdate &st, cudaStream_t stream) {
   const long long tasks = (long long)((p.d_size + 31) / 32) * p.x_size;
   const unsigned blocks = (unsigned)((tasks + 7) / 8);
-  if (st.list_s != nullptr) {
-    if (p.dw_min_std > 0.0f) {
-      AB200_CUDA(launchChained(pulsedUpdateListKernel<KIND, true>, dim3(blocks), dim3(256), 0, stream, p, st));
-    } else {
-      AB200_CUDA(launchChained(pulsedUpdateListKernel<KIND, false>, dim3(blocks), dim3(256), 0, stream, p, st));
-    }
-    return;
-  }
   if (p.dw_min_std > 0.0f) {
-    AB200_CUDA(launchChained(pulsedUpdateStreamKernel<KIND, true>, dim3(blocks), dim3(256), 0, stream, p, st));
+    AB200_CUDA(launchChained(pulsedUpdateListKernel<KIND, true>, dim3(blocks), dim3(256), 0, stream, p, st));
   } else {
-    AB200_CUDA(launchChained(pulsedUpdateStreamKernel<KIND, false>, dim3(blocks), dim3(256), 0, stream, p, st));
+    AB200_CUDA(launchChained(pulsedUpdateListKernel<KIND, false>, dim3(blocks), dim3(256), 0, stream, p, st));
   }
 }
 
@@ -1070,7 +932,8 @@ void launchPulseTranspose(const UpdateProblem &p0, uint32_t *xwT, uint32_t *xnzT
 void launchPulseCompact(const UpdateProblem &p0, const uint32_t *xwT, const uint32_t *xnzT, int m_pad,
                         uint32_t *list_s, uint32_t *list_x, uint32_t *list_off, cudaStream_t stream) {
   const UpdateProblem p = inRows(p0);
-  const unsigned blocks = (unsigned)(((long long)p.x_size * 32 + 255) / 256);
+  const int n_seg = (m_pad / 32 + UCS_SEG_WORDS - 1) / UCS_SEG_WORDS;
+  const unsigned blocks = (unsigned)(((long long)p.x_size * n_seg * 32 + 255) / 256);
   AB200_CUDA(launchChained(pulseCompactKernel, dim3(blocks), dim3(256), 0, stream, xwT, xnzT, p.x_size, m_pad,
                            list_s, list_x, list_off));
   AB200_LAUNCH_CHECK();
