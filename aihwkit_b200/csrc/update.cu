@@ -767,7 +767,8 @@ template <int KIND, bool NOISY>
 __global__ void __launch_bounds__(256) pulsedUpdateListKernel(UpdateProblem p, StreamUpdate st) {
   pdlEnter();
   __shared__ float pool[8][USP_POOL];
-  __shared__ uint8_t evq[USL_QCAP][256];
+  // rows padded by one word: lanes at different fill levels then fall into different banks
+  __shared__ uint8_t evq[USL_QCAP][256 + 4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_dblk = (p.d_size + 31) >> 5;
   const long long task = (long long)blockIdx.x * 8 + warp;
