@@ -123,9 +123,7 @@ UpEff resolveUp(const ab200_update_params &up) {
     // pulse in k - the same law per weight, in the same per-weight order, as the compressed type.
     e.pulse_type = AB200_PULSE_STOCHASTIC_COMPRESSED;
   }
-  if (up.sto_round) {
-    AB200_FATAL("stochastic rounding of pulse probabilities is not implemented");
-  }
+  e.sto_round = up.sto_round != 0;
   return e;
 }
 

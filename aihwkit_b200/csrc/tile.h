@@ -66,6 +66,7 @@ struct UpEff {
   int fixed_bl;
   int update_management;
   int update_bl_management;
+  int sto_round; // stochastic rounding of the pulse probabilities to `res`
   float um_grad_scale;
   float res;
   float x_res_implicit;

@@ -116,6 +116,19 @@ pulseTrain(float pp, int BL, int seg, PhiloxKey key, uint32_t line, uint32_t sam
   return bits;
 }
 
+// getDiscretizedValue of a pulse probability (src/rpucuda/utility_functions.h:186-193): to the
+// nearest multiple of `res`, or - with sto_round - up or down at random in proportion to the
+// remainder; the uniform of a line is a function of (line, sample, call).
+__device__ __forceinline__ float
+pulseProb(const UpdateProblem &p, float v, float res, uint32_t line, uint32_t sample, uint32_t tag) {
+  if (!p.up.sto_round || !(res > 0.0f)) {
+    return discretize(v, res);
+  }
+  uint32_t r[4];
+  philox4x32<7>(line, sample, p.call, tag ^ 0x08000000u, p.key, r);
+  return __fmul_rn(rintf(__fadd_rn(__fdiv_rn(v, res), __fadd_rn(u01(r[0]), -0.5f))), res);
+}
+
 __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
   pdlEnter();
   __shared__ float sh[8];
@@ -164,7 +177,8 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
       // generateDetImplicit (dense_bit_line_maker.cpp:210-238); d-values carry the factor BL
       // (generateCoincidencesDetI :240-264)
       float vv = p.lr_neg ? -v : v;
-      float pp = discretize(__fmul_rn(fabsf(vv), P), is_x ? p.up.x_res_implicit : p.up.d_res_implicit);
+      float pp = pulseProb(p, __fmul_rn(fabsf(vv), P), is_x ? p.up.x_res_implicit : p.up.d_res_implicit,
+                           (uint32_t)idx, (uint32_t)s, is_x ? TAG_PULSE_X : TAG_PULSE_D);
       pp = fmaxf(fminf(pp, 1.0f), 0.0f);
       float sv = vv >= 0.0f ? pp : -pp;
       if (BL == 0) {
@@ -179,7 +193,8 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
       // number of pulses per line, no fluctuation; the d count carries the factor 1 / BL, so the
       // coincidences are rint(d * x) like those of the implicit type
       const float vv = p.lr_neg ? -v : v;
-      const float pp = discretize(__fmul_rn(fabsf(vv), P), p.up.res);
+      const float pp = pulseProb(p, __fmul_rn(fabsf(vv), P), p.up.res, (uint32_t)idx, (uint32_t)s,
+                                 is_x ? TAG_PULSE_X : TAG_PULSE_D);
       float sv = 0.0f;
       if (pp != 0.0f && BL > 0) {
         const int ntimes = max(min((int)rintf(__fmul_rn((float)BL, pp)), BL), 0);
@@ -193,7 +208,8 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
       float pp = 0.0f;
       uint32_t neg = 0u;
       if (BL > 0) {
-        pp = discretize(__fmul_rn(fabsf(v), P), p.up.res);
+        pp = pulseProb(p, __fmul_rn(fabsf(v), P), p.up.res, (uint32_t)idx, (uint32_t)s,
+                       is_x ? TAG_PULSE_X : TAG_PULSE_D);
         neg = v > 0.0f ? 0u : 1u;
         if (!is_x && p.lr_neg) {
           neg ^= 1u;

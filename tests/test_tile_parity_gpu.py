@@ -727,3 +727,55 @@ def test_running_average_noise_management(nm):
             frac, worst = H.lsb_report(y, yr, lsb)
             assert frac <= 2e-3 and worst <= 1.001, (call, frac, worst)
     assert fio.noise_management in (5, 6)
+
+
+def test_stochastic_rounding_of_pulse_probabilities():
+    """update.sto_round (sparse_bit_line_maker.cpp:174, :224; utility_functions.h:186-193): the
+    pulse probabilities are rounded to `res` up or down at random, so a coarse `res` leaves the mean
+    update where the fine one has it, while rounding to nearest moves it; moments against the
+    compiled reference with the same setting."""
+    from oracle import ref
+
+    rng = np.random.default_rng(91)
+    x_size, d_size, m, reps = 24, 16, 6, 200
+    W0 = np.zeros((d_size, x_size), np.float32)
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.1, (m, d_size)).astype(np.float32)
+
+    def mean_update(res, sto, use_ref=False):
+        p = H.training_params(noise=False, pulse_det=False)
+        p.update.res = res
+        p.update.sto_round = sto
+        dp = H.device("cs", False, dw_min_dtod=0.0, up_down_dtod=0.0, w_max_dtod=0.0, w_min_dtod=0.0)
+        cfg = p._config(x_size, d_size, dp, seed=5)
+        if use_ref:
+            t = ref.RefTile(cfg)
+            t.set_learning_rate(0.05)
+            out = []
+            for _ in range(reps):
+                t.set_weights(W0)
+                t.update(X, Dm)
+                out.append(t.get_weights())
+            return np.stack(out)
+        from aihwkit_b200.rpu_base import tiles as T
+
+        t = T.AnalogTile(cfg, cuda_device=0)
+        t.set_learning_rate(0.05)
+        xg, dg = torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda()
+        out = []
+        for _ in range(reps):
+            t.set_weights(torch.from_numpy(W0))
+            t.update(xg, dg)
+            out.append(t.get_weights().numpy())
+        return np.stack(out)
+
+    fine = mean_update(0.0, False)
+    sto = mean_update(0.25, True)
+    near = mean_update(0.25, False)
+    se = np.sqrt(fine.var(axis=0) / reps + sto.var(axis=0) / reps) + 1e-9
+    z = (fine.mean(axis=0) - sto.mean(axis=0)) / se
+    assert np.abs(z).max() < 5.5 and abs(z.mean()) < 0.5, (np.abs(z).max(), z.mean())
+    # rounding to nearest at this resolution changes the update as a whole
+    assert np.abs(near.mean(axis=0) - fine.mean(axis=0)).sum() > 0.2 * np.abs(fine.mean(axis=0)).sum()
+    if ref.available():
+        H.assert_moments_agree(sto, mean_update(0.25, True, use_ref=True))
