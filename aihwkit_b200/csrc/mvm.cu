@@ -123,7 +123,11 @@ __global__ void nmAverageKernel(float *sval, int m, float decay, float *state) {
 // PCM ("line chain"): also accumulate per output sum_k |w| v^2 (variance factor of the PCMRead
 // weight noise), sum_k |w| |v| (line current) and sum_k w v posw(k) (position-weighted product) for
 // the IR drop, and run the long output chain (lineChain) instead of the merged noise draw.
-template <bool A_K_FAST, bool B_N_FAST, int T, bool PCM>
+// NMF (small problems, T = 1): the noise management of the CTA's sixteen rows runs in the prologue
+// instead of a kernel of its own - sixteen threads per row reduce the row's statistics, every
+// column CTA of a row block repeats that (a few KB), and the first one leaves the per-row values
+// for the bound-management re-run. One launch less per pass where launches are what a pass costs.
+template <bool A_K_FAST, bool B_N_FAST, int T, bool PCM, bool NMF = false>
 __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   pdlEnter();
   constexpr int BM = 16 * T, BN = 16 * T;
@@ -131,6 +135,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   __shared__ float s_scale[BM];
+  __shared__ float s_fac[NMF ? BM : 1];
   const IOEff &io = p.io;
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
@@ -138,7 +143,47 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   const int K = p.in_size, N = p.out_size;
   const ElemRng g{p.key, p.call, (p.backward ? TAG_BWD_IN : TAG_FWD_IN) + p.noise_id};
 
-  if (tid < BM) {
+  if (NMF) {
+    // BM = 16 rows, 16 threads per row
+    const int r = tid >> 4, part = tid & 15;
+    const int gr = row0 + r;
+    NmStats st;
+    if (gr < p.m && nmNeedsStats(io)) {
+      const float *row = p.in + (long long)gr * p.in_ss;
+      for (int k = part; k < K; k += 16) {
+        st.add(k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f);
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {
+      st.amax = fmaxf(st.amax, __shfl_xor_sync(0xffffffffu, st.amax, o));
+      st.vmax = fmaxf(st.vmax, __shfl_xor_sync(0xffffffffu, st.vmax, o));
+      st.psum += __shfl_xor_sync(0xffffffffu, st.psum, o);
+      st.nsum += __shfl_xor_sync(0xffffffffu, st.nsum, o);
+    }
+    if (part == 0) {
+      float scale = 0.0f, fac = 0.0f;
+      if (gr < p.m) {
+        const float sval = nmValue(io, st);
+        scale = inputScale(io, sval, /*reduction=*/1.0f, !p.backward);
+        fac = outputFactor(io, p.alpha, sval, scale, p.backward);
+        if (blockIdx.x == 0) {
+          // what the bound-management re-run reads; the flags are zero between passes (the
+          // re-run clears the ones it has served)
+          p.scale[gr] = scale;
+          p.sval[gr] = sval;
+          p.factor[gr] = fac;
+          p.vnorm[gr] = 0.0f;
+        }
+      }
+      s_scale[r] = scale;
+      s_fac[NMF ? r : 0] = fac;
+    }
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && !p.backward && p.bm_stats) {
+      p.bm_stats[0] = 0;
+      p.bm_stats[1] = 0;
+    }
+  } else if (tid < BM) {
     int r = row0 + tid;
     s_scale[tid] = r < p.m ? p.scale[r] : 0.0f;
   }
@@ -240,7 +285,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
       continue;
     }
     float sc = s_scale[ty * T + i];
-    float fac = p.factor[r];
+    float fac = NMF ? s_fac[NMF ? ty * T + i : 0] : p.factor[r];
     float y[T];
 #pragma unroll
     for (int j = 0; j < T; j++) {
@@ -259,7 +304,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
       }
     } else {
       const bool line_sigma = p.out_noise_vals != nullptr;
-      const float vn = p.vnorm[r];
+      const float vn = NMF ? 0.0f : p.vnorm[r];
       float sigma = PCM ? io.out_noise : outputSigma(io, vn);
       float z[4] = {0.f, 0.f, 0.f, 0.f};
       if (sigma > 0.0f || line_sigma) {
@@ -438,6 +483,7 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
     if (threadIdx.x == 0) {
       atomicAdd(&p.bm_stats[0], 1);
       atomicMax(&p.bm_stats[1], __float_as_int(reduction));
+      p.flags[r] = 0; // served: the flags are zero again when the next pass starts
     }
     __syncthreads();
   }
@@ -457,6 +503,33 @@ void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
   };
   const bool running = !p.io.is_perfect && (p.io.nm == AB200_NM_AVERAGE_ABS_MAX ||
                                             p.io.nm == AB200_NM_AVERAGE_ABS_MAX_SINGLE_VALUE);
+  // small problems (the 16 x 16 tile is chosen below) without per-row norms or running values:
+  // the noise management goes into the prologue of the product kernel
+  static int n_sm_f = 0;
+  if (n_sm_f == 0) {
+    int dev = 0;
+    AB200_CUDA(cudaGetDevice(&dev));
+    AB200_CUDA(cudaDeviceGetAttribute(&n_sm_f, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const long long ctas2 = (long long)((p.out_size + 31) / 32) * ((p.m + 31) / 32);
+  const bool fused_nm = !running && !ioNeedsLineChain(p.io) && ctas2 < n_sm_f && p.in_size <= 4096 &&
+                        !(p.io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && p.io.w_noise > 0.0f &&
+                          !p.io.is_perfect);
+  if (fused_nm) {
+    dim3 grid((p.out_size + 15) / 16, (p.m + 15) / 16);
+    const bool a_k = p.in_fs == 1, b_n = p.wn == 1;
+    if (a_k && b_n) {
+      AB200_CUDA(launchChained(mvmSimtKernel<true, true, 1, false, true>, grid, dim3(256), 0, stream, p));
+    } else if (a_k) {
+      AB200_CUDA(launchChained(mvmSimtKernel<true, false, 1, false, true>, grid, dim3(256), 0, stream, p));
+    } else if (b_n) {
+      AB200_CUDA(launchChained(mvmSimtKernel<false, true, 1, false, true>, grid, dim3(256), 0, stream, p));
+    } else {
+      AB200_CUDA(launchChained(mvmSimtKernel<false, false, 1, false, true>, grid, dim3(256), 0, stream, p));
+    }
+    AB200_LAUNCH_CHECK();
+    return;
+  }
   if (running) {
     if (!p.nm_state) {
       AB200_FATAL("running-average noise management needs a tile (its state lives there)");

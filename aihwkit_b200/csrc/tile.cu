@@ -779,6 +779,8 @@ void Tile::ensureScratch(int m) {
   AB200_CUDA(cudaMalloc(&vnorm_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&sval_, (size_t)cap * sizeof(float)));
   AB200_CUDA(cudaMalloc(&flags_, (size_t)cap * sizeof(int)));
+  // the flags are zero between passes: a pass sets them, the re-run clears the ones it serves
+  AB200_CUDA(cudaMemset(flags_, 0, (size_t)cap * sizeof(int)));
   xw_ = dw_ = nullptr;
   if (cfg_.device_kind != AB200_DEVICE_IDEAL && up_.pulse_type != AB200_PULSE_NONE) {
     AB200_CUDA(cudaMalloc(&xw_, (size_t)cap * x_size_ * sizeof(uint32_t)));
