@@ -505,14 +505,14 @@ void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
                                             p.io.nm == AB200_NM_AVERAGE_ABS_MAX_SINGLE_VALUE);
   // small problems (the 16 x 16 tile is chosen below) without per-row norms or running values:
   // the noise management goes into the prologue of the product kernel
-  static int n_sm_f = 0;
-  if (n_sm_f == 0) {
+  static int n_sm = 0; // SMs of the GPUs of this process (one kind per process)
+  if (n_sm == 0) {
     int dev = 0;
     AB200_CUDA(cudaGetDevice(&dev));
-    AB200_CUDA(cudaDeviceGetAttribute(&n_sm_f, cudaDevAttrMultiProcessorCount, dev));
+    AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
   }
   const long long ctas2 = (long long)((p.out_size + 31) / 32) * ((p.m + 31) / 32);
-  const bool fused_nm = !running && !ioNeedsLineChain(p.io) && ctas2 < n_sm_f && p.in_size <= 4096 &&
+  const bool fused_nm = !running && !ioNeedsLineChain(p.io) && ctas2 < n_sm && p.in_size <= 4096 &&
                         !(p.io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && p.io.w_noise > 0.0f &&
                           !p.io.is_perfect);
   if (fused_nm) {
@@ -546,12 +546,6 @@ void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
   const bool a_k_fast = p.in_fs == 1;
   const bool b_n_fast = p.wn == 1;
   // the largest tile that still gives every SM a CTA
-  static int n_sm = 0;
-  if (n_sm == 0) {
-    int dev = 0;
-    AB200_CUDA(cudaGetDevice(&dev));
-    AB200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-  }
   auto ctas = [&](int t) {
     return (long long)((p.out_size + 16 * t - 1) / (16 * t)) * ((p.m + 16 * t - 1) / (16 * t));
   };
