@@ -175,6 +175,14 @@ class TransferParams(C.Structure):
         ("thres_scale", C.c_float),
         ("step", C.c_float),
         ("momentum", C.c_float),
+        ("chopped", C.c_int32),
+        ("in_chop_random", C.c_int32),
+        ("correct_gradient_magnitudes", C.c_int32),
+        ("no_buffer", C.c_int32),
+        ("in_chop_prob", C.c_float),
+        ("out_chop_prob", C.c_float),
+        ("auto_granularity", C.c_float),
+        ("buffer_granularity", C.c_float),
     ]
 
 

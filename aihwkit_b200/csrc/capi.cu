@@ -152,6 +152,9 @@ void ab200_default_transfer_params(ab200_transfer_params *tp) {
   std::memset(tp, 0, sizeof(*tp));
   tp->transfer_every = 1.0f;
   tp->n_reads_per_transfer = 1;
+  tp->in_chop_prob = 1.0f; /* rpu_chopped_transfer_device.h:24-37 */
+  tp->in_chop_random = 1;
+  tp->buffer_granularity = 1.0f;
   tp->thres_scale = 1.0f;
   tp->step = 1.0f;
   tp->forget_buffer = 1;

@@ -386,6 +386,19 @@ Tile::Tile(const ab200_tile_config &cfg, int cuda_device) : cfg_(cfg) {
     if (t.n_reads_per_transfer < 0) {
       AB200_FATAL("Transfer: n_reads_per_transfer must be >= 0");
     }
+    if (t.chopped) {
+      // ChoppedTransferRPUDeviceMetaParameter::checkSupported (rpu_chopped_transfer_device.cpp:66-88)
+      if (!t.buffered) {
+        AB200_FATAL("ChoppedTransfer: expects the buffered transfer parameters (buffered = 1)");
+      }
+      if (t.n_reads_per_transfer != 1) {
+        AB200_FATAL("In / out chopper not implemented the given parameters. \nRequired: n_devices==2, "
+                    "n_reads_per_transfer==1, random_selection=false).\n");
+      }
+      if (t.transfer_every < 0.0f) {
+        AB200_FATAL("ChoppedTransfer: the automatic transfer period is not implemented");
+      }
+    }
     // transfer IO: noise and bound management are turned off (rpu_transfer_device.cpp:208-217)
     ab200_io_params tio = t.transfer_io;
     tio.noise_management = AB200_NM_NONE;
@@ -515,6 +528,8 @@ Tile::~Tile() {
     cudaFree(xls_);
     cudaFree(xlx_);
     cudaFree(xloff_);
+    cudaFree(chop_in_);
+    cudaFree(chop_out_);
     cudaFree(nm_state_);
     cudaFree(f_lt_.voff);
     cudaFree(f_lt_.nl);
@@ -622,6 +637,15 @@ void Tile::toDevice(int cuda_device) {
     if (cfg_.transfer.buffered) {
       AB200_CUDA(cudaMalloc(&t_buffer_, size * sizeof(float)));
       AB200_CUDA(cudaMemset(t_buffer_, 0, size * sizeof(float)));
+    }
+    if (cfg_.transfer.chopped) {
+      // all choppers start unflipped (ChoppedTransferRPUDevice::populate,
+      // rpu_chopped_transfer_device.cpp:214-227)
+      AB200_CUDA(cudaMalloc(&chop_in_, (size_t)x_size_));
+      AB200_CUDA(cudaMalloc(&chop_out_, (size_t)d_size_));
+      AB200_CUDA(cudaMemset(chop_in_, 0, (size_t)x_size_));
+      AB200_CUDA(cudaMemset(chop_out_, 0, (size_t)d_size_));
+      chop_passes_ = 0;
     }
   }
   AB200_CUDA(cudaMalloc(&bm_stats_, 2 * sizeof(int)));
@@ -1325,7 +1349,49 @@ void Tile::doTransfer(cudaStream_t s) {
     }
     uint32_t call = transfer_calls_++;
     float write_lr = t_lr;
-    if (t.buffered) {
+    if (t.chopped) {
+      // Tiki-Taka with choppers (ChoppedTransferRPUDevice::readAndUpdate,
+      // rpu_chopped_transfer_device.cpp:357-470): plain read of the (chopped) fast tile, de-chopped
+      // and accumulated in units of the buffer granularity; whole units go to the slow tile
+      launchTransferRead(w_fast_, col, d_size_, t_io_, key_, call, onehot_, x_size_, tread_, 1.0f, s);
+      const float from_gran = dev_[0].dw_min, to_gran = dev_[1].dw_min;
+      // getBufferGranularity / getTransferLRScale (:108-142)
+      float bg = t.buffer_granularity > 0.0f ? t.buffer_granularity : 1.0f;
+      if (t.auto_granularity > 0.0f) {
+        const float period = (float)x_size_ * fabsf(t.transfer_every);
+        bg *= from_gran * t.auto_granularity / period;
+      } else {
+        bg *= from_gran;
+      }
+      float lr_scale;
+      if (t.correct_gradient_magnitudes) {
+        bg *= to_gran / from_gran;
+        lr_scale = fabsf(t_lr) / pulseCountLR() / bg;
+      } else {
+        lr_scale = fabsf(t_lr) / bg;
+      }
+      // the in chopper of this line flips after the transfer: always / never / at random / every
+      // n-th pass over the matrix (:439-452); the host decides, the kernel flips
+      int flip_in = 0;
+      if (t.in_chop_prob > 0.0f) {
+        if (t.in_chop_random) {
+          flip_in = chop_rng_.uniform() < t.in_chop_prob ? 1 : 0;
+        } else {
+          const uint64_t n_samples = (uint64_t)std::max((int)ceilf(1.0f / t.in_chop_prob), 2);
+          flip_in = (chop_passes_ % n_samples) + 1 == n_samples ? 1 : 0;
+        }
+      }
+      launchTransferChopBuffer(t_buffer_ + (size_t)col * d_size_, tread_, d_size_, lr_scale,
+                               (float)t_up_.desired_bl, t.momentum, t.forget_buffer, t.no_buffer,
+                               chop_in_, col, chop_out_, flip_in, s);
+      write_lr = t.step * to_gran;
+      if (col == x_size_ - 1) {
+        if (t.out_chop_prob > 0.0f) {
+          launchFlipChoppers(chop_out_, d_size_, t.out_chop_prob, key_, call, s);
+        }
+        chop_passes_++;
+      }
+    } else if (t.buffered) {
       // Tiki-Taka v2 (BufferedTransferRPUDevice::readAndUpdate,
       // rpu_buffered_transfer_device.cpp:142-212): plain read, accumulate into the buffer column,
       // pulse the slow tile with the whole steps only, each worth `step` granularities
@@ -1466,6 +1532,10 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
   u.pw = dev_[0].pw;
   u.pw_n = dev_[0].pw_n;
   u.mult_noise = dev_[0].mult_noise;
+  if (cfg_.device_kind == AB200_DEVICE_TRANSFER && cfg_.transfer.chopped) {
+    u.chop_x = chop_in_;
+    u.chop_d = chop_out_;
+  }
   launchPulsePrepare(u, s);
   const bool stream_upd = streamUpdateEligible(u);
   const int m_pad = (m * u.nseg + 31) / 32 * 32;

@@ -10,6 +10,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <random>
 #include <vector>
 
 namespace ab200 {
@@ -178,6 +179,9 @@ struct UpdateProblem {
   float4 es0, es1; // ExpStep globals (DeviceStore)
   const float *pw;  // PiecewiseStep tables (DeviceStore), pw_n nodes per direction
   int pw_n;
+  // choppers of a chopped transfer compound (one byte per x-line / d-line, non-zero = the sign
+  // of that line's pulses is flipped), or null
+  const unsigned char *chop_x, *chop_d;
   int s_begin, s_end; // sample range applied by the update kernel
 };
 
@@ -203,6 +207,17 @@ void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream);
 void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream);
 void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream,
                     bool overwrite = false, bool clip_each = false);
+// Chopped transfer: de-chop the read of column `col`, accumulate it in the buffer column in units
+// of the buffer granularity, turn whole units into the write-out (d = -n), flip the in chopper of
+// the column when `flip_in` is set (ChoppedTransferRPUDevice::readAndUpdate,
+// rpu_chopped_transfer_device.cpp:357-470)
+void launchTransferChopBuffer(float *buffer_col, float *read_inout, int d_size, float lr_scale,
+                              float max_steps, float momentum, int forget_buffer, int no_buffer,
+                              unsigned char *chop_in, int col, const unsigned char *chop_out,
+                              int flip_in, cudaStream_t stream);
+// flip every out chopper with probability `prob`
+void launchFlipChoppers(unsigned char *chop, int n, float prob, PhiloxKey key, uint32_t call,
+                        cudaStream_t stream);
 void launchTransferRead(const float *w_fast, int col, int d_size, const IOEff &io, PhiloxKey key,
                         uint32_t call, float *x_onehot, int x_size, float *r_out, float alpha,
                         cudaStream_t stream);
@@ -369,6 +384,13 @@ private:
   // backward (x_size), drawn once per tile (rpu_forward_backward_pass.cpp:306-313)
   float *f_onv_ = nullptr, *b_onv_ = nullptr;
   float *nm_state_ = nullptr;
+  unsigned char *chop_in_ = nullptr, *chop_out_ = nullptr; // chopped transfer: x_size / d_size flags
+  uint64_t chop_passes_ = 0;                               // full passes over the matrix (transfer_counter_)
+  struct ChopRng { // host draws of the random in-chopper flips
+    std::mt19937 gen{0x9e3779b9u};
+    std::uniform_real_distribution<float> ud{0.0f, 1.0f};
+    float uniform() { return ud(gen); }
+  } chop_rng_;
   uint32_t *xls_ = nullptr, *xlx_ = nullptr, *xloff_ = nullptr; // compacted x lists (stream update)
   // per-line tables of a direction (MVParameter, rpu_forward_backward_pass.h:14-22)
   struct LineTables {

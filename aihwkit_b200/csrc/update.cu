@@ -214,6 +214,7 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
         if (!is_x && p.lr_neg) {
           neg ^= 1u;
         }
+
       }
       const int n_lines = is_x ? p.x_size : p.d_size;
       for (int g = 0; g < nseg; g++) {
@@ -505,6 +506,14 @@ __global__ void __launch_bounds__(UT_I *UTJ / EJ, (UT_I * UTJ / EJ) >= 1024 ? 1 
     for (int t = 0; t < UE_J; t++) {
       const int jl = tj * UE_J + t;
       const long long idx = (long long)(j0 + t) * p.d_size + i;
+      // chopped transfer compound: the pulses of this weight enter with the opposite sign when
+      // exactly one of its two lines is chopped (ChoppedTransferRPUDevice::doSparseUpdate /
+      // doDenseUpdate, rpu_chopped_transfer_device.cpp:472-515); read per launch, so a flip by
+      // a transfer between two launches of a batch takes effect for the samples after it
+      bool chop_flip = false;
+      if (p.chop_x != nullptr) {
+        chop_flip = ((j0 + t < p.x_size ? p.chop_x[j0 + t] : 0) != 0) != ((i_ok ? p.chop_d[i] : 0) != 0);
+      }
       int wi = 0;
       uint32_t cand = sm.sdnz[0][ti] & sm.sxnz[0][jl];
       while (true) {
@@ -526,12 +535,12 @@ __global__ void __launch_bounds__(UT_I *UTJ / EJ, (UT_I * UTJ / EJ) >= 1024 ? 1 
             // n = rint(d * BL * x), positive = decrease (dense_bit_line_maker.cpp:240-264)
             float c = rintf(__fmul_rn(__uint_as_float(dwv), __uint_as_float(xwv)));
             n = (int)fabsf(c);
-            down = c > 0.0f;
+            down = (c > 0.0f) != chop_flip;
           } else {
             // coincidences of the two trains; equal line signs = decrease
             // (rpu_weight_updater.cpp:246-268)
             n = __popc((xwv & dwv) >> 1);
-            down = ((xwv ^ dwv) & 1u) == 0u;
+            down = (((xwv ^ dwv) & 1u) == 0u) != chop_flip;
           }
           if (n != 0) {
             break;
@@ -808,6 +817,11 @@ __global__ void __launch_bounds__(256) pulsedUpdateListKernel(UpdateProblem p, S
   }
   const float w_in = w;
   const float std = p.dw_min_std;
+  // chopped transfer compound: direction flipped when exactly one of the two lines is chopped
+  uint32_t chop_flip = 0u;
+  if (p.chop_x != nullptr) {
+    chop_flip = (p.chop_x[j] != 0 ? 1u : 0u) ^ ((i_ok && p.chop_d[i] != 0) ? 1u : 0u);
+  }
   int cnt = 0;
   int pool_pos = USP_POOL; // empty
   uint32_t refills = 0;
@@ -890,7 +904,8 @@ __global__ void __launch_bounds__(256) pulsedUpdateListKernel(UpdateProblem p, S
         const uint32_t both = xv[c] & dwv[c] & ~1u;
         if (both != 0u) {
           // equal line signs = decrease (rpu_weight_updater.cpp:246-268); the x sign is stored flipped
-          evq[cnt][threadIdx.x] = (uint8_t)(((uint32_t)__popc(both) << 1) | ((xv[c] ^ dwv[c]) & 1u));
+          evq[cnt][threadIdx.x] =
+              (uint8_t)(((uint32_t)__popc(both) << 1) | (((xv[c] ^ dwv[c]) & 1u) ^ chop_flip));
           cnt++;
         }
       }
@@ -1221,6 +1236,64 @@ __global__ void transferBufferKernel(float *buffer_col, float *read_inout, int d
   }
   buffer_col[t] = h;
   read_inout[t] = -n;
+}
+
+__global__ void __launch_bounds__(256)
+    transferChopBufferKernel(float *buffer_col, float *read_inout, int d_size, float lr_scale,
+                             float max_steps, float momentum, int forget_buffer, int no_buffer,
+                             unsigned char *chop_in, int col, const unsigned char *chop_out,
+                             int flip_in) {
+  pdlEnter();
+  // one CTA: the in chopper of the column is read by all threads before thread 0 flips it
+  const bool in_chop = chop_in[col] != 0;
+  const float sub_momentum = 1.0f - fmaxf(fminf(momentum, 1.0f), 0.0f);
+  for (int t = threadIdx.x; t < d_size; t += blockDim.x) {
+    float omega = no_buffer ? 0.0f : buffer_col[t];
+    const float val = __fmul_rn(read_inout[t], lr_scale);
+    omega = __fadd_rn(omega, (in_chop != (chop_out[t] != 0)) ? -val : val);
+    float n = 0.0f;
+    if (fabsf(omega) >= 1.0f) {
+      n = fmaxf(fminf(truncf(omega), max_steps), -max_steps);
+      omega = forget_buffer ? __fmul_rn(omega, momentum) : __fsub_rn(omega, __fmul_rn(sub_momentum, n));
+    }
+    buffer_col[t] = omega;
+    read_inout[t] = -n;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && flip_in) {
+    chop_in[col] = in_chop ? 0 : 1;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    flipChoppersKernel(unsigned char *chop, int n, float prob, PhiloxKey key, uint32_t call) {
+  pdlEnter();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) {
+    return;
+  }
+  uint32_t r[4];
+  philox4x32<7>((uint32_t)t, 0u, call, TAG_TRANSFER_READ ^ 0x01000000u, key, r);
+  if (u01(r[0]) < prob) {
+    chop[t] = chop[t] ? 0 : 1;
+  }
+}
+
+void launchTransferChopBuffer(float *buffer_col, float *read_inout, int d_size, float lr_scale,
+                              float max_steps, float momentum, int forget_buffer, int no_buffer,
+                              unsigned char *chop_in, int col, const unsigned char *chop_out,
+                              int flip_in, cudaStream_t stream) {
+  AB200_CUDA(launchChained(transferChopBufferKernel, dim3(1), dim3(256), 0, stream, buffer_col, read_inout,
+                           d_size, lr_scale, max_steps, momentum, forget_buffer, no_buffer, chop_in, col,
+                           chop_out, flip_in));
+  AB200_LAUNCH_CHECK();
+}
+
+void launchFlipChoppers(unsigned char *chop, int n, float prob, PhiloxKey key, uint32_t call,
+                        cudaStream_t stream) {
+  AB200_CUDA(launchChained(flipChoppersKernel, dim3((n + 255) / 256), dim3(256), 0, stream, chop, n, prob, key,
+                           call));
+  AB200_LAUNCH_CHECK();
 }
 
 void launchTransferBuffer(float *buffer_col, float *read_inout, int d_size, float lr_abs,

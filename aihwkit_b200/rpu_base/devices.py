@@ -629,6 +629,45 @@ class BufferedTransferResistiveDeviceParameter(TransferResistiveDeviceParameter)
         return c
 
 
+class ChoppedTransferResistiveDeviceParameter(BufferedTransferResistiveDeviceParameter):
+    """ChoppedTransferRPUDeviceMetaParameter, Tiki-Taka with choppers (rpu_base_devices.cpp:893-910;
+    src/rpucuda/rpu_chopped_transfer_device.h:22-60)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.in_chop_prob = 1.0
+        self.in_chop_random = True
+        self.out_chop_prob = 0.0
+        self.auto_scale = False
+        self.correct_gradient_magnitudes = False
+        self.auto_momentum = 0.99
+        self.auto_granularity = 0.0
+        self.buffer_granularity = 1.0
+        self.no_buffer = False
+        self.n_reads_per_transfer = 1
+
+    def _to_c(self) -> _cabi.TransferParams:
+        if self.auto_scale:
+            raise RuntimeError("ChoppedTransfer: auto_scale is not implemented by the B200 analog tile")
+        if float(self.transfer_every) < 0:
+            raise RuntimeError("ChoppedTransfer: the automatic transfer period (transfer_every < 0) is "
+                               "not implemented by the B200 analog tile")
+        if int(self.n_reads_per_transfer) != 1:
+            # ChoppedTransferRPUDeviceMetaParameter::checkSupported (rpu_chopped_transfer_device.cpp:66-88)
+            raise RuntimeError("In / out chopper not implemented the given parameters. \nRequired: "
+                               "n_devices==2, n_reads_per_transfer==1, random_selection=false).\n")
+        c = super()._to_c()
+        c.chopped = 1
+        c.in_chop_random = int(bool(self.in_chop_random))
+        c.correct_gradient_magnitudes = int(bool(self.correct_gradient_magnitudes))
+        c.no_buffer = int(bool(self.no_buffer))
+        c.in_chop_prob = float(self.in_chop_prob)
+        c.out_chop_prob = float(self.out_chop_prob)
+        c.auto_granularity = float(self.auto_granularity)
+        c.buffer_granularity = float(self.buffer_granularity)
+        return c
+
+
 class AnalogTileParameter:
     """PulsedMetaParameter (rpu_base_devices.cpp:453-467)."""
 

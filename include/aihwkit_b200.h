@@ -256,6 +256,23 @@ typedef struct ab200_transfer_params {
   float thres_scale;
   float step;
   float momentum;
+  /* ChoppedTransferRPUDeviceMetaParameter (Tiki-Taka with choppers,
+   * src/rpucuda/rpu_chopped_transfer_device.h:22-40; needs buffered = 1, one read per transfer): the
+   * gradient pulses of input line j and output line i reach the fast tile with the sign
+   * in_chopper[j] xor out_chopper[i]; a transfer de-chops its read with the same signs and
+   * accumulates it in units of the buffer granularity (whole units are written to the slow
+   * tile); the in chopper of the transferred line then flips with probability in_chop_prob (at
+   * random, or every ceil(1 / in_chop_prob) passes over the matrix when in_chop_random = 0), the
+   * out choppers with probability out_chop_prob after every full pass. auto_scale and a negative
+   * transfer_every (automatic period) are not implemented. */
+  int32_t chopped;
+  int32_t in_chop_random;
+  int32_t correct_gradient_magnitudes;
+  int32_t no_buffer;
+  float in_chop_prob;
+  float out_chop_prob;
+  float auto_granularity;
+  float buffer_granularity;
 } ab200_transfer_params;
 
 /* Everything PulsedMetaParameter::createRPUArray needs

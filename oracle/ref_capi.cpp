@@ -13,6 +13,7 @@
 
 #include "dense_bit_line_maker.h"
 #include "rpu_buffered_transfer_device.h"
+#include "rpu_chopped_transfer_device.h"
 #include "rpu_constantstep_device.h"
 #include "rpu_expstep_device.h"
 #include "rpu_linearstep_device.h"
@@ -223,7 +224,21 @@ int ref_tile_create(const ab200_tile_config *cfg, void **out) {
   std::unique_ptr<AbstractRPUDeviceMetaParameter<float>> dp;
   if (cfg->device_kind == AB200_DEVICE_TRANSFER) {
     std::unique_ptr<TransferRPUDeviceMetaParameter<float>> tp;
-    if (cfg->transfer.buffered) {
+    if (cfg->transfer.chopped) {
+      auto cp = std::make_unique<ChoppedTransferRPUDeviceMetaParameter<float>>();
+      cp->thres_scale = cfg->transfer.thres_scale;
+      cp->step = cfg->transfer.step;
+      cp->momentum = cfg->transfer.momentum;
+      cp->forget_buffer = cfg->transfer.forget_buffer != 0;
+      cp->in_chop_prob = cfg->transfer.in_chop_prob;
+      cp->in_chop_random = cfg->transfer.in_chop_random != 0;
+      cp->out_chop_prob = cfg->transfer.out_chop_prob;
+      cp->correct_gradient_magnitudes = cfg->transfer.correct_gradient_magnitudes != 0;
+      cp->auto_granularity = cfg->transfer.auto_granularity;
+      cp->buffer_granularity = cfg->transfer.buffer_granularity;
+      cp->no_buffer = cfg->transfer.no_buffer != 0;
+      tp = std::move(cp);
+    } else if (cfg->transfer.buffered) {
       auto bp = std::make_unique<BufferedTransferRPUDeviceMetaParameter<float>>();
       bp->thres_scale = cfg->transfer.thres_scale;
       bp->step = cfg->transfer.step;

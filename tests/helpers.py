@@ -147,3 +147,29 @@ def buffered_transfer_device(seed: int = 21, transfer_every: float = 1.0, n_read
     dp.transfer_forward.out_noise = 0.0
     dp.transfer_forward.bound_management = D.BoundManagementType.Iterative
     return dp
+
+
+def chopped_transfer_device(seed: int = 21, transfer_every: float = 1.0, in_chop_prob: float = 1.0,
+                            in_chop_random: bool = True, out_chop_prob: float = 0.0,
+                            momentum: float = 0.0, forget_buffer: bool = True,
+                            transfer_lr: float = 1.0, buffer_granularity: float = 1.0,
+                            correct_gradient_magnitudes: bool = False, auto_granularity: float = 0.0):
+    """Tiki-Taka with choppers: ChoppedTransferCompound of two noise-free SoftBoundsReference
+    devices, one read per transfer."""
+    dp = D.ChoppedTransferResistiveDeviceParameter()
+    for _ in range(2):
+        dp.append_parameter(device("sbr", False, dw_min=0.002, w_max=1.0, w_min=-1.0))
+    dp.construction_seed = seed
+    dp.gamma = 0.0
+    dp.transfer_every = transfer_every
+    dp.units_in_mbatch = False
+    dp.transfer_lr = transfer_lr
+    dp.fast_lr = 1.0
+    dp.momentum, dp.forget_buffer = momentum, forget_buffer
+    dp.in_chop_prob, dp.in_chop_random, dp.out_chop_prob = in_chop_prob, in_chop_random, out_chop_prob
+    dp.buffer_granularity = buffer_granularity
+    dp.correct_gradient_magnitudes = correct_gradient_magnitudes
+    dp.auto_granularity = auto_granularity
+    dp.transfer_forward.out_noise = 0.0
+    dp.transfer_forward.bound_management = D.BoundManagementType.Iterative
+    return dp

@@ -502,3 +502,67 @@ def test_buffered_transfer_deterministic(forget, momentum, thres):
     t2.set_weights(t.get_weights())
     t2.set_hidden_parameters(t.get_hidden_parameters())
     assert torch.equal(t2.get_hidden_parameters(), t.get_hidden_parameters())
+
+
+@pytest.mark.parametrize("kw", [
+    dict(),                                              # every transfer flips its in chopper
+    dict(in_chop_prob=0.3, in_chop_random=False),        # regular: every fourth pass
+    dict(in_chop_prob=0.0),                              # choppers never move: Tiki-Taka v2 in buffer units
+    dict(momentum=0.3, forget_buffer=False, buffer_granularity=0.5, correct_gradient_magnitudes=True),
+    dict(auto_granularity=30.0, transfer_every=2.0),
+])
+def test_chopped_transfer_deterministic_against_reference(kw):
+    """Tiki-Taka with choppers (src/rpucuda/rpu_chopped_transfer_device.cpp:357-515) with
+    deterministic pulses and chopper schedules that involve no random draw: fast tile, buffer and
+    visible weights follow the compiled reference update by update, transfers falling inside the
+    batches (so that a chopper flips between two samples of one update call)."""
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    if not ref.available():
+        pytest.skip("compiled reference not built")
+    rng = np.random.default_rng(17)
+    x_size, d_size, m = 12, 10, 5
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.chopped_transfer_device(transfer_lr=4.0, **kw)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    rt = ref.RefTile(cfg)
+    names = t.get_hidden_parameter_names()
+    assert names == rt.hidden_parameter_names()
+    assert np.array_equal(t.get_hidden_parameters().numpy(), rt.get_hidden_parameters())
+    ia, ih = names.index("hidden_weights_0"), names.index("buffered_FP_weight_0")
+    lr = 0.1
+    t.set_learning_rate(lr)
+    rt.set_learning_rate(lr)
+    moved = False
+    for step in range(12):
+        x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        d = rng.normal(0, 0.5, (m, d_size)).astype(np.float32)
+        t.update(torch.from_numpy(x).cuda(), torch.from_numpy(d).cuda())
+        rt.update(x, d)
+        hp, hr = t.get_hidden_parameters().numpy(), rt.get_hidden_parameters()
+        assert np.abs(hp[ia] - hr[ia]).max() <= 1e-6, f"fast tile, update {step}"
+        assert np.abs(hp[ih] - hr[ih]).max() <= 1e-4, f"buffer, update {step}"
+        assert np.abs(t.get_weights().numpy() - rt.get_weights()).max() <= 1e-6, f"weights, update {step}"
+        moved = moved or np.abs(rt.get_weights()).max() > 0
+    assert moved and np.abs(hr[ia]).max() > 0
+
+
+def test_chopped_transfer_random_choppers_statistics():
+    """Random in / out chopper flips: the slow tile still integrates the gradient (the de-chopped
+    read has the sign of the accumulated gradient whatever the chopper history)."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(19)
+    x_size, d_size, m = 16, 12, 8
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.chopped_transfer_device(transfer_lr=4.0, in_chop_prob=0.5, out_chop_prob=0.3)
+    t = T.AnalogTile(p._config(x_size, d_size, dp, seed=3), cuda_device=0)
+    t.set_learning_rate(0.1)
+    X = rng.uniform(0.2, 1, (m, x_size)).astype(np.float32)
+    Dm = np.abs(rng.normal(0, 0.5, (m, d_size))).astype(np.float32) + 0.1  # constant-sign gradient
+    for _ in range(40):
+        t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    w = t.get_weights().numpy()
+    assert (w < 0).mean() > 0.95 and np.abs(w).max() > 0.01  # w -= lr d x^T, all terms positive
