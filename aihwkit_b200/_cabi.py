@@ -183,6 +183,10 @@ class TransferParams(C.Structure):
         ("out_chop_prob", C.c_float),
         ("auto_granularity", C.c_float),
         ("buffer_granularity", C.c_float),
+        ("dynamic", C.c_int32),
+        ("correct_accumulation", C.c_int32),
+        ("tail_weightening", C.c_float),
+        ("buffer_cap", C.c_float),
     ]
 
 

@@ -155,6 +155,8 @@ void ab200_default_transfer_params(ab200_transfer_params *tp) {
   tp->in_chop_prob = 1.0f; /* rpu_chopped_transfer_device.h:24-37 */
   tp->in_chop_random = 1;
   tp->buffer_granularity = 1.0f;
+  tp->tail_weightening = 1.0f; /* rpu_dynamic_transfer_device.h:28-29 */
+  tp->buffer_cap = 10.0f;
   tp->thres_scale = 1.0f;
   tp->step = 1.0f;
   tp->forget_buffer = 1;

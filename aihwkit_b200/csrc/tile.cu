@@ -399,6 +399,15 @@ Tile::Tile(const ab200_tile_config &cfg, int cuda_device) : cfg_(cfg) {
         AB200_FATAL("ChoppedTransfer: the automatic transfer period is not implemented");
       }
     }
+    if (t.dynamic) {
+      // DynamicTransferRPUDeviceMetaParameter::checkSupported (rpu_dynamic_transfer_device.cpp:38-49)
+      if (!t.chopped) {
+        AB200_FATAL("DynamicTransfer: expects the chopped transfer parameters (chopped = 1)");
+      }
+      if (t.in_chop_prob <= 0.0f) {
+        AB200_FATAL("In chopper prob needs to be positive.");
+      }
+    }
     // transfer IO: noise and bound management are turned off (rpu_transfer_device.cpp:208-217)
     ab200_io_params tio = t.transfer_io;
     tio.noise_management = AB200_NM_NONE;
@@ -545,6 +554,8 @@ Tile::~Tile() {
     cudaFree(tread_);
     cudaFree(t_words_);
     cudaFree(t_buffer_);
+    cudaFree(t_mean_);
+    cudaFree(t_past_);
     cudaFree(idx_);
     cudaFree(cols_x_);
     cudaFree(cols_d_);
@@ -646,6 +657,13 @@ void Tile::toDevice(int cuda_device) {
       AB200_CUDA(cudaMemset(chop_in_, 0, (size_t)x_size_));
       AB200_CUDA(cudaMemset(chop_out_, 0, (size_t)d_size_));
       chop_passes_ = 0;
+    }
+    if (cfg_.transfer.dynamic) {
+      AB200_CUDA(cudaMalloc(&t_mean_, size * sizeof(float)));
+      AB200_CUDA(cudaMalloc(&t_past_, size * sizeof(float)));
+      AB200_CUDA(cudaMemset(t_mean_, 0, size * sizeof(float)));
+      AB200_CUDA(cudaMemset(t_past_, 0, size * sizeof(float)));
+      chop_switched_.assign((size_t)x_size_, 0);
     }
   }
   AB200_CUDA(cudaMalloc(&bm_stats_, 2 * sizeof(int)));
@@ -947,7 +965,7 @@ int Tile::hiddenCount() const {
   }
   if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
     return (int)dev_[0].names.size() + (int)dev_[1].names.size() + 2 +
-           (cfg_.transfer.buffered ? 1 : 0);
+           (cfg_.transfer.dynamic ? 3 : cfg_.transfer.buffered ? 1 : 0);
   }
   return (int)dev_[0].names.size();
 }
@@ -961,6 +979,11 @@ const char *Tile::hiddenName(int i) const {
     return dev_[0].names[i].c_str();
   }
   int n0 = (int)dev_[0].names.size();
+  if (cfg_.transfer.dynamic && i >= hiddenCount() - 3) {
+    // rpu_dynamic_transfer_device.cpp:361-382
+    static const char *const kDynamic[3] = {"buffered_FP_weight", "running_mean_weight", "past_mean_weight"};
+    return kDynamic[i - (hiddenCount() - 3)];
+  }
   if (cfg_.transfer.buffered && i == hiddenCount() - 1) {
     buf = "buffered_FP_weight_0"; // rpu_buffered_transfer_device.cpp:217-227
     return buf.c_str();
@@ -1005,10 +1028,13 @@ void Tile::getHidden(float *out) {
     }
     o += size;
   }
-  if (cfg_.transfer.buffered) {
+  // digital planes of the buffered forms: the buffer, then (dynamic) running and reference mean
+  const float *planes[3] = {t_buffer_, t_mean_, t_past_};
+  const int n_planes = cfg_.transfer.dynamic ? 3 : cfg_.transfer.buffered ? 1 : 0;
+  for (int q = 0; q < n_planes; q++) {
     if (device_ >= 0) {
       std::vector<float> t(size);
-      AB200_CUDA(cudaMemcpy(t.data(), t_buffer_, size * sizeof(float), cudaMemcpyDeviceToHost));
+      AB200_CUDA(cudaMemcpy(t.data(), planes[q], size * sizeof(float), cudaMemcpyDeviceToHost));
       for (int i = 0; i < d_size_; i++) {
         for (int j = 0; j < x_size_; j++) {
           o[(size_t)i * x_size_ + j] = t[(size_t)j * d_size_ + i];
@@ -1017,6 +1043,7 @@ void Tile::getHidden(float *out) {
     } else {
       std::memset(o, 0, size * sizeof(float));
     }
+    o += size;
   }
 }
 
@@ -1070,13 +1097,18 @@ void Tile::setHidden(const float *in) {
     }
   }
   if (cfg_.device_kind == AB200_DEVICE_TRANSFER && cfg_.transfer.buffered && device_ >= 0) {
+    float *planes[3] = {t_buffer_, t_mean_, t_past_};
+    const int n_planes = cfg_.transfer.dynamic ? 3 : 1;
     std::vector<float> t(size);
-    for (int i = 0; i < d_size_; i++) {
-      for (int j = 0; j < x_size_; j++) {
-        t[(size_t)j * d_size_ + i] = p[(size_t)i * x_size_ + j];
+    for (int q = 0; q < n_planes; q++) {
+      for (int i = 0; i < d_size_; i++) {
+        for (int j = 0; j < x_size_; j++) {
+          t[(size_t)j * d_size_ + i] = p[(size_t)i * x_size_ + j];
+        }
       }
+      AB200_CUDA(cudaMemcpy(planes[q], t.data(), size * sizeof(float), cudaMemcpyHostToDevice));
+      p += size;
     }
-    AB200_CUDA(cudaMemcpy(t_buffer_, t.data(), size * sizeof(float), cudaMemcpyHostToDevice));
   }
   // weights are re-clipped to the new bounds (onSetWeights at the end of setDeviceParameter)
   w_version_++;
@@ -1349,6 +1381,7 @@ void Tile::doTransfer(cudaStream_t s) {
     }
     uint32_t call = transfer_calls_++;
     float write_lr = t_lr;
+    bool skip_write = false;
     if (t.chopped) {
       // Tiki-Taka with choppers (ChoppedTransferRPUDevice::readAndUpdate,
       // rpu_chopped_transfer_device.cpp:357-470): plain read of the (chopped) fast tile, de-chopped
@@ -1370,23 +1403,46 @@ void Tile::doTransfer(cudaStream_t s) {
       } else {
         lr_scale = fabsf(t_lr) / bg;
       }
-      // the in chopper of this line flips after the transfer: always / never / at random / every
-      // n-th pass over the matrix (:439-452); the host decides, the kernel flips
-      int flip_in = 0;
-      if (t.in_chop_prob > 0.0f) {
-        if (t.in_chop_random) {
-          flip_in = chop_rng_.uniform() < t.in_chop_prob ? 1 : 0;
-        } else {
-          const uint64_t n_samples = (uint64_t)std::max((int)ceilf(1.0f / t.in_chop_prob), 2);
-          flip_in = (chop_passes_ % n_samples) + 1 == n_samples ? 1 : 0;
+      const uint64_t n_samples = (uint64_t)std::max((int)ceilf(1.0f / std::max(t.in_chop_prob, 1e-30f)), 2);
+      const uint64_t current_sample = chop_passes_ % n_samples + 1;
+      if (t.dynamic) {
+        // DynamicTransferRPUDevice::readAndUpdate (rpu_dynamic_transfer_device.cpp:198-343): the in
+        // chopper flips at the last sample of its period (and, with in_chop_random, also by
+        // chance); nothing is written during the first period
+        if (t.correct_accumulation) {
+          lr_scale /= std::min((float)current_sample, 1.0f / from_gran);
         }
+        int flip_in = current_sample == n_samples ? 1 : 0;
+        if (t.in_chop_random && chop_rng_.uniform() < t.in_chop_prob) {
+          flip_in = 1;
+        }
+        const size_t off = (size_t)col * d_size_;
+        launchTransferDynamicBuffer(t_buffer_ + off, t_mean_ + off, t_past_ + off, tread_, d_size_, lr_scale,
+                                    (float)t_up_.desired_bl, t.momentum, t.forget_buffer,
+                                    (float)t_up_.desired_bl * t.buffer_cap,
+                                    std::min(t.tail_weightening / (float)n_samples, 1.0f),
+                                    chop_switched_[col], chop_in_, col, chop_out_, flip_in, s);
+        chop_switched_[col] = (unsigned char)flip_in;
+        skip_write = chop_passes_ <= n_samples;
+      } else {
+        // the in chopper of this line flips after the transfer: always / never / at random / every
+        // n-th pass over the matrix (:439-452); the host decides, the kernel flips
+        int flip_in = 0;
+        if (t.in_chop_prob > 0.0f) {
+          if (t.in_chop_random) {
+            flip_in = chop_rng_.uniform() < t.in_chop_prob ? 1 : 0;
+          } else {
+            flip_in = current_sample == n_samples ? 1 : 0;
+          }
+        }
+        launchTransferChopBuffer(t_buffer_ + (size_t)col * d_size_, tread_, d_size_, lr_scale,
+                                 (float)t_up_.desired_bl, t.momentum, t.forget_buffer, t.no_buffer,
+                                 chop_in_, col, chop_out_, flip_in, s);
       }
-      launchTransferChopBuffer(t_buffer_ + (size_t)col * d_size_, tread_, d_size_, lr_scale,
-                               (float)t_up_.desired_bl, t.momentum, t.forget_buffer, t.no_buffer,
-                               chop_in_, col, chop_out_, flip_in, s);
       write_lr = t.step * to_gran;
       if (col == x_size_ - 1) {
-        if (t.out_chop_prob > 0.0f) {
+        // the dynamic form never flips the out choppers (rpu_dynamic_transfer_device.cpp:326-343)
+        if (t.out_chop_prob > 0.0f && !t.dynamic) {
           launchFlipChoppers(chop_out_, d_size_, t.out_chop_prob, key_, call, s);
         }
         chop_passes_++;
@@ -1403,6 +1459,9 @@ void Tile::doTransfer(cudaStream_t s) {
       write_lr = t.step * gran;
     } else {
       launchTransferRead(w_fast_, col, d_size_, t_io_, key_, call, onehot_, x_size_, tread_, -1.0f, s);
+    }
+    if (skip_write) {
+      continue;
     }
     UpdateProblem u{};
     u.x = onehot_;

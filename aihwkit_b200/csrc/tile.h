@@ -215,6 +215,16 @@ void launchTransferChopBuffer(float *buffer_col, float *read_inout, int d_size, 
                               float max_steps, float momentum, int forget_buffer, int no_buffer,
                               unsigned char *chop_in, int col, const unsigned char *chop_out,
                               int flip_in, cudaStream_t stream);
+// Dynamic transfer: as above, with the read taken against the reference mean of the element
+// (replaced by its running mean when the in chopper of the line flipped at the previous
+// transfer), the running mean advanced by the read, and the buffer clamped to +-buffer_cap
+// (DynamicTransferRPUDevice::readAndUpdate, rpu_dynamic_transfer_device.cpp:198-343)
+void launchTransferDynamicBuffer(float *buffer_col, float *mean_col, float *past_col,
+                                 float *read_inout, int d_size, float lr_scale, float max_steps,
+                                 float momentum, int forget_buffer, float buffer_cap,
+                                 float sample_momentum, int previously_switched,
+                                 unsigned char *chop_in, int col, const unsigned char *chop_out,
+                                 int flip_in, cudaStream_t stream);
 // flip every out chopper with probability `prob`
 void launchFlipChoppers(unsigned char *chop, int n, float prob, PhiloxKey key, uint32_t call,
                         cudaStream_t stream);
@@ -370,6 +380,10 @@ private:
   float *delta_w_ = nullptr; // caller-owned target of the update in delta-weight mode
   float *w_fast_ = nullptr; // Transfer: fast (hidden) tile A, [x][d]
   float *t_buffer_ = nullptr; // buffered Transfer: digital buffer per element, [x][d]
+  // dynamic Transfer: running mean of the reads and the reference mean per element, [x][d];
+  // per line, whether its in chopper flipped at its previous transfer
+  float *t_mean_ = nullptr, *t_past_ = nullptr;
+  std::vector<unsigned char> chop_switched_;
   DeviceStore dev_[2];
   int n_dev_ = 1;
   // Transfer counters (rpu_transfer_device.cpp:396-516, rpu_vector_device.cpp:513-526)

@@ -1266,6 +1266,51 @@ __global__ void __launch_bounds__(256)
 }
 
 __global__ void __launch_bounds__(256)
+    transferDynamicBufferKernel(float *buffer_col, float *mean_col, float *past_col, float *read_inout,
+                                int d_size, float lr_scale, float max_steps, float momentum,
+                                int forget_buffer, float buffer_cap, float sample_momentum,
+                                int previously_switched, unsigned char *chop_in, int col,
+                                const unsigned char *chop_out, int flip_in) {
+  pdlEnter();
+  // one CTA: the in chopper of the column is read by all threads before thread 0 flips it
+  const bool in_chop = chop_in[col] != 0;
+  const float keep = 1.0f - sample_momentum, forget = 1.0f - momentum;
+  for (int t = threadIdx.x; t < d_size; t += blockDim.x) {
+    const float val = read_inout[t];
+    float omega = buffer_col[t];
+    float mu_past = past_col[t];
+    const float mean = mean_col[t];
+    if (previously_switched) {
+      // a new chopper phase: the mean of the phase that ended becomes the reference
+      mu_past = mean;
+      past_col[t] = mean;
+    }
+    float dw = __fsub_rn(val, mu_past);
+    dw = (in_chop != (chop_out[t] != 0)) ? -dw : dw;
+    omega = __fadd_rn(omega, __fmul_rn(dw, lr_scale));
+    float n = 0.0f;
+    if (fabsf(omega) >= 1.0f) {
+      n = fmaxf(fminf(truncf(omega), max_steps), -max_steps);
+      if (forget_buffer) {
+        omega = __fmul_rn(omega, momentum);
+      } else {
+        omega = __fsub_rn(omega, __fmul_rn(forget, n));
+        if (buffer_cap > 0.0f) {
+          omega = fminf(fmaxf(omega, -buffer_cap), buffer_cap);
+        }
+      }
+    }
+    buffer_col[t] = omega;
+    read_inout[t] = -n;
+    mean_col[t] = __fadd_rn(__fmul_rn(mean, keep), __fmul_rn(val, sample_momentum));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && flip_in) {
+    chop_in[col] = in_chop ? 0 : 1;
+  }
+}
+
+__global__ void __launch_bounds__(256)
     flipChoppersKernel(unsigned char *chop, int n, float prob, PhiloxKey key, uint32_t call) {
   pdlEnter();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1286,6 +1331,19 @@ void launchTransferChopBuffer(float *buffer_col, float *read_inout, int d_size, 
   AB200_CUDA(launchChained(transferChopBufferKernel, dim3(1), dim3(256), 0, stream, buffer_col, read_inout,
                            d_size, lr_scale, max_steps, momentum, forget_buffer, no_buffer, chop_in, col,
                            chop_out, flip_in));
+  AB200_LAUNCH_CHECK();
+}
+
+void launchTransferDynamicBuffer(float *buffer_col, float *mean_col, float *past_col,
+                                 float *read_inout, int d_size, float lr_scale, float max_steps,
+                                 float momentum, int forget_buffer, float buffer_cap,
+                                 float sample_momentum, int previously_switched,
+                                 unsigned char *chop_in, int col, const unsigned char *chop_out,
+                                 int flip_in, cudaStream_t stream) {
+  AB200_CUDA(launchChained(transferDynamicBufferKernel, dim3(1), dim3(256), 0, stream, buffer_col, mean_col,
+                           past_col, read_inout, d_size, lr_scale, max_steps, momentum, forget_buffer,
+                           buffer_cap, sample_momentum, previously_switched, chop_in, col, chop_out,
+                           flip_in));
   AB200_LAUNCH_CHECK();
 }
 

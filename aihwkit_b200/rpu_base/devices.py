@@ -8,9 +8,9 @@ reference's meta-parameter structs (``src/rpucuda/rpu_pulsed_meta_parameter.h:18
 ``rpu_transfer_device.h:52-75``).  ``AnalogTileParameter.create_array`` is the factory the
 reference exposes at ``rpu_base_devices.cpp:453-467``.
 
-Also provided: ExpStep, PowStep and the buffered transfer (Tiki-Taka v2).  Other devices
-(PiecewiseStep, MixedPrec, OneSided, Chopped / Dynamic transfer, ...) are not; there is no class
-for them here.
+Also provided: ExpStep, PowStep, PiecewiseStep and the buffered, chopped and dynamic transfer
+compounds (Tiki-Taka v2 to v4).  Other devices (MixedPrec, OneSided, Vector, ...) are not; there
+is no class for them here.
 """
 
 from __future__ import annotations
@@ -665,6 +665,31 @@ class ChoppedTransferResistiveDeviceParameter(BufferedTransferResistiveDevicePar
         c.out_chop_prob = float(self.out_chop_prob)
         c.auto_granularity = float(self.auto_granularity)
         c.buffer_granularity = float(self.buffer_granularity)
+        return c
+
+
+class DynamicTransferResistiveDeviceParameter(ChoppedTransferResistiveDeviceParameter):
+    """DynamicTransferRPUDeviceMetaParameter, Tiki-Taka with choppers and a running-mean reference
+    (rpu_base_devices.cpp:912-924; src/rpucuda/rpu_dynamic_transfer_device.h:26-62)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.in_chop_random = False  # initDefaults (rpu_dynamic_transfer_device.h:61)
+        self.tail_weightening = 1.0
+        self.buffer_cap = 10.0
+        self.experimental_correct_accumulation = False
+
+    def _to_c(self) -> _cabi.TransferParams:
+        if float(self.in_chop_prob) <= 0.0:
+            # DynamicTransferRPUDeviceMetaParameter::checkSupported (rpu_dynamic_transfer_device.cpp:38-49)
+            raise RuntimeError("In chopper prob needs to be positive.")
+        if not 0.0 < float(self.auto_momentum) < 1.0:
+            raise RuntimeError("Auto-momentum needs to be smaller than 1 and larger than 0.")
+        c = super()._to_c()
+        c.dynamic = 1
+        c.correct_accumulation = int(bool(self.experimental_correct_accumulation))
+        c.tail_weightening = float(self.tail_weightening)
+        c.buffer_cap = float(self.buffer_cap)
         return c
 
 

@@ -273,6 +273,20 @@ typedef struct ab200_transfer_params {
   float out_chop_prob;
   float auto_granularity;
   float buffer_granularity;
+  /* DynamicTransferRPUDeviceMetaParameter (Tiki-Taka with choppers and a dynamically estimated
+   * reference, src/rpucuda/rpu_dynamic_transfer_device.h:26-36; needs chopped = 1 and
+   * in_chop_prob > 0): every element keeps a running mean of its reads (weight of a new read
+   * min(tail_weightening / n_samples, 1), n_samples = max(ceil(1 / in_chop_prob), 2)); when the
+   * in chopper of a line has flipped, the mean becomes the reference that later reads of the
+   * line are taken against. Writes start after n_samples passes over the matrix. With
+   * forget_buffer = 0 the buffer is clamped to buffer_cap * desired_bl of the transfer update
+   * (buffer_cap <= 0: no clamp). correct_accumulation divides the transfer scale by
+   * min(sample index within the chopper period, 1 / fast granularity). The reference's
+   * experimental_fast_lr_feedback (not reachable through its Python bindings) is not built. */
+  int32_t dynamic;
+  int32_t correct_accumulation;
+  float tail_weightening;
+  float buffer_cap;
 } ab200_transfer_params;
 
 /* Everything PulsedMetaParameter::createRPUArray needs

@@ -14,6 +14,7 @@
 #include "dense_bit_line_maker.h"
 #include "rpu_buffered_transfer_device.h"
 #include "rpu_chopped_transfer_device.h"
+#include "rpu_dynamic_transfer_device.h"
 #include "rpu_constantstep_device.h"
 #include "rpu_expstep_device.h"
 #include "rpu_linearstep_device.h"
@@ -225,7 +226,16 @@ int ref_tile_create(const ab200_tile_config *cfg, void **out) {
   if (cfg->device_kind == AB200_DEVICE_TRANSFER) {
     std::unique_ptr<TransferRPUDeviceMetaParameter<float>> tp;
     if (cfg->transfer.chopped) {
-      auto cp = std::make_unique<ChoppedTransferRPUDeviceMetaParameter<float>>();
+      std::unique_ptr<ChoppedTransferRPUDeviceMetaParameter<float>> cp;
+      if (cfg->transfer.dynamic) {
+        auto yp = std::make_unique<DynamicTransferRPUDeviceMetaParameter<float>>();
+        yp->tail_weightening = cfg->transfer.tail_weightening;
+        yp->buffer_cap = cfg->transfer.buffer_cap;
+        yp->experimental_correct_accumulation = cfg->transfer.correct_accumulation != 0;
+        cp = std::move(yp);
+      } else {
+        cp = std::make_unique<ChoppedTransferRPUDeviceMetaParameter<float>>();
+      }
       cp->thres_scale = cfg->transfer.thres_scale;
       cp->step = cfg->transfer.step;
       cp->momentum = cfg->transfer.momentum;

@@ -173,3 +173,16 @@ def chopped_transfer_device(seed: int = 21, transfer_every: float = 1.0, in_chop
     dp.transfer_forward.out_noise = 0.0
     dp.transfer_forward.bound_management = D.BoundManagementType.Iterative
     return dp
+
+
+def dynamic_transfer_device(in_chop_prob: float = 0.5, tail_weightening: float = 1.0,
+                            buffer_cap: float = 10.0, correct_accumulation: bool = False, **kw):
+    """Tiki-Taka with choppers and a running-mean reference: DynamicTransferCompound of two
+    noise-free SoftBoundsReference devices, regular in-chopper schedule."""
+    base = chopped_transfer_device(in_chop_prob=in_chop_prob, in_chop_random=False, **kw)
+    dp = D.DynamicTransferResistiveDeviceParameter()
+    for k, v in vars(base).items():
+        setattr(dp, k, v)
+    dp.tail_weightening, dp.buffer_cap = tail_weightening, buffer_cap
+    dp.experimental_correct_accumulation = correct_accumulation
+    return dp

@@ -549,6 +549,57 @@ def test_chopped_transfer_deterministic_against_reference(kw):
     assert moved and np.abs(hr[ia]).max() > 0
 
 
+@pytest.mark.parametrize("kw", [
+    dict(),                                               # period of two passes
+    dict(in_chop_prob=0.3, tail_weightening=2.5),         # period of four passes, heavier tail
+    dict(momentum=0.2, forget_buffer=False, buffer_cap=0.5, buffer_granularity=0.5),
+    dict(correct_accumulation=True, in_chop_prob=0.25, correct_gradient_magnitudes=True),
+])
+def test_dynamic_transfer_deterministic_against_reference(kw):
+    """Tiki-Taka with choppers and a running-mean reference
+    (src/rpucuda/rpu_dynamic_transfer_device.cpp:198-343) with deterministic pulses and the
+    regular chopper schedule: fast tile, buffer, running mean, reference mean and visible weights
+    follow the compiled reference update by update; writes start after the first chopper period."""
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    if not ref.available():
+        pytest.skip("compiled reference not built")
+    rng = np.random.default_rng(23)
+    x_size, d_size, m = 6, 10, 5
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.dynamic_transfer_device(transfer_lr=4.0, **kw)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    rt = ref.RefTile(cfg)
+    names = t.get_hidden_parameter_names()
+    assert names == rt.hidden_parameter_names()
+    assert names[-3:] == ["buffered_FP_weight", "running_mean_weight", "past_mean_weight"]
+    assert np.array_equal(t.get_hidden_parameters().numpy(), rt.get_hidden_parameters())
+    ia = names.index("hidden_weights_0")
+    lr = 0.1
+    t.set_learning_rate(lr)
+    rt.set_learning_rate(lr)
+    moved = False
+    for step in range(16):
+        x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        d = rng.normal(0, 0.5, (m, d_size)).astype(np.float32)
+        t.update(torch.from_numpy(x).cuda(), torch.from_numpy(d).cuda())
+        rt.update(x, d)
+        hp, hr = t.get_hidden_parameters().numpy(), rt.get_hidden_parameters()
+        assert np.abs(hp[ia] - hr[ia]).max() <= 1e-6, f"fast tile, update {step}"
+        for q, name in enumerate(names[-3:]):
+            assert np.abs(hp[-3 + q] - hr[-3 + q]).max() <= 1e-4, f"{name}, update {step}"
+        assert np.abs(t.get_weights().numpy() - rt.get_weights()).max() <= 1e-6, f"weights, update {step}"
+        moved = moved or np.abs(rt.get_weights()).max() > 0
+    assert moved and np.abs(hr[-1]).max() > 0 and np.abs(hr[-2]).max() > 0
+    # the three digital planes travel with the hidden parameters
+    t2 = T.AnalogTile(cfg, cuda_device=0)
+    t2.set_weights(t.get_weights())
+    t2.set_hidden_parameters(t.get_hidden_parameters())
+    assert torch.equal(t2.get_hidden_parameters(), t.get_hidden_parameters())
+
+
 def test_chopped_transfer_random_choppers_statistics():
     """Random in / out chopper flips: the slow tile still integrates the gradient (the de-chopped
     read has the sign of the accumulated gradient whatever the chopper history)."""
