@@ -5,11 +5,15 @@
 // updateIndexed (src/rpucuda/rpu.cpp:846-1013, 1117-1239); the reference GPU reads through
 // iterators instead (src/rpucuda/cuda/io_iterator.h:194-303).
 //
-// Here the gather writes the sample-major matrix [dim3 * m_batch][x_size] that the MVM and
-// update kernels read (row = one output position of one image), so the tensor-core path with
-// its TMA-tiled operands applies unchanged; the image-major output layout [dim3][d_size][m_batch]
-// is produced by a batched transpose.
+// Here the forward pass on the tensor-core path and the pulsed update read the images through
+// the index array themselves (the DAC kernel and the pulse-preparation kernel gather a row each,
+// RowGather in tile.h), so the unfolded matrix is never written; other cases (CUDA-core MVM,
+// floating-point update) and the backward pass go through the sample-major matrix
+// [dim3 * m_batch][x_size] (row = one output position of one image). The image-major output
+// layout [dim3][d_size][m_batch] is produced by a batched transpose.
 #include "tile.h"
+
+#include <cstdlib>
 
 namespace ab200 {
 
@@ -154,6 +158,7 @@ void Tile::setMatrixIndices(const int32_t *indices, long long n, cudaStream_t s)
   }
   idx_count_ = n;
   idx_max_ = hi;
+  idx_t_valid_ = false;
 }
 
 void Tile::requireIndices(const char *what, long long image_size, int m_batch, int n_img) const {
@@ -176,17 +181,57 @@ void Tile::requireIndices(const char *what, long long image_size, int m_batch, i
   }
 }
 
-void Tile::ensureIndexedScratch(long long b) {
-  if (b > cols_cap_) {
+void Tile::ensureIndexedScratch(long long b, bool need_x, bool need_d) {
+  if (need_x && b > cols_x_cap_) {
     if (cols_x_) {
+      AB200_CUDA(cudaDeviceSynchronize());
       AB200_CUDA(cudaFree(cols_x_));
-      AB200_CUDA(cudaFree(cols_d_));
-      cols_x_ = cols_d_ = nullptr;
+      cols_x_ = nullptr;
     }
     AB200_CUDA(cudaMalloc(&cols_x_, (size_t)b * x_size_ * sizeof(float)));
-    AB200_CUDA(cudaMalloc(&cols_d_, (size_t)b * d_size_ * sizeof(float)));
-    cols_cap_ = b;
+    cols_x_cap_ = b;
   }
+  if (need_d && b > cols_d_cap_) {
+    if (cols_d_) {
+      AB200_CUDA(cudaDeviceSynchronize());
+      AB200_CUDA(cudaFree(cols_d_));
+      cols_d_ = nullptr;
+    }
+    AB200_CUDA(cudaMalloc(&cols_d_, (size_t)b * d_size_ * sizeof(float)));
+    cols_d_cap_ = b;
+  }
+}
+
+const int32_t *Tile::rowMajorIndices(int m_batch, bool trans, cudaStream_t s) {
+  if (!trans) {
+    return idx_; // already [m_batch][x_size]
+  }
+  if (!idx_t_valid_) {
+    if (idx_count_ > idx_t_cap_) {
+      if (idx_t_) {
+        AB200_CUDA(cudaDeviceSynchronize());
+        AB200_CUDA(cudaFree(idx_t_));
+        idx_t_ = nullptr;
+      }
+      AB200_CUDA(cudaMalloc(&idx_t_, (size_t)idx_count_ * sizeof(int32_t)));
+      idx_t_cap_ = idx_count_;
+    }
+    // [x_size][m_batch] -> [m_batch][x_size]; the entries are moved as 32-bit words
+    launchBatchedTranspose(reinterpret_cast<const float *>(idx_), reinterpret_cast<float *>(idx_t_), x_size_,
+                           m_batch, 1, s);
+    idx_t_valid_ = true;
+  }
+  return idx_t_;
+}
+
+bool Tile::updateGatherEligible() const {
+  static const bool off = [] {
+    const char *e = getenv("AB200_INDEXED_GATHER");
+    return e && e[0] == '0';
+  }();
+  // the pulse-preparation kernel is the only reader of x on the pulsed path
+  return !off && cfg_.device_kind != AB200_DEVICE_IDEAL && up_.pulse_type != AB200_PULSE_NONE &&
+         up_.pulse_type != AB200_PULSE_NONE_WITH_DEVICE && delta_w_ == nullptr;
 }
 
 void Tile::gatherIndexed(const float *x, long long in_mat, int m_batch, int n_img, bool trans,
@@ -211,13 +256,22 @@ void Tile::forwardIndexed(const float *x, float *d, long long total_input_size, 
   if (b > 0x7fffffffLL) {
     AB200_FATAL("forward_indexed: m_batch * dim3 does not fit an int");
   }
-  ensureIndexedScratch(b);
-  gatherIndexed(x, in_mat, m_batch, n_img, trans, s);
-  if (trans) {
-    forward(cols_x_, cols_d_, false, (int)b, false, false, is_test, s);
-    launchBatchedTranspose(cols_d_, d, m_batch, d_size_, n_img, s); // -> [dim3][d_size][m_batch]
+  const bool fused = forwardGatherEligible((int)b);
+  ensureIndexedScratch(b, !fused, trans);
+  float *rows_out = trans ? cols_d_ : d;
+  if (fused) {
+    RowGather g;
+    g.idx = rowMajorIndices(m_batch, trans, s);
+    g.m_batch = m_batch;
+    g.ld = x_size_;
+    g.image_size = in_mat;
+    forwardGathered(x, g, rows_out, (int)b, is_test, s);
   } else {
-    forward(cols_x_, d, false, (int)b, false, false, is_test, s);
+    gatherIndexed(x, in_mat, m_batch, n_img, trans, s);
+    forward(cols_x_, rows_out, false, (int)b, false, false, is_test, s);
+  }
+  if (trans) {
+    launchBatchedTranspose(cols_d_, d, m_batch, d_size_, n_img, s); // -> [dim3][d_size][m_batch]
   }
 }
 
@@ -230,7 +284,7 @@ void Tile::backwardIndexed(const float *d, float *x, long long total_output_size
   if (b > 0x7fffffffLL) {
     AB200_FATAL("backward_indexed: m_batch * dim3 does not fit an int");
   }
-  ensureIndexedScratch(b);
+  ensureIndexedScratch(b, true, trans);
   const float *src = d;
   if (trans) {
     launchBatchedTranspose(d, cols_d_, d_size_, m_batch, n_img, s); // -> [dim3][m_batch][d_size]
@@ -258,14 +312,29 @@ void Tile::updateIndexed(const float *x, const float *d, long long total_input_s
   if (b > 0x7fffffffLL) {
     AB200_FATAL("update_indexed: m_batch * dim3 does not fit an int");
   }
-  ensureIndexedScratch(b);
-  gatherIndexed(x, in_mat, m_batch, n_img, trans, s);
+  const bool fused = updateGatherEligible();
+  ensureIndexedScratch(b, !fused, trans);
   const float *src = d;
   if (trans) {
     launchBatchedTranspose(d, cols_d_, d_size_, m_batch, n_img, s);
     src = cols_d_;
   }
-  update(cols_x_, src, false, (int)b, false, false, s);
+  if (fused) {
+    upd_gather_.idx = rowMajorIndices(m_batch, trans, s);
+    upd_gather_.m_batch = m_batch;
+    upd_gather_.ld = x_size_;
+    upd_gather_.image_size = in_mat;
+    try {
+      update(x, src, false, (int)b, false, false, s);
+    } catch (...) {
+      upd_gather_ = RowGather{};
+      throw;
+    }
+    upd_gather_ = RowGather{};
+  } else {
+    gatherIndexed(x, in_mat, m_batch, n_img, trans, s);
+    update(cols_x_, src, false, (int)b, false, false, s);
+  }
 }
 
 } // namespace ab200

@@ -366,6 +366,7 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
     }
     float sval = p.sval[r];
     const float *row = p.in + (long long)r * p.in_ss;
+    const bool gathered = p.gather.idx != nullptr; // rows read through an index array
     float reduction = 1.0f;
     float scale = 1.0f;
     int round = 0;
@@ -378,7 +379,8 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
         // halving again from there (rpu_forward_backward_pass.cpp:945-950)
         NmStats st;
         for (int k = threadIdx.x; k < K; k += blockDim.x) {
-          st.add(k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f);
+          st.add(gathered ? gatherRowElement(p.gather, p.in, r, k)
+                          : (k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f));
         }
         st.warpReduce();
         __shared__ float st_sh[8][3];
@@ -402,8 +404,9 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
       const ElemRng g{p.key, p.call, TAG_FWD_IN + p.noise_id + (uint32_t)round * 0x10000u};
       float nacc = 0.0f;
       for (int k = threadIdx.x; k < K; k += blockDim.x) {
-        float v = prepareInput(io, k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f, scale, g,
-                               (uint32_t)r, (uint32_t)k);
+        const float xin = gathered ? gatherRowElement(p.gather, p.in, r, k)
+                                   : (k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f);
+        float v = prepareInput(io, xin, scale, g, (uint32_t)r, (uint32_t)k);
         v_sh[k] = v;
         nacc = fmaf(v, v, nacc);
       }

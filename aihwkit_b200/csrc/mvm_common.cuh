@@ -9,6 +9,13 @@
 
 namespace ab200 {
 
+// element k of gathered row r (RowGather, tile.h)
+__device__ __forceinline__ float gatherRowElement(const RowGather &g, const float *images, int r, int k) {
+  const int n = r / g.m_batch, l = r - n * g.m_batch;
+  const int j = __ldg(g.idx + (long long)l * g.ld + k);
+  return j <= 1 ? (float)j : __ldg(images + (long long)n * g.image_size + (j - 2));
+}
+
 // Per-sample statistics of the raw input that the noise-management types need.
 struct NmStats {
   float amax = 0.0f;      // max |x|

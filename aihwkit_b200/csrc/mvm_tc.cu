@@ -928,6 +928,10 @@ struct DacParams {
   int backward;
   float code_bound; // largest |code| = inp_bound / res_in
   float inv_res_in; // 1 / res_in: first guess of the DAC code
+  // rows gathered from whole images at `in` (null index: plain rows); row 0 of this launch is
+  // row g_row0 of the gathered batch
+  RowGather gather;
+  int g_row0;
 };
 
 // rint((x * scale) / res_in), clipped: the reference's DAC in its own association. The division is
@@ -1177,6 +1181,95 @@ __global__ void __launch_bounds__(256) dacQuantizeLongRowKernel(DacParams p) {
   }
 }
 
+// Rows gathered from whole images through the index array of the indexed convolution interface:
+// one warp per (row, in-split). The gathered values are staged in the warp's slice of shared
+// memory between the abs-max pass and the quantisation, so every index and image element is read
+// once and the sample-major matrix of the unfolded images never exists in HBM.
+constexpr int kGatherWarps = 4;
+__global__ void __launch_bounds__(kGatherWarps * 32) dacQuantizeGatherKernel(DacParams p) {
+  pdlEnter();
+  extern __shared__ __align__(16) float g_sh[]; // [kGatherWarps][kpad]
+  const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)p.m * p.I) {
+    return;
+  }
+  const int i = (int)(wid / p.m), row = (int)(wid % p.m);
+  const int4 is = p.insplit[i];
+  const int K = is.z;
+  const int grow = p.g_row0 + row;
+  const int n = grow / p.gather.m_batch, l = grow - n * p.gather.m_batch;
+  const int32_t *ix = p.gather.idx + (long long)l * p.gather.ld + is.w;
+  const float *img = p.in + (long long)n * p.gather.image_size;
+  float *sh = g_sh + (threadIdx.x >> 5) * p.kpad;
+  const IOEff &io = p.io;
+  float amax = 0.0f;
+  // eight index loads, then eight image loads in flight per lane: the two dependent loads of an
+  // element are latency, not bandwidth
+  constexpr int kU = 8;
+  for (int k0 = lane; k0 < p.kpad; k0 += 32 * kU) {
+    int j[kU];
+#pragma unroll
+    for (int u = 0; u < kU; u++) {
+      const int k = k0 + 32 * u;
+      j[u] = k < K ? __ldg(ix + k) : 0;
+    }
+    float v[kU];
+#pragma unroll
+    for (int u = 0; u < kU; u++) {
+      v[u] = j[u] <= 1 ? (float)j[u] : __ldg(img + (j[u] - 2));
+    }
+#pragma unroll
+    for (int u = 0; u < kU; u++) {
+      const int k = k0 + 32 * u;
+      if (k < p.kpad) {
+        sh[k] = v[u];
+      }
+      amax = fmaxf(amax, fabsf(v[u]));
+    }
+  }
+  if (io.nm == AB200_NM_ABS_MAX) {
+    for (int o = 16; o > 0; o >>= 1) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    }
+  } else {
+    amax = 0.0f;
+  }
+  __syncwarp();
+  const float sval = nmValue(io, amax);
+  const float scale = inputScale(io, sval, 1.0f, !p.backward);
+  __nv_bfloat16 *c = p.codes + (long long)row * p.codes_ld + is.x;
+  float acc = 0.0f;
+  const int KP4 = p.kpad >> 2;
+  const float4 *sh4 = reinterpret_cast<const float4 *>(sh);
+#pragma unroll 2
+  for (int k = lane; k < KP4; k += 32) {
+    float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
+    if (scale != 0.0f) {
+      const float4 v = sh4[k]; // zero beyond K: code 0
+      c0 = dacCode(p, v.x, scale);
+      c1 = dacCode(p, v.y, scale);
+      c2 = dacCode(p, v.z, scale);
+      c3 = dacCode(p, v.w, scale);
+    }
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(c0, c1), hi = __floats2bfloat162_rn(c2, c3);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const uint32_t *>(&lo);
+    pk.y = *reinterpret_cast<const uint32_t *>(&hi);
+    *reinterpret_cast<uint2 *>(c + 4 * k) = pk;
+    acc = fmaf(c0, c0, acc);
+    acc = fmaf(c1, c1, acc);
+    acc = fmaf(c2, c2, acc);
+    acc = fmaf(c3, c3, acc);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  }
+  if (lane == 0) {
+    dacRowScalars(p, i, row, sval, scale, acc);
+  }
+}
+
 // B[n][k] = w[k * wk + n * wn]  ->  bf16 hi, lo at row (row0 + n) of the padded operand
 __global__ void __launch_bounds__(256)
     splitWeightsKernel(const float *w, long long wk, long long wn, int N, int K, __nv_bfloat16 *hi,
@@ -1265,6 +1358,12 @@ bool TcEngine::codesSupported(const IOEff &io) {
                      (io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f);
   const float bc = io.out_bound / io.res_out;
   return noisy && bc <= 127.0f && fabsf(bc - rintf(bc)) < 1e-3f;
+}
+
+bool TcEngine::gatherSupported(int in_size) {
+  // kGatherWarps rows of the padded width, fp32, in the shared memory of one CTA
+  const size_t kpad = ((size_t)in_size + 63) / 64 * 64;
+  return kGatherWarps * kpad * sizeof(float) <= 200 * 1024;
 }
 
 bool TcEngine::ioSupported(const IOEff &io) {
@@ -1528,6 +1627,22 @@ void TcEngine::launchDac(const Run &r, int row0, int rows, cudaStream_t s) {
   d.backward = r.backward ? 1 : 0;
   d.code_bound = rintf(r.io.inp_bound / r.io.res_in);
   d.inv_res_in = 1.0f / r.io.res_in;
+  if (r.gather.idx != nullptr) {
+    d.in = r.in;
+    d.gather = r.gather;
+    d.g_row0 = row0;
+    const size_t smem = (size_t)kGatherWarps * kpad_ * sizeof(float);
+    if (smem > 48 * 1024 && smem > gather_smem_raised_) {
+      AB200_CUDA(cudaFuncSetAttribute(dacQuantizeGatherKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+      gather_smem_raised_ = smem;
+    }
+    const long long warps = (long long)rows * I;
+    AB200_CUDA(launchChained(dacQuantizeGatherKernel, dim3((unsigned)((warps + kGatherWarps - 1) / kGatherWarps)),
+                             dim3(kGatherWarps * 32), smem, s, d));
+    AB200_LAUNCH_CHECK();
+    return;
+  }
   bool vec = (((uintptr_t)d.in) & 15) == 0 && (r.in_ss & 3) == 0;
   for (int i = 0; i < I && vec; i++) {
     vec = (in_off_[i] & 3) == 0 && (in_sizes_[i] & 3) == 0;

@@ -30,6 +30,8 @@ public:
   struct Run {
     const float *in = nullptr; // [m][*], row stride in_ss, in-split i starts at column in_off[i]
     long long in_ss = 0;
+    // rows gathered from whole images at `in` (indexed convolution interface) instead
+    RowGather gather;
     int m = 0;
     float *out = nullptr; // [m][N_total], row stride out_ss
     long long out_ss = 0;
@@ -85,6 +87,9 @@ public:
 
   // whether the IO settings can be expressed as integer DAC codes in bf16
   static bool ioSupported(const IOEff &io);
+  // whether rows of this engine's width can be gathered through an index array by the DAC pass
+  // (its shared-memory staging of one row per warp must fit)
+  static bool gatherSupported(int in_size);
   // whether, in addition, every in-split's result can leave the kernel as signed-byte ADC codes
   static bool codesSupported(const IOEff &io);
   // throws if an earlier launch reported a device-side failure (timeout of a bounded wait)
@@ -103,6 +108,7 @@ private:
 
   int n_sm_ = 0;
   unsigned smem_raised_ = 0; // kernel variants whose shared-memory limit is set
+  size_t gather_smem_raised_ = 0; // shared-memory limit set for the gathering DAC kernel
   int device_;
   std::vector<int> in_sizes_, out_sizes_, in_off_, out_off_;
   int kpad_ = 0;      // padded K of every in-split (multiple of 64)

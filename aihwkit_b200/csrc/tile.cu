@@ -557,6 +557,7 @@ Tile::~Tile() {
     cudaFree(t_mean_);
     cudaFree(t_past_);
     cudaFree(idx_);
+    cudaFree(idx_t_);
     cudaFree(cols_x_);
     cudaFree(cols_d_);
     cudaFree(stage_dev_);
@@ -1180,6 +1181,53 @@ void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, boo
   }
 }
 
+// Forward pass over rows that the DAC kernel gathers from whole images (indexed convolution
+// interface): the tensor-core path of forward() with the unfolded matrix left out.
+bool Tile::forwardGatherEligible(int b) const {
+  static const bool off = [] {
+    const char *e = getenv("AB200_INDEXED_GATHER");
+    return e && e[0] == '0';
+  }();
+  MvmProblem p{};
+  p.in_fs = p.out_fs = 1;
+  p.in_size = p.in_real = x_size_;
+  p.out_size = p.out_store = d_size_;
+  p.m = b;
+  p.io = f_io_;
+  return !off && tcEligible(p) && TcEngine::gatherSupported(x_size_);
+}
+
+void Tile::forwardGathered(const float *images, const RowGather &g, float *d, int b, bool is_test,
+                           cudaStream_t s) {
+  MvmProblem p{};
+  p.in = images;
+  p.gather = g;
+  p.in_ss = x_size_;
+  p.in_fs = 1;
+  p.in_size = x_size_;
+  p.in_real = x_size_;
+  p.out = d;
+  p.out_ss = d_size_;
+  p.out_fs = 1;
+  p.out_size = d_size_;
+  p.out_store = d_size_;
+  p.accumulate = 0;
+  p.w = fbWeights(is_test);
+  p.wk = d_size_;
+  p.wn = 1;
+  p.m = b;
+  p.backward = 0;
+  p.io = f_io_;
+  setLineTables(p, f_lt_, f_onv_);
+  p.alpha = 1.0f;
+  p.call = fwd_calls_++;
+  p.noise_id = 0;
+  fillMvmScratch(p);
+  AB200_CUDA(cudaMemsetAsync(bm_stats_, 0, 2 * sizeof(int), s));
+  runTc(p, s);
+  launchBmRerun(p, s);
+}
+
 void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_ss, int m,
                           bool accumulate, uint32_t noise_id, float out_scale, cudaStream_t s) {
   requireDevice("forward");
@@ -1319,6 +1367,7 @@ void Tile::runTc(const MvmProblem &p, cudaStream_t s) {
   TcEngine::Run r;
   r.in = p.in;
   r.in_ss = p.in_ss;
+  r.gather = p.gather;
   r.m = p.m;
   r.out = p.out;
   r.out_ss = p.out_ss;
@@ -1595,6 +1644,7 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
     u.chop_x = chop_in_;
     u.chop_d = chop_out_;
   }
+  u.gather = upd_gather_;
   launchPulsePrepare(u, s);
   const bool stream_upd = streamUpdateEligible(u);
   const int m_pad = (m * u.nseg + 31) / 32 * 32;

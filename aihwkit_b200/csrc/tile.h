@@ -77,6 +77,17 @@ struct UpEff {
 UpEff resolveUp(const ab200_update_params &up);
 
 // One IO-managed matrix-vector batch: out[s][n] = IO( sum_k in[s][k] * W(k, n) ).
+// Rows read through the index array of the indexed convolution interface instead of from a
+// matrix: row r is output position l = r % m_batch of image n = r / m_batch, its element k is
+// element idx[l * ld + k] - 2 of that image (entry 0: padding, reads as 0; entry 1: the constant
+// input of an analog bias, reads as 1). `idx` is null for plain rows.
+struct RowGather {
+  const int32_t *idx = nullptr; // [m_batch][ld]
+  int m_batch = 0;
+  int ld = 0;
+  long long image_size = 0; // elements between two images
+};
+
 struct MvmProblem {
   const float *in;
   long long in_ss, in_fs; // strides of sample / feature
@@ -113,6 +124,8 @@ struct MvmProblem {
   const float *v_offset = nullptr;
   const float *out_nl = nullptr;
   float nl_factor = 1.0f;
+  // tensor-core path only: `in` holds whole images and the rows are gathered from them
+  RowGather gather;
 };
 
 // CUDA-core path: noise management, fused MVM, bound-management re-run
@@ -183,6 +196,8 @@ struct UpdateProblem {
   // of that line's pulses is flipped), or null
   const unsigned char *chop_x, *chop_d;
   int s_begin, s_end; // sample range applied by the update kernel
+  // pulsed update only: `x` holds whole images and the samples are gathered from them
+  RowGather gather;
 };
 
 void launchPulsePrepare(const UpdateProblem &p, cudaStream_t stream);
@@ -359,7 +374,15 @@ private:
   void ensurePar3(DeviceStore &ds);
   int opTargets(float *w[2], DeviceStore *ds[2]);
   void requireIndices(const char *what, long long image_size, int m_batch, int n_img) const;
-  void ensureIndexedScratch(long long b);
+  void ensureIndexedScratch(long long b, bool need_x, bool need_d);
+  // the index array as [m_batch][x_size] (transposed on the device when the caller's is
+  // [x_size][m_batch])
+  const int32_t *rowMajorIndices(int m_batch, bool trans, cudaStream_t s);
+  // whether the forward pass / the update of `b` gathered rows can read the images directly
+  bool forwardGatherEligible(int b) const;
+  bool updateGatherEligible() const;
+  void forwardGathered(const float *images, const RowGather &g, float *d, int b, bool is_test,
+                       cudaStream_t s);
   void gatherIndexed(const float *x, long long in_mat, int m_batch, int n_img, bool trans,
                      cudaStream_t s);
 
@@ -444,7 +467,13 @@ private:
   long long idx_cap_ = 0, idx_count_ = 0;
   int32_t idx_max_ = 0;
   float *cols_x_ = nullptr, *cols_d_ = nullptr;
-  long long cols_cap_ = 0;
+  long long cols_x_cap_ = 0, cols_d_cap_ = 0;
+  // the index array as [m_batch][x_size] for callers that hand it over as [x_size][m_batch]
+  // (built on the first such call after set_matrix_indices)
+  int32_t *idx_t_ = nullptr;
+  long long idx_t_cap_ = 0;
+  bool idx_t_valid_ = false;
+  RowGather upd_gather_; // set around an update whose samples are gathered from images
   unsigned char *clip_stats_ = nullptr; // statistics of clipWeights (sum, sum of squares, row maxima)
   // output block of a tile that adds to earlier in-splits under bound management
   float *acc_block_ = nullptr;

@@ -138,10 +138,18 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
   const float *xr = p.x + (long long)s * p.x_ss;
   const float *dr = p.d + (long long)s * p.d_ss;
   const bool need_max = p.up.update_management || p.up.update_bl_management;
+  // samples gathered from whole images (indexed convolution interface) or plain rows
+  const bool gathered = p.gather.idx != nullptr;
+  auto xValue = [&](int j) -> float {
+    if (gathered) {
+      return gatherRowElement(p.gather, p.x, s, j);
+    }
+    return j < p.x_real ? xr[(long long)j * p.x_fs] : 1.0f;
+  };
   float xm = 0.0f, dm = 0.0f;
   if (need_max) {
     for (int j = threadIdx.x; j < p.x_size; j += blockDim.x) {
-      xm = fmaxf(xm, fabsf(j < p.x_real ? xr[(long long)j * p.x_fs] : 1.0f));
+      xm = fmaxf(xm, fabsf(xValue(j)));
     }
     for (int i = threadIdx.x; i < p.d_size; i += blockDim.x) {
       dm = fmaxf(dm, fabsf(dr[(long long)i * p.d_fs]));
@@ -169,8 +177,7 @@ __global__ void __launch_bounds__(256) pulsePrepareKernel(UpdateProblem p) {
   for (int l = threadIdx.x; l < p.x_size + p.d_size; l += blockDim.x) {
     const bool is_x = l < p.x_size;
     const int idx = is_x ? l : l - p.x_size;
-    float v = is_x ? (idx < p.x_real ? xr[(long long)idx * p.x_fs] : 1.0f)
-                   : dr[(long long)idx * p.d_fs];
+    float v = is_x ? xValue(idx) : dr[(long long)idx * p.d_fs];
     const float P = is_x ? B : A;
     uint32_t word;
     if (implicit) {

@@ -62,10 +62,24 @@ def test_golden_indexed_conv():
     assert np.abs(t.get_weights().numpy() - g["w1"]).max() <= 1e-6
 
 
+@pytest.fixture
+def mvm_path(request):
+    """Kernel selection of the MVM for one test: 0 automatic, 2 tensor cores wherever possible."""
+    from aihwkit_b200 import _cabi
+
+    lib = _cabi.lib()
+    assert lib.ab200_set_mvm_path(request.param) == 0
+    yield request.param
+    lib.ab200_set_mvm_path(0)
+
+
 @pytest.mark.parametrize("trans", [True, False])
 @pytest.mark.parametrize("analog_bias", [False, True])
-def test_layouts_against_oracle(trans, analog_bias):
-    """Both index layouts through the C ABI (the Python binding only uses `trans`)."""
+@pytest.mark.parametrize("mvm_path", [0, 2], indirect=True)
+def test_layouts_against_oracle(trans, analog_bias, mvm_path):
+    """Both index layouts through the C ABI (the Python binding only uses `trans`); on the
+    tensor-core path the DAC kernel and the bound-management re-run gather the rows from the
+    images themselves, on the CUDA-core path the unfolded matrix is written first."""
     from aihwkit_b200 import _cabi
     from aihwkit_b200.rpu_base import tiles as T
     from oracle import analog_tile_oracle as O
