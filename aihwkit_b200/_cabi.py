@@ -50,6 +50,7 @@ class IOParams(C.Structure):
         ("out_nonlinearity", C.c_float),
         ("out_nonlinearity_std", C.c_float),
         ("slope_calibration", C.c_float),
+        ("mv_type", C.c_int32),
     ]
 
 

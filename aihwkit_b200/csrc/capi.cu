@@ -98,6 +98,7 @@ void ab200_default_io_params(ab200_io_params *io) {
   io->nm_decay = 1e-3f;
   io->ir_drop_g_ratio = 5.7143e5f;
   io->slope_calibration = 0.5f;
+  io->mv_type = AB200_MV_ONE_PASS;
   io->max_bm_res = 0.25f;
 }
 

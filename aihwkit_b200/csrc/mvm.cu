@@ -127,8 +127,14 @@ __global__ void nmAverageKernel(float *sval, int m, float decay, float *state) {
 // instead of a kernel of its own - sixteen threads per row reduce the row's statistics, every
 // column CTA of a row block repeats that (a few KB), and the first one leaves the per-row values
 // for the bound-management re-run. One launch less per pass where launches are what a pass costs.
-template <bool A_K_FAST, bool B_N_FAST, int T, bool PCM, bool NMF = false>
+// PN (with PCM): the negative and the positive prepared inputs accumulate separately, with the
+// norm of each half, and the epilogue runs the analog chain of the line once per half before it
+// adds them in front of (pos_neg = 1) or behind (pos_neg = 2) the output stage
+// (computeAnalogMV, rpu_forward_backward_pass.cpp:820-876).
+template <bool A_K_FAST, bool B_N_FAST, int T, bool PCM, bool NMF = false, bool PN = false>
 __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
+  static_assert(!PN || PCM, "separate passes use the line-chain variant");
+  constexpr int S = PN ? 2 : 1; // accumulator sets: [negative inputs, positive inputs] or one
   pdlEnter();
   constexpr int BM = 16 * T, BN = 16 * T;
   constexpr int BK = T == 1 ? 64 : (T == 2 ? 32 : 16);
@@ -189,17 +195,22 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
   }
   __syncthreads();
 
-  float acc[T][T];
-  float acc2[PCM ? T : 1][PCM ? T : 1], acc_c[PCM ? T : 1][PCM ? T : 1], acc_i[PCM ? T : 1][PCM ? T : 1];
+  float acc[S][T][T];
+  float acc2[S][PCM ? T : 1][PCM ? T : 1], acc_c[S][PCM ? T : 1][PCM ? T : 1], acc_i[S][PCM ? T : 1][PCM ? T : 1];
+  float vn2[S][PN ? T : 1]; // PN: squared norm of each half of the prepared input, per row
 #pragma unroll
-  for (int i = 0; i < T; i++) {
+  for (int h = 0; h < S; h++) {
 #pragma unroll
-    for (int j = 0; j < T; j++) {
-      acc[i][j] = 0.0f;
-      if (PCM) {
-        acc2[PCM ? i : 0][PCM ? j : 0] = 0.0f;
-        acc_c[PCM ? i : 0][PCM ? j : 0] = 0.0f;
-        acc_i[PCM ? i : 0][PCM ? j : 0] = 0.0f;
+    for (int i = 0; i < T; i++) {
+      vn2[h][PN ? i : 0] = 0.0f;
+#pragma unroll
+      for (int j = 0; j < T; j++) {
+        acc[h][i][j] = 0.0f;
+        if (PCM) {
+          acc2[h][PCM ? i : 0][PCM ? j : 0] = 0.0f;
+          acc_c[h][PCM ? i : 0][PCM ? j : 0] = 0.0f;
+          acc_i[h][PCM ? i : 0][PCM ? j : 0] = 0.0f;
+        }
       }
     }
   }
@@ -253,15 +264,23 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
         b[j] = Bs[kk][tx * T + j];
       }
 #pragma unroll
-      for (int i = 0; i < T; i++) {
+      for (int h = 0; h < S; h++) {
 #pragma unroll
-        for (int j = 0; j < T; j++) {
-          acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
-          if (PCM) {
-            const float ab = fabsf(b[j]);
-            acc2[PCM ? i : 0][PCM ? j : 0] = fmaf(a[i] * a[i], ab, acc2[PCM ? i : 0][PCM ? j : 0]);
-            acc_c[PCM ? i : 0][PCM ? j : 0] = fmaf(fabsf(a[i]), ab, acc_c[PCM ? i : 0][PCM ? j : 0]);
-            acc_i[PCM ? i : 0][PCM ? j : 0] = fmaf(a[i] * posw, b[j], acc_i[PCM ? i : 0][PCM ? j : 0]);
+        for (int i = 0; i < T; i++) {
+          // PN: half 0 takes the negative inputs, half 1 the positive ones
+          const float ah = PN ? (h == 0 ? fminf(a[i], 0.0f) : fmaxf(a[i], 0.0f)) : a[i];
+          if (PN) {
+            vn2[h][PN ? i : 0] = fmaf(ah, ah, vn2[h][PN ? i : 0]);
+          }
+#pragma unroll
+          for (int j = 0; j < T; j++) {
+            acc[h][i][j] = fmaf(ah, b[j], acc[h][i][j]);
+            if (PCM) {
+              const float ab = fabsf(b[j]);
+              acc2[h][PCM ? i : 0][PCM ? j : 0] = fmaf(ah * ah, ab, acc2[h][PCM ? i : 0][PCM ? j : 0]);
+              acc_c[h][PCM ? i : 0][PCM ? j : 0] = fmaf(fabsf(ah), ab, acc_c[h][PCM ? i : 0][PCM ? j : 0]);
+              acc_i[h][PCM ? i : 0][PCM ? j : 0] = fmaf(ah * posw, b[j], acc_i[h][PCM ? i : 0][PCM ? j : 0]);
+            }
           }
         }
       }
@@ -289,7 +308,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
     float y[T];
 #pragma unroll
     for (int j = 0; j < T; j++) {
-      y[j] = acc[i][j];
+      y[j] = acc[S - 1][i][j]; // PN: the positive half
     }
     bool exceeded = false;
     if (sc == 0.0f) {
@@ -306,33 +325,68 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
       const bool line_sigma = p.out_noise_vals != nullptr;
       const float vn = NMF ? 0.0f : p.vnorm[r];
       float sigma = PCM ? io.out_noise : outputSigma(io, vn);
+      const uint64_t blk = (uint64_t)r * n4 + (uint64_t)(c >> 2);
+      const bool w_draw = PCM && io.w_noise > 0.0f && io.w_noise_type != AB200_WNOISE_NONE;
       float z[4] = {0.f, 0.f, 0.f, 0.f};
       if (sigma > 0.0f || line_sigma) {
-        gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag, z);
+        gauss4(p.key, blk, p.call, tag, z);
       }
       float zw[4] = {0.f, 0.f, 0.f, 0.f};
-      if (PCM && io.w_noise > 0.0f && io.w_noise_type != AB200_WNOISE_NONE) {
+      if (w_draw) {
         // the weight noise enters before the non-linearity: a draw of its own
-        gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag ^ 0x04000000u, zw);
+        gauss4(p.key, blk, p.call, tag ^ 0x04000000u, zw);
       }
       float u[4] = {0.5f, 0.5f, 0.5f, 0.5f};
       if (io.out_sto_round) {
-        uniform4(p.key, (uint64_t)r * n4 + (uint64_t)(c >> 2), p.call, tag_u, u);
+        uniform4(p.key, blk, p.call, tag_u, u);
+      }
+      // PN: the draws of the pass over the negative inputs
+      float zn[4] = {0.f, 0.f, 0.f, 0.f}, zwn[4] = {0.f, 0.f, 0.f, 0.f}, un[4] = {0.5f, 0.5f, 0.5f, 0.5f};
+      if (PN) {
+        if (io.pos_neg == 2 && (sigma > 0.0f || line_sigma)) {
+          gauss4(p.key, blk, p.call, tag ^ 0x08000000u, zn);
+        }
+        if (w_draw) {
+          gauss4(p.key, blk, p.call, tag ^ 0x0c000000u, zwn);
+        }
+        if (io.pos_neg == 2 && io.out_sto_round) {
+          uniform4(p.key, blk, p.call, tag_u ^ 0x08000000u, un);
+        }
       }
       const LineChain lc{p.v_offset, p.out_nl, p.nl_factor, __fdiv_rn((float)K, io.ir_g_ratio)};
 #pragma unroll
       for (int j = 0; j < T; j++) {
         const int q = (c + j) & 3; // T divides 4 and c is a multiple of T: same block for all j
+        float yn = 0.0f;
         if (c + j < N) {
           if (line_sigma) {
             sigma = PCM ? p.out_noise_vals[c + j] : outputSigmaLine(io, vn, p.out_noise_vals, c + j, 0.0f);
           }
           if (PCM) {
-            y[j] = lineChain(io, lc, y[j], c + j, acc_c[PCM ? i : 0][PCM ? j : 0],
-                             acc_i[PCM ? i : 0][PCM ? j : 0], acc2[PCM ? i : 0][PCM ? j : 0], vn, zw[q]);
+            y[j] = lineChain(io, lc, y[j], c + j, acc_c[S - 1][PCM ? i : 0][PCM ? j : 0],
+                             acc_i[S - 1][PCM ? i : 0][PCM ? j : 0], acc2[S - 1][PCM ? i : 0][PCM ? j : 0],
+                             PN ? sqrtf(vn2[S - 1][PN ? i : 0]) : vn, zw[q], /*with_nl=*/!PN);
+          }
+          if (PN) {
+            yn = lineChain(io, lc, acc[0][i][j], c + j, acc_c[0][PCM ? i : 0][PCM ? j : 0],
+                           acc_i[0][PCM ? i : 0][PCM ? j : 0], acc2[0][PCM ? i : 0][PCM ? j : 0],
+                           sqrtf(vn2[0][PN ? i : 0]), zwn[q], /*with_nl=*/false);
+            if (io.pos_neg == 2) {
+              yn = lineNonLinearity(lc, yn, c + j);
+              y[j] = lineNonLinearity(lc, y[j], c + j);
+            } else {
+              y[j] = lineNonLinearity(lc, __fadd_rn(y[j], yn), c + j); // analog sum, then the output stage
+            }
           }
         }
-        y[j] = finalizeOutput(io, y[j], sigma, z[q], exceeded, u[q]) * fac;
+        if (PN && io.pos_neg == 2) {
+          // each pass through its own output stage, digital sum
+          yn = finalizeOutput(io, yn, sigma, zn[q], exceeded, un[q]);
+          y[j] = finalizeOutput(io, y[j], sigma, z[q], exceeded, u[q]);
+          y[j] = __fadd_rn(y[j], yn) * fac;
+        } else {
+          y[j] = finalizeOutput(io, y[j], sigma, z[q], exceeded, u[q]) * fac;
+        }
       }
     }
     if (exceeded && io.bm != AB200_BM_NONE) {
@@ -356,7 +410,6 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
 __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
   pdlEnter();
   extern __shared__ float v_sh[]; // K prepared inputs
-  __shared__ float red_sh[8];
   const IOEff &io = p.io;
   const int K = p.in_size, N = p.out_size;
   const uint64_t n4 = (uint64_t)(((N + 7) >> 3) << 1);
@@ -402,74 +455,130 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
       }
       scale = inputScale(io, sval, reduction, true);
       const ElemRng g{p.key, p.call, TAG_FWD_IN + p.noise_id + (uint32_t)round * 0x10000u};
-      float nacc = 0.0f;
+      // squared norm of the prepared input, negative and positive half apart (the separate
+      // passes of pos_neg each see their own half)
+      float nacc_n = 0.0f, nacc_p = 0.0f;
       for (int k = threadIdx.x; k < K; k += blockDim.x) {
         const float xin = gathered ? gatherRowElement(p.gather, p.in, r, k)
                                    : (k < p.in_real ? row[(long long)k * p.in_fs] : 1.0f);
         float v = prepareInput(io, xin, scale, g, (uint32_t)r, (uint32_t)k);
         v_sh[k] = v;
-        nacc = fmaf(v, v, nacc);
+        if (v < 0.0f) {
+          nacc_n = fmaf(v, v, nacc_n);
+        } else {
+          nacc_p = fmaf(v, v, nacc_p);
+        }
       }
-      float vn = 0.0f;
+      float vn = 0.0f, vn_n = 0.0f, vn_p = 0.0f;
       if (io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f) {
         for (int o = 16; o > 0; o >>= 1) {
-          nacc += __shfl_xor_sync(0xffffffffu, nacc, o);
+          nacc_n += __shfl_xor_sync(0xffffffffu, nacc_n, o);
+          nacc_p += __shfl_xor_sync(0xffffffffu, nacc_p, o);
         }
+        __shared__ float red2_sh[8][2];
         if ((threadIdx.x & 31) == 0) {
-          red_sh[threadIdx.x >> 5] = nacc;
+          red2_sh[threadIdx.x >> 5][0] = nacc_n;
+          red2_sh[threadIdx.x >> 5][1] = nacc_p;
         }
         __syncthreads();
-        float t = 0.0f;
+        float tn = 0.0f, tp = 0.0f;
         for (int i = 0; i < (int)(blockDim.x >> 5); i++) {
-          t += red_sh[i];
+          tn += red2_sh[i][0];
+          tp += red2_sh[i][1];
         }
-        vn = sqrtf(t);
+        vn = sqrtf(tn + tp);
+        vn_n = sqrtf(tn);
+        vn_p = sqrtf(tp);
       }
       __syncthreads();
       const bool pcm = ioNeedsLineChain(io);
+      const int pos_neg = io.pos_neg;
       float sigma = pcm ? io.out_noise : outputSigma(io, vn);
       const bool line_sigma = p.out_noise_vals != nullptr;
       const LineChain lc{p.v_offset, p.out_nl, p.nl_factor, __fdiv_rn((float)K, io.ir_g_ratio)};
       const uint32_t round_tag = TAG_FWD_OUT + p.noise_id + (uint32_t)round * 0x10000u;
+      const uint32_t round_tag_u = TAG_FWD_OUT_U + p.noise_id + (uint32_t)round * 0x10000u;
+      const bool w_draw = io.w_noise > 0.0f && io.w_noise_type != AB200_WNOISE_NONE;
       int fail = 0;
       for (int n = threadIdx.x; n < N; n += blockDim.x) {
-        float acc = 0.0f, acc2 = 0.0f, acc_c = 0.0f, acc_i = 0.0f;
+        // accumulator sets: [0] the only pass, or the pass over the positive inputs; [1] the
+        // pass over the negative inputs
+        float acc[2] = {0.0f, 0.0f}, acc2[2] = {0.0f, 0.0f}, acc_c[2] = {0.0f, 0.0f}, acc_i[2] = {0.0f, 0.0f};
         const float *wp = p.w + (long long)n * p.wn;
-        if (pcm) {
+        if (pos_neg != 0) {
           for (int k = 0; k < K; k++) {
             const float wv = wp[(long long)k * p.wk], v = v_sh[k];
-            acc = fmaf(v, wv, acc);
-            acc2 = fmaf(v * v, fabsf(wv), acc2);
-            acc_c = fmaf(fabsf(v), fabsf(wv), acc_c);
-            acc_i = fmaf(v * irPosWeight(k, K), wv, acc_i);
+            const float vp = fmaxf(v, 0.0f), vm = fminf(v, 0.0f), pw = irPosWeight(k, K), aw = fabsf(wv);
+            acc[0] = fmaf(vp, wv, acc[0]);
+            acc2[0] = fmaf(vp * vp, aw, acc2[0]);
+            acc_c[0] = fmaf(vp, aw, acc_c[0]);
+            acc_i[0] = fmaf(vp * pw, wv, acc_i[0]);
+            acc[1] = fmaf(vm, wv, acc[1]);
+            acc2[1] = fmaf(vm * vm, aw, acc2[1]);
+            acc_c[1] = fmaf(-vm, aw, acc_c[1]);
+            acc_i[1] = fmaf(vm * pw, wv, acc_i[1]);
+          }
+        } else if (pcm) {
+          for (int k = 0; k < K; k++) {
+            const float wv = wp[(long long)k * p.wk], v = v_sh[k];
+            acc[0] = fmaf(v, wv, acc[0]);
+            acc2[0] = fmaf(v * v, fabsf(wv), acc2[0]);
+            acc_c[0] = fmaf(fabsf(v), fabsf(wv), acc_c[0]);
+            acc_i[0] = fmaf(v * irPosWeight(k, K), wv, acc_i[0]);
           }
         } else {
           for (int k = 0; k < K; k++) {
-            acc = fmaf(v_sh[k], wp[(long long)k * p.wk], acc);
+            acc[0] = fmaf(v_sh[k], wp[(long long)k * p.wk], acc[0]);
           }
         }
         if (line_sigma) {
           sigma = pcm ? p.out_noise_vals[n] : outputSigmaLine(io, vn, p.out_noise_vals, n, 0.0f);
         }
+        const uint64_t blk = (uint64_t)r * n4 + (uint64_t)(n >> 2);
         if (pcm) {
           float zw[4] = {0.f, 0.f, 0.f, 0.f};
-          if (io.w_noise > 0.0f && io.w_noise_type != AB200_WNOISE_NONE) {
-            gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(n >> 2), p.call, round_tag ^ 0x04000000u, zw);
+          if (w_draw) {
+            gauss4(p.key, blk, p.call, round_tag ^ 0x04000000u, zw);
           }
-          acc = lineChain(io, lc, acc, n, acc_c, acc_i, acc2, vn, zw[n & 3]);
+          acc[0] = lineChain(io, lc, acc[0], n, acc_c[0], acc_i[0], acc2[0], pos_neg != 0 ? vn_p : vn, zw[n & 3],
+                             /*with_nl=*/pos_neg == 0);
+          if (pos_neg != 0) {
+            float zwn[4] = {0.f, 0.f, 0.f, 0.f};
+            if (w_draw) {
+              gauss4(p.key, blk, p.call, round_tag ^ 0x0c000000u, zwn);
+            }
+            acc[1] = lineChain(io, lc, acc[1], n, acc_c[1], acc_i[1], acc2[1], vn_n, zwn[n & 3], /*with_nl=*/false);
+            if (pos_neg == 2) {
+              acc[0] = lineNonLinearity(lc, acc[0], n);
+              acc[1] = lineNonLinearity(lc, acc[1], n);
+            } else {
+              acc[0] = lineNonLinearity(lc, __fadd_rn(acc[0], acc[1]), n); // analog sum, then the output stage
+            }
+          }
         }
         float z[4] = {0.f, 0.f, 0.f, 0.f};
         if (sigma > 0.0f) {
-          gauss4(p.key, (uint64_t)r * n4 + (uint64_t)(n >> 2), p.call,
-                 TAG_FWD_OUT + p.noise_id + (uint32_t)round * 0x10000u, z);
+          gauss4(p.key, blk, p.call, round_tag, z);
         }
         float u[4] = {0.5f, 0.5f, 0.5f, 0.5f};
         if (io.out_sto_round) {
-          uniform4(p.key, (uint64_t)r * n4 + (uint64_t)(n >> 2), p.call,
-                   TAG_FWD_OUT_U + p.noise_id + (uint32_t)round * 0x10000u, u);
+          uniform4(p.key, blk, p.call, round_tag_u, u);
         }
         bool ex = false;
-        float y = finalizeOutput(io, acc, sigma, z[n & 3], ex, u[n & 3]);
+        float y;
+        if (pos_neg == 2) {
+          float zn[4] = {0.f, 0.f, 0.f, 0.f}, un[4] = {0.5f, 0.5f, 0.5f, 0.5f};
+          if (sigma > 0.0f) {
+            gauss4(p.key, blk, p.call, round_tag ^ 0x08000000u, zn);
+          }
+          if (io.out_sto_round) {
+            uniform4(p.key, blk, p.call, round_tag_u ^ 0x08000000u, un);
+          }
+          const float yn = finalizeOutput(io, acc[1], sigma, zn[n & 3], ex, un[n & 3]);
+          y = __fadd_rn(finalizeOutput(io, acc[0], sigma, z[n & 3], ex, u[n & 3]), yn);
+        } else {
+          y = finalizeOutput(io, acc[0], sigma, z[n & 3], ex, u[n & 3]);
+        }
         fail |= ex ? 1 : 0;
         if (n < p.out_store) {
           p.out[(long long)r * p.out_ss + (long long)n * p.out_fs] = y;
@@ -567,7 +676,19 @@ void launchMvmSimt(const MvmProblem &p, cudaStream_t stream) {
       AB200_CUDA(launchChained(mvmSimtKernel<false, false, TT, PCM>, grid, dim3(256), 0, stream, p));                           \
     }                                                                                              \
   }
-  if (pcm) { // the second accumulator doubles the registers of a thread: the 32-wide tile at most
+  if (pcm && p.io.pos_neg != 0) {
+    // separate passes: two sets of the line-chain accumulators, the 16-wide tile
+    dim3 grid((p.out_size + 15) / 16, (p.m + 15) / 16);
+    if (a_k_fast && b_n_fast) {
+      AB200_CUDA(launchChained(mvmSimtKernel<true, true, 1, true, false, true>, grid, dim3(256), 0, stream, p));
+    } else if (a_k_fast) {
+      AB200_CUDA(launchChained(mvmSimtKernel<true, false, 1, true, false, true>, grid, dim3(256), 0, stream, p));
+    } else if (b_n_fast) {
+      AB200_CUDA(launchChained(mvmSimtKernel<false, true, 1, true, false, true>, grid, dim3(256), 0, stream, p));
+    } else {
+      AB200_CUDA(launchChained(mvmSimtKernel<false, false, 1, true, false, true>, grid, dim3(256), 0, stream, p));
+    }
+  } else if (pcm) { // the second accumulator doubles the registers of a thread: the 32-wide tile at most
     if (T >= 2) {
       AB200_SIMT(2, true)
     } else {

@@ -196,7 +196,7 @@ __host__ __device__ __forceinline__ bool ioLineSigma(const IOEff &io) {
 __host__ __device__ __forceinline__ bool ioNeedsLineChain(const IOEff &io) {
   return !io.is_perfect &&
          ((io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) || io.ir_drop > 0.0f ||
-          io.v_offset_std > 0.0f || io.r_series > 0.0f || io.out_nl > 0.0f);
+          io.v_offset_std > 0.0f || io.r_series > 0.0f || io.out_nl > 0.0f || io.pos_neg != 0);
 }
 
 // Weight of input position k in the IR-drop term: 1 - (1 - k / n)^2
@@ -216,8 +216,18 @@ struct LineChain {
   float nl_factor;
   float a_scale; // in_size / ir_drop_g_ratio
 };
+// The output non-linearity of a line: first step of the output stage (finalizeOutput :673-719)
+__device__ __forceinline__ float lineNonLinearity(const LineChain &lc, float y, int col) {
+  if (lc.out_nl) {
+    y = __fdiv_rn(__fmul_rn(lc.nl_factor, y), __fadd_rn(1.0f, fabsf(__fmul_rn(lc.out_nl[col], y))));
+  }
+  return y;
+}
+// `with_nl = false` stops after the steps that belong to one pass through the array
+// (applyNonIdealities); the two-pass MV types add their halves there.
 __device__ __forceinline__ float lineChain(const IOEff &io, const LineChain &lc, float y, int col,
-                                           float cur, float irsum, float pcm, float vnorm, float z_w) {
+                                           float cur, float irsum, float pcm, float vnorm, float z_w,
+                                           bool with_nl = true) {
   if (io.ir_drop > 0.0f) {
     const float a = __fmul_rn(lc.a_scale, cur);
     const float c = __fmul_rn(a, __fadd_rn(__fmul_rn(a, __fsub_rn(__fmul_rn(0.05f, a), 0.2f)), 0.5f));
@@ -239,10 +249,7 @@ __device__ __forceinline__ float lineChain(const IOEff &io, const LineChain &lc,
       y = __fadd_rn(y, __fmul_rn(__fmul_rn(io.w_noise, sqrtf(pcm)), z_w));
     }
   }
-  if (lc.out_nl) {
-    y = __fdiv_rn(__fmul_rn(lc.nl_factor, y), __fadd_rn(1.0f, fabsf(__fmul_rn(lc.out_nl[col], y))));
-  }
-  return y;
+  return with_nl ? lineNonLinearity(lc, y, col) : y;
 }
 
 // four uniforms in (0,1) for the stochastic ADC rounding of noise block `blk` (four output columns)

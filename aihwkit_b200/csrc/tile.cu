@@ -69,6 +69,17 @@ IOEff resolveIO(const ab200_io_params &io, bool backward, bool plain_only) {
   e.out_asym = 1.0f - io.out_asymmetry;
   e.inp_sto_round = io.inp_sto_round;
   e.out_sto_round = io.out_sto_round;
+  e.pos_neg = 0;
+  if (!io.is_perfect && io.mv_type != AB200_MV_ONE_PASS) {
+    if (io.mv_type != AB200_MV_POS_NEG_SEPARATE && io.mv_type != AB200_MV_POS_NEG_SEPARATE_DIGITAL_SUM) {
+      AB200_FATAL("AnalogMVType not implemented.");
+    }
+    if (plain_only) {
+      AB200_FATAL("separate passes for negative and positive inputs are not implemented for the "
+                  "read-out of a transfer");
+    }
+    e.pos_neg = io.mv_type == AB200_MV_POS_NEG_SEPARATE ? 1 : 2;
+  }
   if (!io.is_perfect) {
     if (io.noise_management != AB200_NM_NONE && io.inp_bound != 1.0f) {
       AB200_FATAL((backward ? "Backward noise managment expects input bound==1"

@@ -52,6 +52,9 @@ struct IOEff {
   float out_asym;
   int inp_sto_round;
   int out_sto_round;
+  // 0: one pass; 1 / 2: negative and positive inputs in two passes, summed before / after the
+  // output stage (CUDA-core kernels)
+  int pos_neg;
 };
 
 // `plain_only`: reject the settings only the forward / backward kernels implement (input noise,

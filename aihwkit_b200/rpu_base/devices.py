@@ -133,13 +133,14 @@ class AnalogTileInputOutputParameter:
                 "B200 analog tile"
             )
         mv = int(self.mv_type)
-        if mv not in (int(AnalogMVType.Ideal), int(AnalogMVType.OnePass)):
-            raise RuntimeError("MV type not implemented.")
+        if mv not in (0, 1, 2, 3):
+            raise RuntimeError("AnalogMVType not implemented.")
         nm = int(self.noise_management)
         if nm not in (0, 1, 2, 3, 4, 5, 6):
             raise RuntimeError("Noise Management type not implemented!")
         c = _cabi.IOParams()
         c.is_perfect = int(bool(self.is_perfect) or mv == int(AnalogMVType.Ideal))
+        c.mv_type = max(mv - 1, 0)  # ab200_mv_type: one pass, pos / neg separate, digital sum
         c.noise_management = nm
         c.bound_management = int(self.bound_management)
         c.w_noise_type = int(self.w_noise_type)

@@ -130,7 +130,21 @@ typedef struct ab200_io_params {
   float out_nonlinearity;
   float out_nonlinearity_std;
   float slope_calibration;
+  /* AnalogMVType (src/rpucuda/rpu_pulsed_meta_parameter.h:41-48, computeAnalogMV
+   * rpu_forward_backward_pass.cpp:820-876): ONE_PASS, or the negative and the positive inputs in
+   * two passes through the array, each with its own analog non-idealities and weight noise; the
+   * two results are added before the output stage (POS_NEG_SEPARATE: one output noise draw, one
+   * ADC conversion of the sum) or after it (POS_NEG_SEPARATE_DIGITAL_SUM: each pass converted on
+   * its own, bound management needs both inside the bound). CUDA-core kernels only. */
+  int32_t mv_type; /* enum ab200_mv_type */
 } ab200_io_params;
+
+/* AnalogMVType::Ideal of the reference is is_perfect = 1 here */
+enum ab200_mv_type {
+  AB200_MV_ONE_PASS = 0,
+  AB200_MV_POS_NEG_SEPARATE = 1,
+  AB200_MV_POS_NEG_SEPARATE_DIGITAL_SUM = 2
+};
 
 /* PulsedUpdateMetaParameter (src/rpucuda/rpu_pulsed_meta_parameter.h:248-279;
  * rpu_base_devices.cpp:469-483). */

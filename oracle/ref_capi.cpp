@@ -69,6 +69,10 @@ void toIO(const ab200_io_params &s, IOMetaParameter<float> &io) {
   io.out_nonlinearity = s.out_nonlinearity;
   io.out_nonlinearity_std = s.out_nonlinearity_std;
   io.slope_calibration = s.slope_calibration;
+  io.mv_type = s.mv_type == AB200_MV_POS_NEG_SEPARATE
+                   ? AnalogMVType::PosNegSeparate
+                   : (s.mv_type == AB200_MV_POS_NEG_SEPARATE_DIGITAL_SUM ? AnalogMVType::PosNegSeparateDigitalSum
+                                                                         : AnalogMVType::OnePass);
 }
 
 void toUp(const ab200_update_params &s, PulsedUpdateMetaParameter<float> &up) {

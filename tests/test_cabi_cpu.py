@@ -32,7 +32,7 @@ def test_struct_sizes_match_header():
     for which, cls in enumerate((_cabi.IOParams, _cabi.UpdateParams, _cabi.DeviceParams,
                                  _cabi.TransferParams, _cabi.TileConfig, _cabi.ScatterPlan)):
         assert C.sizeof(cls) == lib.ab200_sizeof(which), cls.__name__
-    assert C.sizeof(_cabi.IOParams) == 31 * 4
+    assert C.sizeof(_cabi.IOParams) == 32 * 4
     assert C.sizeof(_cabi.TileConfig) % 8 == 0
 
 

@@ -280,3 +280,108 @@ def test_weight_noise_enters_before_the_non_linearity():
     sig = 0.02 * np.sqrt((v ** 2).sum(axis=1, keepdims=True)) / (1.0 + np.abs(nl * y0)) ** 2
     ratio = ys.std(axis=0) / sig
     assert abs(ratio.mean() - 1.0) < 0.02, ratio.mean()
+
+
+@pytest.mark.parametrize("mv", ["PosNegSeparate", "PosNegSeparateDigitalSum"])
+@pytest.mark.parametrize("bm", [False, True])
+@pytest.mark.parametrize("lines", ["none", "all"])
+def test_pos_neg_separate_against_reference(mv, bm, lines):
+    """Negative and positive inputs in two passes through the array, summed before or after the
+    output stage (computeAnalogMV, src/rpucuda/rpu_forward_backward_pass.cpp:820-876), noise
+    off: outputs of the compiled reference up to single ADC steps (two for the digital sum, whose
+    two conversions can each flip), forward with and without bound-management re-runs, and
+    backward; alone and on top of the line non-idealities, which each pass sees on its own."""
+    from aihwkit_b200.rpu_base import devices as D
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    if not ref.available():
+        pytest.skip("compiled reference not built")
+    rng = np.random.default_rng(31)
+    x_size, d_size, m = 150, 70, 48
+    out_bound = 2.0 if bm else 12.0
+    p = H.training_params(noise=False, pulse_det=True, bm=bm, out_bound=out_bound)
+    for io in (p.forward_io, p.backward_io):
+        io.mv_type = getattr(D.AnalogMVType, mv)
+        if lines == "all":
+            for k, v in _LINE_SETTINGS["all"].items():
+                setattr(io, k, v)
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=9)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    rt = ref.RefTile(cfg)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().cpu().numpy()
+    rt.set_weights(W)
+    if lines == "all":
+        for backward, n in ((False, d_size), (True, x_size)):
+            for which in (0, 1):
+                v = rt.get_io_vector(backward, which, n)
+                if v.size:
+                    t.set_io_vector(backward, which, torch.from_numpy(v))
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+    steps = 2.002 if mv.endswith("DigitalSum") else 1.001
+    y = t.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+    yr = rt.forward(X)
+    res_out = 2.0 * out_bound / 510.0
+    lsb = res_out * np.abs(X).max(axis=1, keepdims=True) * (t.last_bm_stats()[1] if bm else 1.0)
+    frac, worst = H.lsb_report(y, yr, lsb)
+    assert frac <= 1e-2 and worst <= steps, (frac, worst)
+    if bm:
+        assert t.last_bm_stats()[0] > 0
+    g = t.backward(torch.from_numpy(Dm).cuda()).cpu().numpy()
+    gr = rt.backward(Dm)
+    lsb_b = (2.0 * 12.0 / 510.0) * np.abs(Dm).max(axis=1, keepdims=True)
+    frac, worst = H.lsb_report(g, gr, lsb_b)
+    assert frac <= 1e-2 and worst <= steps, (frac, worst)
+    if mv.endswith("DigitalSum") and not bm and lines == "none":
+        # two conversions: the result lies off the single-pass ADC grid for many elements
+        p1 = H.training_params(noise=False, pulse_det=True, bm=False, out_bound=out_bound)
+        t1 = T.AnalogTile(p1._config(x_size, d_size, H.device("cs", False), seed=9), cuda_device=0)
+        t1.set_weights(torch.from_numpy(W))
+        y1 = t1.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+        assert np.mean(np.abs(y1 - y) > 0.25 * lsb) > 0.1
+
+
+@pytest.mark.parametrize("mv", ["PosNegSeparate", "PosNegSeparateDigitalSum"])
+def test_pos_neg_separate_noise_moments(mv):
+    """Output noise and additive weight noise under the two-pass types: the analog sum carries one
+    output-noise draw and the weight noise of both halves (w^2 ||v||^2 in total), the digital sum
+    two output-noise draws; std-dev per element against the closed form and the reference."""
+    from aihwkit_b200.rpu_base import devices as D
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    rng = np.random.default_rng(37)
+    x_size, d_size, m = 96, 48, 12
+    p = H.training_params(noise=False, pulse_det=True, bm=False, adc=False, out_bound=0.0)
+    io = p.forward_io
+    io.mv_type = getattr(D.AnalogMVType, mv)
+    io.out_noise, io.w_noise = 0.03, 0.02
+    io.w_noise_type = D.WeightNoiseType.AdditiveConstant
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=9)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().cpu().numpy()
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    X /= np.abs(X).max(axis=1, keepdims=True)
+    xg = torch.from_numpy(X).cuda()
+    reps = 400
+    ys = _repeat(lambda: t.forward(xg).cpu().numpy(), reps)
+    res = np.float32(2.0 / 126.0)
+    v = np.clip(np.rint(X / res) * res, -1, 1).astype(np.float64)
+    n_out = 2.0 if mv.endswith("DigitalSum") else 1.0
+    sig = np.sqrt(n_out * 0.03 ** 2 + 0.02 ** 2 * (v ** 2).sum(axis=1, keepdims=True)) * np.ones((1, d_size))
+    ratio = ys.std(axis=0) / sig
+    assert abs(ratio.mean() - 1.0) < 0.01, ratio.mean()
+    assert np.abs(ratio - 1.0).max() < 5.5 / np.sqrt(2 * reps), np.abs(ratio - 1.0).max()
+    zmean = (ys.mean(axis=0) - v @ W.astype(np.float64).T) / (sig / np.sqrt(reps))
+    assert np.abs(zmean).max() < 5.5
+    if ref.available():
+        rt = ref.RefTile(cfg)
+        rt.set_weights(W)
+        yr = _repeat(lambda: rt.forward(X), reps)
+        rr = ys.std(axis=0) / yr.std(axis=0)
+        assert abs(rr.mean() - 1.0) < 0.02 and np.abs(rr - 1.0).max() < 0.35
