@@ -8,12 +8,16 @@
 // Here the forward pass on the tensor-core path and the pulsed update read the images through
 // the index array themselves (the DAC kernel and the pulse-preparation kernel gather a row each,
 // RowGather in tile.h), so the unfolded matrix is never written; other cases (CUDA-core MVM,
-// floating-point update) and the backward pass go through the sample-major matrix
-// [dim3 * m_batch][x_size] (row = one output position of one image). The image-major output
-// layout [dim3][d_size][m_batch] is produced by a batched transpose.
+// floating-point update) go through the sample-major matrix [dim3 * m_batch][x_size] (row = one
+// output position of one image). The MVM kernels store image-major outputs
+// [dim3][d_size][m_batch] themselves (MvmProblem::out_t_rows). The backward pass stores the input
+// gradients of all positions in the layout of the index array, and every image element then sums
+// the positions that name it through an inverse index built once per index array: no atomics,
+// and the same bits on every run.
 #include "tile.h"
 
 #include <cstdlib>
+#include <vector>
 
 namespace ab200 {
 
@@ -59,42 +63,28 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-// out(n, idx[r][l]) += cols[(n * m_batch + l) * size + r]
+// out(n, e) = sum over the positions t of the index array that name element e of cols[n][t], in
+// ascending t: the backward pass of the indexed interface as a gather, without atomics and with a
+// fixed summation order. `cols` has the layout of the index array per image. Neighbouring
+// elements are named by neighbouring positions (same kernel tap, next output position), so the
+// reads of a warp are contiguous where the index array is [x_size][m_batch].
 __global__ void __launch_bounds__(256)
-    scatterTransKernel(const float *cols, const int *idx, float *out, int size, int m_batch,
-                       long long out_mat) {
-  __shared__ float tile[32][33];
-  const int n = blockIdx.z;
-  const int l0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-  for (int k = threadIdx.y; k < 32; k += 8) {
-    const int l = l0 + k, r = r0 + threadIdx.x;
-    tile[k][threadIdx.x] =
-        (r < size && l < m_batch) ? cols[((long long)n * m_batch + l) * size + r] : 0.0f;
-  }
-  __syncthreads();
-  float *img = out + (long long)n * out_mat;
-  for (int k = threadIdx.y; k < 32; k += 8) {
-    const int r = r0 + k, l = l0 + threadIdx.x;
-    if (r < size && l < m_batch) {
-      const int j = idx[(long long)r * m_batch + l];
-      if (j > 1) {
-        atomicAdd(img + (j - 2), tile[threadIdx.x][k]);
-      }
-    }
-  }
-}
-
-__global__ void __launch_bounds__(256)
-    scatterPlainKernel(const float *cols, const int *idx, float *out, long long per_image,
-                       long long out_mat) {
+    gatherSumKernel(const float *cols, const int *csr_off, const int *csr_pos, float *out,
+                    long long csr_elems, long long out_mat, long long per_image) {
   const int n = blockIdx.y;
-  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (t < per_image) {
-    const int j = idx[t];
-    if (j > 1) {
-      atomicAdd(out + n * out_mat + (j - 2), cols[n * per_image + t]);
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= out_mat) {
+    return;
+  }
+  float acc = 0.0f;
+  if (e < csr_elems) {
+    const float *c = cols + n * per_image;
+    const int t1 = csr_off[e + 1];
+    for (int t = csr_off[e]; t < t1; t++) {
+      acc += c[csr_pos[t]];
     }
   }
+  out[n * out_mat + e] = acc;
 }
 
 // dst[b][c][r] = src[b][r][c]
@@ -159,6 +149,36 @@ void Tile::setMatrixIndices(const int32_t *indices, long long n, cudaStream_t s)
   idx_count_ = n;
   idx_max_ = hi;
   idx_t_valid_ = false;
+  // inverse index (counting sort by image element; positions stay in ascending order)
+  csr_elems_ = hi >= 2 ? (long long)hi - 1 : 0;
+  std::vector<int32_t> off((size_t)csr_elems_ + 1, 0), pos;
+  for (long long k = 0; k < n; k++) {
+    if (host[k] >= 2) {
+      off[(size_t)host[k] - 1]++; // element e = host[k] - 2 counts into off[e + 1]
+    }
+  }
+  for (long long e = 0; e < csr_elems_; e++) {
+    off[(size_t)e + 1] += off[(size_t)e];
+  }
+  pos.resize((size_t)off[(size_t)csr_elems_]);
+  {
+    std::vector<int32_t> fill(off.begin(), off.end() - 1);
+    for (long long k = 0; k < n; k++) {
+      if (host[k] >= 2) {
+        pos[(size_t)fill[(size_t)host[k] - 2]++] = (int32_t)k;
+      }
+    }
+  }
+  AB200_CUDA(cudaStreamSynchronize(s));
+  cudaFree(csr_off_);
+  cudaFree(csr_pos_);
+  csr_off_ = csr_pos_ = nullptr;
+  AB200_CUDA(cudaMalloc(&csr_off_, off.size() * sizeof(int32_t)));
+  AB200_CUDA(cudaMalloc(&csr_pos_, (pos.empty() ? 1 : pos.size()) * sizeof(int32_t)));
+  AB200_CUDA(cudaMemcpy(csr_off_, off.data(), off.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
+  if (!pos.empty()) {
+    AB200_CUDA(cudaMemcpy(csr_pos_, pos.data(), pos.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
+  }
 }
 
 void Tile::requireIndices(const char *what, long long image_size, int m_batch, int n_img) const {
@@ -257,21 +277,19 @@ void Tile::forwardIndexed(const float *x, float *d, long long total_input_size, 
     AB200_FATAL("forward_indexed: m_batch * dim3 does not fit an int");
   }
   const bool fused = forwardGatherEligible((int)b);
-  ensureIndexedScratch(b, !fused, trans);
-  float *rows_out = trans ? cols_d_ : d;
+  ensureIndexedScratch(b, !fused, false);
+  // image-major outputs [dim3][d_size][m_batch] are stored by the MVM kernels themselves
+  const int out_t_rows = trans ? m_batch : 0;
   if (fused) {
     RowGather g;
     g.idx = rowMajorIndices(m_batch, trans, s);
     g.m_batch = m_batch;
     g.ld = x_size_;
     g.image_size = in_mat;
-    forwardGathered(x, g, rows_out, (int)b, is_test, s);
+    forwardGathered(x, g, d, (int)b, is_test, s, out_t_rows);
   } else {
     gatherIndexed(x, in_mat, m_batch, n_img, trans, s);
-    forward(cols_x_, rows_out, false, (int)b, false, false, is_test, s);
-  }
-  if (trans) {
-    launchBatchedTranspose(cols_d_, d, m_batch, d_size_, n_img, s); // -> [dim3][d_size][m_batch]
+    forward(cols_x_, d, false, (int)b, false, false, is_test, s, out_t_rows);
   }
 }
 
@@ -290,16 +308,13 @@ void Tile::backwardIndexed(const float *d, float *x, long long total_output_size
     launchBatchedTranspose(d, cols_d_, d_size_, m_batch, n_img, s); // -> [dim3][m_batch][d_size]
     src = cols_d_;
   }
-  backward(src, cols_x_, false, (int)b, false, false, s);
-  AB200_CUDA(cudaMemsetAsync(x, 0, (size_t)total_output_size * sizeof(float), s));
-  if (trans) {
-    dim3 grid((m_batch + 31) / 32, (x_size_ + 31) / 32, n_img), block(32, 8);
-    scatterTransKernel<<<grid, block, 0, s>>>(cols_x_, idx_, x, x_size_, m_batch, out_mat);
-  } else {
-    const long long per_image = (long long)m_batch * x_size_;
-    dim3 grid((unsigned)((per_image + 255) / 256), n_img);
-    scatterPlainKernel<<<grid, 256, 0, s>>>(cols_x_, idx_, x, per_image, out_mat);
-  }
+  // the input gradients of all positions in the layout of the index array ([x_size][m_batch] per
+  // image: stored transposed by the MVM kernels), then every image element sums the positions
+  // that name it
+  backwardCore(src, d_size_, 1, cols_x_, x_size_, 1, x_size_, (int)b, false, 0, 1.0f, s, trans ? m_batch : 0);
+  const long long per_image = (long long)m_batch * x_size_;
+  dim3 grid((unsigned)((out_mat + 255) / 256), n_img);
+  gatherSumKernel<<<grid, 256, 0, s>>>(cols_x_, csr_off_, csr_pos_, x, csr_elems_, out_mat, per_image);
   AB200_LAUNCH_CHECK();
 }
 

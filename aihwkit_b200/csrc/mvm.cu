@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(256) mvmSimtKernel(MvmProblem p) {
 #pragma unroll
     for (int j = 0; j < T; j++) {
       if (c + j < p.out_store) {
-        float *o = p.out + (long long)r * p.out_ss + (long long)(c + j) * p.out_fs;
+        float *o = mvmOutPtr(p, r, c + j);
         *o = p.accumulate ? *o + y[j] : y[j];
       }
     }
@@ -581,7 +581,7 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
         }
         fail |= ex ? 1 : 0;
         if (n < p.out_store) {
-          p.out[(long long)r * p.out_ss + (long long)n * p.out_fs] = y;
+          *mvmOutPtr(p, r, n) = y;
         }
       }
       int any_fail = __syncthreads_or(fail);
@@ -590,7 +590,7 @@ __global__ void __launch_bounds__(256) bmRerunKernel(MvmProblem p) {
     }
     float fac = outputFactor(io, p.alpha, sval, scale, false);
     for (int n = threadIdx.x; n < N && n < p.out_store; n += blockDim.x) {
-      p.out[(long long)r * p.out_ss + (long long)n * p.out_fs] *= fac;
+      *mvmOutPtr(p, r, n) *= fac;
     }
     if (threadIdx.x == 0) {
       atomicAdd(&p.bm_stats[0], 1);

@@ -16,6 +16,15 @@ __device__ __forceinline__ float gatherRowElement(const RowGather &g, const floa
   return j <= 1 ? (float)j : __ldg(images + (long long)n * g.image_size + (j - 2));
 }
 
+// address of output (row r, column n) of an MVM: strided, or transposed in blocks of rows
+__device__ __forceinline__ float *mvmOutPtr(const MvmProblem &p, int r, int n) {
+  if (p.out_t_rows > 0) {
+    const int blk = r / p.out_t_rows, l = r - blk * p.out_t_rows;
+    return p.out + ((long long)blk * p.out_size + n) * p.out_t_rows + l;
+  }
+  return p.out + (long long)r * p.out_ss + (long long)n * p.out_fs;
+}
+
 // Per-sample statistics of the raw input that the noise-management types need.
 struct NmStats {
   float amax = 0.0f;      // max |x|

@@ -117,6 +117,12 @@ struct TcKernelParams {
   // row, instead of 16 bytes in each of 32 rows - for outputs so wide that the stores bound the
   // kernel
   int row_stores;
+  // > 0: the output is stored transposed in blocks of that many rows: row r, column c goes to
+  // out[((r / out_t_rows) * out_ss + c) * out_t_rows + r % out_t_rows] (out_ss = columns of the
+  // whole layer) - the image-major layout of the indexed convolution interface. The row-per-lane
+  // layout of the accumulators is already the right one: every store instruction writes 128
+  // contiguous bytes of one column.
+  int out_t_rows;
   IOEff io;
   int *status;
   // optional per-CTA cycle counters of time spent waiting, by role (diagnostics; null = off):
@@ -830,6 +836,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           if (row0 + r < p.m) {
             o[(long long)r * p.out_ss] = sum[r] + b;
           }
+        }
+      }
+    } else if (ok && row_ok && p.out_t_rows > 0) {
+      const int grow = p.row_base + row; // row of the whole batch
+      const int blk = grow / p.out_t_rows, l = grow - blk * p.out_t_rows;
+      float *o = p.out + ((long long)blk * p.out_ss + ch.z + cbase) * p.out_t_rows + l;
+#pragma unroll
+      for (int c = 0; c < TC_EPI_COLS; c++) {
+        if (cbase + c < ch.w) {
+          o[(long long)c * p.out_t_rows] = sum[c] + (p.bias ? p.bias[ch.z + cbase + c] : 0.0f);
         }
       }
     } else if (ok && row_ok) {
@@ -1667,7 +1683,8 @@ void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
   // this part as a run of its own
   Run r = r0;
   r.m = rows;
-  r.out = r0.out ? r0.out + (long long)row0 * r0.out_ss : nullptr;
+  // (a transposed store addresses by the row of the whole batch: its base stays)
+  r.out = r0.out ? (r0.out_t_rows > 0 ? r0.out : r0.out + (long long)row0 * r0.out_ss) : nullptr;
   void *codes_part = (__nv_bfloat16 *)codes_ + (size_t)row0 * I * kpad_;
   struct {
     float *scale, *factor, *vnorm;
@@ -1753,7 +1770,11 @@ void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
       const char *e = getenv("AB200_TC_ROW_STORES");
       return e && e[0] == '0';
     }();
-    p.row_stores = (!off && !codes && r.out_table == nullptr && !r.accumulate) ? 1 : 0;
+    p.row_stores = (!off && !codes && r.out_table == nullptr && !r.accumulate && r.out_t_rows <= 0) ? 1 : 0;
+  }
+  p.out_t_rows = r.out_t_rows > 0 ? r.out_t_rows : 0;
+  if (p.out_t_rows > 0 && (codes || r.out_table != nullptr || r.accumulate)) {
+    AB200_FATAL("tensor-core MVM: a transposed output can neither be scattered nor accumulated into");
   }
   p.io = r.io;
   p.status = status_dev_;

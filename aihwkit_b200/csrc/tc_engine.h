@@ -35,6 +35,9 @@ public:
     int m = 0;
     float *out = nullptr; // [m][N_total], row stride out_ss
     long long out_ss = 0;
+    // > 0: stored transposed in blocks of that many rows instead, [m / out_t_rows][N_total][out_t_rows]
+    // with out_ss = N_total (image-major layout of the indexed convolution interface)
+    int out_t_rows = 0;
     bool accumulate = false;
     bool backward = false;
     IOEff io;

@@ -569,6 +569,8 @@ Tile::~Tile() {
     cudaFree(t_past_);
     cudaFree(idx_);
     cudaFree(idx_t_);
+    cudaFree(csr_off_);
+    cudaFree(csr_pos_);
     cudaFree(cols_x_);
     cudaFree(cols_d_);
     cudaFree(stage_dev_);
@@ -1152,7 +1154,7 @@ void Tile::fillMvmScratch(MvmProblem &p) {
 }
 
 void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, bool d_trans,
-                   bool is_test, cudaStream_t s) {
+                   bool is_test, cudaStream_t s, int out_t_rows) {
   // the IO noise is present in test mode too (rpu_forward_backward_pass.cpp:808-810); is_test only
   // selects between the weights and their modified copy
   requireDevice("forward");
@@ -1182,6 +1184,7 @@ void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, boo
   p.alpha = 1.0f;
   p.call = fwd_calls_++;
   p.noise_id = 0;
+  p.out_t_rows = out_t_rows;
   fillMvmScratch(p);
   if (tcEligible(p)) {
     AB200_CUDA(cudaMemsetAsync(bm_stats_, 0, 2 * sizeof(int), s));
@@ -1209,10 +1212,11 @@ bool Tile::forwardGatherEligible(int b) const {
 }
 
 void Tile::forwardGathered(const float *images, const RowGather &g, float *d, int b, bool is_test,
-                           cudaStream_t s) {
+                           cudaStream_t s, int out_t_rows) {
   MvmProblem p{};
   p.in = images;
   p.gather = g;
+  p.out_t_rows = out_t_rows;
   p.in_ss = x_size_;
   p.in_fs = 1;
   p.in_size = x_size_;
@@ -1309,7 +1313,7 @@ void Tile::backwardStrided(const float *d, long long d_ss, float *x, long long x
 
 void Tile::backwardCore(const float *d, long long d_ss, long long d_fs, float *x, long long x_ss,
                         long long x_fs, int x_store, int m, bool accumulate, uint32_t noise_id,
-                        float out_scale, cudaStream_t s) {
+                        float out_scale, cudaStream_t s, int out_t_rows) {
   requireDevice("backward");
   if (m <= 0) {
     return;
@@ -1336,6 +1340,7 @@ void Tile::backwardCore(const float *d, long long d_ss, long long d_fs, float *x
   p.alpha = out_scale;
   p.call = bwd_calls_++;
   p.noise_id = noise_id;
+  p.out_t_rows = out_t_rows;
   fillMvmScratch(p);
   if (!accumulate && tcEligible(p)) {
     runTc(p, s);
@@ -1382,6 +1387,7 @@ void Tile::runTc(const MvmProblem &p, cudaStream_t s) {
   r.m = p.m;
   r.out = p.out;
   r.out_ss = p.out_ss;
+  r.out_t_rows = p.out_t_rows;
   r.accumulate = p.accumulate != 0;
   r.backward = p.backward != 0;
   r.io = p.io;

@@ -129,6 +129,9 @@ struct MvmProblem {
   float nl_factor = 1.0f;
   // tensor-core path only: `in` holds whole images and the rows are gathered from them
   RowGather gather;
+  // > 0: outputs stored transposed in blocks of that many rows, row r / column n at
+  // out[((r / out_t_rows) * out_size + n) * out_t_rows + r % out_t_rows] (out_ss / out_fs unused)
+  int out_t_rows = 0;
 };
 
 // CUDA-core path: noise management, fused MVM, bound-management re-run
@@ -295,8 +298,10 @@ public:
   void getHidden(float *out);
   void setHidden(const float *in);
 
+  // out_t_rows > 0: the output is stored transposed in blocks of that many rows
+  // (MvmProblem::out_t_rows); d_trans must be false then
   void forward(const float *x, float *d, bool bias, int m, bool x_trans, bool d_trans,
-               bool is_test, cudaStream_t s);
+               bool is_test, cudaStream_t s, int out_t_rows = 0);
   void backward(const float *d, float *x, bool bias, int m, bool d_trans, bool x_trans,
                 cudaStream_t s);
   void update(const float *x, const float *d, bool bias, int m, bool x_trans, bool d_trans,
@@ -370,7 +375,7 @@ private:
   float pulseCountLR() const;
   void backwardCore(const float *d, long long d_ss, long long d_fs, float *x, long long x_ss,
                     long long x_fs, int x_store, int m, bool accumulate, uint32_t noise_id,
-                    float out_scale, cudaStream_t s);
+                    float out_scale, cudaStream_t s, int out_t_rows = 0);
   void updateCore(const float *x, long long x_ss, long long x_fs, int x_in, const float *d,
                   long long d_ss, long long d_fs, int m, cudaStream_t s);
   void requireSingleDevice(const char *what);
@@ -385,7 +390,7 @@ private:
   bool forwardGatherEligible(int b) const;
   bool updateGatherEligible() const;
   void forwardGathered(const float *images, const RowGather &g, float *d, int b, bool is_test,
-                       cudaStream_t s);
+                       cudaStream_t s, int out_t_rows);
   void gatherIndexed(const float *x, long long in_mat, int m_batch, int n_img, bool trans,
                      cudaStream_t s);
 
@@ -477,6 +482,11 @@ private:
   long long idx_t_cap_ = 0;
   bool idx_t_valid_ = false;
   RowGather upd_gather_; // set around an update whose samples are gathered from images
+  // inverse of the index array for the backward pass: for every image element the positions of
+  // the index array that name it (CSR: csr_off_[e] .. csr_off_[e + 1] into csr_pos_), in
+  // ascending order, so that the sum over them has a fixed order
+  int32_t *csr_off_ = nullptr, *csr_pos_ = nullptr;
+  long long csr_elems_ = 0; // image elements covered by the CSR (largest index - 1)
   unsigned char *clip_stats_ = nullptr; // statistics of clipWeights (sum, sum of squares, row maxima)
   // output block of a tile that adds to earlier in-splits under bound management
   float *acc_block_ = nullptr;

@@ -427,9 +427,10 @@ int ab200_tile_coincidences(ab200_tile *tile, const float *x_dev, const float *d
  * image. It may be host or device memory and is copied (the reference borrows the pointer).
  * Images: x is [dim3][total_size / dim3]; d is [dim3][d_size][m_batch] when `trans`, else
  * [dim3][m_batch][d_size]. m_batch = output positions per image, dim3 = images per call (the
- * binding passes the batch size N and trans = 1). backward_indexed overwrites x_dev with the
- * scatter-added result (sums of at most kernel-size terms are accumulated with float atomics, so
- * the last bit may depend on the execution order). Negative indices are rejected when the array is
+ * binding passes the batch size N and trans = 1). backward_indexed overwrites x_dev: every image
+ * element is the sum, in ascending order of their position in the index array, of the input
+ * gradients of the entries that name it (no atomics: the result is the same on every run).
+ * Negative indices are rejected when the array is
  * set; an index beyond the image size is rejected by every call. */
 int ab200_tile_set_matrix_indices(ab200_tile *tile, const int32_t *indices, long long count,
                                   void *stream);

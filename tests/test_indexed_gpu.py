@@ -126,6 +126,12 @@ def test_layouts_against_oracle(trans, analog_bias, mvm_path):
     step = float((bio.res_out * np.abs(d_cols).max(axis=1)).max())
     diff = np.abs(xg.cpu().numpy().reshape(n, -1) - xg_ref)
     assert diff.max() <= 1.001 * step and np.mean(diff > 1e-6) <= 5e-3
+    # the sum over the entries that name an element has a fixed order: same bits on every run
+    xg2 = torch.full(X.shape, -3.0, device="cuda")
+    _cabi.check(lib.ab200_tile_backward_indexed(t._h, dd.data_ptr(), xg2.data_ptr(), X.size, m_batch, n,
+                                                int(trans), None))
+    torch.cuda.synchronize()
+    assert torch.equal(xg, xg2)
 
     lr = 0.01
     t.set_learning_rate(lr)
