@@ -191,6 +191,23 @@ class TransferParams(C.Structure):
     ]
 
 
+class MixedPrecParams(C.Structure):
+    """``ab200_mixedprec_params``."""
+
+    _fields_ = [
+        ("enabled", C.c_int32),
+        ("transfer_every", C.c_int32),
+        ("n_rows_per_transfer", C.c_int32),
+        ("random_row", C.c_int32),
+        ("granularity", C.c_float),
+        ("n_x_bins", C.c_int32),
+        ("n_d_bins", C.c_int32),
+        ("stoc_round_x", C.c_int32),
+        ("stoc_round_d", C.c_int32),
+        ("transfer_lr", C.c_float),
+    ]
+
+
 class TileConfig(C.Structure):
     """``ab200_tile_config``."""
 
@@ -203,6 +220,7 @@ class TileConfig(C.Structure):
         ("device_kind", C.c_int32),
         ("device", DeviceParams * 2),
         ("transfer", TransferParams),
+        ("mixed", MixedPrecParams),
         ("seed", C.c_uint64),
     ]
 

@@ -77,6 +77,7 @@ size_t ab200_sizeof(int which) {
   case 3: return sizeof(ab200_transfer_params);
   case 4: return sizeof(ab200_tile_config);
   case 5: return sizeof(ab200_scatter_plan);
+  case 6: return sizeof(ab200_mixedprec_params);
   default: return 0;
   }
 }
@@ -167,6 +168,13 @@ void ab200_default_transfer_params(ab200_transfer_params *tp) {
   tp->transfer_columns = 1;
   ab200_default_io_params(&tp->transfer_io);
   ab200_default_update_params(&tp->transfer_up);
+}
+
+void ab200_default_mixedprec_params(ab200_mixedprec_params *mp) {
+  std::memset(mp, 0, sizeof(*mp));
+  mp->transfer_every = 1; /* rpu_mixedprec_device_base.h:26-31, rpu_mixedprec_device.h:32-36 */
+  mp->n_rows_per_transfer = -1;
+  mp->transfer_lr = 1.0f;
 }
 
 int ab200_tile_create(const ab200_tile_config *cfg, int cuda_device, ab200_tile **out) {

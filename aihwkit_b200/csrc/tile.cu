@@ -386,6 +386,19 @@ Tile::Tile(const ab200_tile_config &cfg, int cuda_device) : cfg_(cfg) {
   if (cfg.device_kind < AB200_DEVICE_IDEAL || cfg.device_kind > AB200_DEVICE_PIECEWISE_STEP) {
     AB200_FATAL("device kind not implemented");
   }
+  if (cfg.mixed.enabled) {
+    const ab200_mixedprec_params &mp = cfg.mixed;
+    if (cfg.device_kind == AB200_DEVICE_IDEAL || cfg.device_kind == AB200_DEVICE_TRANSFER) {
+      AB200_FATAL("MixedPrec: expects a pulsed analog device in device[0]");
+    }
+    if ((mp.n_x_bins > 0) != (mp.n_d_bins > 0)) {
+      AB200_FATAL("MixedPrec: quantising only one of x and d is not implemented (set both n_x_bins and "
+                  "n_d_bins, or neither)");
+    }
+    if (mp.transfer_every < 0) {
+      AB200_FATAL("MixedPrec: transfer_every must not be negative");
+    }
+  }
   if (cfg.device_kind == AB200_DEVICE_TRANSFER) {
     const ab200_transfer_params &t = cfg.transfer;
     if (t.gamma != 0.0f) {
@@ -568,6 +581,11 @@ Tile::~Tile() {
     cudaFree(t_mean_);
     cudaFree(t_past_);
     cudaFree(idx_);
+    cudaFree(chi_);
+    cudaFree(mp_qx_);
+    cudaFree(mp_qd_);
+    cudaFree(mp_counts_);
+    cudaFree(mp_onehot_);
     cudaFree(idx_t_);
     cudaFree(csr_off_);
     cudaFree(csr_pos_);
@@ -678,6 +696,18 @@ void Tile::toDevice(int cuda_device) {
       AB200_CUDA(cudaMemset(t_mean_, 0, size * sizeof(float)));
       AB200_CUDA(cudaMemset(t_past_, 0, size * sizeof(float)));
       chop_switched_.assign((size_t)x_size_, 0);
+    }
+  }
+  if (cfg_.mixed.enabled) {
+    AB200_CUDA(cudaMalloc(&chi_, size * sizeof(float)));
+    AB200_CUDA(cudaMemset(chi_, 0, size * sizeof(float)));
+    mp_update_idx_ = 0;
+    mp_row_idx_ = 0;
+    // the device's granularity unless set (MixedPrecRPUDeviceBase::populate,
+    // rpu_mixedprec_device_base.cpp:229-240)
+    mp_granularity_ = cfg_.mixed.granularity > 0.0f ? cfg_.mixed.granularity : dev_[0].dw_min;
+    if (!(mp_granularity_ > 0.0f)) {
+      AB200_FATAL("Cannot establish granularity from device. Need explicit setting >=0.");
     }
   }
   AB200_CUDA(cudaMalloc(&bm_stats_, 2 * sizeof(int)));
@@ -923,6 +953,12 @@ void Tile::setWeightsDevice(const float *w_dev_xd, cudaStream_t s) {
     update_idx_ = 0;
     slice_idx_ = 0;
   }
+  if (cfg_.mixed.enabled) {
+    // MixedPrecRPUDevice::onSetWeights (rpu_mixedprec_device.cpp:348-355): chi and the counters start again
+    AB200_CUDA(cudaMemsetAsync(chi_, 0, size * sizeof(float), s));
+    mp_update_idx_ = 0;
+    mp_row_idx_ = 0;
+  }
   w_version_++;
   AB200_CUDA(cudaStreamSynchronize(s));
 }
@@ -981,7 +1017,7 @@ int Tile::hiddenCount() const {
     return (int)dev_[0].names.size() + (int)dev_[1].names.size() + 2 +
            (cfg_.transfer.dynamic ? 3 : cfg_.transfer.buffered ? 1 : 0);
   }
-  return (int)dev_[0].names.size();
+  return (int)dev_[0].names.size() + (cfg_.mixed.enabled ? 1 : 0);
 }
 
 const char *Tile::hiddenName(int i) const {
@@ -990,6 +1026,9 @@ const char *Tile::hiddenName(int i) const {
     return "";
   }
   if (cfg_.device_kind != AB200_DEVICE_TRANSFER) {
+    if (i == (int)dev_[0].names.size()) {
+      return "hidden_weights_chi"; // MixedPrecRPUDeviceBase::getDPNames (rpu_mixedprec_device_base.cpp:368-378)
+    }
     return dev_[0].names[i].c_str();
   }
   int n0 = (int)dev_[0].names.size();
@@ -1017,6 +1056,21 @@ void Tile::getHidden(float *out) {
   }
   if (cfg_.device_kind != AB200_DEVICE_TRANSFER) {
     std::memcpy(out, dev_[0].host.data(), dev_[0].host.size() * sizeof(float));
+    if (cfg_.mixed.enabled) {
+      float *o = out + dev_[0].host.size();
+      if (device_ >= 0) {
+        std::vector<float> t(size);
+        AB200_CUDA(cudaDeviceSynchronize());
+        AB200_CUDA(cudaMemcpy(t.data(), chi_, size * sizeof(float), cudaMemcpyDeviceToHost));
+        for (int i = 0; i < d_size_; i++) {
+          for (int j = 0; j < x_size_; j++) {
+            o[(size_t)i * x_size_ + j] = t[(size_t)j * d_size_ + i];
+          }
+        }
+      } else {
+        std::memset(o, 0, size * sizeof(float));
+      }
+    }
     return;
   }
   float *o = out;
@@ -1109,6 +1163,15 @@ void Tile::setHidden(const float *in) {
       requireDevice("set_hidden_parameters");
       uploadDeviceStore(dev_[k]);
     }
+  }
+  if (cfg_.mixed.enabled && device_ >= 0) {
+    std::vector<float> t(size);
+    for (int i = 0; i < d_size_; i++) {
+      for (int j = 0; j < x_size_; j++) {
+        t[(size_t)j * d_size_ + i] = p[(size_t)i * x_size_ + j];
+      }
+    }
+    AB200_CUDA(cudaMemcpy(chi_, t.data(), size * sizeof(float), cudaMemcpyHostToDevice));
   }
   if (cfg_.device_kind == AB200_DEVICE_TRANSFER && cfg_.transfer.buffered && device_ >= 0) {
     float *planes[3] = {t_buffer_, t_mean_, t_past_};
@@ -1614,6 +1677,14 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
   u.s_begin = 0;
   u.s_end = m;
 
+  if (cfg_.mixed.enabled) {
+    // the compound updates directly, whatever the pulse type (rpu_weight_updater.cpp:212-216)
+    if (delta_w_) {
+      AB200_FATAL("set_delta_weights is not implemented for the mixed-precision compound");
+    }
+    updateMixed(u, s);
+    return;
+  }
   const bool fp_update = cfg_.device_kind == AB200_DEVICE_IDEAL || up_.pulse_type == AB200_PULSE_NONE;
   if (fp_update) {
     if (cfg_.device_kind == AB200_DEVICE_TRANSFER) {
@@ -1712,6 +1783,132 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
     }
     s0 = s1;
   }
+}
+
+// Mixed-precision compound (MixedPrecRPUDevice::doDirectVectorUpdate, rpu_mixedprec_device.cpp:
+// 196-345; MixedPrecRPUDeviceBase::doTransfer / transfer, rpu_mixedprec_device_base.cpp:282-352):
+// chi += lr q(d) q(x)^T sample by sample; after sample k > 0 with k % (transfer_every * m) == 0
+// the next rows of chi hand their whole granularities to the device.
+void Tile::updateMixed(UpdateProblem &u, cudaStream_t s) {
+  const ab200_mixedprec_params &mp = cfg_.mixed;
+  const int m = u.m;
+  const bool quantised = mp.n_x_bins > 0 && mp.n_d_bins > 0;
+  UpdateProblem a = u; // accumulation into chi
+  a.w = chi_;
+  a.par4 = nullptr;
+  if (quantised) {
+    if (m > mp_q_cap_) {
+      AB200_CUDA(cudaStreamSynchronize(s));
+      cudaFree(mp_qx_);
+      cudaFree(mp_qd_);
+      mp_qx_ = mp_qd_ = nullptr;
+      const int cap = m + m / 4 + 16;
+      AB200_CUDA(cudaMalloc(&mp_qx_, (size_t)cap * x_size_ * sizeof(float)));
+      AB200_CUDA(cudaMalloc(&mp_qd_, (size_t)cap * d_size_ * sizeof(float)));
+      mp_q_cap_ = cap;
+    }
+    launchMixedQuantize(u, mp.n_x_bins, mp.n_d_bins, mp.stoc_round_x, mp.stoc_round_d, mp_qx_, mp_qd_, s);
+    a.x = mp_qx_;
+    a.x_ss = x_size_;
+    a.x_fs = 1;
+    a.x_real = x_size_;
+    a.d = mp_qd_;
+    a.d_ss = d_size_;
+    a.d_fs = 1;
+  }
+  const long long every = (long long)mp.transfer_every * m;
+  int s0 = 0;
+  while (s0 < m) {
+    // the segment ends with the sample after which a transfer falls
+    int s1 = m;
+    if (every > 0) {
+      long long k = mp_update_idx_; // index of sample s0
+      long long next = k > 0 && k % every == 0 ? k : (k / every + 1) * every;
+      if (next - k < (long long)(m - s0)) {
+        s1 = s0 + (int)(next - k) + 1;
+      }
+    }
+    UpdateProblem seg = a;
+    seg.x = a.x + (long long)s0 * a.x_ss;
+    seg.d = a.d + (long long)s0 * a.d_ss;
+    seg.m = s1 - s0;
+    // chi += (lr * d) * x in the order of the samples (the quantised form is a plain loop in
+    // the reference; the unquantised one a BLAS rank-one update)
+    launchFPUpdate(seg, -lr_, s, /*overwrite=*/false, /*clip_each=*/quantised);
+    const long long last = mp_update_idx_ + (s1 - s0) - 1; // index of the segment's last sample
+    mp_update_idx_ += s1 - s0;
+    if (every > 0 && last > 0 && last % every == 0) {
+      transferMixed(s);
+    }
+    s0 = s1;
+  }
+}
+
+void Tile::transferMixed(cudaStream_t s) {
+  const ab200_mixedprec_params &mp = cfg_.mixed;
+  if (mp.n_rows_per_transfer == 0 || mp.transfer_lr == 0.0f) {
+    return;
+  }
+  int n = mp.n_rows_per_transfer < 0 ? d_size_ : std::min(mp.n_rows_per_transfer, d_size_);
+  int row0 = mp_row_idx_;
+  if (mp.random_row && n < d_size_) {
+    row0 = std::max(std::min((int)floorf(chop_rng_.uniform() * (float)d_size_), d_size_ - 1), 0);
+  }
+  if (!mp_counts_) {
+    AB200_CUDA(cudaMalloc(&mp_counts_, (size_t)d_size_ * x_size_ * sizeof(float)));
+    AB200_CUDA(cudaMalloc(&mp_onehot_, (size_t)d_size_ * d_size_ * sizeof(float)));
+  }
+  launchMixedTruncate(chi_, x_size_, d_size_, row0, n, mp_granularity_, mp_counts_, mp_onehot_, s);
+  // one pulsed update with the rows as samples: every row writes only its own weights, so the
+  // result is that of the reference's row-by-row updates
+  UpEff up = up_;
+  up.update_management = 1; // "should be both true to get the desired step" (setUpPar, :293-303)
+  up.update_bl_management = 1;
+  const int nseg = pulseSegments(up);
+  ensureScratch(n * nseg);
+  w_version_++;
+  const float t_lr = mp_granularity_ * mp.transfer_lr;
+  UpdateProblem u{};
+  u.x = mp_counts_;
+  u.x_ss = x_size_;
+  u.x_fs = 1;
+  u.x_real = x_size_;
+  u.d = mp_onehot_;
+  u.d_ss = d_size_;
+  u.d_fs = 1;
+  u.x_size = x_size_;
+  u.d_size = d_size_;
+  u.m = n;
+  u.key = key_;
+  u.call = 0x40000000u + transfer_calls_++;
+  u.xw = xw_;
+  u.dw = dw_;
+  u.w = w_;
+  u.s_begin = 0;
+  u.s_end = n;
+  u.par4 = dev_[0].par4;
+  if (up.pulse_type == AB200_PULSE_NONE) {
+    launchFPUpdate(u, t_lr, s);
+  } else if (up.pulse_type == AB200_PULSE_NONE_WITH_DEVICE) {
+    launchFPUpdate(u, t_lr, s, /*overwrite=*/false, /*clip_each=*/true);
+  } else {
+    u.lr = fabsf(t_lr);
+    u.lr_neg = t_lr < 0.0f;
+    u.up = up;
+    u.nseg = nseg;
+    u.dw_min = dev_[0].dw_min;
+    u.par2 = dev_[0].par2;
+    u.kind = dev_[0].kind;
+    u.dw_min_std = dev_[0].dw_min_std;
+    u.es0 = dev_[0].es0;
+    u.es1 = dev_[0].es1;
+    u.pw = dev_[0].pw;
+    u.pw_n = dev_[0].pw_n;
+    u.mult_noise = dev_[0].mult_noise;
+    launchPulsePrepare(u, s);
+    launchPulsedUpdate(u, s);
+  }
+  mp_row_idx_ = (row0 + n) % d_size_;
 }
 
 void Tile::coincidences(const float *x, const float *d, int32_t *counts, cudaStream_t s) {

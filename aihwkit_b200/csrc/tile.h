@@ -246,6 +246,12 @@ void launchTransferDynamicBuffer(float *buffer_col, float *mean_col, float *past
                                  float sample_momentum, int previously_switched,
                                  unsigned char *chop_in, int col, const unsigned char *chop_out,
                                  int flip_in, cudaStream_t stream);
+// Mixed-precision compound: quantised copies of the x / d samples of a batch; pulse counts (and
+// one-hot d vectors) of the rows of chi that a transfer moves to the device
+void launchMixedQuantize(const UpdateProblem &p, int n_x_bins, int n_d_bins, int sr_x, int sr_d, float *qx,
+                         float *qd, cudaStream_t stream);
+void launchMixedTruncate(float *chi, int x_size, int d_size, int row0, int n_rows, float gran, float *counts,
+                         float *onehot, cudaStream_t stream);
 // flip every out chopper with probability `prob`
 void launchFlipChoppers(unsigned char *chop, int n, float prob, PhiloxKey key, uint32_t call,
                         cudaStream_t stream);
@@ -482,6 +488,16 @@ private:
   long long idx_t_cap_ = 0;
   bool idx_t_valid_ = false;
   RowGather upd_gather_; // set around an update whose samples are gathered from images
+  // mixed-precision compound: digital accumulator chi ([x][d] like the weights), quantised
+  // samples of the current batch, pulse counts / one-hot vectors of the rows in transfer, the
+  // sample counter and the next row to transfer
+  float *chi_ = nullptr, *mp_qx_ = nullptr, *mp_qd_ = nullptr, *mp_counts_ = nullptr, *mp_onehot_ = nullptr;
+  int mp_q_cap_ = 0;
+  long long mp_update_idx_ = 0;
+  int mp_row_idx_ = 0;
+  float mp_granularity_ = 0.0f;
+  void updateMixed(UpdateProblem &u, cudaStream_t s);
+  void transferMixed(cudaStream_t s);
   // inverse of the index array for the backward pass: for every image element the positions of
   // the index array that name it (CSR: csr_off_[e] .. csr_off_[e + 1] into csr_pos_), in
   // ascending order, so that the sum over them has a fixed order

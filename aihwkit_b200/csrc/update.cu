@@ -1123,10 +1123,16 @@ __global__ void __launch_bounds__(256) fpUpdateKernel(UpdateProblem p, float lr_
       hi[t] = lo[t] = 0.0f;
       if (i < p.d_size && j < p.x_size) {
         const long long idx = (long long)j * p.d_size + i;
-        const float4 q = p.par4[idx];
         wv[t] = p.w[idx];
-        hi[t] = q.z;
-        lo[t] = q.w;
+        if (p.par4 != nullptr) {
+          const float4 q = p.par4[idx];
+          hi[t] = q.z;
+          lo[t] = q.w;
+        } else {
+          // no bounds: the digital accumulator of a mixed-precision compound
+          hi[t] = 3.4e38f;
+          lo[t] = -3.4e38f;
+        }
       }
     }
   }
@@ -1186,6 +1192,89 @@ void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream
     AB200_CUDA(launchChained(fpUpdateKernel<false>, grid, dim3(256), 0, stream, p, lr_signed,
                              overwrite ? 1 : 0));
   }
+  AB200_LAUNCH_CHECK();
+}
+
+// Mixed-precision compound (MixedPrecRPUDevice::doDirectVectorUpdate,
+// rpu_mixedprec_device.cpp:196-345): x and d of every sample quantised to n bins of their abs-max,
+// q = clip(rint(v / width + u - 0.5), +-half) * width with width = amax / half, half = n / 2.
+__global__ void __launch_bounds__(256)
+    mixedQuantizeKernel(const float *x, long long x_ss, long long x_fs, int x_real, const float *d,
+                        long long d_ss, long long d_fs, int x_size, int d_size, int n_x_bins, int n_d_bins,
+                        int sr_x, int sr_d, PhiloxKey key, uint32_t call, float *qx, float *qd) {
+  pdlEnter();
+  __shared__ float sh[8];
+  const int s = blockIdx.x;
+  const float *xr = x + (long long)s * x_ss, *dr = d + (long long)s * d_ss;
+  float xm = 0.0f, dm = 0.0f;
+  for (int j = threadIdx.x; j < x_size; j += blockDim.x) {
+    xm = fmaxf(xm, fabsf(j < x_real ? xr[(long long)j * x_fs] : 1.0f));
+  }
+  for (int i = threadIdx.x; i < d_size; i += blockDim.x) {
+    dm = fmaxf(dm, fabsf(dr[(long long)i * d_fs]));
+  }
+  xm = blockMax(xm, sh);
+  dm = blockMax(dm, sh);
+  const float half_x = (float)(n_x_bins / 2), half_d = (float)(n_d_bins / 2);
+  float x_width = __fdiv_rn(xm, half_x), d_width = __fdiv_rn(dm, half_d);
+  x_width = x_width == 0.0f ? 1.0f : x_width;
+  d_width = d_width == 0.0f ? 1.0f : d_width;
+  for (int l = threadIdx.x; l < x_size + d_size; l += blockDim.x) {
+    const bool is_x = l < x_size;
+    const int idx = is_x ? l : l - x_size;
+    const float v = is_x ? (idx < x_real ? xr[(long long)idx * x_fs] : 1.0f) : dr[(long long)idx * d_fs];
+    const float width = is_x ? x_width : d_width, half = is_x ? half_x : half_d;
+    float st = 0.0f;
+    if (is_x ? sr_x : sr_d) {
+      uint32_t r[4];
+      philox4x32<7>((uint32_t)idx, (uint32_t)s, call, is_x ? TAG_PULSE_X : TAG_PULSE_D, key, r);
+      st = __fadd_rn(u01(r[0]), -0.5f);
+    }
+    float q = rintf(__fadd_rn(__fdiv_rn(v, width), st));
+    q = __fmul_rn(fminf(fmaxf(q, -half), half), width);
+    if (is_x) {
+      qx[(long long)s * x_size + idx] = q;
+    } else {
+      qd[(long long)s * d_size + idx] = q;
+    }
+  }
+}
+
+// The whole multiples of the granularity in rows [row0, row0 + n_rows) (mod d_size) of chi leave
+// it as pulse counts (forwardUpdate, rpu_mixedprec_device.cpp:148-190); also writes the one-hot
+// d vectors of the rows. chi is [x][d] like the weights.
+__global__ void __launch_bounds__(256)
+    mixedTruncateKernel(float *chi, int x_size, int d_size, int row0, int n_rows, float gran, float *counts,
+                        float *onehot) {
+  pdlEnter();
+  const int j = blockIdx.y;
+  const int row = (row0 + j) % d_size;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < x_size) {
+    const long long idx = (long long)t * d_size + row;
+    const float value = chi[idx];
+    const float dw = truncf(__fdiv_rn(value, gran));
+    counts[(long long)j * x_size + t] = dw;
+    chi[idx] = __fsub_rn(value, __fmul_rn(dw, gran));
+  }
+  if (t < d_size) {
+    onehot[(long long)j * d_size + t] = t == row ? 1.0f : 0.0f;
+  }
+}
+
+void launchMixedQuantize(const UpdateProblem &p, int n_x_bins, int n_d_bins, int sr_x, int sr_d, float *qx,
+                         float *qd, cudaStream_t stream) {
+  AB200_CUDA(launchChained(mixedQuantizeKernel, dim3(p.m), dim3(256), 0, stream, p.x, p.x_ss, p.x_fs, p.x_real,
+                           p.d, p.d_ss, p.d_fs, p.x_size, p.d_size, n_x_bins, n_d_bins, sr_x, sr_d, p.key,
+                           p.call, qx, qd));
+  AB200_LAUNCH_CHECK();
+}
+
+void launchMixedTruncate(float *chi, int x_size, int d_size, int row0, int n_rows, float gran, float *counts,
+                         float *onehot, cudaStream_t stream) {
+  const int width = x_size > d_size ? x_size : d_size;
+  AB200_CUDA(launchChained(mixedTruncateKernel, dim3((width + 255) / 256, n_rows), dim3(256), 0, stream, chi,
+                           x_size, d_size, row0, n_rows, gran, counts, onehot));
   AB200_LAUNCH_CHECK();
 }
 

@@ -669,6 +669,52 @@ class ChoppedTransferResistiveDeviceParameter(BufferedTransferResistiveDevicePar
         return c
 
 
+class MixedPrecResistiveDeviceParameter:
+    """MixedPrecRPUDeviceMetaParameter (rpu_base_devices.cpp:778-804): a digital rank-update
+    accumulator in front of one pulsed analog device, set with ``set_device_parameter``."""
+
+    def __init__(self) -> None:
+        # SimpleRPUDeviceMetaParameter part (src/rpucuda/rpu.h:140-175)
+        self.construction_seed = 0
+        self.transfer_every = 1
+        self.n_rows_per_transfer = -1
+        self.random_row = False
+        self.granularity = 0.0
+        self.compute_sparsity = False
+        self.n_x_bins = 0
+        self.n_d_bins = 0
+        self.stoc_round_x = False
+        self.stoc_round_d = False
+        self.transfer_lr = 1.0
+        self._device = None
+
+    def set_device_parameter(self, parameter) -> bool:
+        kind = getattr(parameter, "_kind", -1)
+        if kind in (-1, DEVICE_IDEAL, DEVICE_TRANSFER):
+            return False  # setDevicePar accepts pulsed devices only
+        self._device = parameter
+        return True
+
+    @property
+    def _kind(self) -> int:
+        return -1 if self._device is None else self._device._kind
+
+    def _to_c_mixed(self) -> _cabi.MixedPrecParams:
+        if (int(self.n_x_bins) > 0) != (int(self.n_d_bins) > 0):
+            raise RuntimeError("MixedPrec: quantising only one of x and d is not implemented by the "
+                               "B200 analog tile")
+        c = _cabi.MixedPrecParams()
+        c.enabled = 1
+        c.transfer_every = int(self.transfer_every)
+        c.n_rows_per_transfer = int(self.n_rows_per_transfer)
+        c.random_row = int(bool(self.random_row))
+        c.granularity = float(self.granularity)
+        c.n_x_bins, c.n_d_bins = int(self.n_x_bins), int(self.n_d_bins)
+        c.stoc_round_x, c.stoc_round_d = int(bool(self.stoc_round_x)), int(bool(self.stoc_round_d))
+        c.transfer_lr = float(self.transfer_lr)
+        return c
+
+
 class DynamicTransferResistiveDeviceParameter(ChoppedTransferResistiveDeviceParameter):
     """DynamicTransferRPUDeviceMetaParameter, Tiki-Taka with choppers and a running-mean reference
     (rpu_base_devices.cpp:912-924; src/rpucuda/rpu_dynamic_transfer_device.h:26-62)."""
@@ -730,6 +776,11 @@ class AnalogTileParameter:
             cfg.device[0].construction_seed = int(device_par.construction_seed)
             # SimpleMetaParameter: one exponent for all weights (src/rpucuda/rpu.h:165)
             cfg.device[0].drift = device_par.drift._to_c(simple=True)
+        elif isinstance(device_par, MixedPrecResistiveDeviceParameter):
+            cfg.device[0] = device_par._device._to_c()
+            cfg.mixed = device_par._to_c_mixed()
+            if device_par.construction_seed:
+                cfg.device[0].construction_seed = int(device_par.construction_seed)
         else:
             cfg.device[0] = device_par._to_c()
         return cfg

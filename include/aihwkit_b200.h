@@ -303,6 +303,30 @@ typedef struct ab200_transfer_params {
   float buffer_cap;
 } ab200_transfer_params;
 
+/* MixedPrecRPUDeviceMetaParameter (src/rpucuda/rpu_mixedprec_device.h:30-37,
+ * rpu_mixedprec_device_base.h:24-35; Nandakumar et al. 2020): the rank-one update of every sample
+ * is computed digitally, chi += lr * q(d) q(x)^T with x and d quantised to n_x_bins / n_d_bins
+ * levels of their abs-max (rint, optionally stochastic), and kept in a matrix chi. After sample
+ * k > 0 with k % (transfer_every * m_batch) == 0, n_rows_per_transfer rows (< 0: all) starting
+ * at a running row index (random_row: drawn) move their whole multiples of the granularity
+ * (0: that of the device) to the analog device `device[0]` by a pulsed update with update
+ * management and update BL management on and learning rate granularity * transfer_lr.
+ * device_kind names the analog device. Quantising only one of x and d is not built (both
+ * counts positive, or both <= 0 for the unquantised outer product). set_weights clears chi and
+ * the counters. chi is the last hidden parameter, "hidden_weights_chi". */
+typedef struct ab200_mixedprec_params {
+  int32_t enabled;
+  int32_t transfer_every;
+  int32_t n_rows_per_transfer;
+  int32_t random_row;
+  float granularity;
+  int32_t n_x_bins;
+  int32_t n_d_bins;
+  int32_t stoc_round_x;
+  int32_t stoc_round_d;
+  float transfer_lr;
+} ab200_mixedprec_params;
+
 /* Everything PulsedMetaParameter::createRPUArray needs
  * (src/rpucuda/rpu_pulsed.cpp:49-56; rpu_base_devices.cpp:453-467). */
 typedef struct ab200_tile_config {
@@ -314,6 +338,7 @@ typedef struct ab200_tile_config {
   int32_t device_kind;          /* enum ab200_device_kind */
   ab200_device_params device[2]; /* [0] only, or fast/slow pair for TRANSFER */
   ab200_transfer_params transfer;
+  ab200_mixedprec_params mixed; /* enabled = 0 unless the device is a mixed-precision compound */
   uint64_t seed;                /* Philox key for all run-time noise of this tile */
 } ab200_tile_config;
 
@@ -334,6 +359,7 @@ void ab200_default_io_params(ab200_io_params *io);
 void ab200_default_update_params(ab200_update_params *up);
 void ab200_default_device_params(ab200_device_params *dp, int32_t kind);
 void ab200_default_transfer_params(ab200_transfer_params *tp);
+void ab200_default_mixedprec_params(ab200_mixedprec_params *mp); /* enabled = 0 */
 
 /* ---- tile life cycle ------------------------------------------------------------------- */
 

@@ -15,6 +15,7 @@
 #include "rpu_buffered_transfer_device.h"
 #include "rpu_chopped_transfer_device.h"
 #include "rpu_dynamic_transfer_device.h"
+#include "rpu_mixedprec_device.h"
 #include "rpu_constantstep_device.h"
 #include "rpu_expstep_device.h"
 #include "rpu_linearstep_device.h"
@@ -292,6 +293,22 @@ int ref_tile_create(const ab200_tile_config *cfg, void **out) {
     ab200_device_params d = cfg->device[0];
     d.kind = cfg->device_kind;
     dp = makeSingle(d);
+    if (cfg->mixed.enabled) {
+      const ab200_mixedprec_params &m = cfg->mixed;
+      auto mp = std::make_unique<MixedPrecRPUDeviceMetaParameter<float>>();
+      mp->setDevicePar(*dp);
+      mp->transfer_every = m.transfer_every;
+      mp->n_rows_per_transfer = m.n_rows_per_transfer;
+      mp->random_row = m.random_row != 0;
+      mp->granularity = m.granularity;
+      mp->n_x_bins = m.n_x_bins;
+      mp->n_d_bins = m.n_d_bins;
+      mp->stoc_round_x = m.stoc_round_x != 0;
+      mp->stoc_round_d = m.stoc_round_d != 0;
+      mp->transfer_lr = m.transfer_lr;
+      mp->construction_seed = cfg->device[0].construction_seed;
+      dp = std::move(mp);
+    }
   }
 
   auto t = new RefTile();

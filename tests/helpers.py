@@ -186,3 +186,17 @@ def dynamic_transfer_device(in_chop_prob: float = 0.5, tail_weightening: float =
     dp.tail_weightening, dp.buffer_cap = tail_weightening, buffer_cap
     dp.experimental_correct_accumulation = correct_accumulation
     return dp
+
+
+def mixed_precision_device(kind: str = "sb", n_x_bins: int = 9, n_d_bins: int = 5, transfer_every: int = 1,
+                           n_rows_per_transfer: int = -1, granularity: float = 0.0,
+                           transfer_lr: float = 1.0, seed: int = 21, **kw):
+    """MixedPrecisionCompound: a digital rank-update accumulator in front of one noise-free
+    analog device."""
+    dp = D.MixedPrecResistiveDeviceParameter()
+    assert dp.set_device_parameter(device(kind, False, dw_min=0.002, **kw))
+    dp.construction_seed = seed
+    dp.n_x_bins, dp.n_d_bins = n_x_bins, n_d_bins
+    dp.transfer_every, dp.n_rows_per_transfer = transfer_every, n_rows_per_transfer
+    dp.granularity, dp.transfer_lr = granularity, transfer_lr
+    return dp

@@ -617,3 +617,78 @@ def test_chopped_transfer_random_choppers_statistics():
         t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
     w = t.get_weights().numpy()
     assert (w < 0).mean() > 0.95 and np.abs(w).max() > 0.01  # w -= lr d x^T, all terms positive
+
+
+@pytest.mark.parametrize("kw", [
+    dict(),                                                   # all rows after every batch
+    dict(n_rows_per_transfer=3),                              # a running window of three rows
+    dict(transfer_every=2, n_rows_per_transfer=4, granularity=0.004, transfer_lr=0.5),
+    dict(kind="cs", n_x_bins=5, n_d_bins=3),
+])
+def test_mixed_precision_deterministic_against_reference(kw):
+    """Mixed-precision compound (src/rpucuda/rpu_mixedprec_device.cpp:148-345,
+    rpu_mixedprec_device_base.cpp:282-352) with both inputs quantised and deterministic pulses:
+    the digital accumulator chi and the weights follow the compiled reference update by update
+    (the transfer falls after the first sample of a batch, so every call is cut in two)."""
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    if not ref.available():
+        pytest.skip("compiled reference not built")
+    rng = np.random.default_rng(29)
+    x_size, d_size, m = 12, 10, 5
+    p = H.training_params(noise=False, pulse_det=True)
+    dp = H.mixed_precision_device(**kw)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    rt = ref.RefTile(cfg)
+    names = t.get_hidden_parameter_names()
+    assert names == rt.hidden_parameter_names() and names[-1] == "hidden_weights_chi"
+    assert np.array_equal(t.get_hidden_parameters().numpy(), rt.get_hidden_parameters())
+    lr = 0.1
+    t.set_learning_rate(lr)
+    rt.set_learning_rate(lr)
+    for step in range(10):
+        x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        d = rng.normal(0, 0.5, (m, d_size)).astype(np.float32)
+        t.update(torch.from_numpy(x).cuda(), torch.from_numpy(d).cuda())
+        rt.update(x, d)
+        hp, hr = t.get_hidden_parameters().numpy(), rt.get_hidden_parameters()
+        assert np.abs(hp[-1] - hr[-1]).max() <= 1e-6, f"chi, update {step}"
+        assert np.abs(t.get_weights().numpy() - rt.get_weights()).max() <= 1e-6, f"weights, update {step}"
+    assert np.abs(rt.get_weights()).max() > 0.01 and np.abs(hr[-1]).max() > 0
+    # chi travels with the hidden parameters; set_weights clears it and the counters
+    t2 = T.AnalogTile(cfg, cuda_device=0)
+    t2.set_hidden_parameters(t.get_hidden_parameters())
+    assert torch.equal(t2.get_hidden_parameters(), t.get_hidden_parameters())
+    t.set_weights(t.get_weights())
+    assert float(t.get_hidden_parameters()[-1].abs().max()) == 0.0
+
+
+def test_mixed_precision_unquantised_stochastic_pulses():
+    """No quantisation (a plain rank-one accumulation) and stochastic transfer pulses on a
+    constant-step device far from its bounds: the weights follow -lr * sum d x^T on average, and
+    what chi keeps is the last batch plus less than one granularity per element."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(31)
+    x_size, d_size, m, lr, n_upd = 24, 16, 8, 0.002, 12
+    p = H.training_params(noise=False, pulse_det=False)
+    dp = H.mixed_precision_device(kind="cs", n_x_bins=0, n_d_bins=0)
+    t = T.AnalogTile(p._config(x_size, d_size, dp, seed=3), cuda_device=0)
+    t.set_learning_rate(lr)
+    X = rng.uniform(0.2, 1, (m, x_size)).astype(np.float32)
+    Dm = np.abs(rng.normal(0, 0.5, (m, d_size))).astype(np.float32) + 0.1
+    for _ in range(n_upd):
+        t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+    w = t.get_weights().numpy()
+    chi = t.get_hidden_parameters().numpy()[-1]
+    per_batch = lr * Dm.T @ X
+    # the transfer of a batch happens one sample into the next: n_upd - 1 batches have moved
+    want = -(n_upd - 1) * per_batch
+    assert np.abs(want).max() < 0.3  # far from the bounds
+    assert (w <= 0).all() and abs(w.sum() / want.sum() - 1.0) < 0.1, w.sum() / want.sum()
+    assert np.abs(chi).max() < per_batch.max() + 2 * 0.002 + 1e-6
+    # chi + what reached the device is the digital sum up to the stochastic pulse counts
+    total = -(w - chi)
+    assert abs(total.sum() / (n_upd * per_batch).sum() - 1.0) < 0.1
