@@ -117,6 +117,8 @@ struct TcKernelParams {
   // row, instead of 16 bytes in each of 32 rows - for outputs so wide that the stores bound the
   // kernel
   int row_stores;
+  // std-dev of the output noise per output line ([N_total], single tile; LINE variants), or null
+  const float *onv;
   // > 0: the output is stored transposed in blocks of that many rows: row r, column c goes to
   // out[((r / out_t_rows) * out_ss + c) * out_t_rows + r % out_t_rows] (out_ss = columns of the
   // whole layer) - the image-major layout of the indexed convolution interface. The row-per-lane
@@ -348,7 +350,9 @@ __device__ __forceinline__ void ownerOf(const TcKernelParams &p, int grow0, int 
 //               128 rows of codes and half of the stacked weight tile from its own shared memory,
 //               so the shared-memory traffic per SM and per FLOP drops by a third. Each CTA keeps
 //               the accumulator rows of its own 128 rows in its own TMEM and runs its own epilogue.
-template <bool BM, bool PAIR, bool CODES = false>
+// LINE: the std-dev of the output noise is read per output line from a table (out_noise_std > 0,
+// single tile) and combined per element with the weight-noise term of the row.
+template <bool BM, bool PAIR, bool CODES = false, bool LINE = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     mvmTcKernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_bhi,
                 const __grid_constant__ CUtensorMap tm_blo, const TcKernelParams p) {
@@ -649,6 +653,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       const bool last = i + 1 == p.I;
       const float sc = sc_n, fac = fac_n;
       const float sigma = outputSigma(io, vn_n);
+      // LINE: variance of the row's weight-noise term, to be joined with the line's own
+      const float wv = (LINE && io.w_noise_type == AB200_WNOISE_ADDITIVE_CONSTANT && io.w_noise > 0.0f)
+                           ? io.w_noise * vn_n
+                           : 0.0f;
+      const float wv2 = wv * wv;
+      auto lineSigma = [&](int col) -> float { // col: column within the chunk
+        const float o = col < ch.w ? __ldg(p.onv + ch.z + col) : 0.0f;
+        return wv2 > 0.0f ? sqrtf(fmaf(o, o, wv2)) : o;
+      };
       if (row_ok && !last) {
         const long long si = (long long)(i + 1) * p.m + row;
         sc_n = p.scale[si];
@@ -738,7 +751,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           gauss8Keyed(rkeys, ctr + (uint64_t)(c0 >> 3), p.call, tile_tag, z);
 #pragma unroll
           for (int j = 0; j < 8; j++) {
-            float r = fmaf(z[j], sig_codes, acc[j] * in_codes);
+            const float sg = LINE ? (live ? lineSigma(cbase + c0 + j) * inv_res_out : 0.0f) : sig_codes;
+            float r = fmaf(z[j], sg, acc[j] * in_codes);
             r = (r + kMagic) - kMagic; // round to nearest even
             if (BM && cbase + c0 + j < ch.w) {
               exceeded = exceeded || (r > bound_codes) || (io.bm_test_negative_bound && r < -bound_codes);
@@ -764,7 +778,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
               if (cbase + c0 + j < ch.w) {
                 float y;
                 if (sigma > 0.0f) { // noise without an ADC
-                  y = fmaf(acc[j], io.res_in, sigma * z[j]);
+                  y = fmaf(acc[j], io.res_in, (LINE ? lineSigma(cbase + c0 + j) : sigma) * z[j]);
                   if (BM) {
                     exceeded = exceeded || (y > io.out_bound) ||
                                (io.bm_test_negative_bound && y < -io.out_bound);
@@ -1382,7 +1396,7 @@ bool TcEngine::gatherSupported(int in_size) {
   return kGatherWarps * kpad * sizeof(float) <= 200 * 1024;
 }
 
-bool TcEngine::ioSupported(const IOEff &io) {
+bool TcEngine::ioSupported(const IOEff &io, bool line_table) {
   if (io.is_perfect || !(io.res_in > 0.0f) || !(io.inp_bound < 1e30f)) {
     return false;
   }
@@ -1394,7 +1408,11 @@ bool TcEngine::ioSupported(const IOEff &io) {
   }
   // a noise std-dev per output line or per element (PCMRead) likewise, and the non-idealities
   // of the output lines (IR drop, voltage offsets, series resistance, non-linearity)
-  if (ioLineSigma(io) || ioNeedsLineChain(io)) {
+  if ((io.w_noise_type == AB200_WNOISE_PCM_READ && io.w_noise > 0.0f) || ioNeedsLineChain(io)) {
+    return false;
+  }
+  // a std-dev of the output noise per line: only where the caller hands over its table
+  if (io.out_noise_std > 0.0f && !line_table) {
     return false;
   }
   // the DAC kernel of this path knows the common noise-management types only, and the re-run
@@ -1555,7 +1573,7 @@ void TcEngine::run(const Run &r, cudaStream_t s) {
     return;
   }
   const int I = (int)in_sizes_.size();
-  if (!ioSupported(r.io)) {
+  if (!ioSupported(r.io, r.onv != nullptr)) {
     AB200_FATAL("tensor-core MVM: IO settings not expressible as integer DAC codes");
   }
   ensureBatch(r.m);
@@ -1801,12 +1819,18 @@ void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
   const bool chained = pdlEnabled() && p.flag_table == nullptr;
   const bool pair = usePairs(r.m);
   const bool bm = r.io.bm != AB200_BM_NONE;
+  const bool line = r.onv != nullptr;
+  if (line && (codes || in_sizes_.size() != 1 || out_sizes_.size() != 1)) {
+    AB200_FATAL("tensor-core MVM: a noise table per output line needs a single tile and fp32 outputs");
+  }
+  p.onv = r.onv;
   if (pair) {
     const int n_items = n_chunks_ * ((r.m + 2 * TC_M - 1) / (2 * TC_M));
     const int n_pairs = n_items < n_sm / 2 ? n_items : n_sm / 2;
     auto kernel = codes ? mvmTcKernel<false, true, true>
-                        : (bm ? mvmTcKernel<true, true> : mvmTcKernel<false, true>);
-    raiseSmem(kernel, codes ? 0 : (bm ? 1 : 2), TC2_SMEM_BYTES);
+                        : line ? (bm ? mvmTcKernel<true, true, false, true> : mvmTcKernel<false, true, false, true>)
+                               : (bm ? mvmTcKernel<true, true> : mvmTcKernel<false, true>);
+    raiseSmem(kernel, codes ? 0 : (bm ? 1 : 2) + (line ? 6 : 0), TC2_SMEM_BYTES);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * n_pairs);
     cfg.blockDim = dim3(TC_THREADS);
@@ -1827,8 +1851,9 @@ void TcEngine::launchMma(const Run &r0, int row0, int rows, cudaStream_t s) {
     const int n_items = n_chunks_ * ((r.m + TC_M - 1) / TC_M);
     dim3 grid(n_items < n_sm ? n_items : n_sm); // one persistent CTA per SM
     auto kernel = codes ? mvmTcKernel<false, false, true>
-                        : (bm ? mvmTcKernel<true, false> : mvmTcKernel<false, false>);
-    raiseSmem(kernel, codes ? 3 : (bm ? 4 : 5), TC_SMEM_BYTES);
+                        : line ? (bm ? mvmTcKernel<true, false, false, true> : mvmTcKernel<false, false, false, true>)
+                               : (bm ? mvmTcKernel<true, false> : mvmTcKernel<false, false>);
+    raiseSmem(kernel, codes ? 3 : (bm ? 4 : 5) + (line ? 6 : 0), TC_SMEM_BYTES);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(TC_THREADS);

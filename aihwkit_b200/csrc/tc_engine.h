@@ -32,6 +32,8 @@ public:
     long long in_ss = 0;
     // rows gathered from whole images at `in` (indexed convolution interface) instead
     RowGather gather;
+    // std-dev of the output noise of every output line (out_noise_std > 0; single tile), or null
+    const float *onv = nullptr;
     int m = 0;
     float *out = nullptr; // [m][N_total], row stride out_ss
     long long out_ss = 0;
@@ -89,7 +91,8 @@ public:
   void run(const Run &r, cudaStream_t s);
 
   // whether the IO settings can be expressed as integer DAC codes in bf16
-  static bool ioSupported(const IOEff &io);
+  // (`line_table`: the caller passes the std-dev of the output noise of every line, Run::onv)
+  static bool ioSupported(const IOEff &io, bool line_table = false);
   // whether rows of this engine's width can be gathered through an index array by the DAC pass
   // (its shared-memory staging of one row per warp must fit)
   static bool gatherSupported(int in_size);

@@ -1271,6 +1271,7 @@ bool Tile::forwardGatherEligible(int b) const {
   p.out_size = p.out_store = d_size_;
   p.m = b;
   p.io = f_io_;
+  setLineTables(p, f_lt_, f_onv_);
   return !off && tcEligible(p) && TcEngine::gatherSupported(x_size_);
 }
 
@@ -1420,7 +1421,7 @@ bool Tile::tcEligible(const MvmProblem &p) const {
     return false;
   }
   if (p.in_fs != 1 || p.out_fs != 1 || p.in_real != p.in_size || p.out_store != p.out_size ||
-      !TcEngine::ioSupported(p.io)) {
+      !TcEngine::ioSupported(p.io, p.out_noise_vals != nullptr)) {
     return false;
   }
   if (mode >= 2) {
@@ -1447,6 +1448,7 @@ void Tile::runTc(const MvmProblem &p, cudaStream_t s) {
   r.in = p.in;
   r.in_ss = p.in_ss;
   r.gather = p.gather;
+  r.onv = p.out_noise_vals;
   r.m = p.m;
   r.out = p.out;
   r.out_ss = p.out_ss;

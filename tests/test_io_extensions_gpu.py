@@ -385,3 +385,60 @@ def test_pos_neg_separate_noise_moments(mv):
         yr = _repeat(lambda: rt.forward(X), reps)
         rr = ys.std(axis=0) / yr.std(axis=0)
         assert abs(rr.mean() - 1.0) < 0.02 and np.abs(rr - 1.0).max() < 0.35
+
+
+@pytest.mark.parametrize("adc,w_noise", [(True, 0.0), (True, 0.03), (False, 0.0)])
+def test_out_noise_std_on_the_tensor_core_path(adc, w_noise):
+    """out_noise_std with the tensor-core kernels forced on (their LINE variants read the tile's
+    table of per-line std-devs): the std-dev of every output line over repeats follows
+    sqrt(line^2 + (w_noise ||v||)^2), forward and backward, and equals what the CUDA-core kernels
+    give for the same tile."""
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import devices as D
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(41)
+    x_size, d_size, m = 128, 192, 256
+    p = H.training_params(noise=False, pulse_det=True, bm=False, adc=adc, out_bound=12.0 if adc else 0.0)
+    for io in (p.forward_io, p.backward_io):
+        io.out_noise, io.out_noise_std = 0.1, 0.4
+        io.w_noise = w_noise
+        io.w_noise_type = D.WeightNoiseType.AdditiveConstant if w_noise > 0 else D.WeightNoiseType.None_
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=21)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    W = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    X /= np.abs(X).max(axis=1, keepdims=True)
+    Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+    Dm /= np.abs(Dm).max(axis=1, keepdims=True)
+    xg, dg = torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda()
+    res = np.float32(2.0 / 126.0)
+    vx = np.clip(np.rint(X / res) * res, -1, 1).astype(np.float64)
+    vd = np.clip(np.rint(Dm / res) * res, -1, 1).astype(np.float64)
+    lib = _cabi.lib()
+    reps = 40
+    lines = {}
+    try:
+        for mode in (2, 1):  # tensor cores wherever possible, then CUDA cores only
+            assert lib.ab200_set_mvm_path(mode) == 0
+            for backward, inp, v, n in ((False, xg, vx, d_size), (True, dg, vd, x_size)):
+                fn = (lambda: t.backward(inp).cpu().numpy()) if backward else (lambda: t.forward(inp).cpu().numpy())
+                ys = _repeat(fn, reps)
+                table = t.get_io_vector(backward, 2).numpy().astype(np.float64)  # out-noise values
+                assert table.shape == (n,)
+                want = np.sqrt(table[None, :] ** 2 + (w_noise ** 2) * (v ** 2).sum(axis=1, keepdims=True))
+                if adc:  # the ADC step adds its rounding noise
+                    want = np.sqrt(want ** 2 + (2 * 12.0 / 510.0) ** 2 / 12.0)
+                dev = ys - ys.mean(axis=0, keepdims=True)
+                est = np.sqrt((dev ** 2).sum(axis=0) / (reps - 1.0))
+                ratio = (est / want).mean(axis=0)  # per line, averaged over the rows
+                # (a line far below the ADC step does not dither it: no closed form there)
+                ok = table > (0.05 if adc else 0.0)
+                assert ok.mean() > 0.8
+                assert np.abs(ratio[ok] - 1.0).max() < 0.06, (mode, backward, np.abs(ratio[ok] - 1.0).max())
+                lines[(mode, backward)] = est.mean(axis=0)
+    finally:
+        lib.ab200_set_mvm_path(0)
+    for backward in (False, True):
+        assert np.corrcoef(lines[(2, backward)], lines[(1, backward)])[0, 1] > 0.99
