@@ -169,7 +169,7 @@ void Tile::setMatrixIndices(const int32_t *indices, long long n, cudaStream_t s)
       }
     }
   }
-  AB200_CUDA(cudaStreamSynchronize(s));
+  AB200_CUDA(cudaDeviceSynchronize()); // an earlier backward pass may still read the old arrays
   cudaFree(csr_off_);
   cudaFree(csr_pos_);
   csr_off_ = csr_pos_ = nullptr;
@@ -250,8 +250,9 @@ bool Tile::updateGatherEligible() const {
     return e && e[0] == '0';
   }();
   // the pulse-preparation kernel is the only reader of x on the pulsed path
+  // (the mixed-precision compound quantises and accumulates x digitally: it takes the matrix)
   return !off && cfg_.device_kind != AB200_DEVICE_IDEAL && up_.pulse_type != AB200_PULSE_NONE &&
-         up_.pulse_type != AB200_PULSE_NONE_WITH_DEVICE && delta_w_ == nullptr;
+         up_.pulse_type != AB200_PULSE_NONE_WITH_DEVICE && delta_w_ == nullptr && !cfg_.mixed.enabled;
 }
 
 void Tile::gatherIndexed(const float *x, long long in_mat, int m_batch, int n_img, bool trans,
