@@ -1,0 +1,152 @@
+"""Seeded sweep over random tile configurations, noise off, against the compiled reference tile.
+
+Every case draws its own shape (ragged sizes, single rows and columns included), memory layouts
+(transposed inputs / outputs, bias column), noise and bound management types, DAC / ADC
+resolutions, MV type, device kind and pulse type, then checks forward, backward and a few pulsed
+updates on the GPU tile against the reference's CPU tile built from the same configuration:
+outputs within one ADC step (the reference's own GPU-vs-CPU criterion is a relative tolerance on
+unit-scale data, src/rpucuda/cuda/rpucuda_pulsed_test.cpp:437-480), weights to 1e-6. Each case runs
+on the automatic kernel selection and with the tensor-core kernels forced on wherever they apply."""
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+N_CASES = 48
+
+
+def _draw_case(seed):
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(1000 + seed)
+    pick = lambda seq: seq[int(rng.integers(len(seq)))]  # noqa: E731
+    c = dict(seed=seed)
+    c["x_size"] = int(pick([1, 2, 7, 31, 64, 100, 129, 256, 333, 515]))
+    c["d_size"] = int(pick([1, 3, 8, 33, 64, 127, 200, 256]))
+    c["m"] = int(pick([1, 2, 5, 17, 64, 130, 257]))
+    c["bias"] = bool(rng.integers(2)) and c["x_size"] > 1
+    c["x_trans"], c["d_trans"] = bool(rng.integers(2)), bool(rng.integers(2))
+    c["nm"] = pick([D.NoiseManagementType.None_, D.NoiseManagementType.AbsMax, D.NoiseManagementType.Max,
+                    D.NoiseManagementType.Constant, D.NoiseManagementType.AbsMaxNPSum])
+    c["bm"] = pick([D.BoundManagementType.None_, D.BoundManagementType.Iterative,
+                    D.BoundManagementType.IterativeWorstCase])
+    c["inp_res"] = float(pick([1 / 126.0, 1 / 254.0, 1 / 30.0]))
+    c["out_res"] = float(pick([1 / 510.0, 1 / 254.0, 1 / 62.0]))
+    c["out_bound"] = float(pick([12.0, 3.0, 1.0]))
+    c["mv"] = pick([D.AnalogMVType.OnePass, D.AnalogMVType.OnePass, D.AnalogMVType.PosNegSeparate,
+                    D.AnalogMVType.PosNegSeparateDigitalSum])
+    c["asym"] = float(pick([0.0, 0.0, 0.05]))
+    c["kind"] = pick(["cs", "ls", "sb", "sbr", "es", "ps", "pw"])
+    c["pulse"] = pick([D.PulseType.DeterministicImplicit, D.PulseType.MeanCount, D.PulseType.NoneWithDevice])
+    c["bl"] = int(pick([31, 10, 63]))
+    c["um"], c["ublm"] = bool(rng.integers(2)), bool(rng.integers(2))
+    c["lr"] = float(pick([0.01, 0.1]))
+    return c, rng
+
+
+def _row_step(ref_rows, floor):
+    """One ADC step per row, read off the reference's own outputs: the values of a row lie on
+    the grid step * k, so the smallest gap between two of them is a (small) multiple of the step.
+    Rows with a single distinct value fall back to `floor` or the value itself."""
+    out = np.empty((ref_rows.shape[0], 1))
+    for r, row in enumerate(ref_rows.astype(np.float64)):
+        u = np.unique(row)
+        gaps = np.diff(u)
+        gaps = gaps[gaps > 1e-7 * max(np.abs(u).max(), 1e-30)]
+        out[r, 0] = gaps.min() if gaps.size else max(np.abs(u).max(), float(floor[r, 0]))
+    return np.maximum(out, floor)
+
+
+def _build(c):
+    from aihwkit_b200.rpu_base import devices as D
+
+    p = D.AnalogTileParameter()
+    for io in (p.forward_io, p.backward_io):
+        io.inp_res, io.out_res = c["inp_res"], c["out_res"]
+        io.out_noise = 0.0
+        io.out_bound, io.inp_bound = c["out_bound"], 1.0
+        io.noise_management = c["nm"]
+        io.nm_thres = 1.5 if c["nm"] == D.NoiseManagementType.Constant else 0.0
+        io.mv_type = c["mv"]
+        io.inp_asymmetry = io.out_asymmetry = c["asym"]
+    p.forward_io.bound_management = c["bm"]
+    p.update.pulse_type = c["pulse"]
+    p.update.desired_bl = c["bl"]
+    p.update.update_management, p.update.update_bl_management = c["um"], c["ublm"]
+    dp = H.piecewise_device(False) if c["kind"] == "pw" else H.device(c["kind"], False)
+    return p._config(c["x_size"], c["d_size"], dp, seed=5)
+
+
+@pytest.mark.parametrize("seed", range(N_CASES))
+def test_random_configuration_against_reference(seed):
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    if not ref.available():
+        pytest.skip("compiled reference not built")
+    c, rng = _draw_case(seed)
+    cfg = _build(c)
+    x_size, d_size, m, bias = c["x_size"], c["d_size"], c["m"], c["bias"]
+    x_in = x_size - (1 if bias else 0)
+    rt = ref.RefTile(cfg)
+    W = rng.uniform(-0.4, 0.4, (d_size, x_size)).astype(np.float32)
+    rt.set_weights(W)
+    W = rt.get_weights()
+    # inputs with a wide spread of row maxima; one all-zero row
+    X = (rng.uniform(-1, 1, (m, x_in)) * rng.uniform(0.05, 2.0, (m, 1))).astype(np.float32)
+    Dm = (rng.normal(0, 0.3, (m, d_size)) * rng.uniform(0.05, 2.0, (m, 1))).astype(np.float32)
+    if m > 2:
+        X[1] = 0.0
+        Dm[2] = 0.0
+    Xa = np.ascontiguousarray(X.T) if c["x_trans"] else X
+    Da = np.ascontiguousarray(Dm.T) if c["d_trans"] else Dm
+    yr = rt.forward(Xa, bias=bias, x_trans=c["x_trans"], d_trans=c["d_trans"])
+    gr = rt.backward(Da, bias=bias, d_trans=c["d_trans"], x_trans=c["x_trans"])
+    steps = 2.002 if c["mv"].name.endswith("DigitalSum") else 1.001
+    lib = _cabi.lib()
+    try:
+        for mode in (0, 2):
+            assert lib.ab200_set_mvm_path(mode) == 0
+            t = T.AnalogTile(cfg, cuda_device=0)
+            t.set_weights(torch.from_numpy(W))
+            assert np.array_equal(t.get_weights().numpy(), W)
+            y = t.forward(torch.from_numpy(Xa).cuda(), bias, c["x_trans"], c["d_trans"]).cpu().numpy()
+            assert y.shape == yr.shape
+            # one ADC step of the row (at the scale of its last bound-management round); the
+            # largest output magnitude bounds that scale from below
+            ym = (yr.T if c["d_trans"] else yr)
+            yg = (y.T if c["d_trans"] else y)
+            floor = np.maximum(np.abs(ym).max(axis=1, keepdims=True) / c["out_bound"], 1e-30) * \
+                (2.0 * c["out_bound"] * c["out_res"])
+            frac, worst = H.lsb_report(yg, ym, _row_step(ym, floor))
+            assert worst <= steps and frac <= 0.02, ("forward", mode, c, frac, worst)
+            g = t.backward(torch.from_numpy(Da).cuda(), bias, c["d_trans"], c["x_trans"]).cpu().numpy()
+            assert g.shape == gr.shape
+            gm = (gr.T if c["x_trans"] else gr)
+            gg = (g.T if c["x_trans"] else g)
+            floor_b = np.maximum(np.abs(gm).max(axis=1, keepdims=True) / c["out_bound"], 1e-30) * \
+                (2.0 * c["out_bound"] * c["out_res"])
+            frac, worst = H.lsb_report(gg, gm, _row_step(gm, floor_b))
+            assert worst <= steps and frac <= 0.02, ("backward", mode, c, frac, worst)
+    finally:
+        lib.ab200_set_mvm_path(0)
+    # pulsed updates, weights after each call
+    t = T.AnalogTile(cfg, cuda_device=0)
+    t.set_weights(torch.from_numpy(W))
+    t.set_learning_rate(c["lr"])
+    rt.set_learning_rate(c["lr"])
+    for k in range(3):
+        Xu = (rng.uniform(-1, 1, (m, x_in))).astype(np.float32)
+        Du = (rng.normal(0, 0.5, (m, d_size))).astype(np.float32)
+        Xua = np.ascontiguousarray(Xu.T) if c["x_trans"] else Xu
+        Dua = np.ascontiguousarray(Du.T) if c["d_trans"] else Du
+        t.update(torch.from_numpy(Xua).cuda(), torch.from_numpy(Dua).cuda(), bias, c["x_trans"], c["d_trans"])
+        rt.update(Xua, Dua, bias=bias, x_trans=c["x_trans"], d_trans=c["d_trans"])
+        diff = np.abs(t.get_weights().numpy() - rt.get_weights()).max()
+        tol = 2e-6 if c["pulse"].name == "NoneWithDevice" else 1e-6
+        assert diff <= tol, ("update", k, c, diff)
