@@ -150,3 +150,84 @@ def test_random_configuration_against_reference(seed):
         diff = np.abs(t.get_weights().numpy() - rt.get_weights()).max()
         tol = 2e-6 if c["pulse"].name == "NoneWithDevice" else 1e-6
         assert diff <= tol, ("update", k, c, diff)
+
+
+N_COMPOUND_CASES = 40
+
+
+def _draw_compound(seed):
+    rng = np.random.default_rng(5000 + seed)
+    pick = lambda seq: seq[int(rng.integers(len(seq)))]  # noqa: E731
+    fam = pick(["transfer", "buffered", "chopped", "dynamic", "mixed"])
+    x_size, d_size, m = int(pick([3, 8, 13, 40])), int(pick([2, 9, 16, 33])), int(pick([1, 4, 7, 20]))
+    if fam == "transfer":
+        dp = H.transfer_device(False, transfer_every=float(pick([1.0, 2.0, 3.0])),
+                               units_in_mbatch=bool(rng.integers(2)), n_reads=int(pick([1, 2, 3])),
+                               transfer_lr=float(pick([0.01, 0.1, 1.0])), det=True)
+        dp.transfer_forward.out_noise = 0.0
+    elif fam == "buffered":
+        dp = H.buffered_transfer_device(transfer_every=float(pick([1.0, 2.0, 5.0])), n_reads=int(pick([1, 2, 3])),
+                                        thres_scale=float(pick([0.5, 1.0, 2.0])),
+                                        momentum=float(pick([0.0, 0.3])), forget_buffer=bool(rng.integers(2)),
+                                        transfer_lr=float(pick([0.5, 1.0, 4.0])))
+    elif fam == "chopped":
+        dp = H.chopped_transfer_device(transfer_every=float(pick([1.0, 2.0, 3.0])),
+                                       in_chop_prob=float(pick([0.0, 0.25, 0.5, 1.0])), in_chop_random=False,
+                                       momentum=float(pick([0.0, 0.3])), forget_buffer=bool(rng.integers(2)),
+                                       transfer_lr=float(pick([1.0, 4.0])),
+                                       buffer_granularity=float(pick([0.5, 1.0, 2.0])),
+                                       correct_gradient_magnitudes=bool(rng.integers(2)),
+                                       auto_granularity=float(pick([0.0, 0.0, 20.0])))
+        if float(dp.in_chop_prob) == 1.0:
+            dp.in_chop_random = True  # probability one: every transfer flips, no draw decides anything
+    elif fam == "dynamic":
+        dp = H.dynamic_transfer_device(in_chop_prob=float(pick([0.2, 0.34, 0.5])),
+                                       tail_weightening=float(pick([1.0, 2.5, 5.0])),
+                                       buffer_cap=float(pick([0.0, 0.5, 10.0])),
+                                       correct_accumulation=bool(rng.integers(2)),
+                                       transfer_every=float(pick([1.0, 2.0])),
+                                       momentum=float(pick([0.0, 0.2])), forget_buffer=bool(rng.integers(2)),
+                                       transfer_lr=float(pick([1.0, 4.0])),
+                                       buffer_granularity=float(pick([0.5, 1.0])))
+    else:
+        bins = pick([(9, 5), (5, 3), (21, 11)])
+        dp = H.mixed_precision_device(kind=pick(["sb", "cs", "sbr"]), n_x_bins=bins[0], n_d_bins=bins[1],
+                                      transfer_every=int(pick([1, 2])),
+                                      n_rows_per_transfer=int(pick([-1, 1, 3, d_size])),
+                                      granularity=float(pick([0.0, 0.004])), transfer_lr=float(pick([0.5, 1.0])))
+    return fam, dp, x_size, d_size, m, float(pick([0.05, 0.1, 0.3])), rng
+
+
+@pytest.mark.parametrize("seed", range(N_COMPOUND_CASES))
+def test_random_compound_against_reference(seed):
+    """Random parameters of the Tiki-Taka family (plain, buffered, chopped, dynamic) and of the
+    mixed-precision compound, deterministic pulses and chopper schedules, noise off: visible
+    weights and every hidden plane (fast tile, buffers, means, chi) follow the compiled reference
+    through ten update calls."""
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    if not ref.available():
+        pytest.skip("compiled reference not built")
+    fam, dp, x_size, d_size, m, lr, rng = _draw_compound(seed)
+    p = H.training_params(noise=False, pulse_det=True)
+    cfg = p._config(x_size, d_size, dp, seed=3)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    rt = ref.RefTile(cfg)
+    names = t.get_hidden_parameter_names()
+    assert names == rt.hidden_parameter_names()
+    assert np.array_equal(t.get_hidden_parameters().numpy(), rt.get_hidden_parameters())
+    state = [k for k, n in enumerate(names)
+             if n.startswith(("hidden_weights", "buffered_FP", "running_mean", "past_mean"))]
+    t.set_learning_rate(lr)
+    rt.set_learning_rate(lr)
+    for step in range(10):
+        x = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        d = rng.normal(0, 0.5, (m, d_size)).astype(np.float32)
+        t.update(torch.from_numpy(x).cuda(), torch.from_numpy(d).cuda())
+        rt.update(x, d)
+        hp, hr = t.get_hidden_parameters().numpy(), rt.get_hidden_parameters()
+        for k in state:
+            tol = 1e-6 if names[k].startswith("hidden_weights") and not names[k].endswith("chi") else 1e-4
+            assert np.abs(hp[k] - hr[k]).max() <= tol, (fam, names[k], step, np.abs(hp[k] - hr[k]).max())
+        assert np.abs(t.get_weights().numpy() - rt.get_weights()).max() <= 1e-6, (fam, "weights", step)
