@@ -202,3 +202,83 @@ def test_conv_sized_for_tensor_cores():
     finally:
         torch.backends.cudnn.allow_tf32 = tf32
     assert torch.allclose(y2, conv, rtol=1e-4, atol=1e-4)
+
+
+N_GEOMETRIES = 24
+
+
+@pytest.mark.parametrize("seed", range(N_GEOMETRIES))
+def test_random_convolution_geometries(seed):
+    """Random convolution geometries (kernel, stride, padding, dilation, channels, map size, analog
+    bias, both index layouts) through the three indexed entry points, on the automatic kernel
+    selection and with the tensor-core kernels forced on (where the DAC kernel and the
+    bound-management re-run gather the rows and the MVM kernels store image-major outputs),
+    against the numpy restatement of the reference's copyIndexedInput / copyIndexedOutput."""
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import analog_tile_oracle as O
+
+    rng = np.random.default_rng(7000 + seed)
+    pick = lambda seq: seq[int(rng.integers(len(seq)))]  # noqa: E731
+    c, h, w = int(pick([1, 3, 6, 16])), int(pick([4, 7, 12])), int(pick([5, 8, 11]))
+    kernel = (int(pick([1, 2, 3])), int(pick([1, 2, 3])))
+    stride = (int(pick([1, 2])), int(pick([1, 2])))
+    padding = (int(pick([0, 1, 2])), int(pick([0, 1])))
+    dilation = (int(pick([1, 1, 2])), 1)
+    analog_bias, trans = bool(rng.integers(2)), bool(rng.integers(2))
+    n, c_out = int(pick([1, 2, 5])), int(pick([1, 9, 40]))
+    if h + 2 * padding[0] < dilation[0] * (kernel[0] - 1) + 1 or w + 2 * padding[1] < kernel[1]:
+        pytest.skip("kernel larger than the padded map")
+    idx_t = O.conv_indices((c, h, w), kernel, stride, padding, dilation, analog_bias)
+    x_size = c * kernel[0] * kernel[1] + (1 if analog_bias else 0)
+    m_batch = idx_t.size // x_size
+    idx = idx_t if trans else np.ascontiguousarray(idx_t.reshape(x_size, m_batch).T).reshape(-1)
+    p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=float(pick([12.0, 2.0])))
+    dp = H.device("cs", False)
+    cfg = p._config(x_size, c_out, dp, seed=5)
+    fio, bio = O.IO.from_c(cfg.forward_io), O.IO.from_c(cfg.backward_io, backward=True)
+    X = rng.uniform(-1, 1, (n, c, h, w)).astype(np.float32)
+    d_shape = (n, c_out, m_batch) if trans else (n, m_batch, c_out)
+    Dm = rng.normal(0, 0.1, d_shape).astype(np.float32)
+    cols = O.indexed_input(X, idx, x_size, m_batch, n, trans)
+    d_cols = O.to_sample_major(Dm, c_out, m_batch, n, trans)
+    lib = _cabi.lib()
+    try:
+        for mode in (0, 2):
+            assert lib.ab200_set_mvm_path(mode) == 0
+            t = T.AnalogTile(cfg, cuda_device=0)
+            w0 = rng.uniform(-0.5, 0.5, (c_out, x_size)).astype(np.float32)
+            t.set_weights(torch.from_numpy(w0))
+            w0 = t.get_weights().numpy()
+            idx32 = np.ascontiguousarray(idx, np.int32)  # host array this time; kept alive over the call
+            _cabi.check(lib.ab200_tile_set_matrix_indices(t._h, idx32.ctypes.data, idx32.size, None))
+            xd, dd = _gpu(X), _gpu(Dm)
+            y_ref, _, scale, _ = O.forward(w0, cols, fio, return_pre_adc=True)
+            y = torch.full(d_shape, 5.0, device="cuda")
+            _cabi.check(lib.ab200_tile_forward_indexed(t._h, xd.data_ptr(), y.data_ptr(), X.size, m_batch, n,
+                                                       int(trans), 0, None))
+            torch.cuda.synchronize()
+            got = O.to_sample_major(y.cpu().numpy(), c_out, m_batch, n, trans)
+            zero_rows = scale == 0  # rows without input: output 0, no step to compare in
+            lsb = np.where(zero_rows, 1.0, fio.res_out / np.where(zero_rows, 1.0, scale))[:, None]
+            _check_lsb(got, y_ref, lsb, frac_max=1e-2)
+            xg_ref = O.indexed_output(O.backward(w0, d_cols, bio), idx, x_size, m_batch, n, trans, X.size)
+            xg = torch.full(X.shape, 7.0, device="cuda")
+            _cabi.check(lib.ab200_tile_backward_indexed(t._h, dd.data_ptr(), xg.data_ptr(), X.size, m_batch, n,
+                                                        int(trans), None))
+            torch.cuda.synchronize()
+            step = float((bio.res_out * np.abs(d_cols).max(axis=1)).max())
+            diff = np.abs(xg.cpu().numpy().reshape(n, -1) - xg_ref)
+            assert diff.max() <= 1.001 * step and np.mean(diff > 1e-6) <= 1e-2, (mode, diff.max(), step)
+            t.set_learning_rate(0.01)
+            names = t.get_hidden_parameter_names()
+            dev = O.DeviceArrays.from_hidden(O.DEV_CONSTANT_STEP, names, t.get_hidden_parameters().numpy(),
+                                             0.0, True)
+            _cabi.check(lib.ab200_tile_update_indexed(t._h, xd.data_ptr(), dd.data_ptr(), X.size, m_batch, n,
+                                                      int(trans), None))
+            torch.cuda.synchronize()
+            w1 = w0.copy()
+            O.update(w1, cols, d_cols, 0.01, dp.dw_min, O.Up.from_c(cfg.update), dev)
+            assert np.abs(t.get_weights().numpy() - w1).max() <= 1e-6, mode
+    finally:
+        lib.ab200_set_mvm_path(0)
