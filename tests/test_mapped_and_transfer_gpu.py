@@ -692,3 +692,43 @@ def test_mixed_precision_unquantised_stochastic_pulses():
     # chi + what reached the device is the digital sum up to the stochastic pulse counts
     total = -(w - chi)
     assert abs(total.sum() / (n_upd * per_batch).sum() - 1.0) < 0.1
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_mapped_layers_forward(seed):
+    """Random layer shapes and tile sizes (ragged last tiles, single in- or out-splits), with and
+    without weight scaling and digital bias, on the CUDA-core kernels and both tensor-core
+    variants: one ADC step per in-split of the array oracle."""
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import devices as D, tiles as T
+
+    rng = np.random.default_rng(9000 + seed)
+    pick = lambda seq: seq[int(rng.integers(len(seq)))]  # noqa: E731
+    out_size, in_size = int(pick([10, 100, 257, 512, 700])), int(pick([30, 129, 512, 640, 1100]))
+    max_tile = int(pick([64, 100, 256, 512]))
+    m = int(pick([1, 9, 130, 300]))
+    omega = float(pick([0.0, 0.6]))
+    with_bias = bool(rng.integers(2))
+    mode = int(pick([1, 2, 3]))
+    p = H.inference_params(noise=False)
+    p.forward_io.inp_res = float(pick([1 / 254.0, 1 / 126.0]))
+    p.forward_io.out_res = float(pick([1 / 254.0, 1 / 510.0]))
+    cfg = p._config(1, 1, D.IdealResistiveDeviceParameter(), seed=3)
+    W = rng.normal(0, 0.5 / np.sqrt(in_size), (out_size, in_size)).astype(np.float32)
+    bias = rng.normal(0, 0.1, out_size).astype(np.float32) if with_bias else np.zeros(out_size, np.float32)
+    X = (rng.normal(0, 1, (m, in_size)) * rng.uniform(0.1, 3.0, (m, 1))).astype(np.float32)
+    lib = _cabi.lib()
+    assert lib.ab200_set_mvm_path(mode) == 0
+    try:
+        arr = T.TileArray(cfg, out_size, in_size, max_tile, max_tile, cuda_device=0)
+        arr.set_weights(torch.from_numpy(W), weight_scaling_omega=omega)
+        if with_bias:
+            arr.set_bias(torch.from_numpy(bias))
+        y = arr.forward(torch.from_numpy(X).cuda()).cpu().numpy()
+        y_or, lsb, scales = _scaled_array_oracle(W, X, bias, cfg, max_tile, omega)
+        n_in = scales.shape[0]
+        diff = np.abs(y - y_or)
+        assert (diff > 1e-3 * lsb).mean() <= 3e-3 * n_in, (mode, (diff > 1e-3 * lsb).mean())
+        assert (diff <= 1.001 * lsb * n_in + 1e-6).all(), (mode, (diff / lsb).max())
+    finally:
+        lib.ab200_set_mvm_path(0)
