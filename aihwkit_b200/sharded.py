@@ -136,9 +136,11 @@ class ShardedTileArray:
     ITEM_ROWS = 256  # work-item height of the kernel: ownership changes on item boundaries
     FLAG_BYTES = 256
 
-    def enable_scatter(self, m: int, codes: Optional[bool] = None, cyclic: bool = False) -> None:
+    def enable_scatter(self, m: int, codes: Optional[bool] = None, cyclic: bool = False,
+                       buffers: int = 2) -> None:
         """Prepare :meth:`forward_reduce_scatter` for batches of ``m`` rows: every rank allocates
-        two sets of ``world`` slots of ``rows x out_size`` floats (double buffering over steps)
+        ``buffers`` sets of ``world`` slots of ``rows x out_size`` floats (two: double buffering
+        over steps; four: steps pipelined two deep, see ``forward_reduce_scatter(pipelined=True)``)
         plus one arrival flag per sender, shares them with the other ranks of the node through
         CUDA IPC handles, and builds the pointer tables the kernel scatters through.
 
@@ -200,7 +202,7 @@ class ShardedTileArray:
         # that every rank raises (and none waits for a rank that gave up)
         handles, self._sc_mine, self._sc_peers, failure = [], [], [], None
         try:
-            for _ in range(2):
+            for _ in range(buffers):
                 ptr, h = C.c_void_p(), C.create_string_buffer(64)
                 _cabi.check(lib.ab200_peer_alloc(alloc_bytes, dev_index, C.byref(ptr), h))
                 self._sc_mine.append(ptr.value)
@@ -213,7 +215,7 @@ class ShardedTileArray:
         self._sc_tables, self._sc_fac_tables, self._sc_flag_table = [], [], None
         if failure is None:
             try:
-                for b in range(2):
+                for b in range(buffers):
                     ptrs, fptrs, flags = [], [], []
                     for q in range(self.world):
                         if q == self.rank:
@@ -251,6 +253,10 @@ class ShardedTileArray:
         self._sc_step = 0
         self._sc_epoch = 0
         self._sc_wait_ms = 2000.0
+        self._sc_nbuf = buffers
+        self._sc_side = None      # stream of the owner's sums when steps are pipelined
+        self._sc_sum_done = None  # events: sum of step j recorded in slot j % 4
+        self._sc_sum_seen = [-1] * 4  # step whose sum the event in each slot belongs to
         dist.barrier(group=self.group)
 
     def _owned_rows(self, r0: int, rows: int) -> Tuple[int, int]:
@@ -283,7 +289,7 @@ class ShardedTileArray:
                 f"(rank {self.rank}); a rank is missing or far behind")
 
     def _scatter_part(self, x_part: torch.Tensor, r0: int, b: int, out: torch.Tensor,
-                      events=None) -> Tuple[int, int]:
+                      events=None, sum_stream=None) -> Tuple[int, int]:
         """One launch of the scatter kernel on the rows ``[r0, r0 + rows)`` of the batch followed
         by this owner's sum of what all ranks sent for them (which first waits, on the GPU and
         bounded, for the senders' arrival flags).  Returns the owner's local row range.
@@ -317,7 +323,12 @@ class ShardedTileArray:
         if events is not None:
             events[1].record()
         lr0, n = self._owned_rows(r0, x_part.size(0))
-        stream = int(torch.cuda.current_stream(self.local.device).cuda_stream)
+        if sum_stream is not None:
+            # the owner's sum runs on its own stream, behind this step's scatter kernel
+            sum_stream.wait_stream(torch.cuda.current_stream(self.local.device))
+            stream = int(sum_stream.cuda_stream)
+        else:
+            stream = int(torch.cuda.current_stream(self.local.device).cuda_stream)
         base = self._sc_mine[b]
         if self._sc_codes:
             planes = (C.c_int * self.world)(*self._sc_planes)
@@ -336,7 +347,7 @@ class ShardedTileArray:
         return lr0, n
 
     def forward_reduce_scatter(self, x_local: torch.Tensor, out: Optional[torch.Tensor] = None,
-                               events=None) -> torch.Tensor:
+                               events=None, pipelined: bool = False) -> torch.Tensor:
         """Forward of the sharded layer with the sum over the ranks' in-splits done by direct
         stores: every rank's kernel writes its partial sums into its slot at the owner of each
         row block (peer memory over NVLink, tile by tile while it computes) and, once all its
@@ -345,16 +356,55 @@ class ShardedTileArray:
         its ``world`` slots.  No collective, no host synchronisation.  Returns this rank's rows
         ``[rows, out_size]`` of the summed output: rank ``q`` owns rows ``[q * rows, (q + 1) *
         rows)`` with ``rows = self.scatter_rows`` (or, with ``cyclic`` ownership, the 256-row
-        blocks ``q, q + world, ...`` of the batch, packed)."""
+        blocks ``q, q + world, ...`` of the batch, packed).
+
+        ``pipelined`` (needs ``enable_scatter(..., buffers=4)``): consecutive calls overlap - the
+        owner's sum of step ``j`` runs on a side stream while the kernels of step ``j + 1`` run
+        on the caller's.  Step ``j`` writes slot set ``j % 4``; its kernel is held back (by an
+        event, on the host's stream order, no device-side wait) until this rank's sum of step
+        ``j - 2`` is done.  That sum has seen every rank's arrival flag of step ``j - 2``, and
+        every rank launched that step after its own sum of step ``j - 4``: so all owners have
+        finished reading slot set ``j % 4`` before anyone writes it again.  The result is
+        complete when :meth:`scatter_flush` (or a device synchronisation) returns."""
         self._check_wait_status()
-        b = self._sc_step & 1
+        dev = self.local.device
+        j = self._sc_step
+        b = j % self._sc_nbuf
         self._sc_step += 1
         if out is None:
-            out = torch.empty(self._sc_rows, self.out_size, device=self.local.device)
-        _, n = self._scatter_part(x_local, 0, b, out, events)
+            out = torch.empty(self._sc_rows, self.out_size, device=dev)
+        main = torch.cuda.current_stream(dev)
+        if not pipelined:
+            if self._sc_side is not None:
+                main.wait_stream(self._sc_side)  # sums of earlier pipelined steps
+            _, n = self._scatter_part(x_local, 0, b, out, events)
+            if n < self._sc_rows:
+                out[n:].zero_()  # rows of the buffer beyond the batch
+            return out
+        if self._sc_nbuf < 4:
+            raise RuntimeError("pipelined steps need enable_scatter(..., buffers=4)")
+        if self._sc_side is None:
+            self._sc_side = torch.cuda.Stream(device=dev)
+            self._sc_sum_done = [torch.cuda.Event() for _ in range(4)]
+        if j >= 2 and self._sc_sum_seen[(j - 2) % 4] == j - 2:
+            main.wait_event(self._sc_sum_done[(j - 2) % 4])
+        else:
+            # step j - 2 was not a pipelined one (its sum ran on the caller's stream): wait for
+            # whatever the side stream still holds, which orders this step behind all earlier sums
+            main.wait_stream(self._sc_side)
+        out.record_stream(self._sc_side)
+        _, n = self._scatter_part(x_local, 0, b, out, events, sum_stream=self._sc_side)
         if n < self._sc_rows:
-            out[n:].zero_()  # rows of the buffer beyond the batch
+            with torch.cuda.stream(self._sc_side):
+                out[n:].zero_()
+        self._sc_sum_done[j % 4].record(self._sc_side)
+        self._sc_sum_seen[j % 4] = j
         return out
+
+    def scatter_flush(self) -> None:
+        """Make the caller's stream wait for the sums of all pipelined steps issued so far."""
+        if getattr(self, "_sc_side", None) is not None:
+            torch.cuda.current_stream(self.local.device).wait_stream(self._sc_side)
 
     def forward_reduce_scatter_host(self, x_local_host: torch.Tensor, out_rows_host: torch.Tensor,
                                     chunk_rows: int = 2048) -> torch.Tensor:
@@ -380,8 +430,9 @@ class ShardedTileArray:
             self._sh_ev = [[torch.cuda.Event(), torch.cuda.Event()] for _ in range(2)]
         s_h2d, s_d2h = self._sh_streams
         main = torch.cuda.current_stream(dev)
-        b = self._sc_step & 1
+        b = self._sc_step % self._sc_nbuf
         self._sc_step += 1
+        self.scatter_flush()
         s_h2d.wait_stream(main)
         for c, r0 in enumerate(range(0, m, chunk_rows)):
             rows = min(chunk_rows, m - r0)

@@ -311,7 +311,7 @@ def run_ours(args):
         # (peer stores over NVLink), the result stays sharded by rows
         try:
             arr.enable_scatter(m, codes={"auto": None, "on": True, "off": False}[args.scatter_codes],
-                               cyclic=True)
+                               cyclic=True, buffers=4 if args.step_pipeline else 2)
         except RuntimeError as exc:  # raised on every rank alike: fall back to the NCCL reduce
             if rank == 0:
                 print(f"bench: {exc}; using --collective reduce", file=sys.stderr)
@@ -320,7 +320,7 @@ def run_ours(args):
 
     def step():
         if scatter:
-            return arr.forward_reduce_scatter(x_local_dev)
+            return arr.forward_reduce_scatter(x_local_dev, pipelined=bool(args.step_pipeline))
         if world > 1 and args.reduce_chunks > 1:
             return arr.forward_overlapped(x, dst=0, n_chunks=args.reduce_chunks, is_test=True)
         y = arr.forward_partial(x, is_test=True, non_blocking=True)
@@ -363,6 +363,8 @@ def run_ours(args):
     ev0.record()
     for _ in range(args.steps):
         step()
+    if scatter:
+        arr.scatter_flush()  # the owner's sums of the last steps (side stream) belong to the region
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
@@ -381,6 +383,8 @@ def run_ours(args):
     s0.record()
     for _ in range(n_sus):
         step()
+    if scatter:
+        arr.scatter_flush()
     s1.record()
     barrier()
     sus_ms = s0.elapsed_time(s1)
@@ -496,7 +500,10 @@ def run_ours(args):
                                 if getattr(arr, "_sc_codes", False) else "fp32 partial sums")
                              + " stored by the kernel into the row-block owners' memory over NVLink, "
                              "arrival flags, owner's sum (reduce-scatter, no collective call; the "
-                             "256-row blocks are dealt to the ranks in turn and stay there)")
+                             "256-row blocks are dealt to the ranks in turn and stay there)"
+                             + ("; consecutive steps pipelined two deep: the owner's sum of step j runs "
+                                "on a side stream beside the kernels of step j + 1, four slot sets"
+                                if args.step_pipeline else ""))
                 if scatter else (f"in-splits over {world} rank(s), NCCL reduce to rank 0"
                                  if world > 1 else "one rank, all 64 tiles"),
                 "l2": "input (134 MB) and output (134 MB) per step exceed the 126 MB L2",
@@ -599,6 +606,10 @@ def main():
                     help="N > 1 with --collective scatter: send the signed-byte ADC codes of every "
                          "in-split instead of fp32 partial sums (auto: when a rank holds at most "
                          "three in-splits)")
+    ap.add_argument("--step-pipeline", type=int, default=0, choices=[0, 1],
+                    help="N > 1 with --collective scatter: 1 = overlap the owner's sum of a step with the "
+                         "kernels of the next one (side stream, four slot sets); measured slower than "
+                         "one stream (the sum's CTAs delay the persistent MVM kernel's), so off")
     ap.add_argument("--collective", default="scatter", choices=["scatter", "reduce"],
                     help="N > 1: 'scatter' = the MVM kernel stores its partial sums into the row-block "
                          "owners' memory (reduce-scatter fused with the compute); 'reduce' = local "

@@ -78,6 +78,26 @@ def _worker(rank, world, port, out_path):
                 ok = ok and np.allclose(y_host[lrow:lrow + n].numpy(),
                                         fulls[part][bi * blk:bi * blk + n].cpu().numpy(), rtol=tol, atol=tol)
             arr.disable_scatter()
+            # consecutive steps pipelined two deep over four slot sets: the sum of a step runs on
+            # a side stream beside the kernels of the next; every step has its own input and
+            # must give what NCCL gives for the same call number
+            arr.enable_scatter(m, codes=(trial == 2), cyclic=True, buffers=4)
+            arr.local.set_seed(99)
+            arr2.local.set_seed(99)
+            xs = [x_local * (0.5 + 0.25 * k) for k in range(7)]
+            outs = [arr.forward_reduce_scatter(xk, pipelined=True) for xk in xs]
+            outs.append(arr.forward_reduce_scatter(xs[0]))  # a plain step behind pipelined ones
+            outs.append(arr.forward_reduce_scatter(xs[1], pipelined=True))  # and a pipelined one again
+            arr.scatter_flush()
+            torch.cuda.synchronize()
+            for k, xk in enumerate(xs + [xs[0], xs[1]]):
+                fullk = arr2.reduce(arr2.local.forward_local(xk), dst=None)
+                for bi in range(rank, (m + blk - 1) // blk, world):
+                    n = min(blk, m - bi * blk)
+                    lrow = (bi // world) * blk
+                    ok = ok and np.allclose(outs[k][lrow:lrow + n].cpu().numpy(),
+                                            fullk[bi * blk:bi * blk + n].cpu().numpy(), rtol=tol, atol=tol)
+            arr.disable_scatter()
     with open(f"{out_path}.{rank}", "w") as f:
         f.write("ok" if ok else "mismatch")
     dist.barrier()
