@@ -681,6 +681,7 @@ struct CodeSlots {
 // row's factor; planes of a slot first (fused multiply-add chain from zero, as the MVM kernel sums
 // its in-splits), then the slots in order (as sumSlotsKernel adds them)
 __global__ void __launch_bounds__(256) codeSlotsKernel(CodeSlots p) {
+  ab200::pdlEnter(); // launched behind the scatter kernel of the same step: no launch gap between them
   if (p.n_flags > 0 && !waitFlags(p.flags, p.n_flags, p.epoch, p.max_cycles, p.status)) {
     return;
   }
@@ -747,7 +748,8 @@ int ab200_sum_code_slots(const unsigned char *code_slots_dev, long long code_slo
   p.out_size = out_size;
   p.out = out_dev;
   const long long n = (long long)rows_valid * (out_size >> 2);
-  codeSlotsKernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p);
+  AB200_CUDA(ab200::launchChained(codeSlotsKernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
+                                  (cudaStream_t)stream, p));
   AB200_LAUNCH_CHECK();
   AB200_CATCH
 }
@@ -808,6 +810,7 @@ __global__ void __launch_bounds__(256)
     sumSlotsWaitKernel(const float4 *slots, int n_slots, long long stride4, long long e0, long long e1,
                        float4 *out, const int *flags, int n_flags, int epoch, long long max_cycles,
                        int *status) {
+  ab200::pdlEnter();
   if (n_flags > 0 && !waitFlags(flags, n_flags, epoch, max_cycles, status)) {
     return;
   }
@@ -846,9 +849,10 @@ int ab200_sum_slots_wait(const float *slots_dev, int n_slots, long long slot_str
   AB200_CUDA(cudaGetDevice(&dev));
   int *status = waitStatusWord(dev);
   const long long e0 = (long long)row0 * out_size / 4, e1 = (long long)(row0 + rows) * out_size / 4;
-  sumSlotsWaitKernel<<<(unsigned)((e1 - e0 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-      (const float4 *)slots_dev, n_slots, slot_stride / 4, e0, e1, (float4 *)out_dev, flags_dev,
-      flags_dev ? n_flags : 0, epoch, waitCycles(max_wait_ms, dev), status);
+  AB200_CUDA(ab200::launchChained(sumSlotsWaitKernel, dim3((unsigned)((e1 - e0 + 255) / 256)), dim3(256), 0,
+                                  (cudaStream_t)stream, (const float4 *)slots_dev, n_slots, slot_stride / 4,
+                                  e0, e1, (float4 *)out_dev, flags_dev, flags_dev ? n_flags : 0, epoch,
+                                  waitCycles(max_wait_ms, dev), status));
   AB200_LAUNCH_CHECK();
   AB200_CATCH
 }
