@@ -3,6 +3,7 @@
     make -C oracle && python tests/golden/make_golden.py            # everything
     make -C oracle && python tests/golden/make_golden.py indexed    # only indexed_conv.npz
     make -C oracle && python tests/golden/make_golden.py extensions # only extensions_det.npz
+    make -C oracle && python tests/golden/make_golden.py compounds  # only compounds_det.npz
 
 Every array is an input or an output of the unmodified reference CPU tile
 (RPU::RPUPulsed<float>) for the configurations built by tests/helpers.py; nothing here comes from
@@ -264,7 +265,71 @@ def extensions_case(seed):
     return out
 
 
+COMPOUND_CASES = {
+    # name -> (helper in tests/helpers.py, keyword arguments)
+    "chopped": ("chopped_transfer_device", dict(transfer_lr=4.0, in_chop_prob=0.3, in_chop_random=False,
+                                                momentum=0.3, forget_buffer=False, buffer_granularity=0.5)),
+    "dynamic": ("dynamic_transfer_device", dict(transfer_lr=4.0, in_chop_prob=0.5, tail_weightening=2.5,
+                                                momentum=0.2, forget_buffer=False, buffer_cap=0.5)),
+    "mixed": ("mixed_precision_device", dict(n_rows_per_transfer=3)),
+}
+
+
+def compounds_case(seed):
+    """The two-pass MV types (forward and backward outputs, alone and on top of the line
+    non-idealities) and the weight / hidden-plane trajectories of the chopped and dynamic transfer
+    compounds and of the mixed-precision compound over eight deterministic updates."""
+    from aihwkit_b200.rpu_base import devices as D
+
+    rng = np.random.default_rng(seed)
+    out = {}
+    x_size, d_size, m = 60, 36, 12
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+    out.update(pn_w0=W, pn_x=X, pn_d=Dm)
+    for mv in ("PosNegSeparate", "PosNegSeparateDigitalSum"):
+        for lines in (False, True):
+            p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+            for io in (p.forward_io, p.backward_io):
+                io.mv_type = getattr(D.AnalogMVType, mv)
+                if lines:
+                    for k, v in LINE_ALL.items():
+                        setattr(io, k, v)
+            t = ref.RefTile(p._config(x_size, d_size, H.device("cs", False), seed=seed))
+            t.set_weights(W)
+            key = f"pn_{mv}_{int(lines)}"
+            out[key + "_w"] = t.get_weights()
+            if lines:
+                for backward, n, tag in ((False, d_size, "f"), (True, x_size, "b")):
+                    out[f"{key}_voff_{tag}"] = t.get_io_vector(backward, 0, n)
+                    out[f"{key}_nl_{tag}"] = t.get_io_vector(backward, 1, n)
+            out[key + "_y"] = t.forward(X)
+            out[key + "_g"] = t.backward(Dm)
+    x_size, d_size, m = 12, 10, 5
+    xs = rng.uniform(-1, 1, (8, m, x_size)).astype(np.float32)
+    ds = rng.normal(0, 0.5, (8, m, d_size)).astype(np.float32)
+    out.update(cp_x=xs, cp_d=ds)
+    for name, (helper, kw) in COMPOUND_CASES.items():
+        p = H.training_params(noise=False, pulse_det=True)
+        t = ref.RefTile(p._config(x_size, d_size, getattr(H, helper)(**kw), seed=3))
+        t.set_learning_rate(0.1)
+        out[f"cp_{name}_hidden0"] = t.get_hidden_parameters()
+        ws, hs = [], []
+        for k in range(8):
+            t.update(xs[k], ds[k])
+            ws.append(t.get_weights())
+            hs.append(t.get_hidden_parameters())
+        out[f"cp_{name}_w"] = np.stack(ws)
+        out[f"cp_{name}_hidden"] = np.stack(hs)
+    return out
+
+
 def main():
+    if sys.argv[1:] == ["compounds"]:
+        np.savez_compressed(os.path.join(HERE, "compounds_det.npz"), **compounds_case(14))
+        print("wrote compounds_det.npz")
+        return
     if sys.argv[1:] == ["extensions"]:
         np.savez_compressed(os.path.join(HERE, "extensions_det.npz"), **extensions_case(12))
         print("wrote extensions_det.npz")
@@ -286,6 +351,7 @@ def main():
     np.savez_compressed(os.path.join(HERE, "transfer_det.npz"), **transfer_case(8))
     np.savez_compressed(os.path.join(HERE, "indexed_conv.npz"), **indexed_conv_case(9))
     np.savez_compressed(os.path.join(HERE, "extensions_det.npz"), **extensions_case(12))
+    np.savez_compressed(os.path.join(HERE, "compounds_det.npz"), **compounds_case(14))
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 

@@ -217,3 +217,58 @@ def test_extensions_against_reference_vectors():
     t.set_learning_rate(0.2)
     t.update(_gpu(g["nwd_x"]), _gpu(g["nwd_d"]))
     assert np.abs(t.get_weights().numpy() - g["nwd_w1"]).max() <= 2e-6
+
+
+def test_compounds_against_reference_vectors():
+    """The two-pass MV types and the chopped / dynamic transfer and mixed-precision compounds
+    against vectors recorded from the compiled reference (tests/golden/make_golden.py
+    compounds_case): outputs within one ADC step (two for the digital sum), weights and hidden
+    planes through eight updates."""
+    from aihwkit_b200.rpu_base import devices as D
+    from aihwkit_b200.rpu_base import tiles as T
+    from tests.golden.make_golden import COMPOUND_CASES, LINE_ALL
+
+    g = np.load(os.path.join(GOLD, "compounds_det.npz"))
+    d_size, x_size = g["pn_w0"].shape
+    for mv in ("PosNegSeparate", "PosNegSeparateDigitalSum"):
+        for lines in (False, True):
+            key = f"pn_{mv}_{int(lines)}"
+            p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
+            for io in (p.forward_io, p.backward_io):
+                io.mv_type = getattr(D.AnalogMVType, mv)
+                if lines:
+                    for k, v in LINE_ALL.items():
+                        setattr(io, k, v)
+            t = T.AnalogTile(p._config(x_size, d_size, H.device("cs", False), seed=1), cuda_device=0)
+            t.set_weights(torch.from_numpy(g[key + "_w"]))
+            if lines:
+                for backward, tag in ((False, "f"), (True, "b")):
+                    t.set_io_vector(backward, 0, torch.from_numpy(g[f"{key}_voff_{tag}"]))
+                    t.set_io_vector(backward, 1, torch.from_numpy(g[f"{key}_nl_{tag}"]))
+            steps = 2.002 if mv.endswith("DigitalSum") else 1.001
+            y = t.forward(_gpu(g["pn_x"])).cpu().numpy()
+            lsb = (2.0 * 2.0 / 510.0) * np.abs(g["pn_x"]).max(axis=1, keepdims=True) * t.last_bm_stats()[1]
+            frac, worst = H.lsb_report(y, g[key + "_y"], lsb)
+            assert frac <= 1e-2 and worst <= steps, (key, frac, worst)
+            gb = t.backward(_gpu(g["pn_d"])).cpu().numpy()
+            lsb_b = (2.0 * 12.0 / 510.0) * np.abs(g["pn_d"]).max(axis=1, keepdims=True)
+            frac, worst = H.lsb_report(gb, g[key + "_g"], lsb_b)
+            assert frac <= 1e-2 and worst <= steps, (key, "backward", frac, worst)
+
+    m, x_size = g["cp_x"].shape[1:]
+    d_size = g["cp_d"].shape[2]
+    for name, (helper, kw) in COMPOUND_CASES.items():
+        p = H.training_params(noise=False, pulse_det=True)
+        t = T.AnalogTile(p._config(x_size, d_size, getattr(H, helper)(**kw), seed=3), cuda_device=0)
+        assert np.array_equal(t.get_hidden_parameters().numpy(), g[f"cp_{name}_hidden0"]), name
+        names = t.get_hidden_parameter_names()
+        state = [k for k, n in enumerate(names)
+                 if n.startswith(("hidden_weights", "buffered_FP", "running_mean", "past_mean"))]
+        t.set_learning_rate(0.1)
+        for k in range(8):
+            t.update(_gpu(g["cp_x"][k]), _gpu(g["cp_d"][k]))
+            assert np.abs(t.get_weights().numpy() - g[f"cp_{name}_w"][k]).max() <= 1e-6, (name, k)
+            hp = t.get_hidden_parameters().numpy()
+            for q in state:
+                assert np.abs(hp[q] - g[f"cp_{name}_hidden"][k][q]).max() <= 1e-4, (name, names[q], k)
+        assert np.abs(g[f"cp_{name}_w"][-1]).max() > 0
