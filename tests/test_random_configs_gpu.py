@@ -231,3 +231,53 @@ def test_random_compound_against_reference(seed):
             tol = 1e-6 if names[k].startswith("hidden_weights") and not names[k].endswith("chi") else 1e-4
             assert np.abs(hp[k] - hr[k]).max() <= tol, (fam, names[k], step, np.abs(hp[k] - hr[k]).max())
         assert np.abs(t.get_weights().numpy() - rt.get_weights()).max() <= 1e-6, (fam, "weights", step)
+
+
+@pytest.mark.parametrize("seed", range(20))
+def test_random_stochastic_updates_agree_between_the_two_kernels(seed):
+    """Stochastic pulse trains at random ragged sizes, train lengths (one to four 31-slot
+    segments) and device kinds, also through a Tiki-Taka compound: the staged kernel and the
+    streaming kernel see the same trains and apply the same pulses in the same per-weight order,
+    so without device noise the weights (and the fast tile) agree bit for bit; and they move."""
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(11000 + seed)
+    pick = lambda seq: seq[int(rng.integers(len(seq)))]  # noqa: E731
+    x_size, d_size = int(pick([1, 5, 31, 33, 100, 257, 600])), int(pick([1, 7, 32, 65, 130, 300]))
+    m = int(pick([1, 3, 31, 32, 33, 100, 257]))
+    bl = int(pick([1, 7, 31, 40, 63, 100]))
+    compound = bool(rng.integers(4) == 0)
+    p = H.training_params(noise=True, pulse_det=False)
+    p.update.desired_bl = bl
+    p.update.update_management, p.update.update_bl_management = bool(rng.integers(2)), bool(rng.integers(2))
+    if compound:
+        dp = H.transfer_device(False, transfer_every=float(pick([1.0, 3.0])), units_in_mbatch=False,
+                               n_reads=int(pick([1, 2])), transfer_lr=0.1, det=True)
+        dp.transfer_forward.out_noise = 0.0
+    else:
+        dp = H.device(pick(["cs", "ls", "sb", "sbr", "es", "ps"]), False, dw_min=0.002, dw_min_dtod=0.3)
+    cfg = p._config(x_size, d_size, dp, seed=5)
+    W0 = rng.uniform(-0.3, 0.3, (d_size, x_size)).astype(np.float32)
+    X = (np.maximum(rng.standard_normal((m, x_size)), 0) if rng.integers(2)
+         else rng.uniform(-1, 1, (m, x_size))).astype(np.float32)
+    Dm = rng.normal(0, 0.2, (m, d_size)).astype(np.float32)
+    lib = _cabi.lib()
+    results = []
+    try:
+        for mode in (1, 2):
+            _cabi.check(lib.ab200_set_update_path(mode))
+            t = T.AnalogTile(cfg, cuda_device=0)
+            t.set_weights(torch.from_numpy(W0))
+            t.set_learning_rate(0.05)
+            for _ in range(3):
+                t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+            results.append((t.get_weights().numpy(), t.get_hidden_parameters().numpy()))
+    finally:
+        _cabi.check(lib.ab200_set_update_path(0))
+    assert np.array_equal(results[0][0], results[1][0])
+    assert np.array_equal(results[0][1], results[1][1])
+    if np.abs(X).max() > 0 and m * x_size * d_size > 64:
+        moved = np.abs(results[0][0] - np.clip(W0, -0.6, 0.6)).max() > 0 or \
+            (compound and np.abs(results[0][1]).max() > 0)
+        assert moved
