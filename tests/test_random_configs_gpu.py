@@ -281,3 +281,48 @@ def test_random_stochastic_updates_agree_between_the_two_kernels(seed):
         moved = np.abs(results[0][0] - np.clip(W0, -0.6, 0.6)).max() > 0 or \
             (compound and np.abs(results[0][1]).max() > 0)
         assert moved
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_noisy_forward_moments_against_reference(seed):
+    """Random combinations of the stochastic IO settings (output noise, additive or PCMRead weight
+    noise, input noise, stochastic DAC / ADC rounding, asymmetries, per-line output noise, MV
+    type): mean and std-dev per output element over 300 repeats against the same number of repeats
+    of the compiled reference (the reference's own criterion for noisy passes,
+    src/rpucuda/cuda/rpucuda_pulsed_test.cpp:364-435)."""
+    from aihwkit_b200.rpu_base import devices as D
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import ref
+
+    if not ref.available():
+        pytest.skip("compiled reference not built")
+    rng = np.random.default_rng(13000 + seed)
+    pick = lambda seq: seq[int(rng.integers(len(seq)))]  # noqa: E731
+    x_size, d_size, m = int(pick([20, 48, 100])), int(pick([12, 30, 64])), int(pick([4, 9]))
+    p = H.training_params(noise=False, pulse_det=True, bm=False, out_bound=12.0)
+    io = p.forward_io
+    io.out_noise = float(pick([0.02, 0.06, 0.2]))
+    io.w_noise = float(pick([0.0, 0.02, 0.05]))
+    io.w_noise_type = pick([D.WeightNoiseType.AdditiveConstant, D.WeightNoiseType.PCMRead])
+    io.inp_noise = float(pick([0.0, 0.0, 0.02]))
+    io.inp_sto_round, io.out_sto_round = bool(rng.integers(2)), bool(rng.integers(2))
+    io.inp_asymmetry, io.out_asymmetry = float(pick([0.0, 0.03])), float(pick([0.0, 0.03]))
+    io.mv_type = pick([D.AnalogMVType.OnePass, D.AnalogMVType.OnePass, D.AnalogMVType.PosNegSeparate,
+                       D.AnalogMVType.PosNegSeparateDigitalSum])
+    io.out_res = float(pick([1 / 510.0, -1.0]))
+    cfg = p._config(x_size, d_size, H.device("cs", False), seed=9)
+    t = T.AnalogTile(cfg, cuda_device=0)
+    rt = ref.RefTile(cfg)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    t.set_weights(torch.from_numpy(W))
+    W = t.get_weights().numpy()
+    rt.set_weights(W)
+    X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+    xg = torch.from_numpy(X).cuda()
+    reps = 300
+    ys = np.stack([t.forward(xg).cpu().numpy() for _ in range(reps)])
+    yr = np.stack([rt.forward(X) for _ in range(reps)])
+    H.assert_moments_agree(ys, yr, z_max=5.5, std_tol=0.06)
+    # element by element: std-dev within the sampling error of two estimates from `reps` draws
+    ratio = ys.std(axis=0) / np.maximum(yr.std(axis=0), 1e-12)
+    assert np.abs(ratio - 1.0).max() < 6.0 / np.sqrt(reps), np.abs(ratio - 1.0).max()
