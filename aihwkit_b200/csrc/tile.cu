@@ -1232,6 +1232,12 @@ void Tile::forward(const float *x, float *d, bool bias, int m, bool x_trans, boo
   p.in_size = x_size_;
   p.in_real = x_in;
   p.out = d;
+  // a transposed output [d_size][m] is the transposed store with one block of m rows, which the
+  // tensor-core kernels write too
+  if (d_trans && out_t_rows == 0) {
+    out_t_rows = m;
+    d_trans = false;
+  }
   p.out_ss = d_trans ? 1 : d_size_;
   p.out_fs = d_trans ? m : 1;
   p.out_size = d_size_;
@@ -1365,6 +1371,11 @@ void Tile::forwardStrided(const float *x, long long x_ss, float *y, long long y_
 void Tile::backward(const float *d, float *x, bool bias, int m, bool d_trans, bool x_trans,
                     cudaStream_t s) {
   const int x_out = x_size_ - (bias ? 1 : 0);
+  if (x_trans && !bias) {
+    // transposed output [x_size][m]: the transposed store with one block of m rows
+    backwardCore(d, d_trans ? 1 : d_size_, d_trans ? m : 1, x, x_size_, 1, x_out, m, false, 0, 1.0f, s, m);
+    return;
+  }
   backwardCore(d, d_trans ? 1 : d_size_, d_trans ? m : 1, x, x_trans ? 1 : x_out, x_trans ? m : 1,
                x_out, m, false, 0, 1.0f, s);
 }
