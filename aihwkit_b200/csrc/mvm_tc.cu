@@ -1234,9 +1234,9 @@ __global__ void __launch_bounds__(kGatherWarps * 32) dacQuantizeGatherKernel(Dac
   float *sh = g_sh + (threadIdx.x >> 5) * p.kpad;
   const IOEff &io = p.io;
   float amax = 0.0f;
-  // eight index loads, then eight image loads in flight per lane: the two dependent loads of an
-  // element are latency, not bandwidth
-  constexpr int kU = 8;
+  // sixteen index loads, then sixteen image loads in flight per lane: the two dependent loads of
+  // an element are latency, not bandwidth
+  constexpr int kU = 16;
   for (int k0 = lane; k0 < p.kpad; k0 += 32 * kU) {
     int j[kU];
 #pragma unroll
