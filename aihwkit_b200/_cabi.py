@@ -258,6 +258,7 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_default_update_params": (None, [C.POINTER(UpdateParams)]),
         "ab200_default_device_params": (None, [C.POINTER(DeviceParams), C.c_int32]),
         "ab200_default_transfer_params": (None, [C.POINTER(TransferParams)]),
+        "ab200_default_mixedprec_params": (None, [C.POINTER(MixedPrecParams)]),
         "ab200_tile_create": (_I, [cfgp, _I, C.POINTER(_VP)]),
         "ab200_tile_destroy": (_I, [_VP]),
         "ab200_tile_to_device": (_I, [_VP, _I]),

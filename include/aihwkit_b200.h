@@ -350,7 +350,8 @@ const char *ab200_last_error(void);
 /* Library version string. */
 const char *ab200_version(void);
 /* sizeof of the parameter structs as the library was compiled (0 io, 1 update, 2 device,
- * 3 transfer, 4 tile config): lets a foreign-language binding check its own layout. */
+ * 3 transfer, 4 tile config, 5 scatter plan, 6 mixed precision): lets a foreign-language binding
+ * check its own layout. */
 size_t ab200_sizeof(int which);
 
 /* Fill the structs with the reference's defaults (IOMetaParameter / PulsedUpdateMetaParameter /

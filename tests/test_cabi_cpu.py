@@ -30,7 +30,8 @@ def test_struct_sizes_match_header():
     # the ctypes mirrors have the layout the library was compiled with
     lib = _cabi.lib()
     for which, cls in enumerate((_cabi.IOParams, _cabi.UpdateParams, _cabi.DeviceParams,
-                                 _cabi.TransferParams, _cabi.TileConfig, _cabi.ScatterPlan)):
+                                 _cabi.TransferParams, _cabi.TileConfig, _cabi.ScatterPlan,
+                                 _cabi.MixedPrecParams)):
         assert C.sizeof(cls) == lib.ab200_sizeof(which), cls.__name__
     assert C.sizeof(_cabi.IOParams) == 32 * 4
     assert C.sizeof(_cabi.TileConfig) % 8 == 0
@@ -75,6 +76,26 @@ def test_defaults_follow_reference_member_initialisers():
                     assert getattr(dp.drift, f) == pytest.approx(getattr(refd.drift, f)), (kind, f)
                 continue
             assert getattr(dp, name) == pytest.approx(getattr(refd, name)), (kind, name)
+    # compounds: the library's defaults equal what the Python mirrors send for a fresh object
+    tp = _cabi.TransferParams()
+    lib.ab200_default_transfer_params(C.byref(tp))
+    dyn = D.DynamicTransferResistiveDeviceParameter()
+    for _ in range(2):
+        dyn.append_parameter(D.ConstantStepResistiveDeviceParameter())
+    ref_t = dyn._to_c()
+    for name in ("tail_weightening", "buffer_cap", "buffer_granularity", "thres_scale", "step", "forget_buffer"):
+        assert getattr(tp, name) == pytest.approx(getattr(ref_t, name)), name
+    assert tp.dynamic == 0 and tp.chopped == 0 and ref_t.dynamic == 1 and ref_t.chopped == 1
+    mp = _cabi.MixedPrecParams()
+    lib.ab200_default_mixedprec_params(C.byref(mp))
+    mixed = D.MixedPrecResistiveDeviceParameter()
+    assert mixed.set_device_parameter(D.ConstantStepResistiveDeviceParameter())
+    assert not mixed.set_device_parameter(D.IdealResistiveDeviceParameter())
+    ref_m = mixed._to_c_mixed()
+    for name, _ in _cabi.MixedPrecParams._fields_:
+        if name != "enabled":
+            assert getattr(mp, name) == pytest.approx(getattr(ref_m, name)), name
+    assert mp.enabled == 0 and ref_m.enabled == 1
 
 
 @pytest.mark.parametrize("kind", ["cs", "ls", "sb", "sbr"])
@@ -147,6 +168,29 @@ def test_unsupported_settings_raise():
         T.AnalogTile(D.AnalogTileParameter()._config(4, 4, dp))
     with pytest.raises(RuntimeError):
         T.AnalogTile(D.AnalogTileParameter()._config(0, 4, D.ConstantStepResistiveDeviceParameter()))
+    # compounds: what the library refuses, it refuses when the tile is made (no device needed)
+    mixed = D.MixedPrecResistiveDeviceParameter()
+    with pytest.raises(RuntimeError, match="not implemented"):
+        D.AnalogTileParameter()._config(4, 4, mixed)  # no analog device set
+    assert mixed.set_device_parameter(D.ConstantStepResistiveDeviceParameter())
+    mixed.n_x_bins = 5
+    with pytest.raises(RuntimeError, match="only one of x and d"):
+        D.AnalogTileParameter()._config(4, 4, mixed)
+    dyn = H.dynamic_transfer_device(in_chop_prob=0.0)
+    with pytest.raises(RuntimeError, match="needs to be positive"):
+        D.AnalogTileParameter()._config(4, 4, dyn)
+    chop = H.chopped_transfer_device()
+    chop.n_reads_per_transfer = 2
+    with pytest.raises(RuntimeError, match="n_reads_per_transfer==1"):
+        D.AnalogTileParameter()._config(4, 4, chop)
+    cfg = D.AnalogTileParameter()._config(4, 4, H.chopped_transfer_device())
+    cfg.transfer.dynamic, cfg.transfer.chopped = 1, 0  # a raw struct that skips the Python checks
+    with pytest.raises(RuntimeError, match="chopped = 1"):
+        T.AnalogTile(cfg)
+    cfg = D.AnalogTileParameter()._config(4, 4, D.ConstantStepResistiveDeviceParameter())
+    cfg.forward_io.mv_type = 7
+    with pytest.raises(RuntimeError, match="AnalogMVType not implemented"):
+        T.AnalogTile(cfg)
 
 
 def test_learning_rate_and_sizes():
