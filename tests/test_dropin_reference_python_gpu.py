@@ -244,3 +244,52 @@ def test_tiki_taka_tile_through_reference_wrappers(aihwkit):
     diff = (model2.get_weights()[0].cpu() - model.get_weights()[0].cpu()).abs()
     # (a handful of the 2048 elements, depending on the noise of the training steps above)
     assert int((diff > 1e-6).sum()) <= 0.01 * diff.numel() and float(diff.max()) <= 0.3
+
+
+@pytest.mark.parametrize("which", ["chopped", "dynamic", "mixed"])
+def test_later_compounds_through_reference_wrappers(aihwkit, which):
+    """ChoppedTransferCompound (Tiki-Taka v3), DynamicTransferCompound (v4) and
+    MixedPrecisionCompound of the reference's own configuration classes: `as_bindings` fills this
+    module's parameter classes by the binding's attribute names, the tile trains with AnalogSGD,
+    and its extra hidden planes carry the reference's names."""
+    from aihwkit.nn import AnalogLinear
+    from aihwkit.optim import AnalogSGD
+    from aihwkit.simulator.configs import DigitalRankUpdateRPUConfig, UnitCellRPUConfig
+    from aihwkit.simulator.configs.compounds import (ChoppedTransferCompound, DynamicTransferCompound,
+                                                     MixedPrecisionCompound)
+    from aihwkit.simulator.configs.devices import SoftBoundsReferenceDevice
+
+    torch.manual_seed(5)
+    unit = lambda: SoftBoundsReferenceDevice(dw_min=0.002, w_max=1.0, w_min=-1.0)  # noqa: E731
+    if which == "chopped":
+        cfg = UnitCellRPUConfig(device=ChoppedTransferCompound(
+            unit_cell_devices=[unit(), unit()], in_chop_prob=0.1, transfer_every=1.0, units_in_mbatch=False))
+        planes = ["buffered_FP_weight_0"]
+    elif which == "dynamic":
+        cfg = UnitCellRPUConfig(device=DynamicTransferCompound(
+            unit_cell_devices=[unit(), unit()], in_chop_prob=0.5, transfer_every=1.0, units_in_mbatch=False))
+        planes = ["buffered_FP_weight", "running_mean_weight", "past_mean_weight"]
+    else:
+        cfg = DigitalRankUpdateRPUConfig(device=MixedPrecisionCompound(device=unit(), n_x_bins=9, n_d_bins=5))
+        planes = ["hidden_weights_chi"]
+    cfg.mapping.weight_scaling_omega = 0.0
+    cfg.mapping.learn_out_scaling = False
+    model = AnalogLinear(24, 16, bias=False, rpu_config=cfg).cuda()
+    tm = next(model.analog_tiles())
+    hidden = tm.get_hidden_parameters()
+    for name in planes:
+        assert name in hidden, (name, list(hidden))
+    w0 = model.get_weights()[0].clone()
+    opt = AnalogSGD(model.parameters(), lr=0.2)
+    opt.regroup_param_groups(model)
+    x = torch.rand(8, 24, device="cuda")
+    for _ in range(12):
+        opt.zero_grad()
+        model(x).square().mean().backward()
+        opt.step()
+    hidden = tm.get_hidden_parameters()
+    # (with the default forgetting buffer and a transfer scale of 1 / granularity every read
+    # empties its buffer element again: the chopped case is judged by its fast tile)
+    moved = [n for n in planes + ["hidden_weights_0"] if n in hidden and float(hidden[n].abs().max()) > 0]
+    assert moved, list(hidden)
+    assert float((model.get_weights()[0] - w0).abs().max()) > 0
