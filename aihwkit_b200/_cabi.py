@@ -108,6 +108,7 @@ class DeviceParams(C.Structure):
         ("enforce_consistency", C.c_int32),
         ("dw_min_dtod_log_normal", C.c_int32),
         ("perfect_bias", C.c_int32),
+        ("count_pulses", C.c_int32),
         ("dw_min", C.c_float),
         ("dw_min_dtod", C.c_float),
         ("dw_min_std", C.c_float),
@@ -303,6 +304,8 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_reset_columns": (_I, [_VP, _I, _I, C.c_float, _VP]),
         "ab200_tile_set_weights_uniform_random": (_I, [_VP, C.c_float, C.c_float, _VP]),
         "ab200_tile_last_bm_stats": (_I, [_VP, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
+        "ab200_tile_get_pulse_counters": (_I, [_VP, _VP]),
+        "ab200_tile_counts_pulses": (_I, [_VP]),
         "ab200_tile_set_seed": (_I, [_VP, C.c_uint64]),
         "ab200_array_create": (_I, [cfgp, _I, _I, _I, _I, _I, _I, _I, C.POINTER(_VP)]),
         "ab200_array_create_block": (_I, [cfgp, _I, _I, _I, _I, _I, _I, _I, _I, _I, C.POINTER(_VP)]),

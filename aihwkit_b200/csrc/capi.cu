@@ -450,6 +450,23 @@ int ab200_tile_set_weights_uniform_random(ab200_tile *tile, float min_value, flo
   AB200_CATCH
 }
 
+int ab200_tile_get_pulse_counters(ab200_tile *tile, int64_t *out_host) {
+  AB200_TRY
+  if (!out_host) {
+    AB200_FATAL("null argument");
+  }
+  T(tile)->getPulseCounters(out_host);
+  AB200_CATCH
+}
+
+int ab200_tile_counts_pulses(ab200_tile *tile) {
+  try {
+    return tile && T(tile)->countsPulses() ? 1 : 0;
+  } catch (...) {
+    return 0;
+  }
+}
+
 int ab200_tile_last_bm_stats(ab200_tile *tile, int32_t *n_rerun_samples, float *max_reduction) {
   AB200_TRY
   T(tile)->lastBmStats(n_rerun_samples, max_reduction);

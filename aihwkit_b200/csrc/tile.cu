@@ -386,6 +386,11 @@ Tile::Tile(const ab200_tile_config &cfg, int cuda_device) : cfg_(cfg) {
   if (cfg.device_kind < AB200_DEVICE_IDEAL || cfg.device_kind > AB200_DEVICE_PIECEWISE_STEP) {
     AB200_FATAL("device kind not implemented");
   }
+  if (cfg.device[0].count_pulses || cfg.device[1].count_pulses) {
+    if (cfg.device_kind == AB200_DEVICE_IDEAL || cfg.device_kind == AB200_DEVICE_TRANSFER || cfg.mixed.enabled) {
+      AB200_FATAL("count_pulses is implemented for single pulsed devices only");
+    }
+  }
   if (cfg.mixed.enabled) {
     const ab200_mixedprec_params &mp = cfg.mixed;
     if (cfg.device_kind == AB200_DEVICE_IDEAL || cfg.device_kind == AB200_DEVICE_TRANSFER) {
@@ -581,6 +586,8 @@ Tile::~Tile() {
     cudaFree(t_mean_);
     cudaFree(t_past_);
     cudaFree(idx_);
+    cudaFree(pulses_up_);
+    cudaFree(pulses_down_);
     cudaFree(chi_);
     cudaFree(mp_qx_);
     cudaFree(mp_qd_);
@@ -697,6 +704,12 @@ void Tile::toDevice(int cuda_device) {
       AB200_CUDA(cudaMemset(t_past_, 0, size * sizeof(float)));
       chop_switched_.assign((size_t)x_size_, 0);
     }
+  }
+  if (countsPulses()) {
+    AB200_CUDA(cudaMalloc(&pulses_up_, size * sizeof(unsigned long long)));
+    AB200_CUDA(cudaMalloc(&pulses_down_, size * sizeof(unsigned long long)));
+    AB200_CUDA(cudaMemset(pulses_up_, 0, size * sizeof(unsigned long long)));
+    AB200_CUDA(cudaMemset(pulses_down_, 0, size * sizeof(unsigned long long)));
   }
   if (cfg_.mixed.enabled) {
     AB200_CUDA(cudaMalloc(&chi_, size * sizeof(float)));
@@ -1479,6 +1492,29 @@ void Tile::runTc(const MvmProblem &p, cudaStream_t s) {
   eng->run(r, s);
 }
 
+void Tile::getPulseCounters(int64_t *out_2dx) {
+  if (!countsPulses()) {
+    AB200_FATAL("get_pulse_counters: the device was not made with count_pulses");
+  }
+  const size_t size = (size_t)x_size_ * d_size_;
+  if (device_ < 0) {
+    std::memset(out_2dx, 0, 2 * size * sizeof(int64_t)); // no update has run without a device
+    return;
+  }
+  requireDevice("get_pulse_counters");
+  std::vector<unsigned long long> t(size);
+  AB200_CUDA(cudaDeviceSynchronize());
+  const unsigned long long *src[2] = {pulses_up_, pulses_down_};
+  for (int q = 0; q < 2; q++) {
+    AB200_CUDA(cudaMemcpy(t.data(), src[q], size * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    for (int i = 0; i < d_size_; i++) {
+      for (int j = 0; j < x_size_; j++) {
+        out_2dx[(size_t)q * size + (size_t)i * x_size_ + j] = (int64_t)t[(size_t)j * d_size_ + i];
+      }
+    }
+  }
+}
+
 void Tile::lastBmStats(int32_t *n_rerun, float *max_red) {
   requireDevice("last_bm_stats");
   int h[2] = {0, 0};
@@ -1764,6 +1800,9 @@ void Tile::updateCore(const float *x, long long x_ss, long long x_fs, int x_in, 
 
   if (cfg_.device_kind != AB200_DEVICE_TRANSFER) {
     u.w = w_;
+    if (pulses_up_) {
+      launchPulseCounter(u, pulses_up_, pulses_down_, s);
+    }
     applyRange(u);
     return;
   }

@@ -226,6 +226,10 @@ void launchPulsedUpdateStream(const UpdateProblem &p, const uint32_t *xwT, const
                               const uint32_t *list_x, const uint32_t *list_off);
 void launchPulsedUpdate(const UpdateProblem &p, cudaStream_t stream);
 void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream);
+// pulses of the samples [s_begin, s_end) of a prepared batch, added per weight to `up` (the weight
+// rises) and `down` (it falls), both [x][d]
+void launchPulseCounter(const UpdateProblem &p, unsigned long long *up, unsigned long long *down,
+                        cudaStream_t stream);
 void launchFPUpdate(const UpdateProblem &p, float lr_signed, cudaStream_t stream,
                     bool overwrite = false, bool clip_each = false);
 // Chopped transfer: de-chop the read of column `col`, accumulate it in the buffer column in units
@@ -331,6 +335,8 @@ public:
   void updateIndexed(const float *x, const float *d, long long total_input_size, int m_batch,
                      int n_img, bool trans, cudaStream_t s);
   void lastBmStats(int32_t *n_rerun, float *max_red);
+  bool countsPulses() const { return cfg_.device[0].count_pulses != 0; }
+  void getPulseCounters(int64_t *out_2dx);
 
   // state that is neither a weight nor a hidden parameter, as name -> value pairs
   // (RPUSimple / RPUPulsed / TransferRPUDevice::dumpExtra / loadExtra, src/rpucuda/rpu.cpp:405-503,
@@ -488,6 +494,7 @@ private:
   long long idx_t_cap_ = 0;
   bool idx_t_valid_ = false;
   RowGather upd_gather_; // set around an update whose samples are gathered from images
+  unsigned long long *pulses_up_ = nullptr, *pulses_down_ = nullptr; // count_pulses: [x][d] each
   // mixed-precision compound: digital accumulator chi ([x][d] like the weights), quantised
   // samples of the current batch, pulse counts / one-hot vectors of the rows in transfer, the
   // sample counter and the next row to transfer

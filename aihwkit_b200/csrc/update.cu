@@ -1094,6 +1094,59 @@ __global__ void coincidenceKernel(UpdateProblem p, int32_t *counts) {
   counts[t] = n;
 }
 
+// Pulse counters (kernelPulseCounter, src/rpucuda/cuda/pwu_kernel.h:1523-1620): a pass of its
+// own over the prepared pulse words, one thread per weight, before the update applies them.
+__global__ void __launch_bounds__(256)
+    pulseCounterKernel(UpdateProblem p, unsigned long long *up, unsigned long long *down) {
+  pdlEnter();
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= (long long)p.x_size * p.d_size) {
+    return;
+  }
+  const int j = (int)(t / p.d_size), i = (int)(t % p.d_size); // the weights' own order [x][d]
+  const bool implicit = p.up.pulse_type == AB200_PULSE_DETERMINISTIC_IMPLICIT ||
+                        p.up.pulse_type == AB200_PULSE_MEAN_COUNT;
+  const int nseg = p.nseg > 0 ? p.nseg : 1;
+  unsigned long long n_up = 0, n_down = 0;
+  for (int s = p.s_begin; s < p.s_end; s++) {
+    const uint32_t *xw = p.xw + (long long)s * nseg * p.x_size;
+    const uint32_t *dw = p.dw + (long long)s * nseg * p.d_size;
+    if (implicit) {
+      const uint32_t dwv = dw[i];
+      const int n = dwv == 0u ? 0 : (int)rintf(__fmul_rn(__uint_as_float(dwv), __uint_as_float(xw[j])));
+      // a positive product lowers the weight (w -= lr d x)
+      if (n > 0) {
+        n_down += (unsigned)n;
+      } else {
+        n_up += (unsigned)(-n);
+      }
+    } else {
+      for (int g = 0; g < nseg; g++) {
+        const uint32_t xwv = xw[(long long)g * p.x_size + j], dwv = dw[(long long)g * p.d_size + i];
+        const unsigned c = (unsigned)__popc((xwv & dwv) >> 1);
+        if (((xwv ^ dwv) & 1u) == 0u) {
+          n_down += c;
+        } else {
+          n_up += c;
+        }
+      }
+    }
+  }
+  up[t] += n_up;
+  down[t] += n_down;
+}
+
+void launchPulseCounter(const UpdateProblem &p, unsigned long long *up, unsigned long long *down,
+                        cudaStream_t stream) {
+  if (p.s_end <= p.s_begin) {
+    return;
+  }
+  const long long n = (long long)p.x_size * p.d_size;
+  AB200_CUDA(launchChained(pulseCounterKernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, p, up,
+                           down));
+  AB200_LAUNCH_CHECK();
+}
+
 void launchCoincidences(const UpdateProblem &p, int32_t *counts_dx, cudaStream_t stream) {
   long long n = (long long)p.x_size * p.d_size;
   coincidenceKernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p, counts_dx);

@@ -317,8 +317,7 @@ class PulsedResistiveDeviceParameter(AbstractResistiveDeviceParameter):
             raise RuntimeError(
                 "device parameter 'corrupt_devices_prob' is not implemented by the B200 analog tile"
             )
-        if self.count_pulses:
-            raise RuntimeError("count_pulses is not implemented by the B200 analog tile")
+        c.count_pulses = int(bool(self.count_pulses))
         c.kind = self._kind
         c.construction_seed = int(self.construction_seed) & 0xFFFFFFFF
         c.enforce_consistency = int(bool(self.enforce_consistency))

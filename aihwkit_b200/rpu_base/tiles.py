@@ -640,9 +640,13 @@ class AnalogTile:
         self._hidden_update_index = 0
 
     def get_pulse_counters(self) -> torch.Tensor:
-        """rpu_base_tiles.cpp:846-868: int64 ``[k, d_size, x_size]``; empty unless the device
-        counts pulses (``count_pulses``, which the B200 tile does not implement)."""
-        return torch.zeros(0, self.get_d_size(), self.get_x_size(), dtype=torch.int64)
+        """rpu_base_tiles.cpp:846-868: int64 ``[2, d_size, x_size]`` (pulses up, pulses down) of a
+        device made with ``count_pulses``; empty otherwise."""
+        if not self._lib.ab200_tile_counts_pulses(self._h):
+            return torch.zeros(0, dtype=torch.int64)
+        out = torch.empty(2, self.get_d_size(), self.get_x_size(), dtype=torch.int64)
+        check(self._lib.ab200_tile_get_pulse_counters(self._h, out.data_ptr()))
+        return out
 
     def drift_weights(self, time_since_last_call: float) -> None:
         """rpu_base_tiles.cpp:294-314 (power-law drift, src/rpucuda/rpu.cpp:1581-1587,

@@ -188,6 +188,11 @@ typedef struct ab200_device_params {
   int32_t enforce_consistency;
   int32_t dw_min_dtod_log_normal;
   int32_t perfect_bias;
+  /* count the pulses every weight receives, up and down apart (count_pulses,
+   * src/rpucuda/rpu_pulsed_device.h:91; the reference counts on its GPU tile only,
+   * cuda/rpucuda_pulsed_device.cu:470-492, cuda/pwu_kernel.h:1523-1620): read with
+   * ab200_tile_get_pulse_counters. Single devices and the pulsed update only. */
+  int32_t count_pulses;
   float dw_min;
   float dw_min_dtod;
   float dw_min_std;
@@ -575,6 +580,14 @@ int ab200_tile_set_weights_uniform_random(ab200_tile *tile, float min_value, flo
 /* Bound-management statistics of the last forward: number of samples that were re-run at least
  * once and the largest reduction factor used (rpu_forward_backward_pass.cpp:935-983). */
 int ab200_tile_last_bm_stats(ab200_tile *tile, int32_t *n_rerun_samples, float *max_reduction);
+/* Pulse counters of a device created with count_pulses (getPulseCounters, src/rpucuda/rpu.h:511;
+ * get_pulse_counters, rpu_base_tiles.cpp:846-868): pulses that raised the weight in
+ * out[0][d][x], pulses that lowered it in out[1][d][x], summed over all updates since the tile
+ * was made (a pulse counts whether or not the weight was at its bound). `out` holds
+ * 2 * d_size * x_size values, row-major [2][d_size][x_size] (the reference hands out its device
+ * layout unchanged). Returns an error if the device does not count. */
+int ab200_tile_get_pulse_counters(ab200_tile *tile, int64_t *out_host);
+int ab200_tile_counts_pulses(ab200_tile *tile);
 
 /* Re-key the noise generator (RPUSimple::setRandomSeed, src/rpucuda/rpu.cpp:1516-1520). */
 int ab200_tile_set_seed(ab200_tile *tile, uint64_t seed);

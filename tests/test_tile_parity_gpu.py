@@ -779,3 +779,44 @@ def test_stochastic_rounding_of_pulse_probabilities():
     assert np.abs(near.mean(axis=0) - fine.mean(axis=0)).sum() > 0.2 * np.abs(fine.mean(axis=0)).sum()
     if ref.available():
         H.assert_moments_agree(sto, mean_update(0.25, True, use_ref=True))
+
+
+@pytest.mark.parametrize("pulse_det", [False, True])
+@pytest.mark.parametrize("m,bl", [(7, 31), (70, 31), (40, 80)])
+def test_pulse_counters_account_for_the_weight_change(pulse_det, m, bl):
+    """count_pulses: with a noise-free ConstantStep device far from its bounds the weight change
+    of every element is (pulses up) * step_up - (pulses down) * step_down, through the staged and
+    the streaming update kernel, one and several train segments, stochastic and implicit pulses;
+    the counters add up over calls and are empty for a device that does not count."""
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(m + bl)
+    x_size, d_size = 45, 37
+    p = H.training_params(noise=False, pulse_det=pulse_det)
+    p.update.desired_bl = bl
+    dp = H.device("cs", False, dw_min=0.001, dw_min_dtod=0.3, up_down=0.1, up_down_dtod=0.05, w_max=5.0, w_min=-5.0,
+                  w_max_dtod=0.0, w_min_dtod=0.0)
+    assert T.AnalogTile(p._config(x_size, d_size, dp, seed=5), cuda_device=0).get_pulse_counters().numel() == 0
+    dp.count_pulses = True
+    t = T.AnalogTile(p._config(x_size, d_size, dp, seed=5), cuda_device=0)
+    assert int(t.get_pulse_counters().abs().sum()) == 0
+    names = t.get_hidden_parameter_names()
+    hp = t.get_hidden_parameters().numpy().astype(np.float64)
+    step_up, step_down = hp[names.index("dwmin_up")], hp[names.index("dwmin_down")]
+    w0 = t.get_weights().numpy().astype(np.float64)
+    t.set_learning_rate(0.05)
+    total = None
+    for k in range(3):
+        X = rng.uniform(-1, 1, (m, x_size)).astype(np.float32)
+        Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+        t.update(torch.from_numpy(X).cuda(), torch.from_numpy(Dm).cuda())
+        c = t.get_pulse_counters().numpy()
+        assert c.shape == (2, d_size, x_size) and (c >= 0).all()
+        if total is not None:
+            assert (c >= total).all()  # counters only grow
+        total = c
+    w1 = t.get_weights().numpy().astype(np.float64)
+    want = total[0] * step_up - total[1] * step_down
+    assert total.sum() > 10 * x_size * d_size // 20
+    assert np.abs((w1 - w0) - want).max() <= 2e-5 + 1e-6 * np.abs(want).max(), np.abs((w1 - w0) - want).max()
+    assert np.abs(w1).max() < 4.9  # no bound was reached
