@@ -63,7 +63,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=min(8, len(sources))) as ex:
         objs = list(ex.map(compile_one, sources))
     if force or _stale(OUT, objs):
-        cmd = [nvcc, "-shared", "-o", OUT] + objs + ["-cudart", "static", "-ldl", "-lpthread"]
+        # A C-ABI library keeps its runtimes to itself: the CUDA runtime and the C++ runtime are
+        # linked statically and hidden (-Bsymbolic, --exclude-libs), so that a process which also
+        # holds other copies (torch exports its own instantiations of std::string and
+        # std::ostringstream members, and loads the shared CUDA runtime) cannot have this
+        # library's calls bound to them. Without this, loading the library as a dependency of a
+        # torch extension crashed in its error path (the message is built with std::ostringstream).
+        cmd = [nvcc, "-shared", "-o", OUT] + objs + ["-cudart", "static", "-ldl", "-lpthread",
+                                                     "-Xcompiler", "-static-libstdc++",
+                                                     "-Xlinker", "-Bsymbolic", "-Xlinker", "--exclude-libs=ALL"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
@@ -74,6 +82,29 @@ def build(force: bool = False, verbose: bool = False) -> str:
         for src, log in logs.items():
             f.write(f"== {os.path.basename(src)}\n{log}\n")
     return OUT
+
+
+def build_pybind(verbose: bool = False):
+    """Compile ``csrc/pybind_module.cpp`` - the pybind11 / torch binding over the C ABI that a
+    maintainer of the reference would link in place of its own tile classes - in-tree
+    (``csrc/build_pybind/ab200_pybind.so``) and return the imported module.  The binding sees the
+    library through ``include/aihwkit_b200.h`` and the linker only."""
+    from torch.utils.cpp_extension import load
+
+    build()
+    out_dir = os.path.join(HERE, "csrc", "build_pybind")
+    os.makedirs(out_dir, exist_ok=True)
+    return load(
+        name="ab200_pybind",
+        sources=[os.path.join(HERE, "csrc", "pybind_module.cpp")],
+        extra_include_paths=[os.path.join(os.path.dirname(HERE), "include")],
+        extra_cflags=["-O2"],
+        extra_ldflags=[f"-L{os.path.join(HERE, 'csrc')}", "-laihwkit_b200",
+                       f"-Wl,-rpath,{os.path.join(HERE, 'csrc')}"],
+        build_directory=out_dir,
+        with_cuda=True,
+        verbose=verbose,
+    )
 
 
 if __name__ == "__main__":
