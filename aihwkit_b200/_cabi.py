@@ -293,6 +293,11 @@ def _declare(lib: C.CDLL) -> None:
         "ab200_tile_extra_count": (_I, []),
         "ab200_tile_extra_name": (C.c_char_p, [_I]),
         "ab200_tile_dump_extra": (_I, [_VP, C.POINTER(C.c_double)]),
+        "ab200_tile_extra_vector_count": (_I, [_VP]),
+        "ab200_tile_extra_vector_name": (C.c_char_p, [_VP, _I]),
+        "ab200_tile_extra_vector_size": (_I, [_VP, _I]),
+        "ab200_tile_get_extra_vector": (_I, [_VP, _I, C.POINTER(C.c_double)]),
+        "ab200_tile_set_extra_vector": (_I, [_VP, _I, C.POINTER(C.c_double), _I]),
         "ab200_tile_load_extra": (_I, [_VP, C.POINTER(C.c_char_p), C.POINTER(C.c_double), _I, _I]),
         "ab200_tile_decay_weights": (_I, [_VP, C.c_float, _I, _VP]),
         "ab200_tile_drift_weights": (_I, [_VP, C.c_float, _VP]),

@@ -450,6 +450,44 @@ int ab200_tile_set_weights_uniform_random(ab200_tile *tile, float min_value, flo
   AB200_CATCH
 }
 
+int ab200_tile_extra_vector_count(const ab200_tile *tile) {
+  try {
+    return tile ? T(tile)->extraVectorCount() : 0;
+  } catch (...) {
+    return 0;
+  }
+}
+const char *ab200_tile_extra_vector_name(const ab200_tile *tile, int k) {
+  try {
+    return T(tile)->extraVectorName(k);
+  } catch (...) {
+    return "";
+  }
+}
+int ab200_tile_extra_vector_size(const ab200_tile *tile, int k) {
+  try {
+    return T(tile)->extraVectorSize(k);
+  } catch (...) {
+    return 0;
+  }
+}
+int ab200_tile_get_extra_vector(ab200_tile *tile, int k, double *out) {
+  AB200_TRY
+  if (!out) {
+    AB200_FATAL("null argument");
+  }
+  T(tile)->getExtraVector(k, out);
+  AB200_CATCH
+}
+int ab200_tile_set_extra_vector(ab200_tile *tile, int k, const double *in, int n) {
+  AB200_TRY
+  if (!in) {
+    AB200_FATAL("null argument");
+  }
+  T(tile)->setExtraVector(k, in, n);
+  AB200_CATCH
+}
+
 int ab200_tile_get_pulse_counters(ab200_tile *tile, int64_t *out_host) {
   AB200_TRY
   if (!out_host) {

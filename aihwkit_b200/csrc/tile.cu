@@ -472,6 +472,9 @@ const char *const kExtraNames[] = {
     "noise.key0",  "noise.key1",               // Philox key of all run-time noise
     "noise.forward_calls", "noise.backward_calls", "noise.update_calls", "noise.transfer_calls",
     "noise.weight_op_calls",
+    "rpu_device.transfer_counter",             // ChoppedTransferRPUDevice (passes over the matrix)
+    "rpu_device.mixed.current_update_index",   // MixedPrecRPUDeviceBase (rpu_mixedprec_device_base.cpp:252-253)
+    "rpu_device.mixed.current_row_index",
 };
 constexpr int kExtraCount = (int)(sizeof(kExtraNames) / sizeof(kExtraNames[0]));
 } // namespace
@@ -495,7 +498,10 @@ void Tile::dumpExtra(double *values) const {
                                  (double)bwd_calls_,
                                  (double)upd_calls_,
                                  (double)transfer_calls_,
-                                 (double)op_calls_};
+                                 (double)op_calls_,
+                                 (double)chop_passes_,
+                                 (double)mp_update_idx_,
+                                 (double)mp_row_idx_};
   for (int k = 0; k < kExtraCount; k++) {
     values[k] = v[k];
   }
@@ -527,6 +533,9 @@ void Tile::loadExtra(const char *const *names, const double *values, int n, bool
     case 7: upd_calls_ = (uint32_t)v; break;
     case 8: transfer_calls_ = (uint32_t)v; break;
     case 9: op_calls_ = (uint32_t)v; break;
+    case 10: chop_passes_ = (uint64_t)v; break;
+    case 11: mp_update_idx_ = (long long)v; break;
+    case 12: mp_row_idx_ = (int)v; break;
     }
   }
   if (strict) {
@@ -536,6 +545,74 @@ void Tile::loadExtra(const char *const *names, const double *values, int n, bool
       }
     }
   }
+}
+
+// Vector-valued state of the chopped / dynamic transfer compounds: the choppers of the input and
+// output lines and, for the dynamic form, which input choppers flipped at their last transfer
+// (in_chopper_, out_chopper_, in_chopper_switched_ of the reference's dumpExtra,
+// rpu_chopped_transfer_device.cpp:229-262, rpu_dynamic_transfer_device.cpp:196-236).
+int Tile::extraVectorCount() const {
+  if (cfg_.device_kind != AB200_DEVICE_TRANSFER || !cfg_.transfer.chopped) {
+    return 0;
+  }
+  return cfg_.transfer.dynamic ? 3 : 2;
+}
+
+const char *Tile::extraVectorName(int k) const {
+  static const char *const kNames[3] = {"rpu_device.in_chopper", "rpu_device.out_chopper",
+                                        "rpu_device.in_chopper_switched"};
+  if (k < 0 || k >= extraVectorCount()) {
+    AB200_FATAL("extra vector index out of range");
+  }
+  return kNames[k];
+}
+
+int Tile::extraVectorSize(int k) const {
+  if (k < 0 || k >= extraVectorCount()) {
+    AB200_FATAL("extra vector index out of range");
+  }
+  return k == 1 ? d_size_ : x_size_;
+}
+
+void Tile::getExtraVector(int k, double *out) {
+  const int n = extraVectorSize(k);
+  if (k == 2) {
+    for (int i = 0; i < n; i++) {
+      out[i] = i < (int)chop_switched_.size() ? (double)chop_switched_[i] : 0.0;
+    }
+    return;
+  }
+  if (device_ < 0) {
+    std::fill(out, out + n, 0.0); // all choppers start unflipped
+    return;
+  }
+  requireDevice("dump_extra");
+  std::vector<unsigned char> t((size_t)n);
+  AB200_CUDA(cudaDeviceSynchronize());
+  AB200_CUDA(cudaMemcpy(t.data(), k == 0 ? chop_in_ : chop_out_, (size_t)n, cudaMemcpyDeviceToHost));
+  for (int i = 0; i < n; i++) {
+    out[i] = (double)t[i];
+  }
+}
+
+void Tile::setExtraVector(int k, const double *in, int n) {
+  if (n != extraVectorSize(k)) {
+    AB200_FATAL("load_extra: '" << extraVectorName(k) << "' expects " << extraVectorSize(k) << " values");
+  }
+  if (k == 2) {
+    chop_switched_.assign((size_t)n, 0);
+    for (int i = 0; i < n; i++) {
+      chop_switched_[i] = in[i] != 0.0 ? 1 : 0;
+    }
+    return;
+  }
+  requireDevice("load_extra");
+  std::vector<unsigned char> t((size_t)n);
+  for (int i = 0; i < n; i++) {
+    t[i] = in[i] != 0.0 ? 1 : 0;
+  }
+  AB200_CUDA(cudaDeviceSynchronize());
+  AB200_CUDA(cudaMemcpy(k == 0 ? chop_in_ : chop_out_, t.data(), (size_t)n, cudaMemcpyHostToDevice));
 }
 
 Tile::~Tile() {

@@ -335,6 +335,12 @@ public:
   void updateIndexed(const float *x, const float *d, long long total_input_size, int m_batch,
                      int n_img, bool trans, cudaStream_t s);
   void lastBmStats(int32_t *n_rerun, float *max_red);
+  // vector-valued extra state (choppers of the chopped / dynamic transfer compounds)
+  int extraVectorCount() const;
+  const char *extraVectorName(int k) const;
+  int extraVectorSize(int k) const;
+  void getExtraVector(int k, double *out);
+  void setExtraVector(int k, const double *in, int n);
   bool countsPulses() const { return cfg_.device[0].count_pulses != 0; }
   void getPulseCounters(int64_t *out_2dx);
 

@@ -444,20 +444,37 @@ class AnalogTile:
     # -- extra state, copies ---------------------------------------------------------------------
     def dump_extra(self) -> dict:
         """rpu_base_tiles.cpp ``dump_extra``: state besides weights and hidden parameters as
-        ``{name: [values]}`` (learning rate, Tiki-Taka counters, noise key and call counters)."""
+        ``{name: [values]}`` (learning rate, compound counters, noise key and call counters, and
+        the chopper vectors of the chopped / dynamic transfer compounds)."""
         n = self._lib.ab200_tile_extra_count()
         values = (C.c_double * n)()
         check(self._lib.ab200_tile_dump_extra(self._h, values))
-        return {self._lib.ab200_tile_extra_name(k).decode(): [float(values[k])] for k in range(n)}
+        out = {self._lib.ab200_tile_extra_name(k).decode(): [float(values[k])] for k in range(n)}
+        for k in range(self._lib.ab200_tile_extra_vector_count(self._h)):
+            size = self._lib.ab200_tile_extra_vector_size(self._h, k)
+            vec = (C.c_double * size)()
+            check(self._lib.ab200_tile_get_extra_vector(self._h, k, vec))
+            out[self._lib.ab200_tile_extra_vector_name(self._h, k).decode()] = [float(v) for v in vec]
+        return out
 
     def load_extra(self, extra: dict, strict: bool = False) -> None:
         """rpu_base_tiles.cpp ``load_extra``; with ``strict`` unknown or missing keys raise."""
-        names = list(extra.keys())
+        vectors = {self._lib.ab200_tile_extra_vector_name(self._h, k).decode(): k
+                   for k in range(self._lib.ab200_tile_extra_vector_count(self._h))}
+        names = [k for k in extra.keys() if k not in vectors]
         n = len(names)
         c_names = (C.c_char_p * max(n, 1))(*[k.encode() for k in names])
         c_vals = (C.c_double * max(n, 1))(*[float(extra[k][0] if isinstance(extra[k], (list, tuple)) else extra[k])
                                             for k in names])
         check(self._lib.ab200_tile_load_extra(self._h, c_names, c_vals, n, int(strict)))
+        for name, k in vectors.items():
+            if name not in extra:
+                if strict:
+                    raise RuntimeError(f"load_extra: key '{name}' is missing")
+                continue
+            vals = [float(v) for v in extra[name]]
+            vec = (C.c_double * max(len(vals), 1))(*vals)
+            check(self._lib.ab200_tile_set_extra_vector(self._h, k, vec, len(vals)))
 
     def __copy__(self):
         """A new tile with the same configuration, device parameters, weights and state

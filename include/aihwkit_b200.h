@@ -491,6 +491,15 @@ const char *ab200_tile_extra_name(int k);
 int ab200_tile_dump_extra(ab200_tile *tile, double *values);
 int ab200_tile_load_extra(ab200_tile *tile, const char *const *names, const double *values,
                           int count, int strict);
+/* Vector-valued extra state: the choppers of the chopped / dynamic transfer compounds
+ * ("rpu_device.in_chopper" [x_size], "rpu_device.out_chopper" [d_size], and for the dynamic form
+ * "rpu_device.in_chopper_switched" [x_size]; in_chopper_ / out_chopper_ / in_chopper_switched_
+ * of the reference's dumpExtra). count = 0 for every other device. Values are 0 or 1. */
+int ab200_tile_extra_vector_count(const ab200_tile *tile);
+const char *ab200_tile_extra_vector_name(const ab200_tile *tile, int k);
+int ab200_tile_extra_vector_size(const ab200_tile *tile, int k);
+int ab200_tile_get_extra_vector(ab200_tile *tile, int k, double *out);
+int ab200_tile_set_extra_vector(ab200_tile *tile, int k, const double *in, int n);
 
 /* Per-line values of a direction's IO (MVParameter, src/rpucuda/rpu_forward_backward_pass.h:14-22;
  * part of the reference's extra state as fwd.v_offset / fwd.out_nonlinearity / fwd.out_noise_values
