@@ -243,18 +243,22 @@ void TileArray::forwardImpl(const float *x0, long long x_ss, float *y, int m, cu
   }
 }
 
-// dst[r][c] = src[r * src_ld + c] * factor: the gradient block of one out-split, scaled
+// dst[r][c] = src[r * src_ld + c] * factor (or / factor): the gradient block of one out-split,
+// scaled the way the reference's periphery scales it - a product before the backward pass, a
+// quotient before the update (tiles/periphery.py pre_backward / pre_update): the quotient and the
+// product with the reciprocal differ in the last bit, which can move a pulse count
 __global__ void __launch_bounds__(256)
     scaleBlockKernel(const float *src, long long src_ld, float *dst, int cols, long long n,
-                     float factor) {
+                     float factor, int divide) {
   const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (t < n) {
-    dst[t] = src[(t / cols) * src_ld + t % cols] * factor;
+    const float v = src[(t / cols) * src_ld + t % cols];
+    dst[t] = divide ? __fdiv_rn(v, factor) : __fmul_rn(v, factor);
   }
 }
 
 const float *TileArray::scaledGradient(const float *d, int oi, int m, float factor, long long &ld,
-                                       cudaStream_t s) {
+                                       cudaStream_t s, bool divide) {
   if (factor == 1.0f) {
     ld = out_size_;
     return d + out_off_[oi];
@@ -269,7 +273,7 @@ const float *TileArray::scaledGradient(const float *d, int oi, int m, float fact
   }
   scaleBlockKernel<<<(unsigned)((need + 255) / 256), 256, 0, s>>>(d + out_off_[oi], out_size_,
                                                                d_scratch_, cols, (long long)need,
-                                                               factor);
+                                                               factor, divide ? 1 : 0);
   AB200_LAUNCH_CHECK();
   ld = cols;
   return d_scratch_;
@@ -394,7 +398,7 @@ void TileArray::update(const float *x, const float *d, int m, cudaStream_t s) {
           scaled_ ? tile_scale_host_[(size_t)(ii - in_begin_) * n_ol + (oi - out_begin_)] : 1.0f;
       long long ld = 0;
       // pre_update: the gradient is divided by the mapping scale
-      const float *dt = scaledGradient(d, oi, m, 1.0f / alpha, ld, s);
+      const float *dt = scaledGradient(d, oi, m, alpha, ld, s, /*divide=*/true);
       tile(ii - in_begin_, oi - out_begin_).updateStrided(x + in_off_[ii], in_size_, dt, ld, m, s);
     }
   }

@@ -84,7 +84,7 @@ private:
   float *d_scratch_ = nullptr; // [m][largest out-split]: gradients times / over the tile scale
   size_t d_scratch_floats_ = 0;
   const float *scaledGradient(const float *d, int oi, int m, float factor, long long &ld,
-                              cudaStream_t s);
+                              cudaStream_t s, bool divide = false);
   std::unique_ptr<TcEngine> tc_;
   std::vector<uint64_t> tc_versions_;
   bool tcEligible(int m);

@@ -459,8 +459,10 @@ def test_mapped_forward_weight_scaling_and_bias(out_size, in_size, max_tile, m, 
         lib.ab200_set_mvm_path(0)
 
 
-@pytest.mark.parametrize("omega", [0.0, 0.5])
-def test_mapped_backward_and_update(omega):
+@pytest.mark.parametrize("omega,out_size,in_size,max_tile,m", [(0.0, 96, 200, 64, 12), (0.5, 96, 200, 64, 12),
+                                                             (0.7, 130, 520, 256, 150), (0.0, 300, 65, 128, 33),
+                                                             (0.4, 512, 1024, 512, 260)])
+def test_mapped_backward_and_update(omega, out_size, in_size, max_tile, m):
     """Training calls of the mapped layer: backward sums the tiles' IO-managed transposed MVMs over
     the out-splits, update pulses every tile with its block of activations and gradients; with
     weight scaling the gradient is multiplied (backward) / divided (update) by the tile's scale."""
@@ -468,7 +470,6 @@ def test_mapped_backward_and_update(omega):
     from aihwkit_b200.sharded import split_sizes
 
     rng = np.random.default_rng(21)
-    out_size, in_size, max_tile, m = 96, 200, 64, 12
     p = H.training_params(noise=False, pulse_det=True, bm=False)
     dp = H.device("sb", False)
     cfg = p._config(1, 1, dp, seed=3)
