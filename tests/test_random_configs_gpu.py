@@ -326,3 +326,51 @@ def test_random_noisy_forward_moments_against_reference(seed):
     # element by element: std-dev within the sampling error of two estimates from `reps` draws
     ratio = ys.std(axis=0) / np.maximum(yr.std(axis=0), 1e-12)
     assert np.abs(ratio - 1.0).max() < 6.0 / np.sqrt(reps), np.abs(ratio - 1.0).max()
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_floating_point_tiles(seed):
+    """FloatingPointTile (perfect IO, floating-point update; RPUSimple) at random shapes, layouts
+    and bias settings: forward, backward and the rank update against float64 numpy, on the
+    automatic kernel selection and with the tensor-core path forced on (which perfect IO cannot
+    take: the CUDA-core kernels must serve it either way), also through host buffers."""
+    from aihwkit_b200 import _cabi
+    from aihwkit_b200.rpu_base import tiles as T
+
+    rng = np.random.default_rng(15000 + seed)
+    pick = lambda seq: seq[int(rng.integers(len(seq)))]  # noqa: E731
+    x_size, d_size, m = int(pick([1, 3, 30, 129, 512, 700])), int(pick([1, 5, 64, 200, 513])), int(pick([1, 7, 130, 600]))
+    bias = bool(rng.integers(2)) and x_size > 1
+    x_trans, d_trans = bool(rng.integers(2)), bool(rng.integers(2))
+    x_in = x_size - (1 if bias else 0)
+    W = rng.uniform(-0.5, 0.5, (d_size, x_size)).astype(np.float32)
+    X = rng.uniform(-1, 1, (m, x_in)).astype(np.float32)
+    Dm = rng.normal(0, 0.3, (m, d_size)).astype(np.float32)
+    Xb = np.concatenate([X, np.ones((m, 1), np.float32)], 1) if bias else X
+    Xa = np.ascontiguousarray(X.T) if x_trans else X
+    Da = np.ascontiguousarray(Dm.T) if d_trans else Dm
+    y_want = Xb.astype(np.float64) @ W.astype(np.float64).T
+    g_want = (Dm.astype(np.float64) @ W.astype(np.float64))[:, :x_in]
+    tol = 2e-6 * max(x_size, d_size) ** 0.5 + 1e-6
+    lib = _cabi.lib()
+    try:
+        for mode in (0, 2):
+            assert lib.ab200_set_mvm_path(mode) == 0
+            t = T.FloatingPointTile(x_size, d_size).cuda(0)
+            t.set_weights(torch.from_numpy(W))
+            y = t.forward(torch.from_numpy(Xa).cuda(), bias, x_trans, d_trans).cpu().numpy()
+            y = y.T if d_trans else y
+            assert np.abs(y - y_want).max() <= tol * max(np.abs(y_want).max(), 1.0), ("forward", mode)
+            g = t.backward(torch.from_numpy(Da).cuda(), bias, d_trans, x_trans).cpu().numpy()
+            g = g.T if x_trans else g
+            assert g.shape == g_want.shape
+            assert np.abs(g - g_want).max() <= tol * max(np.abs(g_want).max(), 1.0), ("backward", mode)
+            if mode == 0:  # host buffers
+                yh = t.forward(torch.from_numpy(Xa), bias, x_trans, d_trans).numpy()
+                assert np.array_equal(yh.T if d_trans else yh, y)
+            t.set_learning_rate(0.1)
+            t.update(torch.from_numpy(Xa).cuda(), torch.from_numpy(Da).cuda(), bias, x_trans, d_trans)
+            w_want = W.astype(np.float64) - 0.1 * Dm.astype(np.float64).T @ Xb.astype(np.float64)
+            assert np.abs(t.get_weights().numpy() - w_want).max() <= 2e-6 * m ** 0.5 * max(np.abs(w_want).max(), 1.0) + 1e-6
+    finally:
+        lib.ab200_set_mvm_path(0)
