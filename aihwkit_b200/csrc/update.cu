@@ -1284,7 +1284,8 @@ __global__ void __launch_bounds__(256)
       st = __fadd_rn(u01(r[0]), -0.5f);
     }
     float q = rintf(__fadd_rn(__fdiv_rn(v, width), st));
-    q = __fmul_rn(fminf(fmaxf(q, -half), half), width);
+    // (a zero stays a zero also where a single bin makes the width infinite: the reference skips it)
+    q = q == 0.0f ? 0.0f : __fmul_rn(fminf(fmaxf(q, -half), half), width);
     if (is_x) {
       qx[(long long)s * x_size + idx] = q;
     } else {
