@@ -56,8 +56,10 @@ def test_mapped_forward_noise_off(out_size, in_size, max_tile, m):
     assert np.array_equal(y_h.numpy(), y)
 
 
-@pytest.mark.parametrize("m", [40, 256])
-def test_mapped_forward_iterative_bound_management(m):
+@pytest.mark.parametrize("m,out_size,in_size,max_out,max_in", [(40, 512, 640, 256, 320), (256, 512, 640, 256, 320),
+                                                               (300, 200, 1000, 128, 400), (130, 700, 300, 512, 128),
+                                                               (9, 64, 900, 64, 300)])
+def test_mapped_forward_iterative_bound_management(m, out_size, in_size, max_out, max_in):
     """A 2 x 2 mapped layer with the training IO (iterative bound management) and an output bound
     small enough that many rows clip in the first round: every tile re-runs its clipped rows on its
     own before its result joins the sum over the in-splits. 256 rows take the tensor-core kernel
@@ -65,7 +67,6 @@ def test_mapped_forward_iterative_bound_management(m):
     from aihwkit_b200.rpu_base import tiles as T
 
     rng = np.random.default_rng(m)
-    out_size, in_size, max_out, max_in = 512, 640, 256, 320
     p = H.training_params(noise=False, pulse_det=True, bm=True, out_bound=2.0)
     cfg = p._config(1, 1, H.device("cs", False), seed=3)
     arr = T.TileArray(cfg, out_size, in_size, max_out, max_in, cuda_device=0)
@@ -77,7 +78,10 @@ def test_mapped_forward_iterative_bound_management(m):
     y_or, lsb, n_in = _array_oracle(W, X, cfg, max_out, max_in)
     # the test is only meaningful when the first round clips
     io = O.IO.from_c(cfg.forward_io)
-    _, _, _, reductions = O.forward(W[:max_out, :max_in], X[:, :max_in], io, return_pre_adc=True)
+    from aihwkit_b200.sharded import split_sizes
+
+    o0, i0 = split_sizes(out_size, max_out)[0], split_sizes(in_size, max_in)[0]
+    _, _, _, reductions = O.forward(W[:o0, :i0], X[:, :i0], io, return_pre_adc=True)
     assert (reductions > 1).mean() > 0.2
     diff = np.abs(y - y_or)
     assert (diff > 1e-3 * lsb).mean() <= 2e-3 * n_in
