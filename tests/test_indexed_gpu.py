@@ -282,3 +282,46 @@ def test_random_convolution_geometries(seed):
             assert np.abs(t.get_weights().numpy() - w1).max() <= 1e-6, mode
     finally:
         lib.ab200_set_mvm_path(0)
+
+
+@pytest.mark.parametrize("which", ["sb", "transfer", "chopped", "mixed"])
+@pytest.mark.parametrize("n_img", [1, 6])
+def test_indexed_update_equals_update_on_the_unfolded_matrix(which, n_img):
+    """update_indexed (the pulse preparation gathers its samples from the images; a compound cuts
+    the batch at its transfers) against update on the unfolded matrix with the same seed and
+    stochastic pulses: the same samples, the same trains, the same weights and hidden planes bit
+    for bit - small batches (staged kernel) and large ones (streaming kernel)."""
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import analog_tile_oracle as O
+
+    rng = np.random.default_rng(17)
+    c, h, w, c_out = 5, 9, 8, 11
+    idx = O.conv_indices((c, h, w), (3, 3), (1, 1), (1, 1), (1, 1), True)
+    x_size = c * 9 + 1
+    m_batch = idx.size // x_size
+    p = H.training_params(noise=True, pulse_det=False)
+    if which == "sb":
+        dp = H.device("sb", True)
+    elif which == "transfer":
+        dp = H.transfer_device(True, transfer_every=7.0, units_in_mbatch=False, n_reads=2)
+    elif which == "chopped":
+        dp = H.chopped_transfer_device(transfer_lr=4.0, in_chop_prob=0.3, in_chop_random=False, transfer_every=5.0)
+    else:
+        dp = H.mixed_precision_device(n_rows_per_transfer=4)
+    cfg = p._config(x_size, c_out, dp, seed=5)
+    a, b = T.AnalogTile(cfg, cuda_device=0), T.AnalogTile(cfg, cuda_device=0)
+    a.set_matrix_indices(_gpu(idx))
+    W = rng.uniform(-0.3, 0.3, (c_out, x_size)).astype(np.float32)
+    for t in (a, b):
+        t.set_weights(torch.from_numpy(W))
+        t.set_learning_rate(0.05)
+    for _ in range(3):
+        X = np.maximum(rng.standard_normal((n_img, c, h, w)), 0).astype(np.float32)
+        Dm = rng.normal(0, 0.2, (n_img, c_out, m_batch)).astype(np.float32)
+        a.update_indexed(_gpu(X), _gpu(Dm.reshape(n_img, c_out, h, w)))
+        cols = O.indexed_input(X, idx, x_size, m_batch, n_img, True)
+        d_cols = O.to_sample_major(Dm, c_out, m_batch, n_img, True)
+        b.update(_gpu(cols), _gpu(d_cols))
+    assert float((a.get_weights() - torch.from_numpy(np.clip(W, -1, 1))).abs().max()) > 0 or which != "sb"
+    assert torch.equal(a.get_weights(), b.get_weights())
+    assert torch.equal(a.get_hidden_parameters(), b.get_hidden_parameters())
