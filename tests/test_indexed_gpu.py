@@ -325,3 +325,34 @@ def test_indexed_update_equals_update_on_the_unfolded_matrix(which, n_img):
     assert float((a.get_weights() - torch.from_numpy(np.clip(W, -1, 1))).abs().max()) > 0 or which != "sb"
     assert torch.equal(a.get_weights(), b.get_weights())
     assert torch.equal(a.get_hidden_parameters(), b.get_hidden_parameters())
+
+
+@pytest.mark.parametrize("mvm_path", [0, 2], indirect=True)
+def test_indexed_forward_equals_forward_on_the_unfolded_matrix_with_noise(mvm_path):
+    """forward_indexed with all noise sources of the training IO on against forward on the
+    unfolded matrix with the same seed: same DAC codes, same noise counters (keyed by the row of
+    the batch), so the image-major result is the transpose of the row-major one bit for bit -
+    whether the DAC kernel gathers the rows itself (tensor-core path) or the matrix is written
+    first."""
+    from aihwkit_b200.rpu_base import tiles as T
+    from oracle import analog_tile_oracle as O
+
+    rng = np.random.default_rng(19)
+    n_img, c, h, w, c_out = 3, 12, 10, 9, 40
+    idx = O.conv_indices((c, h, w), (3, 3), (1, 1), (1, 1), (1, 1), False)
+    x_size = c * 9
+    m_batch = idx.size // x_size
+    p = H.training_params(noise=True, pulse_det=False, bm=True, out_bound=3.0)
+    cfg = p._config(x_size, c_out, H.device("cs", True), seed=5)
+    a, b = T.AnalogTile(cfg, cuda_device=0), T.AnalogTile(cfg, cuda_device=0)
+    a.set_matrix_indices(_gpu(idx))
+    W = rng.uniform(-0.5, 0.5, (c_out, x_size)).astype(np.float32)
+    for t in (a, b):
+        t.set_weights(torch.from_numpy(W))
+    for _ in range(2):
+        X = rng.uniform(-1, 1, (n_img, c, h, w)).astype(np.float32)
+        ya = a.forward_indexed(_gpu(X), torch.empty(n_img, c_out, h, w, device="cuda")).cpu().numpy()
+        cols = O.indexed_input(X, idx, x_size, m_batch, n_img, True)
+        yb = b.forward(_gpu(cols)).cpu().numpy()
+        assert np.array_equal(O.to_sample_major(ya.reshape(n_img, c_out, m_batch), c_out, m_batch, n_img, True), yb)
+        assert a.last_bm_stats() == b.last_bm_stats() and a.last_bm_stats()[0] > 0
