@@ -241,3 +241,27 @@ def test_extra_state_round_trip_and_copy():
     assert t2.get_learning_rate() == pytest.approx(0.25)
     with pytest.raises(RuntimeError, match="is missing"):
         t2.load_extra({"learning_rate": [0.25]}, strict=True)
+
+
+def test_public_header_is_plain_c(tmp_path):
+    """The drop-in boundary is a C ABI: include/aihwkit_b200.h compiles as C99 with warnings on
+    (plain pointers and sizes, no C++ or torch types), and a C program links every struct."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "hdr.c"
+    src.write_text('#include "aihwkit_b200.h"\n'
+                   "int main(void) {\n"
+                   "  ab200_tile_config c; ab200_mixedprec_params m; ab200_scatter_plan p;\n"
+                   "  ab200_weight_modifier_params w; ab200_drift_params d;\n"
+                   "  (void)c; (void)m; (void)p; (void)w; (void)d;\n"
+                   "  return sizeof(ab200_io_params) == 0;\n"
+                   "}\n")
+    res = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I",
+                          os.path.join(root, "include"), "-c", str(src), "-o", str(tmp_path / "hdr.o")],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
