@@ -265,3 +265,57 @@ def test_public_header_is_plain_c(tmp_path):
                           os.path.join(root, "include"), "-c", str(src), "-o", str(tmp_path / "hdr.o")],
                          capture_output=True, text=True)
     assert res.returncode == 0, res.stderr
+
+
+def test_c_program_links_and_drives_the_library(tmp_path):
+    """A C program (no Python, no C++ runtime of its own) links libaihwkit_b200.so, fills a
+    configuration from the library's defaults, makes a host-side tile, sets and reads weights and
+    gets the library's refusal for a compute call without a device."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = os.path.join(root, "aihwkit_b200", "csrc")
+    _cabi.lib()  # makes sure the library is built
+    src = tmp_path / "main.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include <string.h>
+#include "aihwkit_b200.h"
+int main(void) {
+  ab200_tile_config cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  if (ab200_sizeof(4) != sizeof(cfg)) return 2;
+  cfg.x_size = 6; cfg.d_size = 4; cfg.seed = 7;
+  ab200_default_io_params(&cfg.forward_io);
+  ab200_default_io_params(&cfg.backward_io);
+  ab200_default_update_params(&cfg.update);
+  cfg.device_kind = AB200_DEVICE_CONSTANT_STEP;
+  ab200_default_device_params(&cfg.device[0], AB200_DEVICE_CONSTANT_STEP);
+  ab200_default_transfer_params(&cfg.transfer);
+  ab200_default_mixedprec_params(&cfg.mixed);
+  ab200_tile *t = 0;
+  if (ab200_tile_create(&cfg, -1, &t)) { printf("create: %s\n", ab200_last_error()); return 3; }
+  float w[24], r[24], x[6] = {0}, y[4];
+  for (int k = 0; k < 24; k++) w[k] = 0.01f * (float)(k - 12);
+  if (ab200_tile_set_weights(t, w) || ab200_tile_get_weights(t, r)) return 4;
+  for (int k = 0; k < 24; k++) if (r[k] != w[k]) return 5;
+  if (ab200_tile_get_x_size(t) != 6 || ab200_tile_hidden_parameter_count(t) <= 0) return 6;
+  int rc = ab200_tile_forward(t, x, y, 0, 1, 0, 0, 0, 0);   /* no device: must refuse, not compute */
+  printf("%s|%d|%s\n", ab200_version(), rc, ab200_last_error());
+  ab200_tile_destroy(t);
+  return rc != 0 ? 0 : 7;
+}
+''')
+    exe = tmp_path / "main"
+    res = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", os.path.join(root, "include"), str(src),
+                          "-o", str(exe), f"-L{libdir}", "-laihwkit_b200", f"-Wl,-rpath,{libdir}"],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
+    version, rc, msg = run.stdout.strip().split("|", 2)
+    assert version.startswith("aihwkit_b200") and int(rc) != 0 and "no CPU compute path" in msg
