@@ -319,3 +319,30 @@ int main(void) {
     assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
     version, rc, msg = run.stdout.strip().split("|", 2)
     assert version.startswith("aihwkit_b200") and int(rc) != 0 and "no CPU compute path" in msg
+
+
+def test_product_code_never_touches_the_checker():
+    """The oracle is test infrastructure: nothing under aihwkit_b200/ (Python or CUDA sources)
+    names the oracle package or the working folder, and bench.py reaches it only in its
+    CPU-baseline / reference-arm functions."""
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pat = re.compile(r"\b(from|import)\s+oracle\b|oracle/|_work/|\b_work\b")
+    for base, _, files in os.walk(os.path.join(root, "aihwkit_b200")):
+        if "build" in os.path.basename(base):
+            continue
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
+                text = open(os.path.join(base, f), encoding="utf-8").read()
+                assert not pat.search(text), os.path.join(base, f)
+    bench = open(os.path.join(root, "bench.py"), encoding="utf-8").read()
+    lines = bench.split("\n")
+    users = set()
+    for n, line in enumerate(lines):
+        if re.search(r"\b(from|import)\s+oracle\b", line):
+            k = n
+            while k >= 0 and not lines[k].lstrip().startswith("def "):
+                k -= 1
+            users.add(lines[k].strip().split("(")[0].replace("def ", ""))
+    assert users and all(("cpu" in u or "ref" in u) for u in users), users
